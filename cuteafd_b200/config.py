@@ -1,0 +1,162 @@
+"""Model geometry shared by the CPU oracle, the planner, the loader and the CUDA engine.
+
+One dataclass describes every decoder family the engine serves: GQA or MLA attention,
+dense or routed-MoE feed-forward layers, optional shared expert, optional multi-token
+prediction (MTP) layers and the optional sparse-attention "lightning indexer".  The
+reference keeps the same facts in ``ModelSpec/LayerSpec/AttentionKind/MoeSpec/
+SpeculatorSpec`` (rust/crates/cuteafd-loader/src/plan/spec.rs:7-190).
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+from dataclasses import dataclass, field
+from typing import Any
+
+
+@dataclass(frozen=True)
+class ModelConfig:
+    name: str = "tiny-moe"
+    family: str = "deepseek_v3"          # deepseek_v3 | deepseek_v32 | qwen3_moe | tiny_moe
+    vocab_size: int = 1024
+    num_layers: int = 2
+    hidden: int = 256
+    # attention
+    attention: str = "mla"               # "mla" | "gqa"
+    num_heads: int = 4
+    num_kv_heads: int = 4                # gqa only
+    head_dim: int = 64                   # gqa only
+    qk_norm: bool = False                # Qwen3: RMSNorm over head_dim on q and k
+    q_lora_rank: int = 128               # mla (0 = direct q projection)
+    kv_lora_rank: int = 64
+    qk_nope_dim: int = 32
+    qk_rope_dim: int = 32
+    v_head_dim: int = 32
+    rope_theta: float = 10000.0
+    rope_interleaved: bool = True        # pairs (2i, 2i+1); False = rotate-half (neox)
+    rms_eps: float = 1e-6
+    # feed forward
+    dense_ffn: int = 512                 # intermediate size of the dense SwiGLU layers
+    first_dense_layers: int = 1          # layers [0, first_dense_layers) are dense
+    num_experts: int = 8
+    expert_ffn: int = 128
+    top_k: int = 2
+    scoring: str = "softmax"             # "softmax" | "sigmoid"
+    num_groups: int = 1                  # group-limited routing (DeepSeek-V3: 8)
+    topk_groups: int = 1                 # groups kept (DeepSeek-V3: 4)
+    num_shared_experts: int = 1
+    routed_scale: float = 1.0
+    norm_topk_prob: bool = True
+    router_bias: bool = False            # selection-only correction bias
+    # speculation / sparse attention
+    mtp_layers: int = 0
+    indexer_heads: int = 0               # 0 = dense attention
+    indexer_dim: int = 128
+    indexer_topk: int = 2048
+    # storage
+    weight_format: str = "bf16"          # bf16 | fp8_block128 | nvfp4 | mxfp4 | exl3
+    tie_embeddings: bool = False
+
+    # ---- derived -----------------------------------------------------------------
+    @property
+    def is_mla(self) -> bool:
+        return self.attention == "mla"
+
+    @property
+    def qk_head_dim(self) -> int:
+        return self.qk_nope_dim + self.qk_rope_dim if self.is_mla else self.head_dim
+
+    @property
+    def kv_record_elems(self) -> int:
+        """Elements cached per token per layer (latent+rope for MLA, K and V for GQA)."""
+        if self.is_mla:
+            return self.kv_lora_rank + self.qk_rope_dim
+        return 2 * self.num_kv_heads * self.head_dim
+
+    def is_moe_layer(self, layer: int) -> bool:
+        return self.num_experts > 0 and layer >= self.first_dense_layers
+
+    def attention_params(self) -> int:
+        h = self.hidden
+        if self.is_mla:
+            q = (h * self.q_lora_rank + self.q_lora_rank * self.num_heads * self.qk_head_dim
+                 if self.q_lora_rank else h * self.num_heads * self.qk_head_dim)
+            kv = h * (self.kv_lora_rank + self.qk_rope_dim)
+            kvb = self.kv_lora_rank * self.num_heads * (self.qk_nope_dim + self.v_head_dim)
+            o = self.num_heads * self.v_head_dim * h
+            return q + kv + kvb + o
+        return h * (self.num_heads + 2 * self.num_kv_heads) * self.head_dim + self.num_heads * self.head_dim * h
+
+    def expert_params(self) -> int:
+        return 3 * self.hidden * self.expert_ffn
+
+    def layer_params(self, layer: int) -> int:
+        p = self.attention_params() + 2 * self.hidden
+        if self.is_moe_layer(layer):
+            p += self.num_experts * self.expert_params() + self.hidden * self.num_experts
+            p += self.num_shared_experts * self.expert_params()
+        else:
+            p += 3 * self.hidden * self.dense_ffn
+        return p
+
+    def total_params(self) -> int:
+        p = self.vocab_size * self.hidden * (1 if self.tie_embeddings else 2) + self.hidden
+        return p + sum(self.layer_params(i) for i in range(self.num_layers))
+
+    def to_json(self) -> str:
+        return json.dumps(dataclasses.asdict(self), indent=1, sort_keys=True)
+
+    @staticmethod
+    def from_dict(d: dict[str, Any]) -> "ModelConfig":
+        names = {f.name for f in dataclasses.fields(ModelConfig)}
+        return ModelConfig(**{k: v for k, v in d.items() if k in names})
+
+    def replace(self, **kw: Any) -> "ModelConfig":
+        return dataclasses.replace(self, **kw)
+
+
+def tiny_moe() -> ModelConfig:
+    """The CPU correctness config: 2 layers, MLA, layer 0 dense, layer 1 MoE 8x top-2 + shared."""
+    return ModelConfig()
+
+
+def qwen3_30b_a3b() -> ModelConfig:
+    """Qwen3-30B-A3B geometry (48 layers, GQA 32/4, 128 experts top-8, no shared expert)."""
+    return ModelConfig(
+        name="qwen3-30b-a3b", family="qwen3_moe", vocab_size=151936, num_layers=48, hidden=2048,
+        attention="gqa", num_heads=32, num_kv_heads=4, head_dim=128, qk_norm=True,
+        rope_theta=1.0e6, rope_interleaved=False, rms_eps=1e-6,
+        dense_ffn=6144, first_dense_layers=0, num_experts=128, expert_ffn=768, top_k=8,
+        scoring="softmax", num_shared_experts=0, norm_topk_prob=True, weight_format="bf16")
+
+
+def deepseek_v3() -> ModelConfig:
+    """DeepSeek-V3 geometry (61 layers, MLA 128 heads, 256 experts sigmoid group-limited top-8)."""
+    return ModelConfig(
+        name="deepseek-v3", family="deepseek_v3", vocab_size=129280, num_layers=61, hidden=7168,
+        attention="mla", num_heads=128, q_lora_rank=1536, kv_lora_rank=512, qk_nope_dim=128,
+        qk_rope_dim=64, v_head_dim=128, rope_theta=10000.0, rope_interleaved=True, rms_eps=1e-6,
+        dense_ffn=18432, first_dense_layers=3, num_experts=256, expert_ffn=2048, top_k=8,
+        scoring="sigmoid", num_groups=8, topk_groups=4, num_shared_experts=1, routed_scale=2.5,
+        norm_topk_prob=True, router_bias=True, mtp_layers=1, weight_format="fp8_block128")
+
+
+def deepseek_v32() -> ModelConfig:
+    """DeepSeek-V3.2 geometry: V3 plus the lightning indexer and NVFP4 routed experts."""
+    return deepseek_v3().replace(name="deepseek-v3.2", family="deepseek_v32", indexer_heads=64,
+                                 indexer_dim=128, indexer_topk=2048, weight_format="nvfp4")
+
+
+PRESETS = {
+    "tiny-moe": tiny_moe,
+    "qwen3-30b-a3b": qwen3_30b_a3b,
+    "deepseek-v3": deepseek_v3,
+    "deepseek-v3.2": deepseek_v32,
+}
+
+
+def scaled_down(cfg: ModelConfig, layers: int = 2, vocab: int = 2048) -> ModelConfig:
+    """Same per-layer geometry with fewer layers and a small vocabulary (tests, smoke)."""
+    first_dense = min(cfg.first_dense_layers, max(layers - 1, 0)) if cfg.first_dense_layers else 0
+    return cfg.replace(name=cfg.name + "-mini", num_layers=layers, vocab_size=vocab,
+                       first_dense_layers=first_dense)

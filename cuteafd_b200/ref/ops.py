@@ -1,0 +1,151 @@
+"""Plain PyTorch fp32 restatements of every hot op: the oracle for the CUDA kernels.
+
+Behaviour follows the reference's tiny readable references
+(python/reference/cuteafd_reference/{rmsnorm,rope,router,moe,attention}_ref.py) and, where
+those are silent, the contracts of its CUDA kernels: router bias is used for selection only and
+ties go to the lowest expert id (native/shared/cuda/expert_router.cu:12-55); the MoE combine sums
+routes in slot order in fp32 and rounds once (native/shared/cuda/route_reduce.cu:103-122).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
+    return (y * weight.float()).to(x.dtype)
+
+
+def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6):
+    """residual' = residual + x (rounded to the storage dtype), y = rmsnorm(residual')."""
+    r = (residual.float() + x.float()).to(residual.dtype)
+    return rmsnorm(r, weight, eps), r
+
+
+def rope_angles(dim: int, positions: torch.Tensor, theta: float) -> torch.Tensor:
+    inv = 1.0 / (theta ** (torch.arange(0, dim, 2, device=positions.device).float() / dim))
+    return torch.outer(positions.float(), inv)            # [T, dim/2]
+
+
+def apply_rope(x: torch.Tensor, positions: torch.Tensor, theta: float = 10000.0,
+               interleaved: bool = True) -> torch.Tensor:
+    """x: [T, heads, dim].  interleaved rotates pairs (2i, 2i+1); otherwise (i, i+dim/2)."""
+    dim = x.shape[-1]
+    ang = rope_angles(dim, positions, theta)
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    xf = x.float()
+    if interleaved:
+        a, b = xf[..., 0::2], xf[..., 1::2]
+        out = torch.empty_like(xf)
+        out[..., 0::2] = a * cos - b * sin
+        out[..., 1::2] = a * sin + b * cos
+    else:
+        a, b = xf[..., : dim // 2], xf[..., dim // 2:]
+        out = torch.cat([a * cos - b * sin, a * sin + b * cos], dim=-1)
+    return out.to(x.dtype)
+
+
+def route_topk(logits: torch.Tensor, top_k: int, scoring: str = "softmax", bias: torch.Tensor | None = None,
+               num_groups: int = 1, topk_groups: int = 1, normalize: bool = True,
+               routed_scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Router selection.  Returns (indices int32 [T,k], weights fp32 [T,k]).
+
+    softmax: full-denominator softmax, top-k by probability, optional renormalisation.
+    sigmoid: scores = sigmoid(logits); selection on scores+bias; group-limited routing keeps the
+    ``topk_groups`` groups whose top-2 (biased) scores sum highest; weights are the unbiased
+    scores, normalised with +1e-20 and scaled.  Ties resolve to the lowest expert id.
+    """
+    lf = logits.float()
+    T, E = lf.shape
+    scores = torch.softmax(lf, dim=-1) if scoring == "softmax" else torch.sigmoid(lf)
+    sel = scores + bias.float() if bias is not None else scores.clone()
+    if num_groups > 1:
+        g = sel.view(T, num_groups, E // num_groups)
+        gscore = g.topk(2, dim=-1).values.sum(-1)                      # [T, G]
+        keep = _stable_topk(gscore, topk_groups)[1]
+        mask = torch.zeros(T, num_groups, dtype=torch.bool, device=lf.device)
+        mask.scatter_(1, keep, True)
+        sel = sel.masked_fill(~mask[:, :, None].expand_as(g).reshape(T, E), float("-inf"))
+    idx = _stable_topk(sel, top_k)[1]
+    w = scores.gather(1, idx)
+    if normalize:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return idx.to(torch.int32), (w * routed_scale).float()
+
+
+def _stable_topk(x: torch.Tensor, k: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """top-k, value descending, ties to the lowest index (torch.topk leaves tie order open)."""
+    order = torch.sort(x, dim=-1, descending=True, stable=True)
+    return order.values[..., :k], order.indices[..., :k]
+
+
+def swiglu_mlp(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
+    xf = x.float()
+    h = F.silu(xf @ gate.float().T) * (xf @ up.float().T)
+    return h.to(x.dtype).float() @ down.float().T           # intermediate rounded like the kernels do
+
+
+def moe_forward(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate: torch.Tensor, up: torch.Tensor,
+                down: torch.Tensor, expert_base: int = 0) -> torch.Tensor:
+    """Routed experts for the experts held locally: gate/up [E_local, I, H], down [E_local, H, I].
+
+    Returns fp32 [T, k, H]: per-(token, slot) weighted contribution, zero where the slot's expert
+    is not local.  The caller sums the slots in slot order.
+    """
+    T, k = idx.shape
+    out = torch.zeros(T, k, x.shape[-1], dtype=torch.float32, device=x.device)
+    e_local = gate.shape[0]
+    for e in range(e_local):
+        hit = (idx == e + expert_base)
+        if not hit.any():
+            continue
+        rows, slots = hit.nonzero(as_tuple=True)
+        y = swiglu_mlp(x[rows], gate[e], up[e], down[e])
+        out[rows, slots] = y.to(x.dtype).float() * w[rows, slots][:, None]
+    return out
+
+
+def combine_slots(parts: torch.Tensor, shared: torch.Tensor | None, residual: torch.Tensor | None,
+                  dtype: torch.dtype) -> torch.Tensor:
+    """Ordered fp32 sum over slots, then the shared expert, then the residual; one rounding."""
+    acc = torch.zeros_like(parts[:, 0])
+    for s in range(parts.shape[1]):
+        acc = acc + parts[:, s]
+    if shared is not None:
+        acc = acc + shared.float()
+    if residual is not None:
+        acc = acc + residual.float()
+    return acc.to(dtype)
+
+
+def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_start: int, scale: float | None = None
+                     ) -> torch.Tensor:
+    """q [Tq, Hq, D], k [Tk, Hk, D], v [Tk, Hk, Dv]; query row i sits at position q_start+i."""
+    Tq, Hq, D = q.shape
+    Tk, Hk, _ = k.shape
+    rep = Hq // Hk
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    kf = k.float().repeat_interleave(rep, dim=1)
+    vf = v.float().repeat_interleave(rep, dim=1)
+    s = torch.einsum("qhd,khd->hqk", q.float(), kf) * scale
+    qpos = torch.arange(Tq, device=q.device)[:, None] + q_start
+    kpos = torch.arange(Tk, device=q.device)[None, :]
+    s = s.masked_fill((kpos > qpos)[None], float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return torch.einsum("hqk,khd->qhd", p, vf).to(q.dtype)
+
+
+def greedy_verify(target_logits: torch.Tensor, draft: torch.Tensor) -> tuple[int, int]:
+    """Sample-match verification for greedy rows: accepted prefix length and the bonus token
+    (python/reference/cuteafd_reference/mtp_protocol_ref.py:6-15)."""
+    pred = target_logits.argmax(-1).tolist()
+    n = 0
+    for p, d in zip(pred, draft.tolist()):
+        if p != d:
+            break
+        n += 1
+    return n, pred[n]
