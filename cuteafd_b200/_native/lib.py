@@ -1,0 +1,105 @@
+"""ctypes bindings of libcuteafd_b200.so (CUDA kernels) and libcuteafd_rt.so (host runtime)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+from . import build
+
+_lock = threading.Lock()
+_cuda = None
+_rt = None
+
+c_void_p, c_int, c_float, c_u32p = C.c_void_p, C.c_int, C.c_float, C.c_void_p
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("w0", C.c_void_p), ("w1", C.c_void_p), ("x", C.c_void_p), ("out", C.c_void_p),
+        ("residual", C.c_void_p), ("row_scale", C.c_void_p), ("row_dst", C.c_void_p),
+        ("tile_expert", C.c_void_p), ("tile_row0", C.c_void_p), ("num_x_tiles", C.c_void_p),
+        ("w_scale", C.c_void_p), ("x_scale", C.c_void_p),
+        ("wait_flag", C.c_void_p), ("epoch", C.c_void_p), ("done_counter", C.c_void_p),
+        ("signal_flag", C.c_void_p), ("status", C.c_void_p),
+        ("w_rows_total", C.c_longlong), ("x_rows_total", C.c_longlong),
+        ("k", C.c_int), ("n_features", C.c_int), ("x_rows", C.c_int), ("ldo", C.c_int),
+        ("w_rows_per_expert", C.c_int), ("w1_row_offset", C.c_int), ("max_x_tiles", C.c_int),
+        ("swap", C.c_int), ("dual", C.c_int), ("bx", C.c_int), ("out_f32", C.c_int), ("fp8", C.c_int),
+        ("num_sms", C.c_int),
+    ]
+
+
+MAX_RANKS = 8
+
+
+class MoeLayout(C.Structure):
+    _fields_ = [
+        ("n_ranks", C.c_int), ("expert_lo", C.c_int * (MAX_RANKS + 1)),
+        ("slab", C.c_void_p * MAX_RANKS), ("meta", C.c_void_p * MAX_RANKS), ("flag", C.c_void_p * MAX_RANKS),
+        ("max_tiles", C.c_int), ("max_rows", C.c_int),
+    ]
+
+
+def _sig(lib, name, argtypes, restype=C.c_int):
+    fn = getattr(lib, name)
+    fn.argtypes = argtypes
+    fn.restype = restype
+    return fn
+
+
+def cuda_lib():
+    """Load (building first when the shared object is absent) the CUDA kernel library."""
+    global _cuda
+    with _lock:
+        if _cuda is not None:
+            return _cuda
+        path = build.CUDA_LIB
+        if not os.path.exists(path):
+            build.build_cuda()
+        lib = C.CDLL(path)
+        P, I, F = C.c_void_p, C.c_int, C.c_float
+        _sig(lib, "cafd_gemm", [C.POINTER(GemmArgs), P])
+        for n in ("cafd_gemm_set_wait_limit_ns", "cafd_moe_set_wait_limit_ns", "cafd_attn_set_wait_limit_ns"):
+            _sig(lib, n, [C.c_ulonglong])
+        _sig(lib, "cafd_embed", [P, P, P, I, I, I, P])
+        _sig(lib, "cafd_rmsnorm", [P, P, P, P, I, I, F, P])
+        _sig(lib, "cafd_qk_rope_kv", [P, P, P, P, P, P, P, P, P, I, I, I, I, F, I, P])
+        _sig(lib, "cafd_argmax", [P, P, I, I, I, P])
+        _sig(lib, "cafd_bump_epoch", [P, P])
+        _sig(lib, "cafd_route_topk", [P, P, P, P, I, I, I, I, I, I, I, F, P])
+        _sig(lib, "cafd_moe_meta_ints", [I, I])
+        _sig(lib, "cafd_moe_plan", [P, I, I, I, I, C.POINTER(MoeLayout), P, P, P, P])
+        _sig(lib, "cafd_moe_dispatch", [P, P, P, I, I, I, C.POINTER(MoeLayout), P, P, P])
+        _sig(lib, "cafd_moe_combine", [P, P, P, P, P, I, I, I, P, I, P, P, P])
+        _sig(lib, "cafd_attn_decode_scratch_floats", [I, I, I, I], C.c_longlong)
+        _sig(lib, "cafd_attn_decode", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
+        _sig(lib, "cafd_attn_prefill", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
+        _cuda = lib
+        return lib
+
+
+def rt_lib():
+    """Load the host runtime library (C++; no CUDA needed)."""
+    global _rt
+    with _lock:
+        if _rt is not None:
+            return _rt
+        path = build.RT_LIB
+        if not os.path.exists(path):
+            build.build_rt()
+        _rt = C.CDLL(path)
+        return _rt
+
+
+def loaded_libraries() -> list[str]:
+    return [p for p, l in ((build.CUDA_LIB, _cuda), (build.RT_LIB, _rt)) if l is not None]
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise NativeError(f"{what} failed with code {rc}")

@@ -1,0 +1,330 @@
+// Causal GQA prefill attention over the paged KV cache on tcgen05 tensor cores (head_dim 128).
+//
+// One CTA computes a 128-row query tile of one head.  S = Q K^T and O += P V both run as
+// tcgen05.mma with accumulators in TMEM; K/V pages arrive by TMA straight from the page pool
+// (a 4-D tensor map indexed by page id), so chunked prefill and prefix-cache hits need no
+// gather.  Warp roles:
+//   warp 0     TMA producer: Q tile once, then K and V tiles (two stages each)
+//   warp 1     MMA issuer: QK^T for tile j+1 is issued before P V of tile j, so the tensor pipe
+//              works on the next scores while the softmax warps are busy
+//   warps 2-5  online softmax: thread = query row (its TMEM lane); S is read with tcgen05.ld,
+//              P is written as bf16 into 128B-swizzled shared memory (the A operand of P V),
+//              O is rescaled in TMEM only when the running maximum moved
+// TMEM: S double-buffered (2 x 128 columns) + O (128 columns).
+//
+// Replaces the reference's mma.sync prefill kernels (native/families/glm5/cuda/glm_mla_prefill.cu:78-135)
+// and its exported attention programs for the GQA families.
+#include "cafd_api.h"
+#include "common.cuh"
+#include "host_tma.h"
+
+namespace cafd {
+
+constexpr int kHD = 128;          // head dim
+constexpr int kBQ = 128;          // query rows per CTA
+constexpr int kBKV = 128;         // kv tokens per tile (two 64-token pages)
+constexpr int kPageTok = 64;
+constexpr int kHalfBytes = 128 * 128;   // 128 rows x 64 bf16 (one swizzle atom wide) = 16 KiB
+constexpr int kTileB = 2 * kHalfBytes;  // 32 KiB: a [128 x 128] bf16 tile as two 64-wide halves
+constexpr int kPrefillThreads = 192;
+constexpr int kPrefillSmem = 6 * kTileB + 1024;   // Q, K x2, V x2, P
+
+struct PrefillDev {
+  const int* page_table;   // [seqs, max_pages]
+  const int* seq_lens;     // kv length per sequence (including this chunk)
+  const int* q_start;      // [seqs + 1] row offsets into q/out
+  __nv_bfloat16* out;      // [total_q, Hq, 128]
+  uint32_t* status;
+  int max_pages;
+  int Hq, Hkv;
+  float scale_log2;
+};
+
+__global__ void __launch_bounds__(kPrefillThreads, 1)
+attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_v, const PrefillDev p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + kTileB;          // 2 stages
+  uint8_t* sV = smem + 3 * kTileB;      // 2 stages
+  uint8_t* sP = smem + 5 * kTileB;
+
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_ready, pv_done;
+  __shared__ uint32_t tmem_slot;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq = blockIdx.z;
+  const int head = blockIdx.y;
+  const int kvh = head / (p.Hq / p.Hkv);
+  const int q0 = p.q_start[seq];
+  const int q_len = p.q_start[seq + 1] - q0;
+  const int kv_len = p.seq_lens[seq];
+  const int n_qt = (q_len + kBQ - 1) / kBQ;
+  const int qt = n_qt - 1 - static_cast<int>(blockIdx.x);   // heaviest tiles first
+  if (qt < 0) return;
+  const int row0 = qt * kBQ;                       // first query row of this tile (within the chunk)
+  const int pos0 = kv_len - q_len + row0;          // its absolute position
+  const int last_pos = min(pos0 + kBQ - 1, kv_len - 1);
+  const int n_tiles = last_pos / kBKV + 1;
+  const int seq_pages = (kv_len + kPageTok - 1) / kPageTok;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128);
+    }
+    mbar_init(&p_ready, 128);
+    mbar_init(&pv_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t tS = tmem;            // + 128 * buffer
+  const uint32_t tO = tmem + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+      mbar_expect_tx(&q_full, kTileB);
+      tma_load_2d(sQ, &tm_q, &q_full, head * kHD, q0 + row0);
+      tma_load_2d(sQ + kHalfBytes, &tm_q, &q_full, head * kHD + 64, q0 + row0);
+      const int* pt = p.page_table + static_cast<size_t>(seq) * p.max_pages;
+      bool ok = true;
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int pa = 2 * j < seq_pages ? pt[2 * j] : 0;          // page 0 is the all-zero page
+        const int pb = 2 * j + 1 < seq_pages ? pt[2 * j + 1] : 0;
+        if (!mbar_wait(&k_empty[st], ph ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
+        uint8_t* kd = sK + st * kTileB;
+        mbar_expect_tx(&k_full[st], kTileB);
+        tma_load_4d(kd, &tm_k, &k_full[st], 0, kvh, 0, pa);
+        tma_load_4d(kd + 64 * 128, &tm_k, &k_full[st], 0, kvh, 0, pb);
+        tma_load_4d(kd + kHalfBytes, &tm_k, &k_full[st], 64, kvh, 0, pa);
+        tma_load_4d(kd + kHalfBytes + 64 * 128, &tm_k, &k_full[st], 64, kvh, 0, pb);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
+        uint8_t* vd = sV + st * kTileB;
+        mbar_expect_tx(&v_full[st], kTileB);
+        tma_load_4d(vd, &tm_v, &v_full[st], 0, kvh, 0, pa);
+        tma_load_4d(vd + 64 * 128, &tm_v, &v_full[st], 0, kvh, 0, pb);
+        tma_load_4d(vd + kHalfBytes, &tm_v, &v_full[st], 64, kvh, 0, pa);
+        tma_load_4d(vd + kHalfBytes + 64 * 128, &tm_v, &v_full[st], 64, kvh, 0, pb);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc(128, 128, 1, 1, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc(128, 128, 1, 1, 0, 1);   // B = V is MN-major
+      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+      bool ok = mbar_wait(&q_full, 0, p.status, kTimeoutFullBarrier);
+      auto issue_qk = [&](int j) -> bool {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_full[st], ph, p.status, kTimeoutFullBarrier)) return false;
+        if (!mbar_wait(&s_empty[st], ph ^ 1, p.status, kTimeoutTmemEmpty)) return false;
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + st * kTileB);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            umma_f16(tS + st * 128, smem_desc_k_sw128(aQ + h * kHalfBytes + k4 * 32),
+                     smem_desc_k_sw128(aK + h * kHalfBytes + k4 * 32), idesc_qk, (h | k4) ? 1u : 0u);
+        umma_commit(&k_empty[st]);
+        umma_commit(&s_full[st]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (j + 1 < n_tiles) { if (!issue_qk(j + 1)) { ok = false; break; } }
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&p_ready, j & 1, p.status, kTimeoutSoftmax)) { ok = false; break; }
+        if (!mbar_wait(&v_full[st], ph, p.status, kTimeoutFullBarrier)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aV = smem_u32(sV + st * kTileB);
+#pragma unroll
+        for (int k8 = 0; k8 < 8; ++k8) {
+          // A = P: atom (k8 / 4) of 64 kv columns, 32 bytes per K step inside it
+          // B = V: 16 kv rows per step (2 KiB), two 64-wide d halves 16 KiB apart
+          umma_f16(tO, smem_desc_k_sw128(aP + (k8 >> 2) * kHalfBytes + (k8 & 3) * 32),
+                   smem_desc_mn_sw128(aV + k8 * 2048, kHalfBytes), idesc_pv, (j | k8) ? 1u : 0u);
+        }
+        umma_commit(&v_empty[st]);
+        umma_commit(&pv_done);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;               // row within the tile = TMEM lane
+    const int rowpos = pos0 + row;
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; ok && j < n_tiles; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(&s_full[st], ph, p.status, kTimeoutTmemFull)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t tSj = tS + st * 128 + lane_off;
+      const bool need_mask = (j * kBKV + kBKV - 1) > pos0;
+      const int col_limit = rowpos - j * kBKV;      // columns <= col_limit are visible
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tSj + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = __uint_as_float(r[i]) * p.scale_log2;
+          if (need_mask && (c * 32 + i) > col_limit) v = -INFINITY;
+          mx = fmaxf(mx, v);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float base = (m_new == -INFINITY) ? 0.f : m_new;
+      const float corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - base);
+      // P buffer and O are free once P V of the previous tile has completed
+      if (j > 0) {
+        if (!mbar_wait(&pv_done, (j - 1) & 1, p.status, kTimeoutTmemFull)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tO + lane_off + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+            tmem_st_32x32(tO + lane_off + c * 32, r);
+          }
+        }
+      }
+      // pass 2: P = exp2(S - m) as bf16 into swizzled shared memory; running sum
+      float rs = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tSj + c * 32, r);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float v0 = __uint_as_float(r[i]) * p.scale_log2;
+          float v1 = __uint_as_float(r[i + 1]) * p.scale_log2;
+          if (need_mask) {
+            if ((c * 32 + i) > col_limit) v0 = -INFINITY;
+            if ((c * 32 + i + 1) > col_limit) v1 = -INFINITY;
+          }
+          const uint32_t w = pack_bf16(exp2f(v0 - base), exp2f(v1 - base));
+          rs += bf16_lo(w) + bf16_hi(w);
+          pk[i >> 1] = w;
+        }
+        // columns [32c, 32c+32) -> atom (c / 2), 16-byte chunks ((c & 1) * 4 + q), q = 0..3
+        uint8_t* prow = sP + (c >> 1) * kHalfBytes + row * 128;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = (c & 1) * 4 + q;
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) =
+              make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+        }
+      }
+      l_run = l_run * corr + rs;
+      m_run = m_new;
+      tmem_st_wait();
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&s_empty[st]);
+      mbar_arrive(&p_ready);
+    }
+    // ---- epilogue: O / l ---------------------------------------------------------------------------
+    if (ok && mbar_wait(&pv_done, (n_tiles - 1) & 1, p.status, kTimeoutTmemFull)) {
+      tc_fence_after();
+      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      const bool row_ok = (row0 + row) < q_len;
+      __nv_bfloat16* orow = p.out + (static_cast<size_t>(q0 + row0 + row) * p.Hq + head) * kHD;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tO + lane_off + c * 32, r);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 q;
+            q.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+            q.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+            q.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+            q.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + i) = q;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace cafd
+
+using namespace cafd;
+
+// q/out [total_q, Hq, 128] bf16; caches [num_pages, 64, Hkv, 128] bf16 (page 0 all zero);
+// page_table [num_seqs, max_pages]; seq_lens [num_seqs]; q_start [num_seqs + 1];
+// max_q_len = longest chunk (grid sizing).
+extern "C" int cafd_attn_prefill(const void* q, const void* k_cache, const void* v_cache, const int* page_table,
+                                 const int* seq_lens, const int* q_start, void* out, uint32_t* status, int total_q,
+                                 int num_seqs, int max_q_len, int num_pages, int max_pages, int Hq, int Hkv, int D,
+                                 float scale, cafd_stream_t s) {
+  if (num_seqs <= 0 || total_q <= 0) return 0;
+  if (D != kHD || Hq % Hkv) return -10;
+  CUtensorMap tq, tk, tv;
+  int rc = cached_tmap_2d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, total_q, static_cast<uint64_t>(Hq) * kHD,
+                          static_cast<uint64_t>(Hq) * kHD * 2, kBQ, 64);
+  if (rc) return rc;
+  const uint64_t dims[4] = {static_cast<uint64_t>(kHD), static_cast<uint64_t>(Hkv), kPageTok,
+                            static_cast<uint64_t>(num_pages)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(kHD) * 2, static_cast<uint64_t>(Hkv) * kHD * 2,
+                               static_cast<uint64_t>(kPageTok) * Hkv * kHD * 2};
+  const uint32_t box[4] = {64, 1, kPageTok, 1};
+  rc = make_tmap_nd(&tk, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dims, strides, box, true);
+  if (rc) return rc;
+  rc = make_tmap_nd(&tv, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dims, strides, box, true);
+  if (rc) return rc;
+  PrefillDev p;
+  p.page_table = page_table;
+  p.seq_lens = seq_lens;
+  p.q_start = q_start;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.status = status;
+  p.max_pages = max_pages;
+  p.Hq = Hq;
+  p.Hkv = Hkv;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  static bool attr = false;
+  if (!attr) {
+    CAFD_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem));
+    attr = true;
+  }
+  dim3 grid((max_q_len + kBQ - 1) / kBQ, Hq, num_seqs);
+  attn_prefill_kernel<<<grid, kPrefillThreads, kPrefillSmem, static_cast<cudaStream_t>(s)>>>(tq, tk, tv, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+CAFD_WAIT_LIMIT_SETTER(cafd_attn_set_wait_limit_ns)

@@ -1,0 +1,67 @@
+// C ABI of libcuteafd_b200.so.  Every entry point takes device pointers plus a CUDA stream and
+// returns 0 on success, a positive cudaError_t, or a negative library code.  No entry point
+// allocates device memory: callers own every buffer, including scratch.
+//
+// The reference exposes its native layer the same way, as a dlopen'ed C ABI
+// (native/shared/include/cuteafd_native.h, cuteafd_experts.h, cuteafd_fp8_moe.h:14-76).
+#pragma once
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* cafd_stream_t;
+
+// ---- tcgen05 GEMM family ------------------------------------------------------------------------
+// D = W-side x X-side over K.  "W" is a weight matrix [w_rows_total, K] (experts stacked along
+// rows), "X" an activation matrix [x_rows_total, K]; both row-major bf16 (or e4m3 when fp8 != 0).
+//   swap == 0: token rows on the MMA M side (tile 128), features on N.   Prefill shapes.
+//   swap == 1: feature rows on the MMA M side (tile 128), tokens on N (tile bx = 16..128).  Decode.
+//   dual == 1: two weight tiles (gate, up) per stage and a SwiGLU epilogue: out = silu(g) * u.
+// Grouped mode (tile_expert != NULL): X is an expert-sorted slab whose segments are padded to the
+// token tile; tile t covers rows [tile_row0[t], +tile) of expert tile_expert[t]; *num_x_tiles
+// tiles exist.  Output row r goes to out[row_dst ? row_dst[r] : r] (negative = skip), scaled by
+// row_scale[r] when given.  `out` may point into another GPU's memory (peer mapping).
+typedef struct {
+  const void* w0;            // weights (gate in dual mode)
+  const void* w1;            // up weights in dual mode (may equal w0 with w1_row_offset)
+  const void* x;             // activations
+  void* out;                 // bf16 (or fp32 when out_f32) [*, ldo]
+  const void* residual;      // optional bf16 [*, ldo] added before rounding (same row mapping as out)
+  const float* row_scale;    // optional per X-row multiplier
+  const int* row_dst;        // optional per X-row destination row (-1 = drop)
+  const int* tile_expert;    // grouped: expert of each X tile
+  const int* tile_row0;      // grouped: first X row of each X tile
+  const int* num_x_tiles;    // grouped: device count of X tiles
+  const float* w_scale;      // fp8: weight block scales [w_rows_total/128, K/128]
+  const float* x_scale;      // fp8: activation scales [x_rows_total, K/128]
+  const uint32_t* wait_flag; // optional: wait until *wait_flag >= *epoch before reading anything
+  const uint32_t* epoch;     // device word holding the current step number
+  uint32_t* done_counter;    // local counter used to elect the last CTA (must start at 0)
+  uint32_t* signal_flag;     // optional: set to *epoch (release, system scope) when all stores are done
+  uint32_t* status;          // device status word (0 = ok)
+  long long w_rows_total;
+  long long x_rows_total;
+  int k;
+  int n_features;            // features per expert (rows of W used per expert)
+  int x_rows;                // dense: valid X rows
+  int ldo;
+  int w_rows_per_expert;     // row stride between experts in W
+  int w1_row_offset;         // row offset of the up weights relative to w1's base
+  int max_x_tiles;           // grouped: upper bound of *num_x_tiles (grid sizing)
+  int swap;
+  int dual;
+  int bx;                    // token tile when swap == 1
+  int out_f32;
+  int fp8;
+  int num_sms;               // 0 = query
+} cafd_gemm_args;
+
+int cafd_gemm(const cafd_gemm_args* a, cafd_stream_t stream);
+int cafd_gemm_set_wait_limit_ns(unsigned long long ns);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,253 @@
+// Memory-bound glue kernels: embedding gather, RMSNorm (+ residual add), per-head q/k norm +
+// RoPE + paged KV write, greedy selection.  Each is a single pass over its rows with 16-byte
+// accesses; the roofline for all of them is HBM bandwidth.
+//
+// Reference counterparts: native/shared/cuda/norm.cu:5-84 (rmsnorm), attention.cu:88-135 (rope),
+// kv_cache.cu:48-82 (paged writes), embedding.cu / token_io.cu:21-110 (gather, greedy select with
+// ties to the lowest id and NaN never selected).
+#include "cafd_api.h"
+#include "common.cuh"
+
+namespace cafd {
+
+// ---- embedding gather: bit-identical row copy ---------------------------------------------------
+__global__ void embed_kernel(const int* __restrict__ tokens, const uint4* __restrict__ table, uint4* __restrict__ out,
+                             int T, int row_vec, int vocab) {
+  const int t = blockIdx.x;
+  if (t >= T) return;
+  int tok = tokens[t];
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+  const uint4* src = table + static_cast<size_t>(tok) * row_vec;
+  uint4* dst = out + static_cast<size_t>(t) * row_vec;
+  for (int i = threadIdx.x; i < row_vec; i += blockDim.x) dst[i] = src[i];
+}
+
+// ---- RMSNorm, optional residual add ---------------------------------------------------------------
+// residual' = residual + x (rounded to bf16, written back), y = rmsnorm(residual') * w.
+// With x == nullptr: y = rmsnorm(residual) * w and the residual is left untouched.
+template <int kVecPerThread>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const uint4* __restrict__ x, uint4* __restrict__ residual,
+                                                      const uint4* __restrict__ w, uint4* __restrict__ y, int T,
+                                                      int H, float eps) {
+  const int t = blockIdx.x;
+  if (t >= T) return;
+  const int nvec = H / 8;
+  float v[kVecPerThread][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kVecPerThread; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < nvec) {
+      uint4 r = residual[static_cast<size_t>(t) * nvec + c];
+      const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+      if (x) {
+        uint4 a = x[static_cast<size_t>(t) * nvec + c];
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          ow[e] = pack_bf16(bf16_lo(rw[e]) + bf16_lo(aw[e]), bf16_hi(rw[e]) + bf16_hi(aw[e]));
+          v[i][2 * e] = bf16_lo(ow[e]);
+          v[i][2 * e + 1] = bf16_hi(ow[e]);
+        }
+        residual[static_cast<size_t>(t) * nvec + c] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          v[i][2 * e] = bf16_lo(rw[e]);
+          v[i][2 * e + 1] = bf16_hi(rw[e]);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+    }
+  }
+  __shared__ float red[8];
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < static_cast<int>(blockDim.x >> 5); ++i) tot += red[i];
+  const float inv = rsqrtf(tot / static_cast<float>(H) + eps);
+#pragma unroll
+  for (int i = 0; i < kVecPerThread; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < nvec) {
+      uint4 ww = w[c];
+      const uint32_t wv[4] = {ww.x, ww.y, ww.z, ww.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        o[e] = pack_bf16(v[i][2 * e] * inv * bf16_lo(wv[e]), v[i][2 * e + 1] * inv * bf16_hi(wv[e]));
+      y[static_cast<size_t>(t) * nvec + c] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+// ---- q/k head norm + RoPE + paged KV write (GQA) ----------------------------------------------------
+// qkv [T, (Hq + 2 Hkv) * D] from the fused projection.  One warp per (token, head).  D == 128.
+// q_out [T, Hq, D]; K/V pages [num_pages, page, Hkv, D]; slot[t] = page * page_size + offset.
+// Rounding points follow the oracle: norm -> bf16 -> rope (fp32) -> bf16.
+__global__ void __launch_bounds__(128) qk_rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv,
+                                                         const __nv_bfloat16* __restrict__ q_norm_w,
+                                                         const __nv_bfloat16* __restrict__ k_norm_w,
+                                                         const float* __restrict__ inv_freq,
+                                                         const int* __restrict__ positions,
+                                                         const int* __restrict__ slots, __nv_bfloat16* __restrict__ q_out,
+                                                         __nv_bfloat16* __restrict__ k_cache,
+                                                         __nv_bfloat16* __restrict__ v_cache, int T, int Hq, int Hkv,
+                                                         float eps, int interleaved) {
+  constexpr int D = 128;
+  const int heads = Hq + 2 * Hkv;
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (gw >= T * heads) return;
+  const int t = gw / heads;
+  const int h = gw % heads;
+  const int lane = threadIdx.x & 31;
+  const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * heads * D + h * D;
+  // lane holds elements {2l, 2l+1} and {64+2l, 64+2l+1}
+  const uint32_t a = *reinterpret_cast<const uint32_t*>(src + 2 * lane);
+  const uint32_t b = *reinterpret_cast<const uint32_t*>(src + 64 + 2 * lane);
+  float x0 = bf16_lo(a), x1 = bf16_hi(a), x2 = bf16_lo(b), x3 = bf16_hi(b);
+  const int slot = slots[t];
+  if (h >= Hq + Hkv) {  // V: plain copy into the cache
+    if (slot >= 0) {
+      __nv_bfloat16* dst = v_cache + (static_cast<size_t>(slot) * Hkv + (h - Hq - Hkv)) * D;
+      *reinterpret_cast<uint32_t*>(dst + 2 * lane) = a;
+      *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = b;
+    }
+    return;
+  }
+  const bool is_q = h < Hq;
+  const __nv_bfloat16* nw = is_q ? q_norm_w : k_norm_w;
+  if (nw) {
+    const float ss = warp_sum(x0 * x0 + x1 * x1 + x2 * x2 + x3 * x3);
+    const float inv = rsqrtf(ss / static_cast<float>(D) + eps);
+    const uint32_t wa = *reinterpret_cast<const uint32_t*>(nw + 2 * lane);
+    const uint32_t wb = *reinterpret_cast<const uint32_t*>(nw + 64 + 2 * lane);
+    const uint32_t ra = pack_bf16(x0 * inv * bf16_lo(wa), x1 * inv * bf16_hi(wa));
+    const uint32_t rb = pack_bf16(x2 * inv * bf16_lo(wb), x3 * inv * bf16_hi(wb));
+    x0 = bf16_lo(ra); x1 = bf16_hi(ra); x2 = bf16_lo(rb); x3 = bf16_hi(rb);
+  }
+  const float pos = static_cast<float>(positions[t]);
+  float y0, y1, y2, y3;
+  if (interleaved) {
+    // pairs (2i, 2i+1): frequency index i; this lane holds pair l and pair 32+l
+    float s0, c0, s1, c1;
+    sincosf(pos * inv_freq[lane], &s0, &c0);
+    sincosf(pos * inv_freq[32 + lane], &s1, &c1);
+    y0 = x0 * c0 - x1 * s0; y1 = x0 * s0 + x1 * c0;
+    y2 = x2 * c1 - x3 * s1; y3 = x2 * s1 + x3 * c1;
+  } else {
+    // pairs (i, i+64): this lane holds i = 2l and i = 2l+1
+    float s0, c0, s1, c1;
+    sincosf(pos * inv_freq[2 * lane], &s0, &c0);
+    sincosf(pos * inv_freq[2 * lane + 1], &s1, &c1);
+    y0 = x0 * c0 - x2 * s0; y2 = x0 * s0 + x2 * c0;
+    y1 = x1 * c1 - x3 * s1; y3 = x1 * s1 + x3 * c1;
+  }
+  const uint32_t oa = pack_bf16(y0, y1), ob = pack_bf16(y2, y3);
+  __nv_bfloat16* dst;
+  if (is_q) {
+    dst = q_out + (static_cast<size_t>(t) * Hq + h) * D;
+  } else {
+    if (slot < 0) return;
+    dst = k_cache + (static_cast<size_t>(slot) * Hkv + (h - Hq)) * D;
+  }
+  *reinterpret_cast<uint32_t*>(dst + 2 * lane) = oa;
+  *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = ob;
+}
+
+// ---- greedy selection: argmax, ties to the lowest id, NaN never wins ----------------------------
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int T,
+                                                      int V, int ld) {
+  const int t = blockIdx.x;
+  if (t >= T) return;
+  const float* row = logits + static_cast<size_t>(t) * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int nw = blockDim.x >> 5;
+    best = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
+    bi = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (threadIdx.x == 0) out[t] = (bi == 0x7fffffff) ? 0 : bi;
+  }
+}
+
+// Step counter shared by the flag protocol: one increment per forward step, on the stream.
+__global__ void bump_epoch_kernel(uint32_t* epoch) { *epoch = *epoch + 1; }
+
+}  // namespace cafd
+
+using namespace cafd;
+
+extern "C" int cafd_embed(const int* tokens, const void* table, void* out, int T, int H, int vocab,
+                          cafd_stream_t s) {
+  if (T <= 0) return 0;
+  if (H % 8) return -10;
+  embed_kernel<<<T, 128, 0, static_cast<cudaStream_t>(s)>>>(tokens, static_cast<const uint4*>(table),
+                                                            static_cast<uint4*>(out), T, H / 8, vocab);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int cafd_rmsnorm(const void* x, void* residual, const void* w, void* y, int T, int H, float eps,
+                            cafd_stream_t s) {
+  if (T <= 0) return 0;
+  if (H % 8 || H > 256 * 8 * 8) return -10;
+  const int nvec = H / 8;
+  cudaStream_t st = static_cast<cudaStream_t>(s);
+  const uint4* xp = static_cast<const uint4*>(x);
+  uint4* rp = static_cast<uint4*>(residual);
+  const uint4* wp = static_cast<const uint4*>(w);
+  uint4* yp = static_cast<uint4*>(y);
+  if (nvec <= 256) rmsnorm_kernel<1><<<T, 256, 0, st>>>(xp, rp, wp, yp, T, H, eps);
+  else if (nvec <= 512) rmsnorm_kernel<2><<<T, 256, 0, st>>>(xp, rp, wp, yp, T, H, eps);
+  else if (nvec <= 1024) rmsnorm_kernel<4><<<T, 256, 0, st>>>(xp, rp, wp, yp, T, H, eps);
+  else rmsnorm_kernel<8><<<T, 256, 0, st>>>(xp, rp, wp, yp, T, H, eps);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int cafd_qk_rope_kv(const void* qkv, const void* q_norm_w, const void* k_norm_w, const float* inv_freq,
+                               const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
+                               int T, int Hq, int Hkv, int D, float eps, int interleaved, cafd_stream_t s) {
+  if (T <= 0) return 0;
+  if (D != 128) return -10;
+  const int warps = T * (Hq + 2 * Hkv);
+  const int blocks = (warps + 3) / 4;
+  qk_rope_kv_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(s)>>>(
+      static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(q_norm_w),
+      static_cast<const __nv_bfloat16*>(k_norm_w), inv_freq, positions, slots, static_cast<__nv_bfloat16*>(q_out),
+      static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), T, Hq, Hkv, eps, interleaved);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int cafd_argmax(const float* logits, int* out, int T, int V, int ld, cafd_stream_t s) {
+  if (T <= 0) return 0;
+  argmax_kernel<<<T, 1024, 0, static_cast<cudaStream_t>(s)>>>(logits, out, T, V, ld);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int cafd_bump_epoch(uint32_t* epoch, cafd_stream_t s) {
+  bump_epoch_kernel<<<1, 1, 0, static_cast<cudaStream_t>(s)>>>(epoch);
+  return static_cast<int>(cudaGetLastError());
+}

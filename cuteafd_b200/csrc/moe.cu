@@ -1,0 +1,399 @@
+// MoE routing and the attention-rank side of the expert exchange over NVLink peer memory.
+//
+//   route_topk   router scores -> top-k expert ids + gate weights (softmax / sigmoid, selection
+//                bias, group-limited routing, ties to the lowest id)
+//   moe_plan     histogram + padded per-expert segments per expert rank; writes each rank's tile
+//                list and row map straight into that rank's memory
+//   moe_dispatch copies token rows into the owning rank's slab with SM stores over the peer
+//                mapping and publishes the step number with a system-scope release
+//   moe_combine  waits (bounded) for every expert rank's completion flag, then sums the
+//                per-(token, slot) rows in slot order in fp32 with the gate weights, adds the
+//                shared expert and the residual, and rounds once
+//
+// The reference ships the same pieces as separate programs joined by a host transport worker:
+// router (native/shared/cuda/expert_router.cu:16-163), gather/scatter rows
+// (native/shared/cuda/residual.cu:144-537), ordered combine (native/shared/cuda/route_reduce.cu:30-145)
+// and push + release flag (native/shared/cuda/peer_exchange.cu:69-253).  Here the hand-off is
+// in-kernel: no host proxy, no NIC.
+#include "cafd_api.h"
+#include "common.cuh"
+
+namespace cafd {
+
+constexpr int kMaxRanks = 8;
+constexpr int kMaxExperts = 512;
+constexpr int kMetaHeader = 16;   // ints before the tile list in a rank's meta block
+
+struct MoeLayoutDev {
+  int n_ranks;
+  int expert_lo[kMaxRanks + 1];
+  __nv_bfloat16* slab[kMaxRanks];
+  int* meta[kMaxRanks];
+  uint32_t* flag[kMaxRanks];
+  int max_tiles;
+  int max_rows;
+};
+
+// ---- router -------------------------------------------------------------------------------------
+template <int kPerLane>
+__global__ void __launch_bounds__(128) route_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                                         int* __restrict__ out_idx, float* __restrict__ out_w, int T,
+                                                         int E, int top_k, int sigmoid, int num_groups,
+                                                         int topk_groups, int normalize, float routed_scale) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const int lane = threadIdx.x & 31;
+  float score[kPerLane], sel[kPerLane];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < kPerLane; ++j) {
+    const int e = j * 32 + lane;
+    score[j] = e < E ? logits[static_cast<size_t>(t) * E + e] : -INFINITY;
+    mx = fmaxf(mx, score[j]);
+  }
+  if (sigmoid) {
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+      const int e = j * 32 + lane;
+      score[j] = e < E ? 1.0f / (1.0f + expf(-score[j])) : -INFINITY;
+    }
+  } else {
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+      const int e = j * 32 + lane;
+      score[j] = e < E ? expf(score[j] - mx) : 0.f;
+      sum += score[j];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+      const int e = j * 32 + lane;
+      score[j] = e < E ? score[j] / sum : -INFINITY;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kPerLane; ++j) {
+    const int e = j * 32 + lane;
+    sel[j] = e < E ? score[j] + (bias ? bias[e] : 0.f) : -INFINITY;
+  }
+  if (num_groups > 1) {
+    const int per_group = E / num_groups;
+    unsigned keep = 0;   // bit g set = group g kept
+    float gscore_mine = -INFINITY;   // lane g holds the score of group g
+    for (int g = 0; g < num_groups; ++g) {
+      float top1 = -INFINITY, top2 = -INFINITY;
+      int i1 = 0x7fffffff;
+#pragma unroll
+      for (int j = 0; j < kPerLane; ++j) {
+        const int e = j * 32 + lane;
+        if (e < E && e / per_group == g && (sel[j] > top1 || (sel[j] == top1 && e < i1))) { top1 = sel[j]; i1 = e; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, top1, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, i1, o);
+        if (ov > top1 || (ov == top1 && oi < i1)) { top1 = ov; i1 = oi; }
+      }
+#pragma unroll
+      for (int j = 0; j < kPerLane; ++j) {
+        const int e = j * 32 + lane;
+        if (e < E && e / per_group == g && e != i1) top2 = fmaxf(top2, sel[j]);
+      }
+      top2 = warp_max(top2);
+      if (lane == g) gscore_mine = top1 + top2;
+    }
+    for (int it = 0; it < topk_groups; ++it) {
+      float v = (lane < num_groups && !((keep >> lane) & 1u)) ? gscore_mine : -INFINITY;
+      int gi = lane;
+      // groups with -inf scores can still be picked when fewer finite ones exist: mark via index
+      if (!(lane < num_groups) || ((keep >> lane) & 1u)) gi = 0x7fffffff;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, gi, o);
+        if (ov > v || (ov == v && oi < gi)) { v = ov; gi = oi; }
+      }
+      if (gi != 0x7fffffff) keep |= 1u << gi;
+    }
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+      const int e = j * 32 + lane;
+      if (e < E && !((keep >> (e / per_group)) & 1u)) sel[j] = -INFINITY;
+    }
+  }
+  float wsum = 0.f;
+  float my_w = 0.f;
+  int my_i = 0;
+  unsigned taken = 0;   // bit j: this lane's element j was already selected
+  for (int it = 0; it < top_k; ++it) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    float bs = 0.f;
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+      const int e = j * 32 + lane;
+      if (e < E && !((taken >> j) & 1u) && (sel[j] > bv || (sel[j] == bv && e < bi))) { bv = sel[j]; bi = e; bs = score[j]; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      const float os = __shfl_xor_sync(0xffffffffu, bs, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; bs = os; }
+    }
+    if (bi == 0x7fffffff) { bi = 0; bs = 0.f; }   // every candidate was NaN
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j)
+      if (j * 32 + lane == bi) taken |= 1u << j;
+    wsum += bs;
+    if (lane == it) { my_w = bs; my_i = bi; }
+  }
+  if (lane < top_k) {
+    float w = my_w;
+    if (normalize) w = w / (wsum + 1e-20f);
+    out_idx[static_cast<size_t>(t) * top_k + lane] = my_i;
+    out_w[static_cast<size_t>(t) * top_k + lane] = w * routed_scale;
+  }
+}
+
+// ---- plan -----------------------------------------------------------------------------------------
+// One CTA.  idx [T, k].  dest_row [T*k] (local) receives each entry's row in its owner's slab.
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ idx, int T, int top_k, int E,
+                                                        int tile_rows, MoeLayoutDev L, int* __restrict__ dest_row,
+                                                        int* __restrict__ expert_count_out, uint32_t* status) {
+  __shared__ int counts[kMaxExperts];
+  __shared__ int seg_off[kMaxExperts];
+  __shared__ int cursor[kMaxExperts];
+  __shared__ int rank_of[kMaxExperts];
+  const int n = T * top_k;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) { counts[e] = 0; cursor[e] = 0; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = idx[i];
+    if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x < L.n_ranks) {
+    const int r = threadIdx.x;
+    int* meta = L.meta[r];
+    int* tile_expert = meta + kMetaHeader;
+    int* tile_row0 = tile_expert + L.max_tiles;
+    int off = 0, tiles = 0;
+    bool overflow = false;
+    for (int e = L.expert_lo[r]; e < L.expert_lo[r + 1]; ++e) {
+      rank_of[e] = r;
+      seg_off[e] = off;
+      const int nt = (counts[e] + tile_rows - 1) / tile_rows;
+      for (int j = 0; j < nt; ++j) {
+        if (tiles < L.max_tiles && off + tile_rows <= L.max_rows) {
+          tile_expert[tiles] = e - L.expert_lo[r];
+          tile_row0[tiles] = off;
+          ++tiles;
+        } else {
+          overflow = true;
+        }
+        off += tile_rows;
+      }
+    }
+    meta[0] = tiles;
+    meta[1] = off < L.max_rows ? off : L.max_rows;
+    if (overflow && status) atomicCAS(status, 0u, static_cast<uint32_t>(kBadArgument));
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = idx[i];
+    int row = -1;
+    if (e >= 0 && e < E) {
+      const int pos = atomicAdd(&cursor[e], 1);
+      row = seg_off[e] + pos;
+      const int r = rank_of[e];
+      if (row < L.max_rows) {
+        int* row_dst = L.meta[r] + kMetaHeader + 2 * L.max_tiles;
+        row_dst[row] = i;
+      } else {
+        row = -1;
+      }
+    }
+    dest_row[i] = row;
+  }
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int r = rank_of[e];
+    int* row_dst = L.meta[r] + kMetaHeader + 2 * L.max_tiles;
+    const int padded = (counts[e] + tile_rows - 1) / tile_rows * tile_rows;
+    for (int pos = counts[e]; pos < padded; ++pos)
+      if (seg_off[e] + pos < L.max_rows) row_dst[seg_off[e] + pos] = -1;
+    if (expert_count_out) expert_count_out[e] += counts[e];
+  }
+}
+
+// ---- dispatch -------------------------------------------------------------------------------------
+// One warp per (token, slot).  Rows travel as 16-byte stores into the owner's slab (local or peer).
+__global__ void __launch_bounds__(256) moe_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ idx,
+                                                           const int* __restrict__ dest_row, int n_entries, int top_k,
+                                                           int row_vec, MoeLayoutDev L, const uint32_t* epoch,
+                                                           uint32_t* done_counter) {
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (i < n_entries) {
+    const int row = dest_row[i];
+    if (row >= 0) {
+      const int e = idx[i];
+      int r = 0;
+      while (r + 1 < L.n_ranks && e >= L.expert_lo[r + 1]) ++r;
+      const uint4* src = x + static_cast<size_t>(i / top_k) * row_vec;
+      uint4* dst = reinterpret_cast<uint4*>(L.slab[r]) + static_cast<size_t>(row) * row_vec;
+      for (int c = lane; c < row_vec; c += 32) dst[c] = src[c];
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(done_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *done_counter = 0;
+      __threadfence_system();
+      const uint32_t ep = *epoch;
+      for (int r = 0; r < L.n_ranks; ++r) st_release_sys(L.flag[r], ep);
+    }
+  }
+}
+
+// ---- combine --------------------------------------------------------------------------------------
+// buf [T, k, H] bf16 holds the unweighted expert outputs per (token, slot), written by the expert
+// ranks.  out[t] = bf16( sum_s w[t,s] * buf[t,s] (slot order, fp32) + shared[t] + residual[t] ).
+__global__ void __launch_bounds__(256) moe_combine_kernel(const uint4* __restrict__ buf, const float* __restrict__ w,
+                                                          const uint4* __restrict__ shared_out,
+                                                          const uint4* __restrict__ residual, uint4* __restrict__ out,
+                                                          int T, int top_k, int row_vec, const uint32_t* flags,
+                                                          int n_flags, const uint32_t* epoch, uint32_t* status) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    bool ok = true;
+    if (flags) {
+      const uint32_t ep = *epoch;
+      for (int r = 0; r < n_flags && ok; ++r) ok = wait_flag_ge(flags + r, ep, status);
+    }
+    s_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    for (int c = threadIdx.x; c < row_vec; c += blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int s = 0; s < top_k; ++s) {
+        const float g = w[static_cast<size_t>(t) * top_k + s];
+        const uint4 v = buf[(static_cast<size_t>(t) * top_k + s) * row_vec + c];
+        const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[2 * e] += g * bf16_lo(q[e]);
+          acc[2 * e + 1] += g * bf16_hi(q[e]);
+        }
+      }
+      if (shared_out) {
+        const uint4 v = shared_out[static_cast<size_t>(t) * row_vec + c];
+        const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { acc[2 * e] += bf16_lo(q[e]); acc[2 * e + 1] += bf16_hi(q[e]); }
+      }
+      if (residual) {
+        const uint4 v = residual[static_cast<size_t>(t) * row_vec + c];
+        const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { acc[2 * e] += bf16_lo(q[e]); acc[2 * e + 1] += bf16_hi(q[e]); }
+      }
+      out[static_cast<size_t>(t) * row_vec + c] = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]),
+                                                             pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+    }
+  }
+}
+
+}  // namespace cafd
+
+using namespace cafd;
+
+extern "C" {
+
+typedef struct {
+  int n_ranks;
+  int expert_lo[kMaxRanks + 1];
+  void* slab[kMaxRanks];
+  int* meta[kMaxRanks];
+  uint32_t* flag[kMaxRanks];
+  int max_tiles;
+  int max_rows;
+} cafd_moe_layout;
+
+static MoeLayoutDev to_dev(const cafd_moe_layout* l) {
+  MoeLayoutDev d;
+  d.n_ranks = l->n_ranks;
+  for (int i = 0; i <= kMaxRanks; ++i) d.expert_lo[i] = l->expert_lo[i];
+  for (int i = 0; i < kMaxRanks; ++i) {
+    d.slab[i] = static_cast<__nv_bfloat16*>(l->slab[i]);
+    d.meta[i] = l->meta[i];
+    d.flag[i] = l->flag[i];
+  }
+  d.max_tiles = l->max_tiles;
+  d.max_rows = l->max_rows;
+  return d;
+}
+
+int cafd_route_topk(const float* logits, const float* bias, int* out_idx, float* out_w, int T, int E, int top_k,
+                    int sigmoid, int num_groups, int topk_groups, int normalize, float routed_scale,
+                    cafd_stream_t s) {
+  if (T <= 0) return 0;
+  if (E > kMaxExperts || top_k > 32 || num_groups > 32 || (num_groups > 1 && E % num_groups)) return -10;
+  cudaStream_t st = static_cast<cudaStream_t>(s);
+  const int blocks = (T + 3) / 4;
+#define CAFD_ROUTE(N)                                                                                          \
+  route_topk_kernel<N><<<blocks, 128, 0, st>>>(logits, bias, out_idx, out_w, T, E, top_k, sigmoid, num_groups, \
+                                               topk_groups, normalize, routed_scale)
+  if (E <= 32) CAFD_ROUTE(1);
+  else if (E <= 64) CAFD_ROUTE(2);
+  else if (E <= 128) CAFD_ROUTE(4);
+  else if (E <= 256) CAFD_ROUTE(8);
+  else CAFD_ROUTE(16);
+#undef CAFD_ROUTE
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cafd_moe_meta_ints(int max_tiles, int max_rows) { return kMetaHeader + 2 * max_tiles + max_rows; }
+
+int cafd_moe_plan(const int* idx, int T, int top_k, int E, int tile_rows, const cafd_moe_layout* layout,
+                  int* dest_row, int* expert_count, uint32_t* status, cafd_stream_t s) {
+  if (E > kMaxExperts || layout->n_ranks < 1 || layout->n_ranks > kMaxRanks) return -10;
+  moe_plan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(s)>>>(idx, T, top_k, E, tile_rows, to_dev(layout), dest_row,
+                                                               expert_count, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cafd_moe_dispatch(const void* x, const int* idx, const int* dest_row, int T, int top_k, int H,
+                      const cafd_moe_layout* layout, const uint32_t* epoch, uint32_t* done_counter,
+                      cafd_stream_t s) {
+  if (H % 8) return -10;
+  const int n = T * top_k;
+  const int blocks = n > 0 ? (n + 7) / 8 : 1;
+  moe_dispatch_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(s)>>>(static_cast<const uint4*>(x), idx, dest_row, n,
+                                                                       top_k, H / 8, to_dev(layout), epoch,
+                                                                       done_counter);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cafd_moe_combine(const void* buf, const float* w, const void* shared_out, const void* residual, void* out, int T,
+                     int top_k, int H, const uint32_t* flags, int n_flags, const uint32_t* epoch, uint32_t* status,
+                     cafd_stream_t s) {
+  if (H % 8) return -10;
+  int blocks = T < 1 ? 1 : (T > 4096 ? 4096 : T);
+  moe_combine_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(s)>>>(
+      static_cast<const uint4*>(buf), w, static_cast<const uint4*>(shared_out), static_cast<const uint4*>(residual),
+      static_cast<uint4*>(out), T, top_k, H / 8, flags, n_flags, epoch, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"
+
+CAFD_WAIT_LIMIT_SETTER(cafd_moe_set_wait_limit_ns)

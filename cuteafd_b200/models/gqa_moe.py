@@ -1,0 +1,246 @@
+"""GQA + MoE decoder (Qwen3-MoE geometry and relatives) on the sm_100a kernels.
+
+Weights are held in the layout the kernels stream: fused qkv rows, per-layer stacked expert
+tensors [E, I, H] / [E, H, I].  Stacking copies rows; it re-encodes nothing.  The forward pass is
+a fixed launch sequence over preallocated workspaces, so a decode step can be captured in a CUDA
+graph.  The layer body mirrors the reference's per-layer segment
+(rust/crates/cuteafd-daemon/src/families/glm5/engine.rs:2110-2262: norm -> attention unit ->
+exchange -> post norm -> dense FFN or moe_front / moe_exchange), minus the host transport.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from ..config import ModelConfig
+from ..ops import kernels as K
+from ..parallel.moe_exchange import ExchangeGeometry, LocalExchange, pick_tile_rows
+
+PAGE = 64
+
+
+@dataclass
+class Batch:
+    """Device-side description of one forward step (all int32 tensors on the GPU)."""
+    tokens: torch.Tensor        # [T]
+    positions: torch.Tensor     # [T]
+    slots: torch.Tensor         # [T] page * 64 + offset for the KV write
+    page_table: torch.Tensor    # [S, max_pages]
+    seq_lens: torch.Tensor      # [S] kv length after this step
+    q_start: torch.Tensor       # [S + 1]
+    max_q_len: int
+    prefill: bool
+    last_rows: torch.Tensor | None = None   # rows whose logits are wanted (None = all)
+
+
+class LayerWeights:
+    __slots__ = ("ln1", "ln2", "wqkv", "wo", "q_norm", "k_norm", "router", "router_bias", "w_gate", "w_up", "w_down",
+                 "d_gate", "d_up", "d_down", "s_gate", "s_up", "s_down")
+
+    def __init__(self) -> None:
+        for s in self.__slots__:
+            setattr(self, s, None)
+
+
+class GqaMoeWeights:
+    def __init__(self, cfg: ModelConfig):
+        self.cfg = cfg
+        self.embed: torch.Tensor | None = None
+        self.final_norm: torch.Tensor | None = None
+        self.lm_head: torch.Tensor | None = None
+        self.layers: list[LayerWeights] = []
+
+    @staticmethod
+    def from_params(cfg: ModelConfig, p: dict[str, torch.Tensor], device: torch.device) -> "GqaMoeWeights":
+        """Build from a Hugging Face style name -> tensor dictionary (any float dtype)."""
+        def t(name: str) -> torch.Tensor:
+            return p[name].to(device=device, dtype=torch.bfloat16).contiguous()
+
+        W = GqaMoeWeights(cfg)
+        W.embed, W.final_norm = t("model.embed_tokens.weight"), t("model.norm.weight")
+        W.lm_head = W.embed if cfg.tie_embeddings else t("lm_head.weight")
+        for i in range(cfg.num_layers):
+            pre, L = f"model.layers.{i}.", LayerWeights()
+            a, m = pre + "self_attn.", pre + "mlp."
+            L.ln1, L.ln2 = t(pre + "input_layernorm.weight"), t(pre + "post_attention_layernorm.weight")
+            L.wqkv = torch.cat([t(a + "q_proj.weight"), t(a + "k_proj.weight"), t(a + "v_proj.weight")]).contiguous()
+            L.wo = t(a + "o_proj.weight")
+            if cfg.qk_norm:
+                L.q_norm, L.k_norm = t(a + "q_norm.weight"), t(a + "k_norm.weight")
+            if cfg.is_moe_layer(i):
+                L.router = t(m + "gate.weight")
+                b = p.get(m + "gate.e_score_correction_bias")
+                L.router_bias = None if b is None else b.to(device=device, dtype=torch.float32).contiguous()
+                for dst, src in (("w_gate", "gate_proj"), ("w_up", "up_proj"), ("w_down", "down_proj")):
+                    setattr(L, dst, torch.stack([t(m + f"experts.{e}.{src}.weight") for e in range(cfg.num_experts)]).contiguous())
+                if cfg.num_shared_experts:
+                    L.s_gate, L.s_up, L.s_down = (t(m + f"shared_experts.{n}_proj.weight") for n in ("gate", "up", "down"))
+            else:
+                L.d_gate, L.d_up, L.d_down = (t(m + f"{n}_proj.weight") for n in ("gate", "up", "down"))
+            W.layers.append(L)
+        return W
+
+    @staticmethod
+    def random_init(cfg: ModelConfig, device: torch.device, seed: int = 0, std: float = 0.02) -> "GqaMoeWeights":
+        """N(0, std) weights generated on the device, layer by layer (no host copy of the model)."""
+        g = torch.Generator(device=device).manual_seed(seed)
+
+        def w(*shape: int) -> torch.Tensor:
+            out = torch.empty(*shape, dtype=torch.bfloat16, device=device)
+            out.normal_(0.0, std, generator=g)
+            return out
+
+        def ones(n: int) -> torch.Tensor:
+            return torch.ones(n, dtype=torch.bfloat16, device=device)
+
+        H, D = cfg.hidden, cfg.head_dim
+        W = GqaMoeWeights(cfg)
+        W.embed, W.final_norm = w(cfg.vocab_size, H), ones(H)
+        W.lm_head = W.embed if cfg.tie_embeddings else w(cfg.vocab_size, H)
+        for i in range(cfg.num_layers):
+            L = LayerWeights()
+            L.ln1, L.ln2 = ones(H), ones(H)
+            L.wqkv, L.wo = w((cfg.num_heads + 2 * cfg.num_kv_heads) * D, H), w(H, cfg.num_heads * D)
+            if cfg.qk_norm:
+                L.q_norm, L.k_norm = ones(D), ones(D)
+            if cfg.is_moe_layer(i):
+                L.router = w(cfg.num_experts, H)
+                L.router_bias = torch.zeros(cfg.num_experts, dtype=torch.float32, device=device) if cfg.router_bias else None
+                L.w_gate, L.w_up = w(cfg.num_experts, cfg.expert_ffn, H), w(cfg.num_experts, cfg.expert_ffn, H)
+                L.w_down = w(cfg.num_experts, H, cfg.expert_ffn)
+                if cfg.num_shared_experts:
+                    inter = cfg.expert_ffn * cfg.num_shared_experts
+                    L.s_gate, L.s_up, L.s_down = w(inter, H), w(inter, H), w(H, inter)
+            else:
+                L.d_gate, L.d_up, L.d_down = w(cfg.dense_ffn, H), w(cfg.dense_ffn, H), w(H, cfg.dense_ffn)
+            W.layers.append(L)
+        return W
+
+
+class KvCache:
+    """Paged K/V pools, one pair per layer: [num_pages, 64, Hkv, D] bf16.  Page 0 stays all-zero:
+    kernels read it for table entries past a sequence's end (the reference keeps the same
+    reserved page, rust/crates/cuteafd-engine/src/prefix/family.rs:20-28)."""
+
+    def __init__(self, cfg: ModelConfig, num_pages: int, device: torch.device):
+        shape = (num_pages, PAGE, cfg.num_kv_heads, cfg.head_dim)
+        self.num_pages = num_pages
+        self.k = [torch.zeros(shape, dtype=torch.bfloat16, device=device) for _ in range(cfg.num_layers)]
+        self.v = [torch.zeros(shape, dtype=torch.bfloat16, device=device) for _ in range(cfg.num_layers)]
+
+    def bytes_per_page(self) -> int:
+        return 2 * len(self.k) * self.k[0][0].numel() * 2
+
+
+class Workspace:
+    def __init__(self, cfg: ModelConfig, max_tokens: int, device: torch.device):
+        H, D = cfg.hidden, cfg.head_dim
+        bf = dict(dtype=torch.bfloat16, device=device)
+        self.h = torch.empty(max_tokens, H, **bf)
+        self.x = torch.empty(max_tokens, H, **bf)
+        self.qkv = torch.empty(max_tokens, (cfg.num_heads + 2 * cfg.num_kv_heads) * D, **bf)
+        self.q = torch.empty(max_tokens, cfg.num_heads, D, **bf)
+        self.attn = torch.empty(max_tokens, cfg.num_heads, D, **bf)
+        self.router = torch.empty(max_tokens, max(cfg.num_experts, 1), dtype=torch.float32, device=device)
+        dense = cfg.first_dense_layers > 0 or cfg.num_experts == 0
+        self.ffn_d = torch.empty(max_tokens, cfg.dense_ffn, **bf) if dense else None
+        self.ffn_s = torch.empty(max_tokens, cfg.expert_ffn * cfg.num_shared_experts, **bf) if cfg.num_shared_experts else None
+        self.shared = torch.empty(max_tokens, H, **bf) if cfg.num_shared_experts else None
+
+
+class GqaMoeEngine:
+    """Single-GPU engine (attention and experts on the same device)."""
+
+    def __init__(self, cfg: ModelConfig, weights: GqaMoeWeights, kv: KvCache, max_tokens: int, max_seqs: int = 64):
+        assert cfg.attention == "gqa" and cfg.head_dim == 128
+        self.cfg, self.W, self.kv = cfg, weights, kv
+        self.device = weights.embed.device
+        self.max_tokens = max_tokens
+        self.ws = Workspace(cfg, max_tokens, self.device)
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, dtype=torch.float32) / cfg.head_dim))
+        self.inv_freq = inv.to(self.device)
+        self.moe = None
+        if cfg.num_experts:
+            geo = ExchangeGeometry(cfg.hidden, cfg.expert_ffn, cfg.num_experts, cfg.top_k, max_tokens, 1)
+            self.moe = LocalExchange(geo, self.device)
+        self.route_kw = dict(scoring=cfg.scoring, num_groups=cfg.num_groups, topk_groups=cfg.topk_groups,
+                             normalize=cfg.norm_topk_prob, routed_scale=cfg.routed_scale)
+        self.logits = torch.empty(max_seqs if max_seqs < max_tokens else max_tokens, cfg.vocab_size,
+                                  dtype=torch.float32, device=self.device)
+        self.next_tokens = torch.empty(self.logits.shape[0], dtype=torch.int32, device=self.device)
+        self._scratch: torch.Tensor | None = None
+        self.launches = 0
+
+    # ---- pieces ---------------------------------------------------------------------------------
+    def _attention(self, i: int, T: int, b: Batch) -> None:
+        cfg, L, ws = self.cfg, self.W.layers[i], self.ws
+        K.linear(ws.x[:T], L.wqkv, out=ws.qkv[:T])
+        K.qk_rope_kv(ws.qkv[:T], L.q_norm, L.k_norm, self.inv_freq, b.positions, b.slots, ws.q[:T], self.kv.k[i],
+                     self.kv.v[i], cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.rms_eps, cfg.rope_interleaved)
+        if b.prefill:
+            K.attn_prefill(ws.q[:T], self.kv.k[i], self.kv.v[i], b.page_table, b.seq_lens, b.q_start, ws.attn[:T],
+                           b.max_q_len)
+            self.launches += 3
+        else:
+            S, max_pages = b.page_table.shape
+            q_per_tile = 16 // (cfg.num_heads // cfg.num_kv_heads)
+            tiles = (b.max_q_len + q_per_tile - 1) // q_per_tile
+            splits = K.attn_decode_splits(S, tiles, cfg.num_kv_heads, max_pages)
+            need = K.attn_decode_scratch_floats(S, b.max_q_len, cfg.num_heads, cfg.num_kv_heads, splits)
+            if self._scratch is None or self._scratch.numel() < need:
+                self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
+            K.attn_decode(ws.q[:T], self.kv.k[i], self.kv.v[i], b.page_table, b.seq_lens, b.q_start, ws.attn[:T],
+                          self._scratch, b.max_q_len, splits)
+            self.launches += 3 + (1 if splits > 1 else 0)
+        # o_proj with the residual add fused into the epilogue: h = h + attn @ wo.T
+        K.linear(ws.attn[:T].view(T, -1), L.wo, out=ws.h[:T], residual=ws.h[:T])
+        self.launches += 1
+
+    def _ffn(self, i: int, T: int) -> None:
+        cfg, L, ws = self.cfg, self.W.layers[i], self.ws
+        if L.router is None:
+            K.linear(ws.x[:T], L.d_gate, out=ws.ffn_d[:T], w_up=L.d_up)
+            K.linear(ws.ffn_d[:T], L.d_down, out=ws.h[:T], residual=ws.h[:T])
+            self.launches += 2
+            return
+        shared = None
+        if L.s_gate is not None:
+            K.linear(ws.x[:T], L.s_gate, out=ws.ffn_s[:T], w_up=L.s_up)
+            shared = K.linear(ws.ffn_s[:T], L.s_down, out=ws.shared[:T])
+            self.launches += 2
+        K.linear(ws.x[:T], L.router, out=ws.router[:T, :cfg.num_experts], out_f32=True)
+        kw = dict(self.route_kw, bias=L.router_bias)
+        self.moe.forward(ws.x[:T], ws.router[:T, :cfg.num_experts], kw, L.w_gate, L.w_up, L.w_down, ws.h[:T],
+                         shared=shared, residual=ws.h[:T])
+        self.launches += 7
+
+    # ---- whole step -------------------------------------------------------------------------------
+    def forward(self, b: Batch) -> torch.Tensor:
+        """Runs all layers; returns fp32 logits for ``b.last_rows`` (or every row)."""
+        cfg, ws = self.cfg, self.ws
+        T = b.tokens.shape[0]
+        assert T <= self.max_tokens
+        K.embed(b.tokens, self.W.embed, out=ws.h[:T])
+        self.launches += 1
+        for i in range(cfg.num_layers):
+            L = self.W.layers[i]
+            K.rmsnorm(ws.h[:T], L.ln1, cfg.rms_eps, out=ws.x[:T])
+            self._attention(i, T, b)
+            K.rmsnorm(ws.h[:T], L.ln2, cfg.rms_eps, out=ws.x[:T])
+            self._ffn(i, T)
+            self.launches += 2
+        if b.last_rows is not None:
+            rows = ws.h[:T].index_select(0, b.last_rows)
+        else:
+            rows = ws.h[:T]
+        n = rows.shape[0]
+        xn = K.rmsnorm(rows, self.W.final_norm, cfg.rms_eps, out=ws.x[:n])
+        logits = K.linear(xn, self.W.lm_head, out=self.logits[:n], out_f32=True)
+        self.launches += 2
+        return logits
+
+    def greedy(self, logits: torch.Tensor) -> torch.Tensor:
+        self.launches += 1
+        return K.argmax(logits, out=self.next_tokens[:logits.shape[0]])

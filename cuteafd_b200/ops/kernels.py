@@ -1,0 +1,262 @@
+"""Torch-tensor front end of the sm_100a kernels.
+
+Every function launches on the current CUDA stream, allocates nothing beyond its outputs (and
+not even those when ``out=`` is given), and raises if the native library is missing: there is no
+PyTorch fallback on a GPU box.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from .._native import lib as _n
+
+_status: dict[int, torch.Tensor] = {}
+_NUM_SMS: dict[int, int] = {}
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def status_word(device: torch.device | None = None) -> torch.Tensor:
+    """Per-device status word: kernels CAS a code into it when a bounded wait runs out."""
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    if idx not in _status:
+        _status[idx] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{idx}")
+    return _status[idx]
+
+
+def read_status(reset: bool = True) -> int:
+    s = status_word()
+    v = int(s.item())
+    if reset and v:
+        s.zero_()
+    return v
+
+
+def num_sms() -> int:
+    d = torch.cuda.current_device()
+    if d not in _NUM_SMS:
+        _NUM_SMS[d] = torch.cuda.get_device_properties(d).multi_processor_count
+    return _NUM_SMS[d]
+
+
+def set_wait_limit_ns(ns: int) -> None:
+    L = _n.cuda_lib()
+    for f in (L.cafd_gemm_set_wait_limit_ns, L.cafd_moe_set_wait_limit_ns, L.cafd_attn_set_wait_limit_ns):
+        _n.check(f(ns), "set_wait_limit")
+
+
+# ---- GEMM ------------------------------------------------------------------------------------------
+def pick_token_tile(rows: int) -> int:
+    """Token tile for the weights-on-M orientation."""
+    for b in (16, 32, 64, 128):
+        if rows <= b:
+            return b
+    return 128
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *, w_up: torch.Tensor | None = None,
+           residual: torch.Tensor | None = None, out_f32: bool = False, swap: bool | None = None) -> torch.Tensor:
+    """y = x @ w.T (bf16 in, fp32 accumulate).  With ``w_up``: y = silu(x @ w.T) * (x @ w_up.T).
+
+    x [T, K], w [N, K].  ``swap`` picks the orientation (default: weights on M when T <= 128).
+    """
+    T, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
+    assert w.shape[1] == K
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    if T == 0:
+        return out
+    if swap is None:
+        swap = T <= 128
+    a = _n.GemmArgs()
+    a.w0, a.w1, a.x, a.out = w.data_ptr(), _ptr(w_up), x.data_ptr(), out.data_ptr()
+    a.residual = _ptr(residual)
+    a.status = status_word(x.device).data_ptr()
+    a.w_rows_total, a.x_rows_total = N, T
+    a.k, a.n_features, a.x_rows, a.ldo = K, N, T, out.stride(0)
+    a.w_rows_per_expert, a.w1_row_offset, a.max_x_tiles = 0, 0, 0
+    a.swap, a.dual, a.bx = int(swap), int(w_up is not None), pick_token_tile(T) if swap else 128
+    if swap and T > 128:
+        a.bx = 128
+    a.out_f32, a.fp8, a.num_sms = int(out.dtype == torch.float32), 0, num_sms()
+    _n.check(_n.cuda_lib().cafd_gemm(C.byref(a), _stream()), "cafd_gemm")
+    return out
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_expert: torch.Tensor,
+                   tile_row0: torch.Tensor, num_tiles: torch.Tensor, max_tiles: int, tile_rows: int, *,
+                   w_up: torch.Tensor | None = None, row_dst: torch.Tensor | None = None,
+                   wait_flag: int | None = None, epoch: torch.Tensor | None = None,
+                   signal_flag: int | None = None, done_counter: torch.Tensor | None = None,
+                   out_ptr: int | None = None, ldo: int | None = None) -> None:
+    """Expert-grouped GEMM over an expert-sorted slab.
+
+    x [rows, K] slab, w [E, N, K] stacked expert weights, tiles described by device arrays.
+    ``tile_rows`` 128 puts tokens on M (prefill); 16..64 puts weights on M (decode).
+    ``out_ptr`` overrides the destination address (a peer GPU's buffer).
+    """
+    E, N, K = w.shape
+    a = _n.GemmArgs()
+    a.w0, a.w1, a.x = w.data_ptr(), _ptr(w_up), x.data_ptr()
+    a.out = out_ptr if out_ptr is not None else out.data_ptr()
+    a.row_dst = _ptr(row_dst)
+    a.tile_expert, a.tile_row0, a.num_x_tiles = tile_expert.data_ptr(), tile_row0.data_ptr(), num_tiles.data_ptr()
+    a.wait_flag, a.epoch = wait_flag, _ptr(epoch)
+    a.signal_flag, a.done_counter = signal_flag, _ptr(done_counter)
+    a.status = status_word(x.device).data_ptr()
+    a.w_rows_total, a.x_rows_total = E * N, x.shape[0]
+    a.k, a.n_features, a.x_rows = K, N, x.shape[0]
+    a.ldo = ldo if ldo is not None else out.stride(0)
+    a.w_rows_per_expert, a.w1_row_offset, a.max_x_tiles = N, 0, max_tiles
+    swap = tile_rows < 128
+    a.swap, a.dual, a.bx = int(swap), int(w_up is not None), tile_rows
+    a.out_f32, a.fp8, a.num_sms = 0, 0, num_sms()
+    _n.check(_n.cuda_lib().cafd_gemm(C.byref(a), _stream()), "cafd_gemm(grouped)")
+
+
+# ---- elementwise -----------------------------------------------------------------------------------
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    T, (V, H) = tokens.shape[0], table.shape
+    if out is None:
+        out = torch.empty(T, H, dtype=table.dtype, device=table.device)
+    _n.check(_n.cuda_lib().cafd_embed(tokens.data_ptr(), table.data_ptr(), out.data_ptr(), T, H, V, _stream()), "embed")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    T, H = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    _n.check(_n.cuda_lib().cafd_rmsnorm(None, x.data_ptr(), w.data_ptr(), out.data_ptr(), T, H, eps, _stream()), "rmsnorm")
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, w: torch.Tensor, eps: float,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """residual += x (in place); returns rmsnorm(residual) * w."""
+    T, H = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    _n.check(_n.cuda_lib().cafd_rmsnorm(x.data_ptr(), residual.data_ptr(), w.data_ptr(), out.data_ptr(), T, H, eps,
+                                        _stream()), "add_rmsnorm")
+    return out
+
+
+def qk_rope_kv(qkv: torch.Tensor, q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, inv_freq: torch.Tensor,
+               positions: torch.Tensor, slots: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
+               v_cache: torch.Tensor, Hq: int, Hkv: int, D: int, eps: float, interleaved: bool) -> None:
+    T = qkv.shape[0]
+    _n.check(_n.cuda_lib().cafd_qk_rope_kv(qkv.data_ptr(), _ptr(q_norm), _ptr(k_norm), inv_freq.data_ptr(),
+                                           positions.data_ptr(), slots.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(),
+                                           v_cache.data_ptr(), T, Hq, Hkv, D, eps, int(interleaved), _stream()),
+             "qk_rope_kv")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    T, V = logits.shape
+    if out is None:
+        out = torch.empty(T, dtype=torch.int32, device=logits.device)
+    _n.check(_n.cuda_lib().cafd_argmax(logits.data_ptr(), out.data_ptr(), T, V, logits.stride(0), _stream()), "argmax")
+    return out
+
+
+def bump_epoch(epoch: torch.Tensor) -> None:
+    _n.check(_n.cuda_lib().cafd_bump_epoch(epoch.data_ptr(), _stream()), "bump_epoch")
+
+
+# ---- MoE -------------------------------------------------------------------------------------------
+def route_topk(logits: torch.Tensor, top_k: int, scoring: str = "softmax", bias: torch.Tensor | None = None,
+               num_groups: int = 1, topk_groups: int = 1, normalize: bool = True, routed_scale: float = 1.0,
+               out_idx: torch.Tensor | None = None, out_w: torch.Tensor | None = None):
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    if out_idx is None:
+        out_idx = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+    if out_w is None:
+        out_w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+    _n.check(_n.cuda_lib().cafd_route_topk(logits.data_ptr(), _ptr(bias), out_idx.data_ptr(), out_w.data_ptr(), T, E,
+                                           top_k, int(scoring == "sigmoid"), num_groups, topk_groups, int(normalize),
+                                           routed_scale, _stream()), "route_topk")
+    return out_idx, out_w
+
+
+def moe_meta_ints(max_tiles: int, max_rows: int) -> int:
+    return _n.cuda_lib().cafd_moe_meta_ints(max_tiles, max_rows)
+
+
+def moe_plan(idx: torch.Tensor, E: int, tile_rows: int, layout: "_n.MoeLayout", dest_row: torch.Tensor,
+             expert_count: torch.Tensor | None = None) -> None:
+    T, k = idx.shape
+    _n.check(_n.cuda_lib().cafd_moe_plan(idx.data_ptr(), T, k, E, tile_rows, C.byref(layout), dest_row.data_ptr(),
+                                         _ptr(expert_count), status_word(idx.device).data_ptr(), _stream()), "moe_plan")
+
+
+def moe_dispatch(x: torch.Tensor, idx: torch.Tensor, dest_row: torch.Tensor, layout: "_n.MoeLayout",
+                 epoch: torch.Tensor, done_counter: torch.Tensor) -> None:
+    T, k = idx.shape
+    _n.check(_n.cuda_lib().cafd_moe_dispatch(x.data_ptr(), idx.data_ptr(), dest_row.data_ptr(), T, k, x.shape[1],
+                                             C.byref(layout), epoch.data_ptr(), done_counter.data_ptr(), _stream()),
+             "moe_dispatch")
+
+
+def moe_combine(buf: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, shared: torch.Tensor | None = None,
+                residual: torch.Tensor | None = None, flags_ptr: int | None = None, n_flags: int = 0,
+                epoch: torch.Tensor | None = None) -> torch.Tensor:
+    T, k = w.shape
+    H = out.shape[1]
+    _n.check(_n.cuda_lib().cafd_moe_combine(buf.data_ptr(), w.data_ptr(), _ptr(shared), _ptr(residual), out.data_ptr(),
+                                            T, k, H, flags_ptr, n_flags, _ptr(epoch),
+                                            status_word(out.device).data_ptr(), _stream()), "moe_combine")
+    return out
+
+
+# ---- attention -------------------------------------------------------------------------------------
+def attn_decode_splits(num_seqs: int, tiles_per_seq: int, Hkv: int, max_pages: int) -> int:
+    ctas = max(1, num_seqs * tiles_per_seq * Hkv)
+    want = max(1, (2 * num_sms() + ctas - 1) // ctas)
+    return max(1, min(want, max(1, max_pages // 2), 64))
+
+
+def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
+                seq_lens: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor | None,
+                max_q_len: int, splits: int, scale: float | None = None) -> torch.Tensor:
+    _, Hq, D = q.shape
+    Hkv = k_cache.shape[2]
+    num_seqs, max_pages = page_table.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    _n.check(_n.cuda_lib().cafd_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_table.data_ptr(),
+                                            seq_lens.data_ptr(), q_start.data_ptr(), out.data_ptr(), _ptr(scratch),
+                                            num_seqs, max_q_len, max_pages, Hq, Hkv, D, splits, scale, _stream()),
+             "attn_decode")
+    return out
+
+
+def attn_decode_scratch_floats(num_seqs: int, max_q_len: int, Hq: int, Hkv: int, splits: int) -> int:
+    q_per_tile = 16 // (Hq // Hkv)
+    tiles = (max_q_len + q_per_tile - 1) // q_per_tile
+    return int(_n.cuda_lib().cafd_attn_decode_scratch_floats(num_seqs, tiles, Hkv, splits))
+
+
+def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
+                 seq_lens: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor, max_q_len: int,
+                 scale: float | None = None) -> torch.Tensor:
+    total_q, Hq, D = q.shape
+    num_pages, _, Hkv, _ = k_cache.shape
+    num_seqs, max_pages = page_table.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    _n.check(_n.cuda_lib().cafd_attn_prefill(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_table.data_ptr(),
+                                             seq_lens.data_ptr(), q_start.data_ptr(), out.data_ptr(),
+                                             status_word(q.device).data_ptr(), total_q, num_seqs, max_q_len, num_pages,
+                                             max_pages, Hq, Hkv, D, scale, _stream()), "attn_prefill")
+    return out

@@ -1,0 +1,162 @@
+"""Attention-rank / expert-rank halves of the MoE exchange.
+
+Experts are partitioned by id over the expert ranks (``expert_range``).  The attention rank plans
+the routes, stores token rows straight into each owner's slab (peer memory when the owner is
+another GPU) and publishes a step number; the owner's grouped GEMMs wait for that number, run
+fc1+SwiGLU and fc2, and the fc2 epilogue stores each (token, slot) row straight into the attention
+rank's combine buffer and publishes the step number back.  With one GPU every pointer is local
+and the same kernels run in stream order.
+
+The reference moves the same data with a host transport worker and RoCE SEND/RECV
+(rust/crates/cuteafd-daemon/src/shared/spark_waves.rs:1-84, 1188-1517) and sums TP slices
+(rust/crates/cuteafd-transport/src/expert/topology.rs:1-7); expert-parallel dispatch/combine in
+one kernel per direction is this engine's departure from it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .._native import lib as _n
+from ..ops import kernels as K
+from ..ref.split import expert_range
+
+
+def pick_tile_rows(T: int, top_k: int, num_experts: int) -> int:
+    avg = T * top_k / max(1, num_experts)
+    if avg <= 8:
+        return 16
+    if avg <= 24:
+        return 32
+    if avg <= 48:
+        return 64
+    return 128
+
+
+@dataclass
+class ExchangeGeometry:
+    hidden: int
+    expert_ffn: int
+    num_experts: int
+    top_k: int
+    max_tokens: int
+    n_expert_ranks: int = 1
+
+    def rank_experts(self, r: int) -> tuple[int, int]:
+        return expert_range(self.num_experts, self.n_expert_ranks, r)
+
+    @property
+    def max_rows(self) -> int:
+        """Worst-case slab rows on one rank: every route lands there, plus tile padding."""
+        per_rank = max(hi - lo for lo, hi in (self.rank_experts(r) for r in range(self.n_expert_ranks)))
+        return self.max_tokens * self.top_k + per_rank * 128
+
+    @property
+    def max_tiles(self) -> int:
+        return self.max_rows // 16 + 1
+
+    @property
+    def meta_ints(self) -> int:
+        return 16 + 2 * self.max_tiles + self.max_rows
+
+
+class ExpertSide:
+    """Buffers an expert rank owns: the receive slab, the fc1 output and the plan meta block."""
+
+    def __init__(self, geo: ExchangeGeometry, device: torch.device, slab: torch.Tensor | None = None,
+                 meta: torch.Tensor | None = None, flags: torch.Tensor | None = None, num_layers: int = 1):
+        self.geo = geo
+        self.slab = slab if slab is not None else torch.zeros(geo.max_rows, geo.hidden, dtype=torch.bfloat16, device=device)
+        self.meta = meta if meta is not None else torch.zeros(geo.meta_ints, dtype=torch.int32, device=device)
+        self.flags = flags if flags is not None else torch.zeros(num_layers, dtype=torch.int32, device=device)
+        self.hbuf = torch.zeros(geo.max_rows, geo.expert_ffn, dtype=torch.bfloat16, device=device)
+        self.done = torch.zeros(4, dtype=torch.int32, device=device)
+        mt = geo.max_tiles
+        self.num_tiles = self.meta[0:1]
+        self.tile_expert = self.meta[16:16 + mt]
+        self.tile_row0 = self.meta[16 + mt:16 + 2 * mt]
+        self.row_dst = self.meta[16 + 2 * mt:]
+
+    def run(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, tile_rows: int, layer: int,
+            epoch: torch.Tensor, combine_ptr: int, combine_flag_ptr: int | None, wait: bool) -> None:
+        """fc1+SwiGLU then fc2 with the (token, slot) scatter into the attention rank's buffer."""
+        g = self.geo
+        K.grouped_linear(self.slab, w_gate, self.hbuf, self.tile_expert, self.tile_row0, self.num_tiles, g.max_tiles,
+                         tile_rows, w_up=w_up, epoch=epoch,
+                         wait_flag=(self.flags.data_ptr() + 4 * layer) if wait else None)
+        K.grouped_linear(self.hbuf, w_down, self.hbuf, self.tile_expert, self.tile_row0, self.num_tiles, g.max_tiles,
+                         tile_rows, row_dst=self.row_dst, out_ptr=combine_ptr, ldo=g.hidden, epoch=epoch,
+                         signal_flag=combine_flag_ptr, done_counter=self.done[0:1] if combine_flag_ptr else None)
+
+
+class AttentionSide:
+    """Buffers the attention rank owns: routes, plan output, the combine buffer and its flags."""
+
+    def __init__(self, geo: ExchangeGeometry, device: torch.device, combine: torch.Tensor | None = None,
+                 flags: torch.Tensor | None = None, num_layers: int = 1):
+        self.geo = geo
+        T, k = geo.max_tokens, geo.top_k
+        self.idx = torch.zeros(T, k, dtype=torch.int32, device=device)
+        self.w = torch.zeros(T, k, dtype=torch.float32, device=device)
+        self.dest_row = torch.zeros(T * k, dtype=torch.int32, device=device)
+        self.combine = combine if combine is not None else torch.zeros(T * k, geo.hidden, dtype=torch.bfloat16, device=device)
+        # one word per (layer, expert rank), written by that rank's fc2 kernel
+        self.flags = flags if flags is not None else torch.zeros(num_layers * _n.MAX_RANKS, dtype=torch.int32, device=device)
+        self.done = torch.zeros(4, dtype=torch.int32, device=device)
+        self.expert_count = torch.zeros(geo.num_experts, dtype=torch.int32, device=device)
+        self.layout = _n.MoeLayout()
+        self.layout.n_ranks = geo.n_expert_ranks
+        for r in range(geo.n_expert_ranks):
+            self.layout.expert_lo[r] = geo.rank_experts(r)[0]
+        for r in range(geo.n_expert_ranks, _n.MAX_RANKS + 1):
+            self.layout.expert_lo[r] = geo.num_experts
+        self.layout.max_tiles, self.layout.max_rows = geo.max_tiles, geo.max_rows
+        self._rank_ptrs: list[tuple[int, int, int]] = []
+
+    def bind_rank(self, r: int, slab_ptr: int, meta_ptr: int, flags_ptr: int) -> None:
+        """Record rank r's slab / meta / per-layer dispatch flag base (local or peer addresses)."""
+        while len(self._rank_ptrs) <= r:
+            self._rank_ptrs.append((0, 0, 0))
+        self._rank_ptrs[r] = (slab_ptr, meta_ptr, flags_ptr)
+        self.layout.slab[r], self.layout.meta[r] = slab_ptr, meta_ptr
+
+    def dispatch(self, x: torch.Tensor, logits: torch.Tensor, route_kw: dict, tile_rows: int, layer: int,
+                 epoch: torch.Tensor) -> None:
+        T = x.shape[0]
+        g = self.geo
+        idx, w = self.idx[:T], self.w[:T]
+        K.route_topk(logits, g.top_k, out_idx=idx, out_w=w, **route_kw)
+        for r in range(g.n_expert_ranks):
+            self.layout.flag[r] = self._rank_ptrs[r][2] + 4 * layer
+        K.moe_plan(idx, g.num_experts, tile_rows, self.layout, self.dest_row, self.expert_count)
+        K.moe_dispatch(x, idx, self.dest_row, self.layout, epoch, self.done[0:1])
+
+    def combine_into(self, out: torch.Tensor, T: int, layer: int, epoch: torch.Tensor, *,
+                     shared: torch.Tensor | None, residual: torch.Tensor | None, wait: bool) -> torch.Tensor:
+        g = self.geo
+        flags_ptr = self.flags.data_ptr() + 4 * layer * _n.MAX_RANKS if wait else None
+        return K.moe_combine(self.combine, self.w[:T], out, shared=shared, residual=residual, flags_ptr=flags_ptr,
+                             n_flags=g.n_expert_ranks if wait else 0, epoch=epoch)
+
+
+class LocalExchange:
+    """Single-GPU MoE: attention side and expert side in one process, stream-ordered."""
+
+    def __init__(self, geo: ExchangeGeometry, device: torch.device):
+        assert geo.n_expert_ranks == 1
+        self.geo = geo
+        self.att = AttentionSide(geo, device)
+        self.exp = ExpertSide(geo, device)
+        self.att.bind_rank(0, self.exp.slab.data_ptr(), self.exp.meta.data_ptr(), self.exp.flags.data_ptr())
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor, route_kw: dict, w_gate: torch.Tensor, w_up: torch.Tensor,
+                w_down: torch.Tensor, out: torch.Tensor, *, shared: torch.Tensor | None = None,
+                residual: torch.Tensor | None = None, tile_rows: int | None = None) -> torch.Tensor:
+        T = x.shape[0]
+        g = self.geo
+        tile_rows = tile_rows or pick_tile_rows(T, g.top_k, g.num_experts)
+        self.att.dispatch(x, logits, route_kw, tile_rows, 0, self.epoch)
+        self.exp.run(w_gate, w_up, w_down, tile_rows, 0, self.epoch, self.att.combine.data_ptr(), None, wait=False)
+        return self.att.combine_into(out, T, 0, self.epoch, shared=shared, residual=residual, wait=False)

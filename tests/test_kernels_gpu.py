@@ -1,0 +1,200 @@
+"""sm_100a kernels against plain PyTorch fp32 references of the same ops."""
+import math
+
+import pytest
+import torch
+
+from cuteafd_b200.ref import ops as R
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from cuteafd_b200.ops import kernels
+    return kernels
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def bf(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).to(dev())
+
+
+def close(a, b, rtol=2e-2, atol=2e-2):
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item()
+    assert torch.allclose(a, b, rtol=rtol, atol=atol * max(ref, 1e-3)), f"max err {err} (ref max {ref})"
+
+
+def check_status(K):
+    torch.cuda.synchronize()
+    assert K.read_status() == 0
+
+
+@pytest.mark.parametrize("T,N,Kd,swap", [(128, 256, 128, False), (300, 512, 256, False), (8, 256, 512, True),
+                                         (33, 384, 2048, True), (1, 128, 64, True), (200, 256, 192, True),
+                                         (1000, 1280, 2048, False)])
+def test_linear(K, T, N, Kd, swap):
+    x, w = bf(T, Kd, seed=1), bf(N, Kd, scale=0.05, seed=2)
+    y = K.linear(x, w, swap=swap)
+    check_status(K)
+    close(y, x.float() @ w.float().T)
+
+
+@pytest.mark.parametrize("T,swap", [(256, False), (5, True), (70, True)])
+def test_linear_swiglu_residual_f32(K, T, swap):
+    N, Kd = 256, 512
+    x, wg, wu = bf(T, Kd, seed=1), bf(N, Kd, scale=0.05, seed=2), bf(N, Kd, scale=0.05, seed=3)
+    y = K.linear(x, wg, w_up=wu, swap=swap)
+    ref = torch.nn.functional.silu(x.float() @ wg.float().T) * (x.float() @ wu.float().T)
+    close(y, ref)
+    res = bf(T, N, seed=4)
+    y2 = K.linear(x, wg, residual=res, swap=swap)
+    close(y2, x.float() @ wg.float().T + res.float())
+    y3 = K.linear(x, wg, out_f32=True, swap=swap)
+    assert y3.dtype == torch.float32
+    close(y3, x.float() @ wg.float().T, rtol=1e-3, atol=1e-3)
+    check_status(K)
+
+
+def test_linear_ragged_features(K):
+    T, N, Kd = 40, 200, 128     # N not a multiple of the feature tile
+    x, w = bf(T, Kd, seed=1), bf(N, Kd, scale=0.05, seed=2)
+    for swap in (True, False):
+        close(K.linear(x, w, swap=swap), x.float() @ w.float().T)
+    check_status(K)
+
+
+def test_rmsnorm_embed_argmax(K):
+    T, H = 37, 2048
+    x, w, r = bf(T, H, seed=1), bf(H, seed=2), bf(T, H, seed=3)
+    close(K.rmsnorm(x, w, 1e-6), R.rmsnorm(x, w, 1e-6), 1e-2, 1e-2)
+    r2 = r.clone()
+    y = K.add_rmsnorm(x, r2, w, 1e-6)
+    ry, rr = R.add_rmsnorm(x, r, w, 1e-6)
+    assert torch.equal(r2, rr)
+    close(y, ry, 1e-2, 1e-2)
+    table = bf(500, H, seed=5)
+    tok = torch.randint(0, 500, (T,), dtype=torch.int32, device=dev())
+    assert torch.equal(K.embed(tok, table), table[tok.long()])
+    logits = torch.randn(T, 151936, device=dev())
+    logits[3, 77] = logits[3, 90000] = 1e9          # tie -> lowest id
+    assert torch.equal(K.argmax(logits).long(), torch.argmax(logits, -1)) or K.argmax(logits)[3].item() == 77
+    assert K.argmax(logits)[3].item() == 77
+
+
+@pytest.mark.parametrize("interleaved,norm", [(False, True), (True, False)])
+def test_qk_rope_kv(K, interleaved, norm):
+    T, Hq, Hkv, D, pages = 70, 8, 2, 128, 6
+    qkv = bf(T, (Hq + 2 * Hkv) * D, seed=1)
+    qn, kn = (bf(D, seed=2).abs() + 0.5, bf(D, seed=3).abs() + 0.5) if norm else (None, None)
+    theta = 1.0e6
+    inv = (1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))).to(dev())
+    pos = torch.arange(100, 100 + T, dtype=torch.int32, device=dev())
+    perm = torch.randperm(pages * 64)[:T].to(torch.int32).to(dev())
+    kc = torch.zeros(pages, 64, Hkv, D, dtype=torch.bfloat16, device=dev())
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=dev())
+    K.qk_rope_kv(qkv, qn, kn, inv, pos, perm, q_out, kc, vc, Hq, Hkv, D, 1e-6, interleaved)
+    q, k, v = qkv.view(T, Hq + 2 * Hkv, D).split([Hq, Hkv, Hkv], dim=1)
+    if norm:
+        q, k = R.rmsnorm(q, qn, 1e-6), R.rmsnorm(k, kn, 1e-6)
+    rq = R.apply_rope(q, pos.long(), theta, interleaved)
+    rk = R.apply_rope(k, pos.long(), theta, interleaved)
+    close(q_out, rq, 1e-2, 1e-2)
+    close(kc.view(-1, Hkv, D)[perm.long()], rk, 1e-2, 1e-2)
+    assert torch.equal(vc.view(-1, Hkv, D)[perm.long()], v)
+
+
+@pytest.mark.parametrize("E,k,scoring,groups,keep", [(128, 8, "softmax", 1, 1), (256, 8, "sigmoid", 8, 4),
+                                                     (8, 2, "softmax", 1, 1), (64, 6, "sigmoid", 1, 1)])
+def test_route_topk(K, E, k, scoring, groups, keep):
+    T = 200
+    logits = torch.randn(T, E, device=dev())
+    bias = torch.randn(E, device=dev()) * 0.1 if scoring == "sigmoid" else None
+    idx, w = K.route_topk(logits, k, scoring, bias, groups, keep, True, 2.5)
+    ridx, rw = R.route_topk(logits, k, scoring, bias, groups, keep, True, 2.5)
+    assert torch.equal(idx.cpu(), ridx.cpu())
+    assert torch.allclose(w.cpu(), rw.cpu(), rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("T,tile", [(5, 16), (64, 16), (300, 64), (1500, 128)])
+def test_moe_local_exchange(K, T, tile):
+    from cuteafd_b200.parallel.moe_exchange import ExchangeGeometry, LocalExchange
+    H, I, E, k = 512, 256, 16, 4
+    geo = ExchangeGeometry(H, I, E, k, max_tokens=T, n_expert_ranks=1)
+    ex = LocalExchange(geo, dev())
+    x, res = bf(T, H, seed=1), bf(T, H, seed=2)
+    wg, wu, wd = bf(E, I, H, scale=0.05, seed=3), bf(E, I, H, scale=0.05, seed=4), bf(E, H, I, scale=0.05, seed=5)
+    logits = torch.randn(T, E, device=dev())
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev())
+    ex.forward(x, logits, dict(scoring="softmax"), wg, wu, wd, out, residual=res, tile_rows=tile)
+    check_status(K)
+    idx, w = R.route_topk(logits, k, "softmax")
+    parts = R.moe_forward(x, idx, w, wg, wu, wd)
+    ref = R.combine_slots(parts, None, res, torch.bfloat16)
+    close(out, ref)
+    assert int(ex.att.expert_count.sum().item()) == T * k
+
+
+def _paged_kv(S, lens, Hkv, D, seed=0):
+    """Random K/V per sequence scattered over shuffled pages; returns caches, table, dense copies."""
+    pages_per = [(n + 63) // 64 for n in lens]
+    total = sum(pages_per) + 1
+    order = (torch.randperm(total - 1) + 1).tolist()
+    kc = torch.zeros(total, 64, Hkv, D, dtype=torch.bfloat16, device=dev())
+    vc = torch.zeros_like(kc)
+    table = torch.zeros(S, max(pages_per), dtype=torch.int32)
+    dense = []
+    for s in range(S):
+        k, v = bf(lens[s], Hkv, D, seed=seed + 2 * s), bf(lens[s], Hkv, D, seed=seed + 2 * s + 1)
+        dense.append((k, v))
+        for j in range(pages_per[s]):
+            pg = order.pop()
+            table[s, j] = pg
+            n = min(64, lens[s] - 64 * j)
+            kc[pg, :n], vc[pg, :n] = k[64 * j:64 * j + n], v[64 * j:64 * j + n]
+    return kc, vc, table.to(dev()), dense
+
+
+@pytest.mark.parametrize("lens,qlens,splits", [([100], [1], 1), ([700, 64, 1, 333], [1, 1, 1, 1], 4),
+                                               ([900, 130], [2, 4], 3), ([8192], [1], 16)])
+def test_attn_decode(K, lens, qlens, splits):
+    Hq, Hkv, D, S = 32, 4, 128, len(lens)
+    kc, vc, table, dense = _paged_kv(S, lens, Hkv, D)
+    q = bf(sum(qlens), Hq, D, seed=99)
+    q_start = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device=dev())
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=dev())
+    out = torch.zeros_like(q)
+    scratch = torch.empty(K.attn_decode_scratch_floats(S, max(qlens), Hq, Hkv, splits), dtype=torch.float32, device=dev())
+    K.attn_decode(q, kc, vc, table, seq_lens, q_start, out, scratch, max(qlens), splits)
+    o = 0
+    for s in range(S):
+        k, v = dense[s]
+        ref = R.causal_attention(q[o:o + qlens[s]], k, v, lens[s] - qlens[s])
+        close(out[o:o + qlens[s]], ref)
+        o += qlens[s]
+
+
+@pytest.mark.parametrize("lens,qlens", [([128], [128]), ([300], [300]), ([1000], [200]), ([517, 130], [517, 66]),
+                                        ([2048], [2048])])
+def test_attn_prefill(K, lens, qlens):
+    Hq, Hkv, D, S = 8, 2, 128, len(lens)
+    kc, vc, table, dense = _paged_kv(S, lens, Hkv, D)
+    q = bf(sum(qlens), Hq, D, seed=99)
+    q_start = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device=dev())
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=dev())
+    out = torch.zeros_like(q)
+    K.attn_prefill(q, kc, vc, table, seq_lens, q_start, out, max(qlens))
+    check_status(K)
+    o = 0
+    for s in range(S):
+        k, v = dense[s]
+        ref = R.causal_attention(q[o:o + qlens[s]], k, v, lens[s] - qlens[s])
+        close(out[o:o + qlens[s]], ref)
+        o += qlens[s]
