@@ -67,6 +67,7 @@ def cuda_lib():
         _sig(lib, "cafd_qk_rope_kv", [P, P, P, P, P, P, P, P, P, I, I, I, I, F, I, P])
         _sig(lib, "cafd_argmax", [P, P, I, I, I, P])
         _sig(lib, "cafd_bump_epoch", [P, P])
+        _sig(lib, "cafd_decode_advance", [P, P, P, P, P, P, I, I, I, P])
         _sig(lib, "cafd_route_topk", [P, P, P, P, I, I, I, I, I, I, I, F, P])
         _sig(lib, "cafd_moe_meta_ints", [I, I])
         _sig(lib, "cafd_moe_plan", [P, I, I, I, I, C.POINTER(MoeLayout), P, P, P, P])

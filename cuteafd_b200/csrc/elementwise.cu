@@ -197,6 +197,21 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
 // Step counter shared by the flag protocol: one increment per forward step, on the stream.
 __global__ void bump_epoch_kernel(uint32_t* epoch) { *epoch = *epoch + 1; }
 
+// Device-side bookkeeping between two decode steps of a captured graph: feed the selected token
+// back, advance position and KV length, and look the next KV slot up in the page table.
+__global__ void decode_advance_kernel(int* __restrict__ tokens, const int* __restrict__ next_tokens,
+                                      int* __restrict__ positions, int* __restrict__ seq_lens, int* __restrict__ slots,
+                                      const int* __restrict__ page_table, int max_pages, int S, int page_size) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= S) return;
+  tokens[i] = next_tokens[i];
+  const int pos = positions[i] + 1;
+  positions[i] = pos;
+  seq_lens[i] = pos + 1;
+  const int pg = pos / page_size;
+  slots[i] = pg < max_pages ? page_table[static_cast<size_t>(i) * max_pages + pg] * page_size + pos % page_size : -1;
+}
+
 }  // namespace cafd
 
 using namespace cafd;
@@ -244,6 +259,14 @@ extern "C" int cafd_qk_rope_kv(const void* qkv, const void* q_norm_w, const void
 extern "C" int cafd_argmax(const float* logits, int* out, int T, int V, int ld, cafd_stream_t s) {
   if (T <= 0) return 0;
   argmax_kernel<<<T, 1024, 0, static_cast<cudaStream_t>(s)>>>(logits, out, T, V, ld);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int cafd_decode_advance(int* tokens, const int* next_tokens, int* positions, int* seq_lens, int* slots,
+                                   const int* page_table, int max_pages, int S, int page_size, cafd_stream_t s) {
+  if (S <= 0) return 0;
+  decode_advance_kernel<<<(S + 127) / 128, 128, 0, static_cast<cudaStream_t>(s)>>>(
+      tokens, next_tokens, positions, seq_lens, slots, page_table, max_pages, S, page_size);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -171,6 +171,15 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
     return out
 
 
+def decode_advance(tokens: torch.Tensor, next_tokens: torch.Tensor, positions: torch.Tensor, seq_lens: torch.Tensor,
+                   slots: torch.Tensor, page_table: torch.Tensor, page_size: int = 64) -> None:
+    """Device-side step bookkeeping: token feedback, position/length +1, next KV slot."""
+    S, max_pages = page_table.shape
+    _n.check(_n.cuda_lib().cafd_decode_advance(tokens.data_ptr(), next_tokens.data_ptr(), positions.data_ptr(),
+                                               seq_lens.data_ptr(), slots.data_ptr(), page_table.data_ptr(), max_pages,
+                                               S, page_size, _stream()), "decode_advance")
+
+
 def bump_epoch(epoch: torch.Tensor) -> None:
     _n.check(_n.cuda_lib().cafd_bump_epoch(epoch.data_ptr(), _stream()), "bump_epoch")
 
