@@ -82,27 +82,33 @@ def main() -> None:
         if rank == 0:
             print(f"[bench] {msg}", file=sys.stderr, flush=True)
 
+    pages_per_seq = (args.prompt_len + 2 * (args.steps + warmup) + 128) // 64 + 2
+    num_pages = max(levels) * pages_per_seq + 8 * max(levels) + 64
+    handle = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         from cuteafd_b200.parallel.afd import build_afd
-        gen, sync, shutdown, parallelism = build_afd(cfg, dev, rank, world, max_tokens=args.prompt_len,
-                                                     max_seqs=max(levels), steps=args.steps + warmup,
-                                                     use_graphs=not args.no_graphs)
+        handle = build_afd(cfg, dev, rank, world, max_tokens=args.prompt_len, max_seqs=max(levels),
+                           num_pages=num_pages, pages_per_seq=pages_per_seq, use_graphs=not args.no_graphs)
+        gen, sync, parallelism = handle.generator, None, handle.parallelism
+        torch.cuda.synchronize()
+        dist.barrier()
+        log(f"afd ready: {parallelism}, {torch.cuda.memory_allocated()/2**30:.1f} GiB on the attention rank")
+        if handle.worker is not None:
+            handle.worker.serve()            # returns when the attention rank sends STOP
     else:
         from cuteafd_b200.models.gqa_moe import GqaMoeEngine, GqaMoeWeights, KvCache
         from cuteafd_b200.runtime.generate import Generator
         from cuteafd_b200.runtime.paged import PagePool
         t0 = time.time()
         W = GqaMoeWeights.random_init(cfg, dev, seed=0)
-        pages_per_seq = (args.prompt_len + 2 * (args.steps + warmup) + 128) // 64 + 2
-        num_pages = max(levels) * pages_per_seq + 8 * max(levels) + 64
         kv = KvCache(cfg, num_pages, dev)
         eng = GqaMoeEngine(cfg, W, kv, max_tokens=args.prompt_len, max_seqs=max(levels))
         gen = Generator(eng, PagePool(num_pages), pages_per_seq, max(levels), prefill_chunk=args.prompt_len,
                         use_graphs=not args.no_graphs)
         torch.cuda.synchronize()
         log(f"model + KV ready in {time.time()-t0:.1f}s, {torch.cuda.memory_allocated()/2**30:.1f} GiB")
-        sync, shutdown, parallelism = None, None, "attention+experts on 1 GPU"
+        sync, parallelism = None, "attention+experts on 1 GPU"
 
     out = None
     if gen is not None:                      # attention rank drives the card
@@ -134,7 +140,7 @@ def main() -> None:
             "extra": extra,
         }
     if world > 1:
-        shutdown()
+        handle.shutdown()
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0 and out is not None:

@@ -22,6 +22,8 @@ class GemmArgs(C.Structure):
         ("w_scale", C.c_void_p), ("x_scale", C.c_void_p),
         ("wait_flag", C.c_void_p), ("epoch", C.c_void_p), ("done_counter", C.c_void_p),
         ("signal_flag", C.c_void_p), ("status", C.c_void_p),
+        ("splitk_scratch", C.c_void_p), ("splitk_tickets", C.c_void_p),
+        ("splitk_scratch_floats", C.c_longlong), ("splitk_ticket_count", C.c_int),
         ("w_rows_total", C.c_longlong), ("x_rows_total", C.c_longlong),
         ("k", C.c_int), ("n_features", C.c_int), ("x_rows", C.c_int), ("ldo", C.c_int),
         ("w_rows_per_expert", C.c_int), ("w1_row_offset", C.c_int), ("max_x_tiles", C.c_int),
@@ -65,7 +67,8 @@ def cuda_lib():
         _sig(lib, "cafd_embed", [P, P, P, I, I, I, P])
         _sig(lib, "cafd_rmsnorm", [P, P, P, P, I, I, F, P])
         _sig(lib, "cafd_qk_rope_kv", [P, P, P, P, P, P, P, P, P, I, I, I, I, F, I, P])
-        _sig(lib, "cafd_argmax", [P, P, I, I, I, P])
+        _sig(lib, "cafd_argmax", [P, P, P, I, I, I, P])
+        _sig(lib, "cafd_argmax_slices", [])
         _sig(lib, "cafd_bump_epoch", [P, P])
         _sig(lib, "cafd_decode_advance", [P, P, P, P, P, P, I, I, I, P])
         _sig(lib, "cafd_route_topk", [P, P, P, P, I, I, I, I, I, I, I, F, P])

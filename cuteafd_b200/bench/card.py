@@ -89,11 +89,20 @@ def device_decode_loop(gen: Generator, seqs, last_tokens: list[int], steps: int,
         run = g.replay
     else:
         run = step
+    announce = getattr(eng, "announce", None) if gen.use_graphs else None
+    if announce and warmup > 1:
+        announce(S, warmup - 1, for_replay=True)
     for _ in range(max(0, warmup - 1)):
         run()
     if sync is not None:
         sync()
+    if announce:
+        announce(S, steps, timed=True, for_replay=True)
+    elif hasattr(eng, "announce"):
+        eng.announce(S, steps, timed=True)
     ms = _event_ms(lambda: [run() for _ in range(steps)])
+    if hasattr(eng, "collect_max"):
+        ms = eng.collect_max(ms)                 # max over ranks (expert ranks time the same steps)
     assert K.read_status() == 0, "a bounded wait ran out during the timed region"
     for s in seqs:                           # account for the tokens the device loop appended
         s.kv_len += warmup + steps

@@ -241,32 +241,29 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
   }
 }
 
+// One block per (tile, kv head, row): thread d walks the splits in order for its output element.
 __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict__ partial,
                                                          const int* __restrict__ q_start,
                                                          __nv_bfloat16* __restrict__ out, int Hq, int Hkv,
                                                          int tiles_per_seq, int splits) {
   const int group = Hq / Hkv;
   const int q_per_tile = 16 / group;
-  const int seq = blockIdx.x / tiles_per_seq, qt = blockIdx.x % tiles_per_seq, kvh = blockIdx.y;
+  const int seq = blockIdx.x / tiles_per_seq, qt = blockIdx.x % tiles_per_seq, kvh = blockIdx.y, r = blockIdx.z;
   const int q0 = q_start[seq], q_len = q_start[seq + 1] - q0;
-  const int first_q = qt * q_per_tile;
-  if (first_q >= q_len) return;
+  const int qi = qt * q_per_tile + r / group;
+  if (qi >= q_len) return;
+  const int d = threadIdx.x;
   const float* base = partial + (static_cast<size_t>(blockIdx.x) * Hkv + kvh) * splits * kPartialFloats;
-  for (int i = threadIdx.x; i < 16 * kD; i += blockDim.x) {
-    const int r = i / kD, d = i % kD;
-    const int qi = first_q + r / group;
-    if (qi >= q_len) continue;
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, base[s * kPartialFloats + 16 * kD + r]);
-    float L = 0.f, O = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float m = base[s * kPartialFloats + 16 * kD + r];
-      const float f = (m == -INFINITY) ? 0.f : exp2f(m - M);
-      L += base[s * kPartialFloats + 16 * kD + 16 + r] * f;
-      O += base[s * kPartialFloats + r * kD + d] * f;
-    }
-    out[(static_cast<size_t>(q0 + qi) * Hq + kvh * group + r % group) * kD + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, __ldg(base + s * kPartialFloats + 16 * kD + r));
+  float L = 0.f, O = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float m = __ldg(base + s * kPartialFloats + 16 * kD + r);
+    const float f = (m == -INFINITY) ? 0.f : exp2f(m - M);
+    L += __ldg(base + s * kPartialFloats + 16 * kD + 16 + r) * f;
+    O += __ldg(base + s * kPartialFloats + r * kD + d) * f;
   }
+  out[(static_cast<size_t>(q0 + qi) * Hq + kvh * group + r % group) * kD + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
 }
 
 }  // namespace cafd
@@ -305,7 +302,7 @@ extern "C" int cafd_attn_decode(const void* q, const void* k_cache, const void* 
       static_cast<const __nv_bfloat16*>(v_cache), page_table, seq_lens, q_start, static_cast<__nv_bfloat16*>(out),
       scratch, max_pages, Hq, Hkv, tiles_per_seq, splits, scale * 1.4426950408889634f);
   if (splits > 1) {
-    dim3 g2(num_seqs * tiles_per_seq, Hkv);
+    dim3 g2(num_seqs * tiles_per_seq, Hkv, 16);
     attn_merge_kernel<<<g2, 128, 0, st>>>(scratch, q_start, static_cast<__nv_bfloat16*>(out), Hq, Hkv, tiles_per_seq,
                                           splits);
   }

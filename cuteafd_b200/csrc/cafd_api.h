@@ -42,6 +42,10 @@ typedef struct {
   uint32_t* done_counter;    // local counter used to elect the last CTA (must start at 0)
   uint32_t* signal_flag;     // optional: set to *epoch (release, system scope) when all stores are done
   uint32_t* status;          // device status word (0 = ok)
+  float* splitk_scratch;     // optional split-K scratch (swap == 1): fp32 partial tiles
+  uint32_t* splitk_tickets;  // optional split-K arrival counters, zero between launches
+  long long splitk_scratch_floats;
+  int splitk_ticket_count;
   long long w_rows_total;
   long long x_rows_total;
   int k;

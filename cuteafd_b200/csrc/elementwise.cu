@@ -159,25 +159,17 @@ __global__ void __launch_bounds__(128) qk_rope_kv_kernel(const __nv_bfloat16* __
 }
 
 // ---- greedy selection: argmax, ties to the lowest id, NaN never wins ----------------------------
-__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int T,
-                                                      int V, int ld) {
-  const int t = blockIdx.x;
-  if (t >= T) return;
-  const float* row = logits + static_cast<size_t>(t) * ld;
-  float best = -INFINITY;
-  int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i];
-    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-  }
+// Two stages so a single row still uses the whole GPU: stage 1 reduces a slice of the vocabulary
+// per block into (value, index) candidates, stage 2 reduces the candidates of each row.
+__device__ __forceinline__ void argmax_merge(float& best, int& bi, float ov, int oi) {
+  if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+}
+__device__ __forceinline__ void argmax_block_reduce(float& best, int& bi) {
   __shared__ float sv[32];
   __shared__ int si[32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_merge(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
   if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
   __syncthreads();
   if (threadIdx.x < 32) {
@@ -185,13 +177,30 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
     best = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
     bi = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-    }
-    if (threadIdx.x == 0) out[t] = (bi == 0x7fffffff) ? 0 : bi;
+    for (int o = 16; o > 0; o >>= 1)
+      argmax_merge(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
   }
+}
+__global__ void __launch_bounds__(256) argmax_stage1_kernel(const float* __restrict__ logits, float* __restrict__ cand_v,
+                                                            int* __restrict__ cand_i, int V, int ld, int slices) {
+  const int t = blockIdx.y, sl = blockIdx.x;
+  const int per = (V + slices - 1) / slices;
+  const int lo = sl * per, hi = min(V, lo + per);
+  const float* row = logits + static_cast<size_t>(t) * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) argmax_merge(best, bi, row[i], i);
+  argmax_block_reduce(best, bi);
+  if (threadIdx.x == 0) { cand_v[t * slices + sl] = best; cand_i[t * slices + sl] = bi; }
+}
+__global__ void __launch_bounds__(64) argmax_stage2_kernel(const float* __restrict__ cand_v, const int* __restrict__ cand_i,
+                                                           int* __restrict__ out, int slices) {
+  const int t = blockIdx.x;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < slices; i += blockDim.x) argmax_merge(best, bi, cand_v[t * slices + i], cand_i[t * slices + i]);
+  argmax_block_reduce(best, bi);
+  if (threadIdx.x == 0) out[t] = (bi == 0x7fffffff) ? 0 : bi;
 }
 
 // Step counter shared by the flag protocol: one increment per forward step, on the stream.
@@ -256,9 +265,17 @@ extern "C" int cafd_qk_rope_kv(const void* qkv, const void* q_norm_w, const void
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int cafd_argmax(const float* logits, int* out, int T, int V, int ld, cafd_stream_t s) {
+// scratch: 2 * T * slices 4-byte words (candidate values then indices); slices = cafd_argmax_slices().
+extern "C" int cafd_argmax_slices(void) { return 64; }
+extern "C" int cafd_argmax(const float* logits, int* out, void* scratch, int T, int V, int ld, cafd_stream_t s) {
   if (T <= 0) return 0;
-  argmax_kernel<<<T, 1024, 0, static_cast<cudaStream_t>(s)>>>(logits, out, T, V, ld);
+  if (!scratch) return -10;
+  const int slices = 64;
+  float* cv = static_cast<float*>(scratch);
+  int* ci = reinterpret_cast<int*>(cv + static_cast<size_t>(T) * slices);
+  cudaStream_t st = static_cast<cudaStream_t>(s);
+  argmax_stage1_kernel<<<dim3(slices, T), 256, 0, st>>>(logits, cv, ci, V, ld, slices);
+  argmax_stage2_kernel<<<T, 64, 0, st>>>(cv, ci, out, slices);
   return static_cast<int>(cudaGetLastError());
 }
 

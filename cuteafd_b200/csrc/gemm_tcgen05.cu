@@ -37,6 +37,10 @@ struct GemmDev {
   uint32_t* done_counter;
   uint32_t* signal_flag;
   uint32_t* status;
+  float* splitk_scratch;      // [units][acc cols][128] fp32 partials (weights-on-M orientation only)
+  uint32_t* splitk_tickets;   // one arrival counter per output tile, all zero between launches
+  int splitk_max_units;
+  int splitk_target;          // CTAs worth of work to aim for (the SM count)
   int num_k_blocks;
   int n_features;
   int x_rows;
@@ -82,6 +86,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
   __shared__ uint64_t tempty_bar[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int s_x_tiles;
+  __shared__ int s_last_unit;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -99,7 +104,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
     // A peer may still be writing the slab and the tile list: wait for its flag first.
     int xt = p.x_tiles_static;
     bool ok = true;
-    if (p.wait_flag) ok = wait_flag_ge(p.wait_flag, *p.epoch, p.status);
+    if (p.wait_flag) {
+      ok = wait_flag_ge(p.wait_flag, *p.epoch, p.status);
+      // The rows were written with ordinary stores by another GPU; the TMA engine reads them
+      // through the async proxy, so order the acquire before those reads.
+      asm volatile("fence.proxy.async;" ::: "memory");
+    }
     if (p.num_x_tiles) xt = ok ? *reinterpret_cast<const volatile int*>(p.num_x_tiles) : 0;
     s_x_tiles = ok ? xt : 0;
   }
@@ -112,8 +122,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   const int x_tiles = s_x_tiles;
-  const int total_tiles = x_tiles * p.w_tiles;
+  const int base_tiles = x_tiles * p.w_tiles;
   const int nkb = p.num_k_blocks;
+  // Split-K: when the output tiles alone cannot occupy the GPU, every tile's K range is cut into
+  // `splits` units; partial sums go to scratch and the last unit to arrive adds them in split
+  // order (fixed order, so the result does not depend on scheduling).
+  int splits = 1;
+  if (kSwap && p.splitk_scratch && base_tiles > 0 && base_tiles <= p.splitk_max_units) {
+    splits = p.splitk_target / base_tiles;
+    if (splits > nkb / 4) splits = nkb / 4;
+    if (splits > p.splitk_max_units / base_tiles) splits = p.splitk_max_units / base_tiles;
+    if (splits < 1) splits = 1;
+  }
+  const int total_tiles = base_tiles * splits;   // work units
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -124,13 +145,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int unit = blockIdx.x; ok && unit < total_tiles; unit += gridDim.x) {
+        const int tile = unit / splits, split = unit - tile * splits;
         const int xt = tile % x_tiles;
         const int wt = tile / x_tiles;
         const int x_row0 = p.tile_row0 ? p.tile_row0[xt] : xt * kBX;
         const int expert = p.tile_expert ? p.tile_expert[xt] : 0;
         const int w_row0 = expert * p.w_rows_per_expert + wt * kBW;
-        for (int kb = 0; kb < nkb; ++kb) {
+        const int kb0 = split * nkb / splits, kb1 = (split + 1) * nkb / splits;
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
           uint8_t* st = smem + stage * Cfg::kStageBytes;
           mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
@@ -150,11 +173,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int unit = blockIdx.x; ok && unit < total_tiles; unit += gridDim.x) {
+        const int split = unit % splits;
+        const int kb0 = split * nkb / splits, kb1 = (split + 1) * nkb / splits;
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, p.status, kTimeoutTmemEmpty)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d0 = tmem_base + acc * Cfg::kAccCols;
-        for (int kb = 0; kb < nkb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, p.status, kTimeoutFullBarrier)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sw = smem_u32(smem + stage * Cfg::kStageBytes);
@@ -162,7 +187,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
 #pragma unroll
           for (int k4 = 0; k4 < kBK / kUmmaK; ++k4) {
             const uint32_t koff = k4 * kUmmaK * 2;
-            const uint32_t accum = (kb | k4) ? 1u : 0u;
+            const uint32_t accum = ((kb - kb0) | k4) ? 1u : 0u;
             if (kSwap) {
               // A = weights (128 features), B = tokens (kBX)
               umma_f16(d0, smem_desc_k_sw128(sw + koff), smem_desc_k_sw128(sx + koff), idesc, accum);
@@ -188,13 +213,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+    for (int unit = blockIdx.x; ok && unit < total_tiles; unit += gridDim.x) {
+      const int tile = unit / splits, split = unit - tile * splits;
       const int xt = tile % x_tiles;
       const int wt = tile / x_tiles;
       const int x_row0 = p.tile_row0 ? p.tile_row0[xt] : xt * kBX;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, p.status, kTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * Cfg::kAccCols;
+      const float* part0 = nullptr;   // split-K: first partial of this tile, set for the finishing unit
+      if (kSwap && splits > 1) {
+        const int fl = quad * 32 + lane;
+        float* mine = p.splitk_scratch + static_cast<size_t>(tile * splits + split) * (Cfg::kAccCols * 128);
+#pragma unroll 1
+        for (int c0 = 0; c0 < Cfg::kAccCols; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld_32x16(t0 + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) mine[(c0 + j) * 128 + fl] = __uint_as_float(r[j]);
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (quad == 0 && lane == 0) {
+          const uint32_t prev = atomicAdd(p.splitk_tickets + tile, 1u);
+          s_last_unit = (prev == static_cast<uint32_t>(splits - 1)) ? 1 : 0;
+          if (s_last_unit) p.splitk_tickets[tile] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool last = s_last_unit != 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // everyone has read the flag before it is reused
+        if (!last) {
+          tc_fence_before();
+          mbar_arrive(&tempty_bar[acc]);
+          if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+          continue;
+        }
+        __threadfence();
+        part0 = p.splitk_scratch + static_cast<size_t>(tile * splits) * (Cfg::kAccCols * 128);
+      }
       if (!kSwap) {
         // thread = token row; columns = features
         const int row = x_row0 + quad * 32 + lane;
@@ -277,19 +334,37 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
         const bool f_ok = f < p.n_features;
 #pragma unroll 1
         for (int c0 = 0; c0 < kBX; c0 += 16) {
-          uint32_t r[16];
-          tmem_ld_32x16(t0 + c0, r);
           float v[16];
-          if (kDual) {
-            uint32_t u[16];
-            tmem_ld_32x16(t0 + kBX + c0, u);
-            tmem_ld_wait();
+          if (part0) {
+            // finishing unit of a split tile: add the partials in split order
+            const int fl = quad * 32 + lane;
+            float g[16], u[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = silu(__uint_as_float(r[j])) * __uint_as_float(u[j]);
+            for (int j = 0; j < 16; ++j) { g[j] = 0.f; u[j] = 0.f; }
+            for (int sp = 0; sp < splits; ++sp) {
+              const float* ps = part0 + static_cast<size_t>(sp) * (Cfg::kAccCols * 128);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                g[j] += __ldcg(ps + (c0 + j) * 128 + fl);
+                if (kDual) u[j] += __ldcg(ps + (kBX + c0 + j) * 128 + fl);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = kDual ? silu(g[j]) * u[j] : g[j];
           } else {
-            tmem_ld_wait();
+            uint32_t r[16];
+            tmem_ld_32x16(t0 + c0, r);
+            if (kDual) {
+              uint32_t u[16];
+              tmem_ld_32x16(t0 + kBX + c0, u);
+              tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+              for (int j = 0; j < 16; ++j) v[j] = silu(__uint_as_float(r[j])) * __uint_as_float(u[j]);
+            } else {
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+            }
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -374,6 +449,10 @@ static int launch(const cafd_gemm_args* a, cudaStream_t stream) {
   p.w1_row_offset = a->w1_row_offset;
   p.w_tiles = (a->n_features + kBW - 1) / kBW;
   p.out_f32 = a->out_f32;
+  p.splitk_scratch = nullptr;
+  p.splitk_tickets = nullptr;
+  p.splitk_max_units = 0;
+  p.splitk_target = 0;
   const bool grouped = a->tile_expert != nullptr;
   p.x_tiles_static = grouped ? a->max_x_tiles : (a->x_rows + kBX - 1) / kBX;
 
@@ -386,6 +465,18 @@ static int launch(const cafd_gemm_args* a, cudaStream_t stream) {
   const long long max_tiles = static_cast<long long>(p.x_tiles_static) * p.w_tiles;
   int grid = static_cast<int>(max_tiles < sms ? max_tiles : sms);
   if (grid < 1) grid = 1;
+  if (kSwap && a->splitk_scratch && a->splitk_tickets) {
+    const long long per_unit = static_cast<long long>(Cfg::kAccCols) * 128;
+    long long units = a->splitk_scratch_floats / per_unit;
+    if (units > a->splitk_ticket_count) units = a->splitk_ticket_count;
+    if (units >= 2) {
+      p.splitk_scratch = a->splitk_scratch;
+      p.splitk_tickets = a->splitk_tickets;
+      p.splitk_max_units = static_cast<int>(units);
+      p.splitk_target = sms;
+      grid = sms;
+    }
+  }
   auto kern = gemm_kernel<kSwap, kDual, kBX, kBW>;
   static bool attr_set = false;
   if (!attr_set) {

@@ -175,30 +175,50 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
     if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
   }
   __syncthreads();
-  if (threadIdx.x < L.n_ranks) {
-    const int r = threadIdx.x;
-    int* meta = L.meta[r];
-    int* tile_expert = meta + kMetaHeader;
+  // Exclusive scan of the per-expert tile counts (one thread per expert, Hillis-Steele in shared
+  // memory), then every expert writes its own tiles: no serial walk over the experts.
+  __shared__ int scan[kMaxExperts];
+  for (int e = threadIdx.x; e < kMaxExperts; e += blockDim.x)
+    scan[e] = e < E ? (counts[e] + tile_rows - 1) / tile_rows : 0;
+  __syncthreads();
+  for (int d = 1; d < kMaxExperts; d <<= 1) {
+    int v = 0;
+    const int e = threadIdx.x;
+    if (e < kMaxExperts && e >= d) v = scan[e - d];
+    __syncthreads();
+    if (e < kMaxExperts) scan[e] += v;
+    __syncthreads();
+  }
+  // scan[e] is now inclusive; tiles before expert e inside its rank = scan[e-1] - scan[lo-1]
+  if (threadIdx.x < E) {
+    const int e = threadIdx.x;
+    int r = 0;
+    while (r + 1 < L.n_ranks && e >= L.expert_lo[r + 1]) ++r;
+    const int lo = L.expert_lo[r];
+    const int before_rank = lo > 0 ? scan[lo - 1] : 0;
+    const int before = (e > 0 ? scan[e - 1] : 0) - before_rank;
+    const int nt = scan[e] - (e > 0 ? scan[e - 1] : 0);
+    rank_of[e] = r;
+    seg_off[e] = before * tile_rows;
+    int* tile_expert = L.meta[r] + kMetaHeader;
     int* tile_row0 = tile_expert + L.max_tiles;
-    int off = 0, tiles = 0;
     bool overflow = false;
-    for (int e = L.expert_lo[r]; e < L.expert_lo[r + 1]; ++e) {
-      rank_of[e] = r;
-      seg_off[e] = off;
-      const int nt = (counts[e] + tile_rows - 1) / tile_rows;
-      for (int j = 0; j < nt; ++j) {
-        if (tiles < L.max_tiles && off + tile_rows <= L.max_rows) {
-          tile_expert[tiles] = e - L.expert_lo[r];
-          tile_row0[tiles] = off;
-          ++tiles;
-        } else {
-          overflow = true;
-        }
-        off += tile_rows;
+    for (int j = 0; j < nt; ++j) {
+      const int ti = before + j;
+      if (ti < L.max_tiles && (ti + 1) * tile_rows <= L.max_rows) {
+        tile_expert[ti] = e - lo;
+        tile_row0[ti] = ti * tile_rows;
+      } else {
+        overflow = true;
       }
     }
-    meta[0] = tiles;
-    meta[1] = off < L.max_rows ? off : L.max_rows;
+    if (e == L.expert_lo[r + 1] - 1) {   // last expert of the rank publishes the totals
+      int tiles = before + nt;
+      if (tiles > L.max_tiles) tiles = L.max_tiles;
+      if (tiles * tile_rows > L.max_rows) tiles = L.max_rows / tile_rows;
+      L.meta[r][0] = tiles;
+      L.meta[r][1] = tiles * tile_rows;
+    }
     if (overflow && status) atomicCAS(status, 0u, static_cast<uint32_t>(kBadArgument));
   }
   __syncthreads();

@@ -53,8 +53,10 @@ class GqaMoeWeights:
         self.layers: list[LayerWeights] = []
 
     @staticmethod
-    def from_params(cfg: ModelConfig, p: dict[str, torch.Tensor], device: torch.device) -> "GqaMoeWeights":
-        """Build from a Hugging Face style name -> tensor dictionary (any float dtype)."""
+    def from_params(cfg: ModelConfig, p: dict[str, torch.Tensor], device: torch.device,
+                    with_experts: bool = True) -> "GqaMoeWeights":
+        """Build from a Hugging Face style name -> tensor dictionary (any float dtype).
+        ``with_experts=False`` leaves the routed experts out (they live on expert ranks)."""
         def t(name: str) -> torch.Tensor:
             return p[name].to(device=device, dtype=torch.bfloat16).contiguous()
 
@@ -73,7 +75,7 @@ class GqaMoeWeights:
                 L.router = t(m + "gate.weight")
                 b = p.get(m + "gate.e_score_correction_bias")
                 L.router_bias = None if b is None else b.to(device=device, dtype=torch.float32).contiguous()
-                for dst, src in (("w_gate", "gate_proj"), ("w_up", "up_proj"), ("w_down", "down_proj")):
+                for dst, src in ((("w_gate", "gate_proj"), ("w_up", "up_proj"), ("w_down", "down_proj")) if with_experts else ()):
                     setattr(L, dst, torch.stack([t(m + f"experts.{e}.{src}.weight") for e in range(cfg.num_experts)]).contiguous())
                 if cfg.num_shared_experts:
                     L.s_gate, L.s_up, L.s_down = (t(m + f"shared_experts.{n}_proj.weight") for n in ("gate", "up", "down"))
@@ -83,7 +85,8 @@ class GqaMoeWeights:
         return W
 
     @staticmethod
-    def random_init(cfg: ModelConfig, device: torch.device, seed: int = 0, std: float = 0.02) -> "GqaMoeWeights":
+    def random_init(cfg: ModelConfig, device: torch.device, seed: int = 0, std: float = 0.02,
+                    with_experts: bool = True) -> "GqaMoeWeights":
         """N(0, std) weights generated on the device, layer by layer (no host copy of the model)."""
         g = torch.Generator(device=device).manual_seed(seed)
 
@@ -108,8 +111,9 @@ class GqaMoeWeights:
             if cfg.is_moe_layer(i):
                 L.router = w(cfg.num_experts, H)
                 L.router_bias = torch.zeros(cfg.num_experts, dtype=torch.float32, device=device) if cfg.router_bias else None
-                L.w_gate, L.w_up = w(cfg.num_experts, cfg.expert_ffn, H), w(cfg.num_experts, cfg.expert_ffn, H)
-                L.w_down = w(cfg.num_experts, H, cfg.expert_ffn)
+                if with_experts:
+                    L.w_gate, L.w_up = w(cfg.num_experts, cfg.expert_ffn, H), w(cfg.num_experts, cfg.expert_ffn, H)
+                    L.w_down = w(cfg.num_experts, H, cfg.expert_ffn)
                 if cfg.num_shared_experts:
                     inter = cfg.expert_ffn * cfg.num_shared_experts
                     L.s_gate, L.s_up, L.s_down = w(inter, H), w(inter, H), w(H, inter)
@@ -153,7 +157,8 @@ class Workspace:
 class GqaMoeEngine:
     """Single-GPU engine (attention and experts on the same device)."""
 
-    def __init__(self, cfg: ModelConfig, weights: GqaMoeWeights, kv: KvCache, max_tokens: int, max_seqs: int = 64):
+    def __init__(self, cfg: ModelConfig, weights: GqaMoeWeights, kv: KvCache, max_tokens: int, max_seqs: int = 64,
+                 build_moe: bool = True):
         assert cfg.attention == "gqa" and cfg.head_dim == 128
         self.cfg, self.W, self.kv = cfg, weights, kv
         self.device = weights.embed.device
@@ -162,7 +167,8 @@ class GqaMoeEngine:
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, dtype=torch.float32) / cfg.head_dim))
         self.inv_freq = inv.to(self.device)
         self.moe = None
-        if cfg.num_experts:
+        self.pre_moe = None          # hook(layer) called before each MoE layer's exchange
+        if cfg.num_experts and build_moe:
             geo = ExchangeGeometry(cfg.hidden, cfg.expert_ffn, cfg.num_experts, cfg.top_k, max_tokens, 1)
             self.moe = LocalExchange(geo, self.device)
         self.route_kw = dict(scoring=cfg.scoring, num_groups=cfg.num_groups, topk_groups=cfg.topk_groups,
@@ -212,6 +218,8 @@ class GqaMoeEngine:
             self.launches += 2
         K.linear(ws.x[:T], L.router, out=ws.router[:T, :cfg.num_experts], out_f32=True)
         kw = dict(self.route_kw, bias=L.router_bias)
+        if self.pre_moe is not None:
+            self.pre_moe(i)
         self.moe.forward(ws.x[:T], ws.router[:T, :cfg.num_experts], kw, L.w_gate, L.w_up, L.w_down, ws.h[:T],
                          shared=shared, residual=ws.h[:T])
         self.launches += 7

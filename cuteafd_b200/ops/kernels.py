@@ -55,6 +55,32 @@ def set_wait_limit_ns(ns: int) -> None:
 
 
 # ---- GEMM ------------------------------------------------------------------------------------------
+_splitk: dict[tuple[int, int], tuple[torch.Tensor, torch.Tensor]] = {}
+_splitk_lane = 0                     # callers running lanes on separate streams switch this
+SPLITK_SCRATCH_FLOATS = 8 << 20      # 32 MiB of fp32 partial tiles per (device, stream)
+SPLITK_TICKETS = 4096
+
+
+def splitk_buffers(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Scratch + arrival counters for split-K, one set per (device, lane): launches that overlap
+    on the GPU (different streams) must not share them; see ``set_splitk_lane``."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _splitk_lane)
+    if key not in _splitk:
+        _splitk[key] = (torch.empty(SPLITK_SCRATCH_FLOATS, dtype=torch.float32, device=device),
+                        torch.zeros(SPLITK_TICKETS, dtype=torch.int32, device=device))
+    return _splitk[key]
+
+
+def set_splitk_lane(lane: int) -> None:
+    global _splitk_lane
+    _splitk_lane = lane
+
+
+def _attach_splitk(a: "_n.GemmArgs", device: torch.device) -> None:
+    sc, tk = splitk_buffers(device)
+    a.splitk_scratch, a.splitk_tickets = sc.data_ptr(), tk.data_ptr()
+    a.splitk_scratch_floats, a.splitk_ticket_count = sc.numel(), tk.numel()
+
 def pick_token_tile(rows: int) -> int:
     """Token tile for the weights-on-M orientation."""
     for b in (16, 32, 64, 128):
@@ -64,7 +90,8 @@ def pick_token_tile(rows: int) -> int:
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *, w_up: torch.Tensor | None = None,
-           residual: torch.Tensor | None = None, out_f32: bool = False, swap: bool | None = None) -> torch.Tensor:
+           residual: torch.Tensor | None = None, out_f32: bool = False, swap: bool | None = None,
+           split_k: bool = True) -> torch.Tensor:
     """y = x @ w.T (bf16 in, fp32 accumulate).  With ``w_up``: y = silu(x @ w.T) * (x @ w_up.T).
 
     x [T, K], w [N, K].  ``swap`` picks the orientation (default: weights on M when T <= 128).
@@ -90,6 +117,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, *,
     if swap and T > 128:
         a.bx = 128
     a.out_f32, a.fp8, a.num_sms = int(out.dtype == torch.float32), 0, num_sms()
+    if swap and split_k:
+        _attach_splitk(a, x.device)
     _n.check(_n.cuda_lib().cafd_gemm(C.byref(a), _stream()), "cafd_gemm")
     return out
 
@@ -99,7 +128,7 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_exp
                    w_up: torch.Tensor | None = None, row_dst: torch.Tensor | None = None,
                    wait_flag: int | None = None, epoch: torch.Tensor | None = None,
                    signal_flag: int | None = None, done_counter: torch.Tensor | None = None,
-                   out_ptr: int | None = None, ldo: int | None = None) -> None:
+                   out_ptr: int | None = None, ldo: int | None = None, split_k: bool = True) -> None:
     """Expert-grouped GEMM over an expert-sorted slab.
 
     x [rows, K] slab, w [E, N, K] stacked expert weights, tiles described by device arrays.
@@ -122,6 +151,8 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_exp
     swap = tile_rows < 128
     a.swap, a.dual, a.bx = int(swap), int(w_up is not None), tile_rows
     a.out_f32, a.fp8, a.num_sms = 0, 0, num_sms()
+    if swap and split_k:
+        _attach_splitk(a, x.device)
     _n.check(_n.cuda_lib().cafd_gemm(C.byref(a), _stream()), "cafd_gemm(grouped)")
 
 
@@ -163,11 +194,21 @@ def qk_rope_kv(qkv: torch.Tensor, q_norm: torch.Tensor | None, k_norm: torch.Ten
              "qk_rope_kv")
 
 
+_argmax_scratch: dict[int, torch.Tensor] = {}
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Greedy selection per row: ties to the lowest id, NaN never selected."""
     T, V = logits.shape
     if out is None:
         out = torch.empty(T, dtype=torch.int32, device=logits.device)
-    _n.check(_n.cuda_lib().cafd_argmax(logits.data_ptr(), out.data_ptr(), T, V, logits.stride(0), _stream()), "argmax")
+    L = _n.cuda_lib()
+    need = 2 * T * L.cafd_argmax_slices()
+    d = logits.device.index or 0
+    if d not in _argmax_scratch or _argmax_scratch[d].numel() < need:
+        _argmax_scratch[d] = torch.empty(max(need, 2 * 64 * 64), dtype=torch.int32, device=logits.device)
+    _n.check(L.cafd_argmax(logits.data_ptr(), out.data_ptr(), _argmax_scratch[d].data_ptr(), T, V, logits.stride(0),
+                           _stream()), "argmax")
     return out
 
 

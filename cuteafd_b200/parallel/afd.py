@@ -1,0 +1,266 @@
+"""Attention/FFN disaggregation over one NVLink domain: rank 0 runs the backbone (attention,
+router, head, KV cache); ranks 1..N-1 hold the routed experts, partitioned by expert id.
+
+Data path (no NCCL, no host hop): every rank maps one symmetric buffer of every other rank
+(``torch.distributed._symmetric_memory`` does the handle exchange).  The attention rank's plan and
+dispatch kernels store tile lists and token rows straight into the owners' buffers and publish a
+per-layer step number; the owners' grouped tcgen05 GEMMs wait for it, and the fc2 epilogue stores
+each (token, slot) row straight into the attention rank's combine buffer and publishes the step
+number back; the combine kernel waits for every owner.  Kernel waits are bounded and report
+through the status word.
+
+Control path: one small NCCL broadcast per forward call (op, tokens, steps) so expert ranks know
+how many layer sequences to launch; a run of decode steps is announced once and then proceeds on
+device flags only.
+
+The reference's coordinator/expertd split over RoCE is the same idea with a host transport worker
+in the middle (rust/crates/cuteafd-daemon/src/shared/experts/service.rs:22-135;
+rust/crates/cuteafd-daemon/src/shared/spark_waves.rs:1188-1517).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from .._native import lib as _n
+from ..config import ModelConfig
+from ..ops import kernels as K
+from .moe_exchange import AttentionSide, ExchangeGeometry, ExpertSide, pick_tile_rows
+
+OP_STOP, OP_STEPS, OP_TIMED = 0, 1, 2
+
+
+def _align(x: int, a: int = 1024) -> int:
+    return (x + a - 1) // a * a
+
+
+@dataclass
+class SymLayout:
+    """Byte offsets inside every rank's symmetric buffer (same layout on all ranks)."""
+    slab: int
+    meta: int
+    dflags: int      # per-layer dispatch flags (written by the attention rank)
+    combine: int
+    cflags: int      # per-(layer, rank) completion flags (written by expert ranks)
+    total: int
+
+    @staticmethod
+    def build(geo: ExchangeGeometry, num_layers: int) -> "SymLayout":
+        o = 0
+        slab = o; o = _align(o + geo.max_rows * geo.hidden * 2)
+        meta = o; o = _align(o + geo.meta_ints * 4)
+        dflags = o; o = _align(o + num_layers * 4)
+        combine = o; o = _align(o + geo.max_tokens * geo.top_k * geo.hidden * 2)
+        cflags = o; o = _align(o + num_layers * _n.MAX_RANKS * 4)
+        return SymLayout(slab, meta, dflags, combine, cflags, o)
+
+
+class SymmetricHeap:
+    def __init__(self, nbytes: int, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group or dist.group.WORLD
+        try:
+            symm_mem.enable_symm_mem_for_group(group.group_name)
+        except Exception:
+            pass
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        torch.cuda.synchronize()
+        dist.barrier()
+
+    def view(self, offset: int, nbytes: int, dtype: torch.dtype) -> torch.Tensor:
+        return self.buf[offset:offset + nbytes].view(dtype)
+
+
+class RemoteExchange:
+    """Attention-rank half: same interface as ``LocalExchange`` with experts on other GPUs."""
+
+    def __init__(self, geo: ExchangeGeometry, heap: SymmetricHeap, lay: SymLayout, num_layers: int, rank: int):
+        dev = heap.buf.device
+        self.geo, self.heap, self.lay = geo, heap, lay
+        combine = heap.view(lay.combine, geo.max_tokens * geo.top_k * geo.hidden * 2, torch.bfloat16).view(-1, geo.hidden)
+        cflags = heap.view(lay.cflags, num_layers * _n.MAX_RANKS * 4, torch.int32)
+        self.att = AttentionSide(geo, dev, combine=combine, flags=cflags, num_layers=num_layers)
+        for r in range(geo.n_expert_ranks):
+            base = heap.ptrs[1 + r]
+            self.att.bind_rank(r, base + lay.slab, base + lay.meta, base + lay.dflags)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.layer = 0
+
+    def forward(self, x, logits, route_kw, w_gate, w_up, w_down, out, *, shared=None, residual=None, tile_rows=None):
+        T = x.shape[0]
+        g = self.geo
+        tile_rows = tile_rows or pick_tile_rows(T, g.top_k, g.num_experts)
+        self.att.dispatch(x, logits, route_kw, tile_rows, self.layer, self.epoch)
+        return self.att.combine_into(out, T, self.layer, self.epoch, shared=shared, residual=residual, wait=True)
+
+
+class AfdAttentionEngine:
+    """Wraps a ``GqaMoeEngine`` whose MoE layers go through ``RemoteExchange``."""
+
+    def __init__(self, cfg: ModelConfig, weights, kv, max_tokens: int, max_seqs: int, heap: SymmetricHeap,
+                 lay: SymLayout, geo: ExchangeGeometry):
+        from ..models.gqa_moe import GqaMoeEngine
+        self.inner = GqaMoeEngine(cfg, weights, kv, max_tokens, max_seqs, build_moe=False)
+        self.cfg, self.device = cfg, self.inner.device
+        self.moe_layers = [i for i in range(cfg.num_layers) if cfg.is_moe_layer(i)]
+        self.ex = RemoteExchange(geo, heap, lay, len(self.moe_layers), 0)
+        self.inner.moe = self.ex
+        self.inner.pre_moe = self._pre_moe
+        self.ctrl = torch.zeros(4, dtype=torch.int64, device=self.device)
+        self._announced = 0
+        self.logits, self.next_tokens = self.inner.logits, self.inner.next_tokens
+
+    @property
+    def launches(self) -> int:
+        return self.inner.launches
+
+    def _pre_moe(self, layer: int) -> None:
+        self.ex.layer = self.moe_layers.index(layer)
+
+    def announce(self, T: int, steps: int, timed: bool = False, for_replay: bool = False) -> None:
+        """Tell the expert ranks how many forward steps follow (each with T tokens).  Eager calls of
+        ``forward`` announce themselves; graph replays must be announced by the caller."""
+        self.ctrl.copy_(torch.tensor([OP_TIMED if timed else OP_STEPS, T, steps, 0], dtype=torch.int64))
+        dist.broadcast(self.ctrl, src=0)
+        if not for_replay:
+            self._announced += steps
+
+    def forward(self, b):
+        if not torch.cuda.is_current_stream_capturing():
+            if self._announced == 0:
+                self.announce(b.tokens.shape[0], 1)
+            self._announced -= 1
+        K.bump_epoch(self.ex.epoch)
+        return self.inner.forward(b)
+
+    def greedy(self, logits):
+        return self.inner.greedy(logits)
+
+    def collect_max(self, ms: float) -> float:
+        t = torch.tensor([ms], dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def shutdown(self) -> None:
+        self.ctrl.copy_(torch.tensor([OP_STOP, 0, 0, 0], dtype=torch.int64))
+        dist.broadcast(self.ctrl, src=0)
+
+
+class ExpertWorker:
+    """Expert-rank process: owns experts [lo, hi) of every MoE layer and serves announced steps."""
+
+    def __init__(self, cfg: ModelConfig, expert_weights: list[tuple[torch.Tensor, torch.Tensor, torch.Tensor]],
+                 heap: SymmetricHeap, lay: SymLayout, geo: ExchangeGeometry, rank: int, use_graphs: bool = True):
+        dev = heap.buf.device
+        self.cfg, self.geo, self.rank, self.er = cfg, geo, rank, rank - 1
+        self.weights = expert_weights
+        self.n_layers = len(expert_weights)
+        slab = heap.view(lay.slab, geo.max_rows * geo.hidden * 2, torch.bfloat16).view(geo.max_rows, geo.hidden)
+        meta = heap.view(lay.meta, geo.meta_ints * 4, torch.int32)
+        flags = heap.view(lay.dflags, self.n_layers * 4, torch.int32)
+        self.side = ExpertSide(geo, dev, slab=slab, meta=meta, flags=flags, num_layers=self.n_layers)
+        self.combine_ptr = heap.ptrs[0] + lay.combine
+        self.cflags_ptr = heap.ptrs[0] + lay.cflags
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.ctrl = torch.zeros(4, dtype=torch.int64, device=dev)
+        self.use_graphs = use_graphs
+        self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.device = dev
+        self.steps_served = 0
+
+    def _step(self, tile_rows: int) -> None:
+        K.bump_epoch(self.epoch)
+        for l, (wg, wu, wd) in enumerate(self.weights):
+            flag = self.cflags_ptr + 4 * (l * _n.MAX_RANKS + self.er)
+            self.side.run(wg, wu, wd, tile_rows, l, self.epoch, self.combine_ptr, flag, wait=True)
+
+    def serve(self) -> None:
+        g = self.geo
+        while True:
+            dist.broadcast(self.ctrl, src=0)
+            op, T, steps, _ = (int(v) for v in self.ctrl.tolist())
+            if op == OP_STOP:
+                return
+            tile_rows = pick_tile_rows(T, g.top_k, g.num_experts)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(steps):
+                self._step(tile_rows)
+            b.record()
+            self.steps_served += steps
+            if op == OP_TIMED:
+                torch.cuda.synchronize()
+                t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=self.device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            st = K.read_status()
+            if st:
+                raise RuntimeError(f"expert rank {self.rank}: bounded wait ran out (status {st})")
+
+
+def random_expert_weights(cfg: ModelConfig, lo: int, hi: int, device: torch.device, seed: int = 0, std: float = 0.02):
+    g = torch.Generator(device=device).manual_seed(seed * 1000 + lo)
+    out = []
+    for i in range(cfg.num_layers):
+        if not cfg.is_moe_layer(i):
+            continue
+        def w(*shape):
+            t = torch.empty(*shape, dtype=torch.bfloat16, device=device)
+            t.normal_(0.0, std, generator=g)
+            return t
+        out.append((w(hi - lo, cfg.expert_ffn, cfg.hidden), w(hi - lo, cfg.expert_ffn, cfg.hidden),
+                    w(hi - lo, cfg.hidden, cfg.expert_ffn)))
+    return out
+
+
+@dataclass
+class AfdHandle:
+    generator: object | None      # rank 0: a Generator over the attention engine
+    worker: ExpertWorker | None   # other ranks
+    parallelism: str
+
+    def shutdown(self) -> None:
+        if self.generator is not None:
+            self.generator.engine.shutdown()
+
+
+def build_afd(cfg: ModelConfig, device: torch.device, rank: int, world: int, *, max_tokens: int, max_seqs: int,
+              num_pages: int, pages_per_seq: int, use_graphs: bool = True, params: dict | None = None,
+              seed: int = 0) -> AfdHandle:
+    """Create this rank's half.  ``params`` (HF-style dict) gives real weights; otherwise random."""
+    os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
+    n_exp = world - 1
+    geo = ExchangeGeometry(cfg.hidden, cfg.expert_ffn, cfg.num_experts, cfg.top_k, max_tokens, n_exp)
+    n_moe = sum(1 for i in range(cfg.num_layers) if cfg.is_moe_layer(i))
+    lay = SymLayout.build(geo, n_moe)
+    heap = SymmetricHeap(lay.total, device)
+    par = f"afd: attention on 1 GPU + experts ep{n_exp}"
+    if rank == 0:
+        from ..models.gqa_moe import GqaMoeWeights, KvCache
+        from ..runtime.generate import Generator
+        from ..runtime.paged import PagePool
+        if params is not None:
+            W = GqaMoeWeights.from_params(cfg, params, device, with_experts=False)
+        else:
+            W = GqaMoeWeights.random_init(cfg, device, seed=seed, with_experts=False)
+        kv = KvCache(cfg, num_pages, device)
+        eng = AfdAttentionEngine(cfg, W, kv, max_tokens, max_seqs, heap, lay, geo)
+        gen = Generator(eng, PagePool(num_pages), pages_per_seq, max_seqs, prefill_chunk=max_tokens, use_graphs=use_graphs)
+        return AfdHandle(gen, None, par)
+    lo, hi = geo.rank_experts(rank - 1)
+    if params is not None:
+        ew = []
+        for i in range(cfg.num_layers):
+            if not cfg.is_moe_layer(i):
+                continue
+            m = f"model.layers.{i}.mlp.experts."
+            ew.append(tuple(torch.stack([params[f"{m}{e}.{n}_proj.weight"].to(device=device, dtype=torch.bfloat16)
+                                         for e in range(lo, hi)]).contiguous() for n in ("gate", "up", "down")))
+    else:
+        ew = random_expert_weights(cfg, lo, hi, device, seed)
+    return AfdHandle(None, ExpertWorker(cfg, ew, heap, lay, geo, rank, use_graphs), par)

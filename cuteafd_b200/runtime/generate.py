@@ -123,6 +123,8 @@ class Generator:
                     out = self.engine.greedy(self.engine.forward(batch))
                 self.graphs[S] = (g, out)
             g, out = self.graphs[S]
+            if hasattr(self.engine, "announce"):
+                self.engine.announce(S, 1, for_replay=True)
             g.replay()
         else:
             out = self.engine.greedy(self.engine.forward(self._decode_batch(b, S)))
