@@ -64,6 +64,29 @@ typedef struct {
 } cafd_gemm_args;
 
 int cafd_gemm(const cafd_gemm_args* a, cafd_stream_t stream);
+
+// ---- greedy selection ----------------------------------------------------------------------------
+// out[t] = argmax over logits[t, 0:V] (row pitch ld, fp32); ties go to the lowest index and NaN is
+// never selected.  `scratch` holds 2 * T * cafd_argmax_slices() 4-byte words, owned by the caller.
+int cafd_argmax_slices(void);
+int cafd_argmax(const float* logits, int* out, void* scratch, int T, int V, int ld, cafd_stream_t stream);
+
+// The same selection for callers that cannot allocate device memory at all and therefore cannot
+// hand over scratch: a serving loop that runs after its memory plan is sealed, a host program
+// that owns the CUDA allocator and loads this library as a plug-in, a plain C caller without a
+// tensor library.  This entry point has no counterpart in the reference.
+//   * It calls no cudaMalloc / cudaFree and no allocating library routine.  Its scratch is a
+//     512 KiB array inside the library's device image; each GPU that loads the library keeps it
+//     until the process exits.
+//   * At most cafd_argmax_noalloc_max_rows() rows (1024) per call; more returns -20 and launches
+//     nothing.
+//   * The first call on each device looks the array's device address up (the device must be
+//     current).  Make that first call before starting any stream capture.
+//   * All calls on a device share the one array.  Two calls whose kernels can overlap on the GPU
+//     (different streams, no ordering between them) race; order them.  The array keeps the last
+//     call's candidates; nothing needs clearing, because every word read is written first.
+int cafd_argmax_noalloc_max_rows(void);
+int cafd_argmax_noalloc(const float* logits, int* out, int T, int V, int ld, cafd_stream_t stream);
 int cafd_gemm_set_wait_limit_ns(unsigned long long ns);
 
 #ifdef __cplusplus

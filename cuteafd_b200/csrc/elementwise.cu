@@ -279,6 +279,59 @@ extern "C" int cafd_argmax(const float* logits, int* out, void* scratch, int T, 
   return static_cast<int>(cudaGetLastError());
 }
 
+// ---- greedy selection without any allocation ---------------------------------------------------------
+// Same two-stage selection as cafd_argmax, for callers that cannot provide scratch: code running
+// where the allocator must not be entered (a serving loop whose memory was planned up front and
+// whose ledger forbids late cudaMalloc, a plug-in loaded into a host process that owns the device
+// heap, a C caller with no tensor library).  The candidate buffer lives in a file-scope device
+// array instead; every GPU that loads this library carries it (512 KiB) until the process exits.
+namespace cafd {
+constexpr int kNoAllocArgmaxMaxRows = 1024;
+constexpr int kNoAllocArgmaxSlices = 64;
+static __device__ __align__(256) unsigned char g_noalloc_argmax_scratch[kNoAllocArgmaxMaxRows * kNoAllocArgmaxSlices * 8];
+}  // namespace cafd
+
+#include <mutex>
+
+// In host code the array's name is only a handle for the runtime, not a device address.  The
+// device address is looked up once per device (with that device current) and cached.
+static int noalloc_argmax_scratch(void** out) {
+  static std::mutex mu;
+  static void* by_device[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= 64) return -21;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!by_device[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, cafd::g_noalloc_argmax_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    by_device[dev] = p;
+  }
+  *out = by_device[dev];
+  return 0;
+}
+
+extern "C" int cafd_argmax_noalloc_max_rows(void) { return cafd::kNoAllocArgmaxMaxRows; }
+
+extern "C" int cafd_argmax_noalloc(const float* logits, int* out, int T, int V, int ld, cafd_stream_t s) {
+  if (T <= 0) return 0;
+  if (T > kNoAllocArgmaxMaxRows) return -20;   // more rows than the built-in scratch holds
+  if (!logits || !out || V <= 0 || ld < V) return -10;
+  void* scratch = nullptr;
+  const int rc = noalloc_argmax_scratch(&scratch);
+  if (rc) return rc;
+  const int slices = kNoAllocArgmaxSlices;
+  float* cv = static_cast<float*>(scratch);
+  int* ci = reinterpret_cast<int*>(cv + static_cast<size_t>(T) * slices);
+  cudaStream_t st = static_cast<cudaStream_t>(s);
+  // Stage 1 writes every candidate that stage 2 reads, so nothing has to be cleared between calls.
+  argmax_stage1_kernel<<<dim3(slices, T), 256, 0, st>>>(logits, cv, ci, V, ld, slices);
+  argmax_stage2_kernel<<<T, 64, 0, st>>>(cv, ci, out, slices);
+  return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" int cafd_decode_advance(int* tokens, const int* next_tokens, int* positions, int* seq_lens, int* slots,
                                    const int* page_table, int max_pages, int S, int page_size, cafd_stream_t s) {
   if (S <= 0) return 0;
