@@ -1,0 +1,196 @@
+"""Kernel microbenchmarks with roofline fractions (CUDA-event timing, L2 flushed between runs).
+
+    python -m cuteafd_b200.bench.microbench gemm --tokens 8192 --features 5120 --k 2048
+    python -m cuteafd_b200.bench.microbench attn-prefill --len 8192
+    python -m cuteafd_b200.bench.microbench attn-decode --seqs 32 --len 8192
+    python -m cuteafd_b200.bench.microbench moe --tokens 1,16,128,1024,8192 --hidden 7168 --ffn 2048 \
+        --experts 256 --top-k 8 --scoring sigmoid
+
+Small kernels (a few microseconds) are timed as a CUDA graph of many launches cycling over more
+weight copies than fit in L2, so host launch cost does not pollute the number.  Roofline
+denominators come from MEASURED_PEAKS.json at the repository root when present (measured copy
+bandwidth and cuBLAS bf16 throughput), else 6650 GB/s and 1590 TFLOP/s.
+
+The MoE mode is the dispatch -> expert -> combine benchmark of the reference's exchange path
+(rust/crates/cuteafd-daemon/src/families/glm5/engine.rs:2489-2512 plus the expert worker), here
+plan + dispatch + grouped fc1/SwiGLU + grouped fc2/combine kernels on one GPU or, under torchrun,
+with the experts on the other ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from ..ops import kernels as K
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks() -> dict:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "kind": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "kind": "fallback"}
+
+
+_flush = None
+
+
+def flush_l2(dev) -> None:
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    _flush.zero_()
+
+
+def time_eager(fn, dev, iters: int = 10, warm: int = 3) -> float:
+    """Median milliseconds of one call, L2 flushed before each timed call."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush_l2(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return sorted(ts)[len(ts) // 2]
+
+
+def time_graph(fns, reps: int = 5) -> float:
+    """Median milliseconds per call for a list of calls captured into one CUDA graph."""
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in fns:
+            f()
+    g.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); g.replay(); b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return sorted(ts)[len(ts) // 2] / len(fns)
+
+
+def report(name: str, ms: float, flops: float, byts: float, pk: dict) -> dict:
+    tf, gb = flops / ms / 1e9, byts / ms / 1e6
+    r = {"case": name, "us": round(ms * 1e3, 2), "tflops": round(tf, 1), "gbs": round(gb, 0),
+         "frac_compute": round(tf / pk["bf16_tflops"], 3), "frac_hbm": round(gb / pk["hbm_gbs"], 3), "of": pk["kind"]}
+    print(json.dumps(r), flush=True)
+    return r
+
+
+def bench_gemm(a, dev, pk):
+    T, N, Kd = a.tokens, a.features, a.k
+    x = torch.randn(T, Kd, device=dev).bfloat16()
+    out = torch.empty(T, N, dtype=torch.bfloat16, device=dev)
+    per = N * Kd * 2 * (2 if a.dual else 1)
+    copies = 1 if T > 256 else max(2, min(24, int(200e6 // per) + 1))
+    ws = [(torch.randn(N, Kd, device=dev) * 0.02).bfloat16() for _ in range(copies)]
+    us = [(torch.randn(N, Kd, device=dev) * 0.02).bfloat16() if a.dual else None for _ in range(copies)]
+    if T > 256:
+        ms = time_eager(lambda: K.linear(x, ws[0], out=out, w_up=us[0]), dev, iters=a.iters)
+    else:
+        ms = time_graph([(lambda w=w, u=u: K.linear(x, w, out=out, w_up=u)) for w, u in zip(ws, us)] * 2)
+    flops = 2.0 * T * N * Kd * (2 if a.dual else 1)
+    report(f"gemm T={T} N={N} K={Kd} dual={a.dual}", ms, flops, per + (T * Kd + T * N) * 2, pk)
+    assert K.read_status() == 0
+
+
+def bench_attn_prefill(a, dev, pk):
+    Hq, Hkv, D, n = a.heads, a.kv_heads, 128, a.len
+    pages = (n + 63) // 64 + 1
+    kc = torch.randn(pages, 64, Hkv, D, device=dev).bfloat16()
+    vc = torch.randn_like(kc)
+    kc[0] = 0; vc[0] = 0
+    table = torch.arange(1, pages, dtype=torch.int32, device=dev).view(1, -1).contiguous()
+    q = torch.randn(n, Hq, D, device=dev).bfloat16()
+    out = torch.empty_like(q)
+    sl = torch.tensor([n], dtype=torch.int32, device=dev)
+    qs = torch.tensor([0, n], dtype=torch.int32, device=dev)
+    ms = time_eager(lambda: K.attn_prefill(q, kc, vc, table, sl, qs, out, n), dev, iters=a.iters)
+    report(f"attn_prefill len={n} Hq={Hq} Hkv={Hkv}", ms, 4.0 * n * n * D * Hq / 2, (2 * n * Hq * D + 2 * n * Hkv * D) * 2, pk)
+    assert K.read_status() == 0
+
+
+def bench_attn_decode(a, dev, pk):
+    Hq, Hkv, D, S, n = a.heads, a.kv_heads, 128, a.seqs, a.len
+    pps = (n + 63) // 64
+    pages = S * pps + 1
+    kcs = [torch.randn(pages, 64, Hkv, D, device=dev).bfloat16() for _ in range(2 if S >= 16 else 4)]
+    table = (torch.arange(S * pps, dtype=torch.int32, device=dev) + 1).view(S, pps).contiguous()
+    q = torch.randn(S, Hq, D, device=dev).bfloat16()
+    out = torch.empty_like(q)
+    sl = torch.full((S,), n, dtype=torch.int32, device=dev)
+    qs = torch.arange(S + 1, dtype=torch.int32, device=dev)
+    splits = a.splits or K.attn_decode_splits(S, 1, Hkv, pps)
+    scratch = torch.empty(K.attn_decode_scratch_floats(S, 1, Hq, Hkv, splits), dtype=torch.float32, device=dev)
+    ms = time_graph([(lambda kc=kc: K.attn_decode(q, kc, kc, table, sl, qs, out, scratch, 1, splits)) for kc in kcs] * 3)
+    report(f"attn_decode seqs={S} len={n} splits={splits}", ms, 4.0 * S * n * D * Hq, S * n * Hkv * D * 2 * 2.0, pk)
+
+
+def bench_moe(a, dev, pk):
+    from ..parallel.moe_exchange import ExchangeGeometry, LocalExchange
+    H, I, E, k = a.hidden, a.ffn, a.experts, a.top_k
+    sets = []
+    n_sets = 1 if E * 3 * H * I * 2 > 2e9 else 2
+    for _ in range(n_sets):
+        sets.append(tuple((torch.randn(E, r, c, device=dev) * 0.02).bfloat16() for r, c in ((I, H), (I, H), (H, I))))
+    kw = dict(scoring=a.scoring, num_groups=a.groups, topk_groups=a.topk_groups)
+    for T in [int(t) for t in a.tokens.split(",")]:
+        ex = LocalExchange(ExchangeGeometry(H, I, E, k, T, 1), dev)
+        x = torch.randn(T, H, device=dev).bfloat16()
+        res = torch.randn(T, H, device=dev).bfloat16()
+        logits = torch.randn(T, E, device=dev)
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        fns = [(lambda s=s: ex.forward(x, logits, kw, s[0], s[1], s[2], out, residual=res)) for s in sets]
+        if T <= 256:
+            ms = time_graph(fns * 3)
+        else:
+            ms = time_eager(fns[0], dev, iters=a.iters)
+        idx = ex.att.idx[:T]
+        active = int(torch.unique(idx).numel())
+        byts = active * 3 * H * I * 2 + T * k * H * 2 * 2 + T * k * I * 2 * 2 + T * k * H * 2 * 2
+        report(f"moe T={T} H={H} I={I} E={E} k={k} active={active}", ms, 2.0 * T * k * 3 * H * I, byts, pk)
+        assert K.read_status() == 0
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--tokens", type=int, default=8192); g.add_argument("--features", type=int, default=5120)
+    g.add_argument("--k", type=int, default=2048); g.add_argument("--dual", action="store_true")
+    p = sub.add_parser("attn-prefill")
+    p.add_argument("--len", type=int, default=8192); p.add_argument("--heads", type=int, default=32)
+    p.add_argument("--kv-heads", type=int, default=4)
+    d = sub.add_parser("attn-decode")
+    d.add_argument("--seqs", type=int, default=32); d.add_argument("--len", type=int, default=8192)
+    d.add_argument("--heads", type=int, default=32); d.add_argument("--kv-heads", type=int, default=4)
+    d.add_argument("--splits", type=int, default=0)
+    m = sub.add_parser("moe")
+    m.add_argument("--tokens", default="1,16,128,1024,8192"); m.add_argument("--hidden", type=int, default=2048)
+    m.add_argument("--ffn", type=int, default=768); m.add_argument("--experts", type=int, default=128)
+    m.add_argument("--top-k", type=int, default=8); m.add_argument("--scoring", default="softmax")
+    m.add_argument("--groups", type=int, default=1); m.add_argument("--topk-groups", type=int, default=1)
+    for s in (g, p, d, m):
+        s.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    pk = peaks()
+    {"gemm": bench_gemm, "attn-prefill": bench_attn_prefill, "attn-decode": bench_attn_decode, "moe": bench_moe}[a.cmd](a, dev, pk)
+
+
+if __name__ == "__main__":
+    main()
