@@ -58,6 +58,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ page_table, const int* __restrict__ seq_lens,
     const int* __restrict__ q_start, __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int max_pages,
     int Hq, int Hkv, int tiles_per_seq, int splits, float scale_log2) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ __align__(128) uint8_t smem[];
   const int group = Hq / Hkv;
   const int q_per_tile = 16 / group;
@@ -246,6 +248,8 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict
                                                          const int* __restrict__ q_start,
                                                          __nv_bfloat16* __restrict__ out, int Hq, int Hkv,
                                                          int tiles_per_seq, int splits) {
+  pdl_wait();
+  pdl_trigger();
   const int group = Hq / Hkv;
   const int q_per_tile = 16 / group;
   const int seq = blockIdx.x / tiles_per_seq, qt = blockIdx.x % tiles_per_seq, kvh = blockIdx.y, r = blockIdx.z;
@@ -297,13 +301,13 @@ extern "C" int cafd_attn_decode(const void* q, const void* k_cache, const void* 
     attr = true;
   }
   dim3 grid(num_seqs * tiles_per_seq, Hkv, splits);
-  attn_decode_kernel<<<grid, 128, smem, st>>>(
+  launch_pdl(attn_decode_kernel, grid, dim3(128), smem, st, 
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
       static_cast<const __nv_bfloat16*>(v_cache), page_table, seq_lens, q_start, static_cast<__nv_bfloat16*>(out),
       scratch, max_pages, Hq, Hkv, tiles_per_seq, splits, scale * 1.4426950408889634f);
   if (splits > 1) {
     dim3 g2(num_seqs * tiles_per_seq, Hkv, 16);
-    attn_merge_kernel<<<g2, 128, 0, st>>>(scratch, q_start, static_cast<__nv_bfloat16*>(out), Hq, Hkv, tiles_per_seq,
+    launch_pdl(attn_merge_kernel, g2, dim3(128), 0, st, scratch, q_start, static_cast<__nv_bfloat16*>(out), Hq, Hkv, tiles_per_seq,
                                           splits);
   }
   return static_cast<int>(cudaGetLastError());

@@ -53,6 +53,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_ready, pv_done;
   __shared__ uint32_t tmem_slot;
 
+  pdl_wait();      // the page table, lengths and Q come from kernels earlier in the stream
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq = blockIdx.z;
   const int head = blockIdx.y;
@@ -323,7 +325,7 @@ extern "C" int cafd_attn_prefill(const void* q, const void* k_cache, const void*
     attr = true;
   }
   dim3 grid((max_q_len + kBQ - 1) / kBQ, Hq, num_seqs);
-  attn_prefill_kernel<<<grid, kPrefillThreads, kPrefillSmem, static_cast<cudaStream_t>(s)>>>(tq, tk, tv, p);
+  launch_pdl(attn_prefill_kernel, grid, dim3(kPrefillThreads), kPrefillSmem, static_cast<cudaStream_t>(s), tq, tk, tv, p);
   return static_cast<int>(cudaGetLastError());
 }
 

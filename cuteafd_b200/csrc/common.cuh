@@ -50,6 +50,14 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ---- programmatic dependent launch -------------------------------------------------------------
+// Every kernel of this library is launched with programmatic stream serialization: it may start
+// while its predecessor in the stream is still draining, so launch latency and the prologue
+// (barrier init, TMEM allocation, descriptor prefetch) overlap the predecessor's tail.  A kernel
+// must not read anything a predecessor wrote, nor write anything, before pdl_wait() returns.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier --------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -288,6 +296,35 @@ __device__ __forceinline__ float warp_max(float v) {
   extern "C" int name(unsigned long long ns) {                                            \
     return static_cast<int>(cudaMemcpyToSymbol(cafd::g_wait_limit_ns, &ns, sizeof(ns))); \
   }
+
+// Launch with programmatic stream serialization (set CAFD_PDL=0 in the environment to disable).
+#include <cstdlib>
+#include <utility>
+namespace cafd {
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = std::getenv("CAFD_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+}  // namespace cafd
 
 // Host-side error plumbing shared by the C entry points.
 #define CAFD_CHECK_CUDA(expr)                       \

@@ -13,6 +13,8 @@ namespace cafd {
 // ---- embedding gather: bit-identical row copy ---------------------------------------------------
 __global__ void embed_kernel(const int* __restrict__ tokens, const uint4* __restrict__ table, uint4* __restrict__ out,
                              int T, int row_vec, int vocab) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   if (t >= T) return;
   int tok = tokens[t];
@@ -29,6 +31,8 @@ template <int kVecPerThread>
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint4* __restrict__ x, uint4* __restrict__ residual,
                                                       const uint4* __restrict__ w, uint4* __restrict__ y, int T,
                                                       int H, float eps) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   if (t >= T) return;
   const int nvec = H / 8;
@@ -97,6 +101,8 @@ __global__ void __launch_bounds__(128) qk_rope_kv_kernel(const __nv_bfloat16* __
                                                          __nv_bfloat16* __restrict__ k_cache,
                                                          __nv_bfloat16* __restrict__ v_cache, int T, int Hq, int Hkv,
                                                          float eps, int interleaved) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int D = 128;
   const int heads = Hq + 2 * Hkv;
   const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -183,6 +189,8 @@ __device__ __forceinline__ void argmax_block_reduce(float& best, int& bi) {
 }
 __global__ void __launch_bounds__(256) argmax_stage1_kernel(const float* __restrict__ logits, float* __restrict__ cand_v,
                                                             int* __restrict__ cand_i, int V, int ld, int slices) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.y, sl = blockIdx.x;
   const int per = (V + slices - 1) / slices;
   const int lo = sl * per, hi = min(V, lo + per);
@@ -195,6 +203,8 @@ __global__ void __launch_bounds__(256) argmax_stage1_kernel(const float* __restr
 }
 __global__ void __launch_bounds__(64) argmax_stage2_kernel(const float* __restrict__ cand_v, const int* __restrict__ cand_i,
                                                            int* __restrict__ out, int slices) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   float best = -INFINITY;
   int bi = 0x7fffffff;
@@ -204,13 +214,19 @@ __global__ void __launch_bounds__(64) argmax_stage2_kernel(const float* __restri
 }
 
 // Step counter shared by the flag protocol: one increment per forward step, on the stream.
-__global__ void bump_epoch_kernel(uint32_t* epoch) { *epoch = *epoch + 1; }
+__global__ void bump_epoch_kernel(uint32_t* epoch) {
+  pdl_wait();
+  pdl_trigger();
+  *epoch = *epoch + 1;
+}
 
 // Device-side bookkeeping between two decode steps of a captured graph: feed the selected token
 // back, advance position and KV length, and look the next KV slot up in the page table.
 __global__ void decode_advance_kernel(int* __restrict__ tokens, const int* __restrict__ next_tokens,
                                       int* __restrict__ positions, int* __restrict__ seq_lens, int* __restrict__ slots,
                                       const int* __restrict__ page_table, int max_pages, int S, int page_size) {
+  pdl_wait();
+  pdl_trigger();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= S) return;
   tokens[i] = next_tokens[i];
@@ -229,7 +245,7 @@ extern "C" int cafd_embed(const int* tokens, const void* table, void* out, int T
                           cafd_stream_t s) {
   if (T <= 0) return 0;
   if (H % 8) return -10;
-  embed_kernel<<<T, 128, 0, static_cast<cudaStream_t>(s)>>>(tokens, static_cast<const uint4*>(table),
+  launch_pdl(embed_kernel, dim3(T), dim3(128), 0, static_cast<cudaStream_t>(s), tokens, static_cast<const uint4*>(table),
                                                             static_cast<uint4*>(out), T, H / 8, vocab);
   return static_cast<int>(cudaGetLastError());
 }
@@ -244,10 +260,10 @@ extern "C" int cafd_rmsnorm(const void* x, void* residual, const void* w, void* 
   uint4* rp = static_cast<uint4*>(residual);
   const uint4* wp = static_cast<const uint4*>(w);
   uint4* yp = static_cast<uint4*>(y);
-  if (nvec <= 256) rmsnorm_kernel<1><<<T, 256, 0, st>>>(xp, rp, wp, yp, T, H, eps);
-  else if (nvec <= 512) rmsnorm_kernel<2><<<T, 256, 0, st>>>(xp, rp, wp, yp, T, H, eps);
-  else if (nvec <= 1024) rmsnorm_kernel<4><<<T, 256, 0, st>>>(xp, rp, wp, yp, T, H, eps);
-  else rmsnorm_kernel<8><<<T, 256, 0, st>>>(xp, rp, wp, yp, T, H, eps);
+  if (nvec <= 256) launch_pdl(rmsnorm_kernel<1>, dim3(T), dim3(256), 0, st, xp, rp, wp, yp, T, H, eps);
+  else if (nvec <= 512) launch_pdl(rmsnorm_kernel<2>, dim3(T), dim3(256), 0, st, xp, rp, wp, yp, T, H, eps);
+  else if (nvec <= 1024) launch_pdl(rmsnorm_kernel<4>, dim3(T), dim3(256), 0, st, xp, rp, wp, yp, T, H, eps);
+  else launch_pdl(rmsnorm_kernel<8>, dim3(T), dim3(256), 0, st, xp, rp, wp, yp, T, H, eps);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -258,7 +274,7 @@ extern "C" int cafd_qk_rope_kv(const void* qkv, const void* q_norm_w, const void
   if (D != 128) return -10;
   const int warps = T * (Hq + 2 * Hkv);
   const int blocks = (warps + 3) / 4;
-  qk_rope_kv_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(s)>>>(
+  launch_pdl(qk_rope_kv_kernel, dim3(blocks), dim3(128), 0, static_cast<cudaStream_t>(s), 
       static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(q_norm_w),
       static_cast<const __nv_bfloat16*>(k_norm_w), inv_freq, positions, slots, static_cast<__nv_bfloat16*>(q_out),
       static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), T, Hq, Hkv, eps, interleaved);
@@ -274,8 +290,8 @@ extern "C" int cafd_argmax(const float* logits, int* out, void* scratch, int T, 
   float* cv = static_cast<float*>(scratch);
   int* ci = reinterpret_cast<int*>(cv + static_cast<size_t>(T) * slices);
   cudaStream_t st = static_cast<cudaStream_t>(s);
-  argmax_stage1_kernel<<<dim3(slices, T), 256, 0, st>>>(logits, cv, ci, V, ld, slices);
-  argmax_stage2_kernel<<<T, 64, 0, st>>>(cv, ci, out, slices);
+  launch_pdl(argmax_stage1_kernel, dim3(slices, T), dim3(256), 0, st, logits, cv, ci, V, ld, slices);
+  launch_pdl(argmax_stage2_kernel, dim3(T), dim3(64), 0, st, cv, ci, out, slices);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -327,20 +343,20 @@ extern "C" int cafd_argmax_noalloc(const float* logits, int* out, int T, int V, 
   int* ci = reinterpret_cast<int*>(cv + static_cast<size_t>(T) * slices);
   cudaStream_t st = static_cast<cudaStream_t>(s);
   // Stage 1 writes every candidate that stage 2 reads, so nothing has to be cleared between calls.
-  argmax_stage1_kernel<<<dim3(slices, T), 256, 0, st>>>(logits, cv, ci, V, ld, slices);
-  argmax_stage2_kernel<<<T, 64, 0, st>>>(cv, ci, out, slices);
+  launch_pdl(argmax_stage1_kernel, dim3(slices, T), dim3(256), 0, st, logits, cv, ci, V, ld, slices);
+  launch_pdl(argmax_stage2_kernel, dim3(T), dim3(64), 0, st, cv, ci, out, slices);
   return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int cafd_decode_advance(int* tokens, const int* next_tokens, int* positions, int* seq_lens, int* slots,
                                    const int* page_table, int max_pages, int S, int page_size, cafd_stream_t s) {
   if (S <= 0) return 0;
-  decode_advance_kernel<<<(S + 127) / 128, 128, 0, static_cast<cudaStream_t>(s)>>>(
+  launch_pdl(decode_advance_kernel, dim3((S + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(s), 
       tokens, next_tokens, positions, seq_lens, slots, page_table, max_pages, S, page_size);
   return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int cafd_bump_epoch(uint32_t* epoch, cafd_stream_t s) {
-  bump_epoch_kernel<<<1, 1, 0, static_cast<cudaStream_t>(s)>>>(epoch);
+  launch_pdl(bump_epoch_kernel, dim3(1), dim3(1), 0, static_cast<cudaStream_t>(s), epoch);
   return static_cast<int>(cudaGetLastError());
 }

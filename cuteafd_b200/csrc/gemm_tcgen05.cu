@@ -101,6 +101,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
       mbar_init(&tempty_bar[s], 128);
     }
     mbar_fence_init();
+    pdl_wait();   // flags, tile counts and activations come from kernels earlier in the stream
     // A peer may still be writing the slab and the tile list: wait for its flag first.
     int xt = p.x_tiles_static;
     bool ok = true;
@@ -120,6 +121,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();
+  pdl_trigger();
   const uint32_t tmem_base = tmem_base_slot;
   const int x_tiles = s_x_tiles;
   const int base_tiles = x_tiles * p.w_tiles;
@@ -341,13 +344,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
             float g[16], u[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) { g[j] = 0.f; u[j] = 0.f; }
-            for (int sp = 0; sp < splits; ++sp) {
-              const float* ps = part0 + static_cast<size_t>(sp) * (Cfg::kAccCols * 128);
+            // Loads of four splits are issued together (independent addresses) and then added in
+            // split order, so the L2 round trips overlap while the summation order stays fixed.
+            for (int sp0 = 0; sp0 < splits; sp0 += 4) {
+              float tg[4][16], tu[4][16];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                g[j] += __ldcg(ps + (c0 + j) * 128 + fl);
-                if (kDual) u[j] += __ldcg(ps + (kBX + c0 + j) * 128 + fl);
+              for (int q = 0; q < 4; ++q) {
+                const bool live = sp0 + q < splits;
+                const float* ps = part0 + static_cast<size_t>(live ? sp0 + q : sp0) * (Cfg::kAccCols * 128);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  tg[q][j] = live ? __ldcg(ps + (c0 + j) * 128 + fl) : 0.f;
+                  if (kDual) tu[q][j] = live ? __ldcg(ps + (kBX + c0 + j) * 128 + fl) : 0.f;
+                }
               }
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  g[j] += tg[q][j];
+                  if (kDual) u[j] += tu[q][j];
+                }
             }
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = kDual ? silu(g[j]) * u[j] : g[j];
@@ -483,7 +500,7 @@ static int launch(const cafd_gemm_args* a, cudaStream_t stream) {
     CAFD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_set = true;
   }
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tw0, tw1, tx, p);
+  launch_pdl(kern, grid, dim3(kGemmThreads), Cfg::kSmemBytes, stream, tw0, tw1, tx, p);
   return static_cast<int>(cudaGetLastError());
 }
 

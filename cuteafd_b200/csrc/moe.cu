@@ -40,6 +40,8 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const float* __restrict
                                                          int* __restrict__ out_idx, float* __restrict__ out_w, int T,
                                                          int E, int top_k, int sigmoid, int num_groups,
                                                          int topk_groups, int normalize, float routed_scale) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
   const int lane = threadIdx.x & 31;
@@ -163,6 +165,8 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const float* __restrict
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ idx, int T, int top_k, int E,
                                                         int tile_rows, MoeLayoutDev L, int* __restrict__ dest_row,
                                                         int* __restrict__ expert_count_out, uint32_t* status) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ int counts[kMaxExperts];
   __shared__ int seg_off[kMaxExperts];
   __shared__ int cursor[kMaxExperts];
@@ -254,6 +258,8 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const uint4* __restri
                                                            const int* __restrict__ dest_row, int n_entries, int top_k,
                                                            int row_vec, MoeLayoutDev L, const uint32_t* epoch,
                                                            uint32_t* done_counter) {
+  pdl_wait();
+  pdl_trigger();
   const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (i < n_entries) {
@@ -288,6 +294,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint4* __restric
                                                           const uint4* __restrict__ residual, uint4* __restrict__ out,
                                                           int T, int top_k, int row_vec, const uint32_t* flags,
                                                           int n_flags, const uint32_t* epoch, uint32_t* status) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ int s_ok;
   if (threadIdx.x == 0) {
     bool ok = true;
@@ -370,7 +378,7 @@ int cafd_route_topk(const float* logits, const float* bias, int* out_idx, float*
   cudaStream_t st = static_cast<cudaStream_t>(s);
   const int blocks = (T + 3) / 4;
 #define CAFD_ROUTE(N)                                                                                          \
-  route_topk_kernel<N><<<blocks, 128, 0, st>>>(logits, bias, out_idx, out_w, T, E, top_k, sigmoid, num_groups, \
+  launch_pdl(route_topk_kernel<N>, dim3(blocks), dim3(128), 0, st, logits, bias, out_idx, out_w, T, E, top_k, sigmoid, num_groups, \
                                                topk_groups, normalize, routed_scale)
   if (E <= 32) CAFD_ROUTE(1);
   else if (E <= 64) CAFD_ROUTE(2);
@@ -386,7 +394,7 @@ int cafd_moe_meta_ints(int max_tiles, int max_rows) { return kMetaHeader + 2 * m
 int cafd_moe_plan(const int* idx, int T, int top_k, int E, int tile_rows, const cafd_moe_layout* layout,
                   int* dest_row, int* expert_count, uint32_t* status, cafd_stream_t s) {
   if (E > kMaxExperts || layout->n_ranks < 1 || layout->n_ranks > kMaxRanks) return -10;
-  moe_plan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(s)>>>(idx, T, top_k, E, tile_rows, to_dev(layout), dest_row,
+  launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(s), idx, T, top_k, E, tile_rows, to_dev(layout), dest_row,
                                                                expert_count, status);
   return static_cast<int>(cudaGetLastError());
 }
@@ -397,7 +405,7 @@ int cafd_moe_dispatch(const void* x, const int* idx, const int* dest_row, int T,
   if (H % 8) return -10;
   const int n = T * top_k;
   const int blocks = n > 0 ? (n + 7) / 8 : 1;
-  moe_dispatch_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(s)>>>(static_cast<const uint4*>(x), idx, dest_row, n,
+  launch_pdl(moe_dispatch_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(s), static_cast<const uint4*>(x), idx, dest_row, n,
                                                                        top_k, H / 8, to_dev(layout), epoch,
                                                                        done_counter);
   return static_cast<int>(cudaGetLastError());
@@ -408,7 +416,7 @@ int cafd_moe_combine(const void* buf, const float* w, const void* shared_out, co
                      cafd_stream_t s) {
   if (H % 8) return -10;
   int blocks = T < 1 ? 1 : (T > 4096 ? 4096 : T);
-  moe_combine_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(s)>>>(
+  launch_pdl(moe_combine_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(s), 
       static_cast<const uint4*>(buf), w, static_cast<const uint4*>(shared_out), static_cast<const uint4*>(residual),
       static_cast<uint4*>(out), T, top_k, H / 8, flags, n_flags, epoch, status);
   return static_cast<int>(cudaGetLastError());

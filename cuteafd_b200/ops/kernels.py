@@ -274,8 +274,8 @@ def moe_combine(buf: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, shared
 # ---- attention -------------------------------------------------------------------------------------
 def attn_decode_splits(num_seqs: int, tiles_per_seq: int, Hkv: int, max_pages: int) -> int:
     ctas = max(1, num_seqs * tiles_per_seq * Hkv)
-    want = max(1, (2 * num_sms() + ctas - 1) // ctas)
-    return max(1, min(want, max(1, max_pages // 2), 64))
+    want = max(1, (num_sms() + ctas - 1) // ctas)
+    return max(1, min(want, max(1, max_pages // 4), 32))
 
 
 def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
