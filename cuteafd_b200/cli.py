@@ -1,0 +1,200 @@
+"""``cuteafd`` command line: plan | serve | expertd | golden | bench | fabric | doctor | gateway | usage.
+
+    python -m cuteafd_b200.cli plan deepseek-v3 --layout --gpus 8
+    python -m cuteafd_b200.cli plan /path/to/snapshot --layout --deployment
+    python -m cuteafd_b200.cli serve --snapshot /path/to/snapshot --port 8000
+    python -m cuteafd_b200.cli bench --gpus 1
+
+Counterpart: rust/crates/cuteafd-daemon/src/cli.rs:133-295 (Commands), main.rs:363-641 (dispatch),
+commands/plan.rs.  Options may also come from ``KEY=VALUE`` config files (``--config``) with
+``--set KEY=VALUE`` overrides; unknown keys are refused, as the reference launcher does
+(docs/options.md:210-232).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+
+def _size(s: str) -> int:
+    s = s.strip().lower()
+    for suf, mul in (("gib", 1 << 30), ("gb", 10 ** 9), ("mib", 1 << 20), ("mb", 10 ** 6), ("g", 1 << 30), ("m", 1 << 20)):
+        if s.endswith(suf):
+            return int(float(s[: -len(suf)]) * mul)
+    return int(s)
+
+
+def load_config_file(path: str, overrides: list[str], known: set[str]) -> dict[str, str]:
+    """KEY=VALUE file + ``--set`` overrides; unknown keys exit with status 2."""
+    out: dict[str, str] = {}
+    lines = []
+    if path:
+        with open(path) as f:
+            lines = f.read().splitlines()
+    for raw in list(lines) + list(overrides):
+        line = raw.split("#", 1)[0].strip()
+        if not line:
+            continue
+        if "=" not in line:
+            print(f"config: malformed line {raw!r}", file=sys.stderr)
+            raise SystemExit(2)
+        k, v = line.split("=", 1)
+        k = k.strip().upper()
+        if k not in known:
+            print(f"config: unknown key {k}", file=sys.stderr)
+            raise SystemExit(2)
+        out[k] = v.strip()
+    return out
+
+
+CONFIG_KEYS = {"MODEL", "GPUS", "ATTENTION_RANKS", "EXPERT_RANKS", "POOL_TOKENS", "GPU_MEMORY_CAP", "MAX_CONTEXT_TOKENS",
+               "CONCURRENCY", "SPECULATOR", "DECODE_LANES", "PORT", "HOST", "API_KEY", "DECODE_SHARE", "PREFILL_ROWS",
+               "HTTP_QUEUE_DEPTH", "HTTP_QUEUE_WAIT", "PROFILE", "SPECULATION_TRACE", "KV_FORMAT", "EXPERT_FORMAT"}
+
+
+def cmd_plan(a: argparse.Namespace) -> int:
+    from .planner import plan as P
+    kw = dict(gpus=a.gpus, attention_ranks=a.attention_ranks, expert_ranks=a.expert_ranks, pool_tokens_target=a.pool_tokens,
+              gpu_memory_cap=_size(a.gpu_memory_cap) if a.gpu_memory_cap else None, max_context_tokens=a.max_context_tokens,
+              concurrency=a.concurrency, speculator=a.speculator, decode_lanes=a.decode_lanes,
+              pipeline_stages=a.pipeline_stages, expert_format=a.expert_format, kv_format=a.kv_format)
+    rep = P.plan(a.model, layout=a.layout or a.deployment, fmt=a.format, **kw)
+    if a.deployment:
+        if not (rep.placement and rep.placement.ok):
+            print(P.render(rep), file=sys.stderr)
+            return 1
+        print(json.dumps(P.deployment(rep), indent=1))
+    elif a.files:
+        files = rep.role_files if not a.role else {a.role: rep.role_files.get(a.role, [])}
+        print(json.dumps(files, indent=1))
+    elif a.json:
+        print(json.dumps(P.to_json(rep), indent=1, default=str))
+    else:
+        print(P.render(rep))
+    return 0 if (rep.ready or not a.require_ready) else 1
+
+
+def cmd_serve(a: argparse.Namespace) -> int:
+    from .serve.server import run_server
+    return run_server(a)
+
+
+def cmd_expertd(a: argparse.Namespace) -> int:
+    from .serve.expertd import run_expertd
+    return run_expertd(a)
+
+
+def cmd_golden(a: argparse.Namespace) -> int:
+    from .bench.golden import run_golden
+    return run_golden(a)
+
+
+def cmd_bench(a: argparse.Namespace) -> int:
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, os.path.join(root, "bench.py"), "--gpus", str(a.gpus), "--steps", str(a.steps), "--warmup", str(a.warmup)]
+    if a.gpus > 1:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", str(a.port)] + cmd[1:]
+    return subprocess.call(cmd)
+
+
+def cmd_fabric(a: argparse.Namespace) -> int:
+    from .parallel.fabric import fabric_report
+    rep = fabric_report(p2p=a.p2p)
+    print(json.dumps(rep, indent=1) if a.json else "\n".join(f"{k}: {v}" for k, v in rep.items()))
+    return 0
+
+
+def cmd_doctor(a: argparse.Namespace) -> int:
+    from .utils.doctor import doctor
+    ok, lines = doctor()
+    print("\n".join(lines))
+    return 0 if ok else 1
+
+
+def cmd_gateway(a: argparse.Namespace) -> int:
+    from .serve.gateway import run_gateway
+    return run_gateway(a)
+
+
+def cmd_usage(a: argparse.Namespace) -> int:
+    from .serve.usage import usage_report
+    print(json.dumps(usage_report(a.db, a.hours), indent=1))
+    return 0
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="cuteafd", description="B200-native attention/FFN-disaggregated MoE serving")
+    ap.add_argument("--config", default="", help="KEY=VALUE file")
+    ap.add_argument("--set", action="append", default=[], metavar="KEY=VALUE")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+
+    p = sub.add_parser("plan", help="describe a checkpoint and lay it out on the GPUs")
+    p.add_argument("model")
+    p.add_argument("--layout", action="store_true"); p.add_argument("--json", action="store_true")
+    p.add_argument("--deployment", action="store_true"); p.add_argument("--files", action="store_true")
+    p.add_argument("--role", default=""); p.add_argument("--require-ready", action="store_true")
+    p.add_argument("--gpus", type=int, default=8); p.add_argument("--attention-ranks", type=int, default=None)
+    p.add_argument("--expert-ranks", type=int, default=None); p.add_argument("--pipeline-stages", type=int, default=1)
+    p.add_argument("--pool-tokens", type=int, default=None); p.add_argument("--gpu-memory-cap", default="")
+    p.add_argument("--max-context-tokens", type=int, default=None); p.add_argument("--concurrency", type=int, default=None)
+    p.add_argument("--speculator", default=None, choices=["auto", "off", "mtp"]); p.add_argument("--decode-lanes", type=int, default=None, choices=[1, 2])
+    p.add_argument("--format", default=None); p.add_argument("--expert-format", default=None); p.add_argument("--kv-format", default=None)
+    p.set_defaults(fn=cmd_plan)
+
+    s = sub.add_parser("serve", help="HTTP serving (OpenAI / Anthropic compatible)")
+    s.add_argument("--snapshot", default=""); s.add_argument("--preset", default="")
+    s.add_argument("--host", default="127.0.0.1"); s.add_argument("--port", type=int, default=8000)
+    s.add_argument("--api-key", default=os.environ.get("CUTEAFD_API_KEY", ""))
+    s.add_argument("--max-context-tokens", type=int, default=16384); s.add_argument("--concurrency", type=int, default=8)
+    s.add_argument("--speculator", default="auto"); s.add_argument("--layers", type=int, default=0)
+    s.add_argument("--queue-depth", type=int, default=64); s.add_argument("--queue-wait", type=float, default=30.0)
+    s.add_argument("--fake-engine", action="store_true", help="serve with the CPU oracle engine (no GPU)")
+    s.add_argument("--usage-db", default="")
+    s.set_defaults(fn=cmd_serve)
+
+    e = sub.add_parser("expertd", help="expert-rank worker")
+    e.add_argument("--snapshot", default=""); e.add_argument("--rank", type=int, required=True); e.add_argument("--world", type=int, required=True)
+    e.add_argument("--master-addr", default="127.0.0.1"); e.add_argument("--master-port", type=int, default=29500)
+    e.add_argument("--deployment", default="")
+    e.set_defaults(fn=cmd_expertd)
+
+    g = sub.add_parser("golden", help="layer-by-layer comparison of the engine against the CPU oracle")
+    g.add_argument("--snapshot", default=""); g.add_argument("--preset", default="tiny-moe"); g.add_argument("--tokens", type=int, default=64)
+    g.add_argument("--out", default="")
+    g.set_defaults(fn=cmd_golden)
+
+    b = sub.add_parser("bench", help="run the headline benchmark card")
+    b.add_argument("--gpus", type=int, default=1); b.add_argument("--steps", type=int, default=128)
+    b.add_argument("--warmup", type=int, default=8); b.add_argument("--port", type=int, default=29511)
+    b.set_defaults(fn=cmd_bench)
+
+    f = sub.add_parser("fabric", help="NVLink / peer-access report")
+    f.add_argument("--json", action="store_true"); f.add_argument("--p2p", action="store_true")
+    f.set_defaults(fn=cmd_fabric)
+
+    sub.add_parser("doctor", help="environment checks").set_defaults(fn=cmd_doctor)
+
+    gw = sub.add_parser("gateway", help="protocol gateway in front of an OpenAI-compatible upstream")
+    gw.add_argument("--upstream", default="http://127.0.0.1:8000"); gw.add_argument("--host", default="127.0.0.1")
+    gw.add_argument("--port", type=int, default=8080); gw.add_argument("--model-map", default="")
+    gw.set_defaults(fn=cmd_gateway)
+
+    u = sub.add_parser("usage", help="request accounting report")
+    u.add_argument("--db", default="usage.sqlite"); u.add_argument("--hours", type=float, default=24.0)
+    u.set_defaults(fn=cmd_usage)
+    return ap
+
+
+def main(argv: list[str] | None = None) -> int:
+    ap = build_parser()
+    a = ap.parse_args(argv)
+    a.file_config = load_config_file(a.config, a.set, CONFIG_KEYS) if (a.config or a.set) else {}
+    return a.fn(a)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

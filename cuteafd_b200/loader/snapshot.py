@@ -1,0 +1,139 @@
+"""Hugging Face snapshot layout: ``config.json`` <-> ``ModelConfig``, snapshot resolution, and
+writers of random-init snapshots in each shipped weight format.
+
+A snapshot is a directory with config.json, model.safetensors.index.json and shards; runs load it
+"as shipped", nothing is repacked on disk.  Counterpart: rust/crates/cuteafd-loader/src/snapshot.rs
+(resolve), plan/testing.rs (snapshot writers for tests).
+"""
+from __future__ import annotations
+
+import json
+import os
+
+import torch
+
+from ..config import ModelConfig
+from ..ref.model import init_weights
+from . import formats
+from .safetensors_io import write_sharded
+
+ARCH = {"qwen3_moe": "Qwen3MoeForCausalLM", "deepseek_v3": "DeepseekV3ForCausalLM",
+        "deepseek_v32": "DeepseekV32ForCausalLM", "tiny_moe": "DeepseekV3ForCausalLM"}
+
+
+def to_hf_config(cfg: ModelConfig) -> dict:
+    d = {"architectures": [ARCH.get(cfg.family, "DeepseekV3ForCausalLM")], "model_type": cfg.family,
+         "vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden, "num_hidden_layers": cfg.num_layers,
+         "num_attention_heads": cfg.num_heads, "rms_norm_eps": cfg.rms_eps, "rope_theta": cfg.rope_theta,
+         "tie_word_embeddings": cfg.tie_embeddings, "torch_dtype": "bfloat16",
+         "intermediate_size": cfg.dense_ffn, "moe_intermediate_size": cfg.expert_ffn,
+         "num_experts_per_tok": cfg.top_k, "norm_topk_prob": cfg.norm_topk_prob,
+         "cuteafd": {"name": cfg.name, "rope_interleaved": cfg.rope_interleaved, "family": cfg.family}}
+    if cfg.is_mla:
+        d.update(q_lora_rank=cfg.q_lora_rank or None, kv_lora_rank=cfg.kv_lora_rank, qk_nope_head_dim=cfg.qk_nope_dim,
+                 qk_rope_head_dim=cfg.qk_rope_dim, v_head_dim=cfg.v_head_dim, n_routed_experts=cfg.num_experts,
+                 n_shared_experts=cfg.num_shared_experts, first_k_dense_replace=cfg.first_dense_layers,
+                 scoring_func=cfg.scoring, n_group=cfg.num_groups, topk_group=cfg.topk_groups,
+                 routed_scaling_factor=cfg.routed_scale, num_nextn_predict_layers=cfg.mtp_layers,
+                 topk_method="noaux_tc" if cfg.router_bias else "greedy")
+        if cfg.indexer_heads:
+            d.update(index_n_heads=cfg.indexer_heads, index_head_dim=cfg.indexer_dim, index_topk=cfg.indexer_topk)
+    else:
+        d.update(num_key_value_heads=cfg.num_kv_heads, head_dim=cfg.head_dim, num_experts=cfg.num_experts,
+                 decoder_sparse_step=1, mlp_only_layers=list(range(cfg.first_dense_layers)), qk_norm=cfg.qk_norm)
+    if cfg.weight_format == "fp8_block128":
+        d["quantization_config"] = {"quant_method": "fp8", "fmt": "e4m3", "weight_block_size": [128, 128],
+                                    "activation_scheme": "dynamic"}
+    elif cfg.weight_format == "nvfp4":
+        d["quantization_config"] = {"quant_method": "modelopt", "quant_algo": "NVFP4", "group_size": 16}
+    elif cfg.weight_format == "mxfp4":
+        d["quantization_config"] = {"quant_method": "mxfp4", "group_size": 32}
+    elif cfg.weight_format.startswith("exl3"):
+        d["quantization_config"] = {"quant_method": "exl3", "bits": 4}
+    return d
+
+
+def from_hf_config(d: dict) -> ModelConfig:
+    """Map a config.json onto the engine's geometry.  Unknown architectures raise ValueError."""
+    mt = d.get("model_type", "")
+    extra = d.get("cuteafd", {})
+    q = d.get("quantization_config") or {}
+    fmt = {"fp8": "fp8_block128", "modelopt": "nvfp4", "mxfp4": "mxfp4", "exl3": "exl3"}.get(q.get("quant_method", ""), "bf16")
+    common = dict(name=extra.get("name", d.get("_name_or_path", mt) or mt), vocab_size=d["vocab_size"],
+                  num_layers=d["num_hidden_layers"], hidden=d["hidden_size"], num_heads=d["num_attention_heads"],
+                  rms_eps=d.get("rms_norm_eps", 1e-6), rope_theta=float(d.get("rope_theta", 10000.0)),
+                  tie_embeddings=bool(d.get("tie_word_embeddings", False)), dense_ffn=d.get("intermediate_size", 0),
+                  expert_ffn=d.get("moe_intermediate_size", 0), top_k=d.get("num_experts_per_tok", 0),
+                  norm_topk_prob=bool(d.get("norm_topk_prob", True)), weight_format=fmt)
+    if mt in ("deepseek_v3", "deepseek_v32", "deepseek_v2", "tiny_moe", "glm_moe_dsa", "kimi_k2"):
+        return ModelConfig(
+            family=extra.get("family", "deepseek_v32" if d.get("index_n_heads") else "deepseek_v3"), attention="mla",
+            q_lora_rank=d.get("q_lora_rank") or 0, kv_lora_rank=d["kv_lora_rank"], qk_nope_dim=d["qk_nope_head_dim"],
+            qk_rope_dim=d["qk_rope_head_dim"], v_head_dim=d["v_head_dim"],
+            rope_interleaved=extra.get("rope_interleaved", True), first_dense_layers=d.get("first_k_dense_replace", 0),
+            num_experts=d.get("n_routed_experts", 0), scoring=d.get("scoring_func", "softmax"),
+            num_groups=d.get("n_group", 1) or 1, topk_groups=d.get("topk_group", 1) or 1,
+            num_shared_experts=d.get("n_shared_experts", 0) or 0, routed_scale=d.get("routed_scaling_factor", 1.0),
+            router_bias=d.get("topk_method") == "noaux_tc", mtp_layers=d.get("num_nextn_predict_layers", 0) or 0,
+            indexer_heads=d.get("index_n_heads", 0) or 0, indexer_dim=d.get("index_head_dim", 128),
+            indexer_topk=d.get("index_topk", 2048), **common)
+    if mt in ("qwen3_moe", "qwen3", "qwen2_moe", "mixtral"):
+        return ModelConfig(
+            family="qwen3_moe", attention="gqa", num_kv_heads=d.get("num_key_value_heads", d["num_attention_heads"]),
+            head_dim=d.get("head_dim", d["hidden_size"] // d["num_attention_heads"]), qk_norm=bool(d.get("qk_norm", mt.startswith("qwen3"))),
+            rope_interleaved=extra.get("rope_interleaved", False), first_dense_layers=len(d.get("mlp_only_layers", []) or []),
+            num_experts=d.get("num_experts", d.get("num_local_experts", 0)), scoring="softmax", num_shared_experts=0, **common)
+    raise ValueError(f"unsupported model_type {mt!r}")
+
+
+def resolve(path: str) -> str:
+    """Accept a snapshot directory or a hub cache root (models--org--name/snapshots/<rev>)."""
+    if os.path.isfile(os.path.join(path, "config.json")):
+        return path
+    snaps = os.path.join(path, "snapshots")
+    if os.path.isdir(snaps):
+        revs = sorted(os.listdir(snaps))
+        if revs:
+            return os.path.join(snaps, revs[-1])
+    raise FileNotFoundError(f"{path}: no config.json and no snapshots/ directory")
+
+
+def read_config(path: str) -> tuple[ModelConfig, dict]:
+    with open(os.path.join(resolve(path), "config.json")) as f:
+        d = json.load(f)
+    return from_hf_config(d), d
+
+
+def _quantised(name: str, cfg: ModelConfig, scope: str) -> bool:
+    if not name.endswith(".weight") or "norm" in name or "embed_tokens" in name or name.startswith("lm_head"):
+        return False
+    if ".mlp.gate.weight" in name:
+        return False
+    if scope == "experts":
+        return ".mlp.experts." in name
+    return ".mlp." in name or ".self_attn." in name
+
+
+def write_random_snapshot(cfg: ModelConfig, directory: str, fmt: str | None = None, seed: int = 0,
+                          scope: str = "experts", shard_bytes: int = 1 << 30) -> str:
+    """Random-init snapshot of ``cfg`` in format ``fmt`` (bf16 | fp8_block128 | nvfp4 | mxfp4 | exl3_k4).
+
+    ``scope`` = "experts": only routed experts carry the quantised format (the usual shipped
+    mix); "linear": every projection does (DeepSeek FP8 style)."""
+    fmt = fmt or cfg.weight_format
+    cfg = cfg.replace(weight_format=fmt if not fmt.startswith("exl3") else "exl3")
+    params = init_weights(cfg, seed=seed)
+    gen = torch.Generator().manual_seed(seed + 17)
+    out: dict[str, torch.Tensor] = {}
+    for name, t in params.items():
+        if fmt != "bf16" and _quantised(name, cfg, scope) and t.shape[-1] % 128 == 0 and t.shape[0] % 16 == 0:
+            out.update(formats.encode(t, fmt, name[: -len(".weight")], gen))
+        elif name.endswith("e_score_correction_bias"):
+            out[name] = t.float()
+        else:
+            out[name] = t.to(torch.bfloat16)
+    os.makedirs(directory, exist_ok=True)
+    with open(os.path.join(directory, "config.json"), "w") as f:
+        json.dump(to_hf_config(cfg), f, indent=1, sort_keys=True)
+    write_sharded(directory, out, shard_bytes)
+    return directory

@@ -1,0 +1,130 @@
+"""Checkpoint layer on CPU: codecs, safetensors catalog, format detection, family registry,
+random-init snapshots in every shipped format, and decode-to-oracle round trips."""
+import json
+import os
+
+import pytest
+import torch
+
+from cuteafd_b200 import ModelConfig, tiny_moe
+from cuteafd_b200.loader import families, formats, load, snapshot
+from cuteafd_b200.loader.safetensors_io import Catalog, write_file
+from cuteafd_b200.quant import codecs
+
+
+def small() -> ModelConfig:
+    return tiny_moe().replace(expert_ffn=128, hidden=256, dense_ffn=256)
+
+
+def test_fp8_block_and_row_codecs():
+    w = torch.randn(300, 512) * 0.02
+    q, s = codecs.fp8_quant_block128(w)
+    assert q.dtype == torch.float8_e4m3fn and s.shape == (3, 4)
+    assert (codecs.fp8_dequant_block128(q, s) - w).abs().max() < 0.07 * w.abs().max()
+    x = torch.randn(5, 256)
+    qx, sx = codecs.fp8_quant_rows(x)
+    assert sx.shape == (5, 2)
+    assert (codecs.fp8_dequant_rows(qx, sx) - x).abs().max() < 0.07 * x.abs().max()
+    z, sz = codecs.fp8_quant_rows(torch.zeros(2, 128))
+    assert torch.all(sz == 1.0) and torch.all(z.float() == 0)
+
+
+def test_fp4_codecs_and_nibble_order():
+    codes = torch.tensor([[1, 2, 3, 4]], dtype=torch.uint8)
+    packed = codecs.pack_nibbles(codes)
+    assert packed.tolist() == [[0x21, 0x43]]                 # even element in the low nibble
+    assert torch.equal(codecs.unpack_nibbles(packed), codes)
+    w = torch.randn(64, 256) * 0.02
+    p, e = codecs.mxfp4_quant(w)
+    assert p.shape == (64, 128) and e.shape == (64, 8) and e.dtype == torch.uint8
+    assert (codecs.mxfp4_dequant(p, e) - w).abs().max() < 0.3 * w.abs().max()
+    p, bs, g = codecs.nvfp4_quant(w)
+    assert bs.dtype == torch.float8_e4m3fn and bs.shape == (64, 16) and g.shape == (1,)
+    assert (codecs.nvfp4_dequant(p, bs, g) - w).abs().max() < 0.3 * w.abs().max()
+    exact = torch.tensor([[0.5, -1.5, 6.0, -0.0] * 8]) * 2.0      # representable values survive exactly
+    p, e = codecs.mxfp4_quant(exact)
+    assert torch.equal(codecs.mxfp4_dequant(p, e), exact)
+
+
+def test_exl3_decode_properties():
+    g = torch.Generator().manual_seed(0)
+    for bits in (2, 4):
+        t, suh, svh = codecs.exl3_random(128, 256, bits, g)
+        inner = codecs.exl3_decode_inner(t)
+        assert inner.shape == (128, 256) and torch.isfinite(inner).all()
+        w = codecs.exl3_dequant(t, suh, svh)
+        assert w.shape == (128, 256)
+        # the rotations are orthonormal: energy is preserved up to the sign-scale vectors
+        assert torch.allclose(w.pow(2).sum(), (inner.double() * svh.double().abs()[None]).pow(2).sum(), rtol=1e-6)
+    h = codecs.hadamard128(torch.eye(128))
+    assert torch.allclose(h @ h.T, torch.eye(128, dtype=torch.float64), atol=1e-9)
+
+
+def test_safetensors_catalog_roundtrip(tmp_path):
+    tensors = {"a.weight": torch.randn(8, 16).to(torch.bfloat16), "b": torch.arange(10, dtype=torch.int32),
+               "c.weight": torch.randn(4, 128).to(torch.float8_e4m3fn), "d": torch.randint(-9, 9, (3, 2, 32), dtype=torch.int16)}
+    write_file(str(tmp_path / "model.safetensors"), tensors, {"format": "pt"})
+    cat = Catalog(str(tmp_path))
+    assert cat.names() == sorted(tensors)
+    for k, v in tensors.items():
+        got = cat.read(k)
+        assert got.dtype == v.dtype and torch.equal(got.view(torch.uint8), v.view(torch.uint8))
+    assert torch.equal(cat.read_rows("a.weight", 2, 3), tensors["a.weight"][2:5])
+    assert len(cat.sha256("b")) == 64
+    assert cat.total_bytes() == sum(t.numel() * t.element_size() for t in tensors.values())
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "fp8_block128", "nvfp4", "mxfp4", "exl3_k4"])
+def test_random_snapshot_formats(tmp_path, fmt):
+    cfg = small()
+    d = snapshot.write_random_snapshot(cfg, str(tmp_path / fmt), fmt=fmt, seed=3)
+    assert os.path.exists(os.path.join(d, "model.safetensors.index.json"))
+    snap = load.open_snapshot(d)
+    assert snap.family is not None and snap.model is not None
+    assert snap.cfg.hidden == cfg.hidden and snap.cfg.num_experts == cfg.num_experts
+    assert snap.hints() == []
+    op = snap.operands["model.layers.1.mlp.experts.3.down_proj"]
+    assert op.format.startswith(fmt.split("_k")[0])
+    assert op.shape == (cfg.hidden, cfg.expert_ffn)
+    assert snap.model.classify(op.weight) == ("routed_expert", 1, 3)
+    assert snap.model.classify("model.layers.0.mlp.down_proj.weight")[0] == "dense_ffn"
+    assert snap.model.classify("model.layers.1.mlp.gate.weight")[0] == "router"
+    w = formats.dequantize(op, snap.catalog)
+    assert w.shape == (cfg.hidden, cfg.expert_ffn) and torch.isfinite(w).all()
+    if not fmt.startswith("exl3"):
+        from cuteafd_b200.ref.model import init_weights
+        ref = init_weights(cfg.replace(weight_format=fmt), seed=3)["model.layers.1.mlp.experts.3.down_proj.weight"]
+        tol = {"bf16": 0.01, "fp8_block128": 0.08}.get(fmt, 0.3)
+        assert (w - ref).abs().max() < tol * ref.abs().max()
+
+
+def test_loaded_params_run_the_oracle(tmp_path):
+    from cuteafd_b200.ref.model import KvState, RefDecoder
+    cfg = small()
+    d = snapshot.write_random_snapshot(cfg, str(tmp_path / "s"), fmt="fp8_block128", seed=0, scope="linear")
+    cfg2, params = load.load_params(d)
+    assert cfg2.weight_format == "fp8_block128"
+    logits = RefDecoder(cfg2, params).forward(torch.arange(12) % cfg.vocab_size, KvState(cfg2))
+    assert logits.shape == (12, cfg.vocab_size) and torch.isfinite(logits).all()
+
+
+def test_unsupported_is_a_result_not_a_crash(tmp_path):
+    cfg = small()
+    d = snapshot.write_random_snapshot(cfg, str(tmp_path / "s"), fmt="bf16")
+    hf = json.load(open(os.path.join(d, "config.json")))
+    hf["model_type"] = "some_future_arch"
+    assert families.detect(hf) is None
+    snap = load.open_snapshot(d)
+    op = snap.operands["model.layers.1.mlp.gate"]
+    bad = formats.QuantOperand(op.name, "e4m3", op.shape, op.weight)
+    hint = snap.model.accepts(bad, "router")
+    assert isinstance(hint, families.Hint) and "router" in hint.what
+
+
+def test_hf_config_roundtrip():
+    from cuteafd_b200 import deepseek_v3, deepseek_v32, qwen3_30b_a3b
+    for cfg in (qwen3_30b_a3b(), deepseek_v3(), deepseek_v32(), tiny_moe()):
+        back = snapshot.from_hf_config(snapshot.to_hf_config(cfg))
+        for f in ("hidden", "num_layers", "num_heads", "num_experts", "top_k", "expert_ffn", "attention", "scoring",
+                  "num_groups", "topk_groups", "first_dense_layers", "mtp_layers", "indexer_heads", "weight_format"):
+            assert getattr(back, f) == getattr(cfg, f), (cfg.name, f)
