@@ -232,8 +232,9 @@ def _place(req: PlacementRequest, att: int, exp: int, pp: int) -> Placement:
     room = min(g.free for g in att_devs)
     pool_tokens = min(req.pool_tokens_target, room // max(kv_per_token_dev, 1))
     pool_tokens -= pool_tokens % 64
-    if pool_tokens < req.pool_tokens_min:
-        return Placement(False, f"KV pool would hold {pool_tokens} tokens, minimum is {req.pool_tokens_min}", "", att, exp, pp, devices,
+    pool_min = min(req.pool_tokens_min, req.pool_tokens_target)
+    if pool_tokens < pool_min:
+        return Placement(False, f"KV pool would hold {pool_tokens} tokens, minimum is {pool_min}", "", att, exp, pp, devices,
                          ranges, pool_tokens, kv_per_token_dev, 0, spec, req.decode_lanes)
     for g in att_devs:
         g.add("kv_pool", f"{pool_tokens} tokens", pool_tokens * kv_per_token_dev)
