@@ -1,0 +1,209 @@
+"""Scheduler backends: the CUDA engine and the CPU oracle.
+
+Both keep their KV bookkeeping in the same ``PagePool`` / ``SequenceTable`` / ``PrefixCache``
+objects, so admission, prefix reuse, copy-on-write and eviction behave identically; only where
+the KV bytes live differs (device page pools versus per-sequence oracle tensors).  The oracle
+backend is what the scheduler, API and speculation tests run on, like the reference's scheduler
+test backend and fake server (rust/crates/cuteafd-daemon/src/shared/qwen/scheduler.rs:1600-1670,
+rust/crates/cuteafd-bench/examples/fake_server.rs:1-50).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..config import ModelConfig
+from .paged import PAGE, PagePool, Sequence, SequenceTable
+from .prefix_cache import PROMPT, TURN, PrefixCache
+
+
+@dataclass
+class _Handle:
+    seq: Sequence
+    kv: object = None            # oracle: KvState
+    dead: bool = False
+
+
+class OracleBackend:
+    """CPU reference decoder behind the scheduler's Backend protocol."""
+
+    def __init__(self, cfg: ModelConfig, params: dict[str, torch.Tensor], total_pages: int = 512, prefill_chunk: int = 64,
+                 max_decode_rows: int = 64, fail_on_step: int | None = None):
+        from ..ref.model import RefDecoder
+        self.cfg, self.model = cfg, RefDecoder(cfg, params)
+        self.vocab_size, self.prefill_chunk, self.max_decode_rows = cfg.vocab_size, prefill_chunk, max_decode_rows
+        self.total_pages = total_pages
+        self.pool = PagePool(total_pages)
+        self.table = SequenceTable(self.pool)
+        self.prefix = PrefixCache(self.pool, self.table, max_pages=total_pages // 2)
+        self.steps = 0
+        self.fail_on_step = fail_on_step          # host-side fault injection: the N-th verify raises
+        self.quarantined: list[_Handle] = []
+
+    def open(self, tokens: list[int]) -> tuple[_Handle, int]:
+        from ..ref.model import KvState
+        seq, m = self.prefix.admit(tokens)
+        kv = KvState(self.cfg)
+        if m.length and m.snapshot is not None and m.snapshot.mark is not None:
+            src = m.snapshot.mark
+            kv.rows = [[r[0][:m.length].clone()] if r else [] for r in src.rows]
+        elif m.length:
+            # pages matched through the radix without a snapshot mark at that exact length:
+            # find any snapshot covering the prefix and slice its state
+            src = next((s.mark for s in self.prefix.snapshots.values()
+                        if s.mark is not None and s.length >= m.length and s.tokens[:m.length] == tuple(tokens[:m.length])), None)
+            if src is None:
+                self.table.free(seq)
+                seq, m.length = self.table.new(), 0
+            else:
+                kv.rows = [[r[0][:m.length].clone()] if r else [] for r in src.rows]
+        return _Handle(seq, kv), m.length
+
+    def prefill(self, h: _Handle, tokens: list[int], last: bool):
+        self.table.reserve(h.seq, h.seq.kv_len + len(tokens))
+        with torch.no_grad():
+            hid = self.model.hidden_states(torch.tensor(tokens), h.kv)
+        h.seq.tokens.extend(tokens)
+        h.seq.kv_len += len(tokens)
+        return self.model.head(hid[-1:]) if last else None
+
+    def verify(self, handles: list[_Handle], rows: list[list[int]]) -> torch.Tensor:
+        self.steps += 1
+        if self.fail_on_step is not None and self.steps == self.fail_on_step:
+            raise RuntimeError("injected worker failure")
+        out = []
+        for h, r in zip(handles, rows):
+            self.table.reserve(h.seq, h.seq.kv_len + len(r))
+            with torch.no_grad():
+                out.append(self.model.forward(torch.tensor(r), h.kv))
+            h.seq.tokens.extend(r)
+            h.seq.kv_len += len(r)
+        return torch.cat(out, 0)
+
+    def commit(self, h: _Handle, keep_tokens: int) -> None:
+        if keep_tokens < h.seq.kv_len:
+            self.table.truncate(h.seq, keep_tokens)
+            h.kv.truncate(keep_tokens)
+
+    def capture(self, h: _Handle, kind: str) -> None:
+        import copy
+        self.prefix.capture(h.seq, PROMPT if kind == "prompt" else TURN, mark=copy.deepcopy(h.kv))
+
+    def release(self, h: _Handle) -> None:
+        if not h.dead:
+            self.table.free(h.seq)
+            h.dead = True
+
+    def quarantine(self, h: _Handle) -> None:
+        h.dead = True
+        self.quarantined.append(h)            # pages stay allocated: never handed to another request
+
+    def pages_of(self, h: _Handle) -> int:
+        return len(h.seq.pages)
+
+
+class EngineBackend:
+    """The CUDA engine (single GPU or the attention rank of an AFD group)."""
+
+    def __init__(self, engine, num_pages: int, max_pages_per_seq: int, prefill_chunk: int = 2048, max_decode_rows: int = 64,
+                 use_graphs: bool = True):
+        from .generate import Generator, StepBuffers
+        self.engine = engine
+        self.cfg = engine.cfg
+        self.vocab_size = self.cfg.vocab_size
+        self.prefill_chunk, self.max_decode_rows = prefill_chunk, max_decode_rows
+        self.total_pages = num_pages
+        self.pool = PagePool(num_pages)
+        self.gen = Generator(engine, self.pool, max_pages_per_seq, max_decode_rows, prefill_chunk, use_graphs)
+        self.table = self.gen.table
+        self.prefix = PrefixCache(self.pool, self.table, max_pages=num_pages // 2)
+        self.max_pages = max_pages_per_seq
+        self.bufs = StepBuffers(max_decode_rows * 8, max_decode_rows, max_pages_per_seq, engine.device)
+        self.quarantined: list[_Handle] = []
+
+    def _copy_page(self, src: int, dst: int) -> None:
+        kv = self.engine.kv if hasattr(self.engine, "kv") else self.engine.inner.kv
+        for k, v in zip(kv.k, kv.v):
+            k[dst].copy_(k[src])
+            v[dst].copy_(v[src])
+
+    def open(self, tokens: list[int]) -> tuple[_Handle, int]:
+        seq, m = self.prefix.admit(tokens)
+        return _Handle(seq), m.length
+
+    def prefill(self, h: _Handle, tokens: list[int], last: bool):
+        from ..models.gqa_moe import Batch
+        seq = h.seq
+        start, n = seq.kv_len, len(tokens)
+        self.table.reserve(seq, start + n, copy_page=self._copy_page)
+        b = self.gen.prefill_buf
+        b.tokens[0][:n] = torch.tensor(tokens, dtype=torch.int32)
+        b.positions[0][:n] = torch.arange(start, start + n, dtype=torch.int32)
+        b.slots[0][:n] = torch.tensor(self.table.slots(seq, start, n), dtype=torch.int32)
+        pt = b.page_table[0].view(1, self.max_pages)
+        pt.zero_()
+        pt[0, :len(seq.pages)] = torch.tensor(seq.pages, dtype=torch.int32)
+        b.seq_lens[0][0] = start + n
+        b.q_start[0][0], b.q_start[0][1] = 0, n
+        b.last_rows[0][0] = n - 1
+        b.upload()
+        batch = Batch(b.tokens[1][:n], b.positions[1][:n], b.slots[1][:n], b.page_table[1].view(1, self.max_pages),
+                      b.seq_lens[1][:1], b.q_start[1][:2], n, True, b.last_rows[1][:1])
+        logits = self.engine.forward(batch)
+        seq.tokens.extend(tokens)
+        seq.kv_len = start + n
+        return logits[:1].float().cpu() if last else None
+
+    def verify(self, handles: list[_Handle], rows: list[list[int]]) -> torch.Tensor:
+        from ..models.gqa_moe import Batch
+        S = len(handles)
+        T = sum(len(r) for r in rows)
+        b = self.bufs
+        pt = b.page_table[0].view(b.max_seqs, self.max_pages)
+        o = 0
+        for i, (h, r) in enumerate(zip(handles, rows)):
+            seq = h.seq
+            self.table.reserve(seq, seq.kv_len + len(r), copy_page=self._copy_page)
+            n = len(r)
+            b.tokens[0][o:o + n] = torch.tensor(r, dtype=torch.int32)
+            b.positions[0][o:o + n] = torch.arange(seq.kv_len, seq.kv_len + n, dtype=torch.int32)
+            b.slots[0][o:o + n] = torch.tensor(self.table.slots(seq, seq.kv_len, n), dtype=torch.int32)
+            pt[i].zero_()
+            pt[i, :len(seq.pages)] = torch.tensor(seq.pages, dtype=torch.int32)
+            b.seq_lens[0][i] = seq.kv_len + n
+            b.q_start[0][i] = o
+            o += n
+        b.q_start[0][S] = T
+        b.upload()
+        batch = Batch(b.tokens[1][:T], b.positions[1][:T], b.slots[1][:T], b.page_table[1].view(b.max_seqs, self.max_pages)[:S],
+                      b.seq_lens[1][:S], b.q_start[1][:S + 1], max(len(r) for r in rows), False, None)
+        logits = self.engine.forward(batch)
+        for h, r in zip(handles, rows):
+            h.seq.tokens.extend(r)
+            h.seq.kv_len += len(r)
+        from ..ops import kernels as K
+        out = logits[:T].float().cpu()
+        st = K.read_status()
+        if st:
+            raise RuntimeError(f"a bounded device wait ran out (status {st})")
+        return out
+
+    def commit(self, h: _Handle, keep_tokens: int) -> None:
+        if keep_tokens < h.seq.kv_len:
+            self.table.truncate(h.seq, keep_tokens)
+
+    def capture(self, h: _Handle, kind: str) -> None:
+        self.prefix.capture(h.seq, PROMPT if kind == "prompt" else TURN)
+
+    def release(self, h: _Handle) -> None:
+        if not h.dead:
+            self.table.free(h.seq)
+            h.dead = True
+
+    def quarantine(self, h: _Handle) -> None:
+        h.dead = True
+        self.quarantined.append(h)
+
+    def pages_of(self, h: _Handle) -> int:
+        return len(h.seq.pages)

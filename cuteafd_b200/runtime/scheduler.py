@@ -1,0 +1,416 @@
+"""Shared continuous-batching scheduler.
+
+One loop owns every request: admission (queue bound -> KV lease -> prefix lookup / fork -> bind),
+chunked prefill time-sliced against decode by ``decode_share``, and decode rounds
+(plan drafts -> draft -> settle under the row budget -> verify -> select -> accept -> commit ->
+observe -> emit).  A failed step fails every request of that step with a ``worker`` failure and
+quarantines their KV instead of returning it to the pool.  Readiness is published only after the
+backend, the prefix cache, the selector and the draft policy exist.
+
+The engine is behind a ``Backend`` protocol, so the same loop runs on the CUDA engine and on the
+CPU oracle backend used by the tests and the fake server.  Counterpart:
+rust/crates/cuteafd-daemon/src/shared/qwen/scheduler.rs:103-197 (Backend), :795-1350 (schedule),
+:1368-1584 (decode_round), :1459-1473 (failure + quarantine), serve/lanes.rs (lanes).
+"""
+from __future__ import annotations
+
+import queue
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Any, Protocol
+
+import torch
+
+from . import sampling
+from .reserve import KvReserve
+from .speculation import DraftHistory, DrafterSpec, NoDrafter, Plan
+
+FAIL_BAD_REQUEST, FAIL_UNAVAILABLE, FAIL_RETRY, FAIL_WORKER = "bad_request", "unavailable", "retry", "worker"
+
+
+class Backend(Protocol):
+    vocab_size: int
+    max_decode_rows: int
+    prefill_chunk: int
+    total_pages: int
+
+    def open(self, tokens: list[int]) -> tuple[Any, int]: ...                  # (handle, cached prefix length)
+    def prefill(self, handle: Any, tokens: list[int], last: bool) -> torch.Tensor | None: ...
+    def verify(self, handles: list[Any], rows: list[list[int]]) -> torch.Tensor: ...   # logits [sum(len(rows)), V]
+    def commit(self, handle: Any, keep_tokens: int) -> None: ...               # KV length after the round
+    def capture(self, handle: Any, kind: str) -> None: ...
+    def release(self, handle: Any) -> None: ...
+    def quarantine(self, handle: Any) -> None: ...
+    def pages_of(self, handle: Any) -> int: ...
+
+
+@dataclass
+class Request:
+    prompt: list[int]
+    max_tokens: int = 128
+    params: sampling.SamplingParams = field(default_factory=sampling.SamplingParams)
+    stop_ids: tuple[int, ...] = ()
+    speculation: bool = True
+    record_rows: bool = False          # probe: keep a hash of every selected logit row
+    rid: int = 0
+    events: "queue.Queue[tuple]" = field(default_factory=queue.Queue)
+    cancelled: threading.Event = field(default_factory=threading.Event)
+    arrival: float = 0.0
+
+
+@dataclass
+class Active:
+    req: Request
+    handle: Any
+    cached: int
+    prompt_done: int = 0               # prompt tokens whose KV exists (including cached)
+    generated: list[int] = field(default_factory=list)
+    last_token: int = -1
+    kv_len: int = 0
+    row_hashes: list[str] = field(default_factory=list)
+    spec: dict = field(default_factory=lambda: {"proposed": 0, "accepted": 0, "cycles": 0})
+    first_token_at: float = 0.0
+    stalled: bool = False
+
+
+@dataclass
+class SchedulerStats:
+    admitted: int = 0
+    finished: int = 0
+    failed: int = 0
+    rejected: int = 0
+    prefill_tokens: int = 0
+    cached_tokens: int = 0
+    decode_rounds: int = 0
+    emitted_tokens: int = 0
+    verify_rows: int = 0
+    verify_row_hist: dict = field(default_factory=dict)
+    stalls: int = 0
+    quarantined: int = 0
+
+
+class Scheduler:
+    def __init__(self, backend: Backend, *, max_active: int = 32, queue_depth: int = 64, queue_wait_s: float = 30.0,
+                 decode_share: float = 0.2, drafter=None, draft_control: str = "history", row_budget: int | None = None,
+                 eos_ids: tuple[int, ...] = ()):
+        self.be = backend
+        self.max_active, self.queue_depth, self.queue_wait_s = max_active, queue_depth, queue_wait_s
+        self.decode_share = decode_share
+        self.waiting: "queue.Queue[Request]" = queue.Queue()
+        self.pending: list[Request] = []
+        self.prefilling: list[Active] = []
+        self.decoding: list[Active] = []
+        self.reserve = KvReserve(backend.total_pages)
+        self.drafter = drafter or NoDrafter()
+        self.policy = DraftHistory(self.drafter.spec if hasattr(self.drafter, "spec") else DrafterSpec(0), draft_control)
+        self.row_budget = row_budget or backend.max_decode_rows
+        self.eos_ids = eos_ids
+        self.stats = SchedulerStats()
+        self._rid = 0
+        self._lock = threading.Lock()
+        self._stop = threading.Event()
+        self._t_prefill = 0.0
+        self._t_decode = 0.0
+        self.ready = threading.Event()
+        self.ready.set()                      # everything above is built: publish readiness last
+
+    # ---- submission (any thread) ------------------------------------------------------------------
+    def submit(self, req: Request) -> Request:
+        with self._lock:
+            self._rid += 1
+            req.rid = self._rid
+        req.arrival = time.monotonic()
+        if not req.prompt or any(t < 0 or t >= self.be.vocab_size for t in req.prompt) or req.max_tokens < 1:
+            req.events.put(("error", FAIL_BAD_REQUEST, "empty prompt, token out of range or max_tokens < 1"))
+            self.stats.rejected += 1
+            return req
+        if self.waiting.qsize() + len(self.pending) >= self.queue_depth:
+            req.events.put(("error", FAIL_RETRY, "admission queue full"))
+            self.stats.rejected += 1
+            return req
+        self.waiting.put(req)
+        return req
+
+    # ---- the loop ----------------------------------------------------------------------------------
+    def run_forever(self, idle_sleep: float = 0.001) -> None:
+        while not self._stop.is_set():
+            if not self.step():
+                time.sleep(idle_sleep)
+
+    def stop(self) -> None:
+        self._stop.set()
+
+    def step(self) -> bool:
+        """One scheduling iteration.  Returns False when there was nothing to do."""
+        self._drain_queue()
+        self._admit()
+        # While both kinds of work exist, decode gets ``decode_share`` of the measured step time and
+        # prefill the rest; the shares are tracked with exponentially decayed clocks.
+        if self.prefilling and self.decoding:
+            total = self._t_prefill + self._t_decode
+            do_prefill = total == 0.0 or self._t_decode / total >= self.decode_share
+        else:
+            do_prefill = bool(self.prefilling)
+        t0 = time.monotonic()
+        if do_prefill:
+            did = self._prefill_one()
+            self._t_prefill = 0.9 * self._t_prefill + (time.monotonic() - t0)
+            self._t_decode *= 0.9
+        elif self.decoding:
+            did = self._decode_round()
+            self._t_decode = 0.9 * self._t_decode + (time.monotonic() - t0)
+            self._t_prefill *= 0.9
+        else:
+            did = False
+        return did
+
+    def _drain_queue(self) -> None:
+        while True:
+            try:
+                self.pending.append(self.waiting.get_nowait())
+            except queue.Empty:
+                break
+        now = time.monotonic()
+        keep = []
+        for r in self.pending:
+            if r.cancelled.is_set():
+                continue
+            if now - r.arrival > self.queue_wait_s:
+                r.events.put(("error", FAIL_RETRY, "queue wait exceeded"))
+                self.stats.rejected += 1
+            else:
+                keep.append(r)
+        self.pending = keep
+
+    def _admit(self) -> None:
+        while self.pending and len(self.prefilling) + len(self.decoding) < self.max_active:
+            req = self.pending[0]
+            try:
+                handle, cached = self.be.open(req.prompt)
+            except Exception as e:                      # a failed restore is a miss, not an error
+                req.events.put(("error", FAIL_UNAVAILABLE, f"open failed: {e}"))
+                self.pending.pop(0)
+                self.stats.failed += 1
+                continue
+            lease = self.reserve.lease(req.rid, len(req.prompt), req.max_tokens, shared_pages=cached // 64)
+            if lease is None:
+                self.be.release(handle)
+                if not self.prefilling and not self.decoding:
+                    req.events.put(("error", FAIL_RETRY, "request does not fit the KV pool"))
+                    self.pending.pop(0)
+                    self.stats.rejected += 1
+                    continue
+                break                                   # wait for running requests to release pages
+            self.pending.pop(0)
+            a = Active(req, handle, cached, prompt_done=cached, kv_len=cached)
+            self.prefilling.append(a)
+            self.stats.admitted += 1
+            self.stats.cached_tokens += cached
+
+    # ---- prefill -----------------------------------------------------------------------------------
+    def _prefill_one(self) -> bool:
+        a = self.prefilling[0]
+        if a.req.cancelled.is_set():
+            self.prefilling.pop(0)
+            if a.prompt_done >= 64:
+                self._safe(lambda: self.be.capture(a.handle, "prompt"))     # parked at a chunk boundary
+            self._finish(a, None)
+            return True
+        n = min(self.be.prefill_chunk, len(a.req.prompt) - a.prompt_done)
+        chunk = a.req.prompt[a.prompt_done:a.prompt_done + n]
+        last = a.prompt_done + n == len(a.req.prompt)
+        try:
+            logits = self.be.prefill(a.handle, chunk, last)
+        except Exception as e:
+            self.prefilling.pop(0)
+            self._fail([a], f"prefill failed: {e}")
+            return True
+        a.prompt_done += n
+        a.kv_len = a.prompt_done
+        self.stats.prefill_tokens += n
+        if last:
+            self.prefilling.pop(0)
+            self._safe(lambda: self.be.capture(a.handle, "prompt"))
+            tok = self._select(a, logits[0] if logits.dim() == 2 else logits, len(a.req.prompt))
+            a.first_token_at = time.monotonic()
+            if tok is None:
+                return True
+            if not self._emit(a, [tok]):
+                self.decoding.append(a)
+        return True
+
+    # ---- decode round -------------------------------------------------------------------------------
+    def _decode_round(self) -> bool:
+        batch = [a for a in self.decoding if not a.req.cancelled.is_set()]
+        for a in self.decoding:
+            if a.req.cancelled.is_set():
+                self._finish(a, None, retain=False)        # a cancelled decode is not retained
+        self.decoding = batch
+        if not batch:
+            return False
+        # KV top-ups: a request that cannot grow stalls for this round (never truncated)
+        runnable = []
+        for a in batch:
+            need = a.kv_len + 1 + self.policy.spec.block + self.policy.spec.copy
+            if self.reserve.needs_top_up(a.req.rid, need) and not self.reserve.top_up(a.req.rid):
+                a.stalled = True
+                self.stats.stalls += 1
+                continue
+            a.stalled = False
+            runnable.append(a)
+        if not runnable:
+            return False
+        runnable = runnable[: self.be.max_decode_rows]
+        plans: list[Plan] = []
+        drafts: list[list[int]] = []
+        heads: list[list[float] | None] = []
+        for a in runnable:
+            room = a.req.max_tokens - len(a.generated) - 1
+            use = a.req.speculation and room > 0
+            plan = self.policy.plan(a.req.rid, room if use else 0)
+            toks, scores = (self.drafter.draft(a.req.rid, None, a.last_token, plan.keep) if plan.keep else ([], None))
+            plan = self.policy.refine(plan, len(toks), scores)
+            toks = toks[:plan.keep]
+            extra = self.policy.extend_copy(plan, a.req.prompt + a.generated, toks, a.req.params.greedy) if toks else []
+            plans.append(plan)
+            drafts.append(toks + extra[: max(0, room - len(toks))])
+            heads.append(scores)
+        self.policy.settle(plans, self.row_budget)
+        drafts = [d[: p.keep + p.copy] for d, p in zip(drafts, plans)]
+        rows = [[a.last_token] + d for a, d in zip(runnable, drafts)]
+        try:
+            logits = self.be.verify([a.handle for a in runnable], rows)
+        except Exception as e:
+            self.decoding = [a for a in self.decoding if a not in runnable]
+            self._fail(runnable, f"decode step failed: {e}")
+            return True
+        self.stats.decode_rounds += 1
+        n_rows = sum(len(r) for r in rows)
+        self.stats.verify_rows += n_rows
+        self.stats.verify_row_hist[n_rows] = self.stats.verify_row_hist.get(n_rows, 0) + 1
+        off = 0
+        done: list[Active] = []
+        for a, plan, d, r, hs in zip(runnable, plans, drafts, rows, heads):
+            sel = []
+            bad = False
+            for j in range(len(r)):
+                # row j is drawn at absolute position (tokens so far) + j: layout cannot change a draw
+                t = self._select(a, logits[off + j], len(a.req.prompt) + len(a.generated) + j, emit_error=False)
+                if t is None:
+                    bad = True
+                    break
+                sel.append(t)
+                if j < len(d) and d[j] != t:
+                    break                                  # later rows are conditioned on a rejected draft
+            off += len(r)
+            if bad:
+                self._fail([a], "non-finite logits")
+                done.append(a)
+                continue
+            n_acc, bonus = sampling.accept_prefix(sel, d)
+            new = d[:n_acc] + [bonus]
+            a.kv_len += 1 + n_acc                           # last_token + accepted drafts now have KV
+            self.be.commit(a.handle, a.kv_len)
+            stopped = self._emit(a, new)
+            self.policy.observe(plan, n_acc, censored=stopped and n_acc < len(d), head_scores=hs)
+            self.drafter.accept(a.req.rid, new)
+            a.spec["proposed"] += len(d)
+            a.spec["accepted"] += n_acc
+            a.spec["cycles"] += 1
+            if stopped:
+                done.append(a)
+        self.decoding = [a for a in self.decoding if a not in done]
+        return True
+
+    # ---- helpers -------------------------------------------------------------------------------------
+    def _select(self, a: Active, row: torch.Tensor, position: int, emit_error: bool = True) -> int | None:
+        try:
+            tok = sampling.select_token(row, a.req.params, position)
+        except sampling.SamplingError as e:
+            if emit_error:
+                self._fail([a], str(e))
+            return None
+        if a.req.record_rows:
+            a.row_hashes.append(sampling.row_hash(row))
+        return tok
+
+    def _emit(self, a: Active, toks: list[int]) -> bool:
+        """Append tokens, stream them, return True when the request is finished."""
+        finish = None
+        out = []
+        for t in toks:
+            a.generated.append(t)
+            out.append(t)
+            if t in a.req.stop_ids or t in self.eos_ids:
+                finish = "stop"
+                break
+            if len(a.generated) >= a.req.max_tokens:
+                finish = "length"
+                break
+        a.last_token = a.generated[-1]
+        self.stats.emitted_tokens += len(out)
+        a.req.events.put(("tokens", out))
+        if finish:
+            self._finish(a, finish)
+            return True
+        return False
+
+    def _finish(self, a: Active, reason: str | None, retain: bool = True) -> None:
+        if reason is not None and retain:
+            self._safe(lambda: self.be.capture(a.handle, "turn"))
+        self._safe(lambda: self.be.release(a.handle))
+        self.reserve.release(a.req.rid)
+        self.policy.forget(a.req.rid)
+        if reason is not None:
+            usage = {"prompt_tokens": len(a.req.prompt), "completion_tokens": len(a.generated), "cached_tokens": a.cached,
+                     "speculation": dict(a.spec, request_id=a.req.rid)}
+            a.req.events.put(("done", reason, usage, list(a.row_hashes)))
+            self.stats.finished += 1
+        else:
+            a.req.events.put(("done", "cancelled", {}, []))
+
+    def _fail(self, actives: list[Active], msg: str) -> None:
+        for a in actives:
+            try:
+                self.be.release(a.handle)
+            except Exception:
+                self._safe(lambda: self.be.quarantine(a.handle))
+                self.stats.quarantined += 1
+            self.reserve.release(a.req.rid)
+            self.policy.forget(a.req.rid)
+            a.req.events.put(("error", FAIL_WORKER, msg))
+            self.stats.failed += 1
+
+    @staticmethod
+    def _safe(fn) -> None:
+        try:
+            fn()
+        except Exception:
+            pass
+
+    def snapshot(self) -> dict:
+        s = self.stats
+        return {"active": len(self.decoding), "prefilling": len(self.prefilling), "queued": len(self.pending) + self.waiting.qsize(),
+                "admitted": s.admitted, "finished": s.finished, "failed": s.failed, "rejected": s.rejected,
+                "prefill_tokens": s.prefill_tokens, "cached_tokens": s.cached_tokens, "decode_rounds": s.decode_rounds,
+                "emitted_tokens": s.emitted_tokens, "verify_rows": s.verify_rows, "stalls": s.stalls,
+                "quarantined": s.quarantined, "draft_policy": dict(self.policy.lifetime),
+                "kv": {"total_pages": self.reserve.total, "leased_pages": self.reserve.leased}}
+
+
+def collect(req: Request, timeout: float = 60.0) -> dict:
+    """Block until a request finishes; returns {"tokens", "finish", "usage", "error", "row_hashes"}."""
+    toks: list[int] = []
+    t0 = time.monotonic()
+    while True:
+        try:
+            ev = req.events.get(timeout=max(0.01, timeout - (time.monotonic() - t0)))
+        except queue.Empty:
+            return {"tokens": toks, "finish": None, "usage": {}, "error": ("timeout", "no event"), "row_hashes": []}
+        if ev[0] == "tokens":
+            toks.extend(ev[1])
+        elif ev[0] == "done":
+            return {"tokens": toks, "finish": ev[1], "usage": ev[2], "error": None, "row_hashes": ev[3]}
+        elif ev[0] == "error":
+            return {"tokens": toks, "finish": None, "usage": {}, "error": (ev[1], ev[2]), "row_hashes": []}

@@ -1,0 +1,265 @@
+"""Host-side runtime on CPU: page pool, prefix cache, KV leases, host tier, sampler oracle,
+draft policy, and the scheduler over the oracle backend (lossless speculation, exact prefix
+reuse, failure quarantine, admission limits)."""
+import threading
+
+import pytest
+import torch
+
+from cuteafd_b200 import tiny_moe
+from cuteafd_b200.ref.model import init_weights
+from cuteafd_b200.runtime import hostcache, sampling, speculation
+from cuteafd_b200.runtime.backends import OracleBackend
+from cuteafd_b200.runtime.paged import PAGE, OutOfPages, PagePool, SequenceTable
+from cuteafd_b200.runtime.prefix_cache import PROMPT, TURN, PrefixCache, chain_hashes
+from cuteafd_b200.runtime.reserve import KvReserve
+from cuteafd_b200.runtime.scheduler import FAIL_RETRY, FAIL_WORKER, Request, Scheduler, collect
+
+
+# ---- pages ------------------------------------------------------------------------------------------
+def test_page_pool_cow_and_truncate():
+    pool = PagePool(8)
+    tab = SequenceTable(pool)
+    a = tab.new()
+    tab.reserve(a, 100)
+    a.kv_len, a.tokens = 100, list(range(100))
+    assert len(a.pages) == 2 and 0 not in a.pages
+    b = tab.fork(a)
+    assert b.pages == a.pages and pool.shared(a.pages[1])
+    copied = []
+    tab.reserve(b, 101, copy_page=lambda s, d: copied.append((s, d)))
+    assert copied and b.pages[1] != a.pages[1] and b.pages[0] == a.pages[0]
+    tab.truncate(b, 64)
+    assert len(b.pages) == 1
+    tab.free(a); tab.free(b)
+    assert pool.free_pages == 7
+    with pytest.raises(OutOfPages):
+        c = tab.new()
+        tab.reserve(c, 8 * PAGE)
+
+
+# ---- prefix cache ------------------------------------------------------------------------------------
+def _seq_with(tab, tokens):
+    s = tab.new()
+    tab.reserve(s, len(tokens))
+    s.tokens, s.kv_len = list(tokens), len(tokens)
+    return s
+
+
+def test_prefix_cache_share_tail_and_evict():
+    pool = PagePool(64)
+    tab = SequenceTable(pool)
+    pc = PrefixCache(pool, tab, max_pages=12)
+    base = list(range(200))
+    s = _seq_with(tab, base)
+    snap = pc.capture(s, PROMPT)
+    assert snap.length == 200 and snap.tail_page == s.pages[3]
+    # same prefix + new suffix: full pages and the partial tail are shared
+    q, m = pc.admit(base + [7, 8, 9])
+    assert m.length == 200 and m.tail_shared and q.pages == s.pages[:4]
+    # a request equal to the cached prompt must still compute one token
+    q2, m2 = pc.admit(base)
+    assert 0 < m2.length < 200 and m2.length % PAGE == 0
+    # diverging inside the second page: only the first page matches
+    q3, m3 = pc.admit(base[:70] + [999] * 50)
+    assert m3.length == 64
+    for x in (q, q2, q3, s):
+        tab.free(x)
+    assert pc.held_pages == 4
+    # budget: capturing more than max_pages evicts least recently used prompt snapshots first
+    for i in range(4):
+        t = _seq_with(tab, [1000 * (i + 1) + j for j in range(256)])
+        pc.capture(t, TURN if i == 0 else PROMPT)
+        tab.free(t)
+    assert pc.held_pages <= 12 and pc.stats.evicted >= 1
+    kinds = {s.kind for s in pc.snapshots.values()}
+    assert TURN in kinds                                   # the turn snapshot outlives prompt snapshots
+    pc.clear()
+    assert pc.held_pages == 0 and pool.free_pages == 63
+
+
+def test_chain_hash_is_prefix_stable():
+    a = chain_hashes(list(range(200)))
+    b = chain_hashes(list(range(128)) + [5] * 72)
+    assert len(a) == 3 and a[:2] == b[:2] and a[2] != b[2]
+    assert chain_hashes(list(range(200)), b"img") != a
+
+
+# ---- reserve -----------------------------------------------------------------------------------------
+def test_kv_reserve_bankers_rule():
+    r = KvReserve(total_pages=100, decode_chunk_tokens=640)          # 10-page chunks
+    a = r.lease(1, prompt_tokens=640, max_new_tokens=3200)           # 10 + 10 leased, max 60
+    b = r.lease(2, prompt_tokens=640, max_new_tokens=3200)
+    assert a and b and r.leased == 40
+    assert r.lease(3, prompt_tokens=6400, max_new_tokens=64) is None  # would leave nobody able to finish
+    assert r.top_up(1) and r.top_up(1)                               # 40 pages
+    assert r.top_up(2)                                               # 30 pages -> 70 leased, 30 free
+    assert r.top_up(1)                                               # 50: still safe (1 needs 10 more <= 20 free)
+    assert not r.top_up(2) or r.unleased >= 0
+    r.release(1)
+    assert r.top_up(2)
+    assert r.needs_top_up(2, 64 * 200) is True
+
+
+# ---- host tier ----------------------------------------------------------------------------------------
+def test_host_cache_sharing_timeouts_and_simulator():
+    eng = hostcache.StubCopyEngine(page_bytes=1 << 20, bandwidth_gbs=1.0, latency_s=1e-3)
+    hc = hostcache.HostCache(eng, slots=24)
+    base = list(range(640))
+    k = chain_hashes(base)
+    assert hc.store(tuple(base), "prompt", list(range(10)), k)
+    assert not hc.store(tuple(range(100)), "prompt", [1, 2], [])          # below the 512-token floor
+    longer = base + list(range(64))
+    assert hc.store(tuple(longer), "turn", list(range(11)), chain_hashes(longer))
+    assert hc.stats.shared_pages == 10                                     # common pages stored once
+    s = hc.lookup(longer + [1])
+    assert s is not None and s.length == len(longer)
+    assert not hc.restore(s, list(range(11)), budget_s=1e-6)               # store still in flight: miss
+    eng.advance(1.0)
+    assert hc.restore(s, list(range(11)), budget_s=1.0)
+    hc.check_invariants()
+    for seed in range(5):
+        st = hostcache.simulate(seed, steps=300)
+        assert st.stored > 0 and st.lookups > 0
+    assert hostcache.default_quota_bytes() <= 32 << 30
+
+
+# ---- sampling -----------------------------------------------------------------------------------------
+def test_sampler_semantics():
+    P = sampling.SamplingParams
+    logits = torch.tensor([1.0, 3.0, 3.0, -2.0, 0.5])
+    assert sampling.select_token(logits, P(), 0) == 1                       # greedy tie -> lowest id
+    assert sampling.select_token(logits, P(temperature=1.0, top_k=1), 0) == 1
+    mask = torch.tensor([True, False, False, True, True])
+    assert sampling.select_token(logits, P(), 0, mask) == 0
+    with pytest.raises(sampling.SamplingError):
+        sampling.select_token(logits, P(), 0, torch.zeros(5, dtype=torch.bool))
+    bad = logits.clone(); bad[3] = float("nan")
+    toks, status = sampling.select_rows(torch.stack([logits, bad]), [P(), P()], [0, 0])
+    assert toks[0] == 1 and status == [sampling.STATUS_OK, sampling.STATUS_NONFINITE]
+    p = P(temperature=0.8, top_k=3, top_p=0.9, min_p=0.05, seed=42)
+    draws = [sampling.select_token(logits, p, pos) for pos in range(200)]
+    assert set(draws) <= {0, 1, 2} and len(set(draws)) > 1
+    assert draws == [sampling.select_token(logits, p, pos) for pos in range(200)]     # pure in (seed, position)
+    assert [p.uniform(i) for i in range(3)] != [P(temperature=0.8, seed=43).uniform(i) for i in range(3)]
+    assert all(0.0 <= p.uniform(i) < 1.0 for i in range(1000))
+    # top_p keeps the smallest prefix reaching the mass; uniform at both ends stays inside it
+    sharp = torch.tensor([10.0, 0.0, 0.0, 0.0])
+    assert sampling.select_token(sharp, P(temperature=1.0, top_p=0.5), 0, uniform=0.999) == 0
+    assert sampling.accept_prefix([5, 6, 9, 1], [5, 6, 7]) == (2, 9)
+    assert sampling.accept_prefix([5, 6, 7, 1], [5, 6, 7]) == (3, 1)
+    with pytest.raises(sampling.SamplingError):
+        P(temperature=3.0)
+
+
+# ---- draft policy -------------------------------------------------------------------------------------
+def test_history_policy_grows_and_shrinks():
+    pol = speculation.DraftHistory(speculation.DrafterSpec(block=6))
+    p = pol.plan(1, room=100)
+    assert p.keep == 6                                           # cold neural rate 1.0: optimistic start
+    for _ in range(12):                                          # everything rejected at position 0
+        p = pol.plan(1, room=100)
+        pol.observe(p, accepted=0)
+    p = pol.plan(1, room=100)
+    assert p.keep == 1 and p.explore == 0                        # only the explored position remains
+    for _ in range(12):
+        p = pol.plan(1, room=100)
+        pol.observe(p, accepted=p.keep)
+    assert pol.plan(1, room=100).keep >= 3                        # grows back
+    assert pol.plan(1, room=2).keep <= 2                          # capped by room
+    plans = [pol.plan(r, 100) for r in (10, 11, 12)]
+    for q in plans:
+        q.keep = 6
+    pol.settle(plans, row_budget=9)
+    assert sum(1 + q.keep + q.copy for q in plans) <= 9
+    off = speculation.DraftHistory(speculation.DrafterSpec(block=6), control="off")
+    assert off.plan(1, 100).keep == 0
+
+
+def test_copy_continuation_needs_anchor():
+    hist = [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 50, 1, 2, 3, 4, 5, 6]
+    assert speculation.copy_continuation(hist, [7, 8, 9]) == [10, 11, 12, 50, 1, 2, 3, 4, 5, 6]
+    assert speculation.copy_continuation(hist, [7, 8]) == []               # fewer than 3 agreeing drafts
+    assert speculation.copy_continuation(hist, [7, 99, 9]) == []           # disagreement
+    assert speculation.copy_continuation([1, 2, 3], [4, 5, 6]) == []
+
+
+# ---- scheduler over the oracle --------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def oracle():
+    cfg = tiny_moe()
+    return cfg, init_weights(cfg, seed=0)
+
+
+def _run(sched, reqs, steps=4000):
+    for r in reqs:
+        sched.submit(r)
+    for _ in range(steps):
+        if not sched.step() and sched.waiting.empty() and not sched.pending and not sched.prefilling and not sched.decoding:
+            break
+    return [collect(r, timeout=1.0) for r in reqs]
+
+
+def test_scheduler_lossless_speculation_and_prefix_reuse(oracle):
+    cfg, params = oracle
+    g = torch.Generator().manual_seed(3)
+    pattern = torch.randint(0, cfg.vocab_size, (12,), generator=g).tolist()
+    prompt = (pattern * 9)[:100]                                  # repetitive: the n-gram drafter proposes
+    plain = Scheduler(OracleBackend(cfg, params), drafter=None)
+    base = _run(plain, [Request(prompt, max_tokens=24, record_rows=True, speculation=False)])[0]
+    assert base["finish"] == "length" and len(base["tokens"]) == 24
+    be = OracleBackend(cfg, params)
+    spec = Scheduler(be, drafter=speculation.NgramDrafter(block=4))
+    be_spec = spec.drafter
+    be_spec.hist[1] = list(prompt)                                 # the drafter sees the prompt as history
+    out = _run(spec, [Request(prompt, max_tokens=24, record_rows=True)])[0]
+    assert out["tokens"] == base["tokens"]                         # ids identical with drafts on
+    assert out["usage"]["speculation"]["cycles"] <= 24
+    # the same prompt again: served from the prefix cache, identical tokens and row hashes
+    again = _run(spec, [Request(prompt, max_tokens=24, record_rows=True, speculation=False)])[0]
+    assert again["usage"]["cached_tokens"] >= 64
+    assert again["tokens"] == base["tokens"]
+    assert again["row_hashes"] == base["row_hashes"]
+    assert be.prefix.stats.hits >= 1 and spec.snapshot()["finished"] == 2
+
+
+def test_scheduler_batches_and_sampling_positions(oracle):
+    cfg, params = oracle
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (30, 70, 45)]
+    P = sampling.SamplingParams(temperature=0.9, top_p=0.95, seed=11)
+    solo = [_run(Scheduler(OracleBackend(cfg, params)), [Request(p, max_tokens=10, params=P)])[0]["tokens"] for p in prompts]
+    together = _run(Scheduler(OracleBackend(cfg, params), max_active=3), [Request(p, max_tokens=10, params=P) for p in prompts])
+    assert [o["tokens"] for o in together] == solo                 # batching does not change a sampled token
+
+
+def test_scheduler_failure_quarantine_and_limits(oracle):
+    cfg, params = oracle
+    be = OracleBackend(cfg, params, fail_on_step=2)
+    s = Scheduler(be, queue_depth=2)
+    reqs = [Request([1, 2, 3, 4], max_tokens=8), Request([5, 6, 7], max_tokens=8), Request([9] * 5, max_tokens=8)]
+    out = _run(s, reqs)
+    assert out[2]["error"][0] == FAIL_RETRY                        # third request: queue full -> retry class
+    assert all(o["error"] and o["error"][0] == FAIL_WORKER for o in out[:2])
+    assert s.stats.failed == 2 and s.reserve.leased == 0
+    ok = _run(s, [Request([1, 2, 3], max_tokens=4)])[0]            # the scheduler keeps serving
+    assert ok["finish"] == "length"
+    bad = _run(s, [Request([], max_tokens=4)])[0]
+    assert bad["error"][0] == "bad_request"
+    # a request larger than the pool is refused with the retry class, not a crash
+    tiny = Scheduler(OracleBackend(cfg, params, total_pages=4))
+    big = _run(tiny, [Request([1] * 600, max_tokens=8)])[0]
+    assert big["error"][0] == FAIL_RETRY
+
+
+def test_scheduler_thread_and_cancel(oracle):
+    cfg, params = oracle
+    s = Scheduler(OracleBackend(cfg, params))
+    t = threading.Thread(target=s.run_forever, daemon=True)
+    t.start()
+    r1 = s.submit(Request([3, 4, 5, 6], max_tokens=6, stop_ids=()))
+    r2 = s.submit(Request([3, 4, 5, 6], max_tokens=200))
+    r2.cancelled.set()
+    o1 = collect(r1, timeout=30)
+    s.stop(); t.join(timeout=5)
+    assert o1["finish"] == "length" and len(o1["tokens"]) == 6
