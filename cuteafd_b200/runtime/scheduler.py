@@ -53,6 +53,7 @@ class Request:
     stop_ids: tuple[int, ...] = ()
     speculation: bool = True
     record_rows: bool = False          # probe: keep a hash of every selected logit row
+    constraint: Any = None             # TokenConstraint: allowed-token mask applied first in the chain
     rid: int = 0
     events: "queue.Queue[tuple]" = field(default_factory=queue.Queue)
     cancelled: threading.Event = field(default_factory=threading.Event)
@@ -267,7 +268,7 @@ class Scheduler:
         heads: list[list[float] | None] = []
         for a in runnable:
             room = a.req.max_tokens - len(a.generated) - 1
-            use = a.req.speculation and room > 0
+            use = a.req.speculation and room > 0 and a.req.constraint is None
             plan = self.policy.plan(a.req.rid, room if use else 0)
             toks, scores = (self.drafter.draft(a.req.rid, None, a.last_token, plan.keep) if plan.keep else ([], None))
             plan = self.policy.refine(plan, len(toks), scores)
@@ -326,7 +327,10 @@ class Scheduler:
     # ---- helpers -------------------------------------------------------------------------------------
     def _select(self, a: Active, row: torch.Tensor, position: int, emit_error: bool = True) -> int | None:
         try:
-            tok = sampling.select_token(row, a.req.params, position)
+            c = a.req.constraint
+            tok = sampling.select_token(row, a.req.params, position, c.mask() if c is not None else None)
+            if c is not None:
+                c.advance(tok)
         except sampling.SamplingError as e:
             if emit_error:
                 self._fail([a], str(e))
@@ -343,6 +347,9 @@ class Scheduler:
             a.generated.append(t)
             out.append(t)
             if t in a.req.stop_ids or t in self.eos_ids:
+                finish = "stop"
+                break
+            if a.req.constraint is not None and a.req.constraint.finished():
                 finish = "stop"
                 break
             if len(a.generated) >= a.req.max_tokens:

@@ -1,0 +1,174 @@
+"""Wire formats: OpenAI Chat Completions, Anthropic Messages and OpenAI Responses bodies to and
+from the scheduler's ``Request`` / event stream.
+
+Defaults match the reference: temperature 0 (greedy), top_p 1, min_p 0, no top_k, optional seed
+(rust/crates/cuteafd-api/src/openai.rs:641-660).  Failure classes map to HTTP the same way: bad
+request 400, unavailable 503, retry 429 with ``Retry-After: 1``, worker 500
+(rust/crates/cuteafd-api/src/openai.rs:281-286; docs/client-apis.md:40-50).  ``usage.speculation``
+carries {request_id, proposed, accepted, cycles} (docs/client-apis.md:31-38).  The probe header
+``x-cuteafd-probe`` carries a JSON ProbeSpec: prompt_ids (synthetic token-id prompts),
+no_speculation, record_rows (rust/crates/cuteafd-api/src/openai/probe.rs:19-110).
+"""
+from __future__ import annotations
+
+import json
+import time
+import uuid
+
+from ..runtime import sampling
+from ..runtime.scheduler import FAIL_BAD_REQUEST, FAIL_RETRY, FAIL_UNAVAILABLE, FAIL_WORKER, Request
+from . import constraints
+from .tokenizer import parse_tool_calls, render_chat
+
+HTTP_OF = {FAIL_BAD_REQUEST: 400, FAIL_UNAVAILABLE: 503, FAIL_RETRY: 429, FAIL_WORKER: 500, "timeout": 504}
+PROBE_HEADER = "x-cuteafd-probe"
+
+
+class BadRequest(ValueError):
+    pass
+
+
+def _params(body: dict) -> sampling.SamplingParams:
+    try:
+        return sampling.SamplingParams(temperature=float(body.get("temperature", 0.0) or 0.0), top_p=float(body.get("top_p", 1.0) or 1.0),
+                                       top_k=(int(body["top_k"]) if body.get("top_k") not in (None, 0, -1) else None),
+                                       min_p=float(body.get("min_p", 0.0) or 0.0), seed=int(body.get("seed", 0) or 0))
+    except (sampling.SamplingError, TypeError, ValueError) as e:
+        raise BadRequest(str(e)) from e
+
+
+def _stops(body: dict, tok) -> tuple[int, ...]:
+    stop = body.get("stop") or body.get("stop_sequences") or []
+    if isinstance(stop, str):
+        stop = [stop]
+    ids = []
+    for s in stop:
+        e = tok.encode(s)
+        if len(e) == 1:
+            ids.append(e[0])
+    return tuple(ids) + tuple(getattr(tok, "eos_ids", ()))
+
+
+def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, flavor: str = "openai") -> Request:
+    # a probe too large for a header (a long synthetic prompt) may ride in the body instead
+    probe = {**(body.get("cuteafd_probe") or {}), **(probe or {})}
+    if probe.get("prompt_ids"):
+        prompt = [int(t) for t in probe["prompt_ids"]]
+    else:
+        if flavor == "anthropic":
+            msgs = []
+            if body.get("system"):
+                sysm = body["system"]
+                msgs.append({"role": "system", "content": sysm if isinstance(sysm, str) else "".join(p.get("text", "") for p in sysm)})
+            msgs += list(body.get("messages") or [])
+        elif flavor == "responses":
+            inp = body.get("input")
+            msgs = [{"role": "user", "content": inp}] if isinstance(inp, str) else [
+                {"role": m.get("role", "user"), "content": m.get("content")} for m in (inp or []) if isinstance(m, dict)]
+            if body.get("instructions"):
+                msgs.insert(0, {"role": "system", "content": body["instructions"]})
+        else:
+            msgs = list(body.get("messages") or [])
+        if not msgs:
+            raise BadRequest("messages must not be empty")
+        prompt = tok.encode(render_chat(msgs, True, body.get("tools")))
+    max_tokens = body.get("max_tokens") or body.get("max_completion_tokens") or body.get("max_output_tokens") or 256
+    if not isinstance(max_tokens, int) or max_tokens < 1:
+        raise BadRequest("max_tokens must be a positive integer")
+    try:
+        cons = constraints.from_response_format(body.get("response_format"), tok, vocab_size)
+    except ValueError as e:
+        raise BadRequest(str(e)) from e
+    return Request(prompt=prompt, max_tokens=max_tokens, params=_params(body), stop_ids=_stops(body, tok),
+                   speculation=not probe.get("no_speculation", False), record_rows=bool(probe.get("record_rows", False)),
+                   constraint=cons)
+
+
+def parse_probe(headers) -> dict:
+    raw = headers.get(PROBE_HEADER)
+    if not raw:
+        return {}
+    try:
+        d = json.loads(raw)
+    except json.JSONDecodeError as e:
+        raise BadRequest(f"{PROBE_HEADER}: {e}") from e
+    if not isinstance(d, dict):
+        raise BadRequest(f"{PROBE_HEADER} must be a JSON object")
+    return d
+
+
+def usage_block(u: dict) -> dict:
+    out = {"prompt_tokens": u.get("prompt_tokens", 0), "completion_tokens": u.get("completion_tokens", 0),
+           "total_tokens": u.get("prompt_tokens", 0) + u.get("completion_tokens", 0),
+           "prompt_tokens_details": {"cached_tokens": u.get("cached_tokens", 0)}}
+    if "speculation" in u:
+        out["speculation"] = u["speculation"]
+    return out
+
+
+# ---- OpenAI chat completions ---------------------------------------------------------------------------
+def chat_completion(model: str, text: str, finish: str, usage: dict, probe_rows: list[str] | None = None) -> dict:
+    content, calls = parse_tool_calls(text)
+    msg = {"role": "assistant", "content": content}
+    if calls:
+        msg["tool_calls"] = calls
+        finish = "tool_calls"
+    out = {"id": "chatcmpl-" + uuid.uuid4().hex[:24], "object": "chat.completion", "created": int(time.time()), "model": model,
+           "choices": [{"index": 0, "message": msg, "finish_reason": finish}], "usage": usage_block(usage)}
+    if probe_rows:
+        out["probe"] = {"row_hashes": probe_rows}
+    return out
+
+
+def chat_chunk(cid: str, model: str, delta: dict, finish: str | None = None, usage: dict | None = None) -> dict:
+    out = {"id": cid, "object": "chat.completion.chunk", "created": int(time.time()), "model": model,
+           "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
+    if usage is not None:
+        out["usage"] = usage_block(usage)
+    return out
+
+
+# ---- Anthropic messages -----------------------------------------------------------------------------------
+def anthropic_message(model: str, text: str, finish: str, usage: dict) -> dict:
+    content, calls = parse_tool_calls(text)
+    blocks = [{"type": "text", "text": content}] if content or not calls else []
+    for c in calls:
+        blocks.append({"type": "tool_use", "id": "toolu_" + uuid.uuid4().hex[:20], "name": c["function"]["name"],
+                       "input": json.loads(c["function"]["arguments"] or "{}")})
+    stop = {"stop": "end_turn", "length": "max_tokens"}.get(finish, finish)
+    if calls:
+        stop = "tool_use"
+    return {"id": "msg_" + uuid.uuid4().hex[:24], "type": "message", "role": "assistant", "model": model, "content": blocks,
+            "stop_reason": stop, "stop_sequence": None,
+            "usage": {"input_tokens": usage.get("prompt_tokens", 0), "output_tokens": usage.get("completion_tokens", 0),
+                      "cache_read_input_tokens": usage.get("cached_tokens", 0)}}
+
+
+def anthropic_events(model: str, usage_in: int):
+    mid = "msg_" + uuid.uuid4().hex[:24]
+    start = {"type": "message_start", "message": {"id": mid, "type": "message", "role": "assistant", "model": model, "content": [],
+                                                  "stop_reason": None, "usage": {"input_tokens": usage_in, "output_tokens": 0}}}
+    return mid, [("message_start", start), ("content_block_start", {"type": "content_block_start", "index": 0,
+                                                                     "content_block": {"type": "text", "text": ""}})]
+
+
+# ---- OpenAI responses -------------------------------------------------------------------------------------
+def responses_object(model: str, text: str, finish: str, usage: dict, rid: str | None = None) -> dict:
+    rid = rid or "resp_" + uuid.uuid4().hex[:24]
+    return {"id": rid, "object": "response", "created_at": int(time.time()), "model": model,
+            "status": "completed" if finish in ("stop", "length") else "incomplete",
+            "output": [{"type": "message", "id": "msg_" + uuid.uuid4().hex[:20], "role": "assistant", "status": "completed",
+                        "content": [{"type": "output_text", "text": text, "annotations": []}]}],
+            "output_text": text,
+            "usage": {"input_tokens": usage.get("prompt_tokens", 0), "output_tokens": usage.get("completion_tokens", 0),
+                      "total_tokens": usage.get("prompt_tokens", 0) + usage.get("completion_tokens", 0)}}
+
+
+def error_body(kind: str, message: str, flavor: str = "openai") -> tuple[int, dict, dict]:
+    status = HTTP_OF.get(kind, 500)
+    headers = {"Retry-After": "1"} if kind == FAIL_RETRY else {}
+    if flavor == "anthropic":
+        t = {400: "invalid_request_error", 429: "rate_limit_error", 503: "overloaded_error"}.get(status, "api_error")
+        return status, {"type": "error", "error": {"type": t, "message": message}}, headers
+    t = {400: "invalid_request_error", 429: "rate_limit_exceeded", 503: "service_unavailable"}.get(status, "server_error")
+    return status, {"error": {"message": message, "type": t, "code": kind}}, headers

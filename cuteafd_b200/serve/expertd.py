@@ -1,0 +1,40 @@
+"""``cuteafd expertd``: one expert-rank worker process.
+
+Joins the NCCL group of a deployment, maps the symmetric exchange buffers, loads the routed
+experts it owns (from a snapshot, or random weights for benchmarks) and serves announced steps
+until the attention rank says stop.  Counterpart:
+rust/crates/cuteafd-daemon/src/shared/experts/service.rs:22-135, service/local.rs:278.
+"""
+from __future__ import annotations
+
+import json
+import os
+
+
+def run_expertd(args) -> int:
+    import torch
+    import torch.distributed as dist
+
+    from ..config import PRESETS
+    from ..parallel.afd import build_afd
+    os.environ.setdefault("MASTER_ADDR", args.master_addr)
+    os.environ.setdefault("MASTER_PORT", str(args.master_port))
+    dep = json.load(open(args.deployment)) if args.deployment else {}
+    local = int(os.environ.get("LOCAL_RANK", args.rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", rank=args.rank, world_size=args.world, device_id=dev)
+    params = None
+    if args.snapshot:
+        from ..loader.load import load_params
+        cfg, params = load_params(args.snapshot, dtype=torch.bfloat16, only=".mlp.experts.")
+    else:
+        cfg = PRESETS[dep.get("model", "qwen3-30b-a3b")]()
+    h = build_afd(cfg, dev, args.rank, args.world, max_tokens=dep.get("prefill_rows", 8192), max_seqs=dep.get("decode_rows", 64),
+                  num_pages=2, pages_per_seq=1, params=params)
+    if h.worker is None:
+        raise SystemExit("expertd must not be rank 0 (rank 0 is the attention rank)")
+    h.worker.serve()
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0

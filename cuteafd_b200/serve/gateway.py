@@ -1,0 +1,137 @@
+"""Standalone protocol gateway: accepts Anthropic Messages and OpenAI Responses requests and
+forwards them as OpenAI Chat Completions to an upstream server, translating the reply back.
+A model-name map renames client model ids.  (The in-process server already speaks all three
+protocols; the gateway exists for fronting any OpenAI-compatible upstream.)
+
+Counterpart: rust/crates/cuteafd-api/src/gateway/mod.rs:1-60,148,215-216 and
+rust/crates/cuteafd-daemon/src/commands/gateway.rs.
+"""
+from __future__ import annotations
+
+import json
+import threading
+import urllib.error
+import urllib.request
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+from . import api
+
+
+def to_chat_body(body: dict, flavor: str, model_map: dict[str, str]) -> dict:
+    msgs = []
+    if flavor == "anthropic":
+        if body.get("system"):
+            s = body["system"]
+            msgs.append({"role": "system", "content": s if isinstance(s, str) else "".join(p.get("text", "") for p in s)})
+        for m in body.get("messages", []):
+            c = m.get("content")
+            if isinstance(c, list):
+                c = "".join(p.get("text", "") for p in c if p.get("type") == "text")
+            msgs.append({"role": m.get("role", "user"), "content": c})
+    else:
+        inp = body.get("input")
+        if body.get("instructions"):
+            msgs.append({"role": "system", "content": body["instructions"]})
+        if isinstance(inp, str):
+            msgs.append({"role": "user", "content": inp})
+        else:
+            for m in inp or []:
+                c = m.get("content")
+                if isinstance(c, list):
+                    c = "".join(p.get("text", "") for p in c if isinstance(p, dict))
+                msgs.append({"role": m.get("role", "user"), "content": c})
+    out = {"model": model_map.get(body.get("model", ""), body.get("model", "")), "messages": msgs,
+           "max_tokens": body.get("max_tokens") or body.get("max_output_tokens") or 256}
+    for k in ("temperature", "top_p", "top_k", "seed", "stop"):
+        if k in body:
+            out[k] = body[k]
+    if body.get("stop_sequences"):
+        out["stop"] = body["stop_sequences"]
+    return out
+
+
+def from_chat_reply(reply: dict, flavor: str, model: str) -> dict:
+    ch = reply["choices"][0]
+    text = ch["message"].get("content") or ""
+    u = reply.get("usage", {})
+    usage = {"prompt_tokens": u.get("prompt_tokens", 0), "completion_tokens": u.get("completion_tokens", 0),
+             "cached_tokens": u.get("prompt_tokens_details", {}).get("cached_tokens", 0)}
+    if flavor == "anthropic":
+        return api.anthropic_message(model, text, ch.get("finish_reason", "stop"), usage)
+    return api.responses_object(model, text, ch.get("finish_reason", "stop"), usage)
+
+
+def make_gateway(upstream: str, model_map: dict[str, str]):
+    class H(BaseHTTPRequestHandler):
+        protocol_version = "HTTP/1.1"
+
+        def log_message(self, *a):
+            return
+
+        def _json(self, status, body, headers=None):
+            raw = json.dumps(body).encode()
+            self.send_response(status)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(raw)))
+            for k, v in (headers or {}).items():
+                self.send_header(k, v)
+            self.end_headers()
+            self.wfile.write(raw)
+
+        def do_GET(self):
+            try:
+                with urllib.request.urlopen(upstream + self.path, timeout=30) as r:
+                    return self._json(r.status, json.loads(r.read()))
+            except urllib.error.URLError as e:
+                return self._json(503, {"error": {"message": f"upstream unavailable: {e}"}})
+
+        def do_POST(self):
+            flavor = {"/v1/messages": "anthropic", "/v1/responses": "responses"}.get(self.path.split("?")[0])
+            n = int(self.headers.get("Content-Length", "0") or 0)
+            try:
+                body = json.loads(self.rfile.read(n) or b"{}")
+            except json.JSONDecodeError:
+                return self._json(400, {"error": {"message": "invalid JSON"}})
+            fwd = to_chat_body(body, flavor, model_map) if flavor else body
+            req = urllib.request.Request(upstream + ("/v1/chat/completions" if flavor else self.path), json.dumps(fwd).encode(),
+                                         {"Content-Type": "application/json", "Authorization": self.headers.get("Authorization", "")})
+            try:
+                with urllib.request.urlopen(req, timeout=600) as r:
+                    reply = json.loads(r.read())
+            except urllib.error.HTTPError as e:
+                hd = {"Retry-After": e.headers["Retry-After"]} if e.headers.get("Retry-After") else {}
+                return self._json(e.code, json.loads(e.read() or b"{}"), hd)
+            except urllib.error.URLError as e:
+                return self._json(503, {"error": {"message": f"upstream unavailable: {e}"}})
+            return self._json(200, from_chat_reply(reply, flavor, body.get("model", "")) if flavor else reply)
+
+    return H
+
+
+class Gateway:
+    def __init__(self, upstream: str, host: str = "127.0.0.1", port: int = 0, model_map: dict[str, str] | None = None):
+        self.httpd = ThreadingHTTPServer((host, port), make_gateway(upstream.rstrip("/"), model_map or {}))
+        self.httpd.daemon_threads = True
+        self.port = self.httpd.server_address[1]
+        self.thread = threading.Thread(target=self.httpd.serve_forever, daemon=True)
+
+    def start(self) -> "Gateway":
+        self.thread.start()
+        return self
+
+    def stop(self) -> None:
+        self.httpd.shutdown()
+        self.httpd.server_close()
+
+
+def run_gateway(args) -> int:
+    import time
+    mm = dict(kv.split("=", 1) for kv in args.model_map.split(",") if "=" in kv)
+    gw = Gateway(args.upstream, args.host, args.port, mm).start()
+    print(f"gateway on http://{args.host}:{gw.port} -> {args.upstream}", flush=True)
+    try:
+        while True:
+            time.sleep(3600)
+    except KeyboardInterrupt:
+        gw.stop()
+    return 0

@@ -1,0 +1,341 @@
+"""HTTP serving: OpenAI Chat Completions (JSON and SSE), Anthropic Messages, OpenAI Responses,
+models, health, stats, thermal, fabric, memory, experts, usage, and a minimal console.
+
+Routes mirror the reference's router (rust/crates/cuteafd-api/src/openai.rs:448-474;
+api/gateway/anthropic.rs:25-26; api/gateway/responses.rs:38-45; usage/http.rs:53-66).  Requests are
+handed to the scheduler thread through its queue; each handler thread drains its own event queue.
+The server is plain ``http.server`` threads: the data plane is the GPU, not the HTTP layer.
+"""
+from __future__ import annotations
+
+import hmac
+import json
+import threading
+import time
+import uuid
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+from ..runtime.scheduler import FAIL_BAD_REQUEST, FAIL_UNAVAILABLE, Request, Scheduler
+from . import api
+from .tokenizer import StreamDecoder
+
+CONSOLE_HTML = """<!doctype html><title>cuteafd_b200 console</title>
+<style>body{font:14px monospace;margin:2em}pre{background:#111;color:#9f9;padding:1em}</style>
+<h3>cuteafd_b200</h3><pre id=s>loading</pre>
+<script>async function t(){const r=await fetch('/v1/stats');document.getElementById('s').textContent=
+JSON.stringify(await r.json(),null,1)}t();setInterval(t,1000)</script>"""
+
+
+class ServerState:
+    def __init__(self, scheduler: Scheduler, tokenizer, model_id: str, api_key: str = "", usage=None, extras=None):
+        self.sched, self.tok, self.model_id, self.api_key = scheduler, tokenizer, model_id, api_key
+        self.usage = usage
+        self.extras = extras or {}
+        self.started = time.time()
+        self.responses: dict[str, dict] = {}
+        self.lock = threading.Lock()
+
+
+def make_handler(state: ServerState):
+    class Handler(BaseHTTPRequestHandler):
+        protocol_version = "HTTP/1.1"
+        server_version = "cuteafd_b200"
+
+        def log_message(self, fmt, *args):      # quiet
+            return
+
+        # ---- helpers ------------------------------------------------------------------------------
+        def _json(self, status: int, body, headers: dict | None = None) -> None:
+            raw = json.dumps(body).encode()
+            self.send_response(status)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(raw)))
+            for k, v in (headers or {}).items():
+                self.send_header(k, v)
+            self.end_headers()
+            self.wfile.write(raw)
+
+        def _authorized(self) -> bool:
+            if not state.api_key:
+                return True
+            got = self.headers.get("Authorization", "").removeprefix("Bearer ").strip() or self.headers.get("x-api-key", "")
+            return hmac.compare_digest(got, state.api_key)
+
+        def _body(self) -> dict:
+            n = int(self.headers.get("Content-Length", "0") or 0)
+            if n > 64 << 20:
+                raise api.BadRequest("request body too large")
+            raw = self.rfile.read(n) if n else b"{}"
+            try:
+                d = json.loads(raw or b"{}")
+            except json.JSONDecodeError as e:
+                raise api.BadRequest(f"invalid JSON: {e}") from e
+            if not isinstance(d, dict):
+                raise api.BadRequest("body must be a JSON object")
+            return d
+
+        def _sse_start(self) -> None:
+            self.send_response(200)
+            self.send_header("Content-Type", "text/event-stream")
+            self.send_header("Cache-Control", "no-cache")
+            self.send_header("Connection", "close")
+            self.end_headers()
+
+        def _sse(self, data, event: str | None = None) -> None:
+            msg = (f"event: {event}\n" if event else "") + "data: " + (data if isinstance(data, str) else json.dumps(data)) + "\n\n"
+            self.wfile.write(msg.encode())
+            self.wfile.flush()
+
+        # ---- GET ----------------------------------------------------------------------------------
+        def do_GET(self):
+            path = self.path.split("?", 1)[0]
+            if path == "/health":
+                ok = state.sched.ready.is_set()
+                return self._json(200 if ok else 503, {"status": "ok" if ok else "starting", "model": state.model_id})
+            if path in ("/", "/v1/console"):
+                raw = CONSOLE_HTML.encode()
+                self.send_response(200)
+                self.send_header("Content-Type", "text/html")
+                self.send_header("Content-Length", str(len(raw)))
+                self.end_headers()
+                return self.wfile.write(raw)
+            if not self._authorized():
+                return self._json(401, {"error": {"message": "invalid API key", "type": "authentication_error"}})
+            if path == "/v1/models":
+                return self._json(200, {"object": "list", "data": [{"id": state.model_id, "object": "model", "created": int(state.started),
+                                                                      "owned_by": "cuteafd_b200"}]})
+            if path == "/v1/stats":
+                s = state.sched.snapshot()
+                be = state.sched.be
+                if hasattr(be, "prefix"):
+                    s["prefix"] = be.prefix.describe()
+                s["uptime_s"] = round(time.time() - state.started, 1)
+                return self._json(200, s)
+            if path == "/v1/thermal":
+                from ..utils.thermal import sample_once
+                return self._json(200, sample_once())
+            if path == "/v1/fabric":
+                from ..parallel.fabric import fabric_report
+                return self._json(200, fabric_report())
+            if path == "/memory":
+                from ..utils.memory_ledger import LEDGER
+                return self._json(200, LEDGER.report())
+            if path == "/experts":
+                return self._json(200, state.extras.get("expert_usage", lambda: {})())
+            if path.startswith("/console/usage"):
+                return self._json(200, state.usage.summary(24.0) if state.usage else {})
+            if path.startswith("/v1/responses/"):
+                rid = path.rsplit("/", 1)[1]
+                with state.lock:
+                    r = state.responses.get(rid)
+                return self._json(200, r) if r else self._json(404, {"error": {"message": "no such response"}})
+            return self._json(404, {"error": {"message": f"no route {path}"}})
+
+        def do_DELETE(self):
+            path = self.path.split("?", 1)[0]
+            if path.startswith("/v1/responses/"):
+                with state.lock:
+                    ok = state.responses.pop(path.rsplit("/", 1)[1], None) is not None
+                return self._json(200 if ok else 404, {"deleted": ok})
+            return self._json(404, {"error": {"message": "no route"}})
+
+        # ---- POST ---------------------------------------------------------------------------------
+        def do_POST(self):
+            path = self.path.split("?", 1)[0]
+            flavor = {"/v1/chat/completions": "openai", "/v1/messages": "anthropic", "/v1/responses": "responses",
+                      "/v1/messages/count_tokens": "anthropic", "/v1/responses/input_tokens": "responses"}.get(path)
+            if flavor is None:
+                return self._json(404, {"error": {"message": f"no route {path}"}})
+            if not self._authorized():
+                st, body, hd = 401, {"error": {"message": "invalid API key", "type": "authentication_error"}}, {}
+                return self._json(st, body, hd)
+            try:
+                body = self._body()
+                probe = api.parse_probe(self.headers)
+                req = api.build_request(body, state.tok, state.sched.be.vocab_size, probe, flavor)
+            except api.BadRequest as e:
+                st, eb, hd = api.error_body(FAIL_BAD_REQUEST, str(e), flavor)
+                return self._json(st, eb, hd)
+            if path.endswith("count_tokens") or path.endswith("input_tokens"):
+                return self._json(200, {"input_tokens": len(req.prompt)})
+            if not state.sched.ready.is_set():
+                st, eb, hd = api.error_body(FAIL_UNAVAILABLE, "engine is starting", flavor)
+                return self._json(st, eb, hd)
+            t0 = time.time()
+            state.sched.submit(req)
+            model = body.get("model") or state.model_id
+            try:
+                if body.get("stream"):
+                    self._stream(req, model, flavor)
+                else:
+                    self._complete(req, model, flavor, t0)
+            except (BrokenPipeError, ConnectionResetError):
+                req.cancelled.set()                       # client went away: stop generating
+
+        def _drain(self, req: Request):
+            """Yield ("text", str) / ("done", finish, usage, rows) / ("error", kind, msg)."""
+            dec = StreamDecoder(state.tok)
+            eos = set(getattr(state.tok, "eos_ids", ()))
+            while True:
+                ev = req.events.get()
+                if ev[0] == "tokens":
+                    text = dec.push([t for t in ev[1] if t not in eos])
+                    if text:
+                        yield ("text", text)
+                elif ev[0] == "done":
+                    tail = dec.flush()
+                    if tail:
+                        yield ("text", tail)
+                    yield ev
+                    return
+                else:
+                    yield ev
+                    return
+
+        def _complete(self, req: Request, model: str, flavor: str, t0: float) -> None:
+            text, final = [], None
+            for ev in self._drain(req):
+                if ev[0] == "text":
+                    text.append(ev[1])
+                else:
+                    final = ev
+            if final[0] == "error":
+                st, eb, hd = api.error_body(final[1], final[2], flavor)
+                return self._json(st, eb, hd)
+            _, finish, usage, rows = final
+            out_text = "".join(text)
+            if state.usage:
+                state.usage.record(model, flavor, usage, time.time() - t0, finish)
+            if flavor == "anthropic":
+                return self._json(200, api.anthropic_message(model, out_text, finish, usage))
+            if flavor == "responses":
+                obj = api.responses_object(model, out_text, finish, usage)
+                with state.lock:
+                    state.responses[obj["id"]] = obj
+                return self._json(200, obj)
+            return self._json(200, api.chat_completion(model, out_text, finish, usage, rows or None))
+
+        def _stream(self, req: Request, model: str, flavor: str) -> None:
+            self._sse_start()
+            if flavor == "anthropic":
+                mid, head = api.anthropic_events(model, len(req.prompt))
+                for name, ev in head:
+                    self._sse(ev, name)
+                for ev in self._drain(req):
+                    if ev[0] == "text":
+                        self._sse({"type": "content_block_delta", "index": 0, "delta": {"type": "text_delta", "text": ev[1]}}, "content_block_delta")
+                    elif ev[0] == "done":
+                        self._sse({"type": "content_block_stop", "index": 0}, "content_block_stop")
+                        stop = {"stop": "end_turn", "length": "max_tokens"}.get(ev[1], ev[1])
+                        self._sse({"type": "message_delta", "delta": {"stop_reason": stop},
+                                   "usage": {"output_tokens": ev[2].get("completion_tokens", 0)}}, "message_delta")
+                        self._sse({"type": "message_stop"}, "message_stop")
+                    else:
+                        self._sse({"type": "error", "error": {"type": "api_error", "message": ev[2]}}, "error")
+                return
+            if flavor == "responses":
+                rid = "resp_" + uuid.uuid4().hex[:24]
+                self._sse({"type": "response.created", "response": {"id": rid, "status": "in_progress"}}, "response.created")
+                text = []
+                for ev in self._drain(req):
+                    if ev[0] == "text":
+                        text.append(ev[1])
+                        self._sse({"type": "response.output_text.delta", "delta": ev[1]}, "response.output_text.delta")
+                    elif ev[0] == "done":
+                        obj = api.responses_object(model, "".join(text), ev[1], ev[2], rid)
+                        with state.lock:
+                            state.responses[rid] = obj
+                        self._sse({"type": "response.completed", "response": obj}, "response.completed")
+                    else:
+                        self._sse({"type": "error", "message": ev[2]}, "error")
+                return
+            cid = "chatcmpl-" + uuid.uuid4().hex[:24]
+            self._sse(api.chat_chunk(cid, model, {"role": "assistant", "content": ""}))
+            for ev in self._drain(req):
+                if ev[0] == "text":
+                    self._sse(api.chat_chunk(cid, model, {"content": ev[1]}))
+                elif ev[0] == "done":
+                    self._sse(api.chat_chunk(cid, model, {}, ev[1], ev[2]))
+                else:
+                    self._sse({"error": {"message": ev[2], "code": ev[1]}})
+            self._sse("[DONE]")
+
+    return Handler
+
+
+class Server:
+    """Owns the HTTP listener and the scheduler thread."""
+
+    def __init__(self, state: ServerState, host: str = "127.0.0.1", port: int = 0):
+        self.state = state
+        self.httpd = ThreadingHTTPServer((host, port), make_handler(state))
+        self.httpd.daemon_threads = True
+        self.port = self.httpd.server_address[1]
+        self.t_http = threading.Thread(target=self.httpd.serve_forever, daemon=True)
+        self.t_sched = threading.Thread(target=state.sched.run_forever, daemon=True)
+
+    def start(self) -> "Server":
+        self.t_sched.start()
+        self.t_http.start()
+        return self
+
+    def stop(self) -> None:
+        self.state.sched.stop()
+        self.httpd.shutdown()
+        self.httpd.server_close()
+
+
+def build_state(args) -> ServerState:
+    """Engine + scheduler + tokenizer from ``cuteafd serve`` arguments."""
+    import torch
+
+    from ..config import PRESETS, tiny_moe
+    from ..runtime.speculation import NgramDrafter
+    from .tokenizer import load_tokenizer
+    from .usage import UsageLog
+    snapshot = args.snapshot or None
+    if args.fake_engine or not torch.cuda.is_available():
+        from ..ref.model import init_weights
+        from ..runtime.backends import OracleBackend
+        if snapshot:
+            from ..loader.load import load_params
+            cfg, params = load_params(snapshot)
+        else:
+            cfg = PRESETS.get(args.preset, tiny_moe)() if args.preset else tiny_moe()
+            params = init_weights(cfg, seed=0)
+        be = OracleBackend(cfg, params)
+    else:
+        from ..loader.load import load_gqa_engine_weights
+        from ..models.gqa_moe import GqaMoeEngine, GqaMoeWeights, KvCache
+        from ..runtime.backends import EngineBackend
+        dev = torch.device("cuda:0")
+        if snapshot:
+            cfg, W = load_gqa_engine_weights(snapshot, dev)
+        else:
+            cfg = PRESETS[args.preset or "qwen3-30b-a3b"]()
+            if args.layers:
+                cfg = cfg.replace(num_layers=args.layers)
+            W = GqaMoeWeights.random_init(cfg, dev)
+        pages_per_seq = args.max_context_tokens // 64 + 2
+        num_pages = pages_per_seq * args.concurrency + 64
+        rows = args.concurrency * 8
+        eng = GqaMoeEngine(cfg, W, KvCache(cfg, num_pages, dev), max_tokens=max(2048, rows), max_seqs=rows)
+        be = EngineBackend(eng, num_pages, pages_per_seq, prefill_chunk=2048, max_decode_rows=args.concurrency)
+    tok = load_tokenizer(snapshot, cfg.vocab_size)
+    drafter = NgramDrafter(block=4) if args.speculator in ("auto", "history", "ngram") else None
+    sched = Scheduler(be, max_active=args.concurrency, queue_depth=args.queue_depth, queue_wait_s=args.queue_wait,
+                      drafter=drafter, eos_ids=tuple(getattr(tok, "eos_ids", ())))
+    usage = UsageLog(args.usage_db) if args.usage_db else None
+    return ServerState(sched, tok, cfg.name, args.api_key, usage)
+
+
+def run_server(args) -> int:
+    state = build_state(args)
+    srv = Server(state, args.host, args.port).start()
+    print(f"serving {state.model_id} on http://{args.host}:{srv.port}", flush=True)
+    try:
+        while True:
+            time.sleep(3600)
+    except KeyboardInterrupt:
+        srv.stop()
+    return 0

@@ -1,0 +1,149 @@
+"""Tokenizer, chat template and streaming detokenizer.
+
+A snapshot with ``tokenizer.json`` is served through the Hugging Face ``tokenizers`` runtime; a
+snapshot without one (every synthetic checkpoint here) falls back to a byte-level tokenizer whose
+ids are byte values plus a few control tokens, so text round-trips exactly at any vocabulary of at
+least 260.  Counterpart: rust/crates/cuteafd-loader/src/tokenizer.rs (+ tokenizer/: literal spans,
+streaming decoder), per-family chat encoders in rust/crates/cuteafd-api/src/openai/chat/.
+"""
+from __future__ import annotations
+
+import json
+import os
+
+BOS, EOS, IM_START, IM_END = 256, 257, 258, 259
+SPECIAL = {"<|bos|>": BOS, "<|eos|>": EOS, "<|im_start|>": IM_START, "<|im_end|>": IM_END}
+
+
+class ByteTokenizer:
+    vocab_floor = 260
+
+    def __init__(self, vocab_size: int):
+        if vocab_size < self.vocab_floor:
+            raise ValueError("byte tokenizer needs a vocabulary of at least 260")
+        self.vocab_size = vocab_size
+        self.eos_ids = (EOS, IM_END)
+
+    def encode(self, text: str, specials: bool = True) -> list[int]:
+        out: list[int] = []
+        i = 0
+        while i < len(text):
+            if specials and text[i] == "<":
+                hit = next((s for s in SPECIAL if text.startswith(s, i)), None)
+                if hit:
+                    out.append(SPECIAL[hit])
+                    i += len(hit)
+                    continue
+            out.extend(text[i].encode("utf-8"))
+            i += 1
+        return out
+
+    def decode(self, ids: list[int]) -> str:
+        return self.token_bytes_seq(ids).decode("utf-8", errors="replace")
+
+    def token_bytes(self, tid: int) -> bytes:
+        return bytes([tid]) if tid < 256 else b""
+
+    def token_bytes_seq(self, ids: list[int]) -> bytes:
+        return b"".join(self.token_bytes(t) for t in ids)
+
+
+class HfTokenizer:
+    def __init__(self, path: str):
+        from tokenizers import Tokenizer
+        self.tk = Tokenizer.from_file(path)
+        self.vocab_size = self.tk.get_vocab_size()
+        cfg = {}
+        cfg_path = os.path.join(os.path.dirname(path), "tokenizer_config.json")
+        if os.path.exists(cfg_path):
+            cfg = json.load(open(cfg_path))
+        eos = cfg.get("eos_token")
+        eos = eos.get("content") if isinstance(eos, dict) else eos
+        self.eos_ids = tuple(i for i in (self.tk.token_to_id(eos) if eos else None, self.tk.token_to_id("<|im_end|>")) if i is not None)
+
+    def encode(self, text: str, specials: bool = True) -> list[int]:
+        return self.tk.encode(text, add_special_tokens=False).ids
+
+    def decode(self, ids: list[int]) -> str:
+        return self.tk.decode(ids, skip_special_tokens=True)
+
+    def token_bytes(self, tid: int) -> bytes:
+        return self.tk.decode([tid]).encode()
+
+
+def load_tokenizer(snapshot: str | None, vocab_size: int):
+    if snapshot:
+        p = os.path.join(snapshot, "tokenizer.json")
+        if os.path.exists(p):
+            return HfTokenizer(p)
+    return ByteTokenizer(vocab_size)
+
+
+def render_chat(messages: list[dict], add_generation_prompt: bool = True, tools: list[dict] | None = None) -> str:
+    """ChatML-style template.  Tool definitions ride in a system block; tool results are turns of
+    role ``tool``; content parts of type text are concatenated."""
+    parts = []
+    if tools:
+        parts.append("<|im_start|>system\nYou may call these tools by emitting a JSON object "
+                     '{"name": ..., "arguments": {...}} between <tool_call> tags.\n' + json.dumps(tools) + "<|im_end|>\n")
+    for m in messages:
+        c = m.get("content")
+        if isinstance(c, list):
+            c = "".join(p.get("text", "") for p in c if isinstance(p, dict) and p.get("type") in ("text", "input_text", "output_text"))
+        if c is None:
+            c = ""
+        if m.get("tool_calls"):
+            c += "".join(f"<tool_call>{json.dumps(tc.get('function', tc))}</tool_call>" for tc in m["tool_calls"])
+        parts.append(f"<|im_start|>{m.get('role', 'user')}\n{c}<|im_end|>\n")
+    if add_generation_prompt:
+        parts.append("<|im_start|>assistant\n")
+    return "".join(parts)
+
+
+def parse_tool_calls(text: str) -> tuple[str, list[dict]]:
+    """Split generated text into plain content and tool calls."""
+    calls, out, i = [], [], 0
+    while True:
+        a = text.find("<tool_call>", i)
+        if a < 0:
+            out.append(text[i:])
+            break
+        b = text.find("</tool_call>", a)
+        if b < 0:
+            out.append(text[i:])
+            break
+        out.append(text[i:a])
+        try:
+            obj = json.loads(text[a + 11:b])
+            calls.append({"id": f"call_{len(calls)}", "type": "function",
+                          "function": {"name": obj.get("name", ""), "arguments": json.dumps(obj.get("arguments", {}))}})
+        except json.JSONDecodeError:
+            out.append(text[a:b + 12])
+        i = b + 12
+    return "".join(out), calls
+
+
+class StreamDecoder:
+    """Incremental detokenizer: emits only complete UTF-8 text, holding back partial sequences."""
+
+    def __init__(self, tok):
+        self.tok, self.buf = tok, b""
+
+    def push(self, ids: list[int]) -> str:
+        self.buf += b"".join(self.tok.token_bytes(t) for t in ids)
+        cut = len(self.buf)
+        # hold back an incomplete trailing multi-byte sequence
+        for back in range(1, min(4, len(self.buf)) + 1):
+            b = self.buf[-back]
+            if b & 0xC0 == 0x80:
+                continue
+            need = 2 if b & 0xE0 == 0xC0 else 3 if b & 0xF0 == 0xE0 else 4 if b & 0xF8 == 0xF0 else 1
+            if need > back:
+                cut = len(self.buf) - back
+            break
+        text, self.buf = self.buf[:cut].decode("utf-8", errors="replace"), self.buf[cut:]
+        return text
+
+    def flush(self) -> str:
+        text, self.buf = self.buf.decode("utf-8", errors="replace"), b""
+        return text

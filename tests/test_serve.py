@@ -1,0 +1,161 @@
+"""HTTP surface over the oracle engine: OpenAI chat (JSON + SSE), Anthropic messages, Responses,
+models / health / stats, auth, failure classes, probes, constraints, usage log, gateway, CLI."""
+import http.client
+import json
+
+import pytest
+import torch
+
+from cuteafd_b200 import tiny_moe
+from cuteafd_b200.ref.model import init_weights
+from cuteafd_b200.runtime.backends import OracleBackend
+from cuteafd_b200.runtime.scheduler import Scheduler
+from cuteafd_b200.runtime.speculation import NgramDrafter
+from cuteafd_b200.serve import constraints, tokenizer
+from cuteafd_b200.serve.gateway import Gateway
+from cuteafd_b200.serve.server import Server, ServerState
+from cuteafd_b200.serve.usage import UsageLog
+
+
+@pytest.fixture(scope="module")
+def server():
+    cfg = tiny_moe()
+    be = OracleBackend(cfg, init_weights(cfg, seed=0))
+    tok = tokenizer.ByteTokenizer(cfg.vocab_size)
+    sched = Scheduler(be, max_active=4, queue_depth=8, drafter=NgramDrafter(block=3), eos_ids=tok.eos_ids)
+    usage = UsageLog()
+    srv = Server(ServerState(sched, tok, cfg.name, api_key="sekret", usage=usage), port=0).start()
+    yield srv
+    srv.stop()
+
+
+def call(srv, method, path, body=None, headers=None, key="sekret"):
+    c = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=120)
+    h = {"Content-Type": "application/json"}
+    if key:
+        h["Authorization"] = f"Bearer {key}"
+    h.update(headers or {})
+    c.request(method, path, json.dumps(body).encode() if body is not None else None, h)
+    r = c.getresponse()
+    raw = r.read()
+    c.close()
+    return r.status, dict(r.getheaders()), raw
+
+
+def test_health_models_stats_auth(server):
+    st, _, raw = call(server, "GET", "/health", key="")
+    assert st == 200 and json.loads(raw)["status"] == "ok"
+    assert call(server, "GET", "/v1/models", key="wrong")[0] == 401
+    st, _, raw = call(server, "GET", "/v1/models")
+    assert st == 200 and json.loads(raw)["data"][0]["id"] == "tiny-moe"
+    st, _, raw = call(server, "GET", "/v1/stats")
+    s = json.loads(raw)
+    assert st == 200 and "prefix" in s and "draft_policy" in s and "kv" in s
+    assert call(server, "GET", "/nope")[0] == 404
+    assert call(server, "GET", "/", key="")[0] == 200
+
+
+def test_chat_completion_json_and_probe(server):
+    body = {"model": "tiny-moe", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 12}
+    st, _, raw = call(server, "POST", "/v1/chat/completions", body)
+    out = json.loads(raw)
+    assert st == 200 and out["object"] == "chat.completion"
+    assert out["usage"]["completion_tokens"] <= 12 and out["choices"][0]["finish_reason"] in ("length", "stop")
+    assert set(out["usage"]["speculation"]) >= {"request_id", "proposed", "accepted", "cycles"}
+    # synthetic token-id prompt through the probe header; greedy decode is reproducible and hashes rows
+    probe = {"prompt_ids": list(range(5, 90)), "record_rows": True, "no_speculation": True}
+    a = json.loads(call(server, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "max_tokens": 6},
+                        {"x-cuteafd-probe": json.dumps(probe)})[2])
+    b = json.loads(call(server, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "max_tokens": 6},
+                        {"x-cuteafd-probe": json.dumps(probe)})[2])
+    assert a["probe"]["row_hashes"] == b["probe"]["row_hashes"] and len(a["probe"]["row_hashes"]) == 6
+    assert b["usage"]["prompt_tokens_details"]["cached_tokens"] >= 64        # second run hits the prefix cache
+
+
+def test_streaming_sse(server):
+    body = {"messages": [{"role": "user", "content": "stream"}], "max_tokens": 8, "stream": True}
+    st, hd, raw = call(server, "POST", "/v1/chat/completions", body)
+    assert st == 200 and hd["Content-Type"] == "text/event-stream"
+    events = [l[6:] for l in raw.decode().split("\n") if l.startswith("data: ")]
+    assert events[-1] == "[DONE]"
+    chunks = [json.loads(e) for e in events[:-1]]
+    assert chunks[0]["choices"][0]["delta"].get("role") == "assistant"
+    assert chunks[-1]["choices"][0]["finish_reason"] in ("length", "stop") and "usage" in chunks[-1]
+
+
+def test_anthropic_and_responses(server):
+    body = {"model": "tiny-moe", "system": "be brief", "messages": [{"role": "user", "content": [{"type": "text", "text": "hi"}]}], "max_tokens": 5}
+    st, _, raw = call(server, "POST", "/v1/messages", body)
+    m = json.loads(raw)
+    assert st == 200 and m["type"] == "message" and m["stop_reason"] in ("max_tokens", "end_turn") and m["usage"]["output_tokens"] <= 5
+    st, _, raw = call(server, "POST", "/v1/messages/count_tokens", body)
+    assert st == 200 and json.loads(raw)["input_tokens"] > 0
+    st, _, raw = call(server, "POST", "/v1/messages", dict(body, stream=True))
+    names = [l[7:] for l in raw.decode().split("\n") if l.startswith("event: ")]
+    assert names[0] == "message_start" and names[-1] == "message_stop" and "content_block_stop" in names
+    st, _, raw = call(server, "POST", "/v1/responses", {"model": "tiny-moe", "input": "hello", "max_output_tokens": 4})
+    r = json.loads(raw)
+    assert st == 200 and r["object"] == "response" and r["status"] == "completed"
+    assert call(server, "GET", f"/v1/responses/{r['id']}")[0] == 200
+    assert call(server, "DELETE", f"/v1/responses/{r['id']}")[0] == 200
+    assert call(server, "GET", f"/v1/responses/{r['id']}")[0] == 404
+
+
+def test_failure_classes(server):
+    assert call(server, "POST", "/v1/chat/completions", {"messages": []})[0] == 400
+    assert call(server, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "temperature": 9})[0] == 400
+    st, _, raw = call(server, "POST", "/v1/messages", {"messages": [], "max_tokens": 3})
+    assert st == 400 and json.loads(raw)["type"] == "error"
+    # a prompt that cannot fit the KV pool is refused with the retry class: 429 + Retry-After
+    probe = {"prompt_ids": [7] * 40000}
+    st, hd, raw = call(server, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "max_tokens": 4,
+                                                                 "cuteafd_probe": probe})
+    assert st == 429 and hd.get("Retry-After") == "1"
+
+
+def test_json_constraint_and_usage(server):
+    body = {"messages": [{"role": "user", "content": "give json"}], "max_tokens": 40, "response_format": {"type": "json_object"},
+            "temperature": 0.7, "seed": 3}
+    st, _, raw = call(server, "POST", "/v1/chat/completions", body)
+    out = json.loads(raw)
+    text = out["choices"][0]["message"]["content"]
+    assert st == 200 and text.lstrip().startswith("{")
+    if out["choices"][0]["finish_reason"] == "stop":
+        json.loads(text)                                             # a finished constrained reply parses
+    body = {"messages": [{"role": "user", "content": "pick"}], "max_tokens": 10, "response_format": {"type": "choice", "choices": ["yes", "no"]}}
+    out = json.loads(call(server, "POST", "/v1/chat/completions", body)[2])
+    assert out["choices"][0]["message"]["content"] in ("yes", "no")
+    u = json.loads(call(server, "GET", "/console/usage/summary")[2])
+    assert u["requests"] >= 2 and u["completion_tokens"] > 0
+
+
+def test_gateway_translates(server):
+    gw = Gateway(f"http://127.0.0.1:{server.port}", model_map={"claude-x": "tiny-moe"}).start()
+    try:
+        c = http.client.HTTPConnection("127.0.0.1", gw.port, timeout=120)
+        c.request("POST", "/v1/messages", json.dumps({"model": "claude-x", "messages": [{"role": "user", "content": "hey"}], "max_tokens": 4}),
+                  {"Content-Type": "application/json", "Authorization": "Bearer sekret"})
+        r = c.getresponse()
+        m = json.loads(r.read())
+        assert r.status == 200 and m["type"] == "message" and m["role"] == "assistant"
+    finally:
+        gw.stop()
+
+
+def test_recognizers_and_tokenizer():
+    r = constraints.JsonRecognizer()
+    for b in b'{"a": [1, 2.5e3, true, null, "x\\n\\u00e9"], "b": {"c": -0}}':
+        assert r.feed(b)
+    assert r.complete() and not r.clone().feed(ord("x"))
+    bad = constraints.JsonRecognizer()
+    assert not bad.feed(ord("["))                                    # object_only
+    assert not all(constraints.JsonRecognizer().feed(b) for b in b'{"a" 1}')
+    tok = tokenizer.ByteTokenizer(300)
+    ids = tok.encode("<|im_start|>user\nhé<|im_end|>")
+    assert ids[0] == tokenizer.IM_START and ids[-1] == tokenizer.IM_END and tok.decode(ids) == "user\nhé"
+    d = tokenizer.StreamDecoder(tok)
+    e = "é".encode()
+    assert d.push([e[0]]) == "" and d.push([e[1]]) == "é"
+    text, calls = tokenizer.parse_tool_calls('ok <tool_call>{"name": "f", "arguments": {"x": 1}}</tool_call> done')
+    assert calls[0]["function"]["name"] == "f" and "tool_call" not in text
+    assert "<|im_start|>assistant" in tokenizer.render_chat([{"role": "user", "content": "q"}])
