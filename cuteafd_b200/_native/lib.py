@@ -19,7 +19,7 @@ class GemmArgs(C.Structure):
         ("w0", C.c_void_p), ("w1", C.c_void_p), ("x", C.c_void_p), ("out", C.c_void_p),
         ("residual", C.c_void_p), ("row_scale", C.c_void_p), ("row_dst", C.c_void_p),
         ("tile_expert", C.c_void_p), ("tile_row0", C.c_void_p), ("num_x_tiles", C.c_void_p),
-        ("w_scale", C.c_void_p), ("x_scale", C.c_void_p),
+        ("w_scale", C.c_void_p), ("x_scale", C.c_void_p), ("w_scale1", C.c_void_p),
         ("wait_flag", C.c_void_p), ("epoch", C.c_void_p), ("done_counter", C.c_void_p),
         ("signal_flag", C.c_void_p), ("status", C.c_void_p),
         ("splitk_scratch", C.c_void_p), ("splitk_tickets", C.c_void_p),
@@ -62,7 +62,10 @@ def cuda_lib():
         lib = C.CDLL(path)
         P, I, F = C.c_void_p, C.c_int, C.c_float
         _sig(lib, "cafd_gemm", [C.POINTER(GemmArgs), P])
-        for n in ("cafd_gemm_set_wait_limit_ns", "cafd_moe_set_wait_limit_ns", "cafd_attn_set_wait_limit_ns"):
+        _sig(lib, "cafd_gemm_fp8", [C.POINTER(GemmArgs), P])
+        _sig(lib, "cafd_quant_rows_fp8", [P, P, P, I, I, I, P])
+        for n in ("cafd_gemm_set_wait_limit_ns", "cafd_moe_set_wait_limit_ns", "cafd_attn_set_wait_limit_ns",
+                  "cafd_gemm_fp8_set_wait_limit_ns"):
             _sig(lib, n, [C.c_ulonglong])
         _sig(lib, "cafd_embed", [P, P, P, I, I, I, P])
         _sig(lib, "cafd_rmsnorm", [P, P, P, P, I, I, F, P])

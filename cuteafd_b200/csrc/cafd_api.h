@@ -37,6 +37,7 @@ typedef struct {
   const int* num_x_tiles;    // grouped: device count of X tiles
   const float* w_scale;      // fp8: weight block scales [w_rows_total/128, K/128]
   const float* x_scale;      // fp8: activation scales [x_rows_total, K/128]
+  const float* w_scale1;     // fp8 dual mode: block scales of the up weights (NULL = same as w_scale)
   const uint32_t* wait_flag; // optional: wait until *wait_flag >= *epoch before reading anything
   const uint32_t* epoch;     // device word holding the current step number
   uint32_t* done_counter;    // local counter used to elect the last CTA (must start at 0)
@@ -88,6 +89,12 @@ int cafd_argmax(const float* logits, int* out, void* scratch, int T, int V, int 
 int cafd_argmax_noalloc_max_rows(void);
 int cafd_argmax_noalloc(const float* logits, int* out, int T, int V, int ld, cafd_stream_t stream);
 int cafd_gemm_set_wait_limit_ns(unsigned long long ns);
+
+// Block-scaled FP8 (E4M3) variant of cafd_gemm: same arguments plus w_scale / w_scale1 / x_scale.
+// K must be a multiple of 128; out is bf16.
+int cafd_gemm_fp8(const cafd_gemm_args* a, cafd_stream_t stream);
+// x [T, K] bf16 (row pitch ldx elements) -> q [T, K] E4M3 and s [T, K / 128] fp32 (amax / 448, 1 if zero).
+int cafd_quant_rows_fp8(const void* x, void* q, float* s, int T, int K, int ldx, cafd_stream_t stream);
 
 #ifdef __cplusplus
 }

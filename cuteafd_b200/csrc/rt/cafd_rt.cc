@@ -1,0 +1,517 @@
+// Host runtime structures (see cafd_rt.h).  Plain C++17, no CUDA.
+#include "cafd_rt.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <unordered_map>
+#include <vector>
+
+namespace {
+constexpr int kPage = 64;
+
+struct Seq {
+  bool live = false;
+  int kv_len = 0;
+  std::vector<int> pages;
+};
+}  // namespace
+
+struct cafd_pool {
+  int num_pages;
+  std::vector<int> refs;
+  std::vector<int> free_list;
+  std::vector<Seq> seqs;
+  std::vector<int> free_seq_ids;
+};
+
+extern "C" {
+
+cafd_pool* cafd_pool_new(int num_pages) {
+  if (num_pages < 2) return nullptr;
+  auto* p = new cafd_pool;
+  p->num_pages = num_pages;
+  p->refs.assign(num_pages, 0);
+  p->refs[0] = 1 << 30;   // page 0 is reserved and stays zero
+  for (int i = num_pages - 1; i >= 1; --i) p->free_list.push_back(i);
+  return p;
+}
+void cafd_pool_free(cafd_pool* p) { delete p; }
+int cafd_pool_free_pages(const cafd_pool* p) { return static_cast<int>(p->free_list.size()); }
+int cafd_pool_alloc(cafd_pool* p) {
+  if (p->free_list.empty()) return -1;
+  const int pg = p->free_list.back();
+  p->free_list.pop_back();
+  p->refs[pg] = 1;
+  return pg;
+}
+int cafd_pool_retain(cafd_pool* p, int pg) {
+  if (pg < 0 || pg >= p->num_pages || p->refs[pg] <= 0) return -1;
+  ++p->refs[pg];
+  return 0;
+}
+int cafd_pool_release(cafd_pool* p, int pg) {
+  if (pg <= 0 || pg >= p->num_pages || p->refs[pg] <= 0) return -1;
+  if (--p->refs[pg] == 0) p->free_list.push_back(pg);
+  return 0;
+}
+int cafd_pool_refs(const cafd_pool* p, int pg) { return (pg < 0 || pg >= p->num_pages) ? -1 : p->refs[pg]; }
+
+static Seq* seq_of(const cafd_pool* cp, int id) {
+  cafd_pool* p = const_cast<cafd_pool*>(cp);
+  return (id < 0 || id >= static_cast<int>(p->seqs.size()) || !p->seqs[id].live) ? nullptr : &p->seqs[id];
+}
+
+int cafd_seq_new(cafd_pool* p) {
+  int id;
+  if (!p->free_seq_ids.empty()) {
+    id = p->free_seq_ids.back();
+    p->free_seq_ids.pop_back();
+  } else {
+    id = static_cast<int>(p->seqs.size());
+    p->seqs.emplace_back();
+  }
+  p->seqs[id] = Seq{};
+  p->seqs[id].live = true;
+  return id;
+}
+
+int cafd_seq_reserve(cafd_pool* p, int id, int new_len, int* cow_src, int* cow_dst) {
+  Seq* s = seq_of(p, id);
+  if (cow_src) *cow_src = -1;
+  if (cow_dst) *cow_dst = -1;
+  if (!s) return -1;
+  int added = 0;
+  // a shared partial tail page is copied before it is written
+  if (!s->pages.empty() && (s->kv_len % kPage) && p->refs[s->pages.back()] > 1 && new_len > s->kv_len) {
+    const int fresh = cafd_pool_alloc(p);
+    if (fresh < 0) return -1;
+    if (cow_src) *cow_src = s->pages.back();
+    if (cow_dst) *cow_dst = fresh;
+    cafd_pool_release(p, s->pages.back());
+    s->pages.back() = fresh;
+  }
+  const int need = (new_len + kPage - 1) / kPage - static_cast<int>(s->pages.size());
+  if (need > static_cast<int>(p->free_list.size())) return -1;
+  for (int i = 0; i < need; ++i) {
+    s->pages.push_back(cafd_pool_alloc(p));
+    ++added;
+  }
+  return added;
+}
+
+int cafd_seq_fork(cafd_pool* p, int src, int length) {
+  const Seq* a = seq_of(p, src);
+  if (!a) return -1;
+  if (length < 0 || length > a->kv_len) length = a->kv_len;
+  const int n_pages = (length + kPage - 1) / kPage;
+  const std::vector<int> share(a->pages.begin(), a->pages.begin() + n_pages);
+  const int id = cafd_seq_new(p);
+  Seq* b = seq_of(p, id);
+  b->pages = share;
+  for (int pg : b->pages) cafd_pool_retain(p, pg);
+  b->kv_len = length;
+  return id;
+}
+
+int cafd_seq_truncate(cafd_pool* p, int id, int length) {
+  Seq* s = seq_of(p, id);
+  if (!s) return -1;
+  const int keep = (length + kPage - 1) / kPage;
+  while (static_cast<int>(s->pages.size()) > keep) {
+    cafd_pool_release(p, s->pages.back());
+    s->pages.pop_back();
+  }
+  s->kv_len = length;
+  return 0;
+}
+
+int cafd_seq_free(cafd_pool* p, int id) {
+  Seq* s = seq_of(p, id);
+  if (!s) return -1;
+  for (int pg : s->pages) cafd_pool_release(p, pg);
+  s->pages.clear();
+  s->live = false;
+  p->free_seq_ids.push_back(id);
+  return 0;
+}
+int cafd_seq_set_len(cafd_pool* p, int id, int n) {
+  Seq* s = seq_of(p, id);
+  if (!s) return -1;
+  s->kv_len = n;
+  return 0;
+}
+int cafd_seq_len(const cafd_pool* p, int id) { const Seq* s = seq_of(p, id); return s ? s->kv_len : -1; }
+int cafd_seq_num_pages(const cafd_pool* p, int id) { const Seq* s = seq_of(p, id); return s ? static_cast<int>(s->pages.size()) : -1; }
+int cafd_seq_pages(const cafd_pool* p, int id, int* out, int cap) {
+  const Seq* s = seq_of(p, id);
+  if (!s) return -1;
+  const int n = std::min<int>(cap, static_cast<int>(s->pages.size()));
+  std::memcpy(out, s->pages.data(), n * sizeof(int));
+  return static_cast<int>(s->pages.size());
+}
+int cafd_seq_slots(const cafd_pool* p, int id, int start, int n, int* out) {
+  const Seq* s = seq_of(p, id);
+  if (!s || (start + n + kPage - 1) / kPage > static_cast<int>(s->pages.size())) return -1;
+  for (int i = 0; i < n; ++i) out[i] = s->pages[(start + i) / kPage] * kPage + (start + i) % kPage;
+  return 0;
+}
+
+}  // extern "C"
+
+// ---- prefix index ---------------------------------------------------------------------------------
+namespace {
+struct Snap;
+struct Node {
+  uint64_t key = 0;
+  int page = 0;
+  Node* parent = nullptr;
+  int32_t tokens[kPage];
+  std::unordered_map<uint64_t, std::unique_ptr<Node>> children;
+  int refs = 0;
+  std::vector<Snap*> tails;
+};
+struct Snap {
+  int sid, kind, length;
+  Node* node;
+  int tail_page;
+  std::vector<int32_t> tail_tokens;
+  uint64_t last_use;
+};
+uint64_t mix(uint64_t h, uint64_t v) {
+  h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+  h *= 0xbf58476d1ce4e5b9ull;
+  return h ^ (h >> 31);
+}
+uint64_t chunk_key(uint64_t prev, const int32_t* t) {
+  uint64_t h = prev ^ 0x94d049bb133111ebull;
+  for (int i = 0; i < kPage; ++i) h = mix(h, static_cast<uint32_t>(t[i]));
+  return h;
+}
+}  // namespace
+
+struct cafd_prefix {
+  cafd_pool* pool;
+  int max_pages;
+  int held = 0;
+  int evicted = 0;
+  uint64_t clock = 0;
+  int next_sid = 1;
+  Node root;
+  std::map<int, std::unique_ptr<Snap>> snaps;
+};
+
+static void prefix_release(cafd_prefix* c, int sid) {
+  auto it = c->snaps.find(sid);
+  if (it == c->snaps.end()) return;
+  Snap* s = it->second.get();
+  Node* host = s->node ? s->node : &c->root;
+  if (s->tail_page >= 0) {
+    host->tails.erase(std::remove(host->tails.begin(), host->tails.end(), s), host->tails.end());
+    cafd_pool_release(c->pool, s->tail_page);
+    --c->held;
+  }
+  Node* n = s->node;
+  while (n && n != &c->root) {
+    --n->refs;
+    Node* parent = n->parent;
+    if (n->refs == 0 && n->children.empty() && n->tails.empty()) {
+      cafd_pool_release(c->pool, n->page);
+      --c->held;
+      parent->children.erase(n->key);     // destroys n
+    }
+    n = parent;
+  }
+  c->snaps.erase(it);
+  ++c->evicted;
+}
+
+static void prefix_make_room(cafd_prefix* c, int need) {
+  while (c->held + need > c->max_pages && !c->snaps.empty()) {
+    Snap* v = nullptr;
+    for (int kind = 0; kind < 2 && !v; ++kind)
+      for (auto& kv : c->snaps)
+        if (kv.second->kind == kind && (!v || kv.second->last_use < v->last_use)) v = kv.second.get();
+    if (!v) break;
+    prefix_release(c, v->sid);
+  }
+}
+
+extern "C" {
+
+cafd_prefix* cafd_prefix_new(cafd_pool* pool, int max_pages) {
+  auto* c = new cafd_prefix;
+  c->pool = pool;
+  c->max_pages = max_pages;
+  return c;
+}
+void cafd_prefix_free(cafd_prefix* c) {
+  if (!c) return;
+  while (!c->snaps.empty()) prefix_release(c, c->snaps.begin()->first);
+  delete c;
+}
+
+int cafd_prefix_lookup(cafd_prefix* c, const int32_t* tokens, int n, int* pages_out, int cap, int* n_pages, int* tail_shared) {
+  Node* node = &c->root;
+  std::vector<int> pages;
+  uint64_t prev = 0;
+  for (int i = 0; i + kPage <= n; i += kPage) {
+    const uint64_t k = chunk_key(prev, tokens + i);
+    auto it = node->children.find(k);
+    if (it == node->children.end() || std::memcmp(it->second->tokens, tokens + i, sizeof(int32_t) * kPage) != 0) break;
+    node = it->second.get();
+    pages.push_back(node->page);
+    prev = k;
+  }
+  int length = static_cast<int>(pages.size()) * kPage;
+  Snap* best = nullptr;
+  for (Snap* s : node->tails) {
+    const int t = s->length - length;
+    if (t > 0 && t <= n - length && std::memcmp(s->tail_tokens.data(), tokens + length, sizeof(int32_t) * t) == 0 &&
+        (!best || s->length > best->length))
+      best = s;
+  }
+  int shared = 0;
+  if (best) {
+    pages.push_back(best->tail_page);
+    length = best->length;
+    shared = 1;
+  }
+  if (length >= n) {           // always leave at least one token to compute
+    if (shared) {
+      pages.pop_back();
+      shared = 0;
+      length = static_cast<int>(pages.size()) * kPage;
+    }
+    if (length >= n && !pages.empty()) {
+      pages.pop_back();
+      length = static_cast<int>(pages.size()) * kPage;
+    }
+  }
+  if (length > 0) {
+    ++c->clock;
+    if (best && shared) best->last_use = c->clock;
+    for (auto& kv : c->snaps) {
+      for (Node* m = kv.second->node; m && m != &c->root; m = m->parent)
+        if (m == node) { kv.second->last_use = c->clock; break; }
+    }
+  }
+  *n_pages = static_cast<int>(pages.size());
+  *tail_shared = shared;
+  for (int i = 0; i < std::min<int>(cap, *n_pages); ++i) pages_out[i] = pages[i];
+  return length;
+}
+
+int cafd_prefix_capture(cafd_prefix* c, int seq, const int32_t* tokens, int length, int kind) {
+  const Seq* s = seq_of(c->pool, seq);
+  if (!s || length < kPage || length > s->kv_len) return 0;
+  const int need = (length + kPage - 1) / kPage;
+  if (need > static_cast<int>(s->pages.size())) return 0;
+  prefix_make_room(c, need);
+  Node* node = &c->root;
+  uint64_t prev = 0;
+  std::vector<Node*> path;
+  int i = 0;
+  for (; i + kPage <= length; i += kPage) {
+    const uint64_t k = chunk_key(prev, tokens + i);
+    auto it = node->children.find(k);
+    if (it == node->children.end()) {
+      auto nn = std::make_unique<Node>();
+      nn->key = k;
+      nn->page = s->pages[i / kPage];
+      nn->parent = node;
+      std::memcpy(nn->tokens, tokens + i, sizeof(int32_t) * kPage);
+      cafd_pool_retain(c->pool, nn->page);
+      ++c->held;
+      it = node->children.emplace(k, std::move(nn)).first;
+    } else if (std::memcmp(it->second->tokens, tokens + i, sizeof(int32_t) * kPage) != 0) {
+      break;   // hash collision: stop extending this path
+    }
+    node = it->second.get();
+    path.push_back(node);
+    prev = k;
+  }
+  for (Node* n : path) ++n->refs;
+  auto snap = std::make_unique<Snap>();
+  snap->sid = c->next_sid++;
+  snap->kind = kind;
+  snap->length = length;
+  snap->node = path.empty() ? nullptr : node;
+  snap->tail_page = -1;
+  snap->last_use = ++c->clock;
+  if (length % kPage && i + kPage > length) {
+    snap->tail_page = s->pages[i / kPage];
+    snap->tail_tokens.assign(tokens + i, tokens + length);
+    cafd_pool_retain(c->pool, snap->tail_page);
+    ++c->held;
+    node->tails.push_back(snap.get());
+  } else {
+    snap->length = i;
+  }
+  const int sid = snap->sid;
+  c->snaps.emplace(sid, std::move(snap));
+  return sid;
+}
+
+int cafd_prefix_release(cafd_prefix* c, int sid) {
+  const int before = c->evicted;
+  prefix_release(c, sid);
+  return c->evicted - before;
+}
+int cafd_prefix_held_pages(const cafd_prefix* c) { return c->held; }
+int cafd_prefix_snapshots(const cafd_prefix* c) { return static_cast<int>(c->snaps.size()); }
+int cafd_prefix_evicted(const cafd_prefix* c) { return c->evicted; }
+
+}  // extern "C"
+
+// ---- KV reserve -----------------------------------------------------------------------------------
+namespace {
+struct LeaseRec { int leased, max_pages, shared; };
+int pages_for(int tokens) { return (tokens + kPage - 1) / kPage; }
+}  // namespace
+
+struct cafd_reserve {
+  int total, chunk_pages;
+  std::map<int, LeaseRec> leases;
+};
+
+static int reserve_leased(const cafd_reserve* r) {
+  int n = 0;
+  for (auto& kv : r->leases) n += kv.second.leased;
+  return n;
+}
+static bool reserve_safe(int unleased, std::vector<LeaseRec> v) {
+  std::sort(v.begin(), v.end(), [](const LeaseRec& a, const LeaseRec& b) {
+    return std::max(0, a.max_pages - a.leased) < std::max(0, b.max_pages - b.leased);
+  });
+  int free_pages = unleased;
+  for (auto& l : v) {
+    if (std::max(0, l.max_pages - l.leased) > free_pages) return false;
+    free_pages += l.leased;
+  }
+  return true;
+}
+
+extern "C" {
+
+cafd_reserve* cafd_reserve_new(int total_pages, int chunk_tokens) {
+  auto* r = new cafd_reserve;
+  r->total = total_pages;
+  r->chunk_pages = pages_for(chunk_tokens);
+  return r;
+}
+void cafd_reserve_free(cafd_reserve* r) { delete r; }
+int cafd_reserve_leased(const cafd_reserve* r) { return reserve_leased(r); }
+
+int cafd_reserve_lease(cafd_reserve* r, int rid, int prompt_tokens, int max_new_tokens, int shared_pages) {
+  const int prompt_pages = std::max(0, pages_for(prompt_tokens) - shared_pages);
+  const int max_pages = std::max(0, pages_for(prompt_tokens + max_new_tokens) - shared_pages);
+  const int want = std::min(max_pages, prompt_pages + r->chunk_pages);
+  const int unleased = r->total - reserve_leased(r);
+  if (want > unleased) return 0;
+  std::vector<LeaseRec> v;
+  for (auto& kv : r->leases) v.push_back(kv.second);
+  v.push_back({want, max_pages, shared_pages});
+  if (!reserve_safe(unleased - want, v)) return 0;
+  r->leases[rid] = {want, max_pages, shared_pages};
+  return 1;
+}
+
+int cafd_reserve_top_up(cafd_reserve* r, int rid) {
+  auto it = r->leases.find(rid);
+  if (it == r->leases.end()) return 0;
+  LeaseRec& l = it->second;
+  if (l.leased >= l.max_pages) return 1;
+  const int add = std::min(r->chunk_pages, l.max_pages - l.leased);
+  if (add > r->total - reserve_leased(r)) return 0;
+  l.leased += add;
+  std::vector<LeaseRec> v;
+  for (auto& kv : r->leases) v.push_back(kv.second);
+  if (!reserve_safe(r->total - reserve_leased(r), v)) {
+    l.leased -= add;
+    return 0;
+  }
+  return 1;
+}
+int cafd_reserve_release(cafd_reserve* r, int rid) { return static_cast<int>(r->leases.erase(rid)); }
+
+// ---- sampler ----------------------------------------------------------------------------------------
+float cafd_sample_uniform(uint64_t seed, uint64_t position) {
+  uint64_t x = seed + 0x7f4a7c159e3779b9ull + position * 0x9e3779b97f4a7c15ull + 0x9e3779b97f4a7c15ull;
+  x = (x ^ (x >> 30)) * 0xbf58476d1ce4e5b9ull;
+  x = (x ^ (x >> 27)) * 0x94d049bb133111ebull;
+  x ^= x >> 31;
+  return static_cast<float>(x >> 40) * (1.0f / 16777216.0f);
+}
+
+int cafd_sample_token(const float* logits, int vocab, const uint8_t* mask, float temperature, float top_p, int top_k,
+                      float min_p, uint64_t seed, uint64_t position, int use_uniform, float uniform) {
+  if (vocab <= 0 || !(temperature >= 0.f && temperature <= 2.f) || !(top_p > 0.f && top_p <= 1.f) ||
+      !(min_p >= 0.f && min_p <= 1.f))
+    return -3;
+  bool any = false;
+  for (int i = 0; i < vocab; ++i) {
+    if (mask && !mask[i]) continue;
+    any = true;
+    if (!std::isfinite(logits[i])) return -1;
+  }
+  if (!any) return -2;
+  const bool greedy = temperature < 1.0e-5f || top_k == 1;
+  if (greedy) {
+    int best = -1;
+    for (int i = 0; i < vocab; ++i) {
+      if (mask && !mask[i]) continue;
+      if (best < 0 || logits[i] > logits[best]) best = i;
+    }
+    return best;
+  }
+  std::vector<std::pair<float, int>> cand;
+  cand.reserve(vocab);
+  float mx = -INFINITY;
+  for (int i = 0; i < vocab; ++i) {
+    if (mask && !mask[i]) continue;
+    const float v = logits[i] / temperature;
+    cand.emplace_back(v, i);
+    mx = std::max(mx, v);
+  }
+  if (min_p > 0.f) {
+    const float cut = mx + std::log(min_p);
+    cand.erase(std::remove_if(cand.begin(), cand.end(), [cut](const std::pair<float, int>& c) { return c.first < cut; }), cand.end());
+  }
+  std::stable_sort(cand.begin(), cand.end(), [](const std::pair<float, int>& a, const std::pair<float, int>& b) {
+    return a.first > b.first || (a.first == b.first && a.second < b.second);
+  });
+  if (top_k > 0 && top_k < static_cast<int>(cand.size())) cand.resize(top_k);
+  std::vector<double> pr(cand.size());
+  double sum = 0.0;
+  for (size_t i = 0; i < cand.size(); ++i) { pr[i] = std::exp(static_cast<double>(cand[i].first) - mx); sum += pr[i]; }
+  for (double& v : pr) v /= sum;
+  if (top_p < 1.f) {
+    double cum = 0.0;
+    size_t keep = cand.size();
+    for (size_t i = 0; i < cand.size(); ++i) {
+      cum += pr[i];
+      if (cum >= static_cast<double>(top_p)) { keep = i + 1; break; }
+    }
+    cand.resize(keep);
+    pr.resize(keep);
+    double s2 = 0.0;
+    for (double v : pr) s2 += v;
+    for (double& v : pr) v /= s2;
+  }
+  float u = use_uniform ? uniform : cafd_sample_uniform(seed, position);
+  u = std::min(std::max(u, 0.0f), 0.99999994f);
+  double total = 0.0;
+  for (double v : pr) total += v;
+  const double target = static_cast<double>(u) * total;
+  double cum = 0.0;
+  for (size_t i = 0; i < cand.size(); ++i) {
+    cum += pr[i];
+    if (cum > target) return cand[i].second;
+  }
+  return cand.back().second;
+}
+
+}  // extern "C"

@@ -1,0 +1,70 @@
+// C ABI of libcuteafd_rt.so: host-side runtime structures in C++ (no CUDA dependency).
+//
+//   page pool + sequence tables   refcounted 64-token KV pages, fork (share) / copy-on-write / truncate
+//   prefix index                  radix over chained 64-token chunk hashes holding page references,
+//                                 snapshots with partial tails, LRU eviction by bank (prompt before turn)
+//   KV reserve                    leases with decode-chunk top-ups and the banker's-rule safety check
+//   target sampler                mask -> temperature -> min_p -> top_k -> top_p, (seed, position) draw
+//
+// The Python classes of the same names in cuteafd_b200/runtime are the readable models; tests drive
+// both with the same random workloads and require identical results.  The reference keeps these
+// structures in Rust (rust/crates/cuteafd-engine/src/prefix/*, reserve.rs,
+// rust/crates/cuteafd-core/src/{kv_cache/allocator.rs,target_sampling.rs}).
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct cafd_pool cafd_pool;
+cafd_pool* cafd_pool_new(int num_pages);
+void cafd_pool_free(cafd_pool*);
+int cafd_pool_free_pages(const cafd_pool*);
+int cafd_pool_alloc(cafd_pool*);                 // page id, or -1 when exhausted
+int cafd_pool_retain(cafd_pool*, int page);
+int cafd_pool_release(cafd_pool*, int page);     // 0 ok, -1 on misuse
+int cafd_pool_refs(const cafd_pool*, int page);
+
+// sequences live inside the pool object; ids are dense small integers
+int cafd_seq_new(cafd_pool*);
+int cafd_seq_reserve(cafd_pool*, int seq, int new_len, int* cow_src, int* cow_dst);   // >=0 pages added, -1 out of pages; cow_* = page copy to perform or -1
+int cafd_seq_fork(cafd_pool*, int src, int length);
+int cafd_seq_truncate(cafd_pool*, int seq, int length);
+int cafd_seq_free(cafd_pool*, int seq);
+int cafd_seq_set_len(cafd_pool*, int seq, int kv_len);
+int cafd_seq_len(const cafd_pool*, int seq);
+int cafd_seq_num_pages(const cafd_pool*, int seq);
+int cafd_seq_pages(const cafd_pool*, int seq, int* out, int cap);
+int cafd_seq_slots(const cafd_pool*, int seq, int start, int n, int* out);            // page*64+offset per token
+
+typedef struct cafd_prefix cafd_prefix;
+cafd_prefix* cafd_prefix_new(cafd_pool*, int max_pages);
+void cafd_prefix_free(cafd_prefix*);
+// longest cached prefix of tokens[0:n]; writes shared pages to pages_out; returns matched length.
+// *tail_shared = 1 when the last page is a shared partial tail.  Always leaves >= 1 token to compute.
+int cafd_prefix_lookup(cafd_prefix*, const int32_t* tokens, int n, int* pages_out, int cap, int* n_pages, int* tail_shared);
+// retain seq's first `length` tokens; kind 0 = prompt, 1 = turn.  returns snapshot id (>0) or 0.
+int cafd_prefix_capture(cafd_prefix*, int seq, const int32_t* tokens, int length, int kind);
+int cafd_prefix_release(cafd_prefix*, int sid);
+int cafd_prefix_held_pages(const cafd_prefix*);
+int cafd_prefix_snapshots(const cafd_prefix*);
+int cafd_prefix_evicted(const cafd_prefix*);
+
+typedef struct cafd_reserve cafd_reserve;
+cafd_reserve* cafd_reserve_new(int total_pages, int chunk_tokens);
+void cafd_reserve_free(cafd_reserve*);
+int cafd_reserve_lease(cafd_reserve*, int rid, int prompt_tokens, int max_new_tokens, int shared_pages);   // 1 admitted, 0 refused
+int cafd_reserve_top_up(cafd_reserve*, int rid);
+int cafd_reserve_release(cafd_reserve*, int rid);
+int cafd_reserve_leased(const cafd_reserve*);
+
+// One row.  mask may be NULL (uint8 per token, non-zero = allowed).  top_k <= 0 disables.  Returns the token, or
+// -1 non-finite logit, -2 empty mask, -3 bad parameter.
+int cafd_sample_token(const float* logits, int vocab, const uint8_t* mask, float temperature, float top_p, int top_k,
+                      float min_p, uint64_t seed, uint64_t position, int use_uniform, float uniform);
+float cafd_sample_uniform(uint64_t seed, uint64_t position);
+
+#ifdef __cplusplus
+}
+#endif

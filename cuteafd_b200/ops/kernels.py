@@ -310,3 +310,80 @@ def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
                                              status_word(q.device).data_ptr(), total_q, num_seqs, max_q_len, num_pages,
                                              max_pages, Hq, Hkv, D, scale, _stream()), "attn_prefill")
     return out
+
+
+# ---- FP8 block-scaled GEMM -----------------------------------------------------------------------------
+def quant_rows_fp8(x: torch.Tensor, q: torch.Tensor | None = None, s: torch.Tensor | None = None):
+    """bf16 [T, K] -> (E4M3 [T, K], fp32 scales [T, K/128]); scale = amax/448 per row and 128 columns."""
+    T, Kd = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and Kd % 128 == 0
+    if q is None:
+        q = torch.empty(T, Kd, dtype=torch.float8_e4m3fn, device=x.device)
+    if s is None:
+        s = torch.empty(T, Kd // 128, dtype=torch.float32, device=x.device)
+    _n.check(_n.cuda_lib().cafd_quant_rows_fp8(x.data_ptr(), q.data_ptr(), s.data_ptr(), T, Kd, x.stride(0), _stream()),
+             "quant_rows_fp8")
+    return q, s
+
+
+def _fp8_common(a: "_n.GemmArgs", device: torch.device, split_k: bool) -> None:
+    a.status = status_word(device).data_ptr()
+    a.out_f32, a.fp8, a.num_sms = 0, 1, num_sms()
+    if a.swap and split_k:
+        _attach_splitk(a, device)
+
+
+def linear_fp8(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor, out: torch.Tensor | None = None, *,
+               w_up: torch.Tensor | None = None, ws_up: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+               swap: bool | None = None, split_k: bool = True) -> torch.Tensor:
+    """y = dequant(xq, xs) @ dequant(wq, ws).T with E4M3 operands on the tensor cores.
+
+    xq [T, K] e4m3 + xs [T, K/128]; wq [N, K] e4m3 + ws [N/128, K/128].  ``w_up``: SwiGLU pair."""
+    T, Kd = xq.shape
+    N = wq.shape[0]
+    assert xq.is_contiguous() and wq.is_contiguous() and xs.is_contiguous() and ws.is_contiguous() and N % 128 == 0
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=xq.device)
+    if T == 0:
+        return out
+    if swap is None:
+        swap = T <= 64
+    a = _n.GemmArgs()
+    a.w0, a.w1, a.x, a.out = wq.data_ptr(), _ptr(w_up), xq.data_ptr(), out.data_ptr()
+    a.w_scale, a.w_scale1, a.x_scale = ws.data_ptr(), _ptr(ws_up), xs.data_ptr()
+    a.residual = _ptr(residual)
+    a.w_rows_total, a.x_rows_total = N, T
+    a.k, a.n_features, a.x_rows, a.ldo = Kd, N, T, out.stride(0)
+    a.w_rows_per_expert, a.w1_row_offset, a.max_x_tiles = 0, 0, 0
+    a.swap, a.dual = int(swap), int(w_up is not None)
+    a.bx = (64 if (w_up is not None and T > 32) else pick_token_tile(T)) if swap else 128
+    if swap and T > a.bx:
+        a.bx = 64 if w_up is not None else 128
+    _fp8_common(a, xq.device, split_k)
+    _n.check(_n.cuda_lib().cafd_gemm_fp8(C.byref(a), _stream()), "cafd_gemm_fp8")
+    return out
+
+
+def grouped_linear_fp8(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor, out: torch.Tensor,
+                       tile_expert: torch.Tensor, tile_row0: torch.Tensor, num_tiles: torch.Tensor, max_tiles: int,
+                       tile_rows: int, *, w_up: torch.Tensor | None = None, ws_up: torch.Tensor | None = None,
+                       row_dst: torch.Tensor | None = None, wait_flag: int | None = None, epoch: torch.Tensor | None = None,
+                       signal_flag: int | None = None, done_counter: torch.Tensor | None = None, out_ptr: int | None = None,
+                       ldo: int | None = None, split_k: bool = True) -> None:
+    """Expert-grouped FP8 GEMM over an expert-sorted E4M3 slab (wq [E, N, K], ws [E, N/128, K/128])."""
+    E, N, Kd = wq.shape
+    a = _n.GemmArgs()
+    a.w0, a.w1, a.x = wq.data_ptr(), _ptr(w_up), xq.data_ptr()
+    a.w_scale, a.w_scale1, a.x_scale = ws.data_ptr(), _ptr(ws_up), xs.data_ptr()
+    a.out = out_ptr if out_ptr is not None else out.data_ptr()
+    a.row_dst = _ptr(row_dst)
+    a.tile_expert, a.tile_row0, a.num_x_tiles = tile_expert.data_ptr(), tile_row0.data_ptr(), num_tiles.data_ptr()
+    a.wait_flag, a.epoch = wait_flag, _ptr(epoch)
+    a.signal_flag, a.done_counter = signal_flag, _ptr(done_counter)
+    a.w_rows_total, a.x_rows_total = E * N, xq.shape[0]
+    a.k, a.n_features, a.x_rows = Kd, N, xq.shape[0]
+    a.ldo = ldo if ldo is not None else out.stride(0)
+    a.w_rows_per_expert, a.w1_row_offset, a.max_x_tiles = N, 0, max_tiles
+    a.swap, a.dual, a.bx = int(tile_rows < 128), int(w_up is not None), tile_rows
+    _fp8_common(a, xq.device, split_k)
+    _n.check(_n.cuda_lib().cafd_gemm_fp8(C.byref(a), _stream()), "cafd_gemm_fp8(grouped)")

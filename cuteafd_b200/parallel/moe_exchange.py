@@ -160,3 +160,30 @@ class LocalExchange:
         self.att.dispatch(x, logits, route_kw, tile_rows, 0, self.epoch)
         self.exp.run(w_gate, w_up, w_down, tile_rows, 0, self.epoch, self.att.combine.data_ptr(), None, wait=False)
         return self.att.combine_into(out, T, 0, self.epoch, shared=shared, residual=residual, wait=False)
+
+    def forward_fp8(self, x: torch.Tensor, logits: torch.Tensor, route_kw: dict, w_gate, w_up, w_down, out: torch.Tensor, *,
+                    shared: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+                    tile_rows: int | None = None) -> torch.Tensor:
+        """Same exchange with E4M3 experts: each ``w_*`` is (values [E, N, K] e4m3, scales [E, N/128, K/128]).
+        Rows are quantised 1x128 on the expert side before each grouped GEMM."""
+        T = x.shape[0]
+        g = self.geo
+        tile_rows = tile_rows or pick_tile_rows(T, g.top_k, g.num_experts)
+        if tile_rows == 128 and T * g.top_k < 128 * g.num_experts:
+            tile_rows = 64                          # the fp8 kernel's weights-on-M path tops out at 64 rows
+        self.att.dispatch(x, logits, route_kw, tile_rows, 0, self.epoch)
+        e = self.exp
+        rows = min(g.max_rows, T * g.top_k + g.num_experts * tile_rows)
+        if not hasattr(e, "slab_q"):
+            dev = e.slab.device
+            e.slab_q = torch.zeros(g.max_rows, g.hidden, dtype=torch.float8_e4m3fn, device=dev)
+            e.slab_s = torch.ones(g.max_rows, g.hidden // 128, dtype=torch.float32, device=dev)
+            e.h_q = torch.zeros(g.max_rows, g.expert_ffn, dtype=torch.float8_e4m3fn, device=dev)
+            e.h_s = torch.ones(g.max_rows, g.expert_ffn // 128, dtype=torch.float32, device=dev)
+        K.quant_rows_fp8(e.slab[:rows], e.slab_q[:rows], e.slab_s[:rows])
+        K.grouped_linear_fp8(e.slab_q, e.slab_s, w_gate[0], w_gate[1], e.hbuf, e.tile_expert, e.tile_row0, e.num_tiles,
+                             g.max_tiles, tile_rows, w_up=w_up[0], ws_up=w_up[1])
+        K.quant_rows_fp8(e.hbuf[:rows], e.h_q[:rows], e.h_s[:rows])
+        K.grouped_linear_fp8(e.h_q, e.h_s, w_down[0], w_down[1], e.hbuf, e.tile_expert, e.tile_row0, e.num_tiles,
+                             g.max_tiles, tile_rows, row_dst=e.row_dst, out_ptr=self.att.combine.data_ptr(), ldo=g.hidden)
+        return self.att.combine_into(out, T, 0, self.epoch, shared=shared, residual=residual, wait=False)

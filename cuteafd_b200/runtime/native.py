@@ -1,0 +1,168 @@
+"""ctypes front end of libcuteafd_rt.so: the C++ page pool, prefix index, KV reserve and sampler.
+
+Same behaviour as the Python classes in this package (``paged``, ``prefix_cache``, ``reserve``,
+``sampling``); the tests drive both with identical random workloads.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+from .._native import lib as _n
+
+_sigs_done = False
+
+
+def _lib():
+    global _sigs_done
+    L = _n.rt_lib()
+    if not _sigs_done:
+        P, I, IP = C.c_void_p, C.c_int, C.POINTER(C.c_int)
+        def sig(name, args, res=I):
+            f = getattr(L, name); f.argtypes, f.restype = args, res
+        sig("cafd_pool_new", [I], P); sig("cafd_pool_free", [P], None); sig("cafd_pool_free_pages", [P])
+        sig("cafd_pool_alloc", [P]); sig("cafd_pool_retain", [P, I]); sig("cafd_pool_release", [P, I]); sig("cafd_pool_refs", [P, I])
+        sig("cafd_seq_new", [P]); sig("cafd_seq_reserve", [P, I, I, IP, IP]); sig("cafd_seq_fork", [P, I, I])
+        sig("cafd_seq_truncate", [P, I, I]); sig("cafd_seq_free", [P, I]); sig("cafd_seq_set_len", [P, I, I]); sig("cafd_seq_len", [P, I])
+        sig("cafd_seq_num_pages", [P, I]); sig("cafd_seq_pages", [P, I, IP, I]); sig("cafd_seq_slots", [P, I, I, I, IP])
+        sig("cafd_prefix_new", [P, I], P); sig("cafd_prefix_free", [P], None)
+        sig("cafd_prefix_lookup", [P, C.POINTER(C.c_int32), I, IP, I, IP, IP]); sig("cafd_prefix_capture", [P, I, C.POINTER(C.c_int32), I, I])
+        sig("cafd_prefix_release", [P, I]); sig("cafd_prefix_held_pages", [P]); sig("cafd_prefix_snapshots", [P]); sig("cafd_prefix_evicted", [P])
+        sig("cafd_reserve_new", [I, I], P); sig("cafd_reserve_free", [P], None); sig("cafd_reserve_lease", [P, I, I, I, I])
+        sig("cafd_reserve_top_up", [P, I]); sig("cafd_reserve_release", [P, I]); sig("cafd_reserve_leased", [P])
+        sig("cafd_sample_token", [C.POINTER(C.c_float), I, C.POINTER(C.c_uint8), C.c_float, C.c_float, I, C.c_float, C.c_uint64, C.c_uint64, I, C.c_float])
+        sig("cafd_sample_uniform", [C.c_uint64, C.c_uint64], C.c_float)
+        _sigs_done = True
+    return L
+
+
+class NativePool:
+    def __init__(self, num_pages: int):
+        self.L = _lib()
+        self.h = self.L.cafd_pool_new(num_pages)
+        if not self.h:
+            raise ValueError("pool needs at least 2 pages")
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.L.cafd_pool_free(self.h)
+            self.h = None
+
+    @property
+    def free_pages(self) -> int:
+        return self.L.cafd_pool_free_pages(self.h)
+
+    def refs(self, page: int) -> int:
+        return self.L.cafd_pool_refs(self.h, page)
+
+    def new_seq(self) -> int:
+        return self.L.cafd_seq_new(self.h)
+
+    def reserve(self, seq: int, new_len: int) -> tuple[int, tuple[int, int] | None]:
+        """Returns (pages added or -1, (src, dst) page copy to perform or None)."""
+        a, b = C.c_int(-1), C.c_int(-1)
+        n = self.L.cafd_seq_reserve(self.h, seq, new_len, C.byref(a), C.byref(b))
+        return n, ((a.value, b.value) if a.value >= 0 else None)
+
+    def fork(self, seq: int, length: int = -1) -> int:
+        return self.L.cafd_seq_fork(self.h, seq, length)
+
+    def truncate(self, seq: int, length: int) -> None:
+        self.L.cafd_seq_truncate(self.h, seq, length)
+
+    def free(self, seq: int) -> None:
+        self.L.cafd_seq_free(self.h, seq)
+
+    def set_len(self, seq: int, n: int) -> None:
+        self.L.cafd_seq_set_len(self.h, seq, n)
+
+    def pages(self, seq: int) -> list[int]:
+        n = self.L.cafd_seq_num_pages(self.h, seq)
+        buf = (C.c_int * max(n, 1))()
+        self.L.cafd_seq_pages(self.h, seq, buf, n)
+        return list(buf[:n])
+
+    def slots(self, seq: int, start: int, n: int) -> list[int]:
+        buf = (C.c_int * max(n, 1))()
+        if self.L.cafd_seq_slots(self.h, seq, start, n, buf) != 0:
+            raise IndexError("slots outside the reserved pages")
+        return list(buf[:n])
+
+
+class NativePrefix:
+    def __init__(self, pool: NativePool, max_pages: int):
+        self.L, self.pool = _lib(), pool
+        self.h = self.L.cafd_prefix_new(pool.h, max_pages)
+
+    def __del__(self):
+        if getattr(self, "h", None) and getattr(self.pool, "h", None):
+            self.L.cafd_prefix_free(self.h)
+            self.h = None
+
+    def lookup(self, tokens: list[int]) -> tuple[int, list[int], bool]:
+        n = len(tokens)
+        arr = (C.c_int32 * max(n, 1))(*tokens)
+        cap = n // 64 + 2
+        out = (C.c_int * cap)()
+        np_, tail = C.c_int(0), C.c_int(0)
+        length = self.L.cafd_prefix_lookup(self.h, arr, n, out, cap, C.byref(np_), C.byref(tail))
+        return length, list(out[:np_.value]), bool(tail.value)
+
+    def capture(self, seq: int, tokens: list[int], kind: str = "prompt") -> int:
+        arr = (C.c_int32 * max(len(tokens), 1))(*tokens)
+        return self.L.cafd_prefix_capture(self.h, seq, arr, len(tokens), 0 if kind == "prompt" else 1)
+
+    def release(self, sid: int) -> None:
+        self.L.cafd_prefix_release(self.h, sid)
+
+    @property
+    def held_pages(self) -> int:
+        return self.L.cafd_prefix_held_pages(self.h)
+
+    @property
+    def snapshots(self) -> int:
+        return self.L.cafd_prefix_snapshots(self.h)
+
+    @property
+    def evicted(self) -> int:
+        return self.L.cafd_prefix_evicted(self.h)
+
+
+class NativeReserve:
+    def __init__(self, total_pages: int, chunk_tokens: int = 16384):
+        self.L = _lib()
+        self.h = self.L.cafd_reserve_new(total_pages, chunk_tokens)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.L.cafd_reserve_free(self.h)
+            self.h = None
+
+    def lease(self, rid: int, prompt: int, max_new: int, shared_pages: int = 0) -> bool:
+        return bool(self.L.cafd_reserve_lease(self.h, rid, prompt, max_new, shared_pages))
+
+    def top_up(self, rid: int) -> bool:
+        return bool(self.L.cafd_reserve_top_up(self.h, rid))
+
+    def release(self, rid: int) -> None:
+        self.L.cafd_reserve_release(self.h, rid)
+
+    @property
+    def leased(self) -> int:
+        return self.L.cafd_reserve_leased(self.h)
+
+
+def sample_token(logits, temperature=0.0, top_p=1.0, top_k=None, min_p=0.0, seed=0, position=0, mask=None, uniform=None) -> int:
+    """Native sampler on a float32 CPU tensor row.  Negative return values are row status codes."""
+    L = _lib()
+    x = logits.detach().float().contiguous().cpu()
+    lp = C.cast(x.data_ptr(), C.POINTER(C.c_float))
+    mp = None
+    if mask is not None:
+        m = mask.to("cpu").to(dtype=__import__("torch").uint8).contiguous()
+        mp = C.cast(m.data_ptr(), C.POINTER(C.c_uint8))
+    return L.cafd_sample_token(lp, x.numel(), mp, temperature, top_p, top_k or 0, min_p, seed, position,
+                               int(uniform is not None), float(uniform or 0.0))
+
+
+def sample_uniform(seed: int, position: int) -> float:
+    return float(_lib().cafd_sample_uniform(seed, position))

@@ -198,3 +198,68 @@ def test_attn_prefill(K, lens, qlens):
         ref = R.causal_attention(q[o:o + qlens[s]], k, v, lens[s] - qlens[s])
         close(out[o:o + qlens[s]], ref)
         o += qlens[s]
+
+
+# ---- FP8 block-scaled -----------------------------------------------------------------------------------
+def _fp8_ref(x, w, w_up=None):
+    from cuteafd_b200.quant import codecs
+    xq, xs = codecs.fp8_quant_rows(x.float())
+    wq, ws = codecs.fp8_quant_block128(w.float())
+    xd, wd = codecs.fp8_dequant_rows(xq, xs), codecs.fp8_dequant_block128(wq, ws)
+    y = xd @ wd.T
+    if w_up is not None:
+        uq, us = codecs.fp8_quant_block128(w_up.float())
+        y = torch.nn.functional.silu(y) * (xd @ codecs.fp8_dequant_block128(uq, us).T)
+        return y, (xq, xs, wq, ws, uq, us)
+    return y, (xq, xs, wq, ws, None, None)
+
+
+def test_quant_rows_fp8_matches_codec(K):
+    from cuteafd_b200.quant import codecs
+    x = bf(37, 512, seed=3)
+    q, s = K.quant_rows_fp8(x)
+    rq, rs = codecs.fp8_quant_rows(x.float())
+    assert torch.allclose(s, rs, rtol=1e-6)
+    assert (codecs.fp8_dequant_rows(q, s) - codecs.fp8_dequant_rows(rq, rs)).abs().max() <= 0.07 * x.float().abs().max()
+
+
+@pytest.mark.parametrize("T,N,Kd,swap,dual", [(8, 256, 512, True, False), (33, 384, 1024, True, True), (200, 256, 256, False, False),
+                                             (300, 512, 768, False, True), (1, 128, 2048, True, False), (64, 2048, 7168, True, False)])
+def test_linear_fp8(K, T, N, Kd, swap, dual):
+    x, w = bf(T, Kd, seed=1), bf(N, Kd, scale=0.05, seed=2)
+    wu = bf(N, Kd, scale=0.05, seed=3) if dual else None
+    ref, (xq, xs, wq, ws, uq, us) = _fp8_ref(x, w, wu)
+    y = K.linear_fp8(xq.contiguous(), xs.contiguous(), wq.contiguous(), ws.contiguous(), w_up=uq, ws_up=us, swap=swap)
+    check_status(K)
+    close(y, ref)
+
+
+@pytest.mark.parametrize("T,tile", [(6, 16), (300, 64), (1500, 128)])
+def test_moe_fp8_grouped(K, T, tile):
+    """Routed experts in FP8: plan/dispatch in bf16, rows quantised on the expert side, fp8 fc1/fc2."""
+    from cuteafd_b200.parallel.moe_exchange import ExchangeGeometry, LocalExchange
+    from cuteafd_b200.quant import codecs
+    H, I, E, k = 512, 256, 16, 4
+    ex = LocalExchange(ExchangeGeometry(H, I, E, k, max_tokens=T, n_expert_ranks=1), dev())
+    x, res = bf(T, H, seed=1), bf(T, H, seed=2)
+    wg, wu, wd = bf(E, I, H, scale=0.05, seed=3), bf(E, I, H, scale=0.05, seed=4), bf(E, H, I, scale=0.05, seed=5)
+    q = {n: [codecs.fp8_quant_block128(w[e].float()) for e in range(E)] for n, w in (("g", wg), ("u", wu), ("d", wd))}
+    st = lambda n, i: torch.stack([p[i] for p in q[n]]).contiguous()
+    logits = torch.randn(T, E, device=dev())
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev())
+    ex.forward_fp8(x, logits, dict(scoring="softmax"), (st("g", 0), st("g", 1)), (st("u", 0), st("u", 1)), (st("d", 0), st("d", 1)),
+                   out, residual=res, tile_rows=tile)
+    check_status(K)
+    idx, w = R.route_topk(logits, k, "softmax")
+    deq = lambda n: torch.stack([codecs.fp8_dequant_block128(*p) for p in q[n]])
+    xq, xs = codecs.fp8_quant_rows(x.float())
+    xd = codecs.fp8_dequant_rows(xq, xs).to(torch.bfloat16)
+    parts = torch.zeros(T, k, H, device=dev())
+    for e in range(E):
+        rows, slots = (idx == e).nonzero(as_tuple=True)
+        if rows.numel():
+            h = (torch.nn.functional.silu(xd[rows].float() @ deq("g")[e].T) * (xd[rows].float() @ deq("u")[e].T)).to(torch.bfloat16)
+            hq, hs = codecs.fp8_quant_rows(h.float())
+            y = codecs.fp8_dequant_rows(hq, hs) @ deq("d")[e].T
+            parts[rows, slots] = y.to(torch.bfloat16).float() * w[rows, slots][:, None]
+    close(out, R.combine_slots(parts, None, res, torch.bfloat16), 3e-2, 3e-2)
