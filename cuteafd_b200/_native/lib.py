@@ -29,6 +29,9 @@ class GemmArgs(C.Structure):
         ("w_rows_per_expert", C.c_int), ("w1_row_offset", C.c_int), ("max_x_tiles", C.c_int),
         ("swap", C.c_int), ("dual", C.c_int), ("bx", C.c_int), ("out_f32", C.c_int), ("fp8", C.c_int),
         ("num_sms", C.c_int),
+        ("rs_ranks", C.c_int), ("rs_rows_per_rank", C.c_int), ("rs_my_rank", C.c_int), ("n_signal_flags", C.c_int),
+        ("n_wait_flags", C.c_int), ("reserved0", C.c_int),
+        ("rs_out", C.c_void_p * 8), ("signal_flags", C.c_void_p * 8),
     ]
 
 
@@ -40,6 +43,15 @@ class MoeLayout(C.Structure):
         ("n_ranks", C.c_int), ("expert_lo", C.c_int * (MAX_RANKS + 1)),
         ("slab", C.c_void_p * MAX_RANKS), ("meta", C.c_void_p * MAX_RANKS), ("flag", C.c_void_p * MAX_RANKS),
         ("max_tiles", C.c_int), ("max_rows", C.c_int),
+    ]
+
+
+class TpReduceArgs(C.Structure):
+    _fields_ = [
+        ("partials", C.c_void_p), ("residual", C.c_void_p), ("norm_w", C.c_void_p), ("x_out", C.c_void_p * 8),
+        ("rs_flags", C.c_void_p), ("ag_flags", C.c_void_p * 8), ("epoch", C.c_void_p), ("done_counter", C.c_void_p),
+        ("status", C.c_void_p), ("ranks", C.c_int), ("my_rank", C.c_int), ("rows_per_rank", C.c_int),
+        ("rows_valid", C.c_int), ("N", C.c_int), ("eps", C.c_float),
     ]
 
 
@@ -76,6 +88,8 @@ def cuda_lib():
         _sig(lib, "cafd_decode_advance", [P, P, P, P, P, P, I, I, I, P])
         _sig(lib, "cafd_route_topk", [P, P, P, P, I, I, I, I, I, I, I, F, P])
         _sig(lib, "cafd_moe_meta_ints", [I, I])
+        _sig(lib, "cafd_wait_flag", [P, P, P, P])
+        _sig(lib, "cafd_tp_reduce_norm_gather", [C.POINTER(TpReduceArgs), P])
         _sig(lib, "cafd_moe_plan", [P, I, I, I, I, C.POINTER(MoeLayout), P, P, P, P])
         _sig(lib, "cafd_moe_dispatch", [P, P, P, I, I, I, C.POINTER(MoeLayout), P, P, P])
         _sig(lib, "cafd_moe_combine", [P, P, P, P, P, I, I, I, P, I, P, P, P])

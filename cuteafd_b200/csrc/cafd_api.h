@@ -62,6 +62,17 @@ typedef struct {
   int out_f32;
   int fp8;
   int num_sms;               // 0 = query
+  // Tensor-parallel reduce-scatter epilogue (0 ranks = off): output row r is stored into
+  // rs_out[r / rs_rows_per_rank] (a local or peer receive buffer [rs_ranks][rs_rows_per_rank][ldo])
+  // at plane rs_my_rank; signal_flags[0..n) are all set to *epoch when the stores are complete.
+  int rs_ranks;
+  int rs_rows_per_rank;
+  int rs_my_rank;
+  int n_signal_flags;
+  int n_wait_flags;          // wait_flag points at this many consecutive words (0 = 1)
+  int reserved0;
+  void* rs_out[8];
+  uint32_t* signal_flags[8];
 } cafd_gemm_args;
 
 int cafd_gemm(const cafd_gemm_args* a, cafd_stream_t stream);

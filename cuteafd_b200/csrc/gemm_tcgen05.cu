@@ -37,6 +37,16 @@ struct GemmDev {
   uint32_t* done_counter;
   uint32_t* signal_flag;
   uint32_t* status;
+  // Reduce-scatter epilogue (tensor-parallel row-parallel GEMM): output row r belongs to rank
+  // r / rs_rows_per_rank and is stored into that rank's receive buffer
+  // [rs_ranks][rs_rows_per_rank][ldo] at plane rs_my_rank (peer memory for other ranks).
+  void* rs_out[8];
+  uint32_t* signal_flags[8];  // flags set to *epoch when every store of this launch is done
+  int rs_ranks;
+  int rs_rows_per_rank;
+  int rs_my_rank;
+  int n_signal;
+  int n_wait;                 // consecutive flag words to wait on (all must reach *epoch)
   float* splitk_scratch;      // [units][acc cols][128] fp32 partials (weights-on-M orientation only)
   uint32_t* splitk_tickets;   // one arrival counter per output tile, all zero between launches
   int splitk_max_units;
@@ -58,14 +68,15 @@ struct GemmCfg {
   static constexpr int kWBytes = kBW * kBK * 2;
   static constexpr int kXBytes = kBX * kBK * 2;
   static constexpr int kStageBytes = kWTiles * kWBytes + kXBytes;
-  static constexpr int kStages = (200 * 1024 / kStageBytes) > 10 ? 10 : (200 * 1024 / kStageBytes);
+  static constexpr int kStages = (192 * 1024 / kStageBytes) > 10 ? 10 : (192 * 1024 / kStageBytes);
   // accumulator columns per buffer
   static constexpr int kAccCols = kSwap ? kBX * kWTiles : kBW * kWTiles;
   static constexpr int kTmemCols = (2 * kAccCols <= 32) ? 32 : (2 * kAccCols <= 64) ? 64 : (2 * kAccCols <= 128) ? 128
                                    : (2 * kAccCols <= 256) ? 256 : 512;
   static constexpr int kMmaM = 128;
   static constexpr int kMmaN = kSwap ? kBX : kBW * kWTiles;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+  static constexpr int kStagingBytes = kSwap ? 0 : 4 * 32 * 64 * 4;   // epilogue staging (tokens-on-M only)
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024;
   static_assert(2 * kAccCols <= 512, "accumulators exceed TMEM");
   static_assert(kSwap ? (kBW == 128) : (kBX == 128), "the M side is always 128 rows");
   static_assert(kMmaN % 16 == 0 && kMmaN >= 16 && kMmaN <= 256, "invalid UMMA N");
@@ -87,6 +98,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
   __shared__ uint32_t tmem_base_slot;
   __shared__ int s_x_tiles;
   __shared__ int s_last_unit;
+  __shared__ void* s_rs_out[8];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -101,12 +113,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
       mbar_init(&tempty_bar[s], 128);
     }
     mbar_fence_init();
+    for (int r = 0; r < 8; ++r) s_rs_out[r] = p.rs_out[r];
     pdl_wait();   // flags, tile counts and activations come from kernels earlier in the stream
     // A peer may still be writing the slab and the tile list: wait for its flag first.
     int xt = p.x_tiles_static;
     bool ok = true;
     if (p.wait_flag) {
-      ok = wait_flag_ge(p.wait_flag, *p.epoch, p.status);
+      const uint32_t ep = *p.epoch;
+      for (int i = 0; i < p.n_wait && ok; ++i) ok = wait_flag_ge(p.wait_flag + i, ep, p.status);
       // The rows were written with ordinary stores by another GPU; the TMA engine reads them
       // through the async proxy, so order the acquire before those reads.
       asm volatile("fence.proxy.async;" ::: "memory");
@@ -256,80 +270,95 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
         part0 = p.splitk_scratch + static_cast<size_t>(tile * splits) * (Cfg::kAccCols * 128);
       }
       if (!kSwap) {
-        // thread = token row; columns = features
+        // thread = token row; columns = features.  Every 64-column chunk passes through a
+        // warp-private fp32 staging tile so that the global (or peer) stores are 128 contiguous
+        // bytes per row instead of one 16-byte piece per thread and row.
         const int row = x_row0 + quad * 32 + lane;
         int dst = row;
         bool row_ok = p.tile_row0 ? true : (row < p.x_rows);
         if (p.row_dst && row_ok) { dst = p.row_dst[row]; row_ok = dst >= 0; }
+        if (!row_ok) dst = -1;
+        int owner = 0;
+        if (p.rs_ranks && dst >= 0) {
+          owner = dst / p.rs_rows_per_rank;
+          dst = p.rs_my_rank * p.rs_rows_per_rank + (dst - owner * p.rs_rows_per_rank);
+          if (owner >= p.rs_ranks) dst = -1;
+        }
         const float scale = (p.row_scale && row_ok) ? p.row_scale[row] : 1.0f;
         const int f_base = wt * kBW;
+        float* stg = reinterpret_cast<float*>(smem + Cfg::kStages * Cfg::kStageBytes) + (warp - 2) * (32 * 64);
 #pragma unroll 1
-        for (int c0 = 0; c0 < kBW; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(t0 + c0, r);
-          float v[32];
-          if (kDual) {
-            uint32_t u[32];
-            tmem_ld_32x32(t0 + kBW + c0, u);
-            tmem_ld_wait();
+        for (int c0 = 0; c0 < kBW; c0 += 64) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = silu(__uint_as_float(r[j])) * __uint_as_float(u[j]);
-          } else {
-            tmem_ld_wait();
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            tmem_ld_32x32(t0 + c0 + 32 * h, r);
+            float v[32];
+            if (kDual) {
+              uint32_t u[32];
+              tmem_ld_32x32(t0 + kBW + c0 + 32 * h, u);
+              tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          }
-          const int f0 = f_base + c0;
-          if (row_ok && f0 < p.n_features) {
-            const size_t off = static_cast<size_t>(dst) * p.ldo + f0;
-            const bool full = f0 + 32 <= p.n_features;
-            if (p.out_f32) {
-              float* o = reinterpret_cast<float*>(p.out) + off;
-              if (full) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                  *reinterpret_cast<float4*>(o + j) =
-                      make_float4(v[j] * scale, v[j + 1] * scale, v[j + 2] * scale, v[j + 3] * scale);
-              } else {
-                for (int j = 0; j < 32 && f0 + j < p.n_features; ++j) o[j] = v[j] * scale;
-              }
+              for (int j = 0; j < 32; ++j) v[j] = silu(__uint_as_float(r[j])) * __uint_as_float(u[j]) * scale;
             } else {
-              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + off;
-              if (p.residual) {
-                const __nv_bfloat16* rs = reinterpret_cast<const __nv_bfloat16*>(p.residual) + off;
-                if (full) {
+              tmem_ld_wait();
 #pragma unroll
-                  for (int j = 0; j < 32; j += 8) {
-                    uint4 q = *reinterpret_cast<const uint4*>(rs + j);
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * scale;
+            }
+            // staging row = lane: 16 chunks of 4 floats, chunk index XOR (lane & 15)
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const int chunk = (32 * h + j) >> 2;
+              *reinterpret_cast<float4*>(stg + lane * 64 + ((chunk ^ (lane & 15)) << 2)) =
+                  make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+          }
+          __syncwarp();
+          // store phase: one instruction covers 4 rows x 8 pieces of 8 columns
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = 4 * i + (lane >> 3), oc = lane & 7;
+            const int d = __shfl_sync(0xffffffffu, dst, rr);
+            const int own = __shfl_sync(0xffffffffu, owner, rr);
+            uint8_t* out_base = reinterpret_cast<uint8_t*>(p.rs_ranks ? s_rs_out[own] : p.out);
+            const int f0 = f_base + c0 + 8 * oc;
+            const float4 a4 = *reinterpret_cast<const float4*>(stg + rr * 64 + (((2 * oc) ^ (rr & 15)) << 2));
+            const float4 b4 = *reinterpret_cast<const float4*>(stg + rr * 64 + (((2 * oc + 1) ^ (rr & 15)) << 2));
+            float v8[8] = {a4.x, a4.y, a4.z, a4.w, b4.x, b4.y, b4.z, b4.w};
+            if (d >= 0 && f0 < p.n_features) {
+              const size_t off = static_cast<size_t>(d) * p.ldo + f0;
+              const bool full = f0 + 8 <= p.n_features;
+              if (p.out_f32) {
+                float* o = reinterpret_cast<float*>(out_base) + off;
+                if (full) {
+                  *reinterpret_cast<float4*>(o) = a4;
+                  *reinterpret_cast<float4*>(o + 4) = b4;
+                } else {
+                  for (int j = 0; j < 8 && f0 + j < p.n_features; ++j) o[j] = v8[j];
+                }
+              } else {
+                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out_base) + off;
+                if (p.residual) {
+                  const __nv_bfloat16* rs = reinterpret_cast<const __nv_bfloat16*>(p.residual) + off;
+                  if (full) {
+                    const uint4 q = *reinterpret_cast<const uint4*>(rs);
                     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                      v[j + 2 * e] = v[j + 2 * e] * scale + bf16_lo(w[e]);
-                      v[j + 2 * e + 1] = v[j + 2 * e + 1] * scale + bf16_hi(w[e]);
-                    }
+                    for (int e = 0; e < 4; ++e) { v8[2 * e] += bf16_lo(w[e]); v8[2 * e + 1] += bf16_hi(w[e]); }
+                  } else {
+                    for (int j = 0; j < 8 && f0 + j < p.n_features; ++j) v8[j] += __bfloat162float(rs[j]);
                   }
+                }
+                if (full) {
+                  *reinterpret_cast<uint4*>(o) = make_uint4(pack_bf16(v8[0], v8[1]), pack_bf16(v8[2], v8[3]),
+                                                            pack_bf16(v8[4], v8[5]), pack_bf16(v8[6], v8[7]));
                 } else {
-                  for (int j = 0; j < 32 && f0 + j < p.n_features; ++j) v[j] = v[j] * scale + __bfloat162float(rs[j]);
+                  for (int j = 0; j < 8 && f0 + j < p.n_features; ++j) o[j] = __float2bfloat16(v8[j]);
                 }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] *= scale;
-              }
-              if (full) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  uint4 q;
-                  q.x = pack_bf16(v[j], v[j + 1]);
-                  q.y = pack_bf16(v[j + 2], v[j + 3]);
-                  q.z = pack_bf16(v[j + 4], v[j + 5]);
-                  q.w = pack_bf16(v[j + 6], v[j + 7]);
-                  *reinterpret_cast<uint4*>(o + j) = q;
-                }
-              } else {
-                for (int j = 0; j < 32 && f0 + j < p.n_features; ++j) o[j] = __float2bfloat16(v[j]);
               }
             }
           }
+          __syncwarp();
         }
       } else {
         // thread = feature; columns = tokens
@@ -389,15 +418,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
             int dst = row;
             bool row_ok = p.tile_row0 ? true : (row < p.x_rows);
             if (p.row_dst && row_ok) { dst = p.row_dst[row]; row_ok = dst >= 0; }
+            void* out_base = p.out;
+            if (p.rs_ranks && row_ok) {
+              const int owner = dst / p.rs_rows_per_rank;
+              dst = p.rs_my_rank * p.rs_rows_per_rank + (dst - owner * p.rs_rows_per_rank);
+              row_ok = owner < p.rs_ranks;
+              out_base = s_rs_out[owner < p.rs_ranks ? owner : 0];
+            }
             if (row_ok && f_ok) {
               float val = v[j];
               if (p.row_scale) val *= p.row_scale[row];
               const size_t off = static_cast<size_t>(dst) * p.ldo + f;
               if (p.out_f32) {
-                reinterpret_cast<float*>(p.out)[off] = val;
+                reinterpret_cast<float*>(out_base)[off] = val;
               } else {
                 if (p.residual) val += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.residual)[off]);
-                reinterpret_cast<__nv_bfloat16*>(p.out)[off] = __float2bfloat16(val);
+                reinterpret_cast<__nv_bfloat16*>(out_base)[off] = __float2bfloat16(val);
               }
             }
           }
@@ -407,7 +443,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
       mbar_arrive(&tempty_bar[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
-    if (p.signal_flag) __threadfence_system();
+    if (p.signal_flag || p.n_signal) __threadfence_system();
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -417,14 +453,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
-  if (p.signal_flag && threadIdx.x == 0) {
+  if ((p.signal_flag || p.n_signal) && threadIdx.x == 0) {
     // The last CTA to finish publishes the step number to the consumer (possibly another GPU).
     __threadfence();
     const uint32_t prev = atomicAdd(p.done_counter, 1u);
     if (prev == gridDim.x - 1) {
       *p.done_counter = 0;
       __threadfence_system();
-      st_release_sys(p.signal_flag, *p.epoch);
+      const uint32_t ep = *p.epoch;
+      if (p.signal_flag) st_release_sys(p.signal_flag, ep);
+      for (int r = 0; r < p.n_signal; ++r) st_release_sys(p.signal_flags[r], ep);
     }
   }
 }
@@ -457,6 +495,15 @@ static int launch(const cafd_gemm_args* a, cudaStream_t stream) {
   p.epoch = a->epoch;
   p.done_counter = a->done_counter;
   p.signal_flag = a->signal_flag;
+  for (int r = 0; r < 8; ++r) {
+    p.rs_out[r] = a->rs_out[r];
+    p.signal_flags[r] = a->signal_flags[r];
+  }
+  p.rs_ranks = a->rs_ranks;
+  p.rs_rows_per_rank = a->rs_rows_per_rank;
+  p.rs_my_rank = a->rs_my_rank;
+  p.n_signal = a->n_signal_flags;
+  p.n_wait = a->n_wait_flags > 0 ? a->n_wait_flags : 1;
   p.status = a->status;
   p.num_k_blocks = (a->k + kBK - 1) / kBK;
   p.n_features = a->n_features;
@@ -511,7 +558,8 @@ extern "C" int cafd_gemm(const cafd_gemm_args* a, cafd_stream_t stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (!a || !a->w0 || !a->x || !a->out || a->k <= 0 || (a->k % 8) != 0) return -10;
   if (a->fp8) return -11;  // block-scaled fp8 lives in gemm_fp8_tcgen05.cu
-  if (a->signal_flag && (!a->done_counter || !a->epoch)) return -12;
+  if ((a->signal_flag || a->n_signal_flags) && (!a->done_counter || !a->epoch)) return -12;
+  if (a->rs_ranks < 0 || a->rs_ranks > 8 || a->n_signal_flags < 0 || a->n_signal_flags > 8 || (a->rs_ranks && a->rs_rows_per_rank <= 0)) return -16;
   if (a->wait_flag && !a->epoch) return -12;
   if (a->swap) {
     if (a->dual) {

@@ -340,6 +340,15 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint4* __restric
   }
 }
 
+// One thread waits (bounded) for a peer's flag so that plain kernels launched after it in the
+// stream may read what the peer wrote.
+__global__ void wait_flag_kernel(const uint32_t* flag, const uint32_t* epoch, uint32_t* status) {
+  pdl_wait();
+  pdl_trigger();
+  wait_flag_ge(flag, *epoch, status);
+  __threadfence_system();
+}
+
 }  // namespace cafd
 
 using namespace cafd;
@@ -419,6 +428,11 @@ int cafd_moe_combine(const void* buf, const float* w, const void* shared_out, co
   launch_pdl(moe_combine_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(s), 
       static_cast<const uint4*>(buf), w, static_cast<const uint4*>(shared_out), static_cast<const uint4*>(residual),
       static_cast<uint4*>(out), T, top_k, H / 8, flags, n_flags, epoch, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cafd_wait_flag(const uint32_t* flag, const uint32_t* epoch, uint32_t* status, cafd_stream_t s) {
+  launch_pdl(wait_flag_kernel, dim3(1), dim3(1), 0, static_cast<cudaStream_t>(s), flag, epoch, status);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -1,0 +1,155 @@
+// Tensor-parallel collectives fused with their neighbours, over NVLink peer memory.
+//
+//   GEMM -> reduce-scatter : the row-parallel GEMM's epilogue (gemm_tcgen05.cu, rs_out) stores each
+//                            output row into the receive buffer of the rank that owns the row and
+//                            raises that rank's flag; no separate collective runs.
+//   reduce + residual + RMSNorm + all-gather (this file): the owner waits for every rank's flag,
+//                            adds the partial rows in rank order in fp32 (same bits on every
+//                            rank), adds the residual, rounds once, normalises, and stores the
+//                            normalised rows into every rank's activation buffer; then raises the
+//                            flag the next column-parallel GEMM waits on (all-gather -> GEMM).
+//
+// Rows of the residual stream are sharded over the tensor-parallel ranks (rank r owns rows
+// [r * rows_per_rank, ...)), so nothing here is replicated work.
+//
+// Reference counterpart: push partial to peer + wait + ordered add + fused norm
+// (native/shared/cuda/peer_exchange.cu:69-263, cuteafd_peer_add_bf16_async; "projection_norm"
+// program in rust/crates/cuteafd-daemon/src/families/glm5/engine.rs:2187-2192), degree 2 only.
+#include "cafd_api.h"
+#include "common.cuh"
+
+namespace cafd {
+
+struct TpReduceDev {
+  const __nv_bfloat16* partials;    // [ranks][rows_per_rank][N], this rank's receive buffer
+  __nv_bfloat16* residual;          // [rows_per_rank][N] owned rows of the residual stream (in/out)
+  const __nv_bfloat16* norm_w;      // [N]
+  __nv_bfloat16* x_out[8];          // every rank's gathered activation buffer [ranks * rows_per_rank][N]
+  const uint32_t* rs_flags;         // [ranks] raised by the producers' GEMMs
+  uint32_t* ag_flags[8];            // per destination rank: word this rank raises there
+  const uint32_t* epoch;
+  uint32_t* done_counter;
+  uint32_t* status;
+  int ranks, my_rank, rows_per_rank, rows_valid, N;
+  float eps;
+};
+
+__global__ void __launch_bounds__(256) tp_reduce_norm_gather_kernel(const TpReduceDev p) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ int s_ok;
+  __shared__ float red[8];
+  if (threadIdx.x == 0) {
+    bool ok = true;
+    const uint32_t ep = *p.epoch;
+    for (int r = 0; r < p.ranks && ok; ++r) ok = wait_flag_ge(p.rs_flags + r, ep, p.status);
+    s_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const int nvec = p.N / 8;
+  for (int row = blockIdx.x; row < p.rows_valid; row += gridDim.x) {
+    float ss = 0.f;
+    // pass 1: ordered sum + residual, rounded once to bf16 and written back as the new residual
+    for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+      float acc[8];
+      {
+        const uint4 v = *reinterpret_cast<const uint4*>(p.residual + static_cast<size_t>(row) * p.N + c * 8);
+        const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { acc[2 * e] = bf16_lo(q[e]); acc[2 * e + 1] = bf16_hi(q[e]); }
+      }
+      for (int r = 0; r < p.ranks; ++r) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p.partials + (static_cast<size_t>(r) * p.rows_per_rank + row) * p.N + c * 8);
+        const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { acc[2 * e] += bf16_lo(q[e]); acc[2 * e + 1] += bf16_hi(q[e]); }
+      }
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        o[e] = pack_bf16(acc[2 * e], acc[2 * e + 1]);
+        const float a = bf16_lo(o[e]), b = bf16_hi(o[e]);
+        ss += a * a + b * b;
+      }
+      *reinterpret_cast<uint4*>(p.residual + static_cast<size_t>(row) * p.N + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    ss = warp_sum(ss);
+    __syncthreads();                 // the previous row's use of `red` is over
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < static_cast<int>(blockDim.x >> 5); ++i) tot += red[i];
+    const float inv = rsqrtf(tot / static_cast<float>(p.N) + p.eps);
+    // pass 2: normalise the rounded residual and store it to every rank (all-gather by push)
+    const size_t grow = static_cast<size_t>(p.my_rank) * p.rows_per_rank + row;
+    for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+      const uint4 hv = *reinterpret_cast<const uint4*>(p.residual + static_cast<size_t>(row) * p.N + c * 8);
+      const uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + c * 8);
+      const uint32_t hq[4] = {hv.x, hv.y, hv.z, hv.w}, wq[4] = {wv.x, wv.y, wv.z, wv.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        o[e] = pack_bf16(bf16_lo(hq[e]) * inv * bf16_lo(wq[e]), bf16_hi(hq[e]) * inv * bf16_hi(wq[e]));
+      const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+      for (int r = 0; r < p.ranks; ++r)
+        *reinterpret_cast<uint4*>(p.x_out[r] + grow * p.N + c * 8) = ov;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(p.done_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.done_counter = 0;
+      __threadfence_system();
+      const uint32_t ep = *p.epoch;
+      for (int r = 0; r < p.ranks; ++r) st_release_sys(p.ag_flags[r], ep);
+    }
+  }
+}
+
+}  // namespace cafd
+
+using namespace cafd;
+
+extern "C" {
+
+typedef struct {
+  const void* partials;
+  void* residual;
+  const void* norm_w;
+  void* x_out[8];
+  const uint32_t* rs_flags;
+  uint32_t* ag_flags[8];
+  const uint32_t* epoch;
+  uint32_t* done_counter;
+  uint32_t* status;
+  int ranks, my_rank, rows_per_rank, rows_valid, N;
+  float eps;
+} cafd_tp_reduce_args;
+
+int cafd_tp_reduce_norm_gather(const cafd_tp_reduce_args* a, cafd_stream_t s) {
+  if (!a || a->ranks < 1 || a->ranks > 8 || a->N % 8 || a->rows_valid > a->rows_per_rank) return -10;
+  TpReduceDev p;
+  p.partials = static_cast<const __nv_bfloat16*>(a->partials);
+  p.residual = static_cast<__nv_bfloat16*>(a->residual);
+  p.norm_w = static_cast<const __nv_bfloat16*>(a->norm_w);
+  for (int r = 0; r < 8; ++r) {
+    p.x_out[r] = static_cast<__nv_bfloat16*>(a->x_out[r]);
+    p.ag_flags[r] = a->ag_flags[r];
+  }
+  p.rs_flags = a->rs_flags;
+  p.epoch = a->epoch;
+  p.done_counter = a->done_counter;
+  p.status = a->status;
+  p.ranks = a->ranks; p.my_rank = a->my_rank; p.rows_per_rank = a->rows_per_rank; p.rows_valid = a->rows_valid; p.N = a->N;
+  p.eps = a->eps;
+  int blocks = a->rows_valid < 1 ? 1 : (a->rows_valid > 1184 ? 1184 : a->rows_valid);
+  launch_pdl(tp_reduce_norm_gather_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(s), p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"
+
+CAFD_WAIT_LIMIT_SETTER(cafd_tp_set_wait_limit_ns)

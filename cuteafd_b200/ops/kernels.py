@@ -241,6 +241,11 @@ def route_topk(logits: torch.Tensor, top_k: int, scoring: str = "softmax", bias:
     return out_idx, out_w
 
 
+def wait_flag(flag_ptr: int, epoch: torch.Tensor) -> None:
+    """Stream-ordered bounded wait until *flag >= *epoch (a peer GPU writes the flag)."""
+    _n.check(_n.cuda_lib().cafd_wait_flag(flag_ptr, epoch.data_ptr(), status_word(epoch.device).data_ptr(), _stream()), "wait_flag")
+
+
 def moe_meta_ints(max_tiles: int, max_rows: int) -> int:
     return _n.cuda_lib().cafd_moe_meta_ints(max_tiles, max_rows)
 

@@ -90,6 +90,30 @@ class ExpertSide:
                          signal_flag=combine_flag_ptr, done_counter=self.done[0:1] if combine_flag_ptr else None)
 
 
+    def run_fp8(self, w_gate, w_up, w_down, tile_rows: int, rows: int, layer: int, epoch: torch.Tensor, combine_ptr: int,
+                combine_flag_ptr: int | None, wait: bool) -> None:
+        """E4M3 experts: ``w_*`` = (values [E, N, K], scales [E, N/128, K/128]).  Received rows and the
+        fc1 output are quantised 1x128 here, next to the GEMMs that consume them."""
+        g = self.geo
+        if not hasattr(self, "slab_q"):
+            dev = self.slab.device
+            self.slab_q = torch.zeros(g.max_rows, g.hidden, dtype=torch.float8_e4m3fn, device=dev)
+            self.slab_s = torch.ones(g.max_rows, g.hidden // 128, dtype=torch.float32, device=dev)
+            self.h_q = torch.zeros(g.max_rows, g.expert_ffn, dtype=torch.float8_e4m3fn, device=dev)
+            self.h_s = torch.ones(g.max_rows, g.expert_ffn // 128, dtype=torch.float32, device=dev)
+        rows = min(rows, g.max_rows)
+        if wait:
+            K.wait_flag(self.flags.data_ptr() + 4 * layer, epoch)
+        K.quant_rows_fp8(self.slab[:rows], self.slab_q[:rows], self.slab_s[:rows])
+        K.grouped_linear_fp8(self.slab_q, self.slab_s, w_gate[0], w_gate[1], self.hbuf, self.tile_expert, self.tile_row0,
+                             self.num_tiles, g.max_tiles, tile_rows, w_up=w_up[0], ws_up=w_up[1])
+        K.quant_rows_fp8(self.hbuf[:rows], self.h_q[:rows], self.h_s[:rows])
+        K.grouped_linear_fp8(self.h_q, self.h_s, w_down[0], w_down[1], self.hbuf, self.tile_expert, self.tile_row0,
+                             self.num_tiles, g.max_tiles, tile_rows, row_dst=self.row_dst, out_ptr=combine_ptr, ldo=g.hidden,
+                             epoch=epoch, signal_flag=combine_flag_ptr,
+                             done_counter=self.done[0:1] if combine_flag_ptr else None)
+
+
 class AttentionSide:
     """Buffers the attention rank owns: routes, plan output, the combine buffer and its flags."""
 
