@@ -1,0 +1,353 @@
+// Absorbed multi-head latent attention (MLA) over the paged latent cache on tcgen05 tensor cores.
+//
+// Every head attends to the same cached record per token, [512 latent | 64 rope] bf16, so the
+// query rows of one kernel tile are (token, head) pairs: 128 rows = 128 / heads tokens x heads.
+// Scores use all 576 dimensions (q_nope already multiplied by W_uk, q_rope rotated); the output
+// is the probability-weighted sum of the 512 latent dimensions (W_uv is applied afterwards).
+// One kernel serves decode rows, speculative-verify rows and prefill chunks; a split over the
+// KV range plus a fixed-order merge covers the decode case with few rows.
+//
+//   grid (row block, half of the 512 output dims, kv split)       192 threads
+//   warp 0   TMA: the 128 x 576 query block once (9 swizzle atoms), then 32-token KV tiles
+//            (9 atoms each, two stages) straight from the page pool
+//   warp 1   MMA: S = Q C^T (36 steps of 128x32x16), O += P V with V = the CTA's 256 latent
+//            columns read MN-major from the same tile (2 steps of 128x256x16)
+//   warps 2-5 softmax: thread = row; P goes to shared memory in the unswizzled canonical layout
+// TMEM: S double-buffered (2 x 32 columns) + O (256 columns).
+//
+// Reference counterparts: SIMT absorbed/sparse MLA kernels and the LSE state merge
+// (native/shared/cuda/attention.cu:249-925), compose of the absorbed query
+// (native/shared/cuda/mla_indexing.cu:46), and the exported b12x sparse_mla programs.
+#include "cafd_api.h"
+#include "common.cuh"
+#include "host_tma.h"
+
+namespace cafd {
+
+constexpr int kLat = 512, kRope = 64, kRec = kLat + kRope;     // 576 cached dims per token
+constexpr int kAtoms = kRec / 64;                             // 9 swizzle atoms along the record
+constexpr int kMlaRows = 128;
+constexpr int kKvTile = 32;
+constexpr int kQBytes = kAtoms * kMlaRows * 128;              // 147456
+constexpr int kKvBytes = kAtoms * kKvTile * 128;              // 36864
+constexpr int kPBytes = kMlaRows * kKvTile * 2;               // 8192
+constexpr int kMlaSmem = kQBytes + 2 * kKvBytes + kPBytes + 1024;
+constexpr int kMlaThreads = 192;
+constexpr int kHalf = 256;                                    // output columns per CTA
+constexpr int kMlaPartial = kMlaRows * kHalf + 2 * kMlaRows;  // floats per (block, half, split)
+
+struct MlaDev {
+  const int* page_table;
+  const int* seq_lens;
+  const int* q_start;      // token offsets per sequence [S + 1]
+  const int* block_seq;    // per row block: sequence index
+  const int* block_tok0;   // per row block: first query token (within the sequence's new tokens)
+  __nv_bfloat16* out;      // [rows, 512]
+  float* partial;
+  uint32_t* status;
+  int max_pages, heads, splits;
+  float scale_log2;
+};
+
+// Shared-memory descriptor without swizzle (canonical K-major "interleave" layout): 8x16-byte core
+// matrices, `lbo` bytes between the two cores along K, `sbo` bytes between 8-row groups.
+__device__ __forceinline__ uint64_t smem_desc_k_noswz(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+
+__global__ void __launch_bounds__(kMlaThreads, 1)
+mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_c, const MlaDev p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sC = smem + kQBytes;                 // two stages
+  uint8_t* sP = smem + kQBytes + 2 * kKvBytes;
+
+  __shared__ uint64_t q_full, c_full[2], c_empty[2], s_full[2], s_empty[2], p_ready, pv_done;
+  __shared__ uint32_t tmem_slot;
+
+  pdl_wait();
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int blk = blockIdx.x, dh = blockIdx.y, split = blockIdx.z;
+  const int seq = p.block_seq[blk];
+  const int tok0 = p.block_tok0[blk];
+  const int q0 = p.q_start[seq], q_len = p.q_start[seq + 1] - q0;
+  const int kv_len = p.seq_lens[seq];
+  const int tok_per_blk = kMlaRows / p.heads;
+  // visible kv positions for the last valid token of this block
+  const int last_tok = min(tok0 + tok_per_blk, q_len) - 1;
+  const int max_limit = kv_len - q_len + last_tok + 1;
+  const int total_tiles = (max_limit + kKvTile - 1) / kKvTile;
+  const int per_split = (total_tiles + p.splits - 1) / p.splits;
+  const int t_begin = split * per_split;
+  const int t_end = min(total_tiles, t_begin + per_split);
+  const int n_tiles = max(0, t_end - t_begin);
+  const int seq_pages = (kv_len + 63) / 64;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&c_full[i], 1); mbar_init(&c_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128);
+    }
+    mbar_init(&p_ready, 128);
+    mbar_init(&pv_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t tS = tmem;          // + 32 * buffer
+  const uint32_t tO = tmem + 64;
+
+  if (warp == 0) {
+    if (lane == 0 && n_tiles > 0) {
+      tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_c);
+      mbar_expect_tx(&q_full, kQBytes);
+      const int qrow = (q0 + tok0) * p.heads;
+      for (int a = 0; a < kAtoms; ++a) tma_load_2d(sQ + a * kMlaRows * 128, &tm_q, &q_full, a * 64, qrow);
+      const int* pt = p.page_table + static_cast<size_t>(seq) * p.max_pages;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int tile = t_begin + j;
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int pg_i = tile >> 1;
+        const int page = pg_i < seq_pages ? pt[pg_i] : 0;
+        if (!mbar_wait(&c_empty[st], ph ^ 1, p.status, kTimeoutEmptyBarrier)) break;
+        uint8_t* cd = sC + st * kKvBytes;
+        mbar_expect_tx(&c_full[st], kKvBytes);
+        for (int a = 0; a < kAtoms; ++a) tma_load_3d(cd + a * kKvTile * 128, &tm_c, &c_full[st], a * 64, (tile & 1) * kKvTile, page);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_qk = make_idesc(128, kKvTile, 1, 1, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc(128, kHalf, 1, 1, 0, 1);      // B = V is MN-major
+      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+      bool ok = mbar_wait(&q_full, 0, p.status, kTimeoutFullBarrier);
+      auto issue_qk = [&](int j) -> bool {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&c_full[st], ph, p.status, kTimeoutFullBarrier)) return false;
+        if (!mbar_wait(&s_empty[st], ph ^ 1, p.status, kTimeoutTmemEmpty)) return false;
+        tc_fence_after();
+        const uint32_t aC = smem_u32(sC + st * kKvBytes);
+#pragma unroll 1
+        for (int a = 0; a < kAtoms; ++a)
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            umma_f16(tS + st * 32, smem_desc_k_sw128(aQ + a * kMlaRows * 128 + k4 * 32),
+                     smem_desc_k_sw128(aC + a * kKvTile * 128 + k4 * 32), idesc_qk, (a | k4) ? 1u : 0u);
+        umma_commit(&s_full[st]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (j + 1 < n_tiles) { if (!issue_qk(j + 1)) { ok = false; break; } }
+        const int st = j & 1;
+        if (!mbar_wait(&p_ready, j & 1, p.status, kTimeoutSoftmax)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aV = smem_u32(sC + st * kKvBytes) + dh * 4 * (kKvTile * 128);
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+          // A = P rows, K cores ks*2 and ks*2+1 (128 bytes apart), 8-row groups 512 bytes apart
+          // B = V: 16 kv rows per step (2 KiB), 64-column blocks 4 KiB apart, 8-row groups 1 KiB apart
+          umma_f16(tO, smem_desc_k_noswz(aP + ks * 256, 128, 512), smem_desc_mn_sw128(aV + ks * 2048, kKvTile * 128),
+                   idesc_pv, (j | ks) ? 1u : 0u);
+        }
+        umma_commit(&c_empty[st]);
+        umma_commit(&pv_done);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int ti = row / p.heads;
+    const bool row_valid = (tok0 + ti) < q_len;
+    const int limit = row_valid ? (kv_len - q_len + tok0 + ti + 1) : 0;
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; ok && j < n_tiles; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(&s_full[st], ph, p.status, kTimeoutTmemFull)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t r[32];
+      tmem_ld_32x32(tS + st * 32 + lane_off, r);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&s_empty[st]);
+      const int col0 = (t_begin + j) * kKvTile;
+      float mx = -INFINITY;
+      float s[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        s[i] = (col0 + i < limit) ? __uint_as_float(r[i]) * p.scale_log2 : -INFINITY;
+        mx = fmaxf(mx, s[i]);
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float base = (m_new == -INFINITY) ? 0.f : m_new;
+      const float corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - base);
+      if (j > 0) {
+        if (!mbar_wait(&pv_done, (j - 1) & 1, p.status, kTimeoutTmemFull)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll 1
+          for (int c = 0; c < kHalf; c += 32) {
+            uint32_t o[32];
+            tmem_ld_32x32(tO + lane_off + c, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+            tmem_st_32x32(tO + lane_off + c, o);
+          }
+        }
+      }
+      float rs = 0.f;
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const uint32_t w = pack_bf16(exp2f(s[i] - base), exp2f(s[i + 1] - base));
+        rs += bf16_lo(w) + bf16_hi(w);
+        pk[i >> 1] = w;
+      }
+      // canonical unswizzled K-major layout: core (row / 8, k / 8) at (row/8)*512 + (k/8)*128, rows 16 B apart
+      uint8_t* prow = sP + (row >> 3) * 512 + (row & 7) * 16;
+#pragma unroll
+      for (int kc = 0; kc < 4; ++kc)
+        *reinterpret_cast<uint4*>(prow + kc * 128) = make_uint4(pk[4 * kc], pk[4 * kc + 1], pk[4 * kc + 2], pk[4 * kc + 3]);
+      l_run = l_run * corr + rs;
+      m_run = m_new;
+      tmem_st_wait();
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&p_ready);
+    }
+    // ---- epilogue ------------------------------------------------------------------------------------
+    bool have = n_tiles > 0 && ok;
+    if (have) have = mbar_wait(&pv_done, (n_tiles - 1) & 1, p.status, kTimeoutTmemFull);
+    tc_fence_after();
+    const size_t grow = static_cast<size_t>(q0 + tok0) * p.heads + row;
+    if (p.splits == 1) {
+      if (row_valid) {
+        const float inv = (have && l_run > 0.f) ? 1.0f / l_run : 0.f;
+        __nv_bfloat16* orow = p.out + grow * kLat + dh * kHalf;
+#pragma unroll 1
+        for (int c = 0; c < kHalf; c += 32) {
+          uint32_t o[32];
+          if (have) { tmem_ld_32x32(tO + lane_off + c, o); tmem_ld_wait(); }
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 q;
+            q.x = pack_bf16(have ? __uint_as_float(o[i]) * inv : 0.f, have ? __uint_as_float(o[i + 1]) * inv : 0.f);
+            q.y = pack_bf16(have ? __uint_as_float(o[i + 2]) * inv : 0.f, have ? __uint_as_float(o[i + 3]) * inv : 0.f);
+            q.z = pack_bf16(have ? __uint_as_float(o[i + 4]) * inv : 0.f, have ? __uint_as_float(o[i + 5]) * inv : 0.f);
+            q.w = pack_bf16(have ? __uint_as_float(o[i + 6]) * inv : 0.f, have ? __uint_as_float(o[i + 7]) * inv : 0.f);
+            *reinterpret_cast<uint4*>(orow + c + i) = q;
+          }
+        }
+      }
+    } else {
+      float* part = p.partial + ((static_cast<size_t>(blk) * 2 + dh) * p.splits + split) * kMlaPartial;
+#pragma unroll 1
+      for (int c = 0; c < kHalf; c += 32) {
+        uint32_t o[32];
+        if (have) { tmem_ld_32x32(tO + lane_off + c, o); tmem_ld_wait(); }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) part[static_cast<size_t>(c + i) * kMlaRows + row] = have ? __uint_as_float(o[i]) : 0.f;
+      }
+      part[kMlaRows * kHalf + row] = have ? m_run : -INFINITY;
+      part[kMlaRows * kHalf + kMlaRows + row] = have ? l_run : 0.f;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// One block per (row block, half, row): thread c walks the splits in order for its output column.
+__global__ void __launch_bounds__(256) mla_merge_kernel(const float* __restrict__ partial, const int* __restrict__ block_seq,
+                                                        const int* __restrict__ block_tok0, const int* __restrict__ q_start,
+                                                        __nv_bfloat16* __restrict__ out, int heads, int splits) {
+  pdl_wait();
+  pdl_trigger();
+  const int blk = blockIdx.x, dh = blockIdx.y, row = blockIdx.z, c = threadIdx.x;
+  const int seq = block_seq[blk], tok0 = block_tok0[blk];
+  const int q0 = q_start[seq], q_len = q_start[seq + 1] - q0;
+  if (tok0 + row / heads >= q_len) return;
+  const float* base = partial + (static_cast<size_t>(blk) * 2 + dh) * splits * kMlaPartial;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, __ldg(base + static_cast<size_t>(s) * kMlaPartial + kMlaRows * kHalf + row));
+  float L = 0.f, O = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float* ps = base + static_cast<size_t>(s) * kMlaPartial;
+    const float m = __ldg(ps + kMlaRows * kHalf + row);
+    const float f = (m == -INFINITY) ? 0.f : exp2f(m - M);
+    L += __ldg(ps + kMlaRows * kHalf + kMlaRows + row) * f;
+    O += __ldg(ps + static_cast<size_t>(c) * kMlaRows + row) * f;
+  }
+  out[(static_cast<size_t>(q0 + tok0) * heads + row) * kLat + dh * kHalf + c] = __float2bfloat16(L > 0.f ? O / L : 0.f);
+}
+
+}  // namespace cafd
+
+using namespace cafd;
+
+extern "C" long long cafd_mla_scratch_floats(int n_blocks, int splits) {
+  return static_cast<long long>(n_blocks) * 2 * splits * kMlaPartial;
+}
+
+// q [rows, 576] bf16 with rows = (token, head) pairs (head fastest); cache [num_pages, 64, 576] bf16 with
+// page 0 all zero; block_seq / block_tok0 [n_blocks] describe each 128-row block (128 / heads tokens);
+// out [rows, 512] bf16.  heads must divide 128.
+extern "C" int cafd_mla_attention(const void* q, const void* cache, const int* page_table, const int* seq_lens,
+                                  const int* q_start, const int* block_seq, const int* block_tok0, void* out,
+                                  float* scratch, uint32_t* status, long long total_rows, int n_blocks, int num_pages,
+                                  int max_pages, int heads, int splits, float scale, cafd_stream_t s) {
+  if (n_blocks <= 0) return 0;
+  if (heads <= 0 || kMlaRows % heads) return -10;
+  if (splits < 1) splits = 1;
+  if (splits > 1 && !scratch) return -12;
+  CUtensorMap tq, tc;
+  int rc = cached_tmap_2d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, total_rows, kRec, kRec * 2, kMlaRows, 64);
+  if (rc) return rc;
+  const uint64_t dims[3] = {static_cast<uint64_t>(kRec), 64, static_cast<uint64_t>(num_pages)};
+  const uint64_t strides[2] = {static_cast<uint64_t>(kRec) * 2, static_cast<uint64_t>(64) * kRec * 2};
+  const uint32_t box[3] = {64, kKvTile, 1};
+  rc = make_tmap_nd(&tc, cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, true);
+  if (rc) return rc;
+  MlaDev p;
+  p.page_table = page_table; p.seq_lens = seq_lens; p.q_start = q_start; p.block_seq = block_seq; p.block_tok0 = block_tok0;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.partial = scratch;
+  p.status = status;
+  p.max_pages = max_pages; p.heads = heads; p.splits = splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  static bool attr = false;
+  if (!attr) {
+    CAFD_CHECK_CUDA(cudaFuncSetAttribute(mla_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));
+    attr = true;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(s);
+  launch_pdl(mla_attn_kernel, dim3(n_blocks, 2, splits), dim3(kMlaThreads), kMlaSmem, st, tq, tc, p);
+  if (splits > 1)
+    launch_pdl(mla_merge_kernel, dim3(n_blocks, 2, kMlaRows), dim3(kHalf), 0, st, static_cast<const float*>(scratch), block_seq,
+               block_tok0, q_start, static_cast<__nv_bfloat16*>(out), heads, splits);
+  return static_cast<int>(cudaGetLastError());
+}
+
+CAFD_WAIT_LIMIT_SETTER(cafd_mla_set_wait_limit_ns)

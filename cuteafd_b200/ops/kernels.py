@@ -317,6 +317,39 @@ def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     return out
 
 
+def mla_blocks(q_lens: list[int], heads: int) -> tuple[list[int], list[int]]:
+    """Row-block table for ``mla_attention``: every block covers 128 / heads query tokens of one sequence."""
+    per = 128 // heads
+    seqs, toks = [], []
+    for s, n in enumerate(q_lens):
+        for t0 in range(0, n, per):
+            seqs.append(s)
+            toks.append(t0)
+    return seqs, toks
+
+
+def mla_scratch_floats(n_blocks: int, splits: int) -> int:
+    return int(_n.cuda_lib().cafd_mla_scratch_floats(n_blocks, splits))
+
+
+def mla_attention(q_abs: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor, seq_lens: torch.Tensor,
+                  q_start: torch.Tensor, block_seq: torch.Tensor, block_tok0: torch.Tensor, out: torch.Tensor,
+                  scale: float, splits: int = 1, scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """Absorbed MLA: q_abs [tokens, heads, 576] (512 latent-projected + 64 rope), cache [pages, 64, 576]
+    (page 0 zero), out [tokens, heads, 512] = softmax(q c^T * scale) c[:, :512] with the causal rule
+    that query token i of a sequence sees kv positions <= seq_len - q_len + i."""
+    T, heads, rec = q_abs.shape
+    assert rec == 576 and 128 % heads == 0 and q_abs.is_contiguous() and out.is_contiguous() and cache.is_contiguous()
+    num_pages = cache.shape[0]
+    _, max_pages = page_table.shape
+    _n.check(_n.cuda_lib().cafd_mla_attention(q_abs.data_ptr(), cache.data_ptr(), page_table.data_ptr(), seq_lens.data_ptr(),
+                                              q_start.data_ptr(), block_seq.data_ptr(), block_tok0.data_ptr(), out.data_ptr(),
+                                              _ptr(scratch), status_word(q_abs.device).data_ptr(), T * heads,
+                                              block_seq.numel(), num_pages, max_pages, heads, splits, scale, _stream()),
+             "mla_attention")
+    return out
+
+
 # ---- FP8 block-scaled GEMM -----------------------------------------------------------------------------
 def quant_rows_fp8(x: torch.Tensor, q: torch.Tensor | None = None, s: torch.Tensor | None = None):
     """bf16 [T, K] -> (E4M3 [T, K], fp32 scales [T, K/128]); scale = amax/448 per row and 128 columns."""

@@ -1,0 +1,83 @@
+"""Absorbed MLA attention kernel (tcgen05, paged latent cache) against fp32 PyTorch math."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from cuteafd_b200.ops import kernels
+    return kernels
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _latent_cache(lens, seed=0):
+    """Random paged latent cache; returns (cache [pages,64,576], table, dense list of [len,576])."""
+    g = torch.Generator().manual_seed(seed)
+    S = len(lens)
+    max_pages = max((n + 63) // 64 for n in lens) + 1
+    total = 1 + sum((n + 63) // 64 for n in lens)
+    cache = torch.zeros(total, 64, 576, dtype=torch.bfloat16)
+    table = torch.zeros(S, max_pages, dtype=torch.int32)
+    perm = (torch.randperm(total - 1, generator=g) + 1).tolist()
+    dense, nxt = [], 0
+    for s, n in enumerate(lens):
+        c = (torch.randn(n, 576, generator=g) * 0.5).to(torch.bfloat16)
+        dense.append(c)
+        for pi in range((n + 63) // 64):
+            pg = perm[nxt]; nxt += 1
+            table[s, pi] = pg
+            rows = c[pi * 64:(pi + 1) * 64]
+            cache[pg, :rows.shape[0]] = rows
+    return cache.to(_dev()), table.to(_dev()), dense
+
+
+def _ref(q, c, prior, scale):
+    """q [n, heads, 576], c [len, 576] fp32 math; token i sees positions <= prior + i."""
+    n = q.shape[0]
+    s = torch.einsum("nhd,ld->nhl", q.float(), c.float()) * scale
+    pos = torch.arange(c.shape[0])[None, None, :]
+    lim = (prior + torch.arange(n))[:, None, None]
+    s = s.masked_fill(pos > lim, float("-inf"))
+    return torch.einsum("nhl,ld->nhd", torch.softmax(s, -1), c[:, :512].float())
+
+
+@pytest.mark.parametrize("heads,lens,qlens,splits", [
+    (16, [100], [1], 1),
+    (16, [700, 64, 1, 333], [1, 1, 1, 1], 4),
+    (128, [65, 2000], [1, 1], 8),
+    (64, [300], [300], 1),
+    (16, [517, 130], [517, 66], 1),
+    (128, [200], [3], 2),
+    (32, [1000, 40], [5, 40], 3),
+])
+def test_mla_attention(K, heads, lens, qlens, splits):
+    cache, table, dense = _latent_cache(lens, seed=heads + len(lens))
+    g = torch.Generator().manual_seed(7)
+    T = sum(qlens)
+    q = (torch.randn(T, heads, 576, generator=g) * 0.5).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(192)
+    bs, bt = K.mla_blocks(qlens, heads)
+    dev = _dev()
+    i32 = dict(dtype=torch.int32, device=dev)
+    q_start = torch.tensor([0] + torch.tensor(qlens).cumsum(0).tolist(), **i32)
+    out = torch.full((T, heads, 512), 7.0, dtype=torch.bfloat16, device=dev)
+    scratch = torch.empty(K.mla_scratch_floats(len(bs), splits), dtype=torch.float32, device=dev) if splits > 1 else None
+    for _ in range(2):                      # twice: barriers, TMEM and scratch are reused cleanly
+        K.mla_attention(q.to(dev), cache, table, torch.tensor(lens, **i32), q_start, torch.tensor(bs, **i32),
+                        torch.tensor(bt, **i32), out, scale, splits, scratch)
+    torch.cuda.synchronize()
+    assert K.read_status() == 0
+    o = 0
+    for s, n in enumerate(qlens):
+        ref = _ref(q[o:o + n], dense[s], lens[s] - n, scale)
+        got = out[o:o + n].float().cpu()
+        err = (got - ref).abs().max().item()
+        assert err < 0.03 * max(1.0, ref.abs().max().item()), (s, err)
+        o += n
