@@ -97,7 +97,11 @@ def cuda_lib():
         _sig(lib, "cafd_attn_decode", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
         _sig(lib, "cafd_attn_prefill", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
         _sig(lib, "cafd_mla_scratch_floats", [I, I], C.c_longlong)
-        _sig(lib, "cafd_mla_attention", [P, P, P, P, P, P, P, P, P, P, C.c_longlong, I, I, I, I, I, F, P])
+        _sig(lib, "cafd_mla_attention", [P, P, P, P, P, P, P, P, P, P, C.c_longlong, I, I, I, I, I, I, F, P])
+        _sig(lib, "cafd_mla_prep_a", [P, I, I, P, P, P, P, P, P, P, I, F, I, P])
+        _sig(lib, "cafd_sample_rows", [P, I, I, P, P, I, P, P, P])
+        _sig(lib, "cafd_accept_prefix", [P, P, P, I, P, P, P])
+        _sig(lib, "cafd_mla_q_split", [P, I, P, P, P, P, I, I, I, I, P])
         _cuda = lib
         return lib
 

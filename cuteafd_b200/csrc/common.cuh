@@ -90,6 +90,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
+    // a wait that already ran out elsewhere (this CTA or another) ends every later blocked wait at once
+    if (status && *reinterpret_cast<volatile uint32_t*>(status) != 0u) return false;
     if (globaltimer_ns() - t0 > limit) {
       if (status) atomicCAS(status, 0u, code);
       return false;

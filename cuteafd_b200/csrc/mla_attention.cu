@@ -45,7 +45,9 @@ struct MlaDev {
   __nv_bfloat16* out;      // [rows, 512]
   float* partial;
   uint32_t* status;
+  uint32_t* trace;         // optional progress words, 4 per CTA (producer, MMA, softmax, exit); host-mapped memory works
   int max_pages, heads, splits;
+  int out_tpad;            // 0: out rows are (token, head); > 0: head-major rows head * out_tpad + token
   float scale_log2;
 };
 
@@ -57,6 +59,10 @@ __device__ __forceinline__ uint64_t smem_desc_k_noswz(uint32_t addr, uint32_t lb
   d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32;
   d |= static_cast<uint64_t>(1) << 46;
   return d;
+}
+
+__device__ __forceinline__ void mla_trace(uint32_t* t, int slot, uint32_t v) {
+  if (t) { reinterpret_cast<volatile uint32_t*>(t)[slot] = v; __threadfence_system(); }
 }
 
 __global__ void __launch_bounds__(kMlaThreads, 1)
@@ -82,12 +88,13 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // visible kv positions for the last valid token of this block
   const int last_tok = min(tok0 + tok_per_blk, q_len) - 1;
   const int max_limit = kv_len - q_len + last_tok + 1;
-  const int total_tiles = (max_limit + kKvTile - 1) / kKvTile;
+  const int total_tiles = (tok0 < q_len && max_limit > 0) ? (max_limit + kKvTile - 1) / kKvTile : 0;   // block past the new tokens: idle
   const int per_split = (total_tiles + p.splits - 1) / p.splits;
   const int t_begin = split * per_split;
   const int t_end = min(total_tiles, t_begin + per_split);
   const int n_tiles = max(0, t_end - t_begin);
   const int seq_pages = (kv_len + 63) / 64;
+  uint32_t* tr = p.trace ? p.trace + 4 * ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : nullptr;
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
@@ -116,6 +123,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_expect_tx(&q_full, kQBytes);
       const int qrow = (q0 + tok0) * p.heads;
       for (int a = 0; a < kAtoms; ++a) tma_load_2d(sQ + a * kMlaRows * 128, &tm_q, &q_full, a * 64, qrow);
+      mla_trace(tr, 0, 1);
       const int* pt = p.page_table + static_cast<size_t>(seq) * p.max_pages;
       for (int j = 0; j < n_tiles; ++j) {
         const int tile = t_begin + j;
@@ -127,6 +135,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint8_t* cd = sC + st * kKvBytes;
         mbar_expect_tx(&c_full[st], kKvBytes);
         for (int a = 0; a < kAtoms; ++a) tma_load_3d(cd + a * kKvTile * 128, &tm_c, &c_full[st], a * 64, (tile & 1) * kKvTile, page);
+        mla_trace(tr, 0, 100 + j);
       }
     }
   } else if (warp == 1) {
@@ -135,6 +144,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       constexpr uint32_t idesc_pv = make_idesc(128, kHalf, 1, 1, 0, 1);      // B = V is MN-major
       const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
       bool ok = mbar_wait(&q_full, 0, p.status, kTimeoutFullBarrier);
+      mla_trace(tr, 1, ok ? 1 : 2);
       auto issue_qk = [&](int j) -> bool {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
@@ -149,6 +159,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             umma_f16(tS + st * 32, smem_desc_k_sw128(aQ + a * kMlaRows * 128 + k4 * 32),
                      smem_desc_k_sw128(aC + a * kKvTile * 128 + k4 * 32), idesc_qk, (a | k4) ? 1u : 0u);
         umma_commit(&s_full[st]);
+        mla_trace(tr, 1, 100 + j);
         return true;
       };
       if (ok) ok = issue_qk(0);
@@ -167,6 +178,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         umma_commit(&c_empty[st]);
         umma_commit(&pv_done);
+        mla_trace(tr, 1, 10000 + j);
       }
     }
   } else {
@@ -183,6 +195,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t ph = (j >> 1) & 1;
       if (!mbar_wait(&s_full[st], ph, p.status, kTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
+      if (threadIdx.x == 64) mla_trace(tr, 2, 100 + j);
       uint32_t r[32];
       tmem_ld_32x32(tS + st * 32 + lane_off, r);
       tmem_ld_wait();
@@ -233,42 +246,47 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(&p_ready);
+      if (threadIdx.x == 64) mla_trace(tr, 2, 10000 + j);
     }
     // ---- epilogue ------------------------------------------------------------------------------------
     bool have = n_tiles > 0 && ok;
     if (have) have = mbar_wait(&pv_done, (n_tiles - 1) & 1, p.status, kTimeoutTmemFull);
     tc_fence_after();
-    const size_t grow = static_cast<size_t>(q0 + tok0) * p.heads + row;
+    const size_t grow = p.out_tpad > 0 ? static_cast<size_t>(row % p.heads) * p.out_tpad + (q0 + tok0 + ti)
+                                       : static_cast<size_t>(q0 + tok0) * p.heads + row;
     if (p.splits == 1) {
-      if (row_valid) {
-        const float inv = (have && l_run > 0.f) ? 1.0f / l_run : 0.f;
-        __nv_bfloat16* orow = p.out + grow * kLat + dh * kHalf;
+      // tcgen05.ld is warp-collective: every lane loads, only valid rows store
+      const float inv = (have && l_run > 0.f) ? 1.0f / l_run : 0.f;
+      __nv_bfloat16* orow = p.out + grow * kLat + dh * kHalf;
+      const bool any_have = __all_sync(0xffffffffu, have);
 #pragma unroll 1
-        for (int c = 0; c < kHalf; c += 32) {
-          uint32_t o[32];
-          if (have) { tmem_ld_32x32(tO + lane_off + c, o); tmem_ld_wait(); }
+      for (int c = 0; c < kHalf; c += 32) {
+        uint32_t o[32];
+        if (any_have) { tmem_ld_32x32(tO + lane_off + c, o); tmem_ld_wait(); }
+        if (row_valid) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 q;
-            q.x = pack_bf16(have ? __uint_as_float(o[i]) * inv : 0.f, have ? __uint_as_float(o[i + 1]) * inv : 0.f);
-            q.y = pack_bf16(have ? __uint_as_float(o[i + 2]) * inv : 0.f, have ? __uint_as_float(o[i + 3]) * inv : 0.f);
-            q.z = pack_bf16(have ? __uint_as_float(o[i + 4]) * inv : 0.f, have ? __uint_as_float(o[i + 5]) * inv : 0.f);
-            q.w = pack_bf16(have ? __uint_as_float(o[i + 6]) * inv : 0.f, have ? __uint_as_float(o[i + 7]) * inv : 0.f);
+            q.x = pack_bf16(any_have ? __uint_as_float(o[i]) * inv : 0.f, any_have ? __uint_as_float(o[i + 1]) * inv : 0.f);
+            q.y = pack_bf16(any_have ? __uint_as_float(o[i + 2]) * inv : 0.f, any_have ? __uint_as_float(o[i + 3]) * inv : 0.f);
+            q.z = pack_bf16(any_have ? __uint_as_float(o[i + 4]) * inv : 0.f, any_have ? __uint_as_float(o[i + 5]) * inv : 0.f);
+            q.w = pack_bf16(any_have ? __uint_as_float(o[i + 6]) * inv : 0.f, any_have ? __uint_as_float(o[i + 7]) * inv : 0.f);
             *reinterpret_cast<uint4*>(orow + c + i) = q;
           }
         }
       }
     } else {
       float* part = p.partial + ((static_cast<size_t>(blk) * 2 + dh) * p.splits + split) * kMlaPartial;
+      const bool have_all = __all_sync(0xffffffffu, have);
 #pragma unroll 1
       for (int c = 0; c < kHalf; c += 32) {
         uint32_t o[32];
-        if (have) { tmem_ld_32x32(tO + lane_off + c, o); tmem_ld_wait(); }
+        if (have_all) { tmem_ld_32x32(tO + lane_off + c, o); tmem_ld_wait(); }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) part[static_cast<size_t>(c + i) * kMlaRows + row] = have ? __uint_as_float(o[i]) : 0.f;
+        for (int i = 0; i < 32; ++i) part[static_cast<size_t>(c + i) * kMlaRows + row] = have_all ? __uint_as_float(o[i]) : 0.f;
       }
-      part[kMlaRows * kHalf + row] = have ? m_run : -INFINITY;
-      part[kMlaRows * kHalf + kMlaRows + row] = have ? l_run : 0.f;
+      part[kMlaRows * kHalf + row] = have_all ? m_run : -INFINITY;
+      part[kMlaRows * kHalf + kMlaRows + row] = have_all ? l_run : 0.f;
     }
   }
   tc_fence_before();
@@ -276,13 +294,14 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
+    if (lane == 0) mla_trace(tr, 3, 1000);
   }
 }
 
 // One block per (row block, half, row): thread c walks the splits in order for its output column.
 __global__ void __launch_bounds__(256) mla_merge_kernel(const float* __restrict__ partial, const int* __restrict__ block_seq,
                                                         const int* __restrict__ block_tok0, const int* __restrict__ q_start,
-                                                        __nv_bfloat16* __restrict__ out, int heads, int splits) {
+                                                        __nv_bfloat16* __restrict__ out, int heads, int splits, int out_tpad) {
   pdl_wait();
   pdl_trigger();
   const int blk = blockIdx.x, dh = blockIdx.y, row = blockIdx.z, c = threadIdx.x;
@@ -300,12 +319,18 @@ __global__ void __launch_bounds__(256) mla_merge_kernel(const float* __restrict_
     L += __ldg(ps + kMlaRows * kHalf + kMlaRows + row) * f;
     O += __ldg(ps + static_cast<size_t>(c) * kMlaRows + row) * f;
   }
-  out[(static_cast<size_t>(q0 + tok0) * heads + row) * kLat + dh * kHalf + c] = __float2bfloat16(L > 0.f ? O / L : 0.f);
+  const size_t grow = out_tpad > 0 ? static_cast<size_t>(row % heads) * out_tpad + (q0 + tok0 + row / heads)
+                                   : static_cast<size_t>(q0 + tok0) * heads + row;
+  out[grow * kLat + dh * kHalf + c] = __float2bfloat16(L > 0.f ? O / L : 0.f);
 }
 
 }  // namespace cafd
 
 using namespace cafd;
+
+static uint32_t* g_mla_trace = nullptr;
+// Progress words for debugging a stalled launch: 4 x uint32 per CTA (grid order x, y, z).  Null switches it off.
+extern "C" void cafd_mla_set_trace(uint32_t* words) { g_mla_trace = words; }
 
 extern "C" long long cafd_mla_scratch_floats(int n_blocks, int splits) {
   return static_cast<long long>(n_blocks) * 2 * splits * kMlaPartial;
@@ -313,11 +338,13 @@ extern "C" long long cafd_mla_scratch_floats(int n_blocks, int splits) {
 
 // q [rows, 576] bf16 with rows = (token, head) pairs (head fastest); cache [num_pages, 64, 576] bf16 with
 // page 0 all zero; block_seq / block_tok0 [n_blocks] describe each 128-row block (128 / heads tokens);
-// out [rows, 512] bf16.  heads must divide 128.
+// out [rows, 512] bf16, rows ordered like q, or head-major (row = head * out_tpad + token) when out_tpad > 0.
+// heads must divide 128.
 extern "C" int cafd_mla_attention(const void* q, const void* cache, const int* page_table, const int* seq_lens,
                                   const int* q_start, const int* block_seq, const int* block_tok0, void* out,
                                   float* scratch, uint32_t* status, long long total_rows, int n_blocks, int num_pages,
-                                  int max_pages, int heads, int splits, float scale, cafd_stream_t s) {
+                                  int max_pages, int heads, int splits, int out_tpad, float scale,
+                                  cafd_stream_t s) {
   if (n_blocks <= 0) return 0;
   if (heads <= 0 || kMlaRows % heads) return -10;
   if (splits < 1) splits = 1;
@@ -335,7 +362,8 @@ extern "C" int cafd_mla_attention(const void* q, const void* cache, const int* p
   p.out = static_cast<__nv_bfloat16*>(out);
   p.partial = scratch;
   p.status = status;
-  p.max_pages = max_pages; p.heads = heads; p.splits = splits;
+  p.trace = g_mla_trace;
+  p.max_pages = max_pages; p.heads = heads; p.splits = splits; p.out_tpad = out_tpad;
   p.scale_log2 = scale * 1.4426950408889634f;
   static bool attr = false;
   if (!attr) {
@@ -346,7 +374,7 @@ extern "C" int cafd_mla_attention(const void* q, const void* cache, const int* p
   launch_pdl(mla_attn_kernel, dim3(n_blocks, 2, splits), dim3(kMlaThreads), kMlaSmem, st, tq, tc, p);
   if (splits > 1)
     launch_pdl(mla_merge_kernel, dim3(n_blocks, 2, kMlaRows), dim3(kHalf), 0, st, static_cast<const float*>(scratch), block_seq,
-               block_tok0, q_start, static_cast<__nv_bfloat16*>(out), heads, splits);
+               block_tok0, q_start, static_cast<__nv_bfloat16*>(out), heads, splits, out_tpad);
   return static_cast<int>(cudaGetLastError());
 }
 

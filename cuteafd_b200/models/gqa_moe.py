@@ -137,6 +137,11 @@ class KvCache:
     def bytes_per_page(self) -> int:
         return 2 * len(self.k) * self.k[0][0].numel() * 2
 
+    def copy_page(self, src: int, dst: int) -> None:
+        for k, v in zip(self.k, self.v):
+            k[dst].copy_(k[src])
+            v[dst].copy_(v[src])
+
 
 class Workspace:
     def __init__(self, cfg: ModelConfig, max_tokens: int, device: torch.device):

@@ -334,10 +334,11 @@ def mla_scratch_floats(n_blocks: int, splits: int) -> int:
 
 def mla_attention(q_abs: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor, seq_lens: torch.Tensor,
                   q_start: torch.Tensor, block_seq: torch.Tensor, block_tok0: torch.Tensor, out: torch.Tensor,
-                  scale: float, splits: int = 1, scratch: torch.Tensor | None = None) -> torch.Tensor:
+                  scale: float, splits: int = 1, scratch: torch.Tensor | None = None, out_tpad: int = 0) -> torch.Tensor:
     """Absorbed MLA: q_abs [tokens, heads, 576] (512 latent-projected + 64 rope), cache [pages, 64, 576]
     (page 0 zero), out [tokens, heads, 512] = softmax(q c^T * scale) c[:, :512] with the causal rule
-    that query token i of a sequence sees kv positions <= seq_len - q_len + i."""
+    that query token i of a sequence sees kv positions <= seq_len - q_len + i.  With ``out_tpad`` > 0
+    the output is head-major: out [heads, out_tpad, 512]."""
     T, heads, rec = q_abs.shape
     assert rec == 576 and 128 % heads == 0 and q_abs.is_contiguous() and out.is_contiguous() and cache.is_contiguous()
     num_pages = cache.shape[0]
@@ -345,9 +346,74 @@ def mla_attention(q_abs: torch.Tensor, cache: torch.Tensor, page_table: torch.Te
     _n.check(_n.cuda_lib().cafd_mla_attention(q_abs.data_ptr(), cache.data_ptr(), page_table.data_ptr(), seq_lens.data_ptr(),
                                               q_start.data_ptr(), block_seq.data_ptr(), block_tok0.data_ptr(), out.data_ptr(),
                                               _ptr(scratch), status_word(q_abs.device).data_ptr(), T * heads,
-                                              block_seq.numel(), num_pages, max_pages, heads, splits, scale, _stream()),
+                                              block_seq.numel(), num_pages, max_pages, heads, splits, out_tpad, scale, _stream()),
              "mla_attention")
     return out
+
+
+def mla_prep_a(a: torch.Tensor, q_lora: int, q_norm_w: torch.Tensor | None, kv_norm_w: torch.Tensor, inv_freq: torch.Tensor,
+               positions: torch.Tensor, slots: torch.Tensor, q_a_out: torch.Tensor | None, cache: torch.Tensor, eps: float,
+               interleaved: bool) -> None:
+    """a [T, q_lora + 576] -> q_a_out [T, q_lora] (normalised) and the [latent | rope] record at cache slot ``slots[t]``."""
+    T = a.shape[0]
+    assert a.shape[1] == q_lora + 576 and a.stride(1) == 1 and cache.shape[-1] == 576
+    _n.check(_n.cuda_lib().cafd_mla_prep_a(a.data_ptr(), a.stride(0), q_lora, _ptr(q_norm_w), kv_norm_w.data_ptr(),
+                                           inv_freq.data_ptr(), positions.data_ptr(), slots.data_ptr(), _ptr(q_a_out),
+                                           cache.data_ptr(), T, eps, int(interleaved), _stream()), "mla_prep_a")
+
+
+def mla_q_split(q: torch.Tensor, inv_freq: torch.Tensor, positions: torch.Tensor, slab: torch.Tensor, q_abs: torch.Tensor,
+                heads: int, interleaved: bool) -> None:
+    """q [T, heads*192] -> slab [heads, t_pad, 128] (nope dims, head-major) and q_abs[:, :, 512:] (rotated rope dims)."""
+    T = q.shape[0]
+    assert q.shape[1] == heads * 192 and slab.shape[0] == heads and slab.shape[2] == 128
+    _n.check(_n.cuda_lib().cafd_mla_q_split(q.data_ptr(), q.stride(0), inv_freq.data_ptr(), positions.data_ptr(),
+                                            slab.data_ptr(), q_abs.data_ptr(), T, heads, slab.shape[1], int(interleaved),
+                                            _stream()), "mla_q_split")
+
+
+# ---- sampling ---------------------------------------------------------------------------------------------
+_SAMPLE_ROW = None
+
+
+def sample_row_dtype():
+    """numpy dtype of the 64-byte row record read by the sampling kernel."""
+    global _SAMPLE_ROW
+    if _SAMPLE_ROW is None:
+        import numpy as np
+        _SAMPLE_ROW = np.dtype([("temperature", "<f4"), ("top_p", "<f4"), ("min_p", "<f4"), ("top_k", "<i4"), ("seed", "<u8"),
+                                ("position", "<i8"), ("mask_word0", "<i8"), ("logits_row", "<i4"), ("pad", "<i4", (5,))])
+        assert _SAMPLE_ROW.itemsize == 64
+    return _SAMPLE_ROW
+
+
+def pack_sample_rows(params, positions, logits_rows=None, mask_word0=None) -> torch.Tensor:
+    """Host-side row records (uint8 tensor [n, 64]) for ``sample_rows`` from SamplingParams-like objects."""
+    import numpy as np
+    n = len(params)
+    rec = np.zeros(n, dtype=sample_row_dtype())
+    for i, p in enumerate(params):
+        rec[i]["temperature"], rec[i]["top_p"], rec[i]["min_p"] = p.temperature, p.top_p, p.min_p
+        rec[i]["top_k"] = p.top_k if p.top_k is not None else 0
+        rec[i]["seed"], rec[i]["position"] = p.seed & 0xFFFFFFFFFFFFFFFF, positions[i]
+        rec[i]["mask_word0"] = -1 if mask_word0 is None or mask_word0[i] is None else mask_word0[i]
+        rec[i]["logits_row"] = i if logits_rows is None else logits_rows[i]
+    return torch.from_numpy(rec.view(np.uint8).reshape(n, 64))
+
+
+def sample_rows(logits: torch.Tensor, rows: torch.Tensor, out_token: torch.Tensor, out_status: torch.Tensor,
+                masks: torch.Tensor | None = None) -> None:
+    """Exact target sampling: ``rows`` is a device uint8 [n, 64] tensor of row records, ``masks`` packed int32 bits."""
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and rows.dtype == torch.uint8 and rows.shape[1] == 64
+    _n.check(_n.cuda_lib().cafd_sample_rows(logits.data_ptr(), logits.stride(0), logits.shape[1], rows.data_ptr(), _ptr(masks),
+                                            rows.shape[0], out_token.data_ptr(), out_status.data_ptr(), _stream()), "sample_rows")
+
+
+def accept_prefix(selected: torch.Tensor, draft: torch.Tensor, row_start: torch.Tensor, accepted: torch.Tensor,
+                  bonus: torch.Tensor) -> None:
+    S = row_start.numel() - 1
+    _n.check(_n.cuda_lib().cafd_accept_prefix(selected.data_ptr(), draft.data_ptr(), row_start.data_ptr(), S,
+                                              accepted.data_ptr(), bonus.data_ptr(), _stream()), "accept_prefix")
 
 
 # ---- FP8 block-scaled GEMM -----------------------------------------------------------------------------

@@ -40,6 +40,7 @@ class OracleBackend:
         self.steps = 0
         self.fail_on_step = fail_on_step          # host-side fault injection: the N-th verify raises
         self.quarantined: list[_Handle] = []
+        self._sel = None
 
     def open(self, tokens: list[int]) -> tuple[_Handle, int]:
         from ..ref.model import KvState
@@ -124,9 +125,7 @@ class EngineBackend:
 
     def _copy_page(self, src: int, dst: int) -> None:
         kv = self.engine.kv if hasattr(self.engine, "kv") else self.engine.inner.kv
-        for k, v in zip(kv.k, kv.v):
-            k[dst].copy_(k[src])
-            v[dst].copy_(v[src])
+        kv.copy_page(src, dst)
 
     def open(self, tokens: list[int]) -> tuple[_Handle, int]:
         seq, m = self.prefix.admit(tokens)
@@ -155,7 +154,7 @@ class EngineBackend:
         seq.kv_len = start + n
         return logits[:1].float().cpu() if last else None
 
-    def verify(self, handles: list[_Handle], rows: list[list[int]]) -> torch.Tensor:
+    def _verify_device(self, handles: list[_Handle], rows: list[list[int]]) -> torch.Tensor:
         from ..models.gqa_moe import Batch
         S = len(handles)
         T = sum(len(r) for r in rows)
@@ -182,12 +181,37 @@ class EngineBackend:
         for h, r in zip(handles, rows):
             h.seq.tokens.extend(r)
             h.seq.kv_len += len(r)
+        return logits[:T]
+
+    def verify(self, handles: list[_Handle], rows: list[list[int]]) -> torch.Tensor:
         from ..ops import kernels as K
-        out = logits[:T].float().cpu()
+        out = self._verify_device(handles, rows).float().cpu()
         st = K.read_status()
         if st:
             raise RuntimeError(f"a bounded device wait ran out (status {st})")
         return out
+
+    def verify_select(self, handles: list[_Handle], rows: list[list[int]], params: list, positions: list[int]) -> tuple[list[int], list[int]]:
+        """Forward + exact target sampling on the GPU: one 64-byte record per row goes up, 8 bytes per row
+        come back (token, row status) instead of a full-vocabulary logit row."""
+        from ..ops import kernels as K
+        logits = self._verify_device(handles, rows)
+        T = logits.shape[0]
+        rec = K.pack_sample_rows(params, positions)
+        if self._sel is None or self._sel[0].shape[0] < T:
+            n = max(T, self.bufs.max_tokens)
+            self._sel = (torch.empty(n, 64, dtype=torch.uint8, device=self.engine.device),
+                         torch.empty(2, n, dtype=torch.int32, device=self.engine.device),
+                         torch.empty(n, 64, dtype=torch.uint8).pin_memory())
+        dev_rec, dev_out, host_rec = self._sel
+        host_rec[:T].copy_(rec)
+        dev_rec[:T].copy_(host_rec[:T], non_blocking=True)
+        K.sample_rows(logits, dev_rec[:T], dev_out[0, :T], dev_out[1, :T])
+        out = dev_out[:, :T].cpu()
+        st = K.read_status()
+        if st:
+            raise RuntimeError(f"a bounded device wait ran out (status {st})")
+        return out[0].tolist(), out[1].tolist()
 
     def commit(self, h: _Handle, keep_tokens: int) -> None:
         if keep_tokens < h.seq.kv_len:

@@ -280,8 +280,19 @@ class Scheduler:
         self.policy.settle(plans, self.row_budget)
         drafts = [d[: p.keep + p.copy] for d, p in zip(drafts, plans)]
         rows = [[a.last_token] + d for a, d in zip(runnable, drafts)]
+        # GPU selection when nothing needs the logit rows on the host (grammar masks advance per token on the
+        # host; row hashes are taken from the row bytes)
+        on_device = hasattr(self.be, "verify_select") and all(a.req.constraint is None and not a.req.record_rows for a in runnable)
+        picked: list[int] | None = None
+        picked_status: list[int] = []
         try:
-            logits = self.be.verify([a.handle for a in runnable], rows)
+            if on_device:
+                flat_params = [a.req.params for a, r in zip(runnable, rows) for _ in r]
+                flat_pos = [len(a.req.prompt) + len(a.generated) + j for a, r in zip(runnable, rows) for j in range(len(r))]
+                picked, picked_status = self.be.verify_select([a.handle for a in runnable], rows, flat_params, flat_pos)
+                logits = None
+            else:
+                logits = self.be.verify([a.handle for a in runnable], rows)
         except Exception as e:
             self.decoding = [a for a in self.decoding if a not in runnable]
             self._fail(runnable, f"decode step failed: {e}")
@@ -297,7 +308,10 @@ class Scheduler:
             bad = False
             for j in range(len(r)):
                 # row j is drawn at absolute position (tokens so far) + j: layout cannot change a draw
-                t = self._select(a, logits[off + j], len(a.req.prompt) + len(a.generated) + j, emit_error=False)
+                if picked is not None:
+                    t = picked[off + j] if picked_status[off + j] == 0 else None
+                else:
+                    t = self._select(a, logits[off + j], len(a.req.prompt) + len(a.generated) + j, emit_error=False)
                 if t is None:
                     bad = True
                     break
