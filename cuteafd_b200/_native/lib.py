@@ -97,7 +97,10 @@ def cuda_lib():
         _sig(lib, "cafd_attn_decode", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
         _sig(lib, "cafd_attn_prefill", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
         _sig(lib, "cafd_mla_scratch_floats", [I, I], C.c_longlong)
-        _sig(lib, "cafd_mla_attention", [P, P, P, P, P, P, P, P, P, P, C.c_longlong, I, I, I, I, I, I, F, P])
+        _sig(lib, "cafd_mla_attention", [P, P, P, P, P, P, P, P, P, P, C.c_longlong, I, I, I, I, I, I, F, P, I, P])
+        _sig(lib, "cafd_indexer_scores", [P, P, P, I, F, P, P, P, P, P, P, P, C.c_longlong, I, I, I, I, I, I, P])
+        _sig(lib, "cafd_index_topk", [P, I, P, P, P, I, I, I, P, P])
+        _sig(lib, "cafd_index_k_store", [P, I, P, P, I, P])
         _sig(lib, "cafd_mla_prep_a", [P, I, I, P, P, P, P, P, P, P, I, F, I, P])
         _sig(lib, "cafd_sample_rows", [P, I, I, P, P, I, P, P, P])
         _sig(lib, "cafd_accept_prefix", [P, P, P, I, P, P, P])

@@ -49,6 +49,11 @@ struct MlaDev {
   int max_pages, heads, splits;
   int out_tpad;            // 0: out rows are (token, head); > 0: head-major rows head * out_tpad + token
   float scale_log2;
+  // sparse mode (sparse_idx != null): every row block is ONE query token; its kv set is the first
+  // min(visible positions, sparse_k) entries of sparse_idx[token] (ascending positions).
+  const int* sparse_idx;   // [tokens, sparse_k]
+  const uint8_t* cache;    // latent cache base (records gathered with plain 16-byte async copies)
+  int sparse_k;
 };
 
 // Shared-memory descriptor without swizzle (canonical K-major "interleave" layout): 8x16-byte core
@@ -84,10 +89,11 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int tok0 = p.block_tok0[blk];
   const int q0 = p.q_start[seq], q_len = p.q_start[seq + 1] - q0;
   const int kv_len = p.seq_lens[seq];
-  const int tok_per_blk = kMlaRows / p.heads;
+  const bool sparse = p.sparse_idx != nullptr;
+  const int tok_per_blk = sparse ? 1 : kMlaRows / p.heads;
   // visible kv positions for the last valid token of this block
   const int last_tok = min(tok0 + tok_per_blk, q_len) - 1;
-  const int max_limit = kv_len - q_len + last_tok + 1;
+  const int max_limit = sparse ? min(kv_len - q_len + last_tok + 1, p.sparse_k) : kv_len - q_len + last_tok + 1;
   const int total_tiles = (tok0 < q_len && max_limit > 0) ? (max_limit + kKvTile - 1) / kKvTile : 0;   // block past the new tokens: idle
   const int per_split = (total_tiles + p.splits - 1) / p.splits;
   const int t_begin = split * per_split;
@@ -99,7 +105,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&c_full[i], 1); mbar_init(&c_empty[i], 1);
+      mbar_init(&c_full[i], sparse ? 32 : 1); mbar_init(&c_empty[i], 1);
       mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128);
     }
     mbar_init(&p_ready, 128);
@@ -117,7 +123,49 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tS = tmem;          // + 32 * buffer
   const uint32_t tO = tmem + 64;
 
-  if (warp == 0) {
+  if (warp == 0 && sparse) {
+    // gather producer: the whole warp copies 32 records (1152 bytes each) per tile into the swizzled
+    // tile layout with 16-byte async copies; the copies of tile j are in flight while tile j-1 is consumed
+    if (n_tiles > 0) {
+      if (lane == 0) {
+        tma_prefetch_desc(&tm_q);
+        mbar_expect_tx(&q_full, kQBytes);
+        const int qrow = (q0 + tok0) * p.heads;
+        for (int a = 0; a < kAtoms; ++a) tma_load_2d(sQ + a * kMlaRows * 128, &tm_q, &q_full, a * 64, qrow);
+      }
+      const int* idx = p.sparse_idx + static_cast<size_t>(q0 + tok0) * p.sparse_k;
+      const int* pt = p.page_table + static_cast<size_t>(seq) * p.max_pages;
+      bool ok = true;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (j > 0) {                       // publish tile j-1 before blocking: freeing a stage needs it consumed
+          asm volatile("cp.async.wait_group 0;" ::: "memory");
+          fence_async_smem();
+          mbar_arrive(&c_full[(j - 1) & 1]);
+        }
+        if (!mbar_wait(&c_empty[st], ph ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
+        const int e = (t_begin + j) * kKvTile + lane;
+        const int pos = e < max_limit ? idx[e] : -1;
+        long long rec = -1;
+        if (pos >= 0 && (pos >> 6) < seq_pages) rec = (static_cast<long long>(pt[pos >> 6]) * 64 + (pos & 63)) * (kRec * 2);
+        const uint32_t dst0 = smem_u32(sC + st * kKvBytes);
+#pragma unroll 4
+        for (int c = lane; c < kKvTile * 72; c += 32) {
+          const int tok = c / 72, piece = c - tok * 72;
+          const long long r = __shfl_sync(0xffffffffu, rec, tok);
+          const uint32_t dst = dst0 + (piece >> 3) * (kKvTile * 128) + tok * 128 + (((piece & 7) ^ (tok & 7)) << 4);
+          const uint8_t* src = p.cache + (r >= 0 ? r : 0) + piece * 16;
+          const uint32_t sz = r >= 0 ? 16u : 0u;                      // size 0: the 16 bytes are zero-filled
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      fence_async_smem();
+      if (ok) mbar_arrive(&c_full[(n_tiles - 1) & 1]);
+    }
+  } else if (warp == 0) {
     if (lane == 0 && n_tiles > 0) {
       tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_c);
       mbar_expect_tx(&q_full, kQBytes);
@@ -185,8 +233,8 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     const int ti = row / p.heads;
-    const bool row_valid = (tok0 + ti) < q_len;
-    const int limit = row_valid ? (kv_len - q_len + tok0 + ti + 1) : 0;
+    const bool row_valid = (tok0 + ti) < q_len && ti < tok_per_blk;
+    const int limit = !row_valid ? 0 : sparse ? max_limit : (kv_len - q_len + tok0 + ti + 1);
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
@@ -301,13 +349,13 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // One block per (row block, half, row): thread c walks the splits in order for its output column.
 __global__ void __launch_bounds__(256) mla_merge_kernel(const float* __restrict__ partial, const int* __restrict__ block_seq,
                                                         const int* __restrict__ block_tok0, const int* __restrict__ q_start,
-                                                        __nv_bfloat16* __restrict__ out, int heads, int splits, int out_tpad) {
+                                                        __nv_bfloat16* __restrict__ out, int heads, int splits, int out_tpad, int one_token) {
   pdl_wait();
   pdl_trigger();
   const int blk = blockIdx.x, dh = blockIdx.y, row = blockIdx.z, c = threadIdx.x;
   const int seq = block_seq[blk], tok0 = block_tok0[blk];
   const int q0 = q_start[seq], q_len = q_start[seq + 1] - q0;
-  if (tok0 + row / heads >= q_len) return;
+  if (tok0 + row / heads >= q_len || (one_token && row >= heads)) return;
   const float* base = partial + (static_cast<size_t>(blk) * 2 + dh) * splits * kMlaPartial;
   float M = -INFINITY;
   for (int s = 0; s < splits; ++s) M = fmaxf(M, __ldg(base + static_cast<size_t>(s) * kMlaPartial + kMlaRows * kHalf + row));
@@ -339,12 +387,13 @@ extern "C" long long cafd_mla_scratch_floats(int n_blocks, int splits) {
 // q [rows, 576] bf16 with rows = (token, head) pairs (head fastest); cache [num_pages, 64, 576] bf16 with
 // page 0 all zero; block_seq / block_tok0 [n_blocks] describe each 128-row block (128 / heads tokens);
 // out [rows, 512] bf16, rows ordered like q, or head-major (row = head * out_tpad + token) when out_tpad > 0.
-// heads must divide 128.
+// heads must divide 128.  With sparse_idx [tokens, sparse_k] (ascending positions, -1 padded) every block is one query token
+// and attends only to its listed positions.
 extern "C" int cafd_mla_attention(const void* q, const void* cache, const int* page_table, const int* seq_lens,
                                   const int* q_start, const int* block_seq, const int* block_tok0, void* out,
                                   float* scratch, uint32_t* status, long long total_rows, int n_blocks, int num_pages,
                                   int max_pages, int heads, int splits, int out_tpad, float scale,
-                                  cafd_stream_t s) {
+                                  const int* sparse_idx, int sparse_k, cafd_stream_t s) {
   if (n_blocks <= 0) return 0;
   if (heads <= 0 || kMlaRows % heads) return -10;
   if (splits < 1) splits = 1;
@@ -365,6 +414,7 @@ extern "C" int cafd_mla_attention(const void* q, const void* cache, const int* p
   p.trace = g_mla_trace;
   p.max_pages = max_pages; p.heads = heads; p.splits = splits; p.out_tpad = out_tpad;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.sparse_idx = sparse_idx; p.sparse_k = sparse_k; p.cache = static_cast<const uint8_t*>(cache);
   static bool attr = false;
   if (!attr) {
     CAFD_CHECK_CUDA(cudaFuncSetAttribute(mla_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));
@@ -374,7 +424,7 @@ extern "C" int cafd_mla_attention(const void* q, const void* cache, const int* p
   launch_pdl(mla_attn_kernel, dim3(n_blocks, 2, splits), dim3(kMlaThreads), kMlaSmem, st, tq, tc, p);
   if (splits > 1)
     launch_pdl(mla_merge_kernel, dim3(n_blocks, 2, kMlaRows), dim3(kHalf), 0, st, static_cast<const float*>(scratch), block_seq,
-               block_tok0, q_start, static_cast<__nv_bfloat16*>(out), heads, splits, out_tpad);
+               block_tok0, q_start, static_cast<__nv_bfloat16*>(out), heads, splits, out_tpad, sparse_idx ? 1 : 0);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -29,7 +29,7 @@ REC = 576
 
 
 class MlaLayerWeights(LayerWeights):
-    __slots__ = ("wqkv_a", "q_a_norm", "kv_a_norm", "wq_b", "w_uk", "w_uv")
+    __slots__ = ("wqkv_a", "q_a_norm", "kv_a_norm", "wq_b", "w_uk", "w_uv", "wq_idx")
 
     def __init__(self) -> None:
         for s in LayerWeights.__slots__ + MlaLayerWeights.__slots__:
@@ -68,6 +68,9 @@ class MlaMoeWeights:
             else:
                 L.wqkv_a, L.wq_b = t(a + "kv_a_proj_with_mqa.weight"), t(a + "q_proj.weight")
             L.kv_a_norm = t(a + "kv_a_layernorm.weight")
+            if cfg.indexer_heads:      # index keys and head weights ride on the fused q_a / kv_a projection
+                L.wqkv_a = torch.cat([L.wqkv_a, t(a + "indexer.wk.weight"), t(a + "indexer.weights_proj.weight")]).contiguous()
+                L.wq_idx = t(a + "indexer.wq.weight")
             L.w_uk, L.w_uv = MlaMoeWeights._split_kv_b(cfg, t(a + "kv_b_proj.weight"))
             L.wo = t(a + "o_proj.weight")
             if cfg.is_moe_layer(i):
@@ -103,7 +106,8 @@ class MlaMoeWeights:
         for i in range(cfg.num_layers):
             L = MlaLayerWeights()
             L.ln1, L.ln2 = ones(H), ones(H)
-            L.wqkv_a = w(cfg.q_lora_rank + REC, H)
+            L.wqkv_a = w(cfg.q_lora_rank + REC + ((cfg.indexer_dim + cfg.indexer_heads) if cfg.indexer_heads else 0), H)
+            L.wq_idx = w(cfg.indexer_heads * cfg.indexer_dim, H) if cfg.indexer_heads else None
             L.q_a_norm = ones(cfg.q_lora_rank) if cfg.q_lora_rank else None
             L.kv_a_norm = ones(cfg.kv_lora_rank)
             L.wq_b = w(cfg.num_heads * cfg.qk_head_dim, cfg.q_lora_rank or H)
@@ -131,12 +135,15 @@ class LatentCache:
     def __init__(self, cfg: ModelConfig, num_pages: int, device: torch.device):
         self.num_pages = num_pages
         self.c = [torch.zeros(num_pages, PAGE, REC, dtype=torch.bfloat16, device=device) for _ in range(cfg.num_layers)]
+        # index keys of the lightning indexer, paged like the latent records
+        self.idx = ([torch.zeros(num_pages, PAGE, cfg.indexer_dim, dtype=torch.bfloat16, device=device) for _ in range(cfg.num_layers)]
+                    if cfg.indexer_heads else [])
 
     def bytes_per_page(self) -> int:
-        return len(self.c) * PAGE * REC * 2
+        return len(self.c) * PAGE * REC * 2 + sum(t[0].numel() * 2 for t in self.idx)
 
     def copy_page(self, src: int, dst: int) -> None:
-        for c in self.c:
+        for c in self.c + self.idx:
             c[dst].copy_(c[src])
 
 
@@ -165,6 +172,7 @@ class MlaMoeEngine(GqaMoeEngine):
                  build_moe: bool = True):
         assert cfg.is_mla and cfg.kv_lora_rank == 512 and cfg.qk_rope_dim == 64 and cfg.qk_nope_dim == 128 and cfg.v_head_dim == 128
         assert 128 % cfg.num_heads == 0, "local head count must divide 128"
+        assert not cfg.indexer_heads or (cfg.indexer_dim == 128 and cfg.indexer_heads in (32, 64, 128, 256))
         self.cfg, self.W, self.kv = cfg, weights, kv
         self.device = dev = weights.embed.device
         self.max_tokens = max_tokens
@@ -175,7 +183,10 @@ class MlaMoeEngine(GqaMoeEngine):
             pass
         ws = self.ws = _Ws()
         ws.h, ws.x = torch.empty(max_tokens, H, **bf), torch.empty(max_tokens, H, **bf)
-        ws.a = torch.empty(max_tokens, cfg.q_lora_rank + REC, **bf)
+        ws.a = torch.empty(max_tokens, cfg.q_lora_rank + REC + ((cfg.indexer_dim + cfg.indexer_heads) if cfg.indexer_heads else 0), **bf)
+        ws.q_idx = torch.empty(max_tokens, cfg.indexer_heads * cfg.indexer_dim, **bf) if cfg.indexer_heads else None
+        ws.sel = torch.empty(max_tokens, cfg.indexer_topk, dtype=torch.int32, device=dev) if cfg.indexer_heads else None
+        ws.scores = None
         ws.q_a = torch.empty(max_tokens, cfg.q_lora_rank, **bf) if cfg.q_lora_rank else None
         ws.q = torch.empty(max_tokens, heads * cfg.qk_head_dim, **bf)
         t_pad_max = ((max_tokens + 127) // 128) * 128
@@ -201,15 +212,16 @@ class MlaMoeEngine(GqaMoeEngine):
         self.next_tokens = torch.empty(self.logits.shape[0], dtype=torch.int32, device=dev)
         self._scratch: torch.Tensor | None = None
         self._tiles: dict[int, _HeadTiles] = {}
-        self._blocks: dict[tuple[int, int], tuple[torch.Tensor, torch.Tensor]] = {}
+        self.select_hook = None      # callable(layer, selection [T, top_k]) for tests and traces (eager mode only)
+        self._blocks: dict[tuple[int, int, int], tuple[torch.Tensor, torch.Tensor]] = {}
         self.launches = 0
 
-    def _block_table(self, S: int, max_q_len: int) -> tuple[torch.Tensor, torch.Tensor]:
-        """Row blocks of the attention kernel: every sequence gets ceil(max_q_len / tokens per block) blocks;
-        a block past a shorter sequence's new tokens does nothing."""
-        key = (S, max_q_len)
+    def _block_table(self, S: int, max_q_len: int, per: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """Row blocks of the attention / indexer kernels: every sequence gets ceil(max_q_len / tokens per block)
+        blocks; a block past a shorter sequence's new tokens does nothing."""
+        per = per or 128 // self.cfg.num_heads
+        key = (S, max_q_len, per)
         if key not in self._blocks:
-            per = 128 // self.cfg.num_heads
             nb = (max_q_len + per - 1) // per
             i32 = dict(dtype=torch.int32, device=self.device)
             seq = torch.arange(S, **i32).repeat_interleave(nb).contiguous()
@@ -224,7 +236,7 @@ class MlaMoeEngine(GqaMoeEngine):
             self._tiles[T] = _HeadTiles(T, heads, self.device)
         ht = self._tiles[T]
         K.linear(ws.x[:T], L.wqkv_a, out=ws.a[:T])
-        K.mla_prep_a(ws.a[:T], ql, L.q_a_norm, L.kv_a_norm, self.inv_freq, b.positions, b.slots,
+        K.mla_prep_a(ws.a[:T, :ql + REC], ql, L.q_a_norm, L.kv_a_norm, self.inv_freq, b.positions, b.slots,
                      ws.q_a[:T] if ql else None, self.kv.c[i], cfg.rms_eps, cfg.rope_interleaved)
         K.linear(ws.q_a[:T] if ql else ws.x[:T], L.wq_b, out=ws.q[:T])
         q_slab = ws.q_slab[:heads * ht.t_pad * 128].view(heads, ht.t_pad, 128)
@@ -233,17 +245,40 @@ class MlaMoeEngine(GqaMoeEngine):
         K.grouped_linear(q_slab.view(-1, 128), L.w_uk, ws.q_abs, ht.tile_expert, ht.tile_row0, ht.num_tiles, ht.max_tiles,
                          ht.tile_rows, row_dst=ht.row_dst, ldo=REC, split_k=False)
         S, max_pages = b.page_table.shape
-        bseq, btok = self._block_table(S, b.max_q_len)
+        sel = self._select(i, T, b) if cfg.indexer_heads else None
+        bseq, btok = self._block_table(S, b.max_q_len, 1 if sel is not None else None)
         nb = bseq.numel()
-        tiles = max_pages * 2
+        tiles = (min(cfg.indexer_topk, max_pages * 64) // 32) if sel is not None else max_pages * 2
         splits = 1 if b.prefill else max(1, min(K.num_sms() // max(1, nb * 2), max(1, tiles // 8), 32))
         if splits > 1:
             need = K.mla_scratch_floats(nb, splits)
             if self._scratch is None or self._scratch.numel() < need:
                 self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
         K.mla_attention(ws.q_abs[:T], self.kv.c[i], b.page_table, b.seq_lens, b.q_start, bseq, btok, o_slab, self.scale,
-                        splits, self._scratch if splits > 1 else None, out_tpad=ht.t_pad)
+                        splits, self._scratch if splits > 1 else None, out_tpad=ht.t_pad, sparse_idx=sel)
         K.grouped_linear(o_slab.view(-1, 512), L.w_uv, ws.attn, ht.tile_expert, ht.tile_row0, ht.num_tiles, ht.max_tiles,
                          ht.tile_rows, row_dst=ht.row_dst, ldo=cfg.v_head_dim, split_k=False)
         K.linear(ws.attn[:T], L.wo, out=ws.h[:T], residual=ws.h[:T])
         self.launches += 8 + (1 if splits > 1 else 0)
+
+    def _select(self, i: int, T: int, b: Batch) -> torch.Tensor:
+        """Lightning indexer: store this step's index keys, score every visible position, keep the top-k per token."""
+        cfg, L, ws = self.cfg, self.W.layers[i], self.ws
+        Hi, off_k = cfg.indexer_heads, cfg.q_lora_rank + REC
+        off_w = off_k + cfg.indexer_dim
+        S, max_pages = b.page_table.shape
+        ld = ((max_pages * PAGE + 127) // 128) * 128
+        if ws.scores is None or ws.scores.shape[1] < ld:
+            ws.scores = torch.empty(self.max_tokens, ld, dtype=torch.float32, device=self.device)
+        K.index_k_store(ws.a[:T, off_k:off_w], b.slots, self.kv.idx[i])
+        K.linear(ws.x[:T], L.wq_idx, out=ws.q_idx[:T])
+        ibs, ibt = self._block_table(S, b.max_q_len, 256 // Hi)
+        tiles = (max_pages + 1) // 2
+        splits = 1 if b.prefill else max(1, min(K.num_sms() // max(1, ibs.numel()), max(1, tiles // 2), 64))
+        K.indexer_scores(ws.q_idx[:T].view(T, Hi, cfg.indexer_dim), self.kv.idx[i], ws.a[:T, off_w:off_w + Hi], b.page_table,
+                         b.seq_lens, b.q_start, ibs, ibt, ws.scores[:T], splits, w_scale=Hi ** -0.5)
+        K.index_topk(ws.scores[:T], cfg.indexer_topk, ws.sel[:T], seq_lens=b.seq_lens, q_start=b.q_start)
+        self.launches += 4
+        if self.select_hook is not None:
+            self.select_hook(i, ws.sel[:T])
+        return ws.sel[:T]

@@ -334,11 +334,14 @@ def mla_scratch_floats(n_blocks: int, splits: int) -> int:
 
 def mla_attention(q_abs: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor, seq_lens: torch.Tensor,
                   q_start: torch.Tensor, block_seq: torch.Tensor, block_tok0: torch.Tensor, out: torch.Tensor,
-                  scale: float, splits: int = 1, scratch: torch.Tensor | None = None, out_tpad: int = 0) -> torch.Tensor:
+                  scale: float, splits: int = 1, scratch: torch.Tensor | None = None, out_tpad: int = 0,
+                  sparse_idx: torch.Tensor | None = None) -> torch.Tensor:
     """Absorbed MLA: q_abs [tokens, heads, 576] (512 latent-projected + 64 rope), cache [pages, 64, 576]
     (page 0 zero), out [tokens, heads, 512] = softmax(q c^T * scale) c[:, :512] with the causal rule
     that query token i of a sequence sees kv positions <= seq_len - q_len + i.  With ``out_tpad`` > 0
-    the output is head-major: out [heads, out_tpad, 512]."""
+    the output is head-major: out [heads, out_tpad, 512].  With ``sparse_idx`` [tokens, k] (ascending positions,
+    -1 padded; from ``index_topk``) each block must be a single token (``mla_blocks(q_lens, 128)``) and the
+    token attends to its listed positions only."""
     T, heads, rec = q_abs.shape
     assert rec == 576 and 128 % heads == 0 and q_abs.is_contiguous() and out.is_contiguous() and cache.is_contiguous()
     num_pages = cache.shape[0]
@@ -346,9 +349,45 @@ def mla_attention(q_abs: torch.Tensor, cache: torch.Tensor, page_table: torch.Te
     _n.check(_n.cuda_lib().cafd_mla_attention(q_abs.data_ptr(), cache.data_ptr(), page_table.data_ptr(), seq_lens.data_ptr(),
                                               q_start.data_ptr(), block_seq.data_ptr(), block_tok0.data_ptr(), out.data_ptr(),
                                               _ptr(scratch), status_word(q_abs.device).data_ptr(), T * heads,
-                                              block_seq.numel(), num_pages, max_pages, heads, splits, out_tpad, scale, _stream()),
+                                              block_seq.numel(), num_pages, max_pages, heads, splits, out_tpad, scale,
+                                              _ptr(sparse_idx), sparse_idx.shape[1] if sparse_idx is not None else 0, _stream()),
              "mla_attention")
     return out
+
+
+def indexer_scores(q_idx: torch.Tensor, k_cache: torch.Tensor, head_w: torch.Tensor, page_table: torch.Tensor,
+                   seq_lens: torch.Tensor, q_start: torch.Tensor, block_seq: torch.Tensor, block_tok0: torch.Tensor,
+                   scores: torch.Tensor, splits: int = 1, w_scale: float = 1.0) -> torch.Tensor:
+    """scores[t, s] = sum_h w_scale * head_w[t, h] * relu(q_idx[t, h] . k_cache[s]) for visible s, -inf beyond (inside
+    the 128-position tiles that were computed).  q_idx [T, heads, 128] bf16; head_w [T, heads] bf16 (any row stride);
+    k_cache [pages, 64, 128] bf16; blocks cover 256 / heads tokens (``mla_blocks(q_lens, heads // 2)``)."""
+    T, heads, d = q_idx.shape
+    assert d == 128 and q_idx.is_contiguous() and head_w.dtype == torch.bfloat16 and head_w.stride(1) == 1
+    assert scores.dtype == torch.float32 and scores.stride(1) == 1
+    _n.check(_n.cuda_lib().cafd_indexer_scores(q_idx.data_ptr(), k_cache.data_ptr(), head_w.data_ptr(), head_w.stride(0), w_scale,
+                                               page_table.data_ptr(), seq_lens.data_ptr(), q_start.data_ptr(),
+                                               block_seq.data_ptr(), block_tok0.data_ptr(), scores.data_ptr(),
+                                               status_word(q_idx.device).data_ptr(), T * heads, block_seq.numel(),
+                                               k_cache.shape[0], page_table.shape[1], heads, splits, scores.stride(0),
+                                               _stream()), "indexer_scores")
+    return scores
+
+
+def index_topk(scores: torch.Tensor, top_k: int, out: torch.Tensor, limits: torch.Tensor | None = None,
+               seq_lens: torch.Tensor | None = None, q_start: torch.Tensor | None = None) -> torch.Tensor:
+    """Top ``top_k`` positions per row among the visible scores: ties to the lower position, ascending output, -1
+    padded.  The visible count is ``limits[t]``, or derived from (seq_lens, q_start) like the attention kernels do."""
+    T = scores.shape[0]
+    assert out.shape == (T, top_k) and out.dtype == torch.int32 and out.is_contiguous()
+    S = q_start.numel() - 1 if q_start is not None else 0
+    _n.check(_n.cuda_lib().cafd_index_topk(scores.data_ptr(), scores.stride(0), _ptr(limits), _ptr(seq_lens), _ptr(q_start), S,
+                                           T, top_k, out.data_ptr(), _stream()), "index_topk")
+    return out
+
+
+def index_k_store(k: torch.Tensor, slots: torch.Tensor, cache: torch.Tensor) -> None:
+    _n.check(_n.cuda_lib().cafd_index_k_store(k.data_ptr(), k.stride(0), slots.data_ptr(), cache.data_ptr(), k.shape[0],
+                                              _stream()), "index_k_store")
 
 
 def mla_prep_a(a: torch.Tensor, q_lora: int, q_norm_w: torch.Tensor | None, kv_norm_w: torch.Tensor, inv_freq: torch.Tensor,

@@ -119,6 +119,7 @@ class RefDecoder:
 
     def __init__(self, cfg: ModelConfig, params: dict[str, torch.Tensor], moe_fn: MoeFn | None = None):
         self.cfg, self.p, self.moe_fn = cfg, params, moe_fn
+        self.select_fn = None        # optional (layer, start, Tq, Tk) -> bool mask [Tq, Tk] replacing the indexer's choice
         self._stacked: dict[int, tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
 
     # ---- pieces ---------------------------------------------------------------------------
@@ -149,14 +150,27 @@ class RefDecoder:
             ckv = (x.float() @ p[a + "kv_a_proj_with_mqa.weight"].float().T).to(x.dtype)
             latent = ops.rmsnorm(ckv[:, : cfg.kv_lora_rank], p[a + "kv_a_layernorm.weight"], cfg.rms_eps)
             k_rope = ops.apply_rope(ckv[:, None, cfg.kv_lora_rank:], positions, cfg.rope_theta, cfg.rope_interleaved)[:, 0]
-            full = kv.append(layer, torch.cat([latent, k_rope], dim=-1))
-            lat_all, rope_all = full[:, : cfg.kv_lora_rank], full[:, cfg.kv_lora_rank:]
+            rec = [latent, k_rope]
+            if cfg.indexer_heads:
+                rec.append((x.float() @ p[a + "indexer.wk.weight"].float().T).to(x.dtype))
+            full = kv.append(layer, torch.cat(rec, dim=-1))
+            lat_all, rope_all = full[:, : cfg.kv_lora_rank], full[:, cfg.kv_lora_rank: cfg.kv_lora_rank + cfg.qk_rope_dim]
+            allowed = None
+            if cfg.indexer_heads:
+                # lightning indexer (simplified: no rope / rotation on the index vectors): index queries and
+                # head weights from the layer input, index keys cached beside the latent record
+                q_idx = (x.float() @ p[a + "indexer.wq.weight"].float().T).to(x.dtype).view(T, cfg.indexer_heads, cfg.indexer_dim)
+                hw = (x.float() @ p[a + "indexer.weights_proj.weight"].float().T).to(x.dtype).float() * cfg.indexer_heads ** -0.5
+                allowed = ops.index_select(q_idx, full[:, cfg.kv_lora_rank + cfg.qk_rope_dim:], hw, start, cfg.indexer_topk)
+                if self.select_fn is not None:
+                    forced = self.select_fn(layer, start, T, full.shape[0], allowed)
+                    allowed = allowed if forced is None else forced
             kvb = (lat_all.float() @ p[a + "kv_b_proj.weight"].float().T).to(x.dtype)
             kvb = kvb.view(-1, cfg.num_heads, cfg.qk_nope_dim + cfg.v_head_dim)
             k = torch.cat([kvb[..., : cfg.qk_nope_dim], rope_all[:, None, :].expand(-1, cfg.num_heads, -1)], dim=-1)
             v = kvb[..., cfg.qk_nope_dim:]
             qq = torch.cat([q_nope, q_rope], dim=-1)
-            o = ops.causal_attention(qq, k, v, start, 1.0 / math.sqrt(cfg.qk_head_dim))
+            o = ops.causal_attention(qq, k, v, start, 1.0 / math.sqrt(cfg.qk_head_dim), allowed)
             o = o.reshape(T, cfg.num_heads * cfg.v_head_dim)
         else:
             q = (x.float() @ p[a + "q_proj.weight"].float().T).to(x.dtype).view(T, cfg.num_heads, cfg.head_dim)

@@ -122,9 +122,27 @@ def combine_slots(parts: torch.Tensor, shared: torch.Tensor | None, residual: to
     return acc.to(dtype)
 
 
-def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_start: int, scale: float | None = None
-                     ) -> torch.Tensor:
-    """q [Tq, Hq, D], k [Tk, Hk, D], v [Tk, Hk, Dv]; query row i sits at position q_start+i."""
+def index_select(q_idx: torch.Tensor, k_idx: torch.Tensor, head_w: torch.Tensor, q_start: int, top_k: int) -> torch.Tensor:
+    """Lightning-indexer selection.  q_idx [Tq, Hi, Di], k_idx [Tk, Di], head_w [Tq, Hi] (fp32).  Returns a bool
+    mask [Tq, Tk]: the top_k visible positions by sum_h w * relu(q . k), ties to the lower position; every
+    visible position when there are at most top_k."""
+    s = torch.einsum("th,thl->tl", head_w.float(), torch.relu(torch.einsum("thd,ld->thl", q_idx.float(), k_idx.float())))
+    Tq, Tk = s.shape
+    allowed = torch.zeros(Tq, Tk, dtype=torch.bool)
+    for i in range(Tq):
+        n = min(Tk, q_start + i + 1)
+        if n <= top_k:
+            allowed[i, :n] = True
+        else:
+            order = torch.sort(s[i, :n], descending=True, stable=True).indices[:top_k]
+            allowed[i, order] = True
+    return allowed
+
+
+def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_start: int, scale: float | None = None,
+                     allowed: torch.Tensor | None = None) -> torch.Tensor:
+    """q [Tq, Hq, D], k [Tk, Hk, D], v [Tk, Hk, Dv]; query row i sits at position q_start+i.  ``allowed`` [Tq, Tk]
+    further restricts the visible positions (sparse attention)."""
     Tq, Hq, D = q.shape
     Tk, Hk, _ = k.shape
     rep = Hq // Hk
@@ -135,6 +153,8 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_start:
     qpos = torch.arange(Tq, device=q.device)[:, None] + q_start
     kpos = torch.arange(Tk, device=q.device)[None, :]
     s = s.masked_fill((kpos > qpos)[None], float("-inf"))
+    if allowed is not None:
+        s = s.masked_fill(~allowed.to(s.device)[None], float("-inf"))
     p = torch.softmax(s, dim=-1)
     return torch.einsum("hqk,khd->qhd", p, vf).to(q.dtype)
 

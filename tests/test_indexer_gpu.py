@@ -1,0 +1,132 @@
+"""Lightning indexer (scores + top-k) and sparse MLA attention against fp32 PyTorch math."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from cuteafd_b200.ops import kernels
+    return kernels
+
+
+DEV = torch.device("cuda", 0)
+
+
+def _paged(lens, width, seed):
+    g = torch.Generator().manual_seed(seed)
+    S = len(lens)
+    max_pages = max((n + 63) // 64 for n in lens) + 1
+    total = 1 + sum((n + 63) // 64 for n in lens)
+    cache = torch.zeros(total, 64, width, dtype=torch.bfloat16)
+    table = torch.zeros(S, max_pages, dtype=torch.int32)
+    perm = (torch.randperm(total - 1, generator=g) + 1).tolist()
+    dense, nxt = [], 0
+    for s, n in enumerate(lens):
+        c = (torch.randn(n, width, generator=g) * 0.5).to(torch.bfloat16)
+        dense.append(c)
+        for pi in range((n + 63) // 64):
+            pg = perm[nxt]; nxt += 1
+            table[s, pi] = pg
+            rows = c[pi * 64:(pi + 1) * 64]
+            cache[pg, :rows.shape[0]] = rows
+    return cache.to(DEV), table.to(DEV), dense
+
+
+@pytest.mark.parametrize("heads,lens,qlens,splits", [(32, [100], [1], 1), (64, [700, 64, 1, 333], [1, 1, 1, 1], 3),
+                                                     (64, [300], [300], 1), (32, [517, 130], [517, 66], 1), (128, [1000], [5], 2)])
+def test_indexer_scores(K, heads, lens, qlens, splits):
+    cache, table, dense = _paged(lens, 128, seed=heads)
+    g = torch.Generator().manual_seed(3)
+    T = sum(qlens)
+    q = (torch.randn(T, heads, 128, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(T, heads, generator=g) * 0.2).to(torch.bfloat16)
+    i32 = dict(dtype=torch.int32, device=DEV)
+    bs, bt = K.mla_blocks(qlens, heads // 2)              # 256 / heads tokens per block
+    ld = ((max(lens) + 127) // 128) * 128
+    scores = torch.full((T, ld), 123.0, dtype=torch.float32, device=DEV)
+    q_start = torch.tensor([0] + torch.tensor(qlens).cumsum(0).tolist(), **i32)
+    for _ in range(2):
+        K.indexer_scores(q.to(DEV), cache, w.to(DEV), table, torch.tensor(lens, **i32), q_start, torch.tensor(bs, **i32),
+                         torch.tensor(bt, **i32), scores, splits, w_scale=0.5)
+    torch.cuda.synchronize()
+    assert K.read_status() == 0
+    got = scores.cpu()
+    o = 0
+    for s, n in enumerate(qlens):
+        ref = torch.einsum("th,thl->tl", w[o:o + n].float() * 0.5, torch.relu(torch.einsum("thd,ld->thl", q[o:o + n].float(), dense[s].float())))
+        for i in range(n):
+            lim = lens[s] - n + i + 1
+            err = (got[o + i, :lim] - ref[i, :lim]).abs().max().item()
+            assert err < 0.02 * max(1.0, ref[i, :lim].abs().max().item()), (s, i, err)
+            tile_end = min(ld, ((lim + 127) // 128) * 128)
+            assert torch.isneginf(got[o + i, lim:tile_end]).all()
+        o += n
+
+
+def _topk_ref(row, n, k):
+    if n <= k:
+        return list(range(n)) + [-1] * (k - n)
+    x = row[:n].clone()
+    x[torch.isnan(x)] = float("-inf")
+    order = sorted(range(n), key=lambda i: (-x[i].item(), i))[:k]
+    return sorted(order)
+
+
+def test_index_topk(K):
+    g = torch.Generator().manual_seed(0)
+    T, ld, k = 9, 5000, 64
+    scores = torch.randn(T, ld, generator=g)
+    scores[1] = torch.round(scores[1] * 2) / 2            # heavy ties
+    scores[2, ::3] = float("-inf")
+    scores[3, 10] = float("nan")
+    scores[4] = 1.0                                       # all equal: the lowest positions win
+    limits = [5000, 4097, 3000, 777, 500, 64, 10, 65, 1]
+    out = torch.full((T, k), -9, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        K.index_topk(scores.to(DEV), k, out, limits=torch.tensor(limits, dtype=torch.int32, device=DEV))
+    torch.cuda.synchronize()
+    got = out.cpu().tolist()
+    for t in range(T):
+        assert got[t] == _topk_ref(scores[t], limits[t], k), t
+
+
+@pytest.mark.parametrize("heads,lens,qlens,topk,splits", [(128, [300], [1], 64, 1), (64, [900, 70], [1, 1], 128, 2),
+                                                         (128, [200], [6], 96, 1), (16, [1500], [3], 512, 4)])
+def test_sparse_mla(K, heads, lens, qlens, topk, splits):
+    cache, table, dense = _paged(lens, 576, seed=heads + 1)
+    g = torch.Generator().manual_seed(11)
+    T = sum(qlens)
+    q = (torch.randn(T, heads, 576, generator=g) * 0.5).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(192)
+    idx = torch.full((T, topk), -1, dtype=torch.int32)
+    o = 0
+    sel = []
+    for s, n in enumerate(qlens):
+        for i in range(n):
+            lim = lens[s] - n + i + 1
+            m = min(lim, topk)
+            pos = torch.randperm(lim, generator=g)[:m].sort().values
+            idx[o + i, :m] = pos.to(torch.int32)
+            sel.append((s, pos))
+        o += n
+    i32 = dict(dtype=torch.int32, device=DEV)
+    bs, bt = K.mla_blocks(qlens, 128)                     # one token per block
+    q_start = torch.tensor([0] + torch.tensor(qlens).cumsum(0).tolist(), **i32)
+    out = torch.full((T, heads, 512), 7.0, dtype=torch.bfloat16, device=DEV)
+    scratch = torch.empty(K.mla_scratch_floats(len(bs), splits), dtype=torch.float32, device=DEV) if splits > 1 else None
+    for _ in range(2):
+        K.mla_attention(q.to(DEV), cache, table, torch.tensor(lens, **i32), q_start, torch.tensor(bs, **i32),
+                        torch.tensor(bt, **i32), out, scale, splits, scratch, sparse_idx=idx.to(DEV))
+    torch.cuda.synchronize()
+    assert K.read_status() == 0
+    got = out.float().cpu()
+    for t, (s, pos) in enumerate(sel):
+        c = dense[s][pos.long()].float()
+        p = torch.softmax(q[t].float() @ c.T * scale, -1)
+        ref = p @ c[:, :512]
+        err = (got[t] - ref).abs().max().item()
+        assert err < 0.03 * max(1.0, ref.abs().max().item()), (t, err)

@@ -92,43 +92,77 @@ def _mla_cfg():
                        num_shared_experts=1, routed_scale=2.5, router_bias=True)
 
 
-@pytest.mark.parametrize("use_graphs", [False, True])
-def test_mla_engine_matches_oracle(K, use_graphs):
+@pytest.mark.parametrize("use_graphs,indexer", [(False, False), (True, False), (False, True), (True, True)])
+def test_mla_engine_matches_oracle(K, use_graphs, indexer):
     from cuteafd_b200.models.mla_moe import LatentCache, MlaMoeEngine, MlaMoeWeights
     from cuteafd_b200.ref.model import KvState, RefDecoder, init_weights
     from cuteafd_b200.runtime.generate import Generator
     from cuteafd_b200.runtime.paged import PagePool
     cfg = _mla_cfg()
+    if indexer:                                   # sparse attention: 48 of up to ~200 cached positions per token
+        cfg = cfg.replace(family="deepseek_v32", indexer_heads=32, indexer_dim=128, indexer_topk=48)
     dev = _dev()
     params = {k: v.to(torch.bfloat16).float() for k, v in init_weights(cfg, seed=0).items()}
     eng = MlaMoeEngine(cfg, MlaMoeWeights.from_params(cfg, params, dev), LatentCache(cfg, 64, dev), max_tokens=256, max_seqs=8)
     gen = Generator(eng, PagePool(64), max_pages_per_seq=8, max_seqs=8, prefill_chunk=128, use_graphs=use_graphs)
     ref = RefDecoder(cfg, params)
+    # Index scores of near-tied positions flip with bf16 noise, so in eager mode the oracle attends to the
+    # positions the engine selected (and the two selections are compared); under graphs only a loose bound holds.
+    forced = indexer and not use_graphs
+    picked, agree = {}, []
+    if forced:
+        eng.select_hook = lambda layer, sel: picked.setdefault(layer, []).append(sel.cpu())
+
+        def select_fn(layer, start, Tq, Tk, own):
+            sel = picked[layer].pop(0)            # selections arrive in the order the engine ran its forward passes
+            assert sel.shape[0] == Tq
+            m = torch.zeros(Tq, Tk, dtype=torch.bool)
+            for i in range(Tq):
+                m[i, sel[i][sel[i] >= 0].long()] = True
+            agree.append(((m & own).sum().float() / own.sum().float()).item())      # shared share of the selected positions
+            return m
+        ref.select_fn = select_fn
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g) for n in (200, 77)]
-    seqs, last, ref_kv = [], [], []
+    seqs, last, ref_kv, errs = [], [], [], []
     with torch.no_grad():
         for p in prompts:
             s = gen.table.new()
+            picked.clear()
             gen.prefill(s, p.tolist())
             kvs = KvState(cfg)
-            rl = ref.forward(p, kvs)[-1]
+            if forced:                            # the oracle sees the prompt in the same chunks as the engine
+                for c0 in range(0, len(p), 128):
+                    rl = ref.forward(p[c0:c0 + 128], kvs)[-1]
+            else:
+                rl = ref.forward(p, kvs)[-1]
             got = eng.logits[0].float().cpu()
-            err = (got - rl).abs().max().item()
-            assert err < 0.05 * max(rl.abs().max().item(), 1.0), err
+            err = (got - rl).abs().max().item() / max(rl.abs().max().item(), 1.0)
+            if indexer and not forced:
+                errs.append(err)
+            else:
+                assert err < 0.05, err
             seqs.append(s); ref_kv.append(kvs)
             last.append(int(rl.argmax()))
-        errs = []
         for step in range(5):
+            picked.clear()
             gen.decode(seqs, last)
             torch.cuda.synchronize()
             assert K.read_status() == 0
+            rows = {layer: v[0] for layer, v in picked.items()}
             for i in range(len(seqs)):
+                for layer in rows:
+                    picked[layer] = [rows[layer][i:i + 1]]
                 rl = ref.forward(torch.tensor([last[i]]), ref_kv[i])[-1]
                 got = eng.logits[i].float().cpu()
                 errs.append((got - rl).abs().max().item() / max(rl.abs().max().item(), 1.0))
                 last[i] = int(rl.argmax())
+    errs.sort()
+    if indexer and not forced:
+        assert errs[len(errs) // 2] < 0.15 and errs[-1] < 0.4, errs
+    else:
         # the absorbed form rounds at different points than the oracle's expanded form, so a near-tie in the
         # sigmoid router can pick another expert for a row: most rows must agree tightly, none may be far off
-        errs.sort()
         assert errs[len(errs) // 2] < 0.03 and errs[-3] < 0.05 and errs[-1] < 0.25, errs
+    if forced:
+        assert sum(agree) / len(agree) > 0.95 and min(agree) > 0.8, agree
