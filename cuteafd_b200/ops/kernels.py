@@ -530,3 +530,74 @@ def grouped_linear_fp8(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws:
     a.swap, a.dual, a.bx = int(tile_rows < 128), int(w_up is not None), tile_rows
     _fp8_common(a, xq.device, split_k)
     _n.check(_n.cuda_lib().cafd_gemm_fp8(C.byref(a), _stream()), "cafd_gemm_fp8(grouped)")
+
+
+# ---- 4-bit weights (MXFP4 / NVFP4) --------------------------------------------------------------------------
+W4_FORMATS = {"mxfp4": 2, "nvfp4": 3}
+
+
+def linear_w4(x: torch.Tensor, w: tuple, fmt: str, out: torch.Tensor | None = None, *, w_up: tuple | None = None,
+              residual: torch.Tensor | None = None, out_f32: bool = False) -> torch.Tensor:
+    """y = x @ dequant(w).T for T <= 128 rows with the weights expanded on the way into shared memory.
+    ``w`` = (packed [N, K/2] uint8, block scales [N, K/32] UE8M0 or [N, K/16] E4M3, global fp32 [1] or None);
+    ``w_up`` selects SwiGLU.  Larger batches: ``w4_dequant`` + ``linear``."""
+    T, Kd = x.shape
+    packed, scales, glob = w
+    N = packed.shape[0]
+    assert T <= 128 and Kd % 128 == 0 and packed.shape[1] * 2 == Kd and x.dtype == torch.bfloat16 and x.stride(1) == 1
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    a = _n.GemmArgs()
+    a.w0, a.w1, a.x, a.out = packed.data_ptr(), (w_up[0].data_ptr() if w_up else None), x.data_ptr(), out.data_ptr()
+    a.w_scale, a.w_scale1 = scales.data_ptr(), (w_up[1].data_ptr() if w_up else None)
+    a.residual = _ptr(residual)
+    a.status = status_word(x.device).data_ptr()
+    a.w_rows_total, a.x_rows_total = N, T
+    a.k, a.n_features, a.x_rows, a.ldo = Kd, N, T, out.stride(0)
+    a.w_rows_per_expert = N
+    a.swap, a.dual, a.bx = 1, int(w_up is not None), pick_token_tile(T)
+    a.out_f32, a.num_sms = int(out_f32), num_sms()
+    _n.check(_n.cuda_lib().cafd_gemm_w4(C.byref(a), W4_FORMATS[fmt], _ptr(glob), _ptr(w_up[2]) if w_up else None, _stream()),
+             "cafd_gemm_w4")
+    return out
+
+
+def grouped_linear_w4(x: torch.Tensor, w: tuple, fmt: str, out: torch.Tensor, tile_expert: torch.Tensor, tile_row0: torch.Tensor,
+                      num_tiles: torch.Tensor, max_tiles: int, tile_rows: int, *, w_up: tuple | None = None,
+                      row_dst: torch.Tensor | None = None, wait_flag: int | None = None, epoch: torch.Tensor | None = None,
+                      signal_flag: int | None = None, done_counter: torch.Tensor | None = None, out_ptr: int | None = None,
+                      ldo: int | None = None) -> None:
+    """Expert-grouped form: ``w`` = (packed [E, N, K/2], scales [E, N, K/g], global fp32 [E] or None); tile_rows <= 128
+    (<= 64 with ``w_up``)."""
+    packed, scales, glob = w
+    E, N, Kh = packed.shape
+    a = _n.GemmArgs()
+    a.w0, a.w1, a.x = packed.data_ptr(), (w_up[0].data_ptr() if w_up else None), x.data_ptr()
+    a.w_scale, a.w_scale1 = scales.data_ptr(), (w_up[1].data_ptr() if w_up else None)
+    a.out = out_ptr if out_ptr is not None else out.data_ptr()
+    a.row_dst = _ptr(row_dst)
+    a.tile_expert, a.tile_row0, a.num_x_tiles = tile_expert.data_ptr(), tile_row0.data_ptr(), num_tiles.data_ptr()
+    a.wait_flag, a.epoch = wait_flag, _ptr(epoch)
+    a.signal_flag, a.done_counter = signal_flag, _ptr(done_counter)
+    a.status = status_word(x.device).data_ptr()
+    a.w_rows_total, a.x_rows_total = E * N, x.shape[0]
+    a.k, a.n_features, a.x_rows = Kh * 2, N, x.shape[0]
+    a.ldo = ldo if ldo is not None else out.stride(0)
+    a.w_rows_per_expert, a.max_x_tiles = N, max_tiles
+    a.swap, a.dual, a.bx = 1, int(w_up is not None), tile_rows
+    a.num_sms = num_sms()
+    _n.check(_n.cuda_lib().cafd_gemm_w4(C.byref(a), W4_FORMATS[fmt], _ptr(glob), _ptr(w_up[2]) if w_up else None, _stream()),
+             "cafd_gemm_w4(grouped)")
+
+
+def w4_dequant(w: tuple, fmt: str, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Packed 4-bit weights -> bf16 (same leading shape, last dim K); NVFP4 folds the global scale in."""
+    packed, scales, glob = w
+    Kd = packed.shape[-1] * 2
+    rows = packed.numel() // packed.shape[-1]
+    if out is None:
+        out = torch.empty(*packed.shape[:-1], Kd, dtype=torch.bfloat16, device=packed.device)
+    rpe = packed.shape[-2] if packed.dim() == 3 else rows
+    _n.check(_n.cuda_lib().cafd_w4_dequant(packed.data_ptr(), scales.data_ptr(), _ptr(glob), out.data_ptr(), rows, Kd,
+                                           W4_FORMATS[fmt], rpe, _stream()), "w4_dequant")
+    return out

@@ -113,6 +113,19 @@ class ExpertSide:
                              epoch=epoch, signal_flag=combine_flag_ptr,
                              done_counter=self.done[0:1] if combine_flag_ptr else None)
 
+    def run_w4(self, fmt: str, w_gate, w_up, w_down, tile_rows: int, layer: int, epoch: torch.Tensor, combine_ptr: int,
+               combine_flag_ptr: int | None, wait: bool) -> None:
+        """MXFP4 / NVFP4 experts (decode-sized tiles, <= 64 rows): ``w_*`` = (packed [E, N, K/2], block scales, global
+        scales [E] or None).  Weights are expanded inside the grouped GEMMs; activations stay bf16."""
+        g = self.geo
+        assert tile_rows <= 64
+        K.grouped_linear_w4(self.slab, w_gate, fmt, self.hbuf, self.tile_expert, self.tile_row0, self.num_tiles, g.max_tiles,
+                            tile_rows, w_up=w_up, wait_flag=(self.flags.data_ptr() + 4 * layer) if wait else None,
+                            epoch=epoch if wait else None)
+        K.grouped_linear_w4(self.hbuf, w_down, fmt, self.hbuf, self.tile_expert, self.tile_row0, self.num_tiles, g.max_tiles,
+                            tile_rows, row_dst=self.row_dst, out_ptr=combine_ptr, ldo=g.hidden, epoch=epoch,
+                            signal_flag=combine_flag_ptr, done_counter=self.done[0:1] if combine_flag_ptr else None)
+
 
 class AttentionSide:
     """Buffers the attention rank owns: routes, plan output, the combine buffer and its flags."""
@@ -211,3 +224,21 @@ class LocalExchange:
         K.grouped_linear_fp8(e.h_q, e.h_s, w_down[0], w_down[1], e.hbuf, e.tile_expert, e.tile_row0, e.num_tiles,
                              g.max_tiles, tile_rows, row_dst=e.row_dst, out_ptr=self.att.combine.data_ptr(), ldo=g.hidden)
         return self.att.combine_into(out, T, 0, self.epoch, shared=shared, residual=residual, wait=False)
+
+
+def _forward_w4(self, fmt: str, x: torch.Tensor, logits: torch.Tensor, route_kw: dict, w_gate, w_up, w_down, out: torch.Tensor, *,
+                shared: torch.Tensor | None = None, residual: torch.Tensor | None = None) -> torch.Tensor:
+    """Local exchange with MXFP4 / NVFP4 experts.  Decode-sized steps run the weight-expanding grouped GEMM; larger
+    ones expand the layer's experts to bf16 once and take the bf16 path."""
+    T = x.shape[0]
+    g = self.geo
+    tile_rows = pick_tile_rows(T, g.top_k, g.num_experts)
+    if tile_rows > 64:
+        dq = [K.w4_dequant(w, fmt) for w in (w_gate, w_up, w_down)]
+        return self.forward(x, logits, route_kw, dq[0], dq[1], dq[2], out, shared=shared, residual=residual)
+    self.att.dispatch(x, logits, route_kw, tile_rows, 0, self.epoch)
+    self.exp.run_w4(fmt, w_gate, w_up, w_down, tile_rows, 0, self.epoch, self.att.combine.data_ptr(), None, wait=False)
+    return self.att.combine_into(out, T, 0, self.epoch, shared=shared, residual=residual, wait=False)
+
+
+LocalExchange.forward_w4 = _forward_w4
