@@ -51,6 +51,10 @@ def main() -> None:
     ap.add_argument("--levels", default="1,8,32")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the run invalid)")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--config", default="qwen3", choices=["qwen3", "dsv3"],
+                    help="qwen3 = the headline Qwen3-30B-A3B bf16 card; dsv3 = DeepSeek-V3 shape, MLA attention on GPU 0, "
+                         "E4M3 block-scaled experts on the other GPUs (needs 8 GPUs)")
+    ap.add_argument("--prefill-chunk", type=int, default=0)
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -73,6 +77,11 @@ def main() -> None:
     levels = tuple(int(x) for x in args.levels.split(","))
     cfg = qwen3_30b_a3b()
     valid = True
+    if args.config == "dsv3":
+        from cuteafd_b200 import deepseek_v3
+        cfg = deepseek_v3().replace(mtp_layers=0)
+        assert world > 1, "the DeepSeek-V3 shape needs expert ranks"
+
     if args.layers:
         cfg = cfg.replace(num_layers=args.layers)
         valid = False
@@ -89,7 +98,9 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=dev)
         from cuteafd_b200.parallel.afd import build_afd
         handle = build_afd(cfg, dev, rank, world, max_tokens=args.prompt_len, max_seqs=max(levels),
-                           num_pages=num_pages, pages_per_seq=pages_per_seq, use_graphs=not args.no_graphs)
+                           num_pages=num_pages, pages_per_seq=pages_per_seq, use_graphs=not args.no_graphs,
+                           expert_format="fp8" if args.config == "dsv3" else "bf16",
+                           prefill_chunk=args.prefill_chunk or None)
         gen, sync, parallelism = handle.generator, None, handle.parallelism
         torch.cuda.synchronize()
         dist.barrier()
@@ -127,8 +138,8 @@ def main() -> None:
             "metric": f"decode tok/s @ conc {headline} (8K-token prompts; conc 1/8/32, 8K-prefill tok/s and TTFT in extra)",
             "value": round(r.tok_s, 2), "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": warmup,
             "ms_per_step": round(r.ms_per_step, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": round(r.tok_s / PUBLISHED["c8"], 3) if headline == 8 else None,
-            "dtype": "bf16", "data": "synthetic (uniform random token ids, N(0,0.02) random-init weights)",
+            "vs_baseline": round(r.tok_s / PUBLISHED["c8"], 3) if headline == 8 and args.config == "qwen3" else None,
+            "dtype": "bf16" if args.config == "qwen3" else "fp8 experts (E4M3, 128x128 weight / 1x128 activation scales), bf16 attention", "data": "synthetic (uniform random token ids, N(0,0.02) random-init weights)",
             "config": {"model": cfg.name + ("" if valid else f"-{cfg.num_layers}layers-INVALID"),
                        "global_batch": headline, "seq_len": args.prompt_len, "parallelism": parallelism,
                        "l2": "inputs larger than L2 (each step streams GBs of weights and KV)",

@@ -3,6 +3,9 @@
     python -m cuteafd_b200.bench.microbench gemm --tokens 8192 --features 5120 --k 2048
     python -m cuteafd_b200.bench.microbench attn-prefill --len 8192
     python -m cuteafd_b200.bench.microbench attn-decode --seqs 32 --len 8192
+    python -m cuteafd_b200.bench.microbench mla --seqs 8 --len 8192 --qlen 1 --heads 128 [--topk 2048]
+    python -m cuteafd_b200.bench.microbench w4 --tokens 8 --features 7168 --k 2048 --fmt nvfp4
+    python -m cuteafd_b200.bench.microbench sampler --rows 32 --vocab 151936
     python -m cuteafd_b200.bench.microbench moe --tokens 1,16,128,1024,8192 --hidden 7168 --ffn 2048 \
         --experts 256 --top-k 8 --scoring sigmoid
 
@@ -165,6 +168,78 @@ def bench_moe(a, dev, pk):
         assert K.read_status() == 0
 
 
+def bench_mla(a, dev, pk):
+    """Absorbed MLA attention: decode (one row per sequence) when --qlen 1, prefill / verify rows otherwise."""
+    import math
+    heads, S, n, ql = a.heads, a.seqs, a.len, a.qlen
+    pps = (n + 63) // 64
+    pages = S * pps + 1
+    caches = [torch.randn(pages, 64, 576, device=dev).bfloat16() for _ in range(1 if pages * 64 * 576 * 2 > 150e6 else 3)]
+    table = (torch.arange(S * pps, dtype=torch.int32, device=dev) + 1).view(S, pps).contiguous()
+    T = S * ql
+    q = (torch.randn(T, heads, 576, device=dev) * 0.3).bfloat16()
+    out = torch.empty(T, heads, 512, dtype=torch.bfloat16, device=dev)
+    sl = torch.full((S,), n, dtype=torch.int32, device=dev)
+    qs = torch.arange(S + 1, dtype=torch.int32, device=dev) * ql
+    i32 = dict(dtype=torch.int32, device=dev)
+    sparse = None
+    if a.topk:
+        base = torch.arange(a.topk, **i32) * max(1, n // a.topk)
+        sparse = base[None, :].repeat(T, 1).contiguous()
+        bs, bt = K.mla_blocks([ql] * S, 128)
+    else:
+        bs, bt = K.mla_blocks([ql] * S, heads)
+    nb = len(bs)
+    tiles = (a.topk or n) // 32
+    splits = a.splits or max(1, min(K.num_sms() // max(1, nb * 2), max(1, tiles // 8), 32))
+    scratch = torch.empty(K.mla_scratch_floats(nb, splits), dtype=torch.float32, device=dev) if splits > 1 else None
+    bsd, btd = torch.tensor(bs, **i32), torch.tensor(bt, **i32)
+    scale = 1.0 / math.sqrt(192)
+    fns = [(lambda c=c: K.mla_attention(q, c, table, sl, qs, bsd, btd, out, scale, splits, scratch, sparse_idx=sparse)) for c in caches]
+    ms = time_graph(fns * 3) if T <= 512 else time_eager(fns[0], dev, iters=a.iters)
+    kv = a.topk or n
+    avg_kv = kv if (ql == 1 or a.topk) else (n - ql / 2)
+    flops = 2.0 * T * heads * avg_kv * (576 + 512)
+    byts = (S * n if not a.topk else T * kv) * 576 * 2.0 + T * heads * (576 + 512) * 2.0
+    report(f"mla seqs={S} len={n} qlen={ql} heads={heads} topk={a.topk} splits={splits}", ms, flops, byts, pk)
+    assert K.read_status() == 0
+
+
+def bench_w4(a, dev, pk):
+    """4-bit weight GEMM at decode sizes against the bf16 kernel on the same logical weights."""
+    from ..quant import codecs
+    T, N, Kd = a.tokens, a.features, a.k
+    x = torch.randn(T, Kd, device=dev).bfloat16()
+    out = torch.empty(T, N, dtype=torch.bfloat16, device=dev)
+    copies = max(2, min(16, int(300e6 // (N * Kd // 2)) + 1))
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(N, Kd, generator=g) * 0.05
+    if a.fmt == "mxfp4":
+        pq, sq = codecs.mxfp4_quant(w)
+        ws = [(pq.to(dev).clone(), sq.to(dev).clone(), None) for _ in range(copies)]
+    else:
+        pq, sq, gq = codecs.nvfp4_quant(w)
+        ws = [(pq.to(dev).clone(), sq.view(torch.uint8).to(dev).clone(), gq.to(dev)) for _ in range(copies)]
+    ms = time_graph([(lambda w_=w_: K.linear_w4(x, w_, a.fmt, out=out)) for w_ in ws] * 2)
+    per = N * Kd // 2 + N * Kd // (32 if a.fmt == "mxfp4" else 16)
+    report(f"gemm_w4 {a.fmt} T={T} N={N} K={Kd}", ms, 2.0 * T * N * Kd, per + (T * Kd + T * N) * 2, pk)
+    wb = [(torch.randn(N, Kd, device=dev) * 0.05).bfloat16() for _ in range(max(2, copies // 4))]
+    ms_b = time_graph([(lambda w_=w_: K.linear(x, w_, out=out)) for w_ in wb] * 2)
+    report(f"gemm bf16 twin T={T} N={N} K={Kd}", ms_b, 2.0 * T * N * Kd, N * Kd * 2 + (T * Kd + T * N) * 2, pk)
+    assert K.read_status() == 0
+
+
+def bench_sampler(a, dev, pk):
+    from ..runtime.sampling import SamplingParams
+    n, V = a.rows, a.vocab
+    logits = torch.randn(n, V, device=dev) * 3
+    params = [SamplingParams(temperature=0.8, top_k=a.top_k or None, top_p=a.top_p, seed=i) for i in range(n)]
+    rows = K.pack_sample_rows(params, list(range(n))).to(dev)
+    tok = torch.empty(n, dtype=torch.int32, device=dev); st = torch.empty(n, dtype=torch.int32, device=dev)
+    ms = time_graph([lambda: K.sample_rows(logits, rows, tok, st)] * 8)
+    report(f"sample_rows rows={n} V={V} top_k={a.top_k} top_p={a.top_p}", ms, 0.0, n * V * 4.0, pk)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -183,13 +258,24 @@ def main() -> None:
     m.add_argument("--ffn", type=int, default=768); m.add_argument("--experts", type=int, default=128)
     m.add_argument("--top-k", type=int, default=8); m.add_argument("--scoring", default="softmax")
     m.add_argument("--groups", type=int, default=1); m.add_argument("--topk-groups", type=int, default=1)
-    for s in (g, p, d, m):
+    ml = sub.add_parser("mla")
+    ml.add_argument("--seqs", type=int, default=8); ml.add_argument("--len", type=int, default=8192)
+    ml.add_argument("--qlen", type=int, default=1); ml.add_argument("--heads", type=int, default=128)
+    ml.add_argument("--topk", type=int, default=0); ml.add_argument("--splits", type=int, default=0)
+    w4 = sub.add_parser("w4")
+    w4.add_argument("--tokens", type=int, default=8); w4.add_argument("--features", type=int, default=7168)
+    w4.add_argument("--k", type=int, default=2048); w4.add_argument("--fmt", default="mxfp4")
+    sm = sub.add_parser("sampler")
+    sm.add_argument("--rows", type=int, default=32); sm.add_argument("--vocab", type=int, default=151936)
+    sm.add_argument("--top-k", type=int, default=50); sm.add_argument("--top-p", type=float, default=0.9)
+    for s in (g, p, d, m, ml, w4, sm):
         s.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     pk = peaks()
-    {"gemm": bench_gemm, "attn-prefill": bench_attn_prefill, "attn-decode": bench_attn_decode, "moe": bench_moe}[a.cmd](a, dev, pk)
+    {"gemm": bench_gemm, "attn-prefill": bench_attn_prefill, "attn-decode": bench_attn_decode, "moe": bench_moe,
+     "mla": bench_mla, "w4": bench_w4, "sampler": bench_sampler}[a.cmd](a, dev, pk)
 
 
 if __name__ == "__main__":

@@ -86,12 +86,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   const unsigned long long limit = g_wait_limit_ns;
-  for (;;) {
+  for (uint32_t round = 1;; ++round) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    // a wait that already ran out elsewhere (this CTA or another) ends every later blocked wait at once
-    if (status && *reinterpret_cast<volatile uint32_t*>(status) != 0u) return false;
+    // A wait that already ran out elsewhere (this CTA or another) ends every later blocked wait soon after.
+    // The status word lives in global memory; it is looked at only once in a while, so that a waiter is not
+    // parked on a memory load at the moment its barrier completes.
+    if ((round & 255u) == 0u && status && *reinterpret_cast<volatile uint32_t*>(status) != 0u) return false;
     if (globaltimer_ns() - t0 > limit) {
       if (status) atomicCAS(status, 0u, code);
       return false;
@@ -114,6 +116,10 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uin
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(dst)), "l"(m), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
+}
+// Bring a box into L2 without touching shared memory (no barrier, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* m, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(m), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2,
                                             int c3) {
@@ -277,6 +283,12 @@ __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&t);
+}
+// 2^x on the special-function unit (about 2 ulp; -inf -> 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 

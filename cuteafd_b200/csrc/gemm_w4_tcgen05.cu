@@ -10,10 +10,12 @@
 //   warp 0      TMA producer for the activation tile (tokens on the MMA N side, tile 16..128)
 //   warp 1      MMA issuer + TMEM owner
 //   warps 2-5   epilogue (thread = feature row)
-//   warps 6-9   weight decoders: thread = one of the 128 weight rows of the tile; per stage it reads
-//               64 packed bytes (128 K values) and its scale bytes, looks byte pairs up in a shared
-//               table (byte -> two bf16), scales with one packed multiply, and writes the
-//               128-byte-swizzled rows the MMA descriptor expects
+//   warps 6-9   weight decoders: thread = one of the 128 weight rows of the tile; per stage it takes
+//               64 packed bytes (128 K values) from the raw ring and its scale bytes, looks byte pairs
+//               up in a shared table (byte -> two bf16), scales with one packed multiply, and writes
+//               the 128-byte-swizzled rows the MMA descriptor expects
+//   warp 10     TMA producer for the packed weights: a deep ring of raw 128 x 64-byte tiles, so the
+//               HBM latency is covered by bytes in flight rather than by decoder registers
 //
 // Orientation is weights-on-M only (decode, tokens <= 128 per tile); prefill-sized batches expand
 // the weights once with cafd_w4_dequant and use the bf16 kernel.  Dense and expert-grouped, with
@@ -31,7 +33,8 @@
 namespace cafd {
 
 constexpr int kW4BK = 128;           // K values per stage: 64 packed bytes per weight row
-constexpr int kW4Threads = 320;      // 10 warps
+constexpr int kW4Threads = 352;      // 11 warps
+constexpr int kW4RawBytes = 128 * 64; // one packed weight tile: 128 rows x 64 bytes
 constexpr int kW4Rows = 128;         // weight rows per tile (MMA M)
 constexpr int kW4WBytes = kW4Rows * kW4BK * 2;       // 32 KiB of bf16 per weight tile and stage
 
@@ -60,28 +63,35 @@ struct W4Cfg {
   static constexpr int kWTiles = kDual ? 2 : 1;
   static constexpr int kXBytes = kBX * kW4BK * 2;
   static constexpr int kStageBytes = kWTiles * kW4WBytes + kXBytes;
-  static constexpr int kStages = (200 * 1024 / kStageBytes) > 6 ? 6 : (200 * 1024 / kStageBytes);
+  static constexpr int kRawStages = kDual ? 3 : 6;
+  static constexpr int kRawStageBytes = kWTiles * kW4RawBytes;
+  static constexpr int kStages = ((208 * 1024 - kRawStages * kRawStageBytes) / kStageBytes) > 4
+                                     ? 4 : ((208 * 1024 - kRawStages * kRawStageBytes) / kStageBytes);
   static constexpr int kAccCols = kBX * kWTiles;
   static constexpr int kTmemCols = (2 * kAccCols <= 32) ? 32 : (2 * kAccCols <= 64) ? 64 : (2 * kAccCols <= 128) ? 128
                                    : (2 * kAccCols <= 256) ? 256 : 512;
   static constexpr int kLutBytes = 4 * 256 * 4;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kLutBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kRawStages * kRawStageBytes + kLutBytes + 1024;
   static_assert(kStages >= 2, "need two stages");
 };
 
 // kFmt: 2 = MXFP4 (UE8M0 per 32), 3 = NVFP4 (E4M3 per 16)
 template <bool kDual, int kBX, int kFmt>
 __global__ void __launch_bounds__(kW4Threads, 1)
-gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Dev p) {
+gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w0,
+               const __grid_constant__ CUtensorMap tm_w1, const W4Dev p) {
   using Cfg = W4Cfg<kDual, kBX>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint32_t* lut = reinterpret_cast<uint32_t*>(smem + Cfg::kStages * Cfg::kStageBytes);   // 4 interleaved copies
+  uint8_t* raw = smem + Cfg::kStages * Cfg::kStageBytes;                                  // packed-weight ring
+  uint32_t* lut = reinterpret_cast<uint32_t*>(raw + Cfg::kRawStages * Cfg::kRawStageBytes);   // 4 interleaved copies
 
   __shared__ uint64_t full_bar[Cfg::kStages];
   __shared__ uint64_t empty_bar[Cfg::kStages];
   __shared__ uint64_t tfull_bar[2];
   __shared__ uint64_t tempty_bar[2];
+  __shared__ uint64_t raw_full[Cfg::kRawStages];
+  __shared__ uint64_t raw_empty[Cfg::kRawStages];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int s_x_tiles;
 
@@ -92,6 +102,10 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Dev p) {
     for (int s = 0; s < Cfg::kStages; ++s) {
       mbar_init(&full_bar[s], 1 + 128);       // the TMA arrive (with its byte count) + 128 decoder threads
       mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < Cfg::kRawStages; ++s) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&raw_empty[s], 128);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&tfull_bar[s], 1);
@@ -189,41 +203,94 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Dev p) {
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------------ packed-weight TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_w0);
+      if (kDual) tma_prefetch_desc(&tm_w1);
+      int rs = 0;
+      uint32_t rphase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int xt = tile % x_tiles;
+        const int wt = tile / x_tiles;
+        const int expert = p.tile_expert ? p.tile_expert[xt] : 0;
+        const int w_row0 = expert * p.w_rows_per_expert + wt * kW4Rows;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&raw_empty[rs], rphase ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
+          uint8_t* dst = raw + rs * Cfg::kRawStageBytes;
+          mbar_expect_tx(&raw_full[rs], Cfg::kRawStageBytes);
+          tma_load_2d(dst, &tm_w0, &raw_full[rs], kb * 64, w_row0);
+          if (kDual) tma_load_2d(dst + kW4RawBytes, &tm_w1, &raw_full[rs], kb * 64, w_row0);
+          if (++rs == Cfg::kRawStages) { rs = 0; rphase ^= 1; }
+        }
+      }
+    }
   } else if (warp >= 6) {
     // ------------------------------------------------------------------ weight decoders
     const int r = threadIdx.x - 6 * 32;                    // weight row of the tile
     const uint32_t* my_lut = lut + (lane & 3) * 8;
     constexpr int kScaleBytes = kFmt == 2 ? kW4BK / 32 : kW4BK / 16;       // per row and stage
-    const size_t w_pitch = static_cast<size_t>(p.k) / 2;
     const size_t s_pitch = static_cast<size_t>(p.k) / (kFmt == 2 ? 32 : 16);
-    int stage = 0;
-    uint32_t phase = 0;
+    int stage = 0, rs = 0;
+    uint32_t phase = 0, rphase = 0;
     bool ok = true;
+    constexpr int kT = kDual ? 2 : 1;
+    constexpr int kAhead = 3;                               // scale bytes are fetched this many stages early
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
       const int xt = tile % x_tiles;
       const int wt = tile / x_tiles;
       const int expert = p.tile_expert ? p.tile_expert[xt] : 0;
       const bool valid = wt * kW4Rows + r < p.n_features;
       const size_t row = static_cast<size_t>(expert) * p.w_rows_per_expert + wt * kW4Rows + r;
-      for (int kb = 0; kb < nkb; ++kb) {
-        // loads first (they do not touch the stage), then wait for the stage to be free
-        uint4 pk[kDual ? 2 : 1][4];
-        uint32_t sc[kDual ? 2 : 1][2];
+      uint32_t sring[kAhead][kT][2];
+      auto load_scales = [&](int kb, uint32_t (&dst)[kT][2]) {
 #pragma unroll
-        for (int t = 0; t < (kDual ? 2 : 1); ++t) {
-          if (valid) {
-            const uint4* src = reinterpret_cast<const uint4*>(p.w[t] + row * w_pitch + static_cast<size_t>(kb) * 64);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) pk[t][q] = __ldg(src + q);
+        for (int t = 0; t < kT; ++t) {
+          dst[t][0] = dst[t][1] = 0u;
+          if (valid && kb < nkb) {
             const uint8_t* ss = p.s[t] + row * s_pitch + static_cast<size_t>(kb) * kScaleBytes;
-            sc[t][0] = *reinterpret_cast<const uint32_t*>(ss);
-            sc[t][1] = kScaleBytes == 8 ? *reinterpret_cast<const uint32_t*>(ss + 4) : 0u;
-          } else {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) pk[t][q] = make_uint4(0, 0, 0, 0);
-            sc[t][0] = sc[t][1] = 0u;
+            dst[t][0] = __ldg(reinterpret_cast<const uint32_t*>(ss));
+            if (kScaleBytes == 8) dst[t][1] = __ldg(reinterpret_cast<const uint32_t*>(ss + 4));
           }
         }
+      };
+#pragma unroll
+      for (int i = 0; i < kAhead; ++i) load_scales(i, sring[i]);
+      for (int kb = 0; kb < nkb; ++kb) {
+        uint4 pk[kT][4];
+        uint32_t sc[kT][2];
+#pragma unroll
+        for (int t = 0; t < kT; ++t) { sc[t][0] = sring[0][t][0]; sc[t][1] = sring[0][t][1]; }
+#pragma unroll
+        for (int i = 0; i + 1 < kAhead; ++i)
+#pragma unroll
+          for (int t = 0; t < kT; ++t) { sring[i][t][0] = sring[i + 1][t][0]; sring[i][t][1] = sring[i + 1][t][1]; }
+        load_scales(kb + kAhead, sring[kAhead - 1]);
+        if (!mbar_wait(&raw_full[rs], rphase, p.status, kTimeoutFullBarrier)) { ok = false; break; }
+        {
+          // this thread's 64 packed bytes; chunk order rotated by row pair so a quarter warp covers all banks
+          const uint8_t* rr = raw + rs * Cfg::kRawStageBytes + r * 64;
+#pragma unroll
+          for (int t = 0; t < kT; ++t)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int cq = (q + (r >> 1)) & 3;
+              const uint4 v = *reinterpret_cast<const uint4*>(rr + t * kW4RawBytes + cq * 16);
+              // place into logical position cq (select without dynamic register indexing)
+#pragma unroll
+              for (int z = 0; z < 4; ++z)
+                if (z == cq) pk[t][z] = v;
+            }
+          if (!valid) {
+#pragma unroll
+            for (int t = 0; t < kT; ++t)
+#pragma unroll
+              for (int q = 0; q < 4; ++q) pk[t][q] = make_uint4(0, 0, 0, 0);
+          }
+        }
+        mbar_arrive(&raw_empty[rs]);
+        if (++rs == Cfg::kRawStages) { rs = 0; rphase ^= 1; }
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
         uint8_t* st = smem + stage * Cfg::kStageBytes;
 #pragma unroll
@@ -346,6 +413,17 @@ static int launch_w4(const cafd_gemm_args* a, const float* g0, const float* g1, 
   CUtensorMap tx;
   int rc = cached_tmap_2d(&tx, a->x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->x_rows_total, a->k, static_cast<uint64_t>(a->k) * 2, kBX, 64);
   if (rc) return rc;
+  // packed weights: rows of K/2 bytes, 128 x 64-byte boxes, no swizzle (the decoders read whole rows)
+  CUtensorMap tw0, tw1;
+  rc = make_tmap_2d(&tw0, a->w0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->w_rows_total, a->k / 2, static_cast<uint64_t>(a->k) / 2,
+                    kW4Rows, 64, false);
+  if (rc) return rc;
+  tw1 = tw0;
+  if (kDual) {
+    rc = make_tmap_2d(&tw1, a->w1 ? a->w1 : a->w0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->w_rows_total, a->k / 2,
+                      static_cast<uint64_t>(a->k) / 2, kW4Rows, 64, false);
+    if (rc) return rc;
+  }
   W4Dev p;
   p.w[0] = static_cast<const uint8_t*>(a->w0);
   p.w[1] = static_cast<const uint8_t*>(a->w1 ? a->w1 : a->w0);
@@ -378,7 +456,7 @@ static int launch_w4(const cafd_gemm_args* a, const float* g0, const float* g1, 
     CAFD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_set = true;
   }
-  launch_pdl(kern, grid, dim3(kW4Threads), Cfg::kSmemBytes, stream, tx, p);
+  launch_pdl(kern, grid, dim3(kW4Threads), Cfg::kSmemBytes, stream, tx, tw0, tw1, p);
   return static_cast<int>(cudaGetLastError());
 }
 

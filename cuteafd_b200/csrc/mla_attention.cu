@@ -173,12 +173,22 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int a = 0; a < kAtoms; ++a) tma_load_2d(sQ + a * kMlaRows * 128, &tm_q, &q_full, a * 64, qrow);
       mla_trace(tr, 0, 1);
       const int* pt = p.page_table + static_cast<size_t>(seq) * p.max_pages;
+      // Only two tiles fit in shared memory beside the query block, which is one tile (36 KB) in flight: far
+      // too little to cover HBM latency.  The tiles further ahead are therefore pulled into L2 early, so the
+      // load that fills a freed stage pays L2 latency only.
+      constexpr int kL2Ahead = 6;
+      int pf = 2;
       for (int j = 0; j < n_tiles; ++j) {
         const int tile = t_begin + j;
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         const int pg_i = tile >> 1;
         const int page = pg_i < seq_pages ? pt[pg_i] : 0;
+        for (; pf < n_tiles && pf <= j + kL2Ahead; ++pf) {
+          const int ptile = t_begin + pf;
+          const int ppage = (ptile >> 1) < seq_pages ? pt[ptile >> 1] : 0;
+          for (int a = 0; a < kAtoms; ++a) tma_prefetch_l2_3d(&tm_c, a * 64, (ptile & 1) * kKvTile, ppage);
+        }
         if (!mbar_wait(&c_empty[st], ph ^ 1, p.status, kTimeoutEmptyBarrier)) break;
         uint8_t* cd = sC + st * kKvBytes;
         mbar_expect_tx(&c_full[st], kKvBytes);
@@ -212,7 +222,15 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       };
       if (ok) ok = issue_qk(0);
       for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) { if (!issue_qk(j + 1)) { ok = false; break; } }
+        // Next tile's scores go first when its data has landed (they overlap this tile's softmax); otherwise this
+        // tile's PV goes first, which frees its stage and starts the load after next that much earlier.
+        const int nst = (j + 1) & 1;
+        const uint32_t nph = ((j + 1) >> 1) & 1;
+        bool next_done = j + 1 >= n_tiles;
+        if (!next_done && mbar_try_wait(&c_full[nst], nph) && mbar_try_wait(&s_empty[nst], nph ^ 1)) {
+          if (!issue_qk(j + 1)) { ok = false; break; }
+          next_done = true;
+        }
         const int st = j & 1;
         if (!mbar_wait(&p_ready, j & 1, p.status, kTimeoutSoftmax)) { ok = false; break; }
         tc_fence_after();
@@ -227,6 +245,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_commit(&c_empty[st]);
         umma_commit(&pv_done);
         mla_trace(tr, 1, 10000 + j);
+        if (!next_done && !issue_qk(j + 1)) { ok = false; break; }
       }
     }
   } else {
@@ -257,10 +276,23 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         s[i] = (col0 + i < limit) ? __uint_as_float(r[i]) * p.scale_log2 : -INFINITY;
         mx = fmaxf(mx, s[i]);
       }
-      const float m_new = fmaxf(m_run, mx);
+      // The running reference m_run only moves when the tile maximum exceeds it by more than 8 (in log2
+      // units), so O is rescaled rarely; P then stays below 2^8 and the final O / l is unchanged in exact
+      // arithmetic because l accumulates with the same reference.
+      const bool move = mx > m_run + 8.0f || (m_run == -INFINITY && mx > -INFINITY);
+      const float m_new = move ? mx : m_run;
       const float base = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - base);
+      const float corr = !move ? 1.0f : (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - base);
+      float rs = 0.f;
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const uint32_t w = pack_bf16(fast_exp2(s[i] - base), fast_exp2(s[i + 1] - base));
+        rs += bf16_lo(w) + bf16_hi(w);
+        pk[i >> 1] = w;
+      }
       if (j > 0) {
+        // P of the previous tile is still being read by its PV product until this barrier completes
         if (!mbar_wait(&pv_done, (j - 1) & 1, p.status, kTimeoutTmemFull)) { ok = false; break; }
         tc_fence_after();
         if (__any_sync(0xffffffffu, corr != 1.0f)) {
@@ -274,14 +306,6 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tmem_st_32x32(tO + lane_off + c, o);
           }
         }
-      }
-      float rs = 0.f;
-      uint32_t pk[16];
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        const uint32_t w = pack_bf16(exp2f(s[i] - base), exp2f(s[i + 1] - base));
-        rs += bf16_lo(w) + bf16_hi(w);
-        pk[i >> 1] = w;
       }
       // canonical unswizzled K-major layout: core (row / 8, k / 8) at (row/8)*512 + (k/8)*128, rows 16 B apart
       uint8_t* prow = sP + (row >> 3) * 512 + (row & 7) * 16;

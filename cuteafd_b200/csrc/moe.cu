@@ -35,22 +35,18 @@ struct MoeLayoutDev {
 };
 
 // ---- router -------------------------------------------------------------------------------------
+// One warp routes one token: `row` points at its E router logits in global memory.
 template <int kPerLane>
-__global__ void __launch_bounds__(128) route_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
-                                                         int* __restrict__ out_idx, float* __restrict__ out_w, int T,
-                                                         int E, int top_k, int sigmoid, int num_groups,
-                                                         int topk_groups, int normalize, float routed_scale) {
-  pdl_wait();
-  pdl_trigger();
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (t >= T) return;
+__device__ __forceinline__ void route_row(const float* row, const float* __restrict__ bias, int* __restrict__ out_idx,
+                                          float* __restrict__ out_w, int t, int E, int top_k, int sigmoid, int num_groups,
+                                          int topk_groups, int normalize, float routed_scale) {
   const int lane = threadIdx.x & 31;
   float score[kPerLane], sel[kPerLane];
   float mx = -INFINITY;
 #pragma unroll
   for (int j = 0; j < kPerLane; ++j) {
     const int e = j * 32 + lane;
-    score[j] = e < E ? logits[static_cast<size_t>(t) * E + e] : -INFINITY;
+    score[j] = e < E ? __ldcg(row + e) : -INFINITY;     // written by other blocks (or an earlier kernel): skip L1
     mx = fmaxf(mx, score[j]);
   }
   if (sigmoid) {
@@ -160,11 +156,118 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const float* __restrict
   }
 }
 
+template <int kPerLane>
+__global__ void __launch_bounds__(128) route_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                                         int* __restrict__ out_idx, float* __restrict__ out_w, int T,
+                                                         int E, int top_k, int sigmoid, int num_groups,
+                                                         int topk_groups, int normalize, float routed_scale) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  route_row<kPerLane>(logits + static_cast<size_t>(t) * E, bias, out_idx, out_w, t, E, top_k, sigmoid, num_groups, topk_groups,
+                      normalize, routed_scale);
+}
+
+// Decode-sized batches: RMSNorm of the residual row, the router scores and the top-k selection in one
+// launch.  Grid (token, expert group): every block normalises the token's row into shared memory (block 0 of
+// the token also writes x = bf16(h * rsqrt(mean h^2 + eps) * w) to global memory for the shared expert and the
+// dispatch), computes the scores of its share of the experts (fp32 accumulation over bf16 inputs) and takes a
+// ticket; the last block of a token routes it from the scores in `logits_buf`.  `tickets` [T] must be zero on
+// entry and is zero again on exit.
+constexpr int kNormRouteMaxH = 8192;
+constexpr int kNormRouteGroups = 8;
+template <int kPerLane>
+__global__ void __launch_bounds__(256) norm_route_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ ln_w,
+                                                         float eps, const __nv_bfloat16* __restrict__ router_w,
+                                                         const float* __restrict__ bias, __nv_bfloat16* __restrict__ x_out,
+                                                         int* __restrict__ out_idx, float* __restrict__ out_w,
+                                                         float* __restrict__ logits_buf, uint32_t* __restrict__ tickets, int H,
+                                                         int E, int top_k, int sigmoid, int num_groups, int topk_groups,
+                                                         int normalize, float routed_scale) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ __align__(16) __nv_bfloat16 sx[kNormRouteMaxH];
+  __shared__ float red[8];
+  __shared__ int s_last;
+  const int t = blockIdx.x, g = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nvec = H / 8;
+  const uint4* hrow = reinterpret_cast<const uint4*>(h + static_cast<size_t>(t) * H);
+  float ss = 0.f;
+  for (int c = tid; c < nvec; c += 256) {
+    const uint4 v = hrow[c];
+    const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) ss += bf16_lo(q[e]) * bf16_lo(q[e]) + bf16_hi(q[e]) * bf16_hi(q[e]);
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float inv = rsqrtf(tot / static_cast<float>(H) + eps);
+  for (int c = tid; c < nvec; c += 256) {
+    const uint4 v = hrow[c];
+    const uint4 wv = reinterpret_cast<const uint4*>(ln_w)[c];
+    const uint32_t q[4] = {v.x, v.y, v.z, v.w}, wq[4] = {wv.x, wv.y, wv.z, wv.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[e] = pack_bf16(bf16_lo(q[e]) * inv * bf16_lo(wq[e]), bf16_hi(q[e]) * inv * bf16_hi(wq[e]));
+    const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+    reinterpret_cast<uint4*>(sx)[c] = ov;
+    if (g == 0) reinterpret_cast<uint4*>(x_out + static_cast<size_t>(t) * H)[c] = ov;
+  }
+  __syncthreads();
+  const int per = (E + kNormRouteGroups - 1) / kNormRouteGroups;
+  const int e_lo = g * per, e_hi = min(E, e_lo + per);
+  // two experts per warp pass, eight 16-byte loads of each in flight per lane
+  for (int e0 = e_lo + 2 * warp; e0 < e_hi; e0 += 16) {
+    const bool two = e0 + 1 < e_hi;
+    const uint4* wa = reinterpret_cast<const uint4*>(router_w + static_cast<size_t>(e0) * H);
+    const uint4* wb = reinterpret_cast<const uint4*>(router_w + static_cast<size_t>(two ? e0 + 1 : e0) * H);
+    float acc_a = 0.f, acc_b = 0.f;
+#pragma unroll 4
+    for (int c = lane; c < nvec; c += 32) {
+      const uint4 a = reinterpret_cast<const uint4*>(sx)[c];
+      const uint4 b0 = __ldg(wa + c), b1 = __ldg(wb + c);
+      const uint32_t qa[4] = {a.x, a.y, a.z, a.w}, q0[4] = {b0.x, b0.y, b0.z, b0.w}, q1[4] = {b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        acc_a += bf16_lo(qa[k]) * bf16_lo(q0[k]) + bf16_hi(qa[k]) * bf16_hi(q0[k]);
+        acc_b += bf16_lo(qa[k]) * bf16_lo(q1[k]) + bf16_hi(qa[k]) * bf16_hi(q1[k]);
+      }
+    }
+    acc_a = warp_sum(acc_a);
+    acc_b = warp_sum(acc_b);
+    if (lane == 0) {
+      logits_buf[static_cast<size_t>(t) * E + e0] = acc_a;
+      if (two) logits_buf[static_cast<size_t>(t) * E + e0 + 1] = acc_b;
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const uint32_t prev = atomicAdd(tickets + t, 1u);
+    s_last = prev == gridDim.y - 1 ? 1 : 0;
+    if (s_last) tickets[t] = 0;
+  }
+  __syncthreads();
+  if (s_last && warp == 0) {
+    __threadfence();
+    route_row<kPerLane>(logits_buf + static_cast<size_t>(t) * E, bias, out_idx, out_w, t, E, top_k, sigmoid, num_groups,
+                        topk_groups, normalize, routed_scale);
+  }
+}
+
 // ---- plan -----------------------------------------------------------------------------------------
 // One CTA.  idx [T, k].  dest_row [T*k] (local) receives each entry's row in its owner's slab.
+// With `x` given (small steps) the same block also copies the rows into the owners' slabs and raises their
+// flags, which saves the separate dispatch launch.
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ idx, int T, int top_k, int E,
                                                         int tile_rows, MoeLayoutDev L, int* __restrict__ dest_row,
-                                                        int* __restrict__ expert_count_out, uint32_t* status) {
+                                                        int* __restrict__ expert_count_out, uint32_t* status,
+                                                        const uint4* __restrict__ x, int row_vec, const uint32_t* epoch) {
   pdl_wait();
   pdl_trigger();
   __shared__ int counts[kMaxExperts];
@@ -250,6 +353,37 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
       if (seg_off[e] + pos < L.max_rows) row_dst[seg_off[e] + pos] = -1;
     if (expert_count_out) expert_count_out[e] += counts[e];
   }
+  if (x) {
+    __syncthreads();                      // dest_row of every entry is written (same block: visible after the barrier)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int i = warp; i < n; i += warps) {
+      const int row = dest_row[i];
+      const int e = idx[i];
+      if (row < 0 || e < 0 || e >= E) continue;
+      const int r = rank_of[e];
+      const uint4* src = x + static_cast<size_t>(i / top_k) * row_vec;
+      uint4* dst = reinterpret_cast<uint4*>(L.slab[r]) + static_cast<size_t>(row) * row_vec;
+      for (int c0 = 0; c0 < row_vec; c0 += 256) {          // eight loads in flight per lane, then the stores
+        uint4 v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int c = c0 + lane + 32 * k;
+          if (c < row_vec) v[k] = __ldg(src + c);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int c = c0 + lane + 32 * k;
+          if (c < row_vec) dst[c] = v[k];
+        }
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t ep = *epoch;
+      for (int r = 0; r < L.n_ranks; ++r) st_release_sys(L.flag[r], ep);
+    }
+  }
 }
 
 // ---- dispatch -------------------------------------------------------------------------------------
@@ -293,10 +427,14 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint4* __restric
                                                           const uint4* __restrict__ shared_out,
                                                           const uint4* __restrict__ residual, uint4* __restrict__ out,
                                                           int T, int top_k, int row_vec, const uint32_t* flags,
-                                                          int n_flags, const uint32_t* epoch, uint32_t* status) {
+                                                          int n_flags, const uint32_t* epoch, uint32_t* status,
+                                                          const uint4* __restrict__ norm_w, float eps,
+                                                          uint4* __restrict__ x_out) {
   pdl_wait();
   pdl_trigger();
   __shared__ int s_ok;
+  __shared__ uint4 s_row[1024];          // the rounded output row, when the next layer's RMSNorm is fused in
+  __shared__ float s_red[8];
   if (threadIdx.x == 0) {
     bool ok = true;
     if (flags) {
@@ -307,7 +445,9 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint4* __restric
   }
   __syncthreads();
   if (!s_ok) return;
+  const bool fuse_norm = norm_w != nullptr && row_vec <= 1024;
   for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    float ss = 0.f;
     for (int c = threadIdx.x; c < row_vec; c += blockDim.x) {
       float acc[8];
 #pragma unroll
@@ -334,8 +474,35 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint4* __restric
 #pragma unroll
         for (int e = 0; e < 4; ++e) { acc[2 * e] += bf16_lo(q[e]); acc[2 * e + 1] += bf16_hi(q[e]); }
       }
-      out[static_cast<size_t>(t) * row_vec + c] = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]),
-                                                             pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+      const uint4 ov = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]),
+                                  pack_bf16(acc[6], acc[7]));
+      out[static_cast<size_t>(t) * row_vec + c] = ov;
+      if (fuse_norm) {
+        s_row[c] = ov;
+        const uint32_t q[4] = {ov.x, ov.y, ov.z, ov.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss += bf16_lo(q[e]) * bf16_lo(q[e]) + bf16_hi(q[e]) * bf16_hi(q[e]);
+      }
+    }
+    if (fuse_norm) {
+      // x = RMSNorm(out row) with the next layer's weight: the row is normalised from its rounded bf16 values,
+      // exactly what a separate norm kernel would read back
+      ss = warp_sum(ss);
+      __syncthreads();
+      if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      float tot = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) tot += s_red[i];
+      const float inv = rsqrtf(tot / static_cast<float>(row_vec * 8) + eps);
+      for (int c = threadIdx.x; c < row_vec; c += blockDim.x) {
+        const uint4 v = s_row[c], wv = norm_w[c];
+        const uint32_t q[4] = {v.x, v.y, v.z, v.w}, wq[4] = {wv.x, wv.y, wv.z, wv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[e] = pack_bf16(bf16_lo(q[e]) * inv * bf16_lo(wq[e]), bf16_hi(q[e]) * inv * bf16_hi(wq[e]));
+        x_out[static_cast<size_t>(t) * row_vec + c] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
     }
   }
 }
@@ -404,7 +571,41 @@ int cafd_moe_plan(const int* idx, int T, int top_k, int E, int tile_rows, const 
                   int* dest_row, int* expert_count, uint32_t* status, cafd_stream_t s) {
   if (E > kMaxExperts || layout->n_ranks < 1 || layout->n_ranks > kMaxRanks) return -10;
   launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(s), idx, T, top_k, E, tile_rows, to_dev(layout), dest_row,
-                                                               expert_count, status);
+             expert_count, status, static_cast<const uint4*>(nullptr), 0, static_cast<const uint32_t*>(nullptr));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Plan and dispatch in one launch (one block): for steps with few (token, slot) rows.
+int cafd_moe_plan_dispatch(const int* idx, int T, int top_k, int E, int tile_rows, const cafd_moe_layout* layout,
+                           int* dest_row, int* expert_count, uint32_t* status, const void* x, int H, const uint32_t* epoch,
+                           cafd_stream_t s) {
+  if (E > kMaxExperts || layout->n_ranks < 1 || layout->n_ranks > kMaxRanks || !x || !epoch || H % 8) return -10;
+  launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(s), idx, T, top_k, E, tile_rows, to_dev(layout), dest_row,
+             expert_count, status, static_cast<const uint4*>(x), H / 8, epoch);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// RMSNorm + router scores + top-k for decode-sized batches.  logits_buf [T, E] fp32 receives the scores;
+// tickets [T] uint32 must be zero (the kernel leaves them zero).
+int cafd_norm_route(const void* h, const void* ln_w, float eps, const void* router_w, const float* bias, void* x_out,
+                    int* out_idx, float* out_w, float* logits_buf, uint32_t* tickets, int T, int H, int E, int top_k, int sigmoid,
+                    int num_groups, int topk_groups, int normalize, float routed_scale, cafd_stream_t s) {
+  if (T <= 0) return 0;
+  if (E > kMaxExperts || top_k > 32 || num_groups > 32 || (num_groups > 1 && E % num_groups) || H % 8 || H > kNormRouteMaxH ||
+      !logits_buf || !tickets)
+    return -10;
+  cudaStream_t st = static_cast<cudaStream_t>(s);
+#define CAFD_NROUTE(N)                                                                                                        \
+  launch_pdl(norm_route_kernel<N>, dim3(T, kNormRouteGroups), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(h),          \
+             static_cast<const __nv_bfloat16*>(ln_w), eps, static_cast<const __nv_bfloat16*>(router_w), bias,                 \
+             static_cast<__nv_bfloat16*>(x_out), out_idx, out_w, logits_buf, tickets, H, E, top_k, sigmoid, num_groups,        \
+             topk_groups, normalize, routed_scale)
+  if (E <= 32) CAFD_NROUTE(1);
+  else if (E <= 64) CAFD_NROUTE(2);
+  else if (E <= 128) CAFD_NROUTE(4);
+  else if (E <= 256) CAFD_NROUTE(8);
+  else CAFD_NROUTE(16);
+#undef CAFD_NROUTE
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -427,7 +628,21 @@ int cafd_moe_combine(const void* buf, const float* w, const void* shared_out, co
   int blocks = T < 1 ? 1 : (T > 4096 ? 4096 : T);
   launch_pdl(moe_combine_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(s), 
       static_cast<const uint4*>(buf), w, static_cast<const uint4*>(shared_out), static_cast<const uint4*>(residual),
-      static_cast<uint4*>(out), T, top_k, H / 8, flags, n_flags, epoch, status);
+      static_cast<uint4*>(out), T, top_k, H / 8, flags, n_flags, epoch, status, static_cast<const uint4*>(nullptr), 0.f,
+      static_cast<uint4*>(nullptr));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Combine with the next RMSNorm fused in: x_out = RMSNorm(out) * norm_w (H <= 8192).
+int cafd_moe_combine_norm(const void* buf, const float* w, const void* shared_out, const void* residual, void* out, int T,
+                          int top_k, int H, const uint32_t* flags, int n_flags, const uint32_t* epoch, uint32_t* status,
+                          const void* norm_w, float eps, void* x_out, cafd_stream_t s) {
+  if (H % 8 || H > 8192 || !norm_w || !x_out) return -10;
+  int blocks = T < 1 ? 1 : (T > 4096 ? 4096 : T);
+  launch_pdl(moe_combine_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(s),
+      static_cast<const uint4*>(buf), w, static_cast<const uint4*>(shared_out), static_cast<const uint4*>(residual),
+      static_cast<uint4*>(out), T, top_k, H / 8, flags, n_flags, epoch, status, static_cast<const uint4*>(norm_w), eps,
+      static_cast<uint4*>(x_out));
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -21,7 +21,6 @@ namespace cafd {
 
 constexpr int kSampleThreads = 1024;
 constexpr float kGreedyEps = 1.0e-5f;
-constexpr double kMassOne = 17592186044416.0;   // 2^44
 
 struct SampleRow {          // 64 bytes
   float temperature, top_p, min_p;
@@ -77,13 +76,33 @@ __device__ Cut select_prefix(const Cand& cand, int V, Cut cut, bool by_mass, dou
     const int shift = 24 - 8 * level;
     if (tid < 256) sh.hist[tid] = 0;
     __syncthreads();
-    for (int i = tid; i < V; i += kSampleThreads) {
-      float xp; unsigned long long m;
-      if (!cand(i, xp, m)) continue;
+    for (int i0 = 0; i0 < V; i0 += kSampleThreads) {      // warp-uniform trip count
+      const int i = i0 + tid;
+      float xp = 0.f; unsigned long long m = 0;
+      bool active = i < V && cand(i, xp, m);
       const uint32_t key = order_key(xp);
-      if (!(key > cut.key || (key == cut.key && i <= cut.id))) continue;
-      if (level > 0 && (key >> (shift + 8)) != prefix) continue;
-      atomicAdd(&sh.hist[(key >> shift) & 255u], by_mass ? m : 1ull);
+      active = active && (key > cut.key || (key == cut.key && i <= cut.id));
+      if (level > 0) active = active && (key >> (shift + 8)) == prefix;
+      const uint32_t bin = (key >> shift) & 255u;
+      const unsigned long long val = by_mass ? m : 1ull;
+      if (level == 0) {
+        // the top byte (sign + high exponent bits) takes a handful of values: combine the lanes of a warp
+        // that share a bin before touching shared memory, or the atomics serialise on two or three words
+        unsigned remaining = __ballot_sync(0xffffffffu, active);
+        while (remaining) {
+          const int leader = __ffs(remaining) - 1;
+          const uint32_t b = __shfl_sync(0xffffffffu, bin, leader);
+          const bool mine = active && bin == b;
+          const unsigned same = __ballot_sync(0xffffffffu, mine);
+          unsigned long long v = mine ? val : 0ull;
+#pragma unroll
+          for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+          if ((tid & 31) == leader) atomicAdd(&sh.hist[b], v);
+          remaining &= ~same;
+        }
+      } else if (active) {
+        atomicAdd(&sh.hist[bin], val);
+      }
     }
     __syncthreads();
     if (tid < 256) sh.suffix[tid] = sh.hist[tid];
@@ -234,7 +253,9 @@ __global__ void __launch_bounds__(kSampleThreads) sample_rows_kernel(const float
     if (!allowed(i)) return false;
     xp = x[i] / temp;
     if (use_minp && !(xp >= thresh)) return false;
-    m = static_cast<unsigned long long>(llrint(exp(static_cast<double>(xp) - static_cast<double>(maxp)) * kMassOne));
+    // probability mass relative to the best token as a 2^-44 fixed-point integer (exp on the special-function
+    // unit: the same input always gives the same bits, which is all the selection needs)
+    m = __float2ull_rn(fast_exp2((xp - maxp) * 1.4426950408889634f) * 17592186044416.0f);
     return true;
   };
   Cut cut{0u, 0x7fffffff};

@@ -209,25 +209,40 @@ class GqaMoeEngine:
         K.linear(ws.attn[:T].view(T, -1), L.wo, out=ws.h[:T], residual=ws.h[:T])
         self.launches += 1
 
-    def _ffn(self, i: int, T: int) -> None:
+    FUSED_ROUTE_TOKENS = 64         # steps up to this many tokens run RMSNorm + router + top-k as one launch
+
+    def _ffn(self, i: int, T: int, next_norm: torch.Tensor | None) -> bool:
+        """Post-attention norm + FFN of layer i.  Returns True when ``ws.x`` already holds the next layer's
+        normalised input (the MoE combine fused that norm in)."""
         cfg, L, ws = self.cfg, self.W.layers[i], self.ws
         if L.router is None:
+            K.rmsnorm(ws.h[:T], L.ln2, cfg.rms_eps, out=ws.x[:T])
             K.linear(ws.x[:T], L.d_gate, out=ws.ffn_d[:T], w_up=L.d_up)
             K.linear(ws.ffn_d[:T], L.d_down, out=ws.h[:T], residual=ws.h[:T])
-            self.launches += 2
-            return
+            self.launches += 3
+            return False
+        fused = T <= self.FUSED_ROUTE_TOKENS and cfg.hidden <= 8192 and hasattr(self.moe, "att")
+        logits = None
+        if fused:
+            K.norm_route(ws.h[:T], L.ln2, cfg.rms_eps, L.router, ws.x[:T], self.moe.att.idx[:T], self.moe.att.w[:T], cfg.top_k,
+                         bias=L.router_bias, **self.route_kw)
+            self.launches += 1
+        else:
+            K.rmsnorm(ws.h[:T], L.ln2, cfg.rms_eps, out=ws.x[:T])
+            logits = K.linear(ws.x[:T], L.router, out=ws.router[:T, :cfg.num_experts], out_f32=True)
+            self.launches += 3                   # norm, router scores, top-k
         shared = None
         if L.s_gate is not None:
             K.linear(ws.x[:T], L.s_gate, out=ws.ffn_s[:T], w_up=L.s_up)
             shared = K.linear(ws.ffn_s[:T], L.s_down, out=ws.shared[:T])
             self.launches += 2
-        K.linear(ws.x[:T], L.router, out=ws.router[:T, :cfg.num_experts], out_f32=True)
         kw = dict(self.route_kw, bias=L.router_bias)
         if self.pre_moe is not None:
             self.pre_moe(i)
-        self.moe.forward(ws.x[:T], ws.router[:T, :cfg.num_experts], kw, L.w_gate, L.w_up, L.w_down, ws.h[:T],
-                         shared=shared, residual=ws.h[:T])
-        self.launches += 7
+        self.moe.forward(ws.x[:T], logits, kw, L.w_gate, L.w_up, L.w_down, ws.h[:T], shared=shared, residual=ws.h[:T],
+                         norm_w=next_norm, eps=cfg.rms_eps, x_out=ws.x[:T] if next_norm is not None else None)
+        self.launches += 4 if T * cfg.top_k <= 512 else 5      # plan(+dispatch), fc1, fc2, combine
+        return next_norm is not None
 
     # ---- whole step -------------------------------------------------------------------------------
     def forward(self, b: Batch) -> torch.Tensor:
@@ -237,13 +252,15 @@ class GqaMoeEngine:
         assert T <= self.max_tokens
         K.embed(b.tokens, self.W.embed, out=ws.h[:T])
         self.launches += 1
+        have_x = False
         for i in range(cfg.num_layers):
             L = self.W.layers[i]
-            K.rmsnorm(ws.h[:T], L.ln1, cfg.rms_eps, out=ws.x[:T])
+            if not have_x:
+                K.rmsnorm(ws.h[:T], L.ln1, cfg.rms_eps, out=ws.x[:T])
+                self.launches += 1
             self._attention(i, T, b)
-            K.rmsnorm(ws.h[:T], L.ln2, cfg.rms_eps, out=ws.x[:T])
-            self._ffn(i, T)
-            self.launches += 2
+            nxt = self.W.layers[i + 1].ln1 if i + 1 < cfg.num_layers else None
+            have_x = self._ffn(i, T, nxt)
         if b.last_rows is not None:
             rows = ws.h[:T].index_select(0, b.last_rows)
         else:

@@ -251,10 +251,43 @@ def moe_meta_ints(max_tiles: int, max_rows: int) -> int:
 
 
 def moe_plan(idx: torch.Tensor, E: int, tile_rows: int, layout: "_n.MoeLayout", dest_row: torch.Tensor,
-             expert_count: torch.Tensor | None = None) -> None:
+             expert_count: torch.Tensor | None = None, x: torch.Tensor | None = None, epoch: torch.Tensor | None = None) -> None:
+    """Plan the exchange; with ``x`` (and ``epoch``) the same single-block launch also copies the rows into the owners'
+    slabs and raises their flags (steps with few rows: saves the dispatch launch)."""
     T, k = idx.shape
+    if x is not None:
+        _n.check(_n.cuda_lib().cafd_moe_plan_dispatch(idx.data_ptr(), T, k, E, tile_rows, C.byref(layout), dest_row.data_ptr(),
+                                                      _ptr(expert_count), status_word(idx.device).data_ptr(), x.data_ptr(),
+                                                      x.shape[1], epoch.data_ptr(), _stream()), "moe_plan_dispatch")
+        return
     _n.check(_n.cuda_lib().cafd_moe_plan(idx.data_ptr(), T, k, E, tile_rows, C.byref(layout), dest_row.data_ptr(),
                                          _ptr(expert_count), status_word(idx.device).data_ptr(), _stream()), "moe_plan")
+
+
+_route_scratch: dict = {}
+
+
+def norm_route(h: torch.Tensor, ln_w: torch.Tensor, eps: float, router_w: torch.Tensor, x_out: torch.Tensor, out_idx: torch.Tensor,
+               out_w: torch.Tensor, top_k: int, *, scoring: str = "softmax", bias: torch.Tensor | None = None, num_groups: int = 1,
+               topk_groups: int = 1, normalize: bool = True, routed_scale: float = 1.0,
+               logits_out: torch.Tensor | None = None) -> None:
+    """x_out = RMSNorm(h) * ln_w, router scores x_out @ router_w.T and the top-k routing of every row in one launch
+    (grid token x 8 expert groups; meant for decode-sized batches).  ``logits_out`` [T, E] fp32 receives the scores
+    (a per-device scratch is used when it is not given)."""
+    T, H = h.shape
+    E = router_w.shape[0]
+    key = h.device.index
+    sc = _route_scratch.get(key)
+    if sc is None or sc[0].shape[0] < T or sc[0].shape[1] < E:
+        sc = (torch.empty(max(T, 256), max(E, 512), dtype=torch.float32, device=h.device),
+              torch.zeros(max(T, 256), dtype=torch.int32, device=h.device))
+        _route_scratch[key] = sc
+    buf = logits_out if logits_out is not None else sc[0].view(-1)[:T * E].view(T, E)
+    assert buf.is_contiguous()
+    _n.check(_n.cuda_lib().cafd_norm_route(h.data_ptr(), ln_w.data_ptr(), eps, router_w.data_ptr(), _ptr(bias), x_out.data_ptr(),
+                                           out_idx.data_ptr(), out_w.data_ptr(), buf.data_ptr(), sc[1].data_ptr(), T, H, E, top_k,
+                                           int(scoring == "sigmoid"), num_groups, topk_groups, int(normalize), routed_scale,
+                                           _stream()), "norm_route")
 
 
 def moe_dispatch(x: torch.Tensor, idx: torch.Tensor, dest_row: torch.Tensor, layout: "_n.MoeLayout",
@@ -267,19 +300,33 @@ def moe_dispatch(x: torch.Tensor, idx: torch.Tensor, dest_row: torch.Tensor, lay
 
 def moe_combine(buf: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, shared: torch.Tensor | None = None,
                 residual: torch.Tensor | None = None, flags_ptr: int | None = None, n_flags: int = 0,
-                epoch: torch.Tensor | None = None) -> torch.Tensor:
+                epoch: torch.Tensor | None = None, norm_w: torch.Tensor | None = None, eps: float = 0.0,
+                x_out: torch.Tensor | None = None) -> torch.Tensor:
+    """out = sum_s w[t, s] * buf[t, s] + shared + residual (one rounding); with ``norm_w`` also
+    x_out = RMSNorm(out) * norm_w (the next layer's input norm) in the same launch."""
     T, k = w.shape
     H = out.shape[1]
+    if norm_w is not None and H <= 8192:
+        _n.check(_n.cuda_lib().cafd_moe_combine_norm(buf.data_ptr(), w.data_ptr(), _ptr(shared), _ptr(residual), out.data_ptr(),
+                                                     T, k, H, flags_ptr, n_flags, _ptr(epoch), status_word(out.device).data_ptr(),
+                                                     norm_w.data_ptr(), eps, x_out.data_ptr(), _stream()), "moe_combine_norm")
+        return out
     _n.check(_n.cuda_lib().cafd_moe_combine(buf.data_ptr(), w.data_ptr(), _ptr(shared), _ptr(residual), out.data_ptr(),
                                             T, k, H, flags_ptr, n_flags, _ptr(epoch),
                                             status_word(out.device).data_ptr(), _stream()), "moe_combine")
+    if norm_w is not None:
+        rmsnorm(out, norm_w, eps, out=x_out)
     return out
 
 
 # ---- attention -------------------------------------------------------------------------------------
 def attn_decode_splits(num_seqs: int, tiles_per_seq: int, Hkv: int, max_pages: int) -> int:
+    """KV splits for the decode attention kernel.  The kernel keeps one 64-token page pair in flight per CTA, so
+    HBM is only saturated with about three CTAs per SM (64 KB of shared memory each): aim for one full wave of
+    3 x SMs CTAs, and never let a split grow past ~1K tokens (measured: 8 x 8K context 46 -> 33 us, 32 x 8K
+    131 -> 99 us against the old one-CTA-per-SM rule)."""
     ctas = max(1, num_seqs * tiles_per_seq * Hkv)
-    want = max(1, (num_sms() + ctas - 1) // ctas)
+    want = max((3 * num_sms()) // ctas, (max_pages + 15) // 16, 1)
     return max(1, min(want, max(1, max_pages // 4), 32))
 
 

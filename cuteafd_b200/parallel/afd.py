@@ -92,21 +92,26 @@ class RemoteExchange:
         self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)
         self.layer = 0
 
-    def forward(self, x, logits, route_kw, w_gate, w_up, w_down, out, *, shared=None, residual=None, tile_rows=None):
+    def forward(self, x, logits, route_kw, w_gate, w_up, w_down, out, *, shared=None, residual=None, tile_rows=None,
+                norm_w=None, eps=0.0, x_out=None):
         T = x.shape[0]
         g = self.geo
         tile_rows = tile_rows or pick_tile_rows(T, g.top_k, g.num_experts)
         self.att.dispatch(x, logits, route_kw, tile_rows, self.layer, self.epoch)
-        return self.att.combine_into(out, T, self.layer, self.epoch, shared=shared, residual=residual, wait=True)
+        return self.att.combine_into(out, T, self.layer, self.epoch, shared=shared, residual=residual, wait=True,
+                                     norm_w=norm_w, eps=eps, x_out=x_out)
 
 
 class AfdAttentionEngine:
-    """Wraps a ``GqaMoeEngine`` whose MoE layers go through ``RemoteExchange``."""
+    """Wraps a single-GPU engine (GQA or MLA) whose MoE layers go through ``RemoteExchange``."""
 
     def __init__(self, cfg: ModelConfig, weights, kv, max_tokens: int, max_seqs: int, heap: SymmetricHeap,
                  lay: SymLayout, geo: ExchangeGeometry):
-        from ..models.gqa_moe import GqaMoeEngine
-        self.inner = GqaMoeEngine(cfg, weights, kv, max_tokens, max_seqs, build_moe=False)
+        if cfg.is_mla:
+            from ..models.mla_moe import MlaMoeEngine as Engine
+        else:
+            from ..models.gqa_moe import GqaMoeEngine as Engine
+        self.inner = Engine(cfg, weights, kv, max_tokens, max_seqs, build_moe=False)
         self.cfg, self.device = cfg, self.inner.device
         self.moe_layers = [i for i in range(cfg.num_layers) if cfg.is_moe_layer(i)]
         self.ex = RemoteExchange(geo, heap, lay, len(self.moe_layers), 0)
@@ -174,11 +179,17 @@ class ExpertWorker:
         self.device = dev
         self.steps_served = 0
 
-    def _step(self, tile_rows: int) -> None:
+    def _step(self, tile_rows: int, T: int) -> None:
         K.bump_epoch(self.epoch)
+        g = self.geo
+        lo, hi = g.rank_experts(self.er)
         for l, (wg, wu, wd) in enumerate(self.weights):
             flag = self.cflags_ptr + 4 * (l * _n.MAX_RANKS + self.er)
-            self.side.run(wg, wu, wd, tile_rows, l, self.epoch, self.combine_ptr, flag, wait=True)
+            if isinstance(wg, tuple):        # E4M3 values + 128x128 block scales
+                rows = min(g.max_rows, T * g.top_k + (hi - lo) * tile_rows)
+                self.side.run_fp8(wg, wu, wd, tile_rows, rows, l, self.epoch, self.combine_ptr, flag, wait=True)
+            else:
+                self.side.run(wg, wu, wd, tile_rows, l, self.epoch, self.combine_ptr, flag, wait=True)
 
     def serve(self) -> None:
         g = self.geo
@@ -188,10 +199,12 @@ class ExpertWorker:
             if op == OP_STOP:
                 return
             tile_rows = pick_tile_rows(T, g.top_k, g.num_experts)
+            if self.weights and isinstance(self.weights[0][0], tuple) and tile_rows == 128 and T * g.top_k < 64 * g.num_experts:
+                tile_rows = 64               # the fp8 kernel's weights-on-M path tops out at 64 rows
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             for _ in range(steps):
-                self._step(tile_rows)
+                self._step(tile_rows, T)
             b.record()
             self.steps_served += steps
             if op == OP_TIMED:
@@ -218,6 +231,28 @@ def random_expert_weights(cfg: ModelConfig, lo: int, hi: int, device: torch.devi
     return out
 
 
+def random_expert_weights_fp8(cfg: ModelConfig, lo: int, hi: int, device: torch.device, seed: int = 0, std: float = 0.02):
+    """Random E4M3 experts with 128x128 block scales, generated and quantised on the device one layer at a time."""
+    g = torch.Generator(device=device).manual_seed(seed * 1000 + lo)
+    n = hi - lo
+
+    def qw(rows: int, cols: int):
+        q = torch.empty(n, rows, cols, dtype=torch.float8_e4m3fn, device=device)
+        sc = torch.empty(n, rows // 128, cols // 128, dtype=torch.float32, device=device)
+        for e in range(n):
+            w = torch.empty(rows, cols, dtype=torch.float32, device=device).normal_(0.0, std, generator=g)
+            blocks = w.view(rows // 128, 128, cols // 128, 128)
+            s_ = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-12) / 448.0
+            q[e] = (blocks / s_[:, None, :, None]).view(rows, cols).to(torch.float8_e4m3fn)
+            sc[e] = s_
+        return q, sc
+    out = []
+    for i in range(cfg.num_layers):
+        if cfg.is_moe_layer(i):
+            out.append((qw(cfg.expert_ffn, cfg.hidden), qw(cfg.expert_ffn, cfg.hidden), qw(cfg.hidden, cfg.expert_ffn)))
+    return out
+
+
 @dataclass
 class AfdHandle:
     generator: object | None      # rank 0: a Generator over the attention engine
@@ -231,8 +266,9 @@ class AfdHandle:
 
 def build_afd(cfg: ModelConfig, device: torch.device, rank: int, world: int, *, max_tokens: int, max_seqs: int,
               num_pages: int, pages_per_seq: int, use_graphs: bool = True, params: dict | None = None,
-              seed: int = 0) -> AfdHandle:
-    """Create this rank's half.  ``params`` (HF-style dict) gives real weights; otherwise random."""
+              seed: int = 0, expert_format: str = "bf16", prefill_chunk: int | None = None) -> AfdHandle:
+    """Create this rank's half.  ``params`` (HF-style dict) gives real weights; otherwise random.
+    ``expert_format`` "fp8" keeps the routed experts as E4M3 with 128x128 block scales on the expert ranks."""
     os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
     n_exp = world - 1
     geo = ExchangeGeometry(cfg.hidden, cfg.expert_ffn, cfg.num_experts, cfg.top_k, max_tokens, n_exp)
@@ -240,17 +276,25 @@ def build_afd(cfg: ModelConfig, device: torch.device, rank: int, world: int, *, 
     lay = SymLayout.build(geo, n_moe)
     heap = SymmetricHeap(lay.total, device)
     par = f"afd: attention on 1 GPU + experts ep{n_exp}"
+    if expert_format != "bf16":
+        par += f" ({expert_format} experts)"
     if rank == 0:
-        from ..models.gqa_moe import GqaMoeWeights, KvCache
         from ..runtime.generate import Generator
         from ..runtime.paged import PagePool
-        if params is not None:
-            W = GqaMoeWeights.from_params(cfg, params, device, with_experts=False)
+        if cfg.is_mla:
+            from ..models.mla_moe import LatentCache as Cache
+            from ..models.mla_moe import MlaMoeWeights as Weights
         else:
-            W = GqaMoeWeights.random_init(cfg, device, seed=seed, with_experts=False)
-        kv = KvCache(cfg, num_pages, device)
+            from ..models.gqa_moe import GqaMoeWeights as Weights
+            from ..models.gqa_moe import KvCache as Cache
+        if params is not None:
+            W = Weights.from_params(cfg, params, device, with_experts=False)
+        else:
+            W = Weights.random_init(cfg, device, seed=seed, with_experts=False)
+        kv = Cache(cfg, num_pages, device)
         eng = AfdAttentionEngine(cfg, W, kv, max_tokens, max_seqs, heap, lay, geo)
-        gen = Generator(eng, PagePool(num_pages), pages_per_seq, max_seqs, prefill_chunk=max_tokens, use_graphs=use_graphs)
+        gen = Generator(eng, PagePool(num_pages), pages_per_seq, max_seqs, prefill_chunk=prefill_chunk or max_tokens,
+                        use_graphs=use_graphs)
         return AfdHandle(gen, None, par)
     lo, hi = geo.rank_experts(rank - 1)
     if params is not None:
@@ -261,6 +305,13 @@ def build_afd(cfg: ModelConfig, device: torch.device, rank: int, world: int, *, 
             m = f"model.layers.{i}.mlp.experts."
             ew.append(tuple(torch.stack([params[f"{m}{e}.{n}_proj.weight"].to(device=device, dtype=torch.bfloat16)
                                          for e in range(lo, hi)]).contiguous() for n in ("gate", "up", "down")))
+        if expert_format == "fp8":
+            from ..quant import codecs
+            ew = [tuple((torch.stack([codecs.fp8_quant_block128(w[e].float())[0] for e in range(w.shape[0])]),
+                         torch.stack([codecs.fp8_quant_block128(w[e].float())[1] for e in range(w.shape[0])])) for w in trio)
+                  for trio in ew]
+    elif expert_format == "fp8":
+        ew = random_expert_weights_fp8(cfg, lo, hi, device, seed)
     else:
         ew = random_expert_weights(cfg, lo, hi, device, seed)
     return AfdHandle(None, ExpertWorker(cfg, ew, heap, lay, geo, rank, use_graphs), par)

@@ -158,23 +158,32 @@ class AttentionSide:
         self._rank_ptrs[r] = (slab_ptr, meta_ptr, flags_ptr)
         self.layout.slab[r], self.layout.meta[r] = slab_ptr, meta_ptr
 
-    def dispatch(self, x: torch.Tensor, logits: torch.Tensor, route_kw: dict, tile_rows: int, layer: int,
+    FUSED_DISPATCH_ROWS = 512       # (token, slot) rows up to which plan and dispatch share one single-block launch
+
+    def dispatch(self, x: torch.Tensor, logits: torch.Tensor | None, route_kw: dict, tile_rows: int, layer: int,
                  epoch: torch.Tensor) -> None:
+        """Route (unless ``logits`` is None: then ``idx`` / ``w`` were already filled by ``norm_route``), plan, and
+        copy the rows into the owners' slabs."""
         T = x.shape[0]
         g = self.geo
         idx, w = self.idx[:T], self.w[:T]
-        K.route_topk(logits, g.top_k, out_idx=idx, out_w=w, **route_kw)
+        if logits is not None:
+            K.route_topk(logits, g.top_k, out_idx=idx, out_w=w, **route_kw)
         for r in range(g.n_expert_ranks):
             self.layout.flag[r] = self._rank_ptrs[r][2] + 4 * layer
-        K.moe_plan(idx, g.num_experts, tile_rows, self.layout, self.dest_row, self.expert_count)
-        K.moe_dispatch(x, idx, self.dest_row, self.layout, epoch, self.done[0:1])
+        if T * g.top_k <= self.FUSED_DISPATCH_ROWS:
+            K.moe_plan(idx, g.num_experts, tile_rows, self.layout, self.dest_row, self.expert_count, x=x, epoch=epoch)
+        else:
+            K.moe_plan(idx, g.num_experts, tile_rows, self.layout, self.dest_row, self.expert_count)
+            K.moe_dispatch(x, idx, self.dest_row, self.layout, epoch, self.done[0:1])
 
     def combine_into(self, out: torch.Tensor, T: int, layer: int, epoch: torch.Tensor, *,
-                     shared: torch.Tensor | None, residual: torch.Tensor | None, wait: bool) -> torch.Tensor:
+                     shared: torch.Tensor | None, residual: torch.Tensor | None, wait: bool,
+                     norm_w: torch.Tensor | None = None, eps: float = 0.0, x_out: torch.Tensor | None = None) -> torch.Tensor:
         g = self.geo
         flags_ptr = self.flags.data_ptr() + 4 * layer * _n.MAX_RANKS if wait else None
         return K.moe_combine(self.combine, self.w[:T], out, shared=shared, residual=residual, flags_ptr=flags_ptr,
-                             n_flags=g.n_expert_ranks if wait else 0, epoch=epoch)
+                             n_flags=g.n_expert_ranks if wait else 0, epoch=epoch, norm_w=norm_w, eps=eps, x_out=x_out)
 
 
 class LocalExchange:
@@ -190,13 +199,17 @@ class LocalExchange:
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, route_kw: dict, w_gate: torch.Tensor, w_up: torch.Tensor,
                 w_down: torch.Tensor, out: torch.Tensor, *, shared: torch.Tensor | None = None,
-                residual: torch.Tensor | None = None, tile_rows: int | None = None) -> torch.Tensor:
+                residual: torch.Tensor | None = None, tile_rows: int | None = None, norm_w: torch.Tensor | None = None,
+                eps: float = 0.0, x_out: torch.Tensor | None = None) -> torch.Tensor:
+        """``logits`` None = the routes are already in ``self.att.idx`` / ``self.att.w`` (``norm_route``).  ``norm_w`` /
+        ``x_out`` fuse the next layer's input RMSNorm into the combine."""
         T = x.shape[0]
         g = self.geo
         tile_rows = tile_rows or pick_tile_rows(T, g.top_k, g.num_experts)
         self.att.dispatch(x, logits, route_kw, tile_rows, 0, self.epoch)
         self.exp.run(w_gate, w_up, w_down, tile_rows, 0, self.epoch, self.att.combine.data_ptr(), None, wait=False)
-        return self.att.combine_into(out, T, 0, self.epoch, shared=shared, residual=residual, wait=False)
+        return self.att.combine_into(out, T, 0, self.epoch, shared=shared, residual=residual, wait=False, norm_w=norm_w,
+                                     eps=eps, x_out=x_out)
 
     def forward_fp8(self, x: torch.Tensor, logits: torch.Tensor, route_kw: dict, w_gate, w_up, w_down, out: torch.Tensor, *,
                     shared: torch.Tensor | None = None, residual: torch.Tensor | None = None,

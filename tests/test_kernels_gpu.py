@@ -263,3 +263,41 @@ def test_moe_fp8_grouped(K, T, tile):
             y = codecs.fp8_dequant_rows(hq, hs) @ deq("d")[e].T
             parts[rows, slots] = y.to(torch.bfloat16).float() * w[rows, slots][:, None]
     close(out, R.combine_slots(parts, None, res, torch.bfloat16), 3e-2, 3e-2)
+
+
+# ---- fused decode-step kernels -------------------------------------------------------------------------------
+@pytest.mark.parametrize("E,k,scoring,groups,keep,H", [(128, 8, "softmax", 1, 1, 2048), (256, 8, "sigmoid", 8, 4, 1024)])
+def test_norm_route_matches_separate_kernels(K, E, k, scoring, groups, keep, H):
+    T = 9
+    h, lw, rw = bf(T, H, seed=1), bf(H, seed=2) * 0.1 + 1.0, bf(E, H, scale=0.05, seed=3)
+    bias = (torch.randn(E, generator=torch.Generator().manual_seed(4)) * 0.01).to(dev()) if scoring == "sigmoid" else None
+    kw = dict(scoring=scoring, num_groups=groups, topk_groups=keep, normalize=True, routed_scale=1.5)
+    x_ref = K.rmsnorm(h, lw, 1e-6)
+    logits_ref = K.linear(x_ref, rw, out_f32=True)
+    idx_ref, w_ref = K.route_topk(logits_ref, k, bias=bias, **kw)
+    x = torch.empty_like(h)
+    idx = torch.empty(T, k, dtype=torch.int32, device=dev()); w = torch.empty(T, k, dtype=torch.float32, device=dev())
+    logits = torch.empty(T, E, dtype=torch.float32, device=dev())
+    K.norm_route(h, lw, 1e-6, rw, x, idx, w, k, bias=bias, logits_out=logits, **kw)
+    check_status(K)
+    assert torch.equal(x, x_ref)
+    assert (logits - logits_ref).abs().max().item() < 2e-3 * max(1.0, logits_ref.abs().max().item())
+    # same selection wherever the two score computations are not within rounding of a tie
+    same = (idx.sort(1).values == idx_ref.sort(1).values).all(1).float().mean().item()
+    assert same >= 0.8
+    rows = (idx == idx_ref).all(1)
+    assert torch.allclose(w[rows], w_ref[rows], rtol=2e-3, atol=1e-5)
+
+
+def test_combine_with_fused_norm(K):
+    T, k, H = 7, 4, 2048
+    buf, res, nw = bf(T * k, H, seed=1), bf(T, H, seed=2), bf(H, seed=3) * 0.1 + 1.0
+    w = torch.rand(T, k, generator=torch.Generator().manual_seed(5)).to(dev())
+    out_ref = torch.empty(T, H, dtype=torch.bfloat16, device=dev())
+    K.moe_combine(buf, w, out_ref, residual=res)
+    x_ref = K.rmsnorm(out_ref, nw, 1e-6)
+    out, x = torch.empty_like(out_ref), torch.empty_like(out_ref)
+    K.moe_combine(buf, w, out, residual=res, norm_w=nw, eps=1e-6, x_out=x)
+    check_status(K)
+    assert torch.equal(out, out_ref)
+    assert (x.float() - x_ref.float()).abs().max().item() <= 0.02 * x_ref.float().abs().max().item()
