@@ -36,6 +36,10 @@ class GemmArgs(C.Structure):
 
 
 MAX_RANKS = 8
+# one setter per translation unit that waits (each holds its own copy of the limit)
+WAIT_LIMIT_SETTERS = ("cafd_gemm_set_wait_limit_ns", "cafd_moe_set_wait_limit_ns", "cafd_attn_set_wait_limit_ns",
+                      "cafd_gemm_fp8_set_wait_limit_ns", "cafd_tp_set_wait_limit_ns", "cafd_mla_set_wait_limit_ns",
+                      "cafd_indexer_set_wait_limit_ns", "cafd_gemm_w4_set_wait_limit_ns")
 
 
 class MoeLayout(C.Structure):
@@ -76,8 +80,7 @@ def cuda_lib():
         _sig(lib, "cafd_gemm", [C.POINTER(GemmArgs), P])
         _sig(lib, "cafd_gemm_fp8", [C.POINTER(GemmArgs), P])
         _sig(lib, "cafd_quant_rows_fp8", [P, P, P, I, I, I, P])
-        for n in ("cafd_gemm_set_wait_limit_ns", "cafd_moe_set_wait_limit_ns", "cafd_attn_set_wait_limit_ns",
-                  "cafd_gemm_fp8_set_wait_limit_ns"):
+        for n in WAIT_LIMIT_SETTERS:
             _sig(lib, n, [C.c_ulonglong])
         _sig(lib, "cafd_embed", [P, P, P, I, I, I, P])
         _sig(lib, "cafd_rmsnorm", [P, P, P, P, I, I, F, P])

@@ -49,9 +49,10 @@ def num_sms() -> int:
 
 
 def set_wait_limit_ns(ns: int) -> None:
+    """Wall-clock limit of every bounded device wait (default 2 s), for all kernels of the library."""
     L = _n.cuda_lib()
-    for f in (L.cafd_gemm_set_wait_limit_ns, L.cafd_moe_set_wait_limit_ns, L.cafd_attn_set_wait_limit_ns):
-        _n.check(f(ns), "set_wait_limit")
+    for name in _n.WAIT_LIMIT_SETTERS:
+        _n.check(getattr(L, name)(ns), "set_wait_limit")
 
 
 # ---- GEMM ------------------------------------------------------------------------------------------

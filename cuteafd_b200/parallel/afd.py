@@ -119,6 +119,8 @@ class AfdAttentionEngine:
         self.inner.pre_moe = self._pre_moe
         self.ctrl = torch.zeros(4, dtype=torch.int64, device=self.device)
         self._announced = 0
+        from .health import HealthLatch
+        self.latch = HealthLatch()       # terminal: once tripped, no further step is launched against the expert ranks
         self.logits, self.next_tokens = self.inner.logits, self.inner.next_tokens
 
     @property
@@ -136,7 +138,13 @@ class AfdAttentionEngine:
         if not for_replay:
             self._announced += steps
 
+    def check_health(self) -> None:
+        """Between steps: fold the device status word into the latch (a wait on an expert rank's flag that ran out)."""
+        self.latch.check_device(K.read_status(reset=False), "attention rank")
+        self.latch.require()
+
     def forward(self, b):
+        self.latch.require()
         if not torch.cuda.is_current_stream_capturing():
             if self._announced == 0:
                 self.announce(b.tokens.shape[0], 1)

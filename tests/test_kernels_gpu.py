@@ -301,3 +301,26 @@ def test_combine_with_fused_norm(K):
     check_status(K)
     assert torch.equal(out, out_ref)
     assert (x.float() - x_ref.float()).abs().max().item() <= 0.02 * x_ref.float().abs().max().item()
+
+
+def test_bounded_wait_reports_timeout_and_context_survives(K):
+    """A flag that nothing ever sets: the wait gives up after its (shortened) limit, records the peer-flag code in
+    the status word and returns; later kernels run normally on the same context."""
+    from cuteafd_b200.parallel.health import HealthLatch
+    K.set_wait_limit_ns(50_000_000)
+    try:
+        flag = torch.zeros(1, dtype=torch.int32, device=dev())
+        epoch = torch.ones(1, dtype=torch.int32, device=dev())
+        K.wait_flag(flag.data_ptr(), epoch)
+        torch.cuda.synchronize()
+        status = K.read_status()
+        assert status == 5
+        latch = HealthLatch()
+        latch.check_device(status, "test wait")
+        assert not latch.ok and "peer flag" in latch.reason
+        x, w = bf(4, 256, seed=1), bf(256, seed=2)
+        y = K.rmsnorm(x, w, 1e-6)
+        torch.cuda.synchronize()
+        assert torch.isfinite(y.float()).all() and K.read_status() == 0
+    finally:
+        K.set_wait_limit_ns(2_000_000_000)
