@@ -110,6 +110,7 @@ def cuda_lib():
         _sig(lib, "cafd_mla_prep_a", [P, I, I, P, P, P, P, P, P, P, I, F, I, P])
         _sig(lib, "cafd_gemm_w4", [C.POINTER(GemmArgs), I, P, P, P])
         _sig(lib, "cafd_w4_dequant", [P, P, P, P, C.c_longlong, I, I, I, P])
+        _sig(lib, "cafd_fp8_dequant_block128", [P, P, P, C.c_longlong, I, P])
         _sig(lib, "cafd_sample_rows", [P, I, I, P, P, I, P, P, P])
         _sig(lib, "cafd_accept_prefix", [P, P, P, I, P, P, P])
         _sig(lib, "cafd_mla_q_split", [P, I, P, P, P, P, I, I, I, I, P])

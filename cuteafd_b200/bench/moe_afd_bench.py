@@ -25,8 +25,8 @@ import torch
 import torch.distributed as dist
 
 from ..ops import kernels as K
-from ..parallel.afd import SymLayout, SymmetricHeap
-from ..parallel.moe_exchange import AttentionSide, ExchangeGeometry, ExpertSide, pick_tile_rows
+from ..parallel.afd import ExpertWorker, RemoteExchange, SymLayout, SymmetricHeap
+from ..parallel.moe_exchange import ExchangeGeometry, pick_tile_rows
 from ..quant import codecs
 from .microbench import peaks
 
@@ -53,6 +53,7 @@ def main() -> None:
     ap.add_argument("--topk-groups", type=int, default=4)
     ap.add_argument("--fp8", action="store_true"); ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warm", type=int, default=3); ap.add_argument("--baseline", action="store_true")
+    ap.add_argument("--wave-tokens", type=int, default=4096, help="steps above this many tokens are exchanged in waves (0 = off)")
     a = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -62,38 +63,28 @@ def main() -> None:
     Ts = [int(t) for t in a.tokens.split(",")]
     H, I, E, k = a.hidden, a.ffn, a.experts, a.top_k
     n_exp = world - 1
-    geo = ExchangeGeometry(H, I, E, k, max(Ts), n_exp)
+    geo = ExchangeGeometry(H, I, E, k, max(Ts), n_exp, wave_tokens=a.wave_tokens if max(Ts) > a.wave_tokens > 0 else 0)
     lay = SymLayout.build(geo, 1)
     heap = SymmetricHeap(lay.total, dev)
     pk = peaks()
-    epoch = torch.zeros(1, dtype=torch.int32, device=dev)
     route_kw = dict(scoring=a.scoring, num_groups=a.groups if a.scoring == "sigmoid" else 1,
                     topk_groups=a.topk_groups if a.scoring == "sigmoid" else 1)
     g = torch.Generator(device=dev).manual_seed(rank)
     results = []
     if rank == 0:
-        combine = heap.view(lay.combine, geo.max_tokens * k * H * 2, torch.bfloat16).view(-1, H)
-        cflags = heap.view(lay.cflags, 8 * 4, torch.int32)
-        att = AttentionSide(geo, dev, combine=combine, flags=cflags, num_layers=1)
-        for r in range(n_exp):
-            base = heap.ptrs[1 + r]
-            att.bind_rank(r, base + lay.slab, base + lay.meta, base + lay.dflags)
+        ex = RemoteExchange(geo, heap, lay, 1, 0)
+        epoch = ex.epoch
     else:
         lo, hi = geo.rank_experts(rank - 1)
         wg, wu, wd = _rand_w(hi - lo, I, H, dev, g), _rand_w(hi - lo, I, H, dev, g), _rand_w(hi - lo, H, I, dev, g)
+        weights = [(wg, wu, wd)]
         if a.fp8:
-            wgq, wuq, wdq = _quant_stack(wg), _quant_stack(wu), _quant_stack(wd)
-        slab = heap.view(lay.slab, geo.max_rows * H * 2, torch.bfloat16).view(geo.max_rows, H)
-        meta = heap.view(lay.meta, geo.meta_ints * 4, torch.int32)
-        flags = heap.view(lay.dflags, 4, torch.int32)
-        exp = ExpertSide(geo, dev, slab=slab, meta=meta, flags=flags, num_layers=1)
-        combine_ptr = heap.ptrs[0] + lay.combine
-        cflag = heap.ptrs[0] + lay.cflags + 4 * (rank - 1)
+            weights = [(_quant_stack(wg), _quant_stack(wu), _quant_stack(wd))]
+        worker = ExpertWorker(None, weights, heap, lay, geo, rank)
+        epoch = worker.epoch
     dist.barrier()
     for T in Ts:
-        tile = pick_tile_rows(T, k, E)
-        if a.fp8 and tile == 128 and T * k < 64 * E:
-            tile = 64
+        tile = pick_tile_rows(min(T, geo.region().max_tokens), k, E)
         if rank == 0:
             x = torch.randn(T, H, device=dev, generator=g).bfloat16()
             res = torch.randn(T, H, device=dev, generator=g).bfloat16()
@@ -102,15 +93,13 @@ def main() -> None:
         times = []
         for it in range(a.warm + a.iters):
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            K.bump_epoch(epoch)
+            if rank == 0:
+                K.bump_epoch(epoch)
             s.record()
             if rank == 0:
-                att.dispatch(x, logits, route_kw, tile, 0, epoch)
-                att.combine_into(out, T, 0, epoch, shared=None, residual=res, wait=True)
-            elif a.fp8:
-                exp.run_fp8(wgq, wuq, wdq, tile, T * k + (hi - lo) * tile, 0, epoch, combine_ptr, cflag, wait=True)
+                ex.forward(x, logits, route_kw, None, None, None, out, residual=res)
             else:
-                exp.run(wg, wu, wd, tile, 0, epoch, combine_ptr, cflag, wait=True)
+                worker._step(T)              # bumps its own epoch
             e.record()
             torch.cuda.synchronize()
             if it >= a.warm:
@@ -128,7 +117,7 @@ def main() -> None:
         active = min(per_rank, T * k)
         w_bytes = active * 3 * H * I * (1.0 if a.fp8 else 2.0)
         target_ms = max(flops / n_exp / peak, link_bytes / (NVLINK_GBS * 1e9), w_bytes / (pk["hbm_gbs"] * 1e9)) * 1e3
-        r = {"case": f"moe_afd T={T} H={H} I={I} E={E} k={k} ep={n_exp} {'fp8' if a.fp8 else 'bf16'} tile={tile}", "ms": round(ms, 4),
+        r = {"case": f"moe_afd T={T} H={H} I={I} E={E} k={k} ep={n_exp} {'fp8' if a.fp8 else 'bf16'} tile={tile} waves={len(geo.waves(T))}", "ms": round(ms, 4),
              "nvlink_gbs_each_way": round(link_bytes / ms / 1e6, 1), "tflops": round(flops / ms / 1e9, 1),
              "roofline_target_ms": round(target_ms, 4), "roofline_frac": round(target_ms / ms, 3), "status": int(t[1]), "of": pk["kind"]}
         results.append(r)

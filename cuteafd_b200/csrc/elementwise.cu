@@ -360,3 +360,46 @@ extern "C" int cafd_bump_epoch(uint32_t* epoch, cafd_stream_t s) {
   launch_pdl(bump_epoch_kernel, dim3(1), dim3(1), 0, static_cast<cudaStream_t>(s), epoch);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---- E4M3 block-scaled weights -> bf16 ---------------------------------------------------------------------
+// q [rows, cols] e4m3 with one fp32 scale per 128 x 128 block (scales [rows/128, cols/128]); out = bf16(float(q) * scale).
+// Used by expert ranks for prefill-sized steps, where the bf16 grouped GEMM is faster than folding block scales in
+// the epilogue (reference: native/shared/cuda/fp8_block_dequant.cu:30).
+namespace cafd {
+__global__ void fp8_dequant_block128_kernel(const uint4* __restrict__ q, const float* __restrict__ scales,
+                                            __nv_bfloat16* __restrict__ out, long long rows, int cols) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;      // 16-element chunk
+  const int cpr = cols / 16;
+  if (i >= rows * cpr) return;
+  const long long row = i / cpr;
+  const int c = static_cast<int>(i - row * cpr);
+  const float s = scales[(row / 128) * (cols / 128) + (c * 16) / 128];
+  const uint4 v = q[i];
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float f[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const __nv_fp8_storage_t byte = static_cast<__nv_fp8_storage_t>((w[k] >> (8 * b)) & 0xFFu);
+      f[b] = __half2float(__half(__nv_cvt_fp8_to_halfraw(byte, __NV_E4M3))) * s;
+    }
+    o[2 * k] = pack_bf16(f[0], f[1]);
+    o[2 * k + 1] = pack_bf16(f[2], f[3]);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(out + row * cols + c * 16);
+  dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+  dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
+}  // namespace cafd
+
+extern "C" int cafd_fp8_dequant_block128(const void* q, const float* scales, void* out, long long rows, int cols,
+                                         cafd_stream_t s) {
+  if (rows <= 0) return 0;
+  if (cols % 128 || rows % 128) return -10;
+  const long long chunks = rows * (cols / 16);
+  cafd::fp8_dequant_block128_kernel<<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, static_cast<cudaStream_t>(s)>>>(
+      static_cast<const uint4*>(q), scales, static_cast<__nv_bfloat16*>(out), rows, cols);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -649,3 +649,16 @@ def w4_dequant(w: tuple, fmt: str, out: torch.Tensor | None = None) -> torch.Ten
     _n.check(_n.cuda_lib().cafd_w4_dequant(packed.data_ptr(), scales.data_ptr(), _ptr(glob), out.data_ptr(), rows, Kd,
                                            W4_FORMATS[fmt], rpe, _stream()), "w4_dequant")
     return out
+
+
+def fp8_dequant_block128(q: torch.Tensor, scales: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """E4M3 weights [..., N, K] with 128x128 block scales [..., N/128, K/128] -> bf16 (stacked experts are treated as
+    one tall matrix: N must be a multiple of 128)."""
+    Kd = q.shape[-1]
+    rows = q.numel() // Kd
+    assert q.shape[-2] % 128 == 0 and Kd % 128 == 0 and q.is_contiguous() and scales.is_contiguous()
+    if out is None:
+        out = torch.empty(q.shape, dtype=torch.bfloat16, device=q.device)
+    _n.check(_n.cuda_lib().cafd_fp8_dequant_block128(q.data_ptr(), scales.data_ptr(), out.data_ptr(), rows, Kd, _stream()),
+             "fp8_dequant_block128")
+    return out

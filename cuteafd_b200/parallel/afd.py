@@ -49,13 +49,24 @@ class SymLayout:
 
     @staticmethod
     def build(geo: ExchangeGeometry, num_layers: int) -> "SymLayout":
+        """``geo.regions`` slab regions and plan blocks (one per wave of a large step) and one flag slot per
+        (layer, region); slot = layer * regions + region."""
+        rg, n = geo.region(), geo.regions
         o = 0
-        slab = o; o = _align(o + geo.max_rows * geo.hidden * 2)
-        meta = o; o = _align(o + geo.meta_ints * 4)
-        dflags = o; o = _align(o + num_layers * 4)
+        slab = o; o = _align(o + n * SymLayout.slab_stride(geo))
+        meta = o; o = _align(o + n * SymLayout.meta_stride(geo))
+        dflags = o; o = _align(o + num_layers * n * 4)
         combine = o; o = _align(o + geo.max_tokens * geo.top_k * geo.hidden * 2)
-        cflags = o; o = _align(o + num_layers * _n.MAX_RANKS * 4)
+        cflags = o; o = _align(o + num_layers * n * _n.MAX_RANKS * 4)
         return SymLayout(slab, meta, dflags, combine, cflags, o)
+
+    @staticmethod
+    def slab_stride(geo: ExchangeGeometry) -> int:
+        return _align(geo.region().max_rows * geo.hidden * 2)
+
+    @staticmethod
+    def meta_stride(geo: ExchangeGeometry) -> int:
+        return _align(geo.region().meta_ints * 4)
 
 
 class SymmetricHeap:
@@ -78,17 +89,24 @@ class SymmetricHeap:
 
 
 class RemoteExchange:
-    """Attention-rank half: same interface as ``LocalExchange`` with experts on other GPUs."""
+    """Attention-rank half: same interface as ``LocalExchange`` with experts on other GPUs.  A step larger than
+    ``geo.wave_tokens`` goes out as several waves (own slab region / plan block / flags each)."""
 
     def __init__(self, geo: ExchangeGeometry, heap: SymmetricHeap, lay: SymLayout, num_layers: int, rank: int):
         dev = heap.buf.device
         self.geo, self.heap, self.lay = geo, heap, lay
-        combine = heap.view(lay.combine, geo.max_tokens * geo.top_k * geo.hidden * 2, torch.bfloat16).view(-1, geo.hidden)
-        cflags = heap.view(lay.cflags, num_layers * _n.MAX_RANKS * 4, torch.int32)
-        self.att = AttentionSide(geo, dev, combine=combine, flags=cflags, num_layers=num_layers)
-        for r in range(geo.n_expert_ranks):
-            base = heap.ptrs[1 + r]
-            self.att.bind_rank(r, base + lay.slab, base + lay.meta, base + lay.dflags)
+        rg, n = geo.region(), geo.regions
+        self.combine = heap.view(lay.combine, geo.max_tokens * geo.top_k * geo.hidden * 2, torch.bfloat16).view(-1, geo.hidden)
+        cflags = heap.view(lay.cflags, num_layers * n * _n.MAX_RANKS * 4, torch.int32)
+        self.sides: list[AttentionSide] = []
+        for w in range(n):
+            side = AttentionSide(rg, dev, combine=self.combine, flags=cflags, num_layers=num_layers * n)
+            for r in range(geo.n_expert_ranks):
+                base = heap.ptrs[1 + r]
+                side.bind_rank(r, base + lay.slab + w * SymLayout.slab_stride(geo), base + lay.meta + w * SymLayout.meta_stride(geo),
+                               base + lay.dflags)
+            self.sides.append(side)
+        self.att = self.sides[0]                 # routes of a single-wave step live here (``norm_route`` writes them)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)
         self.layer = 0
 
@@ -96,10 +114,25 @@ class RemoteExchange:
                 norm_w=None, eps=0.0, x_out=None):
         T = x.shape[0]
         g = self.geo
-        tile_rows = tile_rows or pick_tile_rows(T, g.top_k, g.num_experts)
-        self.att.dispatch(x, logits, route_kw, tile_rows, self.layer, self.epoch)
-        return self.att.combine_into(out, T, self.layer, self.epoch, shared=shared, residual=residual, wait=True,
-                                     norm_w=norm_w, eps=eps, x_out=x_out)
+        waves = g.waves(T)
+        n = g.regions
+        if len(waves) == 1:
+            tile_rows = tile_rows or pick_tile_rows(T, g.top_k, g.num_experts)
+            self.att.dispatch(x, logits, route_kw, tile_rows, self.layer * n, self.epoch)
+            return self.att.combine_into(out, T, self.layer * n, self.epoch, shared=shared, residual=residual, wait=True,
+                                         norm_w=norm_w, eps=eps, x_out=x_out)
+        assert logits is not None, "fused routing is for single-wave steps"
+        k = g.top_k
+        for w, (a, b) in enumerate(waves):
+            side = self.sides[w]
+            side.combine = self.combine[a * k:]
+            side.dispatch(x[a:b], logits[a:b], route_kw, pick_tile_rows(b - a, k, g.num_experts), self.layer * n + w, self.epoch)
+        for w, (a, b) in enumerate(waves):
+            self.sides[w].combine_into(out[a:b], b - a, self.layer * n + w, self.epoch,
+                                       shared=None if shared is None else shared[a:b],
+                                       residual=None if residual is None else residual[a:b], wait=True,
+                                       norm_w=norm_w, eps=eps, x_out=None if x_out is None else x_out[a:b])
+        return out
 
 
 class AfdAttentionEngine:
@@ -174,10 +207,17 @@ class ExpertWorker:
         self.cfg, self.geo, self.rank, self.er = cfg, geo, rank, rank - 1
         self.weights = expert_weights
         self.n_layers = len(expert_weights)
-        slab = heap.view(lay.slab, geo.max_rows * geo.hidden * 2, torch.bfloat16).view(geo.max_rows, geo.hidden)
-        meta = heap.view(lay.meta, geo.meta_ints * 4, torch.int32)
-        flags = heap.view(lay.dflags, self.n_layers * 4, torch.int32)
-        self.side = ExpertSide(geo, dev, slab=slab, meta=meta, flags=flags, num_layers=self.n_layers)
+        rg, n = geo.region(), geo.regions
+        flags = heap.view(lay.dflags, self.n_layers * n * 4, torch.int32)
+        self.sides: list[ExpertSide] = []
+        for w in range(n):
+            slab = heap.view(lay.slab + w * SymLayout.slab_stride(geo), rg.max_rows * geo.hidden * 2, torch.bfloat16).view(rg.max_rows, geo.hidden)
+            meta = heap.view(lay.meta + w * SymLayout.meta_stride(geo), rg.meta_ints * 4, torch.int32)
+            side = ExpertSide(rg, dev, slab=slab, meta=meta, flags=flags, num_layers=self.n_layers * n)
+            if w:
+                side.hbuf = self.sides[0].hbuf           # the waves of a step run one after the other on this rank
+            self.sides.append(side)
+        self.side = self.sides[0]
         self.combine_ptr = heap.ptrs[0] + lay.combine
         self.cflags_ptr = heap.ptrs[0] + lay.cflags
         self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -187,17 +227,28 @@ class ExpertWorker:
         self.device = dev
         self.steps_served = 0
 
-    def _step(self, tile_rows: int, T: int) -> None:
+    def _step(self, T: int) -> None:
         K.bump_epoch(self.epoch)
         g = self.geo
+        n = g.regions
         lo, hi = g.rank_experts(self.er)
+        waves = g.waves(T)
+        fp8 = bool(self.weights) and isinstance(self.weights[0][0], tuple)
         for l, (wg, wu, wd) in enumerate(self.weights):
-            flag = self.cflags_ptr + 4 * (l * _n.MAX_RANKS + self.er)
-            if isinstance(wg, tuple):        # E4M3 values + 128x128 block scales
-                rows = min(g.max_rows, T * g.top_k + (hi - lo) * tile_rows)
-                self.side.run_fp8(wg, wu, wd, tile_rows, rows, l, self.epoch, self.combine_ptr, flag, wait=True)
-            else:
-                self.side.run(wg, wu, wd, tile_rows, l, self.epoch, self.combine_ptr, flag, wait=True)
+            for w, (a, b) in enumerate(waves):
+                slot = l * n + w
+                flag = self.cflags_ptr + 4 * (slot * _n.MAX_RANKS + self.er)
+                side = self.sides[w]
+                combine_ptr = self.combine_ptr + a * g.top_k * g.hidden * 2
+                tile_rows = pick_tile_rows(b - a, g.top_k, g.num_experts)
+                if fp8:                          # E4M3 values + 128x128 block scales
+                    if tile_rows == 128 and (b - a) * g.top_k < 64 * g.num_experts:
+                        tile_rows = 64           # the fp8 kernel's weights-on-M path tops out at 64 rows
+                    rows = min(side.geo.max_rows, (b - a) * g.top_k + (hi - lo) * tile_rows)
+                    side.run_fp8(wg, wu, wd, tile_rows, rows, slot, self.epoch, combine_ptr, flag, wait=True,
+                                 reuse_dequant=w > 0)
+                else:
+                    side.run(wg, wu, wd, tile_rows, slot, self.epoch, combine_ptr, flag, wait=True)
 
     def serve(self) -> None:
         g = self.geo
@@ -206,13 +257,10 @@ class ExpertWorker:
             op, T, steps, _ = (int(v) for v in self.ctrl.tolist())
             if op == OP_STOP:
                 return
-            tile_rows = pick_tile_rows(T, g.top_k, g.num_experts)
-            if self.weights and isinstance(self.weights[0][0], tuple) and tile_rows == 128 and T * g.top_k < 64 * g.num_experts:
-                tile_rows = 64               # the fp8 kernel's weights-on-M path tops out at 64 rows
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             for _ in range(steps):
-                self._step(tile_rows, T)
+                self._step(T)
             b.record()
             self.steps_served += steps
             if op == OP_TIMED:
@@ -274,12 +322,14 @@ class AfdHandle:
 
 def build_afd(cfg: ModelConfig, device: torch.device, rank: int, world: int, *, max_tokens: int, max_seqs: int,
               num_pages: int, pages_per_seq: int, use_graphs: bool = True, params: dict | None = None,
-              seed: int = 0, expert_format: str = "bf16", prefill_chunk: int | None = None) -> AfdHandle:
+              seed: int = 0, expert_format: str = "bf16", prefill_chunk: int | None = None,
+              wave_tokens: int = 4096) -> AfdHandle:
     """Create this rank's half.  ``params`` (HF-style dict) gives real weights; otherwise random.
     ``expert_format`` "fp8" keeps the routed experts as E4M3 with 128x128 block scales on the expert ranks."""
     os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
     n_exp = world - 1
-    geo = ExchangeGeometry(cfg.hidden, cfg.expert_ffn, cfg.num_experts, cfg.top_k, max_tokens, n_exp)
+    geo = ExchangeGeometry(cfg.hidden, cfg.expert_ffn, cfg.num_experts, cfg.top_k, max_tokens, n_exp,
+                           wave_tokens=wave_tokens if max_tokens > wave_tokens else 0)
     n_moe = sum(1 for i in range(cfg.num_layers) if cfg.is_moe_layer(i))
     lay = SymLayout.build(geo, n_moe)
     heap = SymmetricHeap(lay.total, device)

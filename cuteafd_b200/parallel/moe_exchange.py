@@ -42,9 +42,34 @@ class ExchangeGeometry:
     top_k: int
     max_tokens: int
     n_expert_ranks: int = 1
+    # Waves: a step with more than ``wave_tokens`` tokens is exchanged as several independent sub-exchanges (own slab
+    # region, plan block and flags each), so that the transfer of wave w+1 overlaps the expert GEMMs of wave w and the
+    # return of wave w-1.  0 = one exchange per step.  The reference pipelines prefill the same way (units x waves,
+    # rust/crates/cuteafd-daemon/src/shared/spark_waves.rs:1188-1517).
+    wave_tokens: int = 0
 
     def rank_experts(self, r: int) -> tuple[int, int]:
         return expert_range(self.num_experts, self.n_expert_ranks, r)
+
+    @property
+    def regions(self) -> int:
+        """Slab regions (= maximum number of waves of one step)."""
+        return 1 if self.wave_tokens <= 0 else max(1, -(-self.max_tokens // self.wave_tokens))
+
+    def region(self) -> "ExchangeGeometry":
+        """Geometry of one region: what the plan / dispatch / grouped GEMM kernels of one wave see."""
+        if self.wave_tokens <= 0 or self.wave_tokens >= self.max_tokens:
+            return ExchangeGeometry(self.hidden, self.expert_ffn, self.num_experts, self.top_k, self.max_tokens, self.n_expert_ranks)
+        return ExchangeGeometry(self.hidden, self.expert_ffn, self.num_experts, self.top_k, self.wave_tokens, self.n_expert_ranks)
+
+    def waves(self, T: int) -> list[tuple[int, int]]:
+        """Token ranges of the waves of a step with T tokens (every rank derives the same list)."""
+        if self.wave_tokens <= 0 or T <= self.wave_tokens:
+            return [(0, T)]
+        n = -(-T // self.wave_tokens)
+        per = -(-T // n)
+        per = -(-per // 128) * 128                     # whole 128-row tiles per wave
+        return [(a, min(T, a + per)) for a in range(0, T, per)]
 
     @property
     def max_rows(self) -> int:
@@ -63,6 +88,7 @@ class ExchangeGeometry:
 
 class ExpertSide:
     """Buffers an expert rank owns: the receive slab, the fc1 output and the plan meta block."""
+    _dq_scratch: dict = {}           # per device: one layer's experts expanded to bf16 (shared by all regions)
 
     def __init__(self, geo: ExchangeGeometry, device: torch.device, slab: torch.Tensor | None = None,
                  meta: torch.Tensor | None = None, flags: torch.Tensor | None = None, num_layers: int = 1):
@@ -91,10 +117,24 @@ class ExpertSide:
 
 
     def run_fp8(self, w_gate, w_up, w_down, tile_rows: int, rows: int, layer: int, epoch: torch.Tensor, combine_ptr: int,
-                combine_flag_ptr: int | None, wait: bool) -> None:
+                combine_flag_ptr: int | None, wait: bool, reuse_dequant: bool = False) -> None:
         """E4M3 experts: ``w_*`` = (values [E, N, K], scales [E, N/128, K/128]).  Received rows and the
         fc1 output are quantised 1x128 here, next to the GEMMs that consume them."""
         g = self.geo
+        if tile_rows == 128:
+            # Prefill-sized step: the block-scaled kernel folds scales in its epilogue warps and falls behind the bf16
+            # kernel at large row counts, so this layer's experts are expanded to bf16 (one layer's worth of scratch,
+            # reused by every layer) and the bf16 grouped GEMMs run instead.
+            dq = ExpertSide._dq_scratch.get(w_gate[0].device)
+            if dq is None or dq[0].shape != w_gate[0].shape:
+                dq = tuple(torch.empty(w[0].shape, dtype=torch.bfloat16, device=w[0].device) for w in (w_gate, w_up, w_down))
+                ExpertSide._dq_scratch[w_gate[0].device] = dq
+            self._dq = dq
+            if not reuse_dequant:                # later waves of the same layer find the expanded weights in place
+                for w, o in zip((w_gate, w_up, w_down), self._dq):
+                    K.fp8_dequant_block128(w[0], w[1], o)
+            self.run(self._dq[0], self._dq[1], self._dq[2], tile_rows, layer, epoch, combine_ptr, combine_flag_ptr, wait)
+            return
         if not hasattr(self, "slab_q"):
             dev = self.slab.device
             self.slab_q = torch.zeros(g.max_rows, g.hidden, dtype=torch.float8_e4m3fn, device=dev)

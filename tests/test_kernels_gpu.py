@@ -324,3 +324,13 @@ def test_bounded_wait_reports_timeout_and_context_survives(K):
         assert torch.isfinite(y.float()).all() and K.read_status() == 0
     finally:
         K.set_wait_limit_ns(2_000_000_000)
+
+
+def test_fp8_dequant_block128(K):
+    from cuteafd_b200.quant import codecs
+    w = torch.randn(3, 256, 384, generator=torch.Generator().manual_seed(0)) * 0.05
+    qs = [codecs.fp8_quant_block128(w[e]) for e in range(3)]
+    q = torch.stack([a for a, _ in qs]).to(dev()); s = torch.stack([b for _, b in qs]).to(dev())
+    out = K.fp8_dequant_block128(q, s)
+    ref = torch.stack([codecs.fp8_dequant_block128(a, b) for a, b in qs])
+    assert (out.float().cpu() - ref.float()).abs().max().item() <= 0.01 * ref.abs().max().item()
