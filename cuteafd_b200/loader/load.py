@@ -108,3 +108,22 @@ def load_gqa_engine_weights(path: str, device: torch.device, with_experts: bool 
             L.d_gate, L.d_up, L.d_down = (dense(f"{m}{n}_proj") for n in ("gate", "up", "down"))
         W.layers.append(L)
     return cfg, W
+
+
+def load_engine(path: str, device: torch.device, num_pages: int, max_tokens: int, max_seqs: int):
+    """(cfg, engine) for a snapshot: the GQA engine streams its weights tensor by tensor; MLA checkpoints (and any
+    checkpoint with MTP depths) go through the dense parameter dictionary, decoded to bf16."""
+    snap = open_snapshot(path)
+    cfg = snap.cfg
+    if cfg.is_mla:
+        from ..models.mla_moe import LatentCache, MlaMoeEngine, MlaMoeWeights
+        _, params = load_params(path, dtype=torch.bfloat16)
+        W = MlaMoeWeights.from_params(cfg, params, device)
+        return cfg, MlaMoeEngine(cfg, W, LatentCache(cfg, num_pages, device), max_tokens=max_tokens, max_seqs=max_seqs)
+    from ..models.gqa_moe import GqaMoeEngine, GqaMoeWeights, KvCache
+    if cfg.mtp_layers:
+        _, params = load_params(path, dtype=torch.bfloat16)
+        W = GqaMoeWeights.from_params(cfg, params, device)
+    else:
+        _, W = load_gqa_engine_weights(path, device)
+    return cfg, GqaMoeEngine(cfg, W, KvCache(cfg, num_pages, device), max_tokens=max_tokens, max_seqs=max_seqs)

@@ -44,6 +44,34 @@ class LayerWeights:
             setattr(self, s, None)
 
 
+@dataclass
+class MtpExtras:
+    """What one multi-token-prediction depth adds around its decoder layer: the two input norms, the projection of
+    [norm(embed(x_{t+1})) | norm(h_t)] split into its two column halves, and the norm before the shared head."""
+    enorm: torch.Tensor
+    hnorm: torch.Tensor
+    w_e: torch.Tensor        # eh_proj[:, :H]
+    w_h: torch.Tensor        # eh_proj[:, H:]
+    head_norm: torch.Tensor
+
+
+def layer_is_moe(cfg: ModelConfig, i: int) -> bool:
+    return cfg.is_moe_layer(i) if i < cfg.num_layers else cfg.num_experts > 0
+
+
+def load_mtp_extras(cfg: ModelConfig, p: dict, t) -> list[MtpExtras]:
+    out = []
+    H = cfg.hidden
+    for j in range(cfg.mtp_layers):
+        pre = f"model.layers.{cfg.num_layers + j}."
+        if pre + "eh_proj.weight" not in p:
+            break
+        eh = t(pre + "eh_proj.weight")
+        out.append(MtpExtras(t(pre + "enorm.weight"), t(pre + "hnorm.weight"), eh[:, :H].contiguous(), eh[:, H:].contiguous(),
+                             t(pre + "shared_head.norm.weight")))
+    return out
+
+
 class GqaMoeWeights:
     def __init__(self, cfg: ModelConfig):
         self.cfg = cfg
@@ -51,6 +79,7 @@ class GqaMoeWeights:
         self.final_norm: torch.Tensor | None = None
         self.lm_head: torch.Tensor | None = None
         self.layers: list[LayerWeights] = []
+        self.mtp: list[MtpExtras] = []
 
     @staticmethod
     def from_params(cfg: ModelConfig, p: dict[str, torch.Tensor], device: torch.device,
@@ -63,7 +92,8 @@ class GqaMoeWeights:
         W = GqaMoeWeights(cfg)
         W.embed, W.final_norm = t("model.embed_tokens.weight"), t("model.norm.weight")
         W.lm_head = W.embed if cfg.tie_embeddings else t("lm_head.weight")
-        for i in range(cfg.num_layers):
+        W.mtp = load_mtp_extras(cfg, p, t)
+        for i in range(cfg.num_layers + cfg.mtp_layers):     # MTP decoder layers follow the main stack
             pre, L = f"model.layers.{i}.", LayerWeights()
             a, m = pre + "self_attn.", pre + "mlp."
             L.ln1, L.ln2 = t(pre + "input_layernorm.weight"), t(pre + "post_attention_layernorm.weight")
@@ -71,7 +101,7 @@ class GqaMoeWeights:
             L.wo = t(a + "o_proj.weight")
             if cfg.qk_norm:
                 L.q_norm, L.k_norm = t(a + "q_norm.weight"), t(a + "k_norm.weight")
-            if cfg.is_moe_layer(i):
+            if layer_is_moe(cfg, i):
                 L.router = t(m + "gate.weight")
                 b = p.get(m + "gate.e_score_correction_bias")
                 L.router_bias = None if b is None else b.to(device=device, dtype=torch.float32).contiguous()
@@ -102,13 +132,14 @@ class GqaMoeWeights:
         W = GqaMoeWeights(cfg)
         W.embed, W.final_norm = w(cfg.vocab_size, H), ones(H)
         W.lm_head = W.embed if cfg.tie_embeddings else w(cfg.vocab_size, H)
-        for i in range(cfg.num_layers):
+        W.mtp = [MtpExtras(ones(H), ones(H), w(H, H), w(H, H), ones(H)) for _ in range(cfg.mtp_layers)]
+        for i in range(cfg.num_layers + cfg.mtp_layers):
             L = LayerWeights()
             L.ln1, L.ln2 = ones(H), ones(H)
             L.wqkv, L.wo = w((cfg.num_heads + 2 * cfg.num_kv_heads) * D, H), w(H, cfg.num_heads * D)
             if cfg.qk_norm:
                 L.q_norm, L.k_norm = ones(D), ones(D)
-            if cfg.is_moe_layer(i):
+            if layer_is_moe(cfg, i):
                 L.router = w(cfg.num_experts, H)
                 L.router_bias = torch.zeros(cfg.num_experts, dtype=torch.float32, device=device) if cfg.router_bias else None
                 if with_experts:
@@ -131,8 +162,9 @@ class KvCache:
     def __init__(self, cfg: ModelConfig, num_pages: int, device: torch.device):
         shape = (num_pages, PAGE, cfg.num_kv_heads, cfg.head_dim)
         self.num_pages = num_pages
-        self.k = [torch.zeros(shape, dtype=torch.bfloat16, device=device) for _ in range(cfg.num_layers)]
-        self.v = [torch.zeros(shape, dtype=torch.bfloat16, device=device) for _ in range(cfg.num_layers)]
+        n = cfg.num_layers + cfg.mtp_layers              # MTP decoder layers keep their own K/V, same pages
+        self.k = [torch.zeros(shape, dtype=torch.bfloat16, device=device) for _ in range(n)]
+        self.v = [torch.zeros(shape, dtype=torch.bfloat16, device=device) for _ in range(n)]
 
     def bytes_per_page(self) -> int:
         return 2 * len(self.k) * self.k[0][0].numel() * 2
@@ -270,6 +302,33 @@ class GqaMoeEngine:
         logits = K.linear(xn, self.W.lm_head, out=self.logits[:n], out_f32=True)
         self.launches += 2
         return logits
+
+    # ---- multi-token prediction ---------------------------------------------------------------------
+    def mtp_forward(self, j: int, b: Batch, next_tokens: torch.Tensor) -> torch.Tensor:
+        """MTP depth j right after ``forward(b)``: row t pairs the backbone's final hidden state of position t (still
+        in the workspace) with ``next_tokens[t]`` (the token that follows it), runs the depth's decoder layer with its
+        own K/V at the same positions and pages, and returns fp32 logits predicting the token after next for every row
+        (python/reference/families/qwen4/mtp.py:1-32; speculation/recurrent.rs:18-40 in the reference daemon)."""
+        cfg, ws, X = self.cfg, self.ws, self.W.mtp[j]
+        li = cfg.num_layers + j
+        T = b.tokens.shape[0]
+        if getattr(ws, "mtp_e", None) is None:
+            bf = dict(dtype=torch.bfloat16, device=self.device)
+            ws.mtp_e, ws.mtp_t = torch.empty(self.max_tokens, cfg.hidden, **bf), torch.empty(self.max_tokens, cfg.hidden, **bf)
+            self.mtp_logits = torch.empty(min(self.max_tokens, max(256, self.logits.shape[0] * 8)), cfg.vocab_size, dtype=torch.float32,
+                                          device=self.device)
+        K.rmsnorm(ws.h[:T], X.hnorm, cfg.rms_eps, out=ws.mtp_t[:T])                 # h_t before it is overwritten
+        K.embed(next_tokens, self.W.embed, out=ws.mtp_e[:T])
+        K.rmsnorm(ws.mtp_e[:T], X.enorm, cfg.rms_eps, out=ws.x[:T])
+        K.linear(ws.x[:T], X.w_e, out=ws.mtp_e[:T])
+        K.linear(ws.mtp_t[:T], X.w_h, out=ws.h[:T], residual=ws.mtp_e[:T])          # eh_proj([e | h]) as two halves
+        K.rmsnorm(ws.h[:T], self.W.layers[li].ln1, cfg.rms_eps, out=ws.x[:T])
+        self._attention(li, T, b)
+        self._ffn(li, T, None)
+        n = min(T, self.mtp_logits.shape[0])
+        K.rmsnorm(ws.h[:n], X.head_norm, cfg.rms_eps, out=ws.x[:n])
+        self.launches += 8
+        return K.linear(ws.x[:n], self.W.lm_head, out=self.mtp_logits[:n], out_f32=True)
 
     def greedy(self, logits: torch.Tensor) -> torch.Tensor:
         self.launches += 1

@@ -23,7 +23,7 @@ import torch
 from ..config import ModelConfig
 from ..ops import kernels as K
 from ..parallel.moe_exchange import ExchangeGeometry, LocalExchange
-from .gqa_moe import PAGE, Batch, GqaMoeEngine, LayerWeights
+from .gqa_moe import PAGE, Batch, GqaMoeEngine, LayerWeights, MtpExtras, layer_is_moe, load_mtp_extras
 
 REC = 576
 
@@ -41,6 +41,7 @@ class MlaMoeWeights:
         self.cfg = cfg
         self.embed = self.final_norm = self.lm_head = None
         self.layers: list[MlaLayerWeights] = []
+        self.mtp: list[MtpExtras] = []
 
     @staticmethod
     def _split_kv_b(cfg: ModelConfig, kv_b: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
@@ -58,7 +59,8 @@ class MlaMoeWeights:
         W = MlaMoeWeights(cfg)
         W.embed, W.final_norm = t("model.embed_tokens.weight"), t("model.norm.weight")
         W.lm_head = W.embed if cfg.tie_embeddings else t("lm_head.weight")
-        for i in range(cfg.num_layers):
+        W.mtp = load_mtp_extras(cfg, p, t)
+        for i in range(cfg.num_layers + cfg.mtp_layers):
             pre, L = f"model.layers.{i}.", MlaLayerWeights()
             a, m = pre + "self_attn.", pre + "mlp."
             L.ln1, L.ln2 = t(pre + "input_layernorm.weight"), t(pre + "post_attention_layernorm.weight")
@@ -73,7 +75,7 @@ class MlaMoeWeights:
                 L.wq_idx = t(a + "indexer.wq.weight")
             L.w_uk, L.w_uv = MlaMoeWeights._split_kv_b(cfg, t(a + "kv_b_proj.weight"))
             L.wo = t(a + "o_proj.weight")
-            if cfg.is_moe_layer(i):
+            if layer_is_moe(cfg, i):
                 L.router = t(m + "gate.weight")
                 b = p.get(m + "gate.e_score_correction_bias")
                 L.router_bias = None if b is None else b.to(device=device, dtype=torch.float32).contiguous()
@@ -103,7 +105,8 @@ class MlaMoeWeights:
         W = MlaMoeWeights(cfg)
         W.embed, W.final_norm = w(cfg.vocab_size, H), ones(H)
         W.lm_head = W.embed if cfg.tie_embeddings else w(cfg.vocab_size, H)
-        for i in range(cfg.num_layers):
+        W.mtp = [MtpExtras(ones(H), ones(H), w(H, H), w(H, H), ones(H)) for _ in range(cfg.mtp_layers)]
+        for i in range(cfg.num_layers + cfg.mtp_layers):
             L = MlaLayerWeights()
             L.ln1, L.ln2 = ones(H), ones(H)
             L.wqkv_a = w(cfg.q_lora_rank + REC + ((cfg.indexer_dim + cfg.indexer_heads) if cfg.indexer_heads else 0), H)
@@ -113,7 +116,7 @@ class MlaMoeWeights:
             L.wq_b = w(cfg.num_heads * cfg.qk_head_dim, cfg.q_lora_rank or H)
             L.w_uk, L.w_uv = w(cfg.num_heads, cfg.kv_lora_rank, cfg.qk_nope_dim), w(cfg.num_heads, cfg.v_head_dim, cfg.kv_lora_rank)
             L.wo = w(H, cfg.num_heads * cfg.v_head_dim)
-            if cfg.is_moe_layer(i):
+            if layer_is_moe(cfg, i):
                 L.router = w(cfg.num_experts, H)
                 L.router_bias = torch.zeros(cfg.num_experts, dtype=torch.float32, device=device) if cfg.router_bias else None
                 if with_experts:
@@ -134,9 +137,10 @@ class LatentCache:
 
     def __init__(self, cfg: ModelConfig, num_pages: int, device: torch.device):
         self.num_pages = num_pages
-        self.c = [torch.zeros(num_pages, PAGE, REC, dtype=torch.bfloat16, device=device) for _ in range(cfg.num_layers)]
+        n = cfg.num_layers + cfg.mtp_layers
+        self.c = [torch.zeros(num_pages, PAGE, REC, dtype=torch.bfloat16, device=device) for _ in range(n)]
         # index keys of the lightning indexer, paged like the latent records
-        self.idx = ([torch.zeros(num_pages, PAGE, cfg.indexer_dim, dtype=torch.bfloat16, device=device) for _ in range(cfg.num_layers)]
+        self.idx = ([torch.zeros(num_pages, PAGE, cfg.indexer_dim, dtype=torch.bfloat16, device=device) for _ in range(n)]
                     if cfg.indexer_heads else [])
 
     def bytes_per_page(self) -> int:

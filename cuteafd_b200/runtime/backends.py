@@ -40,7 +40,34 @@ class OracleBackend:
         self.steps = 0
         self.fail_on_step = fail_on_step          # host-side fault injection: the N-th verify raises
         self.quarantined: list[_Handle] = []
-        self._sel = None
+        self.has_mtp = cfg.mtp_layers > 0 and f"model.layers.{cfg.num_layers}.eh_proj.weight" in params
+        self.last_mtp: list[int] | None = None
+        if self.has_mtp:
+            self.verify_select = self._verify_select     # selection next to the model, as on the GPU backend
+
+    def _verify_select(self, handles: list[_Handle], rows: list[list[int]], params: list, positions: list[int]):
+        """Forward, exact selection and the MTP depth on the same rows (the oracle of ``EngineBackend.verify_select``)."""
+        from . import sampling
+        self.steps += 1
+        if self.fail_on_step is not None and self.steps == self.fail_on_step:
+            raise RuntimeError("injected worker failure")
+        toks, status, mtp, off = [], [], [], 0
+        for h, r in zip(handles, rows):
+            self.table.reserve(h.seq, h.seq.kv_len + len(r))
+            start = h.seq.kv_len
+            with torch.no_grad():
+                hid = self.model.hidden_states(torch.tensor(r), h.kv)
+                logits = self.model.head(hid)
+                t, s = sampling.select_rows(logits, params[off:off + len(r)], positions[off:off + len(r)])
+                nxt = torch.tensor([max(x, 0) for x in t])
+                ml, _ = self.model.mtp_forward(0, hid, nxt, torch.arange(start, start + len(r)), h.kv)
+            toks += t; status += s
+            mtp += ml.argmax(-1).tolist()
+            off += len(r)
+            h.seq.tokens.extend(r)
+            h.seq.kv_len += len(r)
+        self.last_mtp = mtp
+        return toks, status
 
     def open(self, tokens: list[int]) -> tuple[_Handle, int]:
         from ..ref.model import KvState
@@ -63,8 +90,11 @@ class OracleBackend:
 
     def prefill(self, h: _Handle, tokens: list[int], last: bool):
         self.table.reserve(h.seq, h.seq.kv_len + len(tokens))
+        start = h.seq.kv_len
         with torch.no_grad():
             hid = self.model.hidden_states(torch.tensor(tokens), h.kv)
+            if self.has_mtp:                 # the MTP depth's K/V for the prompt (see EngineBackend.prefill)
+                self.model.mtp_forward(0, hid, torch.tensor(tokens[1:] + tokens[-1:]), torch.arange(start, start + len(tokens)), h.kv)
         h.seq.tokens.extend(tokens)
         h.seq.kv_len += len(tokens)
         return self.model.head(hid[-1:]) if last else None
@@ -122,6 +152,11 @@ class EngineBackend:
         self.max_pages = max_pages_per_seq
         self.bufs = StepBuffers(max_decode_rows * 8, max_decode_rows, max_pages_per_seq, engine.device)
         self.quarantined: list[_Handle] = []
+        self._sel = None
+        self._last_batch = None
+        self.last_mtp: list[int] | None = None
+        inner = getattr(engine, "inner", engine)
+        self.has_mtp = bool(getattr(getattr(inner, "W", None), "mtp", None)) and hasattr(engine, "mtp_forward")
 
     def _copy_page(self, src: int, dst: int) -> None:
         kv = self.engine.kv if hasattr(self.engine, "kv") else self.engine.inner.kv
@@ -150,6 +185,11 @@ class EngineBackend:
         batch = Batch(b.tokens[1][:n], b.positions[1][:n], b.slots[1][:n], b.page_table[1].view(1, self.max_pages),
                       b.seq_lens[1][:1], b.q_start[1][:2], n, True, b.last_rows[1][:1])
         logits = self.engine.forward(batch)
+        if self.has_mtp:
+            # fill the MTP depth's K/V for the prompt: position t pairs with prompt token t+1 (the chunk's last row
+            # repeats its own token: its true successor is not known yet; it only colours one draft)
+            nxt = torch.tensor(tokens[1:] + tokens[-1:], dtype=torch.int32).to(self.engine.device, non_blocking=True)
+            self.engine.mtp_forward(0, batch, nxt)
         seq.tokens.extend(tokens)
         seq.kv_len = start + n
         return logits[:1].float().cpu() if last else None
@@ -181,6 +221,7 @@ class EngineBackend:
         for h, r in zip(handles, rows):
             h.seq.tokens.extend(r)
             h.seq.kv_len += len(r)
+        self._last_batch = batch
         return logits[:T]
 
     def verify(self, handles: list[_Handle], rows: list[list[int]]) -> torch.Tensor:
@@ -201,13 +242,23 @@ class EngineBackend:
         if self._sel is None or self._sel[0].shape[0] < T:
             n = max(T, self.bufs.max_tokens)
             self._sel = (torch.empty(n, 64, dtype=torch.uint8, device=self.engine.device),
-                         torch.empty(2, n, dtype=torch.int32, device=self.engine.device),
+                         torch.zeros(3, n, dtype=torch.int32, device=self.engine.device),
                          torch.empty(n, 64, dtype=torch.uint8).pin_memory())
         dev_rec, dev_out, host_rec = self._sel
         host_rec[:T].copy_(rec)
         dev_rec[:T].copy_(host_rec[:T], non_blocking=True)
         K.sample_rows(logits, dev_rec[:T], dev_out[0, :T], dev_out[1, :T])
+        self.last_mtp = None
+        if self.has_mtp:
+            # MTP depth on the same rows: (final hidden of row t, token selected for row t) -> draft of the token after.
+            # Rows past a sequence's accepted prefix compute drafts nobody reads and K/V that the commit truncates.
+            nxt = torch.clamp_min(dev_out[0, :T], 0)
+            mtp_logits = self.engine.mtp_forward(0, self._last_batch, nxt)
+            n = mtp_logits.shape[0]
+            K.argmax(mtp_logits, out=dev_out[2, :n])
         out = dev_out[:, :T].cpu()
+        if self.has_mtp:
+            self.last_mtp = out[2].tolist()
         st = K.read_status()
         if st:
             raise RuntimeError(f"a bounded device wait ran out (status {st})")

@@ -325,6 +325,12 @@ class Scheduler:
                 continue
             n_acc, bonus = sampling.accept_prefix(sel, d)
             new = d[:n_acc] + [bonus]
+            mtp = getattr(self.be, "last_mtp", None)
+            if picked is not None and mtp is not None and hasattr(self.drafter, "offer"):
+                # the MTP depth ran on this step's rows: the row that supplied the bonus token drafts the token after it
+                row = off - len(r) + n_acc
+                if row < len(mtp):
+                    self.drafter.offer(a.req.rid, [mtp[row]])
             a.kv_len += 1 + n_acc                           # last_token + accepted drafts now have KV
             self.be.commit(a.handle, a.kv_len)
             stopped = self._emit(a, new)

@@ -296,3 +296,30 @@ class NgramDrafter:
 
     def accept(self, rid, accepted_tokens):
         self.hist.setdefault(rid, []).extend(accepted_tokens)
+
+
+class MtpDrafter:
+    """Native multi-token-prediction drafter (depth 1).  The engine runs its MTP depth right after every verify step
+    on the rows just scored, pairing each row's final hidden state with the token selected for it, so the draft for
+    the next step is ready when the step returns; the backend hands it over with ``offer``.  A draft is consumed by
+    the next ``draft`` call; verification decides, so a stale or missing draft costs speed, never correctness.
+    (The reference's "recurrent" block drafter, rust/crates/cuteafd-daemon/src/shared/speculation/recurrent.rs:18-40.)"""
+
+    def __init__(self, block: int = 1):
+        self.spec = DrafterSpec(block=block, head=False, copy=COPY_MAX_EXTRA)
+        self.pending: dict[int, list[int]] = {}
+        self.offered = 0
+
+    def offer(self, rid: int, tokens: list[int]) -> None:
+        self.pending[rid] = list(tokens)
+        self.offered += len(tokens)
+
+    def draft(self, rid, last_hidden, last_token, n):
+        toks = self.pending.pop(rid, [])
+        return toks[:n], None
+
+    def accept(self, rid, accepted_tokens):
+        pass
+
+    def forget(self, rid: int) -> None:
+        self.pending.pop(rid, None)

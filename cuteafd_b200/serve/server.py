@@ -305,24 +305,29 @@ def build_state(args) -> ServerState:
             params = init_weights(cfg, seed=0)
         be = OracleBackend(cfg, params)
     else:
-        from ..loader.load import load_gqa_engine_weights
-        from ..models.gqa_moe import GqaMoeEngine, GqaMoeWeights, KvCache
         from ..runtime.backends import EngineBackend
         dev = torch.device("cuda:0")
+        pages_per_seq = args.max_context_tokens // 64 + 2
+        num_pages = pages_per_seq * args.concurrency + 64
+        rows = args.concurrency * 8
         if snapshot:
-            cfg, W = load_gqa_engine_weights(snapshot, dev)
+            from ..loader.load import load_engine
+            cfg, eng = load_engine(snapshot, dev, num_pages, max(2048, rows), rows)
         else:
             cfg = PRESETS[args.preset or "qwen3-30b-a3b"]()
             if args.layers:
                 cfg = cfg.replace(num_layers=args.layers)
-            W = GqaMoeWeights.random_init(cfg, dev)
-        pages_per_seq = args.max_context_tokens // 64 + 2
-        num_pages = pages_per_seq * args.concurrency + 64
-        rows = args.concurrency * 8
-        eng = GqaMoeEngine(cfg, W, KvCache(cfg, num_pages, dev), max_tokens=max(2048, rows), max_seqs=rows)
+            if cfg.is_mla:
+                from ..models.mla_moe import LatentCache as Cache, MlaMoeEngine as Engine, MlaMoeWeights as Weights
+            else:
+                from ..models.gqa_moe import GqaMoeEngine as Engine, GqaMoeWeights as Weights, KvCache as Cache
+            eng = Engine(cfg, Weights.random_init(cfg, dev), Cache(cfg, num_pages, dev), max_tokens=max(2048, rows), max_seqs=rows)
         be = EngineBackend(eng, num_pages, pages_per_seq, prefill_chunk=2048, max_decode_rows=args.concurrency)
     tok = load_tokenizer(snapshot, cfg.vocab_size)
     drafter = NgramDrafter(block=4) if args.speculator in ("auto", "history", "ngram") else None
+    if args.speculator in ("auto", "mtp") and getattr(be, "has_mtp", False):
+        from ..runtime.speculation import MtpDrafter
+        drafter = MtpDrafter()              # native MTP depth of the checkpoint
     sched = Scheduler(be, max_active=args.concurrency, queue_depth=args.queue_depth, queue_wait_s=args.queue_wait,
                       drafter=drafter, eos_ids=tuple(getattr(tok, "eos_ids", ())))
     usage = UsageLog(args.usage_db) if args.usage_db else None

@@ -61,3 +61,56 @@ def test_prefill_and_decode_match_oracle(use_graphs):
                 assert err < 0.05 * max(rl.abs().max().item(), 1.0), (step, i, err)
                 last[i] = int(rl.argmax())
     assert gen.h2d_bytes > 0 and gen.d2h_bytes > 0
+
+
+@pytest.mark.parametrize("family", ["gqa", "mla"])
+def test_mtp_depth_matches_oracle(family):
+    """The multi-token-prediction depth (norms, split eh_proj, one decoder layer with its own K/V, shared head) after a
+    prefill chunk and after a decode step."""
+    from cuteafd_b200.models.gqa_moe import Batch
+    from cuteafd_b200.ops import kernels as K
+    from cuteafd_b200.ref.model import KvState, RefDecoder, init_weights
+    from cuteafd_b200.runtime.generate import Generator
+    from cuteafd_b200.runtime.paged import PagePool
+    dev = torch.device("cuda:0")
+    if family == "gqa":
+        from cuteafd_b200.models.gqa_moe import GqaMoeEngine as Engine, GqaMoeWeights as Weights, KvCache as Cache
+        cfg = small_cfg().replace(mtp_layers=1)
+    else:
+        from cuteafd_b200.models.mla_moe import LatentCache as Cache, MlaMoeEngine as Engine, MlaMoeWeights as Weights
+        from tests.test_mla_gpu import _mla_cfg
+        cfg = _mla_cfg().replace(mtp_layers=1)
+    params = {k: v.to(torch.bfloat16).float() for k, v in init_weights(cfg, seed=0).items()}
+    eng = Engine(cfg, Weights.from_params(cfg, params, dev), Cache(cfg, 64, dev), max_tokens=256, max_seqs=8)
+    gen = Generator(eng, PagePool(64), max_pages_per_seq=8, max_seqs=8, prefill_chunk=128, use_graphs=False)
+    ref = RefDecoder(cfg, params)
+    g = torch.Generator().manual_seed(3)
+    n = 100
+    p = torch.randint(0, cfg.vocab_size, (n,), generator=g)
+    errs = []
+    with torch.no_grad():
+        s = gen.table.new()
+        first = gen.prefill(s, p.tolist())
+        b = gen.prefill_buf
+        batch = Batch(b.tokens[1][:n], b.positions[1][:n], b.slots[1][:n], b.page_table[1].view(1, gen.max_pages),
+                      b.seq_lens[1][:1], b.q_start[1][:2], n, True, None)
+        nxt = torch.cat([p[1:], torch.tensor([first])])
+        got = eng.mtp_forward(0, batch, nxt.to(torch.int32).to(dev)).float().cpu()
+        kvs = KvState(cfg)
+        h = ref.hidden_states(p, kvs)
+        want, _ = ref.mtp_forward(0, h, nxt, torch.arange(n), kvs)
+        for r in range(n):
+            errs.append((got[r] - want[r]).abs().max().item() / max(want[r].abs().max().item(), 1.0))
+        # one decode step: the depth sees (h of the new position, the token after it)
+        tok2 = gen.decode([s], [first])[0]
+        d = gen.decode_bufs[1]
+        dbatch = Batch(d.tokens[1][:1], d.positions[1][:1], d.slots[1][:1], d.page_table[1].view(1, gen.max_pages),
+                       d.seq_lens[1][:1], d.q_start[1][:2], 1, False, None)
+        got2 = eng.mtp_forward(0, dbatch, torch.tensor([tok2], dtype=torch.int32, device=dev)).float().cpu()
+        h2 = ref.hidden_states(torch.tensor([first]), kvs)
+        want2, _ = ref.mtp_forward(0, h2, torch.tensor([tok2]), torch.tensor([n]), kvs)
+        errs.append((got2[0] - want2[0]).abs().max().item() / max(want2[0].abs().max().item(), 1.0))
+    torch.cuda.synchronize()
+    assert K.read_status() == 0
+    errs.sort()
+    assert errs[len(errs) // 2] < 0.03 and errs[int(len(errs) * 0.9)] < 0.06 and errs[-1] < 0.3, errs[-10:]

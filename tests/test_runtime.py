@@ -263,3 +263,23 @@ def test_scheduler_thread_and_cancel(oracle):
     o1 = collect(r1, timeout=30)
     s.stop(); t.join(timeout=5)
     assert o1["finish"] == "length" and len(o1["tokens"]) == 6
+
+
+def test_mtp_drafter_is_lossless_and_feeds_the_next_step():
+    """Native MTP drafts: the depth runs on every verify step's rows, its draft for the bonus row is offered to the
+    drafter, the next step verifies it; emitted tokens equal the run without speculation."""
+    from cuteafd_b200.config import tiny_moe
+    from cuteafd_b200.ref.model import init_weights
+    cfg = tiny_moe().replace(mtp_layers=1)
+    params = init_weights(cfg, seed=0)
+    g = torch.Generator().manual_seed(9)
+    prompt = torch.randint(0, cfg.vocab_size, (70,), generator=g).tolist()
+    base = _run(Scheduler(OracleBackend(cfg.replace(mtp_layers=0), params), drafter=None),
+                [Request(prompt, max_tokens=20, speculation=False)])[0]
+    be = OracleBackend(cfg, params)
+    assert be.has_mtp
+    drafter = speculation.MtpDrafter()
+    out = _run(Scheduler(be, drafter=drafter), [Request(prompt, max_tokens=20)])[0]
+    assert out["tokens"] == base["tokens"]
+    sp = out["usage"]["speculation"]
+    assert drafter.offered >= 10 and sp["proposed"] >= 5 and sp["cycles"] <= 20
