@@ -43,8 +43,9 @@ class StepBuffers:
 
 class Generator:
     def __init__(self, engine, pool: PagePool, max_pages_per_seq: int, max_seqs: int, prefill_chunk: int = 8192,
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, max_graphs: int = 16):
         self.engine, self.pool = engine, pool
+        self.max_graphs = max_graphs          # decode graphs kept (exact batch size is the key); least recently used goes first
         self.table = SequenceTable(pool)
         self.device = engine.device
         self.max_pages, self.max_seqs, self.chunk = max_pages_per_seq, max_seqs, prefill_chunk
@@ -122,7 +123,12 @@ class Generator:
                 with torch.cuda.graph(g):
                     out = self.engine.greedy(self.engine.forward(batch))
                 self.graphs[S] = (g, out)
-            g, out = self.graphs[S]
+                while len(self.graphs) > self.max_graphs:
+                    old = next(iter(self.graphs))
+                    del self.graphs[old]
+                    self.decode_bufs.pop(old, None)
+            g, out = self.graphs.pop(S)
+            self.graphs[S] = (g, out)          # most recently used last
             if hasattr(self.engine, "announce"):
                 self.engine.announce(S, 1, for_replay=True)
             g.replay()
