@@ -87,6 +87,7 @@ class SchedulerStats:
     emitted_tokens: int = 0
     verify_rows: int = 0
     verify_row_hist: dict = field(default_factory=dict)
+    lane_rounds: dict = field(default_factory=dict)
     stalls: int = 0
     quarantined: int = 0
 
@@ -94,8 +95,14 @@ class SchedulerStats:
 class Scheduler:
     def __init__(self, backend: Backend, *, max_active: int = 32, queue_depth: int = 64, queue_wait_s: float = 30.0,
                  decode_share: float = 0.2, drafter=None, draft_control: str = "history", row_budget: int | None = None,
-                 eos_ids: tuple[int, ...] = ()):
+                 eos_ids: tuple[int, ...] = (), decode_lanes: int = 1):
         self.be = backend
+        # Decode lanes: 1 or 2 independent decode batches served in turn on the one engine thread.  A request stays in
+        # the lane it was assigned when its prefill finished; each lane keeps its own batch geometry (its own decode
+        # graphs).  On a disaggregated deployment lane A's attention overlaps lane B's expert exchange
+        # (rust/crates/cuteafd-daemon/src/shared/qwen/scheduler.rs decode lanes; shared-engine.md:181-281).
+        self.decode_lanes = max(1, min(2, decode_lanes))
+        self._lane_turn = 0
         self.max_active, self.queue_depth, self.queue_wait_s = max_active, queue_depth, queue_wait_s
         self.decode_share = decode_share
         self.waiting: "queue.Queue[Request]" = queue.Queue()
@@ -250,6 +257,16 @@ class Scheduler:
         self.decoding = batch
         if not batch:
             return False
+        if self.decode_lanes > 1:
+            # serve one lane per round, alternating; a lane with nothing to do yields its turn
+            for _ in range(self.decode_lanes):
+                lane = self._lane_turn
+                self._lane_turn = (self._lane_turn + 1) % self.decode_lanes
+                mine = [a for a in batch if a.req.rid % self.decode_lanes == lane]
+                if mine:
+                    batch = mine
+                    self.stats.lane_rounds[lane] = self.stats.lane_rounds.get(lane, 0) + 1
+                    break
         # KV top-ups: a request that cannot grow stalls for this round (never truncated)
         runnable = []
         for a in batch:

@@ -283,3 +283,14 @@ def test_mtp_drafter_is_lossless_and_feeds_the_next_step():
     assert out["tokens"] == base["tokens"]
     sp = out["usage"]["speculation"]
     assert drafter.offered >= 10 and sp["proposed"] >= 5 and sp["cycles"] <= 20
+
+
+def test_two_decode_lanes_serve_alternately_without_changing_tokens(oracle):
+    cfg, params = oracle
+    g = torch.Generator().manual_seed(21)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (20, 33, 41, 27)]
+    one = _run(Scheduler(OracleBackend(cfg, params), max_active=4), [Request(p, max_tokens=8) for p in prompts])
+    sch = Scheduler(OracleBackend(cfg, params), max_active=4, decode_lanes=2)
+    two = _run(sch, [Request(p, max_tokens=8) for p in prompts])
+    assert [o["tokens"] for o in two] == [o["tokens"] for o in one]
+    assert sch.stats.lane_rounds.get(0, 0) > 0 and sch.stats.lane_rounds.get(1, 0) > 0
