@@ -39,7 +39,7 @@ MAX_RANKS = 8
 # one setter per translation unit that waits (each holds its own copy of the limit)
 WAIT_LIMIT_SETTERS = ("cafd_gemm_set_wait_limit_ns", "cafd_moe_set_wait_limit_ns", "cafd_attn_set_wait_limit_ns",
                       "cafd_gemm_fp8_set_wait_limit_ns", "cafd_tp_set_wait_limit_ns", "cafd_mla_set_wait_limit_ns",
-                      "cafd_indexer_set_wait_limit_ns", "cafd_gemm_w4_set_wait_limit_ns")
+                      "cafd_indexer_set_wait_limit_ns", "cafd_gemm_w4_set_wait_limit_ns", "cafd_gemm_exl3_set_wait_limit_ns")
 
 
 class MoeLayout(C.Structure):
@@ -111,6 +111,7 @@ def cuda_lib():
         _sig(lib, "cafd_gemm_w4", [C.POINTER(GemmArgs), I, P, P, P])
         _sig(lib, "cafd_w4_dequant", [P, P, P, P, C.c_longlong, I, I, I, P])
         _sig(lib, "cafd_fp8_dequant_block128", [P, P, P, C.c_longlong, I, P])
+        _sig(lib, "cafd_gemm_exl3", [P, I, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, P])
         _sig(lib, "cafd_sample_rows", [P, I, I, P, P, I, P, P, P])
         _sig(lib, "cafd_accept_prefix", [P, P, P, I, P, P, P])
         _sig(lib, "cafd_mla_q_split", [P, I, P, P, P, P, I, I, I, I, P])

@@ -662,3 +662,30 @@ def fp8_dequant_block128(q: torch.Tensor, scales: torch.Tensor, out: torch.Tenso
     _n.check(_n.cuda_lib().cafd_fp8_dequant_block128(q.data_ptr(), scales.data_ptr(), out.data_ptr(), rows, Kd, _stream()),
              "fp8_dequant_block128")
     return out
+
+
+# ---- EXL3 (trellis-coded weights) ---------------------------------------------------------------------------
+_exl3_scratch: dict = {}
+
+
+def linear_exl3(x: torch.Tensor, trellis: torch.Tensor, suh: torch.Tensor, svh: torch.Tensor, out: torch.Tensor | None = None,
+                residual: torch.Tensor | None = None) -> torch.Tensor:
+    """y = x @ W for an EXL3 tensor: trellis int16 [K/16, N/16, 16 * bits], suh [K] / svh [N] fp16 sign-scale vectors;
+    W = H128_K-rotated, trellis-decoded, H128_N-rotated (see ``quant.codecs.exl3_dequant``).  T <= 128 rows."""
+    T, Kd = x.shape
+    Kt, Nt, W = trellis.shape
+    N, bits = Nt * 16, W // 16
+    assert Kt * 16 == Kd and Kd % 128 == 0 and N % 128 == 0 and T <= 128 and trellis.dtype == torch.int16 and trellis.is_contiguous()
+    assert suh.dtype == torch.float16 and svh.dtype == torch.float16 and x.dtype == torch.bfloat16 and x.stride(1) == 1
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+    key = (x.device.index, Kd, N)
+    sc = _exl3_scratch.get(key)
+    if sc is None:
+        sc = (torch.empty(128, Kd, dtype=torch.float16, device=x.device), torch.empty(128, N, dtype=torch.float32, device=x.device))
+        _exl3_scratch[key] = sc
+    _n.check(_n.cuda_lib().cafd_gemm_exl3(x.data_ptr(), x.stride(0), trellis.data_ptr(), suh.data_ptr(), svh.data_ptr(),
+                                          _ptr(residual), out.data_ptr(), out.stride(0), sc[0].data_ptr(), sc[1].data_ptr(),
+                                          status_word(x.device).data_ptr(), T, Kd, N, bits, pick_token_tile(T), num_sms(),
+                                          _stream()), "cafd_gemm_exl3")
+    return out

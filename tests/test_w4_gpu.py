@@ -73,3 +73,20 @@ def test_moe_w4(K, fmt, T):
     assert K.read_status() == 0
     err = (out.float() - ref.float()).abs().max().item()
     assert err < 0.03 * max(1.0, ref.float().abs().max().item()), err
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 5, 8])
+@pytest.mark.parametrize("T,Kd,N", [(1, 256, 128), (8, 512, 384), (70, 1024, 256)])
+def test_linear_exl3(K, bits, T, Kd, N):
+    from cuteafd_b200.quant import codecs
+    g = torch.Generator().manual_seed(bits * 100 + T)
+    trellis, suh, svh = codecs.exl3_random(Kd, N, bits, g, scale=0.02)
+    x = torch.randn(T, Kd, generator=g).to(torch.bfloat16)
+    w = codecs.exl3_dequant(trellis, suh, svh)                      # [K, N] float64
+    ref = (x.double() @ w).float()
+    for _ in range(2):
+        out = K.linear_exl3(x.to(DEV), trellis.to(DEV), suh.to(DEV), svh.to(DEV))
+    torch.cuda.synchronize()
+    assert K.read_status() == 0
+    err = (out.float().cpu() - ref).abs().max().item()
+    assert err < 0.02 * max(1.0, ref.abs().max().item()), err
