@@ -107,7 +107,8 @@ def cuda_lib():
         _sig(lib, "cafd_indexer_scores", [P, P, P, I, F, P, P, P, P, P, P, P, C.c_longlong, I, I, I, I, I, I, P])
         _sig(lib, "cafd_index_topk", [P, I, P, P, P, I, I, I, P, P])
         _sig(lib, "cafd_index_k_store", [P, I, P, P, I, P])
-        _sig(lib, "cafd_mla_prep_a", [P, I, I, P, P, P, P, P, P, P, I, F, I, P])
+        _sig(lib, "cafd_mla_prep_a", [P, I, I, P, P, P, P, P, P, P, I, F, I, P, P])
+        _sig(lib, "cafd_attn_prefill_mla", [P, I, P, I, I, P, P, C.c_longlong, P, P, P, P, P, P, P, I, I, I, I, I, I, F, P])
         _sig(lib, "cafd_gemm_w4", [C.POINTER(GemmArgs), I, P, P, P])
         _sig(lib, "cafd_w4_dequant", [P, P, P, P, C.c_longlong, I, I, I, P])
         _sig(lib, "cafd_fp8_dequant_block128", [P, P, P, C.c_longlong, I, P])

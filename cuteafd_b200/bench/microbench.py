@@ -205,6 +205,25 @@ def bench_mla(a, dev, pk):
     assert K.read_status() == 0
 
 
+def bench_mla_prefill_expanded(a, dev, pk):
+    """MLA prefill in expanded form (per-head K_nope / V from kv_b, shared rope keys from the latent cache)."""
+    import math
+    heads, n = a.heads, a.len
+    pages = (n + 63) // 64 + 1
+    cache = torch.randn(pages, 64, 576, device=dev).bfloat16(); cache[0] = 0
+    table = torch.arange(1, pages, dtype=torch.int32, device=dev).view(1, -1).contiguous()
+    q = (torch.randn(n, heads * 192, device=dev) * 0.3).bfloat16()
+    qr = (torch.randn(n, heads, 576, device=dev) * 0.3).bfloat16()
+    rows = ((n + 63) // 64) * 64
+    kx = (torch.randn(rows, heads * 128, device=dev) * 0.3).bfloat16(); vx = torch.randn_like(kx)
+    out = torch.empty(n, heads, 128, dtype=torch.bfloat16, device=dev)
+    i32 = dict(dtype=torch.int32, device=dev)
+    sl, qs, z = torch.tensor([n], **i32), torch.tensor([0, n], **i32), torch.zeros(1, **i32)
+    ms = time_eager(lambda: K.attn_prefill_mla(q, qr, kx, vx, z, cache, table, sl, qs, out, n, heads, 1.0 / math.sqrt(192)), dev, iters=a.iters)
+    report(f"mla_prefill_expanded len={n} heads={heads}", ms, 2.0 * n * n / 2 * heads * (192 + 128), (n * heads * (192 + 128 + 256)) * 2.0, pk)
+    assert K.read_status() == 0
+
+
 def bench_w4(a, dev, pk):
     """4-bit weight GEMM at decode sizes against the bf16 kernel on the same logical weights."""
     from ..quant import codecs
@@ -262,20 +281,22 @@ def main() -> None:
     ml.add_argument("--seqs", type=int, default=8); ml.add_argument("--len", type=int, default=8192)
     ml.add_argument("--qlen", type=int, default=1); ml.add_argument("--heads", type=int, default=128)
     ml.add_argument("--topk", type=int, default=0); ml.add_argument("--splits", type=int, default=0)
+    mp_ = sub.add_parser("mla-prefill")
+    mp_.add_argument("--len", type=int, default=8192); mp_.add_argument("--heads", type=int, default=128)
     w4 = sub.add_parser("w4")
     w4.add_argument("--tokens", type=int, default=8); w4.add_argument("--features", type=int, default=7168)
     w4.add_argument("--k", type=int, default=2048); w4.add_argument("--fmt", default="mxfp4")
     sm = sub.add_parser("sampler")
     sm.add_argument("--rows", type=int, default=32); sm.add_argument("--vocab", type=int, default=151936)
     sm.add_argument("--top-k", type=int, default=50); sm.add_argument("--top-p", type=float, default=0.9)
-    for s in (g, p, d, m, ml, w4, sm):
+    for s in (g, p, d, m, ml, mp_, w4, sm):
         s.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     pk = peaks()
     {"gemm": bench_gemm, "attn-prefill": bench_attn_prefill, "attn-decode": bench_attn_decode, "moe": bench_moe,
-     "mla": bench_mla, "w4": bench_w4, "sampler": bench_sampler}[a.cmd](a, dev, pk)
+     "mla": bench_mla, "mla-prefill": bench_mla_prefill_expanded, "w4": bench_w4, "sampler": bench_sampler}[a.cmd](a, dev, pk)
 
 
 if __name__ == "__main__":

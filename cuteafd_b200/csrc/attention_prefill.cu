@@ -12,6 +12,11 @@
 //              O is rescaled in TMEM only when the running maximum moved
 // TMEM: S double-buffered (2 x 128 columns) + O (128 columns).
 //
+// The kRope variant serves MLA prefill in its expanded (non-absorbed) form: per-head K_nope / V tiles come from a
+// contiguous expansion buffer (kv_b applied to the chunk's latents), and a 64-wide rotary part that all heads share
+// is added to the scores with four more MMAs per tile, its keys read straight from the paged latent cache
+// (columns 512..575 of every record).  Query dims are then 128 + 64, value dims 128.
+//
 // Replaces the reference's mma.sync prefill kernels (native/families/glm5/cuda/glm_mla_prefill.cu:78-135)
 // and its exported attention programs for the GQA families.
 #include "cafd_api.h"
@@ -28,6 +33,7 @@ constexpr int kHalfBytes = 128 * 128;   // 128 rows x 64 bf16 (one swizzle atom 
 constexpr int kTileB = 2 * kHalfBytes;  // 32 KiB: a [128 x 128] bf16 tile as two 64-wide halves
 constexpr int kPrefillThreads = 192;
 constexpr int kPrefillSmem = 6 * kTileB + 1024;   // Q, K x2, V x2, P
+constexpr int kPrefillSmemRope = 5 * kTileB + 3 * kHalfBytes + 1024;   // Q, Qr, (K, Kr) x2, V x1, P
 
 struct PrefillDev {
   const int* page_table;   // [seqs, max_pages]
@@ -38,17 +44,27 @@ struct PrefillDev {
   int max_pages;
   int Hq, Hkv;
   float scale_log2;
+  // kRope only
+  const int* kv_tmp_start; // [seqs] first row of the sequence in the expansion buffers (multiple of 64)
+  int q_head_stride;       // elements between heads in the nope query matrix (192 for [T, heads * 192])
+  int qr_head_stride;      // elements between heads in the rope query matrix (576 for the absorbed-query buffer)
+  int qr_col0;             // first rope column inside a head of that matrix (512)
 };
 
+template <bool kRope>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                    const __grid_constant__ CUtensorMap tm_v, const PrefillDev p) {
+                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_qr,
+                    const __grid_constant__ CUtensorMap tm_kr, const PrefillDev p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kVS = kRope ? 1 : 2;    // V stages (the rope tiles take the room of the second one)
   uint8_t* sQ = smem;
   uint8_t* sK = smem + kTileB;          // 2 stages
-  uint8_t* sV = smem + 3 * kTileB;      // 2 stages
-  uint8_t* sP = smem + 5 * kTileB;
+  uint8_t* sV = smem + 3 * kTileB;      // kVS stages
+  uint8_t* sP = sV + kVS * kTileB;
+  uint8_t* sQr = sP + kTileB;           // kRope: 128 x 64 rope queries, then two stages of 128 x 64 rope keys
+  uint8_t* sKr = sQr + kHalfBytes;
 
   __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_ready, pv_done;
   __shared__ uint32_t tmem_slot;
@@ -96,30 +112,43 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
-      mbar_expect_tx(&q_full, kTileB);
-      tma_load_2d(sQ, &tm_q, &q_full, head * kHD, q0 + row0);
-      tma_load_2d(sQ + kHalfBytes, &tm_q, &q_full, head * kHD + 64, q0 + row0);
+      if (kRope) { tma_prefetch_desc(&tm_qr); tma_prefetch_desc(&tm_kr); }
+      const int qcol = kRope ? head * p.q_head_stride : head * kHD;
+      mbar_expect_tx(&q_full, kTileB + (kRope ? kHalfBytes : 0));
+      tma_load_2d(sQ, &tm_q, &q_full, qcol, q0 + row0);
+      tma_load_2d(sQ + kHalfBytes, &tm_q, &q_full, qcol + 64, q0 + row0);
+      if (kRope) tma_load_2d(sQr, &tm_qr, &q_full, head * p.qr_head_stride + p.qr_col0, q0 + row0);
       const int* pt = p.page_table + static_cast<size_t>(seq) * p.max_pages;
+      const int tmp_page0 = kRope ? p.kv_tmp_start[seq] / kPageTok : 0;
       bool ok = true;
       for (int j = 0; ok && j < n_tiles; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         const int pa = 2 * j < seq_pages ? pt[2 * j] : 0;          // page 0 is the all-zero page
         const int pb = 2 * j + 1 < seq_pages ? pt[2 * j + 1] : 0;
+        // expanded K / V (kRope) sit in order in their buffer: "page" = row block of 64; past the end TMA fills zeros
+        const int ka = kRope ? tmp_page0 + 2 * j : pa, kb = kRope ? tmp_page0 + 2 * j + 1 : pb;
         if (!mbar_wait(&k_empty[st], ph ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
         uint8_t* kd = sK + st * kTileB;
-        mbar_expect_tx(&k_full[st], kTileB);
-        tma_load_4d(kd, &tm_k, &k_full[st], 0, kvh, 0, pa);
-        tma_load_4d(kd + 64 * 128, &tm_k, &k_full[st], 0, kvh, 0, pb);
-        tma_load_4d(kd + kHalfBytes, &tm_k, &k_full[st], 64, kvh, 0, pa);
-        tma_load_4d(kd + kHalfBytes + 64 * 128, &tm_k, &k_full[st], 64, kvh, 0, pb);
-        if (!mbar_wait(&v_empty[st], ph ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
-        uint8_t* vd = sV + st * kTileB;
-        mbar_expect_tx(&v_full[st], kTileB);
-        tma_load_4d(vd, &tm_v, &v_full[st], 0, kvh, 0, pa);
-        tma_load_4d(vd + 64 * 128, &tm_v, &v_full[st], 0, kvh, 0, pb);
-        tma_load_4d(vd + kHalfBytes, &tm_v, &v_full[st], 64, kvh, 0, pa);
-        tma_load_4d(vd + kHalfBytes + 64 * 128, &tm_v, &v_full[st], 64, kvh, 0, pb);
+        mbar_expect_tx(&k_full[st], kTileB + (kRope ? kHalfBytes : 0));
+        tma_load_4d(kd, &tm_k, &k_full[st], 0, kvh, 0, ka);
+        tma_load_4d(kd + 64 * 128, &tm_k, &k_full[st], 0, kvh, 0, kb);
+        tma_load_4d(kd + kHalfBytes, &tm_k, &k_full[st], 64, kvh, 0, ka);
+        tma_load_4d(kd + kHalfBytes + 64 * 128, &tm_k, &k_full[st], 64, kvh, 0, kb);
+        if (kRope) {
+          uint8_t* rd = sKr + st * kHalfBytes;
+          tma_load_3d(rd, &tm_kr, &k_full[st], 512, 0, pa);
+          tma_load_3d(rd + 64 * 128, &tm_kr, &k_full[st], 512, 0, pb);
+        }
+        const int vs = kVS == 2 ? st : 0;
+        const uint32_t vph = kVS == 2 ? ph : (j & 1);
+        if (!mbar_wait(&v_empty[vs], vph ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
+        uint8_t* vd = sV + vs * kTileB;
+        mbar_expect_tx(&v_full[vs], kTileB);
+        tma_load_4d(vd, &tm_v, &v_full[vs], 0, kvh, 0, ka);
+        tma_load_4d(vd + 64 * 128, &tm_v, &v_full[vs], 0, kvh, 0, kb);
+        tma_load_4d(vd + kHalfBytes, &tm_v, &v_full[vs], 64, kvh, 0, ka);
+        tma_load_4d(vd + kHalfBytes + 64 * 128, &tm_v, &v_full[vs], 64, kvh, 0, kb);
       }
     }
   } else if (warp == 1) {
@@ -141,6 +170,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           for (int k4 = 0; k4 < 4; ++k4)
             umma_f16(tS + st * 128, smem_desc_k_sw128(aQ + h * kHalfBytes + k4 * 32),
                      smem_desc_k_sw128(aK + h * kHalfBytes + k4 * 32), idesc_qk, (h | k4) ? 1u : 0u);
+        if (kRope) {
+          const uint32_t aQr = smem_u32(sQr), aKr = smem_u32(sKr + st * kHalfBytes);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            umma_f16(tS + st * 128, smem_desc_k_sw128(aQr + k4 * 32), smem_desc_k_sw128(aKr + k4 * 32), idesc_qk, 1u);
+        }
         umma_commit(&k_empty[st]);
         umma_commit(&s_full[st]);
         return true;
@@ -151,9 +186,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(&p_ready, j & 1, p.status, kTimeoutSoftmax)) { ok = false; break; }
-        if (!mbar_wait(&v_full[st], ph, p.status, kTimeoutFullBarrier)) { ok = false; break; }
+        const int vs = kVS == 2 ? st : 0;
+        const uint32_t vph = kVS == 2 ? ph : (j & 1);
+        if (!mbar_wait(&v_full[vs], vph, p.status, kTimeoutFullBarrier)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t aV = smem_u32(sV + st * kTileB);
+        const uint32_t aV = smem_u32(sV + vs * kTileB);
 #pragma unroll
         for (int k8 = 0; k8 < 8; ++k8) {
           // A = P: atom (k8 / 4) of 64 kv columns, 32 bytes per K step inside it
@@ -161,7 +198,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           umma_f16(tO, smem_desc_k_sw128(aP + (k8 >> 2) * kHalfBytes + (k8 & 3) * 32),
                    smem_desc_mn_sw128(aV + k8 * 2048, kHalfBytes), idesc_pv, (j | k8) ? 1u : 0u);
         }
-        umma_commit(&v_empty[st]);
+        umma_commit(&v_empty[vs]);
         umma_commit(&pv_done);
       }
     }
@@ -196,7 +233,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
       const float m_new = fmaxf(m_run, mx);
       const float base = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - base);
+      const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - base);
       // P buffer and O are free once P V of the previous tile has completed
       if (j > 0) {
         if (!mbar_wait(&pv_done, (j - 1) & 1, p.status, kTimeoutTmemFull)) { ok = false; break; }
@@ -229,7 +266,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             if ((c * 32 + i) > col_limit) v0 = -INFINITY;
             if ((c * 32 + i + 1) > col_limit) v1 = -INFINITY;
           }
-          const uint32_t w = pack_bf16(exp2f(v0 - base), exp2f(v1 - base));
+          const uint32_t w = pack_bf16(fast_exp2(v0 - base), fast_exp2(v1 - base));
           rs += bf16_lo(w) + bf16_hi(w);
           pk[i >> 1] = w;
         }
@@ -319,13 +356,64 @@ extern "C" int cafd_attn_prefill(const void* q, const void* k_cache, const void*
   p.Hq = Hq;
   p.Hkv = Hkv;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.kv_tmp_start = nullptr; p.q_head_stride = kHD; p.qr_head_stride = 0; p.qr_col0 = 0;
   static bool attr = false;
   if (!attr) {
-    CAFD_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem));
+    CAFD_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem));
     attr = true;
   }
   dim3 grid((max_q_len + kBQ - 1) / kBQ, Hq, num_seqs);
-  launch_pdl(attn_prefill_kernel, grid, dim3(kPrefillThreads), kPrefillSmem, static_cast<cudaStream_t>(s), tq, tk, tv, p);
+  launch_pdl(attn_prefill_kernel<false>, grid, dim3(kPrefillThreads), kPrefillSmem, static_cast<cudaStream_t>(s), tq, tk, tv, tq, tq, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// MLA prefill in expanded form.  q_nope [total_q, heads * q_head_stride] bf16 (the first 128 columns of every head);
+// q_rope [total_q, heads * qr_head_stride] bf16 with the rotated 64 rope dims of head h at column
+// h * qr_head_stride + qr_col0; k_exp / v_exp [tmp_rows, heads * 128] bf16 = per-head K_nope / V of every cached
+// token of the sequences, sequence s starting at row kv_tmp_start[s] (a multiple of 64); latent cache
+// [num_pages, 64, 576] supplies the shared rope keys (columns 512..575) through the page table.
+// out [total_q, heads, 128].
+extern "C" int cafd_attn_prefill_mla(const void* q_nope, int q_head_stride, const void* q_rope, int qr_head_stride, int qr_col0,
+                                     const void* k_exp, const void* v_exp, long long tmp_rows, const int* kv_tmp_start,
+                                     const void* latent_cache, const int* page_table, const int* seq_lens, const int* q_start,
+                                     void* out, uint32_t* status, int total_q, int num_seqs, int max_q_len, int num_pages,
+                                     int max_pages, int heads, float scale, cafd_stream_t s) {
+  if (num_seqs <= 0 || total_q <= 0) return 0;
+  if (tmp_rows % kPageTok || (q_head_stride % 8) || (qr_head_stride % 8) || (qr_col0 % 8)) return -10;
+  CUtensorMap tq, tqr, tk, tv, tkr;
+  int rc = cached_tmap_2d(&tq, q_nope, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, total_q, static_cast<uint64_t>(heads) * q_head_stride,
+                          static_cast<uint64_t>(heads) * q_head_stride * 2, kBQ, 64);
+  if (rc) return rc;
+  rc = cached_tmap_2d(&tqr, q_rope, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, total_q, static_cast<uint64_t>(heads) * qr_head_stride,
+                      static_cast<uint64_t>(heads) * qr_head_stride * 2, kBQ, 64);
+  if (rc) return rc;
+  const uint64_t dims[4] = {static_cast<uint64_t>(kHD), static_cast<uint64_t>(heads), kPageTok, static_cast<uint64_t>(tmp_rows / kPageTok)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(kHD) * 2, static_cast<uint64_t>(heads) * kHD * 2,
+                               static_cast<uint64_t>(kPageTok) * heads * kHD * 2};
+  const uint32_t box[4] = {64, 1, kPageTok, 1};
+  rc = make_tmap_nd(&tk, k_exp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dims, strides, box, true);
+  if (rc) return rc;
+  rc = make_tmap_nd(&tv, v_exp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dims, strides, box, true);
+  if (rc) return rc;
+  const uint64_t ldims[3] = {576, kPageTok, static_cast<uint64_t>(num_pages)};
+  const uint64_t lstrides[2] = {576 * 2, static_cast<uint64_t>(kPageTok) * 576 * 2};
+  const uint32_t lbox[3] = {64, kPageTok, 1};
+  rc = make_tmap_nd(&tkr, latent_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, ldims, lstrides, lbox, true);
+  if (rc) return rc;
+  PrefillDev p;
+  p.page_table = page_table; p.seq_lens = seq_lens; p.q_start = q_start;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.status = status;
+  p.max_pages = max_pages; p.Hq = heads; p.Hkv = heads;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.kv_tmp_start = kv_tmp_start; p.q_head_stride = q_head_stride; p.qr_head_stride = qr_head_stride; p.qr_col0 = qr_col0;
+  static bool attr = false;
+  if (!attr) {
+    CAFD_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmemRope));
+    attr = true;
+  }
+  dim3 grid((max_q_len + kBQ - 1) / kBQ, heads, num_seqs);
+  launch_pdl(attn_prefill_kernel<true>, grid, dim3(kPrefillThreads), kPrefillSmemRope, static_cast<cudaStream_t>(s), tq, tk, tv, tqr, tkr, p);
   return static_cast<int>(cudaGetLastError());
 }
 

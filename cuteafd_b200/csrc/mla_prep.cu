@@ -33,7 +33,8 @@ __global__ void __launch_bounds__(256) mla_prep_a_kernel(const __nv_bfloat16* __
                                                          const __nv_bfloat16* __restrict__ kv_norm_w,
                                                          const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                                          const int* __restrict__ slots, __nv_bfloat16* __restrict__ q_a_out,
-                                                         __nv_bfloat16* __restrict__ cache, float eps, int interleaved) {
+                                                         __nv_bfloat16* __restrict__ cache, float eps, int interleaved,
+                                                         __nv_bfloat16* __restrict__ lat_out) {
   pdl_wait();
   pdl_trigger();
   __shared__ float red[8];
@@ -57,10 +58,13 @@ __global__ void __launch_bounds__(256) mla_prep_a_kernel(const __nv_bfloat16* __
   const __nv_bfloat16* kv = row + q_lora;
   const uint32_t v = *reinterpret_cast<const uint32_t*>(kv + threadIdx.x * 2);          // 256 threads x 2 = 512 latent
   const float inv = rsqrtf(block_sum_256(bf16_lo(v) * bf16_lo(v) + bf16_hi(v) * bf16_hi(v), red) / static_cast<float>(kLatent) + eps);
+  const uint32_t w = *reinterpret_cast<const uint32_t*>(kv_norm_w + threadIdx.x * 2);
+  const uint32_t normed = pack_bf16(bf16_lo(v) * inv * bf16_lo(w), bf16_hi(v) * inv * bf16_hi(w));
+  // the same normalised latent, in token order, for the expanded-form prefill (kv_b is applied to it)
+  if (lat_out) *reinterpret_cast<uint32_t*>(lat_out + static_cast<size_t>(t) * kLatent + threadIdx.x * 2) = normed;
   if (slot < 0) return;
   __nv_bfloat16* dst = cache + static_cast<size_t>(slot) * kRecord;
-  const uint32_t w = *reinterpret_cast<const uint32_t*>(kv_norm_w + threadIdx.x * 2);
-  *reinterpret_cast<uint32_t*>(dst + threadIdx.x * 2) = pack_bf16(bf16_lo(v) * inv * bf16_lo(w), bf16_hi(v) * inv * bf16_hi(w));
+  *reinterpret_cast<uint32_t*>(dst + threadIdx.x * 2) = normed;
   if (threadIdx.x < 32) {
     const int i = threadIdx.x;                         // frequency index
     const float pos = static_cast<float>(positions[t]);
@@ -114,12 +118,13 @@ using namespace cafd;
 
 extern "C" int cafd_mla_prep_a(const void* a, int lda, int q_lora, const void* q_norm_w, const void* kv_norm_w,
                                const float* inv_freq, const int* positions, const int* slots, void* q_a_out, void* cache,
-                               int T, float eps, int interleaved, cafd_stream_t s) {
+                               int T, float eps, int interleaved, void* lat_out, cafd_stream_t s) {
   if (T <= 0) return 0;
   if ((q_lora & 1) || (lda & 1)) return -10;
   launch_pdl(mla_prep_a_kernel, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(s), static_cast<const __nv_bfloat16*>(a), lda,
              q_lora, static_cast<const __nv_bfloat16*>(q_norm_w), static_cast<const __nv_bfloat16*>(kv_norm_w), inv_freq,
-             positions, slots, static_cast<__nv_bfloat16*>(q_a_out), static_cast<__nv_bfloat16*>(cache), eps, interleaved);
+             positions, slots, static_cast<__nv_bfloat16*>(q_a_out), static_cast<__nv_bfloat16*>(cache), eps, interleaved,
+             static_cast<__nv_bfloat16*>(lat_out));
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -33,6 +33,7 @@ class Batch:
     max_q_len: int
     prefill: bool
     last_rows: torch.Tensor | None = None   # rows whose logits are wanted (None = all)
+    fresh: bool = False                     # prefill of a single sequence from position 0 (no earlier context in the cache)
 
 
 class LayerWeights:

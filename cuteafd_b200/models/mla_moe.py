@@ -29,7 +29,7 @@ REC = 576
 
 
 class MlaLayerWeights(LayerWeights):
-    __slots__ = ("wqkv_a", "q_a_norm", "kv_a_norm", "wq_b", "w_uk", "w_uv", "wq_idx")
+    __slots__ = ("wqkv_a", "q_a_norm", "kv_a_norm", "wq_b", "w_uk", "w_uv", "wq_idx", "w_kb")
 
     def __init__(self) -> None:
         for s in LayerWeights.__slots__ + MlaLayerWeights.__slots__:
@@ -74,6 +74,7 @@ class MlaMoeWeights:
                 L.wqkv_a = torch.cat([L.wqkv_a, t(a + "indexer.wk.weight"), t(a + "indexer.weights_proj.weight")]).contiguous()
                 L.wq_idx = t(a + "indexer.wq.weight")
             L.w_uk, L.w_uv = MlaMoeWeights._split_kv_b(cfg, t(a + "kv_b_proj.weight"))
+            L.w_kb = L.w_uk.transpose(1, 2).reshape(cfg.num_heads * cfg.qk_nope_dim, cfg.kv_lora_rank).contiguous()
             L.wo = t(a + "o_proj.weight")
             if layer_is_moe(cfg, i):
                 L.router = t(m + "gate.weight")
@@ -115,6 +116,7 @@ class MlaMoeWeights:
             L.kv_a_norm = ones(cfg.kv_lora_rank)
             L.wq_b = w(cfg.num_heads * cfg.qk_head_dim, cfg.q_lora_rank or H)
             L.w_uk, L.w_uv = w(cfg.num_heads, cfg.kv_lora_rank, cfg.qk_nope_dim), w(cfg.num_heads, cfg.v_head_dim, cfg.kv_lora_rank)
+            L.w_kb = L.w_uk.transpose(1, 2).reshape(cfg.num_heads * cfg.qk_nope_dim, cfg.kv_lora_rank).contiguous()
             L.wo = w(H, cfg.num_heads * cfg.v_head_dim)
             if layer_is_moe(cfg, i):
                 L.router = w(cfg.num_experts, H)
@@ -171,6 +173,7 @@ class _HeadTiles:
 
 class MlaMoeEngine(GqaMoeEngine):
     """Single-GPU MLA engine; shares the FFN half, the logits head and greedy selection with the GQA engine."""
+    EXPANDED_PREFILL_TOKENS = 64     # fresh prompt chunks of at least this many tokens use the expanded-form attention
 
     def __init__(self, cfg: ModelConfig, weights: MlaMoeWeights, kv: LatentCache, max_tokens: int, max_seqs: int = 64,
                  build_moe: bool = True):
@@ -217,6 +220,7 @@ class MlaMoeEngine(GqaMoeEngine):
         self._scratch: torch.Tensor | None = None
         self._tiles: dict[int, _HeadTiles] = {}
         self.select_hook = None      # callable(layer, selection [T, top_k]) for tests and traces (eager mode only)
+        self._zero1 = torch.zeros(1, dtype=torch.int32, device=dev)
         self._blocks: dict[tuple[int, int, int], tuple[torch.Tensor, torch.Tensor]] = {}
         self.launches = 0
 
@@ -239,13 +243,32 @@ class MlaMoeEngine(GqaMoeEngine):
         if T not in self._tiles:
             self._tiles[T] = _HeadTiles(T, heads, self.device)
         ht = self._tiles[T]
+        # A fresh prompt chunk (one sequence from position 0) of some length attends in the expanded form: kv_b applied
+        # to the chunk's latents gives per-head K_nope / V, the scores take 128 + 64 dims and the values 128, a third of
+        # the absorbed form's work (576 / 512).  Decode, continued chunks and sparse attention stay absorbed.
+        expanded = b.prefill and b.fresh and not cfg.indexer_heads and T >= self.EXPANDED_PREFILL_TOKENS
+        if expanded and getattr(ws, "lat", None) is None:
+            bf = dict(dtype=torch.bfloat16, device=self.device)
+            rows = ((self.max_tokens + 63) // 64) * 64
+            ws.lat = torch.zeros(self.max_tokens, cfg.kv_lora_rank, **bf)
+            ws.k_exp, ws.v_exp = torch.zeros(rows, heads * 128, **bf), torch.zeros(rows, heads * 128, **bf)
         K.linear(ws.x[:T], L.wqkv_a, out=ws.a[:T])
         K.mla_prep_a(ws.a[:T, :ql + REC], ql, L.q_a_norm, L.kv_a_norm, self.inv_freq, b.positions, b.slots,
-                     ws.q_a[:T] if ql else None, self.kv.c[i], cfg.rms_eps, cfg.rope_interleaved)
+                     ws.q_a[:T] if ql else None, self.kv.c[i], cfg.rms_eps, cfg.rope_interleaved,
+                     lat_out=ws.lat[:T] if expanded else None)
         K.linear(ws.q_a[:T] if ql else ws.x[:T], L.wq_b, out=ws.q[:T])
         q_slab = ws.q_slab[:heads * ht.t_pad * 128].view(heads, ht.t_pad, 128)
         o_slab = ws.o_slab[:heads * ht.t_pad * 512].view(heads, ht.t_pad, 512)
         K.mla_q_split(ws.q[:T], self.inv_freq, b.positions, q_slab, ws.q_abs[:T], heads, cfg.rope_interleaved)
+        if expanded:
+            rows = ((T + 63) // 64) * 64
+            K.linear(ws.lat[:T], L.w_kb, out=ws.k_exp[:T])
+            K.linear(ws.lat[:T], L.w_uv.view(heads * 128, cfg.kv_lora_rank), out=ws.v_exp[:T])
+            K.attn_prefill_mla(ws.q[:T], ws.q_abs[:T], ws.k_exp[:rows], ws.v_exp[:rows], self._zero1, self.kv.c[i], b.page_table,
+                               b.seq_lens, b.q_start, ws.attn[:T], b.max_q_len, heads, self.scale)
+            K.linear(ws.attn[:T], L.wo, out=ws.h[:T], residual=ws.h[:T])
+            self.launches += 8
+            return
         K.grouped_linear(q_slab.view(-1, 128), L.w_uk, ws.q_abs, ht.tile_expert, ht.tile_row0, ht.num_tiles, ht.max_tiles,
                          ht.tile_rows, row_dst=ht.row_dst, ldo=REC, split_k=False)
         S, max_pages = b.page_table.shape

@@ -440,13 +440,32 @@ def index_k_store(k: torch.Tensor, slots: torch.Tensor, cache: torch.Tensor) -> 
 
 def mla_prep_a(a: torch.Tensor, q_lora: int, q_norm_w: torch.Tensor | None, kv_norm_w: torch.Tensor, inv_freq: torch.Tensor,
                positions: torch.Tensor, slots: torch.Tensor, q_a_out: torch.Tensor | None, cache: torch.Tensor, eps: float,
-               interleaved: bool) -> None:
+               interleaved: bool, lat_out: torch.Tensor | None = None) -> None:
     """a [T, q_lora + 576] -> q_a_out [T, q_lora] (normalised) and the [latent | rope] record at cache slot ``slots[t]``."""
     T = a.shape[0]
     assert a.shape[1] == q_lora + 576 and a.stride(1) == 1 and cache.shape[-1] == 576
     _n.check(_n.cuda_lib().cafd_mla_prep_a(a.data_ptr(), a.stride(0), q_lora, _ptr(q_norm_w), kv_norm_w.data_ptr(),
                                            inv_freq.data_ptr(), positions.data_ptr(), slots.data_ptr(), _ptr(q_a_out),
-                                           cache.data_ptr(), T, eps, int(interleaved), _stream()), "mla_prep_a")
+                                           cache.data_ptr(), T, eps, int(interleaved), _ptr(lat_out), _stream()), "mla_prep_a")
+
+
+def attn_prefill_mla(q_nope: torch.Tensor, q_rope: torch.Tensor, k_exp: torch.Tensor, v_exp: torch.Tensor, kv_tmp_start: torch.Tensor,
+                     latent_cache: torch.Tensor, page_table: torch.Tensor, seq_lens: torch.Tensor, q_start: torch.Tensor,
+                     out: torch.Tensor, max_q_len: int, heads: int, scale: float, qr_col0: int = 512) -> torch.Tensor:
+    """MLA prefill in expanded form.  q_nope [T, heads * 192] (first 128 columns of each head are used), q_rope
+    [T, heads, 576]-like buffer holding the rotated rope dims at ``qr_col0`` of every head, k_exp / v_exp
+    [rows, heads * 128] (kv_b applied to the cached latents in order; rows a multiple of 64), the latent cache for
+    the shared rope keys.  out [T, heads, 128]."""
+    T = q_nope.shape[0]
+    S, max_pages = page_table.shape
+    qs, qrs = q_nope.shape[1] // heads, q_rope.numel() // (q_rope.shape[0] * heads)
+    assert k_exp.shape[0] % 64 == 0 and k_exp.shape[1] == heads * 128 and k_exp.is_contiguous() and v_exp.is_contiguous()
+    _n.check(_n.cuda_lib().cafd_attn_prefill_mla(q_nope.data_ptr(), qs, q_rope.data_ptr(), qrs, qr_col0, k_exp.data_ptr(),
+                                                 v_exp.data_ptr(), k_exp.shape[0], kv_tmp_start.data_ptr(), latent_cache.data_ptr(),
+                                                 page_table.data_ptr(), seq_lens.data_ptr(), q_start.data_ptr(), out.data_ptr(),
+                                                 status_word(q_nope.device).data_ptr(), T, S, max_q_len, latent_cache.shape[0],
+                                                 max_pages, heads, scale, _stream()), "attn_prefill_mla")
+    return out
 
 
 def mla_q_split(q: torch.Tensor, inv_freq: torch.Tensor, positions: torch.Tensor, slab: torch.Tensor, q_abs: torch.Tensor,

@@ -183,7 +183,7 @@ class EngineBackend:
         b.last_rows[0][0] = n - 1
         b.upload()
         batch = Batch(b.tokens[1][:n], b.positions[1][:n], b.slots[1][:n], b.page_table[1].view(1, self.max_pages),
-                      b.seq_lens[1][:1], b.q_start[1][:2], n, True, b.last_rows[1][:1])
+                      b.seq_lens[1][:1], b.q_start[1][:2], n, True, b.last_rows[1][:1], fresh=start == 0)
         logits = self.engine.forward(batch)
         if self.has_mtp:
             # fill the MTP depth's K/V for the prompt: position t pairs with prompt token t+1 (the chunk's last row

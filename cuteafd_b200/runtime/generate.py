@@ -76,7 +76,7 @@ class Generator:
             b.last_rows[0][0] = n - 1
             self.h2d_bytes += b.upload()
             batch = Batch(b.tokens[1][:n], b.positions[1][:n], b.slots[1][:n], b.page_table[1].view(1, self.max_pages),
-                          b.seq_lens[1][:1], b.q_start[1][:2], n, True, b.last_rows[1][:1])
+                          b.seq_lens[1][:1], b.q_start[1][:2], n, True, b.last_rows[1][:1], fresh=start == 0)
             logits = self.engine.forward(batch)
             seq.tokens.extend(part)
             seq.kv_len = start + n

@@ -166,3 +166,33 @@ def test_mla_engine_matches_oracle(K, use_graphs, indexer):
         assert errs[len(errs) // 2] < 0.03 and errs[-3] < 0.05 and errs[-1] < 0.25, errs
     if forced:
         assert sum(agree) / len(agree) > 0.95 and min(agree) > 0.8, agree
+
+
+@pytest.mark.parametrize("heads,n", [(16, 128), (16, 300), (128, 200)])
+def test_mla_prefill_expanded_form(K, heads, n):
+    """Expanded-form MLA prefill kernel: per-head 128-dim keys/values plus a 64-dim rope part shared by all heads."""
+    g = torch.Generator().manual_seed(heads + n)
+    dev = _dev()
+    cache, table, dense = _latent_cache([n], seed=5)
+    q = (torch.randn(n, heads, 192, generator=g) * 0.5).to(torch.bfloat16)
+    qr_buf = torch.zeros(n, heads, 576, dtype=torch.bfloat16)
+    qr_buf[:, :, 512:] = q[:, :, 128:]
+    rows = ((n + 63) // 64) * 64
+    kx = torch.zeros(rows, heads, 128, dtype=torch.bfloat16); vx = torch.zeros(rows, heads, 128, dtype=torch.bfloat16)
+    kx[:n] = (torch.randn(n, heads, 128, generator=g) * 0.5).to(torch.bfloat16)
+    vx[:n] = (torch.randn(n, heads, 128, generator=g) * 0.5).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(192)
+    out = torch.full((n, heads, 128), 7.0, dtype=torch.bfloat16, device=dev)
+    i32 = dict(dtype=torch.int32, device=dev)
+    for _ in range(2):
+        K.attn_prefill_mla(q.reshape(n, heads * 192).to(dev), qr_buf.to(dev), kx.reshape(rows, -1).to(dev), vx.reshape(rows, -1).to(dev),
+                           torch.zeros(1, **i32), cache, table, torch.tensor([n], **i32), torch.tensor([0, n], **i32), out, n, heads, scale)
+    torch.cuda.synchronize()
+    assert K.read_status() == 0
+    k_rope = dense[0][:, 512:].float()                                     # shared across heads
+    s = (torch.einsum("nhd,lhd->nhl", q[:, :, :128].float(), kx[:n].float()) +
+         torch.einsum("nhd,ld->nhl", q[:, :, 128:].float(), k_rope)) * scale
+    mask = torch.arange(n)[None, None, :] > torch.arange(n)[:, None, None]
+    ref = torch.einsum("nhl,lhd->nhd", torch.softmax(s.masked_fill(mask, float("-inf")), -1), vx[:n].float())
+    err = (out.float().cpu() - ref).abs().max().item()
+    assert err < 0.03 * max(1.0, ref.abs().max().item()), err
