@@ -32,7 +32,7 @@ PUBLISHED = {"c1": 199.2, "c8": 504.1, "c16": 734.6, "prefill_tok_s": 8646.0, "t
 def reference_arm() -> None:
     """The reference is a Rust + CUDA (sm_120/sm_121) engine whose kernel submodule is absent and
     whose Python package does not install offline; there is nothing runnable to time."""
-    why = ("reference not installable offline: /root/reference has no pyproject/setup.py at its root, "
+    why = ("reference not installable offline: its source tree has no pyproject/setup.py at its root, "
            "python/ fails metadata generation without its index-only dependencies, the Rust workspace needs "
            "cargo + crates.io, and third_party/sparkinfer (all hot kernels) is an empty submodule")
     ref_dir = os.path.join(REPO, "baseline", "_ref")
