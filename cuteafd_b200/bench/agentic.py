@@ -1,0 +1,128 @@
+"""Agentic prefix-cache workload: several sessions share a long prefix and run many turns; every turn appends new
+tokens to the session's whole history and decodes a reply.  The exact prefix cache should serve everything but the
+appended tokens from cached pages, byte for byte.
+
+    python -m cuteafd_b200.bench.agentic --sessions 8 --prefix 16384 --turns 20 --append 512 --decode 128 --layers 4
+    python -m cuteafd_b200.bench.agentic --oracle --sessions 3 --prefix 256 --turns 4 --append 32 --decode 8    # CPU
+
+Reports prefill tokens served from cache vs computed, wall time, decode tok/s, and (``--verify N``) checks N sampled
+turns twice: served again from the warm cache they must reproduce the hash of every selected logit row exactly, and
+recomputed on a cold cache they must emit the same tokens.  The reference checks the same property in its release card ("exact
+prefix-cache restore", docs/release-testing.md:9-20) and keeps snapshots per turn
+(rust/crates/cuteafd-engine/src/prefix/cache.rs).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import random
+import time
+
+import torch
+
+from ..runtime.scheduler import Request, Scheduler, collect
+
+
+def drive(sched: Scheduler, reqs: list[Request], max_steps: int = 10_000_000) -> list[dict]:
+    for r in reqs:
+        sched.submit(r)
+    for _ in range(max_steps):
+        if not sched.step() and sched.waiting.empty() and not sched.pending and not sched.prefilling and not sched.decoding:
+            break
+    return [collect(r, timeout=5.0) for r in reqs]
+
+
+def run(make_backend, vocab: int, sessions: int, prefix: int, turns: int, append: int, decode: int, verify: int,
+        concurrency: int, seed: int = 0) -> dict:
+    rng = random.Random(seed)
+    shared = [rng.randrange(vocab) for _ in range(prefix)]
+    hist = [list(shared) for _ in range(sessions)]
+    be = make_backend()
+    sched = Scheduler(be, max_active=concurrency)
+    log = []                                              # (session, turn, prompt, tokens, row hashes)
+    cached = computed = emitted = 0
+    t0 = time.time()
+    for turn in range(turns):
+        reqs = []
+        for s in range(sessions):
+            hist[s] += [rng.randrange(vocab) for _ in range(append)]
+            reqs.append(Request(list(hist[s]), max_tokens=decode, record_rows=True, speculation=False))
+        outs = drive(sched, reqs)
+        for s, (r, o) in enumerate(zip(reqs, outs)):
+            if o["error"]:
+                raise RuntimeError(f"session {s} turn {turn}: {o['error']}")
+            c = o["usage"].get("cached_tokens", 0)
+            cached += c
+            computed += len(r.prompt) - c
+            emitted += len(o["tokens"])
+            log.append((s, turn, list(r.prompt), o["tokens"], o["row_hashes"]))
+            hist[s] += o["tokens"]
+    wall = time.time() - t0
+    # (a) exact restore: the same turn served again from the warm cache must reproduce every selected logit row bit for
+    #     bit (the restored pages are the bytes that were computed the first time);
+    # (b) cold recompute on an empty cache: the emitted tokens must agree.  Row bits can differ there, because a cold
+    #     prefill computes in one chunk what the live session computed as decode steps, and the GEMM / attention
+    #     kernels are not batch-invariant (split-K and split-KV change the summation order).
+    restore_mism = token_mism = checked = 0
+    if verify:
+        picks = rng.sample(log, min(verify, len(log)))
+        for s, turn, prompt, toks, hashes in picks:
+            o = drive(sched, [Request(prompt, max_tokens=len(toks), record_rows=True, speculation=False)])[0]
+            again = drive(sched, [Request(prompt, max_tokens=len(toks), record_rows=True, speculation=False)])[0]
+            checked += 1
+            if o["tokens"] != again["tokens"] or o["row_hashes"] != again["row_hashes"]:
+                restore_mism += 1
+        cold_be = make_backend()
+        for s, turn, prompt, toks, hashes in picks:
+            o = drive(Scheduler(cold_be, max_active=1), [Request(prompt, max_tokens=len(toks), speculation=False)])[0]
+            if o["tokens"] != toks:
+                token_mism += 1
+    total_prompt = cached + computed
+    return {"sessions": sessions, "prefix": prefix, "turns": turns, "append": append, "decode": decode,
+            "prompt_tokens": total_prompt, "served_from_cache": cached, "computed": computed,
+            "cache_share": round(cached / max(1, total_prompt), 4), "emitted_tokens": emitted, "wall_s": round(wall, 2),
+            "emitted_tok_s": round(emitted / wall, 1), "verified_turns": checked, "restore_mismatches": restore_mism,
+            "cold_token_mismatches": token_mism,
+            "prefix_stats": be.prefix.describe() if hasattr(be, "prefix") else {}}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--sessions", type=int, default=8); ap.add_argument("--prefix", type=int, default=16384)
+    ap.add_argument("--turns", type=int, default=20); ap.add_argument("--append", type=int, default=512)
+    ap.add_argument("--decode", type=int, default=128); ap.add_argument("--verify", type=int, default=4)
+    ap.add_argument("--concurrency", type=int, default=8)
+    ap.add_argument("--oracle", action="store_true", help="CPU oracle backend on the tiny model")
+    ap.add_argument("--preset", default="qwen3-30b-a3b"); ap.add_argument("--layers", type=int, default=4)
+    a = ap.parse_args()
+    from ..config import PRESETS, tiny_moe
+    ctx = a.prefix + a.turns * (a.append + a.decode) + 64
+    if a.oracle:
+        from ..ref.model import init_weights
+        from ..runtime.backends import OracleBackend
+        cfg = tiny_moe()
+        params = init_weights(cfg, seed=0)
+        pages = (ctx // 64 + 2) * (a.sessions + 2) * 2
+        make = lambda: OracleBackend(cfg, params, total_pages=pages, prefill_chunk=64, max_decode_rows=a.concurrency)   # noqa: E731
+    else:
+        from ..runtime.backends import EngineBackend
+        dev = torch.device("cuda:0")
+        cfg = PRESETS[a.preset]().replace(num_layers=a.layers)
+        if cfg.is_mla:
+            from ..models.mla_moe import LatentCache as Cache, MlaMoeEngine as Engine, MlaMoeWeights as Weights
+        else:
+            from ..models.gqa_moe import GqaMoeEngine as Engine, GqaMoeWeights as Weights, KvCache as Cache
+        W = Weights.random_init(cfg, dev)
+        pps = ctx // 64 + 2
+        pages = pps * (a.sessions + 2) * 2
+
+        def make():
+            eng = Engine(cfg, W, Cache(cfg, pages, dev), max_tokens=2048, max_seqs=a.concurrency * 2)
+            return EngineBackend(eng, pages, pps, prefill_chunk=2048, max_decode_rows=a.concurrency)
+    out = run(make, cfg.vocab_size, a.sessions, a.prefix, a.turns, a.append, a.decode, a.verify, a.concurrency)
+    out["model"] = cfg.name + (f" ({cfg.num_layers} layers)" if not a.oracle else "")
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

@@ -294,3 +294,17 @@ def test_two_decode_lanes_serve_alternately_without_changing_tokens(oracle):
     two = _run(sch, [Request(p, max_tokens=8) for p in prompts])
     assert [o["tokens"] for o in two] == [o["tokens"] for o in one]
     assert sch.stats.lane_rounds.get(0, 0) > 0 and sch.stats.lane_rounds.get(1, 0) > 0
+
+
+def test_agentic_prefix_workload_on_the_oracle():
+    """Shared prefix, several sessions and turns: most prompt tokens come from the cache, a turn served again from
+    the warm cache reproduces its logit rows exactly, and a cold recompute emits the same tokens."""
+    from cuteafd_b200.bench.agentic import run
+    from cuteafd_b200.config import tiny_moe
+    from cuteafd_b200.ref.model import init_weights
+    cfg = tiny_moe()
+    params = init_weights(cfg, seed=0)
+    out = run(lambda: OracleBackend(cfg, params, total_pages=256, prefill_chunk=64, max_decode_rows=3), cfg.vocab_size,
+              sessions=3, prefix=192, turns=3, append=24, decode=6, verify=3, concurrency=3)
+    assert out["cache_share"] > 0.5 and out["restore_mismatches"] == 0 and out["cold_token_mismatches"] == 0
+    assert out["emitted_tokens"] == 3 * 3 * 6
