@@ -64,6 +64,7 @@ def run(make_backend, vocab: int, sessions: int, prefix: int, turns: int, append
     #     prefill computes in one chunk what the live session computed as decode steps, and the GEMM / attention
     #     kernels are not batch-invariant (split-K and split-KV change the summation order).
     restore_mism = token_mism = checked = 0
+    cold_same = cold_total = 0
     if verify:
         picks = rng.sample(log, min(verify, len(log)))
         for s, turn, prompt, toks, hashes in picks:
@@ -77,12 +78,17 @@ def run(make_backend, vocab: int, sessions: int, prefix: int, turns: int, append
             o = drive(Scheduler(cold_be, max_active=1), [Request(prompt, max_tokens=len(toks), speculation=False)])[0]
             if o["tokens"] != toks:
                 token_mism += 1
+            # share of the reply that agrees before the first divergence (a random-weight model has near-flat logits, so
+            # bf16-level differences between chunked and stepwise computation flip an argmax early; real checkpoints agree)
+            n_same = next((i for i, (x, y) in enumerate(zip(o["tokens"], toks)) if x != y), min(len(o["tokens"]), len(toks)))
+            cold_same += n_same
+            cold_total += len(toks)
     total_prompt = cached + computed
     return {"sessions": sessions, "prefix": prefix, "turns": turns, "append": append, "decode": decode,
             "prompt_tokens": total_prompt, "served_from_cache": cached, "computed": computed,
             "cache_share": round(cached / max(1, total_prompt), 4), "emitted_tokens": emitted, "wall_s": round(wall, 2),
             "emitted_tok_s": round(emitted / wall, 1), "verified_turns": checked, "restore_mismatches": restore_mism,
-            "cold_token_mismatches": token_mism,
+            "cold_token_mismatches": token_mism, "cold_agreeing_prefix_share": round(cold_same / max(1, cold_total), 3),
             "prefix_stats": be.prefix.describe() if hasattr(be, "prefix") else {}}
 
 
