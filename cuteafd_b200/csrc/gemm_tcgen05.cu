@@ -152,6 +152,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
     if (splits < 1) splits = 1;
   }
   const int total_tiles = base_tiles * splits;   // work units
+  // Tile order.  Expert-grouped prefill: the token slab is far larger than L2 and each expert's
+  // weights are used by only a few row tiles, so neighbouring CTAs take the weight tiles of ONE row
+  // tile (the row tile is read from DRAM once, an expert's weights stay in L2 for its few row
+  // tiles).  Otherwise neighbouring CTAs share a weight tile and walk the rows.
+  const bool wt_fastest = !kSwap && p.tile_expert != nullptr;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -164,8 +169,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
       bool ok = true;
       for (int unit = blockIdx.x; ok && unit < total_tiles; unit += gridDim.x) {
         const int tile = unit / splits, split = unit - tile * splits;
-        const int xt = tile % x_tiles;
-        const int wt = tile / x_tiles;
+        const int xt = wt_fastest ? tile / p.w_tiles : tile % x_tiles;
+        const int wt = wt_fastest ? tile % p.w_tiles : tile / x_tiles;
         const int x_row0 = p.tile_row0 ? p.tile_row0[xt] : xt * kBX;
         const int expert = p.tile_expert ? p.tile_expert[xt] : 0;
         const int w_row0 = expert * p.w_rows_per_expert + wt * kBW;
@@ -232,8 +237,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ C
     bool ok = true;
     for (int unit = blockIdx.x; ok && unit < total_tiles; unit += gridDim.x) {
       const int tile = unit / splits, split = unit - tile * splits;
-      const int xt = tile % x_tiles;
-      const int wt = tile / x_tiles;
+      const int xt = wt_fastest ? tile / p.w_tiles : tile % x_tiles;
+      const int wt = wt_fastest ? tile % p.w_tiles : tile / x_tiles;
       const int x_row0 = p.tile_row0 ? p.tile_row0[xt] : xt * kBX;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, p.status, kTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
