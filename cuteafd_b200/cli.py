@@ -120,6 +120,18 @@ def cmd_gateway(a: argparse.Namespace) -> int:
     return run_gateway(a)
 
 
+def cmd_quantize(a: argparse.Namespace) -> int:
+    from .quant.quantize import QUANT_ROLES, Recipe, merge, quantize_snapshot
+    roles = {r: getattr(a, r) for r in QUANT_ROLES if getattr(a, r) != "keep"}
+    recipe = Recipe(roles, seed=a.seed)
+    if not a.merge_only:
+        quantize_snapshot(a.src, a.dst, recipe, a.rank, a.world, a.device)
+    if a.merge_only or a.world == 1:
+        m = merge(a.src, a.dst, recipe, a.world)
+        print(json.dumps(m["summary"]))
+    return 0
+
+
 def cmd_usage(a: argparse.Namespace) -> int:
     from .serve.usage import usage_report
     print(json.dumps(usage_report(a.db, a.hours), indent=1))
@@ -182,6 +194,16 @@ def build_parser() -> argparse.ArgumentParser:
     gw.add_argument("--upstream", default="http://127.0.0.1:8000"); gw.add_argument("--host", default="127.0.0.1")
     gw.add_argument("--port", type=int, default=8080); gw.add_argument("--model-map", default="")
     gw.set_defaults(fn=cmd_gateway)
+
+    q = sub.add_parser("quantize", help="re-encode a snapshot into a serving format (per-role recipe)")
+    q.add_argument("src"); q.add_argument("dst")
+    for role, default in (("routed_expert", "keep"), ("shared_expert", "keep"), ("dense_ffn", "keep"), ("attention", "keep"),
+                          ("indexer", "keep"), ("mtp", "keep")):
+        q.add_argument("--" + role.replace("_", "-"), dest=role, default=default, help="target format for this role")
+    q.add_argument("--rank", type=int, default=0); q.add_argument("--world", type=int, default=1)
+    q.add_argument("--device", default="cpu"); q.add_argument("--seed", type=int, default=0)
+    q.add_argument("--merge-only", action="store_true", help="all workers have finished: write the index and the manifest")
+    q.set_defaults(fn=cmd_quantize)
 
     u = sub.add_parser("usage", help="request accounting report")
     u.add_argument("--db", default="usage.sqlite"); u.add_argument("--hours", type=float, default=24.0)
