@@ -16,7 +16,7 @@ import uuid
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 
 from ..runtime.scheduler import FAIL_BAD_REQUEST, FAIL_UNAVAILABLE, Request, Scheduler
-from . import api
+from . import api, ws
 from .tokenizer import StreamDecoder
 
 CONSOLE_HTML = """<!doctype html><title>cuteafd_b200 console</title>
@@ -89,6 +89,20 @@ def make_handler(state: ServerState):
         # ---- GET ----------------------------------------------------------------------------------
         def do_GET(self):
             path = self.path.split("?", 1)[0]
+            if path in ("/v1/realtime", "/v1/responses") and ws.wants_upgrade(self.headers):
+                if not self._authorized():
+                    return self._json(401, {"error": {"message": "invalid API key", "type": "authentication_error"}})
+                sock = ws.upgrade(self)
+                if sock is None:
+                    return None
+                if path == "/v1/realtime":
+                    query = self.path.partition("?")[2]
+                    model = next((kv[6:] for kv in query.split("&") if kv.startswith("model=")), None)
+                    ws.serve_realtime(state, sock, model)
+                else:
+                    ws.serve_responses(state, sock)
+                sock.close()
+                return None
             if path == "/health":
                 ok = state.sched.ready.is_set()
                 return self._json(200 if ok else 503, {"status": "ok" if ok else "starting", "model": state.model_id})

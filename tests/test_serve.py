@@ -159,3 +159,74 @@ def test_recognizers_and_tokenizer():
     text, calls = tokenizer.parse_tool_calls('ok <tool_call>{"name": "f", "arguments": {"x": 1}}</tool_call> done')
     assert calls[0]["function"]["name"] == "f" and "tool_call" not in text
     assert "<|im_start|>assistant" in tokenizer.render_chat([{"role": "user", "content": "q"}])
+
+
+# ---- WebSocket endpoints --------------------------------------------------------------------------------
+def _ws(server, path, key="sekret"):
+    from websockets.sync.client import connect
+    return connect(f"ws://127.0.0.1:{server.port}{path}", additional_headers={"Authorization": f"Bearer {key}"},
+                   open_timeout=30, close_timeout=5)
+
+
+def _until(ws, kind, limit=400):
+    seen = []
+    for _ in range(limit):
+        ev = json.loads(ws.recv(timeout=120))
+        seen.append(ev)
+        if ev["type"] == kind:
+            return seen
+    raise AssertionError(f"no {kind} in {[e['type'] for e in seen]}")
+
+
+def test_realtime_text_session(server):
+    with _ws(server, "/v1/realtime?model=tiny") as ws:
+        first = json.loads(ws.recv(timeout=30))
+        assert first["type"] == "session.created" and first["session"]["modalities"] == ["text"]
+        assert first["session"]["model"] == "tiny"
+        ws.send(json.dumps({"type": "session.update", "session": {"instructions": "be brief", "temperature": 0.0,
+                                                                    "max_response_output_tokens": 6}}))
+        assert _until(ws, "session.updated")[-1]["session"]["instructions"] == "be brief"
+        ws.send(json.dumps({"type": "conversation.item.create",
+                            "item": {"type": "message", "role": "user", "content": [{"type": "input_text", "text": "hello"}]}}))
+        assert _until(ws, "conversation.item.created")[-1]["item"]["content"][0]["text"] == "hello"
+        ws.send(json.dumps({"type": "response.create"}))
+        evs = _until(ws, "response.done")
+        kinds = [e["type"] for e in evs]
+        assert kinds[0] == "response.created" and "response.output_item.added" in kinds and "response.text.done" in kinds
+        done = evs[-1]["response"]
+        assert done["status"] == "completed" and 1 <= done["usage"]["output_tokens"] <= 6
+        text = "".join(e["delta"] for e in evs if e["type"] == "response.text.delta")
+        assert text == done["output"][0]["content"][0]["text"]
+        # the reply is part of the conversation: a second turn sees a longer prompt
+        ws.send(json.dumps({"type": "response.create", "response": {"max_output_tokens": 3}}))
+        second = _until(ws, "response.done")[-1]["response"]
+        assert second["usage"]["input_tokens"] > done["usage"]["input_tokens"]
+        # audio and unknown events are errors, not disconnects
+        ws.send(json.dumps({"type": "input_audio_buffer.append", "audio": "AAAA"}))
+        assert _until(ws, "error")[-1]["error"]["type"] == "unsupported_modality"
+        ws.send("not json")
+        assert _until(ws, "error")[-1]["error"]["type"] == "invalid_request_error"
+        ws.ping().wait(10)
+
+
+def test_responses_over_websocket_and_cancel(server):
+    with _ws(server, "/v1/responses") as ws:
+        ws.send(json.dumps({"type": "response.create", "response": {"input": "count", "max_output_tokens": 5}}))
+        evs = _until(ws, "response.completed")
+        assert evs[0]["type"] == "response.created"
+        rid = evs[-1]["response"]["id"]
+        st, _, raw = call(server, "GET", f"/v1/responses/{rid}")
+        assert st == 200 and json.loads(raw)["id"] == rid
+        # a long response is cancelled from the client
+        ws.send(json.dumps({"type": "response.create", "input": "go on", "max_output_tokens": 4000}))
+        _until(ws, "response.created")
+        ws.send(json.dumps({"type": "response.cancel"}))
+        assert _until(ws, "response.cancelled", limit=5000)[-1]["response"]["status"] == "cancelled"
+        ws.send(json.dumps({"type": "bogus"}))
+        assert _until(ws, "error")[-1]["error"]["type"] == "invalid_request_error"
+
+
+def test_websocket_needs_the_key(server):
+    from websockets.exceptions import InvalidStatus
+    with pytest.raises(InvalidStatus):
+        _ws(server, "/v1/realtime", key="wrong").__enter__()
