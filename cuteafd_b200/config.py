@@ -56,6 +56,7 @@ class ModelConfig:
     # storage
     weight_format: str = "bf16"          # bf16 | fp8_block128 | nvfp4 | mxfp4 | exl3
     tie_embeddings: bool = False
+    kv_format: str = "bf16"              # MLA cache record: bf16 (1152 bytes) | fp8_ds_mla (656 bytes; sparse attention only)
 
     # ---- derived -----------------------------------------------------------------
     @property

@@ -54,6 +54,9 @@ struct MlaDev {
   const int* sparse_idx;   // [tokens, sparse_k]
   const uint8_t* cache;    // latent cache base (records gathered with plain 16-byte async copies)
   int sparse_k;
+  // gathered mode: `cache` is a bf16 buffer [n_blocks, sparse_k, 576] that already holds entry e of block b at
+  // row b * sparse_k + e (written by mla_fp8_gather from FP8 records); sparse_idx still says which entries exist.
+  int gathered;
 };
 
 // Shared-memory descriptor without swizzle (canonical K-major "interleave" layout): 8x16-byte core
@@ -148,7 +151,9 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int e = (t_begin + j) * kKvTile + lane;
         const int pos = e < max_limit ? idx[e] : -1;
         long long rec = -1;
-        if (pos >= 0 && (pos >> 6) < seq_pages) rec = (static_cast<long long>(pt[pos >> 6]) * 64 + (pos & 63)) * (kRec * 2);
+        if (pos >= 0 && (pos >> 6) < seq_pages)
+          rec = (p.gathered ? static_cast<long long>(blockIdx.x) * p.sparse_k + e
+                            : static_cast<long long>(pt[pos >> 6]) * 64 + (pos & 63)) * (kRec * 2);
         const uint32_t dst0 = smem_u32(sC + st * kKvBytes);
 #pragma unroll 4
         for (int c = lane; c < kKvTile * 72; c += 32) {
@@ -413,11 +418,11 @@ extern "C" long long cafd_mla_scratch_floats(int n_blocks, int splits) {
 // out [rows, 512] bf16, rows ordered like q, or head-major (row = head * out_tpad + token) when out_tpad > 0.
 // heads must divide 128.  With sparse_idx [tokens, sparse_k] (ascending positions, -1 padded) every block is one query token
 // and attends only to its listed positions.
-extern "C" int cafd_mla_attention(const void* q, const void* cache, const int* page_table, const int* seq_lens,
-                                  const int* q_start, const int* block_seq, const int* block_tok0, void* out,
-                                  float* scratch, uint32_t* status, long long total_rows, int n_blocks, int num_pages,
-                                  int max_pages, int heads, int splits, int out_tpad, float scale,
-                                  const int* sparse_idx, int sparse_k, cafd_stream_t s) {
+static int mla_attention_impl(const void* q, const void* cache, const int* page_table, const int* seq_lens,
+                              const int* q_start, const int* block_seq, const int* block_tok0, void* out,
+                              float* scratch, uint32_t* status, long long total_rows, int n_blocks, int num_pages,
+                              int max_pages, int heads, int splits, int out_tpad, float scale,
+                              const int* sparse_idx, int sparse_k, int gathered, cafd_stream_t s) {
   if (n_blocks <= 0) return 0;
   if (heads <= 0 || kMlaRows % heads) return -10;
   if (splits < 1) splits = 1;
@@ -439,6 +444,7 @@ extern "C" int cafd_mla_attention(const void* q, const void* cache, const int* p
   p.max_pages = max_pages; p.heads = heads; p.splits = splits; p.out_tpad = out_tpad;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.sparse_idx = sparse_idx; p.sparse_k = sparse_k; p.cache = static_cast<const uint8_t*>(cache);
+  p.gathered = gathered;
   static bool attr = false;
   if (!attr) {
     CAFD_CHECK_CUDA(cudaFuncSetAttribute(mla_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));
@@ -450,6 +456,29 @@ extern "C" int cafd_mla_attention(const void* q, const void* cache, const int* p
     launch_pdl(mla_merge_kernel, dim3(n_blocks, 2, kMlaRows), dim3(kHalf), 0, st, static_cast<const float*>(scratch), block_seq,
                block_tok0, q_start, static_cast<__nv_bfloat16*>(out), heads, splits, out_tpad, sparse_idx ? 1 : 0);
   return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int cafd_mla_attention(const void* q, const void* cache, const int* page_table, const int* seq_lens,
+                                  const int* q_start, const int* block_seq, const int* block_tok0, void* out,
+                                  float* scratch, uint32_t* status, long long total_rows, int n_blocks, int num_pages,
+                                  int max_pages, int heads, int splits, int out_tpad, float scale,
+                                  const int* sparse_idx, int sparse_k, cafd_stream_t s) {
+  return mla_attention_impl(q, cache, page_table, seq_lens, q_start, block_seq, block_tok0, out, scratch, status, total_rows,
+                            n_blocks, num_pages, max_pages, heads, splits, out_tpad, scale, sparse_idx, sparse_k, 0, s);
+}
+
+// Sparse attention over records that mla_fp8_gather expanded: gathered [n_blocks, sparse_k, 576] bf16.
+extern "C" int cafd_mla_attention_gathered(const void* q, const void* gathered, const int* page_table, const int* seq_lens,
+                                           const int* q_start, const int* block_seq, const int* block_tok0, void* out,
+                                           float* scratch, uint32_t* status, long long total_rows, int n_blocks,
+                                           int max_pages, int heads, int splits, int out_tpad, float scale,
+                                           const int* sparse_idx, int sparse_k, cafd_stream_t s) {
+  if (!sparse_idx || sparse_k <= 0) return -10;
+  // the dense-path tensor map is built but unused in sparse mode: describe the buffer as whole 64-record pages
+  const int pages = static_cast<int>((static_cast<long long>(n_blocks) * sparse_k) / 64);
+  if (pages < 1) return -10;
+  return mla_attention_impl(q, gathered, page_table, seq_lens, q_start, block_seq, block_tok0, out, scratch, status, total_rows,
+                            n_blocks, pages, max_pages, heads, splits, out_tpad, scale, sparse_idx, sparse_k, 1, s);
 }
 
 CAFD_WAIT_LIMIT_SETTER(cafd_mla_set_wait_limit_ns)

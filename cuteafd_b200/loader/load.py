@@ -110,11 +110,17 @@ def load_gqa_engine_weights(path: str, device: torch.device, with_experts: bool 
     return cfg, W
 
 
-def load_engine(path: str, device: torch.device, num_pages: int, max_tokens: int, max_seqs: int):
+def load_engine(path: str, device: torch.device, num_pages: int, max_tokens: int, max_seqs: int, kv_format: str = "auto"):
     """(cfg, engine) for a snapshot: the GQA engine streams its weights tensor by tensor; MLA checkpoints (and any
-    checkpoint with MTP depths) go through the dense parameter dictionary, decoded to bf16."""
+    checkpoint with MTP depths) go through the dense parameter dictionary, decoded to bf16.  ``kv_format`` "auto"
+    picks the 656-byte FP8 latent record for sparse-attention (indexer) checkpoints and bf16 records otherwise."""
     snap = open_snapshot(path)
     cfg = snap.cfg
+    if cfg.is_mla:
+        want = ("fp8_ds_mla" if cfg.indexer_heads else "bf16") if kv_format == "auto" else kv_format
+        if want == "fp8_ds_mla" and not cfg.indexer_heads:
+            raise ValueError("fp8_ds_mla records need the sparse attention path (a checkpoint with an indexer)")
+        cfg = cfg.replace(kv_format=want)
     if cfg.is_mla:
         from ..models.mla_moe import LatentCache, MlaMoeEngine, MlaMoeWeights
         _, params = load_params(path, dtype=torch.bfloat16)

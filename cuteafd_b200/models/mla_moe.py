@@ -134,19 +134,25 @@ class MlaMoeWeights:
 
 
 class LatentCache:
-    """Paged latent pools, one per layer: [num_pages, 64, 576] bf16 (1152 bytes per token and layer, for all
-    heads).  Page 0 stays all-zero."""
+    """Paged latent pools, one per layer.  bf16 records: [num_pages, 64, 576] (1152 bytes per token and layer, for all
+    heads).  FP8 records (``cfg.kv_format == "fp8_ds_mla"``): [num_pages, 64, 656] bytes = 512 E4M3 latents, 4 fp32
+    scales, 64 bf16 rope dims; served by the sparse-attention path only.  Page 0 stays all-zero."""
 
     def __init__(self, cfg: ModelConfig, num_pages: int, device: torch.device):
         self.num_pages = num_pages
         n = cfg.num_layers + cfg.mtp_layers
-        self.c = [torch.zeros(num_pages, PAGE, REC, dtype=torch.bfloat16, device=device) for _ in range(n)]
+        self.fp8 = cfg.kv_format == "fp8_ds_mla"
+        if self.fp8:
+            assert cfg.indexer_heads, "FP8 latent records are read by the sparse (indexer) attention path"
+            self.c = [torch.zeros(num_pages, PAGE, K.FP8_RECORD_BYTES, dtype=torch.uint8, device=device) for _ in range(n)]
+        else:
+            self.c = [torch.zeros(num_pages, PAGE, REC, dtype=torch.bfloat16, device=device) for _ in range(n)]
         # index keys of the lightning indexer, paged like the latent records
         self.idx = ([torch.zeros(num_pages, PAGE, cfg.indexer_dim, dtype=torch.bfloat16, device=device) for _ in range(n)]
                     if cfg.indexer_heads else [])
 
     def bytes_per_page(self) -> int:
-        return len(self.c) * PAGE * REC * 2 + sum(t[0].numel() * 2 for t in self.idx)
+        return sum(t[0].numel() * t.element_size() for t in self.c + self.idx)
 
     def copy_page(self, src: int, dst: int) -> None:
         for c in self.c + self.idx:
@@ -174,6 +180,7 @@ class _HeadTiles:
 class MlaMoeEngine(GqaMoeEngine):
     """Single-GPU MLA engine; shares the FFN half, the logits head and greedy selection with the GQA engine."""
     EXPANDED_PREFILL_TOKENS = 64     # fresh prompt chunks of at least this many tokens use the expanded-form attention
+    GATHER_BLOCKS = 128              # query tokens per FP8 gather + attention pass (2048 records each: 302 MB of bf16)
 
     def __init__(self, cfg: ModelConfig, weights: MlaMoeWeights, kv: LatentCache, max_tokens: int, max_seqs: int = 64,
                  build_moe: bool = True):
@@ -281,8 +288,22 @@ class MlaMoeEngine(GqaMoeEngine):
             need = K.mla_scratch_floats(nb, splits)
             if self._scratch is None or self._scratch.numel() < need:
                 self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
-        K.mla_attention(ws.q_abs[:T], self.kv.c[i], b.page_table, b.seq_lens, b.q_start, bseq, btok, o_slab, self.scale,
-                        splits, self._scratch if splits > 1 else None, out_tpad=ht.t_pad, sparse_idx=sel)
+        if self.kv.fp8:
+            # FP8 records: the selected records of a slice of query tokens are expanded to bf16 (the buffer stays in L2
+            # for decode-sized steps) and the sparse kernel reads them from there
+            k = sel.shape[1]
+            per = min(nb, self.GATHER_BLOCKS)
+            if getattr(ws, "gathered", None) is None or ws.gathered.numel() < max(per * k, 64) * REC:
+                ws.gathered = torch.zeros(max(per * k, 64) * REC, dtype=torch.bfloat16, device=self.device)
+            for b0 in range(0, nb, per):
+                bs, bt = bseq[b0:b0 + per], btok[b0:b0 + per]
+                K.mla_fp8_gather(self.kv.c[i], sel, b.page_table, b.seq_lens, b.q_start, bs, bt, ws.gathered)
+                K.mla_attention(ws.q_abs[:T], None, b.page_table, b.seq_lens, b.q_start, bs, bt, o_slab, self.scale, splits,
+                                self._scratch if splits > 1 else None, out_tpad=ht.t_pad, sparse_idx=sel, gathered=ws.gathered)
+                self.launches += 1 + (1 if splits > 1 else 0) + (1 if b0 else 0)
+        else:
+            K.mla_attention(ws.q_abs[:T], self.kv.c[i], b.page_table, b.seq_lens, b.q_start, bseq, btok, o_slab, self.scale,
+                            splits, self._scratch if splits > 1 else None, out_tpad=ht.t_pad, sparse_idx=sel)
         K.grouped_linear(o_slab.view(-1, 512), L.w_uv, ws.attn, ht.tile_expert, ht.tile_row0, ht.num_tiles, ht.max_tiles,
                          ht.tile_rows, row_dst=ht.row_dst, ldo=cfg.v_head_dim, split_k=False)
         K.linear(ws.attn[:T], L.wo, out=ws.h[:T], residual=ws.h[:T])

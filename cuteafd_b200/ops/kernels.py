@@ -383,23 +383,51 @@ def mla_scratch_floats(n_blocks: int, splits: int) -> int:
 def mla_attention(q_abs: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor, seq_lens: torch.Tensor,
                   q_start: torch.Tensor, block_seq: torch.Tensor, block_tok0: torch.Tensor, out: torch.Tensor,
                   scale: float, splits: int = 1, scratch: torch.Tensor | None = None, out_tpad: int = 0,
-                  sparse_idx: torch.Tensor | None = None) -> torch.Tensor:
+                  sparse_idx: torch.Tensor | None = None, gathered: torch.Tensor | None = None) -> torch.Tensor:
     """Absorbed MLA: q_abs [tokens, heads, 576] (512 latent-projected + 64 rope), cache [pages, 64, 576]
     (page 0 zero), out [tokens, heads, 512] = softmax(q c^T * scale) c[:, :512] with the causal rule
     that query token i of a sequence sees kv positions <= seq_len - q_len + i.  With ``out_tpad`` > 0
     the output is head-major: out [heads, out_tpad, 512].  With ``sparse_idx`` [tokens, k] (ascending positions,
     -1 padded; from ``index_topk``) each block must be a single token (``mla_blocks(q_lens, 128)``) and the
-    token attends to its listed positions only."""
+    token attends to its listed positions only.  With ``gathered`` [blocks, k, 576] (from ``mla_fp8_gather``) the
+    listed records are read from that buffer instead of the cache, which may then be None."""
     T, heads, rec = q_abs.shape
-    assert rec == 576 and 128 % heads == 0 and q_abs.is_contiguous() and out.is_contiguous() and cache.is_contiguous()
-    num_pages = cache.shape[0]
+    assert rec == 576 and 128 % heads == 0 and q_abs.is_contiguous() and out.is_contiguous()
     _, max_pages = page_table.shape
+    if gathered is not None:
+        k = sparse_idx.shape[1]
+        assert gathered.dtype == torch.bfloat16 and gathered.is_contiguous() and gathered.numel() >= max(block_seq.numel() * k, 64) * 576
+        _n.check(_n.cuda_lib().cafd_mla_attention_gathered(
+            q_abs.data_ptr(), gathered.data_ptr(), page_table.data_ptr(), seq_lens.data_ptr(), q_start.data_ptr(),
+            block_seq.data_ptr(), block_tok0.data_ptr(), out.data_ptr(), _ptr(scratch), status_word(q_abs.device).data_ptr(),
+            T * heads, block_seq.numel(), max_pages, heads, splits, out_tpad, scale, sparse_idx.data_ptr(), k, _stream()),
+            "mla_attention_gathered")
+        return out
+    assert cache.is_contiguous() and cache.dtype == torch.bfloat16
+    num_pages = cache.shape[0]
     _n.check(_n.cuda_lib().cafd_mla_attention(q_abs.data_ptr(), cache.data_ptr(), page_table.data_ptr(), seq_lens.data_ptr(),
                                               q_start.data_ptr(), block_seq.data_ptr(), block_tok0.data_ptr(), out.data_ptr(),
                                               _ptr(scratch), status_word(q_abs.device).data_ptr(), T * heads,
                                               block_seq.numel(), num_pages, max_pages, heads, splits, out_tpad, scale,
                                               _ptr(sparse_idx), sparse_idx.shape[1] if sparse_idx is not None else 0, _stream()),
              "mla_attention")
+    return out
+
+
+FP8_RECORD_BYTES = 656      # 512 E4M3 latents + 4 fp32 scales + 64 bf16 rope dims
+
+
+def mla_fp8_gather(cache: torch.Tensor, sparse_idx: torch.Tensor, page_table: torch.Tensor, seq_lens: torch.Tensor,
+                   q_start: torch.Tensor, block_seq: torch.Tensor, block_tok0: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Expand the FP8 records [pages, 64, 656] (uint8) that ``sparse_idx`` [tokens, k] lists into out [blocks, k, 576]
+    bf16; one block per query token, as in sparse attention.  Entries that do not exist are left untouched."""
+    assert cache.dtype == torch.uint8 and cache.shape[-1] == FP8_RECORD_BYTES and cache.is_contiguous()
+    k = sparse_idx.shape[1]
+    assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.numel() >= block_seq.numel() * k * 576
+    _n.check(_n.cuda_lib().cafd_mla_fp8_gather(cache.data_ptr(), sparse_idx.data_ptr(), k, page_table.data_ptr(),
+                                               page_table.shape[1], seq_lens.data_ptr(), q_start.data_ptr(),
+                                               block_seq.data_ptr(), block_tok0.data_ptr(), block_seq.numel(), out.data_ptr(),
+                                               _stream()), "mla_fp8_gather")
     return out
 
 
@@ -441,12 +469,17 @@ def index_k_store(k: torch.Tensor, slots: torch.Tensor, cache: torch.Tensor) -> 
 def mla_prep_a(a: torch.Tensor, q_lora: int, q_norm_w: torch.Tensor | None, kv_norm_w: torch.Tensor, inv_freq: torch.Tensor,
                positions: torch.Tensor, slots: torch.Tensor, q_a_out: torch.Tensor | None, cache: torch.Tensor, eps: float,
                interleaved: bool, lat_out: torch.Tensor | None = None) -> None:
-    """a [T, q_lora + 576] -> q_a_out [T, q_lora] (normalised) and the [latent | rope] record at cache slot ``slots[t]``."""
+    """a [T, q_lora + 576] -> q_a_out [T, q_lora] (normalised) and the [latent | rope] record at cache slot ``slots[t]``.
+    A bf16 cache [.., 576] takes bf16 records; a uint8 cache [.., 656] takes FP8 records (E4M3 latents with one fp32
+    scale per 128, bf16 rope)."""
     T = a.shape[0]
-    assert a.shape[1] == q_lora + 576 and a.stride(1) == 1 and cache.shape[-1] == 576
-    _n.check(_n.cuda_lib().cafd_mla_prep_a(a.data_ptr(), a.stride(0), q_lora, _ptr(q_norm_w), kv_norm_w.data_ptr(),
-                                           inv_freq.data_ptr(), positions.data_ptr(), slots.data_ptr(), _ptr(q_a_out),
-                                           cache.data_ptr(), T, eps, int(interleaved), _ptr(lat_out), _stream()), "mla_prep_a")
+    assert a.shape[1] == q_lora + 576 and a.stride(1) == 1
+    fp8 = cache.dtype == torch.uint8
+    assert cache.shape[-1] == (FP8_RECORD_BYTES if fp8 else 576) and (fp8 or cache.dtype == torch.bfloat16)
+    fn = _n.cuda_lib().cafd_mla_prep_a_fp8 if fp8 else _n.cuda_lib().cafd_mla_prep_a
+    _n.check(fn(a.data_ptr(), a.stride(0), q_lora, _ptr(q_norm_w), kv_norm_w.data_ptr(), inv_freq.data_ptr(),
+                positions.data_ptr(), slots.data_ptr(), _ptr(q_a_out), cache.data_ptr(), T, eps, int(interleaved),
+                _ptr(lat_out), _stream()), "mla_prep_a")
 
 
 def attn_prefill_mla(q_nope: torch.Tensor, q_rope: torch.Tensor, k_exp: torch.Tensor, v_exp: torch.Tensor, kv_tmp_start: torch.Tensor,

@@ -150,6 +150,8 @@ class RefDecoder:
             ckv = (x.float() @ p[a + "kv_a_proj_with_mqa.weight"].float().T).to(x.dtype)
             latent = ops.rmsnorm(ckv[:, : cfg.kv_lora_rank], p[a + "kv_a_layernorm.weight"], cfg.rms_eps)
             k_rope = ops.apply_rope(ckv[:, None, cfg.kv_lora_rank:], positions, cfg.rope_theta, cfg.rope_interleaved)[:, 0]
+            if cfg.kv_format == "fp8_ds_mla":
+                latent = ops.fp8_latent_roundtrip(latent)          # what the 656-byte record keeps of the latents
             rec = [latent, k_rope]
             if cfg.indexer_heads:
                 rec.append((x.float() @ p[a + "indexer.wk.weight"].float().T).to(x.dtype))

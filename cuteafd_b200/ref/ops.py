@@ -169,3 +169,15 @@ def greedy_verify(target_logits: torch.Tensor, draft: torch.Tensor) -> tuple[int
             break
         n += 1
     return n, pred[n]
+
+
+def fp8_latent_roundtrip(latent: torch.Tensor, group: int = 128) -> torch.Tensor:
+    """Latents as the FP8 cache record stores them: per 128 values one fp32 scale amax / 448, values rounded to E4M3,
+    decoded back to the input dtype (reference record: native/shared/cuda/mla_indexing.cu, fp8_ds_mla pack)."""
+    T, D = latent.shape
+    if D % group:
+        group = D
+    v = latent.float().view(T, D // group, group)
+    scale = v.abs().amax(dim=-1, keepdim=True).clamp_min(1e-12) * (1.0 / 448.0)
+    q = (v * (1.0 / scale)).to(torch.float8_e4m3fn).float()
+    return (q * scale).view(T, D).to(latent.dtype)

@@ -326,11 +326,14 @@ def build_state(args) -> ServerState:
         rows = args.concurrency * 8
         if snapshot:
             from ..loader.load import load_engine
-            cfg, eng = load_engine(snapshot, dev, num_pages, max(2048, rows), rows)
+            cfg, eng = load_engine(snapshot, dev, num_pages, max(2048, rows), rows, getattr(args, "kv_format", "auto"))
         else:
             cfg = PRESETS[args.preset or "qwen3-30b-a3b"]()
             if args.layers:
                 cfg = cfg.replace(num_layers=args.layers)
+            kvf = getattr(args, "kv_format", "auto")
+            if cfg.is_mla and (kvf == "fp8_ds_mla" or (kvf == "auto" and cfg.indexer_heads)):
+                cfg = cfg.replace(kv_format="fp8_ds_mla")
             if cfg.is_mla:
                 from ..models.mla_moe import LatentCache as Cache, MlaMoeEngine as Engine, MlaMoeWeights as Weights
             else:

@@ -130,3 +130,88 @@ def test_sparse_mla(K, heads, lens, qlens, topk, splits):
         ref = p @ c[:, :512]
         err = (got[t] - ref).abs().max().item()
         assert err < 0.03 * max(1.0, ref.abs().max().item()), (t, err)
+
+
+def _fp8_record_ref(latent, rope):
+    """[n, 512] bf16 latents + [n, 64] bf16 rope -> (record bytes [n, 656], dequantised latents as bf16)."""
+    n = latent.shape[0]
+    v = latent.float().view(n, 4, 128)
+    scale = v.abs().amax(-1, keepdim=True).clamp_min(1e-12) * (1.0 / 448.0)
+    q = (v * (1.0 / scale)).to(torch.float8_e4m3fn)
+    rec = torch.cat([q.view(n, 512).view(torch.uint8), scale.view(n, 4).contiguous().view(torch.uint8).view(n, 16),
+                     rope.contiguous().view(torch.uint8).view(n, 128)], dim=1)
+    return rec, (q.float() * scale).view(n, 512).to(torch.bfloat16)
+
+
+def test_fp8_latent_record_write(K):
+    """mla_prep_a with a uint8 cache writes E4M3 latents, fp32 scales and bf16 rope in the 656-byte layout."""
+    g = torch.Generator().manual_seed(3)
+    T, ql = 37, 256
+    a = (torch.randn(T, ql + 576, generator=g) * 0.7).to(torch.bfloat16).to(DEV)
+    qw = (1 + 0.1 * torch.randn(ql, generator=g)).to(torch.bfloat16).to(DEV)
+    kw = (1 + 0.1 * torch.randn(512, generator=g)).to(torch.bfloat16).to(DEV)
+    inv = (1.0 / (10000.0 ** (torch.arange(0, 64, 2, dtype=torch.float32) / 64))).to(DEV)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV) + 5
+    slots = (torch.randperm(128, generator=g)[:T].to(torch.int32) + 64).to(DEV)
+    slots[3] = -1
+    qa = torch.empty(T, ql, dtype=torch.bfloat16, device=DEV)
+    bf = torch.zeros(4, 64, 576, dtype=torch.bfloat16, device=DEV)
+    f8 = torch.zeros(4, 64, K.FP8_RECORD_BYTES, dtype=torch.uint8, device=DEV)
+    K.mla_prep_a(a, ql, qw, kw, inv, pos, slots, qa, bf, 1e-6, True)
+    K.mla_prep_a(a, ql, qw, kw, inv, pos, slots, qa, f8, 1e-6, True)
+    torch.cuda.synchronize()
+    flat_bf, flat_f8 = bf.view(-1, 576).cpu(), f8.view(-1, K.FP8_RECORD_BYTES).cpu()
+    for t in range(T):
+        sl = int(slots[t])
+        if sl < 0:
+            continue
+        want, _ = _fp8_record_ref(flat_bf[sl:sl + 1, :512], flat_bf[sl:sl + 1, 512:])
+        assert torch.equal(flat_f8[sl], want[0]), t
+    assert int(flat_f8[:64].sum()) == 0                   # page 0 untouched
+
+
+@pytest.mark.parametrize("heads,lens,qlens,topk,splits", [(128, [300], [1], 64, 1), (64, [900, 70], [1, 1], 128, 2),
+                                                         (16, [1500], [3], 512, 4)])
+def test_sparse_mla_over_fp8_records(K, heads, lens, qlens, topk, splits):
+    cache, table, dense = _paged(lens, 576, seed=heads + 2)
+    # the same pages as FP8 records
+    flat = cache.view(-1, 576).cpu()
+    rec, deq = _fp8_record_ref(flat[:, :512], flat[:, 512:])
+    cache8 = rec.view(cache.shape[0], 64, K.FP8_RECORD_BYTES).to(DEV)
+    deq_cache = torch.cat([deq, flat[:, 512:]], dim=1).view_as(cache).to(DEV)
+    g = torch.Generator().manual_seed(12)
+    T = sum(qlens)
+    q = (torch.randn(T, heads, 576, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    scale = 1.0 / math.sqrt(192)
+    idx = torch.full((T, topk), -1, dtype=torch.int32)
+    o = 0
+    for s, n in enumerate(qlens):
+        for i in range(n):
+            lim = lens[s] - n + i + 1
+            m = min(lim, topk)
+            idx[o + i, :m] = torch.randperm(lim, generator=g)[:m].sort().values.to(torch.int32)
+        o += n
+    idx = idx.to(DEV)
+    i32 = dict(dtype=torch.int32, device=DEV)
+    bs, bt = K.mla_blocks(qlens, 128)
+    bs, bt = torch.tensor(bs, **i32), torch.tensor(bt, **i32)
+    q_start = torch.tensor([0] + torch.tensor(qlens).cumsum(0).tolist(), **i32)
+    sl = torch.tensor(lens, **i32)
+    scratch = torch.empty(K.mla_scratch_floats(len(bs), splits), dtype=torch.float32, device=DEV) if splits > 1 else None
+    want = torch.zeros(T, heads, 512, dtype=torch.bfloat16, device=DEV)
+    K.mla_attention(q, deq_cache, table, sl, q_start, bs, bt, want, scale, splits, scratch, sparse_idx=idx)
+    gathered = torch.full((len(bs), topk, 576), 3.0, dtype=torch.bfloat16, device=DEV)
+    got = torch.zeros_like(want)
+    K.mla_fp8_gather(cache8, idx, table, sl, q_start, bs, bt, gathered)
+    K.mla_attention(q, None, table, sl, q_start, bs, bt, got, scale, splits, scratch, sparse_idx=idx, gathered=gathered)
+    torch.cuda.synchronize()
+    assert K.read_status() == 0
+    # the gathered rows are exactly the dequantised records, and attention over them is the same computation
+    pt = table.cpu()
+    for t in range(T):
+        seq = int(bs[t])
+        for e in (0, int((idx[t] >= 0).sum()) - 1):
+            pos = int(idx[t, e])
+            row = deq_cache[int(pt[seq, pos // 64]), pos % 64]
+            assert torch.equal(gathered[t, e], row), (t, e)
+    assert torch.equal(got, want)

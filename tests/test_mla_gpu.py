@@ -92,7 +92,8 @@ def _mla_cfg():
                        num_shared_experts=1, routed_scale=2.5, router_bias=True)
 
 
-@pytest.mark.parametrize("use_graphs,indexer", [(False, False), (True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("use_graphs,indexer", [(False, False), (True, False), (False, True), (True, True),
+                                                (False, "fp8"), (True, "fp8")])
 def test_mla_engine_matches_oracle(K, use_graphs, indexer):
     from cuteafd_b200.models.mla_moe import LatentCache, MlaMoeEngine, MlaMoeWeights
     from cuteafd_b200.ref.model import KvState, RefDecoder, init_weights
@@ -101,6 +102,8 @@ def test_mla_engine_matches_oracle(K, use_graphs, indexer):
     cfg = _mla_cfg()
     if indexer:                                   # sparse attention: 48 of up to ~200 cached positions per token
         cfg = cfg.replace(family="deepseek_v32", indexer_heads=32, indexer_dim=128, indexer_topk=48)
+    if indexer == "fp8":                          # 656-byte FP8 latent records, expanded per step for the sparse kernel
+        cfg = cfg.replace(kv_format="fp8_ds_mla", indexer_topk=64)
     dev = _dev()
     params = {k: v.to(torch.bfloat16).float() for k, v in init_weights(cfg, seed=0).items()}
     eng = MlaMoeEngine(cfg, MlaMoeWeights.from_params(cfg, params, dev), LatentCache(cfg, 64, dev), max_tokens=256, max_seqs=8)
