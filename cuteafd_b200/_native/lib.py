@@ -55,7 +55,7 @@ class TpReduceArgs(C.Structure):
         ("partials", C.c_void_p), ("residual", C.c_void_p), ("norm_w", C.c_void_p), ("x_out", C.c_void_p * 8),
         ("rs_flags", C.c_void_p), ("ag_flags", C.c_void_p * 8), ("epoch", C.c_void_p), ("done_counter", C.c_void_p),
         ("status", C.c_void_p), ("ranks", C.c_int), ("my_rank", C.c_int), ("rows_per_rank", C.c_int),
-        ("rows_valid", C.c_int), ("N", C.c_int), ("eps", C.c_float),
+        ("rows_valid", C.c_int), ("N", C.c_int), ("eps", C.c_float), ("n_sum", C.c_int), ("n_wait", C.c_int),
     ]
 
 
@@ -93,6 +93,7 @@ def cuda_lib():
         _sig(lib, "cafd_moe_meta_ints", [I, I])
         _sig(lib, "cafd_wait_flag", [P, P, P, P])
         _sig(lib, "cafd_tp_reduce_norm_gather", [C.POINTER(TpReduceArgs), P])
+        _sig(lib, "cafd_tp_signal", [P, I, P, P])
         _sig(lib, "cafd_moe_plan", [P, I, I, I, I, C.POINTER(MoeLayout), P, P, P, P])
         _sig(lib, "cafd_moe_plan_dispatch", [P, I, I, I, I, C.POINTER(MoeLayout), P, P, P, P, I, P, P])
         _sig(lib, "cafd_norm_route", [P, P, F, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])

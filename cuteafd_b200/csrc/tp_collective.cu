@@ -32,6 +32,10 @@ struct TpReduceDev {
   uint32_t* status;
   int ranks, my_rank, rows_per_rank, rows_valid, N;
   float eps;
+  // n_sum partial slots are added (slot stride rows_per_rank * N), n_wait producer flags are waited for.  The
+  // collective round uses ranks / ranks; a rank-local addend (the FFN output of the owned rows) uses 1 / 0, and
+  // 0 / 0 only normalises and gathers.
+  int n_sum, n_wait;
 };
 
 __global__ void __launch_bounds__(256) tp_reduce_norm_gather_kernel(const TpReduceDev p) {
@@ -42,7 +46,7 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_gather_kernel(const TpRedu
   if (threadIdx.x == 0) {
     bool ok = true;
     const uint32_t ep = *p.epoch;
-    for (int r = 0; r < p.ranks && ok; ++r) ok = wait_flag_ge(p.rs_flags + r, ep, p.status);
+    for (int r = 0; r < p.n_wait && ok; ++r) ok = wait_flag_ge(p.rs_flags + r, ep, p.status);
     s_ok = ok ? 1 : 0;
   }
   __syncthreads();
@@ -59,7 +63,7 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_gather_kernel(const TpRedu
 #pragma unroll
         for (int e = 0; e < 4; ++e) { acc[2 * e] = bf16_lo(q[e]); acc[2 * e + 1] = bf16_hi(q[e]); }
       }
-      for (int r = 0; r < p.ranks; ++r) {
+      for (int r = 0; r < p.n_sum; ++r) {
         const uint4 v = *reinterpret_cast<const uint4*>(p.partials + (static_cast<size_t>(r) * p.rows_per_rank + row) * p.N + c * 8);
         const uint32_t q[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -109,6 +113,23 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_gather_kernel(const TpRedu
   }
 }
 
+// Tells every rank that this rank has finished reading what the previous step gathered into its buffers, so
+// that the peers' next step may overwrite them (stream order puts it after those reads).
+struct TpSignalDev {
+  uint32_t* flags[8];
+  int n;
+};
+
+__global__ void tp_signal_kernel(const TpSignalDev p, const uint32_t* __restrict__ epoch) {
+  pdl_wait();
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const uint32_t ep = *epoch;
+    for (int r = 0; r < p.n; ++r) st_release_sys(p.flags[r], ep);
+  }
+}
+
 }  // namespace cafd
 
 using namespace cafd;
@@ -127,10 +148,12 @@ typedef struct {
   uint32_t* status;
   int ranks, my_rank, rows_per_rank, rows_valid, N;
   float eps;
+  int n_sum, n_wait;
 } cafd_tp_reduce_args;
 
 int cafd_tp_reduce_norm_gather(const cafd_tp_reduce_args* a, cafd_stream_t s) {
   if (!a || a->ranks < 1 || a->ranks > 8 || a->N % 8 || a->rows_valid > a->rows_per_rank) return -10;
+  if (a->n_sum < 0 || a->n_sum > a->ranks || a->n_wait < 0 || a->n_wait > a->ranks) return -10;
   TpReduceDev p;
   p.partials = static_cast<const __nv_bfloat16*>(a->partials);
   p.residual = static_cast<__nv_bfloat16*>(a->residual);
@@ -145,8 +168,19 @@ int cafd_tp_reduce_norm_gather(const cafd_tp_reduce_args* a, cafd_stream_t s) {
   p.status = a->status;
   p.ranks = a->ranks; p.my_rank = a->my_rank; p.rows_per_rank = a->rows_per_rank; p.rows_valid = a->rows_valid; p.N = a->N;
   p.eps = a->eps;
+  p.n_sum = a->n_sum; p.n_wait = a->n_wait;
   int blocks = a->rows_valid < 1 ? 1 : (a->rows_valid > 1184 ? 1184 : a->rows_valid);
   launch_pdl(tp_reduce_norm_gather_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(s), p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// flags: n device pointers (one word on every rank of the group), each set to *epoch.
+int cafd_tp_signal(void* const* flags, int n, const uint32_t* epoch, cafd_stream_t s) {
+  if (n < 1 || n > 8) return -10;
+  TpSignalDev p;
+  for (int r = 0; r < 8; ++r) p.flags[r] = r < n ? static_cast<uint32_t*>(flags[r]) : nullptr;
+  p.n = n;
+  launch_pdl(tp_signal_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(s), p, epoch);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -35,18 +35,21 @@ class TpContext:
         self.group = group or dist.group.WORLD
         self.ranks, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         self.hidden, self.device = hidden, device
-        self.rows_per_rank = (max_rows + self.ranks - 1) // self.ranks
+        self.rows_per_rank = self.max_rows_per_rank = (max_rows + self.ranks - 1) // self.ranks
         R, n = self.rows_per_rank, self.ranks
         o = 0
         self.off_partials = o; o = _align(o + n * R * hidden * 2)       # receive buffer [ranks][R][hidden]
         self.off_x = o; o = _align(o + n * R * hidden * 2)              # gathered activations [ranks*R][hidden]
         self.off_rs_flags = o; o = _align(o + 64)
         self.off_ag_flags = o; o = _align(o + 64)
+        self.off_ready_flags = o; o = _align(o + 64)
         self.heap = SymmetricHeap(o, device, self.group)
         self.partials = self.heap.view(self.off_partials, n * R * hidden * 2, torch.bfloat16).view(n, R, hidden)
         self.x_full = self.heap.view(self.off_x, n * R * hidden * 2, torch.bfloat16).view(n * R, hidden)
         self.rs_flags = self.heap.view(self.off_rs_flags, 64, torch.int32)
         self.ag_flags = self.heap.view(self.off_ag_flags, 64, torch.int32)
+        self.ready_flags = self.heap.view(self.off_ready_flags, 64, torch.int32)
+        self._ready_ptrs = (C.c_void_p * 8)(*[self.heap.ptrs[r] + self.off_ready_flags + 4 * self.rank for r in range(n)])
         self.residual = torch.zeros(R, hidden, dtype=torch.bfloat16, device=device)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
         self.done = torch.zeros(4, dtype=torch.int32, device=device)
@@ -82,9 +85,21 @@ class TpContext:
         _n.check(_n.cuda_lib().cafd_gemm(C.byref(a), K._stream()), "cafd_gemm(reduce-scatter)")
 
     # ---- reduce + residual + norm + all-gather -----------------------------------------------------------
-    def reduce_norm_gather(self, total_rows: int, norm_w: torch.Tensor, eps: float) -> None:
+    def reduce_norm_gather(self, total_rows: int, norm_w: torch.Tensor, eps: float, local: torch.Tensor | None = None,
+                           gather_only: bool = False) -> None:
+        """Owned rows: residual += sum of every rank's partial (rank order, fp32, one rounding), x = norm(residual),
+        x stored into every rank's ``x_full`` and the gather flags raised.  ``local`` [rows owned, hidden] replaces
+        the partials by a rank-local addend (the FFN output of the owned rows: nothing to wait for);
+        ``gather_only`` adds nothing (first norm of a step)."""
         a = _n.TpReduceArgs()
-        a.partials, a.residual, a.norm_w = self.partials.data_ptr(), self.residual.data_ptr(), norm_w.data_ptr()
+        a.residual, a.norm_w = self.residual.data_ptr(), norm_w.data_ptr()
+        if gather_only:
+            a.partials, a.n_sum, a.n_wait = self.partials.data_ptr(), 0, 0
+        elif local is not None:
+            assert local.is_contiguous() and local.shape[1] == self.hidden and local.shape[0] >= self.rows_owned(total_rows)
+            a.partials, a.n_sum, a.n_wait = local.data_ptr(), 1, 0
+        else:
+            a.partials, a.n_sum, a.n_wait = self.partials.data_ptr(), self.ranks, self.ranks
         for r in range(self.ranks):
             a.x_out[r] = self.heap.ptrs[r] + self.off_x
             a.ag_flags[r] = self.heap.ptrs[r] + self.off_ag_flags + 4 * self.rank
@@ -93,6 +108,28 @@ class TpContext:
         a.ranks, a.my_rank, a.rows_per_rank, a.rows_valid, a.N, a.eps = (self.ranks, self.rank, self.rows_per_rank,
                                                                       self.rows_owned(total_rows), self.hidden, eps)
         _n.check(_n.cuda_lib().cafd_tp_reduce_norm_gather(C.byref(a), K._stream()), "tp_reduce_norm_gather")
+
+    def set_rows(self, total_rows: int) -> None:
+        """Row ownership of the coming step: rank r owns rows [r * R, (r + 1) * R) with R = ceil(total_rows / ranks), so
+        small steps are shared evenly too.  Every rank must call it with the same value."""
+        r = (total_rows + self.ranks - 1) // self.ranks
+        assert 0 < r <= self.max_rows_per_rank
+        self.rows_per_rank = r
+
+    def release_buffers(self) -> None:
+        """End of a step: this rank's reads of the gathered activations are done (stream order); tell every rank."""
+        _n.check(_n.cuda_lib().cafd_tp_signal(self._ready_ptrs, self.ranks, self.epoch.data_ptr(), K._stream()), "tp_signal")
+
+    def wait_buffers_free(self) -> None:
+        """Start of a step, before the epoch moves: wait until every rank has released the previous step's buffers."""
+        for r in range(self.ranks):
+            K.wait_flag(self.ready_flags.data_ptr() + 4 * r, self.epoch)
+
+    def wait_gathered(self) -> None:
+        """Stream-ordered wait until every rank's rows of ``x_full`` have arrived (for readers that are not the
+        flag-waiting GEMM)."""
+        for r in range(self.ranks):
+            K.wait_flag(self.ag_flags.data_ptr() + 4 * r, self.epoch)
 
     # ---- all-gather -> GEMM -----------------------------------------------------------------------------------
     def column_parallel_linear(self, total_rows: int, w_shard: torch.Tensor, out: torch.Tensor, w_up: torch.Tensor | None = None) -> torch.Tensor:
