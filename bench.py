@@ -55,6 +55,10 @@ def main() -> None:
                     help="qwen3 = the headline Qwen3-30B-A3B bf16 card; dsv3 = DeepSeek-V3 shape, MLA attention on GPU 0, "
                          "E4M3 block-scaled experts on the other GPUs (needs 8 GPUs)")
     ap.add_argument("--prefill-chunk", type=int, default=0)
+    ap.add_argument("--parallelism", default="auto", choices=["auto", "afd", "tp"],
+                    help="layout on more than one GPU: afd = attention on GPU 0, routed experts on the others; tp = attention "
+                         "heads split over all GPUs with the residual rows sharded and every rank running the FFN of its "
+                         "own rows (experts replicated); auto = afd")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -94,7 +98,25 @@ def main() -> None:
     pages_per_seq = (args.prompt_len + 2 * (args.steps + warmup) + 128) // 64 + 2
     num_pages = max(levels) * pages_per_seq + 8 * max(levels) + 64
     handle = None
-    if world > 1:
+    mode = "afd" if args.parallelism == "auto" else args.parallelism
+    if world > 1 and mode == "tp":
+        assert args.config == "qwen3", "the tensor-parallel layout serves the GQA family"
+        dist.init_process_group("nccl", device_id=dev)
+        from cuteafd_b200.models.gqa_moe import GqaMoeWeights
+        from cuteafd_b200.models.tp_gqa import TpGqaMoeEngine
+        from cuteafd_b200.runtime.generate import Generator
+        from cuteafd_b200.runtime.paged import PagePool
+        W = GqaMoeWeights.random_init(cfg, dev, seed=0)
+        eng = TpGqaMoeEngine(cfg, W, num_pages, max_tokens=args.prompt_len, max_seqs=max(levels))
+        gen = Generator(eng, PagePool(num_pages), pages_per_seq, max(levels), prefill_chunk=args.prompt_len,
+                        use_graphs=not args.no_graphs)
+        torch.cuda.synchronize()
+        dist.barrier()
+        sync = dist.barrier
+        parallelism = (f"tp{world}: attention heads split over {world} GPUs, residual rows sharded, FFN of the owned rows on "
+                       f"every rank (experts replicated), fused reduce-scatter / all-gather kernels over NVLink")
+        log(f"tp ready: {torch.cuda.memory_allocated()/2**30:.1f} GiB per rank")
+    elif world > 1:
         dist.init_process_group("nccl", device_id=dev)
         from cuteafd_b200.parallel.afd import build_afd
         handle = build_afd(cfg, dev, rank, world, max_tokens=args.prompt_len, max_seqs=max(levels),
@@ -151,7 +173,8 @@ def main() -> None:
             "extra": extra,
         }
     if world > 1:
-        handle.shutdown()
+        if handle is not None:
+            handle.shutdown()
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0 and out is not None:

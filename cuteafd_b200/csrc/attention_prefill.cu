@@ -215,23 +215,34 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       if (!mbar_wait(&s_full[st], ph, p.status, kTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
       const uint32_t tSj = tS + st * 128 + lane_off;
-      const bool need_mask = (j * kBKV + kBKV - 1) > pos0;
+      const bool need_mask = (j * kBKV + kBKV - 1) > pos0;      // uniform over the CTA
       const int col_limit = rowpos - j * kBKV;      // columns <= col_limit are visible
-      // pass 1: row maximum
+      // The whole score row goes to registers with one wait; the TMEM buffer is handed back at once, so the MMA
+      // warp can start the scores of tile j + 2 while this tile's exponentials run.
+      uint32_t r[128];
+      tmem_ld_32x32(tSj, *reinterpret_cast<uint32_t(*)[32]>(r));
+      tmem_ld_32x32(tSj + 32, *reinterpret_cast<uint32_t(*)[32]>(r + 32));
+      tmem_ld_32x32(tSj + 64, *reinterpret_cast<uint32_t(*)[32]>(r + 64));
+      tmem_ld_32x32(tSj + 96, *reinterpret_cast<uint32_t(*)[32]>(r + 96));
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&s_empty[st]);
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tSj + c * 32, r);
-        tmem_ld_wait();
+      if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(r[i]) * p.scale_log2;
-          if (need_mask && (c * 32 + i) > col_limit) v = -INFINITY;
-          mx = fmaxf(mx, v);
+        for (int i = 0; i < 128; ++i) {
+          if (i > col_limit) r[i] = 0xff800000u;    // -inf
+          mx = fmaxf(mx, __uint_as_float(r[i]));
         }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
       }
-      const float m_new = fmaxf(m_run, mx);
+      mx *= p.scale_log2;                            // scale > 0: the maximum commutes with it
+      // The reference maximum only moves when the row maximum exceeds it by more than 8 (factor 256): P stays
+      // within bf16 / fp32 range and O is rescaled rarely; O and the running sum share the reference, so the
+      // quotient is exact all the same.
+      const float m_new = (mx > m_run + 8.0f) ? mx : m_run;
       const float base = (m_new == -INFINITY) ? 0.f : m_new;
       const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - base);
       // P buffer and O are free once P V of the previous tile has completed
@@ -241,34 +252,28 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32(tO + lane_off + c * 32, r);
+            uint32_t o[32];
+            tmem_ld_32x32(tO + lane_off + c * 32, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
-            tmem_st_32x32(tO + lane_off + c * 32, r);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+            tmem_st_32x32(tO + lane_off + c * 32, o);
           }
         }
       }
-      // pass 2: P = exp2(S - m) as bf16 into swizzled shared memory; running sum
-      float rs = 0.f;
-#pragma unroll 1
+      // P = exp2(S * scale - m) as bf16 into swizzled shared memory; running sum in fp32
+      float rs0 = 0.f, rs1 = 0.f;
+      const float nbase = -base;
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tSj + c * 32, r);
-        tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float v0 = __uint_as_float(r[i]) * p.scale_log2;
-          float v1 = __uint_as_float(r[i + 1]) * p.scale_log2;
-          if (need_mask) {
-            if ((c * 32 + i) > col_limit) v0 = -INFINITY;
-            if ((c * 32 + i + 1) > col_limit) v1 = -INFINITY;
-          }
-          const uint32_t w = pack_bf16(fast_exp2(v0 - base), fast_exp2(v1 - base));
-          rs += bf16_lo(w) + bf16_hi(w);
-          pk[i >> 1] = w;
+          const float e0 = fast_exp2(fmaf(__uint_as_float(r[c * 32 + i]), p.scale_log2, nbase));
+          const float e1 = fast_exp2(fmaf(__uint_as_float(r[c * 32 + i + 1]), p.scale_log2, nbase));
+          rs0 += e0;
+          rs1 += e1;
+          pk[i >> 1] = pack_bf16(e0, e1);
         }
         // columns [32c, 32c+32) -> atom (c / 2), 16-byte chunks ((c & 1) * 4 + q), q = 0..3
         uint8_t* prow = sP + (c >> 1) * kHalfBytes + row * 128;
@@ -279,12 +284,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
               make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
         }
       }
+      const float rs = rs0 + rs1;
       l_run = l_run * corr + rs;
       m_run = m_new;
       tmem_st_wait();
       fence_async_smem();
       tc_fence_before();
-      mbar_arrive(&s_empty[st]);
       mbar_arrive(&p_ready);
     }
     // ---- epilogue: O / l ---------------------------------------------------------------------------

@@ -70,6 +70,12 @@ class TpGqaMoeEngine(GqaMoeEngine):
         self.own_out = torch.zeros(self.tp.max_rows_per_rank, cfg.hidden, dtype=torch.bfloat16, device=dev)
         self.collectives = 0
 
+    def collect_max(self, ms: float) -> float:
+        """Largest device time over the ranks of the group (benchmarks report the slowest rank)."""
+        t = torch.tensor([ms], dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        return float(t.item())
+
     # owned rows of the current step
     def _own(self, T: int) -> tuple[int, int]:
         lo = self.rank * self.tp.rows_per_rank
