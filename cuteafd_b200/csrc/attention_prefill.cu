@@ -7,9 +7,12 @@
 //   warp 0     TMA producer: Q tile once, then K and V tiles (two stages each)
 //   warp 1     MMA issuer: QK^T for tile j+1 is issued before P V of tile j, so the tensor pipe
 //              works on the next scores while the softmax warps are busy
-//   warps 2-5  online softmax: thread = query row (its TMEM lane); S is read with tcgen05.ld,
-//              P is written as bf16 into 128B-swizzled shared memory (the A operand of P V),
-//              O is rescaled in TMEM only when the running maximum moved
+//   warps 2-9  online softmax: thread = (query row, half of the tile's kv columns); warps w and w + 4 share a
+//              TMEM lane quarter, so each scheduler has two warps to overlap.  A half row of S is read into
+//              registers with one tcgen05.ld wait (the S buffer is released right away), the halves exchange
+//              their maxima through shared memory, P is written as bf16 into 128B-swizzled shared memory (the
+//              A operand of P V; two buffers in the GQA variant), O is rescaled in TMEM only when the reference
+//              maximum moved (it moves when a row maximum exceeds it by more than 8 in log2 units)
 // TMEM: S double-buffered (2 x 128 columns) + O (128 columns).
 //
 // The kRope variant serves MLA prefill in its expanded (non-absorbed) form: per-head K_nope / V tiles come from a
@@ -31,8 +34,8 @@ constexpr int kBKV = 128;         // kv tokens per tile (two 64-token pages)
 constexpr int kPageTok = 64;
 constexpr int kHalfBytes = 128 * 128;   // 128 rows x 64 bf16 (one swizzle atom wide) = 16 KiB
 constexpr int kTileB = 2 * kHalfBytes;  // 32 KiB: a [128 x 128] bf16 tile as two 64-wide halves
-constexpr int kPrefillThreads = 192;
-constexpr int kPrefillSmem = 6 * kTileB + 1024;   // Q, K x2, V x2, P
+constexpr int kPrefillThreads = 320;   // TMA warp, MMA warp, 8 softmax warps
+constexpr int kPrefillSmem = 7 * kTileB + 1024;   // Q, K x2, V x2, P x2
 constexpr int kPrefillSmemRope = 5 * kTileB + 3 * kHalfBytes + 1024;   // Q, Qr, (K, Kr) x2, V x1, P
 
 struct PrefillDev {
@@ -59,14 +62,20 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int kVS = kRope ? 1 : 2;    // V stages (the rope tiles take the room of the second one)
+  // P buffers.  With two, the exponentials of tile j are stored while P V of tile j - 1 still runs; only a
+  // rescale of O (rare with the lazy reference maximum) has to wait for that MMA.
+  constexpr int kPB = kRope ? 1 : 2;
   uint8_t* sQ = smem;
   uint8_t* sK = smem + kTileB;          // 2 stages
   uint8_t* sV = smem + 3 * kTileB;      // kVS stages
   uint8_t* sP = sV + kVS * kTileB;
-  uint8_t* sQr = sP + kTileB;           // kRope: 128 x 64 rope queries, then two stages of 128 x 64 rope keys
+  uint8_t* sQr = sP + kPB * kTileB;     // kRope: 128 x 64 rope queries, then two stages of 128 x 64 rope keys
   uint8_t* sKr = sQr + kHalfBytes;
 
-  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_ready, pv_done;
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_ready[2], pv_done[2], mx_bar[2];
+  // Exchange between the two column halves of a row: maxima as bf16 [tile parity][half][row] (rounded up, so the
+  // common reference is never below a score), and at the very end the row sums as fp32 [half][row] in the same bytes.
+  __shared__ uint32_t s_xch[256];
   __shared__ uint32_t tmem_slot;
 
   pdl_wait();      // the page table, lengths and Q come from kernels earlier in the stream
@@ -92,10 +101,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 256);
     }
-    mbar_init(&p_ready, 128);
-    mbar_init(&pv_done, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&p_ready[i], 256); mbar_init(&pv_done[i], 1); mbar_init(&mx_bar[i], 256); }
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -120,15 +128,19 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       if (kRope) tma_load_2d(sQr, &tm_qr, &q_full, head * p.qr_head_stride + p.qr_col0, q0 + row0);
       const int* pt = p.page_table + static_cast<size_t>(seq) * p.max_pages;
       const int tmp_page0 = kRope ? p.kv_tmp_start[seq] / kPageTok : 0;
-      bool ok = true;
-      for (int j = 0; ok && j < n_tiles; ++j) {
+      auto pages_of = [&](int j, int& pa, int& pb, int& ka, int& kb) {
+        pa = 2 * j < seq_pages ? pt[2 * j] : 0;                      // page 0 is the all-zero page
+        pb = 2 * j + 1 < seq_pages ? pt[2 * j + 1] : 0;
+        // expanded K / V (kRope) sit in order in their buffer: "page" = row block of 64; past the end TMA fills zeros
+        ka = kRope ? tmp_page0 + 2 * j : pa;
+        kb = kRope ? tmp_page0 + 2 * j + 1 : pb;
+      };
+      auto load_k = [&](int j) -> bool {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        const int pa = 2 * j < seq_pages ? pt[2 * j] : 0;          // page 0 is the all-zero page
-        const int pb = 2 * j + 1 < seq_pages ? pt[2 * j + 1] : 0;
-        // expanded K / V (kRope) sit in order in their buffer: "page" = row block of 64; past the end TMA fills zeros
-        const int ka = kRope ? tmp_page0 + 2 * j : pa, kb = kRope ? tmp_page0 + 2 * j + 1 : pb;
-        if (!mbar_wait(&k_empty[st], ph ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
+        int pa, pb, ka, kb;
+        pages_of(j, pa, pb, ka, kb);
+        if (!mbar_wait(&k_empty[st], ph ^ 1, p.status, kTimeoutEmptyBarrier)) return false;
         uint8_t* kd = sK + st * kTileB;
         mbar_expect_tx(&k_full[st], kTileB + (kRope ? kHalfBytes : 0));
         tma_load_4d(kd, &tm_k, &k_full[st], 0, kvh, 0, ka);
@@ -140,15 +152,31 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           tma_load_3d(rd, &tm_kr, &k_full[st], 512, 0, pa);
           tma_load_3d(rd + 64 * 128, &tm_kr, &k_full[st], 512, 0, pb);
         }
-        const int vs = kVS == 2 ? st : 0;
-        const uint32_t vph = kVS == 2 ? ph : (j & 1);
-        if (!mbar_wait(&v_empty[vs], vph ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
+        return true;
+      };
+      auto load_v = [&](int j) -> bool {
+        const int vs = kVS == 2 ? (j & 1) : 0;
+        const uint32_t vph = kVS == 2 ? ((j >> 1) & 1) : (j & 1);
+        int pa, pb, ka, kb;
+        pages_of(j, pa, pb, ka, kb);
+        if (!mbar_wait(&v_empty[vs], vph ^ 1, p.status, kTimeoutEmptyBarrier)) return false;
         uint8_t* vd = sV + vs * kTileB;
         mbar_expect_tx(&v_full[vs], kTileB);
         tma_load_4d(vd, &tm_v, &v_full[vs], 0, kvh, 0, ka);
         tma_load_4d(vd + 64 * 128, &tm_v, &v_full[vs], 0, kvh, 0, kb);
         tma_load_4d(vd + kHalfBytes, &tm_v, &v_full[vs], 64, kvh, 0, ka);
         tma_load_4d(vd + kHalfBytes + 64 * 128, &tm_v, &v_full[vs], 64, kvh, 0, kb);
+        return true;
+      };
+      // K runs ahead of V by as many tiles as the scores run ahead of P V (see the MMA warp): a K stage is free as
+      // soon as its scores are done, long before the V stage of the same tile is.
+      constexpr int kLead = kVS == 2 ? 2 : 0;
+      bool ok = true;
+      for (int j = 0; ok && j < kLead && j < n_tiles; ++j) ok = load_k(j);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (kLead == 0) ok = load_k(j);
+        if (ok) ok = load_v(j);
+        if (ok && kLead > 0 && j + kLead < n_tiles) ok = load_k(j + kLead);
       }
     }
   } else if (warp == 1) {
@@ -180,12 +208,19 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         umma_commit(&s_full[st]);
         return true;
       };
+      // Scores run two tiles ahead of P V: the softmax warps release a score buffer as soon as they have read it
+      // into registers, so S(j + 2) is computed while they work on tile j and S(j + 1) is already waiting.
+      // (The kRope variant has one V stage: its producer cannot load K(j + 2) before P V(j) has freed V, so there
+      // the scores stay one tile ahead.)
+      constexpr int kAhead = kVS == 2 ? 2 : 1;
       if (ok) ok = issue_qk(0);
+      if (ok && kAhead == 2 && n_tiles > 1) ok = issue_qk(1);
       for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) { if (!issue_qk(j + 1)) { ok = false; break; } }
+        if (j + kAhead < n_tiles) { if (!issue_qk(j + kAhead)) { ok = false; break; } }
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&p_ready, j & 1, p.status, kTimeoutSoftmax)) { ok = false; break; }
+        const int pb = j % kPB;
+        if (!mbar_wait(&p_ready[pb], (j / kPB) & 1, p.status, kTimeoutSoftmax)) { ok = false; break; }
         const int vs = kVS == 2 ? st : 0;
         const uint32_t vph = kVS == 2 ? ph : (j & 1);
         if (!mbar_wait(&v_full[vs], vph, p.status, kTimeoutFullBarrier)) { ok = false; break; }
@@ -195,77 +230,89 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         for (int k8 = 0; k8 < 8; ++k8) {
           // A = P: atom (k8 / 4) of 64 kv columns, 32 bytes per K step inside it
           // B = V: 16 kv rows per step (2 KiB), two 64-wide d halves 16 KiB apart
-          umma_f16(tO, smem_desc_k_sw128(aP + (k8 >> 2) * kHalfBytes + (k8 & 3) * 32),
+          umma_f16(tO, smem_desc_k_sw128(aP + pb * kTileB + (k8 >> 2) * kHalfBytes + (k8 & 3) * 32),
                    smem_desc_mn_sw128(aV + k8 * 2048, kHalfBytes), idesc_pv, (j | k8) ? 1u : 0u);
         }
         umma_commit(&v_empty[vs]);
-        umma_commit(&pv_done);
+        umma_commit(&pv_done[pb]);
       }
     }
   } else {
+    // Eight softmax warps: warps w and w + 4 share a TMEM lane quarter (32 query rows) and split the tile's 128
+    // kv columns in halves, so every scheduler has two warps to cover each other's instruction latencies.
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;                // 0: columns 0..63, 1: columns 64..127
     const int row = quad * 32 + lane;               // row within the tile = TMEM lane
     const int rowpos = pos0 + row;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;           // l_run: this half's share of the row sum
     bool ok = true;
     for (int j = 0; ok && j < n_tiles; ++j) {
       const int st = j & 1;
       const uint32_t ph = (j >> 1) & 1;
       if (!mbar_wait(&s_full[st], ph, p.status, kTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t tSj = tS + st * 128 + lane_off;
+      const uint32_t tSj = tS + st * 128 + lane_off + half * 64;
       const bool need_mask = (j * kBKV + kBKV - 1) > pos0;      // uniform over the CTA
-      const int col_limit = rowpos - j * kBKV;      // columns <= col_limit are visible
-      // The whole score row goes to registers with one wait; the TMEM buffer is handed back at once, so the MMA
-      // warp can start the scores of tile j + 2 while this tile's exponentials run.
-      uint32_t r[128];
+      const int col_limit = rowpos - j * kBKV - half * 64;      // local columns <= col_limit are visible
+      // This half of the score row goes to registers with one wait; the TMEM buffer is handed back at once, so
+      // the MMA warp can start the scores of tile j + 2 while this tile's exponentials run.
+      uint32_t r[64];
       tmem_ld_32x32(tSj, *reinterpret_cast<uint32_t(*)[32]>(r));
       tmem_ld_32x32(tSj + 32, *reinterpret_cast<uint32_t(*)[32]>(r + 32));
-      tmem_ld_32x32(tSj + 64, *reinterpret_cast<uint32_t(*)[32]>(r + 64));
-      tmem_ld_32x32(tSj + 96, *reinterpret_cast<uint32_t(*)[32]>(r + 96));
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&s_empty[st]);
-      float mx = -INFINITY;
       if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 128; ++i) {
+        for (int i = 0; i < 64; ++i)
           if (i > col_limit) r[i] = 0xff800000u;    // -inf
-          mx = fmaxf(mx, __uint_as_float(r[i]));
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
       }
-      mx *= p.scale_log2;                            // scale > 0: the maximum commutes with it
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains: the maximum is latency-bound
+#pragma unroll
+      for (int i = 0; i < 64; i += 4) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mx4[k] = fmaxf(mx4[k], __uint_as_float(r[i + k]));
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // the row maximum over both halves: both use max(ceil_bf16(own), ceil_bf16(other)), the same value
+      __nv_bfloat16* xmx = reinterpret_cast<__nv_bfloat16*>(s_xch) + st * 256;
+      const __nv_bfloat16 own = __float2bfloat16_ru(mx);
+      xmx[half * 128 + row] = own;
+      mbar_arrive(&mx_bar[st]);
+      if (!mbar_wait(&mx_bar[st], ph, p.status, kTimeoutSoftmax)) { ok = false; break; }
+      mx = fmaxf(__bfloat162float(own), __bfloat162float(xmx[(half ^ 1) * 128 + row])) * p.scale_log2;   // scale > 0
       // The reference maximum only moves when the row maximum exceeds it by more than 8 (factor 256): P stays
       // within bf16 / fp32 range and O is rescaled rarely; O and the running sum share the reference, so the
       // quotient is exact all the same.
       const float m_new = (mx > m_run + 8.0f) ? mx : m_run;
       const float base = (m_new == -INFINITY) ? 0.f : m_new;
       const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - base);
-      // P buffer and O are free once P V of the previous tile has completed
-      if (j > 0) {
-        if (!mbar_wait(&pv_done, (j - 1) & 1, p.status, kTimeoutTmemFull)) { ok = false; break; }
+      // O may be rescaled once P V of the previous tile has completed; P buffer pb is free once the P V that read
+      // it (tile j - kPB) has
+      const int pb = j % kPB;
+      const bool rescale = j > 0 && __any_sync(0xffffffffu, corr != 1.0f);
+      if (j >= kPB && !mbar_wait(&pv_done[pb], (j / kPB - 1) & 1, p.status, kTimeoutTmemFull)) { ok = false; break; }
+      if (rescale) {
+        if (!mbar_wait(&pv_done[(j - 1) % kPB], ((j - 1) / kPB) & 1, p.status, kTimeoutTmemFull)) { ok = false; break; }
         tc_fence_after();
-        if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[32];
-            tmem_ld_32x32(tO + lane_off + c * 32, o);
-            tmem_ld_wait();
+        for (int c = 0; c < 2; ++c) {             // this half's 64 columns of O
+          uint32_t o[32];
+          tmem_ld_32x32(tO + lane_off + half * 64 + c * 32, o);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-            tmem_st_32x32(tO + lane_off + c * 32, o);
-          }
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+          tmem_st_32x32(tO + lane_off + half * 64 + c * 32, o);
         }
       }
       // P = exp2(S * scale - m) as bf16 into swizzled shared memory; running sum in fp32
       float rs0 = 0.f, rs1 = 0.f;
       const float nbase = -base;
+      // local columns [0, 64) of this half = swizzle atom `half`, 16-byte chunks 0..7
+      uint8_t* prow = sP + pb * kTileB + half * kHalfBytes + row * 128;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -275,33 +322,38 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           rs1 += e1;
           pk[i >> 1] = pack_bf16(e0, e1);
         }
-        // columns [32c, 32c+32) -> atom (c / 2), 16-byte chunks ((c & 1) * 4 + q), q = 0..3
-        uint8_t* prow = sP + (c >> 1) * kHalfBytes + row * 128;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const int chunk = (c & 1) * 4 + q;
+          const int chunk = c * 4 + q;
           *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) =
               make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
         }
       }
-      const float rs = rs0 + rs1;
-      l_run = l_run * corr + rs;
+      l_run = l_run * corr + (rs0 + rs1);
       m_run = m_new;
       tmem_st_wait();
       fence_async_smem();
       tc_fence_before();
-      mbar_arrive(&p_ready);
+      mbar_arrive(&p_ready[pb]);
     }
     // ---- epilogue: O / l ---------------------------------------------------------------------------
-    if (ok && mbar_wait(&pv_done, (n_tiles - 1) & 1, p.status, kTimeoutTmemFull)) {
+    if (ok && mbar_wait(&pv_done[(n_tiles - 1) % kPB], ((n_tiles - 1) / kPB) & 1, p.status, kTimeoutTmemFull)) {
+      // The last P V has run, so every softmax thread is past its last read of the exchange buffer: the two halves
+      // now add their row sums through it.
+      float* xl = reinterpret_cast<float*>(s_xch);
+      const int fb = n_tiles & 1;                    // the barrier that tile n_tiles would have used
+      xl[half * 128 + row] = l_run;
+      mbar_arrive(&mx_bar[fb]);
+      if (mbar_wait(&mx_bar[fb], (n_tiles >> 1) & 1, p.status, kTimeoutSoftmax)) l_run += xl[(half ^ 1) * 128 + row];
+      else l_run = 0.f;
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
       const bool row_ok = (row0 + row) < q_len;
-      __nv_bfloat16* orow = p.out + (static_cast<size_t>(q0 + row0 + row) * p.Hq + head) * kHD;
+      __nv_bfloat16* orow = p.out + (static_cast<size_t>(q0 + row0 + row) * p.Hq + head) * kHD + half * 64;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32(tO + lane_off + c * 32, r);
+        tmem_ld_32x32(tO + lane_off + half * 64 + c * 32, r);
         tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
