@@ -95,6 +95,8 @@ def cuda_lib():
         _sig(lib, "cafd_tp_reduce_norm_gather", [C.POINTER(TpReduceArgs), P])
         _sig(lib, "cafd_tp_signal", [P, I, P, P])
         _sig(lib, "cafd_moe_plan", [P, I, I, I, I, C.POINTER(MoeLayout), P, P, P, P])
+        _sig(lib, "cafd_moe_plan_wide", [P, I, I, I, I, C.POINTER(MoeLayout), P, P, P, P, P])
+        _sig(lib, "cafd_moe_plan_wide_ints", [I, I])
         _sig(lib, "cafd_moe_plan_dispatch", [P, I, I, I, I, C.POINTER(MoeLayout), P, P, P, P, I, P, P])
         _sig(lib, "cafd_norm_route", [P, P, F, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
         _sig(lib, "cafd_moe_combine_norm", [P, P, P, P, P, I, I, I, P, I, P, P, P, F, P, P])

@@ -267,7 +267,8 @@ __global__ void __launch_bounds__(256) norm_route_kernel(const __nv_bfloat16* __
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ idx, int T, int top_k, int E,
                                                         int tile_rows, MoeLayoutDev L, int* __restrict__ dest_row,
                                                         int* __restrict__ expert_count_out, uint32_t* status,
-                                                        const uint4* __restrict__ x, int row_vec, const uint32_t* epoch) {
+                                                        const uint4* __restrict__ x, int row_vec, const uint32_t* epoch,
+                                                        int* __restrict__ wide_hist, int wide_chunks) {
   pdl_wait();
   pdl_trigger();
   __shared__ int counts[kMaxExperts];
@@ -275,13 +276,65 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
   __shared__ int cursor[kMaxExperts];
   __shared__ int rank_of[kMaxExperts];
   const int n = T * top_k;
-  for (int e = threadIdx.x; e < E; e += blockDim.x) { counts[e] = 0; cursor[e] = 0; }
-  __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int e = idx[i];
-    if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+  constexpr int kPlanSlots = 8192;                       // 32 KB of histograms: 32 warps up to 256 experts, 16 beyond
+  __shared__ int wcount_flat[kPlanSlots];
+  const int e_stride = (E + 31) & ~31;
+  const int lane_id = threadIdx.x & 31, warp_id = threadIdx.x >> 5;
+  const int n_warps = min(static_cast<int>(blockDim.x >> 5), kPlanSlots / e_stride);   // warps that walk entries
+  auto wcount = [&](int w, int e) -> int& { return wcount_flat[w * e_stride + e]; };
+  const int chunk = ((n + n_warps - 1) / n_warps + 31) & ~31;
+  const int c_lo = min(n, warp_id * chunk), c_hi = warp_id < n_warps ? min(n, c_lo + chunk) : c_lo;
+  if (wide_hist) {
+    // Wide form (prefill-sized steps): moe_count_kernel left one histogram per 256-entry chunk; turn them into each
+    // chunk's first position per expert.  moe_scatter_kernel places the entries afterwards.
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      int run = 0;
+      for (int g0 = 0; g0 < wide_chunks; g0 += 8) {
+        int c[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) c[k] = g0 + k < wide_chunks ? wide_hist[static_cast<size_t>(g0 + k) * e_stride + e] : 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          if (g0 + k < wide_chunks) wide_hist[static_cast<size_t>(g0 + k) * e_stride + e] = run;
+          run += c[k];
+        }
+      }
+      counts[e] = run;
+      cursor[e] = 0;
+    }
+    __syncthreads();
+  } else {
+  // Per-warp histograms over contiguous chunks of the entries: a warp's atomics only meet its own lanes, and the
+  // prefix over warps below gives every warp its first row per expert, so rows keep the order of the entries
+  // (the plan is the same on every run).
+  if (warp_id < n_warps)
+    for (int e = lane_id; e < E; e += 32) wcount(warp_id, e) = 0;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cursor[e] = 0;
+  __syncwarp();
+  // eight loads in flight per lane: one block walks all entries, so the walk is bound by load latency
+  for (int i0 = c_lo; i0 < c_hi; i0 += 256) {
+    int ev[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int i = i0 + k * 32 + lane_id;
+      ev[k] = i < c_hi ? __ldg(idx + i) : -1;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (ev[k] >= 0 && ev[k] < E) atomicAdd(&wcount(warp_id, ev[k]), 1);
   }
   __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < n_warps; ++w) {
+      const int c = wcount(w, e);
+      wcount(w, e) = run;                  // first position of warp w inside expert e
+      run += c;
+    }
+    counts[e] = run;
+  }
+  __syncthreads();
+  }
   // Exclusive scan of the per-expert tile counts (one thread per expert, Hillis-Steele in shared
   // memory), then every expert writes its own tiles: no serial walk over the experts.
   __shared__ int scan[kMaxExperts];
@@ -329,22 +382,46 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
     if (overflow && status) atomicCAS(status, 0u, static_cast<uint32_t>(kBadArgument));
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int e = idx[i];
-    int row = -1;
-    if (e >= 0 && e < E) {
-      const int pos = atomicAdd(&cursor[e], 1);
-      row = seg_off[e] + pos;
-      const int r = rank_of[e];
-      if (row < L.max_rows) {
-        int* row_dst = L.meta[r] + kMetaHeader + 2 * L.max_tiles;
-        row_dst[row] = i;
-      } else {
-        row = -1;
-      }
+  if (wide_hist) {
+    // publish each expert's first row and rank for the scatter kernel
+    int* seg_out = wide_hist + static_cast<size_t>(wide_chunks) * e_stride;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) { seg_out[e] = seg_off[e]; seg_out[e_stride + e] = rank_of[e]; }
+  } else {
+  for (int i0 = c_lo; i0 < c_hi; i0 += 256) {
+    int ev[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int i = i0 + k * 32 + lane_id;
+      ev[k] = i < c_hi ? __ldg(idx + i) : -1;
     }
-    dest_row[i] = row;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int i = i0 + k * 32 + lane_id;
+      const bool live = i < c_hi;
+      const int e = ev[k];
+      const bool valid = e >= 0 && e < E;
+      // lanes with the same expert take consecutive positions in lane order
+      const uint32_t peers = __match_any_sync(0xffffffffu, valid ? e : -1 - lane_id);
+      int row = -1;
+      if (valid) {
+        const int pos = wcount(warp_id, e) + __popc(peers & ((1u << lane_id) - 1u));
+        row = seg_off[e] + pos;
+        const int r = rank_of[e];
+        if (row < L.max_rows) {
+          int* row_dst = L.meta[r] + kMetaHeader + 2 * L.max_tiles;
+          row_dst[row] = i;
+        } else {
+          row = -1;
+        }
+      }
+      __syncwarp();
+      if (valid && (peers >> lane_id) == 1u) wcount(warp_id, e) += __popc(peers);   // highest lane of the group advances it
+      __syncwarp();
+      if (live) dest_row[i] = row;
+    }
   }
+  }
+  __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     const int r = rank_of[e];
     int* row_dst = L.meta[r] + kMetaHeader + 2 * L.max_tiles;
@@ -383,6 +460,82 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
       const uint32_t ep = *epoch;
       for (int r = 0; r < L.n_ranks; ++r) st_release_sys(L.flag[r], ep);
     }
+  }
+}
+
+// ---- wide plan (prefill-sized steps) ------------------------------------------------------------------
+// The single-block plan walks every entry from one SM; beyond a few thousand entries that walk is the whole cost.
+// Wide form: (1) moe_count_kernel, one warp per 256 entries, writes that chunk's histogram; (2) moe_plan_kernel in
+// wide mode turns the histograms into first positions and does the per-expert tile tables; (3) moe_scatter_kernel,
+// again one warp per chunk, places the entries.  Rows keep the order of the entries, as in the single-block form.
+constexpr int kWideChunk = 256;        // entries per warp
+constexpr int kWideWarps = 8;          // warps per block
+
+__global__ void __launch_bounds__(kWideWarps * 32) moe_count_kernel(const int* __restrict__ idx, int n, int E,
+                                                                    int* __restrict__ hist) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ int h[kWideWarps][kMaxExperts];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = blockIdx.x * kWideWarps + warp;
+  const int e_stride = (E + 31) & ~31;
+  const int lo = g * kWideChunk;
+  if (lo >= n) return;
+  for (int e = lane; e < E; e += 32) h[warp][e] = 0;
+  __syncwarp();
+  int ev[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int i = lo + k * 32 + lane;
+    ev[k] = i < n ? __ldg(idx + i) : -1;
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k)
+    if (ev[k] >= 0 && ev[k] < E) atomicAdd(&h[warp][ev[k]], 1);
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) hist[static_cast<size_t>(g) * e_stride + e] = h[warp][e];
+}
+
+__global__ void __launch_bounds__(kWideWarps * 32) moe_scatter_kernel(const int* __restrict__ idx, int n, int E, int chunks,
+                                                                      const int* __restrict__ hist, MoeLayoutDev L,
+                                                                      int* __restrict__ dest_row) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ int base[kWideWarps][kMaxExperts];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = blockIdx.x * kWideWarps + warp;
+  const int e_stride = (E + 31) & ~31;
+  const int lo = g * kWideChunk;
+  if (lo >= n) return;
+  const int* seg = hist + static_cast<size_t>(chunks) * e_stride;     // first row of every expert, then its rank
+  for (int e = lane; e < E; e += 32) base[warp][e] = seg[e] + hist[static_cast<size_t>(g) * e_stride + e];
+  __syncwarp();
+  int ev[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int i = lo + k * 32 + lane;
+    ev[k] = i < n ? __ldg(idx + i) : -1;
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int i = lo + k * 32 + lane;
+    const int e = ev[k];
+    const bool valid = e >= 0 && e < E;
+    const uint32_t peers = __match_any_sync(0xffffffffu, valid ? e : -1 - lane);
+    int row = -1;
+    if (valid) {
+      row = base[warp][e] + __popc(peers & ((1u << lane) - 1u));
+      if (row < L.max_rows) {
+        const int r = seg[e_stride + e];
+        (L.meta[r] + kMetaHeader + 2 * L.max_tiles)[row] = i;
+      } else {
+        row = -1;
+      }
+    }
+    __syncwarp();
+    if (valid && (peers >> lane) == 1u) base[warp][e] += __popc(peers);
+    __syncwarp();
+    if (i < n) dest_row[i] = row;
   }
 }
 
@@ -571,7 +724,31 @@ int cafd_moe_plan(const int* idx, int T, int top_k, int E, int tile_rows, const 
                   int* dest_row, int* expert_count, uint32_t* status, cafd_stream_t s) {
   if (E > kMaxExperts || layout->n_ranks < 1 || layout->n_ranks > kMaxRanks) return -10;
   launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(s), idx, T, top_k, E, tile_rows, to_dev(layout), dest_row,
-             expert_count, status, static_cast<const uint4*>(nullptr), 0, static_cast<const uint32_t*>(nullptr));
+             expert_count, status, static_cast<const uint4*>(nullptr), 0, static_cast<const uint32_t*>(nullptr),
+             static_cast<int*>(nullptr), 0);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Wide plan: three launches that use the whole GPU (see moe_count_kernel).  scratch: cafd_moe_plan_wide_ints(T * top_k, E) ints.
+int cafd_moe_plan_wide_ints(int n_entries, int E) {
+  const int e_stride = (E + 31) & ~31;
+  const int chunks = (n_entries + kWideChunk - 1) / kWideChunk;
+  return (chunks + 2) * e_stride;
+}
+
+int cafd_moe_plan_wide(const int* idx, int T, int top_k, int E, int tile_rows, const cafd_moe_layout* layout,
+                       int* dest_row, int* expert_count, uint32_t* status, int* scratch, cafd_stream_t s) {
+  if (E > kMaxExperts || layout->n_ranks < 1 || layout->n_ranks > kMaxRanks || !scratch) return -10;
+  const int n = T * top_k;
+  if (n <= 0) return 0;
+  const int chunks = (n + kWideChunk - 1) / kWideChunk;
+  const int blocks = (chunks + kWideWarps - 1) / kWideWarps;
+  cudaStream_t st = static_cast<cudaStream_t>(s);
+  launch_pdl(moe_count_kernel, dim3(blocks), dim3(kWideWarps * 32), 0, st, idx, n, E, scratch);
+  launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, st, idx, T, top_k, E, tile_rows, to_dev(layout), dest_row, expert_count,
+             status, static_cast<const uint4*>(nullptr), 0, static_cast<const uint32_t*>(nullptr), scratch, chunks);
+  launch_pdl(moe_scatter_kernel, dim3(blocks), dim3(kWideWarps * 32), 0, st, idx, n, E, chunks, static_cast<const int*>(scratch),
+             to_dev(layout), dest_row);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -581,7 +758,7 @@ int cafd_moe_plan_dispatch(const int* idx, int T, int top_k, int E, int tile_row
                            cafd_stream_t s) {
   if (E > kMaxExperts || layout->n_ranks < 1 || layout->n_ranks > kMaxRanks || !x || !epoch || H % 8) return -10;
   launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(s), idx, T, top_k, E, tile_rows, to_dev(layout), dest_row,
-             expert_count, status, static_cast<const uint4*>(x), H / 8, epoch);
+             expert_count, status, static_cast<const uint4*>(x), H / 8, epoch, static_cast<int*>(nullptr), 0);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -261,8 +261,23 @@ def moe_plan(idx: torch.Tensor, E: int, tile_rows: int, layout: "_n.MoeLayout", 
                                                       _ptr(expert_count), status_word(idx.device).data_ptr(), x.data_ptr(),
                                                       x.shape[1], epoch.data_ptr(), _stream()), "moe_plan_dispatch")
         return
+    if T * k >= WIDE_PLAN_ENTRIES:
+        # prefill-sized step: count / scan / scatter over the whole GPU instead of one block walking every entry
+        need = _n.cuda_lib().cafd_moe_plan_wide_ints(T * k, E)
+        sc = _plan_scratch.get(idx.device.index)
+        if sc is None or sc.numel() < need:
+            sc = torch.empty(max(need, 1 << 16), dtype=torch.int32, device=idx.device)
+            _plan_scratch[idx.device.index] = sc
+        _n.check(_n.cuda_lib().cafd_moe_plan_wide(idx.data_ptr(), T, k, E, tile_rows, C.byref(layout), dest_row.data_ptr(),
+                                                  _ptr(expert_count), status_word(idx.device).data_ptr(), sc.data_ptr(),
+                                                  _stream()), "moe_plan_wide")
+        return
     _n.check(_n.cuda_lib().cafd_moe_plan(idx.data_ptr(), T, k, E, tile_rows, C.byref(layout), dest_row.data_ptr(),
                                          _ptr(expert_count), status_word(idx.device).data_ptr(), _stream()), "moe_plan")
+
+
+WIDE_PLAN_ENTRIES = 8192      # (token, slot) entries from which the plan runs in its three-launch wide form
+_plan_scratch: dict = {}
 
 
 _route_scratch: dict = {}

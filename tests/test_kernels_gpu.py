@@ -142,6 +142,35 @@ def test_moe_local_exchange(K, T, tile):
     assert int(ex.att.expert_count.sum().item()) == T * k
 
 
+@pytest.mark.parametrize("T,E,k", [(2500, 16, 4), (3000, 128, 8)])
+def test_moe_wide_plan_matches_single_block(K, T, E, k):
+    """Prefill-sized steps plan in three launches (count, scan, scatter); the result is the single-block plan's."""
+    from cuteafd_b200.parallel.moe_exchange import ExchangeGeometry, LocalExchange
+    assert T * k >= K.WIDE_PLAN_ENTRIES
+    H, I = 256, 128
+    logits = torch.randn(T, E, device=dev())
+    logits[:, 1] -= 50.0                                   # an expert that nobody picks
+    outs = []
+    for wide in (True, False):
+        old = K.WIDE_PLAN_ENTRIES
+        K.WIDE_PLAN_ENTRIES = old if wide else 1 << 30
+        try:
+            ex = LocalExchange(ExchangeGeometry(H, I, E, k, max_tokens=T, n_expert_ranks=1), dev())
+            x = bf(T, H, seed=1)
+            wg, wu, wd = bf(E, I, H, scale=0.05, seed=3), bf(E, I, H, scale=0.05, seed=4), bf(E, H, I, scale=0.05, seed=5)
+            out = torch.empty(T, H, dtype=torch.bfloat16, device=dev())
+            ex.forward(x, logits, dict(scoring="softmax"), wg, wu, wd, out, tile_rows=128)
+            check_status(K)
+            outs.append((ex.att.dest_row[:T * k].clone(), ex.exp.meta.clone(), out.clone(), ex.att.expert_count.clone()))
+        finally:
+            K.WIDE_PLAN_ENTRIES = old
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a, b)
+    idx, w = R.route_topk(logits, k, "softmax")
+    ref = R.combine_slots(R.moe_forward(x, idx, w, wg, wu, wd), None, None, torch.bfloat16)
+    close(outs[0][2], ref)
+
+
 def _paged_kv(S, lens, Hkv, D, seed=0):
     """Random K/V per sequence scattered over shuffled pages; returns caches, table, dense copies."""
     pages_per = [(n + 63) // 64 for n in lens]
