@@ -540,24 +540,44 @@ __global__ void __launch_bounds__(kWideWarps * 32) moe_scatter_kernel(const int*
 }
 
 // ---- dispatch -------------------------------------------------------------------------------------
-// One warp per (token, slot).  Rows travel as 16-byte stores into the owner's slab (local or peer).
+// One warp per token.  Rows travel as 16-byte stores into the owners' slabs (local or peer).
 __global__ void __launch_bounds__(256) moe_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ idx,
                                                            const int* __restrict__ dest_row, int n_entries, int top_k,
                                                            int row_vec, MoeLayoutDev L, const uint32_t* epoch,
                                                            uint32_t* done_counter) {
   pdl_wait();
   pdl_trigger();
-  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  // One warp per token: the row is read once (eight 16-byte loads in flight per lane) and stored to each of its
+  // top_k destinations.
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  if (i < n_entries) {
-    const int row = dest_row[i];
-    if (row >= 0) {
+  if (t * top_k < n_entries) {
+    int my_row = -1, my_rank = 0;
+    if (lane < top_k) {
+      const int i = t * top_k + lane;
+      my_row = dest_row[i];
       const int e = idx[i];
-      int r = 0;
-      while (r + 1 < L.n_ranks && e >= L.expert_lo[r + 1]) ++r;
-      const uint4* src = x + static_cast<size_t>(i / top_k) * row_vec;
-      uint4* dst = reinterpret_cast<uint4*>(L.slab[r]) + static_cast<size_t>(row) * row_vec;
-      for (int c = lane; c < row_vec; c += 32) dst[c] = src[c];
+      while (my_rank + 1 < L.n_ranks && e >= L.expert_lo[my_rank + 1]) ++my_rank;
+    }
+    const uint4* src = x + static_cast<size_t>(t) * row_vec;
+    for (int c0 = 0; c0 < row_vec; c0 += 256) {
+      uint4 v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int c = c0 + lane + 32 * k;
+        if (c < row_vec) v[k] = __ldg(src + c);
+      }
+      for (int sl = 0; sl < top_k; ++sl) {
+        const int row = __shfl_sync(0xffffffffu, my_row, sl);
+        const int r = __shfl_sync(0xffffffffu, my_rank, sl);
+        if (row < 0) continue;
+        uint4* dst = reinterpret_cast<uint4*>(L.slab[r]) + static_cast<size_t>(row) * row_vec;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int c = c0 + lane + 32 * k;
+          if (c < row_vec) dst[c] = v[k];
+        }
+      }
     }
   }
   __threadfence_system();
@@ -789,9 +809,9 @@ int cafd_norm_route(const void* h, const void* ln_w, float eps, const void* rout
 int cafd_moe_dispatch(const void* x, const int* idx, const int* dest_row, int T, int top_k, int H,
                       const cafd_moe_layout* layout, const uint32_t* epoch, uint32_t* done_counter,
                       cafd_stream_t s) {
-  if (H % 8) return -10;
+  if (H % 8 || top_k > 32) return -10;
   const int n = T * top_k;
-  const int blocks = n > 0 ? (n + 7) / 8 : 1;
+  const int blocks = T > 0 ? (T + 7) / 8 : 1;            // eight warps per block, one token each
   launch_pdl(moe_dispatch_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(s), static_cast<const uint4*>(x), idx, dest_row, n,
                                                                        top_k, H / 8, to_dev(layout), epoch,
                                                                        done_counter);
