@@ -34,6 +34,9 @@ class Batch:
     prefill: bool
     last_rows: torch.Tensor | None = None   # rows whose logits are wanted (None = all)
     fresh: bool = False                     # prefill of a single sequence from position 0 (no earlier context in the cache)
+    # media rows: (row indices int64 [m], embeddings [m, hidden] bf16), both on the device; those rows of the input
+    # take the tower's output instead of the embedding table's row (eager prefill only)
+    embeds: tuple | None = None
 
 
 class LayerWeights:
@@ -285,6 +288,8 @@ class GqaMoeEngine:
         assert T <= self.max_tokens
         K.embed(b.tokens, self.W.embed, out=ws.h[:T])
         self.launches += 1
+        if b.embeds is not None:
+            ws.h[:T].index_copy_(0, b.embeds[0], b.embeds[1])
         have_x = False
         for i in range(cfg.num_layers):
             L = self.W.layers[i]

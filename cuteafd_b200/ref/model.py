@@ -232,17 +232,26 @@ class RefDecoder:
         w = self.p["model.embed_tokens.weight"] if self.cfg.tie_embeddings else self.p["lm_head.weight"]
         return x.float() @ w.float().T
 
-    def hidden_states(self, tokens: torch.Tensor, kv: KvState) -> torch.Tensor:
+    def hidden_states(self, tokens: torch.Tensor, kv: KvState, embeds: tuple | None = None) -> torch.Tensor:
+        """``embeds`` = (rows, values [m, hidden]): those input rows take ``values`` (media tower output) instead of
+        the embedding table's row; their token ids may lie above the vocabulary."""
         start = kv.length(0)
         positions = torch.arange(start, start + tokens.shape[0], device=tokens.device)
-        h = self.embed(tokens)
+        if embeds is not None:
+            rows = torch.as_tensor(embeds[0], dtype=torch.long)
+            tokens = tokens.clone()
+            tokens[rows] = 0
+            h = self.embed(tokens).clone()
+            h[rows] = embeds[1].to(h.dtype)
+        else:
+            h = self.embed(tokens)
         for i in range(self.cfg.num_layers):
             h = self.layer(i, h, positions, kv)
         return h
 
-    def forward(self, tokens: torch.Tensor, kv: KvState) -> torch.Tensor:
+    def forward(self, tokens: torch.Tensor, kv: KvState, embeds: tuple | None = None) -> torch.Tensor:
         """Logits [T, vocab] (fp32) for the new tokens appended to ``kv``."""
-        return self.head(self.hidden_states(tokens, kv))
+        return self.head(self.hidden_states(tokens, kv, embeds))
 
     def mtp_forward(self, j: int, h_prev: torch.Tensor, next_tokens: torch.Tensor, positions: torch.Tensor,
                     kv: KvState) -> tuple[torch.Tensor, torch.Tensor]:

@@ -23,6 +23,7 @@ class _Handle:
     seq: Sequence
     kv: object = None            # oracle: KvState
     dead: bool = False
+    media: object = None         # the request's media spans (rows whose embeddings come from a tower)
 
 
 class OracleBackend:
@@ -89,10 +90,12 @@ class OracleBackend:
         return _Handle(seq, kv), m.length
 
     def prefill(self, h: _Handle, tokens: list[int], last: bool):
+        from ..media.processor import overrides_for
         self.table.reserve(h.seq, h.seq.kv_len + len(tokens))
         start = h.seq.kv_len
+        ov = overrides_for(getattr(h, "media", None), start, len(tokens))
         with torch.no_grad():
-            hid = self.model.hidden_states(torch.tensor(tokens), h.kv)
+            hid = self.model.hidden_states(torch.tensor(tokens), h.kv, ov)
             if self.has_mtp:                 # the MTP depth's K/V for the prompt (see EngineBackend.prefill)
                 self.model.mtp_forward(0, hid, torch.tensor(tokens[1:] + tokens[-1:]), torch.arange(start, start + len(tokens)), h.kv)
         h.seq.tokens.extend(tokens)
@@ -172,7 +175,16 @@ class EngineBackend:
         start, n = seq.kv_len, len(tokens)
         self.table.reserve(seq, start + n, copy_page=self._copy_page)
         b = self.gen.prefill_buf
-        b.tokens[0][:n] = torch.tensor(tokens, dtype=torch.int32)
+        # ids above the vocabulary mark media rows (their embeddings come from the request's spans); the embedding
+        # kernel still needs a valid id there
+        V = self.vocab_size
+        ov = None
+        if any(t >= V for t in tokens):
+            from ..media.processor import overrides_for
+            ov = overrides_for(getattr(h, "media", None), start, n)
+            if ov is None or len(ov[0]) != sum(t >= V for t in tokens):
+                raise ValueError("media rows in the prompt without their embeddings")
+        b.tokens[0][:n] = torch.tensor([t if t < V else 0 for t in tokens] if ov is not None else tokens, dtype=torch.int32)
         b.positions[0][:n] = torch.arange(start, start + n, dtype=torch.int32)
         b.slots[0][:n] = torch.tensor(self.table.slots(seq, start, n), dtype=torch.int32)
         pt = b.page_table[0].view(1, self.max_pages)
@@ -184,6 +196,9 @@ class EngineBackend:
         b.upload()
         batch = Batch(b.tokens[1][:n], b.positions[1][:n], b.slots[1][:n], b.page_table[1].view(1, self.max_pages),
                       b.seq_lens[1][:1], b.q_start[1][:2], n, True, b.last_rows[1][:1], fresh=start == 0)
+        if ov is not None:
+            dev = self.engine.device
+            batch.embeds = (torch.tensor(ov[0], dtype=torch.long).to(dev), ov[1].to(dev, torch.bfloat16))
         logits = self.engine.forward(batch)
         if self.has_mtp:
             # fill the MTP depth's K/V for the prompt: position t pairs with prompt token t+1 (the chunk's last row

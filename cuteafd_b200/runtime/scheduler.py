@@ -54,6 +54,7 @@ class Request:
     speculation: bool = True
     record_rows: bool = False          # probe: keep a hash of every selected logit row
     constraint: Any = None             # TokenConstraint: allowed-token mask applied first in the chain
+    media: Any = None                  # list of media spans (prompt position, embedding rows) for ids above the vocabulary
     rid: int = 0
     events: "queue.Queue[tuple]" = field(default_factory=queue.Queue)
     cancelled: threading.Event = field(default_factory=threading.Event)
@@ -129,7 +130,12 @@ class Scheduler:
             self._rid += 1
             req.rid = self._rid
         req.arrival = time.monotonic()
-        if not req.prompt or any(t < 0 or t >= self.be.vocab_size for t in req.prompt) or req.max_tokens < 1:
+        # ids at or above the vocabulary are media rows: each must be covered by one of the request's spans
+        covered = set()
+        for sp in req.media or ():
+            covered.update(range(sp.start, sp.start + sp.length))
+        V = self.be.vocab_size
+        if not req.prompt or any(t < 0 or (t >= V and i not in covered) for i, t in enumerate(req.prompt)) or req.max_tokens < 1:
             req.events.put(("error", FAIL_BAD_REQUEST, "empty prompt, token out of range or max_tokens < 1"))
             self.stats.rejected += 1
             return req
@@ -211,6 +217,8 @@ class Scheduler:
                     continue
                 break                                   # wait for running requests to release pages
             self.pending.pop(0)
+            if req.media:
+                handle.media = req.media
             a = Active(req, handle, cached, prompt_done=cached, kv_len=cached)
             self.prefilling.append(a)
             self.stats.admitted += 1
@@ -296,6 +304,9 @@ class Scheduler:
             heads.append(scores)
         self.policy.settle(plans, self.row_budget)
         drafts = [d[: p.keep + p.copy] for d, p in zip(drafts, plans)]
+        # a copied history may contain media rows (ids above the vocabulary): a draft stops before the first one
+        V = self.be.vocab_size
+        drafts = [d[: next((i for i, t in enumerate(d) if t >= V or t < 0), len(d))] for d in drafts]
         rows = [[a.last_token] + d for a, d in zip(runnable, drafts)]
         # GPU selection when nothing needs the logit rows on the host (grammar masks advance per token on the
         # host; row hashes are taken from the row bytes)

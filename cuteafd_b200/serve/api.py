@@ -49,11 +49,12 @@ def _stops(body: dict, tok) -> tuple[int, ...]:
     return tuple(ids) + tuple(getattr(tok, "eos_ids", ()))
 
 
-def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, flavor: str = "openai") -> Request:
+def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, flavor: str = "openai",
+                  media=None) -> Request:
     # a probe too large for a header (a long synthetic prompt) may ride in the body instead
     probe = {**(body.get("cuteafd_probe") or {}), **(probe or {})}
     if probe.get("prompt_ids"):
-        prompt = [int(t) for t in probe["prompt_ids"]]
+        prompt, spans = [int(t) for t in probe["prompt_ids"]], None
     else:
         if flavor == "anthropic":
             msgs = []
@@ -71,7 +72,21 @@ def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, f
             msgs = list(body.get("messages") or [])
         if not msgs:
             raise BadRequest("messages must not be empty")
-        prompt = tok.encode(render_chat(msgs, True, body.get("tools")))
+        items: list = []
+        text = render_chat(msgs, True, body.get("tools"), media=items)
+        if items:
+            # image / audio parts: tower rows replace placeholder ids (``media`` is the deployment's MediaProcessor)
+            from ..media.image import MediaError, bytes_from_url
+            from .tokenizer import split_media
+            if media is None:
+                raise BadRequest("this deployment serves text only (no media tower is loaded)")
+            try:
+                segs = [s if isinstance(s, str) else (s[0], bytes_from_url(s[1])) for s in split_media(text, items)]
+                prompt, spans = media.expand(segs, tok.encode)
+            except MediaError as e:
+                raise BadRequest(str(e)) from e
+        else:
+            prompt, spans = tok.encode(text), None
     max_tokens = body.get("max_tokens") or body.get("max_completion_tokens") or body.get("max_output_tokens") or 256
     if not isinstance(max_tokens, int) or max_tokens < 1:
         raise BadRequest("max_tokens must be a positive integer")
@@ -81,7 +96,7 @@ def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, f
         raise BadRequest(str(e)) from e
     return Request(prompt=prompt, max_tokens=max_tokens, params=_params(body), stop_ids=_stops(body, tok),
                    speculation=not probe.get("no_speculation", False), record_rows=bool(probe.get("record_rows", False)),
-                   constraint=cons)
+                   constraint=cons, media=spans)
 
 
 def parse_probe(headers) -> dict:

@@ -27,8 +27,9 @@ JSON.stringify(await r.json(),null,1)}t();setInterval(t,1000)</script>"""
 
 
 class ServerState:
-    def __init__(self, scheduler: Scheduler, tokenizer, model_id: str, api_key: str = "", usage=None, extras=None):
+    def __init__(self, scheduler: Scheduler, tokenizer, model_id: str, api_key: str = "", usage=None, extras=None, media=None):
         self.sched, self.tok, self.model_id, self.api_key = scheduler, tokenizer, model_id, api_key
+        self.media = media                  # MediaProcessor, or None for a text-only deployment
         self.usage = usage
         self.extras = extras or {}
         self.started = time.time()
@@ -134,6 +135,8 @@ def make_handler(state: ServerState):
             if path == "/memory":
                 from ..utils.memory_ledger import LEDGER
                 return self._json(200, LEDGER.report())
+            if path == "/v1/media":
+                return self._json(200, state.media.describe() if state.media else {"vision": False, "audio": False})
             if path == "/experts":
                 return self._json(200, state.extras.get("expert_usage", lambda: {})())
             if path.startswith("/console/usage"):
@@ -166,7 +169,7 @@ def make_handler(state: ServerState):
             try:
                 body = self._body()
                 probe = api.parse_probe(self.headers)
-                req = api.build_request(body, state.tok, state.sched.be.vocab_size, probe, flavor)
+                req = api.build_request(body, state.tok, state.sched.be.vocab_size, probe, flavor, state.media)
             except api.BadRequest as e:
                 st, eb, hd = api.error_body(FAIL_BAD_REQUEST, str(e), flavor)
                 return self._json(st, eb, hd)
@@ -348,7 +351,19 @@ def build_state(args) -> ServerState:
     sched = Scheduler(be, max_active=args.concurrency, queue_depth=args.queue_depth, queue_wait_s=args.queue_wait,
                       drafter=drafter, eos_ids=tuple(getattr(tok, "eos_ids", ())))
     usage = UsageLog(args.usage_db) if args.usage_db else None
-    return ServerState(sched, tok, cfg.name, args.api_key, usage)
+    media = None
+    if getattr(args, "media", "none") != "none":
+        from ..media import AudioTower, AudioTowerConfig, MediaProcessor, VisionTower, VisionTowerConfig
+        from ..media.loader import load_towers
+        mdev = "cuda:0" if (torch.cuda.is_available() and not args.fake_engine) else "cpu"
+        vision, audio = load_towers(snapshot, cfg.hidden, mdev) if snapshot else (None, None)
+        if args.media == "random":           # geometry checks and benchmarks without a multimodal checkpoint
+            small = dict(width=256, depth=2, heads=4, mlp=512, out_hidden=cfg.hidden)
+            vision = vision or VisionTower(VisionTowerConfig(**small), VisionTower.random_weights(VisionTowerConfig(**small)), mdev)
+            audio = audio or AudioTower(AudioTowerConfig(**small), AudioTower.random_weights(AudioTowerConfig(**small)), mdev)
+        if vision is not None or audio is not None:
+            media = MediaProcessor(cfg.vocab_size, cfg.hidden, vision, audio)
+    return ServerState(sched, tok, cfg.name, args.api_key, usage, media=media)
 
 
 def run_server(args) -> int:

@@ -79,9 +79,26 @@ def load_tokenizer(snapshot: str | None, vocab_size: int):
     return ByteTokenizer(vocab_size)
 
 
-def render_chat(messages: list[dict], add_generation_prompt: bool = True, tools: list[dict] | None = None) -> str:
+MEDIA_MARK = "\x00media:{}\x00"      # stands for media item i of the request inside the rendered text
+
+
+def split_media(rendered: str, items: list) -> list:
+    """Rendered chat text with ``MEDIA_MARK`` markers -> [text, item, text, ...] in prompt order."""
+    out, rest = [], rendered
+    for i, item in enumerate(items):
+        head, mark, rest = rest.partition(MEDIA_MARK.format(i))
+        out.append(head)
+        if mark:
+            out.append(item)
+    out.append(rest)
+    return out
+
+
+def render_chat(messages: list[dict], add_generation_prompt: bool = True, tools: list[dict] | None = None,
+                media: list | None = None) -> str:
     """ChatML-style template.  Tool definitions ride in a system block; tool results are turns of
-    role ``tool``; content parts of type text are concatenated."""
+    role ``tool``; content parts of type text are concatenated.  With ``media`` (a list to fill), image / audio parts
+    are appended to it as (kind, payload) and a ``MEDIA_MARK`` marker takes their place in the text."""
     parts = []
     if tools:
         parts.append("<|im_start|>system\nYou may call these tools by emitting a JSON object "
@@ -89,7 +106,28 @@ def render_chat(messages: list[dict], add_generation_prompt: bool = True, tools:
     for m in messages:
         c = m.get("content")
         if isinstance(c, list):
-            c = "".join(p.get("text", "") for p in c if isinstance(p, dict) and p.get("type") in ("text", "input_text", "output_text"))
+            pieces = []
+            for p in c:
+                if not isinstance(p, dict):
+                    continue
+                t = p.get("type")
+                if t in ("text", "input_text", "output_text"):
+                    pieces.append(str(p.get("text", "")).replace("\x00", ""))
+                elif media is not None and t in ("image_url", "input_image", "image"):
+                    url = p.get("image_url")
+                    url = url.get("url") if isinstance(url, dict) else url
+                    if url is None and isinstance(p.get("source"), dict):            # Anthropic: {"type": "base64", "media_type", "data"}
+                        src = p["source"]
+                        url = f"data:{src.get('media_type', 'image/png')};base64,{src.get('data', '')}"
+                    pieces.append(MEDIA_MARK.format(len(media)))
+                    media.append(("image", url))
+                elif media is not None and t in ("input_audio", "audio"):
+                    a = p.get("input_audio") or p.get("audio") or {}
+                    pieces.append(MEDIA_MARK.format(len(media)))
+                    media.append(("audio", f"data:audio/{a.get('format', 'wav')};base64,{a.get('data', '')}"))
+            c = "".join(pieces)
+        elif isinstance(c, str):
+            c = c.replace("\x00", "")
         if c is None:
             c = ""
         if m.get("tool_calls"):
