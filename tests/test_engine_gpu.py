@@ -114,3 +114,47 @@ def test_mtp_depth_matches_oracle(family):
     assert K.read_status() == 0
     errs.sort()
     assert errs[len(errs) // 2] < 0.03 and errs[int(len(errs) * 0.9)] < 0.06 and errs[-1] < 0.3, errs[-10:]
+
+
+def test_media_rows_through_the_engine_backend():
+    """A prompt with media rows (ids above the vocabulary + embedding spans) prefilled in chunks by the engine
+    backend gives the oracle's logits."""
+    from cuteafd_b200.media.processor import MediaSpan, overrides_for
+    from cuteafd_b200.ref.model import KvState, RefDecoder
+    from cuteafd_b200.runtime.backends import EngineBackend
+    cfg = small_cfg()
+    params, eng, _ = build(cfg, False)
+    be = EngineBackend(eng, 64, 8, prefill_chunk=64, max_decode_rows=4)
+    g = torch.Generator().manual_seed(4)
+    ids = torch.randint(0, cfg.vocab_size, (150,), generator=g).tolist()
+    emb = (torch.randn(70, cfg.hidden, generator=g) * 0.05).to(torch.bfloat16)
+    span = MediaSpan(40, emb, b"k" * 16, "image")            # rows 40..109 cross two chunk boundaries
+    for i in range(40, 110):
+        ids[i] = cfg.vocab_size + 12345
+    h, cached = be.open(ids)
+    h.media = [span]
+    assert cached == 0
+    logits = None
+    for c0 in range(0, len(ids), 64):
+        logits = be.prefill(h, ids[c0:c0 + 64], c0 + 64 >= len(ids))
+    ref = RefDecoder(cfg, params)
+    rl = ref.forward(torch.tensor(ids), KvState(cfg), overrides_for([span], 0, len(ids)))[-1]
+    err = (logits[0] - rl).abs().max().item()
+    assert err < 0.05 * max(rl.abs().max().item(), 1.0), err
+    with pytest.raises(ValueError):
+        h2, _ = be.open(ids)
+        be.prefill(h2, ids[:64], False)                      # media ids without their spans
+
+
+def test_vision_tower_on_the_gpu_matches_cpu():
+    """bf16 tower with its projections on the tcgen05 GEMM against the fp32 CPU tower."""
+    from cuteafd_b200.media import VisionTower, VisionTowerConfig, preprocess_image
+    cfg = VisionTowerConfig(width=256, depth=2, heads=4, mlp=512, out_hidden=512)
+    w = {k: v.to(torch.bfloat16).float() for k, v in VisionTower.random_weights(cfg, seed=3, std=0.05).items()}
+    px = torch.randint(0, 255, (120, 200, 3), generator=torch.Generator().manual_seed(0), dtype=torch.uint8)
+    patches, grid = preprocess_image(px)
+    ref = VisionTower(cfg, w, "cpu").forward(patches, grid)
+    got = VisionTower(cfg, w, "cuda:0").forward(patches, grid).float().cpu()
+    assert got.shape == ref.shape
+    err = (got - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
+    assert err < 0.05, err
