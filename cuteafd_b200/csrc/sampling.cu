@@ -48,10 +48,13 @@ __device__ __forceinline__ float splitmix_uniform(unsigned long long seed, long 
   return static_cast<float>(x >> 40) * (1.0f / 16777216.0f);
 }
 
+constexpr int kCompactMax = 2048;     // members of a cut up to which later selections walk a gathered list
+
 struct Cut { uint32_t key; int id; };     // members: key > cut.key, or key == cut.key and id <= cut.id
 
 struct SampleShared {
   unsigned long long hist[256];
+  unsigned int hist32[256];      // count-mode histogram: native 32-bit shared atomics
   unsigned long long suffix[256];
   unsigned long long total, acc;
   int counts[kSampleThreads];
@@ -74,7 +77,7 @@ __device__ Cut select_prefix(const Cand& cand, int V, Cut cut, bool by_mass, dou
   uint32_t prefix = 0;
   for (int level = 0; level < 4; ++level) {
     const int shift = 24 - 8 * level;
-    if (tid < 256) sh.hist[tid] = 0;
+    if (tid < 256) { sh.hist[tid] = 0; sh.hist32[tid] = 0; }
     __syncthreads();
     for (int i0 = 0; i0 < V; i0 += kSampleThreads) {      // warp-uniform trip count
       const int i = i0 + tid;
@@ -85,7 +88,9 @@ __device__ Cut select_prefix(const Cand& cand, int V, Cut cut, bool by_mass, dou
       if (level > 0) active = active && (key >> (shift + 8)) == prefix;
       const uint32_t bin = (key >> shift) & 255u;
       const unsigned long long val = by_mass ? m : 1ull;
-      if (level == 0) {
+      if (!by_mass) {
+        if (active) atomicAdd(&sh.hist32[bin], 1u);
+      } else if (level == 0) {
         // the top byte (sign + high exponent bits) takes a handful of values: combine the lanes of a warp
         // that share a bin before touching shared memory, or the atomics serialise on two or three words
         unsigned remaining = __ballot_sync(0xffffffffu, active);
@@ -105,6 +110,7 @@ __device__ Cut select_prefix(const Cand& cand, int V, Cut cut, bool by_mass, dou
       }
     }
     __syncthreads();
+    if (!by_mass && tid < 256) sh.hist[tid] = sh.hist32[tid];
     if (tid < 256) sh.suffix[tid] = sh.hist[tid];
     __syncthreads();
     for (int d = 1; d < 256; d <<= 1) {          // inclusive suffix sums: suffix[b] = sum of bins >= b
@@ -258,13 +264,74 @@ __global__ void __launch_bounds__(kSampleThreads) sample_rows_kernel(const float
     m = __float2ull_rn(fast_exp2((xp - maxp) * 1.4426950408889634f) * 17592186044416.0f);
     return true;
   };
-  Cut cut{0u, 0x7fffffff};
-  if (rp.top_k > 0 && rp.top_k < V) cut = select_prefix(cand, V, cut, false, 0.0, false, rp.top_k, sh);
-  if (rp.top_p < 1.0f) cut = select_prefix(cand, V, cut, true, static_cast<double>(rp.top_p), false, 0, sh);
+  // Once a cut has few members (top-k of 50, a sharp nucleus) they are gathered, in id order, into a short list and
+  // every later selection walks the list instead of the vocabulary: the same selections over the same order (list
+  // position order = id order, so ties resolve identically), two iterations per thread instead of V / 1024.
+  __shared__ int s_list[kCompactMax];
+  __shared__ int s_nlist;
+  auto compact = [&](const Cut c) -> bool {
+    const int chunk = (V + kSampleThreads - 1) / kSampleThreads;
+    const int lo = tid * chunk, hi = min(V, lo + chunk);
+    int mine = 0;
+    for (int i = lo; i < hi; ++i) {
+      float xp; unsigned long long m;
+      if (!cand(i, xp, m)) continue;
+      const uint32_t key = order_key(xp);
+      if (key > c.key || (key == c.key && i <= c.id)) ++mine;
+    }
+    sh.counts[tid] = mine;
+    __syncthreads();
+    for (int d = 1; d < kSampleThreads; d <<= 1) {
+      int add = 0;
+      if (tid >= d) add = sh.counts[tid - d];
+      __syncthreads();
+      sh.counts[tid] += add;
+      __syncthreads();
+    }
+    const int total = sh.counts[kSampleThreads - 1];
+    const bool fits = total > 0 && total <= kCompactMax;
+    if (fits) {
+      int at = sh.counts[tid] - mine;
+      for (int i = lo; i < hi && mine > 0; ++i) {
+        float xp; unsigned long long m;
+        if (!cand(i, xp, m)) continue;
+        const uint32_t key = order_key(xp);
+        if (key > c.key || (key == c.key && i <= c.id)) s_list[at++] = i;
+      }
+      if (tid == 0) s_nlist = total;
+    }
+    __syncthreads();
+    return fits;
+  };
+  auto cand_l = [&](int j, float& xp, unsigned long long& m) -> bool { return cand(s_list[j], xp, m); };
+  const Cut all{0u, 0x7fffffff};
+  Cut cut = all;
+  bool listed = false;
+  if (rp.top_k > 0 && rp.top_k < V) {
+    cut = select_prefix(cand, V, cut, false, 0.0, false, rp.top_k, sh);
+    if (rp.top_k <= kCompactMax) listed = compact(cut);
+    if (listed) cut = all;
+  }
+  if (rp.top_p < 1.0f) {
+    if (listed) {
+      cut = select_prefix(cand_l, s_nlist, cut, true, static_cast<double>(rp.top_p), false, 0, sh);
+    } else {
+      cut = select_prefix(cand, V, cut, true, static_cast<double>(rp.top_p), false, 0, sh);
+      listed = compact(cut);
+      if (listed) cut = all;
+    }
+  }
   float u = splitmix_uniform(rp.seed, rp.position);
   u = fminf(fmaxf(u, 0.f), 0.99999994f);
-  const Cut pick = select_prefix(cand, V, cut, true, static_cast<double>(u), true, 0, sh);
-  if (tid == 0) { out_token[blockIdx.x] = pick.id >= 0 ? pick.id : bi; out_status[blockIdx.x] = kSampleOk; }
+  int token;
+  if (listed) {
+    const Cut pick = select_prefix(cand_l, s_nlist, cut, true, static_cast<double>(u), true, 0, sh);
+    token = pick.id >= 0 ? s_list[pick.id] : bi;
+  } else {
+    const Cut pick = select_prefix(cand, V, cut, true, static_cast<double>(u), true, 0, sh);
+    token = pick.id >= 0 ? pick.id : bi;
+  }
+  if (tid == 0) { out_token[blockIdx.x] = token; out_status[blockIdx.x] = kSampleOk; }
 }
 
 // Sample-match verification.  Rows [row_start[s], row_start[s+1]) belong to sequence s: row j holds the
