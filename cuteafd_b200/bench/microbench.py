@@ -113,7 +113,7 @@ def bench_gemm(a, dev, pk):
 def bench_attn_prefill(a, dev, pk):
     Hq, Hkv, D, n = a.heads, a.kv_heads, 128, a.len
     pages = (n + 63) // 64 + 1
-    kc = torch.randn(pages, 64, Hkv, D, device=dev).bfloat16()
+    kc = torch.randn(pages, Hkv, 64, D, device=dev).bfloat16()
     vc = torch.randn_like(kc)
     kc[0] = 0; vc[0] = 0
     table = torch.arange(1, pages, dtype=torch.int32, device=dev).view(1, -1).contiguous()
@@ -130,7 +130,7 @@ def bench_attn_decode(a, dev, pk):
     Hq, Hkv, D, S, n = a.heads, a.kv_heads, 128, a.seqs, a.len
     pps = (n + 63) // 64
     pages = S * pps + 1
-    kcs = [torch.randn(pages, 64, Hkv, D, device=dev).bfloat16() for _ in range(2 if S >= 16 else 4)]
+    kcs = [torch.randn(pages, Hkv, 64, D, device=dev).bfloat16() for _ in range(2 if S >= 16 else 4)]
     table = (torch.arange(S * pps, dtype=torch.int32, device=dev) + 1).view(S, pps).contiguous()
     q = torch.randn(S, Hq, D, device=dev).bfloat16()
     out = torch.empty_like(q)

@@ -45,7 +45,8 @@ __device__ __forceinline__ void load_page(uint8_t* dst, const __nv_bfloat16* cac
   // from 8 different rows hit different banks.
   for (int i = threadIdx.x; i < kPage * 16; i += blockDim.x) {
     const int tok = i >> 4, ch = i & 15;
-    const __nv_bfloat16* src = cache + ((static_cast<size_t>(page) * kPage + tok) * Hkv + kvh) * kD + ch * 8;
+    // cache layout [page, kv head, 64 tokens, D]: the tile of one (page, head) is 16 KB of contiguous memory
+    const __nv_bfloat16* src = cache + ((static_cast<size_t>(page) * Hkv + kvh) * kPage + tok) * kD + ch * 8;
     cp_async_16(dst + tok * 256 + ((ch ^ (tok & 7)) << 4), src);
   }
 }

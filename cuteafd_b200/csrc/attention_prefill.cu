@@ -396,7 +396,9 @@ extern "C" int cafd_attn_prefill(const void* q, const void* k_cache, const void*
   if (rc) return rc;
   const uint64_t dims[4] = {static_cast<uint64_t>(kHD), static_cast<uint64_t>(Hkv), kPageTok,
                             static_cast<uint64_t>(num_pages)};
-  const uint64_t strides[3] = {static_cast<uint64_t>(kHD) * 2, static_cast<uint64_t>(Hkv) * kHD * 2,
+  // The pools are [page, kv head, 64 tokens, D]; the map keeps the coordinate order (d, kv head, token, page) the
+  // kernel uses and only names the strides of that memory layout (head stride 64 * D, token stride D).
+  const uint64_t strides[3] = {static_cast<uint64_t>(kPageTok) * kHD * 2, static_cast<uint64_t>(kHD) * 2,
                                static_cast<uint64_t>(kPageTok) * Hkv * kHD * 2};
   const uint32_t box[4] = {64, 1, kPageTok, 1};
   rc = make_tmap_nd(&tk, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dims, strides, box, true);

@@ -118,7 +118,8 @@ __global__ void __launch_bounds__(128) qk_rope_kv_kernel(const __nv_bfloat16* __
   const int slot = slots[t];
   if (h >= Hq + Hkv) {  // V: plain copy into the cache
     if (slot >= 0) {
-      __nv_bfloat16* dst = v_cache + (static_cast<size_t>(slot) * Hkv + (h - Hq - Hkv)) * D;
+      // cache layout [page, kv head, 64 tokens, D]: one (page, head) tile is 16 KB of contiguous memory
+      __nv_bfloat16* dst = v_cache + ((static_cast<size_t>(slot >> 6) * Hkv + (h - Hq - Hkv)) * 64 + (slot & 63)) * D;
       *reinterpret_cast<uint32_t*>(dst + 2 * lane) = a;
       *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = b;
     }
@@ -158,7 +159,7 @@ __global__ void __launch_bounds__(128) qk_rope_kv_kernel(const __nv_bfloat16* __
     dst = q_out + (static_cast<size_t>(t) * Hq + h) * D;
   } else {
     if (slot < 0) return;
-    dst = k_cache + (static_cast<size_t>(slot) * Hkv + (h - Hq)) * D;
+    dst = k_cache + ((static_cast<size_t>(slot >> 6) * Hkv + (h - Hq)) * 64 + (slot & 63)) * D;
   }
   *reinterpret_cast<uint32_t*>(dst + 2 * lane) = oa;
   *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = ob;

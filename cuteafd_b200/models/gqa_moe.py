@@ -159,12 +159,13 @@ class GqaMoeWeights:
 
 
 class KvCache:
-    """Paged K/V pools, one pair per layer: [num_pages, 64, Hkv, D] bf16.  Page 0 stays all-zero:
+    """Paged K/V pools, one pair per layer: [num_pages, Hkv, 64, D] bf16 (the tile of one page and kv head is 16 KB of
+    contiguous memory: decode attention streams whole tiles).  Page 0 stays all-zero:
     kernels read it for table entries past a sequence's end (the reference keeps the same
     reserved page, rust/crates/cuteafd-engine/src/prefix/family.rs:20-28)."""
 
     def __init__(self, cfg: ModelConfig, num_pages: int, device: torch.device):
-        shape = (num_pages, PAGE, cfg.num_kv_heads, cfg.head_dim)
+        shape = (num_pages, cfg.num_kv_heads, PAGE, cfg.head_dim)     # one (page, head) tile is contiguous
         self.num_pages = num_pages
         n = cfg.num_layers + cfg.mtp_layers              # MTP decoder layers keep their own K/V, same pages
         self.k = [torch.zeros(shape, dtype=torch.bfloat16, device=device) for _ in range(n)]

@@ -350,7 +350,7 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, p
                 seq_lens: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor | None,
                 max_q_len: int, splits: int, scale: float | None = None) -> torch.Tensor:
     _, Hq, D = q.shape
-    Hkv = k_cache.shape[2]
+    Hkv = k_cache.shape[1]                 # pools are [pages, kv heads, 64, D]
     num_seqs, max_pages = page_table.shape
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     _n.check(_n.cuda_lib().cafd_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_table.data_ptr(),
@@ -370,7 +370,7 @@ def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
                  seq_lens: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor, max_q_len: int,
                  scale: float | None = None) -> torch.Tensor:
     total_q, Hq, D = q.shape
-    num_pages, _, Hkv, _ = k_cache.shape
+    num_pages, Hkv, _, _ = k_cache.shape   # pools are [pages, kv heads, 64, D]
     num_seqs, max_pages = page_table.shape
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     _n.check(_n.cuda_lib().cafd_attn_prefill(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_table.data_ptr(),

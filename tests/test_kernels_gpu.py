@@ -97,7 +97,7 @@ def test_qk_rope_kv(K, interleaved, norm):
     inv = (1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))).to(dev())
     pos = torch.arange(100, 100 + T, dtype=torch.int32, device=dev())
     perm = torch.randperm(pages * 64)[:T].to(torch.int32).to(dev())
-    kc = torch.zeros(pages, 64, Hkv, D, dtype=torch.bfloat16, device=dev())
+    kc = torch.zeros(pages, Hkv, 64, D, dtype=torch.bfloat16, device=dev())       # [page, kv head, token, D]
     vc = torch.zeros_like(kc)
     q_out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=dev())
     K.qk_rope_kv(qkv, qn, kn, inv, pos, perm, q_out, kc, vc, Hq, Hkv, D, 1e-6, interleaved)
@@ -107,8 +107,9 @@ def test_qk_rope_kv(K, interleaved, norm):
     rq = R.apply_rope(q, pos.long(), theta, interleaved)
     rk = R.apply_rope(k, pos.long(), theta, interleaved)
     close(q_out, rq, 1e-2, 1e-2)
-    close(kc.view(-1, Hkv, D)[perm.long()], rk, 1e-2, 1e-2)
-    assert torch.equal(vc.view(-1, Hkv, D)[perm.long()], v)
+    by_slot = lambda c: c.permute(0, 2, 1, 3).reshape(-1, Hkv, D)               # noqa: E731  slot = page * 64 + token
+    close(by_slot(kc)[perm.long()], rk, 1e-2, 1e-2)
+    assert torch.equal(by_slot(vc)[perm.long()], v)
 
 
 @pytest.mark.parametrize("E,k,scoring,groups,keep", [(128, 8, "softmax", 1, 1), (256, 8, "sigmoid", 8, 4),
@@ -176,7 +177,7 @@ def _paged_kv(S, lens, Hkv, D, seed=0):
     pages_per = [(n + 63) // 64 for n in lens]
     total = sum(pages_per) + 1
     order = (torch.randperm(total - 1) + 1).tolist()
-    kc = torch.zeros(total, 64, Hkv, D, dtype=torch.bfloat16, device=dev())
+    kc = torch.zeros(total, Hkv, 64, D, dtype=torch.bfloat16, device=dev())       # [page, kv head, token, D]
     vc = torch.zeros_like(kc)
     table = torch.zeros(S, max(pages_per), dtype=torch.int32)
     dense = []
@@ -187,7 +188,7 @@ def _paged_kv(S, lens, Hkv, D, seed=0):
             pg = order.pop()
             table[s, j] = pg
             n = min(64, lens[s] - 64 * j)
-            kc[pg, :n], vc[pg, :n] = k[64 * j:64 * j + n], v[64 * j:64 * j + n]
+            kc[pg, :, :n], vc[pg, :, :n] = k[64 * j:64 * j + n].transpose(0, 1), v[64 * j:64 * j + n].transpose(0, 1)
     return kc, vc, table.to(dev()), dense
 
 
