@@ -158,6 +158,15 @@ class EngineBackend:
         self._sel = None
         self._last_batch = None
         self.last_mtp: list[int] | None = None
+        # Decode graph bank: one CUDA graph per exact step geometry (sequences, rows, longest row run).  A geometry is
+        # captured once it has been seen ``graph_after`` times (or named by a prewarm list), replayed from then on, and
+        # dropped least recently used first beyond ``max_graphs``; a step never waits for a capture it does not need
+        # (the eager path serves it).  Counterpart: rust/crates/cuteafd-daemon/src/shared/decode_graph/bank.rs.
+        self.use_graphs = use_graphs
+        self.max_graphs, self.graph_after = 32, 2
+        self.graphs: dict[tuple[int, int, int], tuple] = {}
+        self.geometry_seen: dict[tuple[int, int, int], int] = {}
+        self.graph_stats = {"replays": 0, "eager": 0, "captures": 0, "evictions": 0}
         inner = getattr(engine, "inner", engine)
         self.has_mtp = bool(getattr(getattr(inner, "W", None), "mtp", None)) and hasattr(engine, "mtp_forward")
 
@@ -209,6 +218,79 @@ class EngineBackend:
         seq.kv_len = start + n
         return logits[:1].float().cpu() if last else None
 
+    # ---- decode graph bank ------------------------------------------------------------------------------
+    def _step_batch(self, key: tuple[int, int, int]):
+        from ..models.gqa_moe import Batch
+        S, T, mq = key
+        b = self.bufs
+        return Batch(b.tokens[1][:T], b.positions[1][:T], b.slots[1][:T], b.page_table[1].view(b.max_seqs, self.max_pages)[:S],
+                     b.seq_lens[1][:S], b.q_start[1][:S + 1], mq, False, None)
+
+    def _capture(self, key: tuple[int, int, int], batch) -> None:
+        """The step's inputs are already in the static buffers.  Kernels run during the warm-up write the same K/V the
+        replay writes again, so capturing in the middle of serving is harmless."""
+        for _ in range(2):
+            self.engine.forward(batch)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = self.engine.forward(batch)
+        self.graphs[key] = (g, out)
+        self.graph_stats["captures"] += 1
+        while len(self.graphs) > self.max_graphs:
+            del self.graphs[next(iter(self.graphs))]
+            self.graph_stats["evictions"] += 1
+
+    def _run_step(self, key: tuple[int, int, int], batch) -> torch.Tensor:
+        seen = self.geometry_seen[key] = self.geometry_seen.get(key, 0) + 1
+        if self.use_graphs and key not in self.graphs and seen >= self.graph_after:
+            self._capture(key, batch)
+        if self.use_graphs and key in self.graphs:
+            g, out = self.graphs.pop(key)
+            self.graphs[key] = (g, out)                       # most recently used last
+            if hasattr(self.engine, "announce"):
+                self.engine.announce(key[1], 1, for_replay=True)
+            g.replay()
+            self.graph_stats["replays"] += 1
+            return out
+        self.graph_stats["eager"] += 1
+        return self.engine.forward(batch)
+
+    def prewarm(self, keys: list) -> int:
+        """Capture the listed geometries before traffic arrives ([sequences, rows, longest run] triples, e.g. the list a
+        previous run saved with ``save_prewarm``).  The capture runs on a dummy step: no K/V slot is written (slot -1),
+        every table entry is the zero page.  Returns the number of graphs captured."""
+        if not self.use_graphs:
+            return 0
+        b = self.bufs
+        n = 0
+        for key in keys:
+            S, T, mq = (int(v) for v in key)
+            if (S, T, mq) in self.graphs or S < 1 or S > b.max_seqs or T < S or T > b.max_tokens or mq * S < T:
+                continue
+            b.tokens[0][:T] = 0
+            b.positions[0][:T] = 0
+            b.slots[0][:T] = -1
+            b.page_table[0].zero_()
+            b.seq_lens[0][:S] = mq
+            per, extra = divmod(T, S)
+            starts = [0]
+            for i in range(S):
+                starts.append(starts[-1] + per + (1 if i < extra else 0))
+            b.q_start[0][:S + 1] = torch.tensor(starts, dtype=torch.int32)
+            b.upload()
+            self._capture((S, T, mq), self._step_batch((S, T, mq)))
+            n += 1
+        return n
+
+    def save_prewarm(self, path: str, top: int = 16) -> list:
+        """Write the most frequent step geometries of this run as a prewarm list (JSON)."""
+        import json
+        keys = [list(k) for k, _ in sorted(self.geometry_seen.items(), key=lambda kv: -kv[1])[:top]]
+        with open(path, "w") as f:
+            json.dump({"geometries": keys, "seen": {",".join(map(str, k)): v for k, v in self.geometry_seen.items()}}, f)
+        return keys
+
     def _verify_device(self, handles: list[_Handle], rows: list[list[int]]) -> torch.Tensor:
         from ..models.gqa_moe import Batch
         S = len(handles)
@@ -230,9 +312,9 @@ class EngineBackend:
             o += n
         b.q_start[0][S] = T
         b.upload()
-        batch = Batch(b.tokens[1][:T], b.positions[1][:T], b.slots[1][:T], b.page_table[1].view(b.max_seqs, self.max_pages)[:S],
-                      b.seq_lens[1][:S], b.q_start[1][:S + 1], max(len(r) for r in rows), False, None)
-        logits = self.engine.forward(batch)
+        key = (S, T, max(len(r) for r in rows))
+        batch = self._step_batch(key)
+        logits = self._run_step(key, batch)
         for h, r in zip(handles, rows):
             h.seq.tokens.extend(r)
             h.seq.kv_len += len(r)

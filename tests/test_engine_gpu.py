@@ -158,3 +158,54 @@ def test_vision_tower_on_the_gpu_matches_cpu():
     assert got.shape == ref.shape
     err = (got - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
     assert err < 0.05, err
+
+
+def test_decode_graph_bank_and_prewarm(tmp_path):
+    """The serving backend replays one CUDA graph per step geometry: same tokens as the eager path, a geometry is
+    captured on its second sight, a saved prewarm list captures before traffic."""
+    import json
+    from cuteafd_b200.ops import kernels as K
+    from cuteafd_b200.runtime.backends import EngineBackend
+    from cuteafd_b200.runtime.scheduler import Request, Scheduler
+    cfg = small_cfg()
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (70, 33, 90)]
+
+    def run(use_graphs, prewarm=None):
+        _, eng, _ = build(cfg, False)
+        be = EngineBackend(eng, 64, 8, prefill_chunk=64, max_decode_rows=4, use_graphs=use_graphs)
+        if prewarm:
+            assert be.prewarm(prewarm) == len(prewarm)
+        sched = Scheduler(be, max_active=4)
+        reqs = [Request(prompt=list(p), max_tokens=12, speculation=False) for p in prompts]
+        for r in reqs:
+            sched.submit(r)
+        toks = [[] for _ in reqs]
+        done = 0
+        for _ in range(400):
+            sched.step()
+            for i, r in enumerate(reqs):
+                while not r.events.empty():
+                    ev = r.events.get()
+                    if ev[0] == "tokens":
+                        toks[i] += ev[1]
+                    elif ev[0] in ("done", "error"):
+                        assert ev[0] == "done", ev
+                        done += 1
+            if done == len(reqs):
+                break
+        assert done == len(reqs)
+        torch.cuda.synchronize()
+        assert K.read_status() == 0
+        return toks, be
+
+    eager, be0 = run(False)
+    graphs, be1 = run(True)
+    assert eager == graphs
+    assert be0.graph_stats["replays"] == 0 and be1.graph_stats["replays"] > 0 and be1.graph_stats["captures"] >= 1
+    path = str(tmp_path / "prewarm.json")
+    keys = be1.save_prewarm(path, top=2)
+    assert json.load(open(path))["geometries"] == keys and len(keys) >= 1
+    warm, be2 = run(True, prewarm=keys)
+    assert warm == eager
+    assert be2.graph_stats["captures"] >= len(keys) and be2.graph_stats["eager"] < be1.graph_stats["eager"] + 1
