@@ -343,6 +343,14 @@ def build_state(args) -> ServerState:
                 from ..models.gqa_moe import GqaMoeEngine as Engine, GqaMoeWeights as Weights, KvCache as Cache
             eng = Engine(cfg, Weights.random_init(cfg, dev), Cache(cfg, num_pages, dev), max_tokens=max(2048, rows), max_seqs=rows)
         be = EngineBackend(eng, num_pages, pages_per_seq, prefill_chunk=2048, max_decode_rows=args.concurrency)
+        pw = getattr(args, "prewarm", "")
+        if pw:
+            import json
+            import os
+            if os.path.exists(pw):               # geometries a previous run saved (EngineBackend.save_prewarm)
+                with open(pw) as f:
+                    n = be.prewarm(json.load(f).get("geometries", []))
+                print(f"prewarmed {n} decode graphs from {pw}", flush=True)
     tok = load_tokenizer(snapshot, cfg.vocab_size)
     drafter = NgramDrafter(block=4) if args.speculator in ("auto", "history", "ngram") else None
     if args.speculator in ("auto", "mtp") and getattr(be, "has_mtp", False):
@@ -375,4 +383,7 @@ def run_server(args) -> int:
             time.sleep(3600)
     except KeyboardInterrupt:
         srv.stop()
+        be = state.sched.be
+        if getattr(args, "prewarm", "") and hasattr(be, "save_prewarm"):
+            be.save_prewarm(args.prewarm)        # the next start captures this run's frequent geometries up front
     return 0
