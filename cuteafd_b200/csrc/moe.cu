@@ -280,7 +280,8 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
   __shared__ int wcount_flat[kPlanSlots];
   const int e_stride = (E + 31) & ~31;
   const int lane_id = threadIdx.x & 31, warp_id = threadIdx.x >> 5;
-  const int n_warps = min(static_cast<int>(blockDim.x >> 5), kPlanSlots / e_stride);   // warps that walk entries
+  // warps that walk entries: no more than there are 32-entry groups (a decode step has two or three)
+  const int n_warps = max(1, min(min(static_cast<int>(blockDim.x >> 5), kPlanSlots / e_stride), (n + 31) >> 5));
   auto wcount = [&](int w, int e) -> int& { return wcount_flat[w * e_stride + e]; };
   const int chunk = ((n + n_warps - 1) / n_warps + 31) & ~31;
   const int c_lo = min(n, warp_id * chunk), c_hi = warp_id < n_warps ? min(n, c_lo + chunk) : c_lo;
@@ -396,6 +397,7 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
     }
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
+      if (i0 + k * 32 >= c_hi) break;                     // warp-uniform: nothing left in this chunk
       const int i = i0 + k * 32 + lane_id;
       const bool live = i < c_hi;
       const int e = ev[k];
