@@ -248,6 +248,71 @@ def bench_w4(a, dev, pk):
     assert K.read_status() == 0
 
 
+def bench_exl3(a, dev, pk):
+    """EXL3 trellis GEMM at decode sizes (Hadamard rotations + in-kernel trellis decode + tcgen05)."""
+    from ..quant import codecs
+    T, N, Kd, bits = a.tokens, a.features, a.k, a.bits
+    x = torch.randn(T, Kd, device=dev).bfloat16()
+    copies = max(2, min(16, int(300e6 // (N * Kd * bits // 8)) + 1))
+    g = torch.Generator().manual_seed(0)
+    ws = []
+    for _ in range(copies):
+        t, su, sv = codecs.exl3_random(Kd, N, bits, g)
+        ws.append((t.to(dev), su.to(dev), sv.to(dev)))
+    out = torch.empty(T, N, dtype=torch.bfloat16, device=dev)
+    ms = time_graph([(lambda w=w: K.linear_exl3(x, w[0], w[1], w[2], out=out)) for w in ws] * 2)
+    per = N * Kd * bits // 8 + (N + Kd) * 2
+    report(f"gemm_exl3 k{bits} T={T} N={N} K={Kd}", ms, 2.0 * T * N * Kd, per + (T * Kd + T * N) * 2, pk)
+    assert K.read_status() == 0
+
+
+def bench_gemm_fp8(a, dev, pk):
+    """Block-scaled E4M3 GEMM (128 x 128 weight scales, 1 x 128 activation scales)."""
+    from ..quant import codecs
+    T, N, Kd = a.tokens, a.features, a.k
+    x = torch.randn(T, Kd, device=dev).bfloat16()
+    xq = torch.empty(T, Kd, dtype=torch.float8_e4m3fn, device=dev)
+    xs = torch.empty(T, Kd // 128, dtype=torch.float32, device=dev)
+    K.quant_rows_fp8(x, xq, xs)
+    copies = 1 if T > 256 else max(2, min(24, int(200e6 // (N * Kd)) + 1))
+    ws = []
+    for i in range(copies):
+        q, sc = codecs.fp8_quant_block128(torch.randn(N, Kd, generator=torch.Generator().manual_seed(i)) * 0.05)
+        ws.append((q.to(dev), sc.to(dev)))
+    out = torch.empty(T, N, dtype=torch.bfloat16, device=dev)
+    if T > 256:
+        ms = time_eager(lambda: K.linear_fp8(xq, xs, ws[0][0], ws[0][1], out=out), dev, iters=a.iters)
+    else:
+        ms = time_graph([(lambda w=w: K.linear_fp8(xq, xs, w[0], w[1], out=out)) for w in ws] * 2)
+    report(f"gemm_fp8 T={T} N={N} K={Kd}", ms, 2.0 * T * N * Kd, N * Kd + T * Kd + T * N * 2, pk)
+    assert K.read_status() == 0
+
+
+def bench_indexer(a, dev, pk):
+    """Lightning indexer: scores of every cached position for each query token, then the radix top-k."""
+    heads, S, n, topk = a.heads, a.seqs, a.len, a.topk
+    pps = (n + 63) // 64
+    pages = S * pps + 1
+    kc = torch.randn(pages, 64, 128, device=dev).bfloat16()
+    table = (torch.arange(S * pps, dtype=torch.int32, device=dev) + 1).view(S, pps).contiguous()
+    q = (torch.randn(S, heads, 128, device=dev) * 0.3).bfloat16()
+    hw = torch.rand(S, heads, device=dev).bfloat16()
+    sl = torch.full((S,), n, dtype=torch.int32, device=dev)
+    qs = torch.arange(S + 1, dtype=torch.int32, device=dev)
+    bs, bt = K.mla_blocks([1] * S, heads // 2)
+    i32 = dict(dtype=torch.int32, device=dev)
+    bsd, btd = torch.tensor(bs, **i32), torch.tensor(bt, **i32)
+    ld = ((pps * 64 + 127) // 128) * 128
+    scores = torch.empty(S, ld, dtype=torch.float32, device=dev)
+    sel = torch.empty(S, topk, dtype=torch.int32, device=dev)
+    splits = max(1, min(K.num_sms() // max(1, len(bs)), max(1, (pps + 1) // 4), 64))
+    ms = time_graph([lambda: K.indexer_scores(q, kc, hw, table, sl, qs, bsd, btd, scores, splits, w_scale=heads ** -0.5)] * 6)
+    report(f"indexer_scores seqs={S} len={n} heads={heads} splits={splits}", ms, 2.0 * S * heads * n * 128, S * n * 128 * 2.0, pk)
+    ms2 = time_graph([lambda: K.index_topk(scores, topk, sel, seq_lens=sl, q_start=qs)] * 6)
+    report(f"index_topk seqs={S} len={n} k={topk}", ms2, 0.0, S * n * 4.0, pk)
+    assert K.read_status() == 0
+
+
 def bench_sampler(a, dev, pk):
     from ..runtime.sampling import SamplingParams
     n, V = a.rows, a.vocab
@@ -262,6 +327,15 @@ def bench_sampler(a, dev, pk):
 def main() -> None:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
+    ex = sub.add_parser("exl3")
+    ex.add_argument("--tokens", type=int, default=8); ex.add_argument("--features", type=int, default=7168)
+    ex.add_argument("--k", type=int, default=2048); ex.add_argument("--bits", type=int, default=4)
+    f8 = sub.add_parser("gemm-fp8")
+    f8.add_argument("--tokens", type=int, default=8); f8.add_argument("--features", type=int, default=7168)
+    f8.add_argument("--k", type=int, default=2048); f8.add_argument("--iters", type=int, default=10)
+    ix = sub.add_parser("indexer")
+    ix.add_argument("--seqs", type=int, default=8); ix.add_argument("--len", type=int, default=32768)
+    ix.add_argument("--heads", type=int, default=64); ix.add_argument("--topk", type=int, default=2048)
     g = sub.add_parser("gemm")
     g.add_argument("--tokens", type=int, default=8192); g.add_argument("--features", type=int, default=5120)
     g.add_argument("--k", type=int, default=2048); g.add_argument("--dual", action="store_true")
@@ -295,7 +369,7 @@ def main() -> None:
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     pk = peaks()
-    {"gemm": bench_gemm, "attn-prefill": bench_attn_prefill, "attn-decode": bench_attn_decode, "moe": bench_moe,
+    {"exl3": bench_exl3, "gemm-fp8": bench_gemm_fp8, "indexer": bench_indexer, "gemm": bench_gemm, "attn-prefill": bench_attn_prefill, "attn-decode": bench_attn_decode, "moe": bench_moe,
      "mla": bench_mla, "mla-prefill": bench_mla_prefill_expanded, "w4": bench_w4, "sampler": bench_sampler}[a.cmd](a, dev, pk)
 
 
