@@ -148,8 +148,28 @@ def deepseek_v32() -> ModelConfig:
                                  indexer_dim=128, indexer_topk=2048, weight_format="nvfp4")
 
 
+def mixtral_8x7b() -> ModelConfig:
+    """Mixtral-8x7B geometry (32 layers, GQA 32/8, 8 experts top-2, softmax over the selected pair); served by the
+    GQA engine, tensor names canonicalised by ``loader.families.canonical_name``."""
+    return ModelConfig(
+        name="mixtral-8x7b", family="qwen3_moe", vocab_size=32000, num_layers=32, hidden=4096,
+        attention="gqa", num_heads=32, num_kv_heads=8, head_dim=128, qk_norm=False,
+        rope_theta=1.0e6, rope_interleaved=False, rms_eps=1e-5,
+        dense_ffn=14336, first_dense_layers=0, num_experts=8, expert_ffn=14336, top_k=2,
+        scoring="softmax", num_shared_experts=0, norm_topk_prob=True, weight_format="bf16")
+
+
+def kimi_k2() -> ModelConfig:
+    """Kimi-K2 geometry: the DeepSeek-V3 architecture with 64 heads and 384 routed experts (one dense layer, one
+    routing group); served by the MLA engine."""
+    return deepseek_v3().replace(name="kimi-k2", vocab_size=163840, num_heads=64, first_dense_layers=1, num_experts=384,
+                                 num_groups=1, topk_groups=1, routed_scale=2.827, mtp_layers=0, rope_theta=50000.0)
+
+
 PRESETS = {
     "tiny-moe": tiny_moe,
+    "mixtral-8x7b": mixtral_8x7b,
+    "kimi-k2": kimi_k2,
     "qwen3-30b-a3b": qwen3_30b_a3b,
     "deepseek-v3": deepseek_v3,
     "deepseek-v3.2": deepseek_v32,

@@ -131,6 +131,21 @@ class TinyMoe(Family):
     id, model_types = "tiny_moe", ("tiny_moe",)
 
 
+_ALIASES = ((".block_sparse_moe.gate.", ".mlp.gate."), (".block_sparse_moe.experts.", ".mlp.experts."),
+            (".mlp.shared_expert.", ".mlp.shared_experts."))
+_MIXTRAL_PROJ = {"w1": "gate_proj", "w3": "up_proj", "w2": "down_proj"}
+_MIXTRAL_RE = re.compile(r"(\.mlp\.experts\.\d+\.)(w[123])(\.)")
+
+
+def canonical_name(name: str) -> str:
+    """Checkpoint tensor name -> the name the loaders use.  Mixtral-style files call the MoE block
+    ``block_sparse_moe`` and its projections ``w1 / w3 / w2`` (gate / up / down); Qwen2-MoE says ``shared_expert``."""
+    for a, b in _ALIASES:
+        if a in name:
+            name = name.replace(a, b)
+    return _MIXTRAL_RE.sub(lambda m: m.group(1) + _MIXTRAL_PROJ[m.group(2)] + m.group(3), name)
+
+
 REGISTRY: tuple[Family, ...] = (DeepseekV32(), DeepseekV3(), Qwen3Moe(), TinyMoe())
 
 

@@ -44,7 +44,7 @@ class OpenedSnapshot:
 def open_snapshot(path: str) -> OpenedSnapshot:
     path = resolve(path)
     cfg, hf = read_config(path)
-    cat = Catalog(path)
+    cat = Catalog(path, rename=families.canonical_name)
     ops = formats.detect_operands(cat)
     fam = families.detect(hf)
     model = fam.open(cfg, hf) if fam else None

@@ -59,7 +59,9 @@ def read_header(path: str) -> tuple[dict, int]:
 class Catalog:
     """Every tensor of a snapshot directory by name (headers only)."""
 
-    def __init__(self, directory: str):
+    def __init__(self, directory: str, rename=None):
+        """``rename(name) -> name`` maps a checkpoint's tensor names onto the canonical ones the loaders use (families
+        whose files say ``block_sparse_moe.experts.3.w1`` for ``mlp.experts.3.gate_proj``); nothing is rewritten."""
         self.directory = directory
         self.entries: dict[str, TensorEntry] = {}
         self.metadata: dict[str, dict] = {}
@@ -74,6 +76,7 @@ class Catalog:
                 b, e = info["data_offsets"]
                 if info["dtype"] not in DTYPES:
                     raise ValueError(f"{fn}:{name}: unsupported dtype {info['dtype']}")
+                name = rename(name) if rename else name
                 self.entries[name] = TensorEntry(name, info["dtype"], tuple(info["shape"]), path, base + b, base + e)
         self._maps: dict[str, mmap.mmap] = {}
 

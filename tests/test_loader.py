@@ -128,3 +128,50 @@ def test_hf_config_roundtrip():
         for f in ("hidden", "num_layers", "num_heads", "num_experts", "top_k", "expert_ffn", "attention", "scoring",
                   "num_groups", "topk_groups", "first_dense_layers", "mtp_layers", "indexer_heads", "weight_format"):
             assert getattr(back, f) == getattr(cfg, f), (cfg.name, f)
+
+
+def test_mixtral_style_names_are_canonicalised(tmp_path):
+    """A checkpoint that names its MoE block ``block_sparse_moe`` and its projections w1 / w3 / w2 loads like any other:
+    the catalogue shows canonical names, the operands classify as routed experts, the oracle gives the same logits."""
+    from cuteafd_b200.loader.safetensors_io import write_sharded
+    from cuteafd_b200.ref.model import KvState, RefDecoder, init_weights
+    cfg = tiny_moe().replace(family="qwen3_moe", attention="gqa", num_heads=2, num_kv_heads=2, head_dim=64, hidden=128,
+                             expert_ffn=128, dense_ffn=128, num_experts=4, top_k=2, vocab_size=256, num_shared_experts=0,
+                             scoring="softmax", first_dense_layers=0, qk_norm=False)
+    params = init_weights(cfg, seed=5)
+    proj = {"gate_proj": "w1", "up_proj": "w3", "down_proj": "w2"}
+    renamed = {}
+    for k, v in params.items():
+        k2 = k.replace(".mlp.gate.", ".block_sparse_moe.gate.")
+        if ".mlp.experts." in k2:
+            k2 = k2.replace(".mlp.experts.", ".block_sparse_moe.experts.")
+            for a, b in proj.items():
+                k2 = k2.replace("." + a + ".", "." + b + ".")
+        renamed[k2] = v.to(torch.bfloat16)
+    assert any(".block_sparse_moe.experts.0.w1.weight" in k for k in renamed)
+    d = str(tmp_path / "mixtral")
+    os.makedirs(d)
+    hf = snapshot.to_hf_config(cfg)
+    hf.update(model_type="mixtral", num_local_experts=cfg.num_experts)
+    hf.pop("num_experts", None); hf.pop("qk_norm", None)
+    json.dump(hf, open(os.path.join(d, "config.json"), "w"))
+    write_sharded(d, renamed, 1 << 20)
+    snap = load.open_snapshot(d)
+    assert snap.family is not None and snap.family.id == "qwen3_moe" and snap.cfg.num_experts == 4 and not snap.cfg.qk_norm
+    op = snap.operands["model.layers.1.mlp.experts.2.up_proj"]
+    assert snap.model.classify(op.weight) == ("routed_expert", 1, 2) and snap.hints() == []
+    cfg2, loaded = load.load_params(d)
+    toks = torch.arange(9) % cfg.vocab_size
+    want = RefDecoder(cfg, {k: v.to(torch.bfloat16).float() for k, v in params.items()}).forward(toks, KvState(cfg))
+    got = RefDecoder(cfg2, loaded).forward(toks, KvState(cfg2))
+    assert torch.allclose(got, want, atol=1e-4)
+
+
+def test_new_presets_are_consistent():
+    from cuteafd_b200 import PRESETS, kimi_k2, mixtral_8x7b
+    m, k = mixtral_8x7b(), kimi_k2()
+    assert PRESETS["mixtral-8x7b"]().num_experts == 8 and m.head_dim * m.num_heads == m.hidden
+    assert k.is_mla and k.num_experts == 384 and 128 % k.num_heads == 0
+    for cfg in (m, k):
+        back = snapshot.from_hf_config(snapshot.to_hf_config(cfg))
+        assert back.num_experts == cfg.num_experts and back.num_heads == cfg.num_heads and back.attention == cfg.attention
