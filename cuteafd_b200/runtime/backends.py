@@ -102,6 +102,10 @@ class OracleBackend:
         h.seq.kv_len += len(tokens)
         return self.model.head(hid[-1:]) if last else None
 
+    def prefill_packed(self, items: list) -> list:
+        """[(handle, tokens, last)] -> logits of the last row for the items that end their prompt, else None."""
+        return [self.prefill(h, toks, last) for h, toks, last in items]
+
     def verify(self, handles: list[_Handle], rows: list[list[int]]) -> torch.Tensor:
         self.steps += 1
         if self.fail_on_step is not None and self.steps == self.fail_on_step:
@@ -135,6 +139,11 @@ class OracleBackend:
 
     def pages_of(self, h: _Handle) -> int:
         return len(h.seq.pages)
+
+
+def pt_dev(b, max_pages: int) -> torch.Tensor:
+    """Device page table of a ``StepBuffers`` as [max_seqs, max_pages]."""
+    return b.page_table[1].view(b.max_seqs, max_pages)
 
 
 class EngineBackend:
@@ -217,6 +226,58 @@ class EngineBackend:
         seq.tokens.extend(tokens)
         seq.kv_len = start + n
         return logits[:1].float().cpu() if last else None
+
+    def prefill_packed(self, items: list) -> list:
+        """Chunks of several prompts in one forward step: [(handle, tokens, last)] -> per item the fp32 logits of its
+        last row when ``last`` (on the host), else None.  Media rows and the MTP fill work as in ``prefill``."""
+        from ..models.gqa_moe import Batch
+        from ..media.processor import overrides_for
+        from .generate import StepBuffers
+        S, T = len(items), sum(len(t) for _, t, _ in items)
+        if getattr(self, "_pack_bufs", None) is None:
+            self._pack_bufs = StepBuffers(self.prefill_chunk, 16, self.max_pages, self.engine.device)
+        b = self._pack_bufs
+        assert S <= b.max_seqs and T <= b.max_tokens
+        V = self.vocab_size
+        pt = b.page_table[0].view(b.max_seqs, self.max_pages)
+        o, rows, vals, nxt = 0, [], [], []
+        for i, (h, toks, _) in enumerate(items):
+            seq = h.seq
+            start, n = seq.kv_len, len(toks)
+            self.table.reserve(seq, start + n, copy_page=self._copy_page)
+            if any(t >= V for t in toks):
+                ov = overrides_for(getattr(h, "media", None), start, n)
+                if ov is None or len(ov[0]) != sum(t >= V for t in toks):
+                    raise ValueError("media rows in the prompt without their embeddings")
+                rows += [o + r for r in ov[0]]
+                vals.append(ov[1])
+            b.tokens[0][o:o + n] = torch.tensor([t if t < V else 0 for t in toks], dtype=torch.int32)
+            b.positions[0][o:o + n] = torch.arange(start, start + n, dtype=torch.int32)
+            b.slots[0][o:o + n] = torch.tensor(self.table.slots(seq, start, n), dtype=torch.int32)
+            pt[i].zero_()
+            pt[i, :len(seq.pages)] = torch.tensor(seq.pages, dtype=torch.int32)
+            b.seq_lens[0][i] = start + n
+            b.q_start[0][i] = o
+            b.last_rows[0][i] = o + n - 1
+            nxt += toks[1:] + toks[-1:]
+            o += n
+        b.q_start[0][S] = T
+        b.upload()
+        batch = Batch(b.tokens[1][:T], b.positions[1][:T], b.slots[1][:T], pt_dev(b, self.max_pages)[:S], b.seq_lens[1][:S],
+                      b.q_start[1][:S + 1], max(len(t) for _, t, _ in items), True, b.last_rows[1][:S], fresh=False)
+        if rows:
+            dev = self.engine.device
+            batch.embeds = (torch.tensor(rows, dtype=torch.long).to(dev), torch.cat(vals).to(dev, torch.bfloat16))
+        logits = self.engine.forward(batch)
+        if self.has_mtp:
+            self.engine.mtp_forward(0, batch, torch.tensor([t if t < V else 0 for t in nxt], dtype=torch.int32).to(self.engine.device))
+        host = logits[:S].float().cpu() if any(last for _, _, last in items) else None
+        out = []
+        for i, (h, toks, last) in enumerate(items):
+            h.seq.tokens.extend(toks)
+            h.seq.kv_len += len(toks)
+            out.append(host[i:i + 1] if last else None)
+        return out
 
     # ---- decode graph bank ------------------------------------------------------------------------------
     def _step_batch(self, key: tuple[int, int, int]):

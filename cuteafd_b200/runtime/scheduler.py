@@ -79,6 +79,7 @@ class Active:
 @dataclass
 class SchedulerStats:
     admitted: int = 0
+    packed_steps: int = 0              # prefill steps that carried chunks of more than one prompt
     finished: int = 0
     failed: int = 0
     rejected: int = 0
@@ -168,7 +169,7 @@ class Scheduler:
             do_prefill = bool(self.prefilling)
         t0 = time.monotonic()
         if do_prefill:
-            did = self._prefill_one()
+            did = self._prefill_packed() if len(self.prefilling) > 1 and hasattr(self.be, "prefill_packed") else self._prefill_one()
             self._t_prefill = 0.9 * self._t_prefill + (time.monotonic() - t0)
             self._t_decode *= 0.9
         elif self.decoding:
@@ -225,6 +226,50 @@ class Scheduler:
             self.stats.cached_tokens += cached
 
     # ---- prefill -----------------------------------------------------------------------------------
+    PACK_MAX = 8                       # prompts whose chunks may share one prefill step
+
+    def _prefill_packed(self) -> bool:
+        """Several short prompts in one forward step: the head request's chunk plus whole chunks of the requests
+        behind it while the token budget of a step lasts.  Counterpart: the reference's prefill packing
+        (rust/crates/cuteafd-daemon/src/shared/prefill_pipeline.rs)."""
+        budget = self.be.prefill_chunk
+        group, used = [], 0
+        for a in self.prefilling[: self.PACK_MAX]:
+            if a.req.cancelled.is_set():
+                break
+            n = min(budget - used, len(a.req.prompt) - a.prompt_done)
+            if n <= 0 or (group and n < len(a.req.prompt) - a.prompt_done and n < 64):
+                break                                   # no sliver chunks for the requests behind the head
+            group.append((a, n))
+            used += n
+            if used >= budget:
+                break
+        if len(group) < 2:
+            return self._prefill_one()
+        items = [(a.handle, a.req.prompt[a.prompt_done:a.prompt_done + n], a.prompt_done + n == len(a.req.prompt)) for a, n in group]
+        try:
+            outs = self.be.prefill_packed(items)
+        except Exception as e:
+            for a, _ in group:
+                self.prefilling.remove(a)
+            self._fail([a for a, _ in group], f"prefill failed: {e}")
+            return True
+        self.stats.packed_steps += 1
+        for (a, n), (_, _, last), logits in zip(group, items, outs):
+            a.prompt_done += n
+            a.kv_len = a.prompt_done
+            self.stats.prefill_tokens += n
+            if last:
+                self.prefilling.remove(a)
+                self._safe(lambda a=a: self.be.capture(a.handle, "prompt"))
+                tok = self._select(a, logits[0] if logits.dim() == 2 else logits, len(a.req.prompt))
+                a.first_token_at = time.monotonic()
+                if tok is None:
+                    continue
+                if not self._emit(a, [tok]):
+                    self.decoding.append(a)
+        return True
+
     def _prefill_one(self) -> bool:
         a = self.prefilling[0]
         if a.req.cancelled.is_set():

@@ -209,3 +209,42 @@ def test_decode_graph_bank_and_prewarm(tmp_path):
     warm, be2 = run(True, prewarm=keys)
     assert warm == eager
     assert be2.graph_stats["captures"] >= len(keys) and be2.graph_stats["eager"] < be1.graph_stats["eager"] + 1
+
+
+def test_prompt_packing_on_the_engine():
+    """Chunks of several prompts in one engine step (multi-sequence prefill batch) give the tokens of serving the
+    prompts one at a time."""
+    from cuteafd_b200.ops import kernels as K
+    from cuteafd_b200.runtime.backends import EngineBackend
+    from cuteafd_b200.runtime.scheduler import Request, Scheduler
+    cfg = small_cfg()
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (30, 70, 9, 100)]
+
+    def serve(max_active):
+        _, eng, _ = build(cfg, False)
+        be = EngineBackend(eng, 64, 8, prefill_chunk=128, max_decode_rows=4, use_graphs=False)
+        sched = Scheduler(be, max_active=max_active)
+        reqs = [Request(prompt=list(p), max_tokens=6, speculation=False) for p in prompts]
+        for r in reqs:
+            sched.submit(r)
+        out = [[] for _ in reqs]
+        for _ in range(400):
+            sched.step()
+            for i, r in enumerate(reqs):
+                while not r.events.empty():
+                    ev = r.events.get()
+                    if ev[0] == "tokens":
+                        out[i] += ev[1]
+                    assert ev[0] != "error", ev
+            if sched.stats.finished == len(reqs):
+                break
+        torch.cuda.synchronize()
+        assert K.read_status() == 0 and sched.stats.finished == len(reqs)
+        return out, sched.stats.packed_steps
+    alone, p1 = serve(1)
+    packed, p4 = serve(4)
+    assert p1 == 0 and p4 >= 1
+    # batched and single-sequence kernels round alike here (same tiles per sequence); allow a late divergence only
+    same = sum(a[:3] == b[:3] for a, b in zip(alone, packed))
+    assert same == len(prompts), (alone, packed)

@@ -308,3 +308,36 @@ def test_agentic_prefix_workload_on_the_oracle():
               sessions=3, prefix=192, turns=3, append=24, decode=6, verify=3, concurrency=3)
     assert out["cache_share"] > 0.5 and out["restore_mismatches"] == 0 and out["cold_token_mismatches"] == 0
     assert out["emitted_tokens"] == 3 * 3 * 6
+
+
+def test_prompt_packing_matches_one_at_a_time():
+    """Short prompts that wait together share prefill steps; the generated tokens are those of serving them alone."""
+    from cuteafd_b200 import tiny_moe
+    from cuteafd_b200.ref.model import init_weights
+    from cuteafd_b200.runtime.backends import OracleBackend
+    from cuteafd_b200.runtime.scheduler import Request, Scheduler
+    cfg = tiny_moe()
+    params = init_weights(cfg, seed=0)
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 21, 5, 40, 13)]
+
+    def serve(max_active):
+        sched = Scheduler(OracleBackend(cfg, params, prefill_chunk=64), max_active=max_active)
+        reqs = [Request(prompt=list(p), max_tokens=5, speculation=False) for p in prompts]
+        for r in reqs:
+            sched.submit(r)
+        out = [[] for _ in reqs]
+        for _ in range(500):
+            sched.step()
+            for i, r in enumerate(reqs):
+                while not r.events.empty():
+                    ev = r.events.get()
+                    if ev[0] == "tokens":
+                        out[i] += ev[1]
+            if sched.stats.finished == len(reqs):
+                break
+        assert sched.stats.finished == len(reqs)
+        return out, sched.stats.packed_steps
+    alone, p1 = serve(1)
+    packed, p5 = serve(5)
+    assert alone == packed and p1 == 0 and p5 >= 1
