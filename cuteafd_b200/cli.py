@@ -196,6 +196,8 @@ def build_parser() -> argparse.ArgumentParser:
     gw = sub.add_parser("gateway", help="protocol gateway in front of an OpenAI-compatible upstream")
     gw.add_argument("--upstream", default="http://127.0.0.1:8000"); gw.add_argument("--host", default="127.0.0.1")
     gw.add_argument("--port", type=int, default=8080); gw.add_argument("--model-map", default="")
+    gw.add_argument("--record", default="", help="append every upstream exchange to this JSONL file")
+    gw.add_argument("--replay", default="", help="answer from a recorded JSONL file, never contacting the upstream")
     gw.set_defaults(fn=cmd_gateway)
 
     q = sub.add_parser("quantize", help="re-encode a snapshot into a serving format (per-role recipe)")

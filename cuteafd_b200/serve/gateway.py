@@ -61,7 +61,44 @@ def from_chat_reply(reply: dict, flavor: str, model: str) -> dict:
     return api.responses_object(model, text, ch.get("finish_reason", "stop"), usage)
 
 
-def make_gateway(upstream: str, model_map: dict[str, str]):
+class Tape:
+    """Record / replay of upstream exchanges.  ``record``: every forwarded request body and the reply it got are appended
+    to a JSONL file.  ``replay``: replies come from the file, matched by the hash of the forwarded body, and the
+    upstream is never contacted (client tests and demos without an engine).  Counterpart: the gateway's record/replay
+    mode (rust/crates/cuteafd-api/src/gateway/mod.rs)."""
+
+    def __init__(self, path: str, mode: str):
+        assert mode in ("record", "replay")
+        self.path, self.mode = path, mode
+        self.lock = threading.Lock()
+        self.replies: dict[str, list] = {}
+        if mode == "replay":
+            with open(path) as f:
+                for line in f:
+                    rec = json.loads(line)
+                    self.replies.setdefault(rec["key"], []).append(rec)
+
+    @staticmethod
+    def key(path: str, body: dict) -> str:
+        import hashlib
+        return hashlib.sha256((path + "\n" + json.dumps(body, sort_keys=True)).encode()).hexdigest()
+
+    def store(self, path: str, body: dict, status: int, reply: dict) -> None:
+        with self.lock, open(self.path, "a") as f:
+            f.write(json.dumps({"key": self.key(path, body), "path": path, "request": body, "status": status, "reply": reply}) + "\n")
+
+    def fetch(self, path: str, body: dict):
+        """(status, reply) of the recorded exchange; repeated identical requests walk their recordings in order and
+        stay on the last one."""
+        with self.lock:
+            recs = self.replies.get(self.key(path, body))
+            if not recs:
+                return None
+            rec = recs.pop(0) if len(recs) > 1 else recs[0]
+        return rec["status"], rec["reply"]
+
+
+def make_gateway(upstream: str, model_map: dict[str, str], tape: "Tape | None" = None):
     class H(BaseHTTPRequestHandler):
         protocol_version = "HTTP/1.1"
 
@@ -93,6 +130,13 @@ def make_gateway(upstream: str, model_map: dict[str, str]):
             except json.JSONDecodeError:
                 return self._json(400, {"error": {"message": "invalid JSON"}})
             fwd = to_chat_body(body, flavor, model_map) if flavor else body
+            fpath = "/v1/chat/completions" if flavor else self.path
+            if tape is not None and tape.mode == "replay":
+                hit = tape.fetch(fpath, fwd)
+                if hit is None:
+                    return self._json(404, {"error": {"message": "no recorded exchange for this request", "type": "replay_miss"}})
+                st, reply = hit
+                return self._json(st, from_chat_reply(reply, flavor, body.get("model", "")) if (flavor and st == 200) else reply)
             req = urllib.request.Request(upstream + ("/v1/chat/completions" if flavor else self.path), json.dumps(fwd).encode(),
                                          {"Content-Type": "application/json", "Authorization": self.headers.get("Authorization", "")})
             try:
@@ -103,14 +147,17 @@ def make_gateway(upstream: str, model_map: dict[str, str]):
                 return self._json(e.code, json.loads(e.read() or b"{}"), hd)
             except urllib.error.URLError as e:
                 return self._json(503, {"error": {"message": f"upstream unavailable: {e}"}})
+            if tape is not None:
+                tape.store(fpath, fwd, 200, reply)
             return self._json(200, from_chat_reply(reply, flavor, body.get("model", "")) if flavor else reply)
 
     return H
 
 
 class Gateway:
-    def __init__(self, upstream: str, host: str = "127.0.0.1", port: int = 0, model_map: dict[str, str] | None = None):
-        self.httpd = ThreadingHTTPServer((host, port), make_gateway(upstream.rstrip("/"), model_map or {}))
+    def __init__(self, upstream: str, host: str = "127.0.0.1", port: int = 0, model_map: dict[str, str] | None = None,
+                 tape: Tape | None = None):
+        self.httpd = ThreadingHTTPServer((host, port), make_gateway(upstream.rstrip("/"), model_map or {}, tape))
         self.httpd.daemon_threads = True
         self.port = self.httpd.server_address[1]
         self.thread = threading.Thread(target=self.httpd.serve_forever, daemon=True)
@@ -127,7 +174,12 @@ class Gateway:
 def run_gateway(args) -> int:
     import time
     mm = dict(kv.split("=", 1) for kv in args.model_map.split(",") if "=" in kv)
-    gw = Gateway(args.upstream, args.host, args.port, mm).start()
+    tape = None
+    if getattr(args, "record", ""):
+        tape = Tape(args.record, "record")
+    elif getattr(args, "replay", ""):
+        tape = Tape(args.replay, "replay")
+    gw = Gateway(args.upstream, args.host, args.port, mm, tape).start()
     print(f"gateway on http://{args.host}:{gw.port} -> {args.upstream}", flush=True)
     try:
         while True:

@@ -142,6 +142,34 @@ def test_gateway_translates(server):
         gw.stop()
 
 
+def test_gateway_record_and_replay(server, tmp_path):
+    from cuteafd_b200.serve.gateway import Tape
+    path = str(tmp_path / "tape.jsonl")
+    body = {"model": "claude-x", "messages": [{"role": "user", "content": "hey"}], "max_tokens": 4, "temperature": 0}
+    hdr = {"Content-Type": "application/json", "Authorization": "Bearer sekret"}
+
+    def ask(gw, b):
+        c = http.client.HTTPConnection("127.0.0.1", gw.port, timeout=120)
+        c.request("POST", "/v1/messages", json.dumps(b), hdr)
+        r = c.getresponse()
+        return r.status, json.loads(r.read())
+    gw = Gateway(f"http://127.0.0.1:{server.port}", model_map={"claude-x": "tiny-moe"}, tape=Tape(path, "record")).start()
+    try:
+        st, live = ask(gw, body)
+        assert st == 200
+    finally:
+        gw.stop()
+    assert len(open(path).read().splitlines()) == 1
+    gw2 = Gateway("http://127.0.0.1:9", model_map={"claude-x": "tiny-moe"}, tape=Tape(path, "replay")).start()    # dead upstream
+    try:
+        st, again = ask(gw2, body)
+        assert st == 200 and again["content"] == live["content"] and again["usage"] == live["usage"]
+        st, miss = ask(gw2, dict(body, max_tokens=5))
+        assert st == 404 and miss["error"]["type"] == "replay_miss"
+    finally:
+        gw2.stop()
+
+
 def test_recognizers_and_tokenizer():
     r = constraints.JsonRecognizer()
     for b in b'{"a": [1, 2.5e3, true, null, "x\\n\\u00e9"], "b": {"c": -0}}':
