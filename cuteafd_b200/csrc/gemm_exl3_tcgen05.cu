@@ -37,6 +37,7 @@ struct Exl3Dev {
   float* out;                // y' [x_rows, ldo] fp32
   uint32_t* status;
   int bits, k, n, num_k_blocks, x_rows, ldo, w_tiles, x_tiles;
+  long long plane;              // floats between the split-K planes of the raw product
 };
 
 template <int kBX>
@@ -85,6 +86,10 @@ gemm_exl3_kernel(const __grid_constant__ CUtensorMap tm_x, const Exl3Dev p) {
   pdl_trigger();
   const uint32_t tmem_base = tmem_base_slot;
   const int total_tiles = p.x_tiles * p.w_tiles, nkb = p.num_k_blocks;
+  // split K: grid.y CTAs share a tile's K range; each writes its own fp32 plane, the output kernel adds the planes in
+  // order (decode-sized calls have fewer 128-feature tiles than the GPU has SMs)
+  const int kb0 = static_cast<int>(blockIdx.y) * nkb / static_cast<int>(gridDim.y);
+  const int kb1 = (static_cast<int>(blockIdx.y) + 1) * nkb / static_cast<int>(gridDim.y);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -92,7 +97,7 @@ gemm_exl3_kernel(const __grid_constant__ CUtensorMap tm_x, const Exl3Dev p) {
       int stage = 0; uint32_t phase = 0; bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         const int x_row0 = (tile % p.x_tiles) * kBX;
-        for (int kb = 0; kb < nkb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
           uint8_t* sx = smem + stage * Cfg::kStageBytes + kXWBytes;
           mbar_expect_tx(&full_bar[stage], Cfg::kXBytes);
@@ -110,7 +115,7 @@ gemm_exl3_kernel(const __grid_constant__ CUtensorMap tm_x, const Exl3Dev p) {
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, p.status, kTimeoutTmemEmpty)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d0 = tmem_base + acc * kBX;
-        for (int kb = 0; kb < nkb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, p.status, kTimeoutFullBarrier)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sw = smem_u32(smem + stage * Cfg::kStageBytes), sx = sw + kXWBytes;
@@ -119,7 +124,7 @@ gemm_exl3_kernel(const __grid_constant__ CUtensorMap tm_x, const Exl3Dev p) {
 #pragma unroll
             for (int k4 = 0; k4 < 4; ++k4)
               umma_f16(d0, smem_desc_k_sw128(sw + a * (kXRows * 128) + k4 * 32), smem_desc_k_sw128(sx + a * (kBX * 128) + k4 * 32),
-                       idesc, (kb | a | k4) ? 1u : 0u);
+                       idesc, ((kb - kb0) | a | k4) ? 1u : 0u);
           umma_commit(&empty_bar[stage]);
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
         }
@@ -143,25 +148,29 @@ gemm_exl3_kernel(const __grid_constant__ CUtensorMap tm_x, const Exl3Dev p) {
     int stage = 0; uint32_t phase = 0; bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
       const int wt = tile / p.x_tiles;
-      for (int kb = 0; kb < nkb; ++kb) {
+      for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
         uint8_t* st = smem + stage * Cfg::kStageBytes;
 #pragma unroll 1
         for (int tcol = 0; tcol < 2; ++tcol) {
           const int nt = wt * 8 + dw * 2 + tcol;          // global tile column
           const bool live = nt < nt_total;
-#pragma unroll 2
-          for (int kt = 0; kt < 8; ++kt) {
-            uint32_t w[4] = {0u, 0u, 0u, 0u};
-            if (live) {
-              const uint32_t* src = p.trellis + (static_cast<size_t>(kb * 8 + kt) * nt_total + nt) * words;
+          // all eight tile rows' words first (32 loads in flight per lane), then the decode: the loads of one row no
+          // longer wait behind the arithmetic of the previous one
+          uint32_t wv[8][4];
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                int m = m0 + q;
-                if (m >= words) m -= words;
-                w[q] = __ldg(src + m);
-              }
+          for (int kt = 0; kt < 8; ++kt) {
+            const uint32_t* src = p.trellis + (static_cast<size_t>(kb * 8 + kt) * nt_total + (live ? nt : 0)) * words;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              int m = m0 + q;
+              if (m >= words) m -= words;
+              wv[kt][q] = live ? __ldg(src + m) : 0u;
             }
+          }
+#pragma unroll
+          for (int kt = 0; kt < 8; ++kt) {
+            const uint32_t* w = wv[kt];
             uint32_t code[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -205,7 +214,8 @@ gemm_exl3_kernel(const __grid_constant__ CUtensorMap tm_x, const Exl3Dev p) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int row = xt * kBX + c0 + j;
-          if (row < p.x_rows && f < p.n) p.out[static_cast<size_t>(row) * p.ldo + f] = __uint_as_float(rr[j]);
+          if (row < p.x_rows && f < p.n)
+            p.out[static_cast<size_t>(blockIdx.y) * p.plane + static_cast<size_t>(row) * p.ldo + f] = __uint_as_float(rr[j]);
         }
       }
       tc_fence_before();
@@ -256,7 +266,7 @@ __global__ void exl3_pre_kernel(const __nv_bfloat16* __restrict__ x, int ldx, co
 }
 
 // y' [T, N] fp32 -> y = H128(y') * svh, bf16 (+ optional residual, same layout as out).
-__global__ void exl3_post_kernel(const float* __restrict__ y, int ldy, const __half* __restrict__ svh,
+__global__ void exl3_post_kernel(const float* __restrict__ y, int ldy, int splits, long long plane, const __half* __restrict__ svh,
                                  const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out, int ldo, int T, int N) {
   pdl_wait();
   pdl_trigger();
@@ -265,7 +275,11 @@ __global__ void exl3_post_kernel(const float* __restrict__ y, int ldy, const __h
   if (gw >= T * blocks) return;
   const int t = gw / blocks, b = gw % blocks, n0 = b * 128 + lane * 4;
   float v[4];
-  const float4 in = *reinterpret_cast<const float4*>(y + static_cast<size_t>(t) * ldy + n0);
+  float4 in = *reinterpret_cast<const float4*>(y + static_cast<size_t>(t) * ldy + n0);
+  for (int sp = 1; sp < splits; ++sp) {          // split-K planes, fixed order
+    const float4 more = *reinterpret_cast<const float4*>(y + sp * plane + static_cast<size_t>(t) * ldy + n0);
+    in.x += more.x; in.y += more.y; in.z += more.z; in.w += more.w;
+  }
   v[0] = in.x; v[1] = in.y; v[2] = in.z; v[3] = in.w;
   hadamard128_warp(v);
 #pragma unroll
@@ -281,7 +295,7 @@ __global__ void exl3_post_kernel(const float* __restrict__ y, int ldy, const __h
 
 template <int kBX>
 static int launch_exl3(const void* xh, const void* trellis, float* yraw, uint32_t* status, int T, int K, int N, int bits, int sms,
-                       cudaStream_t stream) {
+                       int splits, long long plane, cudaStream_t stream) {
   using Cfg = Exl3Cfg<kBX>;
   CUtensorMap tx;
   int rc = cached_tmap_2d(&tx, xh, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, T, K, static_cast<uint64_t>(K) * 2, kBX, 64);
@@ -289,6 +303,7 @@ static int launch_exl3(const void* xh, const void* trellis, float* yraw, uint32_
   Exl3Dev p;
   p.trellis = static_cast<const uint32_t*>(trellis);
   p.out = yraw; p.status = status; p.bits = bits; p.k = K; p.n = N; p.num_k_blocks = K / kXBK; p.x_rows = T; p.ldo = N;
+  p.plane = plane;
   p.w_tiles = (N + kXRows - 1) / kXRows;
   p.x_tiles = (T + kBX - 1) / kBX;
   int grid = p.w_tiles * p.x_tiles < sms ? p.w_tiles * p.x_tiles : sms;
@@ -298,7 +313,7 @@ static int launch_exl3(const void* xh, const void* trellis, float* yraw, uint32_
     CAFD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr = true;
   }
-  launch_pdl(kern, dim3(grid), dim3(kXThreads), Cfg::kSmemBytes, stream, tx, p);
+  launch_pdl(kern, dim3(grid, splits), dim3(kXThreads), Cfg::kSmemBytes, stream, tx, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -323,16 +338,25 @@ extern "C" int cafd_gemm_exl3(const void* x, int ldx, const void* trellis, const
   const int warps_pre = T * (K / 128), warps_post = T * (N / 128);
   launch_pdl(exl3_pre_kernel, dim3((warps_pre + 7) / 8), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), ldx,
              static_cast<const __half*>(suh), static_cast<__half*>(xh), T, K);
+  // split K while the 128-feature tiles alone leave SMs idle; the scratch holds 128 rows, so T rows allow 128 / T planes
+  const int tiles = ((N + 127) / 128) * ((T + bx - 1) / bx);
+  const int rows16 = ((T + 15) / 16) * 16;
+  int splits = sms / (tiles > 0 ? tiles : 1);
+  if (splits > 128 / rows16) splits = 128 / rows16;
+  if (splits > (K / 128) / 2) splits = (K / 128) / 2;
+  if (splits > 8) splits = 8;
+  if (splits < 1) splits = 1;
+  const long long plane = static_cast<long long>(rows16) * N;
   int rc;
   switch (bx) {
-    case 16: rc = launch_exl3<16>(xh, trellis, yraw, status, T, K, N, bits, sms, stream); break;
-    case 32: rc = launch_exl3<32>(xh, trellis, yraw, status, T, K, N, bits, sms, stream); break;
-    case 64: rc = launch_exl3<64>(xh, trellis, yraw, status, T, K, N, bits, sms, stream); break;
-    case 128: rc = launch_exl3<128>(xh, trellis, yraw, status, T, K, N, bits, sms, stream); break;
+    case 16: rc = launch_exl3<16>(xh, trellis, yraw, status, T, K, N, bits, sms, splits, plane, stream); break;
+    case 32: rc = launch_exl3<32>(xh, trellis, yraw, status, T, K, N, bits, sms, splits, plane, stream); break;
+    case 64: rc = launch_exl3<64>(xh, trellis, yraw, status, T, K, N, bits, sms, splits, plane, stream); break;
+    case 128: rc = launch_exl3<128>(xh, trellis, yraw, status, T, K, N, bits, sms, splits, plane, stream); break;
     default: return -12;
   }
   if (rc) return rc;
-  launch_pdl(exl3_post_kernel, dim3((warps_post + 7) / 8), dim3(256), 0, stream, static_cast<const float*>(yraw), N,
+  launch_pdl(exl3_post_kernel, dim3((warps_post + 7) / 8), dim3(256), 0, stream, static_cast<const float*>(yraw), N, splits, plane,
              static_cast<const __half*>(svh), static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(out), ldo, T, N);
   return static_cast<int>(cudaGetLastError());
 }
