@@ -99,6 +99,7 @@ class Placement:
     decode_lanes: int
     notes: list[str] = field(default_factory=list)
     score: float = 0.0
+    engine: str = ""                   # which engine serves this layout today ("" = none yet, see the last note)
 
     def to_json(self) -> dict:
         d = asdict(self)
@@ -254,6 +255,21 @@ def _place(req: PlacementRequest, att: int, exp: int, pp: int) -> Placement:
                      req.decode_lanes, notes, score=1.0 / max(step, 1.0))
 
 
+def engine_for(cfg: ModelConfig, att: int, exp: int, pp: int) -> tuple[str, str]:
+    """(engine that serves the layout, note).  The solver sizes any (attention TP, expert EP, stages) split; this names
+    the code path that runs it, so a plan never silently proposes a layout nothing can execute."""
+    if pp > 1:
+        return "", "pipeline stages: the hop exists (parallel/pp.py) but no engine runs layer ranges yet"
+    if att == 1:
+        return ("afd", "attention on one GPU, routed experts on the others (parallel/afd.py)") if exp else \
+               ("single", "attention and experts on one GPU")
+    if exp == 0 and not cfg.is_mla and cfg.num_kv_heads % att == 0:
+        return "tp", "heads split over the GPUs, residual rows sharded, experts replicated (models/tp_gqa.py)"
+    if exp == 0:
+        return "", "tensor-parallel attention is wired for the GQA family with kv heads divisible by the degree"
+    return "", "tensor-parallel attention ranks in front of the expert exchange are not wired yet"
+
+
 def candidates(req: PlacementRequest) -> list[tuple[int, int, int]]:
     cfg = req.cfg
     out = []
@@ -279,7 +295,10 @@ def solve(req: PlacementRequest) -> Placement:
     fail: Placement | None = None
     for a, e, pp in candidates(req):
         p = _place(req, a, e, pp)
-        if p.ok and (best is None or p.score > best.score):
+        p.engine, why = engine_for(req.cfg, a, e, pp)
+        p.notes.append(("served by: " if p.engine else "not served yet: ") + why)
+        # a layout an engine runs today wins over a faster-looking one that nothing executes
+        if p.ok and (best is None or (bool(p.engine), p.score) > (bool(best.engine), best.score)):
             best = p
         elif not p.ok and fail is None:
             fail = p
@@ -292,4 +311,7 @@ def solve(req: PlacementRequest) -> Placement:
 
 def solve_frozen(req: PlacementRequest, attention_ranks: int, expert_ranks: int, pipeline_stages: int = 1) -> Placement:
     """Re-check a layout decided earlier (runtime admission against the planned baseline)."""
-    return _place(req, attention_ranks, expert_ranks, pipeline_stages)
+    p = _place(req, attention_ranks, expert_ranks, pipeline_stages)
+    p.engine, why = engine_for(req.cfg, attention_ranks, expert_ranks, pipeline_stages)
+    p.notes.append(("served by: " if p.engine else "not served yet: ") + why)
+    return p

@@ -74,3 +74,18 @@ def test_config_file_refuses_unknown_keys(tmp_path):
     with pytest.raises(SystemExit) as e:
         load_config_file(str(f), ["NOPE=1"], {"GPUS", "POOL_TOKENS"})
     assert e.value.code == 2
+
+
+def test_plan_names_the_engine_that_serves_it():
+    from cuteafd_b200 import deepseek_v3, qwen3_30b_a3b
+    from cuteafd_b200.planner.solver import PlacementRequest, engine_for, solve, solve_frozen
+    q, d = qwen3_30b_a3b(), deepseek_v3()
+    assert engine_for(q, 1, 7, 1)[0] == "afd" and engine_for(q, 1, 0, 1)[0] == "single"
+    assert engine_for(q, 4, 0, 1)[0] == "tp" and engine_for(q, 8, 0, 1)[0] == ""        # 4 kv heads
+    assert engine_for(d, 2, 6, 1)[0] == "" and engine_for(d, 2, 0, 1)[0] == "" and engine_for(q, 1, 3, 2)[0] == ""
+    best = solve(PlacementRequest(cfg=d, gpus=8))
+    assert best.ok and best.engine == "afd" and best.attention_ranks == 1 and best.expert_ranks == 7
+    assert any(n.startswith("served by:") for n in best.notes)
+    frozen = solve_frozen(PlacementRequest(cfg=d, gpus=8), 2, 6)
+    assert frozen.engine == "" and any(n.startswith("not served yet:") for n in frozen.notes)
+    assert "engine" in best.to_json()
