@@ -230,6 +230,12 @@ def from_response_format(fmt: dict | None, tokenizer, vocab_size: int) -> TokenC
     if not fmt:
         return None
     t = fmt.get("type")
+    if t == "json_schema":
+        spec = fmt.get("json_schema") or {}
+        schema = spec.get("schema") if isinstance(spec, dict) and "schema" in spec else fmt.get("schema")
+        if isinstance(schema, dict) and schema:
+            from .schema import SchemaRecognizer
+            return TokenConstraint(SchemaRecognizer(schema), tokenizer, vocab_size)      # ValueError: unsupported keyword
     if t in ("json_object", "json_schema"):
         return TokenConstraint(JsonRecognizer(object_only=True), tokenizer, vocab_size)
     if t == "choice":
