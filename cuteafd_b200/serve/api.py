@@ -168,6 +168,41 @@ def anthropic_events(model: str, usage_in: int):
 
 
 # ---- OpenAI responses -------------------------------------------------------------------------------------
+def responses_messages(body: dict) -> list[dict]:
+    """The Responses request as a chat message list (instructions first)."""
+    inp = body.get("input")
+    msgs = [{"role": "user", "content": inp}] if isinstance(inp, str) else [
+        {"role": m.get("role", "user"), "content": m.get("content")} for m in (inp or []) if isinstance(m, dict)]
+    if body.get("instructions"):
+        msgs.insert(0, {"role": "system", "content": body["instructions"]})
+    return msgs
+
+
+def continue_session(body: dict, sessions: dict) -> tuple[dict, list[dict]]:
+    """Resolve ``previous_response_id``: (request body whose input is the whole conversation, that conversation)."""
+    msgs = responses_messages(body)
+    prev = body.get("previous_response_id")
+    if prev:
+        hist = sessions.get(prev)
+        if hist is None:
+            raise BadRequest(f"previous_response_id {prev!r} is unknown (responses are kept in memory until deleted)")
+        msgs = list(hist) + [m for m in msgs if m.get("role") != "system" or not any(h.get("role") == "system" for h in hist)]
+    out = {k: v for k, v in body.items() if k not in ("previous_response_id", "instructions")}
+    out["input"] = msgs
+    return out, msgs
+
+
+def input_items(msgs: list[dict]) -> dict:
+    data = []
+    for i, m in enumerate(msgs):
+        c = m.get("content")
+        text = c if isinstance(c, str) else "".join(p.get("text", "") for p in (c or []) if isinstance(p, dict))
+        kind = "output_text" if m.get("role") == "assistant" else "input_text"
+        data.append({"id": f"item_{i}", "type": "message", "role": m.get("role", "user"), "content": [{"type": kind, "text": text}]})
+    return {"object": "list", "data": data, "has_more": False}
+
+
+
 def responses_object(model: str, text: str, finish: str, usage: dict, rid: str | None = None) -> dict:
     rid = rid or "resp_" + uuid.uuid4().hex[:24]
     return {"id": rid, "object": "response", "created_at": int(time.time()), "model": model,

@@ -34,6 +34,7 @@ class ServerState:
         self.extras = extras or {}
         self.started = time.time()
         self.responses: dict[str, dict] = {}
+        self.sessions: dict[str, list] = {}      # response id -> the conversation that produced it, reply included
         self.lock = threading.Lock()
 
 
@@ -141,6 +142,12 @@ def make_handler(state: ServerState):
                 return self._json(200, state.extras.get("expert_usage", lambda: {})())
             if path.startswith("/console/usage"):
                 return self._json(200, state.usage.summary(24.0) if state.usage else {})
+            if path.startswith("/v1/responses/") and path.endswith("/input_items"):
+                with state.lock:
+                    conv = state.sessions.get(path.split("/")[3])
+                if conv is None:
+                    return self._json(404, {"error": {"message": "no such response"}})
+                return self._json(200, api.input_items(conv[:-1]))
             if path.startswith("/v1/responses/"):
                 rid = path.rsplit("/", 1)[1]
                 with state.lock:
@@ -153,6 +160,7 @@ def make_handler(state: ServerState):
             if path.startswith("/v1/responses/"):
                 with state.lock:
                     ok = state.responses.pop(path.rsplit("/", 1)[1], None) is not None
+                    state.sessions.pop(path.rsplit("/", 1)[1], None)
                 return self._json(200 if ok else 404, {"deleted": ok})
             return self._json(404, {"error": {"message": "no route"}})
 
@@ -161,14 +169,25 @@ def make_handler(state: ServerState):
             path = self.path.split("?", 1)[0]
             flavor = {"/v1/chat/completions": "openai", "/v1/messages": "anthropic", "/v1/responses": "responses",
                       "/v1/messages/count_tokens": "anthropic", "/v1/responses/input_tokens": "responses"}.get(path)
+            if flavor is None and path.startswith("/v1/responses/") and path.endswith("/cancel"):
+                flavor = "responses"
             if flavor is None:
                 return self._json(404, {"error": {"message": f"no route {path}"}})
             if not self._authorized():
                 st, body, hd = 401, {"error": {"message": "invalid API key", "type": "authentication_error"}}, {}
                 return self._json(st, body, hd)
+            if path.startswith("/v1/responses/") and path.endswith("/cancel"):
+                with state.lock:
+                    r = state.responses.get(path.split("/")[3])
+                # responses run in the foreground: by the time an id is known the response has completed
+                return self._json(200, r) if r else self._json(404, {"error": {"message": "no such response"}})
             try:
                 body = self._body()
                 probe = api.parse_probe(self.headers)
+                self._session = None
+                if flavor == "responses":
+                    with state.lock:
+                        body, self._session = api.continue_session(body, state.sessions)
                 req = api.build_request(body, state.tok, state.sched.be.vocab_size, probe, flavor, state.media)
             except api.BadRequest as e:
                 st, eb, hd = api.error_body(FAIL_BAD_REQUEST, str(e), flavor)
@@ -229,6 +248,7 @@ def make_handler(state: ServerState):
                 obj = api.responses_object(model, out_text, finish, usage)
                 with state.lock:
                     state.responses[obj["id"]] = obj
+                    state.sessions[obj["id"]] = list(self._session or []) + [{"role": "assistant", "content": out_text}]
                 return self._json(200, obj)
             return self._json(200, api.chat_completion(model, out_text, finish, usage, rows or None))
 
@@ -262,6 +282,7 @@ def make_handler(state: ServerState):
                         obj = api.responses_object(model, "".join(text), ev[1], ev[2], rid)
                         with state.lock:
                             state.responses[rid] = obj
+                            state.sessions[rid] = list(getattr(self, "_session", None) or []) + [{"role": "assistant", "content": "".join(text)}]
                         self._sse({"type": "response.completed", "response": obj}, "response.completed")
                     else:
                         self._sse({"type": "error", "message": ev[2]}, "error")

@@ -257,6 +257,12 @@ def serve_responses(state, ws: Socket) -> None:
         model = body.get("model") or state.model_id
         rid = "resp_" + uuid.uuid4().hex[:24]
         try:
+            with state.lock:
+                body, conv = api.continue_session(body, getattr(state, "sessions", {}))
+        except api.BadRequest as e:
+            ws.send_json({"type": "error", "error": {"type": "invalid_request_error", "message": str(e)}})
+            continue
+        try:
             ws.send_json({"type": "response.created", "response": {"id": rid, "status": "in_progress", "model": model}})
             t0 = time.time()
             out = _generate(state, ws, body, "responses",
@@ -266,6 +272,8 @@ def serve_responses(state, ws: Socket) -> None:
                 obj = api.responses_object(model, out[3], out[1], out[2], rid)
                 with state.lock:
                     state.responses[rid] = obj
+                    if hasattr(state, "sessions"):
+                        state.sessions[rid] = list(conv) + [{"role": "assistant", "content": out[3]}]
                 if state.usage:
                     state.usage.record(model, "responses", out[2], time.time() - t0, out[1])
                 ws.send_json({"type": "response.completed", "response": obj})

@@ -258,3 +258,23 @@ def test_websocket_needs_the_key(server):
     from websockets.exceptions import InvalidStatus
     with pytest.raises(InvalidStatus):
         _ws(server, "/v1/realtime", key="wrong").__enter__()
+
+
+def test_responses_sessions(server):
+    """previous_response_id continues the stored conversation; input_items lists it; cancel and delete behave."""
+    st, _, raw = call(server, "POST", "/v1/responses", {"input": "first turn", "instructions": "be brief", "max_output_tokens": 4})
+    a = json.loads(raw)
+    assert st == 200
+    st, _, raw = call(server, "POST", "/v1/responses", {"input": "second turn", "previous_response_id": a["id"], "max_output_tokens": 4})
+    b = json.loads(raw)
+    assert st == 200 and b["usage"]["input_tokens"] > a["usage"]["input_tokens"] + a["usage"]["output_tokens"]
+    st, _, raw = call(server, "GET", f"/v1/responses/{b['id']}/input_items")
+    items = json.loads(raw)["data"]
+    assert st == 200 and [i["role"] for i in items] == ["system", "user", "assistant", "user"]
+    assert items[1]["content"][0]["text"] == "first turn" and items[3]["content"][0]["text"] == "second turn"
+    st, _, raw = call(server, "POST", f"/v1/responses/{b['id']}/cancel", {})
+    assert st == 200 and json.loads(raw)["id"] == b["id"]
+    assert call(server, "POST", "/v1/responses", {"input": "x", "previous_response_id": "resp_nope"})[0] == 400
+    assert call(server, "DELETE", f"/v1/responses/{a['id']}")[0] == 200
+    assert call(server, "GET", f"/v1/responses/{a['id']}/input_items")[0] == 404
+    assert call(server, "POST", "/v1/responses", {"input": "x", "previous_response_id": a["id"]})[0] == 400
