@@ -59,3 +59,48 @@ def _worker(rank, world, port, out_dir):
 def test_pipeline_hop_and_sharded_head(tmp_path):
     mp.spawn(_worker, args=(2, _port(), str(tmp_path)), nprocs=2, join=True)
     assert all(os.path.exists(tmp_path / f"ok{r}") for r in range(2))
+
+
+def _pp_worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+
+    from cuteafd_b200 import tiny_moe
+    from cuteafd_b200.parallel.pp import StagePlan
+    from cuteafd_b200.ref.model import KvState, RefDecoder, init_weights
+    from cuteafd_b200.ref.pipeline import PipelinedDecoder
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = tiny_moe().replace(num_layers=4, first_dense_layers=1)
+    params = init_weights(cfg, seed=2)
+    plan = StagePlan.even(cfg.num_layers, world)
+    pd = PipelinedDecoder(RefDecoder(cfg, params), plan, rank)
+    kv = KvState(cfg)
+    toks = torch.arange(3, 15) % cfg.vocab_size
+    got = []
+    nxt = torch.zeros(1, dtype=torch.long)
+    for step in range(4):
+        logits = pd.forward(toks, kv)
+        if rank == world - 1:
+            got.append(logits[-1].clone())
+            nxt = logits[-1].argmax().view(1)
+        dist.broadcast(nxt, src=world - 1)              # every stage feeds the token the last stage chose
+        toks = nxt.clone()
+    if rank == world - 1:
+        whole, wkv = RefDecoder(cfg, params), KvState(cfg)
+        t = torch.arange(3, 15) % cfg.vocab_size
+        errs = []
+        for step in range(4):
+            ref = whole.forward(t, wkv)[-1]
+            errs.append((got[step] - ref).abs().max().item())
+            t = ref.argmax().view(1)
+        torch.save({"errs": errs, "own": [kv.length(i) for i in range(cfg.num_layers)]}, os.path.join(out_dir, "pp.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_oracle_decoder_as_pipeline_stages(tmp_path):
+    import torch.multiprocessing as mp
+    mp.spawn(_pp_worker, args=(2, _port(), str(tmp_path)), nprocs=2, join=True)
+    d = torch.load(str(tmp_path / "pp.pt"))
+    assert max(d["errs"]) == 0.0                       # same arithmetic, only the process boundary moved
+    assert d["own"] == [0, 0, 15, 15]                  # the last stage cached K/V for its own layers only
