@@ -125,7 +125,7 @@ def cmd_quantize(a: argparse.Namespace) -> int:
     roles = {r: getattr(a, r) for r in QUANT_ROLES if getattr(a, r) != "keep"}
     recipe = Recipe(roles, seed=a.seed)
     if not a.merge_only:
-        quantize_snapshot(a.src, a.dst, recipe, a.rank, a.world, a.device)
+        quantize_snapshot(a.src, a.dst, recipe, a.rank, a.world, a.device, hessians=a.hessians or None)
     if a.merge_only or a.world == 1:
         m = merge(a.src, a.dst, recipe, a.world)
         print(json.dumps(m["summary"]))
@@ -207,6 +207,7 @@ def build_parser() -> argparse.ArgumentParser:
         q.add_argument("--" + role.replace("_", "-"), dest=role, default=default, help="target format for this role")
     q.add_argument("--rank", type=int, default=0); q.add_argument("--world", type=int, default=1)
     q.add_argument("--device", default="cpu"); q.add_argument("--seed", type=int, default=0)
+    q.add_argument("--hessians", default="", help="directory of <operand>.hessian tensors from a calibration run (EXL3 error feedback)")
     q.add_argument("--merge-only", action="store_true", help="all workers have finished: write the index and the manifest")
     q.set_defaults(fn=cmd_quantize)
 

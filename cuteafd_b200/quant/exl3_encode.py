@@ -12,7 +12,9 @@ shifts into a 16-bit window and the window indexes the computed codebook, so the
 last symbols), which the search meets with the usual two passes: a free pass fixes the window at the middle of the
 tile, a second pass starts and ends in that window.
 
-Plain rounding in the rotated space is used (no calibration Hessian); ``proxy_error`` reports the relative error.
+Without calibration data the tiles are rounded independently in the rotated space; with the input Hessian of the layer
+(``hessian=``) the 16-row blocks are encoded in sequence with GPTQ-style error feedback, which cuts the output error
+the calibration inputs see several times over.  ``proxy_error`` reports the relative weight error.
 Counterpart: the reference's EXL3 quantiser (python/cuteafd_runtime/exl3_quantizer.py) and its trellis decoder
 (native/shared/cuda/exl3_codebook.cuh); the codebook arithmetic is shared with ``codecs.exl3_decode_inner``.
 """
@@ -93,9 +95,23 @@ def _pack(symbols: torch.Tensor, bits: int) -> torch.Tensor:
     return torch.where(words >= 32768, words - 65536, words).to(torch.int16)
 
 
+def _rotate_hessian(h: torch.Tensor, su: torch.Tensor) -> torch.Tensor:
+    """Hessian of the layer input x -> Hessian of the rotated input x' = H_K (x * su)."""
+    d = h.double() * su[:, None] * su[None, :]
+    d = codecs.hadamard128(d.contiguous())                      # columns
+    return codecs.hadamard128(d.T.contiguous()).T.contiguous()   # rows
+
+
 def exl3_quantize(w: torch.Tensor, bits: int, gen: torch.Generator | None = None, tile_batch: int = 128,
-                  device: str | torch.device | None = None) -> dict[str, torch.Tensor]:
-    """w [K, N] (input dimension first, both multiples of 128) -> {"trellis", "suh", "svh", "proxy_error"}."""
+                  device: str | torch.device | None = None, hessian: torch.Tensor | None = None,
+                  damp: float = 0.01) -> dict[str, torch.Tensor]:
+    """w [K, N] (input dimension first, both multiples of 128) -> {"trellis", "suh", "svh", "proxy_error"}.
+
+    ``hessian`` [K, K] (sum of x x^T over calibration inputs) switches from plain rounding to block error feedback:
+    the 16-row blocks of the rotated weight are encoded one after the other, and the error of a block is spread over
+    the rows still to come through the inverse Hessian's Cholesky factor (the GPTQ update with the trellis as the
+    block quantiser), which lowers the output error tr(E^T H E) the calibration data sees.  ``hessian_error`` in the
+    result is that quantity relative to tr(W^T H W)."""
     K, N = w.shape
     assert K % 128 == 0 and N % 128 == 0 and 1 <= bits <= 8
     gen = gen or torch.Generator().manual_seed(0)
@@ -110,16 +126,48 @@ def exl3_quantize(w: torch.Tensor, bits: int, gen: torch.Generator | None = None
     svh = (sv * col).to(torch.float16)
     suh = su.to(torch.float16)
     inner_t = codecs.hadamard128((a / svh.double()[None, :]).contiguous())            # ... . diag(1/svh) . H_N
-    # tiles in stream order
     Kt, Nt = K // 16, N // 16
-    tiles = inner_t.view(Kt, 16, Nt, 16).permute(0, 2, 1, 3).reshape(Kt * Nt, 256)
     perm = codecs._exl3_lane_permutation()
-    stream_t = tiles[:, perm].float().to(dev)
-    sym = torch.empty(Kt * Nt, 256, dtype=torch.int64, device=dev)
-    for t0 in range(0, Kt * Nt, tile_batch):
-        s, _ = encode_tiles(stream_t[t0 : t0 + tile_batch], bits)
-        sym[t0 : t0 + tile_batch] = s
-    trellis = _pack(sym, bits).view(Kt, Nt, 16 * bits).cpu()
+
+    def encode_rows(block: torch.Tensor) -> torch.Tensor:
+        """[16 * r, N] rows of the rotated weight -> int16 words [r, Nt, 16 * bits]."""
+        r = block.shape[0] // 16
+        tiles = block.view(r, 16, Nt, 16).permute(0, 2, 1, 3).reshape(r * Nt, 256)
+        stream_t = tiles[:, perm].float().to(dev)
+        sym = torch.empty(r * Nt, 256, dtype=torch.int64, device=dev)
+        for t0 in range(0, r * Nt, tile_batch):
+            sym[t0:t0 + tile_batch] = encode_tiles(stream_t[t0:t0 + tile_batch], bits)[0]
+        return _pack(sym, bits).view(r, Nt, 16 * bits).cpu()
+
+    out: dict[str, torch.Tensor] = {}
+    if hessian is None:
+        trellis = encode_rows(inner_t)
+    else:
+        assert hessian.shape == (K, K)
+        hr = _rotate_hessian(hessian.cpu(), su)
+        hr = hr + damp * hr.diagonal().mean() * torch.eye(K, dtype=torch.float64)
+        hinv = torch.linalg.cholesky(torch.linalg.inv(hr), upper=True)               # [K, K]
+        wt = inner_t.T.clone()                                                       # [N, K]: columns = input rows
+        trellis = torch.empty(Kt, Nt, 16 * bits, dtype=torch.int16)
+        for kb in range(Kt):
+            blk = slice(16 * kb, 16 * kb + 16)
+            words = encode_rows(wt[:, blk].T.contiguous())
+            trellis[kb] = words[0]
+            q = codecs.exl3_decode_inner(words).double()                              # [16, N]
+            err = (wt[:, blk] - q.T) @ torch.linalg.inv(hinv[blk, blk])
+            if kb + 1 < Kt:
+                wt[:, 16 * kb + 16:] -= err @ hinv[blk, 16 * kb + 16:]
+        e = codecs.exl3_decode_inner(trellis).double() - inner_t
+        out["hessian_error"] = (torch.einsum("kn,kj,jn->", e, _rotate_hessian(hessian.cpu(), su), e)
+                                / torch.einsum("kn,kj,jn->", inner_t, _rotate_hessian(hessian.cpu(), su), inner_t).clamp_min(1e-30)).float()
     got = codecs.exl3_dequant(trellis, suh, svh)
     err = ((got - wd).pow(2).sum() / wd.pow(2).sum().clamp_min(1e-30)).sqrt()
-    return {"trellis": trellis, "suh": suh, "svh": svh, "proxy_error": err.float()}
+    out.update({"trellis": trellis, "suh": suh, "svh": svh, "proxy_error": err.float()})
+    return out
+
+
+def hessian_error(w: torch.Tensor, q: dict, hessian: torch.Tensor) -> float:
+    """tr(E^T H E) / tr(W^T H W) for a quantised result ``q`` of ``w`` [K, N] under the input Hessian ``hessian``."""
+    e = codecs.exl3_dequant(q["trellis"], q["suh"], q["svh"]) - w.double()
+    h = hessian.double()
+    return float(torch.einsum("kn,kj,jn->", e, h, e) / torch.einsum("kn,kj,jn->", w.double(), h, w.double()).clamp_min(1e-30))

@@ -52,13 +52,15 @@ class Recipe:
         return self.roles.get(role, "keep")
 
 
-def encode_operand(w: torch.Tensor, fmt: str, prefix: str, seed: int = 0,
-                   device: str | torch.device = "cpu") -> tuple[dict[str, torch.Tensor], float]:
-    """Encode an [out, in] fp32 weight; returns (tensors to store, relative error of the decoded result)."""
+def encode_operand(w: torch.Tensor, fmt: str, prefix: str, seed: int = 0, device: str | torch.device = "cpu",
+                   hessian: torch.Tensor | None = None) -> tuple[dict[str, torch.Tensor], float]:
+    """Encode an [out, in] fp32 weight; returns (tensors to store, relative error of the decoded result).  ``hessian``
+    [in, in] (sum of x x^T over calibration inputs of this projection) is used by the EXL3 encoder's error feedback."""
     w = w.float()
     if fmt.startswith("exl3"):
         bits = int(fmt.split("k")[-1])
-        r = exl3_encode.exl3_quantize(w.T.contiguous(), bits, torch.Generator().manual_seed(seed), device=device)
+        r = exl3_encode.exl3_quantize(w.T.contiguous(), bits, torch.Generator().manual_seed(seed), device=device,
+                                      hessian=hessian)
         return ({f"{prefix}.trellis": r["trellis"], f"{prefix}.suh": r["suh"], f"{prefix}.svh": r["svh"]},
                 float(r["proxy_error"]))
     out = formats.encode(w, fmt, prefix)
@@ -86,8 +88,11 @@ def _eligible(op: formats.QuantOperand, fmt: str) -> bool:
 
 
 def quantize_snapshot(src: str, dst: str, recipe: Recipe, rank: int = 0, world: int = 1,
-                      device: str | torch.device = "cpu", log=print) -> dict:
-    """Run worker ``rank`` of ``world``.  Returns this worker's manifest part; rank 0 also merges (see ``merge``)."""
+                      device: str | torch.device = "cpu", log=print, hessians: str | None = None) -> dict:
+    """Run worker ``rank`` of ``world``.  Returns this worker's manifest part; rank 0 also merges (see ``merge``).
+    ``hessians``: a directory of safetensors files holding ``<operand prefix>.hessian`` [in, in] tensors from a
+    calibration run; operands that have one are encoded with error feedback (EXL3 targets)."""
+    hcat = Catalog(hessians) if hessians else None
     src = snapshot.resolve(src)
     cfg, hf = snapshot.read_config(src)
     fam = families.detect(hf)
@@ -130,11 +135,12 @@ def quantize_snapshot(src: str, dst: str, recipe: Recipe, rank: int = 0, world: 
             report[pre] = prev
             continue
         w = formats.dequantize(op, cat)
-        enc, err = encode_operand(w, fmt, pre, seed=recipe.seed + len(report), device=device)
+        hess = hcat.read(pre + ".hessian").double() if hcat is not None and (pre + ".hessian") in hcat else None
+        enc, err = encode_operand(w, fmt, pre, seed=recipe.seed + len(report), device=device, hessian=hess)
         fname = f"quant-{rank:03d}-{len(report):06d}.safetensors"
         write_file(os.path.join(dst, fname), enc, {"format": "pt"})
         report[pre] = {"role": role, "format": fmt, "rel_error": err, "source_sha256": digest, "file": fname,
-                       "tensors": sorted(enc)}
+                       "tensors": sorted(enc), "calibrated": hess is not None}
         log(f"[quantize r{rank}] {pre}: {op.format} -> {fmt}  rel err {err:.4f}")
         with open(part_path, "w") as f:
             json.dump({"operands": report}, f)

@@ -97,3 +97,28 @@ def test_cli_quantize(tmp_path):
     assert man["recipe"] == {"routed_expert": "nvfp4"}
     assert os.path.exists(os.path.join(dst, "config.json"))
     assert run  # single-process helper is part of the public surface
+
+
+def test_exl3_error_feedback_with_a_hessian(tmp_path):
+    """With the layer's input Hessian the encoder's block error feedback cuts the output error the calibration data sees."""
+    from cuteafd_b200.loader.safetensors_io import write_file
+    from cuteafd_b200.quant.exl3_encode import hessian_error
+    g = torch.Generator().manual_seed(1)
+    K = N = 128
+    w = torch.randn(K, N, generator=g) * 0.05
+    A = torch.randn(K, K, generator=g) @ torch.diag(torch.logspace(0, -2, K))       # strongly non-uniform input covariance
+    X = torch.randn(1024, K, generator=g) @ A.T
+    H = (X.T @ X).double()
+    plain = exl3_encode.exl3_quantize(w, 3, torch.Generator().manual_seed(0))
+    fed = exl3_encode.exl3_quantize(w, 3, torch.Generator().manual_seed(0), hessian=H)
+    e0, e1 = hessian_error(w, plain, H), hessian_error(w, fed, H)
+    assert e1 < 0.5 * e0, (e0, e1)
+    assert abs(float(fed["hessian_error"]) - e1) < 0.1 * e1
+    # the pipeline hands an operand's Hessian to the encoder
+    hd = str(tmp_path / "h")
+    os.makedirs(hd)
+    write_file(os.path.join(hd, "h.safetensors"), {"x.proj.hessian": H.float()}, {"format": "pt"})
+    enc, _ = encode_operand(w.T.contiguous(), "exl3_k3", "x.proj", hessian=H)
+    got = codecs.exl3_dequant(enc["x.proj.trellis"], enc["x.proj.suh"], enc["x.proj.svh"])
+    e2 = float(torch.einsum("kn,kj,jn->", got - w.double(), H, got - w.double()) / torch.einsum("kn,kj,jn->", w.double(), H, w.double()))
+    assert e2 < 0.5 * e0
