@@ -132,6 +132,24 @@ def cmd_quantize(a: argparse.Namespace) -> int:
     return 0
 
 
+def cmd_calibrate(a: argparse.Namespace) -> int:
+    from .loader.load import load_params
+    from .quant import calibrate
+    from .serve.tokenizer import load_tokenizer
+    cfg, params = load_params(a.src, dtype=torch_dtype(a.dtype))
+    tok = load_tokenizer(a.src, cfg.vocab_size) if a.tokens else None
+    col = calibrate.collect(cfg, params, calibrate.token_batches(a.tokens or None, tok, cfg.vocab_size, a.rows, a.seq, a.seed))
+    files = calibrate.save(col, a.dst)
+    print(json.dumps({"operands": len(col.h), "rows_min": min(col.rows.values()), "rows_max": max(col.rows.values()),
+                      "files": files}))
+    return 0
+
+
+def torch_dtype(name: str):
+    import torch
+    return {"f32": torch.float32, "bf16": torch.bfloat16}[name]
+
+
 def cmd_usage(a: argparse.Namespace) -> int:
     from .serve.usage import usage_report
     print(json.dumps(usage_report(a.db, a.hours), indent=1))
@@ -210,6 +228,13 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--hessians", default="", help="directory of <operand>.hessian tensors from a calibration run (EXL3 error feedback)")
     q.add_argument("--merge-only", action="store_true", help="all workers have finished: write the index and the manifest")
     q.set_defaults(fn=cmd_quantize)
+
+    c = sub.add_parser("calibrate", help="collect per-projection input Hessians for quantize --hessians")
+    c.add_argument("src"); c.add_argument("dst")
+    c.add_argument("--tokens", default="", help="text file of calibration lines (default: random ids)")
+    c.add_argument("--rows", type=int, default=2048); c.add_argument("--seq", type=int, default=256)
+    c.add_argument("--seed", type=int, default=0); c.add_argument("--dtype", default="f32", choices=("f32", "bf16"))
+    c.set_defaults(fn=cmd_calibrate)
 
     u = sub.add_parser("usage", help="request accounting report")
     u.add_argument("--db", default="usage.sqlite"); u.add_argument("--hours", type=float, default=24.0)

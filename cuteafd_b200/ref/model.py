@@ -120,7 +120,23 @@ class RefDecoder:
     def __init__(self, cfg: ModelConfig, params: dict[str, torch.Tensor], moe_fn: MoeFn | None = None):
         self.cfg, self.p, self.moe_fn = cfg, params, moe_fn
         self.select_fn = None        # optional (layer, start, Tq, Tk) -> bool mask [Tq, Tk] replacing the indexer's choice
+        self.observe = None          # optional (operand prefix, input rows [n, in]) -> None, called before every projection
         self._stacked: dict[int, tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
+
+    def _see(self, prefix: str, x: torch.Tensor) -> None:
+        if self.observe is not None and x.shape[0]:
+            self.observe(prefix, x)
+
+    def _see_mlp(self, prefix: str, x: torch.Tensor) -> None:
+        """Inputs of a SwiGLU block's three projections (the down projection sees the rounded activation)."""
+        if self.observe is None or not x.shape[0]:
+            return
+        p = self.p
+        self.observe(prefix + "gate_proj", x)
+        self.observe(prefix + "up_proj", x)
+        xf = x.float()
+        act = torch.nn.functional.silu(xf @ p[prefix + "gate_proj.weight"].float().T) * (xf @ p[prefix + "up_proj.weight"].float().T)
+        self.observe(prefix + "down_proj", act.to(x.dtype))
 
     # ---- pieces ---------------------------------------------------------------------------
     def expert_stack(self, layer: int, lo: int = 0, hi: int | None = None):
@@ -137,10 +153,16 @@ class RefDecoder:
         a = f"model.layers.{layer}.self_attn."
         T = x.shape[0]
         start = int(positions[0])
+        if self.observe is not None:
+            for name in ("q_a_proj", "q_proj", "kv_a_proj_with_mqa", "k_proj", "v_proj", "indexer.wk", "indexer.wq",
+                         "indexer.weights_proj"):
+                if a + name + ".weight" in p:
+                    self._see(a + name, x)
         if cfg.is_mla:
             if cfg.q_lora_rank:
                 qa = ops.rmsnorm((x.float() @ p[a + "q_a_proj.weight"].float().T).to(x.dtype),
                                  p[a + "q_a_layernorm.weight"], cfg.rms_eps)
+                self._see(a + "q_b_proj", qa)
                 q = (qa.float() @ p[a + "q_b_proj.weight"].float().T).to(x.dtype)
             else:
                 q = (x.float() @ p[a + "q_proj.weight"].float().T).to(x.dtype)
@@ -167,6 +189,7 @@ class RefDecoder:
                 if self.select_fn is not None:
                     forced = self.select_fn(layer, start, T, full.shape[0], allowed)
                     allowed = allowed if forced is None else forced
+            self._see(a + "kv_b_proj", lat_all[-T:])
             kvb = (lat_all.float() @ p[a + "kv_b_proj.weight"].float().T).to(x.dtype)
             kvb = kvb.view(-1, cfg.num_heads, cfg.qk_nope_dim + cfg.v_head_dim)
             k = torch.cat([kvb[..., : cfg.qk_nope_dim], rope_all[:, None, :].expand(-1, cfg.num_heads, -1)], dim=-1)
@@ -188,6 +211,7 @@ class RefDecoder:
             k_all = full[:, :half].view(-1, cfg.num_kv_heads, cfg.head_dim)
             v_all = full[:, half:].view(-1, cfg.num_kv_heads, cfg.head_dim)
             o = ops.causal_attention(q, k_all, v_all, start).reshape(T, cfg.num_heads * cfg.head_dim)
+        self._see(a + "o_proj", o)
         return (o.float() @ p[a + "o_proj.weight"].float().T).to(x.dtype)
 
     def route(self, layer: int, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
@@ -200,9 +224,15 @@ class RefDecoder:
         """Returns the new residual stream: residual + ffn(x), rounded once."""
         p, m = self.p, f"model.layers.{layer}.mlp."
         if not moe:
+            self._see_mlp(m, x)
             y = ops.swiglu_mlp(x, p[m + "gate_proj.weight"], p[m + "up_proj.weight"], p[m + "down_proj.weight"])
             return (residual.float() + y.to(x.dtype).float()).to(x.dtype)
         idx, w = self.route(layer, x)
+        if self.observe is not None:
+            for e in idx.unique().tolist():
+                self._see_mlp(f"{m}experts.{e}.", x[(idx == e).any(dim=-1)])
+            if self.cfg.num_shared_experts:
+                self._see_mlp(m + "shared_experts.", x)
         if self.moe_fn is not None:
             parts = self.moe_fn(layer, x, idx, w)
         else:

@@ -122,3 +122,37 @@ def test_exl3_error_feedback_with_a_hessian(tmp_path):
     got = codecs.exl3_dequant(enc["x.proj.trellis"], enc["x.proj.suh"], enc["x.proj.svh"])
     e2 = float(torch.einsum("kn,kj,jn->", got - w.double(), H, got - w.double()) / torch.einsum("kn,kj,jn->", w.double(), H, w.double()))
     assert e2 < 0.5 * e0
+
+
+def test_calibrate_then_quantize_with_hessians(tmp_path):
+    """The calibration run names every projection the way the quantiser looks it up, routed experts see only their
+    rows, and a calibrated EXL3 re-encode records that it used the Hessians."""
+    from cuteafd_b200.cli import main
+    from cuteafd_b200.loader.safetensors_io import Catalog
+    from cuteafd_b200.quant import calibrate
+    cfg = small()
+    src = snapshot.write_random_snapshot(cfg, str(tmp_path / "src"), fmt="bf16", seed=3)
+    hd = str(tmp_path / "hess")
+    assert main(["calibrate", src, hd, "--rows", "256", "--seq", "64"]) == 0
+    cat = Catalog(hd)
+    snap = load.open_snapshot(src)
+    quantisable = [p for p in snap.operands if p.endswith("_proj")]
+    missing = [p for p in quantisable if p + ".hessian" not in cat]
+    # an expert no token was routed to has no Hessian; everything else must be there
+    assert all(".experts." in p for p in missing), missing
+    h = cat.read("model.layers.0.self_attn.o_proj.hessian")
+    assert h.shape == (cfg.num_heads * cfg.head_dim, cfg.num_heads * cfg.head_dim)
+    assert torch.allclose(h, h.T, atol=1e-5) and torch.linalg.eigvalsh(h.double()).min() > -1e-6
+    assert int(cat.read("model.layers.0.self_attn.o_proj.rows")) == 256
+    er = [int(cat.read(f"model.layers.1.mlp.experts.{e}.up_proj.rows")) for e in range(cfg.num_experts)
+          if f"model.layers.1.mlp.experts.{e}.up_proj.rows" in cat]
+    assert sum(er) == 256 * cfg.top_k and max(er) < 256 * cfg.top_k
+    # the collector's sum is the plain sum of outer products
+    col = calibrate.HessianCollector()
+    x = torch.randn(5, 8)
+    col("a", x[:2]); col("a", x[2:])
+    assert torch.allclose(col.h["a"], (x.T @ x).double()) and col.rows["a"] == 5
+    dst = str(tmp_path / "dst")
+    assert main(["quantize", src, dst, "--dense-ffn", "exl3_k3", "--hessians", hd]) == 0
+    man = json.load(open(os.path.join(dst, "quantization.json")))
+    assert man["operands"]["model.layers.0.mlp.down_proj"]["calibrated"] is True
