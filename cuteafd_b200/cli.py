@@ -183,7 +183,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--speculator", default="auto"); s.add_argument("--layers", type=int, default=0)
     s.add_argument("--queue-depth", type=int, default=64); s.add_argument("--queue-wait", type=float, default=30.0)
     s.add_argument("--fake-engine", action="store_true", help="serve with the CPU oracle engine (no GPU)")
-    s.add_argument("--usage-db", default=""); s.add_argument("--kv-format", default="auto", choices=["auto", "bf16", "fp8_ds_mla"])
+    s.add_argument("--usage-db", default=""); s.add_argument("--memory-spool", default="", help="file opened at start-up that receives the ledger's state when an allocation fails"); s.add_argument("--kv-format", default="auto", choices=["auto", "bf16", "fp8_ds_mla"])
     s.add_argument("--prewarm", default="", help="JSON list of decode step geometries: read at start, rewritten at exit")
     s.add_argument("--media", default="none", choices=["none", "auto", "random"],
                    help="auto: load the vision / audio towers the snapshot bundles; random: small random-init towers")

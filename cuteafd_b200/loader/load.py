@@ -71,42 +71,86 @@ def load_params(path: str, dtype: torch.dtype = torch.float32, device: str = "cp
 
 
 def load_gqa_engine_weights(path: str, device: torch.device, with_experts: bool = True,
-                            expert_range: tuple[int, int] | None = None):
-    """Device weights for ``GqaMoeEngine`` straight from a snapshot (bf16 compute form)."""
+                            expert_range: tuple[int, int] | None = None, reserve_bytes: int = 0):
+    """Device weights for ``GqaMoeEngine`` straight from a snapshot (bf16 compute form), in one weight arena.
+
+    Two passes over the same item list: the first only reads shapes from the catalog and reserves a slot per engine
+    tensor (fused q/k/v rows, stacked experts), the arena is checked against the device's free memory (less
+    ``reserve_bytes`` for KV and workspaces) and allocated once, and the second decodes every stored tensor and copies
+    it straight into its rows of its slot, so no concatenated or stacked temporary ever exists on the device."""
     from ..models.gqa_moe import GqaMoeWeights, LayerWeights
+    from ..runtime.arena import WeightArena
     snap = open_snapshot(path)
     cfg, cat, ops = snap.cfg, snap.catalog, snap.operands
+    device = torch.device(device)
+    arena = WeightArena(device, owner=f"gqa:{cfg.name}")
+    items: list = []
+    bf16 = torch.bfloat16
 
-    def dense(prefix: str) -> torch.Tensor:
-        return formats.dequantize(ops[prefix], cat).to(torch.bfloat16).to(device).contiguous()
+    def shape_of(part) -> tuple[int, ...]:
+        kind, name = part
+        return tuple(ops[name].shape) if kind == "dense" else tuple(cat.entries[name].shape)
 
-    def raw(name: str, dt=torch.bfloat16) -> torch.Tensor:
-        return cat.read(name).to(dt).to(device).contiguous()
+    def want(obj, attr: str, slot: str, parts: list, mode: str = "cat", dt: torch.dtype = bf16) -> None:
+        shapes = [shape_of(p) for p in parts]
+        shape = (len(parts), *shapes[0]) if mode == "stack" else (sum(s[0] for s in shapes), *shapes[0][1:])
+        arena.reserve(slot, shape, dt)
+        items.append((obj, attr, slot, parts, mode, dt))
 
     W = GqaMoeWeights(cfg)
-    W.embed, W.final_norm = raw("model.embed_tokens.weight"), raw("model.norm.weight")
-    W.lm_head = W.embed if cfg.tie_embeddings else raw("lm_head.weight")
+    want(W, "embed", "embed", [("raw", "model.embed_tokens.weight")])
+    want(W, "final_norm", "final_norm", [("raw", "model.norm.weight")])
+    if not cfg.tie_embeddings:
+        want(W, "lm_head", "lm_head", [("raw", "lm_head.weight")])
     lo, hi = expert_range or (0, cfg.num_experts)
     for i in range(cfg.num_layers):
         pre, L = f"model.layers.{i}.", LayerWeights()
-        a, m = pre + "self_attn.", pre + "mlp."
-        L.ln1, L.ln2 = raw(pre + "input_layernorm.weight"), raw(pre + "post_attention_layernorm.weight")
-        L.wqkv = torch.cat([dense(a + "q_proj"), dense(a + "k_proj"), dense(a + "v_proj")]).contiguous()
-        L.wo = dense(a + "o_proj")
+        a, m, s = pre + "self_attn.", pre + "mlp.", f"layers.{i}."
+        want(L, "ln1", s + "ln1", [("raw", pre + "input_layernorm.weight")])
+        want(L, "ln2", s + "ln2", [("raw", pre + "post_attention_layernorm.weight")])
+        want(L, "wqkv", s + "wqkv", [("dense", a + "q_proj"), ("dense", a + "k_proj"), ("dense", a + "v_proj")])
+        want(L, "wo", s + "wo", [("dense", a + "o_proj")])
         if cfg.qk_norm:
-            L.q_norm, L.k_norm = raw(a + "q_norm.weight"), raw(a + "k_norm.weight")
+            want(L, "q_norm", s + "q_norm", [("raw", a + "q_norm.weight")])
+            want(L, "k_norm", s + "k_norm", [("raw", a + "k_norm.weight")])
         if cfg.is_moe_layer(i):
-            L.router = raw(m + "gate.weight")
+            want(L, "router", s + "router", [("raw", m + "gate.weight")])
             bn = m + "gate.e_score_correction_bias"
-            L.router_bias = raw(bn, torch.float32) if bn in cat else None
+            L.router_bias = None
+            if bn in cat:
+                want(L, "router_bias", s + "router_bias", [("raw", bn)], dt=torch.float32)
             if with_experts:
                 for dst, src in (("w_gate", "gate_proj"), ("w_up", "up_proj"), ("w_down", "down_proj")):
-                    setattr(L, dst, torch.stack([dense(f"{m}experts.{e}.{src}") for e in range(lo, hi)]).contiguous())
+                    want(L, dst, s + dst, [("dense", f"{m}experts.{e}.{src}") for e in range(lo, hi)], mode="stack")
             if cfg.num_shared_experts:
-                L.s_gate, L.s_up, L.s_down = (dense(f"{m}shared_experts.{n}_proj") for n in ("gate", "up", "down"))
+                for n in ("gate", "up", "down"):
+                    want(L, "s_" + n, s + "s_" + n, [("dense", f"{m}shared_experts.{n}_proj")])
         else:
-            L.d_gate, L.d_up, L.d_down = (dense(f"{m}{n}_proj") for n in ("gate", "up", "down"))
+            for n in ("gate", "up", "down"):
+                want(L, "d_" + n, s + "d_" + n, [("dense", f"{m}{n}_proj")])
         W.layers.append(L)
+
+    if device.type == "cuda":
+        arena.check_fits(torch.cuda.mem_get_info(device)[0], reserve_bytes)
+    arena.allocate()
+    for obj, attr, slot, parts, mode, dt in items:
+        row = 0
+        for kind, name in parts:
+            t = formats.dequantize(ops[name], cat) if kind == "dense" else cat.read(name)
+            t = t.to(dt)
+            if mode == "stack":
+                arena.fill_rows(slot, row, t[None].to(device))
+                row += 1
+            else:
+                arena.fill_rows(slot, row, t.to(device))
+                row += t.shape[0]
+        setattr(obj, attr, arena.view(slot))
+    left = arena.missing()
+    if left:
+        raise RuntimeError(f"weights left unwritten: {left[:4]}")
+    if cfg.tie_embeddings:
+        W.lm_head = W.embed
+    W.arena = arena
     return cfg, W
 
 

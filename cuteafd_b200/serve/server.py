@@ -128,8 +128,8 @@ def make_handler(state: ServerState):
                 s["uptime_s"] = round(time.time() - state.started, 1)
                 return self._json(200, s)
             if path == "/v1/thermal":
-                from ..utils.thermal import sample_once
-                return self._json(200, sample_once())
+                from ..utils.thermal import monitor
+                return self._json(200, monitor().report(60.0))
             if path == "/v1/fabric":
                 from ..parallel.fabric import fabric_report
                 return self._json(200, fabric_report())
@@ -364,6 +364,15 @@ def build_state(args) -> ServerState:
                 from ..models.gqa_moe import GqaMoeEngine as Engine, GqaMoeWeights as Weights, KvCache as Cache
             eng = Engine(cfg, Weights.random_init(cfg, dev), Cache(cfg, num_pages, dev), max_tokens=max(2048, rows), max_seqs=rows)
         be = EngineBackend(eng, num_pages, pages_per_seq, prefill_chunk=2048, max_decode_rows=args.concurrency)
+        from ..utils.memory_ledger import LEDGER
+        LEDGER.tag_tree("weights", "engine", eng.W)            # an arena's storage is already counted: adds nothing then
+        LEDGER.tag_tree("kv", "engine", eng.kv)
+        LEDGER.tag_tree("workspace", "engine", eng)
+        LEDGER.tag_tree("workspace", "backend", be)
+        if getattr(args, "memory_spool", ""):
+            LEDGER.open_spool(args.memory_spool)
+        for line in LEDGER.lines():
+            print(line, flush=True)
         pw = getattr(args, "prewarm", "")
         if pw:
             import json
