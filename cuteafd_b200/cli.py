@@ -156,7 +156,79 @@ def cmd_usage(a: argparse.Namespace) -> int:
     return 0
 
 
+# Help for flags declared without one; keyed by destination, or by (subcommand, destination) where the meaning differs.
+_HELP = {
+    "set": "override one configuration key (repeatable); wins over --config",
+    "model": "snapshot directory, Hugging Face cache name, or a preset name",
+    "layout": "print the per-GPU memory layout (weights by role, KV pool, workspaces, graphs)",
+    ("plan", "json"): "print the plan as JSON", ("fabric", "json"): "print the report as JSON",
+    ("plan", "deployment"): "print the typed launch description (one entry per rank) as JSON",
+    ("expertd", "deployment"): "launch description written by plan --deployment (expert ranges, peers)",
+    "files": "list the checkpoint files (and byte ranges) each role needs",
+    "role": "restrict --files to one role (attention, experts, head, ...)",
+    "require_ready": "exit 1 when a tensor has no kernel that serves its format",
+    ("plan", "gpus"): "GPUs of the box to plan for", ("bench", "gpus"): "GPUs to run the benchmark on",
+    "attention_ranks": "GPUs that run attention and the dense backbone (default: solver's choice)",
+    "expert_ranks": "GPUs that hold routed experts (default: solver's choice)",
+    "pipeline_stages": "split the layers into this many pipeline stages",
+    "pool_tokens": "KV pool size in tokens (default: what memory allows, at least 256K)",
+    "gpu_memory_cap": "usable memory per GPU, e.g. 160GiB (default: all of it less a safety margin)",
+    ("plan", "max_context_tokens"): "longest context a request may reach (sizes workspaces)",
+    ("serve", "max_context_tokens"): "longest context a request may reach (sizes the KV pool and workspaces)",
+    ("plan", "concurrency"): "requests decoded together (sizes graphs and workspaces)",
+    ("serve", "concurrency"): "requests decoded together; more wait in the admission queue",
+    ("plan", "speculator"): "speculative decoding to plan memory for",
+    ("serve", "speculator"): "auto (MTP depth of the checkpoint, else history n-gram), history, ngram, mtp, off",
+    "decode_lanes": "independent decode batches served alternately",
+    "format": "override the detected storage format of dense weights",
+    "expert_format": "override the detected storage format of routed experts",
+    ("plan", "kv_format"): "KV record format to plan for (bf16, fp8_ds_mla)",
+    ("serve", "kv_format"): "KV record format: auto picks the 656-byte FP8 latent record for sparse-attention checkpoints",
+    ("serve", "snapshot"): "checkpoint to serve (default: random-init weights of --preset)",
+    ("expertd", "snapshot"): "checkpoint to read this rank's experts from",
+    ("golden", "snapshot"): "checkpoint to compare (default: random-init weights of --preset)",
+    ("serve", "preset"): "architecture preset when no snapshot is given", ("golden", "preset"): "architecture preset when no snapshot is given",
+    ("serve", "host"): "address to listen on", ("gateway", "host"): "address to listen on",
+    ("serve", "port"): "port to listen on", ("gateway", "port"): "port to listen on",
+    ("bench", "port"): "rendezvous port for multi-GPU runs",
+    "api_key": "require this bearer token (default: $CUTEAFD_API_KEY; empty = no authentication)",
+    "layers": "serve only the first N layers of a preset (smoke runs)",
+    "queue_depth": "requests that may wait for admission; further ones get HTTP 429",
+    "queue_wait": "seconds a request may wait for admission before HTTP 429",
+    "usage_db": "sqlite file for request accounting (empty = off)",
+    ("expertd", "rank"): "this worker's rank in the job", ("expertd", "world"): "ranks in the job",
+    ("quantize", "rank"): "this worker's index", ("quantize", "world"): "workers that share the operands",
+    "master_addr": "rendezvous address", "master_port": "rendezvous port",
+    ("golden", "tokens"): "tokens in the comparison prompt", "out": "write the per-layer report to this JSON file",
+    "steps": "timed steps", "warmup": "untimed warm-up steps",
+    "p2p": "also time a 256 MiB peer copy between GPU 0 and GPU 1",
+    "upstream": "OpenAI-compatible server the gateway forwards to",
+    "model_map": "comma-separated client=upstream model name pairs",
+    ("quantize", "src"): "source snapshot", ("quantize", "dst"): "output directory",
+    ("calibrate", "src"): "snapshot to run", ("calibrate", "dst"): "output directory for the Hessian shards",
+    "device": "device the encoders run on (cpu, cuda:0, ...)",
+    ("quantize", "seed"): "seed of the EXL3 sign flips", ("calibrate", "seed"): "seed of the random-id fallback",
+    "rows": "calibration tokens in total", "seq": "tokens per calibration sequence",
+    "dtype": "precision the oracle decoder runs in",
+    "db": "sqlite file written by serve --usage-db", "hours": "window of the report",
+}
+
+
+def _fill_help(ap: argparse.ArgumentParser) -> None:
+    subs = next(a for a in ap._actions if isinstance(a, argparse._SubParsersAction))
+    for name, sp in [("", ap)] + list(subs.choices.items()):
+        for a in sp._actions:
+            if a.help is None:
+                a.help = _HELP.get((name, a.dest), _HELP.get(a.dest))
+
+
 def build_parser() -> argparse.ArgumentParser:
+    ap = _build_parser()
+    _fill_help(ap)
+    return ap
+
+
+def _build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="cuteafd", description="B200-native attention/FFN-disaggregated MoE serving")
     ap.add_argument("--config", default="", help="KEY=VALUE file")
     ap.add_argument("--set", action="append", default=[], metavar="KEY=VALUE")
