@@ -256,6 +256,20 @@ def _build_parser() -> argparse.ArgumentParser:
     s.add_argument("--queue-depth", type=int, default=64); s.add_argument("--queue-wait", type=float, default=30.0)
     s.add_argument("--fake-engine", action="store_true", help="serve with the CPU oracle engine (no GPU)")
     s.add_argument("--usage-db", default=""); s.add_argument("--memory-spool", default="", help="file opened at start-up that receives the ledger's state when an allocation fails"); s.add_argument("--kv-format", default="auto", choices=["auto", "bf16", "fp8_ds_mla"])
+    s.add_argument("--loop-abort-run", type=int, default=int(os.environ.get("CUTEAFD_LOOP_ABORT_RUN", 512)),
+                   help="end a response (finish_reason length, finish_detail repetition) after this many consecutive "
+                        "32-token shingles that repeat a block longer than 256 tokens; 0 = off")
+    s.add_argument("--loop-abort-copies", type=int, default=int(os.environ.get("CUTEAFD_LOOP_ABORT_COPIES", 8)),
+                   help="verbatim copies of a long block that count as a loop")
+    s.add_argument("--loop-fast-span", type=int, default=int(os.environ.get("CUTEAFD_LOOP_FAST_SPAN", 1024)),
+                   help="short-cycle rule: tokens the copies after the first must span; 0 = off")
+    s.add_argument("--loop-fast-copies", type=int, default=int(os.environ.get("CUTEAFD_LOOP_FAST_COPIES", 8)),
+                   help="identical copies of a short unit (1..256 tokens) that count as a loop")
+    s.add_argument("--speculation-trace", default="", help="JSONL file, one record per decode round (also $SPECULATION_TRACE); "
+                                                            "written by a bounded background writer that drops, never blocks")
+    s.add_argument("--stall-dump-seconds", type=float, default=0.0,
+                   help="write every thread's stack when requests are in flight and the loop has not ticked for this long; 0 = off")
+    s.add_argument("--stack-dump-file", default="", help="where SIGUSR1 and stall dumps go (default: stderr)")
     s.add_argument("--prewarm", default="", help="JSON list of decode step geometries: read at start, rewritten at exit")
     s.add_argument("--media", default="none", choices=["none", "auto", "random"],
                    help="auto: load the vision / audio towers the snapshot bundles; random: small random-init towers")

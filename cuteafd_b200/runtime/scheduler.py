@@ -74,6 +74,8 @@ class Active:
     spec: dict = field(default_factory=lambda: {"proposed": 0, "accepted": 0, "cycles": 0})
     first_token_at: float = 0.0
     stalled: bool = False
+    guard: Any = None                  # RepeatGuard (loop abort), None when the detector is off
+    finish_detail: str = ""
 
 
 @dataclass
@@ -92,13 +94,17 @@ class SchedulerStats:
     lane_rounds: dict = field(default_factory=dict)
     stalls: int = 0
     quarantined: int = 0
+    loop_aborts: int = 0
 
 
 class Scheduler:
     def __init__(self, backend: Backend, *, max_active: int = 32, queue_depth: int = 64, queue_wait_s: float = 30.0,
                  decode_share: float = 0.2, drafter=None, draft_control: str = "history", row_budget: int | None = None,
-                 eos_ids: tuple[int, ...] = (), decode_lanes: int = 1):
+                 eos_ids: tuple[int, ...] = (), decode_lanes: int = 1, loop_abort=None):
         self.be = backend
+        self.loop_abort = loop_abort          # LoopAbortConfig or None (runtime/repeat_guard.py)
+        self.trace = None                     # utils.trace.JsonlTrace: one record per decode round when set
+        self.watchdog = None                  # utils.diagnostics.StallWatchdog: beaten every step when set
         # Decode lanes: 1 or 2 independent decode batches served in turn on the one engine thread.  A request stays in
         # the lane it was assigned when its prefill finished; each lane keeps its own batch geometry (its own decode
         # graphs).  On a disaggregated deployment lane A's attention overlaps lane B's expert exchange
@@ -158,6 +164,9 @@ class Scheduler:
 
     def step(self) -> bool:
         """One scheduling iteration.  Returns False when there was nothing to do."""
+        if self.watchdog is not None:
+            self.watchdog.beat()
+            self.watchdog.busy(len(self.prefilling) + len(self.decoding))
         self._drain_queue()
         self._admit()
         # While both kinds of work exist, decode gets ``decode_share`` of the measured step time and
@@ -221,6 +230,7 @@ class Scheduler:
             if req.media:
                 handle.media = req.media
             a = Active(req, handle, cached, prompt_done=cached, kv_len=cached)
+            a.guard = self.loop_abort.guard() if self.loop_abort is not None else None
             self.prefilling.append(a)
             self.stats.admitted += 1
             self.stats.cached_tokens += cached
@@ -376,6 +386,8 @@ class Scheduler:
         self.stats.verify_row_hist[n_rows] = self.stats.verify_row_hist.get(n_rows, 0) + 1
         off = 0
         done: list[Active] = []
+        t_round = time.monotonic()
+        acc_round: list[int] = []
         for a, plan, d, r, hs in zip(runnable, plans, drafts, rows, heads):
             sel = []
             bad = False
@@ -412,8 +424,14 @@ class Scheduler:
             a.spec["proposed"] += len(d)
             a.spec["accepted"] += n_acc
             a.spec["cycles"] += 1
+            acc_round.append(n_acc)
             if stopped:
                 done.append(a)
+        if self.trace is not None:
+            self.trace.record(round=self.stats.decode_rounds, requests=[a.req.rid for a in runnable], rows=n_rows,
+                              proposed=[len(d) for d in drafts], kept=[p.keep for p in plans], copied=[p.copy for p in plans],
+                              accepted=acc_round, on_device=picked is not None, finished=len(done),
+                              select_ms=round((time.monotonic() - t_round) * 1e3, 3))
         self.decoding = [a for a in self.decoding if a not in done]
         return True
 
@@ -448,6 +466,10 @@ class Scheduler:
             if len(a.generated) >= a.req.max_tokens:
                 finish = "length"
                 break
+            if a.guard is not None and a.guard.push(t):
+                finish, a.finish_detail = "length", "repetition"      # an exact loop ends like max_tokens
+                self.stats.loop_aborts += 1
+                break
         a.last_token = a.generated[-1]
         self.stats.emitted_tokens += len(out)
         a.req.events.put(("tokens", out))
@@ -465,6 +487,8 @@ class Scheduler:
         if reason is not None:
             usage = {"prompt_tokens": len(a.req.prompt), "completion_tokens": len(a.generated), "cached_tokens": a.cached,
                      "speculation": dict(a.spec, request_id=a.req.rid)}
+            if a.finish_detail:
+                usage["finish_detail"] = a.finish_detail
             a.req.events.put(("done", reason, usage, list(a.row_hashes)))
             self.stats.finished += 1
         else:
@@ -495,7 +519,7 @@ class Scheduler:
                 "admitted": s.admitted, "finished": s.finished, "failed": s.failed, "rejected": s.rejected,
                 "prefill_tokens": s.prefill_tokens, "cached_tokens": s.cached_tokens, "decode_rounds": s.decode_rounds,
                 "emitted_tokens": s.emitted_tokens, "verify_rows": s.verify_rows, "stalls": s.stalls,
-                "quarantined": s.quarantined, "draft_policy": dict(self.policy.lifetime),
+                "quarantined": s.quarantined, "loop_aborts": s.loop_aborts, "draft_policy": dict(self.policy.lifetime),
                 "kv": {"total_pages": self.reserve.total, "leased_pages": self.reserve.leased}}
 
 

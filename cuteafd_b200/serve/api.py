@@ -118,6 +118,8 @@ def usage_block(u: dict) -> dict:
            "prompt_tokens_details": {"cached_tokens": u.get("cached_tokens", 0)}}
     if "speculation" in u:
         out["speculation"] = u["speculation"]
+    if u.get("finish_detail"):
+        out["finish_detail"] = u["finish_detail"]            # "repetition": the loop detector ended the reply
     return out
 
 

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import hmac
 import json
+import os
 import threading
 import time
 import uuid
@@ -386,8 +387,20 @@ def build_state(args) -> ServerState:
     if args.speculator in ("auto", "mtp") and getattr(be, "has_mtp", False):
         from ..runtime.speculation import MtpDrafter
         drafter = MtpDrafter()              # native MTP depth of the checkpoint
+    from ..runtime.repeat_guard import LoopAbortConfig
+    loop = LoopAbortConfig(getattr(args, "loop_abort_run", 512), getattr(args, "loop_abort_copies", 8),
+                           getattr(args, "loop_fast_span", 1024), getattr(args, "loop_fast_copies", 8))
     sched = Scheduler(be, max_active=args.concurrency, queue_depth=args.queue_depth, queue_wait_s=args.queue_wait,
+                      loop_abort=loop if loop.enabled else None,
                       drafter=drafter, eos_ids=tuple(getattr(tok, "eos_ids", ())))
+    trace_path = getattr(args, "speculation_trace", "") or os.environ.get("SPECULATION_TRACE", "")
+    if trace_path:
+        from ..utils.trace import JsonlTrace
+        sched.trace = JsonlTrace(trace_path)
+    stall_s = float(getattr(args, "stall_dump_seconds", 0) or 0)
+    if stall_s > 0:
+        from ..utils.diagnostics import StallWatchdog
+        sched.watchdog = StallWatchdog(stall_s, getattr(args, "stack_dump_file", "") or None).start()
     usage = UsageLog(args.usage_db) if args.usage_db else None
     media = None
     if getattr(args, "media", "none") != "none":
@@ -406,6 +419,8 @@ def build_state(args) -> ServerState:
 
 def run_server(args) -> int:
     state = build_state(args)
+    from ..utils.diagnostics import install_stack_dump
+    install_stack_dump(getattr(args, "stack_dump_file", "") or None)      # kill -USR1 <pid>: every thread's stack
     srv = Server(state, args.host, args.port).start()
     print(f"serving {state.model_id} on http://{args.host}:{srv.port}", flush=True)
     try:
@@ -413,6 +428,8 @@ def run_server(args) -> int:
             time.sleep(3600)
     except KeyboardInterrupt:
         srv.stop()
+        if state.sched.trace is not None:
+            state.sched.trace.close()
         be = state.sched.be
         if getattr(args, "prewarm", "") and hasattr(be, "save_prewarm"):
             be.save_prewarm(args.prewarm)        # the next start captures this run's frequent geometries up front

@@ -1,0 +1,52 @@
+"""Stack dumps, stall watchdog and host heap monitor (host only)."""
+import os
+import signal
+import threading
+import time
+
+from cuteafd_b200.utils.diagnostics import HostHeapMonitor, StallWatchdog, format_stacks, install_stack_dump, resident_bytes
+
+
+def test_stack_dump_names_threads_and_signal_writes_file(tmp_path):
+    ev = threading.Event()
+    t = threading.Thread(target=ev.wait, name="parked-worker", daemon=True)
+    t.start()
+    text = format_stacks()
+    assert "parked-worker" in text and "MainThread" in text and "ev.wait" not in text.split("parked-worker")[0]
+    path = str(tmp_path / "stacks.txt")
+    assert install_stack_dump(path)
+    os.kill(os.getpid(), signal.SIGUSR1)
+    for _ in range(100):
+        if os.path.exists(path) and "parked-worker" in open(path).read():
+            break
+        time.sleep(0.02)
+    assert "parked-worker" in open(path).read()
+    ev.set()
+    signal.signal(signal.SIGUSR1, signal.SIG_DFL)
+
+
+def test_watchdog_dumps_once_per_stall_and_only_when_busy(tmp_path):
+    now = [0.0]
+    wd = StallWatchdog(limit_s=5.0, path=str(tmp_path / "stall.txt"), clock=lambda: now[0])
+    now[0] = 10.0
+    assert not wd.check()                       # idle: a quiet loop is not a stall
+    wd.busy(3)
+    assert wd.check() and wd.stalls == 1
+    now[0] = 20.0
+    assert not wd.check()                       # still the same stall: one dump
+    wd.beat()
+    now[0] = 22.0
+    assert not wd.check()
+    now[0] = 26.0
+    assert wd.check() and wd.stalls == 2
+    assert open(str(tmp_path / "stall.txt")).read().count("==== stack dump") == 2
+
+
+def test_host_heap_monitor_warns_once():
+    assert resident_bytes() > 0
+    vals = iter([1 << 30, 3 << 30, 4 << 30])
+    msgs = []
+    m = HostHeapMonitor(limit_bytes=2 << 30, pinned=lambda: 1 << 20, read=lambda: next(vals), log=msgs.append)
+    assert m.sample()["resident_bytes"] == 1 << 30 and not msgs
+    m.sample(); m.sample()
+    assert len(msgs) == 1 and m.peak == 4 << 30

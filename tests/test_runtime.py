@@ -341,3 +341,74 @@ def test_prompt_packing_matches_one_at_a_time():
     alone, p1 = serve(1)
     packed, p5 = serve(5)
     assert alone == packed and p1 == 0 and p5 >= 1
+
+
+def test_repeat_guard_rules():
+    """Rule F (short cycles) and rule R (long blocks) fire where their definitions say, and not on ordinary text."""
+    import random
+    from cuteafd_b200.runtime.repeat_guard import LoopAbortConfig, RepeatGuard
+    rnd = random.Random(0)
+
+    def fires_at(tokens_of, cfg=LoopAbortConfig()):
+        g, i = RepeatGuard(cfg), 0
+        while not g.push(tokens_of(i)):
+            i += 1
+            assert i < 100000
+        return g.pushed, g.hit
+    assert fires_at(lambda i: 7) == (1025, {"rule": "fast", "period": 1, "at": 1025})
+    blk = [rnd.randrange(50000) for _ in range(40)]
+    assert fires_at(lambda i: blk[i % 40])[0] == 40 + 1024
+    big = [rnd.randrange(50000) for _ in range(300)]
+    n, hit = fires_at(lambda i: big[i % 300])
+    assert n == 7 * 300 + 543 and hit["rule"] == "repeat" and hit["period"] == 300
+    # each rule has its own off switch
+    n, hit = fires_at(lambda i: big[i % 300], LoopAbortConfig(run=64, copies=3, fast_span=0))
+    assert hit["rule"] == "repeat" and n == 2 * 300 + 31 + 64
+    g = RepeatGuard(LoopAbortConfig(run=0, fast_span=1024))
+    assert not any(g.push(big[i % 300]) for i in range(5000))
+    assert LoopAbortConfig(run=0, fast_span=0).guard() is None
+    # ordinary text, and a 400-token run of one value inside it, pass
+    g = RepeatGuard()
+    text = [rnd.randrange(1, 50000) for _ in range(3000)]
+    assert not any(g.push(t) for t in text[:1500] + [0] * 400 + text[1500:])
+
+
+def test_scheduler_ends_a_looping_reply(oracle):
+    from cuteafd_b200.runtime.repeat_guard import LoopAbortConfig
+    cfg, params = oracle
+
+    class OnlyToken:                       # a constraint that leaves one token: the reply is a period-1 loop
+        def mask(self):
+            m = torch.zeros(cfg.vocab_size, dtype=torch.bool)
+            m[5] = True
+            return m
+
+        def advance(self, tok): pass
+        def finished(self): return False
+
+    sched = Scheduler(OracleBackend(cfg, params), loop_abort=LoopAbortConfig(run=0, fast_span=24, fast_copies=4))
+    out = _run(sched, [Request([1, 2, 3], max_tokens=200, constraint=OnlyToken())])[0]
+    assert out["finish"] == "length" and len(out["tokens"]) == 25 and set(out["tokens"]) == {5}
+    assert out["usage"]["finish_detail"] == "repetition" and sched.snapshot()["loop_aborts"] == 1
+    # with the detector off the same request runs to max_tokens
+    off = _run(Scheduler(OracleBackend(cfg, params)), [Request([1, 2, 3], max_tokens=40, constraint=OnlyToken())])[0]
+    assert len(off["tokens"]) == 40 and "finish_detail" not in off["usage"]
+
+
+def test_speculation_trace_and_watchdog_hooks(oracle, tmp_path):
+    import json
+    from cuteafd_b200.utils.diagnostics import StallWatchdog
+    from cuteafd_b200.utils.trace import JsonlTrace
+    cfg, params = oracle
+    sched = Scheduler(OracleBackend(cfg, params), drafter=speculation.NgramDrafter(block=4))
+    path = str(tmp_path / "rounds.jsonl")
+    sched.trace = JsonlTrace(path)
+    sched.watchdog = StallWatchdog(limit_s=1000.0)
+    pattern = [3, 9, 4, 7, 1, 8]
+    out = _run(sched, [Request((pattern * 12)[:64], max_tokens=12)])[0]
+    sched.trace.close()
+    recs = [json.loads(l) for l in open(path)]
+    assert len(recs) == sched.stats.decode_rounds and sched.trace.dropped == 0
+    assert sum(sum(r["accepted"]) + len(r["accepted"]) for r in recs) >= len(out["tokens"]) - 1   # the first token came from prefill
+    assert all({"round", "requests", "rows", "proposed", "accepted", "kept", "copied", "ts"} <= set(r) for r in recs)
+    assert sched.watchdog.stalls == 0 and sched.watchdog._busy == 0        # the last step saw an empty engine
