@@ -513,13 +513,33 @@ class Scheduler:
         except Exception:
             pass
 
+    def lanes(self) -> list[dict]:
+        """One row per request in flight (console view; read from another thread, so lists are copied first)."""
+        now = time.monotonic()
+        out = []
+        for phase, group in (("prefill", list(self.prefilling)), ("decode", list(self.decoding))):
+            for a in group:
+                prop = a.spec["proposed"]
+                out.append({"rid": a.req.rid, "phase": "stalled" if a.stalled else phase,
+                            "lane": a.req.rid % self.decode_lanes, "prompt_tokens": len(a.req.prompt),
+                            "prompt_done": a.prompt_done, "cached_tokens": a.cached, "generated": len(a.generated),
+                            "max_tokens": a.req.max_tokens, "kv_len": a.kv_len, "cycles": a.spec["cycles"],
+                            "acceptance": round(a.spec["accepted"] / prop, 3) if prop else None,
+                            "tokens_per_cycle": round(len(a.generated) / a.spec["cycles"], 2) if a.spec["cycles"] else None,
+                            "age_s": round(now - a.req.arrival, 2),
+                            "ttft_s": round(a.first_token_at - a.req.arrival, 3) if a.first_token_at else None})
+        return out
+
     def snapshot(self) -> dict:
         s = self.stats
         return {"active": len(self.decoding), "prefilling": len(self.prefilling), "queued": len(self.pending) + self.waiting.qsize(),
                 "admitted": s.admitted, "finished": s.finished, "failed": s.failed, "rejected": s.rejected,
                 "prefill_tokens": s.prefill_tokens, "cached_tokens": s.cached_tokens, "decode_rounds": s.decode_rounds,
                 "emitted_tokens": s.emitted_tokens, "verify_rows": s.verify_rows, "stalls": s.stalls,
-                "quarantined": s.quarantined, "loop_aborts": s.loop_aborts, "draft_policy": dict(self.policy.lifetime),
+                "quarantined": s.quarantined, "loop_aborts": s.loop_aborts, "packed_steps": s.packed_steps,
+                "verify_row_hist": dict(s.verify_row_hist), "lane_rounds": dict(s.lane_rounds),
+                "time_share": {"prefill": round(self._t_prefill, 4), "decode": round(self._t_decode, 4)},
+                "draft_policy": dict(self.policy.lifetime),
                 "kv": {"total_pages": self.reserve.total, "leased_pages": self.reserve.leased}}
 
 

@@ -20,13 +20,6 @@ from ..runtime.scheduler import FAIL_BAD_REQUEST, FAIL_UNAVAILABLE, Request, Sch
 from . import api, ws
 from .tokenizer import StreamDecoder
 
-CONSOLE_HTML = """<!doctype html><title>cuteafd_b200 console</title>
-<style>body{font:14px monospace;margin:2em}pre{background:#111;color:#9f9;padding:1em}</style>
-<h3>cuteafd_b200</h3><pre id=s>loading</pre>
-<script>async function t(){const r=await fetch('/v1/stats');document.getElementById('s').textContent=
-JSON.stringify(await r.json(),null,1)}t();setInterval(t,1000)</script>"""
-
-
 class ServerState:
     def __init__(self, scheduler: Scheduler, tokenizer, model_id: str, api_key: str = "", usage=None, extras=None, media=None):
         self.sched, self.tok, self.model_id, self.api_key = scheduler, tokenizer, model_id, api_key
@@ -110,7 +103,8 @@ def make_handler(state: ServerState):
                 ok = state.sched.ready.is_set()
                 return self._json(200 if ok else 503, {"status": "ok" if ok else "starting", "model": state.model_id})
             if path in ("/", "/v1/console"):
-                raw = CONSOLE_HTML.encode()
+                from .console import PAGE
+                raw = PAGE.encode()
                 self.send_response(200)
                 self.send_header("Content-Type", "text/html")
                 self.send_header("Content-Length", str(len(raw)))
@@ -121,6 +115,14 @@ def make_handler(state: ServerState):
             if path == "/v1/models":
                 return self._json(200, {"object": "list", "data": [{"id": state.model_id, "object": "model", "created": int(state.started),
                                                                       "owned_by": "cuteafd_b200"}]})
+            if path == "/v1/console/state":
+                from .console import console_state
+                return self._json(200, console_state(state))
+            if path == "/console/memory":
+                from ..utils.memory_ledger import LEDGER
+                return self._json(200, LEDGER.report())
+            if path == "/console/experts":
+                return self._json(200, state.extras.get("expert_usage", lambda: {})())
             if path == "/v1/stats":
                 s = state.sched.snapshot()
                 be = state.sched.be
@@ -142,7 +144,19 @@ def make_handler(state: ServerState):
             if path == "/experts":
                 return self._json(200, state.extras.get("expert_usage", lambda: {})())
             if path.startswith("/console/usage"):
-                return self._json(200, state.usage.summary(24.0) if state.usage else {})
+                if not state.usage:
+                    return self._json(200, {})
+                q = dict(p.split("=", 1) for p in self.path.partition("?")[2].split("&") if "=" in p)
+                tail = path[len("/console/usage"):].strip("/")
+                if tail == "hourly":
+                    return self._json(200, {"hourly": state.usage.hourly(int(q.get("hours", 24)))})
+                if tail == "requests":
+                    before = int(q["before"]) if "before" in q else None
+                    return self._json(200, {"requests": state.usage.requests(int(q.get("limit", 50)), before)})
+                if tail.startswith("request/"):
+                    one = state.usage.request(int(tail.split("/", 1)[1])) if tail.split("/", 1)[1].isdigit() else None
+                    return self._json(200, one) if one else self._json(404, {"error": {"message": "no such request"}})
+                return self._json(200, state.usage.summary(float(q.get("hours", 24.0))))
             if path.startswith("/v1/responses/") and path.endswith("/input_items"):
                 with state.lock:
                     conv = state.sessions.get(path.split("/")[3])
@@ -201,6 +215,7 @@ def make_handler(state: ServerState):
             t0 = time.time()
             state.sched.submit(req)
             model = body.get("model") or state.model_id
+            self._acct = (model, flavor, t0, body)
             try:
                 if body.get("stream"):
                     self._stream(req, model, flavor)
@@ -213,16 +228,26 @@ def make_handler(state: ServerState):
             """Yield ("text", str) / ("done", finish, usage, rows) / ("error", kind, msg)."""
             dec = StreamDecoder(state.tok)
             eos = set(getattr(state.tok, "eos_ids", ()))
+            said: list[str] = []
+            first = None
             while True:
                 ev = req.events.get()
                 if ev[0] == "tokens":
+                    first = first or time.time()
                     text = dec.push([t for t in ev[1] if t not in eos])
                     if text:
+                        said.append(text)
                         yield ("text", text)
                 elif ev[0] == "done":
                     tail = dec.flush()
                     if tail:
+                        said.append(tail)
                         yield ("text", tail)
+                    acct = getattr(self, "_acct", None)
+                    if state.usage and acct and ev[1] != "cancelled":       # streamed and plain replies both land here
+                        model, flavor, t0, body = acct
+                        state.usage.record(model, flavor, ev[2], time.time() - t0, ev[1], request=body, reply="".join(said),
+                                           ttft=(first - t0) if first else None, client=self.client_address[0])
                     yield ev
                     return
                 else:
@@ -241,8 +266,6 @@ def make_handler(state: ServerState):
                 return self._json(st, eb, hd)
             _, finish, usage, rows = final
             out_text = "".join(text)
-            if state.usage:
-                state.usage.record(model, flavor, usage, time.time() - t0, finish)
             if flavor == "anthropic":
                 return self._json(200, api.anthropic_message(model, out_text, finish, usage))
             if flavor == "responses":

@@ -278,3 +278,42 @@ def test_responses_sessions(server):
     assert call(server, "DELETE", f"/v1/responses/{a['id']}")[0] == 200
     assert call(server, "GET", f"/v1/responses/{a['id']}/input_items")[0] == 404
     assert call(server, "POST", "/v1/responses", {"input": "x", "previous_response_id": a["id"]})[0] == 400
+
+
+def test_console_state_and_usage_log(server):
+    """The console document carries the live sections, and streamed replies are accounted like plain ones."""
+    st, hd, raw = call(server, "GET", "/")
+    assert st == 200 and b"/v1/console/state" in raw
+    body = {"messages": [{"role": "user", "content": "count to three"}], "max_tokens": 6, "stream": True}
+    st, _, raw = call(server, "POST", "/v1/chat/completions", body)
+    assert st == 200 and b"[DONE]" in raw
+    doc = json.loads(call(server, "GET", "/v1/console/state")[2])
+    assert {"lanes", "pipeline", "drafts", "memory", "thermal", "usage"} <= set(doc) and doc["ready"] is True
+    assert doc["pipeline"]["finished"] >= 1 and doc["pipeline"]["kv"]["total_pages"] > 0 and isinstance(doc["lanes"], list)
+    rows = json.loads(call(server, "GET", "/console/usage/requests?limit=3")[2])["requests"]
+    assert rows and rows[0]["api"] == "openai" and rows[0]["completion_tokens"] >= 1 and rows[0]["ttft"] is not None
+    one = json.loads(call(server, "GET", f"/console/usage/request/{rows[0]['id']}")[2])
+    assert one["logged"] and "count to three" in one["request"] and isinstance(one["reply"], str)
+    hourly = json.loads(call(server, "GET", "/console/usage/hourly?hours=2")[2])["hourly"]
+    assert len(hourly) == 2 and hourly[-1]["requests"] >= 1
+    assert call(server, "GET", "/console/usage/request/999999")[0] == 404
+    assert json.loads(call(server, "GET", "/console/memory")[2])["tracked_bytes"] >= 0
+
+
+def test_usage_log_prunes_bodies_after_a_day(tmp_path):
+    from cuteafd_b200.serve.usage import UsageLog
+    now = [1_000_000.0]
+    log = UsageLog(str(tmp_path / "u.sqlite"), clock=lambda: now[0])
+    a = log.record("m", "openai", {"prompt_tokens": 10, "completion_tokens": 4, "cached_tokens": 5,
+                                   "speculation": {"proposed": 8, "accepted": 6}}, 0.5, "stop", request={"x": 1}, reply="hi", ttft=0.1)
+    now[0] += 25 * 3600
+    b = log.record("m", "anthropic", {"prompt_tokens": 20, "completion_tokens": 2, "finish_detail": "repetition"}, 0.2, "length",
+                   request="raw body", reply="yo")
+    log.prune()
+    assert log.request(a)["logged"] is False and log.request(b)["reply"] == "yo"       # accounting rows stay, bodies go
+    s = log.summary(48)
+    assert s["requests"] == 2 and s["draft_acceptance"] == 0.75 and s["loop_aborts"] == 1 and s["by_api"] == {"openai": 1, "anthropic": 1}
+    assert log.summary(1)["requests"] == 1 and log.summary(1)["cached_share"] == 0.0
+    assert [r["id"] for r in log.requests(10)] == [b, a] and [r["id"] for r in log.requests(10, before_id=b)] == [a]
+    # a second handle on the same file sees the rows (the command-line report reads while the server writes)
+    assert UsageLog(str(tmp_path / "u.sqlite"), clock=lambda: now[0]).summary(48)["requests"] == 2
