@@ -1,6 +1,8 @@
 """Standalone protocol gateway: accepts Anthropic Messages and OpenAI Responses requests and
 forwards them as OpenAI Chat Completions to an upstream server, translating the reply back.
-A model-name map renames client model ids.  (The in-process server already speaks all three
+A model-name map renames client model ids.  Hosted web search (``serve/search.py``): when the client declares a
+server-side search tool the gateway runs the searches the model asks for, and ``POST /v1/alpha/search`` serves the
+search / open / find / time commands of client-executed search extensions.  (The in-process server already speaks all three
 protocols; the gateway exists for fronting any OpenAI-compatible upstream.)
 
 Counterpart: rust/crates/cuteafd-api/src/gateway/mod.rs:1-60,148,215-216 and
@@ -14,7 +16,7 @@ import urllib.error
 import urllib.request
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 
-from . import api
+from . import api, search
 
 
 def to_chat_body(body: dict, flavor: str, model_map: dict[str, str]) -> dict:
@@ -98,7 +100,32 @@ class Tape:
         return rec["status"], rec["reply"]
 
 
-def make_gateway(upstream: str, model_map: dict[str, str], tape: "Tape | None" = None):
+class _UpstreamFailed(Exception):
+    pass
+
+
+def attach_searches(out: dict, flavor: str, ran: list[dict]) -> None:
+    """Show the client the searches the gateway ran for it, in its own protocol's block types."""
+    if flavor == "anthropic":
+        blocks = []
+        for i, r in enumerate(ran):
+            tid = f"srvtoolu_{i}"
+            blocks.append({"type": "server_tool_use", "id": tid, "name": "web_search", "input": {"query": r["query"]}})
+            blocks.append({"type": "web_search_tool_result", "tool_use_id": tid,
+                           "content": [{"type": "web_search_result", "url": h["url"], "title": h["title"],
+                                        "page_age": h.get("published")} for h in r["results"]]})
+        out["content"] = blocks + out.get("content", [])
+        out.setdefault("usage", {})["server_tool_use"] = {"web_search_requests": len(ran)}
+    else:
+        items = [{"type": "web_search_call", "id": f"ws_{i}", "status": "completed", "action": {"type": "search", "query": r["query"]}}
+                 for i, r in enumerate(ran)]
+        out["output"] = items + out.get("output", [])
+
+
+def make_gateway(upstream: str, model_map: dict[str, str], tape: "Tape | None" = None, provider=None):
+    sessions: dict = {}
+    sessions_lock = threading.Lock()
+
     class H(BaseHTTPRequestHandler):
         protocol_version = "HTTP/1.1"
 
@@ -122,42 +149,80 @@ def make_gateway(upstream: str, model_map: dict[str, str], tape: "Tape | None" =
             except urllib.error.URLError as e:
                 return self._json(503, {"error": {"message": f"upstream unavailable: {e}"}})
 
-        def do_POST(self):
-            flavor = {"/v1/messages": "anthropic", "/v1/responses": "responses"}.get(self.path.split("?")[0])
-            n = int(self.headers.get("Content-Length", "0") or 0)
-            try:
-                body = json.loads(self.rfile.read(n) or b"{}")
-            except json.JSONDecodeError:
-                return self._json(400, {"error": {"message": "invalid JSON"}})
-            fwd = to_chat_body(body, flavor, model_map) if flavor else body
-            fpath = "/v1/chat/completions" if flavor else self.path
+        def _session(self, body: dict) -> "search.SearchSession":
+            key = (self.headers.get("Authorization", ""), str(body.get("session_id") or body.get("previous_response_id") or ""))
+            with sessions_lock:
+                if len(sessions) > 1024:
+                    sessions.clear()
+                return sessions.setdefault(key, search.SearchSession())
+
+        def _chat(self, fpath: str, fwd: dict) -> tuple[int, dict, dict]:
+            """One upstream exchange (or its recording): (status, reply, headers to pass on)."""
             if tape is not None and tape.mode == "replay":
                 hit = tape.fetch(fpath, fwd)
                 if hit is None:
-                    return self._json(404, {"error": {"message": "no recorded exchange for this request", "type": "replay_miss"}})
-                st, reply = hit
-                return self._json(st, from_chat_reply(reply, flavor, body.get("model", "")) if (flavor and st == 200) else reply)
-            req = urllib.request.Request(upstream + ("/v1/chat/completions" if flavor else self.path), json.dumps(fwd).encode(),
+                    return 404, {"error": {"message": "no recorded exchange for this request", "type": "replay_miss"}}, {}
+                return hit[0], hit[1], {}
+            req = urllib.request.Request(upstream + fpath, json.dumps(fwd).encode(),
                                          {"Content-Type": "application/json", "Authorization": self.headers.get("Authorization", "")})
             try:
                 with urllib.request.urlopen(req, timeout=600) as r:
                     reply = json.loads(r.read())
             except urllib.error.HTTPError as e:
                 hd = {"Retry-After": e.headers["Retry-After"]} if e.headers.get("Retry-After") else {}
-                return self._json(e.code, json.loads(e.read() or b"{}"), hd)
+                return e.code, json.loads(e.read() or b"{}"), hd
             except urllib.error.URLError as e:
-                return self._json(503, {"error": {"message": f"upstream unavailable: {e}"}})
+                return 503, {"error": {"message": f"upstream unavailable: {e}"}}, {}
             if tape is not None:
                 tape.store(fpath, fwd, 200, reply)
-            return self._json(200, from_chat_reply(reply, flavor, body.get("model", "")) if flavor else reply)
+            return 200, reply, {}
+
+        def do_POST(self):
+            path = self.path.split("?")[0]
+            flavor = {"/v1/messages": "anthropic", "/v1/responses": "responses"}.get(path)
+            n = int(self.headers.get("Content-Length", "0") or 0)
+            try:
+                body = json.loads(self.rfile.read(n) or b"{}")
+            except json.JSONDecodeError:
+                return self._json(400, {"error": {"message": "invalid JSON"}})
+            if path == "/v1/alpha/search":
+                return self._json(200, search.alpha_search(provider, self._session(body), body))
+            fwd = to_chat_body(body, flavor, model_map) if flavor else body
+            fpath = "/v1/chat/completions" if flavor else self.path
+            decl = search.wants_hosted_search(body) if flavor else None
+            ran: list[dict] = []
+            if decl is not None and provider is not None:
+                failed: list = []
+
+                def chat(b: dict) -> dict:
+                    st, reply, hd = self._chat(fpath, b)
+                    if st != 200:
+                        failed.append((st, reply, hd))
+                        raise _UpstreamFailed()
+                    return reply
+                try:
+                    reply, ran = search.run_tool_loop(chat, fwd, decl, provider, self._session(body))
+                except _UpstreamFailed:
+                    st, reply, hd = failed[0]
+                    return self._json(st, reply, hd)
+            else:
+                st, reply, hd = self._chat(fpath, fwd)
+                if st != 200:
+                    return self._json(st, reply, hd)
+            if not flavor:
+                return self._json(200, reply)
+            out = from_chat_reply(reply, flavor, body.get("model", ""))
+            if ran:
+                attach_searches(out, flavor, ran)
+            return self._json(200, out)
 
     return H
 
 
 class Gateway:
     def __init__(self, upstream: str, host: str = "127.0.0.1", port: int = 0, model_map: dict[str, str] | None = None,
-                 tape: Tape | None = None):
-        self.httpd = ThreadingHTTPServer((host, port), make_gateway(upstream.rstrip("/"), model_map or {}, tape))
+                 tape: Tape | None = None, provider=None):
+        self.httpd = ThreadingHTTPServer((host, port), make_gateway(upstream.rstrip("/"), model_map or {}, tape, provider))
         self.httpd.daemon_threads = True
         self.port = self.httpd.server_address[1]
         self.thread = threading.Thread(target=self.httpd.serve_forever, daemon=True)
@@ -179,7 +244,9 @@ def run_gateway(args) -> int:
         tape = Tape(args.record, "record")
     elif getattr(args, "replay", ""):
         tape = Tape(args.replay, "replay")
-    gw = Gateway(args.upstream, args.host, args.port, mm, tape).start()
+    import os
+    provider = search.provider_from_env(dict(os.environ))        # EXA_API_KEY / SEARXNG_URL
+    gw = Gateway(args.upstream, args.host, args.port, mm, tape, provider).start()
     print(f"gateway on http://{args.host}:{gw.port} -> {args.upstream}", flush=True)
     try:
         while True:
