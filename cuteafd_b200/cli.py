@@ -276,7 +276,12 @@ def _build_parser() -> argparse.ArgumentParser:
     s.set_defaults(fn=cmd_serve)
 
     e = sub.add_parser("expertd", help="expert-rank worker")
-    e.add_argument("--snapshot", default=""); e.add_argument("--rank", type=int, required=True); e.add_argument("--world", type=int, required=True)
+    e.add_argument("--snapshot", default=""); e.add_argument("--rank", type=int, default=1); e.add_argument("--world", type=int, default=2)
+    e.add_argument("--tcp-port", type=int, default=None,
+                   help="serve over the TCP wire protocol instead of joining the box's NVLink group (a worker on another host); 0 = any port")
+    e.add_argument("--experts", default="", help="with --tcp-port: first:end of the expert ids this worker holds")
+    e.add_argument("--host", default="127.0.0.1", help="with --tcp-port: address to listen on")
+    e.add_argument("--device", default="cpu", help="with --tcp-port: device the experts run on")
     e.add_argument("--master-addr", default="127.0.0.1"); e.add_argument("--master-port", type=int, default=29500)
     e.add_argument("--deployment", default="")
     e.set_defaults(fn=cmd_expertd)

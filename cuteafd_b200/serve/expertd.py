@@ -11,7 +11,39 @@ import json
 import os
 
 
+def run_tcp_worker(args) -> int:
+    """Off-box worker: serves experts [first, end) of a snapshot over the wire protocol (``parallel/wire.py``).  The
+    experts run as plain tensor code on ``--device``; the plan hash covers the model name and the expert range, so an
+    attention rank configured for another split is refused at the handshake."""
+    import time
+
+    import torch
+
+    from ..loader.load import load_params
+    from ..parallel import wire
+    lo, hi = (int(v) for v in args.experts.split(":"))
+    cfg, params = load_params(args.snapshot, dtype=torch.bfloat16, device=args.device, only=".mlp.experts.")
+    stacks: dict[int, tuple] = {}
+
+    def stack_of(layer: int):
+        if layer not in stacks:
+            m = f"model.layers.{layer}.mlp.experts."
+            stacks[layer] = tuple(torch.stack([params[f"{m}{e}.{n}_proj.weight"] for e in range(lo, hi)]) for n in ("gate", "up", "down"))
+        return stacks[layer]
+    plan = wire.plan_hash({"model": cfg.name, "experts": cfg.num_experts, "range": [lo, hi]})
+    srv = wire.ExpertServer(wire.reference_compute(stack_of, lo), plan, args.host, args.tcp_port).start()
+    print(f"expert worker for experts [{lo}, {hi}) of {cfg.name} on {args.host}:{srv.port}", flush=True)
+    try:
+        while True:
+            time.sleep(3600)
+    except KeyboardInterrupt:
+        srv.stop()
+    return 0
+
+
 def run_expertd(args) -> int:
+    if getattr(args, "tcp_port", None) is not None:
+        return run_tcp_worker(args)
     import torch
     import torch.distributed as dist
 
