@@ -90,8 +90,16 @@ def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, f
     max_tokens = body.get("max_tokens") or body.get("max_completion_tokens") or body.get("max_output_tokens") or 256
     if not isinstance(max_tokens, int) or max_tokens < 1:
         raise BadRequest("max_tokens must be a positive integer")
+    fmt = body.get("response_format")
+    if fmt is None:                                        # the guided_* spellings some clients send at the top level
+        if "guided_regex" in body:
+            fmt = {"type": "regex", "pattern": body["guided_regex"]}
+        elif "guided_choice" in body:
+            fmt = {"type": "choice", "choices": body["guided_choice"]}
+        elif "guided_json" in body:
+            fmt = {"type": "json_schema", "schema": body["guided_json"]}
     try:
-        cons = constraints.from_response_format(body.get("response_format"), tok, vocab_size)
+        cons = constraints.from_response_format(fmt, tok, vocab_size)
     except ValueError as e:
         raise BadRequest(str(e)) from e
     return Request(prompt=prompt, max_tokens=max_tokens, params=_params(body), stop_ids=_stops(body, tok),

@@ -240,6 +240,12 @@ def from_response_format(fmt: dict | None, tokenizer, vocab_size: int) -> TokenC
         return TokenConstraint(JsonRecognizer(object_only=True), tokenizer, vocab_size)
     if t == "choice":
         return TokenConstraint(ChoiceRecognizer(list(fmt.get("choices", []))), tokenizer, vocab_size)
+    if t == "regex":
+        from .regex import RegexRecognizer
+        return TokenConstraint(RegexRecognizer(str(fmt.get("pattern") or fmt.get("regex") or "")), tokenizer, vocab_size)
+    if t == "structural_tag":
+        from .regex import StructuralTagRecognizer
+        return TokenConstraint(StructuralTagRecognizer(list(fmt.get("structures") or fmt.get("tags") or [])), tokenizer, vocab_size)
     if t in (None, "text"):
         return None
     raise ValueError(f"unsupported response_format type {t!r}")

@@ -93,3 +93,94 @@ def test_served_request_returns_a_valid_document():
         c.close()
     finally:
         srv.stop()
+
+
+# ---- regular expressions and structural tags ------------------------------------------------------------
+def _accepts(rec, text: str) -> bool:
+    r = rec.clone()
+    return all(r.feed(b) for b in text.encode()) and r.complete()
+
+
+def _prefix_ok(rec, text: str) -> bool:
+    r = rec.clone()
+    return all(r.feed(b) for b in text.encode())
+
+
+def test_regex_recognizer_agrees_with_re_on_full_matches():
+    import itertools
+    import re
+    from cuteafd_b200.serve.regex import RegexRecognizer
+    cases = {
+        r"\d{3}-\d{4}": ["555-1234", "55-1234", "555-12345", ""],
+        r"(yes|no|maybe)!?": ["yes", "no!", "maybe!!", "y", "nope"],
+        r"[A-Z][a-z]+( [A-Z][a-z]+)*": ["Ada Lovelace", "ada", "Ada  Lovelace", "Ada L"],
+        r"[^,\s]+(,[^,\s]+){0,2}": ["a,b,c", "a,b,c,d", "a,,b", "abc"],
+        r"-?(0|[1-9]\d*)(\.\d+)?": ["0", "-12.50", "01", "3.", "-"],
+        r"a{2,}b?": ["a", "aa", "aaaab", "aabb"],
+        r"\w+@\w+\.(com|org)": ["me@site.org", "me@site.net", "@site.com"],
+        r"(?:ab)*c": ["c", "ababc", "abac"],
+        r"\[x\]\.\*": ["[x].*", "x.*"],
+        r"café|naïve": ["café", "naïve", "cafe"],
+    }
+    for pat, texts in cases.items():
+        rec = RegexRecognizer(pat)
+        for t in texts:
+            assert _accepts(rec, t) == bool(re.fullmatch(pat, t)), (pat, t)
+    # prefix property: every prefix of a match is accepted byte by byte, and a dead byte is refused at once
+    rec = RegexRecognizer(r"\d{3}-\d{4}")
+    assert all(_prefix_ok(rec, "555-1234"[:n]) for n in range(9)) and not _prefix_ok(rec, "55a")
+    # exhaustive agreement on short strings over a small alphabet
+    pat = r"(a|bc)*d?"
+    rec = RegexRecognizer(pat)
+    for n in range(6):
+        for tup in itertools.product("abcd", repeat=n):
+            t = "".join(tup)
+            assert _accepts(rec, t) == bool(re.fullmatch(pat, t)), t
+    r = RegexRecognizer(r"ab")
+    assert not r.done and r.feed(ord("a")) and not r.done and r.feed(ord("b")) and r.done
+    r = RegexRecognizer(r"ab*")
+    r.feed(ord("a"))
+    assert r.complete() and not r.done                          # more may follow: the reply ends with end-of-sequence
+    for bad in (r"(a", r"a**?", r"a{5,2}", r"(?=a)b", r"a\1", r"[a", r"*a", r"a{999}", r"[[:alpha:]]"):
+        with pytest.raises(ValueError):
+            RegexRecognizer(bad)
+
+
+def test_structural_tag_recognizer():
+    from cuteafd_b200.serve.regex import StructuralTagRecognizer
+    tags = [{"begin": "<tool_call>", "end": "</tool_call>",
+             "schema": {"type": "object", "properties": {"name": {"enum": ["get_time", "search"]}, "n": {"type": "integer"}},
+                        "required": ["name", "n"]}},
+            {"begin": "<n>", "end": "</n>", "schema": {"type": "integer"}}]
+    rec = StructuralTagRecognizer(tags)
+    assert _accepts(rec, "plain text with < and > signs")
+    assert _accepts(rec, 'Let me check. <tool_call>{"name":"search","n":3}</tool_call> done')
+    assert not _prefix_ok(rec, '<tool_call>{"name":"delete"')                 # not in the enum
+    assert not _prefix_ok(rec, '<tool_call>{"name":"search","n":3} </tool_call>')   # the end string must follow at once
+    assert _prefix_ok(rec, '<tool_call>{"name":"search"') and not _accepts(rec, '<tool_call>{"name":"search"')
+    assert _accepts(rec, "value <n>42</n> and <n>-7</n>")                     # a number ends at the end string's first byte
+    assert not _prefix_ok(rec, "<n>4x")
+    r = rec.clone()
+    for b in b'<n>1</n><tool_call>{"name":"get_time","n":0}</tool_call>':
+        assert r.feed(b)
+    assert r.complete() and r.blocks == 2
+    with pytest.raises(ValueError):
+        StructuralTagRecognizer([])
+
+
+def test_regex_and_structural_tag_through_response_format():
+    from cuteafd_b200.serve import constraints
+    from cuteafd_b200.serve.tokenizer import ByteTokenizer
+    tok = ByteTokenizer(300)
+    c = constraints.from_response_format({"type": "regex", "pattern": r"[ab]{2}"}, tok, 300)
+    m = c.mask()
+    allowed = {t for t in range(300) if m[t]}
+    assert {tok.encode("a")[0], tok.encode("b")[0]} <= allowed and tok.encode("c")[0] not in allowed
+    assert c.advance(tok.encode("a")[0]) and not c.finished() and c.advance(tok.encode("b")[0]) and c.finished()
+    c = constraints.from_response_format({"type": "structural_tag", "structures": [{"begin": "<v>", "schema": {"type": "boolean"}, "end": "</v>"}]}, tok, 300)
+    for t in tok.encode("<v>"):
+        assert c.advance(t)
+    m = c.mask()
+    assert m[tok.encode("t")[0]] and m[tok.encode("f")[0]] and not m[tok.encode("x")[0]]
+    with pytest.raises(ValueError):
+        constraints.from_response_format({"type": "regex", "pattern": "(a"}, tok, 300)
