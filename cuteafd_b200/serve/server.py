@@ -123,6 +123,13 @@ def make_handler(state: ServerState):
                 return self._json(200, LEDGER.report())
             if path == "/console/experts":
                 return self._json(200, state.extras.get("expert_usage", lambda: {})())
+            if path == "/v1/codex/models.json":
+                # model catalog for clients that size their compaction from it: the served context window and reply limit
+                be = state.sched.be
+                window = int(getattr(be, "max_context_tokens", 0) or getattr(be, "max_pages", 0) * 64 or 16384)
+                return self._json(200, {"models": [{"slug": state.model_id, "display_name": state.model_id, "context_window": window,
+                                                    "max_output_tokens": min(window // 2, 32768), "supports_reasoning": False,
+                                                    "supports_parallel_tool_calls": True, "wire_api": "responses"}]})
             if path == "/v1/stats":
                 s = state.sched.snapshot()
                 be = state.sched.be

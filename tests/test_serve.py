@@ -317,3 +317,9 @@ def test_usage_log_prunes_bodies_after_a_day(tmp_path):
     assert [r["id"] for r in log.requests(10)] == [b, a] and [r["id"] for r in log.requests(10, before_id=b)] == [a]
     # a second handle on the same file sees the rows (the command-line report reads while the server writes)
     assert UsageLog(str(tmp_path / "u.sqlite"), clock=lambda: now[0]).summary(48)["requests"] == 2
+
+
+def test_model_catalog(server):
+    st, _, raw = call(server, "GET", "/v1/codex/models.json")
+    m = json.loads(raw)["models"][0]
+    assert st == 200 and m["slug"] == "tiny-moe" and m["context_window"] >= 1024 and m["max_output_tokens"] <= m["context_window"]
