@@ -1,0 +1,279 @@
+"""Benchmark and quality panels run against a live server over its HTTP API, so they exercise exactly what a client
+gets (tokenizer, templates, scheduler, prefix cache, speculation, engine) whatever backend serves.
+
+    python -m cuteafd_b200.cli bench --url http://127.0.0.1:8000 --panels smoke,cache_exact,lossless,speed
+    python -m cuteafd_b200.cli bench --url ... --panels sweep --levels 1,4,8,16 --max-tokens 128
+    python -m cuteafd_b200.cli bench --url ... --panels sustained --seconds 60 --concurrency 8
+
+Panels
+  smoke        /health, /v1/models, one short completion, one streamed completion
+  cache_exact  the same prompt twice: the second is served from the prefix cache and must reproduce every selected
+               logit row bit for bit (row hashes through the probe header) and the same text
+  lossless     greedy decoding with and without speculative drafts gives the same tokens
+  template     chat rendering is stable: the prompt token count of the same conversation does not change between
+               calls, and grows when a turn is appended (``/v1/responses/input_tokens``)
+  tools        a tool declaration reaches the template and a constrained reply (``response_format`` choice) comes back
+               as one of the choices
+  speed        C1 decode tok/s and TTFT on a short prompt, and prefill tok/s + TTFT on a long one (streamed, timed at
+               the client)
+  sweep        aggregate decode tok/s at each concurrency of ``levels`` with a distinct prompt per stream
+  sustained    ``concurrency`` streams kept busy for ``seconds``: requests, tokens/s, TTFT p50 / p99, failures
+
+Every panel returns ``{"panel", "ok", ...numbers}``; the runner attaches the server's thermal window for the time the
+panel ran (``/v1/thermal``) the way every phase of the reference's card carries its throttle summary.
+
+Counterpart: rust/crates/cuteafd-bench/src/baseline.rs:1-25 (card), the quick-quality checks (cache_exact, lossless
+speculation, template round-trip) and the panels / sustained / sweep / smoke modes of the reference's bench crate.
+"""
+from __future__ import annotations
+
+import http.client
+import json
+import random
+import statistics
+import threading
+import time
+import urllib.parse
+
+PROBE = "x-cuteafd-probe"
+WORDS = ("tensor memory barrier tile warp cluster stream graph expert router token cache page latent index prefix "
+         "draft verify commit lane queue batch kernel copy fence flag epoch slot").split()
+
+
+class Client:
+    def __init__(self, url: str, api_key: str = "", timeout: float = 600.0):
+        u = urllib.parse.urlparse(url)
+        self.host, self.port, self.key, self.timeout = u.hostname, u.port or 80, api_key, timeout
+
+    def _conn(self) -> http.client.HTTPConnection:
+        return http.client.HTTPConnection(self.host, self.port, timeout=self.timeout)
+
+    def _headers(self, extra: dict | None = None) -> dict:
+        h = {"Content-Type": "application/json"}
+        if self.key:
+            h["Authorization"] = "Bearer " + self.key
+        h.update(extra or {})
+        return h
+
+    def get(self, path: str):
+        c = self._conn()
+        c.request("GET", path, headers=self._headers())
+        r = c.getresponse()
+        raw = r.read()
+        c.close()
+        try:
+            return r.status, json.loads(raw)
+        except json.JSONDecodeError:
+            return r.status, raw
+
+    def post(self, path: str, body: dict, headers: dict | None = None):
+        c = self._conn()
+        c.request("POST", path, json.dumps(body), self._headers(headers))
+        r = c.getresponse()
+        raw = r.read()
+        c.close()
+        return r.status, json.loads(raw or b"{}")
+
+    def stream(self, body: dict) -> dict:
+        """Streamed chat completion timed at the client: {"status", "text", "ttft_s", "seconds", "usage", "chunks"}."""
+        c = self._conn()
+        t0 = time.perf_counter()
+        c.request("POST", "/v1/chat/completions", json.dumps(dict(body, stream=True)), self._headers())
+        r = c.getresponse()
+        if r.status != 200:
+            raw = r.read()
+            c.close()
+            return {"status": r.status, "text": "", "ttft_s": None, "seconds": time.perf_counter() - t0, "usage": {}, "chunks": 0,
+                    "error": raw[:200].decode("utf-8", "replace")}
+        text, first, usage, chunks = [], None, {}, 0
+        for line in r:
+            if not line.startswith(b"data: "):
+                continue
+            data = line[6:].strip()
+            if data == b"[DONE]":
+                break
+            ev = json.loads(data)
+            if "error" in ev:
+                c.close()
+                return {"status": 500, "text": "".join(text), "ttft_s": first, "seconds": time.perf_counter() - t0, "usage": {},
+                        "chunks": chunks, "error": str(ev["error"])[:200]}
+            delta = ev["choices"][0]["delta"].get("content")
+            if delta:
+                first = first if first is not None else time.perf_counter() - t0
+                text.append(delta)
+                chunks += 1
+            usage = ev.get("usage") or usage
+        c.close()
+        return {"status": 200, "text": "".join(text), "ttft_s": first, "seconds": time.perf_counter() - t0, "usage": usage, "chunks": chunks}
+
+
+def prompt_of(n_words: int, seed: int) -> str:
+    rnd = random.Random(seed)
+    return " ".join(rnd.choice(WORDS) for _ in range(n_words))
+
+
+def _chat(text: str, max_tokens: int, **kw) -> dict:
+    return dict({"messages": [{"role": "user", "content": text}], "max_tokens": max_tokens, "temperature": 0}, **kw)
+
+
+# ---- panels ------------------------------------------------------------------------------------------
+def smoke(c: Client, o: dict) -> dict:
+    st_h, health = c.get("/health")
+    st_m, models = c.get("/v1/models")
+    st_c, out = c.post("/v1/chat/completions", _chat("say hello", 8))
+    s = c.stream(_chat("count to five", 8))
+    ok = st_h == 200 and st_m == 200 and st_c == 200 and s["status"] == 200 and bool(models.get("data"))
+    return {"ok": ok, "health": health.get("status") if isinstance(health, dict) else None,
+            "model": models["data"][0]["id"] if ok else None, "completion_tokens": out.get("usage", {}).get("completion_tokens"),
+            "streamed_chunks": s["chunks"]}
+
+
+def cache_exact(c: Client, o: dict) -> dict:
+    body = _chat(prompt_of(o.get("prompt_words", 160), 11), o.get("max_tokens", 16))
+    probe = {PROBE: json.dumps({"record_rows": True, "no_speculation": True})}
+    st1, a = c.post("/v1/chat/completions", body, probe)
+    st2, b = c.post("/v1/chat/completions", body, probe)
+    if st1 != 200 or st2 != 200:
+        return {"ok": False, "status": [st1, st2]}
+    cached = b["usage"]["prompt_tokens_details"]["cached_tokens"]
+    same_rows = a.get("probe", {}).get("row_hashes") == b.get("probe", {}).get("row_hashes") and bool(a.get("probe"))
+    same_text = a["choices"][0]["message"]["content"] == b["choices"][0]["message"]["content"]
+    return {"ok": same_rows and same_text and cached > 0, "cached_tokens": cached, "prompt_tokens": b["usage"]["prompt_tokens"],
+            "rows_identical": same_rows, "text_identical": same_text}
+
+
+def lossless(c: Client, o: dict) -> dict:
+    unit = prompt_of(12, 5)
+    body = _chat((unit + " ") * 10, o.get("max_tokens", 32))            # repetitive: drafts get proposed
+    st1, plain = c.post("/v1/chat/completions", body, {PROBE: json.dumps({"no_speculation": True})})
+    st2, spec = c.post("/v1/chat/completions", body)
+    if st1 != 200 or st2 != 200:
+        return {"ok": False, "status": [st1, st2]}
+    sp = spec["usage"].get("speculation", {})
+    same = plain["choices"][0]["message"]["content"] == spec["choices"][0]["message"]["content"]
+    return {"ok": same, "text_identical": same, "proposed": sp.get("proposed"), "accepted": sp.get("accepted"), "cycles": sp.get("cycles"),
+            "completion_tokens": spec["usage"]["completion_tokens"]}
+
+
+def template(c: Client, o: dict) -> dict:
+    conv = [{"role": "user", "content": "first question"}, {"role": "assistant", "content": "first answer"},
+            {"role": "user", "content": "second question"}]
+    n1 = c.post("/v1/responses/input_tokens", {"input": conv})[1].get("input_tokens")
+    n2 = c.post("/v1/responses/input_tokens", {"input": conv})[1].get("input_tokens")
+    n3 = c.post("/v1/responses/input_tokens", {"input": conv + [{"role": "assistant", "content": "x"}, {"role": "user", "content": "y"}]})[1].get("input_tokens")
+    ok = isinstance(n1, int) and n1 == n2 and isinstance(n3, int) and n3 > n1
+    return {"ok": ok, "tokens": n1, "tokens_after_append": n3}
+
+
+def tools(c: Client, o: dict) -> dict:
+    tool = {"type": "function", "function": {"name": "get_time", "description": "current time", "parameters": {"type": "object", "properties": {}}}}
+    base = c.post("/v1/responses/input_tokens", {"input": "what time is it"})[1].get("input_tokens", 0)
+    with_tool = c.post("/v1/responses/input_tokens", {"input": "what time is it", "tools": [tool]})[1].get("input_tokens", 0)
+    st, out = c.post("/v1/chat/completions", _chat("pick one", 8, response_format={"type": "choice", "choices": ["get_time", "none"]}))
+    text = out["choices"][0]["message"]["content"] if st == 200 else None
+    return {"ok": st == 200 and text in ("get_time", "none") and with_tool >= base, "choice": text,
+            "template_tokens_with_tool": with_tool, "template_tokens": base}
+
+
+def speed(c: Client, o: dict) -> dict:
+    n = o.get("max_tokens", 64)
+    c.stream(_chat(prompt_of(16, 1), 8))                               # warm-up: graphs, caches
+    short = c.stream(_chat(prompt_of(16, 2), n))
+    long_words = o.get("prefill_words", 2048)
+    long = c.stream(_chat(prompt_of(long_words, 3), 4))
+    if short["status"] != 200 or long["status"] != 200:
+        return {"ok": False, "errors": [short.get("error"), long.get("error")]}
+    toks = short["usage"].get("completion_tokens", 0)
+    decode_s = short["seconds"] - (short["ttft_s"] or 0.0)
+    ptoks = long["usage"].get("prompt_tokens", 0)
+    return {"ok": toks > 0 and ptoks > 0, "c1_decode_tok_s": round((toks - 1) / decode_s, 2) if decode_s > 0 and toks > 1 else None,
+            "c1_ttft_s": short["ttft_s"], "prefill_tokens": ptoks, "prefill_ttft_s": long["ttft_s"],
+            "prefill_tok_s": round(ptoks / long["ttft_s"], 1) if long["ttft_s"] else None}
+
+
+def _fan(c: Client, bodies: list[dict]) -> tuple[list[dict], float]:
+    out: list[dict | None] = [None] * len(bodies)
+
+    def one(i: int) -> None:
+        out[i] = c.stream(bodies[i])
+    ts = [threading.Thread(target=one, args=(i,)) for i in range(len(bodies))]
+    t0 = time.perf_counter()
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    return out, time.perf_counter() - t0
+
+
+def sweep(c: Client, o: dict) -> dict:
+    n = o.get("max_tokens", 64)
+    levels = {}
+    for k in o.get("levels", [1, 4, 8]):
+        res, wall = _fan(c, [_chat(prompt_of(24, 100 * k + i), n) for i in range(k)])      # a distinct prompt per stream
+        toks = sum(r["usage"].get("completion_tokens", 0) for r in res if r["status"] == 200)
+        ttft = [r["ttft_s"] for r in res if r["ttft_s"] is not None]
+        levels[str(k)] = {"tok_s": round(toks / wall, 2), "failed": sum(r["status"] != 200 for r in res),
+                          "ttft_p50_s": round(statistics.median(ttft), 4) if ttft else None}
+    return {"ok": all(v["failed"] == 0 and v["tok_s"] > 0 for v in levels.values()), "levels": levels}
+
+
+def sustained(c: Client, o: dict) -> dict:
+    seconds, conc, n = o.get("seconds", 10.0), o.get("concurrency", 4), o.get("max_tokens", 32)
+    stop = time.perf_counter() + seconds
+    lock = threading.Lock()
+    rec = {"requests": 0, "tokens": 0, "failed": 0, "retry": 0, "ttft": []}
+
+    def worker(w: int) -> None:
+        i = 0
+        while time.perf_counter() < stop:
+            r = c.stream(_chat(prompt_of(24, 7919 * w + i), n))
+            i += 1
+            with lock:
+                rec["requests"] += 1
+                if r["status"] == 200:
+                    rec["tokens"] += r["usage"].get("completion_tokens", 0)
+                    if r["ttft_s"] is not None:
+                        rec["ttft"].append(r["ttft_s"])
+                elif r["status"] == 429:
+                    rec["retry"] += 1                                   # capacity refusal: the client's cue to back off
+                    time.sleep(0.05)
+                else:
+                    rec["failed"] += 1
+    t0 = time.perf_counter()
+    ts = [threading.Thread(target=worker, args=(w,)) for w in range(conc)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    wall = time.perf_counter() - t0
+    tt = sorted(rec["ttft"])
+    return {"ok": rec["failed"] == 0 and rec["tokens"] > 0, "requests": rec["requests"], "failed": rec["failed"], "retried_429": rec["retry"],
+            "tok_s": round(rec["tokens"] / wall, 2), "ttft_p50_s": round(tt[len(tt) // 2], 4) if tt else None,
+            "ttft_p99_s": round(tt[min(len(tt) - 1, int(len(tt) * 0.99))], 4) if tt else None, "seconds": round(wall, 2)}
+
+
+PANELS = {"smoke": smoke, "cache_exact": cache_exact, "lossless": lossless, "template": template, "tools": tools, "speed": speed,
+          "sweep": sweep, "sustained": sustained}
+QUICK = ("smoke", "cache_exact", "lossless", "template", "tools")
+
+
+def run(url: str, panels: list[str], api_key: str = "", options: dict | None = None, log=print) -> dict:
+    c = Client(url, api_key)
+    out = {"url": url, "panels": []}
+    for name in panels:
+        if name not in PANELS:
+            raise ValueError(f"unknown panel {name!r} (choose from {', '.join(PANELS)})")
+        t0 = time.time()
+        try:
+            res = PANELS[name](c, options or {})
+        except (OSError, KeyError, ValueError, http.client.HTTPException) as e:
+            res = {"ok": False, "error": f"{type(e).__name__}: {e}"}
+        res = dict({"panel": name, "seconds": round(time.time() - t0, 2)}, **res)
+        st, th = c.get("/v1/thermal")
+        if st == 200 and isinstance(th, dict) and th.get("available"):
+            res["thermal"] = {g: {"verdict": w.get("verdict"), "sm_mhz": (w.get("sm_mhz") or {}).get("median")}
+                              for g, w in (th.get("window") or {}).items()}
+        out["panels"].append(res)
+        log(json.dumps(res))
+    out["ok"] = all(p["ok"] for p in out["panels"])
+    return out

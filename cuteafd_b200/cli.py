@@ -93,6 +93,14 @@ def cmd_golden(a: argparse.Namespace) -> int:
 
 def cmd_bench(a: argparse.Namespace) -> int:
     import subprocess
+    if a.url:                                  # panels against a live server, over its HTTP API
+        from .bench import panels
+        names = list(panels.QUICK) if a.panels == "quick" else [p for p in a.panels.split(",") if p]
+        opts = {"max_tokens": a.max_tokens, "levels": [int(v) for v in a.levels.split(",") if v], "seconds": a.seconds,
+                "concurrency": a.concurrency}
+        out = panels.run(a.url, names, a.bench_api_key, opts)
+        print(json.dumps({"ok": out["ok"], "panels": len(out["panels"])}))
+        return 0 if out["ok"] else 1
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     cmd = [sys.executable, os.path.join(root, "bench.py"), "--gpus", str(a.gpus), "--steps", str(a.steps), "--warmup", str(a.warmup)]
     if a.gpus > 1:
@@ -294,6 +302,14 @@ def _build_parser() -> argparse.ArgumentParser:
     b = sub.add_parser("bench", help="run the headline benchmark card")
     b.add_argument("--gpus", type=int, default=1); b.add_argument("--steps", type=int, default=128)
     b.add_argument("--warmup", type=int, default=8); b.add_argument("--port", type=int, default=29511)
+    b.add_argument("--url", default="", help="run panels against this live server over HTTP instead of the in-process card")
+    b.add_argument("--panels", default="quick", help="comma-separated: smoke, cache_exact, lossless, template, tools, speed, sweep, "
+                                                       "sustained; quick = the first five")
+    b.add_argument("--api-key", dest="bench_api_key", default=os.environ.get("CUTEAFD_API_KEY", ""), help="bearer token of the server under test")
+    b.add_argument("--max-tokens", type=int, default=64, help="tokens generated per request in the panels")
+    b.add_argument("--levels", default="1,4,8", help="concurrency levels of the sweep panel")
+    b.add_argument("--seconds", type=float, default=10.0, help="duration of the sustained panel")
+    b.add_argument("--concurrency", type=int, default=4, help="streams of the sustained panel")
     b.set_defaults(fn=cmd_bench)
 
     f = sub.add_parser("fabric", help="NVLink / peer-access report")

@@ -323,3 +323,21 @@ def test_model_catalog(server):
     st, _, raw = call(server, "GET", "/v1/codex/models.json")
     m = json.loads(raw)["models"][0]
     assert st == 200 and m["slug"] == "tiny-moe" and m["context_window"] >= 1024 and m["max_output_tokens"] <= m["context_window"]
+
+
+def test_http_panels_on_the_oracle_server(server):
+    from cuteafd_b200.bench import panels
+    out = panels.run(f"http://127.0.0.1:{server.port}", list(panels.QUICK) + ["speed", "sweep", "sustained"], "sekret",
+                     {"max_tokens": 6, "levels": [1, 2], "seconds": 1.0, "concurrency": 2, "prefill_words": 96, "prompt_words": 120},
+                     log=lambda *_: None)
+    by = {p["panel"]: p for p in out["panels"]}
+    assert by["smoke"]["ok"] and by["smoke"]["model"] == "tiny-moe"
+    assert by["cache_exact"]["ok"] and by["cache_exact"]["cached_tokens"] >= 64 and by["cache_exact"]["rows_identical"]
+    assert by["lossless"]["ok"] and by["template"]["ok"] and by["template"]["tokens_after_append"] > by["template"]["tokens"]
+    assert by["tools"]["ok"] and by["tools"]["choice"] in ("get_time", "none")
+    assert by["speed"]["ok"] and by["speed"]["prefill_tokens"] > 90 and by["speed"]["c1_ttft_s"] > 0
+    assert by["sweep"]["ok"] and set(by["sweep"]["levels"]) == {"1", "2"}
+    assert by["sustained"]["ok"] and by["sustained"]["requests"] >= 2 and by["sustained"]["failed"] == 0
+    assert out["ok"]
+    with pytest.raises(ValueError):
+        panels.run(f"http://127.0.0.1:{server.port}", ["nope"], "sekret")
