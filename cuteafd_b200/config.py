@@ -34,6 +34,16 @@ class ModelConfig:
     v_head_dim: int = 32
     rope_theta: float = 10000.0
     rope_interleaved: bool = True        # pairs (2i, 2i+1); False = rotate-half (neox)
+    # long-context frequency scaling of the checkpoint (config.json "rope_scaling"); see ref/ops.py::rope_inv_freq
+    rope_scaling: str = "none"           # none | linear | llama3 | yarn
+    rope_factor: float = 1.0
+    rope_original_max: int = 4096        # positions the base frequencies were trained for (yarn, llama3)
+    rope_beta_fast: float = 32.0         # yarn correction range
+    rope_beta_slow: float = 1.0
+    rope_mscale: float = 1.0             # yarn magnitude terms (DeepSeek: softmax scale *= mscale(all_dim)^2)
+    rope_mscale_all_dim: float = 0.0
+    rope_low_freq_factor: float = 1.0    # llama3
+    rope_high_freq_factor: float = 4.0
     rms_eps: float = 1e-6
     # feed forward
     dense_ffn: int = 512                 # intermediate size of the dense SwiGLU layers
@@ -139,7 +149,10 @@ def deepseek_v3() -> ModelConfig:
         qk_rope_dim=64, v_head_dim=128, rope_theta=10000.0, rope_interleaved=True, rms_eps=1e-6,
         dense_ffn=18432, first_dense_layers=3, num_experts=256, expert_ffn=2048, top_k=8,
         scoring="sigmoid", num_groups=8, topk_groups=4, num_shared_experts=1, routed_scale=2.5,
-        norm_topk_prob=True, router_bias=True, mtp_layers=1, weight_format="fp8_block128")
+        norm_topk_prob=True, router_bias=True, mtp_layers=1, weight_format="fp8_block128",
+        # the shipped long-context setting: YaRN x40 over 4096 trained positions, mscale on the softmax scale
+        rope_scaling="yarn", rope_factor=40.0, rope_original_max=4096, rope_beta_fast=32.0, rope_beta_slow=1.0,
+        rope_mscale=1.0, rope_mscale_all_dim=1.0)
 
 
 def deepseek_v32() -> ModelConfig:
@@ -163,7 +176,8 @@ def kimi_k2() -> ModelConfig:
     """Kimi-K2 geometry: the DeepSeek-V3 architecture with 64 heads and 384 routed experts (one dense layer, one
     routing group); served by the MLA engine."""
     return deepseek_v3().replace(name="kimi-k2", vocab_size=163840, num_heads=64, first_dense_layers=1, num_experts=384,
-                                 num_groups=1, topk_groups=1, routed_scale=2.827, mtp_layers=0, rope_theta=50000.0)
+                                 num_groups=1, topk_groups=1, routed_scale=2.827, mtp_layers=0, rope_theta=50000.0,
+                                 rope_factor=32.0, rope_beta_fast=1.0, rope_beta_slow=1.0)
 
 
 PRESETS = {

@@ -127,6 +127,11 @@ class Qwen3Moe(Family):
     id, model_types, attention = "qwen3_moe", ("qwen3_moe", "qwen2_moe", "mixtral", "qwen3"), "gqa"
 
 
+class Llama(Family):
+    """Dense GQA decoders (Llama, Mistral without a sliding window): served by the GQA engine's dense path."""
+    id, model_types, attention = "llama", ("llama", "mistral"), "gqa"
+
+
 class TinyMoe(Family):
     id, model_types = "tiny_moe", ("tiny_moe",)
 
@@ -146,7 +151,7 @@ def canonical_name(name: str) -> str:
     return _MIXTRAL_RE.sub(lambda m: m.group(1) + _MIXTRAL_PROJ[m.group(2)] + m.group(3), name)
 
 
-REGISTRY: tuple[Family, ...] = (DeepseekV32(), DeepseekV3(), Qwen3Moe(), TinyMoe())
+REGISTRY: tuple[Family, ...] = (DeepseekV32(), DeepseekV3(), Qwen3Moe(), Llama(), TinyMoe())
 
 
 def detect(hf_config: dict) -> Family | None:

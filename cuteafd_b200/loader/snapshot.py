@@ -17,7 +17,7 @@ from ..ref.model import init_weights
 from . import formats
 from .safetensors_io import write_sharded
 
-ARCH = {"qwen3_moe": "Qwen3MoeForCausalLM", "deepseek_v3": "DeepseekV3ForCausalLM",
+ARCH = {"llama": "LlamaForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM", "deepseek_v3": "DeepseekV3ForCausalLM",
         "deepseek_v32": "DeepseekV32ForCausalLM", "tiny_moe": "DeepseekV3ForCausalLM"}
 
 
@@ -41,6 +41,15 @@ def to_hf_config(cfg: ModelConfig) -> dict:
     else:
         d.update(num_key_value_heads=cfg.num_kv_heads, head_dim=cfg.head_dim, num_experts=cfg.num_experts,
                  decoder_sparse_step=1, mlp_only_layers=list(range(cfg.first_dense_layers)), qk_norm=cfg.qk_norm)
+    if cfg.rope_scaling != "none":
+        rs = {"type": cfg.rope_scaling, "rope_type": cfg.rope_scaling, "factor": cfg.rope_factor,
+              "original_max_position_embeddings": cfg.rope_original_max}
+        if cfg.rope_scaling == "yarn":
+            rs.update(beta_fast=cfg.rope_beta_fast, beta_slow=cfg.rope_beta_slow, mscale=cfg.rope_mscale,
+                      mscale_all_dim=cfg.rope_mscale_all_dim)
+        if cfg.rope_scaling == "llama3":
+            rs.update(low_freq_factor=cfg.rope_low_freq_factor, high_freq_factor=cfg.rope_high_freq_factor)
+        d["rope_scaling"] = rs
     if cfg.weight_format == "fp8_block128":
         d["quantization_config"] = {"quant_method": "fp8", "fmt": "e4m3", "weight_block_size": [128, 128],
                                     "activation_scheme": "dynamic"}
@@ -53,6 +62,25 @@ def to_hf_config(cfg: ModelConfig) -> dict:
     return d
 
 
+def _rope_scaling(d: dict) -> dict:
+    """config.json ``rope_scaling`` / ``rope_parameters`` -> ModelConfig fields.  Unknown kinds are refused: serving a
+    long-context checkpoint with the wrong frequencies gives fluent nonsense, not an error."""
+    rs = d.get("rope_scaling") or d.get("rope_parameters") or {}
+    kind = rs.get("rope_type") or rs.get("type") or "none"
+    if kind in ("none", "default") or not rs:
+        return {}
+    if kind not in ("linear", "llama3", "yarn"):
+        raise ValueError(f"unsupported rope scaling {kind!r}")
+    out = dict(rope_scaling=kind, rope_factor=float(rs.get("factor", 1.0)),
+               rope_original_max=int(rs.get("original_max_position_embeddings") or d.get("max_position_embeddings") or 4096))
+    if kind == "yarn":
+        out.update(rope_beta_fast=float(rs.get("beta_fast") or 32.0), rope_beta_slow=float(rs.get("beta_slow") or 1.0),
+                   rope_mscale=float(rs.get("mscale") or 1.0), rope_mscale_all_dim=float(rs.get("mscale_all_dim") or 0.0))
+    if kind == "llama3":
+        out.update(rope_low_freq_factor=float(rs.get("low_freq_factor", 1.0)), rope_high_freq_factor=float(rs.get("high_freq_factor", 4.0)))
+    return out
+
+
 def from_hf_config(d: dict) -> ModelConfig:
     """Map a config.json onto the engine's geometry.  Unknown architectures raise ValueError."""
     mt = d.get("model_type", "")
@@ -61,10 +89,10 @@ def from_hf_config(d: dict) -> ModelConfig:
     fmt = {"fp8": "fp8_block128", "modelopt": "nvfp4", "mxfp4": "mxfp4", "exl3": "exl3"}.get(q.get("quant_method", ""), "bf16")
     common = dict(name=extra.get("name", d.get("_name_or_path", mt) or mt), vocab_size=d["vocab_size"],
                   num_layers=d["num_hidden_layers"], hidden=d["hidden_size"], num_heads=d["num_attention_heads"],
-                  rms_eps=d.get("rms_norm_eps", 1e-6), rope_theta=float(d.get("rope_theta", 10000.0)),
+                  rms_eps=d.get("rms_norm_eps", 1e-6), rope_theta=float(d.get("rope_theta") or (d.get("rope_parameters") or {}).get("rope_theta") or 10000.0),
                   tie_embeddings=bool(d.get("tie_word_embeddings", False)), dense_ffn=d.get("intermediate_size", 0),
                   expert_ffn=d.get("moe_intermediate_size", 0), top_k=d.get("num_experts_per_tok", 0),
-                  norm_topk_prob=bool(d.get("norm_topk_prob", True)), weight_format=fmt)
+                  norm_topk_prob=bool(d.get("norm_topk_prob", True)), weight_format=fmt, **_rope_scaling(d))
     if mt in ("deepseek_v3", "deepseek_v32", "deepseek_v2", "tiny_moe", "glm_moe_dsa", "kimi_k2"):
         return ModelConfig(
             family=extra.get("family", "deepseek_v32" if d.get("index_n_heads") else "deepseek_v3"), attention="mla",
@@ -83,6 +111,17 @@ def from_hf_config(d: dict) -> ModelConfig:
             head_dim=d.get("head_dim", d["hidden_size"] // d["num_attention_heads"]), qk_norm=bool(d.get("qk_norm", mt.startswith("qwen3"))),
             rope_interleaved=extra.get("rope_interleaved", False), first_dense_layers=len(d.get("mlp_only_layers", []) or []),
             num_experts=d.get("num_experts", d.get("num_local_experts", 0)), scoring="softmax", num_shared_experts=0, **common)
+    if mt in ("llama", "mistral"):
+        # dense GQA decoders without projection biases: every layer takes the dense SwiGLU path
+        if d.get("attention_bias") or d.get("mlp_bias"):
+            raise ValueError("projection biases are not supported")
+        if mt == "mistral" and d.get("sliding_window"):
+            raise ValueError("sliding-window attention is not supported")
+        return ModelConfig(
+            family="llama", attention="gqa", num_kv_heads=d.get("num_key_value_heads", d["num_attention_heads"]),
+            head_dim=d.get("head_dim") or d["hidden_size"] // d["num_attention_heads"], qk_norm=False,
+            rope_interleaved=extra.get("rope_interleaved", False), first_dense_layers=d["num_hidden_layers"], num_experts=0,
+            num_shared_experts=0, **dict(common, top_k=0, expert_ffn=0))
     raise ValueError(f"unsupported model_type {mt!r}")
 
 

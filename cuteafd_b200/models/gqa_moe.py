@@ -206,8 +206,11 @@ class GqaMoeEngine:
         self.device = weights.embed.device
         self.max_tokens = max_tokens
         self.ws = Workspace(cfg, max_tokens, self.device)
-        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, dtype=torch.float32) / cfg.head_dim))
-        self.inv_freq = inv.to(self.device)
+        from ..ref.ops import rope_inv_freq, rope_magnitudes
+        if rope_magnitudes(cfg) != (1.0, 1.0):
+            # the GQA attention kernels take no softmax-scale argument and the rope kernel no magnitude
+            raise ValueError("YaRN magnitude scaling is not supported by the GQA engine (linear and llama3 scaling are)")
+        self.inv_freq = rope_inv_freq(cfg, cfg.head_dim).to(self.device)      # long-context scaling is in this table
         self.moe = None
         self.pre_moe = None          # hook(layer) called before each MoE layer's exchange
         if cfg.num_experts and build_moe:

@@ -213,9 +213,12 @@ class MlaMoeEngine(GqaMoeEngine):
         ws.ffn_d = torch.empty(max_tokens, cfg.dense_ffn, **bf) if dense else None
         ws.ffn_s = torch.empty(max_tokens, cfg.expert_ffn * cfg.num_shared_experts, **bf) if cfg.num_shared_experts else None
         ws.shared = torch.empty(max_tokens, H, **bf) if cfg.num_shared_experts else None
-        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.qk_rope_dim, 2, dtype=torch.float32) / cfg.qk_rope_dim))
-        self.inv_freq = inv.to(dev)
-        self.scale = 1.0 / math.sqrt(cfg.qk_head_dim)
+        from ..ref.ops import rope_inv_freq, rope_magnitudes
+        mag, scale_mul = rope_magnitudes(cfg)
+        if mag != 1.0:
+            raise ValueError("a YaRN configuration whose cos / sin magnitude differs from 1 (mscale != mscale_all_dim) is not supported")
+        self.inv_freq = rope_inv_freq(cfg, cfg.qk_rope_dim).to(dev)           # YaRN / linear scaling is in this table
+        self.scale = scale_mul / math.sqrt(cfg.qk_head_dim)                    # DeepSeek YaRN: mscale(all_dim)^2 on the logits
         self.moe = None
         self.pre_moe = None
         if cfg.num_experts and build_moe:

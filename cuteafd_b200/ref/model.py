@@ -120,6 +120,9 @@ class RefDecoder:
     def __init__(self, cfg: ModelConfig, params: dict[str, torch.Tensor], moe_fn: MoeFn | None = None):
         self.cfg, self.p, self.moe_fn = cfg, params, moe_fn
         self.select_fn = None        # optional (layer, start, Tq, Tk) -> bool mask [Tq, Tk] replacing the indexer's choice
+        rd = cfg.qk_rope_dim if cfg.is_mla else cfg.head_dim
+        self.inv_freq = ops.rope_inv_freq(cfg, rd)                  # long-context scaling lives in this table
+        self.rope_mag, self.scale_mul = ops.rope_magnitudes(cfg)
         self.observe = None          # optional (operand prefix, input rows [n, in]) -> None, called before every projection
         self._stacked: dict[int, tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
 
@@ -168,10 +171,11 @@ class RefDecoder:
                 q = (x.float() @ p[a + "q_proj.weight"].float().T).to(x.dtype)
             q = q.view(T, cfg.num_heads, cfg.qk_head_dim)
             q_nope, q_rope = q[..., : cfg.qk_nope_dim], q[..., cfg.qk_nope_dim:]
-            q_rope = ops.apply_rope(q_rope, positions, cfg.rope_theta, cfg.rope_interleaved)
+            q_rope = ops.apply_rope(q_rope, positions, cfg.rope_theta, cfg.rope_interleaved, self.inv_freq, self.rope_mag)
             ckv = (x.float() @ p[a + "kv_a_proj_with_mqa.weight"].float().T).to(x.dtype)
             latent = ops.rmsnorm(ckv[:, : cfg.kv_lora_rank], p[a + "kv_a_layernorm.weight"], cfg.rms_eps)
-            k_rope = ops.apply_rope(ckv[:, None, cfg.kv_lora_rank:], positions, cfg.rope_theta, cfg.rope_interleaved)[:, 0]
+            k_rope = ops.apply_rope(ckv[:, None, cfg.kv_lora_rank:], positions, cfg.rope_theta, cfg.rope_interleaved,
+                                    self.inv_freq, self.rope_mag)[:, 0]
             if cfg.kv_format == "fp8_ds_mla":
                 latent = ops.fp8_latent_roundtrip(latent)          # what the 656-byte record keeps of the latents
             rec = [latent, k_rope]
@@ -195,7 +199,7 @@ class RefDecoder:
             k = torch.cat([kvb[..., : cfg.qk_nope_dim], rope_all[:, None, :].expand(-1, cfg.num_heads, -1)], dim=-1)
             v = kvb[..., cfg.qk_nope_dim:]
             qq = torch.cat([q_nope, q_rope], dim=-1)
-            o = ops.causal_attention(qq, k, v, start, 1.0 / math.sqrt(cfg.qk_head_dim), allowed)
+            o = ops.causal_attention(qq, k, v, start, self.scale_mul / math.sqrt(cfg.qk_head_dim), allowed)
             o = o.reshape(T, cfg.num_heads * cfg.v_head_dim)
         else:
             q = (x.float() @ p[a + "q_proj.weight"].float().T).to(x.dtype).view(T, cfg.num_heads, cfg.head_dim)
@@ -204,8 +208,8 @@ class RefDecoder:
             if cfg.qk_norm:
                 q = ops.rmsnorm(q, p[a + "q_norm.weight"], cfg.rms_eps)
                 k = ops.rmsnorm(k, p[a + "k_norm.weight"], cfg.rms_eps)
-            q = ops.apply_rope(q, positions, cfg.rope_theta, cfg.rope_interleaved)
-            k = ops.apply_rope(k, positions, cfg.rope_theta, cfg.rope_interleaved)
+            q = ops.apply_rope(q, positions, cfg.rope_theta, cfg.rope_interleaved, self.inv_freq, self.rope_mag)
+            k = ops.apply_rope(k, positions, cfg.rope_theta, cfg.rope_interleaved, self.inv_freq, self.rope_mag)
             full = kv.append(layer, torch.cat([k.reshape(T, -1), v.reshape(T, -1)], dim=-1))
             half = cfg.num_kv_heads * cfg.head_dim
             k_all = full[:, :half].view(-1, cfg.num_kv_heads, cfg.head_dim)

@@ -26,17 +26,74 @@ def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, e
     return rmsnorm(r, weight, eps), r
 
 
-def rope_angles(dim: int, positions: torch.Tensor, theta: float) -> torch.Tensor:
-    inv = 1.0 / (theta ** (torch.arange(0, dim, 2, device=positions.device).float() / dim))
+def rope_angles(dim: int, positions: torch.Tensor, theta: float, inv_freq: torch.Tensor | None = None) -> torch.Tensor:
+    inv = inv_freq.to(positions.device) if inv_freq is not None else \
+        1.0 / (theta ** (torch.arange(0, dim, 2, device=positions.device).float() / dim))
     return torch.outer(positions.float(), inv)            # [T, dim/2]
 
 
+def _yarn_mscale(factor: float, m: float) -> float:
+    return 1.0 if factor <= 1.0 or m == 0.0 else 0.1 * m * math.log(factor) + 1.0
+
+
+def rope_inv_freq(cfg, dim: int) -> torch.Tensor:
+    """Rotation frequencies [dim / 2] (fp32) for the checkpoint's long-context scaling.  This table is the only thing
+    the rope kernels read, so every scaling rule is host arithmetic:
+
+    * ``linear``: every frequency divided by the factor (position interpolation).
+    * ``llama3``: wavelengths above ``original_max / low_freq_factor`` are divided by the factor, those below
+      ``original_max / high_freq_factor`` are kept, the band between is blended.
+    * ``yarn``: per dimension a blend of the kept frequency (dimensions that rotate more than ``beta_fast`` times over
+      the original context) and the interpolated one (fewer than ``beta_slow`` rotations), linear ramp between.
+    """
+    base = 1.0 / (cfg.rope_theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+    kind, f = cfg.rope_scaling, float(cfg.rope_factor)
+    if kind in ("none", "default") or f == 1.0:
+        return base
+    if kind == "linear":
+        return base / f
+    if kind == "llama3":
+        old = float(cfg.rope_original_max)
+        lo_w, hi_w = old / cfg.rope_low_freq_factor, old / cfg.rope_high_freq_factor
+        wavelen = 2 * math.pi / base
+        scaled = torch.where(wavelen > lo_w, base / f, base)
+        smooth = (old / wavelen - cfg.rope_low_freq_factor) / (cfg.rope_high_freq_factor - cfg.rope_low_freq_factor)
+        blended = (1 - smooth) * scaled / f + smooth * scaled
+        medium = ~(wavelen < hi_w) & ~(wavelen > lo_w)
+        return torch.where(medium, blended, scaled)
+    if kind == "yarn":
+        def correction_dim(rotations: float) -> float:
+            return dim * math.log(cfg.rope_original_max / (rotations * 2 * math.pi)) / (2 * math.log(cfg.rope_theta))
+        low = max(math.floor(correction_dim(cfg.rope_beta_fast)), 0)
+        high = min(math.ceil(correction_dim(cfg.rope_beta_slow)), dim - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(dim // 2, dtype=torch.float32) - low) / (high - low)).clamp(0, 1)
+        keep = 1 - ramp
+        return (base / f) * (1 - keep) + base * keep
+    raise ValueError(f"unknown rope scaling {kind!r}")
+
+
+def rope_magnitudes(cfg) -> tuple[float, float]:
+    """(multiplier on cos / sin, multiplier on the softmax scale).  YaRN enlarges the logits to keep attention sharp
+    over the longer context: DeepSeek-style configurations (``mscale_all_dim`` set) put ``mscale(all_dim)^2`` on the
+    softmax scale and the ratio ``mscale / mscale(all_dim)`` on cos / sin (1 when the two are equal, as shipped);
+    plain YaRN puts ``0.1 ln(factor) + 1`` on cos / sin."""
+    if cfg.rope_scaling != "yarn" or cfg.rope_factor <= 1.0:
+        return 1.0, 1.0
+    if cfg.rope_mscale_all_dim:
+        all_dim = _yarn_mscale(cfg.rope_factor, cfg.rope_mscale_all_dim)
+        return _yarn_mscale(cfg.rope_factor, cfg.rope_mscale) / all_dim, all_dim * all_dim
+    return _yarn_mscale(cfg.rope_factor, 1.0), 1.0
+
+
 def apply_rope(x: torch.Tensor, positions: torch.Tensor, theta: float = 10000.0,
-               interleaved: bool = True) -> torch.Tensor:
-    """x: [T, heads, dim].  interleaved rotates pairs (2i, 2i+1); otherwise (i, i+dim/2)."""
+               interleaved: bool = True, inv_freq: torch.Tensor | None = None, magnitude: float = 1.0) -> torch.Tensor:
+    """x: [T, heads, dim].  interleaved rotates pairs (2i, 2i+1); otherwise (i, i+dim/2).  ``inv_freq`` replaces the
+    plain ``theta`` table (long-context scaling); ``magnitude`` multiplies cos and sin."""
     dim = x.shape[-1]
-    ang = rope_angles(dim, positions, theta)
-    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    ang = rope_angles(dim, positions, theta, inv_freq)
+    cos, sin = ang.cos()[:, None, :] * magnitude, ang.sin()[:, None, :] * magnitude
     xf = x.float()
     if interleaved:
         a, b = xf[..., 0::2], xf[..., 1::2]
