@@ -158,6 +158,11 @@ def torch_dtype(name: str):
     return {"f32": torch.float32, "bf16": torch.bfloat16}[name]
 
 
+def cmd_fidelity(a: argparse.Namespace) -> int:
+    from .bench.fidelity import run_cli
+    return run_cli(a)
+
+
 def cmd_usage(a: argparse.Namespace) -> int:
     from .serve.usage import usage_report
     print(json.dumps(usage_report(a.db, a.hours), indent=1))
@@ -342,6 +347,18 @@ def _build_parser() -> argparse.ArgumentParser:
     c.add_argument("--rows", type=int, default=2048); c.add_argument("--seq", type=int, default=256)
     c.add_argument("--seed", type=int, default=0); c.add_argument("--dtype", default="f32", choices=("f32", "bf16"))
     c.set_defaults(fn=cmd_calibrate)
+
+    fd = sub.add_parser("fidelity", help="KL / top-1 of a snapshot against sealed reference windows")
+    fd.add_argument("action", choices=["seal", "check"], help="seal: compute and store the reference distributions; check: compare a snapshot with them")
+    fd.add_argument("snapshot", help="reference snapshot (seal) or snapshot under test (check)")
+    fd.add_argument("file", help="sealed window file (.safetensors)")
+    fd.add_argument("--windows", type=int, default=16, help="seal: number of windows")
+    fd.add_argument("--seq", type=int, default=128, help="seal: tokens per window")
+    fd.add_argument("--tokens", default="", help="seal: text file to cut windows from (default: random ids)")
+    fd.add_argument("--seed", type=int, default=0, help="seal: seed of the random windows")
+    fd.add_argument("--max-kl", type=float, default=0.05, help="check: largest mean KL that passes")
+    fd.add_argument("--min-top1", type=float, default=0.9, help="check: smallest top-1 agreement that passes")
+    fd.set_defaults(fn=cmd_fidelity)
 
     u = sub.add_parser("usage", help="request accounting report")
     u.add_argument("--db", default="usage.sqlite"); u.add_argument("--hours", type=float, default=24.0)

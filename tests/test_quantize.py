@@ -156,3 +156,36 @@ def test_calibrate_then_quantize_with_hessians(tmp_path):
     assert main(["quantize", src, dst, "--dense-ffn", "exl3_k3", "--hessians", hd]) == 0
     man = json.load(open(os.path.join(dst, "quantization.json")))
     assert man["operands"]["model.layers.0.mlp.down_proj"]["calibrated"] is True
+
+
+def test_fidelity_sealed_windows(tmp_path):
+    """Sealed windows: the reference against itself is exact, a quantised copy is close and ordered by bit width, and an
+    edited file is refused."""
+    from cuteafd_b200.bench import fidelity
+    from cuteafd_b200.cli import main
+    from cuteafd_b200.loader.safetensors_io import read_header
+    cfg = small()
+    src = snapshot.write_random_snapshot(cfg, str(tmp_path / "src"), fmt="bf16", seed=5)
+    sealed = str(tmp_path / "w" / "windows.safetensors")
+    os.makedirs(os.path.dirname(sealed))
+    assert main(["fidelity", "seal", src, sealed, "--windows", "3", "--seq", "24"]) == 0
+    assert main(["fidelity", "check", src, sealed, "--max-kl", "1e-9", "--min-top1", "1.0"]) == 0
+    tensors, info = fidelity.load_sealed(sealed)
+    assert tensors["tokens"].shape == (3, 24) and info["windows"] == 3 and tensors["top_ids"].shape[-1] == fidelity.TOP_K
+    reports = {}
+    for fmt in ("fp8_block128", "mxfp4"):
+        dst = str(tmp_path / fmt)
+        run(src, dst, Recipe({"routed_expert": fmt, "dense_ffn": fmt, "attention": fmt}), log=lambda *_: None)
+        cfg_q, p_q = load.load_params(dst)
+        reports[fmt] = fidelity.check(fidelity.logits_fn_for(cfg_q, p_q), tensors)
+    assert 0 < reports["fp8_block128"]["kl_mean"] < reports["mxfp4"]["kl_mean"] < 0.05
+    assert reports["fp8_block128"]["top1"] >= reports["mxfp4"]["top1"] > 0.5 and reports["mxfp4"]["kl_max"] >= reports["mxfp4"]["kl_p99"]
+    # a strict threshold fails the 4-bit copy
+    assert main(["fidelity", "check", str(tmp_path / "mxfp4"), sealed, "--max-kl", "1e-7"]) == 1
+    # flipping one stored byte breaks the digest
+    _, base = read_header(sealed)
+    raw = bytearray(open(sealed, "rb").read())
+    raw[base + 5] ^= 1
+    open(sealed, "wb").write(bytes(raw))
+    with pytest.raises(ValueError, match="digest"):
+        fidelity.load_sealed(sealed)
