@@ -56,6 +56,13 @@ CONFIG_KEYS = {"MODEL", "GPUS", "ATTENTION_RANKS", "EXPERT_RANKS", "POOL_TOKENS"
 
 def cmd_plan(a: argparse.Namespace) -> int:
     from .planner import plan as P
+    if a.fetch:
+        from .loader.slice import slice_snapshot
+        er = tuple(int(v) for v in a.expert_range.split(":")) if a.expert_range else None
+        info = slice_snapshot(a.model, a.fetch, roles={r for r in a.role.split(",") if r} or None,
+                              exclude={r for r in a.exclude_role.split(",") if r} or None, expert_range=er)
+        print(json.dumps(info, indent=1))
+        return 0
     kw = dict(gpus=a.gpus, attention_ranks=a.attention_ranks, expert_ranks=a.expert_ranks, pool_tokens_target=a.pool_tokens,
               gpu_memory_cap=_size(a.gpu_memory_cap) if a.gpu_memory_cap else None, max_context_tokens=a.max_context_tokens,
               concurrency=a.concurrency, speculator=a.speculator, decode_lanes=a.decode_lanes,
@@ -252,6 +259,9 @@ def _build_parser() -> argparse.ArgumentParser:
     p.add_argument("--layout", action="store_true"); p.add_argument("--json", action="store_true")
     p.add_argument("--deployment", action="store_true"); p.add_argument("--files", action="store_true")
     p.add_argument("--role", default=""); p.add_argument("--require-ready", action="store_true")
+    p.add_argument("--fetch", default="", help="copy the slice named by --role / --exclude-role / --expert-range into this directory, byte for byte")
+    p.add_argument("--exclude-role", default="", help="with --fetch: comma-separated roles to leave out")
+    p.add_argument("--expert-range", default="", help="with --fetch: first:end of the routed experts to keep")
     p.add_argument("--gpus", type=int, default=8); p.add_argument("--attention-ranks", type=int, default=None)
     p.add_argument("--expert-ranks", type=int, default=None); p.add_argument("--pipeline-stages", type=int, default=1)
     p.add_argument("--pool-tokens", type=int, default=None); p.add_argument("--gpu-memory-cap", default="")

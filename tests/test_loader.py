@@ -175,3 +175,30 @@ def test_new_presets_are_consistent():
     for cfg in (m, k):
         back = snapshot.from_hf_config(snapshot.to_hf_config(cfg))
         assert back.num_experts == cfg.num_experts and back.num_heads == cfg.num_heads and back.attention == cfg.attention
+
+
+def test_sliced_checkpoint_copy(tmp_path):
+    """An expert rank's slice holds its experts only, the attention slice everything else; bytes are the source's."""
+    import json as _json
+    from cuteafd_b200 import tiny_moe
+    from cuteafd_b200.cli import main
+    from cuteafd_b200.loader.slice import slice_snapshot
+    cfg = tiny_moe()
+    src = snapshot.write_random_snapshot(cfg, str(tmp_path / "src"), fmt="fp8_block128", seed=2)
+    full = Catalog(src)
+    ex = slice_snapshot(src, str(tmp_path / "experts"), roles={"routed_expert"}, expert_range=(2, 5), shard_bytes=1 << 16)
+    cat = Catalog(str(tmp_path / "experts"))
+    names = cat.names()
+    assert names and all(".mlp.experts." in n and 2 <= int(n.split(".mlp.experts.")[1].split(".")[0]) < 5 for n in names)
+    assert any(n.endswith("weight_scale_inv") for n in names)                       # scales travel with their weights
+    assert all(cat.sha256(n) == full.sha256(n) for n in names) and ex["tensors"] == len(names) and ex["bytes"] < ex["source_bytes"]
+    assert len({e.file for e in cat.entries.values()}) > 1                          # sharded by the byte limit
+    idx = _json.load(open(tmp_path / "experts" / "model.safetensors.index.json"))
+    assert set(idx["weight_map"]) == set(names) and (tmp_path / "experts" / "config.json").exists()
+    assert main(["plan", src, "--fetch", str(tmp_path / "attn"), "--exclude-role", "routed_expert"]) == 0
+    attn = Catalog(str(tmp_path / "attn"))
+    assert not any(".mlp.experts." in n for n in attn.names()) and "model.embed_tokens.weight" in attn
+    assert set(attn.names()) | {n for n in full.names() if ".mlp.experts." in n} == set(full.names())
+    assert _json.load(open(tmp_path / "attn" / "slice.json"))["exclude"] == ["routed_expert"]
+    with pytest.raises(ValueError, match="matches no tensor"):
+        slice_snapshot(src, str(tmp_path / "none"), roles={"routed_expert"}, expert_range=(100, 101))
