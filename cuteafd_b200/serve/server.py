@@ -379,7 +379,13 @@ def build_state(args) -> ServerState:
         pages_per_seq = args.max_context_tokens // 64 + 2
         num_pages = pages_per_seq * args.concurrency + 64
         rows = args.concurrency * 8
-        if snapshot:
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if world > 1:
+            # Disaggregated deployment (launched with one process per GPU): rank 0 runs attention, the dense backbone
+            # and this HTTP server; the other ranks hold the routed experts and serve announced steps until rank 0
+            # stops them.  The attention engine plugs into the same backend as the single-GPU engine.
+            cfg, eng = _build_afd_rank(args, snapshot, world, num_pages, pages_per_seq, rows)
+        elif snapshot:
             from ..loader.load import load_engine
             cfg, eng = load_engine(snapshot, dev, num_pages, max(2048, rows), rows, getattr(args, "kv_format", "auto"))
         else:
@@ -447,6 +453,47 @@ def build_state(args) -> ServerState:
     return ServerState(sched, tok, cfg.name, args.api_key, usage, media=media)
 
 
+_AFD_HANDLE = None
+
+
+def _build_afd_rank(args, snapshot, world: int, num_pages: int, pages_per_seq: int, rows: int):
+    """Join the deployment's process group and build this rank's half.  Expert ranks never return from here: they
+    serve until the attention rank shuts the group down, then leave the process."""
+    global _AFD_HANDLE
+    import torch
+    import torch.distributed as dist
+
+    from ..config import PRESETS
+    from ..parallel.afd import build_afd
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=dev)
+    params = None
+    if snapshot:
+        from ..loader.load import load_params
+        part = dict(only=".mlp.experts.") if rank else dict(exclude=".mlp.experts.")
+        cfg, params = load_params(snapshot, dtype=torch.bfloat16, **part)
+    else:
+        cfg = PRESETS[args.preset or "qwen3-30b-a3b"]()
+        if args.layers:
+            cfg = cfg.replace(num_layers=args.layers)
+    h = build_afd(cfg, dev, rank, world, max_tokens=max(2048, rows), max_seqs=rows, num_pages=num_pages,
+                  pages_per_seq=pages_per_seq, params=params, prefill_chunk=2048)
+    torch.cuda.synchronize()
+    dist.barrier()
+    if h.worker is not None:
+        h.worker.serve()
+        dist.barrier()
+        dist.destroy_process_group()
+        raise SystemExit(0)
+    _AFD_HANDLE = h
+    print(f"[serve] {h.parallelism}", flush=True)
+    return cfg, h.generator.engine
+
+
 def run_server(args) -> int:
     state = build_state(args)
     from ..utils.diagnostics import install_stack_dump
@@ -458,6 +505,11 @@ def run_server(args) -> int:
             time.sleep(3600)
     except KeyboardInterrupt:
         srv.stop()
+        if _AFD_HANDLE is not None:                       # release the expert ranks, then leave the group together
+            import torch.distributed as dist
+            _AFD_HANDLE.shutdown()
+            dist.barrier()
+            dist.destroy_process_group()
         if state.sched.trace is not None:
             state.sched.trace.close()
         be = state.sched.be

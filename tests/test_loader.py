@@ -202,3 +202,15 @@ def test_sliced_checkpoint_copy(tmp_path):
     assert _json.load(open(tmp_path / "attn" / "slice.json"))["exclude"] == ["routed_expert"]
     with pytest.raises(ValueError, match="matches no tensor"):
         slice_snapshot(src, str(tmp_path / "none"), roles={"routed_expert"}, expert_range=(100, 101))
+
+
+def test_load_params_only_and_exclude_partition_the_checkpoint(tmp_path):
+    from cuteafd_b200 import tiny_moe
+    cfg = tiny_moe()
+    src = snapshot.write_random_snapshot(cfg, str(tmp_path / "s"), fmt="fp8_block128", seed=6)
+    _, everything = load.load_params(src)
+    _, experts = load.load_params(src, only=".mlp.experts.")
+    _, rest = load.load_params(src, exclude=".mlp.experts.")
+    assert experts and all(".mlp.experts." in n for n in experts) and not any(".mlp.experts." in n for n in rest)
+    assert set(experts) | set(rest) == set(everything) and not set(experts) & set(rest)
+    assert not any(n.endswith("weight_scale_inv") for n in rest)            # an excluded operand's scales go with it
