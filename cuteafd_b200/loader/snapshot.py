@@ -106,6 +106,16 @@ def from_hf_config(d: dict) -> ModelConfig:
             indexer_heads=d.get("index_n_heads", 0) or 0, indexer_dim=d.get("index_head_dim", 128),
             indexer_topk=d.get("index_topk", 2048), **common)
     if mt in ("qwen3_moe", "qwen3", "qwen2_moe", "mixtral"):
+        # refuse what the engines would silently compute differently
+        if d.get("shared_expert_intermediate_size"):
+            raise ValueError("a gated shared expert (shared_expert_intermediate_size) is not supported")
+        if d.get("decoder_sparse_step", 1) not in (0, 1):
+            raise ValueError("interleaved dense / sparse layers (decoder_sparse_step > 1) are not supported")
+        dense_layers = sorted(d.get("mlp_only_layers", []) or [])
+        if dense_layers != list(range(len(dense_layers))):
+            raise ValueError("dense layers must be the first layers of the stack")
+        if d.get("attention_bias") or d.get("use_sliding_window"):
+            raise ValueError("projection biases and sliding-window attention are not supported")
         return ModelConfig(
             family="qwen3_moe", attention="gqa", num_kv_heads=d.get("num_key_value_heads", d["num_attention_heads"]),
             head_dim=d.get("head_dim", d["hidden_size"] // d["num_attention_heads"]), qk_norm=bool(d.get("qk_norm", mt.startswith("qwen3"))),

@@ -214,3 +214,15 @@ def test_load_params_only_and_exclude_partition_the_checkpoint(tmp_path):
     assert experts and all(".mlp.experts." in n for n in experts) and not any(".mlp.experts." in n for n in rest)
     assert set(experts) | set(rest) == set(everything) and not set(experts) & set(rest)
     assert not any(n.endswith("weight_scale_inv") for n in rest)            # an excluded operand's scales go with it
+
+
+def test_config_mapping_refuses_what_it_cannot_serve():
+    base = {"model_type": "qwen3_moe", "vocab_size": 1000, "num_hidden_layers": 4, "hidden_size": 256, "num_attention_heads": 2,
+            "num_key_value_heads": 1, "head_dim": 128, "intermediate_size": 512, "moe_intermediate_size": 128, "num_experts": 8,
+            "num_experts_per_tok": 2}
+    assert snapshot.from_hf_config(dict(base, mlp_only_layers=[0, 1])).first_dense_layers == 2
+    for bad, msg in ((dict(shared_expert_intermediate_size=512), "shared expert"), (dict(decoder_sparse_step=2), "interleaved"),
+                     (dict(mlp_only_layers=[1, 3]), "first layers"), (dict(attention_bias=True), "biases"),
+                     (dict(model_type="gpt_oss"), "unsupported model_type")):
+        with pytest.raises(ValueError, match=msg):
+            snapshot.from_hf_config(dict(base, **bad))
