@@ -402,14 +402,17 @@ def build_state(args) -> ServerState:
             eng = Engine(cfg, Weights.random_init(cfg, dev), Cache(cfg, num_pages, dev), max_tokens=max(2048, rows), max_seqs=rows)
         be = EngineBackend(eng, num_pages, pages_per_seq, prefill_chunk=2048, max_decode_rows=args.concurrency)
         from ..utils.memory_ledger import LEDGER
-        LEDGER.tag_tree("weights", "engine", eng.W)            # an arena's storage is already counted: adds nothing then
-        LEDGER.tag_tree("kv", "engine", eng.kv)
-        LEDGER.tag_tree("workspace", "engine", eng)
-        LEDGER.tag_tree("workspace", "backend", be)
-        if getattr(args, "memory_spool", ""):
-            LEDGER.open_spool(args.memory_spool)
-        for line in LEDGER.lines():
-            print(line, flush=True)
+        try:
+            LEDGER.tag_tree("weights", "engine", eng.W)        # an arena's storage is already counted: adds nothing then
+            LEDGER.tag_tree("kv", "engine", eng.kv)
+            LEDGER.tag_tree("workspace", "engine", eng)
+            LEDGER.tag_tree("workspace", "backend", be)
+            if getattr(args, "memory_spool", ""):
+                LEDGER.open_spool(args.memory_spool)
+            for line in LEDGER.lines():
+                print(line, flush=True)
+        except Exception as e:                                 # noqa: BLE001 - accounting never stops a server from starting
+            print(f"[memory] ledger unavailable: {e}", flush=True)
         pw = getattr(args, "prewarm", "")
         if pw:
             import json
