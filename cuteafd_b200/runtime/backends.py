@@ -70,8 +70,10 @@ class OracleBackend:
         self.last_mtp = mtp
         return toks, status
 
-    def open(self, tokens: list[int]) -> tuple[_Handle, int]:
+    def open(self, tokens: list[int], cold: bool = False) -> tuple[_Handle, int]:
         from ..ref.model import KvState
+        if cold:                                   # probe: compute the whole prompt, whatever the cache holds
+            return _Handle(self.table.new(), KvState(self.cfg)), 0
         seq, m = self.prefix.admit(tokens)
         kv = KvState(self.cfg)
         if m.length and m.snapshot is not None and m.snapshot.mark is not None:
@@ -183,7 +185,9 @@ class EngineBackend:
         kv = self.engine.kv if hasattr(self.engine, "kv") else self.engine.inner.kv
         kv.copy_page(src, dst)
 
-    def open(self, tokens: list[int]) -> tuple[_Handle, int]:
+    def open(self, tokens: list[int], cold: bool = False) -> tuple[_Handle, int]:
+        if cold:                                   # probe: compute the whole prompt, whatever the cache holds
+            return _Handle(self.table.new()), 0
         seq, m = self.prefix.admit(tokens)
         return _Handle(seq), m.length
 

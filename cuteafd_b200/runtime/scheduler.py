@@ -54,6 +54,8 @@ class Request:
     speculation: bool = True
     record_rows: bool = False          # probe: keep a hash of every selected logit row
     constraint: Any = None             # TokenConstraint: allowed-token mask applied first in the chain
+    top_logprobs: int = 0              # > 0: keep the chosen token's log-probability and this many alternatives per token
+    cold: bool = False                 # probe: do not look the prompt up in the prefix cache
     media: Any = None                  # list of media spans (prompt position, embedding rows) for ids above the vocabulary
     rid: int = 0
     events: "queue.Queue[tuple]" = field(default_factory=queue.Queue)
@@ -74,6 +76,7 @@ class Active:
     spec: dict = field(default_factory=lambda: {"proposed": 0, "accepted": 0, "cycles": 0})
     first_token_at: float = 0.0
     stalled: bool = False
+    top_rows: list = field(default_factory=list)   # per selected token: (token, logprob, top ids, top logprobs)
     guard: Any = None                  # RepeatGuard (loop abort), None when the detector is off
     finish_detail: str = ""
 
@@ -211,7 +214,7 @@ class Scheduler:
         while self.pending and len(self.prefilling) + len(self.decoding) < self.max_active:
             req = self.pending[0]
             try:
-                handle, cached = self.be.open(req.prompt)
+                handle, cached = self.be.open(req.prompt, cold=True) if req.cold else self.be.open(req.prompt)
             except Exception as e:                      # a failed restore is a miss, not an error
                 req.events.put(("error", FAIL_UNAVAILABLE, f"open failed: {e}"))
                 self.pending.pop(0)
@@ -365,7 +368,8 @@ class Scheduler:
         rows = [[a.last_token] + d for a, d in zip(runnable, drafts)]
         # GPU selection when nothing needs the logit rows on the host (grammar masks advance per token on the
         # host; row hashes are taken from the row bytes)
-        on_device = hasattr(self.be, "verify_select") and all(a.req.constraint is None and not a.req.record_rows for a in runnable)
+        on_device = hasattr(self.be, "verify_select") and all(
+            a.req.constraint is None and not a.req.record_rows and not a.req.top_logprobs for a in runnable)
         picked: list[int] | None = None
         picked_status: list[int] = []
         try:
@@ -448,6 +452,10 @@ class Scheduler:
             return None
         if a.req.record_rows:
             a.row_hashes.append(sampling.row_hash(row))
+        if a.req.top_logprobs:
+            lp = torch.log_softmax(row.float(), dim=-1)
+            v, i = lp.topk(min(a.req.top_logprobs, lp.numel()))
+            a.top_rows.append((int(tok), float(lp[tok]), i.tolist(), v.tolist()))
         return tok
 
     def _emit(self, a: Active, toks: list[int]) -> bool:
@@ -489,6 +497,9 @@ class Scheduler:
                      "speculation": dict(a.spec, request_id=a.req.rid)}
             if a.finish_detail:
                 usage["finish_detail"] = a.finish_detail
+            if a.req.top_logprobs:
+                # rows were kept per selection; a reply cut by a stop or a limit keeps the rows of the emitted tokens
+                usage["top_rows"] = a.top_rows[: len(a.generated)]
             a.req.events.put(("done", reason, usage, list(a.row_hashes)))
             self.stats.finished += 1
         else:

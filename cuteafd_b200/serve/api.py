@@ -7,7 +7,8 @@ request 400, unavailable 503, retry 429 with ``Retry-After: 1``, worker 500
 (rust/crates/cuteafd-api/src/openai.rs:281-286; docs/client-apis.md:40-50).  ``usage.speculation``
 carries {request_id, proposed, accepted, cycles} (docs/client-apis.md:31-38).  The probe header
 ``x-cuteafd-probe`` carries a JSON ProbeSpec: prompt_ids (synthetic token-id prompts),
-no_speculation, record_rows (rust/crates/cuteafd-api/src/openai/probe.rs:19-110).
+no_speculation, record_rows, cold (skip the prefix cache), top_k (top ids and log-probabilities of every selected row)
+(rust/crates/cuteafd-api/src/openai/probe.rs:19-110).
 """
 from __future__ import annotations
 
@@ -102,9 +103,25 @@ def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, f
         cons = constraints.from_response_format(fmt, tok, vocab_size)
     except ValueError as e:
         raise BadRequest(str(e)) from e
+    n_top = body.get("top_logprobs") or 0
+    if not isinstance(n_top, int) or not 0 <= n_top <= 20:
+        raise BadRequest("top_logprobs must be an integer between 0 and 20")
+    keep = max(n_top, 1) if (body.get("logprobs") or n_top) else 0
+    keep = max(keep, int(probe.get("top_k", 0) or 0))
     return Request(prompt=prompt, max_tokens=max_tokens, params=_params(body), stop_ids=_stops(body, tok),
                    speculation=not probe.get("no_speculation", False), record_rows=bool(probe.get("record_rows", False)),
-                   constraint=cons, media=spans)
+                   constraint=cons, media=spans, top_logprobs=keep, cold=bool(probe.get("cold", False)))
+
+
+def logprobs_block(tok, top_rows: list, n_top: int) -> dict:
+    """OpenAI ``choices[].logprobs``: one entry per generated token with its log-probability and ``n_top`` alternatives."""
+    def piece(t: int) -> dict:
+        raw = tok.token_bytes(t) if t < tok.vocab_size else b""
+        return {"token": raw.decode("utf-8", "replace"), "bytes": list(raw)}
+    content = []
+    for t, lp, ids, vals in top_rows:
+        content.append(dict(piece(t), logprob=lp, top_logprobs=[dict(piece(i), logprob=v) for i, v in zip(ids[:n_top], vals[:n_top])]))
+    return {"content": content}
 
 
 def parse_probe(headers) -> dict:
@@ -132,7 +149,8 @@ def usage_block(u: dict) -> dict:
 
 
 # ---- OpenAI chat completions ---------------------------------------------------------------------------
-def chat_completion(model: str, text: str, finish: str, usage: dict, probe_rows: list[str] | None = None) -> dict:
+def chat_completion(model: str, text: str, finish: str, usage: dict, probe_rows: list[str] | None = None,
+                    logprobs: dict | None = None) -> dict:
     content, calls = parse_tool_calls(text)
     msg = {"role": "assistant", "content": content}
     if calls:
@@ -142,6 +160,8 @@ def chat_completion(model: str, text: str, finish: str, usage: dict, probe_rows:
            "choices": [{"index": 0, "message": msg, "finish_reason": finish}], "usage": usage_block(usage)}
     if probe_rows:
         out["probe"] = {"row_hashes": probe_rows}
+    if logprobs is not None:
+        out["choices"][0]["logprobs"] = logprobs
     return out
 
 

@@ -281,7 +281,16 @@ def make_handler(state: ServerState):
                     state.responses[obj["id"]] = obj
                     state.sessions[obj["id"]] = list(self._session or []) + [{"role": "assistant", "content": out_text}]
                 return self._json(200, obj)
-            return self._json(200, api.chat_completion(model, out_text, finish, usage, rows or None))
+            lps = None
+            if usage.get("top_rows") is not None:
+                body = getattr(self, "_acct", (None, None, None, {}))[3] or {}
+                if body.get("logprobs") or body.get("top_logprobs"):
+                    lps = api.logprobs_block(state.tok, usage["top_rows"], int(body.get("top_logprobs") or 0))
+            out = api.chat_completion(model, out_text, finish, usage, rows or None, lps)
+            if usage.get("top_rows") is not None and lps is None:            # asked for through the probe header
+                out.setdefault("probe", {})["top_rows"] = [{"token": t, "logprob": lp, "top_ids": ids, "top_logprobs": v}
+                                                           for t, lp, ids, v in usage["top_rows"]]
+            return self._json(200, out)
 
         def _stream(self, req: Request, model: str, flavor: str) -> None:
             self._sse_start()

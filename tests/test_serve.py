@@ -341,3 +341,27 @@ def test_http_panels_on_the_oracle_server(server):
     assert out["ok"]
     with pytest.raises(ValueError):
         panels.run(f"http://127.0.0.1:{server.port}", ["nope"], "sekret")
+
+
+def test_logprobs_and_probe_cold_top_k(server):
+    body = {"messages": [{"role": "user", "content": "alpha beta gamma " * 30}], "max_tokens": 5, "temperature": 0,
+            "logprobs": True, "top_logprobs": 3}
+    st, _, raw = call(server, "POST", "/v1/chat/completions", body)
+    out = json.loads(raw)
+    lp = out["choices"][0]["logprobs"]["content"]
+    assert st == 200 and len(lp) == out["usage"]["completion_tokens"] == 5
+    for e in lp:
+        tops = e["top_logprobs"]
+        assert len(tops) == 3 and tops[0]["logprob"] >= tops[1]["logprob"] >= tops[2]["logprob"]
+        assert e["logprob"] == tops[0]["logprob"] and e["bytes"] == tops[0]["bytes"] and e["logprob"] <= 0     # greedy: the top row
+    # the same prompt again would hit the prefix cache; a cold probe computes it all, and top_k comes back as ids
+    probe = {"x-cuteafd-probe": json.dumps({"cold": True, "top_k": 2})}
+    st, _, raw = call(server, "POST", "/v1/chat/completions", dict(body, logprobs=False, top_logprobs=0), probe)
+    cold = json.loads(raw)
+    assert st == 200 and cold["usage"]["prompt_tokens_details"]["cached_tokens"] == 0 and "logprobs" not in cold["choices"][0]
+    rows = cold["probe"]["top_rows"]
+    assert len(rows) == 5 and all(len(r["top_ids"]) == 2 and r["token"] == r["top_ids"][0] for r in rows)
+    assert [round(r["logprob"], 4) for r in rows] == [round(e["logprob"], 4) for e in lp]       # cold and warm agree
+    warm = json.loads(call(server, "POST", "/v1/chat/completions", dict(body, logprobs=False, top_logprobs=0))[2])
+    assert warm["usage"]["prompt_tokens_details"]["cached_tokens"] >= 64
+    assert call(server, "POST", "/v1/chat/completions", dict(body, top_logprobs=50))[0] == 400
