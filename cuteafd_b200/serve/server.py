@@ -115,9 +115,24 @@ def make_handler(state: ServerState):
             if path == "/v1/models":
                 return self._json(200, {"object": "list", "data": [{"id": state.model_id, "object": "model", "created": int(state.started),
                                                                       "owned_by": "cuteafd_b200"}]})
-            if path == "/v1/console/state":
+            if path in ("/v1/console/state", "/v1/console/snapshot"):
                 from .console import console_state
                 return self._json(200, console_state(state))
+            if path == "/v1/console/events":
+                # the same document pushed as server-sent events (one per period) until the client goes away
+                from .console import console_state
+                q = dict(p.split("=", 1) for p in self.path.partition("?")[2].split("&") if "=" in p)
+                period = min(10.0, max(0.05, float(q.get("period", 1.0))))
+                count = min(3600, max(1, int(q.get("count", 3600))))
+                self._sse_start()
+                try:
+                    for i in range(count):
+                        self._sse(console_state(state), "snapshot")
+                        if i + 1 < count:
+                            time.sleep(period)
+                except (BrokenPipeError, ConnectionResetError):
+                    pass
+                return None
             if path == "/console/memory":
                 from ..utils.memory_ledger import LEDGER
                 return self._json(200, LEDGER.report())
@@ -193,11 +208,31 @@ def make_handler(state: ServerState):
                       "/v1/messages/count_tokens": "anthropic", "/v1/responses/input_tokens": "responses"}.get(path)
             if flavor is None and path.startswith("/v1/responses/") and path.endswith("/cancel"):
                 flavor = "responses"
-            if flavor is None:
+            if flavor is None and path != "/v1/fabric/phase":
                 return self._json(404, {"error": {"message": f"no route {path}"}})
             if not self._authorized():
                 st, body, hd = 401, {"error": {"message": "invalid API key", "type": "authentication_error"}}, {}
                 return self._json(st, body, hd)
+            if path == "/v1/fabric/phase":
+                # a benchmark driver marks its phases; each mark closes the previous phase and returns what the
+                # server saw during it (scheduler counters as deltas, the thermal window)
+                try:
+                    name = str(self._body().get("phase", ""))
+                except api.BadRequest as e:
+                    return self._json(400, {"error": {"message": str(e)}})
+                from ..utils.thermal import monitor
+                now, snap = time.monotonic(), state.sched.snapshot()
+                with state.lock:
+                    prev = state.extras.get("_phase")
+                    state.extras["_phase"] = {"name": name, "t": now, "snap": snap}
+                closed = None
+                if prev:
+                    keys = ("admitted", "finished", "failed", "rejected", "prefill_tokens", "cached_tokens", "decode_rounds",
+                            "emitted_tokens", "verify_rows", "stalls")
+                    closed = {"phase": prev["name"], "seconds": round(now - prev["t"], 3),
+                              "delta": {k: snap.get(k, 0) - prev["snap"].get(k, 0) for k in keys},
+                              "thermal": monitor().window(prev["t"], now)}
+                return self._json(200, {"phase": name, "closed": closed})
             if path.startswith("/v1/responses/") and path.endswith("/cancel"):
                 with state.lock:
                     r = state.responses.get(path.split("/")[3])

@@ -365,3 +365,19 @@ def test_logprobs_and_probe_cold_top_k(server):
     warm = json.loads(call(server, "POST", "/v1/chat/completions", dict(body, logprobs=False, top_logprobs=0))[2])
     assert warm["usage"]["prompt_tokens_details"]["cached_tokens"] >= 64
     assert call(server, "POST", "/v1/chat/completions", dict(body, top_logprobs=50))[0] == 400
+
+
+def test_console_events_and_fabric_phase(server):
+    c = http.client.HTTPConnection("127.0.0.1", server.port, timeout=30)
+    c.request("GET", "/v1/console/events?period=0.05&count=3", headers={"Authorization": "Bearer sekret"})
+    r = c.getresponse()
+    raw = r.read().decode()
+    assert r.status == 200 and raw.count("event: snapshot") == 3
+    first = json.loads(raw.split("data: ", 1)[1].split("\n\n", 1)[0])
+    assert "pipeline" in first and "lanes" in first
+    assert json.loads(call(server, "GET", "/v1/console/snapshot")[2])["model"] == "tiny-moe"
+    st, _, raw = call(server, "POST", "/v1/fabric/phase", {"phase": "warm"})
+    assert st == 200 and json.loads(raw) == {"phase": "warm", "closed": None} or json.loads(raw)["phase"] == "warm"
+    call(server, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3})
+    closed = json.loads(call(server, "POST", "/v1/fabric/phase", {"phase": "timed"})[2])["closed"]
+    assert closed["phase"] == "warm" and closed["delta"]["finished"] == 1 and closed["delta"]["emitted_tokens"] >= 1 and closed["seconds"] > 0
