@@ -50,6 +50,89 @@ def _stops(body: dict, tok) -> tuple[int, ...]:
     return tuple(ids) + tuple(getattr(tok, "eos_ids", ()))
 
 
+def responses_items_to_messages(items: list) -> list[dict]:
+    """Responses ``input`` items -> chat messages: ``function_call`` items are the assistant's calls (consecutive ones
+    share a turn), ``function_call_output`` items turns of role ``tool``; reasoning items are dropped."""
+    msgs: list[dict] = []
+    for it in items:
+        if not isinstance(it, dict):
+            continue
+        t = it.get("type", "message")
+        if t == "function_call":
+            call = _call(it.get("call_id") or it.get("id", ""), it.get("name", ""), it.get("arguments"))
+            if msgs and msgs[-1].get("role") == "assistant" and msgs[-1].get("_calls_only"):
+                msgs[-1]["tool_calls"].append(call)
+            else:
+                msgs.append({"role": "assistant", "content": "", "tool_calls": [call], "_calls_only": True})
+        elif t == "function_call_output":
+            out = it.get("output")
+            msgs.append({"role": "tool", "tool_call_id": it.get("call_id", ""), "content": out if isinstance(out, str) else json.dumps(out)})
+        elif t == "message" or "role" in it:
+            one = {"role": it.get("role", "user"), "content": it.get("content")}
+            one.update({k: it[k] for k in ("tool_calls", "tool_call_id") if k in it})      # a stored conversation's own form
+            msgs.append(one)
+    for m in msgs:
+        m.pop("_calls_only", None)
+    return msgs
+
+
+def normalize_tools(tools, flavor: str) -> list[dict] | None:
+    """Tool declarations of any flavour -> OpenAI function tools (what the chat template shows the model).  Hosted tool
+    types (web search and the like) are the gateway's business and are left out here."""
+    out = []
+    for t in tools or []:
+        if not isinstance(t, dict):
+            continue
+        if isinstance(t.get("function"), dict):                                  # OpenAI chat
+            out.append({"type": "function", "function": t["function"]})
+        elif flavor == "anthropic" and "name" in t and "input_schema" in t:
+            out.append({"type": "function", "function": {"name": t["name"], "description": t.get("description", ""),
+                                                         "parameters": t["input_schema"]}})
+        elif t.get("type") == "function" and "name" in t:                        # Responses: flat
+            out.append({"type": "function", "function": {"name": t["name"], "description": t.get("description", ""),
+                                                         "parameters": t.get("parameters") or {"type": "object", "properties": {}}}})
+    return out or None
+
+
+def _call(call_id: str, name: str, arguments) -> dict:
+    return {"id": call_id, "type": "function",
+            "function": {"name": name, "arguments": arguments if isinstance(arguments, str) else json.dumps(arguments or {})}}
+
+
+def anthropic_messages(body: dict) -> list[dict]:
+    """Anthropic Messages history -> chat messages: ``tool_use`` blocks become the assistant's tool calls and
+    ``tool_result`` blocks turns of role ``tool``; other parts pass through for the template."""
+    msgs = []
+    if body.get("system"):
+        sysm = body["system"]
+        msgs.append({"role": "system", "content": sysm if isinstance(sysm, str) else "".join(p.get("text", "") for p in sysm)})
+    for m in body.get("messages") or []:
+        c = m.get("content")
+        if not isinstance(c, list):
+            msgs.append({"role": m.get("role", "user"), "content": c})
+            continue
+        keep, calls, results = [], [], []
+        for p in c:
+            if not isinstance(p, dict):
+                continue
+            if p.get("type") == "tool_use":
+                calls.append(_call(p.get("id", ""), p.get("name", ""), p.get("input")))
+            elif p.get("type") == "tool_result":
+                rc = p.get("content")
+                if isinstance(rc, list):
+                    rc = "".join(x.get("text", "") for x in rc if isinstance(x, dict))
+                results.append({"role": "tool", "tool_call_id": p.get("tool_use_id", ""), "content": rc if rc is not None else ""})
+            else:
+                keep.append(p)
+        msgs.extend(results)                                                      # results answer the previous turn: they come first
+        if keep or calls:
+            one = {"role": m.get("role", "user"), "content": keep}
+            if calls:
+                one["tool_calls"] = calls
+            msgs.append(one)
+    return msgs
+
+
 def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, flavor: str = "openai",
                   media=None) -> Request:
     # a probe too large for a header (a long synthetic prompt) may ride in the body instead
@@ -58,15 +141,10 @@ def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, f
         prompt, spans = [int(t) for t in probe["prompt_ids"]], None
     else:
         if flavor == "anthropic":
-            msgs = []
-            if body.get("system"):
-                sysm = body["system"]
-                msgs.append({"role": "system", "content": sysm if isinstance(sysm, str) else "".join(p.get("text", "") for p in sysm)})
-            msgs += list(body.get("messages") or [])
+            msgs = anthropic_messages(body)
         elif flavor == "responses":
             inp = body.get("input")
-            msgs = [{"role": "user", "content": inp}] if isinstance(inp, str) else [
-                {"role": m.get("role", "user"), "content": m.get("content")} for m in (inp or []) if isinstance(m, dict)]
+            msgs = [{"role": "user", "content": inp}] if isinstance(inp, str) else responses_items_to_messages(inp or [])
             if body.get("instructions"):
                 msgs.insert(0, {"role": "system", "content": body["instructions"]})
         else:
@@ -74,7 +152,7 @@ def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, f
         if not msgs:
             raise BadRequest("messages must not be empty")
         items: list = []
-        text = render_chat(msgs, True, body.get("tools"), media=items)
+        text = render_chat(msgs, True, normalize_tools(body.get("tools"), flavor), media=items)
         if items:
             # image / audio parts: tower rows replace placeholder ids (``media`` is the deployment's MediaProcessor)
             from ..media.image import MediaError, bytes_from_url
@@ -201,8 +279,7 @@ def anthropic_events(model: str, usage_in: int):
 def responses_messages(body: dict) -> list[dict]:
     """The Responses request as a chat message list (instructions first)."""
     inp = body.get("input")
-    msgs = [{"role": "user", "content": inp}] if isinstance(inp, str) else [
-        {"role": m.get("role", "user"), "content": m.get("content")} for m in (inp or []) if isinstance(m, dict)]
+    msgs = [{"role": "user", "content": inp}] if isinstance(inp, str) else responses_items_to_messages(inp or [])
     if body.get("instructions"):
         msgs.insert(0, {"role": "system", "content": body["instructions"]})
     return msgs
@@ -235,10 +312,17 @@ def input_items(msgs: list[dict]) -> dict:
 
 def responses_object(model: str, text: str, finish: str, usage: dict, rid: str | None = None) -> dict:
     rid = rid or "resp_" + uuid.uuid4().hex[:24]
+    text, calls = parse_tool_calls(text)
+    output = []
+    if text or not calls:
+        output.append({"type": "message", "id": "msg_" + uuid.uuid4().hex[:20], "role": "assistant", "status": "completed",
+                       "content": [{"type": "output_text", "text": text, "annotations": []}]})
+    for c in calls:                                                               # the model's tool calls as function_call items
+        output.append({"type": "function_call", "id": "fc_" + uuid.uuid4().hex[:20], "call_id": "call_" + uuid.uuid4().hex[:20],
+                       "name": c["function"]["name"], "arguments": c["function"]["arguments"], "status": "completed"})
     return {"id": rid, "object": "response", "created_at": int(time.time()), "model": model,
             "status": "completed" if finish in ("stop", "length") else "incomplete",
-            "output": [{"type": "message", "id": "msg_" + uuid.uuid4().hex[:20], "role": "assistant", "status": "completed",
-                        "content": [{"type": "output_text", "text": text, "annotations": []}]}],
+            "output": output,
             "output_text": text,
             "usage": {"input_tokens": usage.get("prompt_tokens", 0), "output_tokens": usage.get("completion_tokens", 0),
                       "total_tokens": usage.get("prompt_tokens", 0) + usage.get("completion_tokens", 0)}}

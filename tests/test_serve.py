@@ -381,3 +381,39 @@ def test_console_events_and_fabric_phase(server):
     call(server, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3})
     closed = json.loads(call(server, "POST", "/v1/fabric/phase", {"phase": "timed"})[2])["closed"]
     assert closed["phase"] == "warm" and closed["delta"]["finished"] == 1 and closed["delta"]["emitted_tokens"] >= 1 and closed["seconds"] > 0
+
+
+def test_tool_history_translation_across_flavours():
+    from cuteafd_b200.serve import api
+    from cuteafd_b200.serve.tokenizer import render_chat
+    a_tools = [{"name": "get_time", "description": "now", "input_schema": {"type": "object", "properties": {"tz": {"type": "string"}}}},
+               {"type": "web_search_20250305", "name": "web_search"}]
+    norm = api.normalize_tools(a_tools, "anthropic")
+    assert norm == [{"type": "function", "function": {"name": "get_time", "description": "now", "parameters": a_tools[0]["input_schema"]}}]
+    r_tools = [{"type": "function", "name": "get_time", "parameters": {"type": "object", "properties": {}}}, {"type": "web_search"}]
+    assert api.normalize_tools(r_tools, "responses")[0]["function"]["name"] == "get_time" and len(api.normalize_tools(r_tools, "responses")) == 1
+    assert api.normalize_tools([], "openai") is None
+    body = {"system": "be brief", "messages": [
+        {"role": "user", "content": "time in Oslo?"},
+        {"role": "assistant", "content": [{"type": "text", "text": "checking"}, {"type": "tool_use", "id": "tu_1", "name": "get_time", "input": {"tz": "Europe/Oslo"}}]},
+        {"role": "user", "content": [{"type": "tool_result", "tool_use_id": "tu_1", "content": [{"type": "text", "text": "12:00"}]},
+                                     {"type": "text", "text": "thanks, and Paris?"}]}]}
+    msgs = api.anthropic_messages(body)
+    assert [m["role"] for m in msgs] == ["system", "user", "assistant", "tool", "user"]
+    assert msgs[2]["tool_calls"][0]["function"] == {"name": "get_time", "arguments": '{"tz": "Europe/Oslo"}'}
+    assert msgs[3] == {"role": "tool", "tool_call_id": "tu_1", "content": "12:00"}
+    text = render_chat(msgs, True, norm)
+    assert '<tool_call>{"name": "get_time"' in text and "<|im_start|>tool\n12:00" in text and text.index("12:00") < text.index("Paris")
+    items = [{"role": "user", "content": [{"type": "input_text", "text": "time?"}]},
+             {"type": "reasoning", "summary": []},
+             {"type": "function_call", "call_id": "c1", "name": "get_time", "arguments": "{}"},
+             {"type": "function_call", "call_id": "c2", "name": "get_time", "arguments": '{"tz":"UTC"}'},
+             {"type": "function_call_output", "call_id": "c1", "output": "12:00"},
+             {"type": "function_call_output", "call_id": "c2", "output": {"t": "11:00"}}]
+    rm = api.responses_items_to_messages(items)
+    assert [m["role"] for m in rm] == ["user", "assistant", "tool", "tool"] and len(rm[1]["tool_calls"]) == 2
+    assert rm[3]["content"] == '{"t": "11:00"}' and api.responses_items_to_messages(rm) == rm          # a stored conversation passes unchanged
+    obj = api.responses_object("m", 'ok <tool_call>{"name": "get_time", "arguments": {"tz": "UTC"}}</tool_call>', "stop", {})
+    kinds = [o["type"] for o in obj["output"]]
+    assert kinds == ["message", "function_call"] and obj["output"][1]["name"] == "get_time" and json.loads(obj["output"][1]["arguments"]) == {"tz": "UTC"}
+    assert obj["output_text"] == "ok "
