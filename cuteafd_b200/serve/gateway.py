@@ -19,31 +19,24 @@ from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 from . import api, search
 
 
+def _flatten(content):
+    """Text parts of any flavour -> one string (an OpenAI-compatible upstream takes plain strings everywhere)."""
+    if isinstance(content, list):
+        return "".join(p.get("text", "") for p in content if isinstance(p, dict) and p.get("type") in ("text", "input_text", "output_text"))
+    return content if content is not None else ""
+
+
 def to_chat_body(body: dict, flavor: str, model_map: dict[str, str]) -> dict:
-    msgs = []
     if flavor == "anthropic":
-        if body.get("system"):
-            s = body["system"]
-            msgs.append({"role": "system", "content": s if isinstance(s, str) else "".join(p.get("text", "") for p in s)})
-        for m in body.get("messages", []):
-            c = m.get("content")
-            if isinstance(c, list):
-                c = "".join(p.get("text", "") for p in c if p.get("type") == "text")
-            msgs.append({"role": m.get("role", "user"), "content": c})
+        msgs = api.anthropic_messages(body)
     else:
-        inp = body.get("input")
-        if body.get("instructions"):
-            msgs.append({"role": "system", "content": body["instructions"]})
-        if isinstance(inp, str):
-            msgs.append({"role": "user", "content": inp})
-        else:
-            for m in inp or []:
-                c = m.get("content")
-                if isinstance(c, list):
-                    c = "".join(p.get("text", "") for p in c if isinstance(p, dict))
-                msgs.append({"role": m.get("role", "user"), "content": c})
+        msgs = api.responses_messages(body)
+    msgs = [dict(m, content=_flatten(m.get("content"))) for m in msgs]
     out = {"model": model_map.get(body.get("model", ""), body.get("model", "")), "messages": msgs,
            "max_tokens": body.get("max_tokens") or body.get("max_output_tokens") or 256}
+    tools = api.normalize_tools(body.get("tools"), flavor)          # hosted tool types are handled by the gateway itself
+    if tools:
+        out["tools"] = tools
     for k in ("temperature", "top_p", "top_k", "seed", "stop"):
         if k in body:
             out[k] = body[k]
@@ -55,6 +48,13 @@ def to_chat_body(body: dict, flavor: str, model_map: dict[str, str]) -> dict:
 def from_chat_reply(reply: dict, flavor: str, model: str) -> dict:
     ch = reply["choices"][0]
     text = ch["message"].get("content") or ""
+    for c in ch["message"].get("tool_calls") or []:                 # back into the inline form the reply builders parse
+        fn = c.get("function", {})
+        try:
+            args = json.loads(fn.get("arguments") or "{}")
+        except json.JSONDecodeError:
+            args = {}
+        text += "<tool_call>" + json.dumps({"name": fn.get("name", ""), "arguments": args}) + "</tool_call>"
     u = reply.get("usage", {})
     usage = {"prompt_tokens": u.get("prompt_tokens", 0), "completion_tokens": u.get("completion_tokens", 0),
              "cached_tokens": u.get("prompt_tokens_details", {}).get("cached_tokens", 0)}

@@ -54,7 +54,11 @@ class Service:
                 svc.seen.append(("chat", body))
                 svc.turns += 1
                 tool_msgs = [m for m in body["messages"] if m["role"] == "tool"]
-                if not tool_msgs and any(t["function"]["name"] == "web_search" for t in body.get("tools", [])):
+                if not tool_msgs and any(t["function"]["name"] == "get_time" for t in body.get("tools", [])):
+                    msg = {"role": "assistant", "content": "one moment", "tool_calls": [
+                        {"id": "c9", "type": "function", "function": {"name": "get_time", "arguments": '{"tz": "UTC"}'}}]}
+                    fin = "tool_calls"
+                elif not tool_msgs and any(t["function"]["name"] == "web_search" for t in body.get("tools", [])):
                     msg = {"role": "assistant", "content": "", "tool_calls": [
                         {"id": "c1", "type": "function", "function": {"name": "web_search", "arguments": json.dumps({"query": "tma alignment"})}}]}
                     fin = "tool_calls"
@@ -152,5 +156,31 @@ def test_gateway_runs_the_search_the_model_asks_for(svc):
         assert st == 200 and svc.turns == 1 and all(o["type"] != "web_search_call" for o in out["output"])
         st, out = post("/v1/alpha/search", {"command": "search", "query": "tma"})
         assert st == 200 and out["ok"] and out["provider"] == "exa"
+    finally:
+        gw.stop()
+
+
+def test_gateway_forwards_client_tools_and_returns_calls(svc):
+    base = f"http://127.0.0.1:{svc.port}"
+    gw = Gateway(base).start()
+    try:
+        c = http.client.HTTPConnection("127.0.0.1", gw.port, timeout=30)
+        body = {"model": "m", "max_tokens": 32, "messages": [{"role": "user", "content": [{"type": "text", "text": "time?"}]}],
+                "tools": [{"name": "get_time", "description": "now", "input_schema": {"type": "object", "properties": {"tz": {"type": "string"}}}}]}
+        c.request("POST", "/v1/messages", json.dumps(body), {"Content-Type": "application/json"})
+        out = json.loads(c.getresponse().read())
+        sent = [b for k, b in svc.seen if k == "chat"][-1]
+        assert sent["tools"][0]["function"]["name"] == "get_time" and sent["messages"][0]["content"] == "time?"
+        kinds = [b["type"] for b in out["content"]]
+        assert kinds == ["text", "tool_use"] and out["content"][1]["name"] == "get_time" and out["content"][1]["input"] == {"tz": "UTC"}
+        assert out["stop_reason"] == "tool_use"
+        # the client answers with a tool_result: the upstream sees an assistant call and a tool turn
+        body["messages"] += [{"role": "assistant", "content": out["content"]},
+                             {"role": "user", "content": [{"type": "tool_result", "tool_use_id": out["content"][1]["id"], "content": "12:00"}]}]
+        c.request("POST", "/v1/messages", json.dumps(body), {"Content-Type": "application/json"})
+        out2 = json.loads(c.getresponse().read())
+        sent = [b for k, b in svc.seen if k == "chat"][-1]
+        assert [m["role"] for m in sent["messages"]] == ["user", "assistant", "tool"] and sent["messages"][2]["content"] == "12:00"
+        assert out2["content"][-1]["text"].startswith("answer using 12:00")
     finally:
         gw.stop()
