@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Headline benchmark: Qwen3-30B-A3B-shaped MoE, bf16, random init, synthetic token-id prompts.
 
-Workload (the third configuration of BASELINE.json): 8192-token random prompts, then greedy
+Workload (the reference's Qwen3 release card: cold 8K prefill, then decode sweeps): 8192-token random prompts, then greedy
 decode at concurrency 1 / 8 / 32.  Layout: attention on GPU 0; with more than one GPU the routed
 experts are expert-parallel over the remaining GPUs.  A "step" is one decode step of the
 concurrency-8 batch; ``--steps`` steps are timed on the device with CUDA events after
