@@ -515,3 +515,157 @@ int cafd_sample_token(const float* logits, int vocab, const uint8_t* mask, float
 }
 
 }  // extern "C"
+
+// ---- loop abort ---------------------------------------------------------------------------------------
+namespace {
+constexpr int kShingle = 32, kFastWindow = 256, kMaxShingles = 65536;
+struct ShingleRec { uint16_t count; int64_t last; };
+}  // namespace
+
+struct cafd_guard {
+  int run, copies, fast_span, fast_copies;
+  int64_t pushed = 0;
+  int fired = 0, period = 0;
+  int32_t ring[kFastWindow];
+  int64_t streak[kFastWindow + 1];
+  int64_t need[kFastWindow + 1];
+  int32_t tail[kShingle];
+  int tail_len = 0;
+  std::unordered_map<uint64_t, ShingleRec> seen;
+  int64_t consecutive = 0;
+};
+
+extern "C" {
+
+cafd_guard* cafd_guard_new(int run, int copies, int fast_span, int fast_copies) {
+  auto* g = new cafd_guard();
+  g->run = run;
+  g->copies = std::min(std::max(copies, 2), 64);
+  g->fast_span = fast_span;
+  g->fast_copies = std::min(std::max(fast_copies, 2), 64);
+  for (int i = 0; i < kFastWindow; ++i) g->ring[i] = -1;
+  for (int p = 0; p <= kFastWindow; ++p) {
+    g->streak[p] = 0;
+    g->need[p] = std::max<int64_t>(static_cast<int64_t>(g->fast_copies - 1) * p, std::max(fast_span, 1));
+  }
+  return g;
+}
+
+void cafd_guard_free(cafd_guard* g) { delete g; }
+int cafd_guard_period(const cafd_guard* g) { return g->period; }
+int64_t cafd_guard_pushed(const cafd_guard* g) { return g->pushed; }
+
+int cafd_guard_push(cafd_guard* g, int32_t token) {
+  if (g->fired) return g->fired;
+  const int64_t i = g->pushed++;
+  if (g->fast_span > 0) {
+    int hit = 0;
+    for (int p = 1; p <= kFastWindow; ++p) {
+      const bool same = p <= i && g->ring[(i - p) & (kFastWindow - 1)] == token;
+      g->streak[p] = same ? g->streak[p] + 1 : 0;
+      if (!hit && g->streak[p] >= g->need[p]) hit = p;
+    }
+    g->ring[i & (kFastWindow - 1)] = token;
+    if (hit) { g->fired = 1; g->period = hit; return 1; }
+  }
+  if (g->run > 0) {
+    if (g->tail_len == kShingle) {
+      for (int k = 1; k < kShingle; ++k) g->tail[k - 1] = g->tail[k];
+      g->tail[kShingle - 1] = token;
+    } else {
+      g->tail[g->tail_len++] = token;
+    }
+    if (g->tail_len == kShingle) {
+      uint64_t h = 1469598103934665603ull;                       // FNV-1a over the 32 token ids
+      for (int k = 0; k < kShingle; ++k) {
+        uint32_t v = static_cast<uint32_t>(g->tail[k]);
+        for (int b = 0; b < 4; ++b) { h ^= (v >> (8 * b)) & 0xFF; h *= 1099511628211ull; }
+      }
+      auto it = g->seen.find(h);
+      if (it == g->seen.end()) {
+        if (static_cast<int>(g->seen.size()) < kMaxShingles) g->seen.emplace(h, ShingleRec{1, i});
+        g->consecutive = 0;
+      } else {
+        const int64_t period = i - it->second.last;
+        const bool seen = it->second.count >= g->copies - 1 && period > kFastWindow;
+        if (it->second.count < 32768) ++it->second.count;
+        it->second.last = i;
+        g->consecutive = seen ? g->consecutive + 1 : 0;
+        if (g->consecutive >= g->run) { g->fired = 2; g->period = static_cast<int>(period); return 2; }
+      }
+    }
+  }
+  return 0;
+}
+
+}  // extern "C"
+
+// ---- expert wire protocol headers -------------------------------------------------------------------------
+namespace {
+const uint8_t kWireMagic[8] = {'C', 'A', 'F', 'D', 'W', 'I', 'R', 'E'};
+constexpr uint16_t kWireVersion = 2;
+template <typename T> void put(uint8_t* p, T v) { for (size_t i = 0; i < sizeof(T); ++i) p[i] = static_cast<uint8_t>(v >> (8 * i)); }
+template <typename T> T get(const uint8_t* p) { T v = 0; for (size_t i = 0; i < sizeof(T); ++i) v |= static_cast<T>(p[i]) << (8 * i); return v; }
+int wire_elem(int dtype) { return dtype == 1 || dtype == 2 ? 2 : dtype == 3 ? 4 : 0; }
+}  // namespace
+
+extern "C" {
+
+uint32_t cafd_wire_crc32(const uint8_t* data, uint64_t n) {
+  static uint32_t table[256];
+  static bool ready = false;
+  if (!ready) {
+    for (uint32_t i = 0; i < 256; ++i) {
+      uint32_t c = i;
+      for (int k = 0; k < 8; ++k) c = (c & 1) ? 0xEDB88320u ^ (c >> 1) : c >> 1;
+      table[i] = c;
+    }
+    ready = true;
+  }
+  uint32_t c = 0xFFFFFFFFu;
+  for (uint64_t i = 0; i < n; ++i) c = table[(c ^ data[i]) & 0xFF] ^ (c >> 8);
+  return c ^ 0xFFFFFFFFu;
+}
+
+void cafd_wire_pack_request(uint8_t* o, int kind, uint32_t flags, uint64_t seq, uint32_t layer, uint32_t rows, uint32_t hidden,
+                            uint32_t routes, int dtype, int reply_dtype, uint32_t unit, uint64_t payload_bytes, uint32_t crc,
+                            const uint8_t* plan16) {
+  std::memset(o, 0, 96);
+  std::memcpy(o, kWireMagic, 8);
+  put<uint16_t>(o + 8, kWireVersion);
+  put<uint16_t>(o + 10, static_cast<uint16_t>(kind));
+  put<uint32_t>(o + 12, flags);
+  put<uint64_t>(o + 16, seq);
+  put<uint32_t>(o + 24, layer);
+  put<uint32_t>(o + 28, rows);
+  put<uint32_t>(o + 32, hidden);
+  put<uint32_t>(o + 36, routes);
+  put<uint16_t>(o + 40, static_cast<uint16_t>(dtype));
+  put<uint16_t>(o + 42, static_cast<uint16_t>(reply_dtype));
+  put<uint32_t>(o + 44, unit);
+  put<uint64_t>(o + 48, payload_bytes);
+  put<uint32_t>(o + 56, crc);
+  if (plan16) std::memcpy(o + 60, plan16, 16);
+}
+
+int cafd_wire_parse_request(const uint8_t* in, int* kind, uint32_t* flags, uint64_t* seq, uint32_t* layer, uint32_t* rows,
+                            uint32_t* hidden, uint32_t* routes, int* dtype, int* reply_dtype, uint32_t* unit,
+                            uint64_t* payload_bytes, uint32_t* crc, uint8_t* plan16) {
+  *kind = get<uint16_t>(in + 10); *flags = get<uint32_t>(in + 12); *seq = get<uint64_t>(in + 16);
+  *layer = get<uint32_t>(in + 24); *rows = get<uint32_t>(in + 28); *hidden = get<uint32_t>(in + 32);
+  *routes = get<uint32_t>(in + 36); *dtype = get<uint16_t>(in + 40); *reply_dtype = get<uint16_t>(in + 42);
+  *unit = get<uint32_t>(in + 44); *payload_bytes = get<uint64_t>(in + 48); *crc = get<uint32_t>(in + 56);
+  if (plan16) std::memcpy(plan16, in + 60, 16);
+  if (std::memcmp(in, kWireMagic, 8) != 0) return 1;
+  if (get<uint16_t>(in + 8) != kWireVersion) return 2;
+  if (*payload_bytes > (1ull << 31)) return 4;
+  if (*kind == 2) {                                              // MOE: the payload size must follow from the counts
+    const int es = wire_elem(*dtype);
+    if (es == 0 || wire_elem(*reply_dtype) == 0) return 5;
+    const uint64_t want = static_cast<uint64_t>(*routes) * 12 + static_cast<uint64_t>(*rows) * (*hidden) * es;
+    if (*payload_bytes != want || *hidden == 0) return 4;
+  }
+  return 0;
+}
+
+}  // extern "C"

@@ -65,6 +65,27 @@ int cafd_sample_token(const float* logits, int vocab, const uint8_t* mask, float
                       float min_p, uint64_t seed, uint64_t position, int use_uniform, float uniform);
 float cafd_sample_uniform(uint64_t seed, uint64_t position);
 
+// Loop abort (exact-repetition detector fed with every generated token).  Rule F: cycles of period 1..256, fires when
+// the run of t[i] == t[i - P] reaches max((fast_copies - 1) * P, fast_span).  Rule R: 32-token shingles seen copies - 1
+// times before with the previous occurrence more than 256 tokens back, `run` consecutive positions.  push returns
+// 0 (go on), 1 (rule F fired), 2 (rule R fired); the result is sticky.  run == 0 / fast_span == 0 switch a rule off.
+typedef struct cafd_guard cafd_guard;
+cafd_guard* cafd_guard_new(int run, int copies, int fast_span, int fast_copies);
+void cafd_guard_free(cafd_guard*);
+int cafd_guard_push(cafd_guard*, int32_t token);
+int cafd_guard_period(const cafd_guard*);        // period of the loop that fired (0 before)
+int64_t cafd_guard_pushed(const cafd_guard*);
+
+// Expert wire protocol: 96-byte little-endian frame headers (layout in cuteafd_b200/parallel/wire.py) and the payload
+// checksum.  parse returns 0 ok, 1 bad magic, 2 bad version, 4 bad shape, 5 bad dtype (the protocol's status codes).
+uint32_t cafd_wire_crc32(const uint8_t* data, uint64_t n);
+void cafd_wire_pack_request(uint8_t* out96, int kind, uint32_t flags, uint64_t seq, uint32_t layer, uint32_t rows, uint32_t hidden,
+                            uint32_t routes, int dtype, int reply_dtype, uint32_t unit, uint64_t payload_bytes, uint32_t crc,
+                            const uint8_t* plan16);
+int cafd_wire_parse_request(const uint8_t* in96, int* kind, uint32_t* flags, uint64_t* seq, uint32_t* layer, uint32_t* rows,
+                            uint32_t* hidden, uint32_t* routes, int* dtype, int* reply_dtype, uint32_t* unit,
+                            uint64_t* payload_bytes, uint32_t* crc, uint8_t* plan16);
+
 #ifdef __cplusplus
 }
 #endif

@@ -41,8 +41,15 @@ class LoopAbortConfig:
     def enabled(self) -> bool:
         return self.run > 0 or self.fast_span > 0
 
-    def guard(self) -> "RepeatGuard | None":
-        return RepeatGuard(self) if self.enabled else None
+    def guard(self):
+        """A detector for one request: the C++ twin when the runtime library is there, this module's otherwise."""
+        if not self.enabled:
+            return None
+        try:
+            from .native import NativeRepeatGuard
+            return NativeRepeatGuard(self)
+        except (OSError, AttributeError, ImportError):
+            return RepeatGuard(self)
 
 
 class RepeatGuard:

@@ -108,3 +108,51 @@ def test_native_sampler_matches_oracle():
     bad = torch.tensor([1.0, float("nan")])
     assert native.sample_token(bad) == -1
     assert native.sample_token(torch.ones(4), mask=torch.zeros(4, dtype=torch.bool)) == -2
+
+
+def test_native_repeat_guard_matches_python():
+    import random
+    import time
+    from cuteafd_b200.runtime.native import NativeRepeatGuard
+    from cuteafd_b200.runtime.repeat_guard import LoopAbortConfig, RepeatGuard
+    rnd = random.Random(4)
+    streams = []
+    for period in (1, 2, 7, 40, 255, 256, 257, 300, 700):
+        head = [rnd.randrange(50000) for _ in range(rnd.randrange(0, 90))]
+        blk = [rnd.randrange(50000) for _ in range(period)]
+        streams.append(head + blk * (9000 // period + 2))
+    streams.append([rnd.randrange(50000) for _ in range(6000)])                       # never fires
+    streams.append([rnd.randrange(3) for _ in range(6000)])                            # tiny alphabet, no exact long loop
+    for cfg in (LoopAbortConfig(), LoopAbortConfig(run=64, copies=3, fast_span=48, fast_copies=4), LoopAbortConfig(run=0),
+                LoopAbortConfig(fast_span=0)):
+        for toks in streams:
+            a, b = RepeatGuard(cfg), NativeRepeatGuard(cfg)
+            fa = next((i + 1 for i, t in enumerate(toks) if a.push(t)), None)
+            fb = next((i + 1 for i, t in enumerate(toks) if b.push(t)), None)
+            assert fa == fb, (cfg, fa, fb)
+            assert (a.hit or {}).get("rule") == (b.hit or {}).get("rule") and (a.hit or {}).get("period") == (b.hit or {}).get("period")
+    assert type(LoopAbortConfig().guard()).__name__ == "NativeRepeatGuard"
+    g, t0 = NativeRepeatGuard(LoopAbortConfig()), time.perf_counter()
+    for t in streams[-2]:
+        g.push(t)
+    assert (time.perf_counter() - t0) / 6000 < 20e-6
+
+
+def test_native_wire_headers_match_python():
+    import zlib
+    from cuteafd_b200.parallel import wire
+    from cuteafd_b200.runtime import native
+    payload = bytes(range(256)) * 5 + b"tail"
+    assert native.wire_crc32(payload) == zlib.crc32(payload) and native.wire_crc32(b"") == zlib.crc32(b"")
+    req = wire.Request(wire.MOE, seq=9, flags=1, layer=4, rows=3, hidden=8, routes=5, dtype=wire.BF16, reply_dtype=wire.F32, unit=2,
+                       plan=b"0123456789abcdef", payload=bytes(5 * 12 + 3 * 8 * 2))
+    raw = req.pack()[:wire.HEADER]
+    mine = native.wire_pack_request(wire.MOE, 1, 9, 4, 3, 8, 5, wire.BF16, wire.F32, 2, len(req.payload), zlib.crc32(req.payload), req.plan)
+    assert mine == raw
+    st, f = native.wire_parse_request(raw)
+    assert st == wire.OK and (f["seq"], f["layer"], f["rows"], f["hidden"], f["routes"], f["unit"]) == (9, 4, 3, 8, 5, 2) and f["plan"] == req.plan
+    for mutate, want in ((lambda b: b.__setitem__(0, 0x58), wire.BAD_MAGIC), (lambda b: b.__setitem__(8, 7), wire.BAD_VERSION),
+                         (lambda b: b.__setitem__(28, 4), wire.BAD_SHAPE), (lambda b: b.__setitem__(40, 9), wire.BAD_DTYPE)):
+        bad = bytearray(raw)
+        mutate(bad)
+        assert native.wire_parse_request(bytes(bad))[0] == want == wire.parse_request_header(bytes(bad))[3]
