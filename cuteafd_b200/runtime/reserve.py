@@ -93,3 +93,88 @@ class KvReserve:
 
     def release(self, rid: int) -> None:
         self.leases.pop(rid, None)
+
+
+def _split(first_page: int, pages: int, pools: int) -> list[int]:
+    """How many of the logical pages [first_page, first_page + pages) land on each pool (page j lives on pool j mod n)."""
+    out = [pages // pools] * pools
+    for j in range(first_page + pages - pages % pools, first_page + pages):
+        out[j % pools] += 1
+    return out
+
+
+class ParityReserve:
+    """Leases over ``pools`` separate page pools with the pages of a sequence dealt round-robin (logical page j lives on
+    pool j mod n): the layout of a context split, where every GPU of the group holds a share of every sequence's KV.
+    A request is admitted, or topped up, only when every pool passes its own banker's rule; a refusal by one pool rolls
+    the others back, so the pools never disagree about who holds a lease.
+
+    Counterpart: the parity pools (two halves) of rust/crates/cuteafd-daemon/src/shared/kv_reserve.rs."""
+
+    def __init__(self, pages_per_pool: int, pools: int = 2, decode_chunk_tokens: int = DECODE_CHUNK_TOKENS):
+        self.pools = [KvReserve(pages_per_pool, decode_chunk_tokens) for _ in range(pools)]
+        self.n = pools
+        self.chunk_pages = pages_for(decode_chunk_tokens)
+        self.meta: dict[int, dict] = {}          # rid -> {"shared", "leased", "max"} in logical pages
+
+    @property
+    def total(self) -> int:
+        return sum(p.total for p in self.pools)
+
+    @property
+    def leased(self) -> int:
+        return sum(p.leased for p in self.pools)
+
+    def per_pool(self) -> list[dict]:
+        return [{"total": p.total, "leased": p.leased} for p in self.pools]
+
+    def _install(self, rid: int, shared: int, leased: int, max_pages: int) -> bool:
+        """Set rid's lease to ``leased`` logical pages on every pool; all or nothing."""
+        want = _split(shared, leased, self.n)
+        most = _split(shared, max_pages, self.n)
+        before = [p.leases.get(rid) for p in self.pools]
+        done = []
+        for p, w, m in zip(self.pools, want, most):
+            old = p.leases.pop(rid, None)
+            cand = Lease(rid, w, old.used_pages if old else 0, m, 0)
+            if w > p.unleased or not p._safe(p.unleased - w, list(p.leases.values()) + [cand]):
+                if old is not None:
+                    p.leases[rid] = old
+                for q, o in done:                                   # roll the earlier pools back
+                    if o is None:
+                        q.leases.pop(rid, None)
+                    else:
+                        q.leases[rid] = o
+                return False
+            p.leases[rid] = cand
+            done.append((p, old))
+        del before
+        return True
+
+    def lease(self, rid: int, prompt_tokens: int, max_new_tokens: int, shared_pages: int = 0) -> dict | None:
+        prompt_pages = max(0, pages_for(prompt_tokens) - shared_pages)
+        max_pages = max(0, pages_for(prompt_tokens + max_new_tokens) - shared_pages)
+        want = min(max_pages, prompt_pages + self.chunk_pages)
+        if not self._install(rid, shared_pages, want, max_pages):
+            return None
+        self.meta[rid] = {"shared": shared_pages, "leased": want, "max": max_pages}
+        return self.meta[rid]
+
+    def top_up(self, rid: int) -> bool:
+        m = self.meta[rid]
+        if m["leased"] >= m["max"]:
+            return True
+        more = min(m["max"], m["leased"] + self.chunk_pages)
+        if not self._install(rid, m["shared"], more, m["max"]):
+            return False
+        m["leased"] = more
+        return True
+
+    def needs_top_up(self, rid: int, next_len_tokens: int) -> bool:
+        m = self.meta[rid]
+        return pages_for(next_len_tokens) - m["shared"] > m["leased"]
+
+    def release(self, rid: int) -> None:
+        self.meta.pop(rid, None)
+        for p in self.pools:
+            p.release(rid)

@@ -412,3 +412,26 @@ def test_speculation_trace_and_watchdog_hooks(oracle, tmp_path):
     assert sum(sum(r["accepted"]) + len(r["accepted"]) for r in recs) >= len(out["tokens"]) - 1   # the first token came from prefill
     assert all({"round", "requests", "rows", "proposed", "accepted", "kept", "copied", "ts"} <= set(r) for r in recs)
     assert sched.watchdog.stalls == 0 and sched.watchdog._busy == 0        # the last step saw an empty engine
+
+
+def test_parity_reserve_deals_pages_and_stays_consistent():
+    from cuteafd_b200.runtime.reserve import ParityReserve, _split
+    assert _split(0, 5, 2) == [3, 2] and _split(1, 5, 2) == [2, 3] and _split(3, 4, 2) == [2, 2] and _split(2, 7, 3) == [2, 2, 3]
+    assert all(sum(_split(f, n, k)) == n for f in range(5) for n in range(12) for k in (1, 2, 3, 4))
+    r = ParityReserve(pages_per_pool=10, pools=2, decode_chunk_tokens=128)           # chunk = 2 pages
+    a = r.lease(1, prompt_tokens=64 * 5, max_new_tokens=64 * 4)                      # 5 prompt pages + 2: pools get 4 and 3
+    assert a == {"shared": 0, "leased": 7, "max": 9} and [p["leased"] for p in r.per_pool()] == [4, 3]
+    b = r.lease(2, prompt_tokens=64 * 3, max_new_tokens=64 * 2, shared_pages=1)      # logical pages 1..4: two on each pool
+    assert b["leased"] == 4 and [p["leased"] for p in r.per_pool()] == [6, 5]
+    # a request that would fit the sum of the pools but not one of them is refused, and nothing is left behind
+    assert r.lease(3, prompt_tokens=64 * 9, max_new_tokens=64) is None
+    assert [p["leased"] for p in r.per_pool()] == [6, 5] and all(3 not in p.leases for p in r.pools)
+    assert r.needs_top_up(1, 64 * 7 + 1) and r.top_up(1) and r.meta[1]["leased"] == 9
+    assert [p["leased"] for p in r.per_pool()] == [7, 6] and r.top_up(1)              # at the maximum: nothing more to take
+    r.release(1)
+    assert [p["leased"] for p in r.per_pool()] == [2, 2] and r.leased == 4 and r.total == 20
+    # one pool is plain KvReserve
+    one, plain = ParityReserve(20, pools=1, decode_chunk_tokens=128), KvReserve(20, 128)
+    for rid, (p, m) in enumerate([(300, 200), (700, 64), (64, 2000)]):
+        assert (one.lease(rid, p, m) is None) == (plain.lease(rid, p, m) is None)
+    assert one.leased == plain.leased
