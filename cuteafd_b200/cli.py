@@ -293,7 +293,7 @@ def _build_parser() -> argparse.ArgumentParser:
     s.add_argument("--stall-dump-seconds", type=float, default=0.0,
                    help="write every thread's stack when requests are in flight and the loop has not ticked for this long; 0 = off")
     s.add_argument("--stack-dump-file", default="", help="where SIGUSR1 and stall dumps go (default: stderr)")
-    s.add_argument("--prewarm", default="", help="JSON list of decode step geometries: read at start, rewritten at exit")
+    s.add_argument("--prewarm", default="", help="JSON list of decode step geometries: read at start, rewritten at exit; 'auto' = the derived default list")
     s.add_argument("--media", default="none", choices=["none", "auto", "random"],
                    help="auto: load the vision / audio towers the snapshot bundles; random: small random-init towers")
     s.set_defaults(fn=cmd_serve)

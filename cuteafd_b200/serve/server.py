@@ -445,6 +445,11 @@ def build_state(args) -> ServerState:
                 from ..models.gqa_moe import GqaMoeEngine as Engine, GqaMoeWeights as Weights, KvCache as Cache
             eng = Engine(cfg, Weights.random_init(cfg, dev), Cache(cfg, num_pages, dev), max_tokens=max(2048, rows), max_seqs=rows)
         be = EngineBackend(eng, num_pages, pages_per_seq, prefill_chunk=2048, max_decode_rows=args.concurrency)
+        if getattr(args, "prewarm", "") == "auto":              # no trace of an earlier run: the derived default list
+            from ..planner.capacity import default_prewarm
+            block = 0 if args.speculator == "off" else 4
+            n = be.prewarm(default_prewarm(args.concurrency, block))
+            print(f"prewarmed {n} decode graphs (default list)", flush=True)
         from ..utils.memory_ledger import LEDGER
         try:
             LEDGER.tag_tree("weights", "engine", eng.W)        # an arena's storage is already counted: adds nothing then
@@ -458,9 +463,7 @@ def build_state(args) -> ServerState:
         except Exception as e:                                 # noqa: BLE001 - accounting never stops a server from starting
             print(f"[memory] ledger unavailable: {e}", flush=True)
         pw = getattr(args, "prewarm", "")
-        if pw:
-            import json
-            import os
+        if pw and pw != "auto":
             if os.path.exists(pw):               # geometries a previous run saved (EngineBackend.save_prewarm)
                 with open(pw) as f:
                     n = be.prewarm(json.load(f).get("geometries", []))
@@ -560,6 +563,6 @@ def run_server(args) -> int:
         if state.sched.trace is not None:
             state.sched.trace.close()
         be = state.sched.be
-        if getattr(args, "prewarm", "") and hasattr(be, "save_prewarm"):
+        if getattr(args, "prewarm", "") not in ("", "auto") and hasattr(be, "save_prewarm"):
             be.save_prewarm(args.prewarm)        # the next start captures this run's frequent geometries up front
     return 0

@@ -417,3 +417,29 @@ def test_tool_history_translation_across_flavours():
     kinds = [o["type"] for o in obj["output"]]
     assert kinds == ["message", "function_call"] and obj["output"][1]["name"] == "get_time" and json.loads(obj["output"][1]["arguments"]) == {"tz": "UTC"}
     assert obj["output_text"] == "ok "
+
+
+def test_build_state_on_the_oracle_engine(tmp_path):
+    """The command-line path that builds a server (flags -> engine, scheduler, trace, watchdog, loop abort)."""
+    from cuteafd_b200.cli import build_parser
+    from cuteafd_b200.serve.server import build_state
+    args = build_parser().parse_args(["serve", "--fake-engine", "--preset", "tiny-moe", "--speculation-trace", str(tmp_path / "t.jsonl"),
+                                      "--stall-dump-seconds", "30", "--loop-fast-span", "64", "--usage-db", str(tmp_path / "u.sqlite")])
+    state = build_state(args)
+    assert state.sched.trace is not None and state.sched.watchdog is not None and state.usage is not None
+    assert state.sched.loop_abort.fast_span == 64 and state.model_id == "tiny-moe"
+    state.sched.watchdog.stop()
+    state.sched.trace.close()
+
+
+def test_capacity_tables():
+    from cuteafd_b200.config import qwen3_30b_a3b
+    from cuteafd_b200.planner import capacity
+    assert [capacity.prefill_unit_rows(k) for k in (1, 2, 3, 4, 8)] == [8192, 4096, 2688, 2048, 1024]
+    assert capacity.prefill_waves(8192, 2048) == [2048] * 4 and capacity.prefill_waves(5000, 2048) == [2048, 2048, 960]
+    keys = capacity.default_prewarm(8, draft_block=4)
+    assert [1, 1, 1] in keys and [8, 8, 1] in keys and [8, 40, 5] in keys and [4, 8, 2] in keys and len(keys) == len({tuple(k) for k in keys})
+    assert all(s <= 8 and t >= s and q * s >= t for s, t, q in keys)            # what EngineBackend.prewarm accepts
+    assert capacity.default_prewarm(64, 0)[-1] == [64, 64, 1] and len(capacity.default_prewarm(64, 4, limit=10)) == 10
+    cfg = qwen3_30b_a3b()
+    assert 8 * capacity.workspace_bytes(cfg, 1024) == capacity.workspace_bytes(cfg, 8192) < 4 << 30
