@@ -119,3 +119,41 @@ def test_server_checks_payload_and_dtype(split):
     s.settimeout(2)
     assert s.recv(1) == b""
     s.close()
+
+
+def test_expertd_tcp_worker_process(tmp_path):
+    """``cuteafd expertd --tcp-port`` serves a snapshot's expert range to a remote decoder, bit for bit."""
+    import subprocess
+    import sys
+    from cuteafd_b200.loader import load, snapshot
+    cfg = tiny_moe()
+    src = snapshot.write_random_snapshot(cfg, str(tmp_path / "s"), fmt="bf16", seed=7)
+    procs, workers = [], []
+    half = cfg.num_experts // 2
+    try:
+        for lo, hi in ((0, half), (half, cfg.num_experts)):
+            p = subprocess.Popen([sys.executable, "-m", "cuteafd_b200.cli", "expertd", "--snapshot", src, "--tcp-port", "0",
+                                  "--experts", f"{lo}:{hi}"], stdout=subprocess.PIPE, text=True)
+            procs.append(p)
+            line = p.stdout.readline()
+            assert "expert worker" in line, line
+            workers.append(("127.0.0.1", int(line.rsplit(":", 1)[1]), lo, hi))
+        _, params = load.load_params(src, dtype=torch.bfloat16)
+        toks = torch.arange(20) % cfg.vocab_size
+        whole = RefDecoder(cfg, params).forward(toks, KvState(cfg))
+        # each worker's plan hash covers its own range: one link per worker with its own hash
+        links = []
+        for h, port, lo, hi in workers:
+            plan = wire.plan_hash({"model": cfg.name, "experts": cfg.num_experts, "range": [lo, hi]})
+            links.append(wire.RemoteExperts([(h, port, lo, hi)], plan))
+
+        def moe_fn(layer, x, idx, w):
+            return sum(l(layer, x, idx, w) for l in links)
+        got = RefDecoder(cfg, params, moe_fn=moe_fn).forward(toks, KvState(cfg))
+        assert torch.equal(got, whole)
+        for l in links:
+            l.close()
+    finally:
+        for p in procs:
+            p.kill()
+            p.wait(timeout=10)
