@@ -52,15 +52,16 @@ def open_snapshot(path: str) -> OpenedSnapshot:
 
 
 def load_params(path: str, dtype: torch.dtype = torch.float32, device: str = "cpu",
-                only: str | None = None, exclude: str | None = None) -> tuple[ModelConfig, dict[str, torch.Tensor]]:
+                only: str | None = None, exclude: str | None = None, keep=None) -> tuple[ModelConfig, dict[str, torch.Tensor]]:
     """Every parameter decoded to a dense tensor under its ``....weight`` name.  ``only`` / ``exclude`` keep or drop
     the operands whose prefix contains the substring (an expert rank reads ``only=".mlp.experts."``, the attention rank
-    of a disaggregated deployment ``exclude=".mlp.experts."``)."""
+    of a disaggregated deployment ``exclude=".mlp.experts."``); ``keep(prefix) -> bool`` is the general form (an expert
+    rank that reads only its own expert range).  Dropped operands are not read at all."""
     snap = open_snapshot(path)
     out: dict[str, torch.Tensor] = {}
     covered = set()
     for pre, op in snap.operands.items():
-        if exclude and exclude in pre:
+        if (exclude and exclude in pre) or (keep is not None and not keep(pre)):
             covered.update(n for n in (op.weight, op.scale_tensor, op.global_scale, op.input_scale, *op.companions.values()) if n)
             continue
         if only and only not in pre:

@@ -522,16 +522,28 @@ def _build_afd_rank(args, snapshot, world: int, num_pages: int, pages_per_seq: i
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     dist.init_process_group("nccl", device_id=dev)
     params = None
+    expert_format = "bf16"
     if snapshot:
-        from ..loader.load import load_params
-        part = dict(only=".mlp.experts.") if rank else dict(exclude=".mlp.experts.")
+        from ..loader.load import load_params, open_snapshot
+        from ..ref.split import expert_range
+        cfg0 = open_snapshot(snapshot).cfg
+        if rank:                                   # an expert rank reads its own expert range and nothing else
+            lo, hi = expert_range(cfg0.num_experts, world - 1, rank - 1)
+
+            def mine(pre: str) -> bool:
+                return ".mlp.experts." in pre and lo <= int(pre.split(".mlp.experts.")[1].split(".")[0]) < hi
+            part = dict(keep=mine)
+        else:
+            part = dict(exclude=".mlp.experts.")
         cfg, params = load_params(snapshot, dtype=torch.bfloat16, **part)
+        if cfg.weight_format == "fp8_block128":
+            expert_format = "fp8"                  # experts shipped as block-scaled E4M3 stay E4M3 on the expert ranks
     else:
         cfg = PRESETS[args.preset or "qwen3-30b-a3b"]()
         if args.layers:
             cfg = cfg.replace(num_layers=args.layers)
     h = build_afd(cfg, dev, rank, world, max_tokens=max(2048, rows), max_seqs=rows, num_pages=num_pages,
-                  pages_per_seq=pages_per_seq, params=params, prefill_chunk=2048)
+                  pages_per_seq=pages_per_seq, params=params, prefill_chunk=2048, expert_format=expert_format)
     torch.cuda.synchronize()
     dist.barrier()
     if h.worker is not None:

@@ -226,3 +226,16 @@ def test_config_mapping_refuses_what_it_cannot_serve():
                      (dict(model_type="gpt_oss"), "unsupported model_type")):
         with pytest.raises(ValueError, match=msg):
             snapshot.from_hf_config(dict(base, **bad))
+
+
+def test_load_params_keep_reads_one_expert_range(tmp_path):
+    from cuteafd_b200 import tiny_moe
+    from cuteafd_b200.ref.split import expert_range
+    cfg = tiny_moe()
+    src = snapshot.write_random_snapshot(cfg, str(tmp_path / "s"), fmt="fp8_block128", seed=8)
+    lo, hi = expert_range(cfg.num_experts, 3, 1)
+    _, got = load.load_params(src, keep=lambda pre: ".mlp.experts." in pre and lo <= int(pre.split(".mlp.experts.")[1].split(".")[0]) < hi)
+    ids = {int(n.split(".mlp.experts.")[1].split(".")[0]) for n in got if ".mlp.experts." in n}
+    assert ids == set(range(lo, hi)) and all(".mlp.experts." in n for n in got)
+    _, everything = load.load_params(src)
+    assert all(torch.equal(got[n], everything[n]) for n in got)
