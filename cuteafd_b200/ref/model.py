@@ -123,6 +123,7 @@ class RefDecoder:
         rd = cfg.qk_rope_dim if cfg.is_mla else cfg.head_dim
         self.inv_freq = ops.rope_inv_freq(cfg, rd)                  # long-context scaling lives in this table
         self.rope_mag, self.scale_mul = ops.rope_magnitudes(cfg)
+        self.usage: dict[int, torch.Tensor] | None = None     # set to {} to count routed tokens per layer and expert
         self.observe = None          # optional (operand prefix, input rows [n, in]) -> None, called before every projection
         self._stacked: dict[int, tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
 
@@ -232,6 +233,9 @@ class RefDecoder:
             y = ops.swiglu_mlp(x, p[m + "gate_proj.weight"], p[m + "up_proj.weight"], p[m + "down_proj.weight"])
             return (residual.float() + y.to(x.dtype).float()).to(x.dtype)
         idx, w = self.route(layer, x)
+        if self.usage is not None:                       # routed-token counts per layer and expert
+            self.usage.setdefault(layer, torch.zeros(self.cfg.num_experts, dtype=torch.int64)).add_(
+                torch.bincount(idx.reshape(-1), minlength=self.cfg.num_experts))
         if self.observe is not None:
             for e in idx.unique().tolist():
                 self._see_mlp(f"{m}experts.{e}.", x[(idx == e).any(dim=-1)])

@@ -39,12 +39,23 @@ class OracleBackend:
         self.table = SequenceTable(self.pool)
         self.prefix = PrefixCache(self.pool, self.table, max_pages=total_pages // 2)
         self.steps = 0
+        self.model.usage = {}                     # routed-token counters behind ``expert_usage``
         self.fail_on_step = fail_on_step          # host-side fault injection: the N-th verify raises
         self.quarantined: list[_Handle] = []
         self.has_mtp = cfg.mtp_layers > 0 and f"model.layers.{cfg.num_layers}.eh_proj.weight" in params
         self.last_mtp: list[int] | None = None
         if self.has_mtp:
             self.verify_select = self._verify_select     # selection next to the model, as on the GPU backend
+
+    def expert_usage(self) -> dict:
+        """Routed tokens per layer and expert since start, with the load imbalance (max / mean) per layer."""
+        layers = {}
+        for layer, c in sorted((self.model.usage or {}).items()):
+            total = int(c.sum())
+            layers[str(layer)] = {"tokens": c.tolist(), "total": total,
+                                  "imbalance": round(float(c.max()) * c.numel() / total, 3) if total else None,
+                                  "idle_experts": int((c == 0).sum())}
+        return {"experts": self.cfg.num_experts, "top_k": self.cfg.top_k, "layers": layers}
 
     def _verify_select(self, handles: list[_Handle], rows: list[list[int]], params: list, positions: list[int]):
         """Forward, exact selection and the MTP depth on the same rows (the oracle of ``EngineBackend.verify_select``)."""
@@ -184,6 +195,23 @@ class EngineBackend:
     def _copy_page(self, src: int, dst: int) -> None:
         kv = self.engine.kv if hasattr(self.engine, "kv") else self.engine.inner.kv
         kv.copy_page(src, dst)
+
+    def expert_usage(self) -> dict:
+        """A sample, not a total: the routed-token counts the planner kernel left for the last MoE layer of the last
+        step (the exchange keeps one counter vector and every layer overwrites it; accumulating on the device would add
+        a launch per layer to every decode step)."""
+        moe = getattr(self.engine, "moe", None)
+        c = getattr(moe, "expert_count", None)
+        if c is None:
+            return {}
+        try:
+            t = c.detach().to("cpu", torch.int64)
+        except RuntimeError:
+            return {}
+        total = int(t.sum())
+        return {"experts": int(t.numel()), "top_k": self.cfg.top_k, "sample": "last MoE layer of the last step",
+                "tokens": t.tolist(), "total": total,
+                "imbalance": round(float(t.max()) * t.numel() / total, 3) if total else None}
 
     def open(self, tokens: list[int], cold: bool = False) -> tuple[_Handle, int]:
         if cold:                                   # probe: compute the whole prompt, whatever the cache holds

@@ -26,6 +26,8 @@ class ServerState:
         self.media = media                  # MediaProcessor, or None for a text-only deployment
         self.usage = usage
         self.extras = extras or {}
+        if "expert_usage" not in self.extras and hasattr(scheduler.be, "expert_usage"):
+            self.extras["expert_usage"] = scheduler.be.expert_usage        # /experts and the console read the backend's counters
         self.started = time.time()
         self.responses: dict[str, dict] = {}
         self.sessions: dict[str, list] = {}      # response id -> the conversation that produced it, reply included

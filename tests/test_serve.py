@@ -443,3 +443,14 @@ def test_capacity_tables():
     assert capacity.default_prewarm(64, 0)[-1] == [64, 64, 1] and len(capacity.default_prewarm(64, 4, limit=10)) == 10
     cfg = qwen3_30b_a3b()
     assert 8 * capacity.workspace_bytes(cfg, 1024) == capacity.workspace_bytes(cfg, 8192) < 4 << 30
+
+
+def test_expert_usage_counters(server):
+    call(server, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "route some tokens"}], "max_tokens": 4})
+    st, _, raw = call(server, "GET", "/experts")
+    u = json.loads(raw)
+    assert st == 200 and u["experts"] == 8 and u["top_k"] == 2 and u["layers"]
+    for layer in u["layers"].values():
+        assert len(layer["tokens"]) == 8 and layer["total"] == sum(layer["tokens"]) > 0 and layer["total"] % 2 == 0
+        assert layer["imbalance"] >= 1.0
+    assert json.loads(call(server, "GET", "/v1/console/state")[2])["experts"]["layers"].keys() == u["layers"].keys()
