@@ -79,3 +79,36 @@ def test_context_split_over_two_ranks(tmp_path):
         d = torch.load(str(tmp_path / f"r{r}.pt"))
         assert d["err"] < 1e-5
         assert d["sel"][0].tolist() == [0, 10, 11, 12]          # rank 1's three candidates win, one of rank 0's ties (lowest position); ascending output
+
+
+def _decoder_worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    from cuteafd_b200 import tiny_moe
+    from cuteafd_b200.ref.context import ContextSplitDecoder
+    from cuteafd_b200.ref.model import KvState, RefDecoder, init_weights
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = tiny_moe().replace(family="qwen3_moe", attention="gqa", num_heads=4, num_kv_heads=2, head_dim=32, hidden=128, qk_norm=True,
+                             rope_interleaved=False, num_shared_experts=0, scoring="softmax")
+    params = init_weights(cfg, seed=0)
+    toks = torch.randint(0, cfg.vocab_size, (150,), generator=torch.Generator().manual_seed(9))      # more than two pages
+    whole, split = RefDecoder(cfg, params), ContextSplitDecoder(cfg, params)
+    kv_w, kv_s = KvState(cfg), split.new_kv()
+    with torch.no_grad():
+        errs = [(split.forward(toks[:140], kv_s) - whole.forward(toks[:140], kv_w)).abs().max().item()]
+        for t in range(140, 150):                              # decode steps: each row lands on the owner of its page
+            errs.append((split.forward(toks[t:t + 1], kv_s) - whole.forward(toks[t:t + 1], kv_w)).abs().max().item())
+    torch.save({"err": max(errs), "held": kv_s.held(0), "total": kv_s.length(0)}, os.path.join(out_dir, f"d{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_whole_decoder_with_context_split_attention(tmp_path):
+    """Prompt + decode through a full model whose attention runs context-split over two ranks: same logits, and every
+    rank keeps only the KV rows of its pages."""
+    import torch.multiprocessing as mp
+    mp.spawn(_decoder_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    d0, d1 = (torch.load(str(tmp_path / f"d{r}.pt")) for r in range(2))
+    assert d0["err"] < 2e-3 and d1["err"] < 2e-3                 # fp32 oracle: only the summation order differs
+    assert d0["total"] == d1["total"] == 150
+    assert d0["held"] == 64 + 22 and d1["held"] == 64            # pages 0 and 2 (positions 0..63, 128..149) / page 1
