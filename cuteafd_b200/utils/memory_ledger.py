@@ -43,8 +43,9 @@ def _tensors(obj, seen: set, depth: int = 0) -> Iterator:
         vals = obj
     elif dataclasses.is_dataclass(obj) and not isinstance(obj, type):
         vals = (getattr(obj, f.name, None) for f in dataclasses.fields(obj))
-    elif hasattr(obj, "__dict__") and type(obj).__module__.startswith("cuteafd_b200"):
-        vals = vars(obj).values()
+    elif type(obj).__module__.startswith("cuteafd_b200") and (hasattr(obj, "__dict__") or hasattr(type(obj), "__slots__")):
+        vals = list(vars(obj).values()) if hasattr(obj, "__dict__") else []
+        vals += [getattr(obj, s, None) for s in getattr(type(obj), "__slots__", ())]
     else:
         return
     for v in vals:

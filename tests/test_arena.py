@@ -63,6 +63,11 @@ def test_ledger_tree_reconcile_and_failure_spool(tmp_path):
     Holder.__module__ = "cuteafd_b200.fake"
     got = led.tag_tree("kv", "engine", h)
     assert got == (1 << 20) + 1024                       # the view shares storage: counted once
+    from cuteafd_b200.models.gqa_moe import LayerWeights                  # a __slots__ class: no __dict__ to walk
+    L = LayerWeights()
+    L.wo = torch.zeros(512, dtype=torch.float32)
+    assert led.tag_tree("weights", "layer", [L]) == 2048
+    led.release("weights", "layer")
     led.tag("graphs", "bank", 5 << 20, "cpu")
     rec = led.reconcile()["cpu"]
     assert rec["used"] == 40 << 20 and rec["untracked"] == (40 << 20) - led.total("cpu")
