@@ -50,6 +50,39 @@ def _stops(body: dict, tok) -> tuple[int, ...]:
     return tuple(ids) + tuple(getattr(tok, "eos_ids", ()))
 
 
+COMPACT_REQUEST = ("Summarize this conversation so that it can be continued from the summary alone. Keep the user's "
+                   "requirements, the decisions taken, tool results and the work still pending. Answer with the summary only.")
+COMPACT_PREFIX = "Summary of the conversation so far:\n"
+
+
+def encode_opaque(kind: str, text: str) -> str:
+    """Opaque item content a client stores and sends back (``encrypted_content``): tagged, base64; not secret."""
+    import base64
+    return "cafd1." + base64.urlsafe_b64encode(json.dumps({"kind": kind, "text": text}).encode()).decode()
+
+
+def decode_opaque(blob: str, kind: str) -> str:
+    import base64
+    import binascii
+    try:
+        if not blob.startswith("cafd1."):
+            raise ValueError
+        d = json.loads(base64.urlsafe_b64decode(blob[6:].encode()))
+        if d.get("kind") != kind:
+            raise ValueError
+        return str(d["text"])
+    except (ValueError, KeyError, binascii.Error, UnicodeDecodeError) as e:
+        raise BadRequest(f"unreadable {kind} item") from e
+
+
+def compaction_object(summary: str, usage: dict) -> dict:
+    return {"id": "resp_" + uuid.uuid4().hex[:24], "object": "response.compaction", "created_at": int(time.time()),
+            "output": [{"id": "cmp_" + uuid.uuid4().hex[:20], "type": "compaction",
+                        "encrypted_content": encode_opaque("compaction", summary)}],
+            "usage": {"input_tokens": usage.get("prompt_tokens", 0), "output_tokens": usage.get("completion_tokens", 0),
+                      "total_tokens": usage.get("prompt_tokens", 0) + usage.get("completion_tokens", 0)}}
+
+
 def responses_items_to_messages(items: list) -> list[dict]:
     """Responses ``input`` items -> chat messages: ``function_call`` items are the assistant's calls (consecutive ones
     share a turn), ``function_call_output`` items turns of role ``tool``; reasoning items are dropped."""
@@ -64,6 +97,8 @@ def responses_items_to_messages(items: list) -> list[dict]:
                 msgs[-1]["tool_calls"].append(call)
             else:
                 msgs.append({"role": "assistant", "content": "", "tool_calls": [call], "_calls_only": True})
+        elif t == "compaction":                       # what /v1/responses/compact returned earlier: the summary it stands for
+            msgs.append({"role": "user", "content": COMPACT_PREFIX + decode_opaque(str(it.get("encrypted_content", "")), "compaction")})
         elif t == "function_call_output":
             out = it.get("output")
             msgs.append({"role": "tool", "tool_call_id": it.get("call_id", ""), "content": out if isinstance(out, str) else json.dumps(out)})

@@ -207,7 +207,8 @@ def make_handler(state: ServerState):
         def do_POST(self):
             path = self.path.split("?", 1)[0]
             flavor = {"/v1/chat/completions": "openai", "/v1/messages": "anthropic", "/v1/responses": "responses",
-                      "/v1/messages/count_tokens": "anthropic", "/v1/responses/input_tokens": "responses"}.get(path)
+                      "/v1/messages/count_tokens": "anthropic", "/v1/responses/input_tokens": "responses",
+                      "/v1/responses/compact": "responses"}.get(path)
             if flavor is None and path.startswith("/v1/responses/") and path.endswith("/cancel"):
                 flavor = "responses"
             if flavor is None and path != "/v1/fabric/phase":
@@ -247,6 +248,13 @@ def make_handler(state: ServerState):
                 if flavor == "responses":
                     with state.lock:
                         body, self._session = api.continue_session(body, state.sessions)
+                self._compact = path == "/v1/responses/compact"
+                if self._compact:
+                    # the conversation plus one request for its summary; the reply is returned as an opaque item that a
+                    # later request sends back in place of the turns it replaces
+                    conv = body["input"] if isinstance(body.get("input"), list) else [{"role": "user", "content": body.get("input") or ""}]
+                    body = dict(body, input=list(conv) + [{"role": "user", "content": api.COMPACT_REQUEST}], stream=False)
+                    body.setdefault("max_output_tokens", 1024)
                 req = api.build_request(body, state.tok, state.sched.be.vocab_size, probe, flavor, state.media)
             except api.BadRequest as e:
                 st, eb, hd = api.error_body(FAIL_BAD_REQUEST, str(e), flavor)
@@ -312,6 +320,10 @@ def make_handler(state: ServerState):
             out_text = "".join(text)
             if flavor == "anthropic":
                 return self._json(200, api.anthropic_message(model, out_text, finish, usage))
+            if flavor == "responses" and getattr(self, "_compact", False):
+                if not out_text.strip():
+                    return self._json(502, {"error": {"message": "compaction returned no summary", "type": "server_error"}})
+                return self._json(200, api.compaction_object(out_text, usage))
             if flavor == "responses":
                 obj = api.responses_object(model, out_text, finish, usage)
                 with state.lock:

@@ -454,3 +454,26 @@ def test_expert_usage_counters(server):
         assert len(layer["tokens"]) == 8 and layer["total"] == sum(layer["tokens"]) > 0 and layer["total"] % 2 == 0
         assert layer["imbalance"] >= 1.0
     assert json.loads(call(server, "GET", "/v1/console/state")[2])["experts"]["layers"].keys() == u["layers"].keys()
+
+
+def test_responses_compact_round_trip(server):
+    from cuteafd_b200.serve import api
+    conv = [{"role": "user", "content": "plan a trip to Oslo"}, {"role": "assistant", "content": "sure: flights, hotel, museums"},
+            {"role": "user", "content": "book the museums first"}]
+    st, _, raw = call(server, "POST", "/v1/responses/compact", {"input": conv, "max_output_tokens": 12})
+    out = json.loads(raw)
+    assert st == 200 and out["object"] == "response.compaction" and out["output"][0]["type"] == "compaction"
+    assert out["usage"]["output_tokens"] >= 1 and out["usage"]["input_tokens"] > 20
+    item = out["output"][0]
+    summary = api.decode_opaque(item["encrypted_content"], "compaction")
+    assert isinstance(summary, str) and summary
+    # the item stands for the turns it replaced in a later request
+    msgs = api.responses_items_to_messages([item, {"role": "user", "content": "continue"}])
+    assert msgs[0]["role"] == "user" and msgs[0]["content"] == api.COMPACT_PREFIX + summary and msgs[1]["content"] == "continue"
+    st, _, raw = call(server, "POST", "/v1/responses", {"input": [item, {"role": "user", "content": "continue"}], "max_output_tokens": 4})
+    assert st == 200 and json.loads(raw)["status"] in ("completed", "incomplete")
+    bad = dict(item, encrypted_content="cafd1.not-base64!!")
+    assert call(server, "POST", "/v1/responses", {"input": [bad], "max_output_tokens": 4})[0] == 400
+    assert api.decode_opaque(api.encode_opaque("compaction", "héllo"), "compaction") == "héllo"
+    with pytest.raises(api.BadRequest):
+        api.decode_opaque(api.encode_opaque("other", "x"), "compaction")
