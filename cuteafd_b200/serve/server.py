@@ -18,7 +18,7 @@ from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 
 from ..runtime.scheduler import FAIL_BAD_REQUEST, FAIL_UNAVAILABLE, Request, Scheduler
 from . import api, ws
-from .tokenizer import StreamDecoder
+from .tokenizer import StreamDecoder, ToolCallStream
 
 class ServerState:
     def __init__(self, scheduler: Scheduler, tokenizer, model_id: str, api_key: str = "", usage=None, extras=None, media=None):
@@ -347,12 +347,27 @@ def make_handler(state: ServerState):
                 mid, head = api.anthropic_events(model, len(req.prompt))
                 for name, ev in head:
                     self._sse(ev, name)
+                tcs, blocks = ToolCallStream(), 1
+
+                def a_text(t: str) -> None:
+                    if t:
+                        self._sse({"type": "content_block_delta", "index": 0, "delta": {"type": "text_delta", "text": t}}, "content_block_delta")
                 for ev in self._drain(req):
                     if ev[0] == "text":
-                        self._sse({"type": "content_block_delta", "index": 0, "delta": {"type": "text_delta", "text": ev[1]}}, "content_block_delta")
+                        vis, calls = tcs.push(ev[1])
+                        a_text(vis)
+                        for c in calls:                      # each call is its own tool_use block, its input one JSON delta
+                            self._sse({"type": "content_block_start", "index": blocks, "content_block": {
+                                "type": "tool_use", "id": "toolu_" + uuid.uuid4().hex[:20], "name": c["function"]["name"], "input": {}}},
+                                "content_block_start")
+                            self._sse({"type": "content_block_delta", "index": blocks,
+                                       "delta": {"type": "input_json_delta", "partial_json": c["function"]["arguments"]}}, "content_block_delta")
+                            self._sse({"type": "content_block_stop", "index": blocks}, "content_block_stop")
+                            blocks += 1
                     elif ev[0] == "done":
+                        a_text(tcs.flush())
                         self._sse({"type": "content_block_stop", "index": 0}, "content_block_stop")
-                        stop = {"stop": "end_turn", "length": "max_tokens"}.get(ev[1], ev[1])
+                        stop = "tool_use" if tcs.calls else {"stop": "end_turn", "length": "max_tokens"}.get(ev[1], ev[1])
                         self._sse({"type": "message_delta", "delta": {"stop_reason": stop},
                                    "usage": {"output_tokens": ev[2].get("completion_tokens", 0)}}, "message_delta")
                         self._sse({"type": "message_stop"}, "message_stop")
@@ -363,11 +378,20 @@ def make_handler(state: ServerState):
                 rid = "resp_" + uuid.uuid4().hex[:24]
                 self._sse({"type": "response.created", "response": {"id": rid, "status": "in_progress"}}, "response.created")
                 text = []
+                tcs = ToolCallStream()
                 for ev in self._drain(req):
                     if ev[0] == "text":
                         text.append(ev[1])
-                        self._sse({"type": "response.output_text.delta", "delta": ev[1]}, "response.output_text.delta")
+                        vis, calls = tcs.push(ev[1])             # tool calls come as items of the completed response, not as text
+                        if vis:
+                            self._sse({"type": "response.output_text.delta", "delta": vis}, "response.output_text.delta")
+                        for c in calls:
+                            self._sse({"type": "response.function_call_arguments.done", "name": c["function"]["name"],
+                                       "arguments": c["function"]["arguments"]}, "response.function_call_arguments.done")
                     elif ev[0] == "done":
+                        rest = tcs.flush()
+                        if rest:
+                            self._sse({"type": "response.output_text.delta", "delta": rest}, "response.output_text.delta")
                         obj = api.responses_object(model, "".join(text), ev[1], ev[2], rid)
                         with state.lock:
                             state.responses[rid] = obj
@@ -378,11 +402,19 @@ def make_handler(state: ServerState):
                 return
             cid = "chatcmpl-" + uuid.uuid4().hex[:24]
             self._sse(api.chat_chunk(cid, model, {"role": "assistant", "content": ""}))
+            tcs = ToolCallStream()
             for ev in self._drain(req):
                 if ev[0] == "text":
-                    self._sse(api.chat_chunk(cid, model, {"content": ev[1]}))
+                    vis, calls = tcs.push(ev[1])
+                    if vis:
+                        self._sse(api.chat_chunk(cid, model, {"content": vis}))
+                    for c in calls:
+                        self._sse(api.chat_chunk(cid, model, {"tool_calls": [dict(c, index=tcs.calls - len(calls) + calls.index(c))]}))
                 elif ev[0] == "done":
-                    self._sse(api.chat_chunk(cid, model, {}, ev[1], ev[2]))
+                    rest = tcs.flush()
+                    if rest:
+                        self._sse(api.chat_chunk(cid, model, {"content": rest}))
+                    self._sse(api.chat_chunk(cid, model, {}, "tool_calls" if tcs.calls else ev[1], ev[2]))
                 else:
                     self._sse({"error": {"message": ev[2], "code": ev[1]}})
             self._sse("[DONE]")

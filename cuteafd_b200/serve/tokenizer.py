@@ -161,6 +161,52 @@ def parse_tool_calls(text: str) -> tuple[str, list[dict]]:
     return "".join(out), calls
 
 
+class ToolCallStream:
+    """Splits a streamed reply into visible text and completed tool calls.  Text is passed through as it arrives except
+    for what could still turn out to be the opening tag; everything between ``<tool_call>`` and ``</tool_call>`` is held
+    back and comes out as one call (or, when it does not parse, as the text it was)."""
+    OPEN, CLOSE = "<tool_call>", "</tool_call>"
+
+    def __init__(self):
+        self.buf = ""
+        self.inside = False
+        self.calls = 0
+
+    def push(self, text: str) -> tuple[str, list[dict]]:
+        self.buf += text
+        out, calls = [], []
+        while True:
+            if not self.inside:
+                a = self.buf.find(self.OPEN)
+                if a >= 0:
+                    out.append(self.buf[:a])
+                    self.buf, self.inside = self.buf[a + len(self.OPEN):], True
+                    continue
+                # keep back the longest tail that is a prefix of the opening tag
+                keep = next((k for k in range(min(len(self.OPEN) - 1, len(self.buf)), 0, -1) if self.OPEN.startswith(self.buf[-k:])), 0)
+                out.append(self.buf[:len(self.buf) - keep])
+                self.buf = self.buf[len(self.buf) - keep:]
+                break
+            b = self.buf.find(self.CLOSE)
+            if b < 0:
+                break
+            body, self.buf, self.inside = self.buf[:b], self.buf[b + len(self.CLOSE):], False
+            try:
+                obj = json.loads(body)
+                calls.append({"id": f"call_{self.calls}", "type": "function",
+                              "function": {"name": obj.get("name", ""), "arguments": json.dumps(obj.get("arguments", {}))}})
+                self.calls += 1
+            except json.JSONDecodeError:
+                out.append(self.OPEN + body + self.CLOSE)
+        return "".join(out), calls
+
+    def flush(self) -> str:
+        """What is still held when the reply ends (an unfinished tag is text)."""
+        rest = (self.OPEN if self.inside else "") + self.buf
+        self.buf, self.inside = "", False
+        return rest
+
+
 class StreamDecoder:
     """Incremental detokenizer: emits only complete UTF-8 text, holding back partial sequences."""
 

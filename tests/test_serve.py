@@ -477,3 +477,27 @@ def test_responses_compact_round_trip(server):
     assert api.decode_opaque(api.encode_opaque("compaction", "héllo"), "compaction") == "héllo"
     with pytest.raises(api.BadRequest):
         api.decode_opaque(api.encode_opaque("other", "x"), "compaction")
+
+
+def test_tool_call_stream_filter():
+    from cuteafd_b200.serve.tokenizer import ToolCallStream, parse_tool_calls
+    full = 'Let me look. <tool_call>{"name": "get_time", "arguments": {"tz": "UTC"}}</tool_call> and <tool_call>{"name": "x", "arguments": {}}</tool_call>done <tool'
+    want_text, want_calls = parse_tool_calls(full)
+    for step in (1, 3, 7, 1000):                                  # any chunking gives the same text and calls
+        t = ToolCallStream()
+        text, calls = [], []
+        for i in range(0, len(full), step):
+            v, c = t.push(full[i:i + step])
+            assert "<tool_call>" not in v
+            text.append(v)
+            calls += c
+        text.append(t.flush())
+        assert "".join(text) == want_text and [c["function"] for c in calls] == [c["function"] for c in want_calls]
+        assert [c["id"] for c in calls] == ["call_0", "call_1"]
+    t = ToolCallStream()
+    assert t.push("a < b and <to")[0] == "a < b and " and t.push("tal>")[0] == "<total>"      # a false start is released
+    v, c = ToolCallStream().push("<tool_call>not json</tool_call>")
+    assert v == "<tool_call>not json</tool_call>" and c == []
+    t = ToolCallStream()
+    t.push('x<tool_call>{"name"')
+    assert t.flush() == '<tool_call>{"name"'                    # cut off mid-call: returned as text
