@@ -54,6 +54,7 @@ class Request:
     speculation: bool = True
     record_rows: bool = False          # probe: keep a hash of every selected logit row
     constraint: Any = None             # TokenConstraint: allowed-token mask applied first in the chain
+    stop_texts: tuple = ()             # stop strings longer than one token: matched on the decoded text by the server
     top_logprobs: int = 0              # > 0: keep the chosen token's log-probability and this many alternatives per token
     cold: bool = False                 # probe: do not look the prompt up in the prefix cache
     media: Any = None                  # list of media spans (prompt position, embedding rows) for ids above the vocabulary
@@ -503,7 +504,9 @@ class Scheduler:
             a.req.events.put(("done", reason, usage, list(a.row_hashes)))
             self.stats.finished += 1
         else:
-            a.req.events.put(("done", "cancelled", {}, []))
+            # a cancelled request still says what it cost (a stop string ends a reply by cancelling it)
+            a.req.events.put(("done", "cancelled", {"prompt_tokens": len(a.req.prompt), "completion_tokens": len(a.generated),
+                                                    "cached_tokens": a.cached, "speculation": dict(a.spec, request_id=a.req.rid)}, []))
 
     def _fail(self, actives: list[Active], msg: str) -> None:
         for a in actives:

@@ -50,6 +50,17 @@ def _stops(body: dict, tok) -> tuple[int, ...]:
     return tuple(ids) + tuple(getattr(tok, "eos_ids", ()))
 
 
+def _stop_texts(body: dict, tok) -> tuple[str, ...]:
+    """Every stop string, for the match on the decoded text: it ends the reply before the string whatever its
+    tokenisation (a one-token stop also ends generation at the token level, which only saves the extra step)."""
+    stop = body.get("stop") or body.get("stop_sequences") or []
+    if isinstance(stop, str):
+        stop = [stop]
+    if not isinstance(stop, list) or len(stop) > 16 or not all(isinstance(s, str) for s in stop):
+        raise BadRequest("stop must be a string or a list of at most 16 strings")
+    return tuple(s for s in stop if s)
+
+
 COMPACT_REQUEST = ("Summarize this conversation so that it can be continued from the summary alone. Keep the user's "
                    "requirements, the decisions taken, tool results and the work still pending. Answer with the summary only.")
 COMPACT_PREFIX = "Summary of the conversation so far:\n"
@@ -221,9 +232,11 @@ def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, f
         raise BadRequest("top_logprobs must be an integer between 0 and 20")
     keep = max(n_top, 1) if (body.get("logprobs") or n_top) else 0
     keep = max(keep, int(probe.get("top_k", 0) or 0))
+    stop_texts = _stop_texts(body, tok)                    # validates the type of ``stop`` before anything encodes it
     return Request(prompt=prompt, max_tokens=max_tokens, params=_params(body), stop_ids=_stops(body, tok),
                    speculation=not probe.get("no_speculation", False), record_rows=bool(probe.get("record_rows", False)),
-                   constraint=cons, media=spans, top_logprobs=keep, cold=bool(probe.get("cold", False)))
+                   constraint=cons, media=spans, top_logprobs=keep, cold=bool(probe.get("cold", False)),
+                   stop_texts=stop_texts)
 
 
 def logprobs_block(tok, top_rows: list, n_top: int) -> dict:

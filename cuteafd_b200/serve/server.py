@@ -18,7 +18,7 @@ from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 
 from ..runtime.scheduler import FAIL_BAD_REQUEST, FAIL_UNAVAILABLE, Request, Scheduler
 from . import api, ws
-from .tokenizer import StreamDecoder, ToolCallStream
+from .tokenizer import StopStream, StreamDecoder, ToolCallStream
 
 class ServerState:
     def __init__(self, scheduler: Scheduler, tokenizer, model_id: str, api_key: str = "", usage=None, extras=None, media=None):
@@ -282,16 +282,21 @@ def make_handler(state: ServerState):
             eos = set(getattr(state.tok, "eos_ids", ()))
             said: list[str] = []
             first = None
+            stopper = StopStream(getattr(req, "stop_texts", ()))
             while True:
                 ev = req.events.get()
                 if ev[0] == "tokens":
                     first = first or time.time()
-                    text = dec.push([t for t in ev[1] if t not in eos])
+                    text = stopper.push(dec.push([t for t in ev[1] if t not in eos]))
                     if text:
                         said.append(text)
                         yield ("text", text)
+                    if stopper.hit is not None:
+                        req.cancelled.set()                   # a stop string: nothing after it is generated or shown
                 elif ev[0] == "done":
-                    tail = dec.flush()
+                    tail = stopper.push(dec.flush()) + stopper.flush()
+                    if stopper.hit is not None:
+                        ev = ("done", "stop", ev[2], ev[3] if len(ev) > 3 else [])
                     if tail:
                         said.append(tail)
                         yield ("text", tail)

@@ -161,6 +161,39 @@ def parse_tool_calls(text: str) -> tuple[str, list[dict]]:
     return "".join(out), calls
 
 
+class StopStream:
+    """Stop strings that are not single tokens: the reply ends before the first occurrence of any of them.  Text is
+    passed on as it arrives except for a tail that could still grow into a stop string."""
+
+    def __init__(self, stops):
+        self.stops = [s for s in stops if s]
+        self.buf = ""
+        self.hit: str | None = None
+
+    def push(self, text: str) -> str:
+        if self.hit is not None or not self.stops:
+            return "" if self.hit is not None else text
+        self.buf += text
+        first = min(((self.buf.find(s), s) for s in self.stops if s in self.buf), default=None)
+        if first is not None:
+            self.hit = first[1]
+            out, self.buf = self.buf[:first[0]], ""
+            return out
+        keep = 0
+        for s in self.stops:
+            for k in range(min(len(s) - 1, len(self.buf)), keep, -1):
+                if s.startswith(self.buf[-k:]):
+                    keep = k
+                    break
+        out = self.buf[:len(self.buf) - keep]
+        self.buf = self.buf[len(self.buf) - keep:]
+        return out
+
+    def flush(self) -> str:
+        out, self.buf = ("" if self.hit is not None else self.buf), ""
+        return out
+
+
 class ToolCallStream:
     """Splits a streamed reply into visible text and completed tool calls.  Text is passed through as it arrives except
     for what could still turn out to be the opening tag; everything between ``<tool_call>`` and ``</tool_call>`` is held

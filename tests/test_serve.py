@@ -501,3 +501,28 @@ def test_tool_call_stream_filter():
     t = ToolCallStream()
     t.push('x<tool_call>{"name"')
     assert t.flush() == '<tool_call>{"name"'                    # cut off mid-call: returned as text
+
+
+def test_stop_stream_and_multi_token_stop(server):
+    from cuteafd_b200.serve.tokenizer import StopStream
+    for step in (1, 2, 5, 100):
+        s, out = StopStream(["END", "\\n\\nUser:"]), []
+        text = "line one\\nline two EN and then END never shown"
+        for i in range(0, len(text), step):
+            out.append(s.push(text[i:i + step]))
+        out.append(s.flush())
+        assert "".join(out) == "line one\\nline two EN and then " and s.hit == "END"
+    s = StopStream(["xyz"])
+    assert s.push("abcx") == "abc" and s.push("y") == "" and s.push("q") == "xyq" and s.flush() == "" and s.hit is None
+    assert StopStream([]).push("anything") == "anything"
+    # through the server: find a two-token string the greedy reply contains, then ask to stop at it
+    body = {"messages": [{"role": "user", "content": "tell me something long"}], "max_tokens": 24, "temperature": 0}
+    full = json.loads(call(server, "POST", "/v1/chat/completions", body)[2])
+    text = full["choices"][0]["message"]["content"]
+    assert len(text) >= 4
+    stop = text[2:4]
+    cut = json.loads(call(server, "POST", "/v1/chat/completions", dict(body, stop=[stop]))[2])
+    got = cut["choices"][0]["message"]["content"]
+    assert got == text[:text.index(stop)] and cut["choices"][0]["finish_reason"] == "stop"
+    assert 0 < cut["usage"]["completion_tokens"] <= full["usage"]["completion_tokens"]
+    assert call(server, "POST", "/v1/chat/completions", dict(body, stop=[1, 2]))[0] == 400
