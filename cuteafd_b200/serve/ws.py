@@ -26,7 +26,7 @@ import uuid
 
 from ..runtime.scheduler import FAIL_UNAVAILABLE
 from . import api
-from .tokenizer import StreamDecoder
+from .tokenizer import StopStream, StreamDecoder
 
 _GUID = b"258EAFA5-E914-47DA-95CA-C5AB0DC85B11"
 OP_CONT, OP_TEXT, OP_BIN, OP_CLOSE, OP_PING, OP_PONG = 0x0, 0x1, 0x2, 0x8, 0x9, 0xA
@@ -189,6 +189,7 @@ def _generate(state, ws: Socket, body: dict, flavor: str, on_text, cancel_types:
         return ("error", FAIL_UNAVAILABLE, "engine is starting")
     state.sched.submit(req)
     dec = StreamDecoder(state.tok)
+    stopper = StopStream(getattr(req, "stop_texts", ()))       # stop strings end the reply before them, as over HTTP
     eos = set(getattr(state.tok, "eos_ids", ()))
     text: list[str] = []
     cancelled = False
@@ -216,15 +217,19 @@ def _generate(state, ws: Socket, body: dict, flavor: str, on_text, cancel_types:
         if ev is None:
             continue
         if ev[0] == "tokens":
-            piece = dec.push([t for t in ev[1] if t not in eos])
+            piece = stopper.push(dec.push([t for t in ev[1] if t not in eos]))
             if piece and not cancelled:
                 text.append(piece)
                 on_text(piece)
+            if stopper.hit is not None:
+                req.cancelled.set()
         elif ev[0] == "done":
-            tail = dec.flush()
+            tail = stopper.push(dec.flush()) + stopper.flush()
             if tail and not cancelled:
                 text.append(tail)
                 on_text(tail)
+            if stopper.hit is not None and not cancelled:
+                return ("done", "stop", ev[2], "".join(text))
             if cancelled:
                 return ("cancelled", "".join(text), ev[2])
             return ("done", ev[1], ev[2], "".join(text))
