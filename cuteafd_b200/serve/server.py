@@ -147,6 +147,14 @@ def make_handler(state: ServerState):
                 return self._json(200, {"models": [{"slug": state.model_id, "display_name": state.model_id, "context_window": window,
                                                     "max_output_tokens": min(window // 2, 32768), "supports_reasoning": False,
                                                     "supports_parallel_tool_calls": True, "wire_api": "responses"}]})
+            if path == "/metrics":
+                from .metrics import render
+                raw = render(state).encode()
+                self.send_response(200)
+                self.send_header("Content-Type", "text/plain; version=0.0.4; charset=utf-8")
+                self.send_header("Content-Length", str(len(raw)))
+                self.end_headers()
+                return self.wfile.write(raw)
             if path == "/v1/stats":
                 s = state.sched.snapshot()
                 be = state.sched.be

@@ -526,3 +526,19 @@ def test_stop_stream_and_multi_token_stop(server):
     assert got == text[:text.index(stop)] and cut["choices"][0]["finish_reason"] == "stop"
     assert 0 < cut["usage"]["completion_tokens"] <= full["usage"]["completion_tokens"]
     assert call(server, "POST", "/v1/chat/completions", dict(body, stop=[1, 2]))[0] == 400
+
+
+def test_prometheus_metrics(server):
+    call(server, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "count"}], "max_tokens": 3})
+    st, hd, raw = call(server, "GET", "/metrics")
+    text = raw.decode()
+    assert st == 200 and "text/plain" in hd.get("Content-Type", hd.get("content-type", ""))
+    vals = {}
+    for line in text.splitlines():
+        assert line.startswith("#") or line.startswith("cuteafd_"), line
+        if not line.startswith("#"):
+            name, v = line.rsplit(" ", 1)
+            vals[name] = float(v)
+    assert vals["cuteafd_finished_total"] >= 1 and vals["cuteafd_emitted_tokens_total"] >= 1 and vals["cuteafd_ready"] == 1
+    assert vals['cuteafd_kv_pages{kind="total"}'] > 0 and 'cuteafd_requests{state="decode"}' in vals
+    assert text.count("# TYPE cuteafd_finished_total counter") == 1
