@@ -198,7 +198,7 @@ _HELP = {
     ("plan", "concurrency"): "requests decoded together (sizes graphs and workspaces)",
     ("serve", "concurrency"): "requests decoded together; more wait in the admission queue",
     ("plan", "speculator"): "speculative decoding to plan memory for",
-    ("serve", "speculator"): "auto (MTP depth of the checkpoint, else history n-gram), history, ngram, mtp, off",
+    ("serve", "speculator"): "auto (MTP depth of the checkpoint, else history n-gram), history, ngram, mtp, draft-model, off",
     "decode_lanes": "independent decode batches served alternately",
     "format": "override the detected storage format of dense weights",
     "expert_format": "override the detected storage format of routed experts",
@@ -288,6 +288,7 @@ def _build_parser() -> argparse.ArgumentParser:
                    help="short-cycle rule: tokens the copies after the first must span; 0 = off")
     s.add_argument("--loop-fast-copies", type=int, default=int(os.environ.get("CUTEAFD_LOOP_FAST_COPIES", 8)),
                    help="identical copies of a short unit (1..256 tokens) that count as a loop")
+    s.add_argument("--draft-snapshot", default="", help="with --speculator draft-model: the small checkpoint (same vocabulary) that drafts")
     s.add_argument("--speculation-trace", default="", help="JSONL file, one record per decode round (also $SPECULATION_TRACE); "
                                                             "written by a bounded background writer that drops, never blocks")
     s.add_argument("--stall-dump-seconds", type=float, default=0.0,

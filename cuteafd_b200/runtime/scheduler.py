@@ -425,7 +425,8 @@ class Scheduler:
             self.be.commit(a.handle, a.kv_len)
             stopped = self._emit(a, new)
             self.policy.observe(plan, n_acc, censored=stopped and n_acc < len(d), head_scores=hs)
-            self.drafter.accept(a.req.rid, new)
+            if not stopped:                               # a finished request's drafter state is already gone
+                self.drafter.accept(a.req.rid, new)
             a.spec["proposed"] += len(d)
             a.spec["accepted"] += n_acc
             a.spec["cycles"] += 1
@@ -479,6 +480,9 @@ class Scheduler:
                 finish, a.finish_detail = "length", "repetition"      # an exact loop ends like max_tokens
                 self.stats.loop_aborts += 1
                 break
+        if len(a.generated) == len(out) and hasattr(self.drafter, "begin") and a.req.speculation:
+            # the reply's first token: a drafter that keeps per-request state (history, a draft model's KV) starts here
+            self._safe(lambda: self.drafter.begin(a.req.rid, a.req.prompt, a.generated[0]))
         a.last_token = a.generated[-1]
         self.stats.emitted_tokens += len(out)
         a.req.events.put(("tokens", out))
@@ -493,6 +497,8 @@ class Scheduler:
         self._safe(lambda: self.be.release(a.handle))
         self.reserve.release(a.req.rid)
         self.policy.forget(a.req.rid)
+        if hasattr(self.drafter, "forget"):
+            self._safe(lambda: self.drafter.forget(a.req.rid))
         if reason is not None:
             usage = {"prompt_tokens": len(a.req.prompt), "completion_tokens": len(a.generated), "cached_tokens": a.cached,
                      "speculation": dict(a.spec, request_id=a.req.rid)}
@@ -517,6 +523,8 @@ class Scheduler:
                 self.stats.quarantined += 1
             self.reserve.release(a.req.rid)
             self.policy.forget(a.req.rid)
+            if hasattr(self.drafter, "forget"):
+                self._safe(lambda a=a: self.drafter.forget(a.req.rid))
             a.req.events.put(("error", FAIL_WORKER, msg))
             self.stats.failed += 1
 

@@ -294,8 +294,89 @@ class NgramDrafter:
                 return h[s + self.n:s + self.n + n], None
         return [], None
 
+    def begin(self, rid, prompt, first_token):
+        """The request's history starts with its prompt (suffixes of the reply are looked up in it too)."""
+        self.hist[rid] = list(prompt) + [first_token]
+
     def accept(self, rid, accepted_tokens):
         self.hist.setdefault(rid, []).extend(accepted_tokens)
+
+    def forget(self, rid):
+        self.hist.pop(rid, None)
+
+
+class ModelDrafter:
+    """A small draft model proposes the block: ``draft`` runs it greedily for up to ``n`` tokens from the request's
+    last token, ``accept`` rewinds its KV to the tokens the target kept and feeds what the target chose instead.
+    Verification decides, so the reply is the target's whatever the draft model says; a draft model that agrees with
+    the target k tokens ahead turns k + 1 target steps into one.
+
+    ``step(tokens, kv) -> logits [len(tokens), vocab]`` and ``new_kv()`` are the draft model (here the oracle decoder
+    over a small checkpoint; an engine with the same two calls plugs in the same way).  ``scores`` are the draft
+    model's probabilities of its own picks, which the history policy can use as head confidence.
+
+    Counterpart: the reference's dSpark block drafter (a small Qwen3 backbone beside the target,
+    rust/crates/cuteafd-daemon/src/shared/speculation/)."""
+
+    def __init__(self, step, new_kv, block: int = 4, vocab_size: int | None = None):
+        self.spec = DrafterSpec(block=block, head=True, copy=COPY_MAX_EXTRA)
+        self.step, self.new_kv, self.vocab = step, new_kv, vocab_size
+        self.state: dict[int, dict] = {}
+        self.drafted = 0
+
+    @staticmethod
+    def from_oracle(cfg, params, block: int = 4) -> "ModelDrafter":
+        import torch
+
+        from ..ref.model import KvState, RefDecoder
+        dec = RefDecoder(cfg, params)
+
+        def step(tokens, kv):
+            with torch.no_grad():
+                return dec.forward(torch.tensor(tokens, dtype=torch.long), kv)
+        return ModelDrafter(step, lambda: KvState(cfg), block, cfg.vocab_size)
+
+    def begin(self, rid, prompt, first_token):
+        kv = self.new_kv()
+        toks = [t if self.vocab is None or t < self.vocab else 0 for t in prompt]      # media rows: the draft model sees a filler
+        self.step(toks, kv)
+        self.state[rid] = {"kv": kv, "base": len(toks), "pending": first_token, "fed": []}
+
+    def draft(self, rid, last_hidden, last_token, n):
+        st = self.state.get(rid)
+        if st is None or n <= 0:
+            return [], None
+        import torch
+        if st["fed"]:                                   # a draft nobody settled (the plan dropped it): rewind first
+            st["kv"].truncate(st["base"])
+            st["fed"] = []
+        cur, toks, scores = st["pending"], [], []
+        for _ in range(n):
+            lp = torch.log_softmax(self.step([cur], st["kv"])[-1].float(), dim=-1)
+            st["fed"].append(cur)
+            cur = int(lp.argmax())
+            toks.append(cur)
+            scores.append(float(lp[cur].exp()))
+        self.drafted += len(toks)
+        return toks, scores
+
+    def accept(self, rid, accepted_tokens):
+        st = self.state.get(rid)
+        if st is None or not accepted_tokens:
+            return
+        want = [st["pending"]] + list(accepted_tokens[:-1])
+        fed = st["fed"]
+        common = 0
+        while common < min(len(fed), len(want)) and fed[common] == want[common]:
+            common += 1
+        st["kv"].truncate(st["base"] + common)
+        if want[common:]:
+            self.step([t if self.vocab is None or t < self.vocab else 0 for t in want[common:]], st["kv"])
+        st["base"] += len(want)
+        st["pending"], st["fed"] = accepted_tokens[-1], []
+
+    def forget(self, rid):
+        self.state.pop(rid, None)
 
 
 class MtpDrafter:

@@ -529,6 +529,17 @@ def build_state(args) -> ServerState:
                 print(f"prewarmed {n} decode graphs from {pw}", flush=True)
     tok = load_tokenizer(snapshot, cfg.vocab_size)
     drafter = NgramDrafter(block=4) if args.speculator in ("auto", "history", "ngram") else None
+    if args.speculator == "draft-model":
+        # a small checkpoint of the same vocabulary drafts the block; it runs on the oracle decoder (host), which suits
+        # the oracle engine and small draft models; verification by the target keeps the reply exact either way
+        from ..loader.load import load_params
+        from ..runtime.speculation import ModelDrafter
+        if not getattr(args, "draft_snapshot", ""):
+            raise SystemExit("--speculator draft-model needs --draft-snapshot")
+        dcfg, dparams = load_params(args.draft_snapshot)
+        if dcfg.vocab_size != cfg.vocab_size:
+            raise SystemExit(f"draft model vocabulary {dcfg.vocab_size} differs from the target's {cfg.vocab_size}")
+        drafter = ModelDrafter.from_oracle(dcfg, dparams, block=4)
     if args.speculator in ("auto", "mtp") and getattr(be, "has_mtp", False):
         from ..runtime.speculation import MtpDrafter
         drafter = MtpDrafter()              # native MTP depth of the checkpoint

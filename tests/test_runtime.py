@@ -435,3 +435,31 @@ def test_parity_reserve_deals_pages_and_stays_consistent():
     for rid, (p, m) in enumerate([(300, 200), (700, 64), (64, 2000)]):
         assert (one.lease(rid, p, m) is None) == (plain.lease(rid, p, m) is None)
     assert one.leased == plain.leased
+
+
+def test_model_drafter_is_lossless_and_a_perfect_draft_model_is_fully_accepted(oracle):
+    cfg, params = oracle
+    g = torch.Generator().manual_seed(12)
+    prompt = torch.randint(0, cfg.vocab_size, (48,), generator=g).tolist()
+    base = _run(Scheduler(OracleBackend(cfg, params)), [Request(prompt, max_tokens=20, speculation=False)])[0]
+    # the target itself as the draft model: every draft is what the target will pick
+    perfect = speculation.ModelDrafter.from_oracle(cfg, params, block=4)
+    s1 = Scheduler(OracleBackend(cfg, params), drafter=perfect)
+    out = _run(s1, [Request(prompt, max_tokens=20)])[0]
+    sp = out["usage"]["speculation"]
+    assert out["tokens"] == base["tokens"] and sp["proposed"] > 0 and sp["accepted"] == sp["proposed"]
+    assert sp["cycles"] < 20 and perfect.state == {}                       # fewer target steps than tokens; state dropped at finish
+    # an unrelated draft model: drafts are mostly wrong, the reply is still the target's
+    other = speculation.ModelDrafter.from_oracle(cfg, init_weights(cfg, seed=99), block=3)
+    s2 = Scheduler(OracleBackend(cfg, params), drafter=other, draft_control="always") if "draft_control" in Scheduler.__init__.__code__.co_varnames else None
+    out2 = _run(s2, [Request(prompt, max_tokens=20), Request(prompt[:30], max_tokens=12)])
+    solo = _run(Scheduler(OracleBackend(cfg, params)), [Request(prompt[:30], max_tokens=12, speculation=False)])[0]
+    assert out2[0]["tokens"] == base["tokens"] and out2[1]["tokens"] == solo["tokens"] and other.drafted > 0
+    # the n-gram drafter now starts from the prompt and forgets finished requests
+    ng = speculation.NgramDrafter(block=4)
+    pattern = [5, 9, 2, 7, 3, 8] * 10
+    s3 = Scheduler(OracleBackend(cfg, params), drafter=ng)
+    _run(s3, [Request(pattern, max_tokens=8)])
+    assert ng.hist == {}
+    ng.begin(7, [1, 2, 3, 4, 1, 2, 3], 4)
+    assert ng.draft(7, None, 4, 3)[0] == [1, 2, 3]

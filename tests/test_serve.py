@@ -542,3 +542,23 @@ def test_prometheus_metrics(server):
     assert vals["cuteafd_finished_total"] >= 1 and vals["cuteafd_emitted_tokens_total"] >= 1 and vals["cuteafd_ready"] == 1
     assert vals['cuteafd_kv_pages{kind="total"}'] > 0 and 'cuteafd_requests{state="decode"}' in vals
     assert text.count("# TYPE cuteafd_finished_total counter") == 1
+
+
+def test_build_state_with_a_draft_model(tmp_path):
+    from cuteafd_b200 import tiny_moe
+    from cuteafd_b200.cli import build_parser
+    from cuteafd_b200.loader import snapshot
+    from cuteafd_b200.runtime.scheduler import Request, collect
+    from cuteafd_b200.serve.server import build_state
+    cfg = tiny_moe()
+    tgt = snapshot.write_random_snapshot(cfg, str(tmp_path / "t"), fmt="bf16", seed=0)
+    args = build_parser().parse_args(["serve", "--fake-engine", "--snapshot", tgt, "--speculator", "draft-model", "--draft-snapshot", tgt])
+    state = build_state(args)
+    assert type(state.sched.drafter).__name__ == "ModelDrafter"
+    req = state.sched.submit(Request(list(range(1, 40)), max_tokens=12))
+    for _ in range(400):
+        if not state.sched.step() and not state.sched.decoding and not state.sched.prefilling and state.sched.waiting.empty() and not state.sched.pending:
+            break
+    out = collect(req, timeout=1.0)
+    sp = out["usage"]["speculation"]
+    assert len(out["tokens"]) == 12 and sp["accepted"] == sp["proposed"] > 0 and sp["cycles"] < 12     # the target drafting for itself
