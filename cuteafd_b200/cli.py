@@ -165,6 +165,36 @@ def torch_dtype(name: str):
     return {"f32": torch.float32, "bf16": torch.bfloat16}[name]
 
 
+def cmd_encoderd(a: argparse.Namespace) -> int:
+    """Media encoder service: holds the vision / audio towers of a snapshot and serves embedding rows over TCP."""
+    import time
+
+    import torch
+
+    from .loader.snapshot import read_config
+    from .media.loader import load_towers
+    from .media.remote import EncoderServer
+    cfg, _ = read_config(a.snapshot) if a.snapshot else (None, None)
+    hidden = cfg.hidden if cfg else a.hidden
+    dev = a.device if (a.device == "cpu" or torch.cuda.is_available()) else "cpu"
+    vision, audio = load_towers(a.snapshot, hidden, dev) if a.snapshot else (None, None)
+    if a.random:
+        from .media import AudioTower, AudioTowerConfig, VisionTower, VisionTowerConfig
+        small = dict(width=256, depth=2, heads=4, mlp=512, out_hidden=hidden)
+        vision = vision or VisionTower(VisionTowerConfig(**small), VisionTower.random_weights(VisionTowerConfig(**small)), dev)
+        audio = audio or AudioTower(AudioTowerConfig(**small), AudioTower.random_weights(AudioTowerConfig(**small)), dev)
+    if vision is None and audio is None:
+        raise SystemExit("the snapshot bundles no vision or audio tower (use --random for random-init towers)")
+    srv = EncoderServer(vision, audio, a.host, a.port).start()
+    print(f"media encoder ({'vision' if vision else ''}{'+' if vision and audio else ''}{'audio' if audio else ''}) on {a.host}:{srv.port}", flush=True)
+    try:
+        while True:
+            time.sleep(3600)
+    except KeyboardInterrupt:
+        srv.stop()
+    return 0
+
+
 def cmd_fidelity(a: argparse.Namespace) -> int:
     from .bench.fidelity import run_cli
     return run_cli(a)
@@ -295,6 +325,7 @@ def _build_parser() -> argparse.ArgumentParser:
                    help="write every thread's stack when requests are in flight and the loop has not ticked for this long; 0 = off")
     s.add_argument("--stack-dump-file", default="", help="where SIGUSR1 and stall dumps go (default: stderr)")
     s.add_argument("--prewarm", default="", help="JSON list of decode step geometries: read at start, rewritten at exit; 'auto' = the derived default list")
+    s.add_argument("--media-encoder", default="", help="host:port of an encoderd service that holds the media towers (instead of --media)")
     s.add_argument("--media", default="none", choices=["none", "auto", "random"],
                    help="auto: load the vision / audio towers the snapshot bundles; random: small random-init towers")
     s.set_defaults(fn=cmd_serve)
@@ -358,6 +389,15 @@ def _build_parser() -> argparse.ArgumentParser:
     c.add_argument("--rows", type=int, default=2048); c.add_argument("--seq", type=int, default=256)
     c.add_argument("--seed", type=int, default=0); c.add_argument("--dtype", default="f32", choices=("f32", "bf16"))
     c.set_defaults(fn=cmd_calibrate)
+
+    en = sub.add_parser("encoderd", help="media encoder service: the vision / audio towers behind a TCP port")
+    en.add_argument("--snapshot", default="", help="checkpoint whose bundled towers are served")
+    en.add_argument("--host", default="127.0.0.1", help="address to listen on")
+    en.add_argument("--port", type=int, default=0, help="port to listen on (0 = any)")
+    en.add_argument("--device", default="cuda:0", help="device the towers run on (falls back to cpu without a GPU)")
+    en.add_argument("--hidden", type=int, default=2048, help="embedding width when no snapshot is given")
+    en.add_argument("--random", action="store_true", help="small random-init towers for whatever the snapshot lacks")
+    en.set_defaults(fn=cmd_encoderd)
 
     fd = sub.add_parser("fidelity", help="KL / top-1 of a snapshot against sealed reference windows")
     fd.add_argument("action", choices=["seal", "check"], help="seal: compute and store the reference distributions; check: compare a snapshot with them")

@@ -214,6 +214,10 @@ class ExpertServer:
     def stop(self) -> None:
         self._stop.set()
         try:
+            self.sock.shutdown(socket.SHUT_RDWR)            # wakes the thread blocked in accept()
+        except OSError:
+            pass
+        try:
             self.sock.close()
         except OSError:
             pass

@@ -559,7 +559,15 @@ def build_state(args) -> ServerState:
         sched.watchdog = StallWatchdog(stall_s, getattr(args, "stack_dump_file", "") or None).start()
     usage = UsageLog(args.usage_db) if args.usage_db else None
     media = None
-    if getattr(args, "media", "none") != "none":
+    if getattr(args, "media_encoder", ""):
+        # the towers live in an encoder service (another process or host); this process keeps preprocessing and caching
+        from ..media import MediaProcessor
+        from ..media.remote import connect
+        host, _, port = args.media_encoder.rpartition(":")
+        vision, audio = connect(host or "127.0.0.1", int(port))
+        if vision is not None or audio is not None:
+            media = MediaProcessor(cfg.vocab_size, cfg.hidden, vision, audio)
+    elif getattr(args, "media", "none") != "none":
         from ..media import AudioTower, AudioTowerConfig, MediaProcessor, VisionTower, VisionTowerConfig
         from ..media.loader import load_towers
         mdev = "cuda:0" if (torch.cuda.is_available() and not args.fake_engine) else "cpu"

@@ -186,3 +186,55 @@ def test_http_accepts_image_and_audio_parts():
         assert d["vision"] and d["audio"] and d["encoded"] == 2
     finally:
         srv.stop(); plain.stop()
+
+
+def test_remote_encoder_gives_the_same_rows():
+    """Towers behind the encoder service produce what local towers produce; a lost service is a media error on that
+    request and the next request reconnects."""
+    from cuteafd_b200.media.image import MediaError
+    from cuteafd_b200.media.remote import EncoderServer, connect
+    vision, audio = _towers(32)
+    srv = EncoderServer(vision, audio).start()
+    try:
+        rv, ra = connect("127.0.0.1", srv.port)
+        assert rv.cfg == vision.cfg and ra.cfg == audio.cfg and rv.rows_for((4, 6)) == vision.rows_for((4, 6))
+        local = MediaProcessor(1000, 32, vision, audio)
+        remote = MediaProcessor(1000, 32, rv, ra)
+        png, wav = _png(60, 90, 3), _wav(seed=4)
+        assert torch.equal(remote.encode_image(png)[1], local.encode_image(png)[1])
+        assert torch.equal(remote.encode_audio(wav)[1], local.encode_audio(wav)[1])
+        assert srv.encoded == 2
+        only_v = EncoderServer(vision, None).start()
+        v2, a2 = connect("127.0.0.1", only_v.port)
+        assert a2 is None and v2 is not None
+        only_v.stop()
+        # a service that goes away: the request fails as a media error; against a live one the link reconnects
+        rv.link.sock.close()
+        rv.link.sock = None
+        assert torch.equal(remote.encode_image(_png(60, 90, 5))[1], local.encode_image(_png(60, 90, 5))[1])
+    finally:
+        srv.stop()
+    rv.link.sock.close(); rv.link.sock = None
+    with pytest.raises(MediaError, match="unavailable"):
+        remote.encode_image(_png(30, 30, 6))
+
+
+def test_encoderd_process_and_serve_flag(tmp_path):
+    import subprocess
+    import sys
+    from cuteafd_b200.cli import build_parser
+    from cuteafd_b200.serve.server import build_state
+    p = subprocess.Popen([sys.executable, "-m", "cuteafd_b200.cli", "encoderd", "--random", "--hidden", "256", "--device", "cpu"],
+                         stdout=subprocess.PIPE, text=True)
+    try:
+        line = p.stdout.readline()
+        assert "media encoder (vision+audio)" in line, line
+        port = int(line.rsplit(":", 1)[1])
+        args = build_parser().parse_args(["serve", "--fake-engine", "--preset", "tiny-moe", "--media-encoder", f"127.0.0.1:{port}"])
+        state = build_state(args)                              # tiny-moe has hidden 256: the towers' width fits
+        assert state.media is not None and state.media.describe()["vision"] and state.media.describe()["audio"]
+        key, rows = state.media.encode_image(_png(56, 56, 1))
+        assert rows.shape[1] == 256 and torch.isfinite(rows).all()
+    finally:
+        p.kill()
+        p.wait(timeout=10)
