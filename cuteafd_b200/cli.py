@@ -319,6 +319,8 @@ def _build_parser() -> argparse.ArgumentParser:
     s.add_argument("--loop-fast-copies", type=int, default=int(os.environ.get("CUTEAFD_LOOP_FAST_COPIES", 8)),
                    help="identical copies of a short unit (1..256 tokens) that count as a loop")
     s.add_argument("--draft-snapshot", default="", help="with --speculator draft-model: the small checkpoint (same vocabulary) that drafts")
+    s.add_argument("--profile", default="", help="comma-separated host-side profile modes (also $PROFILE): draft-timing, expert-routes, census, step-timing")
+    s.add_argument("--profile-dir", default="", help="directory for the files the profile modes append to (default: the working directory)")
     s.add_argument("--speculation-trace", default="", help="JSONL file, one record per decode round (also $SPECULATION_TRACE); "
                                                             "written by a bounded background writer that drops, never blocks")
     s.add_argument("--stall-dump-seconds", type=float, default=0.0,

@@ -161,6 +161,8 @@ def make_handler(state: ServerState):
                 if hasattr(be, "prefix"):
                     s["prefix"] = be.prefix.describe()
                 s["uptime_s"] = round(time.time() - state.started, 1)
+                if getattr(state.sched, "profile", None) is not None:
+                    s["profile"] = state.sched.profile.report()
                 return self._json(200, s)
             if path == "/v1/thermal":
                 from ..utils.thermal import monitor
@@ -549,6 +551,10 @@ def build_state(args) -> ServerState:
     sched = Scheduler(be, max_active=args.concurrency, queue_depth=args.queue_depth, queue_wait_s=args.queue_wait,
                       loop_abort=loop if loop.enabled else None,
                       drafter=drafter, eos_ids=tuple(getattr(tok, "eos_ids", ())))
+    prof = getattr(args, "profile", "") or os.environ.get("PROFILE", "")
+    if prof:
+        from ..utils.profile import Profile, parse_modes
+        Profile(parse_modes(prof), getattr(args, "profile_dir", "") or ".", 64).attach(sched)
     trace_path = getattr(args, "speculation_trace", "") or os.environ.get("SPECULATION_TRACE", "")
     if trace_path:
         from ..utils.trace import JsonlTrace

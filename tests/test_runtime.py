@@ -463,3 +463,22 @@ def test_model_drafter_is_lossless_and_a_perfect_draft_model_is_fully_accepted(o
     assert ng.hist == {}
     ng.begin(7, [1, 2, 3, 4, 1, 2, 3], 4)
     assert ng.draft(7, None, 4, 3)[0] == [1, 2, 3]
+
+
+def test_profile_modes(oracle, tmp_path):
+    import json
+    from cuteafd_b200.utils.profile import Profile, parse_modes
+    cfg, params = oracle
+    with pytest.raises(ValueError):
+        parse_modes("draft-timing,nsys")
+    sched = Scheduler(OracleBackend(cfg, params), drafter=speculation.NgramDrafter(block=3))
+    prof = Profile(parse_modes("draft-timing, expert-routes,census,step-timing"), str(tmp_path / "p"), period=2).attach(sched)
+    out = _run(sched, [Request(([3, 1, 4, 1, 5, 9] * 8)[:40], max_tokens=10)])[0]
+    assert len(out["tokens"]) == 10
+    rep = prof.report()
+    assert rep["draft"]["draft"]["calls"] >= 1 and rep["draft"]["begin"]["calls"] == 1 and 0 <= rep["draft"]["share_of_decode"] < 1
+    assert rep["steps"]["decode"]["count"] == sched.stats.decode_rounds and rep["steps"]["prefill"]["count"] >= 1
+    routes = [json.loads(l) for l in open(tmp_path / "p" / "expert_routes.jsonl")]
+    census = [json.loads(l) for l in open(tmp_path / "p" / "census.jsonl")]
+    assert routes and routes[-1]["usage"]["layers"] and census and census[-1]["verify_row_hist"]
+    assert len(routes) == len(census) <= sched.stats.decode_rounds // 2 + 1
