@@ -104,6 +104,44 @@ class _UpstreamFailed(Exception):
     pass
 
 
+def sse_events(out: dict, flavor: str) -> list[tuple[str, dict]]:
+    """A finished reply as the event sequence a streaming client of that flavour expects.  The gateway asks its upstream
+    for whole replies (so that it can run hosted tools between turns) and replays them as one-delta streams: the
+    protocol is the streaming one, the text arrives in one piece."""
+    ev: list[tuple[str, dict]] = []
+    if flavor == "anthropic":
+        head = dict(out, content=[], stop_reason=None)
+        ev.append(("message_start", {"type": "message_start", "message": head}))
+        for i, b in enumerate(out.get("content", [])):
+            if b.get("type") == "text":
+                ev.append(("content_block_start", {"type": "content_block_start", "index": i, "content_block": {"type": "text", "text": ""}}))
+                ev.append(("content_block_delta", {"type": "content_block_delta", "index": i, "delta": {"type": "text_delta", "text": b.get("text", "")}}))
+            elif b.get("type") == "tool_use":
+                ev.append(("content_block_start", {"type": "content_block_start", "index": i, "content_block": dict(b, input={})}))
+                ev.append(("content_block_delta", {"type": "content_block_delta", "index": i,
+                                                   "delta": {"type": "input_json_delta", "partial_json": json.dumps(b.get("input", {}))}}))
+            else:                                                   # server tool blocks travel whole
+                ev.append(("content_block_start", {"type": "content_block_start", "index": i, "content_block": b}))
+            ev.append(("content_block_stop", {"type": "content_block_stop", "index": i}))
+        ev.append(("message_delta", {"type": "message_delta", "delta": {"stop_reason": out.get("stop_reason")},
+                                     "usage": {"output_tokens": out.get("usage", {}).get("output_tokens", 0)}}))
+        ev.append(("message_stop", {"type": "message_stop"}))
+        return ev
+    ev.append(("response.created", {"type": "response.created", "response": {"id": out["id"], "status": "in_progress"}}))
+    for i, item in enumerate(out.get("output", [])):
+        ev.append(("response.output_item.added", {"type": "response.output_item.added", "output_index": i, "item": item}))
+        if item.get("type") == "message":
+            for part in item.get("content", []):
+                if part.get("type") == "output_text":
+                    ev.append(("response.output_text.delta", {"type": "response.output_text.delta", "output_index": i, "delta": part.get("text", "")}))
+        elif item.get("type") == "function_call":
+            ev.append(("response.function_call_arguments.done", {"type": "response.function_call_arguments.done", "output_index": i,
+                                                                 "name": item.get("name"), "arguments": item.get("arguments")}))
+        ev.append(("response.output_item.done", {"type": "response.output_item.done", "output_index": i, "item": item}))
+    ev.append(("response.completed", {"type": "response.completed", "response": out}))
+    return ev
+
+
 def attach_searches(out: dict, flavor: str, ran: list[dict]) -> None:
     """Show the client the searches the gateway ran for it, in its own protocol's block types."""
     if flavor == "anthropic":
@@ -149,6 +187,41 @@ def make_gateway(upstream: str, model_map: dict[str, str], tape: "Tape | None" =
             except urllib.error.URLError as e:
                 return self._json(503, {"error": {"message": f"upstream unavailable: {e}"}})
 
+        def _sse_all(self, events: list) -> None:
+            self.send_response(200)
+            self.send_header("Content-Type", "text/event-stream")
+            self.send_header("Cache-Control", "no-cache")
+            self.send_header("Connection", "close")
+            self.end_headers()
+            for name, ev in events:
+                self.wfile.write(f"event: {name}\ndata: {json.dumps(ev)}\n\n".encode())
+            self.wfile.flush()
+            self.close_connection = True
+
+        def _proxy_stream(self, fpath: str, fwd: dict) -> None:
+            """A streamed request in the upstream's own protocol: bytes are passed through as they arrive."""
+            req = urllib.request.Request(upstream + fpath, json.dumps(fwd).encode(),
+                                         {"Content-Type": "application/json", "Authorization": self.headers.get("Authorization", "")})
+            try:
+                r = urllib.request.urlopen(req, timeout=600)
+            except urllib.error.HTTPError as e:
+                return self._json(e.code, json.loads(e.read() or b"{}"))
+            except urllib.error.URLError as e:
+                return self._json(503, {"error": {"message": f"upstream unavailable: {e}"}})
+            with r:
+                self.send_response(r.status)
+                self.send_header("Content-Type", r.headers.get("Content-Type", "text/event-stream"))
+                self.send_header("Cache-Control", "no-cache")
+                self.send_header("Connection", "close")
+                self.end_headers()
+                while True:
+                    chunk = r.read1(65536) if hasattr(r, "read1") else r.read(65536)
+                    if not chunk:
+                        break
+                    self.wfile.write(chunk)
+                    self.wfile.flush()
+            self.close_connection = True
+
         def _session(self, body: dict) -> "search.SearchSession":
             key = (self.headers.get("Authorization", ""), str(body.get("session_id") or body.get("previous_response_id") or ""))
             with sessions_lock:
@@ -189,6 +262,8 @@ def make_gateway(upstream: str, model_map: dict[str, str], tape: "Tape | None" =
                 return self._json(200, search.alpha_search(provider, self._session(body), body))
             fwd = to_chat_body(body, flavor, model_map) if flavor else body
             fpath = "/v1/chat/completions" if flavor else self.path
+            if not flavor and body.get("stream") and not (tape is not None and tape.mode == "replay"):
+                return self._proxy_stream(fpath, fwd)
             decl = search.wants_hosted_search(body) if flavor else None
             ran: list[dict] = []
             if decl is not None and provider is not None:
@@ -214,6 +289,8 @@ def make_gateway(upstream: str, model_map: dict[str, str], tape: "Tape | None" =
             out = from_chat_reply(reply, flavor, body.get("model", ""))
             if ran:
                 attach_searches(out, flavor, ran)
+            if body.get("stream"):
+                return self._sse_all(sse_events(out, flavor))
             return self._json(200, out)
 
     return H

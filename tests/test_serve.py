@@ -562,3 +562,28 @@ def test_build_state_with_a_draft_model(tmp_path):
     out = collect(req, timeout=1.0)
     sp = out["usage"]["speculation"]
     assert len(out["tokens"]) == 12 and sp["accepted"] == sp["proposed"] > 0 and sp["cycles"] < 12     # the target drafting for itself
+
+
+def test_gateway_streams(server):
+    """Streaming clients of the translated flavours get their protocol's event sequence; a streamed request in the
+    upstream's own protocol is passed through."""
+    gw = Gateway(f"http://127.0.0.1:{server.port}", model_map={"claude-x": "tiny-moe"}).start()
+    try:
+        def post(path, body):
+            c = http.client.HTTPConnection("127.0.0.1", gw.port, timeout=120)
+            c.request("POST", path, json.dumps(body), {"Content-Type": "application/json", "Authorization": "Bearer sekret"})
+            r = c.getresponse()
+            return r.status, r.getheader("Content-Type"), r.read().decode()
+        st, ct, raw = post("/v1/messages", {"model": "claude-x", "max_tokens": 5, "stream": True, "messages": [{"role": "user", "content": "hi"}]})
+        names = [l[7:] for l in raw.splitlines() if l.startswith("event: ")]
+        assert st == 200 and "event-stream" in ct
+        assert names[0] == "message_start" and names[-2:] == ["message_delta", "message_stop"] and "content_block_delta" in names
+        st, ct, raw = post("/v1/responses", {"model": "tiny-moe", "max_output_tokens": 5, "stream": True, "input": "hi"})
+        names = [l[7:] for l in raw.splitlines() if l.startswith("event: ")]
+        assert names[0] == "response.created" and names[-1] == "response.completed" and "response.output_text.delta" in names
+        done = json.loads([l for l in raw.splitlines() if l.startswith("data: ")][-1][6:])
+        assert done["response"]["status"] in ("completed", "incomplete") and done["response"]["usage"]["output_tokens"] >= 1
+        st, ct, raw = post("/v1/chat/completions", {"model": "tiny-moe", "max_tokens": 4, "stream": True, "messages": [{"role": "user", "content": "hi"}]})
+        assert st == 200 and "event-stream" in ct and raw.rstrip().endswith("data: [DONE]") and "chat.completion.chunk" in raw
+    finally:
+        gw.stop()
