@@ -182,8 +182,14 @@ def make_gateway(upstream: str, model_map: dict[str, str], tape: "Tape | None" =
 
         def do_GET(self):
             try:
-                with urllib.request.urlopen(upstream + self.path, timeout=30) as r:
+                req = urllib.request.Request(upstream + self.path, headers={"Authorization": self.headers.get("Authorization", "")})
+                with urllib.request.urlopen(req, timeout=30) as r:
                     return self._json(r.status, json.loads(r.read()))
+            except urllib.error.HTTPError as e:
+                try:
+                    return self._json(e.code, json.loads(e.read() or b"{}"))
+                except json.JSONDecodeError:
+                    return self._json(e.code, {"error": {"message": f"upstream answered {e.code}"}})
             except urllib.error.URLError as e:
                 return self._json(503, {"error": {"message": f"upstream unavailable: {e}"}})
 

@@ -587,3 +587,18 @@ def test_gateway_streams(server):
         assert st == 200 and "event-stream" in ct and raw.rstrip().endswith("data: [DONE]") and "chat.completion.chunk" in raw
     finally:
         gw.stop()
+
+
+def test_gateway_get_carries_the_key(server):
+    gw = Gateway(f"http://127.0.0.1:{server.port}").start()
+    try:
+        def get(path, key):
+            c = http.client.HTTPConnection("127.0.0.1", gw.port, timeout=30)
+            c.request("GET", path, headers={"Authorization": f"Bearer {key}"} if key else {})
+            r = c.getresponse()
+            return r.status, json.loads(r.read())
+        st, models = get("/v1/models", "sekret")
+        assert st == 200 and models["data"][0]["id"] == "tiny-moe"
+        assert get("/v1/models", "wrong")[0] == 401 and get("/v1/models", "")[0] == 401
+    finally:
+        gw.stop()
