@@ -269,7 +269,10 @@ def run(url: str, panels: list[str], api_key: str = "", options: dict | None = N
         except (OSError, KeyError, ValueError, http.client.HTTPException) as e:
             res = {"ok": False, "error": f"{type(e).__name__}: {e}"}
         res = dict({"panel": name, "seconds": round(time.time() - t0, 2)}, **res)
-        st, th = c.get("/v1/thermal")
+        try:
+            st, th = c.get("/v1/thermal")
+        except (OSError, http.client.HTTPException):
+            st, th = 0, None                                   # the server is gone: the panel's own result says so
         if st == 200 and isinstance(th, dict) and th.get("available"):
             res["thermal"] = {g: {"verdict": w.get("verdict"), "sm_mhz": (w.get("sm_mhz") or {}).get("median")}
                               for g, w in (th.get("window") or {}).items()}
