@@ -423,13 +423,13 @@ class Scheduler:
                     self.drafter.offer(a.req.rid, [mtp[row]])
             a.kv_len += 1 + n_acc                           # last_token + accepted drafts now have KV
             self.be.commit(a.handle, a.kv_len)
+            a.spec["proposed"] += len(d)                    # before the emission: a reply that ends in this round reports it too
+            a.spec["accepted"] += n_acc
+            a.spec["cycles"] += 1
             stopped = self._emit(a, new)
             self.policy.observe(plan, n_acc, censored=stopped and n_acc < len(d), head_scores=hs)
             if not stopped:                               # a finished request's drafter state is already gone
                 self.drafter.accept(a.req.rid, new)
-            a.spec["proposed"] += len(d)
-            a.spec["accepted"] += n_acc
-            a.spec["cycles"] += 1
             acc_round.append(n_acc)
             if stopped:
                 done.append(a)

@@ -482,3 +482,9 @@ def test_profile_modes(oracle, tmp_path):
     census = [json.loads(l) for l in open(tmp_path / "p" / "census.jsonl")]
     assert routes and routes[-1]["usage"]["layers"] and census and census[-1]["verify_row_hist"]
     assert len(routes) == len(census) <= sched.stats.decode_rounds // 2 + 1
+
+
+def test_usage_counts_the_round_that_ends_the_reply(oracle):
+    cfg, params = oracle
+    out = _run(Scheduler(OracleBackend(cfg, params)), [Request(list(range(1, 30)), max_tokens=5, speculation=False)])[0]
+    assert len(out["tokens"]) == 5 and out["usage"]["speculation"]["cycles"] == 4      # one token from prefill, four decode rounds
