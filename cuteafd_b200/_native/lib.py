@@ -39,7 +39,8 @@ MAX_RANKS = 8
 # one setter per translation unit that waits (each holds its own copy of the limit)
 WAIT_LIMIT_SETTERS = ("cafd_gemm_set_wait_limit_ns", "cafd_moe_set_wait_limit_ns", "cafd_attn_set_wait_limit_ns",
                       "cafd_gemm_fp8_set_wait_limit_ns", "cafd_tp_set_wait_limit_ns", "cafd_mla_set_wait_limit_ns",
-                      "cafd_indexer_set_wait_limit_ns", "cafd_gemm_w4_set_wait_limit_ns", "cafd_gemm_exl3_set_wait_limit_ns")
+                      "cafd_indexer_set_wait_limit_ns", "cafd_gemm_w4_set_wait_limit_ns", "cafd_gemm_exl3_set_wait_limit_ns",
+                      "cafd_decode_step_set_wait_limit_ns")
 
 
 class MoeLayout(C.Structure):

@@ -75,12 +75,15 @@ def device_decode_loop(gen: Generator, seqs, last_tokens: list[int], steps: int,
                   b.seq_lens[1][:S], b.q_start[1][:S + 1], 1, False, None)
 
     def step():
+        if hasattr(eng, "decode_step"):          # forward + selection + device-side advance, one launch where the engine fuses it
+            eng.decode_step(batch, advance=True)
+            return
         out = eng.greedy(eng.forward(batch))
         K.decode_advance(batch.tokens, out, batch.positions, batch.seq_lens, batch.slots, batch.page_table)
 
     l0 = eng.launches
     step()                                   # eager once: attribute setup, descriptor caches, scratch
-    launches = eng.launches - l0 + 1
+    launches = eng.launches - l0 + (0 if hasattr(eng, "decode_step") else 1)
     torch.cuda.synchronize()
     if gen.use_graphs:
         g = torch.cuda.CUDAGraph()

@@ -83,7 +83,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and records `code`) when the limit passes.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t code) {
-  if (mbar_try_wait(bar, parity)) return true;
+  // Fast path first: the clock (%globaltimer is slow to read) is only consulted after many failed polls, so a wait
+  // that completes within microseconds never pays for it.
+#pragma unroll 1
+  for (int i = 0; i < 2048; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   const unsigned long long limit = g_wait_limit_ns;
   for (uint32_t round = 1;; ++round) {
@@ -261,7 +265,10 @@ __device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
 }
 // Wait until *flag >= want (wrap-safe signed distance).  Bounded; false on timeout.
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want, uint32_t* status) {
-  if (static_cast<int32_t>(ld_acquire_sys(flag) - want) >= 0) return true;
+  // a peer usually answers within microseconds: poll without sleeping or reading the clock first
+#pragma unroll 1
+  for (int i = 0; i < 512; ++i)
+    if (static_cast<int32_t>(ld_acquire_sys(flag) - want) >= 0) return true;
   const unsigned long long t0 = globaltimer_ns();
   const unsigned long long limit = g_wait_limit_ns;
   for (;;) {

@@ -198,6 +198,9 @@ class Workspace:
 
 class GqaMoeEngine:
     """Single-GPU engine (attention and experts on the same device)."""
+    fused = None                 # class defaults: subclasses with their own constructor never take the fused step
+    _fused_rows = 0
+    _fused_checked = False
 
     def __init__(self, cfg: ModelConfig, weights: GqaMoeWeights, kv: KvCache, max_tokens: int, max_seqs: int = 64,
                  build_moe: bool = True):
@@ -223,6 +226,39 @@ class GqaMoeEngine:
         self.next_tokens = torch.empty(self.logits.shape[0], dtype=torch.int32, device=self.device)
         self._scratch: torch.Tensor | None = None
         self.launches = 0
+        # one-launch decode step (ops/decode_step.py): built lazily for the geometries it takes, single-GPU experts only
+        self.fused = None
+        self._fused_rows = 0
+        self._fused_checked = False
+
+    # ---- one-launch decode step -------------------------------------------------------------------
+    def _fused_for(self, b: Batch):
+        """The fused decode step when batch ``b`` is a plain decode step it can run, else None."""
+        if b.prefill or b.max_q_len != 1 or b.last_rows is not None or b.embeds is not None:
+            return None
+        if not self._fused_checked:
+            self._fused_checked = True
+            from ..ops.decode_step import FusedDecodeStep
+            if (type(self) is GqaMoeEngine and isinstance(self.moe, LocalExchange) and FusedDecodeStep.supports(self.cfg)
+                    and self.W.layers[0].w_gate is not None and self.device.type == "cuda"):
+                self.fused = FusedDecodeStep(self)
+        if self.fused is None or b.tokens.shape[0] > self.fused.MAX_ROWS or b.page_table.shape[0] != b.tokens.shape[0]:
+            return None
+        return self.fused
+
+    def decode_step(self, b: Batch, advance: bool = False) -> torch.Tensor:
+        """Forward + greedy selection of one decode step; with ``advance`` the batch's token / position / length /
+        slot vectors are moved to the next step on the device.  Returns the selected tokens."""
+        f = self._fused_for(b)
+        if f is not None:
+            _, nxt = f.run(b, advance=advance)
+            self.launches += 1
+            return nxt
+        out = self.greedy(self.forward(b))
+        if advance:
+            K.decode_advance(b.tokens, out, b.positions, b.seq_lens, b.slots, b.page_table)
+            self.launches += 1
+        return out
 
     # ---- pieces ---------------------------------------------------------------------------------
     def _attention(self, i: int, T: int, b: Batch) -> None:
@@ -290,6 +326,13 @@ class GqaMoeEngine:
         cfg, ws = self.cfg, self.ws
         T = b.tokens.shape[0]
         assert T <= self.max_tokens
+        self._fused_rows = 0
+        f = self._fused_for(b)
+        if f is not None:
+            logits, _ = f.run(b)
+            self.launches += 1
+            self._fused_rows = T             # ``greedy`` on these logits returns the tokens the step already selected
+            return logits
         K.embed(b.tokens, self.W.embed, out=ws.h[:T])
         self.launches += 1
         if b.embeds is not None:
@@ -341,5 +384,7 @@ class GqaMoeEngine:
         return K.linear(ws.x[:n], self.W.lm_head, out=self.mtp_logits[:n], out_f32=True)
 
     def greedy(self, logits: torch.Tensor) -> torch.Tensor:
+        if self._fused_rows and self._fused_rows == logits.shape[0] and logits.data_ptr() == self.logits.data_ptr():
+            return self.next_tokens[:logits.shape[0]]
         self.launches += 1
         return K.argmax(logits, out=self.next_tokens[:logits.shape[0]])
