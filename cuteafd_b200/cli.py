@@ -309,6 +309,8 @@ def _build_parser() -> argparse.ArgumentParser:
     s.add_argument("--queue-depth", type=int, default=64); s.add_argument("--queue-wait", type=float, default=30.0)
     s.add_argument("--fake-engine", action="store_true", help="serve with the CPU oracle engine (no GPU)")
     s.add_argument("--usage-db", default=""); s.add_argument("--memory-spool", default="", help="file opened at start-up that receives the ledger's state when an allocation fails"); s.add_argument("--kv-format", default="auto", choices=["auto", "bf16", "fp8_ds_mla"])
+    s.add_argument("--host-cache-gib", type=float, default=float(os.environ.get("CUTEAFD_HOST_CACHE_GIB", "4")),
+                   help="pinned host memory behind the device prefix cache: evicted snapshots are kept there and restored on a later hit (0 = off)")
     s.add_argument("--loop-abort-run", type=int, default=int(os.environ.get("CUTEAFD_LOOP_ABORT_RUN", 512)),
                    help="end a response (finish_reason length, finish_detail repetition) after this many consecutive "
                         "32-token shingles that repeat a block longer than 256 tokens; 0 = off")

@@ -50,9 +50,11 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_gather_kernel(const TpRedu
     s_ok = ok ? 1 : 0;
   }
   __syncthreads();
-  if (!s_ok) return;
+  // A block whose wait ran out skips its rows but still takes its ticket below: the arrival counter must be back at
+  // zero after every launch, or the next step's "last block" test would fire early and raise the gather flags before
+  // all rows are stored.  The flags are not raised once the status word is set.
   const int nvec = p.N / 8;
-  for (int row = blockIdx.x; row < p.rows_valid; row += gridDim.x) {
+  for (int row = blockIdx.x; s_ok && row < p.rows_valid; row += gridDim.x) {
     float ss = 0.f;
     // pass 1: ordered sum + residual, rounded once to bf16 and written back as the new residual
     for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
@@ -108,7 +110,8 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_gather_kernel(const TpRedu
       *p.done_counter = 0;
       __threadfence_system();
       const uint32_t ep = *p.epoch;
-      for (int r = 0; r < p.ranks; ++r) st_release_sys(p.ag_flags[r], ep);
+      const bool clean = *reinterpret_cast<volatile uint32_t*>(p.status) == 0u;
+      for (int r = 0; clean && r < p.ranks; ++r) st_release_sys(p.ag_flags[r], ep);
     }
   }
 }

@@ -61,10 +61,24 @@ def _read(sock: socket.socket) -> tuple[dict, torch.Tensor | None]:
         raise ConnectionError("oversized body")
     t = None
     if "shape" in h:
+        # the header is not trusted: shape and dtype must describe exactly the bytes that follow, before anything is
+        # allocated (the body itself is read either way, so the stream stays framed)
         raw = bytearray(_recv(sock, nb))
-        dt = _DT[h["dtype"]]
-        t = torch.frombuffer(raw, dtype=torch.uint8).view(dt).view(h["shape"]) if nb else torch.empty(h["shape"], dtype=dt)
+        shape, dt = h["shape"], _DT.get(h.get("dtype"))
+        if (dt is None or not isinstance(shape, list) or len(shape) > 8
+                or not all(isinstance(d, int) and not isinstance(d, bool) and d >= 0 for d in shape)):
+            raise MalformedFrame("bad shape or dtype")
+        count = 1
+        for d in shape:
+            count *= d
+        if count * torch.empty(0, dtype=dt).element_size() != nb:
+            raise MalformedFrame("shape and dtype do not match the body length")
+        t = torch.frombuffer(raw, dtype=torch.uint8).view(dt).view(shape) if nb else torch.empty(shape, dtype=dt)
     return h, t
+
+
+class MalformedFrame(ValueError):
+    """A frame whose header and body disagree; the connection is still in step, so the peer gets an error reply."""
 
 
 class EncoderServer:
@@ -105,7 +119,10 @@ class EncoderServer:
             while True:
                 try:
                     h, t = _read(conn)
-                except (ConnectionError, json.JSONDecodeError, struct.error, KeyError):
+                except MalformedFrame as e:
+                    _send(conn, {"ok": False, "error": f"malformed frame: {e}"})
+                    continue
+                except (ConnectionError, json.JSONDecodeError, struct.error, KeyError, ValueError, TypeError):
                     return
                 op = h.get("op")
                 try:

@@ -30,7 +30,7 @@ class OracleBackend:
     """CPU reference decoder behind the scheduler's Backend protocol."""
 
     def __init__(self, cfg: ModelConfig, params: dict[str, torch.Tensor], total_pages: int = 512, prefill_chunk: int = 64,
-                 max_decode_rows: int = 64, fail_on_step: int | None = None):
+                 max_decode_rows: int = 64, fail_on_step: int | None = None, host_slots: int = 0):
         from ..ref.model import RefDecoder
         self.cfg, self.model = cfg, RefDecoder(cfg, params)
         self.vocab_size, self.prefill_chunk, self.max_decode_rows = cfg.vocab_size, prefill_chunk, max_decode_rows
@@ -38,6 +38,11 @@ class OracleBackend:
         self.pool = PagePool(total_pages)
         self.table = SequenceTable(self.pool)
         self.prefix = PrefixCache(self.pool, self.table, max_pages=total_pages // 2)
+        self.tier = None
+        if host_slots:                            # host tier on a virtual clock: the oracle's KV rides in the snapshot marks
+            from .host_tier import HostTier
+            from .hostcache import HostCache, StubCopyEngine
+            self.tier = HostTier(self.prefix, self.pool, self.table, HostCache(StubCopyEngine(1 << 16), host_slots))
         self.steps = 0
         self.model.usage = {}                     # routed-token counters behind ``expert_usage``
         self.fail_on_step = fail_on_step          # host-side fault injection: the N-th verify raises
@@ -87,6 +92,14 @@ class OracleBackend:
             return _Handle(self.table.new(), KvState(self.cfg)), 0
         seq, m = self.prefix.admit(tokens)
         kv = KvState(self.cfg)
+        got = self.tier.try_restore(tokens, m.length) if self.tier is not None else None
+        if got is not None and got[2].mark is not None:
+            self.table.free(seq)
+            seq, length, hs = got
+            kv.rows = [[r[0][:length].clone()] if r else [] for r in hs.mark.rows]
+            return _Handle(seq, kv), length
+        if got is not None:
+            self.table.free(got[0])
         if m.length and m.snapshot is not None and m.snapshot.mark is not None:
             src = m.snapshot.mark
             kv.rows = [[r[0][:m.length].clone()] if r else [] for r in src.rows]
@@ -163,7 +176,7 @@ class EngineBackend:
     """The CUDA engine (single GPU or the attention rank of an AFD group)."""
 
     def __init__(self, engine, num_pages: int, max_pages_per_seq: int, prefill_chunk: int = 2048, max_decode_rows: int = 64,
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, host_cache_bytes: int = 0):
         from .generate import Generator, StepBuffers
         self.engine = engine
         self.cfg = engine.cfg
@@ -174,6 +187,17 @@ class EngineBackend:
         self.gen = Generator(engine, self.pool, max_pages_per_seq, max_decode_rows, prefill_chunk, use_graphs)
         self.table = self.gen.table
         self.prefix = PrefixCache(self.pool, self.table, max_pages=num_pages // 2)
+        self.tier = None
+        if host_cache_bytes > 0 and engine.device.type == "cuda":
+            # pinned-host tier behind the device cache: evicted snapshots are copied out on a side stream and come
+            # back through the same engine when a later request asks for their prefix
+            from .host_tier import HostTier
+            from .hostcache import CudaCopyEngine, HostCache
+            kv = engine.kv if hasattr(engine, "kv") else engine.inner.kv
+            pools = list(getattr(kv, "k", [])) + list(getattr(kv, "v", [])) + list(getattr(kv, "c", [])) + list(getattr(kv, "idx", []))
+            slots = int(host_cache_bytes // max(1, kv.bytes_per_page()))
+            if slots >= 8:
+                self.tier = HostTier(self.prefix, self.pool, self.table, HostCache(CudaCopyEngine(pools, slots), slots))
         self.max_pages = max_pages_per_seq
         self.bufs = StepBuffers(max_decode_rows * 8, max_decode_rows, max_pages_per_seq, engine.device)
         self.quarantined: list[_Handle] = []
@@ -217,6 +241,10 @@ class EngineBackend:
         if cold:                                   # probe: compute the whole prompt, whatever the cache holds
             return _Handle(self.table.new()), 0
         seq, m = self.prefix.admit(tokens)
+        got = self.tier.try_restore(tokens, m.length) if self.tier is not None else None
+        if got is not None:
+            self.table.free(seq)
+            return _Handle(got[0]), got[1]
         return _Handle(seq), m.length
 
     def prefill(self, h: _Handle, tokens: list[int], last: bool):

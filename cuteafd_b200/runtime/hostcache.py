@@ -115,7 +115,11 @@ class CudaCopyEngine:
         return ev
 
     def store(self, device_pages, host_slots):
-        return self._copy(self.s_store, list(zip(device_pages, host_slots)), True)
+        """The evicted pages go back to the pool as soon as this returns, so the compute stream is made to wait for the
+        copy: nothing launched later can overwrite a page before its bytes have left."""
+        ev = self._copy(self.s_store, list(zip(device_pages, host_slots)), True)
+        self.torch.cuda.current_stream().wait_event(ev)
+        return ev
 
     def restore(self, host_slots, device_pages):
         return self._copy(self.s_restore, list(zip(device_pages, host_slots)), False)

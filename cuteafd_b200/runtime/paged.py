@@ -23,12 +23,23 @@ class PagePool:
         self.refs = [0] * num_pages
         self.refs[0] = 1 << 30                       # reserved zero page
         self.free = list(range(num_pages - 1, 0, -1))
+        # Called with the number of pages wanted when the free list is empty; whoever holds reclaimable pages (the
+        # prefix cache's snapshots) gives some back.  The reference evicts snapshots under admission pressure the same
+        # way (rust/crates/cuteafd-engine/src/prefix/cache.rs:1040, ``make_room``).
+        self.on_exhausted = None
 
     @property
     def free_pages(self) -> int:
         return len(self.free)
 
+    @property
+    def usable_pages(self) -> int:
+        """Pages that can ever hold KV (page 0 is reserved)."""
+        return self.num_pages - 1
+
     def alloc(self) -> int:
+        if not self.free and self.on_exhausted is not None:
+            self.on_exhausted(8)                     # a few at a time: the next allocations are likely to follow
         if not self.free:
             raise OutOfPages("KV page pool exhausted")
         p = self.free.pop()

@@ -99,6 +99,7 @@ class PrefixCache:
         self.spill = spill
         self.salt = salt
         self._next = 1
+        pool.on_exhausted = self.reclaim          # snapshots give pages back before an allocation fails
 
     # ---- lookup / admit ---------------------------------------------------------------------------
     def lookup(self, tokens: list[int], media_key: bytes = b"") -> Match:
@@ -176,7 +177,8 @@ class PrefixCache:
             return None
         tokens = tuple(seq.tokens[:length])
         need = (length + PAGE - 1) // PAGE
-        self.make_room(need)
+        if not self.make_room(need):
+            return None                           # larger than the cache's whole budget: not retained
         node = self.root
         hashes = chain_hashes(list(tokens), self.salt + media_key)
         path = []
@@ -256,7 +258,7 @@ class PrefixCache:
             for kind in (PROMPT, TURN):
                 for s in sorted((s for s in self.snapshots.values() if s.kind == kind), key=lambda s: s.last_use):
                     yield s
-        while (self.held_pages + pages_needed > self.max_pages or self.pool.free_pages < 0) and self.snapshots:
+        while self.held_pages + pages_needed > self.max_pages and self.snapshots:
             v = next(victims(), None)
             if v is None:
                 break
@@ -264,7 +266,9 @@ class PrefixCache:
         return self.held_pages + pages_needed <= self.max_pages
 
     def reclaim(self, pages_needed: int) -> int:
-        """Free pool pages for the allocator (admission pressure).  Returns pages actually freed."""
+        """Free pool pages for the allocator (admission pressure): least recently used snapshots go first, prompt
+        bank before turn bank, spilling to the host tier when one is attached.  A snapshot whose pages are all shared
+        with live sequences frees nothing; the walk continues.  Returns pages actually freed."""
         before = self.pool.free_pages
         order = sorted(self.snapshots.values(), key=lambda s: (s.kind != PROMPT, s.last_use))
         for v in order:

@@ -3,8 +3,10 @@
 One loop owns every request: admission (queue bound -> KV lease -> prefix lookup / fork -> bind),
 chunked prefill time-sliced against decode by ``decode_share``, and decode rounds
 (plan drafts -> draft -> settle under the row budget -> verify -> select -> accept -> commit ->
-observe -> emit).  A failed step fails every request of that step with a ``worker`` failure and
-quarantines their KV instead of returning it to the pool.  Readiness is published only after the
+observe -> emit).  A failed device step fails every request of that step with a ``worker`` failure and
+quarantines their KV (kernels of the failed step may still be writing it) instead of returning it to the
+pool; a failure that happened on the host before anything was launched (no pages left, a malformed batch) and a
+per-row sampling error leave the KV intact, so those pages are released.  Readiness is published only after the
 backend, the prefix cache, the selector and the draft policy exist.
 
 The engine is behind a ``Backend`` protocol, so the same loop runs on the CUDA engine and on the
@@ -27,6 +29,12 @@ from .reserve import KvReserve
 from .speculation import DraftHistory, DrafterSpec, NoDrafter, Plan
 
 FAIL_BAD_REQUEST, FAIL_UNAVAILABLE, FAIL_RETRY, FAIL_WORKER = "bad_request", "unavailable", "retry", "worker"
+
+
+def _device_failure(e: Exception) -> bool:
+    """False for failures raised on the host before a kernel of the step was launched."""
+    from .paged import OutOfPages
+    return not isinstance(e, (OutOfPages, ValueError, KeyError, AssertionError))
 
 
 class Backend(Protocol):
@@ -121,7 +129,7 @@ class Scheduler:
         self.pending: list[Request] = []
         self.prefilling: list[Active] = []
         self.decoding: list[Active] = []
-        self.reserve = KvReserve(backend.total_pages)
+        self.reserve = KvReserve(backend.total_pages - 1)        # page 0 is the reserved zero page
         self.drafter = drafter or NoDrafter()
         self.policy = DraftHistory(self.drafter.spec if hasattr(self.drafter, "spec") else DrafterSpec(0), draft_control)
         self.row_budget = row_budget or backend.max_decode_rows
@@ -266,7 +274,7 @@ class Scheduler:
         except Exception as e:
             for a, _ in group:
                 self.prefilling.remove(a)
-            self._fail([a for a, _ in group], f"prefill failed: {e}")
+            self._fail([a for a, _ in group], f"prefill failed: {e}", device=_device_failure(e))
             return True
         self.stats.packed_steps += 1
         for (a, n), (_, _, last), logits in zip(group, items, outs):
@@ -299,7 +307,7 @@ class Scheduler:
             logits = self.be.prefill(a.handle, chunk, last)
         except Exception as e:
             self.prefilling.pop(0)
-            self._fail([a], f"prefill failed: {e}")
+            self._fail([a], f"prefill failed: {e}", device=_device_failure(e))
             return True
         a.prompt_done += n
         a.kv_len = a.prompt_done
@@ -383,7 +391,7 @@ class Scheduler:
                 logits = self.be.verify([a.handle for a in runnable], rows)
         except Exception as e:
             self.decoding = [a for a in self.decoding if a not in runnable]
-            self._fail(runnable, f"decode step failed: {e}")
+            self._fail(runnable, f"decode step failed: {e}", device=_device_failure(e))
             return True
         self.stats.decode_rounds += 1
         n_rows = sum(len(r) for r in rows)
@@ -514,13 +522,19 @@ class Scheduler:
             a.req.events.put(("done", "cancelled", {"prompt_tokens": len(a.req.prompt), "completion_tokens": len(a.generated),
                                                     "cached_tokens": a.cached, "speculation": dict(a.spec, request_id=a.req.rid)}, []))
 
-    def _fail(self, actives: list[Active], msg: str) -> None:
+    def _fail(self, actives: list[Active], msg: str, device: bool = False) -> None:
+        """``device``: the step may have reached the GPU, so the requests' pages are quarantined (kept allocated, never
+        handed out again) rather than released (rust/crates/cuteafd-daemon/src/shared/qwen/scheduler.rs:1459-1473)."""
         for a in actives:
-            try:
-                self.be.release(a.handle)
-            except Exception:
-                self._safe(lambda: self.be.quarantine(a.handle))
+            if device:
+                self._safe(lambda a=a: self.be.quarantine(a.handle))
                 self.stats.quarantined += 1
+            else:
+                try:
+                    self.be.release(a.handle)
+                except Exception:
+                    self._safe(lambda a=a: self.be.quarantine(a.handle))
+                    self.stats.quarantined += 1
             self.reserve.release(a.req.rid)
             self.policy.forget(a.req.rid)
             if hasattr(self.drafter, "forget"):

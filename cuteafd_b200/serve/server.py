@@ -160,6 +160,8 @@ def make_handler(state: ServerState):
                 be = state.sched.be
                 if hasattr(be, "prefix"):
                     s["prefix"] = be.prefix.describe()
+                if getattr(be, "tier", None) is not None:
+                    s["host_tier"] = be.tier.describe()
                 s["uptime_s"] = round(time.time() - state.started, 1)
                 if getattr(state.sched, "profile", None) is not None:
                     s["profile"] = state.sched.profile.report()
@@ -505,7 +507,8 @@ def build_state(args) -> ServerState:
             else:
                 from ..models.gqa_moe import GqaMoeEngine as Engine, GqaMoeWeights as Weights, KvCache as Cache
             eng = Engine(cfg, Weights.random_init(cfg, dev), Cache(cfg, num_pages, dev), max_tokens=max(2048, rows), max_seqs=rows)
-        be = EngineBackend(eng, num_pages, pages_per_seq, prefill_chunk=2048, max_decode_rows=args.concurrency)
+        be = EngineBackend(eng, num_pages, pages_per_seq, prefill_chunk=2048, max_decode_rows=args.concurrency,
+                           host_cache_bytes=int(float(getattr(args, "host_cache_gib", 0.0)) * (1 << 30)))
         if getattr(args, "prewarm", "") == "auto":              # no trace of an earlier run: the derived default list
             from ..planner.capacity import default_prewarm
             block = 0 if args.speculator == "off" else 4

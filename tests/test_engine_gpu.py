@@ -248,3 +248,52 @@ def test_prompt_packing_on_the_engine():
     # batched and single-sequence kernels round alike here (same tiles per sequence); allow a late divergence only
     same = sum(a[:3] == b[:3] for a, b in zip(alone, packed))
     assert same == len(prompts), (alone, packed)
+
+
+def test_host_tier_evict_and_restore_on_the_engine():
+    """Pinned-host tier behind the device prefix cache: snapshots evicted by other traffic are copied out on the side
+    stream and copied back on a later hit; the request served from the host tier emits the same tokens and the same
+    logit row hashes as when the device tier served the same prefix."""
+    from cuteafd_b200.ops import kernels as K
+    from cuteafd_b200.runtime.backends import EngineBackend
+    from cuteafd_b200.runtime.scheduler import Request, Scheduler
+    cfg = small_cfg()
+    _, eng, _ = build(cfg, False)            # 64 KV pages
+    be = EngineBackend(eng, 40, 12, prefill_chunk=128, max_decode_rows=4, use_graphs=False,
+                       host_cache_bytes=64 * eng.kv.bytes_per_page())
+    assert be.tier is not None
+    sched = Scheduler(be, max_active=1)
+
+    def serve(prompt, n):
+        r = Request(prompt=list(prompt), max_tokens=n, speculation=False, record_rows=True)
+        sched.submit(r)
+        toks, usage, hashes = [], None, None
+        for _ in range(600):
+            sched.step()
+            while not r.events.empty():
+                ev = r.events.get()
+                if ev[0] == "tokens":
+                    toks += ev[1]
+                elif ev[0] == "done":
+                    usage, hashes = ev[2], ev[3]
+                else:
+                    raise AssertionError(ev)
+            if usage is not None:
+                break
+        assert usage is not None
+        return toks, usage, hashes
+
+    g = torch.Generator().manual_seed(31)
+    prompt = torch.randint(0, cfg.vocab_size, (600,), generator=g).tolist()
+    cold = serve(prompt, 6)
+    dev_hit = serve(prompt, 6)
+    assert dev_hit[1]["cached_tokens"] >= 512 and dev_hit[0] == cold[0]
+    for _ in range(4):
+        serve(torch.randint(0, cfg.vocab_size, (600,), generator=g).tolist(), 2)
+    assert be.prefix.stats.spilled >= 1 and be.tier.host.stats.stored >= 1
+    host_hit = serve(prompt, 6)
+    torch.cuda.synchronize()
+    assert K.read_status() == 0
+    assert be.prefix.stats.restored >= 1 and host_hit[1]["cached_tokens"] >= 512
+    assert host_hit[0] == dev_hit[0] and host_hit[2] == dev_hit[2]
+    be.tier.host.check_invariants()

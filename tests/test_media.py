@@ -219,6 +219,32 @@ def test_remote_encoder_gives_the_same_rows():
         remote.encode_image(_png(30, 30, 6))
 
 
+def test_encoder_service_rejects_frames_whose_header_lies():
+    """A header whose shape / dtype do not describe the body gets an error reply (nothing is allocated from it) and
+    the connection keeps serving; an unknown dtype likewise."""
+    import json
+    import socket
+    import struct
+    from cuteafd_b200.media.remote import EncoderServer, _read
+    vision, audio = _towers(32)
+    srv = EncoderServer(vision, audio).start()
+    try:
+        with socket.create_connection(("127.0.0.1", srv.port), timeout=5) as c:
+            def frame(header: dict, body: bytes = b""):
+                h = json.dumps(dict(header, bytes=len(body))).encode()
+                c.sendall(struct.pack(">I", len(h)) + h + body)
+                return _read(c)[0]
+            huge = frame({"op": "audio", "shape": [1 << 40, 1 << 20], "dtype": "float32"})      # no body at all
+            assert huge["ok"] is False and "malformed" in huge["error"]
+            short = frame({"op": "audio", "shape": [4, 4], "dtype": "float32"}, b"\0" * 12)
+            assert short["ok"] is False and "malformed" in short["error"]
+            odd = frame({"op": "audio", "shape": [3], "dtype": "complex999"}, b"\0" * 12)
+            assert odd["ok"] is False
+            assert frame({"op": "hello"})["ok"] is True                                          # still in step
+    finally:
+        srv.stop()
+
+
 def test_encoderd_process_and_serve_flag(tmp_path):
     import subprocess
     import sys

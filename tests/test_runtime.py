@@ -242,6 +242,7 @@ def test_scheduler_failure_quarantine_and_limits(oracle):
     assert out[2]["error"][0] == FAIL_RETRY                        # third request: queue full -> retry class
     assert all(o["error"] and o["error"][0] == FAIL_WORKER for o in out[:2])
     assert s.stats.failed == 2 and s.reserve.leased == 0
+    assert s.stats.quarantined == 2 and len(be.quarantined) == 2   # a failed device step: pages kept out of the pool
     ok = _run(s, [Request([1, 2, 3], max_tokens=4)])[0]            # the scheduler keeps serving
     assert ok["finish"] == "length"
     bad = _run(s, [Request([], max_tokens=4)])[0]
@@ -250,6 +251,48 @@ def test_scheduler_failure_quarantine_and_limits(oracle):
     tiny = Scheduler(OracleBackend(cfg, params, total_pages=4))
     big = _run(tiny, [Request([1] * 600, max_tokens=8)])[0]
     assert big["error"][0] == FAIL_RETRY
+
+
+def test_prefix_cache_gives_pages_back_under_admission_pressure(oracle):
+    """A warm cache never turns an admitted request into a failure: snapshots are evicted when the allocator runs
+    dry, and a snapshot that exceeds the cache budget is not retained at all."""
+    cfg, params = oracle
+    be = OracleBackend(cfg, params, total_pages=16)
+    s = Scheduler(be, max_active=1)
+    g = torch.Generator().manual_seed(9)
+    for _ in range(5):                                             # fills the cache's half of the pool with snapshots
+        out = _run(s, [Request(torch.randint(0, cfg.vocab_size, (128,), generator=g).tolist(), max_tokens=2)])[0]
+        assert out["finish"] == "length"
+    held = be.prefix.held_pages
+    assert held > 0 and held <= be.prefix.max_pages
+    big = _run(s, [Request(torch.randint(0, cfg.vocab_size, (640,), generator=g).tolist(), max_tokens=2)])[0]
+    assert big.get("error") is None and big["finish"] == "length"  # 10 pages + decode: needs the cache's pages
+    assert be.prefix.stats.evicted >= 1 and s.stats.failed == 0
+    assert be.prefix.held_pages <= be.prefix.max_pages
+    assert s.reserve.total == 15                                   # the reserved zero page is not leasable
+
+
+def test_host_tier_restores_an_evicted_snapshot_exactly(oracle):
+    """Evicted snapshots go to the host tier; a later request for the same prompt is served from there with the same
+    tokens and the same logit row hashes as when the device tier served it."""
+    cfg, params = oracle
+    be = OracleBackend(cfg, params, total_pages=40, host_slots=64)
+    assert be.tier is not None and be.prefix.spill is not None
+    s = Scheduler(be, max_active=1)
+    g = torch.Generator().manual_seed(21)
+    prompt = torch.randint(0, cfg.vocab_size, (600,), generator=g).tolist()             # >= 512 tokens: worth storing
+    cold = _run(s, [Request(prompt, max_tokens=6, record_rows=True, speculation=False)])[0]
+    first = _run(s, [Request(prompt, max_tokens=6, record_rows=True, speculation=False)])[0]   # from the device tier
+    assert first["usage"]["cached_tokens"] >= 512 and first["tokens"] == cold["tokens"]
+    for _ in range(4):                                                                   # other traffic evicts it
+        _run(s, [Request(torch.randint(0, cfg.vocab_size, (600,), generator=g).tolist(), max_tokens=2)])
+    assert be.prefix.stats.spilled >= 1 and be.tier.host.stats.stored >= 1
+    assert not any(sn.tokens[:600] == tuple(prompt) for sn in be.prefix.snapshots.values())
+    again = _run(s, [Request(prompt, max_tokens=6, record_rows=True, speculation=False)])[0]
+    assert be.prefix.stats.restored >= 1 and be.tier.host.stats.restored >= 1
+    assert again["usage"]["cached_tokens"] >= 512
+    assert again["tokens"] == first["tokens"] and again["row_hashes"] == first["row_hashes"]
+    be.tier.host.check_invariants()
 
 
 def test_scheduler_thread_and_cancel(oracle):

@@ -66,7 +66,27 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
         # NCCL + cuBLAS twin agrees too
         hb, zb = ctx.baseline_block(a_local, wr, res[lo:lo + R_].to(dev) if own == R_ else torch.cat([res[lo:lo + own], res.new_zeros(R_ - own, H)]).to(dev), nwd, 1e-6, wc)
         torch.cuda.synchronize()
-    torch.save({"errs": errs}, os.path.join(out_dir, f"r{rank}.pt"))
+    # A round whose producers never arrive: the reduce kernel's bounded wait runs out on every rank (a flag nothing sets),
+    # the status word says so, the arrival counter is back at zero, no gather flag was raised, and a good round
+    # afterwards completes.
+    K.set_wait_limit_ns(50_000_000)
+    ctx.step()
+    ctx.reduce_norm_gather(T, nwd, 1e-6)
+    torch.cuda.synchronize()
+    timed_out = K.read_status()
+    counter_after = int(ctx.done[1].item())
+    K.set_wait_limit_ns(2_000_000_000)
+    dist.barrier()
+    ctx.step()
+    ctx.row_parallel_linear(a_local, wr)
+    ctx.reduce_norm_gather(T, nwd, 1e-6)
+    z2 = torch.empty(T, N2, dtype=torch.bfloat16, device=dev)
+    ctx.column_parallel_linear(T, wc, z2)
+    torch.cuda.synchronize()
+    dist.barrier()
+    good_after = K.read_status() == 0 and bool(torch.isfinite(z2.float()).all())
+    torch.save({"errs": errs, "timed_out": timed_out, "counter_after": counter_after, "good_after": good_after},
+               os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -78,5 +98,6 @@ def test_tp_block_matches_reference(world, tmp_path):
     import torch.multiprocessing as mp
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
-        errs = torch.load(str(tmp_path / f"r{r}.pt"))["errs"]
-        assert max(errs) < 0.03, (r, errs)
+        rec = torch.load(str(tmp_path / f"r{r}.pt"))
+        assert max(rec["errs"]) < 0.03, (r, rec["errs"])
+        assert rec["timed_out"] != 0 and rec["counter_after"] == 0 and rec["good_after"], (r, rec)
