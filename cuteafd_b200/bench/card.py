@@ -129,43 +129,81 @@ def e2e_decode_loop(gen: Generator, seqs, last_tokens: list[int], steps: int, wa
 
 
 def run_card(gen: Generator, prompts: list[list[int]], levels: tuple[int, ...], steps: int, warmup: int,
-             sync=None, log=print) -> CardResult:
-    """``prompts``: one distinct prompt per stream of the widest level."""
+             sync=None, log=print, replica: int = 0, n_replicas: int = 1) -> CardResult:
+    """``prompts``: one distinct prompt per stream of the widest level.
+
+    With ``n_replicas`` data-parallel attention replicas every replica runs this same script: prompt / stream i belongs
+    to replica i % n_replicas, replica 0 announces each round's token counts for everybody, and a replica without work
+    in a round waits for the round to close.  Decode throughput counts the streams of all replicas over the slowest
+    rank's device time; prefill throughput counts the prompts that were prefilled side by side."""
     res = CardResult()
     table = gen.table
+    eng = gen.engine
+    A, a = n_replicas, replica
+    dp = A > 1
+
+    def peers(counts_of) -> None:
+        if dp and a == 0:
+            eng.peer_counts = [counts_of(j) for j in range(1, A)]
+
+    def close(active: bool) -> None:
+        if dp:
+            eng.end_round(active)
+
     # ---- cold 8K prefill + TTFT: one untimed warm prompt, then every stream's prompt timed ----------
+    peers(lambda j: len(prompts[0]))
     warm = table.new()
     gen.prefill(warm, prompts[0])
     table.free(warm)
     torch.cuda.synchronize()
-    base, first = [], []
-    for p in prompts:
-        s = table.new()
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        nxt = gen.prefill(s, p)              # returns after the first token reached the host
-        dt = time.perf_counter() - t0
-        res.prefill_ms.append(dt * 1e3)
-        base.append(s)
-        first.append(nxt)
+    close(True)
+    base: dict[int, object] = {}
+    first: dict[int, int] = {}
+    rounds = -(-len(prompts) // A)
+    side_by_side = []
+    for r in range(rounds):
+        idx = r * A + a
+        active = idx < len(prompts)
+        peers(lambda j: len(prompts[r * A + j]) if r * A + j < len(prompts) else 0)
+        if active:
+            s = table.new()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            nxt = gen.prefill(s, prompts[idx])              # returns after the first token reached the host
+            dt = time.perf_counter() - t0
+            res.prefill_ms.append(dt * 1e3)
+            base[idx], first[idx] = s, nxt
+            side_by_side.append(min(A, len(prompts) - r * A))
+        close(active)
     res.ttft_s = sorted(res.prefill_ms)[len(res.prefill_ms) // 2] / 1e3
-    res.prefill_tok_s = len(prompts[0]) / res.ttft_s
-    log(f"prefill: {res.prefill_tok_s:.0f} tok/s, TTFT {res.ttft_s*1e3:.1f} ms (median of {len(prompts)})")
+    res.prefill_tok_s = len(prompts[0]) * (sorted(side_by_side)[len(side_by_side) // 2]) / res.ttft_s
+    log(f"prefill: {res.prefill_tok_s:.0f} tok/s, TTFT {res.ttft_s*1e3:.1f} ms (median of {len(res.prefill_ms)}"
+        + (f", {A} prompts side by side" if dp else "") + ")")
     # ---- decode levels --------------------------------------------------------------------------------
     for c in levels:
-        seqs = [table.fork(base[i]) for i in range(c)]
-        ms, launches = device_decode_loop(gen, seqs, first[:c], steps, warmup, sync)
-        for s in seqs:
-            table.free(s)
-        seqs = [table.fork(base[i]) for i in range(c)]
-        e_ms, h2d, d2h = e2e_decode_loop(gen, seqs, first[:c], steps, warmup, sync)
-        for s in seqs:
-            table.free(s)
+        mine = [i for i in range(c) if i % A == a]
+        peers(lambda j: len([i for i in range(c) if i % A == j]))
+        ms, launches = 0.0, 0
+        if mine:
+            seqs = [table.fork(base[i]) for i in mine]
+            ms, launches = device_decode_loop(gen, seqs, [first[i] for i in mine], steps, warmup, sync)
+            for s in seqs:
+                table.free(s)
+        close(bool(mine))
+        e_ms, h2d, d2h = 0.0, 0, 0
+        if mine:
+            seqs = [table.fork(base[i]) for i in mine]
+            e_ms, h2d, d2h = e2e_decode_loop(gen, seqs, [first[i] for i in mine], steps, warmup, sync)
+            for s in seqs:
+                table.free(s)
+        close(bool(mine))
+        if not mine:
+            continue
         r = DecodeResult(c, steps, ms / steps, c * steps / (ms / 1e3), e_ms / steps, c * steps / (e_ms / 1e3),
                          launches, h2d, d2h)
         res.decode[c] = r
         log(f"decode C{c}: device {r.ms_per_step:.3f} ms/step {r.tok_s:.1f} tok/s | e2e {r.e2e_ms_per_step:.3f} ms/step "
             f"{r.e2e_tok_s:.1f} tok/s | {launches} launches/step")
-    for s in base:
+    for s in base.values():
         table.free(s)
     return res

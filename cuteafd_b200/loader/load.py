@@ -76,6 +76,81 @@ def load_params(path: str, dtype: torch.dtype = torch.float32, device: str = "cp
     return snap.cfg, out
 
 
+STORED_EXPERT_FORMATS = {"fp8_block128": "fp8", "mxfp4": "mxfp4", "nvfp4": "nvfp4"}
+
+
+def expert_storage_format(snap: OpenedSnapshot) -> str:
+    """How the routed experts of a snapshot are served: "fp8" (E4M3 + 128x128 scales), "mxfp4", "nvfp4" keep the stored
+    bytes; everything else (bf16 / f16 / f32, EXL3 trellis) is decoded to bf16 on load."""
+    for pre, op in snap.operands.items():
+        if ".mlp.experts." in pre:
+            return STORED_EXPERT_FORMATS.get(op.format, "bf16")
+    return "bf16"
+
+
+def load_experts_as_stored(snap: OpenedSnapshot, lo: int, hi: int, device: torch.device) -> tuple[str, list[tuple]]:
+    """Routed experts [lo, hi) of every MoE layer in the form the grouped GEMMs read, with the checkpoint's bytes
+    untouched: no dequantisation and no re-encoding, only the per-expert tensors stacked along a new first dimension
+    (what the reference calls slicing the stored tensors per rank: rust/crates/cuteafd-loader/src/formats/
+    fp8_experts.rs:8-33,80-86).  Returns (format, [(gate, up, down) per MoE layer]) where each of the three is
+
+      bf16    tensor [n, N, K]
+      fp8     (E4M3 [n, N, K], fp32 block scales [n, N/128, K/128])           scales multiply, whatever their name
+      mxfp4   (packed uint8 [n, N, K/2], UE8M0 uint8 [n, N, K/32], None)
+      nvfp4   (packed uint8 [n, N, K/2], E4M3 scales as bytes [n, N, K/16], fp32 global multipliers [n])
+    """
+    cfg, cat, ops = snap.cfg, snap.catalog, snap.operands
+    fmt = expert_storage_format(snap)
+    out = []
+    for i in range(cfg.num_layers + cfg.mtp_layers):
+        if not (cfg.is_moe_layer(i) if i < cfg.num_layers else cfg.num_experts > 0):
+            continue
+        trio = []
+        for proj in ("gate_proj", "up_proj", "down_proj"):
+            names = [f"model.layers.{i}.mlp.experts.{e}.{proj}" for e in range(lo, hi)]
+            if names[0] not in ops:
+                trio = []
+                break
+            for nme in names:
+                got = STORED_EXPERT_FORMATS.get(ops[nme].format, "bf16")
+                if got != fmt:
+                    raise ValueError(f"{nme}: stored as {ops[nme].format}, the layer's other experts as {fmt}")
+            if fmt == "bf16":
+                trio.append(torch.stack([formats.dequantize(ops[nme], cat).to(torch.bfloat16) for nme in names]).to(device).contiguous())
+                continue
+            # stacked as raw bytes (one copy per tensor, no arithmetic), then viewed back in the stored dtype
+            first = cat.read(ops[names[0]].weight)
+            payload = torch.stack([cat.read(ops[nme].weight).view(torch.uint8) for nme in names]).to(device).contiguous()
+            scales = torch.stack([cat.read(ops[nme].scale_tensor) for nme in names])
+            if fmt == "fp8":
+                payload = payload.view(first.dtype)
+                if ops[names[0]].block_scale is None or ops[names[0]].block_scale.rows != 128 or ops[names[0]].block_scale.cols != 128:
+                    raise ValueError(f"{names[0]}: E4M3 experts need 128x128 block scales")
+                trio.append((payload, scales.float().to(device).contiguous()))
+            elif fmt == "mxfp4":
+                trio.append((payload, scales.view(torch.uint8).to(device).contiguous(), None))
+            else:
+                glob = torch.cat([cat.read(ops[nme].global_scale).float().reshape(1) if ops[nme].global_scale else torch.ones(1)
+                                  for nme in names])
+                trio.append((payload, scales.view(torch.uint8).to(device).contiguous(), glob.to(device).contiguous()))
+        if trio:
+            out.append(tuple(trio))
+    return fmt, out
+
+
+def attach_stored_experts(W, snap: OpenedSnapshot, device: torch.device) -> str:
+    """Give an engine weight set (built without experts) its routed experts in their stored form.  Sets
+    ``W.expert_format`` and each MoE layer's ``w_gate / w_up / w_down``."""
+    cfg = snap.cfg
+    fmt, stacks = load_experts_as_stored(snap, 0, cfg.num_experts, device)
+    it = iter(stacks)
+    for i, L in enumerate(W.layers):
+        if L.router is not None:
+            L.w_gate, L.w_up, L.w_down = next(it)
+    W.expert_format = fmt
+    return fmt
+
+
 def load_gqa_engine_weights(path: str, device: torch.device, with_experts: bool = True,
                             expert_range: tuple[int, int] | None = None, reserve_bytes: int = 0):
     """Device weights for ``GqaMoeEngine`` straight from a snapshot (bf16 compute form), in one weight arena.
@@ -171,13 +246,23 @@ def load_engine(path: str, device: torch.device, num_pages: int, max_tokens: int
         if want == "fp8_ds_mla" and not cfg.indexer_heads:
             raise ValueError("fp8_ds_mla records need the sparse attention path (a checkpoint with an indexer)")
         cfg = cfg.replace(kv_format=want)
+    stored = expert_storage_format(snap) if cfg.num_experts else "bf16"
     if cfg.is_mla:
         from ..models.mla_moe import LatentCache, MlaMoeEngine, MlaMoeWeights
-        _, params = load_params(path, dtype=torch.bfloat16)
-        W = MlaMoeWeights.from_params(cfg, params, device)
+        if stored != "bf16":             # quantised experts stay as stored; the rest of the model is decoded to bf16
+            _, params = load_params(path, dtype=torch.bfloat16, exclude=".mlp.experts.")
+            W = MlaMoeWeights.from_params(cfg, params, device, with_experts=False)
+            attach_stored_experts(W, snap, device)
+        else:
+            _, params = load_params(path, dtype=torch.bfloat16)
+            W = MlaMoeWeights.from_params(cfg, params, device)
         return cfg, MlaMoeEngine(cfg, W, LatentCache(cfg, num_pages, device), max_tokens=max_tokens, max_seqs=max_seqs)
     from ..models.gqa_moe import GqaMoeEngine, GqaMoeWeights, KvCache
-    if cfg.mtp_layers:
+    if stored != "bf16":
+        _, params = load_params(path, dtype=torch.bfloat16, exclude=".mlp.experts.")
+        W = GqaMoeWeights.from_params(cfg, params, device, with_experts=False)
+        attach_stored_experts(W, snap, device)
+    elif cfg.mtp_layers:
         _, params = load_params(path, dtype=torch.bfloat16)
         W = GqaMoeWeights.from_params(cfg, params, device)
     else:

@@ -240,7 +240,8 @@ class GqaMoeEngine:
             self._fused_checked = True
             from ..ops.decode_step import FusedDecodeStep
             if (type(self) is GqaMoeEngine and isinstance(self.moe, LocalExchange) and FusedDecodeStep.supports(self.cfg)
-                    and self.W.layers[0].w_gate is not None and self.device.type == "cuda"):
+                    and self.W.layers[0].w_gate is not None and getattr(self.W, "expert_format", "bf16") == "bf16"
+                    and self.device.type == "cuda"):
                 self.fused = FusedDecodeStep(self)
         if self.fused is None or b.tokens.shape[0] > self.fused.MAX_ROWS or b.page_table.shape[0] != b.tokens.shape[0]:
             return None
@@ -315,6 +316,13 @@ class GqaMoeEngine:
         kw = dict(self.route_kw, bias=L.router_bias)
         if self.pre_moe is not None:
             self.pre_moe(i)
+        fmt = getattr(self.W, "expert_format", "bf16")
+        if fmt != "bf16" and hasattr(self.moe, "forward_stored"):
+            # experts served in their stored form (E4M3 block-scaled / MXFP4 / NVFP4): same exchange, quantised GEMMs
+            self.moe.forward_stored(fmt, ws.x[:T], logits, kw, L.w_gate, L.w_up, L.w_down, ws.h[:T], shared=shared,
+                                    residual=ws.h[:T])
+            self.launches += 6
+            return False
         self.moe.forward(ws.x[:T], logits, kw, L.w_gate, L.w_up, L.w_down, ws.h[:T], shared=shared, residual=ws.h[:T],
                          norm_w=next_norm, eps=cfg.rms_eps, x_out=ws.x[:T] if next_norm is not None else None)
         self.launches += 4 if T * cfg.top_k <= 512 else 5      # plan(+dispatch), fc1, fc2, combine

@@ -167,6 +167,25 @@ class ExpertSide:
                             signal_flag=combine_flag_ptr, done_counter=self.done[0:1] if combine_flag_ptr else None)
 
 
+    def run_w4_any(self, fmt: str, w_gate, w_up, w_down, tile_rows: int, layer: int, epoch: torch.Tensor, combine_ptr: int,
+                   combine_flag_ptr: int | None, reuse_dequant: bool = False, wait: bool = True) -> None:
+        """MXFP4 / NVFP4 experts at any step size: decode-sized tiles read the packed weights directly; prefill-sized
+        steps expand this layer's experts to bf16 once (one layer's worth of scratch, shared by all layers) and take
+        the bf16 grouped GEMMs."""
+        if tile_rows <= 64:
+            return self.run_w4(fmt, w_gate, w_up, w_down, tile_rows, layer, epoch, combine_ptr, combine_flag_ptr, wait=wait)
+        dev = w_gate[0].device
+        shapes = [(*w[0].shape[:-1], w[0].shape[-1] * 2) for w in (w_gate, w_up, w_down)]
+        dq = ExpertSide._dq_scratch.get(dev)
+        if dq is None or [tuple(t.shape) for t in dq] != [tuple(sh) for sh in shapes]:
+            dq = tuple(torch.empty(sh, dtype=torch.bfloat16, device=dev) for sh in shapes)
+            ExpertSide._dq_scratch[dev] = dq
+        if not reuse_dequant:
+            for w, o in zip((w_gate, w_up, w_down), dq):
+                K.w4_dequant(w, fmt, out=o)
+        self.run(dq[0], dq[1], dq[2], tile_rows, layer, epoch, combine_ptr, combine_flag_ptr, wait)
+
+
 class AttentionSide:
     """Buffers the attention rank owns: routes, plan output, the combine buffer and its flags."""
 
@@ -295,3 +314,21 @@ def _forward_w4(self, fmt: str, x: torch.Tensor, logits: torch.Tensor, route_kw:
 
 
 LocalExchange.forward_w4 = _forward_w4
+
+
+def _forward_stored(self, fmt: str, x, logits, route_kw, w_gate, w_up, w_down, out, *, shared=None, residual=None, norm_w=None,
+                    eps: float = 0.0, x_out=None):
+    """One entry for every expert storage format ("bf16", "fp8", "mxfp4", "nvfp4"); the quantised forms do not fuse the
+    next layer's norm into the combine, so the caller norms separately (returns whether ``x_out`` was written)."""
+    if fmt == "bf16":
+        self.forward(x, logits, route_kw, w_gate, w_up, w_down, out, shared=shared, residual=residual, norm_w=norm_w, eps=eps,
+                     x_out=x_out)
+        return norm_w is not None
+    if fmt == "fp8":
+        self.forward_fp8(x, logits, route_kw, w_gate, w_up, w_down, out, shared=shared, residual=residual)
+    else:
+        self.forward_w4(fmt, x, logits, route_kw, w_gate, w_up, w_down, out, shared=shared, residual=residual)
+    return False
+
+
+LocalExchange.forward_stored = _forward_stored

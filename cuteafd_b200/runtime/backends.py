@@ -369,7 +369,9 @@ class EngineBackend:
         if self.use_graphs and key in self.graphs:
             g, out = self.graphs.pop(key)
             self.graphs[key] = (g, out)                       # most recently used last
-            if hasattr(self.engine, "announce"):
+            if hasattr(self.engine, "take_replay"):
+                self.engine.take_replay(key[1])
+            elif hasattr(self.engine, "announce"):
                 self.engine.announce(key[1], 1, for_replay=True)
             g.replay()
             self.graph_stats["replays"] += 1

@@ -129,7 +129,9 @@ class Generator:
                     self.decode_bufs.pop(old, None)
             g, out = self.graphs.pop(S)
             self.graphs[S] = (g, out)          # most recently used last
-            if hasattr(self.engine, "announce"):
+            if hasattr(self.engine, "take_replay"):
+                self.engine.take_replay(S)
+            elif hasattr(self.engine, "announce"):
                 self.engine.announce(S, 1, for_replay=True)
             g.replay()
         else:

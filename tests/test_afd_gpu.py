@@ -1,7 +1,10 @@
-"""Attention rank + expert ranks over NVLink peer memory against the CPU oracle (2+ GPUs).
+"""Attention ranks + expert ranks over NVLink peer memory against the CPU oracle (2+ GPUs).
 
 Runs as child processes, one per GPU, over NCCL for the control messages; the activations move
-through the fused dispatch / combine kernels only.
+through the fused dispatch / combine kernels only.  Modes: one attention rank with dense (bf16)
+weights; two data-parallel attention replicas in front of the same expert ranks; experts loaded
+from a snapshot in their stored format (E4M3 block-scaled, MXFP4, NVFP4) against the oracle
+decoding the same snapshot; the MTP depth on the split deployment.
 """
 import os
 import socket
@@ -18,9 +21,14 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, out_path: str) -> None:
+def _rel(got: torch.Tensor, want: torch.Tensor) -> float:
+    return (got.float().cpu() - want).abs().max().item() / max(want.abs().max().item(), 1.0)
+
+
+def _worker(rank: int, world: int, port: int, out_dir: str, mode: str, snap_dir: str) -> None:
     import torch.distributed as dist
 
+    from cuteafd_b200.models.gqa_moe import Batch
     from cuteafd_b200.ops import kernels as K
     from cuteafd_b200.parallel.afd import build_afd
     from cuteafd_b200.ref.model import KvState, RefDecoder, init_weights
@@ -31,48 +39,106 @@ def _worker(rank: int, world: int, port: int, out_path: str) -> None:
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     cfg = small_cfg()
-    params = {k: v.to(torch.bfloat16).float() for k, v in init_weights(cfg, seed=0).items()}
-    h = build_afd(cfg, dev, rank, world, max_tokens=256, max_seqs=4, num_pages=64, pages_per_seq=8,
-                  use_graphs=True, params=params)
-    result = {"ok": True, "errs": []}
+    A = 2 if mode == "dp2" else 1
+    kw = dict(max_tokens=256, max_seqs=4, num_pages=64, pages_per_seq=8, use_graphs=True, n_attention=A)
+    if mode in ("fp8_block128", "mxfp4", "nvfp4"):
+        from cuteafd_b200.loader.load import load_params
+        cfg, params = load_params(snap_dir)                   # the oracle decodes the same snapshot the ranks load as stored
+        h = build_afd(cfg, dev, rank, world, snapshot=snap_dir, **kw)
+    else:
+        if mode == "mtp":
+            cfg = cfg.replace(mtp_layers=1)
+        params = {k: v.to(torch.bfloat16).float() for k, v in init_weights(cfg, seed=0).items()}
+        h = build_afd(cfg, dev, rank, world, params=params, **kw)
+    result = {"errs": [], "mode": mode}
     if h.worker is not None:
+        if mode in ("fp8_block128", "mxfp4", "nvfp4"):
+            want = {"fp8_block128": "fp8"}.get(mode, mode)
+            assert h.worker.format == want, (h.worker.format, want)
+            first = h.worker.weights[0][0]
+            assert isinstance(first, tuple) and first[0].dtype in (torch.float8_e4m3fn, torch.uint8)    # stored bytes, not bf16
         h.worker.serve()
     else:
-        gen, ref = h.generator, RefDecoder(cfg, params)
+        gen, eng, ref = h.generator, h.generator.engine, RefDecoder(cfg, params)
+        a = h.replica
         g = torch.Generator().manual_seed(1)
-        prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g) for n in (200, 77)]
+        prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g) for n in (200, 200, 77)]
+        # round 1: every replica prefills a 200-token prompt of its own; round 2: replica 0 alone prefills 77 tokens
+        mine = [prompts[a]] + ([prompts[2]] if a == 0 else [])
         seqs, last, kvs = [], [], []
         with torch.no_grad():
-            for p in prompts:
-                s = gen.table.new()
-                gen.prefill(s, p.tolist())
-                kv = KvState(cfg)
-                rl = ref.forward(p, kv)[-1]
-                err = (gen.engine.logits[0].float().cpu() - rl).abs().max().item() / max(rl.abs().max().item(), 1.0)
-                result["errs"].append(err)
-                seqs.append(s); kvs.append(kv); last.append(int(rl.argmax()))
-            for _ in range(4):
-                gen.decode(seqs, last)
-                torch.cuda.synchronize()
-                for i in range(len(seqs)):
-                    rl = ref.forward(torch.tensor([last[i]]), kvs[i])[-1]
-                    err = (gen.engine.logits[i].float().cpu() - rl).abs().max().item() / max(rl.abs().max().item(), 1.0)
-                    result["errs"].append(err)
-                    last[i] = int(rl.argmax())
+            for r, p in enumerate(mine + ([None] if a else [])):
+                if a == 0 and A > 1:
+                    eng.peer_counts = None if r == 0 else [0] * (A - 1)
+                if p is not None:
+                    s = gen.table.new()
+                    gen.prefill(s, p.tolist())
+                    kv = KvState(cfg)
+                    rl = ref.forward(p, kv)[-1]
+                    result["errs"].append(_rel(eng.logits[0], rl))
+                    seqs.append(s); kvs.append(kv); last.append(int(rl.argmax()))
+                if A > 1:
+                    eng.end_round(active=p is not None)
+            if mode == "mtp":
+                # the MTP depth on the split deployment: after a prompt chunk (every row) and after a decode step, as in
+                # the single-GPU test; its decoder layer's experts live on the expert rank
+                p, s, n = mine[0], seqs[0], len(mine[0])
+                first = last[0]
+                b = gen.prefill_buf
+                batch = Batch(b.tokens[1][:n], b.positions[1][:n], b.slots[1][:n], b.page_table[1].view(1, gen.max_pages),
+                              b.seq_lens[1][:1], b.q_start[1][:2], n, True, None)
+                nxt = torch.cat([p[1:], torch.tensor([first])])
+                got = eng.mtp_forward(0, batch, nxt.to(torch.int32).to(dev)).float().cpu()
+                kvs2 = KvState(cfg)
+                hid = ref.hidden_states(p, kvs2)
+                want, _ = ref.mtp_forward(0, hid, nxt, torch.arange(n), kvs2)
+                rows = sorted(_rel(got[r], want[r]) for r in range(n))
+                result["errs"] = [rows[n // 2], rows[int(n * 0.9)] / 2]           # median and 90th percentile (the latter halved: bound 0.1)
+                tok2 = gen.decode([s], [first])[0]
+                d = gen.decode_bufs[1]
+                db = Batch(d.tokens[1][:1], d.positions[1][:1], d.slots[1][:1], d.page_table[1].view(1, gen.max_pages),
+                           d.seq_lens[1][:1], d.q_start[1][:2], 1, False, None)
+                got2 = eng.mtp_forward(0, db, torch.tensor([tok2], dtype=torch.int32, device=dev)).float().cpu()
+                h2 = ref.hidden_states(torch.tensor([first]), kvs2)
+                want2, _ = ref.mtp_forward(0, h2, torch.tensor([tok2]), torch.tensor([n]), kvs2)
+                result["errs"].append(_rel(got2[0], want2[0]) / 2)
+            else:
+                if a == 0 and A > 1:
+                    eng.peer_counts = [1] * (A - 1)            # replica 0 decodes two sequences, the others one
+                for _ in range(4):
+                    gen.decode(seqs, last)
+                    torch.cuda.synchronize()
+                    for i in range(len(seqs)):
+                        rl = ref.forward(torch.tensor([last[i]]), kvs[i])[-1]
+                        result["errs"].append(_rel(eng.logits[i], rl))
+                        last[i] = int(rl.argmax())
+                if A > 1:
+                    eng.end_round()
         result["status"] = K.read_status()
-        h.shutdown()
-        torch.save(result, out_path)
+        if a == 0:
+            h.shutdown()
+        else:
+            eng.ctrl.zero_()
+            dist.broadcast(eng.ctrl, src=0)                   # the stop message
+        torch.save(result, os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_afd_matches_oracle(world, tmp_path):
+@pytest.mark.parametrize("world,mode", [(2, "plain"), (4, "plain"), (4, "dp2"), (2, "fp8_block128"), (2, "mxfp4"), (2, "nvfp4"),
+                                        (2, "mtp")])
+def test_afd_matches_oracle(world, mode, tmp_path):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
-    out = str(tmp_path / "afd.pt")
-    mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
-    r = torch.load(out)
-    assert r["status"] == 0
-    assert max(r["errs"]) < 0.05, r["errs"]
+    snap = ""
+    if mode in ("fp8_block128", "mxfp4", "nvfp4"):
+        from cuteafd_b200.loader.snapshot import write_random_snapshot
+        from tests.test_engine_gpu import small_cfg
+        snap = write_random_snapshot(small_cfg(), str(tmp_path / "snap"), fmt=mode, seed=3)
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), mode, snap), nprocs=world, join=True)
+    replicas = 2 if mode == "dp2" else 1
+    for a in range(replicas):
+        r = torch.load(str(tmp_path / f"r{a}.pt"))
+        assert r["status"] == 0, r
+        assert len(r["errs"]) >= 2 and max(r["errs"]) < 0.05, r["errs"]

@@ -297,3 +297,42 @@ def test_host_tier_evict_and_restore_on_the_engine():
     assert be.prefix.stats.restored >= 1 and host_hit[1]["cached_tokens"] >= 512
     assert host_hit[0] == dev_hit[0] and host_hit[2] == dev_hit[2]
     be.tier.host.check_invariants()
+
+
+@pytest.mark.parametrize("fmt", ["fp8_block128", "mxfp4", "nvfp4"])
+def test_snapshot_served_in_its_stored_format(fmt, tmp_path):
+    """A random snapshot whose routed experts are E4M3 block-scaled / MXFP4 / NVFP4 is loaded without decoding them
+    (the engine holds the stored bytes) and its logits match the oracle that decodes the same snapshot."""
+    from cuteafd_b200.loader.load import load_engine, load_params
+    from cuteafd_b200.loader.snapshot import write_random_snapshot
+    from cuteafd_b200.ops import kernels as K
+    from cuteafd_b200.ref.model import KvState, RefDecoder
+    from cuteafd_b200.runtime.generate import Generator
+    from cuteafd_b200.runtime.paged import PagePool
+    path = write_random_snapshot(small_cfg(), str(tmp_path / "snap"), fmt=fmt, seed=5)
+    dev = torch.device("cuda:0")
+    cfg, eng = load_engine(path, dev, 64, 256, 8)
+    assert eng.W.expert_format == {"fp8_block128": "fp8"}.get(fmt, fmt)
+    stored = eng.W.layers[1].w_gate
+    assert isinstance(stored, tuple) and stored[0].dtype in (torch.float8_e4m3fn, torch.uint8)
+    _, params = load_params(path)
+    ref = RefDecoder(cfg, params)
+    gen = Generator(eng, PagePool(64), max_pages_per_seq=8, max_seqs=8, prefill_chunk=128, use_graphs=False)
+    g = torch.Generator().manual_seed(2)
+    p = torch.randint(0, cfg.vocab_size, (150,), generator=g)
+    errs = []
+    with torch.no_grad():
+        s = gen.table.new()
+        gen.prefill(s, p.tolist())
+        kvs = KvState(cfg)
+        rl = ref.forward(p, kvs)[-1]
+        errs.append((eng.logits[0].float().cpu() - rl).abs().max().item() / max(rl.abs().max().item(), 1.0))
+        last = int(rl.argmax())
+        for _ in range(3):
+            gen.decode([s], [last])
+            rl = ref.forward(torch.tensor([last]), kvs)[-1]
+            errs.append((eng.logits[0].float().cpu() - rl).abs().max().item() / max(rl.abs().max().item(), 1.0))
+            last = int(rl.argmax())
+    torch.cuda.synchronize()
+    assert K.read_status() == 0
+    assert max(errs) < 0.06, errs
