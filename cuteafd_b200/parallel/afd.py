@@ -36,7 +36,7 @@ import torch.distributed as dist
 from .._native import lib as _n
 from ..config import ModelConfig
 from ..ops import kernels as K
-from .moe_exchange import AttentionSide, ExchangeGeometry, ExpertSide, pick_tile_rows
+from .moe_exchange import AttentionSide, ExchangeGeometry, ExpertSide, pick_tile_rows, plan_tile_rows
 
 OP_STOP, OP_STEPS, OP_TIMED, OP_SYNC = 0, 1, 2, 3
 
@@ -110,6 +110,7 @@ class RemoteExchange:
         dev = heap.buf.device
         self.geo, self.heap, self.lay = geo, heap, lay
         self.source, self.n_sources = source, n_sources
+        self.expert_format = "bf16"              # how the expert ranks hold their weights: decides the row tile of a plan
         rg, n = geo.region(), geo.regions
         self.combine = heap.view(lay.combine, geo.max_tokens * geo.top_k * geo.hidden * 2, torch.bfloat16).view(-1, geo.hidden)
         cflags = heap.view(lay.cflags, num_layers * n * _n.MAX_RANKS * 4, torch.int32)
@@ -135,7 +136,7 @@ class RemoteExchange:
         n = g.regions
         dslot = self.layer * self.dflag_stride + self.source * n       # this source's dispatch flags of the layer
         if len(waves) == 1:
-            tile_rows = tile_rows or pick_tile_rows(T, g.top_k, g.num_experts)
+            tile_rows = tile_rows or plan_tile_rows(self.expert_format, T, g.top_k, g.num_experts)
             self.att.dispatch(x, logits, route_kw, tile_rows, dslot, self.epoch)
             return self.att.combine_into(out, T, self.layer * n, self.epoch, shared=shared, residual=residual, wait=True,
                                          norm_w=norm_w, eps=eps, x_out=x_out)
@@ -144,7 +145,7 @@ class RemoteExchange:
         for w, (a, b) in enumerate(waves):
             side = self.sides[w]
             side.combine = self.combine[a * k:]
-            side.dispatch(x[a:b], logits[a:b], route_kw, pick_tile_rows(b - a, k, g.num_experts), dslot + w, self.epoch)
+            side.dispatch(x[a:b], logits[a:b], route_kw, plan_tile_rows(self.expert_format, b - a, k, g.num_experts), dslot + w, self.epoch)
         for w, (a, b) in enumerate(waves):
             self.sides[w].combine_into(out[a:b], b - a, self.layer * n + w, self.epoch,
                                        shared=None if shared is None else shared[a:b],
@@ -348,10 +349,8 @@ class ExpertWorker:
                     flag = self.cflags_ptrs[a] + 4 * ((l * n + w) * _n.MAX_RANKS + self.er)
                     side = self.sides[a][w]
                     combine_ptr = self.combine_ptrs[a] + t0 * g.top_k * g.hidden * 2
-                    tile_rows = pick_tile_rows(t1 - t0, g.top_k, g.num_experts)
+                    tile_rows = plan_tile_rows(fmt, t1 - t0, g.top_k, g.num_experts)
                     if fmt == "fp8":                 # E4M3 values + 128x128 block scales
-                        if tile_rows == 128 and (t1 - t0) * g.top_k < 64 * g.num_experts:
-                            tile_rows = 64           # the fp8 kernel's weights-on-M path tops out at 64 rows
                         rows = min(side.geo.max_rows, (t1 - t0) * g.top_k + (hi - lo) * tile_rows)
                         side.run_fp8(wg, wu, wd, tile_rows, rows, dslot, self.epochs[a], combine_ptr, flag, wait=True,
                                      reuse_dequant=(w > 0 or a != active[0]))
@@ -480,6 +479,7 @@ def build_afd(cfg: ModelConfig, device: torch.device, rank: int, world: int, *, 
             W = Weights.random_init(cfg, device, seed=seed, with_experts=False)      # same seed: replicas hold the same model
         kv = Cache(cfg, num_pages, device)
         eng = AfdAttentionEngine(cfg, W, kv, max_tokens, max_seqs, heap, lay, geo, source=rank, n_sources=A)
+        eng.ex.expert_format = expert_format
         gen = Generator(eng, PagePool(num_pages), pages_per_seq, max_seqs, prefill_chunk=prefill_chunk or max_tokens,
                         use_graphs=use_graphs)
         return AfdHandle(gen, None, par, rank, A)

@@ -34,6 +34,17 @@ def pick_tile_rows(T: int, top_k: int, num_experts: int) -> int:
     return 128
 
 
+def plan_tile_rows(fmt: str, T: int, top_k: int, num_experts: int) -> int:
+    """Row tile of a step's expert segments for experts stored as ``fmt``.  Both halves of an exchange derive it from
+    the same arguments: the planner pads every expert's segment to it and the grouped GEMMs walk the tiles with it.
+    Quantised experts read their packed weights directly up to 64-row tiles; 128-row tiles mean the layer's experts are
+    expanded to bf16 first, which only pays once every expert sees at least 64 rows on average."""
+    t = pick_tile_rows(T, top_k, num_experts)
+    if fmt != "bf16" and t == 128 and T * top_k < 64 * num_experts:
+        t = 64
+    return t
+
+
 @dataclass
 class ExchangeGeometry:
     hidden: int
@@ -277,11 +288,13 @@ class LocalExchange:
         Rows are quantised 1x128 on the expert side before each grouped GEMM."""
         T = x.shape[0]
         g = self.geo
-        tile_rows = tile_rows or pick_tile_rows(T, g.top_k, g.num_experts)
-        if tile_rows == 128 and T * g.top_k < 128 * g.num_experts:
-            tile_rows = 64                          # the fp8 kernel's weights-on-M path tops out at 64 rows
+        tile_rows = tile_rows or plan_tile_rows("fp8", T, g.top_k, g.num_experts)
         self.att.dispatch(x, logits, route_kw, tile_rows, 0, self.epoch)
         e = self.exp
+        if tile_rows == 128:
+            # prefill-sized step: expand this layer's experts to bf16 once and take the bf16 grouped GEMMs
+            e.run_fp8(w_gate, w_up, w_down, tile_rows, 0, 0, self.epoch, self.att.combine.data_ptr(), None, wait=False)
+            return self.att.combine_into(out, T, 0, self.epoch, shared=shared, residual=residual, wait=False)
         rows = min(g.max_rows, T * g.top_k + g.num_experts * tile_rows)
         if not hasattr(e, "slab_q"):
             dev = e.slab.device
@@ -304,12 +317,9 @@ def _forward_w4(self, fmt: str, x: torch.Tensor, logits: torch.Tensor, route_kw:
     ones expand the layer's experts to bf16 once and take the bf16 path."""
     T = x.shape[0]
     g = self.geo
-    tile_rows = pick_tile_rows(T, g.top_k, g.num_experts)
-    if tile_rows > 64:
-        dq = [K.w4_dequant(w, fmt) for w in (w_gate, w_up, w_down)]
-        return self.forward(x, logits, route_kw, dq[0], dq[1], dq[2], out, shared=shared, residual=residual)
+    tile_rows = plan_tile_rows(fmt, T, g.top_k, g.num_experts)
     self.att.dispatch(x, logits, route_kw, tile_rows, 0, self.epoch)
-    self.exp.run_w4(fmt, w_gate, w_up, w_down, tile_rows, 0, self.epoch, self.att.combine.data_ptr(), None, wait=False)
+    self.exp.run_w4_any(fmt, w_gate, w_up, w_down, tile_rows, 0, self.epoch, self.att.combine.data_ptr(), None, wait=False)
     return self.att.combine_into(out, T, 0, self.epoch, shared=shared, residual=residual, wait=False)
 
 

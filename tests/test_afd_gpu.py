@@ -64,7 +64,8 @@ def _worker(rank: int, world: int, port: int, out_dir: str, mode: str, snap_dir:
         g = torch.Generator().manual_seed(1)
         prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g) for n in (200, 200, 77)]
         # round 1: every replica prefills a 200-token prompt of its own; round 2: replica 0 alone prefills 77 tokens
-        mine = [prompts[a]] + ([prompts[2]] if a == 0 else [])
+        # (the MTP mode keeps to one prompt: the depth reads the hidden states the last forward left behind)
+        mine = [prompts[a]] + ([prompts[2]] if a == 0 and mode != "mtp" else [])
         seqs, last, kvs = [], [], []
         with torch.no_grad():
             for r, p in enumerate(mine + ([None] if a else [])):
