@@ -123,6 +123,9 @@ def cuda_lib():
         _sig(lib, "cafd_sample_rows", [P, I, I, P, P, I, P, P, P])
         _sig(lib, "cafd_accept_prefix", [P, P, P, I, P, P, P])
         _sig(lib, "cafd_mla_q_split", [P, I, P, P, P, P, I, I, I, I, P])
+        _sig(lib, "cafd_mla_small_rows", [])
+        _sig(lib, "cafd_mla_absorb_small", [P, I, P, P, P, P, I, I, I, P])
+        _sig(lib, "cafd_mla_unabsorb_small", [P, I, P, P, I, I, P])
         _cuda = lib
         return lib
 

@@ -375,30 +375,84 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
 }
 
-// One block per (row block, half, row): thread c walks the splits in order for its output column.
-__global__ void __launch_bounds__(256) mla_merge_kernel(const float* __restrict__ partial, const int* __restrict__ block_seq,
-                                                        const int* __restrict__ block_tok0, const int* __restrict__ q_start,
-                                                        __nv_bfloat16* __restrict__ out, int heads, int splits, int out_tpad, int one_token) {
+// Merge of the kv splits.  One block per (row block, output half, 8-column chunk); 512 threads = 128 query rows x 4
+// groups that each take every fourth split.  The partials are stored column-major per split ([column][row]), so a
+// warp's loads are contiguous; per-row weights exp2(m_s - M) / L are computed once, every output element is a dot
+// product over the splits with independent loads, the four groups' sums meet in shared memory in group order, and
+// the 128 x 8 tile leaves as one 16-byte piece per row.
+constexpr int kMergeCols = 8;
+constexpr int kMergeGroups = 4;
+constexpr int kMaxSplits = 64;
+__global__ void __launch_bounds__(kMlaRows * kMergeGroups) mla_merge_kernel(const float* __restrict__ partial, const int* __restrict__ block_seq,
+                                                             const int* __restrict__ block_tok0, const int* __restrict__ q_start,
+                                                             __nv_bfloat16* __restrict__ out, int heads, int splits, int out_tpad, int one_token) {
   pdl_wait();
   pdl_trigger();
-  const int blk = blockIdx.x, dh = blockIdx.y, row = blockIdx.z, c = threadIdx.x;
+  __shared__ float s_sum[kMergeGroups][kMergeCols][kMlaRows];
+  __shared__ float s_ml[2][kMergeGroups][kMlaRows];
+  const int blk = blockIdx.x, dh = blockIdx.y, c0 = blockIdx.z * kMergeCols;
+  const int row = threadIdx.x & (kMlaRows - 1), grp = threadIdx.x / kMlaRows;
   const int seq = block_seq[blk], tok0 = block_tok0[blk];
   const int q0 = q_start[seq], q_len = q_start[seq + 1] - q0;
-  if (tok0 + row / heads >= q_len || (one_token && row >= heads)) return;
   const float* base = partial + (static_cast<size_t>(blk) * 2 + dh) * splits * kMlaPartial;
+  // row maximum over the splits: each group its share, then across the groups
   float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, __ldg(base + static_cast<size_t>(s) * kMlaPartial + kMlaRows * kHalf + row));
-  float L = 0.f, O = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float* ps = base + static_cast<size_t>(s) * kMlaPartial;
-    const float m = __ldg(ps + kMlaRows * kHalf + row);
-    const float f = (m == -INFINITY) ? 0.f : exp2f(m - M);
-    L += __ldg(ps + kMlaRows * kHalf + kMlaRows + row) * f;
-    O += __ldg(ps + static_cast<size_t>(c) * kMlaRows + row) * f;
+  for (int s = grp; s < splits; s += kMergeGroups) M = fmaxf(M, __ldg(base + static_cast<size_t>(s) * kMlaPartial + kMlaRows * kHalf + row));
+  s_ml[0][grp][row] = M;
+  __syncthreads();
+#pragma unroll
+  for (int g2 = 0; g2 < kMergeGroups; ++g2) M = fmaxf(M, s_ml[0][g2][row]);
+  float L = 0.f;
+  float fac[kMaxSplits / kMergeGroups];          // this thread's splits: grp, grp + 4, ...
+#pragma unroll
+  for (int i = 0; i < kMaxSplits / kMergeGroups; ++i) {
+    const int s = grp + i * kMergeGroups;
+    fac[i] = 0.f;
+    if (s < splits) {
+      const float* ps = base + static_cast<size_t>(s) * kMlaPartial;
+      const float m = __ldg(ps + kMlaRows * kHalf + row);
+      fac[i] = (m == -INFINITY) ? 0.f : exp2f(m - M);
+      L += __ldg(ps + kMlaRows * kHalf + kMlaRows + row) * fac[i];
+    }
   }
-  const size_t grow = out_tpad > 0 ? static_cast<size_t>(row % heads) * out_tpad + (q0 + tok0 + row / heads)
-                                   : static_cast<size_t>(q0 + tok0) * heads + row;
-  out[grow * kLat + dh * kHalf + c] = __float2bfloat16(L > 0.f ? O / L : 0.f);
+  s_ml[1][grp][row] = L;
+  float acc[kMergeCols];
+#pragma unroll
+  for (int c = 0; c < kMergeCols; ++c) acc[c] = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxSplits / kMergeGroups; ++i) {
+    const int s = grp + i * kMergeGroups;
+    if (s < splits) {
+      const float* ps = base + static_cast<size_t>(s) * kMlaPartial + static_cast<size_t>(c0) * kMlaRows + row;
+      float v[kMergeCols];
+#pragma unroll
+      for (int c = 0; c < kMergeCols; ++c) v[c] = __ldg(ps + c * kMlaRows);
+#pragma unroll
+      for (int c = 0; c < kMergeCols; ++c) acc[c] += v[c] * fac[i];
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < kMergeCols; ++c) s_sum[grp][c][row] = acc[c];
+  __syncthreads();
+  if (grp == 0) {
+    float Ls = 0.f;
+#pragma unroll
+    for (int g2 = 0; g2 < kMergeGroups; ++g2) Ls += s_ml[1][g2][row];
+    const float invL = Ls > 0.f ? 1.0f / Ls : 0.f;
+    if (tok0 + row / heads < q_len && !(one_token && row >= heads)) {
+      uint32_t o[kMergeCols / 2];
+#pragma unroll
+      for (int c = 0; c < kMergeCols; c += 2) {
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int g2 = 0; g2 < kMergeGroups; ++g2) { a0 += s_sum[g2][c][row]; a1 += s_sum[g2][c + 1][row]; }
+        o[c / 2] = pack_bf16(a0 * invL, a1 * invL);
+      }
+      const size_t grow = out_tpad > 0 ? static_cast<size_t>(row % heads) * out_tpad + (q0 + tok0 + row / heads)
+                                       : static_cast<size_t>(q0 + tok0) * heads + row;
+      *reinterpret_cast<uint4*>(out + grow * kLat + dh * kHalf + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
 }
 
 }  // namespace cafd
@@ -426,6 +480,7 @@ static int mla_attention_impl(const void* q, const void* cache, const int* page_
   if (n_blocks <= 0) return 0;
   if (heads <= 0 || kMlaRows % heads) return -10;
   if (splits < 1) splits = 1;
+  if (splits > kMaxSplits) return -13;
   if (splits > 1 && !scratch) return -12;
   CUtensorMap tq, tc;
   int rc = cached_tmap_2d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, total_rows, kRec, kRec * 2, kMlaRows, 64);
@@ -453,7 +508,7 @@ static int mla_attention_impl(const void* q, const void* cache, const int* page_
   cudaStream_t st = static_cast<cudaStream_t>(s);
   launch_pdl(mla_attn_kernel, dim3(n_blocks, 2, splits), dim3(kMlaThreads), kMlaSmem, st, tq, tc, p);
   if (splits > 1)
-    launch_pdl(mla_merge_kernel, dim3(n_blocks, 2, kMlaRows), dim3(kHalf), 0, st, static_cast<const float*>(scratch), block_seq,
+    launch_pdl(mla_merge_kernel, dim3(n_blocks, 2, kHalf / kMergeCols), dim3(kMlaRows * kMergeGroups), 0, st, static_cast<const float*>(scratch), block_seq,
                block_tok0, q_start, static_cast<__nv_bfloat16*>(out), heads, splits, out_tpad, sparse_idx ? 1 : 0);
   return static_cast<int>(cudaGetLastError());
 }

@@ -184,6 +184,116 @@ __global__ void __launch_bounds__(128) mla_q_split_kernel(const __nv_bfloat16* _
   }
 }
 
+// ---- decode-sized absorb / un-absorb ------------------------------------------------------------------------
+// With at most 16 rows the two per-head projections around the attention kernel are 128 tiny matrix-vector
+// products each (16.8 MB of weights per layer): as grouped tensor-core GEMMs they cost 12-19 us of fixed work.
+// Here every CTA streams one slice of one head's weight with one thread per weight row and the rows' vectors in
+// shared memory; the absorb kernel also does what mla_q_split does (nope / rope split + RoPE of the query).
+constexpr int kSmallT = 16;
+
+// q [T, heads * 192] -> q_abs [T, heads, 576]: [0:512] = q_nope @ W_uk[h]^T (W_uk [heads, 512, 128]), [512:576] = rotated rope dims.
+// grid (heads, 4): CTA (h, s) computes latent outputs [128 s, 128 s + 128) of head h for all rows.
+__global__ void __launch_bounds__(128) mla_absorb_small_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
+                                                               const __nv_bfloat16* __restrict__ w_uk,
+                                                               const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                                               __nv_bfloat16* __restrict__ q_abs, int T, int heads, int interleaved) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ float sq[kSmallT][kNope];
+  __shared__ __align__(16) __nv_bfloat16 so[kSmallT][128];
+  const int h = blockIdx.x, slice = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < T * kNope; i += 128) {
+    const int t = i / kNope, k = i - t * kNope;
+    sq[t][k] = __bfloat162float(q[static_cast<size_t>(t) * ldq + h * (kNope + kRopeD) + k]);
+  }
+  if (slice == 0) {
+    // rope dims of the query, one warp per row in turn
+    for (int t = warp; t < T; t += 4) {
+      const __nv_bfloat16* r = q + static_cast<size_t>(t) * ldq + h * (kNope + kRopeD) + kNope;
+      __nv_bfloat16* dst = q_abs + (static_cast<size_t>(t) * heads + h) * kRecord + kLatent;
+      float sn, cs;
+      sincosf(static_cast<float>(positions[t]) * inv_freq[lane], &sn, &cs);
+      if (interleaved) {
+        const uint32_t v = *reinterpret_cast<const uint32_t*>(r + 2 * lane);
+        const float x0 = bf16_lo(v), x1 = bf16_hi(v);
+        *reinterpret_cast<uint32_t*>(dst + 2 * lane) = pack_bf16(x0 * cs - x1 * sn, x0 * sn + x1 * cs);
+      } else {
+        const float x0 = __bfloat162float(r[lane]), x1 = __bfloat162float(r[lane + 32]);
+        dst[lane] = __float2bfloat16(x0 * cs - x1 * sn);
+        dst[lane + 32] = __float2bfloat16(x0 * sn + x1 * cs);
+      }
+    }
+  }
+  __syncthreads();
+  // thread = one weight row (128 K values = 16 loads of 16 bytes, all in flight)
+  const int row = slice * 128 + tid;
+  const uint4* wrow = reinterpret_cast<const uint4*>(w_uk + (static_cast<size_t>(h) * kLatent + row) * kNope);
+  uint4 wv[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) wv[i] = __ldg(wrow + i);
+  for (int t = 0; t < T; ++t) {
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t qv[4] = {wv[i].x, wv[i].y, wv[i].z, wv[i].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc += bf16_lo(qv[e]) * sq[t][i * 8 + 2 * e] + bf16_hi(qv[e]) * sq[t][i * 8 + 2 * e + 1];
+    }
+    so[t][tid] = __float2bfloat16(acc);
+  }
+  __syncthreads();
+  // 256 bytes per row leave as 16 pieces of 16 bytes
+  for (int i = tid; i < T * 16; i += 128) {
+    const int t = i >> 4, piece = i & 15;
+    *reinterpret_cast<uint4*>(q_abs + (static_cast<size_t>(t) * heads + h) * kRecord + slice * 128 + piece * 8) =
+        *reinterpret_cast<const uint4*>(&so[t][piece * 8]);
+  }
+}
+
+// o_lat [heads, t_pad, 512] (head-major attention output) -> attn [T, heads * 128]: attn[t, h] = o_lat[h, t] @ W_uv[h]^T
+// (W_uv [heads, 128, 512]).  grid (heads, 2): CTA (h, s) computes output rows [64 s, 64 s + 64); each of its eight
+// warps takes eight weight rows, lanes along K (a warp load is 512 contiguous bytes), all sixteen loads in flight.
+__global__ void __launch_bounds__(256) mla_unabsorb_small_kernel(const __nv_bfloat16* __restrict__ o_lat, int t_pad,
+                                                                 const __nv_bfloat16* __restrict__ w_uv,
+                                                                 __nv_bfloat16* __restrict__ attn, int T, int heads) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ __align__(16) __nv_bfloat16 sx[kSmallT][kLatent];
+  const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < T * (kLatent / 8); i += 256) {
+    const int t = i / (kLatent / 8), c = i - t * (kLatent / 8);
+    reinterpret_cast<uint4*>(&sx[t][0])[c] = reinterpret_cast<const uint4*>(o_lat + (static_cast<size_t>(h) * t_pad + t) * kLatent)[c];
+  }
+  __syncthreads();
+  const int row0 = blockIdx.y * 64 + warp * 8;
+  const uint4* wbase = reinterpret_cast<const uint4*>(w_uv + (static_cast<size_t>(h) * 128 + row0) * kLatent);
+  uint4 wv[8][2];
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+    wv[r][0] = __ldg(wbase + r * (kLatent / 8) + lane);
+    wv[r][1] = __ldg(wbase + r * (kLatent / 8) + 32 + lane);
+  }
+  for (int t = 0; t < T; ++t) {
+    const uint4 x0 = reinterpret_cast<const uint4*>(&sx[t][0])[lane], x1 = reinterpret_cast<const uint4*>(&sx[t][0])[32 + lane];
+    const uint32_t xa[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    float acc[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const uint32_t wa[8] = {wv[r][0].x, wv[r][0].y, wv[r][0].z, wv[r][0].w, wv[r][1].x, wv[r][1].y, wv[r][1].z, wv[r][1].w};
+      float a = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a += bf16_lo(wa[e]) * bf16_lo(xa[e]) + bf16_hi(wa[e]) * bf16_hi(xa[e]);
+      acc[r] = warp_sum(a);
+    }
+    if (lane < 8) {
+      float v = acc[0];
+#pragma unroll
+      for (int r = 1; r < 8; ++r) v = lane == r ? acc[r] : v;
+      attn[static_cast<size_t>(t) * heads * 128 + h * 128 + row0 + lane] = __float2bfloat16(v);
+    }
+  }
+}
+
 }  // namespace cafd
 
 using namespace cafd;
@@ -239,5 +349,27 @@ extern "C" int cafd_mla_q_split(const void* q, int ldq, const float* inv_freq, c
   launch_pdl(mla_q_split_kernel, dim3((warps + 3) / 4), dim3(128), 0, static_cast<cudaStream_t>(s),
              static_cast<const __nv_bfloat16*>(q), ldq, inv_freq, positions, static_cast<__nv_bfloat16*>(slab),
              static_cast<__nv_bfloat16*>(q_abs), T, heads, t_pad, interleaved);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int cafd_mla_small_rows(void) { return cafd::kSmallT; }
+
+// Decode-sized steps (T <= cafd_mla_small_rows()): q split + RoPE + absorb in one launch, and the un-absorb.
+extern "C" int cafd_mla_absorb_small(const void* q, int ldq, const void* w_uk, const float* inv_freq, const int* positions,
+                                     void* q_abs, int T, int heads, int interleaved, cafd_stream_t s) {
+  if (T <= 0) return 0;
+  if (T > cafd::kSmallT || (ldq & 1)) return -10;
+  launch_pdl(mla_absorb_small_kernel, dim3(heads, 4), dim3(128), 0, static_cast<cudaStream_t>(s),
+             static_cast<const __nv_bfloat16*>(q), ldq, static_cast<const __nv_bfloat16*>(w_uk), inv_freq, positions,
+             static_cast<__nv_bfloat16*>(q_abs), T, heads, interleaved);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int cafd_mla_unabsorb_small(const void* o_lat, int t_pad, const void* w_uv, void* attn, int T, int heads,
+                                       cafd_stream_t s) {
+  if (T <= 0) return 0;
+  if (T > cafd::kSmallT) return -10;
+  launch_pdl(mla_unabsorb_small_kernel, dim3(heads, 2), dim3(256), 0, static_cast<cudaStream_t>(s),
+             static_cast<const __nv_bfloat16*>(o_lat), t_pad, static_cast<const __nv_bfloat16*>(w_uv),
+             static_cast<__nv_bfloat16*>(attn), T, heads);
   return static_cast<int>(cudaGetLastError());
 }

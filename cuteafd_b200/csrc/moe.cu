@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const float* __restrict
 // ticket; the last block of a token routes it from the scores in `logits_buf`.  `tickets` [T] must be zero on
 // entry and is zero again on exit.
 constexpr int kNormRouteMaxH = 8192;
-constexpr int kNormRouteGroups = 8;
+constexpr int kNormRouteMaxGroups = 64;     // expert groups per token (grid.y): enough blocks to fill the GPU at one row
 template <int kPerLane>
 __global__ void __launch_bounds__(256) norm_route_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ ln_w,
                                                          float eps, const __nv_bfloat16* __restrict__ router_w,
@@ -72,10 +72,15 @@ __global__ void __launch_bounds__(256) norm_route_kernel(const __nv_bfloat16* __
   const int t = blockIdx.x, g = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nvec = H / 8;
   const uint4* hrow = reinterpret_cast<const uint4*>(h + static_cast<size_t>(t) * H);
+  // the row is read once and kept in registers (up to 8192 elements: four 16-byte pieces per thread)
+  constexpr int kRowVec = kNormRouteMaxH / 8 / 256;
+  uint4 hv[kRowVec];
   float ss = 0.f;
-  for (int c = tid; c < nvec; c += 256) {
-    const uint4 v = hrow[c];
-    const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < kRowVec; ++i) {
+    const int c = tid + i * 256;
+    hv[i] = c < nvec ? hrow[c] : make_uint4(0u, 0u, 0u, 0u);
+    const uint32_t q[4] = {hv[i].x, hv[i].y, hv[i].z, hv[i].w};
 #pragma unroll
     for (int e = 0; e < 4; ++e) ss += bf16_lo(q[e]) * bf16_lo(q[e]) + bf16_hi(q[e]) * bf16_hi(q[e]);
   }
@@ -86,27 +91,31 @@ __global__ void __launch_bounds__(256) norm_route_kernel(const __nv_bfloat16* __
 #pragma unroll
   for (int i = 0; i < 8; ++i) tot += red[i];
   const float inv = rsqrtf(tot / static_cast<float>(H) + eps);
-  for (int c = tid; c < nvec; c += 256) {
-    const uint4 v = hrow[c];
-    const uint4 wv = reinterpret_cast<const uint4*>(ln_w)[c];
-    const uint32_t q[4] = {v.x, v.y, v.z, v.w}, wq[4] = {wv.x, wv.y, wv.z, wv.w};
-    uint32_t o[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) o[e] = pack_bf16(bf16_lo(q[e]) * inv * bf16_lo(wq[e]), bf16_hi(q[e]) * inv * bf16_hi(wq[e]));
-    const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
-    reinterpret_cast<uint4*>(sx)[c] = ov;
-    if (g == 0) reinterpret_cast<uint4*>(x_out + static_cast<size_t>(t) * H)[c] = ov;
+  for (int i = 0; i < kRowVec; ++i) {
+    const int c = tid + i * 256;
+    if (c < nvec) {
+      const uint4 wv = reinterpret_cast<const uint4*>(ln_w)[c];
+      const uint32_t q[4] = {hv[i].x, hv[i].y, hv[i].z, hv[i].w}, wq[4] = {wv.x, wv.y, wv.z, wv.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[e] = pack_bf16(bf16_lo(q[e]) * inv * bf16_lo(wq[e]), bf16_hi(q[e]) * inv * bf16_hi(wq[e]));
+      const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+      reinterpret_cast<uint4*>(sx)[c] = ov;
+      if (g == 0) reinterpret_cast<uint4*>(x_out + static_cast<size_t>(t) * H)[c] = ov;
+    }
   }
   __syncthreads();
-  const int per = (E + kNormRouteGroups - 1) / kNormRouteGroups;
+  const int per = (E + static_cast<int>(gridDim.y) - 1) / static_cast<int>(gridDim.y);
   const int e_lo = g * per, e_hi = min(E, e_lo + per);
-  // two experts per warp pass, eight 16-byte loads of each in flight per lane
-  for (int e0 = e_lo + 2 * warp; e0 < e_hi; e0 += 16) {
-    const bool two = e0 + 1 < e_hi;
+  // two experts per warp pass (one when the block's share is at most eight), eight 16-byte loads of each in flight
+  const int per_warp = (e_hi - e_lo) > 8 ? 2 : 1;
+  for (int e0 = e_lo + per_warp * warp; e0 < e_hi; e0 += 8 * per_warp) {
+    const bool two = per_warp == 2 && e0 + 1 < e_hi;
     const uint4* wa = reinterpret_cast<const uint4*>(router_w + static_cast<size_t>(e0) * H);
     const uint4* wb = reinterpret_cast<const uint4*>(router_w + static_cast<size_t>(two ? e0 + 1 : e0) * H);
     float acc_a = 0.f, acc_b = 0.f;
-#pragma unroll 4
+#pragma unroll 8
     for (int c = lane; c < nvec; c += 32) {
       const uint4 a = reinterpret_cast<const uint4*>(sx)[c];
       const uint4 b0 = __ldg(wa + c), b1 = __ldg(wb + c);
@@ -218,15 +227,26 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
   // Exclusive scan of the per-expert tile counts (one thread per expert, Hillis-Steele in shared
   // memory), then every expert writes its own tiles: no serial walk over the experts.
   __shared__ int scan[kMaxExperts];
-  for (int e = threadIdx.x; e < kMaxExperts; e += blockDim.x)
-    scan[e] = e < E ? (counts[e] + tile_rows - 1) / tile_rows : 0;
-  __syncthreads();
-  for (int d = 1; d < kMaxExperts; d <<= 1) {
-    int v = 0;
+  __shared__ int warp_tot[kMaxExperts / 32];
+  {
+    // inclusive scan of the per-expert tile counts: shuffles inside each warp of 32 experts, then the warp totals
     const int e = threadIdx.x;
-    if (e < kMaxExperts && e >= d) v = scan[e - d];
+    int v = 0;
+    if (e < kMaxExperts) {
+      v = e < E ? (counts[e] + tile_rows - 1) / tile_rows : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane_id >= o) v += u;
+      }
+      if (lane_id == 31) warp_tot[warp_id] = v;
+    }
     __syncthreads();
-    if (e < kMaxExperts) scan[e] += v;
+    if (e < kMaxExperts) {
+      int before = 0;
+      for (int w = 0; w < warp_id; ++w) before += warp_tot[w];
+      scan[e] = v + before;
+    }
     __syncthreads();
   }
   // scan[e] is now inclusive; tiles before expert e inside its rank = scan[e-1] - scan[lo-1]
@@ -506,14 +526,27 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint4* __restric
       float acc[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      for (int s = 0; s < top_k; ++s) {
-        const float g = w[static_cast<size_t>(t) * top_k + s];
-        const uint4 v = buf[(static_cast<size_t>(t) * top_k + s) * row_vec + c];
-        const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+      // slot rows in batches of eight loads in flight (they come from peer-written memory: latency, not bytes, is the
+      // cost of a decode-sized combine); the sum itself stays in slot order
+      for (int s0 = 0; s0 < top_k; s0 += 8) {
+        uint4 v[8];
+        float g[8];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          acc[2 * e] += g * bf16_lo(q[e]);
-          acc[2 * e + 1] += g * bf16_hi(q[e]);
+        for (int j = 0; j < 8; ++j) {
+          const int sl = s0 + j < top_k ? s0 + j : top_k - 1;
+          v[j] = buf[(static_cast<size_t>(t) * top_k + sl) * row_vec + c];
+          g[j] = s0 + j < top_k ? w[static_cast<size_t>(t) * top_k + sl] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (s0 + j < top_k) {
+            const uint32_t q[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              acc[2 * e] += g[j] * bf16_lo(q[e]);
+              acc[2 * e + 1] += g[j] * bf16_hi(q[e]);
+            }
+          }
         }
       }
       if (shared_out) {
@@ -673,8 +706,13 @@ int cafd_norm_route(const void* h, const void* ln_w, float eps, const void* rout
       !logits_buf || !tickets)
     return -10;
   cudaStream_t st = static_cast<cudaStream_t>(s);
+  // blocks = tokens x expert groups: about two per SM, at least 4 experts and at most 64 groups per token
+  int groups = (2 * 148 + T - 1) / T;
+  if (groups > (E + 3) / 4) groups = (E + 3) / 4;
+  if (groups > kNormRouteMaxGroups) groups = kNormRouteMaxGroups;
+  if (groups < 8) groups = E < 8 ? (E > 0 ? E : 1) : 8;
 #define CAFD_NROUTE(N)                                                                                                        \
-  launch_pdl(norm_route_kernel<N>, dim3(T, kNormRouteGroups), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(h),          \
+  launch_pdl(norm_route_kernel<N>, dim3(T, groups), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(h),                    \
              static_cast<const __nv_bfloat16*>(ln_w), eps, static_cast<const __nv_bfloat16*>(router_w), bias,                 \
              static_cast<__nv_bfloat16*>(x_out), out_idx, out_w, logits_buf, tickets, H, E, top_k, sigmoid, num_groups,        \
              topk_groups, normalize, routed_scale)

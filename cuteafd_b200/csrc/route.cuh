@@ -53,28 +53,35 @@ __device__ __forceinline__ void route_row(const float* row, const float* __restr
   }
   if (num_groups > 1) {
     const int per_group = E / num_groups;
+    // group of each of this lane's experts, computed once (the loops below would otherwise divide per element)
+    int gid[kPerLane];
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+      const int e = j * 32 + lane;
+      gid[j] = e < E ? e / per_group : -1;
+    }
     unsigned keep = 0;   // bit g set = group g kept
     float gscore_mine = -INFINITY;   // lane g holds the score of group g
     for (int g = 0; g < num_groups; ++g) {
+      // the group's two best selection scores: per-lane best and runner-up first, then one warp reduction of pairs
       float top1 = -INFINITY, top2 = -INFINITY;
       int i1 = 0x7fffffff;
 #pragma unroll
       for (int j = 0; j < kPerLane; ++j) {
-        const int e = j * 32 + lane;
-        if (e < E && e / per_group == g && (sel[j] > top1 || (sel[j] == top1 && e < i1))) { top1 = sel[j]; i1 = e; }
+        if (gid[j] == g) {
+          const int e = j * 32 + lane;
+          if (sel[j] > top1 || (sel[j] == top1 && e < i1)) { top2 = top1; top1 = sel[j]; i1 = e; }
+          else top2 = fmaxf(top2, sel[j]);
+        }
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, top1, o);
+        const float o1 = __shfl_xor_sync(0xffffffffu, top1, o);
+        const float o2 = __shfl_xor_sync(0xffffffffu, top2, o);
         const int oi = __shfl_xor_sync(0xffffffffu, i1, o);
-        if (ov > top1 || (ov == top1 && oi < i1)) { top1 = ov; i1 = oi; }
+        if (o1 > top1 || (o1 == top1 && oi < i1)) { top2 = fmaxf(top1, o2); top1 = o1; i1 = oi; }
+        else top2 = fmaxf(top2, o1);
       }
-#pragma unroll
-      for (int j = 0; j < kPerLane; ++j) {
-        const int e = j * 32 + lane;
-        if (e < E && e / per_group == g && e != i1) top2 = fmaxf(top2, sel[j]);
-      }
-      top2 = warp_max(top2);
       if (lane == g) gscore_mine = top1 + top2;
     }
     for (int it = 0; it < topk_groups; ++it) {
@@ -91,10 +98,8 @@ __device__ __forceinline__ void route_row(const float* row, const float* __restr
       if (gi != 0x7fffffff) keep |= 1u << gi;
     }
 #pragma unroll
-    for (int j = 0; j < kPerLane; ++j) {
-      const int e = j * 32 + lane;
-      if (e < E && !((keep >> (e / per_group)) & 1u)) sel[j] = -INFINITY;
-    }
+    for (int j = 0; j < kPerLane; ++j)
+      if (gid[j] >= 0 && !((keep >> gid[j]) & 1u)) sel[j] = -INFINITY;
   }
   float wsum = 0.f;
   float my_w = 0.f;

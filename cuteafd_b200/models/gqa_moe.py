@@ -308,14 +308,24 @@ class GqaMoeEngine:
             K.rmsnorm(ws.h[:T], L.ln2, cfg.rms_eps, out=ws.x[:T])
             logits = K.linear(ws.x[:T], L.router, out=ws.router[:T, :cfg.num_experts], out_f32=True)
             self.launches += 3                   # norm, router scores, top-k
+        kw = dict(self.route_kw, bias=L.router_bias)
+        if self.pre_moe is not None:
+            self.pre_moe(i)
+        split = hasattr(self.moe, "begin")
+        if split:
+            # disaggregated exchange: the rows leave for the expert ranks first, the shared expert's GEMMs run while
+            # they are away, the combine waits for them last
+            self.moe.begin(ws.x[:T], logits, kw)
         shared = None
         if L.s_gate is not None:
             K.linear(ws.x[:T], L.s_gate, out=ws.ffn_s[:T], w_up=L.s_up)
             shared = K.linear(ws.ffn_s[:T], L.s_down, out=ws.shared[:T])
             self.launches += 2
-        kw = dict(self.route_kw, bias=L.router_bias)
-        if self.pre_moe is not None:
-            self.pre_moe(i)
+        if split:
+            self.moe.finish(ws.h[:T], shared=shared, residual=ws.h[:T], norm_w=next_norm, eps=cfg.rms_eps,
+                            x_out=ws.x[:T] if next_norm is not None else None)
+            self.launches += 4 if T * cfg.top_k <= 512 else 5
+            return next_norm is not None
         fmt = getattr(self.W, "expert_format", "bf16")
         if fmt != "bf16" and hasattr(self.moe, "forward_stored"):
             # experts served in their stored form (E4M3 block-scaled / MXFP4 / NVFP4): same exchange, quantised GEMMs

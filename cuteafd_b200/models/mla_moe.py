@@ -269,7 +269,12 @@ class MlaMoeEngine(GqaMoeEngine):
         K.linear(ws.q_a[:T] if ql else ws.x[:T], L.wq_b, out=ws.q[:T])
         q_slab = ws.q_slab[:heads * ht.t_pad * 128].view(heads, ht.t_pad, 128)
         o_slab = ws.o_slab[:heads * ht.t_pad * 512].view(heads, ht.t_pad, 512)
-        K.mla_q_split(ws.q[:T], self.inv_freq, b.positions, q_slab, ws.q_abs[:T], heads, cfg.rope_interleaved)
+        small = T <= K.MLA_SMALL_ROWS and not expanded
+        if small:
+            # decode-sized step: nope / rope split, RoPE and the absorb projection in one launch
+            K.mla_absorb_small(ws.q[:T], L.w_uk, self.inv_freq, b.positions, ws.q_abs[:T], heads, cfg.rope_interleaved)
+        else:
+            K.mla_q_split(ws.q[:T], self.inv_freq, b.positions, q_slab, ws.q_abs[:T], heads, cfg.rope_interleaved)
         if expanded:
             rows = ((T + 63) // 64) * 64
             K.linear(ws.lat[:T], L.w_kb, out=ws.k_exp[:T])
@@ -279,8 +284,9 @@ class MlaMoeEngine(GqaMoeEngine):
             K.linear(ws.attn[:T], L.wo, out=ws.h[:T], residual=ws.h[:T])
             self.launches += 8
             return
-        K.grouped_linear(q_slab.view(-1, 128), L.w_uk, ws.q_abs, ht.tile_expert, ht.tile_row0, ht.num_tiles, ht.max_tiles,
-                         ht.tile_rows, row_dst=ht.row_dst, ldo=REC, split_k=False)
+        if not small:
+            K.grouped_linear(q_slab.view(-1, 128), L.w_uk, ws.q_abs, ht.tile_expert, ht.tile_row0, ht.num_tiles, ht.max_tiles,
+                             ht.tile_rows, row_dst=ht.row_dst, ldo=REC, split_k=False)
         S, max_pages = b.page_table.shape
         sel = self._select(i, T, b) if cfg.indexer_heads else None
         bseq, btok = self._block_table(S, b.max_q_len, 1 if sel is not None else None)
@@ -307,10 +313,13 @@ class MlaMoeEngine(GqaMoeEngine):
         else:
             K.mla_attention(ws.q_abs[:T], self.kv.c[i], b.page_table, b.seq_lens, b.q_start, bseq, btok, o_slab, self.scale,
                             splits, self._scratch if splits > 1 else None, out_tpad=ht.t_pad, sparse_idx=sel)
-        K.grouped_linear(o_slab.view(-1, 512), L.w_uv, ws.attn, ht.tile_expert, ht.tile_row0, ht.num_tiles, ht.max_tiles,
-                         ht.tile_rows, row_dst=ht.row_dst, ldo=cfg.v_head_dim, split_k=False)
+        if small:
+            K.mla_unabsorb_small(o_slab, L.w_uv, ws.attn[:T], T)
+        else:
+            K.grouped_linear(o_slab.view(-1, 512), L.w_uv, ws.attn, ht.tile_expert, ht.tile_row0, ht.num_tiles, ht.max_tiles,
+                             ht.tile_rows, row_dst=ht.row_dst, ldo=cfg.v_head_dim, split_k=False)
         K.linear(ws.attn[:T], L.wo, out=ws.h[:T], residual=ws.h[:T])
-        self.launches += 8 + (1 if splits > 1 else 0)
+        self.launches += (7 if small else 8) + (1 if splits > 1 else 0)
 
     def _select(self, i: int, T: int, b: Batch) -> torch.Tensor:
         """Lightning indexer: store this step's index keys, score every visible position, keep the top-k per token."""

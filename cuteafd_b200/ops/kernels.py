@@ -526,6 +526,29 @@ def mla_q_split(q: torch.Tensor, inv_freq: torch.Tensor, positions: torch.Tensor
                                             _stream()), "mla_q_split")
 
 
+MLA_SMALL_ROWS = 16      # steps of at most this many rows take the decode-sized absorb / un-absorb kernels
+
+
+def mla_absorb_small(q: torch.Tensor, w_uk: torch.Tensor, inv_freq: torch.Tensor, positions: torch.Tensor, q_abs: torch.Tensor,
+                     heads: int, interleaved: bool) -> None:
+    """Decode-sized steps (T <= 16): q [T, heads*192] -> q_abs [T, heads, 576] in one launch: the 128 nope dims of
+    every head multiplied by W_uk[h] [512, 128] into the latent part, the 64 rope dims rotated into the tail."""
+    T = q.shape[0]
+    assert T <= MLA_SMALL_ROWS and q.shape[1] == heads * 192 and w_uk.shape == (heads, 512, 128) and w_uk.is_contiguous()
+    _n.check(_n.cuda_lib().cafd_mla_absorb_small(q.data_ptr(), q.stride(0), w_uk.data_ptr(), inv_freq.data_ptr(),
+                                                 positions.data_ptr(), q_abs.data_ptr(), T, heads, int(interleaved), _stream()),
+             "mla_absorb_small")
+
+
+def mla_unabsorb_small(o_lat: torch.Tensor, w_uv: torch.Tensor, attn: torch.Tensor, T: int) -> None:
+    """Decode-sized steps: o_lat [heads, t_pad, 512] (head-major attention output) -> attn [T, heads*128] through
+    W_uv[h] [128, 512]."""
+    heads, t_pad, _ = o_lat.shape
+    assert T <= MLA_SMALL_ROWS and w_uv.shape == (heads, 128, 512) and w_uv.is_contiguous() and attn.is_contiguous()
+    _n.check(_n.cuda_lib().cafd_mla_unabsorb_small(o_lat.data_ptr(), t_pad, w_uv.data_ptr(), attn.data_ptr(), T, heads, _stream()),
+             "mla_unabsorb_small")
+
+
 # ---- sampling ---------------------------------------------------------------------------------------------
 _SAMPLE_ROW = None
 

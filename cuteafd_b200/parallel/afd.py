@@ -128,30 +128,46 @@ class RemoteExchange:
         self.layer = 0
         self.dflag_stride = n * n_sources        # dispatch flag slots per layer on an expert rank
 
-    def forward(self, x, logits, route_kw, w_gate, w_up, w_down, out, *, shared=None, residual=None, tile_rows=None,
-                norm_w=None, eps=0.0, x_out=None):
+    def begin(self, x, logits, route_kw, tile_rows=None) -> None:
+        """First half of a layer's exchange: route (unless ``norm_route`` already did), plan, store the rows into the
+        owners' slabs and raise their flags.  Whatever the caller launches before ``finish`` (the shared expert's GEMMs)
+        runs while the expert ranks work on these rows."""
         T = x.shape[0]
         g = self.geo
         waves = g.waves(T)
         n = g.regions
+        self._pending = (T, waves)
         dslot = self.layer * self.dflag_stride + self.source * n       # this source's dispatch flags of the layer
         if len(waves) == 1:
             tile_rows = tile_rows or plan_tile_rows(self.expert_format, T, g.top_k, g.num_experts)
             self.att.dispatch(x, logits, route_kw, tile_rows, dslot, self.epoch)
-            return self.att.combine_into(out, T, self.layer * n, self.epoch, shared=shared, residual=residual, wait=True,
-                                         norm_w=norm_w, eps=eps, x_out=x_out)
+            return
         assert logits is not None, "fused routing is for single-wave steps"
         k = g.top_k
         for w, (a, b) in enumerate(waves):
             side = self.sides[w]
             side.combine = self.combine[a * k:]
             side.dispatch(x[a:b], logits[a:b], route_kw, plan_tile_rows(self.expert_format, b - a, k, g.num_experts), dslot + w, self.epoch)
+
+    def finish(self, out, *, shared=None, residual=None, norm_w=None, eps=0.0, x_out=None):
+        """Second half: wait for every owner's completion flag and combine (slot order, + shared expert + residual,
+        one rounding; optionally the next layer's input norm)."""
+        T, waves = self._pending
+        n = self.geo.regions
+        if len(waves) == 1:
+            return self.att.combine_into(out, T, self.layer * n, self.epoch, shared=shared, residual=residual, wait=True,
+                                         norm_w=norm_w, eps=eps, x_out=x_out)
         for w, (a, b) in enumerate(waves):
             self.sides[w].combine_into(out[a:b], b - a, self.layer * n + w, self.epoch,
                                        shared=None if shared is None else shared[a:b],
                                        residual=None if residual is None else residual[a:b], wait=True,
                                        norm_w=norm_w, eps=eps, x_out=None if x_out is None else x_out[a:b])
         return out
+
+    def forward(self, x, logits, route_kw, w_gate, w_up, w_down, out, *, shared=None, residual=None, tile_rows=None,
+                norm_w=None, eps=0.0, x_out=None):
+        self.begin(x, logits, route_kw, tile_rows)
+        return self.finish(out, shared=shared, residual=residual, norm_w=norm_w, eps=eps, x_out=x_out)
 
 
 CTRL_WORDS = 4 + _n.MAX_RANKS          # op, steps, reserved x2, tokens of every attention replica
