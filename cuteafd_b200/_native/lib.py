@@ -48,6 +48,7 @@ class MoeLayout(C.Structure):
         ("n_ranks", C.c_int), ("expert_lo", C.c_int * (MAX_RANKS + 1)),
         ("slab", C.c_void_p * MAX_RANKS), ("meta", C.c_void_p * MAX_RANKS), ("flag", C.c_void_p * MAX_RANKS),
         ("max_tiles", C.c_int), ("max_rows", C.c_int),
+        ("fp8", C.c_int), ("slab_q", C.c_void_p * MAX_RANKS), ("slab_s", C.c_void_p * MAX_RANKS),
     ]
 
 

@@ -237,13 +237,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant
             for (int j = 0; j < 16; ++j) {
               int xr = x_row0 + c0 + j;
               if (xr >= p.x_rows_total) xr = p.x_rows_total - 1;
-              const float sx = __ldg(p.x_scale + static_cast<size_t>(xr) * nkb + kb);
+              const float sx = p.x_scale[static_cast<size_t>(xr) * nkb + kb];     // plain load: a peer may have written it
               acc[c0 + j] += __uint_as_float(r[j]) * (sw0 * sx);
               if (kDual) acc[kBX + c0 + j] += __uint_as_float(u[j]) * (sw1 * sx);
             }
           }
         } else {
-          const float sx = __ldg(p.x_scale + static_cast<size_t>(my_x_row) * nkb + kb);
+          const float sx = p.x_scale[static_cast<size_t>(my_x_row) * nkb + kb];
           // weight blocks along N: one per 128 features (kBW = 128) or gate/up halves (dual, 64 + 64)
           const float s0 = sx * __ldg(ws0 + kb);
           const float s1 = kDual ? sx * __ldg(ws1 + kb) : s0;

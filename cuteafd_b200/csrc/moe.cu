@@ -33,7 +33,38 @@ struct MoeLayoutDev {
   uint32_t* flag[kMaxRanks];
   int max_tiles;
   int max_rows;
+  // Wire quantisation (fp8 != 0): rows leave the attention rank as E4M3 with one fp32 scale per 128 columns
+  // (amax / 448), written to slab_q [max_rows, H] and slab_s [max_rows, H / 128] of the owner instead of bf16 rows:
+  // half the bytes cross the link and the expert rank's GEMM reads them as they are.  The reference's routed
+  // activations travel quantised as well: E4M3 bytes plus one UE8M0 scale per 32 values (python/reference/exlr8.py:94-119,
+  // python/tools/aot/export_b12x_slices_aot.py:171); the scale here is the one this build's block-scaled GEMM consumes.
+  int fp8;
+  uint8_t* slab_q[kMaxRanks];
+  float* slab_s[kMaxRanks];
 };
+
+// One 16-byte vector (8 bf16) per lane, 16 consecutive lanes = one 128-column block: E4M3 bytes + the block's scale.
+// Same arithmetic as the standalone row quantiser (scale = amax / 448, 1 when the block is zero).
+__device__ __forceinline__ void quant_block_e4m3(const uint4& v, uint2& q, float& scale) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  float f[8];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { f[2 * e] = bf16_lo(w[e]); f[2 * e + 1] = bf16_hi(w[e]); }
+  float amax = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  scale = amax > 0.f ? amax / 448.0f : 1.0f;
+  const float inv = 1.0f / scale;
+  uint32_t p[2] = {0u, 0u};
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const __nv_fp8_e4m3 b(fminf(fmaxf(f[e] * inv, -448.f), 448.f));
+    p[e >> 2] |= static_cast<uint32_t>(b.__x) << (8 * (e & 3));
+  }
+  q = make_uint2(p[0], p[1]);
+}
 
 template <int kPerLane>
 __global__ void __launch_bounds__(128) route_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
@@ -341,17 +372,29 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
       const int r = rank_of[e];
       const uint4* src = x + static_cast<size_t>(i / top_k) * row_vec;
       uint4* dst = reinterpret_cast<uint4*>(L.slab[r]) + static_cast<size_t>(row) * row_vec;
+      uint2* dq = reinterpret_cast<uint2*>(L.slab_q[r]) + static_cast<size_t>(row) * row_vec;
+      float* ds = L.slab_s[r] + static_cast<size_t>(row) * (row_vec >> 4);
       for (int c0 = 0; c0 < row_vec; c0 += 256) {          // eight loads in flight per lane, then the stores
         uint4 v[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const int c = c0 + lane + 32 * k;
-          if (c < row_vec) v[k] = __ldg(src + c);
+          v[k] = c < row_vec ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const int c = c0 + lane + 32 * k;
-          if (c < row_vec) dst[c] = v[k];
+          if (L.fp8) {
+            uint2 q;
+            float sc;
+            quant_block_e4m3(v[k], q, sc);
+            if (c < row_vec) {
+              dq[c] = q;
+              if ((lane & 15) == 0) ds[c >> 4] = sc;
+            }
+          } else if (c < row_vec) {
+            dst[c] = v[k];
+          }
         }
       }
     }
@@ -466,12 +509,31 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const uint4* __restri
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         const int c = c0 + lane + 32 * k;
-        if (c < row_vec) v[k] = __ldg(src + c);
+        v[k] = c < row_vec ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
+      }
+      uint2 qv[8];
+      float qs[8];
+      if (L.fp8) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) quant_block_e4m3(v[k], qv[k], qs[k]);      // the row is quantised once, stored top_k times
       }
       for (int sl = 0; sl < top_k; ++sl) {
         const int row = __shfl_sync(0xffffffffu, my_row, sl);
         const int r = __shfl_sync(0xffffffffu, my_rank, sl);
         if (row < 0) continue;
+        if (L.fp8) {
+          uint2* dq = reinterpret_cast<uint2*>(L.slab_q[r]) + static_cast<size_t>(row) * row_vec;
+          float* ds = L.slab_s[r] + static_cast<size_t>(row) * (row_vec >> 4);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int c = c0 + lane + 32 * k;
+            if (c < row_vec) {
+              dq[c] = qv[k];
+              if ((lane & 15) == 0) ds[c >> 4] = qs[k];
+            }
+          }
+          continue;
+        }
         uint4* dst = reinterpret_cast<uint4*>(L.slab[r]) + static_cast<size_t>(row) * row_vec;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -617,6 +679,9 @@ typedef struct {
   uint32_t* flag[kMaxRanks];
   int max_tiles;
   int max_rows;
+  int fp8;                       // rows travel as E4M3 + one fp32 scale per 128 columns (slab_q / slab_s) instead of bf16
+  void* slab_q[kMaxRanks];
+  float* slab_s[kMaxRanks];
 } cafd_moe_layout;
 
 static MoeLayoutDev to_dev(const cafd_moe_layout* l) {
@@ -627,10 +692,21 @@ static MoeLayoutDev to_dev(const cafd_moe_layout* l) {
     d.slab[i] = static_cast<__nv_bfloat16*>(l->slab[i]);
     d.meta[i] = l->meta[i];
     d.flag[i] = l->flag[i];
+    d.slab_q[i] = static_cast<uint8_t*>(l->slab_q[i]);
+    d.slab_s[i] = l->slab_s[i];
   }
   d.max_tiles = l->max_tiles;
   d.max_rows = l->max_rows;
+  d.fp8 = l->fp8;
   return d;
+}
+
+// E4M3 wire format: whole 128-column blocks, and every owner's value / scale buffers bound.
+static bool wire_ok(const cafd_moe_layout* l, int H) {
+  if (H % 128) return false;
+  for (int r = 0; r < l->n_ranks; ++r)
+    if (!l->slab_q[r] || !l->slab_s[r]) return false;
+  return true;
 }
 
 int cafd_route_topk(const float* logits, const float* bias, int* out_idx, float* out_w, int T, int E, int top_k,
@@ -691,6 +767,7 @@ int cafd_moe_plan_dispatch(const int* idx, int T, int top_k, int E, int tile_row
                            int* dest_row, int* expert_count, uint32_t* status, const void* x, int H, const uint32_t* epoch,
                            cafd_stream_t s) {
   if (E > kMaxExperts || layout->n_ranks < 1 || layout->n_ranks > kMaxRanks || !x || !epoch || H % 8) return -10;
+  if (layout->fp8 && !wire_ok(layout, H)) return -11;
   launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(s), idx, T, top_k, E, tile_rows, to_dev(layout), dest_row,
              expert_count, status, static_cast<const uint4*>(x), H / 8, epoch, static_cast<int*>(nullptr), 0);
   return static_cast<int>(cudaGetLastError());
@@ -729,6 +806,7 @@ int cafd_moe_dispatch(const void* x, const int* idx, const int* dest_row, int T,
                       const cafd_moe_layout* layout, const uint32_t* epoch, uint32_t* done_counter,
                       cafd_stream_t s) {
   if (H % 8 || top_k > 32) return -10;
+  if (layout->fp8 && !wire_ok(layout, H)) return -11;
   const int n = T * top_k;
   const int blocks = T > 0 ? (T + 7) / 8 : 1;            // eight warps per block, one token each
   launch_pdl(moe_dispatch_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(s), static_cast<const uint4*>(x), idx, dest_row, n,

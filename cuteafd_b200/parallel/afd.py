@@ -36,7 +36,7 @@ import torch.distributed as dist
 from .._native import lib as _n
 from ..config import ModelConfig
 from ..ops import kernels as K
-from .moe_exchange import AttentionSide, ExchangeGeometry, ExpertSide, pick_tile_rows, plan_tile_rows
+from .moe_exchange import AttentionSide, ExchangeGeometry, ExpertSide, pick_tile_rows, plan_tile_rows, wire_fp8_ok
 
 OP_STOP, OP_STEPS, OP_TIMED, OP_SYNC = 0, 1, 2, 3
 
@@ -128,6 +128,11 @@ class RemoteExchange:
         self.layer = 0
         self.dflag_stride = n * n_sources        # dispatch flag slots per layer on an expert rank
 
+    def _wire(self, side, tile_rows: int) -> bool:
+        """E4M3 experts on decode-sized tiles take their rows quantised: half the bytes over the link and no quantise
+        launch on the expert rank (``ExpertWorker._step`` makes the same call)."""
+        return self.expert_format == "fp8" and wire_fp8_ok(side.geo, tile_rows)
+
     def begin(self, x, logits, route_kw, tile_rows=None) -> None:
         """First half of a layer's exchange: route (unless ``norm_route`` already did), plan, store the rows into the
         owners' slabs and raise their flags.  Whatever the caller launches before ``finish`` (the shared expert's GEMMs)
@@ -140,14 +145,15 @@ class RemoteExchange:
         dslot = self.layer * self.dflag_stride + self.source * n       # this source's dispatch flags of the layer
         if len(waves) == 1:
             tile_rows = tile_rows or plan_tile_rows(self.expert_format, T, g.top_k, g.num_experts)
-            self.att.dispatch(x, logits, route_kw, tile_rows, dslot, self.epoch)
+            self.att.dispatch(x, logits, route_kw, tile_rows, dslot, self.epoch, wire_fp8=self._wire(self.att, tile_rows))
             return
         assert logits is not None, "fused routing is for single-wave steps"
         k = g.top_k
         for w, (a, b) in enumerate(waves):
             side = self.sides[w]
             side.combine = self.combine[a * k:]
-            side.dispatch(x[a:b], logits[a:b], route_kw, plan_tile_rows(self.expert_format, b - a, k, g.num_experts), dslot + w, self.epoch)
+            tr = plan_tile_rows(self.expert_format, b - a, k, g.num_experts)
+            side.dispatch(x[a:b], logits[a:b], route_kw, tr, dslot + w, self.epoch, wire_fp8=self._wire(side, tr))
 
     def finish(self, out, *, shared=None, residual=None, norm_w=None, eps=0.0, x_out=None):
         """Second half: wait for every owner's completion flag and combine (slot order, + shared expert + residual,
@@ -369,7 +375,7 @@ class ExpertWorker:
                     if fmt == "fp8":                 # E4M3 values + 128x128 block scales
                         rows = min(side.geo.max_rows, (t1 - t0) * g.top_k + (hi - lo) * tile_rows)
                         side.run_fp8(wg, wu, wd, tile_rows, rows, dslot, self.epochs[a], combine_ptr, flag, wait=True,
-                                     reuse_dequant=(w > 0 or a != active[0]))
+                                     reuse_dequant=(w > 0 or a != active[0]), wire=wire_fp8_ok(side.geo, tile_rows))
                     elif fmt in ("mxfp4", "nvfp4"):
                         side.run_w4_any(fmt, wg, wu, wd, tile_rows, dslot, self.epochs[a], combine_ptr, flag,
                                         reuse_dequant=(w > 0 or a != active[0]))

@@ -45,6 +45,13 @@ def plan_tile_rows(fmt: str, T: int, top_k: int, num_experts: int) -> int:
     return t
 
 
+def wire_fp8_ok(geo: "ExchangeGeometry", tile_rows: int) -> bool:
+    """Whether a step's rows travel as E4M3 + per-128 scales: the block-scaled expert GEMM consumes them as they are
+    (decode-sized tiles); prefill-sized steps expand the experts to bf16 and want bf16 rows.  Both sides of the
+    exchange call this with the same arguments."""
+    return tile_rows < 128 and geo.hidden % 128 == 0
+
+
 @dataclass
 class ExchangeGeometry:
     hidden: int
@@ -114,6 +121,13 @@ class ExpertSide:
         self.tile_expert = self.meta[16:16 + mt]
         self.tile_row0 = self.meta[16 + mt:16 + 2 * mt]
         self.row_dst = self.meta[16 + 2 * mt:]
+        # E4M3 wire format: the same receive slab read as [max_rows, H] bytes followed by [max_rows, H / 128] fp32 scales
+        # (fits: H + H / 32 bytes per row against 2 H for bf16), so a step may arrive in either form.
+        if geo.hidden % 128 == 0:
+            raw = self.slab.view(-1).view(torch.uint8)
+            nq = geo.max_rows * geo.hidden
+            self.wire_q = raw[:nq].view(torch.float8_e4m3fn).view(geo.max_rows, geo.hidden)
+            self.wire_s = raw[nq:nq + geo.max_rows * (geo.hidden // 128) * 4].view(torch.float32).view(geo.max_rows, geo.hidden // 128)
 
     def run(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, tile_rows: int, layer: int,
             epoch: torch.Tensor, combine_ptr: int, combine_flag_ptr: int | None, wait: bool) -> None:
@@ -128,9 +142,10 @@ class ExpertSide:
 
 
     def run_fp8(self, w_gate, w_up, w_down, tile_rows: int, rows: int, layer: int, epoch: torch.Tensor, combine_ptr: int,
-                combine_flag_ptr: int | None, wait: bool, reuse_dequant: bool = False) -> None:
+                combine_flag_ptr: int | None, wait: bool, reuse_dequant: bool = False, wire: bool = False) -> None:
         """E4M3 experts: ``w_*`` = (values [E, N, K], scales [E, N/128, K/128]).  Received rows and the
-        fc1 output are quantised 1x128 here, next to the GEMMs that consume them."""
+        fc1 output are quantised 1x128 here, next to the GEMMs that consume them; with ``wire`` the rows arrived
+        quantised by the dispatch (``wire_q`` / ``wire_s``) and fc1 itself waits for the dispatch flag."""
         g = self.geo
         if tile_rows == 128:
             # Prefill-sized step: the block-scaled kernel folds scales in its epilogue warps and falls behind the bf16
@@ -153,11 +168,16 @@ class ExpertSide:
             self.h_q = torch.zeros(g.max_rows, g.expert_ffn, dtype=torch.float8_e4m3fn, device=dev)
             self.h_s = torch.ones(g.max_rows, g.expert_ffn // 128, dtype=torch.float32, device=dev)
         rows = min(rows, g.max_rows)
-        if wait:
-            K.wait_flag(self.flags.data_ptr() + 4 * layer, epoch)
-        K.quant_rows_fp8(self.slab[:rows], self.slab_q[:rows], self.slab_s[:rows])
-        K.grouped_linear_fp8(self.slab_q, self.slab_s, w_gate[0], w_gate[1], self.hbuf, self.tile_expert, self.tile_row0,
-                             self.num_tiles, g.max_tiles, tile_rows, w_up=w_up[0], ws_up=w_up[1])
+        if wire:
+            K.grouped_linear_fp8(self.wire_q, self.wire_s, w_gate[0], w_gate[1], self.hbuf, self.tile_expert, self.tile_row0,
+                                 self.num_tiles, g.max_tiles, tile_rows, w_up=w_up[0], ws_up=w_up[1], epoch=epoch,
+                                 wait_flag=(self.flags.data_ptr() + 4 * layer) if wait else None)
+        else:
+            if wait:
+                K.wait_flag(self.flags.data_ptr() + 4 * layer, epoch)
+            K.quant_rows_fp8(self.slab[:rows], self.slab_q[:rows], self.slab_s[:rows])
+            K.grouped_linear_fp8(self.slab_q, self.slab_s, w_gate[0], w_gate[1], self.hbuf, self.tile_expert, self.tile_row0,
+                                 self.num_tiles, g.max_tiles, tile_rows, w_up=w_up[0], ws_up=w_up[1])
         K.quant_rows_fp8(self.hbuf[:rows], self.h_q[:rows], self.h_s[:rows])
         K.grouped_linear_fp8(self.h_q, self.h_s, w_down[0], w_down[1], self.hbuf, self.tile_expert, self.tile_row0,
                              self.num_tiles, g.max_tiles, tile_rows, row_dst=self.row_dst, out_ptr=combine_ptr, ldo=g.hidden,
@@ -227,15 +247,19 @@ class AttentionSide:
             self._rank_ptrs.append((0, 0, 0))
         self._rank_ptrs[r] = (slab_ptr, meta_ptr, flags_ptr)
         self.layout.slab[r], self.layout.meta[r] = slab_ptr, meta_ptr
+        # the E4M3 wire form of the same slab: bytes first, then the per-128 scales (``ExpertSide.wire_q`` / ``wire_s``)
+        self.layout.slab_q[r] = slab_ptr
+        self.layout.slab_s[r] = slab_ptr + self.geo.max_rows * self.geo.hidden
 
     FUSED_DISPATCH_ROWS = 512       # (token, slot) rows up to which plan and dispatch share one single-block launch
 
     def dispatch(self, x: torch.Tensor, logits: torch.Tensor | None, route_kw: dict, tile_rows: int, layer: int,
-                 epoch: torch.Tensor) -> None:
+                 epoch: torch.Tensor, wire_fp8: bool = False) -> None:
         """Route (unless ``logits`` is None: then ``idx`` / ``w`` were already filled by ``norm_route``), plan, and
-        copy the rows into the owners' slabs."""
+        copy the rows into the owners' slabs; ``wire_fp8`` sends them as E4M3 + per-128 scales."""
         T = x.shape[0]
         g = self.geo
+        self.layout.fp8 = int(wire_fp8)
         idx, w = self.idx[:T], self.w[:T]
         if logits is not None:
             K.route_topk(logits, g.top_k, out_idx=idx, out_w=w, **route_kw)
@@ -283,13 +307,15 @@ class LocalExchange:
 
     def forward_fp8(self, x: torch.Tensor, logits: torch.Tensor, route_kw: dict, w_gate, w_up, w_down, out: torch.Tensor, *,
                     shared: torch.Tensor | None = None, residual: torch.Tensor | None = None,
-                    tile_rows: int | None = None) -> torch.Tensor:
+                    tile_rows: int | None = None, wire: bool | None = None) -> torch.Tensor:
         """Same exchange with E4M3 experts: each ``w_*`` is (values [E, N, K] e4m3, scales [E, N/128, K/128]).
-        Rows are quantised 1x128 on the expert side before each grouped GEMM."""
+        Decode-sized steps quantise the rows 1x128 inside the dispatch (``wire``); otherwise on the expert side before
+        each grouped GEMM."""
         T = x.shape[0]
         g = self.geo
         tile_rows = tile_rows or plan_tile_rows("fp8", T, g.top_k, g.num_experts)
-        self.att.dispatch(x, logits, route_kw, tile_rows, 0, self.epoch)
+        wire = wire_fp8_ok(g, tile_rows) if wire is None else wire
+        self.att.dispatch(x, logits, route_kw, tile_rows, 0, self.epoch, wire_fp8=wire)
         e = self.exp
         if tile_rows == 128:
             # prefill-sized step: expand this layer's experts to bf16 once and take the bf16 grouped GEMMs
@@ -302,8 +328,12 @@ class LocalExchange:
             e.slab_s = torch.ones(g.max_rows, g.hidden // 128, dtype=torch.float32, device=dev)
             e.h_q = torch.zeros(g.max_rows, g.expert_ffn, dtype=torch.float8_e4m3fn, device=dev)
             e.h_s = torch.ones(g.max_rows, g.expert_ffn // 128, dtype=torch.float32, device=dev)
-        K.quant_rows_fp8(e.slab[:rows], e.slab_q[:rows], e.slab_s[:rows])
-        K.grouped_linear_fp8(e.slab_q, e.slab_s, w_gate[0], w_gate[1], e.hbuf, e.tile_expert, e.tile_row0, e.num_tiles,
+        if wire:
+            xq, xs = e.wire_q, e.wire_s
+        else:
+            xq, xs = e.slab_q, e.slab_s
+            K.quant_rows_fp8(e.slab[:rows], xq[:rows], xs[:rows])
+        K.grouped_linear_fp8(xq, xs, w_gate[0], w_gate[1], e.hbuf, e.tile_expert, e.tile_row0, e.num_tiles,
                              g.max_tiles, tile_rows, w_up=w_up[0], ws_up=w_up[1])
         K.quant_rows_fp8(e.hbuf[:rows], e.h_q[:rows], e.h_s[:rows])
         K.grouped_linear_fp8(e.h_q, e.h_s, w_down[0], w_down[1], e.hbuf, e.tile_expert, e.tile_row0, e.num_tiles,

@@ -295,6 +295,30 @@ def test_moe_fp8_grouped(K, T, tile):
     close(out, R.combine_slots(parts, None, res, torch.bfloat16), 3e-2, 3e-2)
 
 
+@pytest.mark.parametrize("T,H", [(5, 512), (40, 2048), (300, 7168), (700, 384)])
+def test_dispatch_quantises_on_the_wire(K, T, H):
+    """Rows dispatched as E4M3 + per-128 scales equal the rows dispatched in bf16 and quantised on arrival, bit for bit
+    (single-block plan+dispatch up to 512 entries, the separate dispatch kernel above that)."""
+    from cuteafd_b200.parallel.moe_exchange import ExchangeGeometry, LocalExchange
+    E, k, tile = 16, 4, 16
+    ex = LocalExchange(ExchangeGeometry(H, 256, E, k, max_tokens=T, n_expert_ranks=1), dev())
+    x = bf(T, H, seed=T)
+    x[0, :128] = 0                                               # an all-zero block: scale 1, bytes 0
+    logits = torch.randn(T, E, device=dev())
+    ex.att.dispatch(x, logits, dict(scoring="softmax"), tile, 0, ex.epoch)
+    torch.cuda.synchronize()
+    rows = int(ex.exp.tile_row0[: int(ex.exp.num_tiles)].max()) + tile
+    dst = ex.att.dest_row[: T * k].long()
+    wq, ws = K.quant_rows_fp8(ex.exp.slab[:rows].clone())
+    ex.exp.slab.zero_()
+    ex.att.dispatch(x, None, dict(scoring="softmax"), tile, 0, ex.epoch, wire_fp8=True)
+    torch.cuda.synchronize()
+    check_status(K)
+    assert torch.equal(ex.att.dest_row[: T * k].long(), dst)
+    assert torch.equal(ex.exp.wire_q[dst].view(torch.uint8), wq[dst].view(torch.uint8))
+    assert torch.equal(ex.exp.wire_s[dst], ws[dst])
+
+
 # ---- fused decode-step kernels -------------------------------------------------------------------------------
 @pytest.mark.parametrize("E,k,scoring,groups,keep,H", [(128, 8, "softmax", 1, 1, 2048), (256, 8, "sigmoid", 8, 4, 1024)])
 def test_norm_route_matches_separate_kernels(K, E, k, scoring, groups, keep, H):
