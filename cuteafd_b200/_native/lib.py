@@ -61,6 +61,15 @@ class TpReduceArgs(C.Structure):
     ]
 
 
+class TpHeadArgs(C.Structure):
+    _fields_ = [
+        ("cand_v", C.c_void_p), ("cand_i", C.c_void_p), ("table_out", C.c_void_p * 8), ("table_in", C.c_void_p),
+        ("flags_out", C.c_void_p * 8), ("flags_in", C.c_void_p), ("epoch", C.c_void_p), ("done_counter", C.c_void_p),
+        ("status", C.c_void_p), ("out", C.c_void_p), ("ranks", C.c_int), ("my_rank", C.c_int), ("max_rows", C.c_int),
+        ("T", C.c_int), ("slices", C.c_int), ("lo", C.c_int),
+    ]
+
+
 def _sig(lib, name, argtypes, restype=C.c_int):
     fn = getattr(lib, name)
     fn.argtypes = argtypes
@@ -96,6 +105,8 @@ def cuda_lib():
         _sig(lib, "cafd_wait_flag", [P, P, P, P])
         _sig(lib, "cafd_tp_reduce_norm_gather", [C.POINTER(TpReduceArgs), P])
         _sig(lib, "cafd_tp_signal", [P, I, P, P])
+        _sig(lib, "cafd_tp_head_pick", [C.POINTER(TpHeadArgs), P])
+        _sig(lib, "cafd_argmax_candidates", [P, P, P, I, I, I, P])
         _sig(lib, "cafd_moe_plan", [P, I, I, I, I, C.POINTER(MoeLayout), P, P, P, P])
         _sig(lib, "cafd_moe_plan_wide", [P, I, I, I, I, C.POINTER(MoeLayout), P, P, P, P, P])
         _sig(lib, "cafd_moe_plan_wide_ints", [I, I])

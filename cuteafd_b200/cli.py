@@ -88,6 +88,56 @@ def cmd_serve(a: argparse.Namespace) -> int:
     return run_server(a)
 
 
+def cmd_launch(a: argparse.Namespace) -> int:
+    """Plan, write the deployment document, start one ``serve`` per rank and supervise them."""
+    from . import launch as LA
+    from .planner import plan as P
+    if a.deployment:
+        with open(a.deployment) as f:
+            spec = json.load(f)
+    else:
+        if not a.model:
+            print("launch: name a MODEL (argument or configuration key) or pass --deployment FILE", file=sys.stderr)
+            return 2
+        rep = P.plan(a.model, layout=True, gpus=a.gpus, attention_ranks=a.attention_ranks, expert_ranks=a.expert_ranks,
+                     pool_tokens_target=a.pool_tokens, gpu_memory_cap=_size(a.gpu_memory_cap) if a.gpu_memory_cap else None,
+                     max_context_tokens=a.max_context_tokens, concurrency=a.concurrency, speculator=a.speculator,
+                     decode_lanes=a.decode_lanes)
+        if not (rep.placement and rep.placement.ok and rep.ready):
+            print(P.render(rep), file=sys.stderr)
+            return 1
+        spec = P.deployment(rep, a.master_addr, a.master_port)
+    serve_args = ["--host", a.host, "--port", str(a.port)]
+    if a.api_key:
+        serve_args += ["--api-key", a.api_key]
+    for flag, val in (("--max-context-tokens", a.max_context_tokens), ("--concurrency", a.concurrency)):
+        if val is not None:
+            serve_args += [flag, str(val)]
+    if a.speculator:
+        serve_args += ["--speculator", a.speculator]
+    serve_args += list(a.serve_arg)
+    try:
+        L = LA.build_launch(spec, a.run_dir, serve_args)
+    except ValueError as e:
+        print(f"launch: {e}", file=sys.stderr)
+        return 2
+    print(LA.describe(L), flush=True)
+    if a.dry_run:
+        return 0
+    L.start()
+    print(f"[launch] {len(L.ranks)} ranks started; logs and pid file under {a.run_dir}", flush=True)
+    return L.supervise()
+
+
+def cmd_stop(a: argparse.Namespace) -> int:
+    from . import launch as LA
+    path = os.path.join(a.run_dir, "launch.json")
+    if not os.path.exists(path):
+        print(f"stop: no deployment recorded under {a.run_dir}", file=sys.stderr)
+        return 1
+    return LA.stop_by_pid_file(path)
+
+
 def cmd_expertd(a: argparse.Namespace) -> int:
     from .serve.expertd import run_expertd
     return run_expertd(a)
@@ -302,6 +352,7 @@ def _build_parser() -> argparse.ArgumentParser:
 
     s = sub.add_parser("serve", help="HTTP serving (OpenAI / Anthropic compatible)")
     s.add_argument("--snapshot", default=""); s.add_argument("--preset", default="")
+    s.add_argument("--deployment", default="", help="deployment document (plan --deployment / launch): how many attention ranks the group has, pool and row budgets")
     s.add_argument("--host", default="127.0.0.1"); s.add_argument("--port", type=int, default=8000)
     s.add_argument("--api-key", default=os.environ.get("CUTEAFD_API_KEY", ""))
     s.add_argument("--max-context-tokens", type=int, default=16384); s.add_argument("--concurrency", type=int, default=8)
@@ -333,6 +384,30 @@ def _build_parser() -> argparse.ArgumentParser:
     s.add_argument("--media", default="none", choices=["none", "auto", "random"],
                    help="auto: load the vision / audio towers the snapshot bundles; random: small random-init towers")
     s.set_defaults(fn=cmd_serve)
+
+    la = sub.add_parser("launch", help="plan a checkpoint on this box and start one serving process per rank")
+    la.add_argument("model", nargs="?", default="")
+    la.add_argument("--deployment", default="", help="start this deployment document (from plan --deployment) instead of planning")
+    la.add_argument("--run-dir", default="cuteafd-run", help="directory for the deployment document, the per-rank logs and the pid file")
+    la.add_argument("--dry-run", action="store_true", help="validate the plan and print the per-rank commands without starting anything")
+    la.add_argument("--gpus", type=int, default=8, help="GPUs of the box to plan for")
+    la.add_argument("--attention-ranks", type=int, default=1); la.add_argument("--expert-ranks", type=int, default=None)
+    la.add_argument("--pool-tokens", type=int, default=None); la.add_argument("--gpu-memory-cap", default="")
+    la.add_argument("--max-context-tokens", type=int, default=None, help="longest context a request may reach")
+    la.add_argument("--concurrency", type=int, default=None, help="requests decoded together")
+    la.add_argument("--speculator", default=None, choices=["auto", "off", "mtp"], help="speculative decoding to plan for and serve with")
+    la.add_argument("--decode-lanes", type=int, default=None, choices=[1, 2])
+    la.add_argument("--host", default="127.0.0.1", help="address rank 0's HTTP server listens on")
+    la.add_argument("--port", type=int, default=8000, help="port of rank 0's HTTP server")
+    la.add_argument("--api-key", default=os.environ.get("CUTEAFD_API_KEY", ""), help="bearer key the HTTP server asks for")
+    la.add_argument("--master-addr", default="127.0.0.1", help="rendezvous address of the process group")
+    la.add_argument("--master-port", type=int, default=29500, help="rendezvous port of the process group")
+    la.add_argument("--serve-arg", action="append", default=[], metavar="ARG", help="extra argument handed to every rank's serve command (repeatable)")
+    la.set_defaults(fn=cmd_launch)
+
+    st = sub.add_parser("stop", help="end a deployment started by launch")
+    st.add_argument("--run-dir", default="cuteafd-run", help="the run directory given to launch")
+    st.set_defaults(fn=cmd_stop)
 
     e = sub.add_parser("expertd", help="expert-rank worker")
     e.add_argument("--snapshot", default=""); e.add_argument("--rank", type=int, default=1); e.add_argument("--world", type=int, default=2)
@@ -421,10 +496,43 @@ def _build_parser() -> argparse.ArgumentParser:
     return ap
 
 
+# Configuration key -> flag destination, where the two are not the same word.
+_CONFIG_DEST = {"HTTP_QUEUE_DEPTH": "queue_depth", "HTTP_QUEUE_WAIT": "queue_wait"}
+
+
+def apply_config(ap: argparse.ArgumentParser, a: argparse.Namespace, argv: list[str]) -> None:
+    """Configuration keys become the values of the sub-command's flags of the same name (MODEL also names the
+    ``--snapshot`` of serve / expertd / golden); a flag given on the command line wins over the file, ``--set`` wins
+    over the file's own lines.  Keys the sub-command has no flag for are left for it to read from ``a.file_config``."""
+    subs = next(x for x in ap._actions if isinstance(x, argparse._SubParsersAction))
+    sp = subs.choices[a.cmd]
+    given = {t.split("=", 1)[0] for t in argv if t.startswith("--")}
+    by_dest = {x.dest: x for x in sp._actions if x.option_strings or x.dest == "model"}
+    for key, raw in a.file_config.items():
+        dests = [_CONFIG_DEST.get(key, key.lower())] + (["snapshot"] if key == "MODEL" else [])
+        for d in dests:
+            act = by_dest.get(d)
+            if act is None or any(o in given for o in act.option_strings):
+                continue
+            if not act.option_strings and getattr(a, d, None) not in (None, ""):
+                continue                                         # a positional given on the command line
+            if isinstance(act, (argparse._StoreTrueAction, argparse._StoreFalseAction)):
+                val = raw.strip().lower() in ("1", "on", "true", "yes")
+            else:
+                val = act.type(raw) if act.type is not None else raw
+                if act.choices is not None and val not in act.choices:
+                    print(f"config: {key}={raw} is not one of {sorted(map(str, act.choices))}", file=sys.stderr)
+                    raise SystemExit(2)
+            setattr(a, d, val)
+
+
 def main(argv: list[str] | None = None) -> int:
     ap = build_parser()
+    argv = list(sys.argv[1:] if argv is None else argv)
     a = ap.parse_args(argv)
     a.file_config = load_config_file(a.config, a.set, CONFIG_KEYS) if (a.config or a.set) else {}
+    if a.file_config:
+        apply_config(ap, a, argv)
     return a.fn(a)
 
 

@@ -82,6 +82,8 @@ int cafd_gemm(const cafd_gemm_args* a, cafd_stream_t stream);
 // never selected.  `scratch` holds 2 * T * cafd_argmax_slices() 4-byte words, owned by the caller.
 int cafd_argmax_slices(void);
 int cafd_argmax(const float* logits, int* out, void* scratch, int T, int V, int ld, cafd_stream_t stream);
+// The first stage only: cand_v / cand_i [T, cafd_argmax_slices()] per-slice winners.
+int cafd_argmax_candidates(const float* logits, float* cand_v, int* cand_i, int T, int V, int ld, cafd_stream_t stream);
 
 // The same selection for callers that cannot allocate device memory at all and therefore cannot
 // hand over scratch: a serving loop that runs after its memory plan is sealed, a host program

@@ -296,6 +296,15 @@ extern "C" int cafd_argmax(const float* logits, int* out, void* scratch, int T, 
   return static_cast<int>(cudaGetLastError());
 }
 
+// Stage 1 alone: per-row candidates (value, index) of cafd_argmax_slices() vocabulary slices.  The sharded head
+// reduces and exchanges them itself (tp_collective.cu).
+extern "C" int cafd_argmax_candidates(const float* logits, float* cand_v, int* cand_i, int T, int V, int ld, cafd_stream_t s) {
+  if (T <= 0) return 0;
+  if (!cand_v || !cand_i) return -10;
+  launch_pdl(argmax_stage1_kernel, dim3(64, T), dim3(256), 0, static_cast<cudaStream_t>(s), logits, cand_v, cand_i, V, ld, 64);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // ---- greedy selection without any allocation ---------------------------------------------------------
 // Same two-stage selection as cafd_argmax, for callers that cannot provide scratch: code running
 // where the allocator must not be entered (a serving loop whose memory was planned up front and

@@ -133,6 +133,78 @@ __global__ void tp_signal_kernel(const TpSignalDev p, const uint32_t* __restrict
   }
 }
 
+// ---- vocabulary-sharded head: greedy selection across ranks -------------------------------------------------------
+// Every rank holds rows [lo, hi) of the head and has reduced its slice of each logit row to per-slice candidates
+// (argmax stage 1).  One block per row finishes the local reduction and stores (value, global id) into every rank's
+// candidate table at [my_rank][row]: 8 bytes per row and rank cross the fabric instead of a vocabulary-wide row.  The
+// last block raises this rank's flag everywhere, waits (bounded) for every rank's flag, and picks per row the highest
+// value with ties to the lowest id: the single-GPU argmax rule, same token on every rank.  Reference: the coordinator
+// pair's distributed head exchanges per-rank winners the same way (rust/crates/cuteafd-daemon/src/shared/
+// distributed_head.rs).
+struct TpHeadDev {
+  const float* cand_v;       // [T, slices]
+  const int* cand_i;
+  unsigned long long* table_out[8];     // every rank's table [ranks][max_rows]
+  const unsigned long long* table_in;   // this rank's table
+  uint32_t* flags_out[8];    // per destination rank: word this rank raises there
+  const uint32_t* flags_in;  // [ranks]
+  const uint32_t* epoch;
+  uint32_t* done_counter;
+  uint32_t* status;
+  int* out;                  // [T] selected ids
+  int ranks, my_rank, max_rows, T, slices, lo;
+};
+
+__device__ __forceinline__ void head_merge(float& best, int& bi, float ov, int oi) {
+  if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+}
+
+__global__ void __launch_bounds__(64) tp_head_pick_kernel(const TpHeadDev p) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ int s_last;
+  const int t = blockIdx.x;
+  if (threadIdx.x < 32) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < p.slices; i += 32) head_merge(best, bi, p.cand_v[t * p.slices + i], p.cand_i[t * p.slices + i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      head_merge(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+    if (threadIdx.x == 0) {
+      const int gid = bi == 0x7fffffff ? 0x7fffffff : bi + p.lo;          // an empty or all-NaN slice never wins
+      const unsigned long long word = (static_cast<unsigned long long>(__float_as_uint(best)) << 32) | static_cast<uint32_t>(gid);
+      for (int r = 0; r < p.ranks; ++r) p.table_out[r][static_cast<size_t>(p.my_rank) * p.max_rows + t] = word;
+      __threadfence_system();
+      const uint32_t prev = atomicAdd(p.done_counter, 1u);
+      s_last = prev == gridDim.x - 1;
+    }
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    *p.done_counter = 0;
+    __threadfence_system();
+    const uint32_t ep = *p.epoch;
+    for (int r = 0; r < p.ranks; ++r) st_release_sys(p.flags_out[r], ep);
+    bool ok = true;
+    for (int r = 0; r < p.ranks && ok; ++r) ok = wait_flag_ge(p.flags_in + r, ep, p.status);
+    s_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  for (int row = threadIdx.x; row < p.T; row += blockDim.x) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int r = 0; r < p.ranks; ++r) {
+      const unsigned long long w = *reinterpret_cast<const volatile unsigned long long*>(p.table_in + static_cast<size_t>(r) * p.max_rows + row);
+      head_merge(best, bi, __uint_as_float(static_cast<uint32_t>(w >> 32)), static_cast<int>(static_cast<uint32_t>(w)));
+    }
+    p.out[row] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
 }  // namespace cafd
 
 using namespace cafd;
@@ -184,6 +256,36 @@ int cafd_tp_signal(void* const* flags, int n, const uint32_t* epoch, cafd_stream
   for (int r = 0; r < 8; ++r) p.flags[r] = r < n ? static_cast<uint32_t*>(flags[r]) : nullptr;
   p.n = n;
   launch_pdl(tp_signal_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(s), p, epoch);
+  return static_cast<int>(cudaGetLastError());
+}
+
+typedef struct {
+  const float* cand_v;
+  const int* cand_i;
+  void* table_out[8];
+  const void* table_in;
+  uint32_t* flags_out[8];
+  const uint32_t* flags_in;
+  const uint32_t* epoch;
+  uint32_t* done_counter;
+  uint32_t* status;
+  int* out;
+  int ranks, my_rank, max_rows, T, slices, lo;
+} cafd_tp_head_args;
+
+int cafd_tp_head_pick(const cafd_tp_head_args* a, cafd_stream_t s) {
+  if (!a || a->ranks < 1 || a->ranks > 8 || a->T < 1 || a->T > a->max_rows || a->slices < 1 || !a->out || !a->epoch) return -10;
+  TpHeadDev p;
+  p.cand_v = a->cand_v; p.cand_i = a->cand_i;
+  for (int r = 0; r < 8; ++r) {
+    p.table_out[r] = static_cast<unsigned long long*>(a->table_out[r]);
+    p.flags_out[r] = a->flags_out[r];
+  }
+  p.table_in = static_cast<const unsigned long long*>(a->table_in);
+  p.flags_in = a->flags_in;
+  p.epoch = a->epoch; p.done_counter = a->done_counter; p.status = a->status; p.out = a->out;
+  p.ranks = a->ranks; p.my_rank = a->my_rank; p.max_rows = a->max_rows; p.T = a->T; p.slices = a->slices; p.lo = a->lo;
+  launch_pdl(tp_head_pick_kernel, dim3(a->T), dim3(64), 0, static_cast<cudaStream_t>(s), p);
   return static_cast<int>(cudaGetLastError());
 }
 

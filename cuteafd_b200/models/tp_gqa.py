@@ -58,7 +58,7 @@ class TpGqaMoeEngine(GqaMoeEngine):
     same logits on every rank."""
 
     def __init__(self, cfg: ModelConfig, weights: GqaMoeWeights, num_pages: int, max_tokens: int, max_seqs: int = 64,
-                 group=None, build_moe: bool = True):
+                 group=None, build_moe: bool = True, shard_head: bool = False):
         self.group = group or dist.group.WORLD
         self.ranks, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         self.full_cfg = cfg
@@ -69,6 +69,18 @@ class TpGqaMoeEngine(GqaMoeEngine):
         self.tp = TpContext(cfg.hidden, max_tokens, dev, self.group)
         self.own_out = torch.zeros(self.tp.max_rows_per_rank, cfg.hidden, dtype=torch.bfloat16, device=dev)
         self.collectives = 0
+        # Vocabulary-sharded head: this rank keeps rows [lo, hi) of the head only, ``forward`` returns its slice of the
+        # logits, ``greedy`` exchanges per-rank winners (8 bytes per row and rank) and ``full_logits`` gathers the slices
+        # for rows that are sampled (rust/crates/cuteafd-daemon/src/shared/distributed_head.rs).
+        self.shard_head = shard_head
+        if shard_head:
+            from ..parallel.head import shard_rows
+            self.head_lo, self.head_hi = shard_rows(cfg.vocab_size, self.ranks, self.rank)
+            self.head_per = shard_rows(cfg.vocab_size, self.ranks, 0)[1]
+            self.head_w = weights.lm_head[self.head_lo:self.head_hi].contiguous()
+            self.W.lm_head = None                                        # the full head is not kept on this rank
+            self.logits = None
+            self.local_logits = torch.zeros(max_seqs, max(self.head_per, 1), dtype=torch.float32, device=dev)
 
     def collect_max(self, ms: float) -> float:
         """Largest device time over the ranks of the group (benchmarks report the slowest rank)."""
@@ -158,7 +170,32 @@ class TpGqaMoeEngine(GqaMoeEngine):
         tp.wait_gathered()
         rows = tp.x_full[:T].index_select(0, b.last_rows) if b.last_rows is not None else tp.x_full[:T]
         n_out = rows.shape[0]
-        logits = K.linear(rows.contiguous(), self.W.lm_head, out=self.logits[:n_out], out_f32=True)
+        if self.shard_head:
+            if n_out > self.local_logits.shape[0]:
+                self.local_logits = torch.zeros(n_out, self.local_logits.shape[1], dtype=torch.float32, device=self.device)
+            logits = self.local_logits[:n_out, :self.head_hi - self.head_lo]
+            if self.head_hi > self.head_lo:
+                K.linear(rows.contiguous(), self.head_w, out=logits, out_f32=True)
+        else:
+            logits = K.linear(rows.contiguous(), self.W.lm_head, out=self.logits[:n_out], out_f32=True)
         tp.release_buffers()
         self.launches += 3 + 2 * self.ranks
         return logits
+
+    def greedy(self, logits: torch.Tensor) -> torch.Tensor:
+        if not self.shard_head:
+            return super().greedy(logits)
+        self.launches += 2
+        self.collectives += 1
+        return self.tp.head_pick(logits, self.head_lo, self.next_tokens[:logits.shape[0]])
+
+    def full_logits(self, logits: torch.Tensor) -> torch.Tensor:
+        """Whole-vocabulary logits [T, vocab] on every rank from the slices (rows that are sampled, not argmax'ed)."""
+        if not self.shard_head:
+            return logits
+        T = logits.shape[0]
+        pad = torch.full((T, self.head_per), float("-inf"), dtype=torch.float32, device=self.device)
+        pad[:, :logits.shape[1]] = logits
+        parts = torch.empty(self.ranks, T, self.head_per, dtype=torch.float32, device=self.device)
+        dist.all_gather_into_tensor(parts.view(-1), pad.view(-1), group=self.group)
+        return parts.permute(1, 0, 2).reshape(T, -1)[:, :self.full_cfg.vocab_size]

@@ -67,6 +67,56 @@ class Hop:
         return out
 
 
+class RingHop(Hop):
+    """A hop with its own staging ring, so that transfers overlap the compute on both sides: ``send`` copies the rows
+    into a ring slot (the caller may overwrite its buffer right away) and sends from there on the side stream;
+    ``recv`` lands in a ring slot on the side stream (it can be in flight while the consumer still works on the
+    previous micro-batch) and the consumer copies out.  A slot is reused only after its previous transfer / copy-out
+    has finished (events)."""
+
+    def __init__(self, peer: int, group=None, device: torch.device | None = None, rows: int = 0, width: int = 0,
+                 dtype: torch.dtype = torch.bfloat16, slots: int = 2):
+        super().__init__(peer, group, device)
+        self.ring = [torch.empty(rows, width, dtype=dtype, device=device) for _ in range(slots)] if self.cuda else []
+        self.free_ev: list = [None] * slots
+        self.k = 0
+
+    def send(self, rows: torch.Tensor) -> None:
+        if not self.cuda:
+            return super().send(rows)
+        self.bytes_moved += rows.numel() * rows.element_size()
+        k, self.k = self.k, (self.k + 1) % len(self.ring)
+        cur = torch.cuda.current_stream()
+        if self.free_ev[k] is not None:
+            cur.wait_event(self.free_ev[k])                          # the slot's previous send has left
+        buf = self.ring[k][:rows.shape[0]]
+        buf.copy_(rows)
+        self.stream.wait_stream(cur)
+        with torch.cuda.stream(self.stream):
+            dist.send(buf, self.peer, group=self.group)
+            ev = torch.cuda.Event()
+            ev.record(self.stream)
+        self.free_ev[k] = ev
+
+    def recv(self, out: torch.Tensor) -> torch.Tensor:
+        if not self.cuda:
+            return super().recv(out)
+        self.bytes_moved += out.numel() * out.element_size()
+        k, self.k = self.k, (self.k + 1) % len(self.ring)
+        if self.free_ev[k] is not None:
+            self.stream.wait_event(self.free_ev[k])                  # the slot's previous rows were copied out
+        buf = self.ring[k][:out.shape[0]]
+        with torch.cuda.stream(self.stream):
+            dist.recv(buf, self.peer, group=self.group)
+        cur = torch.cuda.current_stream()
+        cur.wait_stream(self.stream)
+        out.copy_(buf)
+        ev = torch.cuda.Event()
+        ev.record(cur)
+        self.free_ev[k] = ev
+        return out
+
+
 def run_pipelined(stage: int, stages: int, micro_batches: list[torch.Tensor], stage_fn, hop_prev: Hop | None,
                   hop_next: Hop | None, out_like) -> list[torch.Tensor]:
     """Drive one stage over a list of micro-batches: receive (unless first stage), compute, send (unless last).

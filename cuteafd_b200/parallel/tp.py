@@ -43,12 +43,19 @@ class TpContext:
         self.off_rs_flags = o; o = _align(o + 64)
         self.off_ag_flags = o; o = _align(o + 64)
         self.off_ready_flags = o; o = _align(o + 64)
+        self.off_head_flags = o; o = _align(o + 64)
+        self.head_rows = max(64, min(max_rows, 4096))                    # rows one sharded-head selection can cover
+        self.off_head_table = o; o = _align(o + n * self.head_rows * 8)  # (value, id) per rank and row
         self.heap = SymmetricHeap(o, device, self.group)
         self.partials = self.heap.view(self.off_partials, n * R * hidden * 2, torch.bfloat16).view(n, R, hidden)
         self.x_full = self.heap.view(self.off_x, n * R * hidden * 2, torch.bfloat16).view(n * R, hidden)
         self.rs_flags = self.heap.view(self.off_rs_flags, 64, torch.int32)
         self.ag_flags = self.heap.view(self.off_ag_flags, 64, torch.int32)
         self.ready_flags = self.heap.view(self.off_ready_flags, 64, torch.int32)
+        self.head_flags = self.heap.view(self.off_head_flags, 64, torch.int32)
+        self.head_table = self.heap.view(self.off_head_table, n * self.head_rows * 8, torch.int64)
+        self._head_cand = None
+        self.head_epoch = torch.zeros(1, dtype=torch.int32, device=device)   # its own counter: ``epoch`` belongs to the step protocol
         self._ready_ptrs = (C.c_void_p * 8)(*[self.heap.ptrs[r] + self.off_ready_flags + 4 * self.rank for r in range(n)])
         self.residual = torch.zeros(R, hidden, dtype=torch.bfloat16, device=device)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
@@ -130,6 +137,37 @@ class TpContext:
         flag-waiting GEMM)."""
         for r in range(self.ranks):
             K.wait_flag(self.ag_flags.data_ptr() + 4 * r, self.epoch)
+
+    # ---- vocabulary-sharded head: candidates only cross the fabric ------------------------------------------------
+    def head_pick(self, local_logits: torch.Tensor, lo: int, out: torch.Tensor) -> torch.Tensor:
+        """Greedy ids [T] from this rank's slice of the logits ([T, hi - lo] fp32, global ids lo..hi): per-slice
+        candidates, then one kernel that exchanges (value, id) with every rank and picks (ties to the lowest id).
+        Every rank calls it for the same rows, the same number of times (the exchange counts its own rounds)."""
+        T, V = local_logits.shape
+        assert 0 < T <= self.head_rows and local_logits.dtype == torch.float32
+        L = _n.cuda_lib()
+        slices = L.cafd_argmax_slices()
+        if self._head_cand is None:
+            self._head_cand = (torch.empty(self.head_rows * slices, dtype=torch.float32, device=self.device),
+                               torch.empty(self.head_rows * slices, dtype=torch.int32, device=self.device))
+        cv, ci = self._head_cand
+        if V > 0:
+            _n.check(L.cafd_argmax_candidates(local_logits.data_ptr(), cv.data_ptr(), ci.data_ptr(), T, V, local_logits.stride(0),
+                                              K._stream()), "argmax_candidates")
+        else:                                                            # a rank past the end of the vocabulary never wins
+            cv[:T * slices].fill_(float("-inf")); ci[:T * slices].fill_(0x7fffffff)
+        K.bump_epoch(self.head_epoch)
+        a = _n.TpHeadArgs()
+        a.cand_v, a.cand_i = cv.data_ptr(), ci.data_ptr()
+        for r in range(self.ranks):
+            a.table_out[r] = self.heap.ptrs[r] + self.off_head_table
+            a.flags_out[r] = self.heap.ptrs[r] + self.off_head_flags + 4 * self.rank
+        a.table_in, a.flags_in = self.head_table.data_ptr(), self.head_flags.data_ptr()
+        a.epoch, a.done_counter, a.status = self.head_epoch.data_ptr(), self.done[2:3].data_ptr(), K.status_word(self.device).data_ptr()
+        a.out = out.data_ptr()
+        a.ranks, a.my_rank, a.max_rows, a.T, a.slices, a.lo = self.ranks, self.rank, self.head_rows, T, slices, lo
+        _n.check(L.cafd_tp_head_pick(C.byref(a), K._stream()), "tp_head_pick")
+        return out
 
     # ---- all-gather -> GEMM -----------------------------------------------------------------------------------
     def column_parallel_linear(self, total_rows: int, w_shard: torch.Tensor, out: torch.Tensor, w_up: torch.Tensor | None = None) -> torch.Tensor:

@@ -163,6 +163,15 @@ class OracleBackend:
         h.dead = True
         self.quarantined.append(h)            # pages stay allocated: never handed to another request
 
+    def state_hash(self, h: _Handle) -> str:
+        """Probe ``record_state``: hash of the sequence's cached rows, every layer, in position order."""
+        import hashlib
+        d = hashlib.blake2b(digest_size=16)
+        for rows in h.kv.rows:
+            for r in rows:
+                d.update(r.detach().float().contiguous().numpy().tobytes())
+        return d.hexdigest()
+
     def pages_of(self, h: _Handle) -> int:
         return len(h.seq.pages)
 
@@ -499,6 +508,29 @@ class EngineBackend:
     def quarantine(self, h: _Handle) -> None:
         h.dead = True
         self.quarantined.append(h)
+
+    def state_hash(self, h: _Handle) -> str:
+        """Probe ``record_state``: hash of the bytes the sequence's positions [0, kv_len) hold in every paged pool
+        (K / V pages, latent records, index vectors), every layer, in position order.  Synchronous: the pages are copied
+        to the host.  Two sequences with the same tokens hash equal whatever pages they sit in
+        (rust/crates/cuteafd-api/src/openai/probe.rs:94-96)."""
+        import hashlib
+        kv = self.engine.kv if hasattr(self.engine, "kv") else self.engine.inner.kv
+        seq, d = h.seq, hashlib.blake2b(digest_size=16)
+        n = seq.kv_len
+        if n == 0:
+            return d.hexdigest()
+        pages = torch.tensor(seq.pages[: (n + PAGE - 1) // PAGE], dtype=torch.long, device=self.engine.device)
+        tail = n - (len(pages) - 1) * PAGE
+        for name in ("k", "v", "c", "idx"):
+            for pool in getattr(kv, name, []) or []:
+                got = pool.index_select(0, pages)                    # [pages, ..., 64 positions, ...]
+                ax = 2 if name in ("k", "v") else 1                  # K / V pages are [page, head, position, dim]
+                last = got[-1:].narrow(ax, 0, tail)
+                for part in (got[:-1], last):
+                    if part.numel():
+                        d.update(part.contiguous().view(torch.uint8).cpu().numpy().tobytes())
+        return d.hexdigest()
 
     def pages_of(self, h: _Handle) -> int:
         return len(h.seq.pages)

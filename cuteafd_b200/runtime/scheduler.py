@@ -65,6 +65,14 @@ class Request:
     stop_texts: tuple = ()             # stop strings longer than one token: matched on the decoded text by the server
     top_logprobs: int = 0              # > 0: keep the chosen token's log-probability and this many alternatives per token
     cold: bool = False                 # probe: do not look the prompt up in the prefix cache
+    # probe: teacher-forced scoring.  Run the prompt, record the logits row predicting every prompt token from this index
+    # on, end without generating (rust/crates/cuteafd-api/src/openai/probe.rs:50-53).  ``score_want``: per predicted
+    # position, token ids whose log-probability to report; ``verify_rows``: width of the decode-shaped scoring steps.
+    score_from: int | None = None
+    score_want: dict = field(default_factory=dict)
+    score_positions: tuple | None = None
+    verify_rows: int = 0
+    record_state: bool = False         # probe: hash the sequence's persistent state at the prompt and turn frontiers
     media: Any = None                  # list of media spans (prompt position, embedding rows) for ids above the vocabulary
     rid: int = 0
     events: "queue.Queue[tuple]" = field(default_factory=queue.Queue)
@@ -88,6 +96,8 @@ class Active:
     top_rows: list = field(default_factory=list)   # per selected token: (token, logprob, top ids, top logprobs)
     guard: Any = None                  # RepeatGuard (loop abort), None when the detector is off
     finish_detail: str = ""
+    score_rows: list = field(default_factory=list)     # probe ``score_from``: one record per predicted prompt position
+    state_hashes: list = field(default_factory=list)   # probe ``record_state``: (frontier, kv length, hash)
 
 
 @dataclass
@@ -223,7 +233,7 @@ class Scheduler:
         while self.pending and len(self.prefilling) + len(self.decoding) < self.max_active:
             req = self.pending[0]
             try:
-                handle, cached = self.be.open(req.prompt, cold=True) if req.cold else self.be.open(req.prompt)
+                handle, cached = self.be.open(req.prompt, cold=True) if (req.cold or req.score_from is not None) else self.be.open(req.prompt)
             except Exception as e:                      # a failed restore is a miss, not an error
                 req.events.put(("error", FAIL_UNAVAILABLE, f"open failed: {e}"))
                 self.pending.pop(0)
@@ -243,9 +253,67 @@ class Scheduler:
                 handle.media = req.media
             a = Active(req, handle, cached, prompt_done=cached, kv_len=cached)
             a.guard = self.loop_abort.guard() if self.loop_abort is not None else None
-            self.prefilling.append(a)
             self.stats.admitted += 1
             self.stats.cached_tokens += cached
+            if req.score_from is not None:
+                self._score(a)
+                continue
+            self.prefilling.append(a)
+
+    # ---- probes ------------------------------------------------------------------------------------------
+    def _score(self, a: Active) -> None:
+        """Teacher-forced scoring of a prompt (a synchronous diagnostic): prefill up to the first scored position, then
+        decode-shaped steps of ``verify_rows`` prompt tokens each, recording the row that predicts every prompt token
+        from ``score_from`` on.  Nothing is generated and nothing is captured."""
+        req, p = a.req, a.req.prompt
+        first = max(1, min(int(req.score_from), len(p)))           # token 0 has no predicting row
+        width = max(1, min(req.verify_rows or self.be.max_decode_rows, self.be.max_decode_rows))
+        keep = None if req.score_positions is None else set(int(x) for x in req.score_positions)
+
+        def record(position: int, row: torch.Tensor) -> None:
+            if position >= len(p) or (keep is not None and position not in keep):
+                return
+            lp = torch.log_softmax(row.float(), dim=-1).cpu()
+            rec = {"position": position, "token": int(p[position]), "logprob": float(lp[p[position]]),
+                   "hash": sampling.row_hash(row)}
+            if req.top_logprobs:
+                v, i = lp.topk(min(req.top_logprobs, lp.numel()))
+                rec["top_ids"], rec["top_logprobs"] = i.tolist(), v.tolist()
+            want = req.score_want.get(position) or req.score_want.get(str(position))
+            if want:
+                rec["want"] = {int(t): float(lp[int(t)]) for t in want if 0 <= int(t) < lp.numel()}
+            a.score_rows.append(rec)
+
+        try:
+            logits = None
+            while a.prompt_done < first:
+                n = min(self.be.prefill_chunk, first - a.prompt_done)
+                logits = self.be.prefill(a.handle, p[a.prompt_done:a.prompt_done + n], a.prompt_done + n == first)
+                a.prompt_done += n
+                self.stats.prefill_tokens += n
+            if logits is not None:
+                record(first, logits[0] if logits.dim() == 2 else logits)
+            pos = a.prompt_done
+            while pos < len(p) - 1:                                 # feeding token i gives the row predicting token i + 1
+                n = min(width, len(p) - 1 - pos)
+                rows = self.be.verify([a.handle], [p[pos:pos + n]])
+                self.be.commit(a.handle, pos + n)
+                for j in range(n):
+                    record(pos + j + 1, rows[j])
+                pos += n
+                self.stats.verify_rows += n
+            a.kv_len = pos
+            if req.record_state:
+                self._record_state(a, "prompt")
+        except Exception as e:
+            self._fail([a], f"scoring failed: {e}", device=_device_failure(e))
+            return
+        self._finish(a, "stop", retain=False)
+
+    def _record_state(self, a: Active, frontier: str) -> None:
+        fn = getattr(self.be, "state_hash", None)
+        if fn is not None:
+            a.state_hashes.append({"frontier": frontier, "kv_len": a.kv_len, "hash": fn(a.handle)})
 
     # ---- prefill -----------------------------------------------------------------------------------
     PACK_MAX = 8                       # prompts whose chunks may share one prefill step
@@ -284,6 +352,8 @@ class Scheduler:
             if last:
                 self.prefilling.remove(a)
                 self._safe(lambda a=a: self.be.capture(a.handle, "prompt"))
+                if a.req.record_state:
+                    self._safe(lambda a=a: self._record_state(a, "prompt"))
                 tok = self._select(a, logits[0] if logits.dim() == 2 else logits, len(a.req.prompt))
                 a.first_token_at = time.monotonic()
                 if tok is None:
@@ -315,6 +385,8 @@ class Scheduler:
         if last:
             self.prefilling.pop(0)
             self._safe(lambda: self.be.capture(a.handle, "prompt"))
+            if a.req.record_state:
+                self._safe(lambda: self._record_state(a, "prompt"))
             tok = self._select(a, logits[0] if logits.dim() == 2 else logits, len(a.req.prompt))
             a.first_token_at = time.monotonic()
             if tok is None:
@@ -502,6 +574,8 @@ class Scheduler:
     def _finish(self, a: Active, reason: str | None, retain: bool = True) -> None:
         if reason is not None and retain:
             self._safe(lambda: self.be.capture(a.handle, "turn"))
+            if a.req.record_state:
+                self._safe(lambda: self._record_state(a, "turn"))
         self._safe(lambda: self.be.release(a.handle))
         self.reserve.release(a.req.rid)
         self.policy.forget(a.req.rid)
@@ -512,6 +586,10 @@ class Scheduler:
                      "speculation": dict(a.spec, request_id=a.req.rid)}
             if a.finish_detail:
                 usage["finish_detail"] = a.finish_detail
+            if a.req.score_from is not None:
+                usage["score_rows"] = a.score_rows
+            if a.state_hashes:
+                usage["state_hashes"] = a.state_hashes
             if a.req.top_logprobs:
                 # rows were kept per selection; a reply cut by a stop or a limit keeps the rows of the emitted tokens
                 usage["top_rows"] = a.top_rows[: len(a.generated)]

@@ -7,7 +7,9 @@ request 400, unavailable 503, retry 429 with ``Retry-After: 1``, worker 500
 (rust/crates/cuteafd-api/src/openai.rs:281-286; docs/client-apis.md:40-50).  ``usage.speculation``
 carries {request_id, proposed, accepted, cycles} (docs/client-apis.md:31-38).  The probe header
 ``x-cuteafd-probe`` carries a JSON ProbeSpec: prompt_ids (synthetic token-id prompts),
-no_speculation, record_rows, cold (skip the prefix cache), top_k (top ids and log-probabilities of every selected row)
+no_speculation, record_rows, cold (skip the prefix cache), top_k (top ids and log-probabilities of every selected row),
+score_from / want / score_positions / verify_rows (teacher-forced scoring of the prompt: one record per predicted
+position, no generation) and record_state (hashes of the sequence's persistent state at the prompt and turn frontiers)
 (rust/crates/cuteafd-api/src/openai/probe.rs:19-110).
 """
 from __future__ import annotations
@@ -233,10 +235,25 @@ def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, f
     keep = max(n_top, 1) if (body.get("logprobs") or n_top) else 0
     keep = max(keep, int(probe.get("top_k", 0) or 0))
     stop_texts = _stop_texts(body, tok)                    # validates the type of ``stop`` before anything encodes it
+    score_from = probe.get("score_from")
+    if score_from is not None:
+        if isinstance(score_from, bool) or not isinstance(score_from, int) or not 0 <= score_from <= len(prompt):
+            raise BadRequest("probe score_from must be an index into the prompt")
+        if spans:
+            raise BadRequest("probe score_from scores token prompts only")
+    want = probe.get("want") or {}
+    if not isinstance(want, dict):
+        raise BadRequest("probe want must map positions to token ids")
+    verify_rows = int(probe.get("verify_rows") or 0)
+    if verify_rows < 0:
+        raise BadRequest("probe verify_rows must be positive")
+    pos = probe.get("score_positions")
     return Request(prompt=prompt, max_tokens=max_tokens, params=_params(body), stop_ids=_stops(body, tok),
                    speculation=not probe.get("no_speculation", False), record_rows=bool(probe.get("record_rows", False)),
                    constraint=cons, media=spans, top_logprobs=keep, cold=bool(probe.get("cold", False)),
-                   stop_texts=stop_texts)
+                   stop_texts=stop_texts, score_from=score_from, score_want={int(k): [int(t) for t in v] for k, v in want.items()},
+                   score_positions=None if pos is None else tuple(int(x) for x in pos), verify_rows=verify_rows,
+                   record_state=bool(probe.get("record_state", False)))
 
 
 def logprobs_block(tok, top_rows: list, n_top: int) -> dict:

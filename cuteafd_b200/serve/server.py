@@ -353,6 +353,9 @@ def make_handler(state: ServerState):
                 if body.get("logprobs") or body.get("top_logprobs"):
                     lps = api.logprobs_block(state.tok, usage["top_rows"], int(body.get("top_logprobs") or 0))
             out = api.chat_completion(model, out_text, finish, usage, rows or None, lps)
+            for key in ("score_rows", "state_hashes"):                             # probe diagnostics ride beside the reply
+                if usage.get(key) is not None:
+                    out.setdefault("probe", {})[key] = usage.pop(key)
             if usage.get("top_rows") is not None and lps is None:            # asked for through the probe header
                 out.setdefault("probe", {})["top_rows"] = [{"token": t, "logprob": lp, "top_ids": ids, "top_logprobs": v}
                                                            for t, lp, ids, v in usage["top_rows"]]
@@ -608,29 +611,32 @@ def _build_afd_rank(args, snapshot, world: int, num_pages: int, pages_per_seq: i
     dev = torch.device("cuda", local)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     dist.init_process_group("nccl", device_id=dev)
-    params = None
-    expert_format = "bf16"
+    dep = {}
+    if getattr(args, "deployment", ""):
+        with open(args.deployment) as f:
+            dep = json.load(f)
+        if dep.get("world_size", world) != world:
+            raise SystemExit(f"deployment names {dep['world_size']} ranks, the process group has {world}")
+    n_att = int(dep.get("attention_ranks", 1)) * int(dep.get("pipeline_stages", 1))
+    if n_att != 1:
+        # data-parallel attention replicas run in lockstep under one driver (the benchmark's SPMD generator); the HTTP
+        # scheduler drives a single attention rank
+        raise SystemExit("serve drives one attention rank per deployment; plan with --attention-ranks 1")
+    if dep.get("kv_pool_tokens"):
+        num_pages = max(num_pages, min(int(dep["kv_pool_tokens"]) // 64, num_pages * 4))
     if snapshot:
-        from ..loader.load import load_params, open_snapshot
-        from ..ref.split import expert_range
-        cfg0 = open_snapshot(snapshot).cfg
-        if rank:                                   # an expert rank reads its own expert range and nothing else
-            lo, hi = expert_range(cfg0.num_experts, world - 1, rank - 1)
-
-            def mine(pre: str) -> bool:
-                return ".mlp.experts." in pre and lo <= int(pre.split(".mlp.experts.")[1].split(".")[0]) < hi
-            part = dict(keep=mine)
-        else:
-            part = dict(exclude=".mlp.experts.")
-        cfg, params = load_params(snapshot, dtype=torch.bfloat16, **part)
-        if cfg.weight_format == "fp8_block128":
-            expert_format = "fp8"                  # experts shipped as block-scaled E4M3 stay E4M3 on the expert ranks
+        # the attention rank reads everything but the routed experts; every expert rank reads its own expert range in
+        # the stored format (E4M3 block-scaled, MXFP4, NVFP4 stay as stored)
+        from ..loader.load import open_snapshot
+        cfg = open_snapshot(snapshot).cfg
+        kw = dict(snapshot=snapshot)
     else:
         cfg = PRESETS[args.preset or "qwen3-30b-a3b"]()
         if args.layers:
             cfg = cfg.replace(num_layers=args.layers)
+        kw = {}
     h = build_afd(cfg, dev, rank, world, max_tokens=max(2048, rows), max_seqs=rows, num_pages=num_pages,
-                  pages_per_seq=pages_per_seq, params=params, prefill_chunk=2048, expert_format=expert_format)
+                  pages_per_seq=pages_per_seq, prefill_chunk=2048, n_attention=n_att, **kw)
     torch.cuda.synchronize()
     dist.barrier()
     if h.worker is not None:

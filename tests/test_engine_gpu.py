@@ -250,6 +250,44 @@ def test_prompt_packing_on_the_engine():
     assert same == len(prompts), (alone, packed)
 
 
+def test_probe_scoring_and_state_hash_on_the_engine():
+    """Probe fields on the CUDA backend: teacher-forced scoring rows agree with the oracle's teacher-forced log-probs, and
+    the state hash of a prompt is the same cold and through the prefix cache (pages differ, bytes do not)."""
+    from cuteafd_b200.ops import kernels as K
+    from cuteafd_b200.ref.model import KvState, RefDecoder
+    from cuteafd_b200.runtime.backends import EngineBackend
+    from cuteafd_b200.runtime.scheduler import Request, Scheduler, collect
+    cfg = small_cfg()
+    params, eng, _ = build(cfg, False)
+    be = EngineBackend(eng, 64, 8, prefill_chunk=64, max_decode_rows=8, use_graphs=False)
+    sched = Scheduler(be, max_active=2)
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, cfg.vocab_size, (150,), generator=g).tolist()
+
+    def run(req):
+        sched.submit(req)
+        for _ in range(300):
+            sched.step()
+            if not sched.pending and not sched.prefilling and not sched.decoding:
+                break
+        return collect(req, timeout=5)
+    out = run(Request(prompt=list(ids), max_tokens=4, score_from=100, verify_rows=5, top_logprobs=1))
+    assert out["error"] is None and out["tokens"] == []
+    rows = out["usage"]["score_rows"]
+    assert [r["position"] for r in rows] == list(range(100, 150))
+    with torch.no_grad():
+        lp = torch.log_softmax(RefDecoder(cfg, params).forward(torch.tensor(ids), KvState(cfg)).float(), -1)
+    errs = sorted(abs(r["logprob"] - float(lp[r["position"] - 1, r["token"]])) for r in rows)
+    assert errs[len(errs) // 2] < 0.05 and errs[-1] < 0.5, errs
+    a = run(Request(prompt=list(ids), max_tokens=3, cold=True, record_state=True, speculation=False))
+    b = run(Request(prompt=list(ids), max_tokens=3, record_state=True, speculation=False))
+    ha, hb = a["usage"]["state_hashes"], b["usage"]["state_hashes"]
+    assert b["usage"]["cached_tokens"] >= 64 and [h["frontier"] for h in ha] == ["prompt", "turn"]
+    assert ha[0]["hash"] == hb[0]["hash"] and ha[0]["hash"] != ha[1]["hash"]
+    torch.cuda.synchronize()
+    assert K.read_status() == 0
+
+
 def test_host_tier_evict_and_restore_on_the_engine():
     """Pinned-host tier behind the device prefix cache: snapshots evicted by other traffic are copied out on the side
     stream and copied back on a later hit; the request served from the host tier emits the same tokens and the same

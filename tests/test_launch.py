@@ -1,0 +1,132 @@
+"""Launcher: deployment document -> one process per rank, supervised; configuration keys -> flags."""
+import json
+import os
+import signal
+import sys
+import threading
+import time
+
+import pytest
+
+from cuteafd_b200 import cli
+from cuteafd_b200 import launch as LA
+
+
+def _spec(world=3):
+    import hashlib
+    ranks = [{"rank": 0, "device": 0, "role": "attention", "memory": {}, "free_bytes": 0, "tp_rank": 0, "pp_stage": 0}]
+    per = 16 // (world - 1)
+    for r in range(1, world):
+        ranks.append({"rank": r, "device": r, "role": "experts", "memory": {}, "free_bytes": 0, "experts": [(r - 1) * per, r * per]})
+    body = {"model": "m", "source": "/snap", "family": "f", "layout": f"1+{world - 1}", "world_size": world, "attention_ranks": 1,
+            "expert_ranks": world - 1, "pipeline_stages": 1, "rendezvous": {"master_addr": "127.0.0.1", "master_port": 29999},
+            "ranks": ranks}
+    body["plan_hash"] = hashlib.sha256(json.dumps(body, sort_keys=True).encode()).hexdigest()[:16]
+    return json.loads(json.dumps(body))
+
+
+def _child(code: str):
+    return lambda spec_path, spec, entry, extra: [sys.executable, "-c", code.replace("RANK_ID", str(entry["rank"]))]
+
+
+def test_validate_refuses_bad_documents():
+    LA.validate(_spec())
+    bad = _spec(); bad["ranks"][2]["device"] = 1
+    with pytest.raises(ValueError, match="share a device"):
+        LA.validate(bad)
+    bad = _spec(); bad["ranks"][2]["experts"] = [9, 16]
+    with pytest.raises(ValueError, match="tile"):
+        LA.validate(bad)
+    bad = _spec(); bad["layout"] = "edited"
+    with pytest.raises(ValueError, match="plan_hash"):
+        LA.validate(bad)
+    bad = _spec(); bad["ranks"][0]["role"] = "experts"
+    with pytest.raises(ValueError, match="rank 0"):
+        LA.validate(bad)
+
+
+def test_rank_environment_and_commands(tmp_path):
+    L = LA.build_launch(_spec(), str(tmp_path), ["--port", "8123"])
+    assert json.load(open(tmp_path / "deployment.json"))["world_size"] == 3
+    assert [r.env["RANK"] for r in L.ranks] == ["0", "1", "2"] and L.ranks[2].env["LOCAL_RANK"] == "2"
+    assert all(r.env["WORLD_SIZE"] == "3" and r.env["MASTER_PORT"] == "29999" for r in L.ranks)
+    assert L.ranks[1].argv[-2:] == ["--port", "8123"] and "--deployment" in L.ranks[1].argv and "/snap" in L.ranks[1].argv
+    assert "rank 2 [experts]" in LA.describe(L)
+
+
+def test_failed_rank_takes_the_deployment_down(tmp_path):
+    code = "import sys, time\nif RANK_ID == 2:\n    time.sleep(0.3); sys.exit(3)\ntime.sleep(60)"
+    L = LA.build_launch(_spec(), str(tmp_path), [], argv_for=_child(code))
+    L.grace_s = 1.0
+    L.start()
+    assert os.path.exists(L.pid_file)
+    t0 = time.monotonic()
+    rc = L.supervise(poll_s=0.05)
+    assert rc == 3 and time.monotonic() - t0 < 20
+    assert all(r.proc.poll() is not None for r in L.ranks) and not os.path.exists(L.pid_file)
+
+
+def test_clean_exit_and_stop_by_pid_file(tmp_path):
+    L = LA.build_launch(_spec(2), str(tmp_path / "a"), [], argv_for=_child("print('rank', RANK_ID)"))
+    L.start()
+    assert L.supervise(poll_s=0.05) == 0
+    assert "rank 1" in open(L.ranks[1].log).read()
+    # a deployment whose launcher is gone: stop signals the ranks by their recorded pids
+    L2 = LA.build_launch(_spec(2), str(tmp_path / "b"), [], argv_for=_child("import time\ntime.sleep(60)"))
+    L2.start()
+    doc = json.load(open(L2.pid_file))
+    doc["launcher"] = 0
+    json.dump(doc, open(L2.pid_file, "w"))
+    assert LA.stop_by_pid_file(L2.pid_file) == 0
+    for r in L2.ranks:
+        assert r.proc.wait(timeout=10) in (-signal.SIGINT, -signal.SIGTERM, 1, 130)
+
+
+def test_launcher_stops_its_ranks_on_sigterm(tmp_path):
+    L = LA.build_launch(_spec(2), str(tmp_path), [], argv_for=_child("import time\ntime.sleep(60)"))
+    L.grace_s = 1.0
+    L.start()
+    threading.Timer(0.4, lambda: os.kill(os.getpid(), signal.SIGTERM)).start()
+    assert L.supervise(poll_s=0.05) == 0
+    assert all(r.proc.poll() is not None for r in L.ranks)
+
+
+def test_launch_dry_run_plans_a_snapshot(tmp_path, capsys):
+    from cuteafd_b200 import tiny_moe
+    from cuteafd_b200.loader.snapshot import write_random_snapshot
+    snap = write_random_snapshot(tiny_moe(), str(tmp_path / "snap"), fmt="bf16", seed=0)
+    rc = cli.main(["launch", snap, "--gpus", "3", "--attention-ranks", "1", "--expert-ranks", "2", "--dry-run", "--run-dir",
+                   str(tmp_path / "run"), "--port", "8111"])
+    out = capsys.readouterr().out
+    assert rc == 0, out
+    spec = json.load(open(tmp_path / "run" / "deployment.json"))
+    assert spec["world_size"] == 3 and [tuple(r["experts"]) for r in spec["ranks"][1:]] == [(0, 4), (4, 8)]
+    assert out.count("cuteafd_b200.cli serve") == 3 and "--port 8111" in out
+    # an edited document is refused; the stored one starts (dry) as it is
+    assert cli.main(["launch", "--deployment", str(tmp_path / "run" / "deployment.json"), "--dry-run", "--run-dir", str(tmp_path / "r2")]) == 0
+    spec["world_size"] = 4
+    json.dump(spec, open(tmp_path / "bad.json", "w"))
+    assert cli.main(["launch", "--deployment", str(tmp_path / "bad.json"), "--dry-run", "--run-dir", str(tmp_path / "r3")]) == 2
+
+
+def test_config_keys_become_flags(tmp_path):
+    cfg = tmp_path / "cuteafd.config"
+    cfg.write_text("MODEL=/models/x  # the checkpoint\nCONCURRENCY=3\nHTTP_QUEUE_DEPTH=7\nSPECULATOR=off\nPORT=8111\n")
+    ap = cli.build_parser()
+    argv = ["--config", str(cfg), "--set", "CONCURRENCY=5", "serve", "--port", "9000"]
+    a = ap.parse_args(argv)
+    a.file_config = cli.load_config_file(a.config, a.set, cli.CONFIG_KEYS)
+    cli.apply_config(ap, a, argv)
+    assert (a.snapshot, a.concurrency, a.queue_depth, a.speculator, a.port) == ("/models/x", 5, 7, "off", 9000)
+    argv = ["--config", str(cfg), "launch", "--dry-run"]
+    a = ap.parse_args(argv)
+    a.file_config = cli.load_config_file(a.config, a.set, cli.CONFIG_KEYS)
+    cli.apply_config(ap, a, argv)
+    assert a.model == "/models/x" and a.concurrency == 3 and a.port == 8111
+    with pytest.raises(SystemExit):
+        cli.load_config_file("", ["NOPE=1"], cli.CONFIG_KEYS)
+    bad = ["--set", "DECODE_LANES=5", "plan", "m"]
+    a = ap.parse_args(bad)
+    a.file_config = cli.load_config_file(a.config, a.set, cli.CONFIG_KEYS)
+    with pytest.raises(SystemExit):
+        cli.apply_config(ap, a, bad)

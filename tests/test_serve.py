@@ -367,6 +367,45 @@ def test_logprobs_and_probe_cold_top_k(server):
     assert call(server, "POST", "/v1/chat/completions", dict(body, top_logprobs=50))[0] == 400
 
 
+def test_probe_score_from_and_record_state(server):
+    """Teacher-forced scoring through the probe header: one record per predicted prompt position from ``score_from`` on,
+    nothing generated; the rows equal the oracle's own teacher-forced logits, and the width of the scoring steps does
+    not change them.  ``record_state`` hashes the sequence state at the prompt and turn frontiers."""
+    from cuteafd_b200.ref.model import KvState, RefDecoder
+    cfg = tiny_moe()
+    ids = [(7 * i + 3) % cfg.vocab_size for i in range(150)]
+    msg = {"messages": [{"role": "user", "content": "x"}], "max_tokens": 4}
+
+    def score(**kw):
+        probe = dict({"prompt_ids": ids, "score_from": 100, "top_k": 2, "want": {"120": [1, 2, 3]}}, **kw)
+        st, _, raw = call(server, "POST", "/v1/chat/completions", msg, {"x-cuteafd-probe": json.dumps(probe)})
+        assert st == 200, raw
+        return json.loads(raw)
+    out = score(verify_rows=7)
+    rows = out["probe"]["score_rows"]
+    assert out["usage"]["completion_tokens"] == 0 and out["choices"][0]["message"]["content"] == ""
+    assert [r["position"] for r in rows] == list(range(100, 150)) and [r["token"] for r in rows] == ids[100:]
+    ref = RefDecoder(cfg, init_weights(cfg, seed=0))
+    with torch.no_grad():
+        lp = torch.log_softmax(ref.forward(torch.tensor(ids), KvState(cfg)).float(), -1)
+    for r in rows:
+        assert abs(r["logprob"] - float(lp[r["position"] - 1, r["token"]])) < 1e-3
+        assert r["top_ids"][0] == int(lp[r["position"] - 1].argmax()) and len(r["top_ids"]) == 2
+    assert set(rows[20]["want"]) == {"1", "2", "3"} and "want" not in rows[0]
+    wide = score(verify_rows=64, score_positions=[101, 149])["probe"]["score_rows"]
+    assert [r["position"] for r in wide] == [101, 149]
+    assert abs(wide[1]["logprob"] - rows[-1]["logprob"]) < 1e-4
+    assert call(server, "POST", "/v1/chat/completions", msg,
+                {"x-cuteafd-probe": json.dumps({"prompt_ids": ids, "score_from": 999})})[0] == 400
+    # state hashes: the same prompt gives the same prompt-frontier hash cold and through the prefix cache
+    p2 = {"prompt_ids": ids, "record_state": True, "no_speculation": True}
+    a = json.loads(call(server, "POST", "/v1/chat/completions", msg, {"x-cuteafd-probe": json.dumps(dict(p2, cold=True))})[2])
+    b = json.loads(call(server, "POST", "/v1/chat/completions", msg, {"x-cuteafd-probe": json.dumps(p2)})[2])
+    ha, hb = a["probe"]["state_hashes"], b["probe"]["state_hashes"]
+    assert [h["frontier"] for h in ha] == ["prompt", "turn"] and ha[0]["kv_len"] == 150
+    assert ha[0]["hash"] == hb[0]["hash"] and ha[0]["hash"] != ha[1]["hash"]
+
+
 def test_console_events_and_fabric_phase(server):
     c = http.client.HTTPConnection("127.0.0.1", server.port, timeout=30)
     c.request("GET", "/v1/console/events?period=0.05&count=3", headers={"Authorization": "Bearer sekret"})

@@ -23,7 +23,7 @@ def _cfg():
                        num_shared_experts=0, norm_topk_prob=True)
 
 
-def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
+def _worker(rank: int, world: int, port: int, out_dir: str, shard_head: bool = False, vocab: int = 2048) -> None:
     import torch.distributed as dist
 
     from cuteafd_b200.models.gqa_moe import GqaMoeWeights
@@ -37,12 +37,17 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     K.set_wait_limit_ns(2_000_000_000)
-    cfg = _cfg()
+    cfg = _cfg().replace(vocab_size=vocab, num_kv_heads=max(2, world))
     params = {k: v.to(torch.bfloat16).float() for k, v in init_weights(cfg, seed=0).items()}
     ref = RefDecoder(cfg, params)
     errs = {}
     for use_graphs in (False, True):
-        eng = TpGqaMoeEngine(cfg, GqaMoeWeights.from_params(cfg, params, dev), num_pages=64, max_tokens=256, max_seqs=8)
+        eng = TpGqaMoeEngine(cfg, GqaMoeWeights.from_params(cfg, params, dev), num_pages=64, max_tokens=256, max_seqs=8,
+                             shard_head=shard_head)
+        picks_ok = True
+
+        def whole(n):            # logits of the step's first n rows, whole vocabulary
+            return eng.full_logits(eng.local_logits[:n, :eng.head_hi - eng.head_lo]) if shard_head else eng.logits[:n]
         gen = Generator(eng, PagePool(64), max_pages_per_seq=8, max_seqs=8, prefill_chunk=128, use_graphs=use_graphs)
         g = torch.Generator().manual_seed(1)
         prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g) for n in (200, 77, 5)]
@@ -50,39 +55,45 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
         with torch.no_grad():
             for p in prompts:
                 s = gen.table.new()
-                gen.prefill(s, p.tolist())
+                first = gen.prefill(s, p.tolist())
                 kvs = KvState(cfg)
                 rl = ref.forward(p, kvs)[-1]
-                got = eng.logits[0].float().cpu()
+                got = whole(1)[0].float().cpu()
+                picks_ok &= first == int(got.argmax())
                 e.append((got - rl).abs().max().item() / max(rl.abs().max().item(), 1.0))
                 seqs.append(s); kvs_all.append(kvs); last.append(int(rl.argmax()))
             for step in range(4):
-                gen.decode(seqs, last)
+                new = gen.decode(seqs, last)
                 torch.cuda.synchronize()
                 assert K.read_status() == 0
+                full = whole(len(seqs)).float().cpu()
                 for i in range(len(seqs)):
                     rl = ref.forward(torch.tensor([last[i]]), kvs_all[i])[-1]
-                    got = eng.logits[i].float().cpu()
+                    got = full[i]
+                    picks_ok &= new[i] == int(got.argmax())               # the exchanged winners = argmax of the gathered row
                     e.append((got - rl).abs().max().item() / max(rl.abs().max().item(), 1.0))
                     last[i] = int(rl.argmax())
         errs["graphs" if use_graphs else "eager"] = e
         torch.cuda.synchronize()
         dist.barrier()
     assert K.read_status() == 0
-    torch.save({"errs": errs, "collectives": eng.collectives}, os.path.join(out_dir, f"r{rank}.pt"))
+    torch.save({"errs": errs, "collectives": eng.collectives, "picks_ok": picks_ok}, os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_tp_attention_engine_matches_oracle(tmp_path):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("world,shard_head,vocab", [(2, False, 2048), (2, True, 2048), (2, True, 1000), (4, True, 2048)])
+def test_tp_attention_engine_matches_oracle(world, shard_head, vocab, tmp_path):
+    """``shard_head``: every rank keeps a slice of the head's rows and only per-rank winners cross the fabric (vocab 1000
+    leaves the last rank a short slice: shares are rounded up to 128 rows)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
-    for r in range(2):
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), shard_head, vocab), nprocs=world, join=True)
+    for r in range(world):
         d = torch.load(str(tmp_path / f"r{r}.pt"))
         for mode, e in d["errs"].items():
             e = sorted(e)
             # a router near-tie may flip an expert for a row: most rows tight, none far off
             assert e[len(e) // 2] < 0.03 and e[-1] < 0.25, (r, mode, e)
-        assert d["collectives"] > 0
+        assert d["collectives"] > 0 and d["picks_ok"]
