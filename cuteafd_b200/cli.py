@@ -148,15 +148,48 @@ def cmd_golden(a: argparse.Namespace) -> int:
     return run_golden(a)
 
 
+def _build_id() -> str:
+    """Short id of the source tree a report was produced by (the git commit when there is one)."""
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    try:
+        return subprocess.run(["git", "-C", root, "rev-parse", "--short", "HEAD"], capture_output=True, text=True, timeout=5).stdout.strip()
+    except (OSError, subprocess.SubprocessError):
+        return ""
+
+
 def cmd_bench(a: argparse.Namespace) -> int:
     import subprocess
+    if a.publish:                              # rebuild the generated tables from the reports on disk
+        from .bench import report as R
+        try:
+            res = R.publish(a.publish, check=a.check)
+        except (ValueError, OSError) as e:
+            print(f"bench publish: {e}", file=sys.stderr)
+            return 2
+        print(json.dumps(res))
+        return 0 if (res["current"] or not a.check) else 1
+    if a.report_root and a.from_json:          # a saved bench.py line becomes a placed report
+        from .bench import report as R
+        with open(a.from_json) as f:
+            line = json.loads([ln for ln in f.read().splitlines() if ln.strip().startswith("{")][-1])
+        model = (line.get("config") or {}).get("model", "model")
+        rep = R.from_bench_line(line, family=a.family or model, checkpoint=a.checkpoint or model, profile=a.profile_name, build=_build_id())
+        print(json.dumps({"report": R.write_report(rep, a.report_root), "accepted": rep.accepted}))
+        return 0
     if a.url:                                  # panels against a live server, over its HTTP API
         from .bench import panels
         names = list(panels.QUICK) if a.panels == "quick" else [p for p in a.panels.split(",") if p]
         opts = {"max_tokens": a.max_tokens, "levels": [int(v) for v in a.levels.split(",") if v], "seconds": a.seconds,
                 "concurrency": a.concurrency}
         out = panels.run(a.url, names, a.bench_api_key, opts)
-        print(json.dumps({"ok": out["ok"], "panels": len(out["panels"])}))
+        res = {"ok": out["ok"], "panels": len(out["panels"])}
+        if a.report_root:
+            from .bench import report as R
+            rep = R.from_panels(out, family=a.family or "model", checkpoint=a.checkpoint or a.family or "model",
+                                hardware=a.hardware or "1gpu", profile=a.profile_name, build=_build_id())
+            res.update(report=R.write_report(rep, a.report_root), accepted=rep.accepted)
+        print(json.dumps(res))
         return 0 if out["ok"] else 1
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     cmd = [sys.executable, os.path.join(root, "bench.py"), "--gpus", str(a.gpus), "--steps", str(a.steps), "--warmup", str(a.warmup)]
@@ -436,6 +469,14 @@ def _build_parser() -> argparse.ArgumentParser:
     b.add_argument("--levels", default="1,4,8", help="concurrency levels of the sweep panel")
     b.add_argument("--seconds", type=float, default=10.0, help="duration of the sustained panel")
     b.add_argument("--concurrency", type=int, default=4, help="streams of the sustained panel")
+    b.add_argument("--report-root", default="", help="place a report (report.json, card.svg, card.md) of this run under ROOT/benchmarks/<family>/")
+    b.add_argument("--from-json", default="", help="with --report-root: build the report from a saved bench.py result line instead of running")
+    b.add_argument("--family", default="", help="family name the report is filed under")
+    b.add_argument("--checkpoint", default="", help="checkpoint name the report carries")
+    b.add_argument("--hardware", default="", help="hardware layout label of a panel report, e.g. 8gpu-1att-7exp")
+    b.add_argument("--profile-name", default="smoke", help="profile label of the report directory")
+    b.add_argument("--publish", default="", metavar="ROOT", help="rebuild ROOT/README.md's results table and ROOT/benchmarks/README.md from the reports on disk")
+    b.add_argument("--check", action="store_true", help="with --publish: write nothing, exit 1 when the generated blocks are stale")
     b.set_defaults(fn=cmd_bench)
 
     f = sub.add_parser("fabric", help="NVLink / peer-access report")
