@@ -1,6 +1,8 @@
 """In-tree build of the native libraries.
 
 ``libcuteafd_b200.so``  CUDA kernels for sm_100a (nvcc, one object per .cu, plain C ABI)
+``libcuteafd_b200_chk.so``  the same kernels compiled with -DCAFD_BOUNDS_CHECK: indices that address peer buffers are
+                        checked before the access (loaded instead of the first when CAFD_BOUNDS_CHECK=1)
 ``libcuteafd_rt.so``    host runtime in C++ (page pool, radix prefix index, sampler oracle, ...)
 
 Both are loaded with ctypes; neither links against Python or libtorch, so they compile in seconds
@@ -20,6 +22,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(os.path.dirname(HERE), "csrc")
 OBJ = os.path.join(HERE, "build")
 CUDA_LIB = os.path.join(HERE, "libcuteafd_b200.so")
+CHECK_LIB = os.path.join(HERE, "libcuteafd_b200_chk.so")
+CHECK_SOURCES = ("moe.cu", "tp_collective.cu")     # translation units that carry checked sites; the rest are shared objects
 RT_LIB = os.path.join(HERE, "libcuteafd_rt.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -88,6 +92,34 @@ def build_cuda(force: bool = False, verbose: bool = False) -> str:
     return CUDA_LIB
 
 
+def build_check(force: bool = False) -> str:
+    """The bounds-check library: the translation units with checked sites recompiled with -DCAFD_BOUNDS_CHECK, linked
+    with the normal objects of everything else."""
+    build_cuda(force)
+    nvcc = _nvcc()
+    flags = [*NVCC_FLAGS, "-DCAFD_BOUNDS_CHECK"]
+    hdr_digest = _digest(_headers(), " ".join(flags))
+    objs, rebuilt = [], False
+    for f in sorted(os.listdir(CSRC)):
+        if not f.endswith(".cu"):
+            continue
+        if f not in CHECK_SOURCES:
+            objs.append(os.path.join(OBJ, f[:-3] + ".o"))
+            continue
+        s, o = os.path.join(CSRC, f), os.path.join(OBJ, f[:-3] + ".chk.o")
+        d = _digest([s], hdr_digest)
+        objs.append(o)
+        if not force and os.path.exists(o) and os.path.exists(o + ".sha") and open(o + ".sha").read() == d:
+            continue
+        _compile_one([nvcc, *flags, "-I", CSRC, "-c", s, "-o", o], o + ".log")
+        with open(o + ".sha", "w") as fh:
+            fh.write(d)
+        rebuilt = True
+    if rebuilt or not os.path.exists(CHECK_LIB) or os.path.getmtime(CHECK_LIB) < os.path.getmtime(CUDA_LIB):
+        _compile_one([nvcc, "-shared", "-o", CHECK_LIB, *objs, "-lcudart"], os.path.join(OBJ, "link_chk.log"))
+    return CHECK_LIB
+
+
 def build_rt(force: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     rt_dir = os.path.join(CSRC, "rt")
@@ -105,8 +137,8 @@ def build_rt(force: bool = False) -> str:
     return RT_LIB
 
 
-def build_all(force: bool = False, verbose: bool = False) -> tuple[str, str]:
-    return build_cuda(force, verbose), build_rt(force)
+def build_all(force: bool = False, verbose: bool = False) -> tuple[str, ...]:
+    return build_cuda(force, verbose), build_check(force), build_rt(force)
 
 
 if __name__ == "__main__":

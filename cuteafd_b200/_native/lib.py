@@ -43,6 +43,30 @@ WAIT_LIMIT_SETTERS = ("cafd_gemm_set_wait_limit_ns", "cafd_moe_set_wait_limit_ns
                       "cafd_decode_step_set_wait_limit_ns")
 
 
+BOUNDS_UNITS = ("cafd_moe", "cafd_tp")        # translation units with checked peer-store sites
+BOUNDS_SITES = {1: "plan+dispatch: slab row", 2: "plan+dispatch: owner rank", 3: "dispatch: slab row", 4: "dispatch: owner rank",
+                6: "head exchange: table row", 7: "head exchange: rank"}
+
+
+def bounds_check_enabled() -> bool:
+    lib = cuda_lib()
+    return all(getattr(lib, f"{tu}_bounds_check_enabled")() == 1 for tu in BOUNDS_UNITS)
+
+
+def take_bad_indices() -> list[tuple[str, int]]:
+    """Records the bounds-check build left since the last call: (site, offending index).  Synchronises the device."""
+    lib, out = cuda_lib(), []
+    for tu in BOUNDS_UNITS:
+        v = C.c_ulonglong(0)
+        check(getattr(lib, f"{tu}_take_bad_index")(C.byref(v)), f"{tu}_take_bad_index")
+        if v.value:
+            idx = v.value & 0xffffffffffff
+            if idx >= 1 << 47:
+                idx -= 1 << 48
+            out.append((BOUNDS_SITES.get((v.value >> 48) & 0x7fff, "?"), idx))
+    return out
+
+
 class MoeLayout(C.Structure):
     _fields_ = [
         ("n_ranks", C.c_int), ("expert_lo", C.c_int * (MAX_RANKS + 1)),
@@ -83,9 +107,11 @@ def cuda_lib():
     with _lock:
         if _cuda is not None:
             return _cuda
-        path = build.CUDA_LIB
+        # CAFD_BOUNDS_CHECK=1: the library whose peer-store paths check every index before the access
+        checked = os.environ.get("CAFD_BOUNDS_CHECK", "") == "1"
+        path = build.CHECK_LIB if checked else build.CUDA_LIB
         if not os.path.exists(path):
-            build.build_cuda()
+            build.build_check() if checked else build.build_cuda()
         lib = C.CDLL(path)
         P, I, F = C.c_void_p, C.c_int, C.c_float
         _sig(lib, "cafd_gemm", [C.POINTER(GemmArgs), P])
@@ -106,6 +132,9 @@ def cuda_lib():
         _sig(lib, "cafd_tp_reduce_norm_gather", [C.POINTER(TpReduceArgs), P])
         _sig(lib, "cafd_tp_signal", [P, I, P, P])
         _sig(lib, "cafd_tp_head_pick", [C.POINTER(TpHeadArgs), P])
+        for tu in BOUNDS_UNITS:
+            _sig(lib, f"{tu}_bounds_check_enabled", [])
+            _sig(lib, f"{tu}_take_bad_index", [P])
         _sig(lib, "cafd_argmax_candidates", [P, P, P, I, I, I, P])
         _sig(lib, "cafd_moe_plan", [P, I, I, I, I, C.POINTER(MoeLayout), P, P, P, P])
         _sig(lib, "cafd_moe_plan_wide", [P, I, I, I, I, C.POINTER(MoeLayout), P, P, P, P, P])

@@ -312,6 +312,37 @@ __device__ __forceinline__ float warp_max(float v) {
 
 }  // namespace cafd
 
+// ---- bounds-check build ------------------------------------------------------------------------------------------
+// Compiled with -DCAFD_BOUNDS_CHECK (the second library, libcuteafd_b200_chk.so), every index that addresses a buffer
+// another GPU owns (slab rows, owner ranks, combine slots, gathered rows, candidate-table rows) is checked before the
+// access.  A bad index is recorded (site << 48 | index, first one wins) and the access is skipped, so the run goes on
+// and the record says where.  In the normal build the check compiles to `true`.  This is the in-process stand-in for
+// a memory checker on the peer-store paths.
+namespace cafd {
+static __device__ unsigned long long g_bad_index = 0ull;
+__device__ __forceinline__ bool index_ok(long long i, long long n, unsigned site) {
+  if (i >= 0 && i < n) return true;
+  atomicCAS(&g_bad_index, 0ull, (static_cast<unsigned long long>(site) << 48) | (static_cast<unsigned long long>(i) & 0xffffffffffffull) | (1ull << 63));
+  return false;
+}
+}  // namespace cafd
+#ifdef CAFD_BOUNDS_CHECK
+#define CAFD_INDEX_OK(i, n, site) cafd::index_ok(static_cast<long long>(i), static_cast<long long>(n), site)
+#define CAFD_BOUNDS_CHECK_ON 1
+#else
+#define CAFD_INDEX_OK(i, n, site) true
+#define CAFD_BOUNDS_CHECK_ON 0
+#endif
+// Per translation unit: whether it was compiled with the checks, and its record (read and cleared).
+#define CAFD_BOUNDS_API(prefix)                                                                     \
+  extern "C" int prefix##_bounds_check_enabled(void) { return CAFD_BOUNDS_CHECK_ON; }               \
+  extern "C" int prefix##_take_bad_index(unsigned long long* out) {                                 \
+    unsigned long long zero = 0ull;                                                                 \
+    cudaError_t e = cudaMemcpyFromSymbol(out, cafd::g_bad_index, sizeof(*out));                     \
+    if (e == cudaSuccess && *out) e = cudaMemcpyToSymbol(cafd::g_bad_index, &zero, sizeof(zero));   \
+    return static_cast<int>(e);                                                                     \
+  }
+
 // Each translation unit owns a copy of the wait limit; this defines its C setter.
 #define CAFD_WAIT_LIMIT_SETTER(name)                                                      \
   extern "C" int name(unsigned long long ns) {                                            \

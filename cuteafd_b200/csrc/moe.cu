@@ -370,6 +370,7 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
       const int e = idx[i];
       if (row < 0 || e < 0 || e >= E) continue;
       const int r = rank_of[e];
+      if (!CAFD_INDEX_OK(row, L.max_rows, 1) || !CAFD_INDEX_OK(r, L.n_ranks, 2)) continue;
       const uint4* src = x + static_cast<size_t>(i / top_k) * row_vec;
       uint4* dst = reinterpret_cast<uint4*>(L.slab[r]) + static_cast<size_t>(row) * row_vec;
       uint2* dq = reinterpret_cast<uint2*>(L.slab_q[r]) + static_cast<size_t>(row) * row_vec;
@@ -521,6 +522,7 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const uint4* __restri
         const int row = __shfl_sync(0xffffffffu, my_row, sl);
         const int r = __shfl_sync(0xffffffffu, my_rank, sl);
         if (row < 0) continue;
+        if (!CAFD_INDEX_OK(row, L.max_rows, 3) || !CAFD_INDEX_OK(r, L.n_ranks, 4)) continue;
         if (L.fp8) {
           uint2* dq = reinterpret_cast<uint2*>(L.slab_q[r]) + static_cast<size_t>(row) * row_vec;
           float* ds = L.slab_s[r] + static_cast<size_t>(row) * (row_vec >> 4);
@@ -848,3 +850,4 @@ int cafd_wait_flag(const uint32_t* flag, const uint32_t* epoch, uint32_t* status
 }  // extern "C"
 
 CAFD_WAIT_LIMIT_SETTER(cafd_moe_set_wait_limit_ns)
+CAFD_BOUNDS_API(cafd_moe)

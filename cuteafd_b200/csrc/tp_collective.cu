@@ -174,7 +174,8 @@ __global__ void __launch_bounds__(64) tp_head_pick_kernel(const TpHeadDev p) {
     if (threadIdx.x == 0) {
       const int gid = bi == 0x7fffffff ? 0x7fffffff : bi + p.lo;          // an empty or all-NaN slice never wins
       const unsigned long long word = (static_cast<unsigned long long>(__float_as_uint(best)) << 32) | static_cast<uint32_t>(gid);
-      for (int r = 0; r < p.ranks; ++r) p.table_out[r][static_cast<size_t>(p.my_rank) * p.max_rows + t] = word;
+      if (CAFD_INDEX_OK(t, p.max_rows, 6) && CAFD_INDEX_OK(p.my_rank, p.ranks, 7))
+        for (int r = 0; r < p.ranks; ++r) p.table_out[r][static_cast<size_t>(p.my_rank) * p.max_rows + t] = word;
       __threadfence_system();
       const uint32_t prev = atomicAdd(p.done_counter, 1u);
       s_last = prev == gridDim.x - 1;
@@ -292,3 +293,4 @@ int cafd_tp_head_pick(const cafd_tp_head_args* a, cafd_stream_t s) {
 }  // extern "C"
 
 CAFD_WAIT_LIMIT_SETTER(cafd_tp_set_wait_limit_ns)
+CAFD_BOUNDS_API(cafd_tp)

@@ -45,6 +45,15 @@ def _align(x: int, a: int = 1024) -> int:
     return (x + a - 1) // a * a
 
 
+# Guard band after every region of a symmetric buffer that peers write into: filled with a pattern when the buffer is
+# created, looked at by ``SymmetricHeap.damaged()`` (tests, round ends, shutdown).  A kernel that stores past its region
+# (a row index beyond the slab, a flag slot beyond the table) lands in a band instead of in its neighbour's data, and
+# the damage names the region.  The reference guards its exchange buffers with sanitizer builds and poisoned padding
+# (native/CMakeLists.txt sanitizer options; native/shared/src/cuteafd_native.cc buffer registration).
+GUARD = 1024
+GUARD_BYTE = 0xA5
+
+
 @dataclass
 class SymLayout:
     """Byte offsets inside every rank's symmetric buffer (same layout on all ranks)."""
@@ -65,18 +74,27 @@ class SymLayout:
         o = 0
         slab = o; o = _align(o + n * SymLayout.slab_stride(geo))
         meta = o; o = _align(o + n * SymLayout.meta_stride(geo))
-        dflags = o; o = _align(o + num_layers * n * 4)
-        combine = o; o = _align(o + geo.max_tokens * geo.top_k * geo.hidden * 2)
-        cflags = o; o = _align(o + num_layers * geo.regions * _n.MAX_RANKS * 4)
+        dflags = o; o = _align(o + num_layers * n * 4) + GUARD
+        combine = o; o = _align(o + geo.max_tokens * geo.top_k * geo.hidden * 2) + GUARD
+        cflags = o; o = _align(o + num_layers * geo.regions * _n.MAX_RANKS * 4) + GUARD
         return SymLayout(slab, meta, dflags, combine, cflags, o)
 
     @staticmethod
     def slab_stride(geo: ExchangeGeometry) -> int:
-        return _align(geo.region().max_rows * geo.hidden * 2)
+        return _align(geo.region().max_rows * geo.hidden * 2) + GUARD
 
     @staticmethod
     def meta_stride(geo: ExchangeGeometry) -> int:
-        return _align(geo.region().meta_ints * 4)
+        return _align(geo.region().meta_ints * 4) + GUARD
+
+    def guards(self, geo: ExchangeGeometry, n_sources: int = 1) -> list[tuple[str, int]]:
+        """(name, byte offset) of every guard band: the last ``GUARD`` bytes of each slab region and plan block, and of
+        the dispatch-flag table, the combine buffer and the completion-flag table."""
+        n = geo.regions * n_sources
+        out = [(f"slab[{r}]", self.slab + (r + 1) * self.slab_stride(geo) - GUARD) for r in range(n)]
+        out += [(f"meta[{r}]", self.meta + (r + 1) * self.meta_stride(geo) - GUARD) for r in range(n)]
+        out += [("dispatch flags", self.combine - GUARD), ("combine", self.cflags - GUARD), ("completion flags", self.total - GUARD)]
+        return out
 
 
 class SymmetricHeap:
@@ -92,11 +110,27 @@ class SymmetricHeap:
             symm_mem.enable_symm_mem_for_group(group.group_name)
             self.handle = symm_mem.rendezvous(self.buf, group)
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.bands: list[tuple[str, int]] = []
         torch.cuda.synchronize()
         dist.barrier()
 
     def view(self, offset: int, nbytes: int, dtype: torch.dtype) -> torch.Tensor:
         return self.buf[offset:offset + nbytes].view(dtype)
+
+    def arm(self, bands: list[tuple[str, int]]) -> None:
+        """Fill the guard bands (before any peer writes: the constructor's barrier has passed, no step has run)."""
+        self.bands = list(bands)
+        for _, off in self.bands:
+            self.buf[off:off + GUARD].fill_(GUARD_BYTE)
+
+    def damaged(self) -> list[str]:
+        """Names of the guard bands a store has landed in (one small device read per band; not on the step path)."""
+        if not self.bands:
+            return []
+        idx = torch.tensor([off for _, off in self.bands], device=self.buf.device)
+        rows = self.buf[(idx[:, None] + torch.arange(GUARD, device=self.buf.device)[None, :]).view(-1)].view(len(self.bands), GUARD)
+        bad = (rows != GUARD_BYTE).any(dim=1).tolist()
+        return [name for (name, _), b in zip(self.bands, bad) if b]
 
 
 class RemoteExchange:
@@ -324,6 +358,7 @@ class ExpertWorker:
         self.cfg, self.geo, self.rank, self.er, self.n_sources = cfg, geo, rank, rank - n_sources, n_sources
         self.weights = expert_weights
         self.format = expert_format
+        self.heap = heap
         self.n_layers = len(expert_weights)
         self.n_main = sum(1 for i in range(cfg.num_layers) if cfg.is_moe_layer(i))     # the rest are MTP depths' layers
         rg, n = geo.region(), geo.regions
@@ -455,6 +490,12 @@ class AfdHandle:
         if self.generator is not None:
             self.generator.engine.shutdown()
 
+    def damaged_guards(self) -> list[str]:
+        """Guard bands of this rank's exchange buffer that something wrote into (empty = every peer store stayed
+        inside its region)."""
+        heap = self.worker.heap if self.worker is not None else self.generator.engine.ex.heap
+        return heap.damaged()
+
 
 def build_afd(cfg: ModelConfig, device: torch.device, rank: int, world: int, *, max_tokens: int, max_seqs: int,
               num_pages: int, pages_per_seq: int, use_graphs: bool = True, params: dict | None = None,
@@ -474,6 +515,9 @@ def build_afd(cfg: ModelConfig, device: torch.device, rank: int, world: int, *, 
     n_moe = sum(1 for i in range(cfg.num_layers + cfg.mtp_layers) if (cfg.is_moe_layer(i) if i < cfg.num_layers else cfg.num_experts > 0))
     lay = SymLayout.build(geo, n_moe, A)
     heap = SymmetricHeap(lay.total, device)
+    heap.arm(lay.guards(geo, A))
+    torch.cuda.synchronize()
+    dist.barrier()                               # nobody dispatches into a buffer whose bands are still being filled
     snap = None
     if snapshot is not None:
         from ..loader.load import expert_storage_format, open_snapshot

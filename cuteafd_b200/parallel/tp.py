@@ -25,7 +25,7 @@ import torch.distributed as dist
 
 from .._native import lib as _n
 from ..ops import kernels as K
-from .afd import SymmetricHeap, _align
+from .afd import GUARD, SymmetricHeap, _align
 
 
 class TpContext:
@@ -38,15 +38,26 @@ class TpContext:
         self.rows_per_rank = self.max_rows_per_rank = (max_rows + self.ranks - 1) // self.ranks
         R, n = self.rows_per_rank, self.ranks
         o = 0
-        self.off_partials = o; o = _align(o + n * R * hidden * 2)       # receive buffer [ranks][R][hidden]
-        self.off_x = o; o = _align(o + n * R * hidden * 2)              # gathered activations [ranks*R][hidden]
-        self.off_rs_flags = o; o = _align(o + 64)
-        self.off_ag_flags = o; o = _align(o + 64)
-        self.off_ready_flags = o; o = _align(o + 64)
-        self.off_head_flags = o; o = _align(o + 64)
+        bands = []
+
+        def region(name: str, nbytes: int) -> int:                       # every region ends in a guard band
+            nonlocal o
+            start = o
+            o = _align(o + nbytes) + GUARD
+            bands.append((name, o - GUARD))
+            return start
+        self.off_partials = region("partials", n * R * hidden * 2)       # receive buffer [ranks][R][hidden]
+        self.off_x = region("gathered activations", n * R * hidden * 2)  # [ranks*R][hidden]
+        self.off_rs_flags = region("reduce-scatter flags", 64)
+        self.off_ag_flags = region("all-gather flags", 64)
+        self.off_ready_flags = region("ready flags", 64)
+        self.off_head_flags = region("head flags", 64)
         self.head_rows = max(64, min(max_rows, 4096))                    # rows one sharded-head selection can cover
-        self.off_head_table = o; o = _align(o + n * self.head_rows * 8)  # (value, id) per rank and row
+        self.off_head_table = region("head table", n * self.head_rows * 8)   # (value, id) per rank and row
         self.heap = SymmetricHeap(o, device, self.group)
+        self.heap.arm(bands)
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
         self.partials = self.heap.view(self.off_partials, n * R * hidden * 2, torch.bfloat16).view(n, R, hidden)
         self.x_full = self.heap.view(self.off_x, n * R * hidden * 2, torch.bfloat16).view(n * R, hidden)
         self.rs_flags = self.heap.view(self.off_rs_flags, 64, torch.int32)

@@ -58,6 +58,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str, mode: str, snap_dir:
             first = h.worker.weights[0][0]
             assert isinstance(first, tuple) and first[0].dtype in (torch.float8_e4m3fn, torch.uint8)    # stored bytes, not bf16
         h.worker.serve()
+        torch.save({"guards": h.damaged_guards()}, os.path.join(out_dir, f"r{rank}.pt"))
     else:
         gen, eng, ref = h.generator, h.generator.engine, RefDecoder(cfg, params)
         a = h.replica
@@ -116,6 +117,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str, mode: str, snap_dir:
                 if A > 1:
                     eng.end_round()
         result["status"] = K.read_status()
+        result["guards"] = h.damaged_guards()
         if a == 0:
             h.shutdown()
         else:
@@ -139,6 +141,9 @@ def test_afd_matches_oracle(world, mode, tmp_path):
         snap = write_random_snapshot(small_cfg(), str(tmp_path / "snap"), fmt=mode, seed=3)
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), mode, snap), nprocs=world, join=True)
     replicas = 2 if mode == "dp2" else 1
+    for rank in range(world):
+        # no peer store left its region: every guard band of every rank's exchange buffer is intact
+        assert torch.load(str(tmp_path / f"r{rank}.pt"))["guards"] == [], rank
     for a in range(replicas):
         r = torch.load(str(tmp_path / f"r{a}.pt"))
         assert r["status"] == 0, r

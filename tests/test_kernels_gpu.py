@@ -388,3 +388,59 @@ def test_fp8_dequant_block128(K):
     out = K.fp8_dequant_block128(q, s)
     ref = torch.stack([codecs.fp8_dequant_block128(a, b) for a, b in qs])
     assert (out.float().cpu() - ref.float()).abs().max().item() <= 0.01 * ref.abs().max().item()
+
+
+# ---- bounds-check build ------------------------------------------------------------------------------------------
+_BOUNDS_CHILD = r'''
+import json, os, sys
+import torch
+from cuteafd_b200._native import lib as N
+from cuteafd_b200.ops import kernels as K
+from cuteafd_b200.parallel.moe_exchange import ExchangeGeometry, LocalExchange
+assert N.bounds_check_enabled(), "this process must have loaded the checked library"
+dev = torch.device("cuda:0")
+T, H, E, k = 40, 512, 16, 4
+out = {}
+for T in (40, 300):
+    ex = LocalExchange(ExchangeGeometry(H, 256, E, k, max_tokens=T, n_expert_ranks=1), dev)
+    x = torch.randn(T, H, device=dev).to(torch.bfloat16)
+    logits = torch.randn(T, E, device=dev)
+    ex.att.dispatch(x, logits, dict(scoring="softmax"), 16, 0, ex.epoch)
+    torch.cuda.synchronize()
+    clean = N.take_bad_indices()
+    good = ex.exp.slab.clone()
+    # the same plan against a layout that claims a slab shorter than the plan needs: the checked build refuses the
+    # rows past the end (and says which), stores the others, and nothing outside the slab is touched
+    rows = int(ex.att.dest_row[: T * k].max()) + 1
+    ex.att.layout.max_rows = rows - 3
+    ex.exp.slab.zero_()
+    # (the dispatch kernel takes the plan as given; the planner itself never hands out a row past ``max_rows``)
+    K.moe_dispatch(x, ex.att.idx[:T], ex.att.dest_row, ex.att.layout, ex.epoch, ex.att.done[0:1])
+    torch.cuda.synchronize()
+    bad = N.take_bad_indices()
+    kept = bool(torch.equal(ex.exp.slab[: rows - 3], good[: rows - 3]))
+    skipped = bool((ex.exp.slab[rows - 3: rows] == 0).all())
+    out[str(T)] = {"clean": clean, "bad": bad, "kept": kept, "skipped": skipped, "rows": rows}
+K.read_status()
+print("RESULT " + json.dumps(out))
+'''
+
+
+def test_bounds_check_build_catches_a_row_past_the_slab(K):
+    """The checked library (CAFD_BOUNDS_CHECK=1, its own process): a dispatch whose plan points past the end of the slab
+    records the site and the index and skips those stores; a correct dispatch records nothing."""
+    import json
+    import subprocess
+    import sys
+    from cuteafd_b200._native import build
+    if not os.path.exists(build.CHECK_LIB):
+        pytest.fail("libcuteafd_b200_chk.so is not built (python -m cuteafd_b200._native.build)")
+    env = dict(os.environ, CAFD_BOUNDS_CHECK="1")
+    r = subprocess.run([sys.executable, "-c", _BOUNDS_CHILD], env=env, capture_output=True, text=True, timeout=300,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0, r.stdout + r.stderr
+    out = json.loads(next(ln for ln in r.stdout.splitlines() if ln.startswith("RESULT "))[7:])
+    for T, rec in out.items():
+        assert rec["clean"] == [] and rec["kept"] and rec["skipped"], (T, rec)
+        (site, idx), = rec["bad"]
+        assert "slab row" in site and rec["rows"] - 3 <= idx < rec["rows"], (T, rec)

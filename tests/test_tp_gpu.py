@@ -85,7 +85,8 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
     torch.cuda.synchronize()
     dist.barrier()
     good_after = K.read_status() == 0 and bool(torch.isfinite(z2.float()).all())
-    torch.save({"errs": errs, "timed_out": timed_out, "counter_after": counter_after, "good_after": good_after},
+    torch.save({"errs": errs, "timed_out": timed_out, "counter_after": counter_after, "good_after": good_after,
+                "guards": ctx.heap.damaged()},
                os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
@@ -101,3 +102,4 @@ def test_tp_block_matches_reference(world, tmp_path):
         rec = torch.load(str(tmp_path / f"r{r}.pt"))
         assert max(rec["errs"]) < 0.03, (r, rec["errs"])
         assert rec["timed_out"] != 0 and rec["counter_after"] == 0 and rec["good_after"], (r, rec)
+        assert rec["guards"] == [], (r, rec["guards"])                 # every peer store stayed inside its region
