@@ -1,5 +1,6 @@
 """sm_100a kernels against plain PyTorch fp32 references of the same ops."""
 import math
+import os
 
 import pytest
 import torch
