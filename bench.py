@@ -112,10 +112,10 @@ def main() -> None:
             from cuteafd_b200.models.gqa_moe import GqaMoeWeights
             from cuteafd_b200.models.tp_gqa import TpGqaMoeEngine
             from cuteafd_b200.runtime.generate import Generator
-            from cuteafd_b200.runtime.paged import PagePool
+            from cuteafd_b200.runtime.native import make_pool
             W = GqaMoeWeights.random_init(cfg, dev, seed=0)
             eng = TpGqaMoeEngine(cfg, W, num_pages, max_tokens=args.prompt_len, max_seqs=max(levels))
-            gen = Generator(eng, PagePool(num_pages), pages_per_seq, max(levels), prefill_chunk=args.prompt_len,
+            gen = Generator(eng, make_pool(num_pages), pages_per_seq, max(levels), prefill_chunk=args.prompt_len,
                             use_graphs=not args.no_graphs)
             torch.cuda.synchronize()
             dist.barrier()
@@ -138,11 +138,11 @@ def main() -> None:
         else:
             from cuteafd_b200.models.gqa_moe import GqaMoeEngine, GqaMoeWeights, KvCache
             from cuteafd_b200.runtime.generate import Generator
-            from cuteafd_b200.runtime.paged import PagePool
+            from cuteafd_b200.runtime.native import make_pool
             W = GqaMoeWeights.random_init(cfg, dev, seed=0)
             kv = KvCache(cfg, num_pages, dev)
             eng = GqaMoeEngine(cfg, W, kv, max_tokens=args.prompt_len, max_seqs=max(levels))
-            gen = Generator(eng, PagePool(num_pages), pages_per_seq, max(levels), prefill_chunk=args.prompt_len,
+            gen = Generator(eng, make_pool(num_pages), pages_per_seq, max(levels), prefill_chunk=args.prompt_len,
                             use_graphs=not args.no_graphs)
             torch.cuda.synchronize()
             log(f"model + KV ready in {time.time()-t0:.1f}s, {torch.cuda.memory_allocated()/2**30:.1f} GiB")

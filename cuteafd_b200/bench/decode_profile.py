@@ -17,7 +17,7 @@ import torch
 from .. import deepseek_v3, qwen3_30b_a3b
 from ..models.gqa_moe import GqaMoeEngine, GqaMoeWeights, KvCache
 from ..runtime.generate import Generator
-from ..runtime.paged import PagePool
+from ..runtime.native import make_pool
 
 
 def main() -> None:
@@ -41,7 +41,7 @@ def main() -> None:
         cfg = qwen3_30b_a3b().replace(num_layers=a.layers)
         W = GqaMoeWeights.random_init(cfg, dev)
         eng = GqaMoeEngine(cfg, W, KvCache(cfg, pages, dev), max_tokens=a.context, max_seqs=a.concurrency)
-    gen = Generator(eng, PagePool(pages), pps, a.concurrency, prefill_chunk=a.context, use_graphs=False)
+    gen = Generator(eng, make_pool(pages), pps, a.concurrency, prefill_chunk=a.context, use_graphs=False)
     g = torch.Generator().manual_seed(0)
     seqs, last = [], []
     for _ in range(a.concurrency):

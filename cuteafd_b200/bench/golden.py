@@ -30,12 +30,12 @@ def run_golden(args) -> int:
     if torch.cuda.is_available() and cfg.attention == "gqa":
         from ..models.gqa_moe import GqaMoeEngine, GqaMoeWeights, KvCache
         from ..runtime.generate import Generator
-        from ..runtime.paged import PagePool
+        from ..runtime.native import make_pool
         dev = torch.device("cuda:0")
         W = GqaMoeWeights.from_params(cfg, params, dev)
         pages = args.tokens // 64 + 4
         eng = GqaMoeEngine(cfg, W, KvCache(cfg, pages, dev), max_tokens=args.tokens, max_seqs=4)
-        gen = Generator(eng, PagePool(pages), pages, 4, prefill_chunk=args.tokens, use_graphs=False)
+        gen = Generator(eng, make_pool(pages), pages, 4, prefill_chunk=args.tokens, use_graphs=False)
         s = gen.table.new()
         gen.prefill(s, tokens.tolist())
         got = eng.logits[0].float().cpu()

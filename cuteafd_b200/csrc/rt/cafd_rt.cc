@@ -161,211 +161,6 @@ int cafd_seq_slots(const cafd_pool* p, int id, int start, int n, int* out) {
 
 }  // extern "C"
 
-// ---- prefix index ---------------------------------------------------------------------------------
-namespace {
-struct Snap;
-struct Node {
-  uint64_t key = 0;
-  int page = 0;
-  Node* parent = nullptr;
-  int32_t tokens[kPage];
-  std::unordered_map<uint64_t, std::unique_ptr<Node>> children;
-  int refs = 0;
-  std::vector<Snap*> tails;
-};
-struct Snap {
-  int sid, kind, length;
-  Node* node;
-  int tail_page;
-  std::vector<int32_t> tail_tokens;
-  uint64_t last_use;
-};
-uint64_t mix(uint64_t h, uint64_t v) {
-  h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
-  h *= 0xbf58476d1ce4e5b9ull;
-  return h ^ (h >> 31);
-}
-uint64_t chunk_key(uint64_t prev, const int32_t* t) {
-  uint64_t h = prev ^ 0x94d049bb133111ebull;
-  for (int i = 0; i < kPage; ++i) h = mix(h, static_cast<uint32_t>(t[i]));
-  return h;
-}
-}  // namespace
-
-struct cafd_prefix {
-  cafd_pool* pool;
-  int max_pages;
-  int held = 0;
-  int evicted = 0;
-  uint64_t clock = 0;
-  int next_sid = 1;
-  Node root;
-  std::map<int, std::unique_ptr<Snap>> snaps;
-};
-
-static void prefix_release(cafd_prefix* c, int sid) {
-  auto it = c->snaps.find(sid);
-  if (it == c->snaps.end()) return;
-  Snap* s = it->second.get();
-  Node* host = s->node ? s->node : &c->root;
-  if (s->tail_page >= 0) {
-    host->tails.erase(std::remove(host->tails.begin(), host->tails.end(), s), host->tails.end());
-    cafd_pool_release(c->pool, s->tail_page);
-    --c->held;
-  }
-  Node* n = s->node;
-  while (n && n != &c->root) {
-    --n->refs;
-    Node* parent = n->parent;
-    if (n->refs == 0 && n->children.empty() && n->tails.empty()) {
-      cafd_pool_release(c->pool, n->page);
-      --c->held;
-      parent->children.erase(n->key);     // destroys n
-    }
-    n = parent;
-  }
-  c->snaps.erase(it);
-  ++c->evicted;
-}
-
-static void prefix_make_room(cafd_prefix* c, int need) {
-  while (c->held + need > c->max_pages && !c->snaps.empty()) {
-    Snap* v = nullptr;
-    for (int kind = 0; kind < 2 && !v; ++kind)
-      for (auto& kv : c->snaps)
-        if (kv.second->kind == kind && (!v || kv.second->last_use < v->last_use)) v = kv.second.get();
-    if (!v) break;
-    prefix_release(c, v->sid);
-  }
-}
-
-extern "C" {
-
-cafd_prefix* cafd_prefix_new(cafd_pool* pool, int max_pages) {
-  auto* c = new cafd_prefix;
-  c->pool = pool;
-  c->max_pages = max_pages;
-  return c;
-}
-void cafd_prefix_free(cafd_prefix* c) {
-  if (!c) return;
-  while (!c->snaps.empty()) prefix_release(c, c->snaps.begin()->first);
-  delete c;
-}
-
-int cafd_prefix_lookup(cafd_prefix* c, const int32_t* tokens, int n, int* pages_out, int cap, int* n_pages, int* tail_shared) {
-  Node* node = &c->root;
-  std::vector<int> pages;
-  uint64_t prev = 0;
-  for (int i = 0; i + kPage <= n; i += kPage) {
-    const uint64_t k = chunk_key(prev, tokens + i);
-    auto it = node->children.find(k);
-    if (it == node->children.end() || std::memcmp(it->second->tokens, tokens + i, sizeof(int32_t) * kPage) != 0) break;
-    node = it->second.get();
-    pages.push_back(node->page);
-    prev = k;
-  }
-  int length = static_cast<int>(pages.size()) * kPage;
-  Snap* best = nullptr;
-  for (Snap* s : node->tails) {
-    const int t = s->length - length;
-    if (t > 0 && t <= n - length && std::memcmp(s->tail_tokens.data(), tokens + length, sizeof(int32_t) * t) == 0 &&
-        (!best || s->length > best->length))
-      best = s;
-  }
-  int shared = 0;
-  if (best) {
-    pages.push_back(best->tail_page);
-    length = best->length;
-    shared = 1;
-  }
-  if (length >= n) {           // always leave at least one token to compute
-    if (shared) {
-      pages.pop_back();
-      shared = 0;
-      length = static_cast<int>(pages.size()) * kPage;
-    }
-    if (length >= n && !pages.empty()) {
-      pages.pop_back();
-      length = static_cast<int>(pages.size()) * kPage;
-    }
-  }
-  if (length > 0) {
-    ++c->clock;
-    if (best && shared) best->last_use = c->clock;
-    for (auto& kv : c->snaps) {
-      for (Node* m = kv.second->node; m && m != &c->root; m = m->parent)
-        if (m == node) { kv.second->last_use = c->clock; break; }
-    }
-  }
-  *n_pages = static_cast<int>(pages.size());
-  *tail_shared = shared;
-  for (int i = 0; i < std::min<int>(cap, *n_pages); ++i) pages_out[i] = pages[i];
-  return length;
-}
-
-int cafd_prefix_capture(cafd_prefix* c, int seq, const int32_t* tokens, int length, int kind) {
-  const Seq* s = seq_of(c->pool, seq);
-  if (!s || length < kPage || length > s->kv_len) return 0;
-  const int need = (length + kPage - 1) / kPage;
-  if (need > static_cast<int>(s->pages.size())) return 0;
-  prefix_make_room(c, need);
-  Node* node = &c->root;
-  uint64_t prev = 0;
-  std::vector<Node*> path;
-  int i = 0;
-  for (; i + kPage <= length; i += kPage) {
-    const uint64_t k = chunk_key(prev, tokens + i);
-    auto it = node->children.find(k);
-    if (it == node->children.end()) {
-      auto nn = std::make_unique<Node>();
-      nn->key = k;
-      nn->page = s->pages[i / kPage];
-      nn->parent = node;
-      std::memcpy(nn->tokens, tokens + i, sizeof(int32_t) * kPage);
-      cafd_pool_retain(c->pool, nn->page);
-      ++c->held;
-      it = node->children.emplace(k, std::move(nn)).first;
-    } else if (std::memcmp(it->second->tokens, tokens + i, sizeof(int32_t) * kPage) != 0) {
-      break;   // hash collision: stop extending this path
-    }
-    node = it->second.get();
-    path.push_back(node);
-    prev = k;
-  }
-  for (Node* n : path) ++n->refs;
-  auto snap = std::make_unique<Snap>();
-  snap->sid = c->next_sid++;
-  snap->kind = kind;
-  snap->length = length;
-  snap->node = path.empty() ? nullptr : node;
-  snap->tail_page = -1;
-  snap->last_use = ++c->clock;
-  if (length % kPage && i + kPage > length) {
-    snap->tail_page = s->pages[i / kPage];
-    snap->tail_tokens.assign(tokens + i, tokens + length);
-    cafd_pool_retain(c->pool, snap->tail_page);
-    ++c->held;
-    node->tails.push_back(snap.get());
-  } else {
-    snap->length = i;
-  }
-  const int sid = snap->sid;
-  c->snaps.emplace(sid, std::move(snap));
-  return sid;
-}
-
-int cafd_prefix_release(cafd_prefix* c, int sid) {
-  const int before = c->evicted;
-  prefix_release(c, sid);
-  return c->evicted - before;
-}
-int cafd_prefix_held_pages(const cafd_prefix* c) { return c->held; }
-int cafd_prefix_snapshots(const cafd_prefix* c) { return static_cast<int>(c->snaps.size()); }
-int cafd_prefix_evicted(const cafd_prefix* c) { return c->evicted; }
-
-}  // extern "C"
-
 // ---- KV reserve -----------------------------------------------------------------------------------
 namespace {
 struct LeaseRec { int leased, max_pages, shared; };
@@ -436,6 +231,14 @@ int cafd_reserve_top_up(cafd_reserve* r, int rid) {
   return 1;
 }
 int cafd_reserve_release(cafd_reserve* r, int rid) { return static_cast<int>(r->leases.erase(rid)); }
+int cafd_reserve_total(const cafd_reserve* r) { return r->total; }
+int cafd_reserve_count(const cafd_reserve* r) { return static_cast<int>(r->leases.size()); }
+// 1 when a sequence of `next_len_tokens` tokens would outgrow the request's lease, 0 when it fits, -1 for an unknown id
+int cafd_reserve_needs_top_up(const cafd_reserve* r, int rid, int next_len_tokens) {
+  auto it = r->leases.find(rid);
+  if (it == r->leases.end()) return -1;
+  return pages_for(next_len_tokens) - it->second.shared > it->second.leased ? 1 : 0;
+}
 
 // ---- sampler ----------------------------------------------------------------------------------------
 float cafd_sample_uniform(uint64_t seed, uint64_t position) {

@@ -38,19 +38,6 @@ int cafd_seq_num_pages(const cafd_pool*, int seq);
 int cafd_seq_pages(const cafd_pool*, int seq, int* out, int cap);
 int cafd_seq_slots(const cafd_pool*, int seq, int start, int n, int* out);            // page*64+offset per token
 
-typedef struct cafd_prefix cafd_prefix;
-cafd_prefix* cafd_prefix_new(cafd_pool*, int max_pages);
-void cafd_prefix_free(cafd_prefix*);
-// longest cached prefix of tokens[0:n]; writes shared pages to pages_out; returns matched length.
-// *tail_shared = 1 when the last page is a shared partial tail.  Always leaves >= 1 token to compute.
-int cafd_prefix_lookup(cafd_prefix*, const int32_t* tokens, int n, int* pages_out, int cap, int* n_pages, int* tail_shared);
-// retain seq's first `length` tokens; kind 0 = prompt, 1 = turn.  returns snapshot id (>0) or 0.
-int cafd_prefix_capture(cafd_prefix*, int seq, const int32_t* tokens, int length, int kind);
-int cafd_prefix_release(cafd_prefix*, int sid);
-int cafd_prefix_held_pages(const cafd_prefix*);
-int cafd_prefix_snapshots(const cafd_prefix*);
-int cafd_prefix_evicted(const cafd_prefix*);
-
 typedef struct cafd_reserve cafd_reserve;
 cafd_reserve* cafd_reserve_new(int total_pages, int chunk_tokens);
 void cafd_reserve_free(cafd_reserve*);
@@ -58,6 +45,9 @@ int cafd_reserve_lease(cafd_reserve*, int rid, int prompt_tokens, int max_new_to
 int cafd_reserve_top_up(cafd_reserve*, int rid);
 int cafd_reserve_release(cafd_reserve*, int rid);
 int cafd_reserve_leased(const cafd_reserve*);
+int cafd_reserve_total(const cafd_reserve*);
+int cafd_reserve_count(const cafd_reserve*);
+int cafd_reserve_needs_top_up(const cafd_reserve*, int rid, int next_len_tokens);   // 1 outgrows the lease, 0 fits, -1 unknown id
 
 // One row.  mask may be NULL (uint8 per token, non-zero = allowed).  top_k <= 0 disables.  Returns the token, or
 // -1 non-finite logit, -2 empty mask, -3 bad parameter.

@@ -529,7 +529,7 @@ def build_afd(cfg: ModelConfig, device: torch.device, rank: int, world: int, *, 
         par += f" ({expert_format} experts)"
     if rank < A:
         from ..runtime.generate import Generator
-        from ..runtime.paged import PagePool
+        from ..runtime.native import make_pool
         if cfg.is_mla:
             from ..models.mla_moe import LatentCache as Cache
             from ..models.mla_moe import MlaMoeWeights as Weights
@@ -546,7 +546,7 @@ def build_afd(cfg: ModelConfig, device: torch.device, rank: int, world: int, *, 
         kv = Cache(cfg, num_pages, device)
         eng = AfdAttentionEngine(cfg, W, kv, max_tokens, max_seqs, heap, lay, geo, source=rank, n_sources=A)
         eng.ex.expert_format = expert_format
-        gen = Generator(eng, PagePool(num_pages), pages_per_seq, max_seqs, prefill_chunk=prefill_chunk or max_tokens,
+        gen = Generator(eng, make_pool(num_pages), pages_per_seq, max_seqs, prefill_chunk=prefill_chunk or max_tokens,
                         use_graphs=use_graphs)
         return AfdHandle(gen, None, par, rank, A)
     lo, hi = geo.rank_experts(rank - A)

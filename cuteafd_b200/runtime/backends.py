@@ -14,7 +14,8 @@ from dataclasses import dataclass
 import torch
 
 from ..config import ModelConfig
-from .paged import PAGE, PagePool, Sequence, SequenceTable
+from .native import make_pool
+from .paged import PAGE, Sequence, SequenceTable
 from .prefix_cache import PROMPT, TURN, PrefixCache
 
 
@@ -35,7 +36,7 @@ class OracleBackend:
         self.cfg, self.model = cfg, RefDecoder(cfg, params)
         self.vocab_size, self.prefill_chunk, self.max_decode_rows = cfg.vocab_size, prefill_chunk, max_decode_rows
         self.total_pages = total_pages
-        self.pool = PagePool(total_pages)
+        self.pool = make_pool(total_pages)
         self.table = SequenceTable(self.pool)
         self.prefix = PrefixCache(self.pool, self.table, max_pages=total_pages // 2)
         self.tier = None
@@ -192,7 +193,7 @@ class EngineBackend:
         self.vocab_size = self.cfg.vocab_size
         self.prefill_chunk, self.max_decode_rows = prefill_chunk, max_decode_rows
         self.total_pages = num_pages
-        self.pool = PagePool(num_pages)
+        self.pool = make_pool(num_pages)
         self.gen = Generator(engine, self.pool, max_pages_per_seq, max_decode_rows, prefill_chunk, use_graphs)
         self.table = self.gen.table
         self.prefix = PrefixCache(self.pool, self.table, max_pages=num_pages // 2)

@@ -1,7 +1,8 @@
-"""ctypes front end of libcuteafd_rt.so: the C++ page pool, prefix index, KV reserve and sampler.
+"""ctypes front end of libcuteafd_rt.so: the C++ page pool, KV reserve, repeat guard, wire checksum and sampler.
 
-Same behaviour as the Python classes in this package (``paged``, ``prefix_cache``, ``reserve``,
-``sampling``); the tests drive both with identical random workloads.
+``make_pool`` and ``make_reserve`` are what the backends and the scheduler construct: the C++ page pool and banker's-rule
+reserve when the library loads (the default), the Python classes otherwise (or with ``CUTEAFD_NATIVE_RT=0``).  Same
+behaviour either way; the tests drive both with identical random workloads.
 """
 from __future__ import annotations
 
@@ -24,9 +25,7 @@ def _lib():
         sig("cafd_seq_new", [P]); sig("cafd_seq_reserve", [P, I, I, IP, IP]); sig("cafd_seq_fork", [P, I, I])
         sig("cafd_seq_truncate", [P, I, I]); sig("cafd_seq_free", [P, I]); sig("cafd_seq_set_len", [P, I, I]); sig("cafd_seq_len", [P, I])
         sig("cafd_seq_num_pages", [P, I]); sig("cafd_seq_pages", [P, I, IP, I]); sig("cafd_seq_slots", [P, I, I, I, IP])
-        sig("cafd_prefix_new", [P, I], P); sig("cafd_prefix_free", [P], None)
-        sig("cafd_prefix_lookup", [P, C.POINTER(C.c_int32), I, IP, I, IP, IP]); sig("cafd_prefix_capture", [P, I, C.POINTER(C.c_int32), I, I])
-        sig("cafd_prefix_release", [P, I]); sig("cafd_prefix_held_pages", [P]); sig("cafd_prefix_snapshots", [P]); sig("cafd_prefix_evicted", [P])
+        sig("cafd_reserve_total", [P]); sig("cafd_reserve_count", [P]); sig("cafd_reserve_needs_top_up", [P, I, I])
         sig("cafd_reserve_new", [I, I], P); sig("cafd_reserve_free", [P], None); sig("cafd_reserve_lease", [P, I, I, I, I])
         sig("cafd_reserve_top_up", [P, I]); sig("cafd_reserve_release", [P, I]); sig("cafd_reserve_leased", [P])
         sig("cafd_sample_token", [C.POINTER(C.c_float), I, C.POINTER(C.c_uint8), C.c_float, C.c_float, I, C.c_float, C.c_uint64, C.c_uint64, I, C.c_float])
@@ -149,45 +148,6 @@ class NativePool:
         return list(buf[:n])
 
 
-class NativePrefix:
-    def __init__(self, pool: NativePool, max_pages: int):
-        self.L, self.pool = _lib(), pool
-        self.h = self.L.cafd_prefix_new(pool.h, max_pages)
-
-    def __del__(self):
-        if getattr(self, "h", None) and getattr(self.pool, "h", None):
-            self.L.cafd_prefix_free(self.h)
-            self.h = None
-
-    def lookup(self, tokens: list[int]) -> tuple[int, list[int], bool]:
-        n = len(tokens)
-        arr = (C.c_int32 * max(n, 1))(*tokens)
-        cap = n // 64 + 2
-        out = (C.c_int * cap)()
-        np_, tail = C.c_int(0), C.c_int(0)
-        length = self.L.cafd_prefix_lookup(self.h, arr, n, out, cap, C.byref(np_), C.byref(tail))
-        return length, list(out[:np_.value]), bool(tail.value)
-
-    def capture(self, seq: int, tokens: list[int], kind: str = "prompt") -> int:
-        arr = (C.c_int32 * max(len(tokens), 1))(*tokens)
-        return self.L.cafd_prefix_capture(self.h, seq, arr, len(tokens), 0 if kind == "prompt" else 1)
-
-    def release(self, sid: int) -> None:
-        self.L.cafd_prefix_release(self.h, sid)
-
-    @property
-    def held_pages(self) -> int:
-        return self.L.cafd_prefix_held_pages(self.h)
-
-    @property
-    def snapshots(self) -> int:
-        return self.L.cafd_prefix_snapshots(self.h)
-
-    @property
-    def evicted(self) -> int:
-        return self.L.cafd_prefix_evicted(self.h)
-
-
 class NativeReserve:
     def __init__(self, total_pages: int, chunk_tokens: int = 16384):
         self.L = _lib()
@@ -198,8 +158,29 @@ class NativeReserve:
             self.L.cafd_reserve_free(self.h)
             self.h = None
 
-    def lease(self, rid: int, prompt: int, max_new: int, shared_pages: int = 0) -> bool:
-        return bool(self.L.cafd_reserve_lease(self.h, rid, prompt, max_new, shared_pages))
+    def lease(self, rid: int, prompt: int, max_new: int, shared_pages: int = 0):
+        """Truthy when admitted, None when refused (the Python reserve returns the lease record or None)."""
+        return True if self.L.cafd_reserve_lease(self.h, rid, prompt, max_new, shared_pages) else None
+
+    def needs_top_up(self, rid: int, next_len_tokens: int) -> bool:
+        r = self.L.cafd_reserve_needs_top_up(self.h, rid, next_len_tokens)
+        if r < 0:
+            raise KeyError(rid)
+        return bool(r)
+
+    def note_used(self, rid: int, pages: int) -> None:
+        pass
+
+    @property
+    def total(self) -> int:
+        return self.L.cafd_reserve_total(self.h)
+
+    @property
+    def unleased(self) -> int:
+        return self.total - self.leased
+
+    def __len__(self) -> int:
+        return self.L.cafd_reserve_count(self.h)
 
     def top_up(self, rid: int) -> bool:
         return bool(self.L.cafd_reserve_top_up(self.h, rid))
@@ -227,3 +208,27 @@ def sample_token(logits, temperature=0.0, top_p=1.0, top_k=None, min_p=0.0, seed
 
 def sample_uniform(seed: int, position: int) -> float:
     return float(_lib().cafd_sample_uniform(seed, position))
+
+
+def enabled() -> bool:
+    """Whether the serving path builds its host structures on the C++ library (default: yes when it loads)."""
+    import os
+    if os.environ.get("CUTEAFD_NATIVE_RT", "1") == "0":
+        return False
+    try:
+        _lib()
+        return True
+    except OSError:
+        return False
+
+
+def make_reserve(total_pages: int, chunk_tokens: int = 16384):
+    if enabled():
+        return NativeReserve(total_pages, chunk_tokens)
+    from .reserve import KvReserve
+    return KvReserve(total_pages, chunk_tokens)
+
+
+def make_pool(num_pages: int):
+    from .paged import NativePagePool, PagePool
+    return NativePagePool(num_pages) if enabled() else PagePool(num_pages)

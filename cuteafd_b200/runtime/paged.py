@@ -60,6 +60,40 @@ class PagePool:
         return self.refs[p] > 1
 
 
+class NativePagePool(PagePool):
+    """The same pool with its reference counts and free list in the C++ runtime (``csrc/rt/cafd_rt.cc``): what the
+    serving backends construct when the library is present.  Same page order, same misuse checks."""
+
+    def __init__(self, num_pages: int):
+        from .native import NativePool
+        assert num_pages >= 2
+        self.num_pages = num_pages
+        self._n = NativePool(num_pages)
+        self.on_exhausted = None
+
+    @property
+    def free_pages(self) -> int:
+        return self._n.free_pages
+
+    def alloc(self) -> int:
+        p = self._n.L.cafd_pool_alloc(self._n.h)
+        if p < 0 and self.on_exhausted is not None:
+            self.on_exhausted(8)
+            p = self._n.L.cafd_pool_alloc(self._n.h)
+        if p < 0:
+            raise OutOfPages("KV page pool exhausted")
+        return p
+
+    def retain(self, p: int) -> None:
+        assert self._n.L.cafd_pool_retain(self._n.h, p) == 0, p
+
+    def release(self, p: int) -> None:
+        assert self._n.L.cafd_pool_release(self._n.h, p) == 0, p
+
+    def shared(self, p: int) -> bool:
+        return self._n.refs(p) > 1
+
+
 @dataclass
 class Sequence:
     seq_id: int

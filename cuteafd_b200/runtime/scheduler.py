@@ -25,7 +25,7 @@ from typing import Any, Protocol
 import torch
 
 from . import sampling
-from .reserve import KvReserve
+from .native import make_reserve
 from .speculation import DraftHistory, DrafterSpec, NoDrafter, Plan
 
 FAIL_BAD_REQUEST, FAIL_UNAVAILABLE, FAIL_RETRY, FAIL_WORKER = "bad_request", "unavailable", "retry", "worker"
@@ -139,7 +139,7 @@ class Scheduler:
         self.pending: list[Request] = []
         self.prefilling: list[Active] = []
         self.decoding: list[Active] = []
-        self.reserve = KvReserve(backend.total_pages - 1)        # page 0 is the reserved zero page
+        self.reserve = make_reserve(backend.total_pages - 1)     # page 0 is the reserved zero page; C++ reserve when the library loads
         self.drafter = drafter or NoDrafter()
         self.policy = DraftHistory(self.drafter.spec if hasattr(self.drafter, "spec") else DrafterSpec(0), draft_control)
         self.row_budget = row_budget or backend.max_decode_rows

@@ -9,47 +9,37 @@ from cuteafd_b200.runtime.prefix_cache import PROMPT, TURN, PrefixCache
 from cuteafd_b200.runtime.reserve import KvReserve
 
 
-def test_pool_and_prefix_match_python_model():
+def test_native_page_pool_matches_python_pool_under_the_prefix_cache():
+    """The C++ page pool behind the same ``SequenceTable`` + ``PrefixCache`` workload as the Python pool: every lookup,
+    every page id and every free count agree, step by step (this is the pool the serving backends construct)."""
+    from cuteafd_b200.runtime.paged import NativePagePool
     rng = random.Random(7)
     N = 96
-    ppool, npool = PagePool(N), native.NativePool(N)
-    ptab = SequenceTable(ppool)
-    pcache, ncache = PrefixCache(ppool, ptab, max_pages=40), native.NativePrefix(npool, 40)
+    worlds = []
+    for pool in (PagePool(N), NativePagePool(N)):
+        tab = SequenceTable(pool)
+        worlds.append((pool, tab, PrefixCache(pool, tab, max_pages=40)))
     bases = [[rng.randrange(500) for _ in range(300)] for _ in range(3)]
-    for step in range(200):
+    live = [[], []]
+    for step in range(300):
         base = rng.choice(bases)
         toks = base[: rng.choice((64, 100, 128, 200, 300))] + [rng.randrange(500) for _ in range(rng.choice((0, 5, 70)))]
-        # lookup must agree
-        pm = pcache.lookup(toks)
-        nl, npages, ntail = ncache.lookup(toks)
-        assert (pm.length, len(pm.pages), pm.tail_shared) == (nl, len(npages), ntail), (step, len(toks))
-        # admit on both, prefill the rest, capture, free
-        pseq = ptab.new()
-        for p in pm.pages:
-            ppool.retain(p)
-        pseq.pages, pseq.tokens, pseq.kv_len = list(pm.pages), list(toks[:pm.length]), pm.length
-        ptab.reserve(pseq, len(toks))
-        pseq.tokens, pseq.kv_len = list(toks), len(toks)
-        nseq = npool.new_seq()
-        # the native fork path: share the matched pages by retaining them through a scratch sequence
-        for pg in npages:
-            npool.L.cafd_pool_retain(npool.h, pg)
-        # emulate "seq.pages = matched pages" by reserving then swapping is not exposed; instead rebuild:
-        npool.free(nseq)
-        for pg in npages:
-            npool.L.cafd_pool_release(npool.h, pg)
-        nseq = npool.new_seq()
-        added, _ = npool.reserve(nseq, len(toks))
-        npool.set_len(nseq, len(toks))
-        assert added >= 0
-        kind = rng.choice((PROMPT, TURN))
-        ps = pcache.capture(pseq, kind)
-        ns = ncache.capture(nseq, toks, kind)
-        assert (ps is not None) == (ns > 0)
-        ptab.free(pseq)
-        npool.free(nseq)
-        assert ncache.held_pages <= 40 and pcache.held_pages <= 40
-    assert ncache.snapshots > 0
+        kind, drop = rng.choice((PROMPT, TURN)), rng.random() < 0.7
+        seen = []
+        for w, (pool, tab, cache) in enumerate(worlds):
+            seq, m = cache.admit(toks)
+            tab.reserve(seq, len(toks))
+            seq.tokens, seq.kv_len = list(toks), len(toks)
+            snap = cache.capture(seq, kind)
+            live[w].append(seq)
+            if drop or len(live[w]) > 3:
+                tab.free(live[w].pop(0))
+            seen.append((m.length, list(seq.pages), snap is not None, pool.free_pages, cache.held_pages))
+        assert seen[0] == seen[1], (step, seen)
+    assert worlds[1][2].held_pages > 0 and type(native.make_pool(8)).__name__ == "NativePagePool"
+    import pytest
+    with pytest.raises(AssertionError):
+        worlds[1][0].release(0)                        # the reserved page is never released
 
 
 def test_native_cow_fork_truncate():
@@ -79,17 +69,20 @@ def test_reserve_matches_python_model():
         if op < 0.5:
             p, m = rng.randrange(64, 3000), rng.randrange(64, 4000)
             a = py.lease(rid, p, m) is not None
-            b = nat.lease(rid, p, m)
+            b = nat.lease(rid, p, m) is not None
             assert a == b
             if a:
                 live.append(rid)
         elif op < 0.8 and live:
             r = rng.choice(live)
+            n = rng.randrange(1, 8000)
+            assert py.needs_top_up(r, n) == nat.needs_top_up(r, n)
             assert py.top_up(r) == nat.top_up(r)
         elif live:
             r = live.pop(rng.randrange(len(live)))
             py.release(r); nat.release(r)
-        assert py.leased == nat.leased
+        assert py.leased == nat.leased and py.unleased == nat.unleased and len(py.leases) == len(nat)
+    assert type(native.make_reserve(10)).__name__ == "NativeReserve" and nat.total == 200
 
 
 def test_native_sampler_matches_oracle():
