@@ -54,11 +54,23 @@ __device__ __forceinline__ void load_page(uint8_t* dst, const __nv_bfloat16* cac
 // partial layout per (tile, kvh, split): [16 rows][kD] fp32 O (unnormalised), then m[16], l[16]
 constexpr int kPartialFloats = 16 * kD + 32;
 
+// Context split (the KV of a sequence dealt over several GPUs by page): every rank runs this kernel over the pages it
+// holds and stores its partials into EVERY rank's scratch, at split slots [split_offset, split_offset + splits) of
+// total_splits, so that each rank's merge walks all ranks' partials in rank order.  n == 0: the single-GPU form.
+// kv_base (optional, per sequence): query token qi sees the first min(seq_len, kv_base + qi + 1) local positions; the
+// default seq_len - q_len is the causal rule when the new tokens are the last local ones, and a rank that does not
+// hold the new tokens passes its local length (everything it holds is in the past of every query).
+struct AttnPeers {
+  float* scratch[8];
+  int n, split_offset, total_splits;
+};
+
 __global__ void __launch_bounds__(128) attn_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ page_table, const int* __restrict__ seq_lens,
     const int* __restrict__ q_start, __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int max_pages,
-    int Hq, int Hkv, int tiles_per_seq, int splits, float scale_log2) {
+    int Hq, int Hkv, int tiles_per_seq, int splits, float scale_log2, const int* __restrict__ kv_base,
+    const AttnPeers peers) {
   pdl_wait();
   pdl_trigger();
   extern __shared__ __align__(128) uint8_t smem[];
@@ -74,9 +86,13 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
   const int q0 = q_start[seq], q_len = q_start[seq + 1] - q0;
   const int seq_len = seq_lens[seq];
   const int first_q = qt * q_per_tile;
-  float* part = partial + (static_cast<size_t>(blockIdx.x) * Hkv + kvh) * splits * kPartialFloats +
-                static_cast<size_t>(split) * kPartialFloats;
+  const size_t part_off = peers.n
+      ? (static_cast<size_t>(blockIdx.x) * Hkv + kvh) * peers.total_splits * kPartialFloats +
+            static_cast<size_t>(peers.split_offset + split) * kPartialFloats
+      : (static_cast<size_t>(blockIdx.x) * Hkv + kvh) * splits * kPartialFloats + static_cast<size_t>(split) * kPartialFloats;
+  float* part = partial + part_off;
   if (first_q >= q_len) return;   // tile beyond this sequence's queries: nothing to write
+  const int base_vis = kv_base ? kv_base[seq] : seq_len - q_len;
 
   // ---- Q fragments straight from global memory ------------------------------------------------
   // row r of the tile = query token first_q + r / group, head kvh * group + r % group
@@ -87,7 +103,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
     const int r = g + 8 * half;
     const int qi = first_q + r / group;
     const bool valid = qi < q_len;
-    limit[half] = valid ? (seq_len - q_len + qi + 1) : 0;
+    limit[half] = valid ? min(seq_len, base_vis + qi + 1) : 0;
     const __nv_bfloat16* qrow = q + (static_cast<size_t>(q0 + (valid ? qi : 0)) * Hq + kvh * group + r % group) * kD;
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
@@ -231,7 +247,13 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
       L += sm_l[w * 16 + r] * f;
       O += sm_o[(w * 16 + r) * kD + d] * f;
     }
-    if (splits == 1) {
+    if (peers.n) {
+      for (int pr = 0; pr < peers.n; ++pr) {              // plain peer stores; the flag that publishes them follows in stream order
+        float* dst = peers.scratch[pr] + part_off;
+        dst[r * kD + d] = O;
+        if (d == 0) { dst[16 * kD + r] = M; dst[16 * kD + 16 + r] = L; }
+      }
+    } else if (splits == 1) {
       const int qi = first_q + r / group;
       if (qi < q_len) {
         __nv_bfloat16* orow = out + (static_cast<size_t>(q0 + qi) * Hq + kvh * group + r % group) * kD;
@@ -305,11 +327,63 @@ extern "C" int cafd_attn_decode(const void* q, const void* k_cache, const void* 
   launch_pdl(attn_decode_kernel, grid, dim3(128), smem, st, 
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
       static_cast<const __nv_bfloat16*>(v_cache), page_table, seq_lens, q_start, static_cast<__nv_bfloat16*>(out),
-      scratch, max_pages, Hq, Hkv, tiles_per_seq, splits, scale * 1.4426950408889634f);
+      scratch, max_pages, Hq, Hkv, tiles_per_seq, splits, scale * 1.4426950408889634f, static_cast<const int*>(nullptr),
+      AttnPeers{});
   if (splits > 1) {
     dim3 g2(num_seqs * tiles_per_seq, Hkv, 16);
     launch_pdl(attn_merge_kernel, g2, dim3(128), 0, st, scratch, q_start, static_cast<__nv_bfloat16*>(out), Hq, Hkv, tiles_per_seq,
                                           splits);
   }
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Context-split form, first half: partial attention over this rank's pages, stored into the scratch of every rank of
+// the group (peer_scratch[r], r < n_peers; this rank's own buffer included) at split slots
+// [my_rank * splits, (my_rank + 1) * splits) of n_peers * splits.  The caller publishes the stores with a flag per peer
+// and merges with cafd_attn_merge once every rank's flag has arrived.
+extern "C" int cafd_attn_decode_partial(const void* q, const void* k_cache, const void* v_cache, const int* page_table,
+                                        const int* seq_lens, const int* kv_base, const int* q_start, void* const* peer_scratch,
+                                        int n_peers, int my_rank, int num_seqs, int max_q_len, int max_pages, int Hq, int Hkv,
+                                        int D, int splits, float scale, cafd_stream_t s) {
+  if (num_seqs <= 0) return 0;
+  if (D != kD || Hq % Hkv || n_peers < 1 || n_peers > 8 || my_rank < 0 || my_rank >= n_peers || !peer_scratch) return -10;
+  const int group = Hq / Hkv;
+  if (group > 16 || 16 % group) return -11;
+  if (splits < 1) splits = 1;
+  const int q_per_tile = 16 / group;
+  const int tiles_per_seq = (max_q_len + q_per_tile - 1) / q_per_tile;
+  cudaStream_t st = static_cast<cudaStream_t>(s);
+  const int smem = 4 * kTileBytes;
+  static bool attr = false;
+  if (!attr) {
+    CAFD_CHECK_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr = true;
+  }
+  AttnPeers peers{};
+  for (int r = 0; r < n_peers; ++r) {
+    if (!peer_scratch[r]) return -12;
+    peers.scratch[r] = static_cast<float*>(peer_scratch[r]);
+  }
+  peers.n = n_peers; peers.split_offset = my_rank * splits; peers.total_splits = n_peers * splits;
+  dim3 grid(num_seqs * tiles_per_seq, Hkv, splits);
+  launch_pdl(attn_decode_kernel, grid, dim3(128), smem, st, static_cast<const __nv_bfloat16*>(q),
+             static_cast<const __nv_bfloat16*>(k_cache), static_cast<const __nv_bfloat16*>(v_cache), page_table, seq_lens, q_start,
+             static_cast<__nv_bfloat16*>(nullptr), peers.scratch[my_rank], max_pages, Hq, Hkv, tiles_per_seq, splits,
+             scale * 1.4426950408889634f, kv_base, peers);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Second half: merge total_splits partials per (tile, kv head) from this rank's scratch in slot order.
+extern "C" int cafd_attn_merge(const float* scratch, const int* q_start, void* out, int num_seqs, int max_q_len, int Hq, int Hkv,
+                               int total_splits, cafd_stream_t s) {
+  if (num_seqs <= 0) return 0;
+  if (Hq % Hkv || total_splits < 1 || !scratch) return -10;
+  const int group = Hq / Hkv;
+  if (group > 16 || 16 % group) return -11;
+  const int q_per_tile = 16 / group;
+  const int tiles_per_seq = (max_q_len + q_per_tile - 1) / q_per_tile;
+  dim3 g2(num_seqs * tiles_per_seq, Hkv, 16);
+  launch_pdl(attn_merge_kernel, g2, dim3(128), 0, static_cast<cudaStream_t>(s), scratch, q_start, static_cast<__nv_bfloat16*>(out),
+             Hq, Hkv, tiles_per_seq, total_splits);
   return static_cast<int>(cudaGetLastError());
 }

@@ -360,6 +360,31 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, p
     return out
 
 
+def attn_decode_partial(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
+                        seq_lens: torch.Tensor, kv_base: torch.Tensor, q_start: torch.Tensor, peer_scratch: list[int], my_rank: int,
+                        max_q_len: int, splits: int, scale: float | None = None) -> None:
+    """Context split, first half: attention over the pages this rank holds; the unnormalised partials (O, m, l) go into
+    every rank's scratch (``peer_scratch`` device addresses, this rank's own included) at this rank's split slots."""
+    _, Hq, D = q.shape
+    Hkv = k_cache.shape[1]
+    num_seqs, max_pages = page_table.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    arr = (C.c_void_p * 8)(*peer_scratch)
+    _n.check(_n.cuda_lib().cafd_attn_decode_partial(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_table.data_ptr(),
+                                                    seq_lens.data_ptr(), kv_base.data_ptr(), q_start.data_ptr(), arr, len(peer_scratch),
+                                                    my_rank, num_seqs, max_q_len, max_pages, Hq, Hkv, D, splits, scale, _stream()),
+             "attn_decode_partial")
+
+
+def attn_merge(scratch: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor, max_q_len: int, Hkv: int, total_splits: int) -> torch.Tensor:
+    """Context split, second half: merge ``total_splits`` partials per (tile, kv head) in slot order into ``out``
+    [total_q, Hq, D]."""
+    _, Hq, _ = out.shape
+    _n.check(_n.cuda_lib().cafd_attn_merge(scratch.data_ptr(), q_start.data_ptr(), out.data_ptr(), q_start.shape[0] - 1, max_q_len,
+                                           Hq, Hkv, total_splits, _stream()), "attn_merge")
+    return out
+
+
 def attn_decode_scratch_floats(num_seqs: int, max_q_len: int, Hq: int, Hkv: int, splits: int) -> int:
     q_per_tile = 16 // (Hq // Hkv)
     tiles = (max_q_len + q_per_tile - 1) // q_per_tile

@@ -13,10 +13,13 @@ With a sparse-attention indexer there is a fourth: every rank scores its own pos
 candidate lists ([R, k] scores and positions per rank) are merged into the global top-k (ties to the lower
 position) before step 2.
 
-This module is the host-side form: plain tensor math per rank and ``torch.distributed`` collectives, which is what the
-CPU oracle and the gloo tests run.  On GPUs the same three steps map onto kernels that already exist: the split-KV
-attention kernels write exactly these partials (unnormalised O, m, l per split) and ``*_merge_kernel`` merges them in
-split order, so a rank's partials become "splits" of the owner's merge; that binding is not wired yet.
+The first half of this module is the host-side form: plain tensor math per rank and ``torch.distributed`` collectives,
+which is what the CPU oracle and the gloo tests run.  The second half (``DeviceContextSplit``, ``ContextSplitEngine``,
+``ContextSplitDriver``) is the GPU form for the GQA family: the split-KV decode attention kernel runs over the pages a
+rank holds and stores its partials (unnormalised O, m, l per split) straight into every rank's scratch over NVLink, a
+flag per peer publishes them, and the merge kernel walks all ranks' partials in rank order, so a rank's partials are
+simply further "splits" of one merge.  Step 1 costs nothing there because every rank projects all heads (the
+projections are replicated; what the split buys is KV capacity and attention bandwidth for long contexts).
 
 Counterpart: rust/crates/cuteafd-daemon/src/shared/peer_split/context.rs:1-90 (degree 2, query all-gather, candidate
 merge, partial + LSE combine) and native/shared/cuda/attention.cu:925 (state merge).
@@ -131,3 +134,151 @@ class ContextSplit:
         dv = o.shape[-1]
         parts = [(e[:, lo:lo + hn, :dv], e[:, lo:lo + hn, dv], e[:, lo:lo + hn, dv + 1]) for e in every]
         return merge_partials(parts)
+
+
+# ---- GPU form --------------------------------------------------------------------------------------------------------
+class DeviceContextSplit:
+    """Symmetric scratch + flags of a context-split group.  ``attend`` = partial attention over the local pages (stored
+    into every rank's scratch) -> publish -> wait for every rank -> merge.  Two scratch buffers alternate, so a fast
+    rank's partials of the next layer never land in a buffer a slow rank is still merging (it cannot run two layers
+    ahead: its own merge of the next layer waits for the slow rank's partials)."""
+
+    def __init__(self, num_heads: int, num_kv_heads: int, head_dim: int, max_seqs: int, max_q_len: int, splits: int,
+                 device: torch.device, group=None):
+        from ..ops import kernels as K
+        from .afd import SymmetricHeap, _align
+        self.group = group or dist.group.WORLD
+        self.ranks, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.Hq, self.Hkv, self.D, self.splits, self.device = num_heads, num_kv_heads, head_dim, splits, device
+        self.max_seqs, self.max_q_len = max_seqs, max_q_len
+        floats = K.attn_decode_scratch_floats(max_seqs, max_q_len, num_heads, num_kv_heads, splits * self.ranks)
+        self.buf_bytes = _align(floats * 4)
+        self.off_flags = 2 * self.buf_bytes
+        self.heap = SymmetricHeap(self.off_flags + 1024, device, self.group)
+        self.scratch = [self.heap.view(i * self.buf_bytes, floats * 4, torch.float32) for i in range(2)]
+        self.flags = self.heap.view(self.off_flags, 64, torch.int32)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.turn = 0
+        import ctypes as C
+        self._flag_ptrs = (C.c_void_p * 8)(*[self.heap.ptrs[r] + self.off_flags + 4 * self.rank for r in range(self.ranks)])
+
+    def attend(self, q, k_cache, v_cache, page_table, seq_lens, kv_base, q_start, out, max_q_len: int):
+        """q [T, Hq, D] (all heads), local page table / local lengths / visibility bases -> out [T, Hq, D] on every rank."""
+        from .._native import lib as _n
+        from ..ops import kernels as K
+        assert page_table.shape[0] <= self.max_seqs and max_q_len <= self.max_q_len
+        b = self.turn & 1
+        self.turn += 1
+        K.bump_epoch(self.epoch)
+        peers = [self.heap.ptrs[r] + b * self.buf_bytes for r in range(self.ranks)]
+        K.attn_decode_partial(q, k_cache, v_cache, page_table, seq_lens, kv_base, q_start, peers, self.rank, max_q_len, self.splits)
+        _n.check(_n.cuda_lib().cafd_tp_signal(self._flag_ptrs, self.ranks, self.epoch.data_ptr(), K._stream()), "context split signal")
+        for r in range(self.ranks):
+            K.wait_flag(self.flags.data_ptr() + 4 * r, self.epoch)
+        return K.attn_merge(self.scratch[b], q_start, out, max_q_len, self.Hkv, self.splits * self.ranks)
+
+
+def local_pages(n_pages: int, rank: int, ranks: int) -> int:
+    """How many of the logical pages [0, n_pages) rank ``rank`` holds."""
+    return max(0, (n_pages - rank + ranks - 1) // ranks)
+
+
+def local_len(kv_len: int, rank: int, ranks: int, page: int = PAGE) -> int:
+    """How many of the positions [0, kv_len) rank ``rank`` holds."""
+    full, tail = divmod(kv_len, page)
+    n = local_pages(full, rank, ranks) * page
+    return n + (tail if full % ranks == rank else 0)
+
+
+def make_engine(cfg, weights, num_pages: int, max_tokens: int, max_seqs: int, group=None, splits: int = 4):
+    """A GQA MoE engine whose attention reads a context-split KV cache.  Everything else is the single-GPU engine,
+    replicated on every rank of the group."""
+    from ..models.gqa_moe import GqaMoeEngine, KvCache
+    from ..ops import kernels as K
+
+    class ContextSplitEngine(GqaMoeEngine):
+        def __init__(self):
+            dev = weights.embed.device
+            super().__init__(cfg, weights, KvCache(cfg, num_pages, dev), max_tokens, max_seqs)
+            self.cs = DeviceContextSplit(cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, max_seqs, PAGE, splits, dev, group)
+
+        def _attention(self, i: int, T: int, b) -> None:
+            c, L, ws = self.cfg, self.W.layers[i], self.ws
+            K.linear(ws.x[:T], L.wqkv, out=ws.qkv[:T])
+            # slots are -1 on the ranks that do not hold the page of a new token: their K / V rows are dropped there
+            K.qk_rope_kv(ws.qkv[:T], L.q_norm, L.k_norm, self.inv_freq, b.positions, b.slots, ws.q[:T], self.kv.k[i],
+                         self.kv.v[i], c.num_heads, c.num_kv_heads, c.head_dim, c.rms_eps, c.rope_interleaved)
+            self.cs.attend(ws.q[:T], self.kv.k[i], self.kv.v[i], b.page_table, b.seq_lens, b.kv_base, b.q_start, ws.attn[:T],
+                           b.max_q_len)
+            K.linear(ws.attn[:T].view(T, -1), L.wo, out=ws.h[:T], residual=ws.h[:T])
+            self.launches += 7 + self.cs.ranks
+
+    return ContextSplitEngine()
+
+
+class ContextSplitDriver:
+    """Per-rank bookkeeping of a context-split cache: which physical pages hold this rank's share of every sequence,
+    and the step descriptions (local page table, local lengths, visibility bases, KV slots) the engine wants.  Steps
+    never span a page boundary (a prompt goes in page-sized chunks), so the new tokens of a step live on one rank."""
+
+    def __init__(self, engine, num_pages: int, max_pages_per_seq: int):
+        from ..runtime.native import make_pool
+        self.eng, self.pool, self.max_pages = engine, make_pool(num_pages), max_pages_per_seq
+        self.ranks, self.rank = engine.cs.ranks, engine.cs.rank
+        self.pages: dict[int, list[int]] = {}
+        self.kv_len: dict[int, int] = {}
+        self._next = 0
+
+    def new(self) -> int:
+        s, self._next = self._next, self._next + 1
+        self.pages[s], self.kv_len[s] = [], 0
+        return s
+
+    def free(self, s: int) -> None:
+        for p in self.pages.pop(s):
+            self.pool.release(p)
+        del self.kv_len[s]
+
+    def _batch(self, items: list[tuple[int, list[int]]]):
+        """items: (sequence, new tokens) with every run inside one page."""
+        from ..models.gqa_moe import Batch
+        dev = self.eng.device
+        S = len(items)
+        toks, pos, slots, lens, base, qs = [], [], [], [], [], [0]
+        table = torch.zeros(S, self.max_pages, dtype=torch.int32)
+        for i, (s, new) in enumerate(items):
+            start, n = self.kv_len[s], len(new)
+            assert n and start // PAGE == (start + n - 1) // PAGE, "a step stays inside one page"
+            owner = (start // PAGE) % self.ranks
+            need = local_pages((start + n + PAGE - 1) // PAGE, self.rank, self.ranks)
+            while len(self.pages[s]) < need:
+                self.pages[s].append(self.pool.alloc())
+            table[i, :len(self.pages[s])] = torch.tensor(self.pages[s], dtype=torch.int32)
+            mine = owner == self.rank
+            ll = local_len(start + n, self.rank, self.ranks)
+            for j in range(n):
+                p = start + j
+                toks.append(new[j]); pos.append(p)
+                slots.append(self.pages[s][(p // PAGE) // self.ranks] * PAGE + p % PAGE if mine else -1)
+            lens.append(ll)
+            base.append(ll - n if mine else ll)          # a rank without the new tokens: all it holds is in their past
+            qs.append(qs[-1] + n)
+            self.kv_len[s] = start + n
+        t = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)                    # noqa: E731
+        b = Batch(t(toks), t(pos), t(slots), table.to(dev), t(lens), t(qs), max(len(n) for _, n in items), False,
+                  t([q - 1 for q in qs[1:]]))
+        b.kv_base = t(base)
+        return b
+
+    def prefill(self, s: int, tokens: list[int]) -> torch.Tensor:
+        """Append a prompt in page-sized chunks; returns the logits after its last token [1, vocab]."""
+        logits, i = None, 0
+        while i < len(tokens):
+            n = min(PAGE - self.kv_len[s] % PAGE, len(tokens) - i)
+            logits = self.eng.forward(self._batch([(s, tokens[i:i + n])]))
+            i += n
+        return logits
+
+    def decode(self, seqs: list[int], last_tokens: list[int]) -> torch.Tensor:
+        """One step for every sequence; logits [S, vocab]."""
+        return self.eng.forward(self._batch([(s, [t]) for s, t in zip(seqs, last_tokens)]))
