@@ -404,3 +404,56 @@ def reference_compute(stack_of, lo: int):
             out[torch.from_numpy(sel)] = y.to(x.dtype).float() * torch.from_numpy(weight[sel])[:, None]
         return out
     return compute
+
+
+def cuda_compute(stack_of, lo: int, device, expert_ffn: int):
+    """``compute`` for ``ExpertServer`` on a GPU: the request's routes are sorted by expert into an expert-major slab with
+    tile tables, and the routed FFN runs on the tcgen05 expert-grouped GEMMs (fc1 + SwiGLU, then fc2 with its epilogue
+    scattering every row back to its route slot), the same kernels the NVLink expert ranks run.  ``stack_of(layer) ->
+    (gate, up, down)`` bf16 stacks [n, I, H] / [n, H, I] on ``device`` for the experts [lo, lo + n).  Rows come back as
+    bf16-rounded expert outputs times the route weight, as from ``reference_compute``."""
+    from ..ops import kernels as K
+    from .moe_exchange import pick_tile_rows
+    dev = torch.device(device)
+    state: dict = {}
+
+    def buffers(rows: int, tiles: int, H: int):
+        cap = state.get("cap", (0, 0, 0))
+        if rows > cap[0] or tiles > cap[1] or H != cap[2]:
+            rows, tiles = max(rows, 2 * cap[0], 256), max(tiles, 2 * cap[1], 64)
+            state.update(cap=(rows, tiles, H), slab=torch.zeros(rows, H, dtype=torch.bfloat16, device=dev),
+                         hbuf=torch.zeros(rows, expert_ffn, dtype=torch.bfloat16, device=dev),
+                         out=torch.zeros(rows, H, dtype=torch.bfloat16, device=dev))
+        return state["slab"], state["hbuf"], state["out"], state["cap"][1]
+
+    def compute(layer: int, x: torch.Tensor, row: np.ndarray, expert: np.ndarray, weight: np.ndarray) -> torch.Tensor:
+        gate, up, down = stack_of(layer)
+        n_exp, n, H = gate.shape[0], len(row), x.shape[1]
+        if n == 0:
+            return torch.zeros(0, H, dtype=torch.float32)
+        tile = pick_tile_rows(max(1, n // max(1, len(np.unique(expert)))), 1, 1)
+        order = np.argsort(expert, kind="stable")
+        local = expert[order].astype(np.int64) - lo
+        counts = np.bincount(local, minlength=n_exp)
+        padded = (counts + tile - 1) // tile * tile
+        seg = np.concatenate([[0], np.cumsum(padded)])
+        first = np.concatenate([[0], np.cumsum(counts)])
+        slab_row = seg[local] + (np.arange(n) - first[local])             # slab position of every sorted route
+        total = int(seg[-1])
+        tile_expert = np.repeat(np.arange(n_exp), padded // tile).astype(np.int32)
+        tile_row0 = np.concatenate([seg[e] + tile * np.arange(padded[e] // tile) for e in range(n_exp)]).astype(np.int32)
+        row_dst = np.full(total, -1, dtype=np.int32)
+        row_dst[slab_row] = order                                          # fc2's epilogue stores slab row r at out[row_dst[r]]
+        slab, hbuf, out, max_tiles = buffers(total, len(tile_expert), H)
+        xs = x.to(device=dev, dtype=torch.bfloat16)
+        slab[:total].zero_()
+        slab[torch.from_numpy(slab_row).to(dev)] = xs[torch.from_numpy(row[order].astype(np.int64)).to(dev)]
+        te = torch.zeros(max_tiles, dtype=torch.int32, device=dev); te[:len(tile_expert)] = torch.from_numpy(tile_expert).to(dev)
+        t0 = torch.zeros(max_tiles, dtype=torch.int32, device=dev); t0[:len(tile_row0)] = torch.from_numpy(tile_row0).to(dev)
+        nt = torch.tensor([len(tile_expert)], dtype=torch.int32, device=dev)
+        rd = torch.from_numpy(row_dst).to(dev)
+        K.grouped_linear(slab, gate, hbuf, te, t0, nt, max_tiles, tile, w_up=up)
+        K.grouped_linear(hbuf, down, hbuf, te, t0, nt, max_tiles, tile, row_dst=rd, out_ptr=out.data_ptr(), ldo=H)
+        y = out[:n].float() * torch.from_numpy(weight.astype(np.float32)).to(dev)[:, None]
+        return y.cpu()
+    return compute

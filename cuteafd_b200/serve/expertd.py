@@ -12,8 +12,9 @@ import os
 
 
 def run_tcp_worker(args) -> int:
-    """Off-box worker: serves experts [first, end) of a snapshot over the wire protocol (``parallel/wire.py``).  The
-    experts run as plain tensor code on ``--device``; the plan hash covers the model name and the expert range, so an
+    """Off-box worker: serves experts [first, end) of a snapshot over the wire protocol (``parallel/wire.py``).  On a
+    CUDA ``--device`` the routed FFN runs on the tcgen05 expert-grouped GEMMs (``wire.cuda_compute``); on ``cpu`` it is
+    plain tensor code (the oracle's arithmetic).  The plan hash covers the model name and the expert range, so an
     attention rank configured for another split is refused at the handshake."""
     import time
 
@@ -28,10 +29,13 @@ def run_tcp_worker(args) -> int:
     def stack_of(layer: int):
         if layer not in stacks:
             m = f"model.layers.{layer}.mlp.experts."
-            stacks[layer] = tuple(torch.stack([params[f"{m}{e}.{n}_proj.weight"] for e in range(lo, hi)]) for n in ("gate", "up", "down"))
+            stacks[layer] = tuple(torch.stack([params[f"{m}{e}.{n}_proj.weight"] for e in range(lo, hi)]).contiguous()
+                                  for n in ("gate", "up", "down"))
         return stacks[layer]
     plan = wire.plan_hash({"model": cfg.name, "experts": cfg.num_experts, "range": [lo, hi]})
-    srv = wire.ExpertServer(wire.reference_compute(stack_of, lo), plan, args.host, args.tcp_port).start()
+    on_gpu = str(args.device).startswith("cuda")
+    compute = wire.cuda_compute(stack_of, lo, args.device, cfg.expert_ffn) if on_gpu else wire.reference_compute(stack_of, lo)
+    srv = wire.ExpertServer(compute, plan, args.host, args.tcp_port).start()
     print(f"expert worker for experts [{lo}, {hi}) of {cfg.name} on {args.host}:{srv.port}", flush=True)
     try:
         while True:

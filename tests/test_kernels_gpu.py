@@ -461,3 +461,41 @@ def test_bounds_check_build_catches_a_row_past_the_slab(K):
         assert rec["clean"] == [] and rec["kept"] and rec["skipped"], (T, rec)
         (site, idx), = rec["bad"]
         assert "slab row" in site and rec["rows"] - 3 <= idx < rec["rows"], (T, rec)
+
+
+def test_tcp_expert_worker_computes_on_the_gpu(K):
+    """The off-box expert worker's CUDA compute (route sort on the host, tcgen05 grouped GEMMs, scatter back to route
+    order) against its plain-tensor twin, called directly and through the wire server."""
+    import numpy as np
+    from cuteafd_b200.parallel import wire
+    H, I, n_exp, lo = 512, 256, 6, 10
+    g = torch.Generator().manual_seed(4)
+    stacks = tuple((torch.randn(n_exp, a, b, generator=g) * 0.05).to(torch.bfloat16) for a, b in ((I, H), (I, H), (H, I)))
+    on_gpu = tuple(t.to(dev()).contiguous() for t in stacks)
+    cpu_fn = wire.reference_compute(lambda layer: stacks, lo)
+    gpu_fn = wire.cuda_compute(lambda layer: on_gpu, lo, "cuda:0", I)
+    rng = np.random.default_rng(0)
+    for rows, routes in ((5, 9), (40, 150), (300, 1200), (3, 1)):
+        x = (torch.randn(rows, H, generator=g)).to(torch.bfloat16)
+        row = rng.integers(0, rows, routes).astype(np.int64)
+        expert = (lo + rng.integers(0, n_exp - 1, routes)).astype(np.int64)            # the last expert gets no rows
+        weight = rng.random(routes).astype(np.float32)
+        want = cpu_fn(0, x, row, expert, weight)
+        got = gpu_fn(0, x, row, expert, weight)
+        check_status(K)
+        assert got.shape == want.shape and got.dtype == torch.float32
+        close(got, want, 2e-2, 1e-2)
+    plan = wire.plan_hash({"m": 1})
+    srv = wire.ExpertServer(gpu_fn, plan).start()
+    try:
+        remote = wire.RemoteExperts([("127.0.0.1", srv.port, lo, lo + n_exp)], plan)
+        x = torch.randn(16, H, generator=g).to(torch.bfloat16)
+        idx = torch.randint(lo, lo + n_exp, (16, 2), generator=g)
+        w = torch.rand(16, 2, generator=g)
+        got = remote(0, x, idx, w).sum(1)
+        want = sum(cpu_fn(0, x, np.arange(16), idx[:, s].numpy(), w[:, s].numpy()) for s in range(2))
+        close(got, want, 2e-2, 1e-2)
+        assert srv.served > 0
+        remote.close()
+    finally:
+        srv.stop()
