@@ -54,6 +54,18 @@ CONFIG_KEYS = {"MODEL", "GPUS", "ATTENTION_RANKS", "EXPERT_RANKS", "POOL_TOKENS"
                "HTTP_QUEUE_DEPTH", "HTTP_QUEUE_WAIT", "PROFILE", "SPECULATION_TRACE", "KV_FORMAT", "EXPERT_FORMAT"}
 
 
+def graph_reserve_of(value: str) -> tuple[int, str]:
+    """``--graph-reserve``: a prewarm file a serving run saved (its measured base + extra bytes) or a plain size."""
+    if os.path.exists(value):
+        with open(value) as f:
+            doc = json.load(f)
+        if "reserve_base_bytes" not in doc:
+            print(f"plan: {value} carries no measured graph bytes (written by an older run?)", file=sys.stderr)
+            raise SystemExit(2)
+        return int(doc["reserve_base_bytes"]) + int(doc.get("reserve_extra_bytes", 0)), f"measured: {os.path.basename(value)}"
+    return _size(value), "user override"
+
+
 def cmd_plan(a: argparse.Namespace) -> int:
     from .planner import plan as P
     if a.fetch:
@@ -67,6 +79,8 @@ def cmd_plan(a: argparse.Namespace) -> int:
               gpu_memory_cap=_size(a.gpu_memory_cap) if a.gpu_memory_cap else None, max_context_tokens=a.max_context_tokens,
               concurrency=a.concurrency, speculator=a.speculator, decode_lanes=a.decode_lanes,
               pipeline_stages=a.pipeline_stages, expert_format=a.expert_format, kv_format=a.kv_format)
+    if a.graph_reserve:
+        kw["graph_reserve_bytes"], kw["graph_reserve_source"] = graph_reserve_of(a.graph_reserve)
     rep = P.plan(a.model, layout=a.layout or a.deployment, fmt=a.format, **kw)
     if a.deployment:
         if not (rep.placement and rep.placement.ok):
@@ -381,6 +395,8 @@ def _build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-context-tokens", type=int, default=None); p.add_argument("--concurrency", type=int, default=None)
     p.add_argument("--speculator", default=None, choices=["auto", "off", "mtp"]); p.add_argument("--decode-lanes", type=int, default=None, choices=[1, 2])
     p.add_argument("--format", default=None); p.add_argument("--expert-format", default=None); p.add_argument("--kv-format", default=None)
+    p.add_argument("--graph-reserve", default="", help="decode-graph arena per attention GPU: a prewarm file saved by a serving run "
+                                                      "(its measured bytes) or a size such as 600MiB (default: 256 MiB per lane, unmeasured)")
     p.set_defaults(fn=cmd_plan)
 
     s = sub.add_parser("serve", help="HTTP serving (OpenAI / Anthropic compatible)")

@@ -80,6 +80,10 @@ class PlacementRequest:
     kv_format: str = "auto"                 # auto | bf16 | fp8_ds_mla
     reserve_fraction: float = 0.04          # allocator slack + CUDA context per device
     redundant_experts: int = 0              # extra hot-expert replicas per expert rank
+    # Decode-graph arena per attention device.  None = the unmeasured default (256 MiB per lane); a measured value is
+    # base + extra bytes from a prewarm file a serving run wrote (``EngineBackend.save_prewarm``), or a user override.
+    graph_reserve_bytes: int | None = None
+    graph_reserve_source: str = "default"
 
 
 @dataclass
@@ -209,7 +213,10 @@ def _place(req: PlacementRequest, att: int, exp: int, pp: int) -> Placement:
                 if colocated:
                     rows = act_rows * cfg.top_k + e_max * 128
                     g.add("exchange", "slab+fc1", rows * (cfg.hidden + cfg.expert_ffn) * 2)
-            g.add("graphs", "decode graphs", (256 << 20) * req.decode_lanes)
+            if req.graph_reserve_bytes is None:
+                g.add("graphs", "decode graphs (default)", (256 << 20) * req.decode_lanes)
+            else:
+                g.add("graphs", f"decode graphs ({req.graph_reserve_source})", req.graph_reserve_bytes * req.decode_lanes)
             g.add("reserve", "context+slack", req.gpu_memory_cap * req.reserve_fraction)
     # ---- expert devices ------------------------------------------------------------------------------
     for r in range(exp):

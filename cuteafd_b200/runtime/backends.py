@@ -222,7 +222,15 @@ class EngineBackend:
         self.max_graphs, self.graph_after = 32, 2
         self.graphs: dict[tuple[int, int, int], tuple] = {}
         self.geometry_seen: dict[tuple[int, int, int], int] = {}
-        self.graph_stats = {"replays": 0, "eager": 0, "captures": 0, "evictions": 0}
+        self.graph_stats = {"replays": 0, "eager": 0, "captures": 0, "evictions": 0, "refused": 0}
+        # Byte-measured graph arena: every capture is charged the device memory it made the allocator reserve (the
+        # graph's private pool), the bank stays under ``graph_budget_bytes`` by dropping least recently used graphs, and a
+        # capture that would not fit even then is refused (that geometry stays on the eager path).  The measured base
+        # (sum) and extra (largest single capture: the tail one more capture may need) go into the prewarm file, where
+        # the planner reads its graph reserve from.  Counterpart: rust/crates/cuteafd-loader/src/placement/graph_reserve.rs
+        # (trace-derived base + extra per rank).
+        self.graph_bytes: dict[tuple[int, int, int], int] = {}
+        self.graph_budget_bytes = 0                       # 0 = no byte budget (the count limit still applies)
         inner = getattr(engine, "inner", engine)
         self.has_mtp = bool(getattr(getattr(inner, "W", None), "mtp", None)) and hasattr(engine, "mtp_forward")
 
@@ -363,14 +371,38 @@ class EngineBackend:
         for _ in range(2):
             self.engine.forward(batch)
         torch.cuda.synchronize()
+        if self.graph_budget_bytes:
+            guess = max(self.graph_bytes.values(), default=0)          # what one more capture is likely to take
+            while self.graphs and self.graph_bytes_total() + guess > self.graph_budget_bytes:
+                self._evict_oldest()
+            if self.graph_bytes_total() + guess > self.graph_budget_bytes:
+                self.graph_stats["refused"] += 1
+                return
+        before = torch.cuda.memory_reserved(self.engine.device)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             out = self.engine.forward(batch)
+        torch.cuda.synchronize()
         self.graphs[key] = (g, out)
+        self.graph_bytes[key] = max(0, torch.cuda.memory_reserved(self.engine.device) - before)
         self.graph_stats["captures"] += 1
-        while len(self.graphs) > self.max_graphs:
-            del self.graphs[next(iter(self.graphs))]
-            self.graph_stats["evictions"] += 1
+        while len(self.graphs) > self.max_graphs or (self.graph_budget_bytes and len(self.graphs) > 1
+                                                     and self.graph_bytes_total() > self.graph_budget_bytes):
+            self._evict_oldest()
+
+    def _evict_oldest(self) -> None:
+        old = next(iter(self.graphs))
+        del self.graphs[old]
+        self.graph_bytes.pop(old, None)
+        self.graph_stats["evictions"] += 1
+
+    def graph_bytes_total(self) -> int:
+        return sum(self.graph_bytes.get(k, 0) for k in self.graphs)
+
+    def graph_reserve(self) -> dict:
+        """Measured arena of the graphs held now: base = their sum, extra = the largest single capture."""
+        return {"reserve_base_bytes": self.graph_bytes_total(), "reserve_extra_bytes": max(self.graph_bytes.values(), default=0),
+                "graphs": len(self.graphs), "budget_bytes": self.graph_budget_bytes}
 
     def _run_step(self, key: tuple[int, int, int], batch) -> torch.Tensor:
         seen = self.geometry_seen[key] = self.geometry_seen.get(key, 0) + 1
@@ -421,7 +453,8 @@ class EngineBackend:
         import json
         keys = [list(k) for k, _ in sorted(self.geometry_seen.items(), key=lambda kv: -kv[1])[:top]]
         with open(path, "w") as f:
-            json.dump({"geometries": keys, "seen": {",".join(map(str, k)): v for k, v in self.geometry_seen.items()}}, f)
+            json.dump({"geometries": keys, "seen": {",".join(map(str, k)): v for k, v in self.geometry_seen.items()},
+                       "graph_bytes": {",".join(map(str, k)): v for k, v in self.graph_bytes.items()}, **self.graph_reserve()}, f)
         return keys
 
     def _verify_device(self, handles: list[_Handle], rows: list[list[int]]) -> torch.Tensor:

@@ -209,6 +209,20 @@ def test_decode_graph_bank_and_prewarm(tmp_path):
     warm, be2 = run(True, prewarm=keys)
     assert warm == eager
     assert be2.graph_stats["captures"] >= len(keys) and be2.graph_stats["eager"] < be1.graph_stats["eager"] + 1
+    # byte-measured arena: the file carries what the captures made the allocator reserve, and the planner can read it
+    doc = json.load(open(path))
+    res = be1.graph_reserve()
+    assert doc["reserve_base_bytes"] == res["reserve_base_bytes"] >= 0 and doc["reserve_extra_bytes"] == res["reserve_extra_bytes"]
+    assert set(doc["graph_bytes"]) == {",".join(map(str, k)) for k in be1.graph_bytes}
+    from cuteafd_b200.cli import graph_reserve_of
+    assert graph_reserve_of(path)[0] == doc["reserve_base_bytes"] + doc["reserve_extra_bytes"]
+    # a byte budget smaller than one capture: at most one graph is ever held, nothing breaks, tokens are the same
+    _, eng3, _ = build(small_cfg(), False)
+    from cuteafd_b200.runtime.backends import EngineBackend
+    be3 = EngineBackend(eng3, 64, 8, prefill_chunk=64, max_decode_rows=4, use_graphs=True)
+    be3.graph_budget_bytes = 1
+    be3.graph_bytes[(0, 0, 0)] = 1 << 20                    # pretend an earlier capture took 1 MiB: the next guess is over budget
+    assert be3.prewarm([[1, 1, 1], [2, 2, 1]]) == 2 and len(be3.graphs) == 0 and be3.graph_stats["refused"] == 2
 
 
 def test_prompt_packing_on_the_engine():

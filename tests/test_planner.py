@@ -89,3 +89,32 @@ def test_plan_names_the_engine_that_serves_it():
     frozen = solve_frozen(PlacementRequest(cfg=d, gpus=8), 2, 6)
     assert frozen.engine == "" and any(n.startswith("not served yet:") for n in frozen.notes)
     assert "engine" in best.to_json()
+
+
+def test_graph_reserve_from_a_measured_prewarm_file(tmp_path, capsys):
+    """The decode-graph arena of the layout comes from the bytes a serving run measured (base + extra) when a prewarm
+    file is given, from a plain size as a user override, and from the unmeasured default otherwise."""
+    import json
+    from cuteafd_b200 import cli
+    from cuteafd_b200.planner import plan as P
+    base = P.plan("qwen3-30b-a3b", layout=True, gpus=2, attention_ranks=1, expert_ranks=1)
+    g0 = base.placement.devices[0].by_category()["graphs"]
+    assert g0 == 256 << 20
+    pw = tmp_path / "prewarm.json"
+    pw.write_text(json.dumps({"geometries": [[1, 1, 1]], "reserve_base_bytes": 900 << 20, "reserve_extra_bytes": 100 << 20}))
+    nbytes, source = cli.graph_reserve_of(str(pw))
+    assert nbytes == 1000 << 20 and source == "measured: prewarm.json"
+    rep = P.plan("qwen3-30b-a3b", layout=True, gpus=2, attention_ranks=1, expert_ranks=1, graph_reserve_bytes=nbytes,
+                 graph_reserve_source=source)
+    dev = rep.placement.devices[0]
+    assert dev.by_category()["graphs"] == 1000 << 20
+    assert dev.free == base.placement.devices[0].free - (1000 - 256) * (1 << 20) or rep.placement.kv_pool_tokens <= base.placement.kv_pool_tokens
+    assert cli.main(["plan", "qwen3-30b-a3b", "--layout", "--gpus", "2", "--attention-ranks", "1", "--expert-ranks", "1",
+                     "--graph-reserve", "600MiB", "--json"]) == 0
+    out = json.loads(capsys.readouterr().out)
+    dev0 = out["placement"]["devices"][0]
+    assert any("user override" in str(item) for item in json.dumps(dev0).split(","))
+    (tmp_path / "old.json").write_text(json.dumps({"geometries": []}))
+    import pytest
+    with pytest.raises(SystemExit):
+        cli.graph_reserve_of(str(tmp_path / "old.json"))
