@@ -151,6 +151,39 @@ def attach_stored_experts(W, snap: OpenedSnapshot, device: torch.device) -> str:
     return fmt
 
 
+def random_stored_experts(W, cfg, fmt: str, device: torch.device, seed: int = 0, std: float = 0.02) -> str:
+    """Random routed experts in a stored format ("fp8", "mxfp4", "nvfp4"), generated and encoded on the device one
+    expert at a time, attached to ``W`` the way ``attach_stored_experts`` attaches a checkpoint's (benchmarks of the
+    quantised serving paths without a checkpoint on disk).  MTP layers' experts included."""
+    from ..quant import codecs
+    g = torch.Generator(device=device).manual_seed(seed)
+    E, I, H = cfg.num_experts, cfg.expert_ffn, cfg.hidden
+
+    def stack(rows: int, cols: int):
+        parts = []
+        for _ in range(E):
+            w = torch.empty(rows, cols, dtype=torch.float32, device=device).normal_(0.0, std, generator=g)
+            if fmt == "fp8":
+                parts.append(codecs.fp8_quant_block128(w))
+            elif fmt == "mxfp4":
+                parts.append(codecs.mxfp4_quant(w))
+            else:
+                q, bs, glob = codecs.nvfp4_quant(w)
+                parts.append((q, bs.view(torch.uint8), glob))
+        cols_ = list(zip(*parts))
+        if fmt == "fp8":
+            return torch.stack(cols_[0]).contiguous(), torch.stack(cols_[1]).float().contiguous()
+        if fmt == "mxfp4":
+            return torch.stack(cols_[0]).contiguous(), torch.stack(cols_[1]).contiguous(), None
+        return torch.stack(cols_[0]).contiguous(), torch.stack(cols_[1]).contiguous(), torch.cat(cols_[2]).contiguous()
+    assert fmt in ("fp8", "mxfp4", "nvfp4"), fmt
+    for L in W.layers:
+        if L.router is not None:
+            L.w_gate, L.w_up, L.w_down = stack(I, H), stack(I, H), stack(H, I)
+    W.expert_format = fmt
+    return fmt
+
+
 def load_gqa_engine_weights(path: str, device: torch.device, with_experts: bool = True,
                             expert_range: tuple[int, int] | None = None, reserve_bytes: int = 0):
     """Device weights for ``GqaMoeEngine`` straight from a snapshot (bf16 compute form), in one weight arena.
