@@ -193,7 +193,9 @@ def cmd_bench(a: argparse.Namespace) -> int:
         return 0
     if a.url:                                  # panels against a live server, over its HTTP API
         from .bench import panels
-        names = list(panels.QUICK) if a.panels == "quick" else [p for p in a.panels.split(",") if p]
+        names = []
+        for p in a.panels.split(","):                # "quick" stands for the first five, alone or inside a list
+            names += list(panels.QUICK) if p == "quick" else ([p] if p else [])
         opts = {"max_tokens": a.max_tokens, "levels": [int(v) for v in a.levels.split(",") if v], "seconds": a.seconds,
                 "concurrency": a.concurrency}
         out = panels.run(a.url, names, a.bench_api_key, opts)

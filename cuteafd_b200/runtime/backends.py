@@ -209,6 +209,8 @@ class EngineBackend:
             if slots >= 8:
                 self.tier = HostTier(self.prefix, self.pool, self.table, HostCache(CudaCopyEngine(pools, slots), slots))
         self.max_pages = max_pages_per_seq
+        # longest sequence one page-table row can describe (speculative rows of the last step included)
+        self.max_context_tokens = max(PAGE, (max_pages_per_seq - 1) * PAGE)
         self.bufs = StepBuffers(max_decode_rows * 8, max_decode_rows, max_pages_per_seq, engine.device)
         self.quarantined: list[_Handle] = []
         self._sel = None

@@ -168,6 +168,13 @@ class Scheduler:
             req.events.put(("error", FAIL_BAD_REQUEST, "empty prompt, token out of range or max_tokens < 1"))
             self.stats.rejected += 1
             return req
+        limit = getattr(self.be, "max_context_tokens", None)
+        if limit is not None and len(req.prompt) + req.max_tokens > limit:
+            # refused at the door, as a client error: a longer sequence does not fit the per-sequence page table
+            req.events.put(("error", FAIL_BAD_REQUEST, f"prompt ({len(req.prompt)} tokens) + max_tokens ({req.max_tokens}) exceeds the "
+                                                       f"deployment's context of {limit} tokens"))
+            self.stats.rejected += 1
+            return req
         if self.waiting.qsize() + len(self.pending) >= self.queue_depth:
             req.events.put(("error", FAIL_RETRY, "admission queue full"))
             self.stats.rejected += 1

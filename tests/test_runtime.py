@@ -531,3 +531,22 @@ def test_usage_counts_the_round_that_ends_the_reply(oracle):
     cfg, params = oracle
     out = _run(Scheduler(OracleBackend(cfg, params)), [Request(list(range(1, 30)), max_tokens=5, speculation=False)])[0]
     assert len(out["tokens"]) == 5 and out["usage"]["speculation"]["cycles"] == 4      # one token from prefill, four decode rounds
+
+
+def test_request_longer_than_the_context_is_refused_at_the_door():
+    """A prompt + max_tokens beyond what one page-table row can describe is a client error at submit, not a failed step."""
+    from cuteafd_b200 import tiny_moe
+    from cuteafd_b200.ref.model import init_weights
+    from cuteafd_b200.runtime.backends import OracleBackend
+    from cuteafd_b200.runtime.scheduler import FAIL_BAD_REQUEST, Request, Scheduler, collect
+    cfg = tiny_moe()
+    be = OracleBackend(cfg, init_weights(cfg, seed=0), total_pages=32)
+    be.max_context_tokens = 256
+    sched = Scheduler(be, max_active=2)
+    r = sched.submit(Request(prompt=[1] * 250, max_tokens=16))
+    out = collect(r, timeout=1)
+    assert out["error"] and out["error"][0] == FAIL_BAD_REQUEST and "context" in out["error"][1]
+    ok = sched.submit(Request(prompt=[1] * 200, max_tokens=16))
+    for _ in range(200):
+        sched.step()
+    assert collect(ok, timeout=5)["error"] is None and sched.stats.rejected == 1
