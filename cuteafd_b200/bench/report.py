@@ -95,9 +95,10 @@ def from_panels(out: dict, *, family: str, checkpoint: str, hardware: str, profi
     for p in out.get("panels", []):
         checks.append(asdict(Check(p["panel"], bool(p.get("ok")), p.get("error", ""), p["panel"] in GATING)))
         if p["panel"] == "speed" and p.get("ok"):
-            card.update({k: p[k] for k in ("prefill_tok_s", "ttft_s", "decode_tok_s") if k in p})
+            card["prefill_tok_s"], card["ttft_s"] = p.get("prefill_tok_s"), p.get("prefill_ttft_s")
+            card.setdefault("decode_tok_s", {}).setdefault("1", p.get("c1_decode_tok_s"))
         if p["panel"] == "sweep" and p.get("ok") and "levels" in p:
-            card["decode_tok_s"] = {str(k): v for k, v in p["levels"].items()}
+            card["decode_tok_s"] = {str(k): (v.get("tok_s") if isinstance(v, dict) else v) for k, v in p["levels"].items()}
     th = [p.get("thermal") for p in out.get("panels", []) if p.get("thermal")]
     clocks = {"per_panel": th} if th else {}
     return Report(family, checkpoint, hardware, profile, now(), build, config or {}, card, clocks, checks, out.get("panels", []))

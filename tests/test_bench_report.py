@@ -45,11 +45,13 @@ def test_report_from_bench_line_and_card(tmp_path):
 def test_report_from_panels():
     out = {"url": "u", "ok": False, "panels": [
         {"panel": "smoke", "ok": True, "seconds": 1.0}, {"panel": "lossless", "ok": False, "error": "ids differ", "seconds": 2.0},
-        {"panel": "speed", "ok": True, "prefill_tok_s": 1000.0, "ttft_s": 0.5, "decode_tok_s": {"1": 50.0}, "seconds": 3.0},
+        {"panel": "speed", "ok": True, "prefill_tok_s": 1000.0, "prefill_ttft_s": 0.5, "c1_decode_tok_s": 50.0, "seconds": 3.0},
+        {"panel": "sweep", "ok": True, "levels": {"1": {"tok_s": 55.0, "failed": 0}, "4": {"tok_s": 150.0, "failed": 0}}, "seconds": 3.0},
         {"panel": "tools", "ok": False, "seconds": 0.1}]}
     rep = R.from_panels(out, family="f", checkpoint="c", hardware="1gpu")
-    assert not rep.accepted and rep.card["prefill_tok_s"] == 1000.0
-    assert [c["gating"] for c in rep.checks] == [True, True, False, False]
+    assert not rep.accepted and rep.card["prefill_tok_s"] == 1000.0 and rep.card["ttft_s"] == 0.5
+    assert rep.card["decode_tok_s"] == {"1": 55.0, "4": 150.0}
+    assert [c["gating"] for c in rep.checks] == [True, True, False, False, False]
     out["panels"][1]["ok"] = True
     assert R.from_panels(out, family="f", checkpoint="c", hardware="1gpu").accepted      # tools is informational
 
