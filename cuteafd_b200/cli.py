@@ -49,7 +49,7 @@ def load_config_file(path: str, overrides: list[str], known: set[str]) -> dict[s
     return out
 
 
-CONFIG_KEYS = {"MODEL", "GPUS", "ATTENTION_RANKS", "EXPERT_RANKS", "POOL_TOKENS", "GPU_MEMORY_CAP", "MAX_CONTEXT_TOKENS",
+CONFIG_KEYS = {"MODEL", "EMBEDDING_PLACEMENT", "GPUS", "ATTENTION_RANKS", "EXPERT_RANKS", "POOL_TOKENS", "GPU_MEMORY_CAP", "MAX_CONTEXT_TOKENS",
                "CONCURRENCY", "SPECULATOR", "DECODE_LANES", "PORT", "HOST", "API_KEY", "DECODE_SHARE", "PREFILL_ROWS",
                "HTTP_QUEUE_DEPTH", "HTTP_QUEUE_WAIT", "PROFILE", "SPECULATION_TRACE", "KV_FORMAT", "EXPERT_FORMAT"}
 
@@ -411,6 +411,8 @@ def _build_parser() -> argparse.ArgumentParser:
     s.add_argument("--queue-depth", type=int, default=64); s.add_argument("--queue-wait", type=float, default=30.0)
     s.add_argument("--fake-engine", action="store_true", help="serve with the CPU oracle engine (no GPU)")
     s.add_argument("--usage-db", default=""); s.add_argument("--memory-spool", default="", help="file opened at start-up that receives the ledger's state when an allocation fails"); s.add_argument("--kv-format", default="auto", choices=["auto", "bf16", "fp8_ds_mla"])
+    s.add_argument("--embedding-placement", default="gpu", choices=["gpu", "host"],
+                   help="host: the token embedding table stays memory-mapped in host RAM and each step's rows are gathered and uploaded")
     s.add_argument("--host-cache-gib", type=float, default=float(os.environ.get("CUTEAFD_HOST_CACHE_GIB", "4")),
                    help="pinned host memory behind the device prefix cache: evicted snapshots are kept there and restored on a later hit (0 = off)")
     s.add_argument("--loop-abort-run", type=int, default=int(os.environ.get("CUTEAFD_LOOP_ABORT_RUN", 512)),

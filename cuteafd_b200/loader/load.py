@@ -268,6 +268,20 @@ def load_gqa_engine_weights(path: str, device: torch.device, with_experts: bool 
     return cfg, W
 
 
+def host_embedding_table(path: str, **kw):
+    """The snapshot's token embedding as a memory-mapped host table (``--embedding-placement host``): rows are gathered
+    per step instead of the table living in GPU memory.  bf16 / f16 / f32 tables only (a quantised embedding is
+    refused by the family's format rules anyway)."""
+    from .mapped_table import MappedTable
+    snap = open_snapshot(path)
+    name = "model.embed_tokens.weight"
+    if name not in snap.catalog.entries:
+        raise ValueError(f"{path}: no {name} to map")
+    if snap.catalog.entries[name].dtype != "BF16":
+        raise ValueError("a host-resident embedding table is read as stored: it must be bf16 in the checkpoint")
+    return MappedTable.from_safetensors(snap.catalog, name, **kw)
+
+
 def load_engine(path: str, device: torch.device, num_pages: int, max_tokens: int, max_seqs: int, kv_format: str = "auto"):
     """(cfg, engine) for a snapshot: the GQA engine streams its weights tensor by tensor; MLA checkpoints (and any
     checkpoint with MTP depths) go through the dense parameter dictionary, decoded to bf16.  ``kv_format`` "auto"

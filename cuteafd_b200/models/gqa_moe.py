@@ -201,6 +201,7 @@ class GqaMoeEngine:
     fused = None                 # class defaults: subclasses with their own constructor never take the fused step
     _fused_rows = 0
     _fused_checked = False
+    embed_rows = None            # [max_tokens, hidden] staging of a host-resident embedding table's rows (None = table on the GPU)
 
     def __init__(self, cfg: ModelConfig, weights: GqaMoeWeights, kv: KvCache, max_tokens: int, max_seqs: int = 64,
                  build_moe: bool = True):
@@ -351,7 +352,12 @@ class GqaMoeEngine:
             self.launches += 1
             self._fused_rows = T             # ``greedy`` on these logits returns the tokens the step already selected
             return logits
-        K.embed(b.tokens, self.W.embed, out=ws.h[:T])
+        if self.embed_rows is not None:
+            # host-resident embedding table: the backend gathered this step's rows from the memory-mapped table and
+            # staged them in ``embed_rows`` (a fixed buffer, so captured graphs read it too)
+            ws.h[:T].copy_(self.embed_rows[:T])
+        else:
+            K.embed(b.tokens, self.W.embed, out=ws.h[:T])
         self.launches += 1
         if b.embeds is not None:
             ws.h[:T].index_copy_(0, b.embeds[0], b.embeds[1])

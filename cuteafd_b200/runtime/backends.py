@@ -186,7 +186,7 @@ class EngineBackend:
     """The CUDA engine (single GPU or the attention rank of an AFD group)."""
 
     def __init__(self, engine, num_pages: int, max_pages_per_seq: int, prefill_chunk: int = 2048, max_decode_rows: int = 64,
-                 use_graphs: bool = True, host_cache_bytes: int = 0):
+                 use_graphs: bool = True, host_cache_bytes: int = 0, host_embedding=None):
         from .generate import Generator, StepBuffers
         self.engine = engine
         self.cfg = engine.cfg
@@ -208,6 +208,16 @@ class EngineBackend:
             slots = int(host_cache_bytes // max(1, kv.bytes_per_page()))
             if slots >= 8:
                 self.tier = HostTier(self.prefix, self.pool, self.table, HostCache(CudaCopyEngine(pools, slots), slots))
+        # Host-resident embedding table (``loader/mapped_table.py``): every step's rows are gathered from the memory-mapped
+        # checkpoint file by the table's thread pool into pinned memory and copied into the engine's fixed staging buffer
+        # before the step is launched; the next prompt chunk's rows are prefetched while the current one computes.  The
+        # reference keeps token embeddings (and DeepSeek's per-layer tables) on the host the same way
+        # (run.sh --embedding-placement host; rust/crates/cuteafd-loader/src/formats/mapped_table.rs).
+        self.host_embed = host_embedding
+        if host_embedding is not None:
+            rows = max(self.gen.prefill_buf.tokens[0].numel(), max_decode_rows * 8)
+            engine.embed_rows = torch.zeros(rows, self.cfg.hidden, dtype=torch.bfloat16, device=engine.device)
+            self._embed_stage = torch.zeros(rows, self.cfg.hidden, dtype=torch.bfloat16).pin_memory()
         self.max_pages = max_pages_per_seq
         # longest sequence one page-table row can describe (speculative rows of the last step included)
         self.max_context_tokens = max(PAGE, (max_pages_per_seq - 1) * PAGE)
@@ -234,7 +244,19 @@ class EngineBackend:
         self.graph_bytes: dict[tuple[int, int, int], int] = {}
         self.graph_budget_bytes = 0                       # 0 = no byte budget (the count limit still applies)
         inner = getattr(engine, "inner", engine)
-        self.has_mtp = bool(getattr(getattr(inner, "W", None), "mtp", None)) and hasattr(engine, "mtp_forward")
+        self.has_mtp = (bool(getattr(getattr(inner, "W", None), "mtp", None)) and hasattr(engine, "mtp_forward")
+                        and host_embedding is None)      # the MTP depth embeds the selected tokens on the device
+
+    def _stage_embeddings(self, host_tokens: torch.Tensor, lookahead=None) -> None:
+        """Rows of the host embedding table for the step whose token ids were just staged (no-op with the table on the
+        GPU); ``lookahead``: ids a later step will need (the next chunk of the prompt)."""
+        if self.host_embed is None:
+            return
+        n = host_tokens.numel()
+        self.host_embed.gather(host_tokens.numpy(), out=self._embed_stage[:n])
+        self.engine.embed_rows[:n].copy_(self._embed_stage[:n], non_blocking=True)
+        if lookahead:
+            self.host_embed.prefetch(lookahead)
 
     def _copy_page(self, src: int, dst: int) -> None:
         kv = self.engine.kv if hasattr(self.engine, "kv") else self.engine.inner.kv
@@ -292,6 +314,7 @@ class EngineBackend:
         b.q_start[0][0], b.q_start[0][1] = 0, n
         b.last_rows[0][0] = n - 1
         b.upload()
+        self._stage_embeddings(b.tokens[0][:n])
         batch = Batch(b.tokens[1][:n], b.positions[1][:n], b.slots[1][:n], b.page_table[1].view(1, self.max_pages),
                       b.seq_lens[1][:1], b.q_start[1][:2], n, True, b.last_rows[1][:1], fresh=start == 0)
         if ov is not None:
@@ -343,6 +366,7 @@ class EngineBackend:
             o += n
         b.q_start[0][S] = T
         b.upload()
+        self._stage_embeddings(b.tokens[0][:T])
         batch = Batch(b.tokens[1][:T], b.positions[1][:T], b.slots[1][:T], pt_dev(b, self.max_pages)[:S], b.seq_lens[1][:S],
                       b.q_start[1][:S + 1], max(len(t) for _, t, _ in items), True, b.last_rows[1][:S], fresh=False)
         if rows:
@@ -446,6 +470,7 @@ class EngineBackend:
                 starts.append(starts[-1] + per + (1 if i < extra else 0))
             b.q_start[0][:S + 1] = torch.tensor(starts, dtype=torch.int32)
             b.upload()
+            self._stage_embeddings(b.tokens[0][:T])
             self._capture((S, T, mq), self._step_batch((S, T, mq)))
             n += 1
         return n
@@ -480,6 +505,7 @@ class EngineBackend:
             o += n
         b.q_start[0][S] = T
         b.upload()
+        self._stage_embeddings(b.tokens[0][:T])
         key = (S, T, max(len(r) for r in rows))
         batch = self._step_batch(key)
         logits = self._run_step(key, batch)

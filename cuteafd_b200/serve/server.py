@@ -510,8 +510,17 @@ def build_state(args) -> ServerState:
             else:
                 from ..models.gqa_moe import GqaMoeEngine as Engine, GqaMoeWeights as Weights, KvCache as Cache
             eng = Engine(cfg, Weights.random_init(cfg, dev), Cache(cfg, num_pages, dev), max_tokens=max(2048, rows), max_seqs=rows)
+        table = None
+        if getattr(args, "embedding_placement", "gpu") == "host":
+            if not snapshot:
+                raise SystemExit("--embedding-placement host maps the table of a snapshot: give --snapshot")
+            from ..loader.load import host_embedding_table
+            table = host_embedding_table(snapshot)
+            if not cfg.tie_embeddings:
+                getattr(eng, "inner", eng).W.embed = None          # the device copy is not needed: free it
+                torch.cuda.empty_cache()
         be = EngineBackend(eng, num_pages, pages_per_seq, prefill_chunk=2048, max_decode_rows=args.concurrency,
-                           host_cache_bytes=int(float(getattr(args, "host_cache_gib", 0.0)) * (1 << 30)))
+                           host_cache_bytes=int(float(getattr(args, "host_cache_gib", 0.0)) * (1 << 30)), host_embedding=table)
         if getattr(args, "prewarm", "") == "auto":              # no trace of an earlier run: the derived default list
             from ..planner.capacity import default_prewarm
             block = 0 if args.speculator == "off" else 4

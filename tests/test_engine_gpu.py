@@ -388,3 +388,39 @@ def test_snapshot_served_in_its_stored_format(fmt, tmp_path):
     torch.cuda.synchronize()
     assert K.read_status() == 0
     assert max(errs) < 0.06, errs
+
+
+def test_host_resident_embedding_table(tmp_path):
+    """``--embedding-placement host``: the embedding table stays memory-mapped in the snapshot, every step's rows are
+    gathered and staged; replies equal the ones with the table on the GPU, eagerly and through captured decode graphs."""
+    from cuteafd_b200.loader.load import host_embedding_table, load_engine
+    from cuteafd_b200.loader.snapshot import write_random_snapshot
+    from cuteafd_b200.ops import kernels as K
+    from cuteafd_b200.runtime.backends import EngineBackend
+    from cuteafd_b200.runtime.scheduler import Request, Scheduler, collect
+    snap = write_random_snapshot(small_cfg(), str(tmp_path / "snap"), fmt="bf16", seed=5)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, small_cfg().vocab_size, (n,), generator=g).tolist() for n in (150, 40, 9)]
+
+    def serve(host: bool, graphs: bool):
+        cfg, eng = load_engine(snap, torch.device("cuda:0"), 64, 256, 8)
+        table = host_embedding_table(snap) if host else None
+        if host:
+            eng.W.embed = None
+        be = EngineBackend(eng, 64, 8, prefill_chunk=64, max_decode_rows=4, use_graphs=graphs, host_embedding=table)
+        sched = Scheduler(be, max_active=4)
+        reqs = [sched.submit(Request(prompt=list(p), max_tokens=8, speculation=False)) for p in prompts]
+        for _ in range(400):
+            sched.step()
+            if sched.stats.finished == len(reqs):
+                break
+        outs = [collect(r, timeout=5) for r in reqs]
+        assert all(o["error"] is None for o in outs), outs
+        torch.cuda.synchronize()
+        assert K.read_status() == 0
+        return [o["tokens"] for o in outs], table
+    want, _ = serve(False, False)
+    got, table = serve(True, False)
+    assert got == want and table.stats.rows >= sum(len(p) for p in prompts) and table.stats.prefetch_hits >= 0
+    got_g, _ = serve(True, True)
+    assert got_g == want
