@@ -327,7 +327,7 @@ _HELP = {
     ("plan", "concurrency"): "requests decoded together (sizes graphs and workspaces)",
     ("serve", "concurrency"): "requests decoded together; more wait in the admission queue",
     ("plan", "speculator"): "speculative decoding to plan memory for",
-    ("serve", "speculator"): "auto (MTP depth of the checkpoint, else history n-gram), history, ngram, mtp, draft-model, off",
+    ("serve", "speculator"): "auto (MTP depth of the checkpoint, else history n-gram), history, ngram, mtp, draft-model (a small checkpoint drafts token by token), block-draft (it drafts the block in one pass), off",
     "decode_lanes": "independent decode batches served alternately",
     "format": "override the detected storage format of dense weights",
     "expert_format": "override the detected storage format of routed experts",
@@ -424,7 +424,7 @@ def _build_parser() -> argparse.ArgumentParser:
                    help="short-cycle rule: tokens the copies after the first must span; 0 = off")
     s.add_argument("--loop-fast-copies", type=int, default=int(os.environ.get("CUTEAFD_LOOP_FAST_COPIES", 8)),
                    help="identical copies of a short unit (1..256 tokens) that count as a loop")
-    s.add_argument("--draft-snapshot", default="", help="with --speculator draft-model: the small checkpoint (same vocabulary) that drafts")
+    s.add_argument("--draft-snapshot", default="", help="with --speculator draft-model / block-draft: the small checkpoint (same vocabulary) that drafts")
     s.add_argument("--profile", default="", help="comma-separated host-side profile modes (also $PROFILE): draft-timing, expert-routes, census, step-timing")
     s.add_argument("--profile-dir", default="", help="directory for the files the profile modes append to (default: the working directory)")
     s.add_argument("--speculation-trace", default="", help="JSONL file, one record per decode round (also $SPECULATION_TRACE); "

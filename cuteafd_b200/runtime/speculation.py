@@ -325,16 +325,26 @@ class ModelDrafter:
         self.drafted = 0
 
     @staticmethod
-    def from_oracle(cfg, params, block: int = 4) -> "ModelDrafter":
+    def from_oracle(cfg, params, block: int = 4, parallel: bool = False) -> "ModelDrafter":
         import torch
 
         from ..ref.model import KvState, RefDecoder
         dec = RefDecoder(cfg, params)
 
-        def step(tokens, kv):
+        def step(tokens, kv, all_rows: bool = False):
             with torch.no_grad():
                 return dec.forward(torch.tensor(tokens, dtype=torch.long), kv)
-        return ModelDrafter(step, lambda: KvState(cfg), block, cfg.vocab_size)
+        return (BlockModelDrafter if parallel else ModelDrafter)(step, lambda: KvState(cfg), block, cfg.vocab_size)
+
+    @staticmethod
+    def from_engine(engine, num_pages: int, max_pages_per_seq: int, block: int = 4, parallel: bool = False) -> "ModelDrafter":
+        """The draft model is a CUDA engine (a small checkpoint of the same vocabulary on the same GPU) with its own
+        paged KV.  ``parallel``: the block drafter (one pass per block, see ``BlockModelDrafter``)."""
+        m = EngineDraftModel(engine, num_pages, max_pages_per_seq)
+        cls = BlockModelDrafter if parallel else ModelDrafter
+        d = cls(m.step, m.new_kv, block, engine.cfg.vocab_size)
+        d.model = m
+        return d
 
     def begin(self, rid, prompt, first_token):
         kv = self.new_kv()
@@ -377,6 +387,99 @@ class ModelDrafter:
 
     def forget(self, rid):
         self.state.pop(rid, None)
+
+
+class BlockModelDrafter(ModelDrafter):
+    """Block drafter: the whole block comes out of ONE pass of the draft model.  The pass runs over the request's last
+    token followed by mask tokens; row j's argmax is the draft of position j + 1, so positions past the first are
+    predicted from mask inputs and whatever the draft model's attention makes of the context (the way the reference's
+    dSpark / DFlash2 block drafters denoise a masked block in a single forward,
+    rust/crates/cuteafd-daemon/src/shared/speculation/block_dspark.rs:1-60, dflash.rs:1-27).  The mask rows' K/V is
+    dropped after the pass; only the real token's stays.  One draft-model launch chain per round instead of ``block``."""
+
+    def __init__(self, step, new_kv, block: int = 4, vocab_size: int | None = None, mask_token: int | None = None):
+        super().__init__(step, new_kv, block, vocab_size)
+        self.mask_token = mask_token if mask_token is not None else (vocab_size - 1 if vocab_size else 0)
+        self.passes = 0
+
+    def draft(self, rid, last_hidden, last_token, n):
+        st = self.state.get(rid)
+        if st is None or n <= 0:
+            return [], None
+        import torch
+        if st["fed"]:
+            st["kv"].truncate(st["base"])
+            st["fed"] = []
+        rows = [st["pending"]] + [self.mask_token] * (n - 1)
+        lp = torch.log_softmax(self.step(rows, st["kv"], all_rows=True).float(), dim=-1)
+        self.passes += 1
+        st["kv"].truncate(st["base"] + 1)               # the mask rows' K/V means nothing: keep the real token's
+        st["fed"] = [st["pending"]]
+        toks = lp.argmax(dim=-1).tolist()
+        self.drafted += len(toks)
+        return toks, [float(lp[j, t].exp()) for j, t in enumerate(toks)]
+
+
+class EngineDraftModel:
+    """``step`` / ``new_kv`` of ``ModelDrafter`` on a CUDA engine: one sequence of the engine's paged cache per request,
+    tokens appended as prompt-style chunks (causal inside the chunk, the cache before it), logits of the last row or
+    of every row back on the host."""
+
+    def __init__(self, engine, num_pages: int, max_pages_per_seq: int, chunk: int = 256):
+        from .generate import StepBuffers
+        from .native import make_pool
+        from .paged import SequenceTable
+        self.eng, self.max_pages = engine, max_pages_per_seq
+        self.pool = make_pool(num_pages)
+        self.table = SequenceTable(self.pool)
+        self.chunk = min(chunk, engine.max_tokens)
+        self.buf = StepBuffers(self.chunk, 1, max_pages_per_seq, engine.device)
+        self.steps = 0
+
+    class _Seq:
+        def __init__(self, owner):
+            self.owner, self.seq = owner, owner.table.new()
+
+        def truncate(self, length: int) -> None:
+            self.owner.table.truncate(self.seq, length)
+
+        def __del__(self):
+            try:
+                self.owner.table.free(self.seq)
+            except Exception:                            # noqa: BLE001 - interpreter shutdown
+                pass
+
+    def new_kv(self):
+        return EngineDraftModel._Seq(self)
+
+    def step(self, tokens, kv, all_rows: bool = False):
+        import torch
+
+        from ..models.gqa_moe import Batch
+        seq, b, out = kv.seq, self.buf, None
+        rows_cap = self.eng.logits.shape[0]
+        for c0 in range(0, len(tokens), self.chunk):
+            part = tokens[c0:c0 + self.chunk]
+            start, n = seq.kv_len, len(part)
+            self.table.reserve(seq, start + n, copy_page=lambda s, d: self.eng.kv.copy_page(s, d))
+            b.tokens[0][:n] = torch.tensor(part, dtype=torch.int32)
+            b.positions[0][:n] = torch.arange(start, start + n, dtype=torch.int32)
+            b.slots[0][:n] = torch.tensor(self.table.slots(seq, start, n), dtype=torch.int32)
+            pt = b.page_table[0].view(1, self.max_pages)
+            pt.zero_()
+            pt[0, :len(seq.pages)] = torch.tensor(seq.pages, dtype=torch.int32)
+            b.seq_lens[0][0] = start + n
+            b.q_start[0][0], b.q_start[0][1] = 0, n
+            b.last_rows[0][0] = n - 1
+            b.upload()
+            every = all_rows and n <= rows_cap
+            batch = Batch(b.tokens[1][:n], b.positions[1][:n], b.slots[1][:n], b.page_table[1].view(1, self.max_pages),
+                          b.seq_lens[1][:1], b.q_start[1][:2], n, True, None if every else b.last_rows[1][:1], fresh=start == 0)
+            out = self.eng.forward(batch)
+            seq.tokens.extend(part)
+            seq.kv_len = start + n
+            self.steps += 1
+        return out.float().cpu()
 
 
 class MtpDrafter:

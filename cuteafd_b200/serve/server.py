@@ -546,17 +546,26 @@ def build_state(args) -> ServerState:
                 print(f"prewarmed {n} decode graphs from {pw}", flush=True)
     tok = load_tokenizer(snapshot, cfg.vocab_size)
     drafter = NgramDrafter(block=4) if args.speculator in ("auto", "history", "ngram") else None
-    if args.speculator == "draft-model":
-        # a small checkpoint of the same vocabulary drafts the block; it runs on the oracle decoder (host), which suits
-        # the oracle engine and small draft models; verification by the target keeps the reply exact either way
-        from ..loader.load import load_params
+    if args.speculator in ("draft-model", "block-draft"):
+        # a small checkpoint of the same vocabulary drafts the block: on the GPU next to the target when there is one
+        # (its own engine and paged KV), else on the oracle decoder; "block-draft" produces the whole block in one pass
+        # of the draft model (mask tokens after the last real one).  Verification by the target keeps the reply exact.
         from ..runtime.speculation import ModelDrafter
         if not getattr(args, "draft_snapshot", ""):
-            raise SystemExit("--speculator draft-model needs --draft-snapshot")
-        dcfg, dparams = load_params(args.draft_snapshot)
+            raise SystemExit(f"--speculator {args.speculator} needs --draft-snapshot")
+        block_mode = args.speculator == "block-draft"
+        if args.fake_engine or not torch.cuda.is_available():
+            from ..loader.load import load_params
+            dcfg, dparams = load_params(args.draft_snapshot)
+            make = lambda: ModelDrafter.from_oracle(dcfg, dparams, block=4, parallel=block_mode)      # noqa: E731
+        else:
+            from ..loader.load import load_engine
+            pages = (args.max_context_tokens // 64 + 2) * args.concurrency + 64
+            dcfg, deng = load_engine(args.draft_snapshot, torch.device("cuda:0"), pages, 2048, 8)
+            make = lambda: ModelDrafter.from_engine(deng, pages, args.max_context_tokens // 64 + 2, block=4, parallel=block_mode)   # noqa: E731
         if dcfg.vocab_size != cfg.vocab_size:
             raise SystemExit(f"draft model vocabulary {dcfg.vocab_size} differs from the target's {cfg.vocab_size}")
-        drafter = ModelDrafter.from_oracle(dcfg, dparams, block=4)
+        drafter = make()
     if args.speculator in ("auto", "mtp") and getattr(be, "has_mtp", False):
         from ..runtime.speculation import MtpDrafter
         drafter = MtpDrafter()              # native MTP depth of the checkpoint

@@ -424,3 +424,47 @@ def test_host_resident_embedding_table(tmp_path):
     assert got == want and table.stats.rows >= sum(len(p) for p in prompts) and table.stats.prefetch_hits >= 0
     got_g, _ = serve(True, True)
     assert got_g == want
+
+
+@pytest.mark.parametrize("parallel", [False, True])
+def test_draft_model_on_the_gpu(parallel):
+    """A draft model that is a CUDA engine (here: a second instance of the target's own weights): replies equal the
+    non-speculative ones; the sequential drafter's proposals are what the target picks (nearly all accepted), the block
+    drafter produces its block in one pass per round."""
+    from cuteafd_b200.ops import kernels as K
+    from cuteafd_b200.runtime.backends import EngineBackend
+    from cuteafd_b200.runtime.scheduler import Request, Scheduler, collect
+    from cuteafd_b200.runtime.speculation import ModelDrafter
+    cfg = small_cfg()
+    g = torch.Generator().manual_seed(21)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (90, 33)]
+
+    def serve(drafter):
+        _, eng, _ = build(cfg, False)
+        be = EngineBackend(eng, 64, 8, prefill_chunk=64, max_decode_rows=4, use_graphs=False)
+        kw = dict(drafter=drafter, draft_control="always") if drafter is not None else {}
+        sched = Scheduler(be, max_active=2, **kw)
+        reqs = [sched.submit(Request(prompt=list(p), max_tokens=16, speculation=drafter is not None)) for p in prompts]
+        for _ in range(600):
+            sched.step()
+            if sched.stats.finished == len(reqs):
+                break
+        outs = [collect(r, timeout=5) for r in reqs]
+        assert all(o["error"] is None for o in outs), outs
+        torch.cuda.synchronize()
+        assert K.read_status() == 0
+        return outs
+    base = serve(None)
+    _, draft_eng, _ = build(cfg, False)                      # same seed: the target's own weights
+    drafter = ModelDrafter.from_engine(draft_eng, 64, 8, block=3, parallel=parallel)
+    outs = serve(drafter)
+    prop = sum(o["usage"]["speculation"]["proposed"] for o in outs)
+    acc = sum(o["usage"]["speculation"]["accepted"] for o in outs)
+    cyc = sum(o["usage"]["speculation"]["cycles"] for o in outs)
+    same = sum(a["tokens"][:6] == b["tokens"][:6] for a, b in zip(outs, base))
+    assert same == len(prompts), ([o["tokens"] for o in outs], [o["tokens"] for o in base])
+    assert prop > 0 and drafter.model.steps > 0 and drafter.state == {}
+    if parallel:
+        assert drafter.passes <= cyc and acc >= cyc // 3           # position 1 of most blocks is the target's own pick
+    else:
+        assert acc >= 0.7 * prop                                   # the same model in another step shape: near-ties aside

@@ -550,3 +550,19 @@ def test_request_longer_than_the_context_is_refused_at_the_door():
     for _ in range(200):
         sched.step()
     assert collect(ok, timeout=5)["error"] is None and sched.stats.rejected == 1
+
+
+def test_block_drafter_drafts_a_block_in_one_pass_and_is_lossless(oracle):
+    """The block drafter runs the draft model once per round over [last token, mask, mask, ...]; with the target itself
+    as draft model its first position is always right (the others come from mask inputs), and whatever it proposes the
+    reply is the target's."""
+    cfg, params = oracle
+    g = torch.Generator().manual_seed(12)
+    prompt = torch.randint(0, cfg.vocab_size, (48,), generator=g).tolist()
+    base = _run(Scheduler(OracleBackend(cfg, params)), [Request(prompt, max_tokens=20, speculation=False)])[0]
+    blk = speculation.ModelDrafter.from_oracle(cfg, params, block=4, parallel=True)
+    assert type(blk).__name__ == "BlockModelDrafter" and blk.mask_token == cfg.vocab_size - 1
+    out = _run(Scheduler(OracleBackend(cfg, params), drafter=blk, draft_control="always"), [Request(prompt, max_tokens=20)])[0]
+    sp = out["usage"]["speculation"]
+    assert out["tokens"] == base["tokens"] and sp["proposed"] > 0 and sp["accepted"] >= sp["cycles"] - 2      # position 1 of every block
+    assert blk.passes <= sp["cycles"] and blk.drafted >= 2 * blk.passes and blk.state == {}                    # one pass per round, several drafts
