@@ -485,16 +485,18 @@ __global__ void __launch_bounds__(kWideWarps * 32) moe_scatter_kernel(const int*
 }
 
 // ---- dispatch -------------------------------------------------------------------------------------
-// One warp per token.  Rows travel as 16-byte stores into the owners' slabs (local or peer).
+// `wpt` warps per token.  Rows travel as 16-byte stores into the owners' slabs (local or peer).
 __global__ void __launch_bounds__(256) moe_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ idx,
                                                            const int* __restrict__ dest_row, int n_entries, int top_k,
                                                            int row_vec, MoeLayoutDev L, const uint32_t* epoch,
-                                                           uint32_t* done_counter) {
+                                                           uint32_t* done_counter, int wpt) {
   pdl_wait();
   pdl_trigger();
-  // One warp per token: the row is read once (eight 16-byte loads in flight per lane) and stored to each of its
-  // top_k destinations.
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  // wpt = 1 (large steps): one warp per token, the row is read once (eight 16-byte loads in flight per lane) and
+  // stored to each of its top_k destinations.  wpt = 8 (decode-sized steps): a block per token whose eight warps
+  // share the row's columns: a handful of tokens then spreads over as many SMs as there are tokens instead of one.
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int t = gw / wpt, sub = gw - t * wpt;
   const int lane = threadIdx.x & 31;
   if (t * top_k < n_entries) {
     int my_row = -1, my_rank = 0;
@@ -505,18 +507,22 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const uint4* __restri
       while (my_rank + 1 < L.n_ranks && e >= L.expert_lo[my_rank + 1]) ++my_rank;
     }
     const uint4* src = x + static_cast<size_t>(t) * row_vec;
-    for (int c0 = 0; c0 < row_vec; c0 += 256) {
+    // Column share of this warp: its k-th vector of a chunk sits at (k * wpt + sub) * 32 + lane, so the wpt warps of
+    // a token interleave by 32-vector groups (a 128-column quantisation block is 16 lanes of one group) and every
+    // warp stores its columns to all of the token's slots.
+    for (int c0 = 0; c0 < row_vec; c0 += 256 * wpt) {
       uint4 v[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const int c = c0 + lane + 32 * k;
+        const int c = c0 + (k * wpt + sub) * 32 + lane;
         v[k] = c < row_vec ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
       }
       uint2 qv[8];
       float qs[8];
       if (L.fp8) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) quant_block_e4m3(v[k], qv[k], qs[k]);      // the row is quantised once, stored top_k times
+        for (int k = 0; k < 8; ++k)
+          if (c0 + (k * wpt + sub) * 32 < row_vec) quant_block_e4m3(v[k], qv[k], qs[k]);   // quantised once, stored top_k times
       }
       for (int sl = 0; sl < top_k; ++sl) {
         const int row = __shfl_sync(0xffffffffu, my_row, sl);
@@ -528,7 +534,7 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const uint4* __restri
           float* ds = L.slab_s[r] + static_cast<size_t>(row) * (row_vec >> 4);
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
-            const int c = c0 + lane + 32 * k;
+            const int c = c0 + (k * wpt + sub) * 32 + lane;
             if (c < row_vec) {
               dq[c] = qv[k];
               if ((lane & 15) == 0) ds[c >> 4] = qs[k];
@@ -539,7 +545,7 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const uint4* __restri
         uint4* dst = reinterpret_cast<uint4*>(L.slab[r]) + static_cast<size_t>(row) * row_vec;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const int c = c0 + lane + 32 * k;
+          const int c = c0 + (k * wpt + sub) * 32 + lane;
           if (c < row_vec) dst[c] = v[k];
         }
       }
@@ -810,10 +816,11 @@ int cafd_moe_dispatch(const void* x, const int* idx, const int* dest_row, int T,
   if (H % 8 || top_k > 32) return -10;
   if (layout->fp8 && !wire_ok(layout, H)) return -11;
   const int n = T * top_k;
-  const int blocks = T > 0 ? (T + 7) / 8 : 1;            // eight warps per block, one token each
+  const int wpt = T <= 64 ? 8 : 1;                       // few tokens: a block per token, its warps share the slots
+  const int blocks = T > 0 ? (T * wpt + 7) / 8 : 1;      // eight warps per block
   launch_pdl(moe_dispatch_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(s), static_cast<const uint4*>(x), idx, dest_row, n,
                                                                        top_k, H / 8, to_dev(layout), epoch,
-                                                                       done_counter);
+                                                                       done_counter, wpt);
   return static_cast<int>(cudaGetLastError());
 }
 

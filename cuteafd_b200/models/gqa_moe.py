@@ -289,6 +289,14 @@ class GqaMoeEngine:
 
     FUSED_ROUTE_TOKENS = 64         # steps up to this many tokens run RMSNorm + router + top-k as one launch
 
+    def _exchange_launches(self, T: int) -> int:
+        """Kernels one bf16 exchange launches for T tokens: plan (with the dispatch folded in for very small steps, three
+        launches wide from 8192 entries on), dispatch, fc1, fc2, combine."""
+        from ..parallel.moe_exchange import AttentionSide as A
+        n = T * self.cfg.top_k
+        fused = n <= A.FUSED_DISPATCH_ROWS and n * self.cfg.hidden * 2 <= A.FUSED_DISPATCH_BYTES
+        return (4 if fused else 5) + (2 if n >= K.WIDE_PLAN_ENTRIES else 0)
+
     def _ffn(self, i: int, T: int, next_norm: torch.Tensor | None) -> bool:
         """Post-attention norm + FFN of layer i.  Returns True when ``ws.x`` already holds the next layer's
         normalised input (the MoE combine fused that norm in)."""
@@ -325,7 +333,7 @@ class GqaMoeEngine:
         if split:
             self.moe.finish(ws.h[:T], shared=shared, residual=ws.h[:T], norm_w=next_norm, eps=cfg.rms_eps,
                             x_out=ws.x[:T] if next_norm is not None else None)
-            self.launches += 4 if T * cfg.top_k <= 512 else 5
+            self.launches += self._exchange_launches(T)
             return next_norm is not None
         fmt = getattr(self.W, "expert_format", "bf16")
         if fmt != "bf16" and hasattr(self.moe, "forward_stored"):
@@ -336,7 +344,7 @@ class GqaMoeEngine:
             return False
         self.moe.forward(ws.x[:T], logits, kw, L.w_gate, L.w_up, L.w_down, ws.h[:T], shared=shared, residual=ws.h[:T],
                          norm_w=next_norm, eps=cfg.rms_eps, x_out=ws.x[:T] if next_norm is not None else None)
-        self.launches += 4 if T * cfg.top_k <= 512 else 5      # plan(+dispatch), fc1, fc2, combine
+        self.launches += self._exchange_launches(T)             # plan(+dispatch), fc1, fc2, combine
         return next_norm is not None
 
     # ---- whole step -------------------------------------------------------------------------------

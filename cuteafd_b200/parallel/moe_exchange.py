@@ -251,7 +251,12 @@ class AttentionSide:
         self.layout.slab_q[r] = slab_ptr
         self.layout.slab_s[r] = slab_ptr + self.geo.max_rows * self.geo.hidden
 
-    FUSED_DISPATCH_ROWS = 512       # (token, slot) rows up to which plan and dispatch share one single-block launch
+    # Plan and dispatch share one single-block launch only while one SM can copy the rows faster than a second launch
+    # costs: measured in a CUDA graph, Qwen3 rows (4 KB) 8.5 vs 13.0 us at 1 token but 28.7 vs 18.3 us at 32; DeepSeek-V3
+    # rows (14 KB) 11.5 vs 13.2 us at 1 token, 25.7 vs 14.9 us at 8, 143 vs 20 us at 64.  Rows quantised on the wire
+    # always take the separate dispatch kernel (the single block would quantise them all: 18.5 vs 14.5 us at 1 token).
+    FUSED_DISPATCH_ROWS = 512
+    FUSED_DISPATCH_BYTES = 128 << 10
 
     def dispatch(self, x: torch.Tensor, logits: torch.Tensor | None, route_kw: dict, tile_rows: int, layer: int,
                  epoch: torch.Tensor, wire_fp8: bool = False) -> None:
@@ -265,7 +270,8 @@ class AttentionSide:
             K.route_topk(logits, g.top_k, out_idx=idx, out_w=w, **route_kw)
         for r in range(g.n_expert_ranks):
             self.layout.flag[r] = self._rank_ptrs[r][2] + 4 * layer
-        if T * g.top_k <= self.FUSED_DISPATCH_ROWS:
+        if (T * g.top_k <= self.FUSED_DISPATCH_ROWS and T * g.top_k * g.hidden * 2 <= self.FUSED_DISPATCH_BYTES
+                and not wire_fp8):
             K.moe_plan(idx, g.num_experts, tile_rows, self.layout, self.dest_row, self.expert_count, x=x, epoch=epoch)
         else:
             K.moe_plan(idx, g.num_experts, tile_rows, self.layout, self.dest_row, self.expert_count)
