@@ -188,7 +188,7 @@ def main() -> None:
             "value": round(r.tok_s, 2), "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": warmup,
             "ms_per_step": round(r.ms_per_step, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": round(r.tok_s / PUBLISHED["c8"], 3) if headline == 8 and args.config == "qwen3" else None,
-            "dtype": "bf16" if args.config == "qwen3" else "fp8 experts (E4M3, 128x128 weight / 1x128 activation scales), bf16 attention", "data": "synthetic (uniform random token ids, N(0,0.02) random-init weights)",
+            "dtype": "bf16" if args.config == "qwen3" else "fp8 experts and, at decode, fp8 q_b / o / shared-expert projections (E4M3, 128x128 weight / 1x128 activation scales); MLA attention math, q_a / kv_a and prompt chunks in bf16", "data": "synthetic (uniform random token ids, N(0,0.02) random-init weights)",
             "config": {"model": cfg.name + ("" if valid else f"-{cfg.num_layers}layers-INVALID"),
                        "global_batch": headline, "seq_len": args.prompt_len, "parallelism": parallelism,
                        "l2": "inputs larger than L2 (each step streams GBs of weights and KV)",
@@ -207,7 +207,7 @@ def main() -> None:
             if rank == 0 and dres is not None and out is not None:
                 out["extra"].update(card_extra(dres, "dsv3_"))
                 out["extra"]["dsv3_config"] = {"model": dcfg.name + ("" if valid else f"-{dcfg.num_layers}layers-INVALID"),
-                                               "parallelism": dpar, "dtype": "fp8 experts (E4M3, 128x128 weight / 1x128 activation scales), bf16 attention",
+                                               "parallelism": dpar, "dtype": "fp8 experts and, at decode, fp8 q_b / o / shared-expert projections (E4M3, 128x128 weight / 1x128 activation scales); MLA attention math, q_a / kv_a and prompt chunks in bf16",
                                                "clocks": dclk,
                                                "vs_published_glm53_2rtx_6spark": {
                                                    "c1": round(dres.decode[1].tok_s / 39.3, 2) if 1 in dres.decode else None,

@@ -219,14 +219,35 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant
       const float* ws1 = kDual ? p.w_scale1 + static_cast<size_t>((w_row0 + p.w1_row_offset) / 128) * nkb : nullptr;
       int my_x_row = x_row0 + fl;
       if (my_x_row >= p.x_rows_total) my_x_row = p.x_rows_total - 1;
+      // Scales of the next K block are fetched while this one is still waited for and folded: the fold itself then has
+      // no global load in its dependent chain.  Weights-on-M: lane j keeps the activation scale of token column j (and
+      // j + 32), handed to the whole warp by shuffles; tokens-on-M: one activation scale per thread (its own row).
+      float nsw0 = 0.f, nsw1 = 0.f, nsx0 = 0.f, nsx1 = 0.f;
+      auto fetch = [&](int kb) {
+        nsw0 = __ldg(ws0 + kb);
+        if (kDual) nsw1 = __ldg(ws1 + kb);
+        if (kSwap) {
+          int xr = x_row0 + lane;
+          if (xr >= p.x_rows_total) xr = p.x_rows_total - 1;
+          nsx0 = (lane < kBX) ? p.x_scale[static_cast<size_t>(xr) * nkb + kb] : 0.f;     // plain load: a peer may have written it
+          if (kBX > 32) {
+            int xr1 = x_row0 + 32 + lane;
+            if (xr1 >= p.x_rows_total) xr1 = p.x_rows_total - 1;
+            nsx1 = p.x_scale[static_cast<size_t>(xr1) * nkb + kb];
+          }
+        } else {
+          nsx0 = p.x_scale[static_cast<size_t>(my_x_row) * nkb + kb];
+        }
+      };
+      if (kb0 < kb1) fetch(kb0);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int pb = it & 1;
+        const float sw0 = nsw0, sw1 = nsw1, sx0 = nsx0, sx1 = nsx1;
+        if (kb + 1 < kb1) fetch(kb + 1);
         if (!mbar_wait(&pfull_bar[pb], (it >> 1) & 1, p.status, kTimeoutTmemFull)) { ok = false; break; }
         tc_fence_after();
         const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + pb * Cfg::kAccCols;
         if (kSwap) {
-          const float sw0 = __ldg(ws0 + kb);
-          const float sw1 = kDual ? __ldg(ws1 + kb) : 0.f;
 #pragma unroll
           for (int c0 = 0; c0 < kBX; c0 += 16) {
             uint32_t r[16], u[16];
@@ -235,18 +256,15 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              int xr = x_row0 + c0 + j;
-              if (xr >= p.x_rows_total) xr = p.x_rows_total - 1;
-              const float sx = p.x_scale[static_cast<size_t>(xr) * nkb + kb];     // plain load: a peer may have written it
+              const float sx = __shfl_sync(0xffffffffu, (c0 + j) < 32 ? sx0 : sx1, (c0 + j) & 31);
               acc[c0 + j] += __uint_as_float(r[j]) * (sw0 * sx);
               if (kDual) acc[kBX + c0 + j] += __uint_as_float(u[j]) * (sw1 * sx);
             }
           }
         } else {
-          const float sx = p.x_scale[static_cast<size_t>(my_x_row) * nkb + kb];
           // weight blocks along N: one per 128 features (kBW = 128) or gate/up halves (dual, 64 + 64)
-          const float s0 = sx * __ldg(ws0 + kb);
-          const float s1 = kDual ? sx * __ldg(ws1 + kb) : s0;
+          const float s0 = sx0 * sw0;
+          const float s1 = kDual ? sx0 * sw1 : s0;
 #pragma unroll
           for (int c0 = 0; c0 < Cfg::kAccCols; c0 += 32) {
             uint32_t r[32];

@@ -151,6 +151,36 @@ def attach_stored_experts(W, snap: OpenedSnapshot, device: torch.device) -> str:
     return fmt
 
 
+FP8_TWIN_PROJECTIONS = {"wq_b": "self_attn.q_b_proj", "wo": "self_attn.o_proj", "s_gate": "mlp.shared_experts.gate_proj",
+                        "s_up": "mlp.shared_experts.up_proj", "s_down": "mlp.shared_experts.down_proj"}
+
+
+def attach_fp8_twins(W, snap: "OpenedSnapshot | None" = None, device: torch.device | None = None) -> int:
+    """E4M3 twins (values + 128x128 block scales) of the large backbone projections for decode-sized steps: q_b, the
+    o projection and the shared expert.  From a snapshot that stores them as E4M3-block128 the twins are the stored
+    bytes, untouched; otherwise (bf16 checkpoint, random init) they are encoded once from the bf16 weights.  Returns the
+    number of projections that got a twin."""
+    from ..quant import codecs
+    n = 0
+    for i, L in enumerate(W.layers):
+        twins = {}
+        for attr, tensor in FP8_TWIN_PROJECTIONS.items():
+            w = getattr(L, attr, None)
+            if w is None or not torch.is_tensor(w) or w.shape[0] % 128 or w.shape[1] % 128:
+                continue
+            op = snap.operands.get(f"model.layers.{i}.{tensor}") if snap is not None else None
+            if op is not None and op.format == "fp8_block128" and op.block_scale is not None and (op.block_scale.rows, op.block_scale.cols) == (128, 128):
+                q = snap.catalog.read(op.weight).to(device or w.device).contiguous()
+                sc = snap.catalog.read(op.scale_tensor).float().to(device or w.device).contiguous()
+            else:
+                q, sc = codecs.fp8_quant_block128(w.float())
+                q, sc = q.contiguous(), sc.float().contiguous()
+            twins[attr] = (q, sc)
+            n += 1
+        L.fp8 = twins or None
+    return n
+
+
 def random_stored_experts(W, cfg, fmt: str, device: torch.device, seed: int = 0, std: float = 0.02) -> str:
     """Random routed experts in a stored format ("fp8", "mxfp4", "nvfp4"), generated and encoded on the device one
     expert at a time, attached to ``W`` the way ``attach_stored_experts`` attaches a checkpoint's (benchmarks of the
@@ -303,6 +333,8 @@ def load_engine(path: str, device: torch.device, num_pages: int, max_tokens: int
         else:
             _, params = load_params(path, dtype=torch.bfloat16)
             W = MlaMoeWeights.from_params(cfg, params, device)
+        if cfg.weight_format == "fp8_block128":
+            attach_fp8_twins(W, snap, device)
         return cfg, MlaMoeEngine(cfg, W, LatentCache(cfg, num_pages, device), max_tokens=max_tokens, max_seqs=max_seqs)
     from ..models.gqa_moe import GqaMoeEngine, GqaMoeWeights, KvCache
     if stored != "bf16":

@@ -233,6 +233,7 @@ class MlaMoeEngine(GqaMoeEngine):
         self._zero1 = torch.zeros(1, dtype=torch.int32, device=dev)
         self._blocks: dict[tuple[int, int, int], tuple[torch.Tensor, torch.Tensor]] = {}
         self.launches = 0
+        self._f8_rows = {}
 
     def _block_table(self, S: int, max_q_len: int, per: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
         """Row blocks of the attention / indexer kernels: every sequence gets ceil(max_q_len / tokens per block)
@@ -266,7 +267,7 @@ class MlaMoeEngine(GqaMoeEngine):
         K.mla_prep_a(ws.a[:T, :ql + REC], ql, L.q_a_norm, L.kv_a_norm, self.inv_freq, b.positions, b.slots,
                      ws.q_a[:T] if ql else None, self.kv.c[i], cfg.rms_eps, cfg.rope_interleaved,
                      lat_out=ws.lat[:T] if expanded else None)
-        K.linear(ws.q_a[:T] if ql else ws.x[:T], L.wq_b, out=ws.q[:T])
+        self._linear(L, "wq_b", ws.q_a[:T] if ql else ws.x[:T], ws.q[:T])
         q_slab = ws.q_slab[:heads * ht.t_pad * 128].view(heads, ht.t_pad, 128)
         o_slab = ws.o_slab[:heads * ht.t_pad * 512].view(heads, ht.t_pad, 512)
         small = T <= K.MLA_SMALL_ROWS and not expanded
@@ -318,7 +319,7 @@ class MlaMoeEngine(GqaMoeEngine):
         else:
             K.grouped_linear(o_slab.view(-1, 512), L.w_uv, ws.attn, ht.tile_expert, ht.tile_row0, ht.num_tiles, ht.max_tiles,
                              ht.tile_rows, row_dst=ht.row_dst, ldo=cfg.v_head_dim, split_k=False)
-        K.linear(ws.attn[:T], L.wo, out=ws.h[:T], residual=ws.h[:T])
+        self._linear(L, "wo", ws.attn[:T], ws.h[:T], residual=ws.h[:T])
         self.launches += (7 if small else 8) + (1 if splits > 1 else 0)
 
     def _select(self, i: int, T: int, b: Batch) -> torch.Tensor:

@@ -543,6 +543,11 @@ def build_afd(cfg: ModelConfig, device: torch.device, rank: int, world: int, *, 
             W = Weights.from_params(cfg, params, device, with_experts=False)
         else:
             W = Weights.random_init(cfg, device, seed=seed, with_experts=False)      # same seed: replicas hold the same model
+        if cfg.weight_format == "fp8_block128" and cfg.is_mla:
+            # an E4M3 checkpoint: decode-sized steps run q_b, the o projection and the shared expert on E4M3 twins (the
+            # stored bytes when the snapshot has them, encoded once otherwise); prompt chunks keep the bf16 weights
+            from ..loader.load import attach_fp8_twins
+            attach_fp8_twins(W, snap, device)
         kv = Cache(cfg, num_pages, device)
         eng = AfdAttentionEngine(cfg, W, kv, max_tokens, max_seqs, heap, lay, geo, source=rank, n_sources=A)
         eng.ex.expert_format = expert_format
