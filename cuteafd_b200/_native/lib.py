@@ -121,7 +121,7 @@ def cuda_lib():
             _sig(lib, n, [C.c_ulonglong])
         _sig(lib, "cafd_embed", [P, P, P, I, I, I, P])
         _sig(lib, "cafd_rmsnorm", [P, P, P, P, I, I, F, P])
-        _sig(lib, "cafd_qk_rope_kv", [P, P, P, P, P, P, P, P, P, I, I, I, I, F, I, P])
+        _sig(lib, "cafd_qk_rope_kv", [P, P, P, P, P, P, P, P, P, I, I, I, I, F, I, P, I, P])
         _sig(lib, "cafd_argmax", [P, P, P, I, I, I, P])
         _sig(lib, "cafd_argmax_slices", [])
         _sig(lib, "cafd_bump_epoch", [P, P])

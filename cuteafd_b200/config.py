@@ -17,7 +17,7 @@ from typing import Any
 @dataclass(frozen=True)
 class ModelConfig:
     name: str = "tiny-moe"
-    family: str = "deepseek_v3"          # deepseek_v3 | deepseek_v32 | qwen3_moe | tiny_moe
+    family: str = "deepseek_v3"          # deepseek_v3 | deepseek_v32 | qwen3_moe | glm4_moe | qwen2 | llama | tiny_moe
     vocab_size: int = 1024
     num_layers: int = 2
     hidden: int = 256
@@ -27,6 +27,8 @@ class ModelConfig:
     num_kv_heads: int = 4                # gqa only
     head_dim: int = 64                   # gqa only
     qk_norm: bool = False                # Qwen3: RMSNorm over head_dim on q and k
+    rotary_dim: int = 0                  # gqa: leading dims of a head that are rotated (0 = all; GLM-4.5: half the head)
+    attention_bias: bool = False         # gqa: q / k / v projections carry a bias (GLM-4.5, Qwen2)
     q_lora_rank: int = 128               # mla (0 = direct q projection)
     kv_lora_rank: int = 64
     qk_nope_dim: int = 32
@@ -83,6 +85,13 @@ class ModelConfig:
         if self.is_mla:
             return self.kv_lora_rank + self.qk_rope_dim
         return 2 * self.num_kv_heads * self.head_dim
+
+    @property
+    def rope_dim(self) -> int:
+        """Dims of a head that RoPE rotates."""
+        if self.is_mla:
+            return self.qk_rope_dim
+        return self.rotary_dim or self.head_dim
 
     def is_moe_layer(self, layer: int) -> bool:
         return self.num_experts > 0 and layer >= self.first_dense_layers
@@ -172,6 +181,17 @@ def mixtral_8x7b() -> ModelConfig:
         scoring="softmax", num_shared_experts=0, norm_topk_prob=True, weight_format="bf16")
 
 
+def glm45_air() -> ModelConfig:
+    """GLM-4.5-Air geometry (glm4_moe): 46 layers with one dense layer first, GQA 96 / 8 heads of 128 with biased q / k / v
+    projections and RoPE on the first half of every head, 128 routed experts (FFN 1408) with sigmoid top-8 selection under a
+    correction bias, one shared expert, one MTP depth."""
+    return ModelConfig(name="glm-4.5-air", family="glm4_moe", vocab_size=151552, num_layers=46, hidden=4096, attention="gqa",
+                       num_heads=96, num_kv_heads=8, head_dim=128, qk_norm=False, rotary_dim=64, attention_bias=True,
+                       rope_theta=1.0e6, rope_interleaved=False, dense_ffn=10944, first_dense_layers=1, num_experts=128,
+                       expert_ffn=1408, top_k=8, scoring="sigmoid", num_groups=1, topk_groups=1, num_shared_experts=1,
+                       routed_scale=1.0, norm_topk_prob=True, router_bias=True, mtp_layers=1, rms_eps=1e-5)
+
+
 def kimi_k2() -> ModelConfig:
     """Kimi-K2 geometry: the DeepSeek-V3 architecture with 64 heads and 384 routed experts (one dense layer, one
     routing group); served by the MLA engine."""
@@ -184,6 +204,7 @@ PRESETS = {
     "tiny-moe": tiny_moe,
     "mixtral-8x7b": mixtral_8x7b,
     "kimi-k2": kimi_k2,
+    "glm-4.5-air": glm45_air,
     "qwen3-30b-a3b": qwen3_30b_a3b,
     "deepseek-v3": deepseek_v3,
     "deepseek-v3.2": deepseek_v32,

@@ -100,7 +100,10 @@ __global__ void __launch_bounds__(128) qk_rope_kv_kernel(const __nv_bfloat16* __
                                                          const int* __restrict__ slots, __nv_bfloat16* __restrict__ q_out,
                                                          __nv_bfloat16* __restrict__ k_cache,
                                                          __nv_bfloat16* __restrict__ v_cache, int T, int Hq, int Hkv,
-                                                         float eps, int interleaved) {
+                                                         float eps, int interleaved,
+                                                         const __nv_bfloat16* __restrict__ bias, int rot) {
+  // bias (optional) [(Hq + 2 Hkv) * D]: added to the projection's bf16 output and rounded again.  rot: 128 rotates
+  // the whole head, 64 the first half only (partial rotary: the other 64 dims pass through).
   pdl_wait();
   pdl_trigger();
   constexpr int D = 128;
@@ -112,8 +115,14 @@ __global__ void __launch_bounds__(128) qk_rope_kv_kernel(const __nv_bfloat16* __
   const int lane = threadIdx.x & 31;
   const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * heads * D + h * D;
   // lane holds elements {2l, 2l+1} and {64+2l, 64+2l+1}
-  const uint32_t a = *reinterpret_cast<const uint32_t*>(src + 2 * lane);
-  const uint32_t b = *reinterpret_cast<const uint32_t*>(src + 64 + 2 * lane);
+  uint32_t a = *reinterpret_cast<const uint32_t*>(src + 2 * lane);
+  uint32_t b = *reinterpret_cast<const uint32_t*>(src + 64 + 2 * lane);
+  if (bias) {
+    const uint32_t ba = *reinterpret_cast<const uint32_t*>(bias + h * D + 2 * lane);
+    const uint32_t bb = *reinterpret_cast<const uint32_t*>(bias + h * D + 64 + 2 * lane);
+    a = pack_bf16(bf16_lo(a) + bf16_lo(ba), bf16_hi(a) + bf16_hi(ba));
+    b = pack_bf16(bf16_lo(b) + bf16_lo(bb), bf16_hi(b) + bf16_hi(bb));
+  }
   float x0 = bf16_lo(a), x1 = bf16_hi(a), x2 = bf16_lo(b), x3 = bf16_hi(b);
   const int slot = slots[t];
   if (h >= Hq + Hkv) {  // V: plain copy into the cache
@@ -138,7 +147,24 @@ __global__ void __launch_bounds__(128) qk_rope_kv_kernel(const __nv_bfloat16* __
   }
   const float pos = static_cast<float>(positions[t]);
   float y0, y1, y2, y3;
-  if (interleaved) {
+  if (rot == 64) {
+    // partial rotary: only elements [0, 64) rotate (this lane's first pair); 32 frequencies
+    y2 = x2; y3 = x3;
+    if (interleaved) {
+      float s0, c0;
+      sincosf(pos * inv_freq[lane], &s0, &c0);
+      y0 = x0 * c0 - x1 * s0; y1 = x0 * s0 + x1 * c0;
+    } else {
+      // pairs (i, i + 32): lanes 0..15 hold i = 2l, 2l + 1, lanes 16..31 hold their partners
+      const float p0 = __shfl_xor_sync(0xffffffffu, x0, 16), p1 = __shfl_xor_sync(0xffffffffu, x1, 16);
+      const int i0 = (2 * lane) & 31;
+      float s0, c0, s1, c1;
+      sincosf(pos * inv_freq[i0], &s0, &c0);
+      sincosf(pos * inv_freq[i0 + 1], &s1, &c1);
+      if (lane < 16) { y0 = x0 * c0 - p0 * s0; y1 = x1 * c1 - p1 * s1; }
+      else           { y0 = p0 * s0 + x0 * c0; y1 = p1 * s1 + x1 * c1; }
+    }
+  } else if (interleaved) {
     // pairs (2i, 2i+1): frequency index i; this lane holds pair l and pair 32+l
     float s0, c0, s1, c1;
     sincosf(pos * inv_freq[lane], &s0, &c0);
@@ -270,15 +296,17 @@ extern "C" int cafd_rmsnorm(const void* x, void* residual, const void* w, void* 
 
 extern "C" int cafd_qk_rope_kv(const void* qkv, const void* q_norm_w, const void* k_norm_w, const float* inv_freq,
                                const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
-                               int T, int Hq, int Hkv, int D, float eps, int interleaved, cafd_stream_t s) {
+                               int T, int Hq, int Hkv, int D, float eps, int interleaved, const void* bias, int rot,
+                               cafd_stream_t s) {
   if (T <= 0) return 0;
-  if (D != 128) return -10;
+  if (D != 128 || (rot != 128 && rot != 64)) return -10;
   const int warps = T * (Hq + 2 * Hkv);
   const int blocks = (warps + 3) / 4;
   launch_pdl(qk_rope_kv_kernel, dim3(blocks), dim3(128), 0, static_cast<cudaStream_t>(s), 
       static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(q_norm_w),
       static_cast<const __nv_bfloat16*>(k_norm_w), inv_freq, positions, slots, static_cast<__nv_bfloat16*>(q_out),
-      static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), T, Hq, Hkv, eps, interleaved);
+      static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), T, Hq, Hkv, eps, interleaved,
+      static_cast<const __nv_bfloat16*>(bias), rot);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -132,6 +132,18 @@ class Llama(Family):
     id, model_types, attention = "llama", ("llama", "mistral"), "gqa"
 
 
+class Glm4Moe(Family):
+    """GLM-4.5 / 4.6 (glm4_moe): GQA with biased q / k / v and partial rotary, sigmoid routing with a correction bias, a
+    shared expert and an MTP depth; served by the GQA engine."""
+    id, model_types, attention = "glm4_moe", ("glm4_moe",), "gqa"
+    speculators = ("off", "mtp")
+
+
+class Qwen2(Family):
+    """Dense Qwen2 / Qwen2.5 decoders (biased q / k / v): the GQA engine's dense path."""
+    id, model_types, attention = "qwen2", ("qwen2",), "gqa"
+
+
 class TinyMoe(Family):
     id, model_types = "tiny_moe", ("tiny_moe",)
 
@@ -151,7 +163,7 @@ def canonical_name(name: str) -> str:
     return _MIXTRAL_RE.sub(lambda m: m.group(1) + _MIXTRAL_PROJ[m.group(2)] + m.group(3), name)
 
 
-REGISTRY: tuple[Family, ...] = (DeepseekV32(), DeepseekV3(), Qwen3Moe(), Llama(), TinyMoe())
+REGISTRY: tuple[Family, ...] = (DeepseekV32(), DeepseekV3(), Qwen3Moe(), Glm4Moe(), Qwen2(), Llama(), TinyMoe())
 
 
 def detect(hf_config: dict) -> Family | None:

@@ -341,7 +341,7 @@ def load_engine(path: str, device: torch.device, num_pages: int, max_tokens: int
         _, params = load_params(path, dtype=torch.bfloat16, exclude=".mlp.experts.")
         W = GqaMoeWeights.from_params(cfg, params, device, with_experts=False)
         attach_stored_experts(W, snap, device)
-    elif cfg.mtp_layers:
+    elif cfg.mtp_layers or cfg.attention_bias:
         _, params = load_params(path, dtype=torch.bfloat16)
         W = GqaMoeWeights.from_params(cfg, params, device)
     else:

@@ -18,7 +18,8 @@ from . import formats
 from .safetensors_io import write_sharded
 
 ARCH = {"llama": "LlamaForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM", "deepseek_v3": "DeepseekV3ForCausalLM",
-        "deepseek_v32": "DeepseekV32ForCausalLM", "tiny_moe": "DeepseekV3ForCausalLM"}
+        "deepseek_v32": "DeepseekV32ForCausalLM", "tiny_moe": "DeepseekV3ForCausalLM", "glm4_moe": "Glm4MoeForCausalLM",
+        "qwen2": "Qwen2ForCausalLM"}
 
 
 def to_hf_config(cfg: ModelConfig) -> dict:
@@ -38,9 +39,17 @@ def to_hf_config(cfg: ModelConfig) -> dict:
                  topk_method="noaux_tc" if cfg.router_bias else "greedy")
         if cfg.indexer_heads:
             d.update(index_n_heads=cfg.indexer_heads, index_head_dim=cfg.indexer_dim, index_topk=cfg.indexer_topk)
+    elif cfg.family == "glm4_moe":
+        d.update(num_key_value_heads=cfg.num_kv_heads, head_dim=cfg.head_dim, n_routed_experts=cfg.num_experts,
+                 n_shared_experts=cfg.num_shared_experts, first_k_dense_replace=cfg.first_dense_layers, n_group=cfg.num_groups,
+                 topk_group=cfg.topk_groups, routed_scaling_factor=cfg.routed_scale, use_qk_norm=cfg.qk_norm,
+                 attention_bias=cfg.attention_bias, partial_rotary_factor=cfg.rope_dim / cfg.head_dim,
+                 num_nextn_predict_layers=cfg.mtp_layers)
     else:
         d.update(num_key_value_heads=cfg.num_kv_heads, head_dim=cfg.head_dim, num_experts=cfg.num_experts,
                  decoder_sparse_step=1, mlp_only_layers=list(range(cfg.first_dense_layers)), qk_norm=cfg.qk_norm)
+        if cfg.attention_bias:
+            d["attention_bias"] = True
     if cfg.rope_scaling != "none":
         rs = {"type": cfg.rope_scaling, "rope_type": cfg.rope_scaling, "factor": cfg.rope_factor,
               "original_max_position_embeddings": cfg.rope_original_max}
@@ -121,6 +130,30 @@ def from_hf_config(d: dict) -> ModelConfig:
             head_dim=d.get("head_dim", d["hidden_size"] // d["num_attention_heads"]), qk_norm=bool(d.get("qk_norm", mt.startswith("qwen3"))),
             rope_interleaved=extra.get("rope_interleaved", False), first_dense_layers=len(d.get("mlp_only_layers", []) or []),
             num_experts=d.get("num_experts", d.get("num_local_experts", 0)), scoring="softmax", num_shared_experts=0, **common)
+    if mt == "glm4_moe":
+        # GLM-4.5 / 4.6: GQA with biased q / k / v projections and RoPE on part of every head, sigmoid routing under a
+        # correction bias (noaux_tc), one shared expert, dense layers first, optional MTP depth
+        hd = d.get("head_dim") or d["hidden_size"] // d["num_attention_heads"]
+        rot = int(round(hd * float(d.get("partial_rotary_factor", 1.0))))
+        if hd != 128 or rot not in (64, 128):
+            raise ValueError(f"glm4_moe with head_dim {hd} and {rot} rotated dims is not supported (128 with 64 or 128)")
+        return ModelConfig(
+            family="glm4_moe", attention="gqa", num_kv_heads=d.get("num_key_value_heads", d["num_attention_heads"]), head_dim=hd,
+            qk_norm=bool(d.get("use_qk_norm", False)), rotary_dim=0 if rot == hd else rot, attention_bias=bool(d.get("attention_bias", False)),
+            rope_interleaved=extra.get("rope_interleaved", False), first_dense_layers=d.get("first_k_dense_replace", 0),
+            num_experts=d.get("n_routed_experts", 0), scoring="sigmoid", num_groups=d.get("n_group", 1) or 1,
+            topk_groups=d.get("topk_group", 1) or 1, num_shared_experts=d.get("n_shared_experts", 0) or 0,
+            routed_scale=d.get("routed_scaling_factor", 1.0), router_bias=True, mtp_layers=d.get("num_nextn_predict_layers", 0) or 0,
+            **common)
+    if mt == "qwen2":
+        # dense Qwen2 / Qwen2.5: a Llama-shaped stack whose q / k / v projections carry a bias
+        if d.get("use_sliding_window"):
+            raise ValueError("sliding-window attention is not supported")
+        return ModelConfig(
+            family="qwen2", attention="gqa", num_kv_heads=d.get("num_key_value_heads", d["num_attention_heads"]),
+            head_dim=d.get("head_dim") or d["hidden_size"] // d["num_attention_heads"], qk_norm=False, attention_bias=True,
+            rope_interleaved=extra.get("rope_interleaved", False), first_dense_layers=d["num_hidden_layers"], num_experts=0,
+            num_shared_experts=0, **dict(common, top_k=0, expert_ffn=0))
     if mt in ("llama", "mistral"):
         # dense GQA decoders without projection biases: every layer takes the dense SwiGLU path
         if d.get("attention_bias") or d.get("mlp_bias"):

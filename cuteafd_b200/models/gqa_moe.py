@@ -43,7 +43,7 @@ class LayerWeights:
     # ``fp8``: optional {projection name: (E4M3 values [N, K], fp32 128x128 block scales)} twins of the bf16 projections,
     # used for decode-sized steps (``GqaMoeEngine._linear``)
     __slots__ = ("ln1", "ln2", "wqkv", "wo", "q_norm", "k_norm", "router", "router_bias", "w_gate", "w_up", "w_down",
-                 "d_gate", "d_up", "d_down", "s_gate", "s_up", "s_down", "fp8")
+                 "d_gate", "d_up", "d_down", "s_gate", "s_up", "s_down", "fp8", "bqkv")
 
     def __init__(self) -> None:
         for s in self.__slots__:
@@ -104,6 +104,8 @@ class GqaMoeWeights:
             a, m = pre + "self_attn.", pre + "mlp."
             L.ln1, L.ln2 = t(pre + "input_layernorm.weight"), t(pre + "post_attention_layernorm.weight")
             L.wqkv = torch.cat([t(a + "q_proj.weight"), t(a + "k_proj.weight"), t(a + "v_proj.weight")]).contiguous()
+            if cfg.attention_bias:
+                L.bqkv = torch.cat([t(a + "q_proj.bias"), t(a + "k_proj.bias"), t(a + "v_proj.bias")]).contiguous()
             L.wo = t(a + "o_proj.weight")
             if cfg.qk_norm:
                 L.q_norm, L.k_norm = t(a + "q_norm.weight"), t(a + "k_norm.weight")
@@ -143,6 +145,8 @@ class GqaMoeWeights:
             L = LayerWeights()
             L.ln1, L.ln2 = ones(H), ones(H)
             L.wqkv, L.wo = w((cfg.num_heads + 2 * cfg.num_kv_heads) * D, H), w(H, cfg.num_heads * D)
+            if cfg.attention_bias:
+                L.bqkv = w((cfg.num_heads + 2 * cfg.num_kv_heads) * D)
             if cfg.qk_norm:
                 L.q_norm, L.k_norm = ones(D), ones(D)
             if layer_is_moe(cfg, i):
@@ -216,7 +220,7 @@ class GqaMoeEngine:
         if rope_magnitudes(cfg) != (1.0, 1.0):
             # the GQA attention kernels take no softmax-scale argument and the rope kernel no magnitude
             raise ValueError("YaRN magnitude scaling is not supported by the GQA engine (linear and llama3 scaling are)")
-        self.inv_freq = rope_inv_freq(cfg, cfg.head_dim).to(self.device)      # long-context scaling is in this table
+        self.inv_freq = rope_inv_freq(cfg, cfg.rope_dim).to(self.device)      # long-context scaling is in this table
         self.moe = None
         self.pre_moe = None          # hook(layer) called before each MoE layer's exchange
         if cfg.num_experts and build_moe:
@@ -270,7 +274,8 @@ class GqaMoeEngine:
         cfg, L, ws = self.cfg, self.W.layers[i], self.ws
         K.linear(ws.x[:T], L.wqkv, out=ws.qkv[:T])
         K.qk_rope_kv(ws.qkv[:T], L.q_norm, L.k_norm, self.inv_freq, b.positions, b.slots, ws.q[:T], self.kv.k[i],
-                     self.kv.v[i], cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.rms_eps, cfg.rope_interleaved)
+                     self.kv.v[i], cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.rms_eps, cfg.rope_interleaved,
+                     bias=L.bqkv)
         if b.prefill:
             K.attn_prefill(ws.q[:T], self.kv.k[i], self.kv.v[i], b.page_table, b.seq_lens, b.q_start, ws.attn[:T],
                            b.max_q_len)

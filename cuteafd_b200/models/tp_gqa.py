@@ -48,6 +48,10 @@ def shard_attention_weights(cfg: ModelConfig, W: GqaMoeWeights, rank: int, ranks
         S.wqkv = torch.cat([L.wqkv[q0 + rank * hq * D: q0 + (rank + 1) * hq * D],
                             L.wqkv[k0 + rank * hk * D: k0 + (rank + 1) * hk * D],
                             L.wqkv[v0 + rank * hk * D: v0 + (rank + 1) * hk * D]]).contiguous()
+        if L.bqkv is not None:
+            S.bqkv = torch.cat([L.bqkv[q0 + rank * hq * D: q0 + (rank + 1) * hq * D],
+                                L.bqkv[k0 + rank * hk * D: k0 + (rank + 1) * hk * D],
+                                L.bqkv[v0 + rank * hk * D: v0 + (rank + 1) * hk * D]]).contiguous()
         S.wo = L.wo[:, rank * hq * D:(rank + 1) * hq * D].contiguous()
         out.layers.append(S)
     return out
@@ -97,7 +101,7 @@ class TpGqaMoeEngine(GqaMoeEngine):
         cfg, L, ws, tp = self.cfg, self.W.layers[i], self.ws, self.tp
         tp.column_parallel_linear(T, L.wqkv, ws.qkv[:T])
         K.qk_rope_kv(ws.qkv[:T], L.q_norm, L.k_norm, self.inv_freq, b.positions, b.slots, ws.q[:T], self.kv.k[i],
-                     self.kv.v[i], cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.rms_eps, cfg.rope_interleaved)
+                     self.kv.v[i], cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.rms_eps, cfg.rope_interleaved, bias=L.bqkv)
         if b.prefill:
             K.attn_prefill(ws.q[:T], self.kv.k[i], self.kv.v[i], b.page_table, b.seq_lens, b.q_start, ws.attn[:T], b.max_q_len)
         else:

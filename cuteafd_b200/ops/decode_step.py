@@ -84,7 +84,8 @@ class FusedDecodeStep:
                 and 0 < cfg.num_experts <= 256 and cfg.top_k <= 8 and cfg.expert_ffn % 256 == 0 and not cfg.num_shared_experts
                 and cfg.first_dense_layers == 0 and all(cfg.is_moe_layer(i) for i in range(cfg.num_layers))
                 and (cfg.num_heads * 128) % 256 == 0 and cfg.num_heads % cfg.num_kv_heads == 0
-                and cfg.num_heads // cfg.num_kv_heads <= 16 and cfg.num_groups <= 32)
+                and cfg.num_heads // cfg.num_kv_heads <= 16 and cfg.num_groups <= 32
+                and not cfg.attention_bias and cfg.rope_dim == cfg.head_dim)
 
     def __init__(self, engine):
         cfg, W, dev = engine.cfg, engine.W, engine.device

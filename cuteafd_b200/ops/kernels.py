@@ -187,11 +187,15 @@ def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, w: torch.Tensor, eps: f
 
 def qk_rope_kv(qkv: torch.Tensor, q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, inv_freq: torch.Tensor,
                positions: torch.Tensor, slots: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
-               v_cache: torch.Tensor, Hq: int, Hkv: int, D: int, eps: float, interleaved: bool) -> None:
+               v_cache: torch.Tensor, Hq: int, Hkv: int, D: int, eps: float, interleaved: bool,
+               bias: torch.Tensor | None = None) -> None:
+    """q / k head norm (optional), RoPE and the paged K / V write for one step.  ``bias`` [(Hq + 2 Hkv) * D] bf16 is added
+    to the fused projection's rows first; the number of rotated dims is twice the length of ``inv_freq`` (128 or 64)."""
     T = qkv.shape[0]
     _n.check(_n.cuda_lib().cafd_qk_rope_kv(qkv.data_ptr(), _ptr(q_norm), _ptr(k_norm), inv_freq.data_ptr(),
                                            positions.data_ptr(), slots.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(),
-                                           v_cache.data_ptr(), T, Hq, Hkv, D, eps, int(interleaved), _stream()),
+                                           v_cache.data_ptr(), T, Hq, Hkv, D, eps, int(interleaved), _ptr(bias),
+                                           2 * inv_freq.shape[0], _stream()),
              "qk_rope_kv")
 
 

@@ -207,7 +207,7 @@ def make_engine(cfg, weights, num_pages: int, max_tokens: int, max_seqs: int, gr
             K.linear(ws.x[:T], L.wqkv, out=ws.qkv[:T])
             # slots are -1 on the ranks that do not hold the page of a new token: their K / V rows are dropped there
             K.qk_rope_kv(ws.qkv[:T], L.q_norm, L.k_norm, self.inv_freq, b.positions, b.slots, ws.q[:T], self.kv.k[i],
-                         self.kv.v[i], c.num_heads, c.num_kv_heads, c.head_dim, c.rms_eps, c.rope_interleaved)
+                         self.kv.v[i], c.num_heads, c.num_kv_heads, c.head_dim, c.rms_eps, c.rope_interleaved, bias=L.bqkv)
             self.cs.attend(ws.q[:T], self.kv.k[i], self.kv.v[i], b.page_table, b.seq_lens, b.kv_base, b.q_start, ws.attn[:T],
                            b.max_q_len)
             K.linear(ws.attn[:T].view(T, -1), L.wo, out=ws.h[:T], residual=ws.h[:T])

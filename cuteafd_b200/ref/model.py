@@ -61,6 +61,9 @@ def init_weights(cfg: ModelConfig, seed: int = 0, dtype: torch.dtype = torch.flo
             p[a + "k_proj.weight"] = w(cfg.num_kv_heads * cfg.head_dim, H)
             p[a + "v_proj.weight"] = w(cfg.num_kv_heads * cfg.head_dim, H)
             p[a + "o_proj.weight"] = w(H, cfg.num_heads * cfg.head_dim)
+            if cfg.attention_bias:
+                for n, rows in (("q", cfg.num_heads), ("k", cfg.num_kv_heads), ("v", cfg.num_kv_heads)):
+                    p[a + f"{n}_proj.bias"] = w(rows * cfg.head_dim)
             if cfg.qk_norm:
                 p[a + "q_norm.weight"] = ones(cfg.head_dim)
                 p[a + "k_norm.weight"] = ones(cfg.head_dim)
@@ -120,8 +123,7 @@ class RefDecoder:
     def __init__(self, cfg: ModelConfig, params: dict[str, torch.Tensor], moe_fn: MoeFn | None = None):
         self.cfg, self.p, self.moe_fn = cfg, params, moe_fn
         self.select_fn = None        # optional (layer, start, Tq, Tk) -> bool mask [Tq, Tk] replacing the indexer's choice
-        rd = cfg.qk_rope_dim if cfg.is_mla else cfg.head_dim
-        self.inv_freq = ops.rope_inv_freq(cfg, rd)                  # long-context scaling lives in this table
+        self.inv_freq = ops.rope_inv_freq(cfg, cfg.rope_dim)        # long-context scaling lives in this table
         self.rope_mag, self.scale_mul = ops.rope_magnitudes(cfg)
         self.usage: dict[int, torch.Tensor] | None = None     # set to {} to count routed tokens per layer and expert
         self.observe = None          # optional (operand prefix, input rows [n, in]) -> None, called before every projection
@@ -203,9 +205,12 @@ class RefDecoder:
             o = ops.causal_attention(qq, k, v, start, self.scale_mul / math.sqrt(cfg.qk_head_dim), allowed)
             o = o.reshape(T, cfg.num_heads * cfg.v_head_dim)
         else:
-            q = (x.float() @ p[a + "q_proj.weight"].float().T).to(x.dtype).view(T, cfg.num_heads, cfg.head_dim)
-            k = (x.float() @ p[a + "k_proj.weight"].float().T).to(x.dtype).view(T, cfg.num_kv_heads, cfg.head_dim)
-            v = (x.float() @ p[a + "v_proj.weight"].float().T).to(x.dtype).view(T, cfg.num_kv_heads, cfg.head_dim)
+            def proj(name: str, heads: int) -> torch.Tensor:
+                y = (x.float() @ p[a + name + ".weight"].float().T).to(x.dtype)
+                if cfg.attention_bias:       # projection rounded, bias added, rounded again (the engine adds it after the GEMM)
+                    y = (y.float() + p[a + name + ".bias"].float()).to(x.dtype)
+                return y.view(T, heads, cfg.head_dim)
+            q, k, v = proj("q_proj", cfg.num_heads), proj("k_proj", cfg.num_kv_heads), proj("v_proj", cfg.num_kv_heads)
             if cfg.qk_norm:
                 q = ops.rmsnorm(q, p[a + "q_norm.weight"], cfg.rms_eps)
                 k = ops.rmsnorm(k, p[a + "k_norm.weight"], cfg.rms_eps)

@@ -92,6 +92,10 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, theta: float = 10000.0,
     """x: [T, heads, dim].  interleaved rotates pairs (2i, 2i+1); otherwise (i, i+dim/2).  ``inv_freq`` replaces the
     plain ``theta`` table (long-context scaling); ``magnitude`` multiplies cos and sin."""
     dim = x.shape[-1]
+    rot = 2 * inv_freq.shape[0] if inv_freq is not None else dim
+    if rot < dim:                      # partial rotary: the leading ``rot`` dims rotate, the rest pass through
+        head = apply_rope(x[..., :rot], positions, theta, interleaved, inv_freq, magnitude)
+        return torch.cat([head, x[..., rot:]], dim=-1)
     ang = rope_angles(dim, positions, theta, inv_freq)
     cos, sin = ang.cos()[:, None, :] * magnitude, ang.sin()[:, None, :] * magnitude
     xf = x.float()

@@ -28,12 +28,19 @@ def build(cfg, use_graphs):
     return params, eng, gen
 
 
-@pytest.mark.parametrize("use_graphs", [False, True])
-def test_prefill_and_decode_match_oracle(use_graphs):
+def glm_cfg() -> ModelConfig:
+    """GLM-4.5 style layer: biased q / k / v, RoPE on the first half of every head, sigmoid routing under a correction
+    bias, a shared expert."""
+    return small_cfg().replace(name="glm4-moe-small", family="glm4_moe", qk_norm=False, rotary_dim=64, attention_bias=True,
+                               scoring="sigmoid", router_bias=True, routed_scale=1.0, rms_eps=1e-5)
+
+
+@pytest.mark.parametrize("use_graphs,family", [(False, "qwen3"), (True, "qwen3"), (False, "glm4"), (True, "glm4")])
+def test_prefill_and_decode_match_oracle(use_graphs, family):
     from cuteafd_b200.models.gqa_moe import Batch
     from cuteafd_b200.ops import kernels as K
     from cuteafd_b200.ref.model import KvState, RefDecoder
-    cfg = small_cfg()
+    cfg = small_cfg() if family == "qwen3" else glm_cfg()
     params, eng, gen = build(cfg, use_graphs)
     ref = RefDecoder(cfg, params)
     g = torch.Generator().manual_seed(1)

@@ -105,24 +105,31 @@ def test_rmsnorm_embed_argmax(K):
     assert K.argmax(logits)[3].item() == 77
 
 
-@pytest.mark.parametrize("interleaved,norm", [(False, True), (True, False)])
-def test_qk_rope_kv(K, interleaved, norm):
+@pytest.mark.parametrize("interleaved,norm,rot,bias", [(False, True, 128, False), (True, False, 128, False),
+                                                       (False, False, 64, True), (True, True, 64, True), (False, True, 128, True)])
+def test_qk_rope_kv(K, interleaved, norm, rot, bias):
+    """``rot`` 64: partial rotary (the second half of every head passes through); ``bias``: q / k / v projection bias
+    added to the projection's rows (and rounded) before the norm and the rotation."""
     T, Hq, Hkv, D, pages = 70, 8, 2, 128, 6
     qkv = bf(T, (Hq + 2 * Hkv) * D, seed=1)
     qn, kn = (bf(D, seed=2).abs() + 0.5, bf(D, seed=3).abs() + 0.5) if norm else (None, None)
     theta = 1.0e6
-    inv = (1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))).to(dev())
+    inv = (1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(dev())
+    bq = bf((Hq + 2 * Hkv) * D, seed=9) if bias else None
     pos = torch.arange(100, 100 + T, dtype=torch.int32, device=dev())
     perm = torch.randperm(pages * 64)[:T].to(torch.int32).to(dev())
     kc = torch.zeros(pages, Hkv, 64, D, dtype=torch.bfloat16, device=dev())       # [page, kv head, token, D]
     vc = torch.zeros_like(kc)
     q_out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=dev())
-    K.qk_rope_kv(qkv, qn, kn, inv, pos, perm, q_out, kc, vc, Hq, Hkv, D, 1e-6, interleaved)
-    q, k, v = qkv.view(T, Hq + 2 * Hkv, D).split([Hq, Hkv, Hkv], dim=1)
+    K.qk_rope_kv(qkv, qn, kn, inv, pos, perm, q_out, kc, vc, Hq, Hkv, D, 1e-6, interleaved, bias=bq)
+    rows = (qkv.float() + bq.float()).to(torch.bfloat16) if bias else qkv
+    q, k, v = rows.view(T, Hq + 2 * Hkv, D).split([Hq, Hkv, Hkv], dim=1)
     if norm:
         q, k = R.rmsnorm(q, qn, 1e-6), R.rmsnorm(k, kn, 1e-6)
-    rq = R.apply_rope(q, pos.long(), theta, interleaved)
-    rk = R.apply_rope(k, pos.long(), theta, interleaved)
+    rq = R.apply_rope(q, pos.long(), theta, interleaved, inv)
+    rk = R.apply_rope(k, pos.long(), theta, interleaved, inv)
+    if rot < D:                                     # the dims past the rotated ones come out bit for bit
+        assert torch.equal(q_out[..., rot:], q[..., rot:])
     close(q_out, rq, 1e-2, 1e-2)
     by_slot = lambda c: c.permute(0, 2, 1, 3).reshape(-1, Hkv, D)               # noqa: E731  slot = page * 64 + token
     close(by_slot(kc)[perm.long()], rk, 1e-2, 1e-2)

@@ -239,3 +239,43 @@ def test_load_params_keep_reads_one_expert_range(tmp_path):
     assert ids == set(range(lo, hi)) and all(".mlp.experts." in n for n in got)
     _, everything = load.load_params(src)
     assert all(torch.equal(got[n], everything[n]) for n in got)
+
+
+def test_glm4_moe_and_qwen2_configs_map_onto_the_gqa_engine(tmp_path):
+    """glm4_moe (biased q / k / v, partial rotary, sigmoid routing with a correction bias, shared expert, MTP) and dense
+    qwen2 (biased q / k / v) map onto the GQA geometry; a random snapshot round-trips; the oracle's partial rotary leaves
+    the unrotated dims alone and matches a full rotation of the rotated slice."""
+    import torch
+    from cuteafd_b200.config import PRESETS
+    from cuteafd_b200.loader import families, snapshot
+    from cuteafd_b200.loader.load import open_snapshot
+    from cuteafd_b200.ref import ops
+    hf = {"model_type": "glm4_moe", "vocab_size": 151552, "hidden_size": 4096, "num_hidden_layers": 46, "num_attention_heads": 96,
+          "num_key_value_heads": 8, "head_dim": 128, "partial_rotary_factor": 0.5, "attention_bias": True, "use_qk_norm": False,
+          "rope_theta": 1000000, "rms_norm_eps": 1e-5, "intermediate_size": 10944, "moe_intermediate_size": 1408,
+          "n_routed_experts": 128, "n_shared_experts": 1, "num_experts_per_tok": 8, "first_k_dense_replace": 1, "n_group": 1,
+          "topk_group": 1, "routed_scaling_factor": 1.0, "norm_topk_prob": True, "num_nextn_predict_layers": 1}
+    cfg = snapshot.from_hf_config(hf)
+    want = PRESETS["glm-4.5-air"]()
+    assert cfg.replace(name=want.name) == want
+    assert families.detect(hf).id == "glm4_moe" and cfg.rope_dim == 64
+    q2 = snapshot.from_hf_config({"model_type": "qwen2", "vocab_size": 1000, "hidden_size": 512, "num_hidden_layers": 2,
+                                  "num_attention_heads": 4, "num_key_value_heads": 2, "intermediate_size": 1024})
+    assert q2.family == "qwen2" and q2.attention_bias and q2.num_experts == 0 and families.detect({"model_type": "qwen2"}).id == "qwen2"
+    import pytest
+    with pytest.raises(ValueError):
+        snapshot.from_hf_config(dict(hf, partial_rotary_factor=0.25))
+    small = want.replace(vocab_size=512, num_layers=2, hidden=256, num_heads=4, num_kv_heads=2, dense_ffn=512, num_experts=8,
+                         expert_ffn=128, top_k=2, mtp_layers=0)
+    path = snapshot.write_random_snapshot(small, str(tmp_path / "glm"), fmt="bf16", seed=1)
+    snap = open_snapshot(path)
+    assert snap.cfg == small and snap.family.id == "glm4_moe" and snap.hints() == []
+    assert any(n.endswith("self_attn.q_proj.bias") for n in snap.catalog.entries)
+    # partial rotary in the oracle
+    x = torch.randn(5, 3, 128).to(torch.bfloat16)
+    pos = torch.arange(10, 15)
+    inv = ops.rope_inv_freq(small, 64)
+    for inter in (False, True):
+        y = ops.apply_rope(x, pos, small.rope_theta, inter, inv)
+        assert torch.equal(y[..., 64:], x[..., 64:])
+        assert torch.equal(y[..., :64], ops.apply_rope(x[..., :64].contiguous(), pos, small.rope_theta, inter, inv))
