@@ -45,11 +45,17 @@ class Launch:
 
     def start(self) -> None:
         os.makedirs(self.run_dir, exist_ok=True)
-        for r in self.ranks:
-            out = open(r.log, "ab") if r.log else None
-            r.proc = subprocess.Popen(r.argv, env={**os.environ, **r.env}, stdout=out, stderr=subprocess.STDOUT if out else None)
-            if out is not None:
-                out.close()
+        try:
+            for r in self.ranks:
+                out = open(r.log, "ab") if r.log else None
+                try:
+                    r.proc = subprocess.Popen(r.argv, env={**os.environ, **r.env}, stdout=out, stderr=subprocess.STDOUT if out else None)
+                finally:
+                    if out is not None:
+                        out.close()
+        except OSError:
+            self.stop(signal.SIGTERM)          # a rank that could not be started: the ones already running do not stay behind
+            raise
         with open(self.pid_file, "w") as f:
             json.dump({"launcher": os.getpid(), "plan_hash": self.spec.get("plan_hash"),
                        "ranks": [{"rank": r.rank, "role": r.role, "pid": r.proc.pid, "log": r.log} for r in self.ranks]}, f, indent=1)

@@ -130,3 +130,15 @@ def test_config_keys_become_flags(tmp_path):
     a.file_config = cli.load_config_file(a.config, a.set, cli.CONFIG_KEYS)
     with pytest.raises(SystemExit):
         cli.apply_config(ap, a, bad)
+
+
+def test_a_rank_that_cannot_start_leaves_nothing_running(tmp_path):
+    def argv_for(spec_path, spec, entry, extra):
+        if entry["rank"] == 1:
+            return ["/nonexistent/interpreter", "-c", "pass"]
+        return [sys.executable, "-c", "import time\ntime.sleep(60)"]
+    L = LA.build_launch(_spec(2), str(tmp_path), [], argv_for=argv_for)
+    L.grace_s = 0.5
+    with pytest.raises(OSError):
+        L.start()
+    assert L.ranks[0].proc.poll() is not None and L.ranks[1].proc is None
