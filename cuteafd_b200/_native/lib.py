@@ -145,10 +145,10 @@ def cuda_lib():
         _sig(lib, "cafd_moe_dispatch", [P, P, P, I, I, I, C.POINTER(MoeLayout), P, P, P])
         _sig(lib, "cafd_moe_combine", [P, P, P, P, P, I, I, I, P, I, P, P, P])
         _sig(lib, "cafd_attn_decode_scratch_floats", [I, I, I, I], C.c_longlong)
-        _sig(lib, "cafd_attn_decode", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
+        _sig(lib, "cafd_attn_decode", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P])
         _sig(lib, "cafd_attn_decode_partial", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P])
         _sig(lib, "cafd_attn_merge", [P, P, P, I, I, I, I, I, P])
-        _sig(lib, "cafd_attn_prefill", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
+        _sig(lib, "cafd_attn_prefill", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P])
         _sig(lib, "cafd_mla_scratch_floats", [I, I], C.c_longlong)
         _sig(lib, "cafd_mla_attention", [P, P, P, P, P, P, P, P, P, P, C.c_longlong, I, I, I, I, I, I, F, P, I, P])
         _sig(lib, "cafd_indexer_scores", [P, P, P, I, F, P, P, P, P, P, P, P, C.c_longlong, I, I, I, I, I, I, P])

@@ -29,6 +29,8 @@ class ModelConfig:
     qk_norm: bool = False                # Qwen3: RMSNorm over head_dim on q and k
     rotary_dim: int = 0                  # gqa: leading dims of a head that are rotated (0 = all; GLM-4.5: half the head)
     attention_bias: bool = False         # gqa: q / k / v projections carry a bias (GLM-4.5, Qwen2)
+    sliding_window: int = 0              # gqa: a query at position t sees keys (t - window, t] on the windowed layers (0 = none)
+    window_layers: tuple = ()            # per layer, 1 = windowed; empty = every layer when sliding_window is set
     q_lora_rank: int = 128               # mla (0 = direct q projection)
     kv_lora_rank: int = 64
     qk_nope_dim: int = 32
@@ -92,6 +94,14 @@ class ModelConfig:
         if self.is_mla:
             return self.qk_rope_dim
         return self.rotary_dim or self.head_dim
+
+    def window_of(self, layer: int) -> int:
+        """Sliding window of ``layer`` in tokens; 0 = full causal attention."""
+        if not self.sliding_window or self.is_mla:
+            return 0
+        if self.window_layers:
+            return self.sliding_window if layer < len(self.window_layers) and self.window_layers[layer] else 0
+        return self.sliding_window
 
     def is_moe_layer(self, layer: int) -> bool:
         return self.num_experts > 0 and layer >= self.first_dense_layers
@@ -181,6 +191,15 @@ def mixtral_8x7b() -> ModelConfig:
         scoring="softmax", num_shared_experts=0, norm_topk_prob=True, weight_format="bf16")
 
 
+def mistral_7b() -> ModelConfig:
+    """Mistral-7B-v0.1 geometry: a dense GQA 32 / 8 decoder whose every layer attends through a 4096-token sliding
+    window; served by the GQA engine's dense path."""
+    return ModelConfig(name="mistral-7b", family="llama", vocab_size=32000, num_layers=32, hidden=4096, attention="gqa",
+                       num_heads=32, num_kv_heads=8, head_dim=128, qk_norm=False, sliding_window=4096, rope_theta=10000.0,
+                       rope_interleaved=False, rms_eps=1e-5, dense_ffn=14336, first_dense_layers=32, num_experts=0,
+                       expert_ffn=0, top_k=0, num_shared_experts=0)
+
+
 def glm45_air() -> ModelConfig:
     """GLM-4.5-Air geometry (glm4_moe): 46 layers with one dense layer first, GQA 96 / 8 heads of 128 with biased q / k / v
     projections and RoPE on the first half of every head, 128 routed experts (FFN 1408) with sigmoid top-8 selection under a
@@ -203,6 +222,7 @@ def kimi_k2() -> ModelConfig:
 PRESETS = {
     "tiny-moe": tiny_moe,
     "mixtral-8x7b": mixtral_8x7b,
+    "mistral-7b": mistral_7b,
     "kimi-k2": kimi_k2,
     "glm-4.5-air": glm45_air,
     "qwen3-30b-a3b": qwen3_30b_a3b,

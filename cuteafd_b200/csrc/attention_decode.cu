@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ page_table, const int* __restrict__ seq_lens,
     const int* __restrict__ q_start, __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int max_pages,
-    int Hq, int Hkv, int tiles_per_seq, int splits, float scale_log2, const int* __restrict__ kv_base,
+    int Hq, int Hkv, int tiles_per_seq, int splits, float scale_log2, const int* __restrict__ kv_base, int window,
     const AttnPeers peers) {
   pdl_wait();
   pdl_trigger();
@@ -98,12 +98,14 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
   // row r of the tile = query token first_q + r / group, head kvh * group + r % group
   uint32_t qa[8][4];
   int limit[2];   // number of kv positions visible to rows g and g + 8
+  int lo[2];      // first visible position (sliding window; 0 without one)
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const int r = g + 8 * half;
     const int qi = first_q + r / group;
     const bool valid = qi < q_len;
     limit[half] = valid ? min(seq_len, base_vis + qi + 1) : 0;
+    lo[half] = !valid ? 0x7fffffff : (window > 0 ? max(0, limit[half] - window) : 0);
     const __nv_bfloat16* qrow = q + (static_cast<size_t>(q0 + (valid ? qi : 0)) * Hq + kvh * group + r % group) * kD;
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
@@ -114,10 +116,15 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
   int max_limit = limit[0] > limit[1] ? limit[0] : limit[1];
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) max_limit = max(max_limit, __shfl_xor_sync(0xffffffffu, max_limit, o));
+  int min_lo = lo[0] < lo[1] ? lo[0] : lo[1];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) min_lo = min(min_lo, __shfl_xor_sync(0xffffffffu, min_lo, o));
 
+  // pages [first_page, total_pages) hold every position some row of the tile sees; the splits share them
   const int total_pages = (max_limit + kPage - 1) / kPage;
-  const int per_split = (total_pages + splits - 1) / splits;
-  const int p0 = split * per_split;
+  const int first_page = min(min_lo / kPage, total_pages);
+  const int per_split = (total_pages - first_page + splits - 1) / splits;
+  const int p0 = first_page + split * per_split;
   const int p1 = min(total_pages, p0 + per_split);
 
   float m_run[2] = {-INFINITY, -INFINITY};
@@ -170,7 +177,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
       for (int j = 0; j < 4; ++j) {
         const int half = j >> 1;
         const int tok = tok_base + nt * 8 + 2 * t4 + (j & 1);
-        const float v = tok < limit[half] ? s[nt][j] * scale_log2 : -INFINITY;
+        const float v = (tok < limit[half] && tok >= lo[half]) ? s[nt][j] * scale_log2 : -INFINITY;
         s[nt][j] = v;
         mx[half] = fmaxf(mx[half], v);
       }
@@ -307,9 +314,9 @@ extern "C" long long cafd_attn_decode_scratch_floats(int num_seqs, int tiles_per
 extern "C" int cafd_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* page_table,
                                 const int* seq_lens, const int* q_start, void* out, float* scratch, int num_seqs,
                                 int max_q_len, int max_pages, int Hq, int Hkv, int D, int splits, float scale,
-                                cafd_stream_t s) {
+                                int window, cafd_stream_t s) {
   if (num_seqs <= 0) return 0;
-  if (D != kD || Hq % Hkv) return -10;
+  if (D != kD || Hq % Hkv || window < 0) return -10;
   const int group = Hq / Hkv;
   if (group > 16 || 16 % group) return -11;
   if (splits < 1) splits = 1;
@@ -328,7 +335,7 @@ extern "C" int cafd_attn_decode(const void* q, const void* k_cache, const void* 
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
       static_cast<const __nv_bfloat16*>(v_cache), page_table, seq_lens, q_start, static_cast<__nv_bfloat16*>(out),
       scratch, max_pages, Hq, Hkv, tiles_per_seq, splits, scale * 1.4426950408889634f, static_cast<const int*>(nullptr),
-      AttnPeers{});
+      window, AttnPeers{});
   if (splits > 1) {
     dim3 g2(num_seqs * tiles_per_seq, Hkv, 16);
     launch_pdl(attn_merge_kernel, g2, dim3(128), 0, st, scratch, q_start, static_cast<__nv_bfloat16*>(out), Hq, Hkv, tiles_per_seq,
@@ -369,7 +376,7 @@ extern "C" int cafd_attn_decode_partial(const void* q, const void* k_cache, cons
   launch_pdl(attn_decode_kernel, grid, dim3(128), smem, st, static_cast<const __nv_bfloat16*>(q),
              static_cast<const __nv_bfloat16*>(k_cache), static_cast<const __nv_bfloat16*>(v_cache), page_table, seq_lens, q_start,
              static_cast<__nv_bfloat16*>(nullptr), peers.scratch[my_rank], max_pages, Hq, Hkv, tiles_per_seq, splits,
-             scale * 1.4426950408889634f, kv_base, peers);
+             scale * 1.4426950408889634f, kv_base, 0, peers);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -47,6 +47,7 @@ struct PrefillDev {
   int max_pages;
   int Hq, Hkv;
   float scale_log2;
+  int window;              // sliding window: a query at position t sees keys (t - window, t]; 0 = all earlier keys
   // kRope only
   const int* kv_tmp_start; // [seqs] first row of the sequence in the expansion buffers (multiple of 64)
   int q_head_stride;       // elements between heads in the nope query matrix (192 for [T, heads * 192])
@@ -93,7 +94,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int row0 = qt * kBQ;                       // first query row of this tile (within the chunk)
   const int pos0 = kv_len - q_len + row0;          // its absolute position
   const int last_pos = min(pos0 + kBQ - 1, kv_len - 1);
-  const int n_tiles = last_pos / kBKV + 1;
+  // kv tiles [tile0, last_pos / kBKV]: with a sliding window the tiles wholly before the first row's window are skipped
+  const int tile0 = p.window > 0 ? max(0, pos0 - p.window + 1) / kBKV : 0;
+  const int n_tiles = last_pos / kBKV + 1 - tile0;
   const int seq_pages = (kv_len + kPageTok - 1) / kPageTok;
 
   if (threadIdx.x == 0) {
@@ -128,7 +131,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       if (kRope) tma_load_2d(sQr, &tm_qr, &q_full, head * p.qr_head_stride + p.qr_col0, q0 + row0);
       const int* pt = p.page_table + static_cast<size_t>(seq) * p.max_pages;
       const int tmp_page0 = kRope ? p.kv_tmp_start[seq] / kPageTok : 0;
-      auto pages_of = [&](int j, int& pa, int& pb, int& ka, int& kb) {
+      auto pages_of = [&](int jj, int& pa, int& pb, int& ka, int& kb) {
+        const int j = jj + tile0;
         pa = 2 * j < seq_pages ? pt[2 * j] : 0;                      // page 0 is the all-zero page
         pb = 2 * j + 1 < seq_pages ? pt[2 * j + 1] : 0;
         // expanded K / V (kRope) sit in order in their buffer: "page" = row block of 64; past the end TMA fills zeros
@@ -253,8 +257,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       if (!mbar_wait(&s_full[st], ph, p.status, kTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
       const uint32_t tSj = tS + st * 128 + lane_off + half * 64;
-      const bool need_mask = (j * kBKV + kBKV - 1) > pos0;      // uniform over the CTA
-      const int col_limit = rowpos - j * kBKV - half * 64;      // local columns <= col_limit are visible
+      const int col0 = (j + tile0) * kBKV;                      // first kv position of this tile
+      // uniform over the CTA: the tile reaches past the first row's diagonal, or starts before the last row's window
+      const bool need_mask = (col0 + kBKV - 1) > pos0 || (p.window > 0 && col0 < pos0 + kBQ - p.window);
+      const int col_limit = rowpos - col0 - half * 64;          // local columns <= col_limit are visible
+      const int col_lo = p.window > 0 ? col_limit - p.window + 1 : -(1 << 30);   // and local columns >= col_lo
       // This half of the score row goes to registers with one wait; the TMEM buffer is handed back at once, so
       // the MMA warp can start the scores of tile j + 2 while this tile's exponentials run.
       uint32_t r[64];
@@ -266,7 +273,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 64; ++i)
-          if (i > col_limit) r[i] = 0xff800000u;    // -inf
+          if (i > col_limit || i < col_lo) r[i] = 0xff800000u;    // -inf
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains: the maximum is latency-bound
 #pragma unroll
@@ -387,9 +394,9 @@ using namespace cafd;
 extern "C" int cafd_attn_prefill(const void* q, const void* k_cache, const void* v_cache, const int* page_table,
                                  const int* seq_lens, const int* q_start, void* out, uint32_t* status, int total_q,
                                  int num_seqs, int max_q_len, int num_pages, int max_pages, int Hq, int Hkv, int D,
-                                 float scale, cafd_stream_t s) {
+                                 float scale, int window, cafd_stream_t s) {
   if (num_seqs <= 0 || total_q <= 0) return 0;
-  if (D != kHD || Hq % Hkv) return -10;
+  if (D != kHD || Hq % Hkv || window < 0) return -10;
   CUtensorMap tq, tk, tv;
   int rc = cached_tmap_2d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, total_q, static_cast<uint64_t>(Hq) * kHD,
                           static_cast<uint64_t>(Hq) * kHD * 2, kBQ, 64);
@@ -415,6 +422,7 @@ extern "C" int cafd_attn_prefill(const void* q, const void* k_cache, const void*
   p.Hq = Hq;
   p.Hkv = Hkv;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window;
   p.kv_tmp_start = nullptr; p.q_head_stride = kHD; p.qr_head_stride = 0; p.qr_col0 = 0;
   static bool attr = false;
   if (!attr) {
@@ -465,6 +473,7 @@ extern "C" int cafd_attn_prefill_mla(const void* q_nope, int q_head_stride, cons
   p.status = status;
   p.max_pages = max_pages; p.Hq = heads; p.Hkv = heads;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = 0;
   p.kv_tmp_start = kv_tmp_start; p.q_head_stride = q_head_stride; p.qr_head_stride = qr_head_stride; p.qr_col0 = qr_col0;
   static bool attr = false;
   if (!attr) {

@@ -128,7 +128,7 @@ class Qwen3Moe(Family):
 
 
 class Llama(Family):
-    """Dense GQA decoders (Llama, Mistral without a sliding window): served by the GQA engine's dense path."""
+    """Dense GQA decoders (Llama; Mistral, sliding-window layers included): served by the GQA engine's dense path."""
     id, model_types, attention = "llama", ("llama", "mistral"), "gqa"
 
 

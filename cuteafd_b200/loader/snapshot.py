@@ -50,6 +50,9 @@ def to_hf_config(cfg: ModelConfig) -> dict:
                  decoder_sparse_step=1, mlp_only_layers=list(range(cfg.first_dense_layers)), qk_norm=cfg.qk_norm)
         if cfg.attention_bias:
             d["attention_bias"] = True
+    if cfg.sliding_window and not cfg.is_mla:
+        d.update(sliding_window=cfg.sliding_window, use_sliding_window=True,
+                 layer_types=["sliding_attention" if cfg.window_of(i) else "full_attention" for i in range(cfg.num_layers)])
     if cfg.rope_scaling != "none":
         rs = {"type": cfg.rope_scaling, "rope_type": cfg.rope_scaling, "factor": cfg.rope_factor,
               "original_max_position_embeddings": cfg.rope_original_max}
@@ -69,6 +72,27 @@ def to_hf_config(cfg: ModelConfig) -> dict:
     elif cfg.weight_format.startswith("exl3"):
         d["quantization_config"] = {"quant_method": "exl3", "bits": 4}
     return d
+
+
+def _windows(d: dict) -> dict:
+    """config.json sliding-window fields -> ModelConfig fields.  ``layer_types`` names the windowed layers where it is
+    present; the Qwen2 / Qwen3 form (``use_sliding_window`` with ``max_window_layers``) windows the layers from that
+    index on; a bare ``sliding_window`` (Mistral, Mixtral) windows every layer."""
+    w, n = d.get("sliding_window"), d["num_hidden_layers"]
+    kinds = d.get("layer_types")
+    if kinds:
+        unknown = set(kinds) - {"sliding_attention", "full_attention"}
+        if unknown or len(kinds) != n:
+            raise ValueError(f"layer_types {sorted(unknown)} / {len(kinds)} entries for {n} layers is not supported")
+        flags = tuple(1 if k == "sliding_attention" else 0 for k in kinds)
+    elif str(d.get("model_type", "")).startswith("qwen"):
+        first = d.get("max_window_layers", n) if d.get("use_sliding_window") else n
+        flags = tuple(1 if i >= first else 0 for i in range(n))
+    else:
+        flags = (1,) * n
+    if not w or not any(flags):
+        return {}
+    return {"sliding_window": int(w), "window_layers": () if all(flags) else flags}
 
 
 def _rope_scaling(d: dict) -> dict:
@@ -123,13 +147,13 @@ def from_hf_config(d: dict) -> ModelConfig:
         dense_layers = sorted(d.get("mlp_only_layers", []) or [])
         if dense_layers != list(range(len(dense_layers))):
             raise ValueError("dense layers must be the first layers of the stack")
-        if d.get("attention_bias") or d.get("use_sliding_window"):
-            raise ValueError("projection biases and sliding-window attention are not supported")
+        if d.get("attention_bias"):
+            raise ValueError("projection biases are not supported for this model type")
         return ModelConfig(
             family="qwen3_moe", attention="gqa", num_kv_heads=d.get("num_key_value_heads", d["num_attention_heads"]),
             head_dim=d.get("head_dim", d["hidden_size"] // d["num_attention_heads"]), qk_norm=bool(d.get("qk_norm", mt.startswith("qwen3"))),
             rope_interleaved=extra.get("rope_interleaved", False), first_dense_layers=len(d.get("mlp_only_layers", []) or []),
-            num_experts=d.get("num_experts", d.get("num_local_experts", 0)), scoring="softmax", num_shared_experts=0, **common)
+            num_experts=d.get("num_experts", d.get("num_local_experts", 0)), scoring="softmax", num_shared_experts=0, **_windows(d), **common)
     if mt == "glm4_moe":
         # GLM-4.5 / 4.6: GQA with biased q / k / v projections and RoPE on part of every head, sigmoid routing under a
         # correction bias (noaux_tc), one shared expert, dense layers first, optional MTP depth
@@ -147,24 +171,20 @@ def from_hf_config(d: dict) -> ModelConfig:
             **common)
     if mt == "qwen2":
         # dense Qwen2 / Qwen2.5: a Llama-shaped stack whose q / k / v projections carry a bias
-        if d.get("use_sliding_window"):
-            raise ValueError("sliding-window attention is not supported")
         return ModelConfig(
             family="qwen2", attention="gqa", num_kv_heads=d.get("num_key_value_heads", d["num_attention_heads"]),
             head_dim=d.get("head_dim") or d["hidden_size"] // d["num_attention_heads"], qk_norm=False, attention_bias=True,
             rope_interleaved=extra.get("rope_interleaved", False), first_dense_layers=d["num_hidden_layers"], num_experts=0,
-            num_shared_experts=0, **dict(common, top_k=0, expert_ffn=0))
+            num_shared_experts=0, **_windows(d), **dict(common, top_k=0, expert_ffn=0))
     if mt in ("llama", "mistral"):
         # dense GQA decoders without projection biases: every layer takes the dense SwiGLU path
         if d.get("attention_bias") or d.get("mlp_bias"):
             raise ValueError("projection biases are not supported")
-        if mt == "mistral" and d.get("sliding_window"):
-            raise ValueError("sliding-window attention is not supported")
         return ModelConfig(
             family="llama", attention="gqa", num_kv_heads=d.get("num_key_value_heads", d["num_attention_heads"]),
             head_dim=d.get("head_dim") or d["hidden_size"] // d["num_attention_heads"], qk_norm=False,
             rope_interleaved=extra.get("rope_interleaved", False), first_dense_layers=d["num_hidden_layers"], num_experts=0,
-            num_shared_experts=0, **dict(common, top_k=0, expert_ffn=0))
+            num_shared_experts=0, **_windows(d), **dict(common, top_k=0, expert_ffn=0))
     raise ValueError(f"unsupported model_type {mt!r}")
 
 

@@ -278,7 +278,7 @@ class GqaMoeEngine:
                      bias=L.bqkv)
         if b.prefill:
             K.attn_prefill(ws.q[:T], self.kv.k[i], self.kv.v[i], b.page_table, b.seq_lens, b.q_start, ws.attn[:T],
-                           b.max_q_len)
+                           b.max_q_len, window=cfg.window_of(i))
             self.launches += 3
         else:
             S, max_pages = b.page_table.shape
@@ -289,7 +289,7 @@ class GqaMoeEngine:
             if self._scratch is None or self._scratch.numel() < need:
                 self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
             K.attn_decode(ws.q[:T], self.kv.k[i], self.kv.v[i], b.page_table, b.seq_lens, b.q_start, ws.attn[:T],
-                          self._scratch, b.max_q_len, splits)
+                          self._scratch, b.max_q_len, splits, window=cfg.window_of(i))
             self.launches += 3 + (1 if splits > 1 else 0)
         # o_proj with the residual add fused into the epilogue: h = h + attn @ wo.T
         K.linear(ws.attn[:T].view(T, -1), L.wo, out=ws.h[:T], residual=ws.h[:T])

@@ -27,7 +27,8 @@ def stage_config(cfg: ModelConfig, plan: StagePlan, stage: int) -> ModelConfig:
     stay dense), no MTP depth (that belongs to the last stage's drafter, not to the stack)."""
     own = plan.layers(stage)
     dense = max(0, min(len(own), cfg.first_dense_layers - own.start))
-    return cfg.replace(num_layers=len(own), first_dense_layers=dense, mtp_layers=0)
+    return cfg.replace(num_layers=len(own), first_dense_layers=dense, mtp_layers=0,
+                       window_layers=tuple(cfg.window_layers[own.start:own.stop]))
 
 
 def stage_params(cfg: ModelConfig, params: dict, plan: StagePlan, stage: int) -> dict:

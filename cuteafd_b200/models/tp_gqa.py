@@ -103,7 +103,8 @@ class TpGqaMoeEngine(GqaMoeEngine):
         K.qk_rope_kv(ws.qkv[:T], L.q_norm, L.k_norm, self.inv_freq, b.positions, b.slots, ws.q[:T], self.kv.k[i],
                      self.kv.v[i], cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.rms_eps, cfg.rope_interleaved, bias=L.bqkv)
         if b.prefill:
-            K.attn_prefill(ws.q[:T], self.kv.k[i], self.kv.v[i], b.page_table, b.seq_lens, b.q_start, ws.attn[:T], b.max_q_len)
+            K.attn_prefill(ws.q[:T], self.kv.k[i], self.kv.v[i], b.page_table, b.seq_lens, b.q_start, ws.attn[:T], b.max_q_len,
+                           window=cfg.window_of(i))
         else:
             S, max_pages = b.page_table.shape
             q_per_tile = 16 // (cfg.num_heads // cfg.num_kv_heads)
@@ -113,7 +114,7 @@ class TpGqaMoeEngine(GqaMoeEngine):
             if self._scratch is None or self._scratch.numel() < need:
                 self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
             K.attn_decode(ws.q[:T], self.kv.k[i], self.kv.v[i], b.page_table, b.seq_lens, b.q_start, ws.attn[:T],
-                          self._scratch, b.max_q_len, splits)
+                          self._scratch, b.max_q_len, splits, window=cfg.window_of(i))
         tp.step()
         tp.row_parallel_linear(ws.attn[:T].view(T, -1), L.wo)
         tp.reduce_norm_gather(T, L.ln2, cfg.rms_eps)

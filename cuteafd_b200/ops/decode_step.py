@@ -85,7 +85,7 @@ class FusedDecodeStep:
                 and cfg.first_dense_layers == 0 and all(cfg.is_moe_layer(i) for i in range(cfg.num_layers))
                 and (cfg.num_heads * 128) % 256 == 0 and cfg.num_heads % cfg.num_kv_heads == 0
                 and cfg.num_heads // cfg.num_kv_heads <= 16 and cfg.num_groups <= 32
-                and not cfg.attention_bias and cfg.rope_dim == cfg.head_dim)
+                and not cfg.attention_bias and cfg.rope_dim == cfg.head_dim and not cfg.sliding_window)
 
     def __init__(self, engine):
         cfg, W, dev = engine.cfg, engine.W, engine.device

@@ -352,14 +352,16 @@ def attn_decode_splits(num_seqs: int, tiles_per_seq: int, Hkv: int, max_pages: i
 
 def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
                 seq_lens: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor | None,
-                max_q_len: int, splits: int, scale: float | None = None) -> torch.Tensor:
+                max_q_len: int, splits: int, scale: float | None = None, window: int = 0) -> torch.Tensor:
+    """``window`` > 0: a query at position t sees keys (t - window, t] only (sliding-window layers); the pages
+    before the window are not read."""
     _, Hq, D = q.shape
     Hkv = k_cache.shape[1]                 # pools are [pages, kv heads, 64, D]
     num_seqs, max_pages = page_table.shape
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     _n.check(_n.cuda_lib().cafd_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_table.data_ptr(),
                                             seq_lens.data_ptr(), q_start.data_ptr(), out.data_ptr(), _ptr(scratch),
-                                            num_seqs, max_q_len, max_pages, Hq, Hkv, D, splits, scale, _stream()),
+                                            num_seqs, max_q_len, max_pages, Hq, Hkv, D, splits, scale, int(window), _stream()),
              "attn_decode")
     return out
 
@@ -397,7 +399,7 @@ def attn_decode_scratch_floats(num_seqs: int, max_q_len: int, Hq: int, Hkv: int,
 
 def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
                  seq_lens: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor, max_q_len: int,
-                 scale: float | None = None) -> torch.Tensor:
+                 scale: float | None = None, window: int = 0) -> torch.Tensor:
     total_q, Hq, D = q.shape
     num_pages, Hkv, _, _ = k_cache.shape   # pools are [pages, kv heads, 64, D]
     num_seqs, max_pages = page_table.shape
@@ -405,7 +407,7 @@ def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     _n.check(_n.cuda_lib().cafd_attn_prefill(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_table.data_ptr(),
                                              seq_lens.data_ptr(), q_start.data_ptr(), out.data_ptr(),
                                              status_word(q.device).data_ptr(), total_q, num_seqs, max_q_len, num_pages,
-                                             max_pages, Hq, Hkv, D, scale, _stream()), "attn_prefill")
+                                             max_pages, Hq, Hkv, D, scale, int(window), _stream()), "attn_prefill")
     return out
 
 

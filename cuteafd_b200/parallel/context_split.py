@@ -195,6 +195,8 @@ def make_engine(cfg, weights, num_pages: int, max_tokens: int, max_seqs: int, gr
     replicated on every rank of the group."""
     from ..models.gqa_moe import GqaMoeEngine, KvCache
     from ..ops import kernels as K
+    if cfg.sliding_window:
+        raise ValueError("context split and sliding-window layers do not combine: a window never spans more pages than one rank holds")
 
     class ContextSplitEngine(GqaMoeEngine):
         def __init__(self):

@@ -220,7 +220,7 @@ class RefDecoder:
             half = cfg.num_kv_heads * cfg.head_dim
             k_all = full[:, :half].view(-1, cfg.num_kv_heads, cfg.head_dim)
             v_all = full[:, half:].view(-1, cfg.num_kv_heads, cfg.head_dim)
-            o = ops.causal_attention(q, k_all, v_all, start).reshape(T, cfg.num_heads * cfg.head_dim)
+            o = ops.causal_attention(q, k_all, v_all, start, window=cfg.window_of(layer)).reshape(T, cfg.num_heads * cfg.head_dim)
         self._see(a + "o_proj", o)
         return (o.float() @ p[a + "o_proj.weight"].float().T).to(x.dtype)
 

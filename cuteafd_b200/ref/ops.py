@@ -201,9 +201,9 @@ def index_select(q_idx: torch.Tensor, k_idx: torch.Tensor, head_w: torch.Tensor,
 
 
 def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_start: int, scale: float | None = None,
-                     allowed: torch.Tensor | None = None) -> torch.Tensor:
+                     allowed: torch.Tensor | None = None, window: int = 0) -> torch.Tensor:
     """q [Tq, Hq, D], k [Tk, Hk, D], v [Tk, Hk, Dv]; query row i sits at position q_start+i.  ``allowed`` [Tq, Tk]
-    further restricts the visible positions (sparse attention)."""
+    further restricts the visible positions (sparse attention); ``window`` > 0 keeps keys (t - window, t] only."""
     Tq, Hq, D = q.shape
     Tk, Hk, _ = k.shape
     rep = Hq // Hk
@@ -214,6 +214,8 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_start:
     qpos = torch.arange(Tq, device=q.device)[:, None] + q_start
     kpos = torch.arange(Tk, device=q.device)[None, :]
     s = s.masked_fill((kpos > qpos)[None], float("-inf"))
+    if window > 0:
+        s = s.masked_fill((kpos <= qpos - window)[None], float("-inf"))
     if allowed is not None:
         s = s.masked_fill(~allowed.to(s.device)[None], float("-inf"))
     p = torch.softmax(s, dim=-1)

@@ -35,12 +35,19 @@ def glm_cfg() -> ModelConfig:
                                scoring="sigmoid", router_bias=True, routed_scale=1.0, rms_eps=1e-5)
 
 
-@pytest.mark.parametrize("use_graphs,family", [(False, "qwen3"), (True, "qwen3"), (False, "glm4"), (True, "glm4")])
+def swa_cfg() -> ModelConfig:
+    """Hybrid stack: the second layer attends through a 48-token sliding window (shorter than a page and than the
+    prompts), the first to everything."""
+    c = small_cfg()
+    return c.replace(name="swa-small", sliding_window=48, window_layers=tuple(i % 2 for i in range(c.num_layers)))
+
+
+@pytest.mark.parametrize("use_graphs,family", [(False, "qwen3"), (True, "qwen3"), (False, "glm4"), (True, "glm4"), (False, "swa"), (True, "swa")])
 def test_prefill_and_decode_match_oracle(use_graphs, family):
     from cuteafd_b200.models.gqa_moe import Batch
     from cuteafd_b200.ops import kernels as K
     from cuteafd_b200.ref.model import KvState, RefDecoder
-    cfg = small_cfg() if family == "qwen3" else glm_cfg()
+    cfg = {"qwen3": small_cfg, "glm4": glm_cfg, "swa": swa_cfg}[family]()
     params, eng, gen = build(cfg, use_graphs)
     ref = RefDecoder(cfg, params)
     g = torch.Generator().manual_seed(1)

@@ -254,6 +254,47 @@ def test_attn_prefill(K, lens, qlens):
         o += qlens[s]
 
 
+@pytest.mark.parametrize("lens,qlens,splits,window", [([700, 64, 1, 333], [1, 1, 1, 1], 4, 128), ([900, 130], [2, 4], 3, 100),
+                                                      ([8192], [1], 16, 4096), ([500], [1], 2, 1), ([300], [3], 1, 1000)])
+def test_attn_decode_sliding_window(K, lens, qlens, splits, window):
+    """A query at position t sees keys (t - window, t] only; pages before the window are skipped, whatever the split."""
+    Hq, Hkv, D, S = 32, 4, 128, len(lens)
+    kc, vc, table, dense = _paged_kv(S, lens, Hkv, D)
+    q = bf(sum(qlens), Hq, D, seed=99)
+    q_start = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device=dev())
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=dev())
+    out = torch.zeros_like(q)
+    scratch = torch.empty(K.attn_decode_scratch_floats(S, max(qlens), Hq, Hkv, splits), dtype=torch.float32, device=dev())
+    K.attn_decode(q, kc, vc, table, seq_lens, q_start, out, scratch, max(qlens), splits, window=window)
+    o = 0
+    for s in range(S):
+        k, v = dense[s]
+        ref = R.causal_attention(q[o:o + qlens[s]], k, v, lens[s] - qlens[s], window=window)
+        close(out[o:o + qlens[s]], ref)
+        o += qlens[s]
+
+
+@pytest.mark.parametrize("lens,qlens,window", [([300], [300], 64), ([1000], [200], 300), ([517, 130], [517, 66], 128),
+                                               ([2048], [2048], 1000), ([640], [640], 1), ([400], [400], 5000)])
+def test_attn_prefill_sliding_window(K, lens, qlens, window):
+    """kv tiles wholly before the first row's window are not loaded; the tiles that straddle a window edge are masked
+    from below as well as along the diagonal."""
+    Hq, Hkv, D, S = 8, 2, 128, len(lens)
+    kc, vc, table, dense = _paged_kv(S, lens, Hkv, D)
+    q = bf(sum(qlens), Hq, D, seed=99)
+    q_start = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device=dev())
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=dev())
+    out = torch.zeros_like(q)
+    K.attn_prefill(q, kc, vc, table, seq_lens, q_start, out, max(qlens), window=window)
+    check_status(K)
+    o = 0
+    for s in range(S):
+        k, v = dense[s]
+        ref = R.causal_attention(q[o:o + qlens[s]], k, v, lens[s] - qlens[s], window=window)
+        close(out[o:o + qlens[s]], ref)
+        o += qlens[s]
+
+
 # ---- FP8 block-scaled -----------------------------------------------------------------------------------
 def _fp8_ref(x, w, w_up=None):
     from cuteafd_b200.quant import codecs

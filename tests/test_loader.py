@@ -279,3 +279,22 @@ def test_glm4_moe_and_qwen2_configs_map_onto_the_gqa_engine(tmp_path):
         y = ops.apply_rope(x, pos, small.rope_theta, inter, inv)
         assert torch.equal(y[..., 64:], x[..., 64:])
         assert torch.equal(y[..., :64], ops.apply_rope(x[..., :64].contiguous(), pos, small.rope_theta, inter, inv))
+
+
+def test_sliding_window_fields_map_per_layer():
+    """A bare ``sliding_window`` windows every layer (Mistral); the Qwen form windows the layers from ``max_window_layers``
+    on and only with ``use_sliding_window``; ``layer_types`` names them one by one and survives a config round trip."""
+    from cuteafd_b200.loader.snapshot import from_hf_config, to_hf_config
+    base = {"vocab_size": 1000, "hidden_size": 512, "num_hidden_layers": 4, "num_attention_heads": 4, "num_key_value_heads": 2,
+            "head_dim": 128, "intermediate_size": 1024, "sliding_window": 256}
+    c = from_hf_config(dict(base, model_type="mistral"))
+    assert [c.window_of(i) for i in range(4)] == [256] * 4 and c.window_layers == ()
+    c = from_hf_config(dict(base, model_type="qwen3"))
+    assert c.sliding_window == 0
+    c = from_hf_config(dict(base, model_type="qwen3", use_sliding_window=True, max_window_layers=3))
+    assert [c.window_of(i) for i in range(4)] == [0, 0, 0, 256]
+    c = from_hf_config(dict(base, model_type="llama", layer_types=["sliding_attention", "full_attention"] * 2))
+    assert [c.window_of(i) for i in range(4)] == [256, 0, 256, 0]
+    assert from_hf_config(to_hf_config(c)).window_layers == (1, 0, 1, 0)
+    with pytest.raises(ValueError):
+        from_hf_config(dict(base, model_type="llama", layer_types=["chunked_attention"] * 4))

@@ -72,8 +72,9 @@ def test_config_round_trip_and_refusals():
         snapshot.from_hf_config(dict(llama, rope_scaling={"rope_type": "longrope", "factor": 4.0}))
     with pytest.raises(ValueError, match="bias"):
         snapshot.from_hf_config(dict(llama, attention_bias=True))
-    with pytest.raises(ValueError, match="sliding"):
-        snapshot.from_hf_config(dict(llama, model_type="mistral", sliding_window=4096))
+    assert snapshot.from_hf_config(dict(llama, model_type="mistral", sliding_window=4096)).window_of(1) == 4096
+    with pytest.raises(ValueError, match="layer_types"):
+        snapshot.from_hf_config(dict(llama, layer_types=["chunked_attention", "full_attention"]))
     v5 = dict(llama)                                                  # newer configs keep theta inside rope_parameters
     del v5["rope_scaling"], v5["rope_theta"]
     v5["rope_parameters"] = {"rope_type": "default", "rope_theta": 500000.0}
