@@ -10,7 +10,8 @@
 // (position, token) score is independent, so a split over the kv range needs no merge.
 //
 // Selection is a four-level radix descent over order-preserving keys (256-bin count histograms)
-// followed by an ordered compaction, one block per query token; same result on every run.
+// followed by an ordered compaction, one thread-block cluster per query token (histograms and counts meet through
+// distributed shared memory); same result on every run.
 //
 // Reference counterparts: native/families/deepseek_v41/cuda/v41_index_scores.cu:38 (scores; -inf on
 // invalid), v41_index_topk.cu:25-57 (deterministic ties, ascending output, -1 pad), the exported
@@ -18,8 +19,10 @@
 #include "cafd_api.h"
 #include "common.cuh"
 #include "host_tma.h"
+#include <cooperative_groups.h>
 
 namespace cafd {
+namespace cg = cooperative_groups;
 
 constexpr int kIdxD = 128;            // index head dim
 constexpr int kIdxN = 256;            // (token, head) columns per CTA
@@ -172,6 +175,7 @@ indexer_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
 // ---- top-k selection ---------------------------------------------------------------------------------
 constexpr int kTopkThreads = 1024;
+constexpr int kTopkMaxCluster = 8;
 
 __device__ __forceinline__ uint32_t score_key(float x) {
   if (!(x == x)) x = -INFINITY;                      // NaN never wins
@@ -179,8 +183,201 @@ __device__ __forceinline__ uint32_t score_key(float x) {
   return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
-// One block per query token.  The number of visible cached positions is limits[t] when given, else it is derived
-// from the batch description (token t of a sequence with q_len new tokens sees seq_len - q_len + t + 1 positions).
+// One thread-block cluster per query token (grid.x = cluster size C, grid.y = token): CTA r of the cluster owns the
+// contiguous slice r of the token's visible positions, warp w of the CTA a contiguous piece of the slice, which it walks
+// 32 positions at a time (coalesced loads; the order of positions is (step, lane)).  Every radix level each CTA counts
+// its slice into a 256-bin histogram in its own shared memory (a warp merges equal bins before it touches the counter,
+// so a row whose scores share their leading bits does not serialise on one address), the cluster meets at its barrier,
+// and every CTA adds up the C histograms through distributed shared memory and takes the same descent step.  The
+// ordered compaction at the end needs one more exchange: how many kept entries the lower slices hold.  A decode step
+// of a few sequences thus spreads each row over C SMs instead of one.
+// kInReg: the slice has at most 16 positions per thread; the keys are loaded once and stay in registers through the
+// four levels and the compaction.  Otherwise every pass streams the slice again (L2 hits after the first).
+// The number of visible cached positions is limits[t] when given, else it is derived from the batch description
+// (token t of a sequence with q_len new tokens sees seq_len - q_len + t + 1 positions).
+constexpr int kTopkRegKeys = 16;
+template <bool kInReg>
+__device__ __forceinline__ void index_topk_body(const float* __restrict__ x, int* __restrict__ o, int n, int top_k) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int C = static_cast<int>(cluster.num_blocks());
+  const int rank = static_cast<int>(cluster.block_rank());
+  __shared__ uint32_t hist[2][256];                  // by level parity: a level's counts stay readable while the next fills
+  __shared__ uint32_t total[256];
+  __shared__ int warp_gt[32], warp_eq[32];
+  __shared__ int cta_tot[2];                         // this slice's entries above the pivot / equal to it
+  __shared__ uint32_t s_pick, s_next;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  if (tid < 256) hist[0][tid] = 0;
+  __syncthreads();
+  const int slice = (n + C - 1) / C;
+  const int s_lo = min(n, rank * slice), s_hi = min(n, s_lo + slice);
+  const int piece = ((slice + 31) / 32 + 31) / 32 * 32;            // positions per warp, a multiple of 32
+  const int lo = min(s_hi, s_lo + warp * piece), hi = min(s_hi, lo + piece);
+  uint32_t keys[kInReg ? kTopkRegKeys : 1];
+  if constexpr (kInReg) {
+#pragma unroll
+    for (int u = 0; u < kTopkRegKeys; ++u) {
+      const int i = lo + 32 * u + lane;
+      keys[u] = i < hi ? score_key(x[i]) : 0u;
+    }
+  }
+  uint32_t prefix = 0, acc = 0;
+  const uint32_t target = static_cast<uint32_t>(top_k);
+  for (int level = 0; level < 4; ++level) {
+    const int shift = 24 - 8 * level;
+    uint32_t* h = hist[level & 1];
+    auto count = [&](uint32_t key, bool in) {        // called by whole warps
+      const bool valid = in && (level == 0 || (key >> (shift + 8)) == prefix);
+      const uint32_t bin = valid ? ((key >> shift) & 255u) : 256u;
+      const uint32_t same = __match_any_sync(0xffffffffu, bin);
+      if (valid && lane == __ffs(same) - 1) atomicAdd(&h[bin], static_cast<uint32_t>(__popc(same)));
+    };
+    if constexpr (kInReg) {
+#pragma unroll
+      for (int u = 0; u < kTopkRegKeys; ++u)
+        if (lo + 32 * u < hi) count(keys[u], lo + 32 * u + lane < hi);
+    } else {
+      for (int i0 = lo; i0 < hi; i0 += 128) {        // four loads in flight per thread
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + 32 * u + lane;
+          v[u] = i < hi ? x[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) count(score_key(v[u]), i0 + 32 * u + lane < hi);
+      }
+    }
+    cluster.sync();
+    if (tid < 256) {
+      // the other buffer was last read by the cluster one level ago, before every CTA arrived at the barrier just
+      // passed; the block barriers below order this store before the next level's counting
+      hist[(level + 1) & 1][tid] = 0;
+      uint32_t part[kTopkMaxCluster];
+#pragma unroll
+      for (int r = 0; r < kTopkMaxCluster; ++r) part[r] = r < C ? cluster.map_shared_rank(h, r)[tid] : 0u;
+      uint32_t tot = 0;
+#pragma unroll
+      for (int r = 0; r < kTopkMaxCluster; ++r) tot += part[r];
+      total[tid] = tot;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      // lane l holds bins 8l .. 8l + 7: suffix sums inside the lane, then over the lanes above it
+      uint32_t sfx[8], run = 0;
+#pragma unroll
+      for (int j = 7; j >= 0; --j) { run += total[lane * 8 + j]; sfx[j] = run; }
+      uint32_t incl = run;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t up = __shfl_down_sync(0xffffffffu, incl, d);
+        if (lane + d < 32) incl += up;
+      }
+      const uint32_t above = acc + incl - run;       // taken so far + everything in the bins of higher lanes
+      int found = -1;
+      uint32_t nxt = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t here = above + sfx[j], beyond = above + (j < 7 ? sfx[j + 1] : 0u);
+        if (here >= target && beyond < target) { found = j; nxt = beyond - acc; }
+      }
+      const uint32_t who = __ballot_sync(0xffffffffu, found >= 0);
+      if (who && lane == __ffs(who) - 1) { s_pick = static_cast<uint32_t>(lane * 8 + found); s_next = nxt; }
+      if (!who && lane == 0) { s_pick = 0; s_next = 0; }
+    }
+    __syncthreads();
+    acc += s_next;
+    prefix = (prefix << 8) | s_pick;
+  }
+  const uint32_t pv = prefix;
+  const int need = static_cast<int>(target - acc);          // ties of the pivot value to keep (lowest positions)
+  // Ordered compaction: counts per warp first, exclusive over warps and over the lower CTAs of the cluster, then the
+  // same walk writes.
+  int gt = 0, eq = 0;
+  if constexpr (kInReg) {
+#pragma unroll
+    for (int u = 0; u < kTopkRegKeys; ++u) {
+      if (lo + 32 * u < hi) {
+        const bool in = lo + 32 * u + lane < hi;
+        gt += __popc(__ballot_sync(0xffffffffu, in && keys[u] > pv));
+        eq += __popc(__ballot_sync(0xffffffffu, in && keys[u] == pv));
+      }
+    }
+  } else {
+    for (int i0 = lo; i0 < hi; i0 += 128) {
+      uint32_t key[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + 32 * u + lane;
+        key[u] = i < hi ? score_key(x[i]) : 0u;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const bool in = i0 + 32 * u + lane < hi;
+        gt += __popc(__ballot_sync(0xffffffffu, in && key[u] > pv));
+        eq += __popc(__ballot_sync(0xffffffffu, in && key[u] == pv));
+      }
+    }
+  }
+  if (lane == 0) { warp_gt[warp] = gt; warp_eq[warp] = eq; }
+  __syncthreads();
+  if (warp == 0) {
+    int a = warp_gt[lane], b = warp_eq[lane];
+    const int a0 = a, b0 = b;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int ua = __shfl_up_sync(0xffffffffu, a, d), ub = __shfl_up_sync(0xffffffffu, b, d);
+      if (lane >= d) { a += ua; b += ub; }
+    }
+    warp_gt[lane] = a - a0;                           // exclusive over warps
+    warp_eq[lane] = b - b0;
+    if (lane == 31) { cta_tot[0] = a; cta_tot[1] = b; }
+  }
+  __syncthreads();
+  cluster.sync();
+  int gt_before = warp_gt[warp], eq_before = warp_eq[warp];
+  {
+    int og[kTopkMaxCluster], oe[kTopkMaxCluster];
+#pragma unroll
+    for (int r = 0; r < kTopkMaxCluster; ++r) {
+      const int* other = cluster.map_shared_rank(cta_tot, r < rank ? r : rank);
+      og[r] = r < rank ? other[0] : 0;
+      oe[r] = r < rank ? other[1] : 0;
+    }
+#pragma unroll
+    for (int r = 0; r < kTopkMaxCluster; ++r) { gt_before += og[r]; eq_before += oe[r]; }
+  }
+  int w = gt_before + min(eq_before, need);
+  auto place = [&](uint32_t key, int i) {             // called by whole warps
+    const bool in = i < hi;
+    const bool is_eq = in && key == pv;
+    const uint32_t eq_mask = __ballot_sync(0xffffffffu, is_eq);
+    const bool keep = in && (key > pv || (is_eq && eq_before + __popc(eq_mask & lt_mask) < need));
+    const uint32_t keep_mask = __ballot_sync(0xffffffffu, keep);
+    if (keep) o[w + __popc(keep_mask & lt_mask)] = i;
+    w += __popc(keep_mask);
+    eq_before += __popc(eq_mask);
+  };
+  if constexpr (kInReg) {
+#pragma unroll
+    for (int u = 0; u < kTopkRegKeys; ++u)
+      if (lo + 32 * u < hi) place(keys[u], lo + 32 * u + lane);
+  } else {
+    for (int i0 = lo; i0 < hi; i0 += 128) {
+      uint32_t key[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + 32 * u + lane;
+        key[u] = i < hi ? score_key(x[i]) : 0u;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) place(key[u], i0 + 32 * u + lane);
+    }
+  }
+  cluster.sync();                                     // no CTA leaves while another may still read its totals
+}
+
 __global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const float* __restrict__ scores, int ld,
                                                                   const int* __restrict__ limits,
                                                                   const int* __restrict__ seq_lens,
@@ -188,15 +385,10 @@ __global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const float* _
                                                                   int* __restrict__ out) {
   pdl_wait();
   pdl_trigger();
-  __shared__ uint32_t hist[256];
-  __shared__ uint32_t suffix[256];
-  __shared__ int cnt_gt[kTopkThreads];
-  __shared__ int cnt_eq[kTopkThreads];
-  __shared__ int pick;
-  const int t = blockIdx.x, tid = threadIdx.x;
+  __shared__ int s_limit;
+  const int t = blockIdx.y, tid = threadIdx.x;
   const float* x = scores + static_cast<size_t>(t) * ld;
   int* o = out + static_cast<size_t>(t) * top_k;
-  __shared__ int s_limit;
   if (tid == 0) {
     int lim = 0;
     if (limits) {
@@ -209,70 +401,16 @@ __global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(const float* _
   }
   __syncthreads();
   const int n = max(0, min(s_limit, ld));
+  const int C = static_cast<int>(cg::this_cluster().num_blocks());
+  // every branch below is taken by all CTAs of the cluster alike (it depends on the token only), so nobody is left
+  // waiting at a cluster barrier
   if (n <= top_k) {
-    for (int i = tid; i < top_k; i += kTopkThreads) o[i] = i < n ? i : -1;
+    if (cg::this_cluster().block_rank() == 0)
+      for (int i = tid; i < top_k; i += kTopkThreads) o[i] = i < n ? i : -1;
     return;
   }
-  uint32_t prefix = 0, acc = 0;
-  const uint32_t target = static_cast<uint32_t>(top_k);
-  for (int level = 0; level < 4; ++level) {
-    const int shift = 24 - 8 * level;
-    if (tid < 256) hist[tid] = 0;
-    __syncthreads();
-    for (int i = tid; i < n; i += kTopkThreads) {
-      const uint32_t key = score_key(x[i]);
-      if (level > 0 && (key >> (shift + 8)) != prefix) continue;
-      atomicAdd(&hist[(key >> shift) & 255u], 1u);
-    }
-    __syncthreads();
-    if (tid < 256) suffix[tid] = hist[tid];
-    __syncthreads();
-    for (int d = 1; d < 256; d <<= 1) {
-      uint32_t add = 0;
-      if (tid < 256 && tid + d < 256) add = suffix[tid + d];
-      __syncthreads();
-      if (tid < 256) suffix[tid] += add;
-      __syncthreads();
-    }
-    if (tid == 0) pick = 0;
-    __syncthreads();
-    if (tid < 256) {
-      const bool here = acc + suffix[tid] >= target;
-      const bool above = tid < 255 && acc + suffix[tid + 1] >= target;
-      if (here && !above) pick = tid;
-    }
-    __syncthreads();
-    const int b = pick;
-    acc += (b < 255) ? suffix[b + 1] : 0u;
-    prefix = (prefix << 8) | static_cast<uint32_t>(b);
-    __syncthreads();
-  }
-  const uint32_t v = prefix;
-  const int need = static_cast<int>(target - acc);          // ties of the pivot value to keep (lowest positions)
-  const int chunk = (n + kTopkThreads - 1) / kTopkThreads;
-  const int lo = tid * chunk, hi = min(n, lo + chunk);
-  int gt = 0, eq = 0;
-  for (int i = lo; i < hi; ++i) {
-    const uint32_t key = score_key(x[i]);
-    gt += key > v;
-    eq += key == v;
-  }
-  cnt_gt[tid] = gt; cnt_eq[tid] = eq;
-  __syncthreads();
-  for (int d = 1; d < kTopkThreads; d <<= 1) {
-    int a = 0, b = 0;
-    if (tid >= d) { a = cnt_gt[tid - d]; b = cnt_eq[tid - d]; }
-    __syncthreads();
-    cnt_gt[tid] += a; cnt_eq[tid] += b;
-    __syncthreads();
-  }
-  int eq_before = cnt_eq[tid] - eq;
-  int w = (cnt_gt[tid] - gt) + min(eq_before, need);
-  for (int i = lo; i < hi; ++i) {
-    const uint32_t key = score_key(x[i]);
-    if (key > v) o[w++] = i;
-    else if (key == v) { if (eq_before < need) o[w++] = i; ++eq_before; }
-  }
+  if (n <= kTopkRegKeys * kTopkThreads * C) index_topk_body<true>(x, o, n, top_k);
+  else index_topk_body<false>(x, o, n, top_k);
 }
 
 // k_idx rows [T, 128] bf16 -> paged index-key cache [pages, 64, 128] at slots[t]
@@ -327,8 +465,25 @@ extern "C" int cafd_index_topk(const float* scores, int ld, const int* limits, c
                                int T, int top_k, int* out, cafd_stream_t s) {
   if (T <= 0) return 0;
   if (top_k < 1 || (!limits && (!seq_lens || !q_start))) return -10;
-  launch_pdl(index_topk_kernel, dim3(T), dim3(kTopkThreads), 0, static_cast<cudaStream_t>(s), scores, ld, limits, seq_lens, q_start,
-             S, top_k, out);
+  // CTAs per token: spread a few long rows over the SMs, one CTA per row once the rows alone fill them
+  int C = 1;
+  while (C < kTopkMaxCluster && T * C * 2 <= 148 && ld / (C * 2) >= 2048) C *= 2;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(C, T);
+  cfg.blockDim = dim3(kTopkThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = static_cast<cudaStream_t>(s);
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = C;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  CAFD_CHECK_CUDA(cudaLaunchKernelEx(&cfg, index_topk_kernel, scores, ld, limits, seq_lens, q_start, S, top_k, out));
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -72,8 +72,8 @@ def _topk_ref(row, n, k):
         return list(range(n)) + [-1] * (k - n)
     x = row[:n].clone()
     x[torch.isnan(x)] = float("-inf")
-    order = sorted(range(n), key=lambda i: (-x[i].item(), i))[:k]
-    return sorted(order)
+    order = torch.sort(x, descending=True, stable=True).indices[:k]       # stable: equal scores keep the lower position first
+    return sorted(order.tolist())
 
 
 def test_index_topk(K):
@@ -91,6 +91,28 @@ def test_index_topk(K):
     torch.cuda.synchronize()
     got = out.cpu().tolist()
     for t in range(T):
+        assert got[t] == _topk_ref(scores[t], limits[t], k), t
+
+
+@pytest.mark.parametrize("T,ld", [(6, 40000), (40, 40000), (20, 70000)])
+def test_index_topk_over_a_cluster(K, T, ld):
+    """Rows long enough for the selection to spread one row over a cluster of CTAs (6 rows: eight CTAs each, keys in
+    registers; 40 rows: one CTA each, streamed; 20 rows of 70000: four CTAs each, streamed): slices that end inside the
+    row, a row shorter than the request, ties across slice borders, an all-equal row."""
+    g = torch.Generator().manual_seed(1)
+    k = 2048
+    scores = torch.randn(T, ld, generator=g)
+    scores[1] = torch.round(scores[1] * 4) / 4
+    scores[2] = 0.5
+    scores[3, ::2] = float("-inf")
+    scores[5] = torch.relu(scores[5]) * 1e-3            # most entries zero, the rest in a narrow range
+    limits = [ld, ld - 1, ld - 7000, ld // 2 + 11, 2048, 9000] + [ld - 13 * i for i in range(T - 6)]
+    out = torch.full((T, k), -9, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        K.index_topk(scores.to(DEV), k, out, limits=torch.tensor(limits, dtype=torch.int32, device=DEV))
+    torch.cuda.synchronize()
+    got = out.cpu().tolist()
+    for t in list(range(6)) + list(range(6, T, 7)):
         assert got[t] == _topk_ref(scores[t], limits[t], k), t
 
 
