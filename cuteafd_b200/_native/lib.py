@@ -148,6 +148,8 @@ def cuda_lib():
         _sig(lib, "cafd_attn_decode", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P])
         _sig(lib, "cafd_attn_decode_partial", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P])
         _sig(lib, "cafd_attn_merge", [P, P, P, I, I, I, I, I, P])
+        _sig(lib, "cafd_set_fixed_kv_split", [I])
+        _sig(lib, "cafd_fixed_kv_split", [])
         _sig(lib, "cafd_attn_prefill", [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P])
         _sig(lib, "cafd_mla_scratch_floats", [I, I], C.c_longlong)
         _sig(lib, "cafd_mla_attention", [P, P, P, P, P, P, P, P, P, P, C.c_longlong, I, I, I, I, I, I, F, P, I, P])

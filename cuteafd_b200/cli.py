@@ -99,6 +99,8 @@ def cmd_plan(a: argparse.Namespace) -> int:
 
 def cmd_serve(a: argparse.Namespace) -> int:
     from .serve.server import run_server
+    if getattr(a, "batch_invariant", False):
+        os.environ["CAFD_BATCH_INVARIANT"] = "1"         # read by the engines when they are built
     return run_server(a)
 
 
@@ -411,6 +413,9 @@ def _build_parser() -> argparse.ArgumentParser:
     s.add_argument("--queue-depth", type=int, default=64); s.add_argument("--queue-wait", type=float, default=30.0)
     s.add_argument("--fake-engine", action="store_true", help="serve with the CPU oracle engine (no GPU)")
     s.add_argument("--usage-db", default=""); s.add_argument("--memory-spool", default="", help="file opened at start-up that receives the ledger's state when an allocation fails"); s.add_argument("--kv-format", default="auto", choices=["auto", "bf16", "fp8_ds_mla"])
+    s.add_argument("--batch-invariant", action="store_true", default=os.environ.get("CAFD_BATCH_INVARIANT", "0") == "1",
+                   help="a row's output bits do not depend on what else is in a decode step (up to 64 rows): kv splits of a fixed "
+                        "1024 tokens instead of an even division that fills the GPU, one absorb route for every MLA decode width")
     s.add_argument("--embedding-placement", default="gpu", choices=["gpu", "host"],
                    help="host: the token embedding table stays memory-mapped in host RAM and each step's rows are gathered and uploaded")
     s.add_argument("--host-cache-gib", type=float, default=float(os.environ.get("CUTEAFD_HOST_CACHE_GIB", "4")),

@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ page_table, const int* __restrict__ seq_lens,
     const int* __restrict__ q_start, __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int max_pages,
-    int Hq, int Hkv, int tiles_per_seq, int splits, float scale_log2, const int* __restrict__ kv_base, int window,
+    int Hq, int Hkv, int tiles_per_seq, int splits, float scale_log2, const int* __restrict__ kv_base, int window, int split_pages,
     const AttnPeers peers) {
   pdl_wait();
   pdl_trigger();
@@ -123,9 +123,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
   // pages [first_page, total_pages) hold every position some row of the tile sees; the splits share them
   const int total_pages = (max_limit + kPage - 1) / kPage;
   const int first_page = min(min_lo / kPage, total_pages);
-  const int per_split = (total_pages - first_page + splits - 1) / splits;
-  const int p0 = first_page + split * per_split;
-  const int p1 = min(total_pages, p0 + per_split);
+  // split_pages > 0: split s owns pages [s * split_pages, (s + 1) * split_pages) of every sequence, whatever the step holds
+  const int per_split = split_pages > 0 ? split_pages : (total_pages - first_page + splits - 1) / splits;
+  const int p0 = split_pages > 0 ? max(first_page, split * split_pages) : first_page + split * per_split;
+  const int p1 = min(total_pages, (split_pages > 0 ? split * split_pages : p0) + per_split);
 
   float m_run[2] = {-INFINITY, -INFINITY};
   float l_run[2] = {0.f, 0.f};
@@ -304,6 +305,15 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict
 
 using namespace cafd;
 
+// tokens per kv split for every decode attention kernel of the library (GQA and MLA); 0 = even division.  A multiple
+// of 64.
+extern "C" int cafd_set_fixed_kv_split(int tokens) {
+  if (tokens < 0 || tokens % kPage) return -10;
+  fixed_kv_split_tokens() = tokens;
+  return 0;
+}
+extern "C" int cafd_fixed_kv_split() { return fixed_kv_split_tokens(); }
+
 extern "C" long long cafd_attn_decode_scratch_floats(int num_seqs, int tiles_per_seq, int Hkv, int splits) {
   return static_cast<long long>(num_seqs) * tiles_per_seq * Hkv * splits * kPartialFloats;
 }
@@ -321,6 +331,8 @@ extern "C" int cafd_attn_decode(const void* q, const void* k_cache, const void* 
   if (group > 16 || 16 % group) return -11;
   if (splits < 1) splits = 1;
   if (splits > 1 && !scratch) return -12;
+  // fixed-size splits must cover the widest sequence the page table can describe
+  if (fixed_kv_split_tokens() > 0 && static_cast<long long>(splits) * fixed_kv_split_tokens() < static_cast<long long>(max_pages) * kPage) return -14;
   const int q_per_tile = 16 / group;
   const int tiles_per_seq = (max_q_len + q_per_tile - 1) / q_per_tile;
   cudaStream_t st = static_cast<cudaStream_t>(s);
@@ -335,7 +347,7 @@ extern "C" int cafd_attn_decode(const void* q, const void* k_cache, const void* 
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
       static_cast<const __nv_bfloat16*>(v_cache), page_table, seq_lens, q_start, static_cast<__nv_bfloat16*>(out),
       scratch, max_pages, Hq, Hkv, tiles_per_seq, splits, scale * 1.4426950408889634f, static_cast<const int*>(nullptr),
-      window, AttnPeers{});
+      window, fixed_kv_split_tokens() / kPage, AttnPeers{});
   if (splits > 1) {
     dim3 g2(num_seqs * tiles_per_seq, Hkv, 16);
     launch_pdl(attn_merge_kernel, g2, dim3(128), 0, st, scratch, q_start, static_cast<__nv_bfloat16*>(out), Hq, Hkv, tiles_per_seq,
@@ -376,7 +388,7 @@ extern "C" int cafd_attn_decode_partial(const void* q, const void* k_cache, cons
   launch_pdl(attn_decode_kernel, grid, dim3(128), smem, st, static_cast<const __nv_bfloat16*>(q),
              static_cast<const __nv_bfloat16*>(k_cache), static_cast<const __nv_bfloat16*>(v_cache), page_table, seq_lens, q_start,
              static_cast<__nv_bfloat16*>(nullptr), peers.scratch[my_rank], max_pages, Hq, Hkv, tiles_per_seq, splits,
-             scale * 1.4426950408889634f, kv_base, 0, peers);
+             scale * 1.4426950408889634f, kv_base, 0, 0, peers);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -378,6 +378,15 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
 }
 }  // namespace cafd
 
+// Batch-invariant kv splits.  0 (default): the decode attention kernels divide a sequence's kv range evenly over as
+// many splits as fill the GPU, so the summation order of a row depends on what else is in the step.  > 0: every split
+// covers this many tokens counted from position 0, whatever the step holds; a row's partials and their merge order then
+// depend on its own length only.  One value for the whole library (set through cafd_set_fixed_kv_split).
+inline int& fixed_kv_split_tokens() {
+  static int v = 0;
+  return v;
+}
+
 // Host-side error plumbing shared by the C entry points.
 #define CAFD_CHECK_CUDA(expr)                       \
   do {                                              \

@@ -47,6 +47,7 @@ struct MlaDev {
   uint32_t* status;
   uint32_t* trace;         // optional progress words, 4 per CTA (producer, MMA, softmax, exit); host-mapped memory works
   int max_pages, heads, splits;
+  int split_tiles;         // > 0: split s owns kv tiles [s * split_tiles, (s + 1) * split_tiles) of every block (batch-invariant form)
   int out_tpad;            // 0: out rows are (token, head); > 0: head-major rows head * out_tpad + token
   float scale_log2;
   // sparse mode (sparse_idx != null): every row block is ONE query token; its kv set is the first
@@ -98,7 +99,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int last_tok = min(tok0 + tok_per_blk, q_len) - 1;
   const int max_limit = sparse ? min(kv_len - q_len + last_tok + 1, p.sparse_k) : kv_len - q_len + last_tok + 1;
   const int total_tiles = (tok0 < q_len && max_limit > 0) ? (max_limit + kKvTile - 1) / kKvTile : 0;   // block past the new tokens: idle
-  const int per_split = (total_tiles + p.splits - 1) / p.splits;
+  const int per_split = p.split_tiles > 0 ? p.split_tiles : (total_tiles + p.splits - 1) / p.splits;
   const int t_begin = split * per_split;
   const int t_end = min(total_tiles, t_begin + per_split);
   const int n_tiles = max(0, t_end - t_begin);
@@ -497,6 +498,13 @@ static int mla_attention_impl(const void* q, const void* cache, const int* page_
   p.status = status;
   p.trace = g_mla_trace;
   p.max_pages = max_pages; p.heads = heads; p.splits = splits; p.out_tpad = out_tpad;
+  // (a sparse step's kv range is its selection: split s then owns selection slots, not cache positions)
+  p.split_tiles = splits > 1 ? fixed_kv_split_tokens() / kKvTile : 0;
+  {
+    long long widest = static_cast<long long>(max_pages) * 64;
+    if (sparse_idx && sparse_k < widest) widest = sparse_k;
+    if (p.split_tiles > 0 && static_cast<long long>(splits) * fixed_kv_split_tokens() < widest) return -14;
+  }
   p.scale_log2 = scale * 1.4426950408889634f;
   p.sparse_idx = sparse_idx; p.sparse_k = sparse_k; p.cache = static_cast<const uint8_t*>(cache);
   p.gathered = gathered;

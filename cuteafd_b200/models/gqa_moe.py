@@ -232,6 +232,7 @@ class GqaMoeEngine:
                                   dtype=torch.float32, device=self.device)
         self.next_tokens = torch.empty(self.logits.shape[0], dtype=torch.int32, device=self.device)
         self._scratch: torch.Tensor | None = None
+        self.fixed_kv_split = K.batch_invariant_from_env()     # tokens per kv split in the batch-invariant form, else 0
         self.launches = 0
         self._f8_rows = {}
         # one-launch decode step (ops/decode_step.py): built lazily for the geometries it takes, single-GPU experts only
@@ -284,7 +285,7 @@ class GqaMoeEngine:
             S, max_pages = b.page_table.shape
             q_per_tile = 16 // (cfg.num_heads // cfg.num_kv_heads)
             tiles = (b.max_q_len + q_per_tile - 1) // q_per_tile
-            splits = K.attn_decode_splits(S, tiles, cfg.num_kv_heads, max_pages)
+            splits = K.kv_splits_fixed(max_pages) if self.fixed_kv_split else K.attn_decode_splits(S, tiles, cfg.num_kv_heads, max_pages)
             need = K.attn_decode_scratch_floats(S, b.max_q_len, cfg.num_heads, cfg.num_kv_heads, splits)
             if self._scratch is None or self._scratch.numel() < need:
                 self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)

@@ -228,6 +228,7 @@ class MlaMoeEngine(GqaMoeEngine):
         self.logits = torch.empty(min(max_seqs, max_tokens), cfg.vocab_size, dtype=torch.float32, device=dev)
         self.next_tokens = torch.empty(self.logits.shape[0], dtype=torch.int32, device=dev)
         self._scratch: torch.Tensor | None = None
+        self.fixed_kv_split = K.batch_invariant_from_env()     # tokens per kv split in the batch-invariant form, else 0
         self._tiles: dict[int, _HeadTiles] = {}
         self.select_hook = None      # callable(layer, selection [T, top_k]) for tests and traces (eager mode only)
         self._zero1 = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -270,7 +271,8 @@ class MlaMoeEngine(GqaMoeEngine):
         self._linear(L, "wq_b", ws.q_a[:T] if ql else ws.x[:T], ws.q[:T])
         q_slab = ws.q_slab[:heads * ht.t_pad * 128].view(heads, ht.t_pad, 128)
         o_slab = ws.o_slab[:heads * ht.t_pad * 512].view(heads, ht.t_pad, 512)
-        small = T <= K.MLA_SMALL_ROWS and not expanded
+        # (the batch-invariant form keeps one absorb / un-absorb route for every decode width: the grouped GEMMs)
+        small = T <= K.MLA_SMALL_ROWS and not expanded and not self.fixed_kv_split
         if small:
             # decode-sized step: nope / rope split, RoPE and the absorb projection in one launch
             K.mla_absorb_small(ws.q[:T], L.w_uk, self.inv_freq, b.positions, ws.q_abs[:T], heads, cfg.rope_interleaved)
@@ -294,6 +296,8 @@ class MlaMoeEngine(GqaMoeEngine):
         nb = bseq.numel()
         tiles = (min(cfg.indexer_topk, max_pages * 64) // 32) if sel is not None else max_pages * 2
         splits = 1 if b.prefill else max(1, min(K.num_sms() // max(1, nb * 2), max(1, tiles // 8), 32))
+        if self.fixed_kv_split and not b.prefill:       # batch-invariant form: the split grid is a function of the table width only
+            splits = K.kv_splits_fixed((tiles + 1) // 2, cap=64)
         if splits > 1:
             need = K.mla_scratch_floats(nb, splits)
             if self._scratch is None or self._scratch.numel() < need:

@@ -350,6 +350,40 @@ def attn_decode_splits(num_seqs: int, tiles_per_seq: int, Hkv: int, max_pages: i
     return max(1, min(want, max(1, max_pages // 4), 32))
 
 
+def set_fixed_kv_split(tokens: int) -> None:
+    """Batch-invariant decode attention: > 0 makes every kv split of the decode kernels (GQA and dense MLA) cover
+    ``tokens`` positions (a multiple of 64) counted from position 0, so that a row's partial sums and their merge order
+    depend on its own length only; callers then launch ``kv_splits(max_pages)`` splits.  0 restores the even division
+    that fills the GPU.  Counterpart of the reference's fixed (warps, groups) K-walk at every decode width
+    (REPORT-kernel-210.md:14-66)."""
+    _n.check(_n.cuda_lib().cafd_set_fixed_kv_split(int(tokens)), "set_fixed_kv_split")
+
+
+def fixed_kv_split() -> int:
+    return int(_n.cuda_lib().cafd_fixed_kv_split())
+
+
+BATCH_INVARIANT_SPLIT = 1024     # tokens per kv split when CAFD_BATCH_INVARIANT=1 asks for the mode
+
+
+def batch_invariant_from_env() -> int:
+    """Engines call this once when they are built: ``CAFD_BATCH_INVARIANT=1`` switches the library to fixed kv splits
+    (unless a split size was set by hand) and returns the split size; without it the current setting is returned."""
+    import os
+    if os.environ.get("CAFD_BATCH_INVARIANT", "0") == "1" and fixed_kv_split() == 0:
+        set_fixed_kv_split(BATCH_INVARIANT_SPLIT)
+    return fixed_kv_split()
+
+
+def kv_splits_fixed(max_pages: int, cap: int = 0) -> int:
+    """Splits to launch in the fixed-split mode: enough to cover the widest row of the page table.  ``cap`` > 0: the
+    kernel's limit on the number of splits (the mode is refused when the table is wider than cap x split)."""
+    n = max(1, -(-max_pages * 64 // fixed_kv_split()))
+    if cap and n > cap:
+        raise ValueError(f"a page table of {max_pages} pages needs {n} kv splits of {fixed_kv_split()} tokens, the kernel takes {cap}")
+    return n
+
+
 def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
                 seq_lens: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor | None,
                 max_q_len: int, splits: int, scale: float | None = None, window: int = 0) -> torch.Tensor:

@@ -253,8 +253,15 @@ class EngineBackend:
         if self.host_embed is None:
             return
         n = host_tokens.numel()
+        sent = getattr(self, "_embed_sent", None)
+        if sent is not None:
+            sent.synchronize()              # the previous step's copy has read the staging rows
         self.host_embed.gather(host_tokens.numpy(), out=self._embed_stage[:n])
         self.engine.embed_rows[:n].copy_(self._embed_stage[:n], non_blocking=True)
+        if self._embed_stage.is_pinned():
+            if sent is None:
+                sent = self._embed_sent = torch.cuda.Event()
+            sent.record()
         if lookahead:
             self.host_embed.prefetch(lookahead)
 
@@ -536,8 +543,13 @@ class EngineBackend:
                          torch.zeros(3, n, dtype=torch.int32, device=self.engine.device),
                          torch.empty(n, 64, dtype=torch.uint8).pin_memory())
         dev_rec, dev_out, host_rec = self._sel
+        if getattr(self, "_rec_sent", None) is None:
+            self._rec_sent = torch.cuda.Event()
+        else:
+            self._rec_sent.synchronize()    # the previous step's copy has read the staging records
         host_rec[:T].copy_(rec)
         dev_rec[:T].copy_(host_rec[:T], non_blocking=True)
+        self._rec_sent.record()
         K.sample_rows(logits, dev_rec[:T], dev_out[0, :T], dev_out[1, :T])
         self.last_mtp = None
         if self.has_mtp:

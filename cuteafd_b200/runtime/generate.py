@@ -16,13 +16,22 @@ from .paged import PAGE, PagePool, Sequence, SequenceTable
 
 
 class StepBuffers:
-    """Pinned host staging + device buffers for one step shape (max T tokens, S sequences)."""
+    """Pinned host staging + device buffers for one step shape (max T tokens, S sequences).
+
+    Callers fill the ``[0]`` (host) views and call ``upload``.  The copy to the device is asynchronous, and the GPU may
+    be a whole prompt chunk behind the host, so the bytes it reads must not be the ones the caller fills next:
+    ``upload`` snapshots the staging into one of two pinned in-flight buffers (a host memcpy of a few KB) and copies
+    from there; an in-flight buffer is reused only after the copy that read it has completed."""
 
     def __init__(self, max_tokens: int, max_seqs: int, max_pages: int, device: torch.device):
         self.max_tokens, self.max_seqs, self.max_pages = max_tokens, max_seqs, max_pages
         n = 3 * max_tokens + max_seqs * max_pages + max_seqs + (max_seqs + 1) + max_seqs
         self.host = torch.zeros(n, dtype=torch.int32).pin_memory() if device.type == "cuda" else torch.zeros(n, dtype=torch.int32)
         self.dev = torch.zeros(n, dtype=torch.int32, device=device)
+        self._inflight = [torch.zeros(n, dtype=torch.int32).pin_memory() for _ in range(2)] if device.type == "cuda" else []
+        self._sent = [torch.cuda.Event() for _ in self._inflight]
+        self._recorded = [False] * len(self._inflight)
+        self._turn = 0
         o = 0
 
         def take(k: int):
@@ -37,7 +46,17 @@ class StepBuffers:
         self.bytes = n * 4
 
     def upload(self) -> int:
-        self.dev.copy_(self.host, non_blocking=True)
+        if not self._inflight:
+            self.dev.copy_(self.host)
+            return self.bytes
+        k = self._turn
+        self._turn = (k + 1) % len(self._inflight)
+        if self._recorded[k]:
+            self._sent[k].synchronize()               # the copy that last read this buffer (two uploads ago) is done
+        self._inflight[k].copy_(self.host)
+        self.dev.copy_(self._inflight[k], non_blocking=True)
+        self._sent[k].record()
+        self._recorded[k] = True
         return self.bytes
 
 

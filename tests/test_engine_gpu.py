@@ -482,3 +482,23 @@ def test_draft_model_on_the_gpu(parallel):
         assert drafter.passes <= cyc and acc >= cyc // 3           # position 1 of most blocks is the target's own pick
     else:
         assert acc >= 0.7 * prop                                   # the same model in another step shape: near-ties aside
+
+
+def test_step_staging_is_not_overwritten_before_its_copy_ran():
+    """The GPU can be a whole prompt chunk behind the host: what ``upload`` sends must be the values at the call, not
+    what the caller writes into the staging views for the next chunk while the copy is still queued."""
+    from cuteafd_b200.runtime.generate import StepBuffers
+    dev = torch.device("cuda:0")
+    b = StepBuffers(256, 1, 8, dev)
+    busy = torch.randn(4096, 4096, device=dev)
+    torch.cuda.synchronize()
+    for _ in range(60):                              # tens of milliseconds of queued work in front of the copies
+        busy = busy @ busy * 1e-3
+    seen = []
+    for chunk in range(4):
+        b.tokens[0][:] = chunk + 1
+        b.upload()
+        seen.append(b.tokens[1].clone())             # stream-ordered after this chunk's copy
+    b.tokens[0][:] = 99
+    torch.cuda.synchronize()
+    assert [int(t[0]) for t in seen] == [1, 2, 3, 4] and all(bool((t == t[0]).all()) for t in seen)
