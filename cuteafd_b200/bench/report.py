@@ -104,19 +104,28 @@ def from_panels(out: dict, *, family: str, checkpoint: str, hardware: str, profi
     return Report(family, checkpoint, hardware, profile, now(), build, config or {}, card, clocks, checks, out.get("panels", []))
 
 
-def from_bench_line(line: dict, *, family: str, checkpoint: str, profile: str = "card", build: str = "") -> Report:
-    """Report of the one-line JSON ``bench.py`` prints (the device-timed card of a random-init checkpoint)."""
+def from_bench_line(line: dict, *, family: str, checkpoint: str, profile: str = "card", build: str = "",
+                    hardware: str = "") -> Report:
+    """Report of the one-line JSON ``bench.py`` prints (the device-timed card of a random-init checkpoint): its
+    ``extra`` carries ``decode_tok_s_c<N>`` per concurrency, ``prefill_tok_s_8k`` and ``ttft_s_8k``."""
     cfg = line.get("config", {})
     extra = line.get("extra", {})
     n = int(line.get("n_gpus", 1))
-    card = {"prefill_tok_s": extra.get("prefill_tok_s"), "ttft_s": extra.get("ttft_s"),
-            "decode_tok_s": {k[len("decode_c"):-len("_tok_s")]: v for k, v in extra.items()
-                             if k.startswith("decode_c") and k.endswith("_tok_s") and "e2e" not in k}}
+
+    def first(*names):
+        return next((extra[k] for k in names if extra.get(k) is not None), None)
+    decode = {}
+    for k, v in extra.items():
+        for pre, suf in (("decode_tok_s_c", ""), ("decode_c", "_tok_s")):
+            if k.startswith(pre) and k.endswith(suf) and k[len(pre):len(k) - len(suf)].isdigit():
+                decode[k[len(pre):len(k) - len(suf)]] = v
+    card = {"prefill_tok_s": first("prefill_tok_s_8k", "prefill_tok_s"), "ttft_s": first("ttft_s_8k", "ttft_s"),
+            "decode_tok_s": dict(sorted(decode.items(), key=lambda kv: int(kv[0])))}
     if not card["decode_tok_s"]:
         card["decode_tok_s"] = {"headline": line.get("value")}
     checks = [asdict(Check("launches", bool(line.get("gpu_launches")), f"{line.get('gpu_launches')} kernel launches per step")),
               asdict(Check("e2e", bool((line.get("e2e") or {}).get("value")), "end-to-end number with host copies", gating=False))]
-    return Report(family, checkpoint, f"{n}gpu-{_slug(str(cfg.get('parallelism', 'single')))[:40]}", profile, now(), build, cfg, card,
+    return Report(family, checkpoint, hardware or f"{n}gpu-{_slug(str(cfg.get('parallelism', 'single')))[:40]}", profile, now(), build, cfg, card,
                   line.get("clocks") or {}, checks, [])
 
 

@@ -190,7 +190,8 @@ def cmd_bench(a: argparse.Namespace) -> int:
         with open(a.from_json) as f:
             line = json.loads([ln for ln in f.read().splitlines() if ln.strip().startswith("{")][-1])
         model = (line.get("config") or {}).get("model", "model")
-        rep = R.from_bench_line(line, family=a.family or model, checkpoint=a.checkpoint or model, profile=a.profile_name, build=_build_id())
+        rep = R.from_bench_line(line, family=a.family or model, checkpoint=a.checkpoint or model, profile=a.profile_name, build=_build_id(),
+                                hardware=a.hardware)
         print(json.dumps({"report": R.write_report(rep, a.report_root), "accepted": rep.accepted}))
         return 0
     if a.url:                                  # panels against a live server, over its HTTP API

@@ -42,6 +42,14 @@ def test_report_from_bench_line_and_card(tmp_path):
         R.Report.from_json({"schema": "other"})
 
 
+def test_report_reads_the_keys_bench_py_prints():
+    line = dict(LINE, n_gpus=1, extra={"decode_tok_s_c1": 207.1, "decode_tok_s_c8": 857.0, "decode_tok_s_c32": 1745.4,
+                                       "e2e_decode_tok_s_c8": 840.0, "prefill_tok_s_8k": 85714.6, "ttft_s_8k": 0.0956})
+    rep = R.from_bench_line(line, family="qwen3_moe", checkpoint="c", hardware="1gpu")
+    assert rep.hardware == "1gpu" and rep.card == {"prefill_tok_s": 85714.6, "ttft_s": 0.0956,
+                                                   "decode_tok_s": {"1": 207.1, "8": 857.0, "32": 1745.4}}
+
+
 def test_report_from_panels():
     out = {"url": "u", "ok": False, "panels": [
         {"panel": "smoke", "ok": True, "seconds": 1.0}, {"panel": "lossless", "ok": False, "error": "ids differ", "seconds": 2.0},
