@@ -159,6 +159,8 @@ def cuda_lib():
         _sig(lib, "cafd_mla_prep_a", [P, I, I, P, P, P, P, P, P, P, I, F, I, P, P])
         _sig(lib, "cafd_mla_prep_a_fp8", [P, I, I, P, P, P, P, P, P, P, I, F, I, P, P])
         _sig(lib, "cafd_mla_fp8_gather", [P, P, I, P, I, P, P, P, P, I, P, P])
+        _sig(lib, "cafd_mla_attention_partial", [P, P, P, P, P, P, P, P, P, I, I, P, C.c_longlong, I, I, I, I, I, F, P])
+        _sig(lib, "cafd_mla_merge", [P, P, P, P, P, I, I, I, I, P])
         _sig(lib, "cafd_mla_attention_gathered", [P, P, P, P, P, P, P, P, P, P, C.c_longlong, I, I, I, I, I, F, P, I, P])
         _sig(lib, "cafd_attn_prefill_mla", [P, I, P, I, I, P, P, C.c_longlong, P, P, P, P, P, P, P, I, I, I, I, I, I, F, P])
         _sig(lib, "cafd_gemm_w4", [C.POINTER(GemmArgs), I, P, P, P])

@@ -58,6 +58,12 @@ struct MlaDev {
   // gathered mode: `cache` is a bf16 buffer [n_blocks, sparse_k, 576] that already holds entry e of block b at
   // row b * sparse_k + e (written by mla_fp8_gather from FP8 records); sparse_idx still says which entries exist.
   int gathered;
+  // context split (n_peers > 0): this rank holds a share of every sequence's pages; seq_lens are local lengths, query
+  // token i of a sequence sees the first min(local length, kv_base[seq] + i + 1) local positions, and the partials go
+  // into every rank's scratch at split slots [split_offset, split_offset + splits) of total_splits
+  const int* kv_base;
+  float* peer_partial[8];
+  int n_peers, split_offset, total_splits;
 };
 
 // Shared-memory descriptor without swizzle (canonical K-major "interleave" layout): 8x16-byte core
@@ -97,7 +103,8 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int tok_per_blk = sparse ? 1 : kMlaRows / p.heads;
   // visible kv positions for the last valid token of this block
   const int last_tok = min(tok0 + tok_per_blk, q_len) - 1;
-  const int max_limit = sparse ? min(kv_len - q_len + last_tok + 1, p.sparse_k) : kv_len - q_len + last_tok + 1;
+  const int base_vis = p.kv_base ? p.kv_base[seq] : kv_len - q_len;
+  const int max_limit = sparse ? min(kv_len - q_len + last_tok + 1, p.sparse_k) : min(kv_len, base_vis + last_tok + 1);
   const int total_tiles = (tok0 < q_len && max_limit > 0) ? (max_limit + kKvTile - 1) / kKvTile : 0;   // block past the new tokens: idle
   const int per_split = p.split_tiles > 0 ? p.split_tiles : (total_tiles + p.splits - 1) / p.splits;
   const int t_begin = split * per_split;
@@ -259,7 +266,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int row = quad * 32 + lane;
     const int ti = row / p.heads;
     const bool row_valid = (tok0 + ti) < q_len && ti < tok_per_blk;
-    const int limit = !row_valid ? 0 : sparse ? max_limit : (kv_len - q_len + tok0 + ti + 1);
+    const int limit = !row_valid ? 0 : sparse ? max_limit : min(kv_len, base_vis + tok0 + ti + 1);
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
@@ -332,7 +339,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tc_fence_after();
     const size_t grow = p.out_tpad > 0 ? static_cast<size_t>(row % p.heads) * p.out_tpad + (q0 + tok0 + ti)
                                        : static_cast<size_t>(q0 + tok0) * p.heads + row;
-    if (p.splits == 1) {
+    if (p.splits == 1 && p.n_peers == 0) {
       // tcgen05.ld is warp-collective: every lane loads, only valid rows store
       const float inv = (have && l_run > 0.f) ? 1.0f / l_run : 0.f;
       __nv_bfloat16* orow = p.out + grow * kLat + dh * kHalf;
@@ -354,17 +361,26 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
     } else {
-      float* part = p.partial + ((static_cast<size_t>(blk) * 2 + dh) * p.splits + split) * kMlaPartial;
       const bool have_all = __all_sync(0xffffffffu, have);
+      const int n_dst = p.n_peers > 0 ? p.n_peers : 1;
+      const size_t part_off = p.n_peers > 0
+          ? ((static_cast<size_t>(blk) * 2 + dh) * p.total_splits + p.split_offset + split) * kMlaPartial
+          : ((static_cast<size_t>(blk) * 2 + dh) * p.splits + split) * kMlaPartial;
 #pragma unroll 1
       for (int c = 0; c < kHalf; c += 32) {
         uint32_t o[32];
         if (have_all) { tmem_ld_32x32(tO + lane_off + c, o); tmem_ld_wait(); }
+        for (int d = 0; d < n_dst; ++d) {               // plain (peer) stores; the flag that publishes them follows in stream order
+          float* part = (p.n_peers > 0 ? p.peer_partial[d] : p.partial) + part_off;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) part[static_cast<size_t>(c + i) * kMlaRows + row] = have_all ? __uint_as_float(o[i]) : 0.f;
+          for (int i = 0; i < 32; ++i) part[static_cast<size_t>(c + i) * kMlaRows + row] = have_all ? __uint_as_float(o[i]) : 0.f;
+        }
       }
-      part[kMlaRows * kHalf + row] = have_all ? m_run : -INFINITY;
-      part[kMlaRows * kHalf + kMlaRows + row] = have_all ? l_run : 0.f;
+      for (int d = 0; d < n_dst; ++d) {
+        float* part = (p.n_peers > 0 ? p.peer_partial[d] : p.partial) + part_off;
+        part[kMlaRows * kHalf + row] = have_all ? m_run : -INFINITY;
+        part[kMlaRows * kHalf + kMlaRows + row] = have_all ? l_run : 0.f;
+      }
     }
   }
   tc_fence_before();
@@ -477,12 +493,14 @@ static int mla_attention_impl(const void* q, const void* cache, const int* page_
                               const int* q_start, const int* block_seq, const int* block_tok0, void* out,
                               float* scratch, uint32_t* status, long long total_rows, int n_blocks, int num_pages,
                               int max_pages, int heads, int splits, int out_tpad, float scale,
-                              const int* sparse_idx, int sparse_k, int gathered, cafd_stream_t s) {
+                              const int* sparse_idx, int sparse_k, int gathered, cafd_stream_t s,
+                              const int* kv_base = nullptr, void* const* peer_scratch = nullptr, int n_peers = 0, int my_rank = 0) {
   if (n_blocks <= 0) return 0;
   if (heads <= 0 || kMlaRows % heads) return -10;
   if (splits < 1) splits = 1;
   if (splits > kMaxSplits) return -13;
-  if (splits > 1 && !scratch) return -12;
+  if (splits > 1 && !scratch && !n_peers) return -12;
+  if (n_peers < 0 || n_peers > 8 || (n_peers && (!peer_scratch || my_rank < 0 || my_rank >= n_peers || sparse_idx || splits * n_peers > kMaxSplits))) return -15;
   CUtensorMap tq, tc;
   int rc = cached_tmap_2d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, total_rows, kRec, kRec * 2, kMlaRows, 64);
   if (rc) return rc;
@@ -499,7 +517,8 @@ static int mla_attention_impl(const void* q, const void* cache, const int* page_
   p.trace = g_mla_trace;
   p.max_pages = max_pages; p.heads = heads; p.splits = splits; p.out_tpad = out_tpad;
   // (a sparse step's kv range is its selection: split s then owns selection slots, not cache positions)
-  p.split_tiles = splits > 1 ? fixed_kv_split_tokens() / kKvTile : 0;
+  // (context split: the ranks' shares are already a fixed cut of the sequence, and each share is divided evenly)
+  p.split_tiles = (splits > 1 && !n_peers) ? fixed_kv_split_tokens() / kKvTile : 0;
   {
     long long widest = static_cast<long long>(max_pages) * 64;
     if (sparse_idx && sparse_k < widest) widest = sparse_k;
@@ -508,6 +527,13 @@ static int mla_attention_impl(const void* q, const void* cache, const int* page_
   p.scale_log2 = scale * 1.4426950408889634f;
   p.sparse_idx = sparse_idx; p.sparse_k = sparse_k; p.cache = static_cast<const uint8_t*>(cache);
   p.gathered = gathered;
+  p.kv_base = kv_base;
+  p.n_peers = n_peers; p.split_offset = my_rank * splits; p.total_splits = n_peers * splits;
+  for (int r = 0; r < 8; ++r) p.peer_partial[r] = nullptr;
+  for (int r = 0; r < n_peers; ++r) {
+    if (!peer_scratch[r]) return -15;
+    p.peer_partial[r] = static_cast<float*>(peer_scratch[r]);
+  }
   static bool attr = false;
   if (!attr) {
     CAFD_CHECK_CUDA(cudaFuncSetAttribute(mla_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));
@@ -515,7 +541,7 @@ static int mla_attention_impl(const void* q, const void* cache, const int* page_
   }
   cudaStream_t st = static_cast<cudaStream_t>(s);
   launch_pdl(mla_attn_kernel, dim3(n_blocks, 2, splits), dim3(kMlaThreads), kMlaSmem, st, tq, tc, p);
-  if (splits > 1)
+  if (splits > 1 && !n_peers)
     launch_pdl(mla_merge_kernel, dim3(n_blocks, 2, kHalf / kMergeCols), dim3(kMlaRows * kMergeGroups), 0, st, static_cast<const float*>(scratch), block_seq,
                block_tok0, q_start, static_cast<__nv_bfloat16*>(out), heads, splits, out_tpad, sparse_idx ? 1 : 0);
   return static_cast<int>(cudaGetLastError());
@@ -542,6 +568,32 @@ extern "C" int cafd_mla_attention_gathered(const void* q, const void* gathered, 
   if (pages < 1) return -10;
   return mla_attention_impl(q, gathered, page_table, seq_lens, q_start, block_seq, block_tok0, out, scratch, status, total_rows,
                             n_blocks, pages, max_pages, heads, splits, out_tpad, scale, sparse_idx, sparse_k, 1, s);
+}
+
+// Context-split form, first half: absorbed attention over this rank's share of the pages (seq_lens = local lengths,
+// kv_base = visibility bases), the unnormalised partials stored into the scratch of every rank of the group
+// (peer_scratch[r], this rank's own included) at split slots [my_rank * splits, (my_rank + 1) * splits) of
+// n_peers * splits.  The caller publishes the stores with a flag per peer and merges with cafd_mla_merge once every
+// rank's flag has arrived.
+extern "C" int cafd_mla_attention_partial(const void* q, const void* cache, const int* page_table, const int* seq_lens,
+                                          const int* kv_base, const int* q_start, const int* block_seq, const int* block_tok0,
+                                          void* const* peer_scratch, int n_peers, int my_rank, uint32_t* status,
+                                          long long total_rows, int n_blocks, int num_pages, int max_pages, int heads, int splits,
+                                          float scale, cafd_stream_t s) {
+  if (!kv_base || n_peers < 1) return -15;
+  return mla_attention_impl(q, cache, page_table, seq_lens, q_start, block_seq, block_tok0, nullptr, nullptr, status, total_rows,
+                            n_blocks, num_pages, max_pages, heads, splits, 0, scale, nullptr, 0, 0, s, kv_base, peer_scratch, n_peers,
+                            my_rank);
+}
+
+// Second half: merge total_splits partials per (row block, output half) from this rank's scratch in slot order.
+extern "C" int cafd_mla_merge(const float* scratch, const int* block_seq, const int* block_tok0, const int* q_start, void* out,
+                              int n_blocks, int heads, int total_splits, int out_tpad, cafd_stream_t s) {
+  if (n_blocks <= 0) return 0;
+  if (!scratch || total_splits < 1 || total_splits > kMaxSplits || heads <= 0 || kMlaRows % heads) return -10;
+  launch_pdl(mla_merge_kernel, dim3(n_blocks, 2, kHalf / kMergeCols), dim3(kMlaRows * kMergeGroups), 0, static_cast<cudaStream_t>(s), scratch,
+             block_seq, block_tok0, q_start, static_cast<__nv_bfloat16*>(out), heads, total_splits, out_tpad, 0);
+  return static_cast<int>(cudaGetLastError());
 }
 
 CAFD_WAIT_LIMIT_SETTER(cafd_mla_set_wait_limit_ns)

@@ -229,6 +229,7 @@ class MlaMoeEngine(GqaMoeEngine):
         self.next_tokens = torch.empty(self.logits.shape[0], dtype=torch.int32, device=dev)
         self._scratch: torch.Tensor | None = None
         self.fixed_kv_split = K.batch_invariant_from_env()     # tokens per kv split in the batch-invariant form, else 0
+        self.kv_exchange = None                                # context split: parallel.context_split.DeviceContextSplit
         self._tiles: dict[int, _HeadTiles] = {}
         self.select_hook = None      # callable(layer, selection [T, top_k]) for tests and traces (eager mode only)
         self._zero1 = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -294,6 +295,13 @@ class MlaMoeEngine(GqaMoeEngine):
         sel = self._select(i, T, b) if cfg.indexer_heads else None
         bseq, btok = self._block_table(S, b.max_q_len, 1 if sel is not None else None)
         nb = bseq.numel()
+        if self.kv_exchange is not None:
+            # context split: this rank holds a share of every sequence's records; partials meet in every rank's scratch
+            self.kv_exchange.attend_mla(ws.q_abs[:T], self.kv.c[i], b.page_table, b.seq_lens, b.kv_base, b.q_start, bseq, btok,
+                                        o_slab, self.scale, ht.t_pad)
+            self._unabsorb(L, T, small, o_slab, ht)
+            self.launches += (7 if small else 8) + 2 + self.kv_exchange.ranks
+            return
         tiles = (min(cfg.indexer_topk, max_pages * 64) // 32) if sel is not None else max_pages * 2
         splits = 1 if b.prefill else max(1, min(K.num_sms() // max(1, nb * 2), max(1, tiles // 8), 32))
         if self.fixed_kv_split and not b.prefill:       # batch-invariant form: the split grid is a function of the table width only
@@ -318,13 +326,18 @@ class MlaMoeEngine(GqaMoeEngine):
         else:
             K.mla_attention(ws.q_abs[:T], self.kv.c[i], b.page_table, b.seq_lens, b.q_start, bseq, btok, o_slab, self.scale,
                             splits, self._scratch if splits > 1 else None, out_tpad=ht.t_pad, sparse_idx=sel)
+        self._unabsorb(L, T, small, o_slab, ht)
+        self.launches += (7 if small else 8) + (1 if splits > 1 else 0)
+
+    def _unabsorb(self, L, T: int, small: bool, o_slab: torch.Tensor, ht) -> None:
+        """Latent attention output -> per-head values through W_uv, then the o projection with the residual add."""
+        ws = self.ws
         if small:
             K.mla_unabsorb_small(o_slab, L.w_uv, ws.attn[:T], T)
         else:
             K.grouped_linear(o_slab.view(-1, 512), L.w_uv, ws.attn, ht.tile_expert, ht.tile_row0, ht.num_tiles, ht.max_tiles,
-                             ht.tile_rows, row_dst=ht.row_dst, ldo=cfg.v_head_dim, split_k=False)
+                             ht.tile_rows, row_dst=ht.row_dst, ldo=self.cfg.v_head_dim, split_k=False)
         self._linear(L, "wo", ws.attn[:T], ws.h[:T], residual=ws.h[:T])
-        self.launches += (7 if small else 8) + (1 if splits > 1 else 0)
 
     def _select(self, i: int, T: int, b: Batch) -> torch.Tensor:
         """Lightning indexer: store this step's index keys, score every visible position, keep the top-k per token."""

@@ -494,6 +494,29 @@ def mla_attention(q_abs: torch.Tensor, cache: torch.Tensor, page_table: torch.Te
     return out
 
 
+def mla_attention_partial(q_abs: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor, seq_lens: torch.Tensor,
+                          kv_base: torch.Tensor, q_start: torch.Tensor, block_seq: torch.Tensor, block_tok0: torch.Tensor,
+                          peer_scratch: list[int], my_rank: int, scale: float, splits: int) -> None:
+    """Context split, first half (absorbed MLA): attention over the records this rank holds (``seq_lens`` local lengths,
+    ``kv_base`` visibility bases); the unnormalised partials go into every rank's scratch (``peer_scratch`` device
+    addresses, this rank's own included) at this rank's split slots."""
+    T, heads, rec = q_abs.shape
+    assert rec == 576 and 128 % heads == 0 and q_abs.is_contiguous() and cache.is_contiguous() and cache.dtype == torch.bfloat16
+    arr = (C.c_void_p * 8)(*peer_scratch)
+    _n.check(_n.cuda_lib().cafd_mla_attention_partial(
+        q_abs.data_ptr(), cache.data_ptr(), page_table.data_ptr(), seq_lens.data_ptr(), kv_base.data_ptr(), q_start.data_ptr(),
+        block_seq.data_ptr(), block_tok0.data_ptr(), arr, len(peer_scratch), my_rank, status_word(q_abs.device).data_ptr(),
+        T * heads, block_seq.numel(), cache.shape[0], page_table.shape[1], heads, splits, scale, _stream()), "mla_attention_partial")
+
+
+def mla_merge(scratch: torch.Tensor, block_seq: torch.Tensor, block_tok0: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor,
+              heads: int, total_splits: int, out_tpad: int = 0) -> torch.Tensor:
+    """Context split, second half: merge ``total_splits`` partials per (row block, output half) in slot order."""
+    _n.check(_n.cuda_lib().cafd_mla_merge(scratch.data_ptr(), block_seq.data_ptr(), block_tok0.data_ptr(), q_start.data_ptr(),
+                                          out.data_ptr(), block_seq.numel(), heads, total_splits, out_tpad, _stream()), "mla_merge")
+    return out
+
+
 FP8_RECORD_BYTES = 656      # 512 E4M3 latents + 4 fp32 scales + 64 bf16 rope dims
 
 

@@ -144,14 +144,18 @@ class DeviceContextSplit:
     ahead: its own merge of the next layer waits for the slow rank's partials)."""
 
     def __init__(self, num_heads: int, num_kv_heads: int, head_dim: int, max_seqs: int, max_q_len: int, splits: int,
-                 device: torch.device, group=None):
+                 device: torch.device, group=None, mla: bool = False):
         from ..ops import kernels as K
         from .afd import SymmetricHeap, _align
         self.group = group or dist.group.WORLD
         self.ranks, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         self.Hq, self.Hkv, self.D, self.splits, self.device = num_heads, num_kv_heads, head_dim, splits, device
         self.max_seqs, self.max_q_len = max_seqs, max_q_len
-        floats = K.attn_decode_scratch_floats(max_seqs, max_q_len, num_heads, num_kv_heads, splits * self.ranks)
+        if mla:        # absorbed MLA: row blocks of 128 (token, head) pairs, two output halves each
+            self.max_blocks = max_seqs * ((max_q_len * num_heads + 127) // 128)
+            floats = K.mla_scratch_floats(self.max_blocks, splits * self.ranks)
+        else:
+            floats = K.attn_decode_scratch_floats(max_seqs, max_q_len, num_heads, num_kv_heads, splits * self.ranks)
         self.buf_bytes = _align(floats * 4)
         self.off_flags = 2 * self.buf_bytes
         self.heap = SymmetricHeap(self.off_flags + 1024, device, self.group)
@@ -162,20 +166,38 @@ class DeviceContextSplit:
         import ctypes as C
         self._flag_ptrs = (C.c_void_p * 8)(*[self.heap.ptrs[r] + self.off_flags + 4 * self.rank for r in range(self.ranks)])
 
-    def attend(self, q, k_cache, v_cache, page_table, seq_lens, kv_base, q_start, out, max_q_len: int):
-        """q [T, Hq, D] (all heads), local page table / local lengths / visibility bases -> out [T, Hq, D] on every rank."""
+    def _exchange(self, partial, merge):
+        """``partial(peer scratch addresses)`` stores this rank's partials everywhere; ``merge(own scratch)`` runs once
+        every rank's flag of this turn has arrived."""
         from .._native import lib as _n
         from ..ops import kernels as K
-        assert page_table.shape[0] <= self.max_seqs and max_q_len <= self.max_q_len
         b = self.turn & 1
         self.turn += 1
         K.bump_epoch(self.epoch)
-        peers = [self.heap.ptrs[r] + b * self.buf_bytes for r in range(self.ranks)]
-        K.attn_decode_partial(q, k_cache, v_cache, page_table, seq_lens, kv_base, q_start, peers, self.rank, max_q_len, self.splits)
+        partial([self.heap.ptrs[r] + b * self.buf_bytes for r in range(self.ranks)])
         _n.check(_n.cuda_lib().cafd_tp_signal(self._flag_ptrs, self.ranks, self.epoch.data_ptr(), K._stream()), "context split signal")
         for r in range(self.ranks):
             K.wait_flag(self.flags.data_ptr() + 4 * r, self.epoch)
-        return K.attn_merge(self.scratch[b], q_start, out, max_q_len, self.Hkv, self.splits * self.ranks)
+        return merge(self.scratch[b])
+
+    def attend(self, q, k_cache, v_cache, page_table, seq_lens, kv_base, q_start, out, max_q_len: int):
+        """q [T, Hq, D] (all heads), local page table / local lengths / visibility bases -> out [T, Hq, D] on every rank."""
+        from ..ops import kernels as K
+        assert page_table.shape[0] <= self.max_seqs and max_q_len <= self.max_q_len
+        return self._exchange(
+            lambda peers: K.attn_decode_partial(q, k_cache, v_cache, page_table, seq_lens, kv_base, q_start, peers, self.rank,
+                                                max_q_len, self.splits),
+            lambda mine: K.attn_merge(mine, q_start, out, max_q_len, self.Hkv, self.splits * self.ranks))
+
+    def attend_mla(self, q_abs, cache, page_table, seq_lens, kv_base, q_start, block_seq, block_tok0, out, scale: float, out_tpad: int):
+        """Absorbed MLA: q_abs [T, heads, 576] (all heads), this rank's latent records -> out head-major
+        [heads, out_tpad, 512] on every rank."""
+        from ..ops import kernels as K
+        assert block_seq.numel() <= self.max_blocks
+        return self._exchange(
+            lambda peers: K.mla_attention_partial(q_abs, cache, page_table, seq_lens, kv_base, q_start, block_seq, block_tok0, peers,
+                                                  self.rank, scale, self.splits),
+            lambda mine: K.mla_merge(mine, block_seq, block_tok0, q_start, out, self.Hq, self.splits * self.ranks, out_tpad))
 
 
 def local_pages(n_pages: int, rank: int, ranks: int) -> int:
@@ -191,12 +213,21 @@ def local_len(kv_len: int, rank: int, ranks: int, page: int = PAGE) -> int:
 
 
 def make_engine(cfg, weights, num_pages: int, max_tokens: int, max_seqs: int, group=None, splits: int = 4):
-    """A GQA MoE engine whose attention reads a context-split KV cache.  Everything else is the single-GPU engine,
-    replicated on every rank of the group."""
+    """An engine whose attention reads a context-split KV cache (GQA K / V pages, or MLA latent records in the absorbed
+    form).  Everything else is the single-GPU engine, replicated on every rank of the group."""
     from ..models.gqa_moe import GqaMoeEngine, KvCache
     from ..ops import kernels as K
     if cfg.sliding_window:
         raise ValueError("context split and sliding-window layers do not combine: a window never spans more pages than one rank holds")
+    if cfg.is_mla:
+        from ..models.mla_moe import LatentCache, MlaMoeEngine
+        if cfg.indexer_heads or cfg.kv_format != "bf16":
+            raise ValueError("context split serves dense MLA over bf16 records (a sparse selection names global positions)")
+        dev = weights.embed.device
+        eng = MlaMoeEngine(cfg, weights, LatentCache(cfg, num_pages, dev), max_tokens, max_seqs)
+        # (slots are -1 on the ranks that do not hold the page of a new token: mla_prep_a drops the record there)
+        eng.cs = eng.kv_exchange = DeviceContextSplit(cfg.num_heads, 1, 576, max_seqs, PAGE, splits, dev, group, mla=True)
+        return eng
 
     class ContextSplitEngine(GqaMoeEngine):
         def __init__(self):

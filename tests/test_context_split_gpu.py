@@ -15,7 +15,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
+def _worker(rank: int, world: int, port: int, out_dir: str, family: str = "gqa") -> None:
     import torch.distributed as dist
 
     from cuteafd_b200.models.gqa_moe import GqaMoeWeights
@@ -27,10 +27,16 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    cfg = small_cfg()
+    if family == "mla":
+        from cuteafd_b200.models.mla_moe import MlaMoeWeights as Weights
+        from tests.test_mla_gpu import _mla_cfg
+        cfg = _mla_cfg()
+    else:
+        Weights = GqaMoeWeights
+        cfg = small_cfg()
     params = {k: v.to(torch.bfloat16).float() for k, v in init_weights(cfg, seed=0).items()}
     ref = RefDecoder(cfg, params)
-    eng = CS.make_engine(cfg, GqaMoeWeights.from_params(cfg, params, dev), num_pages=40, max_tokens=256, max_seqs=8, splits=2)
+    eng = CS.make_engine(cfg, Weights.from_params(cfg, params, dev), num_pages=40, max_tokens=256, max_seqs=8, splits=2)
     drv = CS.ContextSplitDriver(eng, 40, 16)
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g) for n in (300, 77, 5, 128)]
@@ -60,12 +66,12 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_context_split_matches_oracle(world, tmp_path):
+@pytest.mark.parametrize("world,family", [(2, "gqa"), (4, "gqa"), (2, "mla"), (4, "mla")])
+def test_context_split_matches_oracle(world, family, tmp_path):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
-    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), family), nprocs=world, join=True)
     recs = [torch.load(str(tmp_path / f"r{r}.pt")) for r in range(world)]
     for r, d in enumerate(recs):
         assert d["status"] == 0, (r, d)
