@@ -265,11 +265,11 @@ class MlaMoeEngine(GqaMoeEngine):
             rows = ((self.max_tokens + 63) // 64) * 64
             ws.lat = torch.zeros(self.max_tokens, cfg.kv_lora_rank, **bf)
             ws.k_exp, ws.v_exp = torch.zeros(rows, heads * 128, **bf), torch.zeros(rows, heads * 128, **bf)
-        K.linear(ws.x[:T], L.wqkv_a, out=ws.a[:T])
+        self._proj_a(L, T)
         K.mla_prep_a(ws.a[:T, :ql + REC], ql, L.q_a_norm, L.kv_a_norm, self.inv_freq, b.positions, b.slots,
                      ws.q_a[:T] if ql else None, self.kv.c[i], cfg.rms_eps, cfg.rope_interleaved,
                      lat_out=ws.lat[:T] if expanded else None)
-        self._linear(L, "wq_b", ws.q_a[:T] if ql else ws.x[:T], ws.q[:T])
+        self._linear(L, "wq_b", ws.q_a[:T] if ql else self._x_rows(T), ws.q[:T])
         q_slab = ws.q_slab[:heads * ht.t_pad * 128].view(heads, ht.t_pad, 128)
         o_slab = ws.o_slab[:heads * ht.t_pad * 512].view(heads, ht.t_pad, 512)
         # (the batch-invariant form keeps one absorb / un-absorb route for every decode width: the grouped GEMMs)
@@ -285,7 +285,7 @@ class MlaMoeEngine(GqaMoeEngine):
             K.linear(ws.lat[:T], L.w_uv.view(heads * 128, cfg.kv_lora_rank), out=ws.v_exp[:T])
             K.attn_prefill_mla(ws.q[:T], ws.q_abs[:T], ws.k_exp[:rows], ws.v_exp[:rows], self._zero1, self.kv.c[i], b.page_table,
                                b.seq_lens, b.q_start, ws.attn[:T], b.max_q_len, heads, self.scale)
-            K.linear(ws.attn[:T], L.wo, out=ws.h[:T], residual=ws.h[:T])
+            self._proj_o(L, T, twin=False)
             self.launches += 8
             return
         if not small:
@@ -337,7 +337,22 @@ class MlaMoeEngine(GqaMoeEngine):
         else:
             K.grouped_linear(o_slab.view(-1, 512), L.w_uv, ws.attn, ht.tile_expert, ht.tile_row0, ht.num_tiles, ht.max_tiles,
                              ht.tile_rows, row_dst=ht.row_dst, ldo=self.cfg.v_head_dim, split_k=False)
-        self._linear(L, "wo", ws.attn[:T], ws.h[:T], residual=ws.h[:T])
+        self._proj_o(L, T)
+
+    # The two ends of the attention half that a tensor-parallel engine replaces (models/tp_mla.py): where the
+    # normalised rows come from, and where the o projection's output goes.
+    def _x_rows(self, T: int) -> torch.Tensor:
+        return self.ws.x[:T]
+
+    def _proj_a(self, L, T: int) -> None:
+        K.linear(self.ws.x[:T], L.wqkv_a, out=self.ws.a[:T])
+
+    def _proj_o(self, L, T: int, twin: bool = True) -> None:
+        ws = self.ws
+        if twin:
+            self._linear(L, "wo", ws.attn[:T], ws.h[:T], residual=ws.h[:T])
+        else:
+            K.linear(ws.attn[:T], L.wo, out=ws.h[:T], residual=ws.h[:T])
 
     def _select(self, i: int, T: int, b: Batch) -> torch.Tensor:
         """Lightning indexer: store this step's index keys, score every visible position, keep the top-k per token."""

@@ -70,6 +70,11 @@ class TpGqaMoeEngine(GqaMoeEngine):
         dev = weights.embed.device
         sharded = shard_attention_weights(cfg, weights, self.rank, self.ranks)
         super().__init__(local, sharded, KvCache(local, num_pages, dev), max_tokens, max_seqs, build_moe=build_moe)
+        self._init_tp(cfg, weights, max_tokens, max_seqs, shard_head)
+
+    def _init_tp(self, cfg: ModelConfig, weights, max_tokens: int, max_seqs: int, shard_head: bool) -> None:
+        """The tensor-parallel half of the construction: symmetric buffers, owned-row output, the sharded head."""
+        dev = self.device
         self.tp = TpContext(cfg.hidden, max_tokens, dev, self.group)
         self.own_out = torch.zeros(self.tp.max_rows_per_rank, cfg.hidden, dtype=torch.bfloat16, device=dev)
         self.collectives = 0

@@ -23,7 +23,7 @@ def _cfg():
                        num_shared_experts=0, norm_topk_prob=True)
 
 
-def _worker(rank: int, world: int, port: int, out_dir: str, shard_head: bool = False, vocab: int = 2048) -> None:
+def _worker(rank: int, world: int, port: int, out_dir: str, shard_head: bool = False, vocab: int = 2048, family: str = "gqa") -> None:
     import torch.distributed as dist
 
     from cuteafd_b200.models.gqa_moe import GqaMoeWeights
@@ -37,13 +37,19 @@ def _worker(rank: int, world: int, port: int, out_dir: str, shard_head: bool = F
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     K.set_wait_limit_ns(2_000_000_000)
-    cfg = _cfg().replace(vocab_size=vocab, num_kv_heads=max(2, world))
+    if family == "mla":          # 16 heads of the small MLA model: 8 or 4 per rank
+        from cuteafd_b200.models.mla_moe import MlaMoeWeights as Weights
+        from cuteafd_b200.models.tp_mla import TpMlaMoeEngine as Engine
+        from tests.test_mla_gpu import _mla_cfg
+        cfg = _mla_cfg().replace(vocab_size=vocab)
+    else:
+        Weights, Engine = GqaMoeWeights, TpGqaMoeEngine
+        cfg = _cfg().replace(vocab_size=vocab, num_kv_heads=max(2, world))
     params = {k: v.to(torch.bfloat16).float() for k, v in init_weights(cfg, seed=0).items()}
     ref = RefDecoder(cfg, params)
     errs = {}
     for use_graphs in (False, True):
-        eng = TpGqaMoeEngine(cfg, GqaMoeWeights.from_params(cfg, params, dev), num_pages=64, max_tokens=256, max_seqs=8,
-                             shard_head=shard_head)
+        eng = Engine(cfg, Weights.from_params(cfg, params, dev), num_pages=64, max_tokens=256, max_seqs=8, shard_head=shard_head)
         picks_ok = True
 
         def whole(n):            # logits of the step's first n rows, whole vocabulary
@@ -82,14 +88,16 @@ def _worker(rank: int, world: int, port: int, out_dir: str, shard_head: bool = F
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,shard_head,vocab", [(2, False, 2048), (2, True, 2048), (2, True, 1000), (4, True, 2048)])
-def test_tp_attention_engine_matches_oracle(world, shard_head, vocab, tmp_path):
+@pytest.mark.parametrize("world,shard_head,vocab,family", [(2, False, 2048, "gqa"), (2, True, 2048, "gqa"), (2, True, 1000, "gqa"),
+                                                           (4, True, 2048, "gqa"), (2, False, 2048, "mla"), (2, True, 2048, "mla"),
+                                                           (4, False, 2048, "mla")])
+def test_tp_attention_engine_matches_oracle(world, shard_head, vocab, family, tmp_path):
     """``shard_head``: every rank keeps a slice of the head's rows and only per-rank winners cross the fabric (vocab 1000
     leaves the last rank a short slice: shares are rounded up to 128 rows)."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
-    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), shard_head, vocab), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), shard_head, vocab, family), nprocs=world, join=True)
     for r in range(world):
         d = torch.load(str(tmp_path / f"r{r}.pt"))
         for mode, e in d["errs"].items():
