@@ -26,9 +26,49 @@ def _size(s: str) -> int:
     return int(s)
 
 
+def _gib(v: str) -> str:
+    return f"{_size(v) / (1 << 30):.3f}"
+
+
+# Spellings of the reference's configuration file (cuteafd.config: run.sh --config / --set) -> this framework's keys, with
+# a converter for the value where the unit differs.  A reference configuration is accepted as it is: "auto" leaves the
+# default in place, and keys that describe what this framework does not have (Spark hosts and rails, container images,
+# SSH, the coordinator's GPU pick, TP2 switches of the RTX pair) are skipped with one notice.
+REFERENCE_KEYS = {
+    "MODEL_ID": ("MODEL", None), "EMBEDDING": ("EMBEDDING_PLACEMENT", None), "RTX_GPUS": ("ATTENTION_RANKS", None),
+    "SPARK_COUNT": ("EXPERT_RANKS", None), "KV_TARGET_TOKENS": ("POOL_TOKENS", None), "PREFILL_BATCH_TOKENS": ("PREFILL_ROWS", None),
+    "HTTP_QUEUE_WAIT_MS": ("HTTP_QUEUE_WAIT", lambda v: str(float(v) / 1000.0)), "HOST_CACHE_BYTES": ("HOST_CACHE_GIB", _gib),
+}
+REFERENCE_SKIPPED = ("SPARK_", "COORDINATOR_", "SPARKINFER_", "TP2_", "CUTEAFD_", "MODEL_VARIANT", "MODEL_REVISION", "EXPERT_PORT",
+                     "INSTANCE", "PREFIX_CACHE_ENTRIES", "MAX_OUTPUT_TOKENS", "KV_POOL_SIZE", "KV_MIN_TOKENS", "KV_MAX_TOKENS",
+                     "KV_DECODE_RESERVE_CHUNK", "KV_RESERVE_DRAIN_BUFFER", "KV_EARLY_TERMINATION_MIN_OUTPUT_TOKENS", "DRAFT_LENGTH",
+                     "RTX_EXPERT_LAYERS", "FULL_PREFILL_LOGITS")
+REFERENCE_SPECULATORS = {"dspark": "auto", "dflash2": "auto"}      # trained block drafters of the reference's checkpoints
+
+
+def reference_key(k: str, v: str, skipped: list[str]) -> list[tuple[str, str]]:
+    """One line of a reference configuration -> the (key, value) pairs it means here ([] = nothing to set)."""
+    if k == "ADDR":                                           # host:port of the HTTP listener
+        host, _, port = v.rpartition(":")
+        return ([("HOST", host)] if host else []) + ([("PORT", port)] if port else [])
+    if k == "SPARK_COUNT" or not (k.endswith("_DOCKER_DEV") or k.endswith("_DOCKER_INFERENCE") or k.startswith(REFERENCE_SKIPPED)):
+        name, conv = REFERENCE_KEYS.get(k, (k, None))
+        if v.lower() == "auto" and name not in ("SPECULATOR",):
+            return []                                         # the planner / the flag's default decides
+        if name == "SPECULATOR":
+            v = REFERENCE_SPECULATORS.get(v.lower(), v)
+        if name == "EXPERT_FORMAT" and v.lower() == "native":
+            return []                                         # "as stored" is what the loader does without an override
+        return [(name, conv(v) if conv else v)]
+    skipped.append(k)
+    return []
+
+
 def load_config_file(path: str, overrides: list[str], known: set[str]) -> dict[str, str]:
-    """KEY=VALUE file + ``--set`` overrides; unknown keys exit with status 2."""
+    """KEY=VALUE file + ``--set`` overrides; the reference's spellings are translated (``REFERENCE_KEYS``), its
+    hardware-specific keys skipped with a notice; any other unknown key exits with status 2."""
     out: dict[str, str] = {}
+    skipped: list[str] = []
     lines = []
     if path:
         with open(path) as f:
@@ -41,17 +81,21 @@ def load_config_file(path: str, overrides: list[str], known: set[str]) -> dict[s
             print(f"config: malformed line {raw!r}", file=sys.stderr)
             raise SystemExit(2)
         k, v = line.split("=", 1)
-        k = k.strip().upper()
-        if k not in known:
-            print(f"config: unknown key {k}", file=sys.stderr)
-            raise SystemExit(2)
-        out[k] = v.strip()
+        for k, v in reference_key(k.strip().upper(), v.strip(), skipped):
+            if k not in known:
+                print(f"config: unknown key {k}", file=sys.stderr)
+                raise SystemExit(2)
+            out[k] = v
+    if skipped:
+        print(f"config: {len(skipped)} key(s) of the reference's deployment that have no counterpart here were skipped: "
+              + ", ".join(sorted(set(skipped))[:8]) + (" ..." if len(set(skipped)) > 8 else ""), file=sys.stderr)
     return out
 
 
 CONFIG_KEYS = {"MODEL", "EMBEDDING_PLACEMENT", "GPUS", "ATTENTION_RANKS", "EXPERT_RANKS", "POOL_TOKENS", "GPU_MEMORY_CAP", "MAX_CONTEXT_TOKENS",
                "CONCURRENCY", "SPECULATOR", "DECODE_LANES", "PORT", "HOST", "API_KEY", "DECODE_SHARE", "PREFILL_ROWS",
-               "HTTP_QUEUE_DEPTH", "HTTP_QUEUE_WAIT", "PROFILE", "SPECULATION_TRACE", "KV_FORMAT", "EXPERT_FORMAT"}
+               "HTTP_QUEUE_DEPTH", "HTTP_QUEUE_WAIT", "PROFILE", "SPECULATION_TRACE", "KV_FORMAT", "EXPERT_FORMAT",
+               "HOST_CACHE_GIB", "LOOP_ABORT_RUN", "LOOP_ABORT_COPIES", "LOOP_FAST_SPAN", "LOOP_FAST_COPIES", "BATCH_INVARIANT"}
 
 
 def graph_reserve_of(value: str) -> tuple[int, str]:
@@ -121,6 +165,12 @@ def cmd_launch(a: argparse.Namespace) -> int:
                      decode_lanes=a.decode_lanes)
         if not (rep.placement and rep.placement.ok and rep.ready):
             print(P.render(rep), file=sys.stderr)
+            return 1
+        from .planner.solver import HTTP_ENGINES
+        if rep.placement.engine not in HTTP_ENGINES:
+            print(P.render(rep), file=sys.stderr)
+            print(f"launch: the HTTP server drives one attention rank (layouts {' / '.join(HTTP_ENGINES)}); this plan is "
+                  f"{rep.placement.engine or 'not served by an engine'} - give --attention-ranks 1", file=sys.stderr)
             return 1
         spec = P.deployment(rep, a.master_addr, a.master_port)
     serve_args = ["--host", a.host, "--port", str(a.port)]

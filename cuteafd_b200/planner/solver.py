@@ -266,15 +266,24 @@ def engine_for(cfg: ModelConfig, att: int, exp: int, pp: int) -> tuple[str, str]
     """(engine that serves the layout, note).  The solver sizes any (attention TP, expert EP, stages) split; this names
     the code path that runs it, so a plan never silently proposes a layout nothing can execute."""
     if pp > 1:
-        return "", "pipeline stages: the hop exists (parallel/pp.py) but no engine runs layer ranges yet"
+        if att == 1 and exp == 0 and not cfg.is_mla:
+            return "pp", "layer ranges as pipeline stages with ring hops (models/pp_gqa.py)"
+        return "", "pipeline stages are wired for the GQA family alone (no tensor parallelism or expert ranks beside them)"
     if att == 1:
         return ("afd", "attention on one GPU, routed experts on the others (parallel/afd.py)") if exp else \
                ("single", "attention and experts on one GPU")
     if exp == 0 and not cfg.is_mla and cfg.num_kv_heads % att == 0:
         return "tp", "heads split over the GPUs, residual rows sharded, experts replicated (models/tp_gqa.py)"
+    if exp == 0 and cfg.is_mla and not cfg.indexer_heads and cfg.num_heads % att == 0 and 128 % (cfg.num_heads // att) == 0:
+        return "tp", "MLA heads split over the GPUs, latent cache replicated, residual rows sharded (models/tp_mla.py)"
     if exp == 0:
-        return "", "tensor-parallel attention is wired for the GQA family with kv heads divisible by the degree"
-    return "", "tensor-parallel attention ranks in front of the expert exchange are not wired yet"
+        return "", ("tensor-parallel attention needs kv heads (GQA) or heads (dense MLA, at most 128 per rank) divisible by the degree; "
+                    "the lightning indexer is not split")
+    return "", ("a tensor-parallel attention group in front of the expert exchange is not wired; the benchmark's 2 + 6 and 4 + 4 layouts "
+                "run data-parallel attention replicas instead (bench.py --attention-ranks), which the HTTP server does not drive")
+
+
+HTTP_ENGINES = ("single", "afd")      # what ``serve`` / ``launch`` can start: one attention rank, with or without expert ranks
 
 
 def candidates(req: PlacementRequest) -> list[tuple[int, int, int]]:

@@ -142,3 +142,28 @@ def test_a_rank_that_cannot_start_leaves_nothing_running(tmp_path):
     with pytest.raises(OSError):
         L.start()
     assert L.ranks[0].proc.poll() is not None and L.ranks[1].proc is None
+
+
+def test_a_reference_configuration_file_is_accepted(tmp_path, capsys):
+    """The reference's key spellings mean the same here (units converted), "auto" leaves the default, and the keys of
+    its Spark / container deployment are skipped with one notice instead of refusing the file."""
+    cfg = tmp_path / "cuteafd.config"
+    cfg.write_text("MODEL_ID=/models/x\nMODEL_REVISION=abc\nEXPERT_FORMAT=native\nSPECULATOR=dspark\nTP2_ATTENTION=off\nRTX_GPUS=auto\n"
+                   "MAX_CONTEXT_TOKENS=auto\nCONCURRENCY=16\nHOST_CACHE_BYTES=8GiB\nHTTP_QUEUE_WAIT_MS=2500\nADDR=0.0.0.0:8123\n"
+                   "SPARK_COUNT=6\nSPARK_0_HOST=ostrich\nSPARK_0_LANE_A=10.0.0.1\nCOORDINATOR_DOCKER_DEV=img\nEMBEDDING=host\n"
+                   "LOOP_ABORT_RUN=256\nPREFILL_BATCH_TOKENS=2048\n")
+    got = cli.load_config_file(str(cfg), [], cli.CONFIG_KEYS)
+    assert got == {"MODEL": "/models/x", "SPECULATOR": "auto", "CONCURRENCY": "16", "HOST_CACHE_GIB": "8.000", "HTTP_QUEUE_WAIT": "2.5",
+                   "HOST": "0.0.0.0", "PORT": "8123", "EXPERT_RANKS": "6", "EMBEDDING_PLACEMENT": "host", "LOOP_ABORT_RUN": "256",
+                   "PREFILL_ROWS": "2048"}
+    err = capsys.readouterr().err
+    assert "skipped" in err and "SPARK_0_HOST" in err and "TP2_ATTENTION" in err
+    ap = cli.build_parser()
+    argv = ["--config", str(cfg), "serve"]
+    a = ap.parse_args(argv)
+    a.file_config = got
+    cli.apply_config(ap, a, argv)
+    assert (a.snapshot, a.concurrency, a.port, a.host, a.queue_wait, a.host_cache_gib, a.embedding_placement, a.loop_abort_run) == \
+        ("/models/x", 16, 8123, "0.0.0.0", 2.5, 8.0, "host", 256)
+    with pytest.raises(SystemExit):
+        cli.load_config_file("", ["SOMETHING_ELSE=1"], cli.CONFIG_KEYS)

@@ -82,7 +82,9 @@ def test_plan_names_the_engine_that_serves_it():
     q, d = qwen3_30b_a3b(), deepseek_v3()
     assert engine_for(q, 1, 7, 1)[0] == "afd" and engine_for(q, 1, 0, 1)[0] == "single"
     assert engine_for(q, 4, 0, 1)[0] == "tp" and engine_for(q, 8, 0, 1)[0] == ""        # 4 kv heads
-    assert engine_for(d, 2, 6, 1)[0] == "" and engine_for(d, 2, 0, 1)[0] == "" and engine_for(q, 1, 3, 2)[0] == ""
+    assert engine_for(d, 2, 6, 1)[0] == "" and engine_for(q, 1, 3, 2)[0] == ""
+    assert engine_for(d, 2, 0, 1)[0] == "tp" and engine_for(d.replace(indexer_heads=64), 2, 0, 1)[0] == ""      # dense MLA heads split
+    assert engine_for(q, 1, 0, 2)[0] == "pp" and engine_for(d, 1, 0, 2)[0] == ""
     best = solve(PlacementRequest(cfg=d, gpus=8))
     assert best.ok and best.engine == "afd" and best.attention_ranks == 1 and best.expert_ranks == 7
     assert any(n.startswith("served by:") for n in best.notes)
