@@ -148,7 +148,7 @@ def deployment(rep: PlanReport, master_addr: str = "127.0.0.1", master_port: int
         ranks.append(entry)
     body = {"model": rep.model, "source": rep.source, "family": rep.family, "layout": p.layout,
             "world_size": len(ranks), "attention_ranks": p.attention_ranks, "expert_ranks": p.expert_ranks,
-            "pipeline_stages": p.pipeline_stages, "kv_pool_tokens": p.kv_pool_tokens, "speculator": p.speculator,
+            "pipeline_stages": p.pipeline_stages, "engine": p.engine, "kv_pool_tokens": p.kv_pool_tokens, "speculator": p.speculator,
             "decode_lanes": p.decode_lanes, "prefill_rows": rep.request.prefill_rows, "decode_rows": rep.request.decode_rows,
             "max_context_tokens": rep.request.max_context_tokens, "rendezvous": {"master_addr": master_addr, "master_port": master_port},
             "ranks": ranks}

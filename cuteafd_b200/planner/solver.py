@@ -283,7 +283,9 @@ def engine_for(cfg: ModelConfig, att: int, exp: int, pp: int) -> tuple[str, str]
                 "run data-parallel attention replicas instead (bench.py --attention-ranks), which the HTTP server does not drive")
 
 
-HTTP_ENGINES = ("single", "afd")      # what ``serve`` / ``launch`` can start: one attention rank, with or without expert ranks
+# What ``serve`` / ``launch`` can start: one attention rank with or without expert ranks, or a tensor-parallel attention
+# group whose rank 0 holds the scheduler and whose other ranks repeat its steps (parallel/mirror.py)
+HTTP_ENGINES = ("single", "afd", "tp")
 
 
 def candidates(req: PlacementRequest) -> list[tuple[int, int, int]]:

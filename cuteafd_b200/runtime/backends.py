@@ -444,6 +444,8 @@ class EngineBackend:
         if self.use_graphs and key in self.graphs:
             g, out = self.graphs.pop(key)
             self.graphs[key] = (g, out)                       # most recently used last
+            if hasattr(self.engine, "mirror"):
+                self.engine.mirror(batch)                     # tensor-parallel followers get the step a replay runs
             if hasattr(self.engine, "take_replay"):
                 self.engine.take_replay(key[1])
             elif hasattr(self.engine, "announce"):

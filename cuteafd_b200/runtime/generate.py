@@ -148,6 +148,8 @@ class Generator:
                     self.decode_bufs.pop(old, None)
             g, out = self.graphs.pop(S)
             self.graphs[S] = (g, out)          # most recently used last
+            if hasattr(self.engine, "mirror"):
+                self.engine.mirror(self._decode_batch(b, S))
             if hasattr(self.engine, "take_replay"):
                 self.engine.take_replay(S)
             elif hasattr(self.engine, "announce"):

@@ -494,7 +494,19 @@ def build_state(args) -> ServerState:
             # Disaggregated deployment (launched with one process per GPU): rank 0 runs attention, the dense backbone
             # and this HTTP server; the other ranks hold the routed experts and serve announced steps until rank 0
             # stops them.  The attention engine plugs into the same backend as the single-GPU engine.
-            cfg, eng = _build_afd_rank(args, snapshot, world, num_pages, pages_per_seq, rows)
+            dep_engine = ""
+            if getattr(args, "deployment", ""):
+                with open(args.deployment) as f:
+                    dep_engine = json.load(f).get("engine", "")
+            if dep_engine == "tp":
+                # Tensor-parallel attention group, experts on the same GPUs: rank 0 holds this scheduler and HTTP server,
+                # the other ranks repeat its engine steps on their shard of the heads until it stops them.
+                if getattr(args, "embedding_placement", "gpu") == "host":
+                    raise SystemExit("--embedding-placement host is not available with a tensor-parallel attention group")
+                args.host_cache_gib = 0.0           # a snapshot's pages differ per rank (each holds its own heads)
+                cfg, eng = _build_tp_rank(args, snapshot, world, num_pages, rows)
+            else:
+                cfg, eng = _build_afd_rank(args, snapshot, world, num_pages, pages_per_seq, rows)
         elif snapshot:
             from ..loader.load import load_engine
             cfg, eng = load_engine(snapshot, dev, num_pages, max(2048, rows), rows, getattr(args, "kv_format", "auto"))
@@ -667,6 +679,54 @@ def _build_afd_rank(args, snapshot, world: int, num_pages: int, pages_per_seq: i
     return cfg, h.generator.engine
 
 
+_TP_ENGINE = None
+
+
+def _build_tp_rank(args, snapshot, world: int, num_pages: int, rows: int):
+    """Join the group and build this rank's shard of a tensor-parallel engine.  Rank 0 returns the mirrored engine for
+    the backend; the other ranks follow it from here and leave the process when it stops them."""
+    global _TP_ENGINE
+    import torch
+    import torch.distributed as dist
+
+    from ..config import PRESETS
+    from ..parallel.mirror import MirroredEngine, follow
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=dev)
+    if snapshot:
+        from ..loader.load import load_params
+        cfg, params = load_params(snapshot)
+    else:
+        cfg = PRESETS[args.preset or "qwen3-30b-a3b"]()
+        if args.layers:
+            cfg = cfg.replace(num_layers=args.layers)
+        params = None
+    cfg = cfg.replace(mtp_layers=0)                       # the MTP depth's own step is not mirrored
+    if cfg.is_mla:
+        from ..models.mla_moe import MlaMoeWeights as Weights
+        from ..models.tp_mla import TpMlaMoeEngine as Engine
+    else:
+        from ..models.gqa_moe import GqaMoeWeights as Weights
+        from ..models.tp_gqa import TpGqaMoeEngine as Engine
+    W = Weights.from_params(cfg, params, dev) if params is not None else Weights.random_init(cfg, dev)   # same seed on every rank
+    inner = Engine(cfg, W, num_pages, max_tokens=max(2048, rows), max_seqs=rows)
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank != 0:
+        steps = follow(inner)
+        print(f"[serve] tensor-parallel rank {rank} followed {steps} steps", flush=True)
+        dist.barrier()
+        dist.destroy_process_group()
+        raise SystemExit(0)
+    _TP_ENGINE = MirroredEngine(inner)
+    print(f"[serve] tensor-parallel attention over {world} GPUs, rank 0 drives", flush=True)
+    return cfg, _TP_ENGINE
+
+
 def run_server(args) -> int:
     state = build_state(args)
     from ..utils.diagnostics import install_stack_dump
@@ -681,6 +741,11 @@ def run_server(args) -> int:
         if _AFD_HANDLE is not None:                       # release the expert ranks, then leave the group together
             import torch.distributed as dist
             _AFD_HANDLE.shutdown()
+            dist.barrier()
+            dist.destroy_process_group()
+        if _TP_ENGINE is not None:                        # release the following ranks the same way
+            import torch.distributed as dist
+            _TP_ENGINE.stop()
             dist.barrier()
             dist.destroy_process_group()
         if state.sched.trace is not None:
