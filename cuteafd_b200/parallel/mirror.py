@@ -45,7 +45,12 @@ class MirroredEngine:
         self.kv = _MirroredKv(inner.kv, self)
         self.mirrored_steps = 0
 
+    # the MTP depth's own step and the host-resident embedding rows are not mirrored: the backends see neither
+    HIDDEN = ("mtp_forward", "embed_rows")
+
     def __getattr__(self, name):                      # cfg, W, device, logits, next_tokens, greedy, launches, ...
+        if name in MirroredEngine.HIDDEN or name in ("inner", "group"):
+            raise AttributeError(name)
         return getattr(self.inner, name)
 
     def _send_header(self, words: list[int]) -> None:
@@ -54,6 +59,8 @@ class MirroredEngine:
 
     def mirror(self, b) -> None:
         """Send the step ``b`` describes to the followers (they run it as soon as it arrives)."""
+        if getattr(b, "embeds", None) is not None:
+            raise ValueError("media rows are not mirrored to a tensor-parallel group: text requests only")
         T, (S, max_pages) = b.tokens.shape[0], b.page_table.shape
         last = b.last_rows
         self._send_header([OP_FORWARD, T, S, max_pages, int(b.max_q_len), int(bool(b.prefill)), int(bool(getattr(b, "fresh", False))),
@@ -67,10 +74,6 @@ class MirroredEngine:
         if not (self.inner.device.type == "cuda" and torch.cuda.is_current_stream_capturing()):
             self.mirror(b)
         return self.inner.forward(b)
-
-    @property
-    def mtp_forward(self):                            # the MTP depth's own step is not mirrored: the backends see no MTP head
-        raise AttributeError("mtp_forward")
 
     def take_replay(self, rows: int) -> None:         # the graph bank's hook before a replay: ``mirror`` was called with the batch
         return None
