@@ -121,8 +121,12 @@ def bench_attn_prefill(a, dev, pk):
     out = torch.empty_like(q)
     sl = torch.tensor([n], dtype=torch.int32, device=dev)
     qs = torch.tensor([0, n], dtype=torch.int32, device=dev)
-    ms = time_eager(lambda: K.attn_prefill(q, kc, vc, table, sl, qs, out, n), dev, iters=a.iters)
-    report(f"attn_prefill len={n} Hq={Hq} Hkv={Hkv}", ms, 4.0 * n * n * D * Hq / 2, (2 * n * Hq * D + 2 * n * Hkv * D) * 2, pk)
+    w = a.window
+    ms = time_eager(lambda: K.attn_prefill(q, kc, vc, table, sl, qs, out, n, window=w), dev, iters=a.iters)
+    # visible (query, key) pairs: the causal triangle, or the band of a sliding window
+    pairs = n * n / 2 if not w or w >= n else n * w - w * w / 2
+    report(f"attn_prefill len={n} Hq={Hq} Hkv={Hkv}" + (f" window={w}" if w else ""), ms, 4.0 * pairs * D * Hq,
+           (2 * n * Hq * D + 2 * n * Hkv * D) * 2, pk)
     assert K.read_status() == 0
 
 
@@ -136,10 +140,13 @@ def bench_attn_decode(a, dev, pk):
     out = torch.empty_like(q)
     sl = torch.full((S,), n, dtype=torch.int32, device=dev)
     qs = torch.arange(S + 1, dtype=torch.int32, device=dev)
-    splits = a.splits or K.attn_decode_splits(S, 1, Hkv, pps)
+    splits = a.splits or K.attn_decode_splits(S, 1, Hkv, pps, a.window)
     scratch = torch.empty(K.attn_decode_scratch_floats(S, 1, Hq, Hkv, splits), dtype=torch.float32, device=dev)
-    ms = time_graph([(lambda kc=kc: K.attn_decode(q, kc, kc, table, sl, qs, out, scratch, 1, splits)) for kc in kcs] * 3)
-    report(f"attn_decode seqs={S} len={n} splits={splits}", ms, 4.0 * S * n * D * Hq, S * n * Hkv * D * 2 * 2.0, pk)
+    w = a.window
+    seen = min(n, w) if w else n                                       # positions a row reads
+    ms = time_graph([(lambda kc=kc: K.attn_decode(q, kc, kc, table, sl, qs, out, scratch, 1, splits, window=w)) for kc in kcs] * 3)
+    report(f"attn_decode seqs={S} len={n} splits={splits}" + (f" window={w}" if w else ""), ms, 4.0 * S * seen * D * Hq,
+           S * seen * Hkv * D * 2 * 2.0, pk)
 
 
 def bench_moe(a, dev, pk):
@@ -341,11 +348,11 @@ def main() -> None:
     g.add_argument("--k", type=int, default=2048); g.add_argument("--dual", action="store_true")
     p = sub.add_parser("attn-prefill")
     p.add_argument("--len", type=int, default=8192); p.add_argument("--heads", type=int, default=32)
-    p.add_argument("--kv-heads", type=int, default=4)
+    p.add_argument("--kv-heads", type=int, default=4); p.add_argument("--window", type=int, default=0, help="sliding window in tokens (0 = none)")
     d = sub.add_parser("attn-decode")
     d.add_argument("--seqs", type=int, default=32); d.add_argument("--len", type=int, default=8192)
     d.add_argument("--heads", type=int, default=32); d.add_argument("--kv-heads", type=int, default=4)
-    d.add_argument("--splits", type=int, default=0)
+    d.add_argument("--splits", type=int, default=0); d.add_argument("--window", type=int, default=0, help="sliding window in tokens (0 = none)")
     m = sub.add_parser("moe")
     m.add_argument("--tokens", default="1,16,128,1024,8192"); m.add_argument("--hidden", type=int, default=2048)
     m.add_argument("--ffn", type=int, default=768); m.add_argument("--experts", type=int, default=128)

@@ -114,7 +114,7 @@ class TpGqaMoeEngine(GqaMoeEngine):
             S, max_pages = b.page_table.shape
             q_per_tile = 16 // (cfg.num_heads // cfg.num_kv_heads)
             tiles = (b.max_q_len + q_per_tile - 1) // q_per_tile
-            splits = K.kv_splits_fixed(max_pages) if self.fixed_kv_split else K.attn_decode_splits(S, tiles, cfg.num_kv_heads, max_pages)
+            splits = K.kv_splits_fixed(max_pages) if self.fixed_kv_split else K.attn_decode_splits(S, tiles, cfg.num_kv_heads, max_pages, cfg.window_of(i))
             need = K.attn_decode_scratch_floats(S, b.max_q_len, cfg.num_heads, cfg.num_kv_heads, splits)
             if self._scratch is None or self._scratch.numel() < need:
                 self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)

@@ -340,11 +340,14 @@ def moe_combine(buf: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, shared
 
 
 # ---- attention -------------------------------------------------------------------------------------
-def attn_decode_splits(num_seqs: int, tiles_per_seq: int, Hkv: int, max_pages: int) -> int:
-    """KV splits for the decode attention kernel.  The kernel keeps one 64-token page pair in flight per CTA, so
+def attn_decode_splits(num_seqs: int, tiles_per_seq: int, Hkv: int, max_pages: int, window: int = 0) -> int:
+    """KV splits for the decode attention kernel (``window`` > 0: a row reads at most the pages its window touches, so
+    the splits are sized for those, not for the whole table).  The kernel keeps one 64-token page pair in flight per CTA, so
     HBM is only saturated with about three CTAs per SM (64 KB of shared memory each): aim for one full wave of
     3 x SMs CTAs, and never let a split grow past ~1K tokens (measured: 8 x 8K context 46 -> 33 us, 32 x 8K
     131 -> 99 us against the old one-CTA-per-SM rule)."""
+    if window > 0:
+        max_pages = min(max_pages, (window + 63) // 64 + 1)
     ctas = max(1, num_seqs * tiles_per_seq * Hkv)
     want = max((3 * num_sms()) // ctas, (max_pages + 15) // 16, 1)
     return max(1, min(want, max(1, max_pages // 4), 32))
