@@ -8,7 +8,8 @@ payload, device to device over NCCL on the compute stream) and then runs the ste
 (copy-on-write of shared prefix pages) are mirrored the same way.  ``follow`` is the other ranks' loop: receive, rebuild
 the batch, run the same step on the local shard, until rank 0 says stop.  Rank 0 may replay CUDA graphs (the backend
 calls ``mirror`` itself before a replay; a forward that is being captured sends nothing, since a capture runs nothing);
-the followers run eagerly.
+a follower keeps its own graph bank: a decode geometry it has run eagerly twice is captured right after the second
+run and replayed from then on, its inputs arriving in one static buffer.
 
 Counterpart: the reference's second coordinator GPU follows the first through its peer-split step protocol
 (rust/crates/cuteafd-daemon/src/shared/peer_split/attention.rs); one scheduler, two GPUs' worth of heads.
@@ -82,13 +83,24 @@ class MirroredEngine:
         self._send_header([OP_STOP])
 
 
-def follow(inner, group=None, on_step=None) -> int:
+class FollowerStats:
+    def __init__(self) -> None:
+        self.steps = self.replays = self.captures = 0
+
+
+def follow(inner, group=None, on_step=None, graphs: bool = True, max_graphs: int = 32, stats: FollowerStats | None = None) -> int:
     """The loop of a rank that is not rank 0: repeat every mirrored call on the local shard.  Returns the number of
-    forward steps it ran."""
+    forward steps it ran.  ``graphs``: decode steps of a geometry seen twice run from a CUDA graph of this rank's own
+    (the step's description is received into one static buffer, so a graph's inputs never move)."""
     from ..models.gqa_moe import Batch
     group = group or dist.group.WORLD
     src = dist.get_global_rank(group, 0) if group is not dist.group.WORLD else 0
     dev, steps = inner.device, 0
+    stats = stats or FollowerStats()
+    graphs = graphs and dev.type == "cuda"
+    static = torch.empty(1 << 16, dtype=torch.int32, device=dev)
+    bank: dict[tuple, torch.cuda.CUDAGraph] = {}
+    seen: dict[tuple, int] = {}
     while True:
         h = torch.zeros(HEADER_WORDS, dtype=torch.int64, device=dev)
         dist.broadcast(h, src=src, group=group)
@@ -102,13 +114,35 @@ def follow(inner, group=None, on_step=None) -> int:
             raise RuntimeError(f"mirror: unknown message {w[:4]}")
         _, T, S, max_pages, max_q_len, prefill, fresh, has_last, n_last = w[:9]
         sizes = [T, T, T, S * max_pages, S, S + 1] + ([n_last] if has_last else [])
-        payload = torch.empty(sum(sizes), dtype=torch.int32, device=dev)
+        n = sum(sizes)
+        if n > static.numel():                       # a wider step than any before: the graphs' inputs lived in the old buffer
+            static = torch.empty(2 * n, dtype=torch.int32, device=dev)
+            bank.clear()
+            seen.clear()
+        payload = static[:n]
         dist.broadcast(payload, src=src, group=group)
         f = list(torch.split(payload, sizes))
         b = Batch(f[0], f[1], f[2], f[3].view(S, max_pages), f[4], f[5], max_q_len, bool(prefill), f[6] if has_last else None,
                   fresh=bool(fresh))
+        key = tuple(w[1:9])
         with torch.no_grad():
-            inner.forward(b)
+            if key in bank:
+                bank[key].replay()
+                stats.replays += 1
+            else:
+                inner.forward(b)
+                if graphs and not prefill:
+                    seen[key] = seen.get(key, 0) + 1
+                    if seen[key] == 2 and len(bank) < max_graphs:
+                        # two eager runs have warmed this geometry up; record it now (a capture runs nothing, so the
+                        # group's step count stays what rank 0 made it)
+                        torch.cuda.synchronize(dev)
+                        g = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(g):
+                            inner.forward(b)
+                        bank[key] = g
+                        stats.captures += 1
         steps += 1
+        stats.steps = steps
         if on_step is not None:
             on_step(steps)

@@ -20,7 +20,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str, family: str) -> None
     import torch.distributed as dist
 
     from cuteafd_b200.ops import kernels as K
-    from cuteafd_b200.parallel.mirror import MirroredEngine, follow
+    from cuteafd_b200.parallel.mirror import FollowerStats, MirroredEngine, follow
     from cuteafd_b200.ref.model import KvState, RefDecoder, init_weights
     from cuteafd_b200.runtime.generate import Generator
     from cuteafd_b200.runtime.paged import PagePool
@@ -44,10 +44,11 @@ def _worker(rank: int, world: int, port: int, out_dir: str, family: str) -> None
     pool_of = (lambda kv: kv.c[0]) if family == "mla" else (lambda kv: kv.k[0])
     dist.barrier()
     if rank != 0:
-        steps = follow(inner)
+        st = FollowerStats()
+        steps = follow(inner, stats=st)
         torch.cuda.synchronize()
         page = pool_of(inner.kv)
-        torch.save({"steps": steps, "status": K.read_status(), "copied": bool(torch.equal(page[1], page[60])) and bool(page[1].abs().sum() > 0)},
+        torch.save({"steps": steps, "status": K.read_status(), "captures": st.captures, "replays": st.replays, "copied": bool(torch.equal(page[1], page[60])) and bool(page[1].abs().sum() > 0)},
                    os.path.join(out_dir, f"r{rank}.pt"))
         dist.barrier()
         dist.destroy_process_group()
@@ -99,3 +100,4 @@ def test_followers_repeat_rank_zero(family, tmp_path):
         e = sorted(e)
         assert e[len(e) // 2] < 0.03 and e[-1] < 0.25, (mode, e)
     assert fol["steps"] == lead["mirrored"] > 0 and lead["copied"] and fol["copied"]
+    assert fol["captures"] >= 1 and fol["replays"] >= 4           # the follower's own graph of the 3-sequence decode step
