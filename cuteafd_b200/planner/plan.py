@@ -114,7 +114,10 @@ def render(rep: PlanReport) -> str:
                 L.append(f"  gpu{g.index} {g.role:<17} used {_gib(g.used)} free {_gib(g.free)} | "
                          + " ".join(f"{k} {v/solver.GIB:.1f}" for k, v in cats.items() if v))
             if p.expert_ranges:
-                L.append("experts    " + " ".join(f"[{lo}:{hi})" for lo, hi in p.expert_ranges))
+                if p.expert_ranks == 0 and p.attention_ranks > 1:
+                    L.append(f"experts    [0:{p.expert_ranges[-1][1]}) on every rank of the tensor-parallel group")
+                else:
+                    L.append("experts    " + " ".join(f"[{lo}:{hi})" for lo, hi in p.expert_ranges))
             for n in p.notes:
                 L.append(f"note       {n}")
     L.append(f"ready      {'yes' if rep.ready else 'no'}")
@@ -141,8 +144,8 @@ def deployment(rep: PlanReport, master_addr: str = "127.0.0.1", master_port: int
         entry = {"rank": i, "device": g.index, "role": g.role, "memory": g.by_category(), "free_bytes": g.free}
         if i < n_att:
             entry.update(tp_rank=i % p.attention_ranks, pp_stage=i // p.attention_ranks)
-            if p.expert_ranks == 0 and p.expert_ranges:
-                entry["experts"] = list(p.expert_ranges[i])
+            if p.expert_ranks == 0 and p.expert_ranges and p.attention_ranks == 1:
+                entry["experts"] = list(p.expert_ranges[i])          # (a tensor-parallel group keeps every expert on every rank)
         else:
             entry["experts"] = list(p.expert_ranges[i - n_att])
         ranks.append(entry)

@@ -189,19 +189,21 @@ def _place(req: PlacementRequest, att: int, exp: int, pp: int) -> Placement:
             g.role = "attention+expert" if colocated else "attention"
             frac = layers_per_stage / cfg.num_layers
             g.add("weights", "attention", comp["attention"] * frac / att)
-            g.add("weights", "dense_ffn", comp["dense_ffn"] * frac / att)
-            g.add("weights", "shared_experts", comp["shared_experts"] * frac / att)
+            # a tensor-parallel group splits the attention heads only: every rank runs the whole FFN of the rows it
+            # owns, so dense / shared / routed expert weights and the head are whole on each of its GPUs
+            g.add("weights", "dense_ffn", comp["dense_ffn"] * frac)
+            g.add("weights", "shared_experts", comp["shared_experts"] * frac)
             g.add("weights", "router+norms", (comp["router"] + comp["norms"]) * frac)
             g.add("weights", "indexer", comp["indexer"] * frac / att)
             if s == 0:
                 g.add("weights", "embedding", comp["embedding"])
             if s == pp - 1:
-                g.add("weights", "head", comp["head"] / att)
+                g.add("weights", "head", comp["head"])
                 if spec == "mtp":
                     g.add("weights", "mtp", comp["mtp"] / att if colocated else
                           (comp["mtp"] - cfg.mtp_layers * cfg.num_experts * weight_bytes(cfg.expert_params(), req.expert_format or cfg.weight_format)) / att)
             if colocated and cfg.num_experts:
-                lo, hi = ranges[s * att + t]
+                lo, hi = (0, cfg.num_experts) if att > 1 else ranges[s * att + t]
                 g.add("experts", f"experts[{lo}:{hi}]", comp["one_expert_all_layers"] * (hi - lo) * frac
                       + req.redundant_experts * comp["one_expert_all_layers"] * frac)
             width = cfg.hidden * 2
@@ -253,7 +255,7 @@ def _place(req: PlacementRequest, att: int, exp: int, pp: int) -> Placement:
     layout = (f"attention tp{att}" + (f" x pp{pp}" if pp > 1 else "") + (f" + experts ep{exp}" if exp else " + experts colocated"))
     # ---- throughput proxy for "auto": decode step bytes on the busiest device ---------------------------
     act_exp = min(cfg.num_experts, req.concurrency * cfg.top_k) if cfg.num_experts else 0
-    exp_dev = exp if exp else att * pp
+    exp_dev = exp if exp else pp
     t_experts = comp["one_expert_all_layers"] * act_exp / max(exp_dev, 1)
     t_backbone = (comp["attention"] + comp["dense_ffn"] + comp["shared_experts"] + comp["head"]) / att \
         + req.concurrency * min(req.max_context_tokens, 8192) * kv_tok_layer * cfg.num_layers / kv_shard
