@@ -212,6 +212,17 @@ class Arr:
         return NO
 
 
+class _Finished:
+    """Stands in for an alternative that has matched completely while others can still grow (5 of an enum against
+    the integer 50): the value may end here, and any further byte is not this frame's."""
+
+    def can_end(self) -> bool:
+        return True
+
+    def feed(self, b: int) -> int:
+        return PASS
+
+
 class Alt:
     """Several alternatives in parallel; the ones that reject a byte drop out."""
 
@@ -226,13 +237,12 @@ class Alt:
         live = [(x, r) for x, r in res if r != NO]
         if not live:
             return NO
-        if any(r == DONE for _, r in live):
-            return DONE
+        done = any(r == DONE for _, r in live)
         more = [x for x, r in live if r == MORE]
-        if more:
-            self.f = more
+        if more:                                  # finished for good only when nothing can grow any further
+            self.f = more + ([_Finished()] if done else [])
             return MORE
-        return PASS
+        return DONE if done else PASS
 
 
 class AnyJson:

@@ -42,6 +42,10 @@ def test_scalars_arrays_alternatives_and_any():
     assert accepts({"type": ["null", "boolean"]}, "null") and accepts({"type": ["null", "boolean"]}, "false")
     assert accepts({"anyOf": [{"type": "integer"}, {"type": "string"}]}, '"x"') and accepts({"anyOf": [{"type": "integer"}, {"type": "string"}]}, "42")
     assert accepts({"const": {"a": 1}}, '{"a":1}')
+    # an alternative that is complete does not end the value while another can still grow
+    both = {"anyOf": [{"enum": ["", 5]}, {"type": "integer"}]}
+    assert accepts(both, "5") and accepts(both, "50") and accepts(both, '""') and not accepts(both, "5x")
+    assert accepts({"type": "array", "items": both}, "[5,50,5]")
     nested = {"type": "object", "properties": {"p": {"type": "object", "properties": {"q": {"type": "array", "items": {}}}}}}
     assert accepts(nested, '{"p":{"q":[1,"x",{"k":[true,null]},[2]]}}')
     assert accepts({}, '{"free":[1,2]}') and accepts({}, "3") and accepts({"type": "object"}, '{"a": 1}')
