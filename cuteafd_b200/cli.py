@@ -40,7 +40,7 @@ REFERENCE_KEYS = {
     "HTTP_QUEUE_WAIT_MS": ("HTTP_QUEUE_WAIT", lambda v: str(float(v) / 1000.0)), "HOST_CACHE_BYTES": ("HOST_CACHE_GIB", _gib),
 }
 REFERENCE_SKIPPED = ("SPARK_", "COORDINATOR_", "SPARKINFER_", "TP2_", "CUTEAFD_", "MODEL_VARIANT", "MODEL_REVISION", "EXPERT_PORT",
-                     "INSTANCE", "PREFIX_CACHE_ENTRIES", "MAX_OUTPUT_TOKENS", "KV_POOL_SIZE", "KV_MIN_TOKENS", "KV_MAX_TOKENS",
+                     "INSTANCE", "PREFIX_CACHE_ENTRIES", "KV_POOL_SIZE", "KV_MIN_TOKENS", "KV_MAX_TOKENS",
                      "KV_DECODE_RESERVE_CHUNK", "KV_RESERVE_DRAIN_BUFFER", "KV_EARLY_TERMINATION_MIN_OUTPUT_TOKENS", "DRAFT_LENGTH",
                      "RTX_EXPERT_LAYERS", "FULL_PREFILL_LOGITS")
 REFERENCE_SPECULATORS = {"dspark": "auto", "dflash2": "auto"}      # trained block drafters of the reference's checkpoints
@@ -95,7 +95,8 @@ def load_config_file(path: str, overrides: list[str], known: set[str]) -> dict[s
 CONFIG_KEYS = {"MODEL", "EMBEDDING_PLACEMENT", "GPUS", "ATTENTION_RANKS", "EXPERT_RANKS", "POOL_TOKENS", "GPU_MEMORY_CAP", "MAX_CONTEXT_TOKENS",
                "CONCURRENCY", "SPECULATOR", "DECODE_LANES", "PORT", "HOST", "API_KEY", "DECODE_SHARE", "PREFILL_ROWS",
                "HTTP_QUEUE_DEPTH", "HTTP_QUEUE_WAIT", "PROFILE", "SPECULATION_TRACE", "KV_FORMAT", "EXPERT_FORMAT",
-               "HOST_CACHE_GIB", "LOOP_ABORT_RUN", "LOOP_ABORT_COPIES", "LOOP_FAST_SPAN", "LOOP_FAST_COPIES", "BATCH_INVARIANT"}
+               "HOST_CACHE_GIB", "LOOP_ABORT_RUN", "LOOP_ABORT_COPIES", "LOOP_FAST_SPAN", "LOOP_FAST_COPIES", "BATCH_INVARIANT",
+               "MAX_OUTPUT_TOKENS"}
 
 
 def graph_reserve_of(value: str) -> tuple[int, str]:
@@ -462,6 +463,9 @@ def _build_parser() -> argparse.ArgumentParser:
     s.add_argument("--max-context-tokens", type=int, default=16384); s.add_argument("--concurrency", type=int, default=8)
     s.add_argument("--speculator", default="auto"); s.add_argument("--layers", type=int, default=0)
     s.add_argument("--queue-depth", type=int, default=64); s.add_argument("--queue-wait", type=float, default=30.0)
+    s.add_argument("--max-output-tokens", type=int, default=int(os.environ.get("CUTEAFD_MAX_OUTPUT_TOKENS", 0)),
+                   help="most output tokens a request may ask for, and what a request that names no limit gets; 0 = bounded by the "
+                        "context alone (such a request then gets 256)")
     s.add_argument("--fake-engine", action="store_true", help="serve with the CPU oracle engine (no GPU)")
     s.add_argument("--usage-db", default=""); s.add_argument("--memory-spool", default="", help="file opened at start-up that receives the ledger's state when an allocation fails"); s.add_argument("--kv-format", default="auto", choices=["auto", "bf16", "fp8_ds_mla"])
     s.add_argument("--batch-invariant", action="store_true", default=os.environ.get("CAFD_BATCH_INVARIANT", "0") == "1",

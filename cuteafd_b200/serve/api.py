@@ -182,7 +182,9 @@ def anthropic_messages(body: dict) -> list[dict]:
 
 
 def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, flavor: str = "openai",
-                  media=None) -> Request:
+                  media=None, max_output_tokens: int = 0) -> Request:
+    """``max_output_tokens`` > 0 (the deployment's MAX_OUTPUT_TOKENS): the most a request may ask for, and what a request
+    that names no limit gets; 0 leaves the limit to the context and gives such a request 256 tokens."""
     # a probe too large for a header (a long synthetic prompt) may ride in the body instead
     probe = {**(body.get("cuteafd_probe") or {}), **(probe or {})}
     if probe.get("prompt_ids"):
@@ -214,9 +216,11 @@ def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, f
                 raise BadRequest(str(e)) from e
         else:
             prompt, spans = tok.encode(text), None
-    max_tokens = body.get("max_tokens") or body.get("max_completion_tokens") or body.get("max_output_tokens") or 256
-    if not isinstance(max_tokens, int) or max_tokens < 1:
+    max_tokens = body.get("max_tokens") or body.get("max_completion_tokens") or body.get("max_output_tokens") or (max_output_tokens or 256)
+    if not isinstance(max_tokens, int) or isinstance(max_tokens, bool) or max_tokens < 1:
         raise BadRequest("max_tokens must be a positive integer")
+    if max_output_tokens > 0:
+        max_tokens = min(max_tokens, max_output_tokens)
     fmt = body.get("response_format")
     if fmt is None:                                        # the guided_* spellings some clients send at the top level
         if "guided_regex" in body:

@@ -267,7 +267,8 @@ def make_handler(state: ServerState):
                     conv = body["input"] if isinstance(body.get("input"), list) else [{"role": "user", "content": body.get("input") or ""}]
                     body = dict(body, input=list(conv) + [{"role": "user", "content": api.COMPACT_REQUEST}], stream=False)
                     body.setdefault("max_output_tokens", 1024)
-                req = api.build_request(body, state.tok, state.sched.be.vocab_size, probe, flavor, state.media)
+                req = api.build_request(body, state.tok, state.sched.be.vocab_size, probe, flavor, state.media,
+                                        max_output_tokens=int(state.extras.get("max_output_tokens", 0) or 0))
             except api.BadRequest as e:
                 st, eb, hd = api.error_body(FAIL_BAD_REQUEST, str(e), flavor)
                 return self._json(st, eb, hd)
@@ -620,7 +621,8 @@ def build_state(args) -> ServerState:
             audio = audio or AudioTower(AudioTowerConfig(**small), AudioTower.random_weights(AudioTowerConfig(**small)), mdev)
         if vision is not None or audio is not None:
             media = MediaProcessor(cfg.vocab_size, cfg.hidden, vision, audio)
-    return ServerState(sched, tok, cfg.name, args.api_key, usage, media=media)
+    return ServerState(sched, tok, cfg.name, args.api_key, usage, media=media,
+                       extras={"max_output_tokens": int(getattr(args, "max_output_tokens", 0) or 0)})
 
 
 _AFD_HANDLE = None

@@ -182,7 +182,8 @@ def _generate(state, ws: Socket, body: dict, flavor: str, on_text, cancel_types:
     """Submit a request and pump its events; returns ("done", finish, usage, text) | ("error", kind, message) |
     ("cancelled", text).  Client frames that arrive meanwhile are looked at for a cancel."""
     try:
-        req = api.build_request(body, state.tok, state.sched.be.vocab_size, None, flavor, getattr(state, "media", None))
+        req = api.build_request(body, state.tok, state.sched.be.vocab_size, None, flavor, getattr(state, "media", None),
+                                max_output_tokens=int(getattr(state, "extras", {}).get("max_output_tokens", 0) or 0))
     except api.BadRequest as e:
         return ("error", "invalid_request_error", str(e))
     if not state.sched.ready.is_set():

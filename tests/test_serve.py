@@ -641,3 +641,17 @@ def test_gateway_get_carries_the_key(server):
         assert get("/v1/models", "wrong")[0] == 401 and get("/v1/models", "")[0] == 401
     finally:
         gw.stop()
+
+
+def test_deployment_cap_on_output_tokens():
+    """MAX_OUTPUT_TOKENS: the most a request may ask for, and what a request that names no limit gets."""
+    from cuteafd_b200.serve import api
+    from cuteafd_b200.serve.tokenizer import load_tokenizer
+    tok = load_tokenizer(None, 512)
+    body = {"messages": [{"role": "user", "content": "hi"}]}
+    assert api.build_request(body, tok, 512).max_tokens == 256
+    assert api.build_request(body, tok, 512, max_output_tokens=40).max_tokens == 40
+    assert api.build_request(dict(body, max_tokens=1000), tok, 512, max_output_tokens=40).max_tokens == 40
+    assert api.build_request(dict(body, max_tokens=7), tok, 512, max_output_tokens=40).max_tokens == 7
+    with pytest.raises(api.BadRequest):
+        api.build_request(dict(body, max_tokens=True), tok, 512)
