@@ -122,7 +122,7 @@ class SchedulerStats:
 class Scheduler:
     def __init__(self, backend: Backend, *, max_active: int = 32, queue_depth: int = 64, queue_wait_s: float = 30.0,
                  decode_share: float = 0.2, drafter=None, draft_control: str = "history", row_budget: int | None = None,
-                 eos_ids: tuple[int, ...] = (), decode_lanes: int = 1, loop_abort=None):
+                 eos_ids: tuple[int, ...] = (), decode_lanes: int = 1, loop_abort=None, reserve_chunk_tokens: int = 0):
         self.be = backend
         self.loop_abort = loop_abort          # LoopAbortConfig or None (runtime/repeat_guard.py)
         self.trace = None                     # utils.trace.JsonlTrace: one record per decode round when set
@@ -139,7 +139,10 @@ class Scheduler:
         self.pending: list[Request] = []
         self.prefilling: list[Active] = []
         self.decoding: list[Active] = []
-        self.reserve = make_reserve(backend.total_pages - 1)     # page 0 is the reserved zero page; C++ reserve when the library loads
+        # page 0 is the reserved zero page; C++ reserve when the library loads.  ``reserve_chunk_tokens``: the decode chunk
+        # a request leases beyond its prompt and tops up by (0 = the default of 16 384 tokens)
+        self.reserve = (make_reserve(backend.total_pages - 1, reserve_chunk_tokens) if reserve_chunk_tokens > 0
+                        else make_reserve(backend.total_pages - 1))
         self.drafter = drafter or NoDrafter()
         self.policy = DraftHistory(self.drafter.spec if hasattr(self.drafter, "spec") else DrafterSpec(0), draft_control)
         self.row_budget = row_budget or backend.max_decode_rows

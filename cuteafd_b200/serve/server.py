@@ -587,7 +587,8 @@ def build_state(args) -> ServerState:
                            getattr(args, "loop_fast_span", 1024), getattr(args, "loop_fast_copies", 8))
     sched = Scheduler(be, max_active=args.concurrency, queue_depth=args.queue_depth, queue_wait_s=args.queue_wait,
                       loop_abort=loop if loop.enabled else None,
-                      drafter=drafter, eos_ids=tuple(getattr(tok, "eos_ids", ())))
+                      drafter=drafter, eos_ids=tuple(getattr(tok, "eos_ids", ())),
+                      reserve_chunk_tokens=int(getattr(args, "kv_decode_reserve_chunk", 0) or 0))
     prof = getattr(args, "profile", "") or os.environ.get("PROFILE", "")
     if prof:
         from ..utils.profile import Profile, parse_modes
