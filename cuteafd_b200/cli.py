@@ -40,7 +40,7 @@ REFERENCE_KEYS = {
     "HTTP_QUEUE_WAIT_MS": ("HTTP_QUEUE_WAIT", lambda v: str(float(v) / 1000.0)), "HOST_CACHE_BYTES": ("HOST_CACHE_GIB", _gib),
 }
 REFERENCE_SKIPPED = ("SPARK_", "COORDINATOR_", "SPARKINFER_", "TP2_", "CUTEAFD_", "MODEL_VARIANT", "MODEL_REVISION", "EXPERT_PORT",
-                     "INSTANCE", "PREFIX_CACHE_ENTRIES", "KV_POOL_SIZE", "KV_MIN_TOKENS", "KV_MAX_TOKENS",
+                     "INSTANCE", "KV_POOL_SIZE", "KV_MIN_TOKENS", "KV_MAX_TOKENS",
                      "KV_RESERVE_DRAIN_BUFFER", "KV_EARLY_TERMINATION_MIN_OUTPUT_TOKENS", "DRAFT_LENGTH",
                      "RTX_EXPERT_LAYERS", "FULL_PREFILL_LOGITS")
 REFERENCE_SPECULATORS = {"dspark": "auto", "dflash2": "auto"}      # trained block drafters of the reference's checkpoints
@@ -96,7 +96,7 @@ CONFIG_KEYS = {"MODEL", "EMBEDDING_PLACEMENT", "GPUS", "ATTENTION_RANKS", "EXPER
                "CONCURRENCY", "SPECULATOR", "DECODE_LANES", "PORT", "HOST", "API_KEY", "DECODE_SHARE", "PREFILL_ROWS",
                "HTTP_QUEUE_DEPTH", "HTTP_QUEUE_WAIT", "PROFILE", "SPECULATION_TRACE", "KV_FORMAT", "EXPERT_FORMAT",
                "HOST_CACHE_GIB", "LOOP_ABORT_RUN", "LOOP_ABORT_COPIES", "LOOP_FAST_SPAN", "LOOP_FAST_COPIES", "BATCH_INVARIANT",
-               "MAX_OUTPUT_TOKENS", "KV_DECODE_RESERVE_CHUNK"}
+               "MAX_OUTPUT_TOKENS", "KV_DECODE_RESERVE_CHUNK", "PREFIX_CACHE_ENTRIES"}
 
 
 def graph_reserve_of(value: str) -> tuple[int, str]:
@@ -463,6 +463,8 @@ def _build_parser() -> argparse.ArgumentParser:
     s.add_argument("--max-context-tokens", type=int, default=16384); s.add_argument("--concurrency", type=int, default=8)
     s.add_argument("--speculator", default="auto"); s.add_argument("--layers", type=int, default=0)
     s.add_argument("--queue-depth", type=int, default=64); s.add_argument("--queue-wait", type=float, default=30.0)
+    s.add_argument("--prefix-cache-entries", type=int, default=0,
+                   help="snapshots the prefix cache retains at most (0 = as many as half the KV pool holds); the least recently used goes first")
     s.add_argument("--kv-decode-reserve-chunk", type=int, default=0,
                    help="tokens a request leases beyond its prompt and tops up by when decode reaches them (0 = 16384)")
     s.add_argument("--max-output-tokens", type=int, default=int(os.environ.get("CUTEAFD_MAX_OUTPUT_TOKENS", 0)),

@@ -93,6 +93,7 @@ class PrefixCache:
         self.root = Node(b"", 0, None)
         self.snapshots: dict[int, Snapshot] = {}
         self.max_pages = max_pages if max_pages is not None else pool.num_pages // 2
+        self.max_entries = 0                      # retained snapshots at most (0 = bounded by pages alone); PREFIX_CACHE_ENTRIES
         self.held_pages = 0                       # pages retained by the cache (radix nodes + tails)
         self.clock = 0
         self.stats = PrefixStats()
@@ -258,7 +259,8 @@ class PrefixCache:
             for kind in (PROMPT, TURN):
                 for s in sorted((s for s in self.snapshots.values() if s.kind == kind), key=lambda s: s.last_use):
                     yield s
-        while self.held_pages + pages_needed > self.max_pages and self.snapshots:
+        while self.snapshots and (self.held_pages + pages_needed > self.max_pages
+                                  or (self.max_entries and len(self.snapshots) >= self.max_entries)):
             v = next(victims(), None)
             if v is None:
                 break

@@ -557,6 +557,7 @@ def build_state(args) -> ServerState:
                 with open(pw) as f:
                     n = be.prewarm(json.load(f).get("geometries", []))
                 print(f"prewarmed {n} decode graphs from {pw}", flush=True)
+    be.prefix.max_entries = max(0, int(getattr(args, "prefix_cache_entries", 0) or 0))
     tok = load_tokenizer(snapshot, cfg.vocab_size)
     drafter = NgramDrafter(block=4) if args.speculator in ("auto", "history", "ngram") else None
     if args.speculator in ("draft-model", "block-draft"):

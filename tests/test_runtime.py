@@ -566,3 +566,21 @@ def test_block_drafter_drafts_a_block_in_one_pass_and_is_lossless(oracle):
     sp = out["usage"]["speculation"]
     assert out["tokens"] == base["tokens"] and sp["proposed"] > 0 and sp["accepted"] >= sp["cycles"] - 2      # position 1 of every block
     assert blk.passes <= sp["cycles"] and blk.drafted >= 2 * blk.passes and blk.state == {}                    # one pass per round, several drafts
+
+
+def test_prefix_cache_entry_cap_evicts_the_least_recently_used():
+    from cuteafd_b200.runtime.paged import PagePool, SequenceTable
+    from cuteafd_b200.runtime.prefix_cache import PrefixCache
+    pool = PagePool(64)
+    table = SequenceTable(pool)
+    cache = PrefixCache(pool, table, max_pages=48)
+    cache.max_entries = 2
+    kept = []
+    for i in range(4):
+        s = table.new()
+        table.reserve(s, 70)
+        s.tokens, s.kv_len = [i] * 70, 70
+        kept.append(cache.capture(s))
+        table.free(s)
+    assert len(cache.snapshots) == 2 and set(cache.snapshots) == {kept[2].sid, kept[3].sid}
+    assert cache.lookup([0] * 70 + [9]).length == 0 and cache.lookup([3] * 70 + [9]).length == 70
