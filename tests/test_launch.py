@@ -167,3 +167,16 @@ def test_a_reference_configuration_file_is_accepted(tmp_path, capsys):
         ("/models/x", 16, 8123, "0.0.0.0", 2.5, 8.0, "host", 256)
     with pytest.raises(SystemExit):
         cli.load_config_file("", ["SOMETHING_ELSE=1"], cli.CONFIG_KEYS)
+
+
+@pytest.mark.parametrize("name,world,engine", [("qwen3-30b-a3b-1gpu", 1, "single"), ("deepseek-v3-8gpu", 8, "afd"),
+                                               ("qwen3-30b-a3b-head-split-2gpu", 2, "tp"), ("reference-style", 4, "afd")])
+def test_example_configurations_plan_and_dry_run(name, world, engine, tmp_path, capsys):
+    """Every shipped example is a complete launch: it parses, plans on the GPUs it names and passes the launcher's checks."""
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "configs", name + ".config")
+    extra = ["--gpus", "4"] if name == "reference-style" else []
+    assert cli.main(["--config", path, "launch", "--dry-run", "--run-dir", str(tmp_path)] + extra) == 0
+    spec = json.load(open(tmp_path / "deployment.json"))
+    assert spec["world_size"] == world and spec["engine"] == engine
+    out = capsys.readouterr().out
+    assert out.count("cuteafd_b200.cli serve") == world
