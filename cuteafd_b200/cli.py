@@ -26,6 +26,18 @@ def _size(s: str) -> int:
     return int(s)
 
 
+def _size_bytes(s: str) -> int:
+    """Sizes as the reference writes them: decimal or binary units, fractions allowed (22.5GB, 90GiB, 512MiB, 1048576B)."""
+    t = s.strip().lower()
+    if t.endswith("b") and not t.endswith(("gb", "mb", "kb", "ib")):
+        t = t[:-1]
+    if t.endswith("kib"):
+        return int(float(t[:-3]) * 1024)
+    if t.endswith("kb"):
+        return int(float(t[:-2]) * 1000)
+    return _size(t)
+
+
 def _gib(v: str) -> str:
     return f"{_size(v) / (1 << 30):.3f}"
 
@@ -40,7 +52,7 @@ REFERENCE_KEYS = {
     "HTTP_QUEUE_WAIT_MS": ("HTTP_QUEUE_WAIT", lambda v: str(float(v) / 1000.0)), "HOST_CACHE_BYTES": ("HOST_CACHE_GIB", _gib),
 }
 REFERENCE_SKIPPED = ("SPARK_", "COORDINATOR_", "SPARKINFER_", "TP2_", "CUTEAFD_", "MODEL_VARIANT", "MODEL_REVISION", "EXPERT_PORT",
-                     "INSTANCE", "KV_POOL_SIZE", "KV_MIN_TOKENS", "KV_MAX_TOKENS",
+                     "INSTANCE", "KV_MIN_TOKENS", "KV_MAX_TOKENS",
                      "KV_RESERVE_DRAIN_BUFFER", "KV_EARLY_TERMINATION_MIN_OUTPUT_TOKENS", "DRAFT_LENGTH",
                      "RTX_EXPERT_LAYERS", "FULL_PREFILL_LOGITS")
 REFERENCE_SPECULATORS = {"dspark": "auto", "dflash2": "auto"}      # trained block drafters of the reference's checkpoints
@@ -96,7 +108,7 @@ CONFIG_KEYS = {"MODEL", "EMBEDDING_PLACEMENT", "GPUS", "ATTENTION_RANKS", "EXPER
                "CONCURRENCY", "SPECULATOR", "DECODE_LANES", "PORT", "HOST", "API_KEY", "DECODE_SHARE", "PREFILL_ROWS",
                "HTTP_QUEUE_DEPTH", "HTTP_QUEUE_WAIT", "PROFILE", "SPECULATION_TRACE", "KV_FORMAT", "EXPERT_FORMAT",
                "HOST_CACHE_GIB", "LOOP_ABORT_RUN", "LOOP_ABORT_COPIES", "LOOP_FAST_SPAN", "LOOP_FAST_COPIES", "BATCH_INVARIANT",
-               "MAX_OUTPUT_TOKENS", "KV_DECODE_RESERVE_CHUNK", "PREFIX_CACHE_ENTRIES"}
+               "MAX_OUTPUT_TOKENS", "KV_DECODE_RESERVE_CHUNK", "PREFIX_CACHE_ENTRIES", "KV_POOL_SIZE"}
 
 
 def graph_reserve_of(value: str) -> tuple[int, str]:
@@ -121,6 +133,7 @@ def cmd_plan(a: argparse.Namespace) -> int:
         print(json.dumps(info, indent=1))
         return 0
     kw = dict(gpus=a.gpus, attention_ranks=a.attention_ranks, expert_ranks=a.expert_ranks, pool_tokens_target=a.pool_tokens,
+              kv_pool_bytes=_size_bytes(a.kv_pool_size) if getattr(a, "kv_pool_size", "") else None,
               gpu_memory_cap=_size(a.gpu_memory_cap) if a.gpu_memory_cap else None, max_context_tokens=a.max_context_tokens,
               concurrency=a.concurrency, speculator=a.speculator, decode_lanes=a.decode_lanes,
               pipeline_stages=a.pipeline_stages, expert_format=a.expert_format, kv_format=a.kv_format)
@@ -162,6 +175,7 @@ def cmd_launch(a: argparse.Namespace) -> int:
             return 2
         rep = P.plan(a.model, layout=True, gpus=a.gpus, attention_ranks=a.attention_ranks, expert_ranks=a.expert_ranks,
                      pool_tokens_target=a.pool_tokens, gpu_memory_cap=_size(a.gpu_memory_cap) if a.gpu_memory_cap else None,
+                     kv_pool_bytes=_size_bytes(a.kv_pool_size) if getattr(a, "kv_pool_size", "") else None,
                      max_context_tokens=a.max_context_tokens, concurrency=a.concurrency, speculator=a.speculator,
                      decode_lanes=a.decode_lanes)
         if not (rep.placement and rep.placement.ok and rep.ready):
@@ -448,6 +462,7 @@ def _build_parser() -> argparse.ArgumentParser:
     p.add_argument("--gpus", type=int, default=8); p.add_argument("--attention-ranks", type=int, default=None)
     p.add_argument("--expert-ranks", type=int, default=None); p.add_argument("--pipeline-stages", type=int, default=1)
     p.add_argument("--pool-tokens", type=int, default=None); p.add_argument("--gpu-memory-cap", default="")
+    p.add_argument("--kv-pool-size", default="", help="KV pool target as a size per attention GPU (22.5GB, 90GiB) instead of --pool-tokens")
     p.add_argument("--max-context-tokens", type=int, default=None); p.add_argument("--concurrency", type=int, default=None)
     p.add_argument("--speculator", default=None, choices=["auto", "off", "mtp"]); p.add_argument("--decode-lanes", type=int, default=None, choices=[1, 2])
     p.add_argument("--format", default=None); p.add_argument("--expert-format", default=None); p.add_argument("--kv-format", default=None)
@@ -510,6 +525,7 @@ def _build_parser() -> argparse.ArgumentParser:
     la.add_argument("--gpus", type=int, default=8, help="GPUs of the box to plan for")
     la.add_argument("--attention-ranks", type=int, default=1); la.add_argument("--expert-ranks", type=int, default=None)
     la.add_argument("--pool-tokens", type=int, default=None); la.add_argument("--gpu-memory-cap", default="")
+    la.add_argument("--kv-pool-size", default="", help="KV pool target as a size per attention GPU (22.5GB, 90GiB) instead of --pool-tokens")
     la.add_argument("--max-context-tokens", type=int, default=None, help="longest context a request may reach")
     la.add_argument("--concurrency", type=int, default=None, help="requests decoded together")
     la.add_argument("--speculator", default=None, choices=["auto", "off", "mtp"], help="speculative decoding to plan for and serve with")

@@ -69,6 +69,11 @@ def plan(model: str, *, layout: bool = False, fmt: str | None = None, **req_kw) 
     rep = PlanReport(cfg.name, source, fam.id if fam else None, cfg, {r: dict(c) for r, c in formats_by_role.items()},
                      stored, hints, role_files={r: sorted(f) for r, f in role_files.items()})
     if layout:
+        pool_bytes = req_kw.pop("kv_pool_bytes", None)
+        if pool_bytes and req_kw.get("pool_tokens_target") is None:
+            # a pool given in bytes (the reference's KV_POOL_SIZE): tokens of this model's cache record that fit in it
+            per_token = solver.kv_bytes_per_token_per_layer(cfg, req_kw.get("kv_format") or "auto") * cfg.num_layers
+            req_kw["pool_tokens_target"] = max(64, int(pool_bytes) // per_token // 64 * 64)
         rep.request = solver.PlacementRequest(cfg, **{k: v for k, v in req_kw.items() if v is not None})
         rep.placement = solver.solve(rep.request)
     return rep
