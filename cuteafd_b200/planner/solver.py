@@ -302,7 +302,7 @@ def candidates(req: PlacementRequest) -> list[tuple[int, int, int]]:
         elif not cfg.num_experts:
             exp_opts = [0]
         else:
-            exp_opts = sorted({0, rest} - ({rest} if rest <= 0 else set())) if rest >= 0 else []
+            exp_opts = sorted({0} | ({rest} if rest > 0 else set())) if rest >= 0 else []      # colocated, or every other GPU
         for e in exp_opts:
             if e >= 0 and a * pp + e <= req.gpus:
                 out.append((a, e, pp))

@@ -76,6 +76,13 @@ def test_config_file_refuses_unknown_keys(tmp_path):
     assert e.value.code == 2
 
 
+def test_auto_layout_on_one_gpu_is_the_colocated_one():
+    from cuteafd_b200 import qwen3_30b_a3b
+    from cuteafd_b200.planner.solver import PlacementRequest, solve
+    p = solve(PlacementRequest(qwen3_30b_a3b(), gpus=1))
+    assert p.ok and (p.attention_ranks, p.expert_ranks, p.engine) == (1, 0, "single")
+
+
 def test_plan_names_the_engine_that_serves_it():
     from cuteafd_b200 import deepseek_v3, qwen3_30b_a3b
     from cuteafd_b200.planner.solver import PlacementRequest, engine_for, solve, solve_frozen
