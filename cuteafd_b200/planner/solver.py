@@ -264,9 +264,29 @@ def _place(req: PlacementRequest, att: int, exp: int, pp: int) -> Placement:
                      req.decode_lanes, notes, score=1.0 / max(step, 1.0))
 
 
+def kernel_geometry(cfg: ModelConfig) -> str:
+    """Why the CUDA engines cannot run this geometry ("" = they can): their attention kernels are written for one head
+    shape per family."""
+    if cfg.is_mla:
+        if (cfg.kv_lora_rank, cfg.qk_rope_dim, cfg.qk_nope_dim, cfg.v_head_dim) != (512, 64, 128, 128):
+            return "the MLA kernels take the DeepSeek shape (latent 512, rope 64, nope 128, value 128)"
+        if 128 % cfg.num_heads:
+            return "the MLA kernels take a head count that divides 128"
+        return ""
+    if cfg.head_dim != 128:
+        return "the GQA kernels take head_dim 128"
+    g = cfg.num_heads // max(cfg.num_kv_heads, 1)
+    if cfg.num_heads % max(cfg.num_kv_heads, 1) or g > 16 or 16 % g:
+        return "the GQA decode kernel takes 1, 2, 4, 8 or 16 query heads per kv head"
+    return ""
+
+
 def engine_for(cfg: ModelConfig, att: int, exp: int, pp: int) -> tuple[str, str]:
     """(engine that serves the layout, note).  The solver sizes any (attention TP, expert EP, stages) split; this names
     the code path that runs it, so a plan never silently proposes a layout nothing can execute."""
+    why = kernel_geometry(cfg)
+    if why:
+        return "", why + "; the CPU oracle serves this checkpoint (serve --fake-engine)"
     if pp > 1:
         if att == 1 and exp == 0 and not cfg.is_mla:
             return "pp", "layer ranges as pipeline stages with ring hops (models/pp_gqa.py)"

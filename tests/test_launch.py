@@ -92,9 +92,11 @@ def test_launcher_stops_its_ranks_on_sigterm(tmp_path):
 
 
 def test_launch_dry_run_plans_a_snapshot(tmp_path, capsys):
-    from cuteafd_b200 import tiny_moe
+    from cuteafd_b200 import qwen3_30b_a3b, scaled_down
     from cuteafd_b200.loader.snapshot import write_random_snapshot
-    snap = write_random_snapshot(tiny_moe(), str(tmp_path / "snap"), fmt="bf16", seed=0)
+    small = scaled_down(qwen3_30b_a3b(), layers=1, vocab=512).replace(hidden=256, num_heads=2, num_kv_heads=1, num_experts=8, top_k=2,
+                                                                     expert_ffn=64, name="qwen3-moe-mini")
+    snap = write_random_snapshot(small, str(tmp_path / "snap"), fmt="bf16", seed=0)
     rc = cli.main(["launch", snap, "--gpus", "3", "--attention-ranks", "1", "--expert-ranks", "2", "--dry-run", "--run-dir",
                    str(tmp_path / "run"), "--port", "8111"])
     out = capsys.readouterr().out
@@ -102,6 +104,11 @@ def test_launch_dry_run_plans_a_snapshot(tmp_path, capsys):
     spec = json.load(open(tmp_path / "run" / "deployment.json"))
     assert spec["world_size"] == 3 and [tuple(r["experts"]) for r in spec["ranks"][1:]] == [(0, 4), (4, 8)]
     assert out.count("cuteafd_b200.cli serve") == 3 and "--port 8111" in out
+    # a geometry the CUDA kernels do not take is refused with the reason, not started
+    from cuteafd_b200 import tiny_moe
+    odd = write_random_snapshot(tiny_moe(), str(tmp_path / "odd"), fmt="bf16", seed=0)
+    assert cli.main(["launch", odd, "--gpus", "1", "--dry-run", "--run-dir", str(tmp_path / "r0")]) == 1
+    assert "fake-engine" in capsys.readouterr().err
     # an edited document is refused; the stored one starts (dry) as it is
     assert cli.main(["launch", "--deployment", str(tmp_path / "run" / "deployment.json"), "--dry-run", "--run-dir", str(tmp_path / "r2")]) == 0
     spec["world_size"] = 4
