@@ -15,7 +15,17 @@ import os
 import struct
 from dataclasses import dataclass
 
+import warnings
+
 import torch
+
+
+def _view(buf, nbytes: int, offset: int) -> torch.Tensor:
+    """Bytes of a read-only file mapping as a uint8 tensor (no copy).  Every caller converts or copies what it reads and
+    nothing writes through the view, so torch's warning about a non-writable buffer says nothing new here."""
+    with warnings.catch_warnings():
+        warnings.filterwarnings("ignore", message="The given buffer is not writable")
+        return torch.frombuffer(buf, dtype=torch.uint8, count=nbytes, offset=offset)
 
 DTYPES = {
     "F32": (torch.float32, 4), "F16": (torch.float16, 2), "BF16": (torch.bfloat16, 2),
@@ -99,7 +109,7 @@ class Catalog:
         e = self.entries[name]
         dt, size = DTYPES[e.dtype]
         buf = self._map(e.file)
-        t = torch.frombuffer(buf, dtype=torch.uint8, count=e.nbytes, offset=e.begin)
+        t = _view(buf, e.nbytes, e.begin)
         return t.view(dt).view(e.shape) if e.numel else torch.empty(e.shape, dtype=dt)
 
     def read_rows(self, name: str, first: int, count: int) -> torch.Tensor:
@@ -108,7 +118,7 @@ class Catalog:
         dt, size = DTYPES[e.dtype]
         row = e.numel // e.shape[0] * size
         buf = self._map(e.file)
-        t = torch.frombuffer(buf, dtype=torch.uint8, count=row * count, offset=e.begin + first * row)
+        t = _view(buf, row * count, e.begin + first * row)
         return t.view(dt).view((count, *e.shape[1:]))
 
     def sha256(self, name: str) -> str:
