@@ -53,7 +53,7 @@ REFERENCE_KEYS = {
 }
 REFERENCE_SKIPPED = ("SPARK_", "COORDINATOR_", "SPARKINFER_", "TP2_", "CUTEAFD_", "MODEL_VARIANT", "MODEL_REVISION", "EXPERT_PORT",
                      "INSTANCE", "KV_MIN_TOKENS", "KV_MAX_TOKENS",
-                     "KV_RESERVE_DRAIN_BUFFER", "KV_EARLY_TERMINATION_MIN_OUTPUT_TOKENS", "DRAFT_LENGTH",
+                     "KV_RESERVE_DRAIN_BUFFER", "DRAFT_LENGTH",
                      "RTX_EXPERT_LAYERS", "FULL_PREFILL_LOGITS")
 REFERENCE_SPECULATORS = {"dspark": "auto", "dflash2": "auto"}      # trained block drafters of the reference's checkpoints
 
@@ -108,7 +108,8 @@ CONFIG_KEYS = {"MODEL", "EMBEDDING_PLACEMENT", "GPUS", "ATTENTION_RANKS", "EXPER
                "CONCURRENCY", "SPECULATOR", "DECODE_LANES", "PORT", "HOST", "API_KEY", "DECODE_SHARE", "PREFILL_ROWS",
                "HTTP_QUEUE_DEPTH", "HTTP_QUEUE_WAIT", "PROFILE", "SPECULATION_TRACE", "KV_FORMAT", "EXPERT_FORMAT",
                "HOST_CACHE_GIB", "LOOP_ABORT_RUN", "LOOP_ABORT_COPIES", "LOOP_FAST_SPAN", "LOOP_FAST_COPIES", "BATCH_INVARIANT",
-               "MAX_OUTPUT_TOKENS", "KV_DECODE_RESERVE_CHUNK", "PREFIX_CACHE_ENTRIES", "KV_POOL_SIZE"}
+               "MAX_OUTPUT_TOKENS", "KV_DECODE_RESERVE_CHUNK", "PREFIX_CACHE_ENTRIES", "KV_POOL_SIZE",
+               "KV_EARLY_TERMINATION_MIN_OUTPUT_TOKENS"}
 
 
 def graph_reserve_of(value: str) -> tuple[int, str]:
@@ -478,6 +479,9 @@ def _build_parser() -> argparse.ArgumentParser:
     s.add_argument("--max-context-tokens", type=int, default=16384); s.add_argument("--concurrency", type=int, default=8)
     s.add_argument("--speculator", default="auto"); s.add_argument("--layers", type=int, default=0)
     s.add_argument("--queue-depth", type=int, default=64); s.add_argument("--queue-wait", type=float, default=30.0)
+    s.add_argument("--kv-early-termination-min-output-tokens", type=int, default=-1,
+                   help="end a request that would stall for KV with finish_reason length (finish_detail kv_pressure) once it has "
+                        "produced this many tokens; -1 = off: requests stall, never end early")
     s.add_argument("--prefix-cache-entries", type=int, default=0,
                    help="snapshots the prefix cache retains at most (0 = as many as half the KV pool holds); the least recently used goes first")
     s.add_argument("--kv-decode-reserve-chunk", type=int, default=0,

@@ -122,8 +122,12 @@ class SchedulerStats:
 class Scheduler:
     def __init__(self, backend: Backend, *, max_active: int = 32, queue_depth: int = 64, queue_wait_s: float = 30.0,
                  decode_share: float = 0.2, drafter=None, draft_control: str = "history", row_budget: int | None = None,
-                 eos_ids: tuple[int, ...] = (), decode_lanes: int = 1, loop_abort=None, reserve_chunk_tokens: int = 0):
+                 eos_ids: tuple[int, ...] = (), decode_lanes: int = 1, loop_abort=None, reserve_chunk_tokens: int = 0,
+                 early_end_tokens: int = -1):
         self.be = backend
+        # KV pressure: a request that would stall (its top-up is refused) ends with ``length`` once it has produced this
+        # many tokens; -1 = off, requests stall and never end early (KV_EARLY_TERMINATION_MIN_OUTPUT_TOKENS)
+        self.early_end_tokens = early_end_tokens
         self.loop_abort = loop_abort          # LoopAbortConfig or None (runtime/repeat_guard.py)
         self.trace = None                     # utils.trace.JsonlTrace: one record per decode round when set
         self.watchdog = None                  # utils.diagnostics.StallWatchdog: beaten every step when set
@@ -429,6 +433,11 @@ class Scheduler:
         for a in batch:
             need = a.kv_len + 1 + self.policy.spec.block + self.policy.spec.copy
             if self.reserve.needs_top_up(a.req.rid, need) and not self.reserve.top_up(a.req.rid):
+                if 0 <= self.early_end_tokens <= len(a.generated):
+                    a.finish_detail = "kv_pressure"        # the operator chose a short reply over a stalled one
+                    self.decoding.remove(a)
+                    self._finish(a, "length")
+                    continue
                 a.stalled = True
                 self.stats.stalls += 1
                 continue

@@ -589,7 +589,8 @@ def build_state(args) -> ServerState:
     sched = Scheduler(be, max_active=args.concurrency, queue_depth=args.queue_depth, queue_wait_s=args.queue_wait,
                       loop_abort=loop if loop.enabled else None,
                       drafter=drafter, eos_ids=tuple(getattr(tok, "eos_ids", ())),
-                      reserve_chunk_tokens=int(getattr(args, "kv_decode_reserve_chunk", 0) or 0))
+                      reserve_chunk_tokens=int(getattr(args, "kv_decode_reserve_chunk", 0) or 0),
+                      early_end_tokens=int(getattr(args, "kv_early_termination_min_output_tokens", -1)))
     prof = getattr(args, "profile", "") or os.environ.get("PROFILE", "")
     if prof:
         from ..utils.profile import Profile, parse_modes

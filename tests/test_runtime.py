@@ -584,3 +584,40 @@ def test_prefix_cache_entry_cap_evicts_the_least_recently_used():
         table.free(s)
     assert len(cache.snapshots) == 2 and set(cache.snapshots) == {kept[2].sid, kept[3].sid}
     assert cache.lookup([0] * 70 + [9]).length == 0 and cache.lookup([3] * 70 + [9]).length == 70
+
+
+def test_kv_pressure_stalls_by_default_and_ends_early_when_told_to():
+    """Two long replies in a pool that holds only one to its end: by default the second stalls until the first has
+    finished and both arrive whole; with an early-termination threshold the stalled one ends with ``length`` /
+    ``kv_pressure`` once it has produced that many tokens."""
+    from cuteafd_b200 import tiny_moe
+    from cuteafd_b200.ref.model import init_weights
+    from cuteafd_b200.runtime.backends import OracleBackend
+    from cuteafd_b200.runtime.scheduler import Request, Scheduler
+    cfg = tiny_moe()
+    params = init_weights(cfg, seed=0)
+
+    def serve(early):
+        sched = Scheduler(OracleBackend(cfg, params, total_pages=9, prefill_chunk=64), max_active=2, reserve_chunk_tokens=64,
+                          early_end_tokens=early)
+        reqs = [Request(prompt=[3 + i] * 60, max_tokens=260, speculation=False) for i in range(2)]
+        for r in reqs:
+            sched.submit(r)
+        done = {}
+        for _ in range(4000):
+            sched.step()
+            for i, r in enumerate(reqs):
+                while not r.events.empty():
+                    ev = r.events.get()
+                    if ev[0] == "done":
+                        done[i] = (ev[1], ev[2]["completion_tokens"], ev[2].get("finish_detail", ""))
+            if len(done) == 2:
+                break
+        return done, sched.stats.stalls
+    whole, stalls = serve(-1)
+    assert {v[1] for v in whole.values()} == {260} and all(v[2] == "" for v in whole.values()) and stalls > 0
+    cut, _ = serve(20)
+    kinds = sorted(v[2] for v in cut.values())
+    assert kinds == ["", "kv_pressure"], cut
+    short = next(v for v in cut.values() if v[2] == "kv_pressure")
+    assert short[0] == "length" and 20 <= short[1] < 260
