@@ -53,7 +53,7 @@ REFERENCE_KEYS = {
 }
 REFERENCE_SKIPPED = ("SPARK_", "COORDINATOR_", "SPARKINFER_", "TP2_", "CUTEAFD_", "MODEL_VARIANT", "MODEL_REVISION", "EXPERT_PORT",
                      "INSTANCE", "KV_MIN_TOKENS", "KV_MAX_TOKENS",
-                     "KV_RESERVE_DRAIN_BUFFER", "DRAFT_LENGTH",
+                     "KV_RESERVE_DRAIN_BUFFER",
                      "RTX_EXPERT_LAYERS", "FULL_PREFILL_LOGITS")
 REFERENCE_SPECULATORS = {"dspark": "auto", "dflash2": "auto"}      # trained block drafters of the reference's checkpoints
 
@@ -109,7 +109,7 @@ CONFIG_KEYS = {"MODEL", "EMBEDDING_PLACEMENT", "GPUS", "ATTENTION_RANKS", "EXPER
                "HTTP_QUEUE_DEPTH", "HTTP_QUEUE_WAIT", "PROFILE", "SPECULATION_TRACE", "KV_FORMAT", "EXPERT_FORMAT",
                "HOST_CACHE_GIB", "LOOP_ABORT_RUN", "LOOP_ABORT_COPIES", "LOOP_FAST_SPAN", "LOOP_FAST_COPIES", "BATCH_INVARIANT",
                "MAX_OUTPUT_TOKENS", "KV_DECODE_RESERVE_CHUNK", "PREFIX_CACHE_ENTRIES", "KV_POOL_SIZE",
-               "KV_EARLY_TERMINATION_MIN_OUTPUT_TOKENS"}
+               "KV_EARLY_TERMINATION_MIN_OUTPUT_TOKENS", "DRAFT_LENGTH"}
 
 
 def graph_reserve_of(value: str) -> tuple[int, str]:
@@ -478,6 +478,7 @@ def _build_parser() -> argparse.ArgumentParser:
     s.add_argument("--api-key", default=os.environ.get("CUTEAFD_API_KEY", ""))
     s.add_argument("--max-context-tokens", type=int, default=16384); s.add_argument("--concurrency", type=int, default=8)
     s.add_argument("--speculator", default="auto"); s.add_argument("--layers", type=int, default=0)
+    s.add_argument("--draft-length", type=int, default=4, help="tokens the history / draft-model drafters propose per round (1..16)")
     s.add_argument("--queue-depth", type=int, default=64); s.add_argument("--queue-wait", type=float, default=30.0)
     s.add_argument("--kv-early-termination-min-output-tokens", type=int, default=-1,
                    help="end a request that would stall for KV with finish_reason length (finish_detail kv_pressure) once it has "

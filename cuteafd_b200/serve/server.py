@@ -474,6 +474,7 @@ def build_state(args) -> ServerState:
     from .tokenizer import load_tokenizer
     from .usage import UsageLog
     snapshot = args.snapshot or None
+    draft_len = max(1, min(int(getattr(args, "draft_length", 4) or 4), 16))      # tokens a drafter proposes per round
     if args.fake_engine or not torch.cuda.is_available():
         from ..ref.model import init_weights
         from ..runtime.backends import OracleBackend
@@ -536,7 +537,7 @@ def build_state(args) -> ServerState:
                            host_cache_bytes=int(float(getattr(args, "host_cache_gib", 0.0)) * (1 << 30)), host_embedding=table)
         if getattr(args, "prewarm", "") == "auto":              # no trace of an earlier run: the derived default list
             from ..planner.capacity import default_prewarm
-            block = 0 if args.speculator == "off" else 4
+            block = 0 if args.speculator == "off" else draft_len
             n = be.prewarm(default_prewarm(args.concurrency, block))
             print(f"prewarmed {n} decode graphs (default list)", flush=True)
         from ..utils.memory_ledger import LEDGER
@@ -559,7 +560,7 @@ def build_state(args) -> ServerState:
                 print(f"prewarmed {n} decode graphs from {pw}", flush=True)
     be.prefix.max_entries = max(0, int(getattr(args, "prefix_cache_entries", 0) or 0))
     tok = load_tokenizer(snapshot, cfg.vocab_size)
-    drafter = NgramDrafter(block=4) if args.speculator in ("auto", "history", "ngram") else None
+    drafter = NgramDrafter(block=draft_len) if args.speculator in ("auto", "history", "ngram") else None
     if args.speculator in ("draft-model", "block-draft"):
         # a small checkpoint of the same vocabulary drafts the block: on the GPU next to the target when there is one
         # (its own engine and paged KV), else on the oracle decoder; "block-draft" produces the whole block in one pass
@@ -571,12 +572,12 @@ def build_state(args) -> ServerState:
         if args.fake_engine or not torch.cuda.is_available():
             from ..loader.load import load_params
             dcfg, dparams = load_params(args.draft_snapshot)
-            make = lambda: ModelDrafter.from_oracle(dcfg, dparams, block=4, parallel=block_mode)      # noqa: E731
+            make = lambda: ModelDrafter.from_oracle(dcfg, dparams, block=draft_len, parallel=block_mode)      # noqa: E731
         else:
             from ..loader.load import load_engine
             pages = (args.max_context_tokens // 64 + 2) * args.concurrency + 64
             dcfg, deng = load_engine(args.draft_snapshot, torch.device("cuda:0"), pages, 2048, 8)
-            make = lambda: ModelDrafter.from_engine(deng, pages, args.max_context_tokens // 64 + 2, block=4, parallel=block_mode)   # noqa: E731
+            make = lambda: ModelDrafter.from_engine(deng, pages, args.max_context_tokens // 64 + 2, block=draft_len, parallel=block_mode)   # noqa: E731
         if dcfg.vocab_size != cfg.vocab_size:
             raise SystemExit(f"draft model vocabulary {dcfg.vocab_size} differs from the target's {cfg.vocab_size}")
         drafter = make()
