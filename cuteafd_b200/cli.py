@@ -50,7 +50,22 @@ REFERENCE_KEYS = {
     "MODEL_ID": ("MODEL", None), "EMBEDDING": ("EMBEDDING_PLACEMENT", None), "RTX_GPUS": ("ATTENTION_RANKS", None),
     "SPARK_COUNT": ("EXPERT_RANKS", None), "KV_TARGET_TOKENS": ("POOL_TOKENS", None), "PREFILL_BATCH_TOKENS": ("PREFILL_ROWS", None),
     "HTTP_QUEUE_WAIT_MS": ("HTTP_QUEUE_WAIT", lambda v: str(float(v) / 1000.0)), "HOST_CACHE_BYTES": ("HOST_CACHE_GIB", _gib),
+    "KV_POOL_TOKENS": ("POOL_TOKENS", None), "SPECULATOR_MODEL_ID": ("DRAFT_SNAPSHOT", None), "GRAPH_PREWARM": ("PREWARM", None),
+    "GPU_GRAPH_RESERVE": ("GRAPH_RESERVE", None),
 }
+# Keys the reference documents (docs/options.md of its tree) that have no counterpart here: family-specific kernel
+# switches, its profiler wrappers, Spark / RDMA / container settings, graph-donor and padding policies.  They are skipped
+# with the notice, so a configuration written for it still starts.
+REFERENCE_ONLY = frozenset("""ATTENTION_PLACEMENT ATTENTION_PLAN_ROWS ATTENTION_PRECISION AUDIO_FEATURES_DIR AUDIO CHAT_TEMPLATE_FROM
+CONSOLE_ASSETS CONSOLE_TEXT CORE_VIEW CUDA_MODULE_LOADING DRAFT_CONTEXT_SLOTS DRAFT_CONTEXT_WINDOW DRAFT_KV_CACHE DRAFT_POLICY
+DRAFT_SEQUENCES ENABLE_BENCH ENGRAM_WARM EXLR8_MANIFEST EXLR8_PREFILL_ACTIVATIONS EXPERT_BACKEND EXPERT_INPUT
+EXPERT_PARTIAL_BF16_MAX_ROWS EXPERT_USAGE FAMILY_RESERVE FP8_PREFILL FP8_SCALES GATEWAY GPU_GRAPH_RESERVE_EXTRA_CAP
+GPU_GRAPH_RESERVE_EXTRA GPU_RESERVE GRAPH_DISABLE_LOW_MEM GRAPH_DONOR_ALWAYS GRAPH_DONOR_COLD_LAG GRAPH_NODE_PADDING GRAPH_TRACE
+HOST_ISA HOST_WAIT IDLE_PARK_SECONDS KV_CACHE L2_PREFETCH MAPPED_SCALE_PRELOAD_GIB MEDIA_CACHE_BYTES MEDIA_FEATURES_DIR
+MEMORY_PADDING PREFILL_PACKING PREFILL_SPAN_ROWS PREFILL_WAVES PREFIX_CACHE_MARK_MIB PREFIX_PARTIAL PREFIX_POINT_BOUNDARIES
+PROBE_DUMP_ROOT RDMA_BOND_BALANCE SPECULATOR_DEPTH SPECULATOR_FP8 SPECULATOR_MODEL_REVISION SWA_KV_CACHE TARGET_HEAD THERMAL
+USAGE VISION_REPLICAS VISION V41_FP8_HEAD QWEN_FP8_DECODE QWEN_FP8_HEAD""".split())
+REFERENCE_ONLY_PREFIXES = ("GLM5_FLASH_", "MIMO_", "PROFILE_N", "PROFILE_SPARK", "PROFILE_EXPERT_", "WIP_")
 REFERENCE_SKIPPED = ("SPARK_", "COORDINATOR_", "SPARKINFER_", "TP2_", "CUTEAFD_", "MODEL_VARIANT", "MODEL_REVISION", "EXPERT_PORT",
                      "INSTANCE", "KV_MIN_TOKENS", "KV_MAX_TOKENS",
                      "KV_RESERVE_DRAIN_BUFFER",
@@ -63,6 +78,12 @@ def reference_key(k: str, v: str, skipped: list[str]) -> list[tuple[str, str]]:
     if k == "ADDR":                                           # host:port of the HTTP listener
         host, _, port = v.rpartition(":")
         return ([("HOST", host)] if host else []) + ([("PORT", port)] if port else [])
+    if k == "API_KEY_FILE":                                   # the bearer key kept out of the configuration file
+        with open(os.path.expanduser(v)) as f:
+            return [("API_KEY", f.read().strip())]
+    if k in REFERENCE_ONLY or k.startswith(REFERENCE_ONLY_PREFIXES):
+        skipped.append(k)
+        return []
     if k == "SPARK_COUNT" or not (k.endswith("_DOCKER_DEV") or k.endswith("_DOCKER_INFERENCE") or k.startswith(REFERENCE_SKIPPED)):
         name, conv = REFERENCE_KEYS.get(k, (k, None))
         if v.lower() == "auto" and name not in ("SPECULATOR",):
@@ -109,7 +130,8 @@ CONFIG_KEYS = {"MODEL", "EMBEDDING_PLACEMENT", "GPUS", "ATTENTION_RANKS", "EXPER
                "HTTP_QUEUE_DEPTH", "HTTP_QUEUE_WAIT", "PROFILE", "SPECULATION_TRACE", "KV_FORMAT", "EXPERT_FORMAT",
                "HOST_CACHE_GIB", "LOOP_ABORT_RUN", "LOOP_ABORT_COPIES", "LOOP_FAST_SPAN", "LOOP_FAST_COPIES", "BATCH_INVARIANT",
                "MAX_OUTPUT_TOKENS", "KV_DECODE_RESERVE_CHUNK", "PREFIX_CACHE_ENTRIES", "KV_POOL_SIZE",
-               "KV_EARLY_TERMINATION_MIN_OUTPUT_TOKENS", "DRAFT_LENGTH"}
+               "KV_EARLY_TERMINATION_MIN_OUTPUT_TOKENS", "DRAFT_LENGTH", "DRAFT_SNAPSHOT", "PREWARM", "GRAPH_RESERVE", "PROFILE_DIR",
+               "SERVED_MODEL_ID", "DECODE_GRAPHS"}
 
 
 def graph_reserve_of(value: str) -> tuple[int, str]:
@@ -478,6 +500,8 @@ def _build_parser() -> argparse.ArgumentParser:
     s.add_argument("--api-key", default=os.environ.get("CUTEAFD_API_KEY", ""))
     s.add_argument("--max-context-tokens", type=int, default=16384); s.add_argument("--concurrency", type=int, default=8)
     s.add_argument("--speculator", default="auto"); s.add_argument("--layers", type=int, default=0)
+    s.add_argument("--served-model-id", default="", help="the model id /v1/models and replies carry (default: the checkpoint's name)")
+    s.add_argument("--decode-graphs", default="on", choices=["on", "off"], help="off: every decode step runs eagerly (no CUDA graph bank)")
     s.add_argument("--draft-length", type=int, default=4, help="tokens the history / draft-model drafters propose per round (1..16)")
     s.add_argument("--queue-depth", type=int, default=64); s.add_argument("--queue-wait", type=float, default=30.0)
     s.add_argument("--kv-early-termination-min-output-tokens", type=int, default=-1,

@@ -534,6 +534,7 @@ def build_state(args) -> ServerState:
                 getattr(eng, "inner", eng).W.embed = None          # the device copy is not needed: free it
                 torch.cuda.empty_cache()
         be = EngineBackend(eng, num_pages, pages_per_seq, prefill_chunk=2048, max_decode_rows=args.concurrency,
+                           use_graphs=getattr(args, "decode_graphs", "on") != "off",
                            host_cache_bytes=int(float(getattr(args, "host_cache_gib", 0.0)) * (1 << 30)), host_embedding=table)
         if getattr(args, "prewarm", "") == "auto":              # no trace of an earlier run: the derived default list
             from ..planner.capacity import default_prewarm
@@ -625,7 +626,7 @@ def build_state(args) -> ServerState:
             audio = audio or AudioTower(AudioTowerConfig(**small), AudioTower.random_weights(AudioTowerConfig(**small)), mdev)
         if vision is not None or audio is not None:
             media = MediaProcessor(cfg.vocab_size, cfg.hidden, vision, audio)
-    return ServerState(sched, tok, cfg.name, args.api_key, usage, media=media,
+    return ServerState(sched, tok, getattr(args, "served_model_id", "") or cfg.name, args.api_key, usage, media=media,
                        extras={"max_output_tokens": int(getattr(args, "max_output_tokens", 0) or 0)})
 
 
