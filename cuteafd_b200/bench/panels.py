@@ -18,6 +18,11 @@ Panels
                the client)
   sweep        aggregate decode tok/s at each concurrency of ``levels`` with a distinct prompt per stream
   sustained    ``concurrency`` streams kept busy for ``seconds``: requests, tokens/s, TTFT p50 / p99, failures
+  context_load cold prompts of growing length (``lengths``, cut at the served context window): TTFT and prefill tok/s
+               at each, every one answered
+  fidelity     teacher-forced scoring of sealed reference windows (``windows`` = file written by ``fidelity seal``)
+               through the probe: KL and top-1 agreement of the served model against the sealed distributions, held
+               against ``kl_bar`` / ``top1_bar``
 
 Every panel returns ``{"panel", "ok", ...numbers}``; the runner attaches the server's thermal window for the time the
 panel ran (``/v1/thermal``) the way every phase of the reference's card carries its throttle summary.
@@ -257,8 +262,73 @@ def sustained(c: Client, o: dict) -> dict:
             "ttft_p99_s": round(tt[min(len(tt) - 1, int(len(tt) * 0.99))], 4) if tt else None, "seconds": round(wall, 2)}
 
 
+def _ids_chat(ids: list[int], max_tokens: int, **probe) -> dict:
+    """A request whose prompt is given as token ids (the probe rides in the body: long prompts do not fit a header)."""
+    return {"messages": [{"role": "user", "content": "."}], "max_tokens": max_tokens, "temperature": 0,
+            "cuteafd_probe": dict({"prompt_ids": ids, "no_speculation": True}, **probe)}
+
+
+def context_load(c: Client, o: dict) -> dict:
+    st, cat = c.get("/v1/codex/models.json")
+    window = int(cat["models"][0].get("context_window", 0)) if st == 200 and isinstance(cat, dict) and cat.get("models") else 0
+    vocab = int(o.get("vocab", 256))
+    rnd = random.Random(11)
+    rows, ok = {}, True
+    for n in o.get("lengths", [1024, 4096, 16384, 65536]):
+        if window and n > window - 16:
+            continue
+        # one generated token, not streamed: the reply arrives when the first token exists, whatever text it decodes to
+        t0 = time.perf_counter()
+        st_r, out = c.post("/v1/chat/completions", _ids_chat([rnd.randrange(1, vocab) for _ in range(n)], 1, cold=True))
+        dt = time.perf_counter() - t0
+        good = st_r == 200 and out.get("usage", {}).get("prompt_tokens") == n
+        ok = ok and good
+        rows[str(n)] = {"ok": good, "ttft_s": round(dt, 4), "prefill_tok_s": round(n / dt, 1) if good and dt > 0 else None,
+                        "error": None if good else str(out.get("error", st_r))[:200]}
+    return {"ok": ok and bool(rows), "context_window": window, "lengths": rows}
+
+
+def fidelity(c: Client, o: dict) -> dict:
+    """KL(sealed || served) and top-1 agreement over the sealed windows, computed from the served model's log-probabilities
+    of every sealed id (``want``) at every position (rust/crates/cuteafd-bench/src/fidelity.rs in the reference; the file
+    format is ``bench/fidelity.py``'s)."""
+    import math
+
+    from .fidelity import load_sealed
+    if not o.get("windows"):
+        return {"ok": False, "error": "fidelity needs the sealed windows file (--windows)"}
+    sealed, info = load_sealed(o["windows"])
+    toks, ids, lps, rest = sealed["tokens"], sealed["top_ids"], sealed["top_logprobs"], sealed["rest_logprob"]
+    W, L = toks.shape
+    kls, agree = [], []
+    for w in range(min(W, int(o.get("fidelity_windows", 8)))):
+        want = {str(p): [int(t) for t in ids[w, p - 1].tolist() if t >= 0] for p in range(1, L)}
+        st, out = c.post("/v1/chat/completions", _ids_chat([int(t) for t in toks[w].tolist()], 1, cold=True, score_from=1, want=want, top_k=1))
+        rows = {r["position"]: r for r in (out.get("probe") or {}).get("score_rows", [])} if st == 200 else {}
+        if len(rows) < L - 1:
+            return {"ok": False, "error": f"window {w}: status {st}, {len(rows)} of {L - 1} scored rows"}
+        for p in range(1, L):
+            q = rows[p]["want"]
+            kl, q_mass = 0.0, 0.0
+            for t, lp in zip(ids[w, p - 1].tolist(), lps[w, p - 1].tolist()):
+                if t < 0:
+                    continue
+                lq = q[str(t)] if str(t) in q else q[t]
+                q_mass += math.exp(lq)
+                kl += math.exp(lp) * (lp - lq)
+            lr = float(rest[w, p - 1])
+            kl += math.exp(lr) * (lr - math.log(max(1.0 - q_mass, 1e-12)))
+            kls.append(max(kl, 0.0))
+            agree.append(1.0 if rows[p]["top_ids"][0] == int(ids[w, p - 1, 0]) else 0.0)
+    kls.sort()
+    kl_mean, top1 = sum(kls) / len(kls), sum(agree) / len(agree)
+    return {"ok": kl_mean <= float(o.get("kl_bar", 0.05)) and top1 >= float(o.get("top1_bar", 0.93)), "windows": min(W, int(o.get("fidelity_windows", 8))),
+            "positions": len(kls), "kl_mean": round(kl_mean, 6), "kl_p99": round(kls[min(len(kls) - 1, int(len(kls) * 0.99))], 6),
+            "top1": round(top1, 4), "reference": info.get("model")}
+
+
 PANELS = {"smoke": smoke, "cache_exact": cache_exact, "lossless": lossless, "template": template, "tools": tools, "speed": speed,
-          "sweep": sweep, "sustained": sustained}
+          "sweep": sweep, "sustained": sustained, "context_load": context_load, "fidelity": fidelity}
 QUICK = ("smoke", "cache_exact", "lossless", "template", "tools")
 
 

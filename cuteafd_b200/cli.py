@@ -288,7 +288,8 @@ def cmd_bench(a: argparse.Namespace) -> int:
         for p in a.panels.split(","):                # "quick" stands for the first five, alone or inside a list
             names += list(panels.QUICK) if p == "quick" else ([p] if p else [])
         opts = {"max_tokens": a.max_tokens, "levels": [int(v) for v in a.levels.split(",") if v], "seconds": a.seconds,
-                "concurrency": a.concurrency}
+                "concurrency": a.concurrency, "windows": a.windows, "kl_bar": a.kl_bar, "top1_bar": a.top1_bar,
+                "fidelity_windows": a.fidelity_windows, "lengths": [int(v) for v in a.lengths.split(",") if v], "vocab": a.vocab}
         out = panels.run(a.url, names, a.bench_api_key, opts)
         res = {"ok": out["ok"], "panels": len(out["panels"])}
         if a.report_root:
@@ -592,7 +593,13 @@ def _build_parser() -> argparse.ArgumentParser:
     b.add_argument("--warmup", type=int, default=8); b.add_argument("--port", type=int, default=29511)
     b.add_argument("--url", default="", help="run panels against this live server over HTTP instead of the in-process card")
     b.add_argument("--panels", default="quick", help="comma-separated: smoke, cache_exact, lossless, template, tools, speed, sweep, "
-                                                       "sustained; quick = the first five")
+                                                       "sustained, context_load, fidelity; quick = the first five")
+    b.add_argument("--windows", default="", help="fidelity panel: sealed reference windows (written by `fidelity seal`)")
+    b.add_argument("--kl-bar", type=float, default=0.05, help="fidelity panel: largest accepted mean KL")
+    b.add_argument("--top1-bar", type=float, default=0.93, help="fidelity panel: smallest accepted top-1 agreement")
+    b.add_argument("--fidelity-windows", type=int, default=8, help="fidelity panel: windows scored (8 = the quick set)")
+    b.add_argument("--lengths", default="1024,4096,16384,65536", help="context_load panel: prompt lengths in tokens")
+    b.add_argument("--vocab", type=int, default=256, help="context_load panel: token ids are drawn below this")
     b.add_argument("--api-key", dest="bench_api_key", default=os.environ.get("CUTEAFD_API_KEY", ""), help="bearer token of the server under test")
     b.add_argument("--max-tokens", type=int, default=64, help="tokens generated per request in the panels")
     b.add_argument("--levels", default="1,4,8", help="concurrency levels of the sweep panel")

@@ -343,6 +343,29 @@ def test_http_panels_on_the_oracle_server(server):
         panels.run(f"http://127.0.0.1:{server.port}", ["nope"], "sekret")
 
 
+def test_context_load_and_fidelity_panels(server, tmp_path):
+    """Sealed windows of the served weights score KL ~ 0 and full top-1 agreement through the probe; windows sealed from
+    other weights miss the bars; prompts of growing length are all answered with their prefill rates."""
+    from cuteafd_b200 import tiny_moe
+    from cuteafd_b200.bench import fidelity as F
+    from cuteafd_b200.bench import panels
+    from cuteafd_b200.ref.model import init_weights
+    cfg = tiny_moe()
+    same, other = str(tmp_path / "same.safetensors"), str(tmp_path / "other.safetensors")
+    wins = F.random_windows(cfg.vocab_size, 2, 24, seed=4)
+    F.seal(F.logits_fn_for(cfg, init_weights(cfg, seed=0)), wins, same, meta={"model": cfg.name})
+    F.seal(F.logits_fn_for(cfg, init_weights(cfg, seed=5)), wins, other, meta={"model": "other"})
+    url = f"http://127.0.0.1:{server.port}"
+    out = panels.run(url, ["fidelity", "context_load"], "sekret", {"windows": same, "lengths": [40, 100, 10 ** 7], "vocab": cfg.vocab_size},
+                     log=lambda *_: None)
+    by = {p["panel"]: p for p in out["panels"]}
+    assert by["fidelity"]["ok"] and by["fidelity"]["kl_mean"] < 1e-4 and by["fidelity"]["top1"] == 1.0 and by["fidelity"]["positions"] == 2 * 23
+    assert by["context_load"]["ok"] and set(by["context_load"]["lengths"]) == {"40", "100"}          # the third exceeds the window
+    assert all(v["prefill_tok_s"] > 0 for v in by["context_load"]["lengths"].values())
+    bad = panels.run(url, ["fidelity"], "sekret", {"windows": other}, log=lambda *_: None)["panels"][0]
+    assert not bad["ok"] and bad["kl_mean"] > by["fidelity"]["kl_mean"]
+
+
 def test_logprobs_and_probe_cold_top_k(server):
     body = {"messages": [{"role": "user", "content": "alpha beta gamma " * 30}], "max_tokens": 5, "temperature": 0,
             "logprobs": True, "top_logprobs": 3}
