@@ -18,6 +18,8 @@ Panels
                the client)
   sweep        aggregate decode tok/s at each concurrency of ``levels`` with a distinct prompt per stream
   sustained    ``concurrency`` streams kept busy for ``seconds``: requests, tokens/s, TTFT p50 / p99, failures
+  agentic      ``sessions`` conversations over one shared system prefix, ``turns`` turns each with the reply fed back:
+               share of prompt tokens served from the prefix cache, emitted tok/s, failures
   context_load cold prompts of growing length (``lengths``, cut at the served context window): TTFT and prefill tok/s
                at each, every one answered
   fidelity     teacher-forced scoring of sealed reference windows (``windows`` = file written by ``fidelity seal``)
@@ -262,6 +264,47 @@ def sustained(c: Client, o: dict) -> dict:
             "ttft_p99_s": round(tt[min(len(tt) - 1, int(len(tt) * 0.99))], 4) if tt else None, "seconds": round(wall, 2)}
 
 
+def agentic(c: Client, o: dict) -> dict:
+    """The shape of an agent workload: a long shared preamble, several sessions, every turn re-sends the conversation so
+    far (rust/crates/cuteafd-bench/src/panels/agentic.rs in the reference).  After a session's first turn almost every
+    prompt token should come from the prefix cache."""
+    sessions, turns, n = int(o.get("sessions", 4)), int(o.get("turns", 4)), int(o.get("max_tokens", 16))
+    system = "You are a careful assistant. " + prompt_of(int(o.get("prefix_words", 400)), 5)
+    lock = threading.Lock()
+    rec = {"prompt": 0, "cached": 0, "later_prompt": 0, "later_cached": 0, "emitted": 0, "failed": 0}
+
+    def session(s: int) -> None:
+        msgs = [{"role": "system", "content": system}]
+        for t in range(turns):
+            msgs.append({"role": "user", "content": f"step {t} of task {s}: " + prompt_of(24, 100 * s + t)})
+            st, out = c.post("/v1/chat/completions", {"messages": msgs, "max_tokens": n, "temperature": 0})
+            with lock:
+                if st != 200:
+                    rec["failed"] += 1
+                    return
+                u = out["usage"]
+                cached = u.get("prompt_tokens_details", {}).get("cached_tokens", 0)
+                rec["prompt"] += u["prompt_tokens"]
+                rec["cached"] += cached
+                rec["emitted"] += u["completion_tokens"]
+                if t:
+                    rec["later_prompt"] += u["prompt_tokens"]
+                    rec["later_cached"] += cached
+            msgs.append({"role": "assistant", "content": out["choices"][0]["message"]["content"] or "."})
+    t0 = time.perf_counter()
+    ts = [threading.Thread(target=session, args=(s,)) for s in range(sessions)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    wall = time.perf_counter() - t0
+    share = rec["cached"] / max(rec["prompt"], 1)
+    later = rec["later_cached"] / max(rec["later_prompt"], 1)
+    return {"ok": rec["failed"] == 0 and rec["emitted"] > 0 and later >= float(o.get("cache_bar", 0.5)), "sessions": sessions, "turns": turns,
+            "prompt_tokens": rec["prompt"], "cache_share": round(share, 4), "cache_share_after_first_turn": round(later, 4),
+            "emitted_tokens": rec["emitted"], "tok_s": round(rec["emitted"] / wall, 2), "failed": rec["failed"], "seconds": round(wall, 2)}
+
+
 def _ids_chat(ids: list[int], max_tokens: int, **probe) -> dict:
     """A request whose prompt is given as token ids (the probe rides in the body: long prompts do not fit a header)."""
     return {"messages": [{"role": "user", "content": "."}], "max_tokens": max_tokens, "temperature": 0,
@@ -328,7 +371,7 @@ def fidelity(c: Client, o: dict) -> dict:
 
 
 PANELS = {"smoke": smoke, "cache_exact": cache_exact, "lossless": lossless, "template": template, "tools": tools, "speed": speed,
-          "sweep": sweep, "sustained": sustained, "context_load": context_load, "fidelity": fidelity}
+          "sweep": sweep, "sustained": sustained, "agentic": agentic, "context_load": context_load, "fidelity": fidelity}
 QUICK = ("smoke", "cache_exact", "lossless", "template", "tools")
 
 

@@ -289,7 +289,8 @@ def cmd_bench(a: argparse.Namespace) -> int:
             names += list(panels.QUICK) if p == "quick" else ([p] if p else [])
         opts = {"max_tokens": a.max_tokens, "levels": [int(v) for v in a.levels.split(",") if v], "seconds": a.seconds,
                 "concurrency": a.concurrency, "windows": a.windows, "kl_bar": a.kl_bar, "top1_bar": a.top1_bar,
-                "fidelity_windows": a.fidelity_windows, "lengths": [int(v) for v in a.lengths.split(",") if v], "vocab": a.vocab}
+                "fidelity_windows": a.fidelity_windows, "lengths": [int(v) for v in a.lengths.split(",") if v], "vocab": a.vocab,
+                "sessions": a.sessions, "turns": a.turns}
         out = panels.run(a.url, names, a.bench_api_key, opts)
         res = {"ok": out["ok"], "panels": len(out["panels"])}
         if a.report_root:
@@ -593,7 +594,9 @@ def _build_parser() -> argparse.ArgumentParser:
     b.add_argument("--warmup", type=int, default=8); b.add_argument("--port", type=int, default=29511)
     b.add_argument("--url", default="", help="run panels against this live server over HTTP instead of the in-process card")
     b.add_argument("--panels", default="quick", help="comma-separated: smoke, cache_exact, lossless, template, tools, speed, sweep, "
-                                                       "sustained, context_load, fidelity; quick = the first five")
+                                                       "sustained, agentic, context_load, fidelity; quick = the first five")
+    b.add_argument("--sessions", type=int, default=4, help="agentic panel: conversations run side by side")
+    b.add_argument("--turns", type=int, default=4, help="agentic panel: turns per conversation")
     b.add_argument("--windows", default="", help="fidelity panel: sealed reference windows (written by `fidelity seal`)")
     b.add_argument("--kl-bar", type=float, default=0.05, help="fidelity panel: largest accepted mean KL")
     b.add_argument("--top1-bar", type=float, default=0.93, help="fidelity panel: smallest accepted top-1 agreement")

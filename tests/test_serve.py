@@ -364,6 +364,8 @@ def test_context_load_and_fidelity_panels(server, tmp_path):
     assert all(v["prefill_tok_s"] > 0 for v in by["context_load"]["lengths"].values())
     bad = panels.run(url, ["fidelity"], "sekret", {"windows": other}, log=lambda *_: None)["panels"][0]
     assert not bad["ok"] and bad["kl_mean"] > by["fidelity"]["kl_mean"]
+    ag = panels.run(url, ["agentic"], "sekret", {"sessions": 2, "turns": 3, "max_tokens": 4, "prefix_words": 60}, log=lambda *_: None)["panels"][0]
+    assert ag["ok"] and ag["failed"] == 0 and ag["emitted_tokens"] == 2 * 3 * 4 and ag["cache_share_after_first_turn"] > 0.5
 
 
 def test_logprobs_and_probe_cold_top_k(server):
