@@ -235,6 +235,9 @@ class Scheduler:
         keep = []
         for r in self.pending:
             if r.cancelled.is_set():
+                # cancelled before it was admitted: it still ends, like a request cancelled in flight, with what it cost
+                r.events.put(("done", "cancelled", {"prompt_tokens": len(r.prompt), "completion_tokens": 0, "cached_tokens": 0,
+                                                    "speculation": {"proposed": 0, "accepted": 0, "cycles": 0, "request_id": r.rid}}, []))
                 continue
             if now - r.arrival > self.queue_wait_s:
                 r.events.put(("error", FAIL_RETRY, "queue wait exceeded"))
