@@ -1,6 +1,6 @@
 """The scheduler under generated request mixes on the oracle backend: whatever arrives in whatever order, with
 speculation on or off, repeated prompts, cancels and a pool that is sometimes too small for everybody at once,
-every request ends exactly once, greedy replies equal what the same prompt gives alone, and when the last request is
+every request ends exactly once, greedy and seeded-sampling replies equal what the same prompt gives alone, and when the last request is
 gone no page is left behind (free pages + pages the prefix cache holds = the pool).  The reference qualifies its
 prefix cache with a multi-turn torture and leak accounting (scripts/qualify/qualify-prefix-cache.py)."""
 import torch
@@ -10,6 +10,7 @@ from hypothesis import strategies as st
 from cuteafd_b200 import tiny_moe
 from cuteafd_b200.ref.model import init_weights
 from cuteafd_b200.runtime.backends import OracleBackend
+from cuteafd_b200.runtime.sampling import SamplingParams
 from cuteafd_b200.runtime.scheduler import Request, Scheduler
 from cuteafd_b200.runtime.speculation import NgramDrafter
 
@@ -19,12 +20,12 @@ STEMS = [[5, 6, 7, 8] * 20, [9] * 70 + [3, 4] * 10, [11, 12, 13] * 9]
 _ALONE: dict = {}
 
 
-def _alone(prompt: tuple, n: int) -> list[int]:
+def _alone(prompt: tuple, n: int, params: SamplingParams) -> list[int]:
     """The reply the prompt gets on an empty server without drafts."""
-    key = (prompt, n)
+    key = (prompt, n, params)
     if key not in _ALONE:
         s = Scheduler(OracleBackend(CFG, PARAMS, total_pages=64, prefill_chunk=64), max_active=1)
-        r = s.submit(Request(prompt=list(prompt), max_tokens=n, speculation=False, cold=True))
+        r = s.submit(Request(prompt=list(prompt), max_tokens=n, speculation=False, cold=True, params=params))
         out = []
         for _ in range(2000):
             s.step()
@@ -39,7 +40,7 @@ def _alone(prompt: tuple, n: int) -> list[int]:
     return _ALONE[key]
 
 
-REQ = st.tuples(st.integers(0, 2), st.integers(0, 30), st.integers(1, 9), st.booleans(), st.integers(0, 40))
+REQ = st.tuples(st.integers(0, 2), st.integers(0, 30), st.integers(1, 9), st.booleans(), st.integers(0, 40), st.booleans())
 
 
 @settings(max_examples=12, deadline=None)
@@ -48,9 +49,11 @@ def test_every_request_ends_once_with_the_reply_it_gets_alone_and_no_page_leaks(
     be = OracleBackend(CFG, PARAMS, total_pages=pages, prefill_chunk=64, max_decode_rows=4)
     sched = Scheduler(be, max_active=active, queue_depth=32, drafter=NgramDrafter(block=3), reserve_chunk_tokens=64)
     live = []
-    for stem, tail, n, spec, arrive in reqs:
+    for stem, tail, n, spec, arrive, sample in reqs:
         prompt = STEMS[stem] + [20 + tail % 7] * (tail % 12)
-        live.append([Request(prompt=prompt, max_tokens=n, speculation=spec), arrive, [], None, False])
+        # a sampled request draws from (seed, position) alone: batching, drafts and cache hits may not move a token
+        params = SamplingParams(temperature=0.9, top_k=5, seed=7 * stem + tail) if sample else SamplingParams()
+        live.append([Request(prompt=prompt, max_tokens=n, speculation=spec, params=params), arrive, [], None, False])
     doomed = cancel % (len(live) + 1)                       # one request may be cancelled mid-flight (index len = nobody)
     submitted = 0
     for tick in range(6000):
@@ -82,7 +85,7 @@ def test_every_request_ends_once_with_the_reply_it_gets_alone_and_no_page_leaks(
         if end[1] == "cancelled":
             assert i == doomed
             continue
-        assert end[1] in ("length", "stop") and toks == _alone(tuple(req.prompt), req.max_tokens)[:len(toks)] and len(toks) == end[2]["completion_tokens"]
+        assert end[1] in ("length", "stop") and toks == _alone(tuple(req.prompt), req.max_tokens, req.params)[:len(toks)] and len(toks) == end[2]["completion_tokens"]
     # nothing is left behind: what is not free is held by the prefix cache's snapshots (a partial tail page that a
     # prompt snapshot and a turn snapshot both keep is one page)
     sched.step()
