@@ -44,9 +44,11 @@ REQ = st.tuples(st.integers(0, 2), st.integers(0, 30), st.integers(1, 9), st.boo
 
 
 @settings(max_examples=12, deadline=None)
-@given(reqs=st.lists(REQ, min_size=1, max_size=7), pages=st.sampled_from([12, 20, 64]), active=st.integers(1, 4), cancel=st.integers(0, 10 ** 6))
-def test_every_request_ends_once_with_the_reply_it_gets_alone_and_no_page_leaks(reqs, pages, active, cancel):
-    be = OracleBackend(CFG, PARAMS, total_pages=pages, prefill_chunk=64, max_decode_rows=4)
+@given(reqs=st.lists(REQ, min_size=1, max_size=7), pages=st.sampled_from([12, 20, 64]), active=st.integers(1, 4), cancel=st.integers(0, 10 ** 6),
+       host_slots=st.sampled_from([0, 0, 16]))
+def test_every_request_ends_once_with_the_reply_it_gets_alone_and_no_page_leaks(reqs, pages, active, cancel, host_slots):
+    # (host_slots: a pinned tier behind the device cache, on a virtual clock: evicted snapshots spill and come back)
+    be = OracleBackend(CFG, PARAMS, total_pages=pages, prefill_chunk=64, max_decode_rows=4, host_slots=host_slots)
     sched = Scheduler(be, max_active=active, queue_depth=32, drafter=NgramDrafter(block=3), reserve_chunk_tokens=64)
     live = []
     for stem, tail, n, spec, arrive, sample in reqs:
