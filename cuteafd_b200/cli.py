@@ -248,6 +248,18 @@ def cmd_expertd(a: argparse.Namespace) -> int:
 
 
 def cmd_golden(a: argparse.Namespace) -> int:
+    if getattr(a, "layer_major", ""):
+        import torch
+
+        from .loader.load import open_snapshot
+        from .ref import layer_major as LM
+        if not a.snapshot:
+            print("golden --layer-major reads a checkpoint: give --snapshot", file=sys.stderr)
+            return 2
+        vocab = open_snapshot(a.snapshot).cfg.vocab_size
+        toks = torch.randint(0, vocab, (a.windows, a.tokens), generator=torch.Generator().manual_seed(1))
+        print(json.dumps(LM.run(a.snapshot, toks, a.layer_major, log=lambda m: print(f"[golden] {m}", file=sys.stderr, flush=True))))
+        return 0
     from .bench.golden import run_golden
     return run_golden(a)
 
@@ -587,6 +599,9 @@ def _build_parser() -> argparse.ArgumentParser:
     g = sub.add_parser("golden", help="layer-by-layer comparison of the engine against the CPU oracle")
     g.add_argument("--snapshot", default=""); g.add_argument("--preset", default="tiny-moe"); g.add_argument("--tokens", type=int, default=64)
     g.add_argument("--out", default="")
+    g.add_argument("--layer-major", default="", metavar="DIR", help="write the oracle's reference dumps of --snapshot into DIR (tokens.bin, "
+                   "layerNN.bin, logits.bin) one layer's weights at a time; a run that was interrupted continues after the last finished layer")
+    g.add_argument("--windows", type=int, default=4, help="with --layer-major: independent windows of --tokens tokens each")
     g.set_defaults(fn=cmd_golden)
 
     b = sub.add_parser("bench", help="run the headline benchmark card")
