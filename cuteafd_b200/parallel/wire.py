@@ -49,6 +49,7 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
+from ..utils.fault import InjectedFault
 from .health import HealthError, HealthLatch
 
 MAGIC = b"CAFDWIRE"
@@ -314,12 +315,16 @@ class ExpertLink:
             raise HealthError(f"exchange unavailable: {self.latch.reason}") from e
         self.call(Request(HELLO, plan=plan))
 
+    faults = None            # utils.fault.FaultHooks: a WIRE_SEND fault fails the link before the request leaves
+
     def call(self, req: Request) -> Response:
         with self.lock:
             self.latch.require()                                    # refuses after the first failure, with its reason
             self.seq += 1
             req.seq = self.seq
             try:
+                if self.faults is not None:
+                    self.faults.hit("WIRE_SEND")
                 self.sock.sendall(req.pack())
                 rsp, nbytes, crc = parse_response_header(recv_exact(self.sock, HEADER))
                 rsp.payload = recv_exact(self.sock, nbytes) if nbytes else b""
@@ -329,7 +334,7 @@ class ExpertLink:
                     raise WireError(f"reply {rsp.seq} does not answer request {req.seq}")
                 if rsp.status != OK:
                     raise WireError(f"worker refused: {STATUS_NAMES[rsp.status] if rsp.status < len(STATUS_NAMES) else rsp.status}")
-            except (OSError, WireError, struct.error) as e:
+            except (OSError, WireError, struct.error, InjectedFault) as e:
                 self.latch.trip(f"expert link: {e}")
                 self.close()
                 raise HealthError(f"exchange unavailable: {self.latch.reason}") from e

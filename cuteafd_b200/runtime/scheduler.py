@@ -33,7 +33,10 @@ FAIL_BAD_REQUEST, FAIL_UNAVAILABLE, FAIL_RETRY, FAIL_WORKER = "bad_request", "un
 
 def _device_failure(e: Exception) -> bool:
     """False for failures raised on the host before a kernel of the step was launched."""
+    from ..utils.fault import InjectedFault
     from .paged import OutOfPages
+    if isinstance(e, InjectedFault):
+        return e.device
     return not isinstance(e, (OutOfPages, ValueError, KeyError, AssertionError))
 
 
@@ -125,6 +128,8 @@ class Scheduler:
                  eos_ids: tuple[int, ...] = (), decode_lanes: int = 1, loop_abort=None, reserve_chunk_tokens: int = 0,
                  early_end_tokens: int = -1):
         self.be = backend
+        from ..utils.fault import NONE
+        self.faults = NONE                    # utils.fault.FaultHooks when development fault injection is configured
         # KV pressure: a request that would stall (its top-up is refused) ends with ``length`` once it has produced this
         # many tokens; -1 = off, requests stall and never end early (KV_EARLY_TERMINATION_MIN_OUTPUT_TOKENS)
         self.early_end_tokens = early_end_tokens
@@ -355,7 +360,9 @@ class Scheduler:
             return self._prefill_one()
         items = [(a.handle, a.req.prompt[a.prompt_done:a.prompt_done + n], a.prompt_done + n == len(a.req.prompt)) for a, n in group]
         try:
+            self.faults.hit("BEFORE_PREFILL")
             outs = self.be.prefill_packed(items)
+            self.faults.hit("AFTER_SUBMISSION")
         except Exception as e:
             for a, _ in group:
                 self.prefilling.remove(a)
@@ -391,7 +398,9 @@ class Scheduler:
         chunk = a.req.prompt[a.prompt_done:a.prompt_done + n]
         last = a.prompt_done + n == len(a.req.prompt)
         try:
+            self.faults.hit("BEFORE_PREFILL")
             logits = self.be.prefill(a.handle, chunk, last)
+            self.faults.hit("AFTER_SUBMISSION")
         except Exception as e:
             self.prefilling.pop(0)
             self._fail([a], f"prefill failed: {e}", device=_device_failure(e))
@@ -476,6 +485,7 @@ class Scheduler:
         picked: list[int] | None = None
         picked_status: list[int] = []
         try:
+            self.faults.hit("BEFORE_DECODE")
             if on_device:
                 flat_params = [a.req.params for a, r in zip(runnable, rows) for _ in r]
                 flat_pos = [len(a.req.prompt) + len(a.generated) + j for a, r in zip(runnable, rows) for j in range(len(r))]
@@ -483,6 +493,7 @@ class Scheduler:
                 logits = None
             else:
                 logits = self.be.verify([a.handle for a in runnable], rows)
+            self.faults.hit("AFTER_SUBMISSION")
         except Exception as e:
             self.decoding = [a for a in self.decoding if a not in runnable]
             self._fail(runnable, f"decode step failed: {e}", device=_device_failure(e))

@@ -593,6 +593,12 @@ def build_state(args) -> ServerState:
                       drafter=drafter, eos_ids=tuple(getattr(tok, "eos_ids", ())),
                       reserve_chunk_tokens=int(getattr(args, "kv_decode_reserve_chunk", 0) or 0),
                       early_end_tokens=int(getattr(args, "kv_early_termination_min_output_tokens", -1)))
+    from ..utils.fault import FaultHooks
+    hooks = FaultHooks()                      # refuses a configured fault without CUTEAFD_DEV_FAULT_HOOKS=1
+    if hooks.plan:
+        sched.faults = hooks
+        hooks.arm()                           # the engine is built and prewarmed: visits count from here
+        print(f"[serve] development fault hooks armed: {hooks.plan}", flush=True)
     prof = getattr(args, "profile", "") or os.environ.get("PROFILE", "")
     if prof:
         from ..utils.profile import Profile, parse_modes

@@ -157,3 +157,19 @@ def test_expertd_tcp_worker_process(tmp_path):
         for p in procs:
             p.kill()
             p.wait(timeout=10)
+
+
+def test_injected_wire_fault_trips_the_latch_before_anything_is_sent(split):
+    """The development fault site on the link: the request never leaves, the latch holds the reason, the worker saw
+    nothing of the failed call."""
+    from cuteafd_b200.utils.fault import ENABLE, PREFIX, FaultHooks
+    cfg, params, plan, servers, half = split
+    link = wire.ExpertLink("127.0.0.1", servers[0].port, plan)
+    link.faults = FaultHooks(env={ENABLE: "1", PREFIX + "WIRE_SEND": "2"})
+    link.faults.arm()
+    assert link.call(wire.Request(wire.PING)).status == wire.OK
+    with pytest.raises(HealthError, match="injected fault at WIRE_SEND"):
+        link.call(wire.Request(wire.PING))
+    assert not link.latch.ok and link.sock is None
+    with pytest.raises(HealthError, match="injected fault"):           # terminal, like any other link failure
+        link.call(wire.Request(wire.PING))
