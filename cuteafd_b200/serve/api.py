@@ -187,6 +187,14 @@ def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, f
     that names no limit gets; 0 leaves the limit to the context and gives such a request 256 tokens."""
     # a probe too large for a header (a long synthetic prompt) may ride in the body instead
     probe = {**(body.get("cuteafd_probe") or {}), **(probe or {})}
+    tools = normalize_tools(body.get("tools"), flavor)
+    try:
+        choice = constraints.tool_choice_of(body, flavor)
+        tool_fmt = constraints.tool_call_format(tools, *choice)
+    except ValueError as e:
+        raise BadRequest(str(e)) from e
+    if choice[0] == "none":
+        tools = None                                       # the model is not shown tools it may not call
     if probe.get("prompt_ids"):
         prompt, spans = [int(t) for t in probe["prompt_ids"]], None
     else:
@@ -202,7 +210,7 @@ def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, f
         if not msgs:
             raise BadRequest("messages must not be empty")
         items: list = []
-        text = render_chat(msgs, True, normalize_tools(body.get("tools"), flavor), media=items)
+        text = render_chat(msgs, True, tools, media=items)
         if items:
             # image / audio parts: tower rows replace placeholder ids (``media`` is the deployment's MediaProcessor)
             from ..media.image import MediaError, bytes_from_url
@@ -229,7 +237,9 @@ def build_request(body: dict, tok, vocab_size: int, probe: dict | None = None, f
             fmt = {"type": "choice", "choices": body["guided_choice"]}
         elif "guided_json" in body:
             fmt = {"type": "json_schema", "schema": body["guided_json"]}
-    try:
+    if tool_fmt is not None and (fmt is None or tool_fmt["at_least_one"]):
+        fmt = tool_fmt                                     # a forced call is the whole reply; strict tools under auto
+    try:                                                   # yield to an explicit response_format
         cons = constraints.from_response_format(fmt, tok, vocab_size)
     except ValueError as e:
         raise BadRequest(str(e)) from e

@@ -245,7 +245,75 @@ def from_response_format(fmt: dict | None, tokenizer, vocab_size: int) -> TokenC
         return TokenConstraint(RegexRecognizer(str(fmt.get("pattern") or fmt.get("regex") or "")), tokenizer, vocab_size)
     if t == "structural_tag":
         from .regex import StructuralTagRecognizer
-        return TokenConstraint(StructuralTagRecognizer(list(fmt.get("structures") or fmt.get("tags") or [])), tokenizer, vocab_size)
+        return TokenConstraint(StructuralTagRecognizer(list(fmt.get("structures") or fmt.get("tags") or []),
+                                                       at_least_one=bool(fmt.get("at_least_one")),
+                                                       stop_after_first=bool(fmt.get("stop_after_first"))), tokenizer, vocab_size)
     if t in (None, "text"):
         return None
     raise ValueError(f"unsupported response_format type {t!r}")
+
+
+TOOL_BEGIN, TOOL_END = "<tool_call>", "</tool_call>"
+
+
+def tool_choice_of(body: dict, flavor: str = "openai") -> tuple[str, str | None, bool]:
+    """A request's tool choice in any of the three protocols -> ``(mode, tool name, parallel calls allowed)`` with mode
+    one of ``none | auto | required | named``.  OpenAI chat: ``"none" | "auto" | "required"`` or
+    ``{"type": "function", "function": {"name": N}}`` plus ``parallel_tool_calls``; Responses: the same strings or
+    ``{"type": "function", "name": N}``; Anthropic: ``{"type": "auto" | "any" | "tool" | "none", "name": N,
+    "disable_parallel_tool_use": bool}``."""
+    tc = body.get("tool_choice")
+    parallel = body.get("parallel_tool_calls", True) is not False
+    if tc is None:
+        return "auto", None, parallel
+    if isinstance(tc, str):
+        mode = {"any": "required"}.get(tc, tc)
+        if mode not in ("none", "auto", "required"):
+            raise ValueError(f"tool_choice {tc!r} is not one of none, auto, required")
+        return mode, None, parallel
+    if not isinstance(tc, dict):
+        raise ValueError("tool_choice must be a string or an object")
+    if tc.get("disable_parallel_tool_use"):
+        parallel = False
+    t = tc.get("type")
+    if t in ("function", "tool"):
+        name = (tc.get("function") or {}).get("name") if isinstance(tc.get("function"), dict) else tc.get("name")
+        if not isinstance(name, str) or not name:
+            raise ValueError("tool_choice names no function")
+        return "named", name, parallel
+    if t in ("auto", "none"):
+        return t, None, parallel
+    if t in ("any", "required"):
+        return "required", None, parallel
+    raise ValueError(f"tool_choice type {t!r} is not supported")
+
+
+def tool_call_format(tools: list[dict] | None, mode: str, name: str | None, parallel: bool) -> dict | None:
+    """The ``structural_tag`` format that holds a reply to the request's tool choice, or None when nothing has to be
+    constrained.  ``tools`` are OpenAI function tools.  A call is ``<tool_call>{"name": N, "arguments": {...}}</tool_call>``
+    (the template's inline form); the arguments of a ``strict`` tool follow its ``parameters`` schema, those of other
+    tools are any JSON object.  ``required`` / ``named``: the reply opens with a call; ``auto``: free text, constrained
+    only inside a call and only when some tool is strict.  Without ``parallel`` the reply ends after its first call.
+
+    Counterpart: rust/crates/cuteafd-daemon/src/shared/constraints.rs:290-330,590-620 (tool_choice required / auto with
+    strict parameters compiled to a structural tag; invalid arguments refused token by token)."""
+    fns = [t.get("function", t) for t in tools or [] if isinstance(t, dict)]
+    if mode == "none":
+        return None
+    if mode in ("required", "named") and not fns:
+        raise ValueError(f"tool_choice {mode} needs tools")
+    if mode == "named":
+        fns = [f for f in fns if f.get("name") == name]
+        if not fns:
+            raise ValueError(f"tool_choice names {name!r}, which is not among the tools")
+    if mode == "auto" and not any(f.get("strict") for f in fns):
+        return None
+    calls = []
+    for f in fns:
+        params = f.get("parameters") if f.get("strict") and isinstance(f.get("parameters"), dict) else {"type": "object"}
+        calls.append({"type": "object", "properties": {"name": {"const": f.get("name", "")}, "arguments": params},
+                      "required": ["name", "arguments"], "additionalProperties": False})
+    schema = calls[0] if len(calls) == 1 else {"anyOf": calls}
+    return {"type": "structural_tag", "structures": [{"begin": TOOL_BEGIN, "schema": schema, "end": TOOL_END}],
+            "at_least_one": mode in ("required", "named"), "stop_after_first": not parallel}
+

@@ -37,6 +37,12 @@ def to_chat_body(body: dict, flavor: str, model_map: dict[str, str]) -> dict:
     tools = api.normalize_tools(body.get("tools"), flavor)          # hosted tool types are handled by the gateway itself
     if tools:
         out["tools"] = tools
+        from .constraints import tool_choice_of
+        mode, name, parallel = tool_choice_of(body, flavor)        # any protocol's spelling -> the chat one
+        if mode != "auto":
+            out["tool_choice"] = {"type": "function", "function": {"name": name}} if mode == "named" else mode
+        if not parallel:
+            out["parallel_tool_calls"] = False
     for k in ("temperature", "top_p", "top_k", "seed", "stop"):
         if k in body:
             out[k] = body[k]

@@ -267,9 +267,12 @@ class RegexRecognizer:
 
 
 class StructuralTagRecognizer:
-    """Free text; after a ``begin`` string, schema-constrained JSON, then the ``end`` string."""
+    """Free text; after a ``begin`` string, schema-constrained JSON, then the ``end`` string.
 
-    def __init__(self, tags: list[dict]):
+    ``at_least_one``: the reply opens with a tag (no free text before the first one) and is not complete until one
+    block has closed.  ``stop_after_first``: nothing follows the first block; the reply ends there."""
+
+    def __init__(self, tags: list[dict], at_least_one: bool = False, stop_after_first: bool = False):
         from .schema import compile_schema
         if not tags:
             raise ValueError("structural_tag needs at least one tag")
@@ -286,6 +289,7 @@ class StructuralTagRecognizer:
         self.end = b""
         self.end_at = 0
         self.blocks = 0
+        self.at_least_one, self.stop_after_first = bool(at_least_one), bool(stop_after_first)
 
     def clone(self) -> "StructuralTagRecognizer":
         c = copy.copy(self)
@@ -295,6 +299,10 @@ class StructuralTagRecognizer:
     def feed(self, b: int) -> bool:
         from .schema import DONE, MORE, PASS
         if self.mode == "free":
+            if self.stop_after_first and self.blocks:
+                return False
+            if self.at_least_one and not self.blocks and not any(t[0].startswith(self.tail + bytes([b])) for t in self.tags):
+                return False                  # the first tag opens the reply
             self.tail = (self.tail + bytes([b]))[-self.keep:]
             for begin, make, end in self.tags:
                 if self.tail.endswith(begin):
@@ -327,6 +335,9 @@ class StructuralTagRecognizer:
             self.mode, self.blocks = "free", self.blocks + 1
 
     def complete(self) -> bool:
-        return self.mode == "free"
+        return self.mode == "free" and (self.blocks > 0 or not self.at_least_one)
 
-    done = False                              # free text may always continue: the reply ends with end-of-sequence
+    @property
+    def done(self) -> bool:
+        """Free text may always continue (the reply ends with end-of-sequence) unless the first block ends it."""
+        return self.stop_after_first and self.blocks > 0 and self.mode == "free"
