@@ -148,11 +148,33 @@ def graph_reserve_of(value: str) -> tuple[int, str]:
 
 def cmd_plan(a: argparse.Namespace) -> int:
     from .planner import plan as P
+    if a.file_layout:
+        # host layout: every host's shares (attention, experts:lo:hi, a role name) as one slice per host
+        from .loader import slice as SL
+        try:
+            hosts = SL.read_layout(a.file_layout)
+            if a.host:
+                if a.host not in hosts:
+                    raise ValueError(f"host {a.host!r} is not in the layout ({', '.join(sorted(hosts))})")
+                hosts = {a.host: hosts[a.host]}
+            out = {}
+            for host, sels in hosts.items():
+                if a.fetch and not a.dry_run:
+                    dst = a.fetch if a.host else os.path.join(a.fetch, host)
+                    out[host] = SL.slice_snapshot(a.model, dst, selectors=sels, force=a.force)
+                else:
+                    out[host] = SL.inventory(a.model, sels)
+        except (ValueError, OSError) as e:
+            print(f"plan: {e}", file=sys.stderr)
+            return 2
+        print(json.dumps(out, indent=1))
+        return 0
     if a.fetch:
-        from .loader.slice import slice_snapshot
+        from .loader import slice as SL
         er = tuple(int(v) for v in a.expert_range.split(":")) if a.expert_range else None
-        info = slice_snapshot(a.model, a.fetch, roles={r for r in a.role.split(",") if r} or None,
-                              exclude={r for r in a.exclude_role.split(",") if r} or None, expert_range=er)
+        sel = dict(roles={r for r in a.role.split(",") if r} or None, exclude={r for r in a.exclude_role.split(",") if r} or None,
+                   expert_range=er)
+        info = SL.inventory(a.model, [sel]) if a.dry_run else SL.slice_snapshot(a.model, a.fetch, force=a.force, **sel)
         print(json.dumps(info, indent=1))
         return 0
     kw = dict(gpus=a.gpus, attention_ranks=a.attention_ranks, expert_ranks=a.expert_ranks, pool_tokens_target=a.pool_tokens,
@@ -501,6 +523,11 @@ def _build_parser() -> argparse.ArgumentParser:
     p.add_argument("--pool-tokens", type=int, default=None); p.add_argument("--gpu-memory-cap", default="")
     p.add_argument("--kv-pool-size", default="", help="KV pool target as a size per attention GPU (22.5GB, 90GiB) instead of --pool-tokens")
     p.add_argument("--max-context-tokens", type=int, default=None); p.add_argument("--concurrency", type=int, default=None)
+    p.add_argument("--file-layout", default="", help='JSON host-to-shares map, e.g. {"boxA": ["attention", "experts:0:64"]}: lists '
+                                                     "(or with --fetch copies) what each host has to hold")
+    p.add_argument("--host", default="", help="with --file-layout: this host only (--fetch then writes straight into its directory)")
+    p.add_argument("--dry-run", action="store_true", help="with --fetch: print tensors, bytes and source files, copy nothing")
+    p.add_argument("--force", action="store_true", help="with --fetch: rewrite a destination that already holds this selection")
     p.add_argument("--speculator", default=None, choices=["auto", "off", "mtp"]); p.add_argument("--decode-lanes", type=int, default=None, choices=[1, 2])
     p.add_argument("--format", default=None); p.add_argument("--expert-format", default=None); p.add_argument("--kv-format", default=None)
     p.add_argument("--graph-reserve", default="", help="decode-graph arena per attention GPU: a prewarm file saved by a serving run "

@@ -298,3 +298,44 @@ def test_sliding_window_fields_map_per_layer():
     assert from_hf_config(to_hf_config(c)).window_layers == (1, 0, 1, 0)
     with pytest.raises(ValueError):
         from_hf_config(dict(base, model_type="llama", layer_types=["chunked_attention"] * 4))
+
+
+def test_host_layout_lists_and_copies_each_hosts_share(tmp_path, capsys):
+    """A host that runs an attention rank and an expert rank holds the union once; a dry run copies nothing; a second
+    fetch of the same selection is skipped; the experts of two hosts partition the routed experts."""
+    import json as _json
+    from cuteafd_b200 import tiny_moe
+    from cuteafd_b200.cli import main
+    from cuteafd_b200.loader.safetensors_io import Catalog
+    from cuteafd_b200.loader import slice as SL
+    cfg = tiny_moe()
+    src = snapshot.write_random_snapshot(cfg, str(tmp_path / "src"), fmt="bf16", seed=4)
+    half = cfg.num_experts // 2
+    lay = tmp_path / "layout.json"
+    lay.write_text(_json.dumps({"front": ["attention", f"experts:0:{half}"], "back": [f"experts:{half}:{cfg.num_experts}"]}))
+    assert main(["plan", src, "--file-layout", str(lay), "--files"]) == 0
+    listed = _json.loads(capsys.readouterr().out)
+    full = Catalog(src)
+    assert set(listed) == {"front", "back"} and listed["front"]["bytes"] + listed["back"]["bytes"] == full.total_bytes()
+    assert main(["plan", src, "--file-layout", str(lay), "--fetch", str(tmp_path / "dry"), "--dry-run"]) == 0
+    assert _json.loads(capsys.readouterr().out) == listed and not (tmp_path / "dry").exists()
+    assert main(["plan", src, "--file-layout", str(lay), "--fetch", str(tmp_path / "out")]) == 0
+    capsys.readouterr()
+    front, back = Catalog(str(tmp_path / "out" / "front")), Catalog(str(tmp_path / "out" / "back"))
+    assert set(front.names()) | set(back.names()) == set(full.names()) and not set(front.names()) & set(back.names())
+    assert all(".mlp.experts." in n for n in back.names()) and "model.embed_tokens.weight" in front
+    for n in list(back.names())[:3] + list(front.names())[:3]:
+        assert torch.equal((back if n in back else front).read(n).view(torch.uint8), full.read(n).view(torch.uint8))
+    assert main(["plan", src, "--file-layout", str(lay), "--host", "back", "--fetch", str(tmp_path / "out" / "back")]) == 0
+    assert _json.loads(capsys.readouterr().out)["back"]["skipped"] is True             # same selection already there
+    assert main(["plan", src, "--file-layout", str(lay), "--host", "back", "--fetch", str(tmp_path / "out" / "back"), "--force"]) == 0
+    assert "skipped" not in _json.loads(capsys.readouterr().out)["back"]
+    assert main(["plan", src, "--file-layout", str(lay), "--host", "nowhere", "--files"]) == 2
+    for bad in ({}, {"h": []}, {"h": "attention"}):
+        lay.write_text(_json.dumps(bad))
+        with pytest.raises(ValueError, match="host layout"):
+            SL.read_layout(str(lay))
+    with pytest.raises(ValueError, match="first:end"):
+        SL.parse_share("experts:3")
+    with pytest.raises(ValueError, match="empty expert range"):
+        SL.parse_share("experts:5:5")
