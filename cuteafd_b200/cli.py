@@ -73,6 +73,11 @@ REFERENCE_SKIPPED = ("SPARK_", "COORDINATOR_", "SPARKINFER_", "TP2_", "CUTEAFD_"
 REFERENCE_SPECULATORS = {"dspark": "auto", "dflash2": "auto"}      # trained block drafters of the reference's checkpoints
 
 
+def _speculator(v: str) -> str:
+    """``--speculator`` of plan / launch: the reference's trained block drafters (dspark, dflash2) plan as ``auto``."""
+    return REFERENCE_SPECULATORS.get(v.lower(), v)
+
+
 def reference_key(k: str, v: str, skipped: list[str]) -> list[tuple[str, str]]:
     """One line of a reference configuration -> the (key, value) pairs it means here ([] = nothing to set)."""
     if k == "ADDR":                                           # host:port of the HTTP listener
@@ -528,7 +533,7 @@ def _build_parser() -> argparse.ArgumentParser:
     p.add_argument("--host", default="", help="with --file-layout: this host only (--fetch then writes straight into its directory)")
     p.add_argument("--dry-run", action="store_true", help="with --fetch: print tensors, bytes and source files, copy nothing")
     p.add_argument("--force", action="store_true", help="with --fetch: rewrite a destination that already holds this selection")
-    p.add_argument("--speculator", default=None, choices=["auto", "off", "mtp"]); p.add_argument("--decode-lanes", type=int, default=None, choices=[1, 2])
+    p.add_argument("--speculator", default=None, type=_speculator, choices=["auto", "off", "mtp"]); p.add_argument("--decode-lanes", type=int, default=None, choices=[1, 2])
     p.add_argument("--format", default=None); p.add_argument("--expert-format", default=None); p.add_argument("--kv-format", default=None)
     p.add_argument("--graph-reserve", default="", help="decode-graph arena per attention GPU: a prewarm file saved by a serving run "
                                                       "(its measured bytes) or a size such as 600MiB (default: 256 MiB per lane, unmeasured)")
@@ -598,7 +603,7 @@ def _build_parser() -> argparse.ArgumentParser:
     la.add_argument("--kv-pool-size", default="", help="KV pool target as a size per attention GPU (22.5GB, 90GiB) instead of --pool-tokens")
     la.add_argument("--max-context-tokens", type=int, default=None, help="longest context a request may reach")
     la.add_argument("--concurrency", type=int, default=None, help="requests decoded together")
-    la.add_argument("--speculator", default=None, choices=["auto", "off", "mtp"], help="speculative decoding to plan for and serve with")
+    la.add_argument("--speculator", default=None, type=_speculator, choices=["auto", "off", "mtp"], help="speculative decoding to plan for and serve with")
     la.add_argument("--decode-lanes", type=int, default=None, choices=[1, 2])
     la.add_argument("--host", default="127.0.0.1", help="address rank 0's HTTP server listens on")
     la.add_argument("--port", type=int, default=8000, help="port of rank 0's HTTP server")
