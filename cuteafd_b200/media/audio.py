@@ -1,8 +1,12 @@
-"""Audio input: WAV bytes -> mono 16 kHz samples -> log-mel frames for the audio tower.
+"""Audio input: WAV or FLAC bytes -> mono 16 kHz samples -> log-mel frames for the audio tower.
 
-Counterparts: the reference's audio decode (hound / claxon / nanomp3) and its cuFFT mel front end
-(native/shared/cuda/audio_runtime.cu, pcm_audio_runtime.cu); here WAV (PCM 8/16/24/32-bit, float) only, and the
-transform is ``torch.stft`` on whichever device the samples sit.
+WAV (PCM 8 / 16 / 24 / 32-bit) through the standard library; FLAC through the C++ host runtime (``csrc/rt/flac.cc``:
+every subframe type, both Rice codings, the stereo decorrelations, CRC-checked frames).  MP3 is refused by name.  A clip
+is at most 300 s, a request at most 4 clips and 600 s (``MAX_CLIP_SECONDS``, ``MAX_CLIPS``, ``MAX_REQUEST_SECONDS``).
+
+Counterparts: the reference's audio decode (hound / claxon / nanomp3; docs/multimodal-design.md:230 for the formats and
+the limits) and its cuFFT mel front end (native/shared/cuda/audio_runtime.cu, pcm_audio_runtime.cu); here the transform
+is ``torch.stft`` on whichever device the samples sit.
 """
 from __future__ import annotations
 
@@ -16,7 +20,7 @@ from .image import MediaError
 
 SAMPLE_RATE = 16000
 N_FFT, HOP, N_MELS = 400, 160, 128
-MAX_SECONDS = 600
+MAX_CLIP_SECONDS, MAX_REQUEST_SECONDS, MAX_CLIPS = 300, 600, 4
 
 
 def decode_wav(raw: bytes) -> tuple[torch.Tensor, int]:
@@ -27,8 +31,8 @@ def decode_wav(raw: bytes) -> tuple[torch.Tensor, int]:
             data = w.readframes(n)
     except (wave.Error, EOFError) as e:
         raise MediaError(f"cannot decode audio: {e}") from e
-    if n > rate * MAX_SECONDS:
-        raise MediaError("audio longer than ten minutes")
+    if n > rate * MAX_CLIP_SECONDS:
+        raise MediaError(f"audio clip longer than {MAX_CLIP_SECONDS} seconds")
     buf = bytearray(data)
     if width == 1:
         x = (torch.frombuffer(buf, dtype=torch.uint8).float() - 128.0) / 128.0
@@ -84,6 +88,53 @@ def log_mel(samples: torch.Tensor) -> torch.Tensor:
     return ((lm + 4.0) / 4.0).T.contiguous()
 
 
+_FLAC_ERRORS = {-1: "not a FLAC stream", -2: "no STREAMINFO block", -3: "truncated stream", -4: "bad frame header",
+                -5: "checksum mismatch", -6: "bad subframe", -7: "bad residual coding", -8: "more samples than declared",
+                -9: "sample size changes inside the stream"}
+
+
+def decode_flac(raw: bytes) -> tuple[torch.Tensor, int]:
+    """FLAC bytes -> (float32 samples [n] in [-1, 1], mono; sample rate)."""
+    import ctypes as C
+
+    from .._native import lib as native
+    L = native.rt_lib()
+    L.cafd_flac_info.argtypes = [C.c_char_p, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_uint64)]
+    L.cafd_flac_decode_mono.argtypes, L.cafd_flac_decode_mono.restype = [C.c_char_p, C.c_uint64, C.c_void_p, C.c_uint64], C.c_longlong
+    rate, ch, bits, total = C.c_uint32(), C.c_int(), C.c_int(), C.c_uint64()
+    rc = L.cafd_flac_info(raw, len(raw), rate, ch, bits, total)
+    if rc:
+        raise MediaError(f"cannot decode audio: {_FLAC_ERRORS.get(rc, rc)}")
+    limit = rate.value * MAX_CLIP_SECONDS
+    if total.value > limit:
+        raise MediaError(f"audio clip longer than {MAX_CLIP_SECONDS} seconds")
+    def fail(code):
+        if code == -8:                                       # more frames than the bound it was given
+            return MediaError(f"audio clip longer than {MAX_CLIP_SECONDS} seconds" if not total.value else
+                              "cannot decode audio: more samples than declared")
+        return MediaError(f"cannot decode audio: {_FLAC_ERRORS.get(code, code)}")
+    # a stream that does not declare its length is counted first (same bound), so the buffer is never a guess
+    n = total.value or L.cafd_flac_decode_mono(raw, len(raw), None, limit)
+    if n < 0:
+        raise fail(n)
+    out = torch.empty(max(n, 1), dtype=torch.float32)
+    n = L.cafd_flac_decode_mono(raw, len(raw), out.data_ptr(), n)
+    if n < 0:
+        raise fail(n)
+    return out[:n].contiguous(), rate.value
+
+
+def decode_audio(raw: bytes) -> tuple[torch.Tensor, int]:
+    """Container sniffed from the first bytes (the request's ``format`` field is a hint clients get wrong)."""
+    if raw[:4] == b"RIFF":
+        return decode_wav(raw)
+    if raw[:4] == b"fLaC":
+        return decode_flac(raw)
+    if raw[:3] == b"ID3" or (len(raw) > 1 and raw[0] == 0xFF and raw[1] & 0xE0 == 0xE0):
+        raise MediaError("mp3 audio is not decoded here: send wav or flac")
+    raise MediaError("cannot decode audio: neither a WAV nor a FLAC stream")
+
+
 def preprocess_audio(raw: bytes) -> torch.Tensor:
-    x, rate = decode_wav(raw)
+    x, rate = decode_audio(raw)
     return log_mel(resample(x, rate))

@@ -62,6 +62,7 @@ class MediaProcessor:
         self.start_id, self.end_id = start_id, end_id
         self.max_items = max_items
         self.encoded = 0
+        self._seconds: dict[bytes, float] = {}            # clip length by content key (for the per-request bound)
 
     # ---- one item ----------------------------------------------------------------------------------------
     def encode_image(self, raw: bytes) -> tuple[bytes, torch.Tensor]:
@@ -86,10 +87,22 @@ class MediaProcessor:
         hit = self.cache.get(key)
         if hit is not None:
             return key, hit
-        out = self.audio.forward(A.preprocess_audio(raw))
+        x, rate = A.decode_audio(raw)
+        self._seconds[key] = x.numel() / rate
+        out = self.audio.forward(A.log_mel(A.resample(x, rate)))
         self.cache.put(key, out)
         self.encoded += 1
         return key, out
+
+    def audio_seconds(self, raw: bytes) -> float:
+        """Length of a clip that has been encoded (remembered by content, so a cached clip is not decoded again)."""
+        key = I.content_key(raw, "audio")
+        if key not in self._seconds:
+            x, rate = A.decode_audio(raw)
+            self._seconds[key] = x.numel() / rate
+            while len(self._seconds) > 4096:
+                self._seconds.pop(next(iter(self._seconds)))
+        return self._seconds[key]
 
     # ---- a whole conversation ------------------------------------------------------------------------------
     def expand(self, segments: list, encode_text) -> tuple[list[int], list[MediaSpan]]:
@@ -97,6 +110,7 @@ class MediaProcessor:
         Returns the prompt ids (pseudo ids at media rows) and the spans."""
         ids: list[int] = []
         spans: list[MediaSpan] = []
+        clips, frames = 0, 0
         for seg in segments:
             if isinstance(seg, str):
                 if seg:
@@ -106,6 +120,12 @@ class MediaProcessor:
             if len(spans) >= self.max_items:
                 raise I.MediaError(f"more than {self.max_items} media items in one request")
             key, emb = self.encode_image(raw) if kind == "image" else self.encode_audio(raw)
+            if kind == "audio":                               # per-request bounds: clips, and their summed length
+                clips, frames = clips + 1, frames + self.audio_seconds(raw)
+                if clips > A.MAX_CLIPS:
+                    raise I.MediaError(f"more than {A.MAX_CLIPS} audio clips in one request")
+                if frames > A.MAX_REQUEST_SECONDS:
+                    raise I.MediaError(f"more than {A.MAX_REQUEST_SECONDS} seconds of audio in one request")
             if self.start_id is not None:
                 ids.append(self.start_id)
             spans.append(MediaSpan(len(ids), emb, key, kind))
