@@ -1,4 +1,4 @@
-"""``cuteafd`` command line: plan | serve | expertd | golden | bench | fabric | doctor | gateway | usage.
+"""``cuteafd`` command line: plan | serve | expertd | golden | bench | fabric | doctor | gateway | usage | mc.
 
     python -m cuteafd_b200.cli plan deepseek-v3 --layout --gpus 8
     python -m cuteafd_b200.cli plan /path/to/snapshot --layout --deployment
@@ -57,7 +57,7 @@ REFERENCE_KEYS = {
 # switches, its profiler wrappers, Spark / RDMA / container settings, graph-donor and padding policies.  They are skipped
 # with the notice, so a configuration written for it still starts.
 REFERENCE_ONLY = frozenset("""ATTENTION_PLACEMENT ATTENTION_PLAN_ROWS ATTENTION_PRECISION AUDIO_FEATURES_DIR AUDIO CHAT_TEMPLATE_FROM
-CONSOLE_ASSETS CONSOLE_TEXT CORE_VIEW CUDA_MODULE_LOADING DRAFT_CONTEXT_SLOTS DRAFT_CONTEXT_WINDOW DRAFT_KV_CACHE DRAFT_POLICY
+CONSOLE_ASSETS CONSOLE_TEXT CUDA_MODULE_LOADING DRAFT_CONTEXT_SLOTS DRAFT_CONTEXT_WINDOW DRAFT_KV_CACHE DRAFT_POLICY
 DRAFT_SEQUENCES ENABLE_BENCH ENGRAM_WARM EXLR8_MANIFEST EXLR8_PREFILL_ACTIVATIONS EXPERT_BACKEND EXPERT_INPUT
 EXPERT_PARTIAL_BF16_MAX_ROWS EXPERT_USAGE FAMILY_RESERVE FP8_PREFILL FP8_SCALES GATEWAY GPU_GRAPH_RESERVE_EXTRA_CAP
 GPU_GRAPH_RESERVE_EXTRA GPU_RESERVE GRAPH_DISABLE_LOW_MEM GRAPH_DONOR_ALWAYS GRAPH_DONOR_COLD_LAG GRAPH_NODE_PADDING GRAPH_TRACE
@@ -136,7 +136,7 @@ CONFIG_KEYS = {"MODEL", "EMBEDDING_PLACEMENT", "GPUS", "ATTENTION_RANKS", "EXPER
                "HOST_CACHE_GIB", "LOOP_ABORT_RUN", "LOOP_ABORT_COPIES", "LOOP_FAST_SPAN", "LOOP_FAST_COPIES", "BATCH_INVARIANT",
                "MAX_OUTPUT_TOKENS", "KV_DECODE_RESERVE_CHUNK", "PREFIX_CACHE_ENTRIES", "KV_POOL_SIZE",
                "KV_EARLY_TERMINATION_MIN_OUTPUT_TOKENS", "DRAFT_LENGTH", "DRAFT_SNAPSHOT", "PREWARM", "GRAPH_RESERVE", "PROFILE_DIR",
-               "SERVED_MODEL_ID", "DECODE_GRAPHS"}
+               "SERVED_MODEL_ID", "DECODE_GRAPHS", "CORE_VIEW"}
 
 
 def graph_reserve_of(value: str) -> tuple[int, str]:
@@ -151,8 +151,18 @@ def graph_reserve_of(value: str) -> tuple[int, str]:
     return _size(value), "user override"
 
 
+CORE_VIEWS = ("original", "k8-compact", "k6-compact", "fp8-compact")
+
+
+def _core_view(a: argparse.Namespace) -> None:
+    """``--core-view``: which dense-core variant of a multi-core repository this process opens (read by the loader)."""
+    if getattr(a, "core_view", None):
+        os.environ["CUTEAFD_CORE_VIEW"] = a.core_view
+
+
 def cmd_plan(a: argparse.Namespace) -> int:
     from .planner import plan as P
+    _core_view(a)
     if a.file_layout:
         # host layout: every host's shares (attention, experts:lo:hi, a role name) as one slice per host
         from .loader import slice as SL
@@ -207,6 +217,7 @@ def cmd_plan(a: argparse.Namespace) -> int:
 
 def cmd_serve(a: argparse.Namespace) -> int:
     from .serve.server import run_server
+    _core_view(a)
     if getattr(a, "batch_invariant", False):
         os.environ["CAFD_BATCH_INVARIANT"] = "1"         # read by the engines when they are built
     return run_server(a)
@@ -216,6 +227,7 @@ def cmd_launch(a: argparse.Namespace) -> int:
     """Plan, write the deployment document, start one ``serve`` per rank and supervise them."""
     from . import launch as LA
     from .planner import plan as P
+    _core_view(a)
     if a.deployment:
         with open(a.deployment) as f:
             spec = json.load(f)
@@ -246,6 +258,9 @@ def cmd_launch(a: argparse.Namespace) -> int:
             serve_args += [flag, str(val)]
     if a.speculator:
         serve_args += ["--speculator", a.speculator]
+    if getattr(a, "core_view", None):
+        serve_args += ["--core-view", a.core_view]
+    serve_args += serve_args_from_config(getattr(a, "file_config", {}), serve_args + list(a.serve_arg))
     serve_args += list(a.serve_arg)
     try:
         L = LA.build_launch(spec, a.run_dir, serve_args)
@@ -359,6 +374,26 @@ def cmd_doctor(a: argparse.Namespace) -> int:
     ok, lines = doctor()
     print("\n".join(lines))
     return 0 if ok else 1
+
+
+def cmd_mc(a: argparse.Namespace) -> int:
+    from .loader import mc, snapshot
+    try:
+        d = snapshot.resolve(a.directory)
+        if a.action == "validate":
+            print(json.dumps(mc.validate(d), indent=1))
+            return 0
+        m = mc.discover(d)
+        if m is None:
+            print(f"{d}: a plain checkpoint (no {mc.DISCOVERY}); its only core view is original")
+            return 0
+        for name, v in m.variants.items():
+            print(f"{name:<12} {v.core_bits:>2} bits  {len(v.core_tensors):>5} core tensors  index {v.index}  fingerprint {v.fingerprint[:16]}")
+        print(f"{'fp8-compact':<12}  8 bits  derived from original at load ({mc.FP8_RECIPE})")
+        return 0
+    except (mc.McError, OSError) as e:
+        print(f"mc: {e}", file=sys.stderr)
+        return 1
 
 
 def cmd_gateway(a: argparse.Namespace) -> int:
@@ -528,6 +563,7 @@ def _build_parser() -> argparse.ArgumentParser:
     p.add_argument("--pool-tokens", type=int, default=None); p.add_argument("--gpu-memory-cap", default="")
     p.add_argument("--kv-pool-size", default="", help="KV pool target as a size per attention GPU (22.5GB, 90GiB) instead of --pool-tokens")
     p.add_argument("--max-context-tokens", type=int, default=None); p.add_argument("--concurrency", type=int, default=None)
+    p.add_argument("--core-view", default=None, choices=CORE_VIEWS, help="dense-core variant of a multi-core checkpoint (cuteafd-mc.json): the source core, a stored 8- / 6-bit trellis core, or the source core encoded to E4M3 block-128 at load")
     p.add_argument("--file-layout", default="", help='JSON host-to-shares map, e.g. {"boxA": ["attention", "experts:0:64"]}: lists '
                                                      "(or with --fetch copies) what each host has to hold")
     p.add_argument("--host", default="", help="with --file-layout: this host only (--fetch then writes straight into its directory)")
@@ -546,6 +582,7 @@ def _build_parser() -> argparse.ArgumentParser:
     s.add_argument("--api-key", default=os.environ.get("CUTEAFD_API_KEY", ""))
     s.add_argument("--max-context-tokens", type=int, default=16384); s.add_argument("--concurrency", type=int, default=8)
     s.add_argument("--speculator", default="auto"); s.add_argument("--layers", type=int, default=0)
+    s.add_argument("--core-view", default=None, choices=CORE_VIEWS, help="dense-core variant of a multi-core checkpoint (cuteafd-mc.json): the source core, a stored 8- / 6-bit trellis core, or the source core encoded to E4M3 block-128 at load")
     s.add_argument("--served-model-id", default="", help="the model id /v1/models and replies carry (default: the checkpoint's name)")
     s.add_argument("--decode-graphs", default="on", choices=["on", "off"], help="off: every decode step runs eagerly (no CUDA graph bank)")
     s.add_argument("--draft-length", type=int, default=4, help="tokens the history / draft-model drafters propose per round (1..16)")
@@ -604,6 +641,7 @@ def _build_parser() -> argparse.ArgumentParser:
     la.add_argument("--max-context-tokens", type=int, default=None, help="longest context a request may reach")
     la.add_argument("--concurrency", type=int, default=None, help="requests decoded together")
     la.add_argument("--speculator", default=None, type=_speculator, choices=["auto", "off", "mtp"], help="speculative decoding to plan for and serve with")
+    la.add_argument("--core-view", default=None, choices=CORE_VIEWS, help="dense-core variant of a multi-core checkpoint (cuteafd-mc.json): the source core, a stored 8- / 6-bit trellis core, or the source core encoded to E4M3 block-128 at load")
     la.add_argument("--decode-lanes", type=int, default=None, choices=[1, 2])
     la.add_argument("--host", default="127.0.0.1", help="address rank 0's HTTP server listens on")
     la.add_argument("--port", type=int, default=8000, help="port of rank 0's HTTP server")
@@ -671,6 +709,11 @@ def _build_parser() -> argparse.ArgumentParser:
 
     sub.add_parser("doctor", help="environment checks").set_defaults(fn=cmd_doctor)
 
+    mcp = sub.add_parser("mc", help="multi-core checkpoint repositories (several dense-core variants behind one cuteafd-mc.json)")
+    mcp.add_argument("action", choices=["validate", "views"], help="validate: every view's hashes, fingerprint, shared inventory and "
+                                                                   "the cross-view rules; views: list the views")
+    mcp.add_argument("directory", help="the repository (a snapshot directory)")
+    mcp.set_defaults(fn=cmd_mc)
     gw = sub.add_parser("gateway", help="protocol gateway in front of an OpenAI-compatible upstream")
     gw.add_argument("--upstream", default="http://127.0.0.1:8000"); gw.add_argument("--host", default="127.0.0.1")
     gw.add_argument("--port", type=int, default=8080); gw.add_argument("--model-map", default="")
@@ -725,6 +768,33 @@ def _build_parser() -> argparse.ArgumentParser:
 
 # Configuration key -> flag destination, where the two are not the same word.
 _CONFIG_DEST = {"HTTP_QUEUE_DEPTH": "queue_depth", "HTTP_QUEUE_WAIT": "queue_wait"}
+
+
+def serve_args_from_config(file_config: dict[str, str], already: list[str]) -> list[str]:
+    """Configuration keys that are flags of ``serve`` but not of ``launch`` (MAX_OUTPUT_TOKENS, BATCH_INVARIANT,
+    DRAFT_LENGTH, PROFILE, ...) become arguments of every rank's serve command; a flag the launch line already hands to
+    the ranks (its own or a ``--serve-arg``) wins over the file."""
+    subs = next(x for x in build_parser()._actions if isinstance(x, argparse._SubParsersAction))
+    serve = {x.dest: x for x in subs.choices["serve"]._actions if x.option_strings}
+    launch = {x.dest for x in subs.choices["launch"]._actions if x.option_strings or x.dest == "model"}
+    given = {t.split("=", 1)[0] for t in already if t.startswith("--")}
+    out: list[str] = []
+    for key, raw in file_config.items():
+        dest = _CONFIG_DEST.get(key, key.lower())
+        act = serve.get(dest)
+        if act is None or dest in launch or key == "MODEL" or any(o in given for o in act.option_strings):
+            continue
+        flag = max(act.option_strings, key=len)
+        if isinstance(act, argparse._StoreTrueAction):
+            if raw.strip().lower() in ("1", "on", "true", "yes"):
+                out.append(flag)
+            continue
+        val = act.type(raw) if act.type is not None else raw
+        if act.choices is not None and val not in act.choices:
+            print(f"config: {key}={raw} is not one of {sorted(map(str, act.choices))}", file=sys.stderr)
+            raise SystemExit(2)
+        out += [flag, raw]
+    return out
 
 
 def apply_config(ap: argparse.ArgumentParser, a: argparse.Namespace, argv: list[str]) -> None:

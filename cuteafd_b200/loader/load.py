@@ -27,6 +27,7 @@ class OpenedSnapshot:
     operands: dict[str, formats.QuantOperand]
     family: families.Family | None
     model: families.FamilyModel | None
+    view: "object | None" = None              # loader.mc.Selected for a multi-core repository
 
     def hints(self) -> list[families.Hint]:
         if self.model is None:
@@ -41,14 +42,18 @@ class OpenedSnapshot:
         return out
 
 
-def open_snapshot(path: str) -> OpenedSnapshot:
+def open_snapshot(path: str, core_view: str | None = None) -> OpenedSnapshot:
+    """``core_view``: which dense-core variant of a multi-core repository to open (None: ``$CUTEAFD_CORE_VIEW``, default
+    ``original``); a plain checkpoint accepts ``original`` only."""
+    from .snapshot import core_view as select_view, view_weight_map
     path = resolve(path)
-    cfg, hf = read_config(path)
-    cat = Catalog(path, rename=families.canonical_name)
+    sel = select_view(path, core_view)
+    cfg, hf = read_config(path, core_view)
+    cat = Catalog(path, rename=families.canonical_name, weight_map=view_weight_map(path, core_view))
     ops = formats.detect_operands(cat)
     fam = families.detect(hf)
     model = fam.open(cfg, hf) if fam else None
-    return OpenedSnapshot(path, cfg, hf, cat, ops, fam, model)
+    return OpenedSnapshot(path, cfg, hf, cat, ops, fam, model, sel)
 
 
 def load_params(path: str, dtype: torch.dtype = torch.float32, device: str = "cpu",
@@ -155,7 +160,7 @@ FP8_TWIN_PROJECTIONS = {"wq_b": "self_attn.q_b_proj", "wo": "self_attn.o_proj", 
                         "s_up": "mlp.shared_experts.up_proj", "s_down": "mlp.shared_experts.down_proj"}
 
 
-def attach_fp8_twins(W, snap: "OpenedSnapshot | None" = None, device: torch.device | None = None) -> int:
+def attach_fp8_twins(W, snap: "OpenedSnapshot | None" = None, device: torch.device | None = None, only: set[str] | None = None) -> int:
     """E4M3 twins (values + 128x128 block scales) of the large backbone projections for decode-sized steps: q_b, the
     o projection and the shared expert.  From a snapshot that stores them as E4M3-block128 the twins are the stored
     bytes, untouched; otherwise (bf16 checkpoint, random init) they are encoded once from the bf16 weights.  Returns the
@@ -168,6 +173,8 @@ def attach_fp8_twins(W, snap: "OpenedSnapshot | None" = None, device: torch.devi
             w = getattr(L, attr, None)
             if w is None or not torch.is_tensor(w) or w.shape[0] % 128 or w.shape[1] % 128:
                 continue
+            if only is not None and f"model.layers.{i}.{tensor}.weight" not in only:
+                continue                                  # the fp8-compact view converts its declared core, nothing else
             op = snap.operands.get(f"model.layers.{i}.{tensor}") if snap is not None else None
             if op is not None and op.format == "fp8_block128" and op.block_scale is not None and (op.block_scale.rows, op.block_scale.cols) == (128, 128):
                 q = snap.catalog.read(op.weight).to(device or w.device).contiguous()
@@ -335,8 +342,13 @@ def load_engine(path: str, device: torch.device, num_pages: int, max_tokens: int
             W = MlaMoeWeights.from_params(cfg, params, device)
         if cfg.weight_format == "fp8_block128":
             attach_fp8_twins(W, snap, device)
+        elif snap.view is not None and snap.view.convert_fp8:
+            attach_fp8_twins(W, None, device, only=set(snap.view.view.core_tensors))      # encoded once, here, from bf16
         return cfg, MlaMoeEngine(cfg, W, LatentCache(cfg, num_pages, device), max_tokens=max_tokens, max_seqs=max_seqs)
     from ..models.gqa_moe import GqaMoeEngine, GqaMoeWeights, KvCache
+    if snap.view is not None and snap.view.convert_fp8:
+        raise ValueError("core view fp8-compact: only the MLA engine runs E4M3 backbone projections; serve this "
+                         "checkpoint with the original or a stored compact view")
     if stored != "bf16":
         _, params = load_params(path, dtype=torch.bfloat16, exclude=".mlp.experts.")
         W = GqaMoeWeights.from_params(cfg, params, device, with_experts=False)

@@ -69,13 +69,18 @@ def read_header(path: str) -> tuple[dict, int]:
 class Catalog:
     """Every tensor of a snapshot directory by name (headers only)."""
 
-    def __init__(self, directory: str, rename=None):
+    def __init__(self, directory: str, rename=None, weight_map: dict[str, str] | None = None):
         """``rename(name) -> name`` maps a checkpoint's tensor names onto the canonical ones the loaders use (families
-        whose files say ``block_sparse_moe.experts.3.w1`` for ``mlp.experts.3.gate_proj``); nothing is rewritten."""
+        whose files say ``block_sparse_moe.experts.3.w1`` for ``mlp.experts.3.gate_proj``); nothing is rewritten.
+        ``weight_map`` (tensor name -> shard, an index file's) restricts the catalog to one view of a repository that
+        holds several: only the named tensors belong, only the shards they sit in are opened, and a named tensor that
+        its shard does not hold is an error."""
         self.directory = directory
         self.entries: dict[str, TensorEntry] = {}
         self.metadata: dict[str, dict] = {}
         files = sorted(f for f in os.listdir(directory) if f.endswith(".safetensors"))
+        if weight_map is not None:
+            files = sorted(set(weight_map.values()))
         if not files:
             raise FileNotFoundError(f"no .safetensors files under {directory}")
         for fn in files:
@@ -83,12 +88,18 @@ class Catalog:
             header, base = read_header(path)
             self.metadata[fn] = header.pop("__metadata__", {})
             for name, info in header.items():
+                if weight_map is not None and weight_map.get(name) != fn:
+                    continue                                  # another view's bytes in a shared shard
                 b, e = info["data_offsets"]
                 if info["dtype"] not in DTYPES:
                     raise ValueError(f"{fn}:{name}: unsupported dtype {info['dtype']}")
                 name = rename(name) if rename else name
                 self.entries[name] = TensorEntry(name, info["dtype"], tuple(info["shape"]), path, base + b, base + e)
         self._maps: dict[str, mmap.mmap] = {}
+        if weight_map is not None:
+            lost = [n for n in weight_map if (rename(n) if rename else n) not in self.entries]
+            if lost:
+                raise ValueError(f"the index names {lost[0]} in {weight_map[lost[0]]}, which does not hold it")
 
     def __contains__(self, name: str) -> bool:
         return name in self.entries

@@ -200,8 +200,26 @@ def resolve(path: str) -> str:
     raise FileNotFoundError(f"{path}: no config.json and no snapshots/ directory")
 
 
-def read_config(path: str) -> tuple[ModelConfig, dict]:
-    with open(os.path.join(resolve(path), "config.json")) as f:
+def core_view(path: str, view: str | None = None):
+    """The verified core view of a multi-core repository (``loader/mc.py``), or None for a plain checkpoint served as
+    it is.  ``view`` None reads ``$CUTEAFD_CORE_VIEW`` (what ``serve --core-view`` sets), default ``original``."""
+    from . import mc
+    view = view or os.environ.get("CUTEAFD_CORE_VIEW", "") or "original"
+    return mc.select(mc.discover(resolve(path)), view)
+
+
+def view_weight_map(path: str, view: str | None = None) -> dict[str, str] | None:
+    """tensor name -> shard of the selected view; None when the directory is a plain checkpoint (every shard belongs)."""
+    sel = core_view(path, view)
+    if sel is None:
+        return None
+    with open(os.path.join(resolve(path), sel.view.index)) as f:
+        return json.load(f)["weight_map"]
+
+
+def read_config(path: str, view: str | None = None) -> tuple[ModelConfig, dict]:
+    sel = core_view(path, view)
+    with open(os.path.join(resolve(path), sel.view.config if sel is not None else "config.json")) as f:
         d = json.load(f)
     return from_hf_config(d), d
 

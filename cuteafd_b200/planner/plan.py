@@ -32,6 +32,7 @@ class PlanReport:
     placement: solver.Placement | None = None
     request: solver.PlacementRequest | None = None
     role_files: dict[str, list[str]] = field(default_factory=dict)
+    core_view: dict | None = None    # multi-core repositories: core-view, core-view-fingerprint, core-fp8-recipe
 
     @property
     def ready(self) -> bool:
@@ -44,6 +45,7 @@ def plan(model: str, *, layout: bool = False, fmt: str | None = None, **req_kw) 
     role_files: dict[str, set] = {}
     hints: list[Hint] = []
     stored = 0
+    view = None
     if model in PRESETS and not os.path.exists(model):
         cfg = PRESETS[model]()
         if fmt:
@@ -61,13 +63,14 @@ def plan(model: str, *, layout: bool = False, fmt: str | None = None, **req_kw) 
         if fmt:
             cfg = cfg.replace(weight_format=fmt)
         hints = snap.hints()
+        view = snap.view.settings() if snap.view is not None else None
         for op in snap.operands.values():
             role = snap.model.classify(op.weight)[0] if snap.model else "other"
             formats_by_role.setdefault(role, Counter())[op.format] += 1
             stored += op.stored_bytes(snap.catalog)
             role_files.setdefault(role, set()).add(os.path.basename(snap.catalog.entries[op.weight].file))
     rep = PlanReport(cfg.name, source, fam.id if fam else None, cfg, {r: dict(c) for r, c in formats_by_role.items()},
-                     stored, hints, role_files={r: sorted(f) for r, f in role_files.items()})
+                     stored, hints, role_files={r: sorted(f) for r, f in role_files.items()}, core_view=view)
     if layout:
         pool_bytes = req_kw.pop("kv_pool_bytes", None)
         if pool_bytes and req_kw.get("pool_tokens_target") is None:
@@ -97,6 +100,9 @@ def render(rep: PlanReport) -> str:
          f"stored     {_gib(rep.stored_bytes)}   parameters {c.total_params()/1e9:.1f} B"]
     for role, f in sorted(rep.formats.items()):
         L.append(f"  {role:<15} " + ", ".join(f"{k} x{v}" for k, v in sorted(f.items())))
+    if rep.core_view:
+        L.append(f"core view  {rep.core_view['core-view']} (fingerprint {rep.core_view['core-view-fingerprint'][:16]})"
+                 + (f", encoded at load: {rep.core_view['core-fp8-recipe']}" if rep.core_view.get("core-fp8-recipe") else ""))
     if rep.hints:
         L.append(f"hints      {len(rep.hints)} operand(s) cannot be served as stored:")
         for h in rep.hints[:20]:
@@ -134,7 +140,8 @@ def to_json(rep: PlanReport) -> dict:
     return {"model": rep.model, "source": rep.source, "family": rep.family, "config": dataclasses.asdict(rep.cfg),
             "formats": rep.formats, "stored_bytes": rep.stored_bytes,
             "hints": [{"what": h.what, "how": h.how} for h in rep.hints],
-            "placement": rep.placement.to_json() if rep.placement else None, "ready": rep.ready}
+            "placement": rep.placement.to_json() if rep.placement else None, "ready": rep.ready,
+            "core_view": rep.core_view}
 
 
 def deployment(rep: PlanReport, master_addr: str = "127.0.0.1", master_port: int = 29500) -> dict:

@@ -187,3 +187,21 @@ def test_example_configurations_plan_and_dry_run(name, world, engine, tmp_path, 
     assert spec["world_size"] == world and spec["engine"] == engine
     out = capsys.readouterr().out
     assert out.count("cuteafd_b200.cli serve") == world
+
+
+def test_serve_only_configuration_keys_reach_every_rank(tmp_path, capsys):
+    """A key that is a flag of ``serve`` but not of ``launch`` becomes an argument of the ranks' serve commands; a
+    --serve-arg on the launch line wins over the file; switches appear only when on."""
+    from cuteafd_b200.cli import main, serve_args_from_config
+    conf = tmp_path / "c.config"
+    conf.write_text("MODEL=qwen3-30b-a3b\nGPUS=1\nMAX_OUTPUT_TOKENS=40\nBATCH_INVARIANT=1\nDRAFT_LENGTH=3\nDECODE_GRAPHS=off\nPORT=8123\n")
+    assert main(["--config", str(conf), "launch", "--dry-run", "--run-dir", str(tmp_path / "run")]) == 0
+    line = [l for l in capsys.readouterr().out.splitlines() if " serve " in l][0]
+    for want in ("--max-output-tokens 40", "--batch-invariant", "--draft-length 3", "--decode-graphs off", "--port 8123"):
+        assert want in line, (want, line)
+    assert main(["--config", str(conf), "launch", "--dry-run", "--run-dir", str(tmp_path / "run"), "--serve-arg=--draft-length", "--serve-arg=5"]) == 0
+    line = [l for l in capsys.readouterr().out.splitlines() if " serve " in l][0]
+    assert "--draft-length 5" in line and "--draft-length 3" not in line
+    assert serve_args_from_config({"BATCH_INVARIANT": "0", "MODEL": "x", "GPUS": "2"}, []) == []
+    with pytest.raises(SystemExit):
+        serve_args_from_config({"DECODE_GRAPHS": "sometimes"}, [])
