@@ -285,3 +285,47 @@ def test_clip_and_request_bounds():
         mp.expand([("audio", c) for c in minutes], lambda s: [1])
     with pytest.raises(MediaError, match="more than 600 seconds"):                               # cached clips still count
         mp.expand([("audio", c) for c in minutes], lambda s: [1])
+
+
+def test_damaged_streams_never_read_or_write_out_of_bounds():
+    """Request audio is untrusted input to native code: thousands of bit flips, byte splices and truncations of valid
+    streams must each come back as a count within the caller's bound or as an error code (the buffer's guard words stay
+    intact), never as a crash."""
+    import ctypes as C
+    import random
+
+    from cuteafd_b200._native import lib as native
+    L = native.rt_lib()
+    L.cafd_flac_decode.argtypes, L.cafd_flac_decode.restype = [C.c_char_p, C.c_uint64, C.c_void_p, C.c_uint64], C.c_longlong
+    L.cafd_flac_decode_mono.argtypes, L.cafd_flac_decode_mono.restype = [C.c_char_p, C.c_uint64, C.c_void_p, C.c_uint64], C.c_longlong
+    a, b = signal(2304, 16, 11), signal(2304, 16, 12)
+    lpc = {"kind": "lpc", "coefs": [1500, -700, 90], "shift": 10, "precision": 12, "porder": 2, "k": 8}
+    seeds = [encode([a, b], 44100, 16, [(1152, "mid_side", [dict(lpc), dict(lpc, rice2=True, escape=2)], 3),
+                                         (1152, "left_side", [{"kind": "fixed", "order": 3, "k": 7, "porder": 3}, {"kind": "verbatim"}], 3)])[0],
+             encode([a[:700]], 8000, 16, [(700, None, [{"kind": "fixed", "order": 4, "k": 6, "wasted": 0}], 7)])[0],
+             EXAMPLE_1, b"fLaC\x80\x00\x00\x22" + EXAMPLE_2_INFO + EXAMPLE_2_FRAMES]
+    cap, guard = 2304, 0x5A5A5A5A
+    ints = torch.full((cap * 2 + 64,), guard, dtype=torch.int32)
+    floats = torch.full((cap + 64,), 7.25, dtype=torch.float32)
+    rng = random.Random(5)
+    outcomes = {"ok": 0, "error": 0}
+    for trial in range(4000):
+        d = bytearray(rng.choice(seeds))
+        for _ in range(rng.randint(1, 4)):
+            kind = rng.random()
+            at = rng.randrange(4, len(d))
+            if kind < 0.6:
+                d[at] ^= 1 << rng.randrange(8)
+            elif kind < 0.8:
+                d[at:at + rng.randint(1, 8)] = bytes(rng.randrange(256) for _ in range(rng.randint(0, 8)))
+            else:
+                del d[at:]
+            if len(d) < 8:
+                break
+        raw = bytes(d)
+        n = L.cafd_flac_decode(raw, len(raw), ints.data_ptr(), cap)
+        m = L.cafd_flac_decode_mono(raw, len(raw), floats.data_ptr(), cap)
+        assert n == m and n <= cap
+        outcomes["ok" if n >= 0 else "error"] += 1
+        assert ints[cap * 2:].eq(guard).all() and floats[cap:].eq(7.25).all()
+    assert outcomes["error"] > 3000 and outcomes["ok"] > 0, outcomes          # CRCs catch nearly everything; metadata hits pass
