@@ -583,6 +583,8 @@ def _build_parser() -> argparse.ArgumentParser:
     s.add_argument("--max-context-tokens", type=int, default=16384); s.add_argument("--concurrency", type=int, default=8)
     s.add_argument("--speculator", default="auto"); s.add_argument("--layers", type=int, default=0)
     s.add_argument("--core-view", default=None, choices=CORE_VIEWS, help="dense-core variant of a multi-core checkpoint (cuteafd-mc.json): the source core, a stored 8- / 6-bit trellis core, or the source core encoded to E4M3 block-128 at load")
+    s.add_argument("--expert-workers", default="", help="host:port:first:end,... routed experts served by expertd --tcp-port workers "
+                                                        "(host reference backend; the ranges must partition the experts)")
     s.add_argument("--served-model-id", default="", help="the model id /v1/models and replies carry (default: the checkpoint's name)")
     s.add_argument("--decode-graphs", default="on", choices=["on", "off"], help="off: every decode step runs eagerly (no CUDA graph bank)")
     s.add_argument("--draft-length", type=int, default=4, help="tokens the history / draft-model drafters propose per round (1..16)")

@@ -304,6 +304,8 @@ class ExpertLink:
         self.latch = HealthLatch()
         self.plan, self.seq = plan, 0
         self.pace_us: list[int] = []
+        self.rtt_us: list[int] = []              # whole round trips of the same calls (send .. reply parsed)
+        self.calls = self.sent_bytes = self.recv_bytes = 0
         self.lock = threading.Lock()
         try:
             self.sock = socket.create_connection((host, port), timeout=timeout)
@@ -325,7 +327,9 @@ class ExpertLink:
             try:
                 if self.faults is not None:
                     self.faults.hit("WIRE_SEND")
-                self.sock.sendall(req.pack())
+                t0 = time.perf_counter()
+                frame = req.pack()
+                self.sock.sendall(frame)
                 rsp, nbytes, crc = parse_response_header(recv_exact(self.sock, HEADER))
                 rsp.payload = recv_exact(self.sock, nbytes) if nbytes else b""
                 if zlib.crc32(rsp.payload) != crc:
@@ -340,7 +344,9 @@ class ExpertLink:
                 raise HealthError(f"exchange unavailable: {self.latch.reason}") from e
             if rsp.kind == MOE:
                 self.pace_us.append(rsp.compute_us)
-                del self.pace_us[:-256]
+                self.rtt_us.append(int((time.perf_counter() - t0) * 1e6))
+                del self.pace_us[:-256], self.rtt_us[:-256]
+                self.calls, self.sent_bytes, self.recv_bytes = self.calls + 1, self.sent_bytes + len(frame), self.recv_bytes + HEADER + nbytes
             return rsp
 
     def close(self) -> None:
@@ -355,11 +361,13 @@ class ExpertLink:
 class RemoteExperts:
     """``moe_fn`` for the decoders: sends every worker its routes (in parallel) and assembles [T, k, hidden] fp32."""
 
-    def __init__(self, workers: list[tuple[str, int, int, int]], plan: bytes, timeout: float = 30.0):
-        """workers: (host, port, first expert, end expert)."""
+    def __init__(self, workers: list[tuple[str, int, int, int]], plan, timeout: float = 30.0):
+        """workers: (host, port, first expert, end expert).  ``plan``: one hash for every worker, or
+        ``plan(lo, hi) -> hash`` when each worker's hash covers its own range (what ``expertd --tcp-port`` announces)."""
         self.ranges = [(lo, hi) for _, _, lo, hi in workers]
-        self.links = [ExpertLink(h, p, plan, timeout) for h, p, _, _ in workers]
-        self.plan = plan
+        self.plans = [plan(lo, hi) if callable(plan) else plan for _, _, lo, hi in workers]
+        self.links = [ExpertLink(h, p, pl, timeout) for (h, p, _, _), pl in zip(workers, self.plans)]
+        self.plan = self.plans[0] if self.plans else b""
 
     def __call__(self, layer: int, x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         T, k = idx.shape
@@ -368,7 +376,7 @@ class RemoteExperts:
 
         def one(link: ExpertLink, lo: int, hi: int) -> None:
             try:
-                req, tok, slot = encode_moe(0, layer, x, idx, w, lo, hi, self.plan)
+                req, tok, slot = encode_moe(0, layer, x, idx, w, lo, hi, link.plan)
                 if req.routes == 0:
                     return
                 rsp = link.call(req)
@@ -384,6 +392,21 @@ class RemoteExperts:
         if errors:
             raise errors[0]
         return parts
+
+    def timing(self) -> list[dict]:
+        """Per worker, over its last 256 expert calls: the worker's own compute time (from the reply header), the round
+        trip seen here, and their difference (serialisation + the wire + the worker's queue)."""
+        def stats(v):
+            if not v:
+                return None
+            s = sorted(v)
+            return {"mean_us": round(sum(s) / len(s), 1), "p50_us": s[len(s) // 2], "p99_us": s[min(len(s) - 1, int(len(s) * 0.99))]}
+        out = []
+        for l, (lo, hi) in zip(self.links, self.ranges):
+            wire_us = [max(0, r - c) for r, c in zip(l.rtt_us, l.pace_us)]
+            out.append({"experts": [lo, hi], "ok": l.latch.ok, "calls": l.calls, "sent_bytes": l.sent_bytes, "recv_bytes": l.recv_bytes,
+                        "compute": stats(l.pace_us), "round_trip": stats(l.rtt_us), "transport": stats(wire_us)})
+        return out
 
     def close(self) -> None:
         for l in self.links:

@@ -485,7 +485,23 @@ def build_state(args) -> ServerState:
             cfg = PRESETS.get(args.preset, tiny_moe)() if args.preset else tiny_moe()
             params = init_weights(cfg, seed=0)
         be = OracleBackend(cfg, params)
+        if getattr(args, "expert_workers", ""):
+            # routed experts on workers over TCP (``expertd --tcp-port``): each worker's plan hash covers its own range
+            from ..parallel import wire
+            workers = []
+            for item in args.expert_workers.split(","):
+                host, port, lo, hi = item.rsplit(":", 3)
+                workers.append((host, int(port), int(lo), int(hi)))
+            covered = sorted((lo, hi) for _, _, lo, hi in workers)
+            if [lo for lo, _ in covered] != [0] + [hi for _, hi in covered[:-1]] or covered[-1][1] != cfg.num_experts:
+                raise SystemExit(f"--expert-workers must partition the experts 0..{cfg.num_experts}; got {covered}")
+            be.remote_experts = wire.RemoteExperts(
+                workers, lambda lo, hi: wire.plan_hash({"model": cfg.name, "experts": cfg.num_experts, "range": [lo, hi]}))
+            be.model.moe_fn = be.remote_experts
     else:
+        if getattr(args, "expert_workers", ""):
+            raise SystemExit("--expert-workers is wired to the host reference backend (--fake-engine); the CUDA engines "
+                             "reach their expert ranks over NVLink (launch --expert-ranks N)")
         from ..runtime.backends import EngineBackend
         dev = torch.device("cuda:0")
         pages_per_seq = args.max_context_tokens // 64 + 2
@@ -597,6 +613,8 @@ def build_state(args) -> ServerState:
     hooks = FaultHooks()                      # refuses a configured fault without CUTEAFD_DEV_FAULT_HOOKS=1
     if hooks.plan:
         sched.faults = hooks
+        for link in getattr(getattr(sched.be, "remote_experts", None), "links", []):
+            link.faults = hooks
         hooks.arm()                           # the engine is built and prewarmed: visits count from here
         print(f"[serve] development fault hooks armed: {hooks.plan}", flush=True)
     prof = getattr(args, "profile", "") or os.environ.get("PROFILE", "")

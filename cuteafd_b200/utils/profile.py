@@ -8,6 +8,10 @@ asked for.
 * ``census``         appends the decode graph bank's inventory (captured geometries, replays, eager steps) and the
                      scheduler's verify-row histogram to ``<dir>/census.jsonl`` every ``period`` rounds.
 * ``step-timing``    wall time of every scheduler step by kind (prefill / decode / idle) as running totals.
+* ``transport-timing`` / ``expert-timing``  for expert workers reached over TCP (``serve --expert-workers``): per worker,
+                     the round trip, the worker's own compute time from its reply header, and their difference
+                     (``transport``); ``expert-timing`` adds the slowest worker's share over the mean (imbalance).
+                     Both read what the links already record.
 
 The modes only read counters the serve loop already keeps, or time host calls; none adds a device synchronisation.
 Device-side profiles (``ncu``) are taken on small standalone cases of a kernel, never by wrapping a server.
@@ -21,7 +25,7 @@ import json
 import os
 import time
 
-MODES = ("draft-timing", "expert-routes", "census", "step-timing")
+MODES = ("draft-timing", "expert-routes", "census", "step-timing", "transport-timing", "expert-timing")
 
 
 def parse_modes(text: str) -> list[str]:
@@ -81,6 +85,7 @@ class Profile:
                 return did
             sched.step = step
         sched.profile = self
+        self.remote = getattr(sched.be, "remote_experts", None)      # TCP expert workers, when the backend uses them
         return self
 
     def flush(self, sched) -> None:
@@ -105,6 +110,15 @@ class Profile:
             dec = self.steps["decode"][1]
             if dec:
                 out["draft"]["share_of_decode"] = round(sum(s for _, s in self.draft.values()) / dec, 4)
+        remote = getattr(self, "remote", None)
+        if remote is not None and ("transport-timing" in self.modes or "expert-timing" in self.modes):
+            rows = remote.timing()
+            if "transport-timing" in self.modes:
+                out["transport"] = [{k: r[k] for k in ("experts", "ok", "calls", "sent_bytes", "recv_bytes", "round_trip", "transport")} for r in rows]
+            if "expert-timing" in self.modes:
+                means = [r["compute"]["mean_us"] for r in rows if r["compute"]]
+                out["experts"] = {"workers": [{k: r[k] for k in ("experts", "calls", "compute")} for r in rows],
+                                  "imbalance": round(max(means) / (sum(means) / len(means)), 3) if means and sum(means) else None}
         if "step-timing" in self.modes or "draft-timing" in self.modes:
             out["steps"] = {k: {"count": c, "seconds": round(s, 6)} for k, (c, s) in self.steps.items()}
         return out

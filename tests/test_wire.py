@@ -173,3 +173,54 @@ def test_injected_wire_fault_trips_the_latch_before_anything_is_sent(split):
     assert not link.latch.ok and link.sock is None
     with pytest.raises(HealthError, match="injected fault"):           # terminal, like any other link failure
         link.call(wire.Request(wire.PING))
+
+
+def test_serve_with_tcp_expert_workers(tmp_path, monkeypatch):
+    """``serve --expert-workers`` on the host backend: replies equal the whole model's token for token, the profile
+    modes report per-worker transport and compute time, an injected wire fault ends the step with a worker error."""
+    from cuteafd_b200.cli import build_parser
+    from cuteafd_b200.loader import snapshot
+    from cuteafd_b200.runtime.scheduler import FAIL_WORKER, Request, collect
+    from cuteafd_b200.serve.server import build_state
+    cfg = tiny_moe()
+    src = snapshot.write_random_snapshot(cfg, str(tmp_path / "s"), fmt="bf16", seed=7)
+    from cuteafd_b200.loader import load
+    _, params = load.load_params(src)
+    dec = RefDecoder(cfg, params)
+    half = cfg.num_experts // 2
+    servers = []
+    for lo, hi in ((0, half), (half, cfg.num_experts)):
+        plan = wire.plan_hash({"model": cfg.name, "experts": cfg.num_experts, "range": [lo, hi]})
+        servers.append(wire.ExpertServer(wire.reference_compute(lambda layer, lo=lo, hi=hi: dec.expert_stack(layer, lo, hi), lo), plan).start())
+    spec = ",".join(f"127.0.0.1:{s.port}:{lo}:{hi}" for s, (lo, hi) in zip(servers, ((0, half), (half, cfg.num_experts))))
+
+    def run(state, prompt):
+        r = Request(prompt, max_tokens=8, speculation=False)
+        state.sched.submit(r)
+        for _ in range(500):
+            if not state.sched.step() and not state.sched.decoding and not state.sched.prefilling and not state.sched.pending and state.sched.waiting.empty():
+                break
+        return collect(r, timeout=1.0)
+    try:
+        base = ["serve", "--fake-engine", "--snapshot", src]
+        whole = build_state(build_parser().parse_args(base))
+        split = build_state(build_parser().parse_args(base + ["--expert-workers", spec, "--profile", "transport-timing,expert-timing"]))
+        prompt = [3, 9, 27, 81, 5, 15]
+        a, b = run(whole, prompt), run(split, prompt)
+        assert a["tokens"] == b["tokens"] and b.get("error") is None
+        rep = split.sched.profile.report()
+        assert [w["experts"] for w in rep["transport"]] == [[0, half], [half, cfg.num_experts]]
+        assert all(w["calls"] > 0 and w["round_trip"]["mean_us"] >= w["transport"]["mean_us"] >= 0 and w["sent_bytes"] > 0 for w in rep["transport"])
+        assert rep["experts"]["imbalance"] >= 1.0 and all(w["compute"]["p99_us"] >= w["compute"]["p50_us"] for w in rep["experts"]["workers"])
+        with pytest.raises(SystemExit, match="partition"):
+            build_state(build_parser().parse_args(base + ["--expert-workers", f"127.0.0.1:{servers[0].port}:0:{half}"]))
+        # the development wire fault: first expert call after readiness fails on the host; the latch is terminal
+        monkeypatch.setenv("CUTEAFD_DEV_FAULT_HOOKS", "1")
+        monkeypatch.setenv("CUTEAFD_DIAG_FAULT_WIRE_SEND", "1")
+        faulty = build_state(build_parser().parse_args(base + ["--expert-workers", spec]))
+        out = run(faulty, prompt)
+        assert out["error"] and out["error"][0] == FAIL_WORKER and "injected fault at WIRE_SEND" in out["error"][1]
+        assert not all(l.latch.ok for l in faulty.sched.be.remote_experts.links)
+    finally:
+        for s in servers:
+            s.stop()
