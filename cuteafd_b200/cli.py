@@ -1,4 +1,4 @@
-"""``cuteafd`` command line: plan | serve | expertd | golden | bench | fabric | doctor | gateway | usage | mc.
+"""``cuteafd`` command line: plan | serve | expertd | golden | bench | fabric | doctor | gateway | usage | mc | prewarm.
 
     python -m cuteafd_b200.cli plan deepseek-v3 --layout --gpus 8
     python -m cuteafd_b200.cli plan /path/to/snapshot --layout --deployment
@@ -396,6 +396,23 @@ def cmd_mc(a: argparse.Namespace) -> int:
         return 1
 
 
+def cmd_prewarm(a: argparse.Namespace) -> int:
+    from .utils.trace import prewarm_from_trace
+    try:
+        doc = prewarm_from_trace(a.trace, a.top)
+    except OSError as e:
+        print(f"prewarm: {e}", file=sys.stderr)
+        return 1
+    text = json.dumps(doc, indent=1)
+    if a.out:
+        with open(a.out, "w") as f:
+            f.write(text + "\n")
+        print(f"{len(doc['geometries'])} geometries from {doc['rounds']} rounds -> {a.out}")
+    else:
+        print(text)
+    return 0
+
+
 def cmd_gateway(a: argparse.Namespace) -> int:
     from .serve.gateway import run_gateway
     return run_gateway(a)
@@ -716,6 +733,11 @@ def _build_parser() -> argparse.ArgumentParser:
                                                                    "the cross-view rules; views: list the views")
     mcp.add_argument("directory", help="the repository (a snapshot directory)")
     mcp.set_defaults(fn=cmd_mc)
+    pw = sub.add_parser("prewarm", help="a decode-graph prewarm list from the speculation trace of an earlier run")
+    pw.add_argument("trace", help="JSONL written by serve --speculation-trace")
+    pw.add_argument("--out", default="", help="file to write (default: standard output); give it to serve --prewarm")
+    pw.add_argument("--top", type=int, default=32, help="how many of the most frequent step geometries to keep")
+    pw.set_defaults(fn=cmd_prewarm)
     gw = sub.add_parser("gateway", help="protocol gateway in front of an OpenAI-compatible upstream")
     gw.add_argument("--upstream", default="http://127.0.0.1:8000"); gw.add_argument("--host", default="127.0.0.1")
     gw.add_argument("--port", type=int, default=8080); gw.add_argument("--model-map", default="")

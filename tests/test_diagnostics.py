@@ -50,3 +50,22 @@ def test_host_heap_monitor_warns_once():
     assert m.sample()["resident_bytes"] == 1 << 30 and not msgs
     m.sample(); m.sample()
     assert len(msgs) == 1 and m.peak == 4 << 30
+
+
+def test_prewarm_list_from_a_speculation_trace(tmp_path, capsys):
+    """Round geometries counted from the trace, most frequent first, in the shape ``serve --prewarm`` reads; a line cut
+    short at the end of the file is skipped."""
+    import json
+
+    from cuteafd_b200.cli import main
+    from cuteafd_b200.utils.trace import prewarm_from_trace
+    p = tmp_path / "t.jsonl"
+    rounds = ([{"round": i, "requests": [1, 2], "rows": 2, "kept": [0, 0]} for i in range(5)]
+              + [{"round": 9, "requests": [1, 2], "rows": 7, "kept": [4, 1]}] * 3
+              + [{"round": 10, "requests": [4], "rows": 1, "kept": [0]}] + [{"other": 1}])
+    p.write_text("\n".join(json.dumps(r) for r in rounds) + '\n{"round": 11, "requests": [1')
+    doc = prewarm_from_trace(str(p), top=2)
+    assert doc["geometries"] == [[2, 2, 1], [2, 7, 5]] and doc["seen"] == {"2,2,1": 5, "2,7,5": 3, "1,1,1": 1} and doc["rounds"] == 9
+    assert main(["prewarm", str(p), "--out", str(tmp_path / "pw.json")]) == 0
+    assert json.load(open(tmp_path / "pw.json"))["geometries"][0] == [2, 2, 1] and "3 geometries from 9 rounds" in capsys.readouterr().out
+    assert main(["prewarm", str(tmp_path / "missing.jsonl")]) == 1
