@@ -64,7 +64,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str, mode: str, snap_dir:
         a = h.replica
         g = torch.Generator().manual_seed(1)
         prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g) for n in (200, 200, 77)]
-        # round 1: every replica prefills a 200-token prompt of its own; round 2: replica 0 alone prefills 77 tokens
+        # first pass: every replica prefills a 200-token prompt of its own; second pass: replica 0 alone prefills 77 tokens
         # (the MTP mode keeps to one prompt: the depth reads the hidden states the last forward left behind)
         mine = [prompts[a]] + ([prompts[2]] if a == 0 and mode != "mtp" else [])
         seqs, last, kvs = [], [], []
