@@ -329,3 +329,34 @@ def test_damaged_streams_never_read_or_write_out_of_bounds():
         outcomes["ok" if n >= 0 else "error"] += 1
         assert ints[cap * 2:].eq(guard).all() and floats[cap:].eq(7.25).all()
     assert outcomes["error"] > 3000 and outcomes["ok"] > 0, outcomes          # CRCs catch nearly everything; metadata hits pass
+
+
+def test_a_flac_clip_through_the_chat_api_matches_the_same_clip_as_wav():
+    """``input_audio`` with FLAC bytes reaches the audio tower as the same samples a WAV of the clip gives: same
+    prompt length, same reply."""
+    import base64
+
+    from cuteafd_b200 import tiny_moe
+    from cuteafd_b200.media.processor import MediaProcessor
+    from cuteafd_b200.media.towers import AudioTower, AudioTowerConfig
+    from cuteafd_b200.serve import api, tokenizer
+    cfg = tiny_moe()
+    tok = tokenizer.ByteTokenizer(cfg.vocab_size)
+    ac = AudioTowerConfig(width=64, depth=1, heads=4, mlp=128, out_hidden=cfg.hidden)
+    mp = MediaProcessor(cfg.vocab_size, cfg.hidden, None, AudioTower(ac, AudioTower.random_weights(ac)))
+    L = signal(8000, 16, 21)
+    flac, _ = encode([L], 8000, 16, [(4000, None, [{"kind": "fixed", "order": 2, "k": 9}], 7)] * 2)
+    pcm = io.BytesIO()
+    with wave.open(pcm, "wb") as w:
+        w.setnchannels(1); w.setsampwidth(2); w.setframerate(8000)
+        w.writeframes(struct.pack(f"<{len(L)}h", *L))
+
+    def request(data, fmt):
+        body = {"max_tokens": 2, "messages": [{"role": "user", "content": [
+            {"type": "text", "text": "transcribe"}, {"type": "input_audio", "input_audio": {"data": base64.b64encode(data).decode(), "format": fmt}}]}]}
+        return api.build_request(body, tok, cfg.vocab_size, media=mp)
+    a, b = request(flac, "flac"), request(pcm.getvalue(), "wav")
+    assert len(a.prompt) == len(b.prompt) and len(a.media) == len(b.media) == 1
+    assert torch.equal(a.media[0].embeds, b.media[0].embeds) and a.media[0].key != b.media[0].key      # same rows, cached by content
+    with pytest.raises(api.BadRequest, match="mp3"):
+        request(b"ID3\x04" + bytes(200), "mp3")
